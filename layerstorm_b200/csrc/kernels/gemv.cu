@@ -1,0 +1,120 @@
+// Dense weight-streaming GEMV / skinny GEMM for decode-shaped work (M <= 4 rows per
+// pass): out[m][n] = sum_k x[m][k] * W[n][k].  One warp owns two weight rows, so every
+// weight byte is read exactly once per pass and the kernel runs at HBM speed.
+// Replaces the reference's CUDA-core GEMV family (src/compute/kernels/sm120/gemm/bf16_gemm.cu:41-156,
+// wq_gemm.cu:84-158) with one templated kernel over four weight formats.
+#include "gemv_core.cuh"
+
+namespace lsb {
+
+struct MatBf16 {
+    const bf16* w; int ldw;
+    __device__ __forceinline__ WRowBf16 row(int n) const { return WRowBf16{w + (size_t)n * ldw}; }
+};
+struct MatF32 {
+    const float* w; int ldw;
+    __device__ __forceinline__ WRowF32 row(int n) const { return WRowF32{w + (size_t)n * ldw}; }
+};
+struct MatFp8B {
+    const uint8_t* w; int ldw; const float* scales; int kblocks;
+    __device__ __forceinline__ WRowFp8B row(int n) const {
+        return WRowFp8B{w + (size_t)n * ldw, scales + (size_t)(n >> 7) * kblocks};
+    }
+};
+struct MatNvfp4 {
+    const uint8_t* w; int K; const uint8_t* sf; int gtiles;
+    __device__ __forceinline__ WRowNvfp4 row(int n) const {
+        return WRowNvfp4{w + (size_t)n * (K >> 1), sf, n, gtiles};
+    }
+};
+
+template <class Mat, int MT, bool OUT_BF16>
+__global__ void __launch_bounds__(256) gemv_kernel(Mat mat, const bf16* __restrict__ x, int ldx, void* __restrict__ out,
+                                                   int ldo, int N, int K, float alpha, const float* __restrict__ bias) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = (blockIdx.x * 8 + warp) * 2;
+    if (n0 >= N) return;
+    const int n1 = min(n0 + 1, N - 1);
+    float acc0[MT], acc1[MT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) acc0[m] = acc1[m] = 0.f;
+    auto r0 = mat.row(n0);
+    auto r1 = mat.row(n1);
+    pdl_wait();
+    warp_dot2<decltype(r0), MT>(r0, r1, x, ldx, K, acc0, acc1);
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+        float a = warp_sum(acc0[m]) * alpha, b = warp_sum(acc1[m]) * alpha;
+        if (lane == 0) {
+            if (bias) { a += bias[n0]; b += bias[n1]; }
+            if (OUT_BF16) {
+                bf16* o = reinterpret_cast<bf16*>(out) + (size_t)m * ldo;
+                o[n0] = __float2bfloat16(a);
+                if (n0 + 1 < N) o[n0 + 1] = __float2bfloat16(b);
+            } else {
+                float* o = reinterpret_cast<float*>(out) + (size_t)m * ldo;
+                o[n0] = a;
+                if (n0 + 1 < N) o[n0 + 1] = b;
+            }
+        }
+    }
+    pdl_launch_dependents();
+}
+
+template <class Mat>
+static int launch_gemv(Mat mat, const bf16* x, int ldx, void* out, int ldo, int M, int N, int K, float alpha,
+                       const float* bias, int out_bf16, cudaStream_t st) {
+    const int grid = (N + 15) / 16;
+    const size_t osz = out_bf16 ? 2 : 4;
+    for (int m0 = 0; m0 < M;) {
+        const int rem = M - m0;
+        const int mt = rem >= 4 ? 4 : (rem >= 2 ? 2 : 1);
+        const bf16* xp = x + (size_t)m0 * ldx;
+        void* op = reinterpret_cast<char*>(out) + (size_t)m0 * ldo * osz;
+#define LSB_GEMV_CASE(MT_)                                                                                      \
+    if (out_bf16) gemv_kernel<Mat, MT_, true><<<grid, 256, 0, st>>>(mat, xp, ldx, op, ldo, N, K, alpha, bias); \
+    else gemv_kernel<Mat, MT_, false><<<grid, 256, 0, st>>>(mat, xp, ldx, op, ldo, N, K, alpha, bias);
+        if (mt == 4) { LSB_GEMV_CASE(4) } else if (mt == 2) { LSB_GEMV_CASE(2) } else { LSB_GEMV_CASE(1) }
+#undef LSB_GEMV_CASE
+        m0 += mt;
+    }
+    return (int)cudaGetLastError();
+}
+
+}  // namespace lsb
+
+using namespace lsb;
+
+// x: bf16 [M, ldx]; W: bf16 [N, ldw]; out fp32 or bf16 [M, ldo]. K % 8 == 0, 16-byte aligned rows.
+LSB_API int lsb_gemv_bf16(void* out, const void* x, const void* w, const void* bias, int M, int N, int K, int ldx,
+                          int ldw, int ldo, float alpha, int out_bf16, void* stream) {
+    if (K % 8 || ldw % 8 || ldx % 8) return -1;
+    return launch_gemv(MatBf16{(const bf16*)w, ldw}, (const bf16*)x, ldx, out, ldo, M, N, K, alpha, (const float*)bias,
+                       out_bf16, (cudaStream_t)stream);
+}
+
+// W: fp32 [N, ldw] (router / hyper-connection mixing matrices). K % 4 == 0.
+LSB_API int lsb_gemv_f32w(void* out, const void* x, const void* w, const void* bias, int M, int N, int K, int ldx,
+                          int ldw, int ldo, float alpha, int out_bf16, void* stream) {
+    if (K % 4 || ldw % 4 || ldx % 4) return -1;
+    return launch_gemv(MatF32{(const float*)w, ldw}, (const bf16*)x, ldx, out, ldo, M, N, K, alpha, (const float*)bias,
+                       out_bf16, (cudaStream_t)stream);
+}
+
+// W: e4m3 [N, K] with fp32 scales [ceil(N/128), ceil(K/128)] (128x128 blocks). K % 16 == 0.
+LSB_API int lsb_gemv_fp8b(void* out, const void* x, const void* w, const void* scales, const void* bias, int M, int N,
+                          int K, int ldx, int ldo, float alpha, int out_bf16, void* stream) {
+    if (K % 16 || ldx % 8) return -1;
+    return launch_gemv(MatFp8B{(const uint8_t*)w, K, (const float*)scales, (K + 127) / 128}, (const bf16*)x, ldx, out,
+                       ldo, M, N, K, alpha, (const float*)bias, out_bf16, (cudaStream_t)stream);
+}
+
+// W: packed E2M1 [N, K/2] + e4m3 group scales in the 128x4 atom layout; alpha carries the
+// per-tensor scale (weight_scale_2). K % 32 == 0.
+LSB_API int lsb_gemv_nvfp4(void* out, const void* x, const void* w, const void* sf, const void* bias, int M, int N,
+                           int K, int ldx, int ldo, float alpha, int out_bf16, void* stream) {
+    if (K % 32 || ldx % 8) return -1;
+    const int G = K / 16;
+    return launch_gemv(MatNvfp4{(const uint8_t*)w, K, (const uint8_t*)sf, (G + 3) / 4}, (const bf16*)x, ldx, out, ldo,
+                       M, N, K, alpha, (const float*)bias, out_bf16, (cudaStream_t)stream);
+}

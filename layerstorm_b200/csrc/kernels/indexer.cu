@@ -1,0 +1,353 @@
+// Sparse-attention "lightning" indexer: a cheap single-key-head scorer that picks the
+// top-k cache rows each query attends to.
+//
+//   k_n   = Hadamard(RoPE(LayerNorm(W_k h_n)))  stored as e4m3 + per-entry scale
+//   q_h   = Hadamard(RoPE(W_qb q_c))            h = 1..IH index heads
+//   score[n] = sum_h w_h * ReLU(q_h . k_n),     w = W_w h * IH^-1/2 * ID^-1/2
+//   selection = top-k over causal entries, ties to the lower index, returned ascending.
+// IndexPool ("kpool", P tokens per entry): P consecutive LayerNormed keys are pooled by a
+// per-dimension softmax over (gate + position-embedding) before the rotation; only complete
+// pools are scored (budget = topk / P pools, expanded to token rows) and the incomplete tail
+// of the sequence is always selected.
+// Reference behaviour: src/compute/kernels/sm120/indexer/indexer_prep.cu:16-89,
+// indexer_hadamard.cu:18, external lightning_score / lightning_topk / kpool_compress and the
+// CPU specification tests/unit/kpool_reference.h.
+#include "common.cuh"
+
+namespace lsb {
+
+constexpr int kID = 128;      // index head dim
+constexpr int kIdxRow = 144;  // bytes per cached entry: 128 e4m3 + fp32 scale + pad
+
+__device__ __forceinline__ float fwht128(float v, float* buf) {
+    const int t = threadIdx.x;
+    for (int s = 1; s < kID; s <<= 1) {
+        buf[t] = v;
+        __syncthreads();
+        const float o = buf[t ^ s];
+        v = (t & s) ? (o - v) : (v + o);
+        __syncthreads();
+    }
+    return v * 0.08838834764831845f;
+}
+
+__device__ __forceinline__ void rope_first(float& v, float* buf, int dr, float pos, const float* inv_freq) {
+    // interleaved pairs over the first dr dims
+    const int t = threadIdx.x;
+    buf[t] = v;
+    __syncthreads();
+    if (t < dr) {
+        const int i = t >> 1;
+        float s, c;
+        sincosf(pos * inv_freq[i], &s, &c);
+        const float a = buf[t & ~1], b = buf[t | 1];
+        v = (t & 1) ? (a * s + b * c) : (a * c - b * s);
+    }
+    __syncthreads();
+}
+
+// Quantise one 128-vector (one element per thread) and store [e4m3 x128 | scale].
+__device__ __forceinline__ void store_entry(uint8_t* row, float v, float* red, bool pow2) {
+    const float amax = block_max(fabsf(v), red);
+    float scale;
+    if (pow2) scale = exp2f(ceilf(log2f(fmaxf(amax, 1e-4f) / 448.f)));
+    else scale = fmaxf(amax, 1e-10f) / 448.f;
+    row[threadIdx.x] = float_to_fp8e4m3(fminf(fmaxf(v / scale, -448.f), 448.f));
+    if (threadIdx.x == 0) *reinterpret_cast<float*>(row + kID) = scale;
+}
+
+struct IdxAppendParams {
+    const float* proj; int ldp, off_k, off_gate;   // fp32 projections of the row
+    const float* ln_w; const float* ln_b; const float* ape;   // ape [P,128] (kpool only)
+    const float* inv_freq; int dr;
+    uint8_t* cache; const int* block_table; int max_pages, page;   // entries per page = `page`
+    bf16* tail;               // [slots, P, 2, 128] LayerNormed key | gate of the open pool (kpool only)
+    const int* row_seq; const int* row_pos; const int* row_slot;
+    int P; float ln_eps;
+};
+
+// LayerNorm + RoPE of one row's raw indexer key (one element per thread).
+__device__ __forceinline__ float idx_key_of_row(const IdxAppendParams& p, int row, int pos, float* buf, float* red) {
+    const int t = threadIdx.x;
+    float v = p.proj[(size_t)row * p.ldp + p.off_k + t];
+    const float mean = block_sum(v, red) / (float)kID;
+    const float dv = v - mean;
+    const float var = block_sum(dv * dv, red) / (float)kID;
+    v = dv * rsqrtf(var + p.ln_eps) * p.ln_w[t] + p.ln_b[t];
+    if (p.dr > 0) rope_first(v, buf, p.dr, (float)pos, p.inv_freq);
+    return v;
+}
+
+__global__ void __launch_bounds__(kID) indexer_k_append_kernel(IdxAppendParams p) {
+    __shared__ float buf[kID];
+    __shared__ float red[33];
+    const int r = blockIdx.x, t = threadIdx.x;
+    pdl_wait();
+    const int seq = p.row_seq[r], pos = p.row_pos[r];
+    if (seq < 0) return;
+    const float* pr = p.proj + (size_t)r * p.ldp;
+    float v = idx_key_of_row(p, r, pos, buf, red);
+    if (p.P <= 1) {
+        v = fwht128(__bfloat162float(__float2bfloat16(v)), buf);
+        const int pg = p.block_table[(size_t)seq * p.max_pages + pos / p.page];
+        store_entry(p.cache + ((size_t)pg * p.page + pos % p.page) * kIdxRow, __bfloat162float(__float2bfloat16(v)), red, false);
+    } else {
+        const int slot = p.row_slot[r], j = pos % p.P;
+        bf16* tl = p.tail + ((size_t)slot * p.P + j) * 2 * kID;
+        tl[t] = __float2bfloat16(v);
+        tl[kID + t] = __float2bfloat16(pr[p.off_gate + t]);
+        if (j == p.P - 1) {
+            // Compose the pooled entry: two-pass softmax over the P slots per dimension.  Slots
+            // written by earlier rows of THIS launch are recomputed from their projections (other
+            // blocks may not have stored them yet); older slots come from the tail buffer.
+            const bf16* t0 = p.tail + (size_t)slot * p.P * 2 * kID;
+            float kk[8], s[8];
+            float m = -INFINITY;
+            for (int jj = 0; jj < p.P; ++jj) {
+                const int d = j - jj, rr = r - d;
+                float kv, gv;
+                if (d == 0) {
+                    kv = v; gv = pr[p.off_gate + t];
+                } else if (rr >= 0 && p.row_seq[rr] == seq && p.row_pos[rr] == pos - d) {
+                    kv = idx_key_of_row(p, rr, pos - d, buf, red);
+                    gv = p.proj[(size_t)rr * p.ldp + p.off_gate + t];
+                } else {
+                    kv = __bfloat162float(t0[(size_t)jj * 2 * kID + t]);
+                    gv = __bfloat162float(t0[(size_t)jj * 2 * kID + kID + t]);
+                }
+                kk[jj] = __bfloat162float(__float2bfloat16(kv));
+                s[jj] = __bfloat162float(__float2bfloat16(gv)) + p.ape[jj * kID + t];
+                m = fmaxf(m, s[jj]);
+            }
+            float Z = 0.f, acc = 0.f;
+            for (int jj = 0; jj < p.P; ++jj) {
+                const float e = expf(s[jj] - m);
+                Z += e; acc += e * kk[jj];
+            }
+            float x = __bfloat162float(__float2bfloat16(acc / Z));
+            x = __bfloat162float(__float2bfloat16(fwht128(x, buf)));
+            const int entry = pos / p.P;
+            const int pg = p.block_table[(size_t)seq * p.max_pages + entry / p.page];
+            store_entry(p.cache + ((size_t)pg * p.page + entry % p.page) * kIdxRow, x, red, true);
+        }
+    }
+    pdl_launch_dependents();
+}
+
+// q rows: [R, IH, 128] from the fused q_b projection (bf16, stride ldq, offset off_q);
+// weights from the fused input projection.  Out: q_idx bf16 [R,IH,128], w fp32 [R,IH].
+__global__ void __launch_bounds__(kID) indexer_q_prep_kernel(const bf16* __restrict__ qproj, int ldq, int off_q,
+                                                              const float* __restrict__ proj, int ldp, int off_w, int IH, int dr,
+                                                              const float* __restrict__ inv_freq, const int* __restrict__ row_pos,
+                                                              bf16* __restrict__ q_idx, float* __restrict__ w_out) {
+    __shared__ float buf[kID];
+    const int r = blockIdx.x, t = threadIdx.x;
+    pdl_wait();
+    const float pos = (float)row_pos[r];
+    for (int h = 0; h < IH; ++h) {
+        float v = __bfloat162float(qproj[(size_t)r * ldq + off_q + h * kID + t]);
+        if (dr > 0) rope_first(v, buf, dr, pos, inv_freq);
+        v = fwht128(__bfloat162float(__float2bfloat16(v)), buf);
+        q_idx[((size_t)r * IH + h) * kID + t] = __float2bfloat16(v);
+    }
+    if (t < IH) w_out[(size_t)r * IH + t] = proj[(size_t)r * ldp + off_w + t] * rsqrtf((float)IH) * rsqrtf((float)kID);
+    pdl_launch_dependents();
+}
+
+// scores[r][n] for n < n_entries[r]; one thread per entry, q staged in shared memory.
+__global__ void __launch_bounds__(128) indexer_score_kernel(const bf16* __restrict__ q_idx, const float* __restrict__ w, int IH,
+                                                            const uint8_t* __restrict__ cache, const int* __restrict__ block_table,
+                                                            int max_pages, int page, const int* __restrict__ row_seq,
+                                                            const int* __restrict__ n_entries, float* __restrict__ scores, int ld_scores) {
+    extern __shared__ __align__(16) uint8_t smraw[];
+    bf16* qs = reinterpret_cast<bf16*>(smraw);                 // [IH][128]
+    float* ws = reinterpret_cast<float*>(qs + IH * kID);       // [IH]
+    const int r = blockIdx.y, t = threadIdx.x;
+    pdl_wait();
+    const int seq = row_seq[r];
+    const int ne = seq < 0 ? 0 : n_entries[r];
+    if ((int)(blockIdx.x * blockDim.x) >= ne) return;
+    for (int i = t; i < IH * kID / 8; i += blockDim.x)
+        reinterpret_cast<uint4*>(qs)[i] = reinterpret_cast<const uint4*>(q_idx + (size_t)r * IH * kID)[i];
+    if (t < IH) ws[t] = w[(size_t)r * IH + t];
+    __syncthreads();
+    const int n = blockIdx.x * blockDim.x + t;
+    if (n >= ne) return;
+    const int pg = block_table[(size_t)seq * max_pages + n / page];
+    const uint8_t* row = cache + ((size_t)pg * page + n % page) * kIdxRow;
+    float k[kID];
+#pragma unroll
+    for (int c = 0; c < kID / 16; ++c) {
+        const uint4 v = *reinterpret_cast<const uint4*>(row + c * 16);
+        unpack_fp8x4(v.x, k + c * 16); unpack_fp8x4(v.y, k + c * 16 + 4);
+        unpack_fp8x4(v.z, k + c * 16 + 8); unpack_fp8x4(v.w, k + c * 16 + 12);
+    }
+    const float ks = *reinterpret_cast<const float*>(row + kID);
+    float acc = 0.f;
+    for (int h = 0; h < IH; ++h) {
+        float d = 0.f;
+#pragma unroll
+        for (int c = 0; c < kID; c += 8) {
+            float qf[8];
+            unpack_bf16x8(*reinterpret_cast<const uint4*>(qs + h * kID + c), qf);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) d = fmaf(qf[e], k[c + e], d);
+        }
+        acc = fmaf(fmaxf(d * ks, 0.f), ws[h], acc);
+    }
+    scores[(size_t)r * ld_scores + n] = acc;
+    pdl_launch_dependents();
+}
+
+__device__ __forceinline__ uint32_t sortable(float x) {
+    const uint32_t b = __float_as_uint(x);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
+// Per row: radix-select the `budget` best of n_elig entries (ties to the lower index), emit
+// them in ascending order expanded by P, then append the always-selected tail tokens.
+//   n_elig = complete, causal entries; tail = [n_elig*P, len).  If n_elig <= budget all are taken.
+__global__ void __launch_bounds__(1024) indexer_topk_kernel(const float* __restrict__ scores, int ld_scores,
+                                                            const int* __restrict__ n_entries, const int* __restrict__ row_len,
+                                                            const int* __restrict__ row_seq, int budget, int P,
+                                                            int* __restrict__ sel_idx, int* __restrict__ sel_cnt, int sel_ld) {
+    __shared__ int hist[256];
+    __shared__ int s_scan[33];
+    __shared__ uint32_t s_prefix;
+    __shared__ int s_need, s_base, s_eqbase;
+    const int r = blockIdx.x, t = threadIdx.x;
+    pdl_wait();
+    const int len = row_seq[r] < 0 ? 0 : row_len[r];
+    const int ne = row_seq[r] < 0 ? 0 : n_entries[r];
+    const float* sc = scores + (size_t)r * ld_scores;
+    int* out = sel_idx + (size_t)r * sel_ld;
+    int nsel_entries;
+    if (ne <= budget) {
+        for (int i = t; i < ne * P; i += blockDim.x) out[i] = i;
+        nsel_entries = ne;
+    } else {
+        // find the key of the budget-th largest element, 8 bits at a time
+        if (t == 0) { s_prefix = 0; s_need = budget; }
+        __syncthreads();
+        for (int shift = 24; shift >= 0; shift -= 8) {
+            for (int i = t; i < 256; i += blockDim.x) hist[i] = 0;
+            __syncthreads();
+            const uint32_t prefix = s_prefix;
+            const uint32_t mask = shift == 24 ? 0u : (0xffffffffu << (shift + 8));
+            for (int i = t; i < ne; i += blockDim.x) {
+                const uint32_t k = sortable(sc[i]);
+                if ((k & mask) == prefix) atomicAdd(&hist[(k >> shift) & 255], 1);
+            }
+            __syncthreads();
+            if (t == 0) {
+                int need = s_need, b = 255;
+                for (; b > 0; --b) {
+                    if (hist[b] >= need) break;
+                    need -= hist[b];
+                }
+                s_need = need;
+                s_prefix = prefix | ((uint32_t)b << shift);
+            }
+            __syncthreads();
+        }
+        const uint32_t T = s_prefix;   // threshold key; s_need = how many equal-to-T to take
+        const int quota = s_need;
+        if (t == 0) { s_base = 0; s_eqbase = 0; }
+        __syncthreads();
+        const int lane = t & 31, w = t >> 5;
+        for (int c0 = 0; c0 < ne; c0 += blockDim.x) {
+            const int i = c0 + t;
+            uint32_t k = 0;
+            if (i < ne) k = sortable(sc[i]);
+            const int gt = (i < ne && k > T) ? 1 : 0, eq = (i < ne && k == T) ? 1 : 0;
+            // block exclusive scan of eq
+            int v = eq;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) { const int n = __shfl_up_sync(0xffffffffu, v, o); if (lane >= o) v += n; }
+            if (lane == 31) s_scan[w] = v;
+            __syncthreads();
+            if (w == 0) {
+                int x = s_scan[lane];
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) { const int n = __shfl_up_sync(0xffffffffu, x, o); if (lane >= o) x += n; }
+                s_scan[lane] = x;
+            }
+            __syncthreads();
+            const int eq_rank = s_eqbase + (w ? s_scan[w - 1] : 0) + v - eq;
+            const int eq_total = s_scan[31];
+            const int take = gt | (eq && eq_rank < quota);
+            __syncthreads();
+            int u = take;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) { const int n = __shfl_up_sync(0xffffffffu, u, o); if (lane >= o) u += n; }
+            if (lane == 31) s_scan[w] = u;
+            __syncthreads();
+            if (w == 0) {
+                int x = s_scan[lane];
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) { const int n = __shfl_up_sync(0xffffffffu, x, o); if (lane >= o) x += n; }
+                s_scan[lane] = x;
+            }
+            __syncthreads();
+            const int posn = s_base + (w ? s_scan[w - 1] : 0) + u - take;
+            if (take && posn < budget)
+                for (int j = 0; j < P; ++j) out[posn * P + j] = i * P + j;
+            const int tot = s_scan[31];
+            __syncthreads();
+            if (t == 0) { s_base += tot; s_eqbase += eq_total; }
+            __syncthreads();
+        }
+        nsel_entries = budget;
+    }
+    const int tail0 = ne * P;
+    for (int i = tail0 + t; i < len; i += blockDim.x) out[nsel_entries * P + (i - tail0)] = i;
+    if (t == 0) sel_cnt[r] = nsel_entries * P + max(0, len - tail0);
+    pdl_launch_dependents();
+}
+
+}  // namespace lsb
+using namespace lsb;
+
+LSB_API int lsb_indexer_row_bytes() { return kIdxRow; }
+
+LSB_API int lsb_indexer_k_append(const void* proj, int ldp, int off_k, int off_gate, const void* ln_w, const void* ln_b,
+                                 const void* ape, const void* inv_freq, int dr, void* cache, const void* block_table,
+                                 int max_pages, int page, void* tail, const void* row_seq, const void* row_pos,
+                                 const void* row_slot, int rows, int P, float ln_eps, void* stream) {
+    if (P > 8) return -1;
+    IdxAppendParams p;
+    p.proj = (const float*)proj; p.ldp = ldp; p.off_k = off_k; p.off_gate = off_gate; p.ln_w = (const float*)ln_w;
+    p.ln_b = (const float*)ln_b; p.ape = (const float*)ape; p.inv_freq = (const float*)inv_freq; p.dr = dr;
+    p.cache = (uint8_t*)cache; p.block_table = (const int*)block_table; p.max_pages = max_pages; p.page = page;
+    p.tail = (bf16*)tail; p.row_seq = (const int*)row_seq; p.row_pos = (const int*)row_pos; p.row_slot = (const int*)row_slot;
+    p.P = P; p.ln_eps = ln_eps;
+    indexer_k_append_kernel<<<rows, kID, 0, (cudaStream_t)stream>>>(p);
+    LSB_CHECK_LAUNCH();
+}
+
+LSB_API int lsb_indexer_q_prep(const void* qproj, int ldq, int off_q, const void* proj, int ldp, int off_w, int IH, int dr,
+                               const void* inv_freq, const void* row_pos, void* q_idx, void* w_out, int rows, void* stream) {
+    if (IH > kID) return -1;
+    indexer_q_prep_kernel<<<rows, kID, 0, (cudaStream_t)stream>>>((const bf16*)qproj, ldq, off_q, (const float*)proj, ldp, off_w, IH, dr,
+                                                                 (const float*)inv_freq, (const int*)row_pos, (bf16*)q_idx, (float*)w_out);
+    LSB_CHECK_LAUNCH();
+}
+
+LSB_API int lsb_indexer_score(const void* q_idx, const void* w, int IH, const void* cache, const void* block_table,
+                              int max_pages, int page, const void* row_seq, const void* n_entries, void* scores,
+                              int ld_scores, int rows, int max_entries, void* stream) {
+    if (max_entries <= 0) return 0;
+    dim3 grid((max_entries + 127) / 128, rows);
+    indexer_score_kernel<<<grid, 128, (size_t)IH * kID * 2 + IH * 4, (cudaStream_t)stream>>>((const bf16*)q_idx, (const float*)w, IH, (const uint8_t*)cache,
+                                                                                            (const int*)block_table, max_pages, page, (const int*)row_seq,
+                                                                                            (const int*)n_entries, (float*)scores, ld_scores);
+    LSB_CHECK_LAUNCH();
+}
+
+LSB_API int lsb_indexer_topk(const void* scores, int ld_scores, const void* n_entries, const void* row_len,
+                             const void* row_seq, int budget, int P, void* sel_idx, void* sel_cnt, int sel_ld, int rows,
+                             void* stream) {
+    indexer_topk_kernel<<<rows, 1024, 0, (cudaStream_t)stream>>>((const float*)scores, ld_scores, (const int*)n_entries, (const int*)row_len,
+                                                               (const int*)row_seq, budget, P, (int*)sel_idx, (int*)sel_cnt, sel_ld);
+    LSB_CHECK_LAUNCH();
+}

@@ -1,0 +1,383 @@
+// Multi-head latent attention (MLA), absorbed form, over a paged quantised latent cache.
+//
+// Layer math (reference: src/daemon/attention/arch_mla.cpp:47-312,1824-1994):
+//   q_c = RMSNorm(W_qa h);  q = W_qb q_c -> [H, d_nope + d_rope]
+//   q_abs[h] = [ q_nope[h] . W_UK[h] (-> d_c) | RoPE(q_rope[h]) ]
+//   kv = W_kva h -> [d_c + d_rope];  c = RMSNorm(kv[:d_c]);  k_pe = RoPE(kv[d_c:]);  cache row = (c, k_pe)
+//   attention in latent space (all heads share the cached row), output [H, d_c] -> W_UV per head.
+// RoPE rotates interleaved adjacent pairs.
+//
+// Cache row formats (kv_fmt):
+//   0  bf16: (d_c + d_rope) bf16
+//   1  fp8 : d_c e4m3 bytes | fp32 per-token scale (+12 pad bytes) | d_rope bf16
+//          (the reference's FP8+BF16-RoPE row: docs/DESIGN.md:126, K/sm120/prep/fused_k_append.cu)
+// Pages hold `page` consecutive tokens; a sequence's pages are listed in its block table.
+#include "common.cuh"
+#include "gemv_core.cuh"
+
+namespace lsb {
+
+__host__ __device__ inline int kv_row_bytes(int fmt, int dl, int dr) { return fmt == 0 ? (dl + dr) * 2 : dl + 16 + dr * 2; }
+
+__device__ __forceinline__ void rope_pair(float& a, float& b, float pos, float inv_freq) {
+    float s, c;
+    sincosf(pos * inv_freq, &s, &c);
+    const float x = a * c - b * s, y = a * s + b * c;
+    a = x; b = y;
+}
+
+// One block per row: q_c = RMSNorm(q_a) (bf16 out), latent RMSNorm, RoPE on k_pe, cache append.
+__global__ void mla_prep_kernel(const float* __restrict__ proj, int ldp, int off_qa, int q_lora, int off_kv, int dl, int dr,
+                                const float* __restrict__ qa_norm_w, const float* __restrict__ kv_norm_w,
+                                const float* __restrict__ inv_freq, bf16* __restrict__ q_c, uint8_t* __restrict__ cache,
+                                const int* __restrict__ block_table, int max_pages, const int* __restrict__ row_seq,
+                                const int* __restrict__ row_pos, int page, int kv_fmt, float eps) {
+    __shared__ float red[33];
+    extern __shared__ float sm[];   // [max(q_lora, dl + dr)]
+    const int r = blockIdx.x, t = threadIdx.x;
+    const float* pr = proj + (size_t)r * ldp;
+    pdl_wait();
+    if (q_lora > 0) {
+        float ss = 0.f;
+        for (int i = t; i < q_lora; i += blockDim.x) { const float v = pr[off_qa + i]; sm[i] = v; ss += v * v; }
+        ss = block_sum(ss, red);
+        const float inv = rsqrtf(ss / (float)q_lora + eps);
+        for (int i = t; i < q_lora; i += blockDim.x) q_c[(size_t)r * q_lora + i] = __float2bfloat16(sm[i] * inv * qa_norm_w[i]);
+        __syncthreads();
+    }
+    float ss = 0.f;
+    for (int i = t; i < dl; i += blockDim.x) { const float v = pr[off_kv + i]; sm[i] = v; ss += v * v; }
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / (float)dl + eps);
+    float amax = 0.f;
+    for (int i = t; i < dl; i += blockDim.x) { const float v = sm[i] * inv * kv_norm_w[i]; sm[i] = v; amax = fmaxf(amax, fabsf(v)); }
+    const int seq = row_seq[r], pos = row_pos[r];
+    for (int i = t; i < dr / 2; i += blockDim.x) {
+        float a = pr[off_kv + dl + 2 * i], b = pr[off_kv + dl + 2 * i + 1];
+        rope_pair(a, b, (float)pos, inv_freq[i]);
+        sm[dl + 2 * i] = a; sm[dl + 2 * i + 1] = b;
+    }
+    amax = block_max(amax, red);   // also orders the shared-memory writes above
+    if (seq < 0) return;
+    const int pg = block_table[(size_t)seq * max_pages + pos / page];
+    const int rb = kv_row_bytes(kv_fmt, dl, dr);
+    uint8_t* row = cache + ((size_t)pg * page + (pos % page)) * rb;
+    if (kv_fmt == 0) {
+        bf16* o = reinterpret_cast<bf16*>(row);
+        for (int i = t; i < dl + dr; i += blockDim.x) o[i] = __float2bfloat16(sm[i]);
+    } else {
+        const float scale = fmaxf(amax, 1e-10f) / 448.f;
+        const float inv_s = 1.f / scale;
+        for (int i = t; i < dl; i += blockDim.x) row[i] = float_to_fp8e4m3(sm[i] * inv_s);
+        if (t == 0) *reinterpret_cast<float*>(row + dl) = scale;
+        bf16* o = reinterpret_cast<bf16*>(row + dl + 16);
+        for (int i = t; i < dr; i += blockDim.x) o[i] = __float2bfloat16(sm[dl + i]);
+    }
+    pdl_launch_dependents();
+}
+
+// out[m][b][n] = sum_k x[m][b][k] * W[b][n][k]; used for W_UK absorption and the W_UV up-projection.
+// Optional RoPE tail: out[m][b][N + i] = RoPE(x[m][b][K + i]) for i < dr (query rope half).
+template <int MT>
+__global__ void __launch_bounds__(256) batched_gemv_kernel(bf16* __restrict__ out, const bf16* __restrict__ x, const bf16* __restrict__ w,
+                                                           int N, int K, long long xs_m, long long xs_b, long long os_m,
+                                                           long long os_b, int dr, const float* __restrict__ inv_freq,
+                                                           const int* __restrict__ row_pos, int m_base) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int b = blockIdx.y;
+    const int n0 = (blockIdx.x * 8 + warp) * 2;
+    pdl_wait();
+    if (blockIdx.x == 0 && dr > 0) {
+        for (int m = 0; m < MT; ++m)
+            for (int i = threadIdx.x; i < dr / 2; i += blockDim.x) {
+                const bf16* xp = x + (size_t)m * xs_m + (size_t)b * xs_b + K;
+                float a0 = __bfloat162float(xp[2 * i]), a1 = __bfloat162float(xp[2 * i + 1]);
+                rope_pair(a0, a1, (float)row_pos[m_base + m], inv_freq[i]);
+                bf16* o = out + (size_t)m * os_m + (size_t)b * os_b + N;
+                o[2 * i] = __float2bfloat16(a0); o[2 * i + 1] = __float2bfloat16(a1);
+            }
+    }
+    if (n0 >= N) return;
+    const int n1 = min(n0 + 1, N - 1);
+    const bf16* wb = w + (size_t)b * N * K;
+    WRowBf16 r0{wb + (size_t)n0 * K}, r1{wb + (size_t)n1 * K};
+    float a0[MT], a1[MT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) a0[m] = a1[m] = 0.f;
+    warp_dot2<WRowBf16, MT>(r0, r1, x + (size_t)b * xs_b, (int)xs_m, K, a0, a1);
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+        const float v0 = warp_sum(a0[m]), v1 = warp_sum(a1[m]);
+        if (lane == 0) {
+            bf16* o = out + (size_t)m * os_m + (size_t)b * os_b;
+            o[n0] = __float2bfloat16(v0);
+            if (n0 + 1 < N) o[n0 + 1] = __float2bfloat16(v1);
+        }
+    }
+    pdl_launch_dependents();
+}
+
+constexpr int kHG = 16;   // heads per block
+constexpr int kTK = 32;   // cache rows per tile
+
+struct MlaDecodeParams {
+    const bf16* q;            // [R, H, dl + dr]
+    const uint8_t* cache;
+    const int* block_table; int max_pages;
+    const int* row_seq; const int* row_len;     // causal length (tokens visible) per row
+    const int* sel_idx; const int* sel_cnt; int sel_ld;   // optional sparse selection (token positions)
+    float* o_part; float* ml_part;              // [R,H,NS,dl], [R,H,NS,2]
+    int H, dl, dr, page, kv_fmt, NS;
+    float scale;
+};
+
+__global__ void __launch_bounds__(256) mla_decode_kernel(MlaDecodeParams p) {
+    extern __shared__ __align__(16) uint8_t smraw[];
+    const int D = p.dl + p.dr, DP = D + 8;     // padded bf16 row (16 B mod 128 B => conflict-free 128-bit reads)
+    bf16* Ks = reinterpret_cast<bf16*>(smraw);                 // [kTK][DP]
+    bf16* Qs = Ks + kTK * DP;                                   // [kHG][DP]
+    float* Ps = reinterpret_cast<float*>(Qs + kHG * DP);        // [kTK][kHG]
+    float* sc = Ps + kTK * kHG;                                 // [kTK] row scales
+    float* s_m = sc + kTK;                                      // [kHG]
+    float* s_l = s_m + kHG;                                     // [kHG]
+    float* s_alpha = s_l + kHG;                                 // [kHG]
+    int* s_tok = reinterpret_cast<int*>(s_alpha + kHG);         // [kTK]
+    const int r = blockIdx.x, hg = blockIdx.y, sp = blockIdx.z;
+    const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+    pdl_wait();
+    const int seq = p.row_seq[r];
+    int n = p.sel_idx ? p.sel_cnt[r] : p.row_len[r];
+    if (seq < 0) n = 0;
+    const int per = (((n + p.NS - 1) / p.NS) + kTK - 1) / kTK * kTK;
+    const int beg = sp * per, end = min(n, beg + per);
+    // stage q for this head group
+    for (int i = t; i < kHG * (D / 8); i += blockDim.x) {
+        const int h = i / (D / 8), c = i % (D / 8);
+        const int hh = hg * kHG + h;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (hh < p.H) v = *reinterpret_cast<const uint4*>(p.q + ((size_t)r * p.H + hh) * D + c * 8);
+        *reinterpret_cast<uint4*>(Qs + h * DP + c * 8) = v;
+    }
+    if (t < kHG) { s_m[t] = -INFINITY; s_l[t] = 0.f; }
+    float acc[kHG][2];
+#pragma unroll
+    for (int h = 0; h < kHG; ++h) acc[h][0] = acc[h][1] = 0.f;
+    const int rb = kv_row_bytes(p.kv_fmt, p.dl, p.dr);
+    for (int t0 = beg; t0 < end; t0 += kTK) {
+        __syncthreads();
+        if (t < kTK) {
+            const int i = t0 + t;
+            int tok = -1;
+            if (i < end) tok = p.sel_idx ? p.sel_idx[(size_t)r * p.sel_ld + i] : i;
+            s_tok[t] = tok;
+        }
+        __syncthreads();
+        // load tile
+        if (p.kv_fmt == 0) {
+            const int cpr = D / 8;
+            for (int i = t; i < kTK * cpr; i += blockDim.x) {
+                const int j = i / cpr, c = i % cpr, tok = s_tok[j];
+                uint4 v = make_uint4(0, 0, 0, 0);
+                if (tok >= 0) {
+                    const int pg = p.block_table[(size_t)seq * p.max_pages + tok / p.page];
+                    v = *reinterpret_cast<const uint4*>(p.cache + ((size_t)pg * p.page + tok % p.page) * rb + c * 16);
+                }
+                *reinterpret_cast<uint4*>(Ks + j * DP + c * 8) = v;
+            }
+            if (t < kTK) sc[t] = 1.f;
+        } else {
+            const int c8 = p.dl / 16, cr = p.dr / 8, cpr = c8 + cr;
+            for (int i = t; i < kTK * cpr; i += blockDim.x) {
+                const int j = i / cpr, c = i % cpr, tok = s_tok[j];
+                const uint8_t* row = nullptr;
+                if (tok >= 0) {
+                    const int pg = p.block_table[(size_t)seq * p.max_pages + tok / p.page];
+                    row = p.cache + ((size_t)pg * p.page + tok % p.page) * rb;
+                }
+                if (c < c8) {
+                    uint4 v = row ? *reinterpret_cast<const uint4*>(row + c * 16) : make_uint4(0, 0, 0, 0);
+                    float f[16];
+                    unpack_fp8x4(v.x, f); unpack_fp8x4(v.y, f + 4); unpack_fp8x4(v.z, f + 8); unpack_fp8x4(v.w, f + 12);
+                    bf162* o = reinterpret_cast<bf162*>(Ks + j * DP + c * 16);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) o[e] = __floats2bfloat162_rn(f[2 * e], f[2 * e + 1]);   // e4m3 -> bf16 is exact
+                } else {
+                    const int cc = c - c8;
+                    uint4 v = row ? *reinterpret_cast<const uint4*>(row + p.dl + 16 + cc * 16) : make_uint4(0, 0, 0, 0);
+                    *reinterpret_cast<uint4*>(Ks + j * DP + p.dl + cc * 8) = v;
+                }
+            }
+            if (t < kTK) {
+                const int tok = s_tok[t];
+                float s = 0.f;
+                if (tok >= 0) {
+                    const int pg = p.block_table[(size_t)seq * p.max_pages + tok / p.page];
+                    s = *reinterpret_cast<const float*>(p.cache + ((size_t)pg * p.page + tok % p.page) * rb + p.dl);
+                }
+                sc[t] = s;
+            }
+        }
+        __syncthreads();
+        // scores: warp -> heads (2w, 2w+1); lane -> cache row
+        {
+            const int h0 = 2 * warp, h1 = h0 + 1;
+            float s0 = 0.f, s1 = 0.f, r0 = 0.f, r1 = 0.f;
+            const bf16* kr = Ks + lane * DP;
+            for (int d = 0; d < p.dl; d += 8) {
+                float kf[8], q0[8], q1[8];
+                unpack_bf16x8(*reinterpret_cast<const uint4*>(kr + d), kf);
+                unpack_bf16x8(*reinterpret_cast<const uint4*>(Qs + h0 * DP + d), q0);
+                unpack_bf16x8(*reinterpret_cast<const uint4*>(Qs + h1 * DP + d), q1);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) { s0 = fmaf(kf[e], q0[e], s0); s1 = fmaf(kf[e], q1[e], s1); }
+            }
+            for (int d = p.dl; d < D; d += 8) {
+                float kf[8], q0[8], q1[8];
+                unpack_bf16x8(*reinterpret_cast<const uint4*>(kr + d), kf);
+                unpack_bf16x8(*reinterpret_cast<const uint4*>(Qs + h0 * DP + d), q0);
+                unpack_bf16x8(*reinterpret_cast<const uint4*>(Qs + h1 * DP + d), q1);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) { r0 = fmaf(kf[e], q0[e], r0); r1 = fmaf(kf[e], q1[e], r1); }
+            }
+            const bool valid = s_tok[lane] >= 0;
+            const float rs = sc[lane];
+            s0 = valid ? (s0 * rs + r0) * p.scale : -INFINITY;
+            s1 = valid ? (s1 * rs + r1) * p.scale : -INFINITY;
+            const float m0 = fmaxf(s_m[h0], warp_max(s0)), m1 = fmaxf(s_m[h1], warp_max(s1));
+            const float p0 = valid ? __expf(s0 - m0) : 0.f, p1 = valid ? __expf(s1 - m1) : 0.f;
+            const float l0 = warp_sum(p0), l1 = warp_sum(p1);
+            // the value row is the scaled latent: fold the row scale into p for the PV pass
+            Ps[lane * kHG + h0] = p0 * rs;
+            Ps[lane * kHG + h1] = p1 * rs;
+            if (lane == 0) {
+                const float a0 = (m0 == -INFINITY) ? 1.f : __expf(s_m[h0] - m0), a1 = (m1 == -INFINITY) ? 1.f : __expf(s_m[h1] - m1);
+                s_alpha[h0] = a0; s_alpha[h1] = a1;
+                s_l[h0] = s_l[h0] * a0 + l0; s_l[h1] = s_l[h1] * a1 + l1;
+                s_m[h0] = m0; s_m[h1] = m1;
+            }
+        }
+        __syncthreads();
+        // PV: thread -> latent dims (2t, 2t+1), all heads
+        if (2 * t < p.dl) {
+#pragma unroll
+            for (int h = 0; h < kHG; ++h) { const float a = s_alpha[h]; acc[h][0] *= a; acc[h][1] *= a; }
+            for (int j = 0; j < kTK; ++j) {
+                const bf162 kv = *reinterpret_cast<const bf162*>(Ks + j * DP + 2 * t);
+                const float k0 = __low2float(kv), k1 = __high2float(kv);
+                const float4* pp = reinterpret_cast<const float4*>(Ps + j * kHG);
+#pragma unroll
+                for (int h4 = 0; h4 < kHG / 4; ++h4) {
+                    const float4 pv = pp[h4];
+                    acc[h4 * 4 + 0][0] = fmaf(pv.x, k0, acc[h4 * 4 + 0][0]); acc[h4 * 4 + 0][1] = fmaf(pv.x, k1, acc[h4 * 4 + 0][1]);
+                    acc[h4 * 4 + 1][0] = fmaf(pv.y, k0, acc[h4 * 4 + 1][0]); acc[h4 * 4 + 1][1] = fmaf(pv.y, k1, acc[h4 * 4 + 1][1]);
+                    acc[h4 * 4 + 2][0] = fmaf(pv.z, k0, acc[h4 * 4 + 2][0]); acc[h4 * 4 + 2][1] = fmaf(pv.z, k1, acc[h4 * 4 + 2][1]);
+                    acc[h4 * 4 + 3][0] = fmaf(pv.w, k0, acc[h4 * 4 + 3][0]); acc[h4 * 4 + 3][1] = fmaf(pv.w, k1, acc[h4 * 4 + 3][1]);
+                }
+            }
+        }
+    }
+    __syncthreads();
+    if (2 * t < p.dl) {
+#pragma unroll
+        for (int h = 0; h < kHG; ++h) {
+            const int hh = hg * kHG + h;
+            if (hh < p.H) {
+                float* o = p.o_part + (((size_t)r * p.H + hh) * p.NS + sp) * p.dl + 2 * t;
+                o[0] = acc[h][0]; o[1] = acc[h][1];
+            }
+        }
+    }
+    if (t < kHG && hg * kHG + t < p.H) {
+        float* ml = p.ml_part + (((size_t)r * p.H + hg * kHG + t) * p.NS + sp) * 2;
+        ml[0] = s_m[t]; ml[1] = s_l[t];
+    }
+    pdl_launch_dependents();
+}
+
+// Merge split partials in split order: out = sum_s exp(m_s - M) acc_s / sum_s exp(m_s - M) l_s.
+__global__ void mla_combine_kernel(bf16* __restrict__ out, float* __restrict__ lse, const float* __restrict__ o_part,
+                                   const float* __restrict__ ml_part, int H, int NS, int dl) {
+    const int r = blockIdx.x, h = blockIdx.y;
+    pdl_wait();
+    const float* ml = ml_part + ((size_t)r * H + h) * NS * 2;
+    float M = -INFINITY;
+    for (int s = 0; s < NS; ++s) M = fmaxf(M, ml[2 * s]);
+    float L = 0.f;
+    for (int s = 0; s < NS; ++s) if (ml[2 * s] > -INFINITY) L += __expf(ml[2 * s] - M) * ml[2 * s + 1];
+    const float invL = L > 0.f ? 1.f / L : 0.f;
+    for (int d = threadIdx.x; d < dl; d += blockDim.x) {
+        float a = 0.f;
+        for (int s = 0; s < NS; ++s)
+            if (ml[2 * s] > -INFINITY) a += __expf(ml[2 * s] - M) * o_part[(((size_t)r * H + h) * NS + s) * dl + d];
+        out[((size_t)r * H + h) * dl + d] = __float2bfloat16(a * invL);
+    }
+    if (lse && threadIdx.x == 0) lse[(size_t)r * H + h] = L > 0.f ? M + logf(L) : -INFINITY;
+    pdl_launch_dependents();
+}
+
+}  // namespace lsb
+using namespace lsb;
+
+LSB_API int lsb_kv_row_bytes(int fmt, int dl, int dr) { return kv_row_bytes(fmt, dl, dr); }
+
+LSB_API int lsb_mla_prep(const void* proj, int ldp, int off_qa, int q_lora, int off_kv, int dl, int dr,
+                         const void* qa_norm_w, const void* kv_norm_w, const void* inv_freq, void* q_c, void* cache,
+                         const void* block_table, int max_pages, const void* row_seq, const void* row_pos, int rows,
+                         int page, int kv_fmt, float eps, void* stream) {
+    const int n = q_lora > dl + dr ? q_lora : dl + dr;
+    mla_prep_kernel<<<rows, 256, (size_t)n * 4, (cudaStream_t)stream>>>((const float*)proj, ldp, off_qa, q_lora, off_kv, dl, dr,
+                                                                      (const float*)qa_norm_w, (const float*)kv_norm_w,
+                                                                      (const float*)inv_freq, (bf16*)q_c, (uint8_t*)cache,
+                                                                      (const int*)block_table, max_pages, (const int*)row_seq,
+                                                                      (const int*)row_pos, page, kv_fmt, eps);
+    LSB_CHECK_LAUNCH();
+}
+
+// x: bf16 rows m with stride xs_m, batch stride xs_b; W: bf16 [B, N, K]; out bf16 (strides os_m, os_b).
+LSB_API int lsb_batched_gemv_bf16(void* out, const void* x, const void* w, int M, int B, int N, int K, long long xs_m,
+                                  long long xs_b, long long os_m, long long os_b, int dr, const void* inv_freq,
+                                  const void* row_pos, void* stream) {
+    if (K % 8 || xs_m % 8 || xs_b % 8) return -1;
+    cudaStream_t st = (cudaStream_t)stream;
+    dim3 grid((N + 15) / 16, B);
+    for (int m0 = 0; m0 < M;) {
+        const int rem = M - m0, mt = rem >= 4 ? 4 : (rem >= 2 ? 2 : 1);
+        bf16* o = (bf16*)out + (size_t)m0 * os_m;
+        const bf16* xp = (const bf16*)x + (size_t)m0 * xs_m;
+#define ARGS o, xp, (const bf16*)w, N, K, xs_m, xs_b, os_m, os_b, dr, (const float*)inv_freq, (const int*)row_pos, m0
+        if (mt == 4) batched_gemv_kernel<4><<<grid, 256, 0, st>>>(ARGS);
+        else if (mt == 2) batched_gemv_kernel<2><<<grid, 256, 0, st>>>(ARGS);
+        else batched_gemv_kernel<1><<<grid, 256, 0, st>>>(ARGS);
+#undef ARGS
+        m0 += mt;
+    }
+    LSB_CHECK_LAUNCH();
+}
+
+LSB_API int lsb_mla_decode_smem_bytes(int dl, int dr) {
+    const int DP = dl + dr + 8;
+    return (kTK + kHG) * DP * 2 + kTK * kHG * 4 + kTK * 4 + 3 * kHG * 4 + kTK * 4;
+}
+
+// q: bf16 [R,H,dl+dr]; out: bf16 [R,H,dl]; o_part/ml_part: scratch fp32 [R,H,NS,dl], [R,H,NS,2].
+LSB_API int lsb_mla_decode(const void* q, const void* cache, const void* block_table, int max_pages, const void* row_seq,
+                           const void* row_len, const void* sel_idx, const void* sel_cnt, int sel_ld, void* out, void* lse,
+                           void* o_part, void* ml_part, int R, int H, int dl, int dr, int page, int kv_fmt, int NS,
+                           float scale, void* stream) {
+    if (dl % 16 || dr % 8 || dl > 512) return -1;
+    cudaStream_t st = (cudaStream_t)stream;
+    MlaDecodeParams p;
+    p.q = (const bf16*)q; p.cache = (const uint8_t*)cache; p.block_table = (const int*)block_table; p.max_pages = max_pages;
+    p.row_seq = (const int*)row_seq; p.row_len = (const int*)row_len; p.sel_idx = (const int*)sel_idx; p.sel_cnt = (const int*)sel_cnt;
+    p.sel_ld = sel_ld; p.o_part = (float*)o_part; p.ml_part = (float*)ml_part; p.H = H; p.dl = dl; p.dr = dr; p.page = page;
+    p.kv_fmt = kv_fmt; p.NS = NS; p.scale = scale;
+    const int smem = lsb_mla_decode_smem_bytes(dl, dr);
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaFuncSetAttribute(mla_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        attr_set = true;
+    }
+    mla_decode_kernel<<<dim3(R, (H + kHG - 1) / kHG, NS), 256, smem, st>>>(p);
+    mla_combine_kernel<<<dim3(R, H), 128, 0, st>>>((bf16*)out, (float*)lse, (const float*)o_part, (const float*)ml_part, H, NS, dl);
+    LSB_CHECK_LAUNCH();
+}

@@ -1,0 +1,420 @@
+// Mixture-of-experts routing and the decode-shaped expert FFN.
+//
+//  * router_topk: scoring (sigmoid / softmax / sqrt-softplus) + selection bias + grouped
+//    top-k (group score = sum of the two best biased scores in the group) + top-k by biased
+//    score with ties to the LOWER index + unbiased weights renormalised and scaled; shared
+//    experts appended as extra always-on slots.  Contract taken from the reference's CPU
+//    oracle tests/unit/topk_gating_test.cpp:31-125 (kernel: E/sm120/gating/topk_gating.cu).
+//  * moe_build_groups: counting sort of (row, slot) pairs by expert into groups of <= 4 rows
+//    that share one weight stream (the role of E/smxx/permute/moe_permute.cu, without a
+//    physical permute of activations).
+//  * moe_gateup / moe_down: weight-streaming expert GEMVs with fused SwiGLU(+clamp); experts
+//    are addressed through a slot table so the same kernel serves a fully resident model and
+//    a capped VRAM expert cache.
+//  * moe_combine: out[r] = sum over slots in slot order of w[r][s] * y[r][s]  (fp32, fixed
+//    order => placement-invariant; reference: src/core/expert_device.h:31-52).
+#include "gemv_core.cuh"
+
+namespace lsb {
+
+enum { kScoreSigmoid = 0, kScoreSoftmax = 1, kScoreSqrtSoftplus = 2 };
+
+__global__ void router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int* __restrict__ ids,
+                                   float* __restrict__ wts, int E, int topk, int n_group, int topk_group, int scoring,
+                                   int norm_topk, float scale, int n_shared, int ld_logits) {
+    extern __shared__ float sm[];
+    float* score = sm;            // [E] unbiased
+    float* sel = sm + E;          // [E] biased, -inf when masked/taken
+    __shared__ float red[33];
+    __shared__ int s_best;
+    __shared__ float s_gscore[64];
+    __shared__ int s_pick[64];
+    __shared__ float s_pickw[64];
+    const int r = blockIdx.x, t = threadIdx.x;
+    const float* lg = logits + (size_t)r * ld_logits;
+    pdl_wait();
+    float mx = -INFINITY;
+    if (scoring == kScoreSoftmax) {
+        for (int e = t; e < E; e += blockDim.x) mx = fmaxf(mx, lg[e]);
+        mx = block_max(mx, red);
+    }
+    float ssum = 0.f;
+    for (int e = t; e < E; e += blockDim.x) {
+        const float x = lg[e];
+        float s;
+        if (scoring == kScoreSigmoid) s = 1.f / (1.f + expf(-x));
+        else if (scoring == kScoreSoftmax) s = expf(x - mx);
+        else s = sqrtf(x > 20.f ? x : log1pf(expf(x)));
+        score[e] = s;
+        ssum += s;
+    }
+    if (scoring == kScoreSoftmax) {
+        ssum = block_sum(ssum, red);
+        for (int e = t; e < E; e += blockDim.x) score[e] /= ssum;
+    }
+    __syncthreads();
+    for (int e = t; e < E; e += blockDim.x) sel[e] = score[e] + (bias ? bias[e] : 0.f);
+    __syncthreads();
+    if (n_group > 1) {
+        const int gs = E / n_group;
+        if (t < n_group) {
+            float a = -INFINITY, b = -INFINITY;
+            for (int i = 0; i < gs; ++i) {
+                const float v = sel[t * gs + i];
+                if (v > a) { b = a; a = v; } else if (v > b) b = v;
+            }
+            s_gscore[t] = a + b;
+        }
+        __syncthreads();
+        if (t == 0) {
+            // keep topk_group groups: repeatedly take the best, ties to the lower group
+            bool keep[64];
+            for (int g = 0; g < n_group; ++g) keep[g] = false;
+            for (int k = 0; k < topk_group; ++k) {
+                int best = -1; float bv = -INFINITY;
+                for (int g = 0; g < n_group; ++g)
+                    if (!keep[g] && (best < 0 || s_gscore[g] > bv)) { best = g; bv = s_gscore[g]; }
+                keep[best] = true;
+            }
+            for (int g = 0; g < n_group; ++g) s_pick[g] = keep[g] ? 1 : 0;
+        }
+        __syncthreads();
+        for (int e = t; e < E; e += blockDim.x)
+            if (!s_pick[e / gs]) sel[e] = -INFINITY;
+        __syncthreads();
+    }
+    for (int k = 0; k < topk; ++k) {
+        // block argmax, ties to the lower index
+        float bv = -INFINITY; int bi = 0x7fffffff;
+        for (int e = t; e < E; e += blockDim.x) {
+            const float v = sel[e];
+            if (v > bv || (v == bv && e < bi)) { bv = v; bi = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        const int lane = t & 31, w = t >> 5, nw = (blockDim.x + 31) >> 5;
+        __shared__ float wv[32];
+        __shared__ int wi[32];
+        if (lane == 0) { wv[w] = bv; wi[w] = bi; }
+        __syncthreads();
+        if (t == 0) {
+            float v = wv[0]; int i = wi[0];
+            for (int j = 1; j < nw; ++j)
+                if (wv[j] > v || (wv[j] == v && wi[j] < i)) { v = wv[j]; i = wi[j]; }
+            if (i >= E) i = 0;   // all masked (cannot happen with finite logits)
+            s_best = i;
+            s_pick[k] = i;
+            s_pickw[k] = score[i];
+            sel[i] = -INFINITY;
+        }
+        __syncthreads();
+        (void)s_best;
+    }
+    if (t == 0) {
+        float tot = 0.f;
+        for (int k = 0; k < topk; ++k) tot += s_pickw[k];
+        const int S = topk + n_shared;
+        for (int k = 0; k < topk; ++k) {
+            float w = s_pickw[k];
+            if (norm_topk) w = w / (tot + 1e-20f);
+            ids[r * S + k] = s_pick[k];
+            wts[r * S + k] = w * scale;
+        }
+        for (int k = 0; k < n_shared; ++k) { ids[r * S + topk + k] = E + k; wts[r * S + topk + k] = 1.f; }
+    }
+    pdl_launch_dependents();
+}
+
+// Groups: for every expert (routed and shared) with at least one (row,slot) pair, its pairs
+// in ascending pair order are cut into groups of <= 4.  Output:
+//   group_expert[g], group_n[g], group_pairs[g*4 + i] (pair = row*S + slot), n_groups[0].
+// Single block; deterministic.
+__global__ void moe_build_groups_kernel(const int* __restrict__ ids, int npairs, int E_total, int* __restrict__ group_expert,
+                                        int* __restrict__ group_n, int* __restrict__ group_pairs, int* __restrict__ n_groups,
+                                        int* __restrict__ counts /* scratch [E_total*2+1] */) {
+    pdl_wait();
+    int* cnt = counts;             // [E_total]
+    int* gbase = counts + E_total; // [E_total+1] first group index per expert
+    for (int e = threadIdx.x; e < E_total; e += blockDim.x) cnt[e] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < npairs; i += blockDim.x) {
+        const int e = ids[i];
+        if (e >= 0 && e < E_total) atomicAdd(&cnt[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int g = 0;
+        for (int e = 0; e < E_total; ++e) { gbase[e] = g; g += (cnt[e] + 3) >> 2; }
+        gbase[E_total] = g;
+        n_groups[0] = g;
+    }
+    __syncthreads();
+    // one thread per expert walks the pair list in order (deterministic placement)
+    for (int e = threadIdx.x; e < E_total; e += blockDim.x) {
+        const int c = cnt[e];
+        if (c == 0) continue;
+        int g = gbase[e], k = 0;
+        for (int i = 0; i < npairs && k < c; ++i) {
+            if (ids[i] == e) {
+                group_pairs[(g + (k >> 2)) * 4 + (k & 3)] = i;
+                ++k;
+            }
+        }
+        for (int j = 0; j < (c + 3) >> 2; ++j) {
+            group_expert[g + j] = e;
+            group_n[g + j] = min(4, c - j * 4);
+        }
+    }
+    pdl_launch_dependents();
+}
+
+struct ExpertFmt {
+    int fmt;                 // 0 bf16, 1 fp8 block-128, 2 nvfp4
+    int H, F;                // hidden, expert intermediate
+    long long stride;        // bytes between slots
+    long long off_gate, off_up, off_down;        // weights
+    long long off_sg, off_su, off_sd;            // scales (fp8: fp32 block scales; nvfp4: atoms)
+    long long off_tail;                           // nvfp4: 3 fp32 per-tensor scales (gate, up, down)
+};
+
+template <int FMT> struct RowOf;
+template <> struct RowOf<0> {
+    using T = WRowBf16;
+    static __device__ __forceinline__ T make(const uint8_t* w, const uint8_t*, int n, int K) {
+        return T{reinterpret_cast<const bf16*>(w) + (size_t)n * K};
+    }
+};
+template <> struct RowOf<1> {
+    using T = WRowFp8B;
+    static __device__ __forceinline__ T make(const uint8_t* w, const uint8_t* s, int n, int K) {
+        return T{w + (size_t)n * K, reinterpret_cast<const float*>(s) + (size_t)(n >> 7) * ((K + 127) >> 7)};
+    }
+};
+template <> struct RowOf<2> {
+    using T = WRowNvfp4;
+    static __device__ __forceinline__ T make(const uint8_t* w, const uint8_t* s, int n, int K) {
+        return T{w + (size_t)n * (K >> 1), s, n, ((K >> 4) + 3) >> 2};
+    }
+};
+
+// act[pair][f] = silu(min(g,limit)) * clamp(u) ; g = x[row] . Wgate[f], u = x[row] . Wup[f]
+template <int FMT>
+__global__ void __launch_bounds__(256) moe_gateup_kernel(const bf16* __restrict__ x, const uint8_t* __restrict__ arena,
+                                                         const int* __restrict__ slot_of, ExpertFmt ef,
+                                                         const int* __restrict__ group_expert, const int* __restrict__ group_n,
+                                                         const int* __restrict__ group_pairs, const int* __restrict__ n_groups,
+                                                         bf16* __restrict__ act, int S, float limit, int* __restrict__ miss_flag) {
+    pdl_wait();
+    const int g = blockIdx.y;
+    if (g >= n_groups[0]) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int f = blockIdx.x * 8 + warp;
+    if (f >= ef.F) return;
+    const int e = group_expert[g], n = group_n[g];
+    const int slot = slot_of[e];
+    if (slot < 0) { if (threadIdx.x == 0 && blockIdx.x == 0) atomicExch(miss_flag, e + 1); return; }
+    const uint8_t* base = arena + (size_t)slot * ef.stride;
+    auto rg = RowOf<FMT>::make(base + ef.off_gate, base + ef.off_sg, f, ef.H);
+    auto ru = RowOf<FMT>::make(base + ef.off_up, base + ef.off_su, f, ef.H);
+    float ag[4] = {0, 0, 0, 0}, au[4] = {0, 0, 0, 0};
+    int pr[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) pr[i] = group_pairs[g * 4 + min(i, n - 1)];
+    // rows may be arbitrary: gather pointers instead of a fixed ldx
+    constexpr int E = decltype(rg)::EPL;
+#pragma unroll 2
+    for (int k = lane * E; k + E <= ef.H; k += 32 * E) {
+        float a[E], b[E];
+        rg.load(k, a);
+        ru.load(k, b);
+#pragma unroll
+        for (int m = 0; m < 4; ++m) {
+            if (m < n) {
+                const bf16* xp = x + (size_t)(pr[m] / S) * ef.H + k;
+#pragma unroll
+                for (int e8 = 0; e8 < E; e8 += 8) {
+                    float xf[8];
+                    unpack_bf16x8(__ldg(reinterpret_cast<const uint4*>(xp + e8)), xf);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) { ag[m] = fmaf(a[e8 + i], xf[i], ag[m]); au[m] = fmaf(b[e8 + i], xf[i], au[m]); }
+                }
+            }
+        }
+    }
+    float sg = 1.f, su = 1.f;
+    if (FMT == 2) {
+        const float* tail = reinterpret_cast<const float*>(base + ef.off_tail);
+        sg = tail[0]; su = tail[1];
+    }
+#pragma unroll
+    for (int m = 0; m < 4; ++m) {
+        if (m < n) {
+            float gv = warp_sum(ag[m]) * sg, uv = warp_sum(au[m]) * su;
+            if (limit > 0.f) { gv = fminf(gv, limit); uv = fminf(fmaxf(uv, -limit), limit); }
+            if (lane == 0) act[(size_t)pr[m] * ef.F + f] = __float2bfloat16(siluf_(gv) * uv);
+        }
+    }
+    pdl_launch_dependents();
+}
+
+// y[pair][h] = act[pair] . Wdown[h]   (fp32)
+template <int FMT>
+__global__ void __launch_bounds__(256) moe_down_kernel(const bf16* __restrict__ act, const uint8_t* __restrict__ arena,
+                                                       const int* __restrict__ slot_of, ExpertFmt ef,
+                                                       const int* __restrict__ group_expert, const int* __restrict__ group_n,
+                                                       const int* __restrict__ group_pairs, const int* __restrict__ n_groups,
+                                                       float* __restrict__ y) {
+    pdl_wait();
+    const int g = blockIdx.y;
+    if (g >= n_groups[0]) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int h0 = (blockIdx.x * 8 + warp) * 2;
+    if (h0 >= ef.H) return;
+    const int e = group_expert[g], n = group_n[g];
+    const int slot = slot_of[e];
+    if (slot < 0) return;
+    const uint8_t* base = arena + (size_t)slot * ef.stride;
+    auto r0 = RowOf<FMT>::make(base + ef.off_down, base + ef.off_sd, h0, ef.F);
+    auto r1 = RowOf<FMT>::make(base + ef.off_down, base + ef.off_sd, min(h0 + 1, ef.H - 1), ef.F);
+    float a0[4] = {0, 0, 0, 0}, a1[4] = {0, 0, 0, 0};
+    int pr[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) pr[i] = group_pairs[g * 4 + min(i, n - 1)];
+    constexpr int E = decltype(r0)::EPL;
+#pragma unroll 2
+    for (int k = lane * E; k + E <= ef.F; k += 32 * E) {
+        float a[E], b[E];
+        r0.load(k, a);
+        r1.load(k, b);
+#pragma unroll
+        for (int m = 0; m < 4; ++m) {
+            if (m < n) {
+                const bf16* xp = act + (size_t)pr[m] * ef.F + k;
+#pragma unroll
+                for (int e8 = 0; e8 < E; e8 += 8) {
+                    float xf[8];
+                    unpack_bf16x8(__ldg(reinterpret_cast<const uint4*>(xp + e8)), xf);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) { a0[m] = fmaf(a[e8 + i], xf[i], a0[m]); a1[m] = fmaf(b[e8 + i], xf[i], a1[m]); }
+                }
+            }
+        }
+    }
+    float sd = 1.f;
+    if (FMT == 2) sd = reinterpret_cast<const float*>(base + ef.off_tail)[2];
+#pragma unroll
+    for (int m = 0; m < 4; ++m) {
+        if (m < n) {
+            const float v0 = warp_sum(a0[m]) * sd, v1 = warp_sum(a1[m]) * sd;
+            if (lane == 0) {
+                y[(size_t)pr[m] * ef.H + h0] = v0;
+                if (h0 + 1 < ef.H) y[(size_t)pr[m] * ef.H + h0 + 1] = v1;
+            }
+        }
+    }
+    pdl_launch_dependents();
+}
+
+// out[r][h] = sum_s w[r][s] * y[r*S+s][h], slots in order; experts that were not resident
+// (slot < 0) contribute nothing.  mode 0: write fp32; mode 1: add into out.
+__global__ void moe_combine_kernel(float* __restrict__ out, const float* __restrict__ y, const float* __restrict__ wts,
+                                   const int* __restrict__ ids, const int* __restrict__ slot_of, int S, int H, int accumulate) {
+    pdl_wait();
+    const int r = blockIdx.y;
+    const int h = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (h >= H) return;
+    float4 a = make_float4(0, 0, 0, 0);
+    for (int s = 0; s < S; ++s) {
+        const int e = ids[r * S + s];
+        if (e < 0 || slot_of[e] < 0) continue;
+        const float w = wts[r * S + s];
+        const float4 v = *reinterpret_cast<const float4*>(y + ((size_t)r * S + s) * H + h);
+        a.x = fmaf(w, v.x, a.x); a.y = fmaf(w, v.y, a.y); a.z = fmaf(w, v.z, a.z); a.w = fmaf(w, v.w, a.w);
+    }
+    float4* o = reinterpret_cast<float4*>(out + (size_t)r * H + h);
+    if (accumulate) { float4 p = *o; a.x += p.x; a.y += p.y; a.z += p.z; a.w += p.w; }
+    *o = a;
+    pdl_launch_dependents();
+}
+
+// Dense SwiGLU on a fused [rows, 2F] fp32 projection (gate | up) -> bf16 [rows, F].
+__global__ void swiglu_kernel(bf16* __restrict__ out, const float* __restrict__ gu, int F, float limit) {
+    pdl_wait();
+    const int r = blockIdx.y, f = blockIdx.x * blockDim.x + threadIdx.x;
+    if (f >= F) return;
+    float g = gu[(size_t)r * 2 * F + f], u = gu[(size_t)r * 2 * F + F + f];
+    if (limit > 0.f) { g = fminf(g, limit); u = fminf(fmaxf(u, -limit), limit); }
+    out[(size_t)r * F + f] = __float2bfloat16(siluf_(g) * u);
+    pdl_launch_dependents();
+}
+
+}  // namespace lsb
+using namespace lsb;
+
+LSB_API int lsb_router_topk(const void* logits, const void* bias, void* ids, void* wts, int rows, int E, int topk,
+                            int n_group, int topk_group, int scoring, int norm_topk, float scale, int n_shared,
+                            int ld_logits, void* stream) {
+    if (topk > 64 || n_group > 64 || E > 4096) return -1;
+    router_topk_kernel<<<rows, 256, (size_t)E * 8, (cudaStream_t)stream>>>((const float*)logits, (const float*)bias, (int*)ids,
+                                                                         (float*)wts, E, topk, n_group, topk_group, scoring,
+                                                                         norm_topk, scale, n_shared, ld_logits);
+    LSB_CHECK_LAUNCH();
+}
+
+LSB_API int lsb_moe_build_groups(const void* ids, int npairs, int E_total, void* group_expert, void* group_n,
+                                 void* group_pairs, void* n_groups, void* counts, void* stream) {
+    moe_build_groups_kernel<<<1, 512, 0, (cudaStream_t)stream>>>((const int*)ids, npairs, E_total, (int*)group_expert, (int*)group_n,
+                                                               (int*)group_pairs, (int*)n_groups, (int*)counts);
+    LSB_CHECK_LAUNCH();
+}
+
+LSB_API int lsb_moe_gateup(const void* x, const void* arena, const void* slot_of, const void* fmt_struct,
+                           const void* group_expert, const void* group_n, const void* group_pairs, const void* n_groups,
+                           void* act, int S, int max_groups, float limit, void* miss_flag, void* stream) {
+    ExpertFmt ef = *reinterpret_cast<const ExpertFmt*>(fmt_struct);
+    dim3 grid((ef.F + 7) / 8, max_groups);
+    cudaStream_t st = (cudaStream_t)stream;
+#define ARGS (const bf16*)x, (const uint8_t*)arena, (const int*)slot_of, ef, (const int*)group_expert, (const int*)group_n, \
+             (const int*)group_pairs, (const int*)n_groups, (bf16*)act, S, limit, (int*)miss_flag
+    if (ef.fmt == 0) moe_gateup_kernel<0><<<grid, 256, 0, st>>>(ARGS);
+    else if (ef.fmt == 1) moe_gateup_kernel<1><<<grid, 256, 0, st>>>(ARGS);
+    else if (ef.fmt == 2) moe_gateup_kernel<2><<<grid, 256, 0, st>>>(ARGS);
+    else return -1;
+#undef ARGS
+    LSB_CHECK_LAUNCH();
+}
+
+LSB_API int lsb_moe_down(const void* act, const void* arena, const void* slot_of, const void* fmt_struct,
+                         const void* group_expert, const void* group_n, const void* group_pairs, const void* n_groups,
+                         void* y, int max_groups, void* stream) {
+    ExpertFmt ef = *reinterpret_cast<const ExpertFmt*>(fmt_struct);
+    dim3 grid((ef.H + 15) / 16, max_groups);
+    cudaStream_t st = (cudaStream_t)stream;
+#define ARGS (const bf16*)act, (const uint8_t*)arena, (const int*)slot_of, ef, (const int*)group_expert, (const int*)group_n, \
+             (const int*)group_pairs, (const int*)n_groups, (float*)y
+    if (ef.fmt == 0) moe_down_kernel<0><<<grid, 256, 0, st>>>(ARGS);
+    else if (ef.fmt == 1) moe_down_kernel<1><<<grid, 256, 0, st>>>(ARGS);
+    else if (ef.fmt == 2) moe_down_kernel<2><<<grid, 256, 0, st>>>(ARGS);
+    else return -1;
+#undef ARGS
+    LSB_CHECK_LAUNCH();
+}
+
+LSB_API int lsb_moe_combine(void* out, const void* y, const void* wts, const void* ids, const void* slot_of, int rows,
+                            int S, int H, int accumulate, void* stream) {
+    if (H % 4) return -1;
+    dim3 grid((H / 4 + 255) / 256, rows);
+    moe_combine_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((float*)out, (const float*)y, (const float*)wts, (const int*)ids,
+                                                             (const int*)slot_of, S, H, accumulate);
+    LSB_CHECK_LAUNCH();
+}
+
+LSB_API int lsb_swiglu(void* out, const void* gu, int rows, int F, float limit, void* stream) {
+    dim3 grid((F + 255) / 256, rows);
+    swiglu_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((bf16*)out, (const float*)gu, F, limit);
+    LSB_CHECK_LAUNCH();
+}

@@ -1,0 +1,273 @@
+// RMSNorm family and the hyper-connection (mHC) residual-stream kernels.
+//
+// RMSNorm: plain, strided, fused residual add (reference: src/compute/kernels/sm120/norm/rmsnorm.cu:71-164).
+// mHC: `hc_mult` residual streams per token; "pre" mixes them into the sublayer input
+// (sigmoid gates, Sinkhorn-normalised stream-mixing matrix), "post" writes the sublayer
+// output back (reference: launchers in src/compute/kernels/mhc/mhc.h, math in
+// tools/glm53_numpy_ref.py:128-179).  Here post of sublayer i and pre of sublayer i+1
+// are one fused pass: a partial kernel spread over the hidden dimension followed by a
+// one-block-per-token finalize that also applies the sublayer's input RMSNorm.
+#include "common.cuh"
+
+namespace lsb {
+
+template <typename TIn>
+__device__ __forceinline__ float ld_as_float(const TIn* p, int i);
+template <>
+__device__ __forceinline__ float ld_as_float<float>(const float* p, int i) { return p[i]; }
+template <>
+__device__ __forceinline__ float ld_as_float<bf16>(const bf16* p, int i) { return __bfloat162float(p[i]); }
+
+// out[r] = x[r] / sqrt(mean(x[r]^2) + eps) * w ; optional: resid[r] += x[r] first and
+// normalise the sum (resid updated in place, fp32).
+template <typename TIn, bool ADD>
+__global__ void rmsnorm_kernel(bf16* __restrict__ out, const TIn* __restrict__ x, float* __restrict__ resid,
+                               const float* __restrict__ w, int dim, int ldx, int ldo, int ldr, float eps,
+                               float* __restrict__ out_f32) {
+    __shared__ float red[33];
+    extern __shared__ float row[];
+    const int r = blockIdx.x;
+    const TIn* xr = x + (size_t)r * ldx;
+    pdl_wait();
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+        float v = ld_as_float<TIn>(xr, i);
+        if (ADD) {
+            v += resid[(size_t)r * ldr + i];
+            resid[(size_t)r * ldr + i] = v;
+        }
+        row[i] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / (float)dim + eps);
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+        const float v = row[i] * inv * w[i];
+        out[(size_t)r * ldo + i] = __float2bfloat16(v);
+        if (out_f32) out_f32[(size_t)r * ldo + i] = v;
+    }
+    pdl_launch_dependents();
+}
+
+constexpr int kHcMax = 4;           // residual streams
+constexpr int kHcOut = 2 * kHcMax + kHcMax * kHcMax;   // 24 mixing logits
+constexpr int kHcChunk = 128;       // hidden columns per partial block
+
+// Pass 1 of post+pre.  mode 0: residual[j] = x (replicate, first layer);
+// mode 1: residual[j] = post[j]*x + sum_i comb[i][j]*residual[i].
+// Then partial mixing logits and partial sum of squares of the NEW residual over this
+// block's hidden columns: part[r][chunk][0..23] logits, [24] sum of squares.
+__global__ void __launch_bounds__(kHcChunk) mhc_post_partial_kernel(float* __restrict__ residual, const float* __restrict__ x,
+                                                                    const float* __restrict__ post, const float* __restrict__ comb,
+                                                                    const float* __restrict__ fn, float* __restrict__ part,
+                                                                    int hidden, int n, int mode) {
+    __shared__ float red[4][kHcOut + 1];
+    const int r = blockIdx.x, c = blockIdx.y, h = c * kHcChunk + threadIdx.x;
+    const int nout = 2 * n + n * n;
+    pdl_wait();
+    float res[kHcMax];
+    float* rp = residual + (size_t)r * n * hidden;
+    const float xv = x[(size_t)r * hidden + h];
+    if (mode == 0) {
+#pragma unroll
+        for (int j = 0; j < kHcMax; ++j) res[j] = xv;
+    } else {
+        float old[kHcMax];
+#pragma unroll
+        for (int i = 0; i < kHcMax; ++i) old[i] = i < n ? rp[(size_t)i * hidden + h] : 0.f;
+#pragma unroll
+        for (int j = 0; j < kHcMax; ++j) {
+            float a = 0.f;
+            if (j < n) {
+                a = post[r * n + j] * xv;
+                for (int i = 0; i < n; ++i) a += comb[(r * n + i) * n + j] * old[i];
+            }
+            res[j] = a;
+        }
+    }
+    float acc[kHcOut + 1];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < kHcMax; ++j)
+        if (j < n) {
+            rp[(size_t)j * hidden + h] = res[j];
+            ss += res[j] * res[j];
+        }
+#pragma unroll
+    for (int o = 0; o < kHcOut; ++o) {
+        float a = 0.f;
+        if (o < nout) {
+            const float* f = fn + (size_t)o * n * hidden + h;
+#pragma unroll
+            for (int j = 0; j < kHcMax; ++j)
+                if (j < n) a += res[j] * f[(size_t)j * hidden];
+        }
+        acc[o] = a;
+    }
+    acc[kHcOut] = ss;
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 0; o <= kHcOut; ++o) {
+        const float v = warp_sum(acc[o]);
+        if (lane == 0) red[w][o] = v;
+    }
+    __syncthreads();
+    if (threadIdx.x <= kHcOut) {
+        const float v = red[0][threadIdx.x] + red[1][threadIdx.x] + red[2][threadIdx.x] + red[3][threadIdx.x];
+        part[((size_t)r * gridDim.y + c) * (kHcOut + 1) + threadIdx.x] = v;
+    }
+    pdl_launch_dependents();
+}
+
+// Pass 2: reduce the partials in chunk order, form pre/post gates and the Sinkhorn-
+// normalised mixing matrix, then out = RMSNorm(sum_j pre[j]*residual[j]) * w (bf16).
+__global__ void mhc_finalize_kernel(bf16* __restrict__ out, const float* __restrict__ residual, const float* __restrict__ part,
+                                    const float* __restrict__ hc_scale, const float* __restrict__ hc_base,
+                                    const float* __restrict__ norm_w, float* __restrict__ post_out, float* __restrict__ comb_out,
+                                    int hidden, int n, int nchunks, int iters, float hc_eps, float rms_eps, float post_mult) {
+    __shared__ float red[33];
+    __shared__ float mix[kHcOut + 1];
+    __shared__ float pre[kHcMax];
+    extern __shared__ float row[];
+    const int r = blockIdx.x;
+    const int nout = 2 * n + n * n;
+    pdl_wait();
+    if (threadIdx.x <= kHcOut) {
+        float a = 0.f;
+        for (int c = 0; c < nchunks; ++c) a += part[((size_t)r * nchunks + c) * (kHcOut + 1) + threadIdx.x];
+        mix[threadIdx.x] = a;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const float inv = rsqrtf(mix[kHcOut] / (float)(n * hidden) + rms_eps);
+        float m[kHcOut];
+        for (int o = 0; o < nout; ++o) m[o] = mix[o] * inv;
+        for (int j = 0; j < n; ++j) {
+            pre[j] = sigmoidf_(m[j] * hc_scale[0] + hc_base[j]) + hc_eps;
+            post_out[r * n + j] = sigmoidf_(m[n + j] * hc_scale[1] + hc_base[n + j]) * post_mult;
+        }
+        float cm[kHcMax][kHcMax];
+        for (int i = 0; i < n; ++i) {
+            float mx = -INFINITY;
+            for (int j = 0; j < n; ++j) {
+                cm[i][j] = m[2 * n + i * n + j] * hc_scale[2] + hc_base[2 * n + i * n + j];
+                mx = fmaxf(mx, cm[i][j]);
+            }
+            float s = 0.f;
+            for (int j = 0; j < n; ++j) { cm[i][j] = expf(cm[i][j] - mx); s += cm[i][j]; }
+            for (int j = 0; j < n; ++j) cm[i][j] = cm[i][j] / s + hc_eps;
+        }
+        // column normalise, then (iters-1) x (row normalise, column normalise)
+        for (int j = 0; j < n; ++j) {
+            float s = 0.f;
+            for (int i = 0; i < n; ++i) s += cm[i][j];
+            for (int i = 0; i < n; ++i) cm[i][j] /= (s + hc_eps);
+        }
+        for (int it = 1; it < iters; ++it) {
+            for (int i = 0; i < n; ++i) {
+                float s = 0.f;
+                for (int j = 0; j < n; ++j) s += cm[i][j];
+                for (int j = 0; j < n; ++j) cm[i][j] /= (s + hc_eps);
+            }
+            for (int j = 0; j < n; ++j) {
+                float s = 0.f;
+                for (int i = 0; i < n; ++i) s += cm[i][j];
+                for (int i = 0; i < n; ++i) cm[i][j] /= (s + hc_eps);
+            }
+        }
+        for (int i = 0; i < n; ++i)
+            for (int j = 0; j < n; ++j) comb_out[(r * n + i) * n + j] = cm[i][j];
+    }
+    __syncthreads();
+    const float* rp = residual + (size_t)r * n * hidden;
+    float ss = 0.f;
+    for (int h = threadIdx.x; h < hidden; h += blockDim.x) {
+        float a = 0.f;
+        for (int j = 0; j < n; ++j) a += pre[j] * rp[(size_t)j * hidden + h];
+        row[h] = a;
+        ss += a * a;
+    }
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / (float)hidden + rms_eps);
+    for (int h = threadIdx.x; h < hidden; h += blockDim.x) out[(size_t)r * hidden + h] = __float2bfloat16(row[h] * inv * norm_w[h]);
+    pdl_launch_dependents();
+}
+
+// Last layer: out = RMSNorm(mean_j(post[j]*x + sum_i comb[i][j]*residual[i])) * w.
+__global__ void mhc_contract_norm_kernel(bf16* __restrict__ out, const float* __restrict__ residual, const float* __restrict__ x,
+                                         const float* __restrict__ post, const float* __restrict__ comb,
+                                         const float* __restrict__ norm_w, int hidden, int n, float rms_eps) {
+    __shared__ float red[33];
+    extern __shared__ float row[];
+    const int r = blockIdx.x;
+    pdl_wait();
+    const float* rp = residual + (size_t)r * n * hidden;
+    float pm = 0.f, cw[kHcMax];
+    for (int j = 0; j < n; ++j) pm += post[r * n + j];
+    for (int i = 0; i < n; ++i) {
+        float s = 0.f;
+        for (int j = 0; j < n; ++j) s += comb[(r * n + i) * n + j];
+        cw[i] = s;
+    }
+    float ss = 0.f;
+    for (int h = threadIdx.x; h < hidden; h += blockDim.x) {
+        float a = pm * x[(size_t)r * hidden + h];
+        for (int i = 0; i < n; ++i) a += cw[i] * rp[(size_t)i * hidden + h];
+        a /= (float)n;
+        row[h] = a;
+        ss += a * a;
+    }
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / (float)hidden + rms_eps);
+    for (int h = threadIdx.x; h < hidden; h += blockDim.x) out[(size_t)r * hidden + h] = __float2bfloat16(row[h] * inv * norm_w[h]);
+    pdl_launch_dependents();
+}
+
+}  // namespace lsb
+using namespace lsb;
+
+LSB_API int lsb_rmsnorm(void* out, const void* x, const void* w, int rows, int dim, int ldx, int ldo, float eps,
+                        int x_is_f32, void* out_f32, void* stream) {
+    cudaStream_t st = (cudaStream_t)stream;
+    const int thr = dim >= 2048 ? 512 : 256;
+    const size_t sm = (size_t)dim * 4;
+    if (x_is_f32)
+        rmsnorm_kernel<float, false><<<rows, thr, sm, st>>>((bf16*)out, (const float*)x, nullptr, (const float*)w, dim, ldx, ldo, 0, eps, (float*)out_f32);
+    else
+        rmsnorm_kernel<bf16, false><<<rows, thr, sm, st>>>((bf16*)out, (const bf16*)x, nullptr, (const float*)w, dim, ldx, ldo, 0, eps, (float*)out_f32);
+    LSB_CHECK_LAUNCH();
+}
+
+// resid (fp32, in place) += x (fp32); out = RMSNorm(resid) * w as bf16.
+LSB_API int lsb_add_rmsnorm(void* out, void* resid, const void* x, const void* w, int rows, int dim, float eps, void* stream) {
+    const int thr = dim >= 2048 ? 512 : 256;
+    rmsnorm_kernel<float, true><<<rows, thr, (size_t)dim * 4, (cudaStream_t)stream>>>((bf16*)out, (const float*)x, (float*)resid,
+                                                                                   (const float*)w, dim, dim, dim, dim, eps, nullptr);
+    LSB_CHECK_LAUNCH();
+}
+
+// residual: fp32 [rows, n, hidden] updated in place; x: fp32 [rows, hidden] sublayer output
+// (or the embedding when mode == 0); post/comb: state from the previous finalize (in) and
+// for the next post (out, same buffers).  part: scratch fp32 [rows, hidden/128, 25].
+LSB_API int lsb_mhc_post_pre(void* out_x, void* residual, const void* x, void* post, void* comb, const void* fn,
+                             const void* hc_scale, const void* hc_base, const void* norm_w, void* part, int rows,
+                             int hidden, int n, int mode, int iters, float hc_eps, float rms_eps, float post_mult,
+                             void* stream) {
+    if (hidden % kHcChunk || n > kHcMax) return -1;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int nchunks = hidden / kHcChunk;
+    mhc_post_partial_kernel<<<dim3(rows, nchunks), kHcChunk, 0, st>>>((float*)residual, (const float*)x, (const float*)post,
+                                                                    (const float*)comb, (const float*)fn, (float*)part, hidden, n, mode);
+    mhc_finalize_kernel<<<rows, 512, (size_t)hidden * 4, st>>>((bf16*)out_x, (const float*)residual, (const float*)part,
+                                                              (const float*)hc_scale, (const float*)hc_base, (const float*)norm_w,
+                                                              (float*)post, (float*)comb, hidden, n, nchunks, iters, hc_eps, rms_eps, post_mult);
+    LSB_CHECK_LAUNCH();
+}
+
+LSB_API int lsb_mhc_contract_norm(void* out, const void* residual, const void* x, const void* post, const void* comb,
+                                  const void* norm_w, int rows, int hidden, int n, float rms_eps, void* stream) {
+    mhc_contract_norm_kernel<<<rows, 512, (size_t)hidden * 4, (cudaStream_t)stream>>>((bf16*)out, (const float*)residual, (const float*)x,
+                                                                                      (const float*)post, (const float*)comb,
+                                                                                      (const float*)norm_w, hidden, n, rms_eps);
+    LSB_CHECK_LAUNCH();
+}

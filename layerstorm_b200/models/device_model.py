@@ -1,0 +1,715 @@
+"""Device-resident model: weights in the kernels' storage formats plus the per-step forward
+pass expressed as a fixed sequence of hand-written kernel launches (CUDA-graph capturable:
+all shapes are static for a given workspace, all data-dependent quantities live on the
+device).
+
+Weight formats: bf16, FP8 e4m3 with 128x128 block scales, NVFP4 (16-wide e4m3 scales in the
+128x4 atom layout + per-tensor scale).  Routed and shared experts live in a slotted arena
+per MoE layer (``slot_of[expert] -> slot`` or -1), which is what the VRAM expert cache
+manipulates.  Reference structure: LoadedModel / LayerWeights (src/model/weight_loader),
+the per-layer bodies src/daemon/attention/arch_mla.cpp, arch_glm5_next.cpp and
+src/daemon/moe/moe_driver.cpp:382-1745.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from dataclasses import dataclass
+from typing import Dict, List, Optional
+
+import torch
+
+from ..formats import quant
+from ..ops import _native as nat
+from .config import ModelConfig
+
+KV_FMT = {"bf16": 0, "fp8": 1}
+EXPERT_FMT = {"bf16": 0, "fp8_e4m3": 1, "nvfp4": 2}
+
+
+class ExpertFmt(ctypes.Structure):
+    _fields_ = [("fmt", ctypes.c_int), ("H", ctypes.c_int), ("F", ctypes.c_int),
+                ("stride", ctypes.c_longlong),
+                ("off_gate", ctypes.c_longlong), ("off_up", ctypes.c_longlong), ("off_down", ctypes.c_longlong),
+                ("off_sg", ctypes.c_longlong), ("off_su", ctypes.c_longlong), ("off_sd", ctypes.c_longlong),
+                ("off_tail", ctypes.c_longlong)]
+
+
+def _align(x, a):
+    return (x + a - 1) // a * a
+
+
+def expert_layout(fmt: str, H: int, F: int) -> ExpertFmt:
+    """Byte layout of one expert slot (gate | up | down weights, then their scales, then a tail
+    of per-tensor scales), slot stride 4096-aligned like the reference's prepacked slots
+    (src/model/weight_pipeline/prepacked_format.h:44-52)."""
+    ef = ExpertFmt()
+    ef.fmt, ef.H, ef.F = EXPERT_FMT[fmt], H, F
+    if fmt == "bf16":
+        wb = H * F * 2
+        ef.off_gate, ef.off_up, ef.off_down = 0, wb, 2 * wb
+        ef.off_sg = ef.off_su = ef.off_sd = ef.off_tail = 3 * wb
+        end = 3 * wb
+    elif fmt == "fp8_e4m3":
+        wb = H * F
+        ef.off_gate, ef.off_up, ef.off_down = 0, wb, 2 * wb
+        sgu = ((F + 127) // 128) * ((H + 127) // 128) * 4
+        sd = ((H + 127) // 128) * ((F + 127) // 128) * 4
+        ef.off_sg = _align(3 * wb, 256)
+        ef.off_su = ef.off_sg + _align(sgu, 256)
+        ef.off_sd = ef.off_su + _align(sgu, 256)
+        ef.off_tail = ef.off_sd + _align(sd, 256)
+        end = ef.off_tail
+    elif fmt == "nvfp4":
+        wb = H * F // 2
+        ef.off_gate, ef.off_up, ef.off_down = 0, wb, 2 * wb
+        sgu = quant.sf_atom_size(F, H)
+        sd = quant.sf_atom_size(H, F)
+        ef.off_sg = _align(3 * wb, 512)
+        ef.off_su = ef.off_sg + sgu
+        ef.off_sd = ef.off_su + sgu
+        ef.off_tail = ef.off_sd + sd
+        end = ef.off_tail + 32
+    else:
+        raise ValueError(fmt)
+    ef.stride = _align(end, 4096)
+    return ef
+
+
+class QLinear:
+    """A weight matrix [N, K] in a device storage format, applied to bf16 activations."""
+
+    def __init__(self, fmt: str, N: int, K: int, w: torch.Tensor, scales: Optional[torch.Tensor] = None, alpha: float = 1.0):
+        self.fmt, self.N, self.K, self.w, self.scales, self.alpha = fmt, N, K, w, scales, alpha
+
+    @staticmethod
+    def from_float(wf: torch.Tensor, fmt: str, device) -> "QLinear":
+        N, K = wf.shape
+        wf = wf.to(device)
+        if fmt == "bf16":
+            return QLinear("bf16", N, K, wf.to(torch.bfloat16).contiguous())
+        if fmt == "f32":
+            return QLinear("f32", N, K, wf.float().contiguous())
+        if fmt == "fp8_e4m3":
+            q, s = quant.quantize_fp8_block(wf)
+            return QLinear("fp8_e4m3", N, K, q, s)
+        if fmt == "nvfp4":
+            q, a, gs = quant.quantize_nvfp4(wf)
+            return QLinear("nvfp4", N, K, q, a, gs)
+        raise ValueError(fmt)
+
+    @staticmethod
+    def random(N: int, K: int, fmt: str, device, std: float = 0.02, gen=None) -> "QLinear":
+        """Random-init directly in storage format (no fp32 master copy)."""
+        if fmt == "bf16":
+            w = torch.empty(N, K, dtype=torch.bfloat16, device=device)
+            w.normal_(0.0, std, generator=gen)
+            return QLinear("bf16", N, K, w)
+        if fmt == "f32":
+            w = torch.empty(N, K, dtype=torch.float32, device=device)
+            w.normal_(0.0, std, generator=gen)
+            return QLinear("f32", N, K, w)
+        if fmt == "fp8_e4m3":
+            w = torch.empty(N, K, dtype=torch.uint8, device=device)
+            w.random_(0, 256, generator=gen)
+            w &= 0xBF   # keep |value| <= 1.875: clear the top exponent bit, never a NaN code
+            s = torch.full(((N + 127) // 128, (K + 127) // 128), std / 0.6, dtype=torch.float32, device=device)
+            return QLinear("fp8_e4m3", N, K, w, s)
+        if fmt == "nvfp4":
+            w = torch.empty(N, K // 2, dtype=torch.uint8, device=device)
+            a = torch.empty(quant.sf_atom_size(N, K), dtype=torch.uint8, device=device)
+            gs = quant.random_nvfp4_(w, a, gen) * (std / 0.02)
+            return QLinear("nvfp4", N, K, w, a, gs)
+        raise ValueError(fmt)
+
+    def dequant(self) -> torch.Tensor:
+        if self.fmt in ("bf16", "f32"):
+            return self.w.float()
+        if self.fmt == "fp8_e4m3":
+            return quant.dequantize_fp8_block(self.w, self.scales)
+        return quant.dequantize_nvfp4(self.w, self.scales, self.alpha, self.N, self.K)
+
+    def nbytes(self) -> int:
+        return self.w.numel() * self.w.element_size() + (self.scales.numel() * self.scales.element_size() if self.scales is not None else 0)
+
+    def __call__(self, out: torch.Tensor, x: torch.Tensor, M: int, ldx: Optional[int] = None, ldo: Optional[int] = None,
+                 bias: Optional[torch.Tensor] = None):
+        ldx = ldx if ldx is not None else self.K
+        ldo = ldo if ldo is not None else self.N
+        ob = 1 if out.dtype == torch.bfloat16 else 0
+        if self.fmt == "bf16":
+            nat.call("lsb_gemv_bf16", out, x, self.w, bias, M, self.N, self.K, ldx, self.K, ldo, 1.0, ob)
+        elif self.fmt == "f32":
+            nat.call("lsb_gemv_f32w", out, x, self.w, bias, M, self.N, self.K, ldx, self.K, ldo, 1.0, ob)
+        elif self.fmt == "fp8_e4m3":
+            nat.call("lsb_gemv_fp8b", out, x, self.w, self.scales, bias, M, self.N, self.K, ldx, ldo, 1.0, ob)
+        else:
+            nat.call("lsb_gemv_nvfp4", out, x, self.w, self.scales, bias, M, self.N, self.K, ldx, ldo, self.alpha, ob)
+
+
+@dataclass
+class MlaOffsets:
+    qa: int = 0
+    kv: int = 0
+    idx_k: int = -1
+    idx_w: int = -1
+    idx_gate: int = -1
+    total: int = 0
+    q_idx: int = -1      # offset of indexer q inside the fused q_b output
+    qb_total: int = 0
+
+
+class ExpertArena:
+    """Slotted expert storage of one MoE layer.  ``slot_of`` maps expert id (routed 0..E-1, shared
+    E..E+n_shared-1) to a slot or -1."""
+
+    def __init__(self, ef: ExpertFmt, n_slots: int, n_experts_total: int, device):
+        self.ef = ef
+        self.n_slots = n_slots
+        self.data = torch.empty(n_slots, ef.stride, dtype=torch.uint8, device=device)
+        self.slot_of = torch.full((n_experts_total,), -1, dtype=torch.int32, device=device)
+
+    def slot_view(self, slot: int) -> torch.Tensor:
+        return self.data[slot]
+
+    def write_expert(self, slot: int, gate: QLinear, up: QLinear, down: QLinear):
+        ef, v = self.ef, self.data[slot]
+
+        def put(off, t):
+            b = t.contiguous().view(torch.uint8).reshape(-1)
+            v[off: off + b.numel()] = b
+
+        put(ef.off_gate, gate.w); put(ef.off_up, up.w); put(ef.off_down, down.w)
+        if gate.scales is not None:
+            put(ef.off_sg, gate.scales); put(ef.off_su, up.scales); put(ef.off_sd, down.scales)
+        if ef.fmt == 2:
+            put(ef.off_tail, torch.tensor([gate.alpha, up.alpha, down.alpha], dtype=torch.float32, device=v.device))
+
+    def read_expert(self, slot: int, fmt: str):
+        """Dequantised (gate, up, down) fp32 matrices of a slot (tests / oracle)."""
+        ef, v = self.ef, self.data[slot]
+        H, F = ef.H, ef.F
+        out = []
+        for nm, (N, K), ow, os_ in (("gate", (F, H), ef.off_gate, ef.off_sg), ("up", (F, H), ef.off_up, ef.off_su),
+                                   ("down", (H, F), ef.off_down, ef.off_sd)):
+            if fmt == "bf16":
+                out.append(v[ow: ow + N * K * 2].view(torch.bfloat16).view(N, K).float())
+            elif fmt == "fp8_e4m3":
+                nb = ((N + 127) // 128) * ((K + 127) // 128)
+                s = v[os_: os_ + nb * 4].view(torch.float32).view((N + 127) // 128, (K + 127) // 128)
+                out.append(quant.dequantize_fp8_block(v[ow: ow + N * K].view(N, K), s))
+            else:
+                tail = v[ef.off_tail: ef.off_tail + 12].view(torch.float32)
+                i = {"gate": 0, "up": 1, "down": 2}[nm]
+                out.append(quant.dequantize_nvfp4(v[ow: ow + N * K // 2].view(N, K // 2), v[os_: os_ + quant.sf_atom_size(N, K)],
+                                                  float(tail[i]), N, K))
+        return out
+
+
+class Workspace:
+    """Static activation buffers for steps of up to ``R`` rows."""
+
+    def __init__(self, m: "DeviceModel", R: int, n_logit_rows: int, max_ctx: int):
+        cfg, dev = m.cfg, m.device
+        f32, b16, i32 = torch.float32, torch.bfloat16, torch.int32
+        H, n = cfg.hidden, cfg.hc_mult
+        self.R = R
+
+        def z(*shape, dtype=f32):
+            return torch.zeros(*shape, dtype=dtype, device=dev)
+
+        # step inputs: one packed int32 buffer so a step needs a single host->device copy
+        self.inp = z(9, R, dtype=i32)
+        self.inp[1].fill_(-1)
+        (self.tok, self.row_seq, self.row_pos, self.row_len, self.row_slot, self.n_entries,
+         self.seq_row0, self.seq_nrows, self.seq_slot) = (self.inp[j] for j in range(9))
+        # activations
+        self.x = z(R, H, dtype=b16)
+        self.sub = z(R, H)
+        self.resid = z(R, n, H)
+        self.post = z(R, n); self.comb = z(R, n, n)
+        self.part = z(R, max(1, H // 128), 25)
+        self.proj = z(R, m.max_proj)
+        C = cfg.kda_heads * cfg.kda_head_dim
+        self.kda_out = z(R, max(C, 1), dtype=b16)
+        Hh = cfg.n_heads
+        self.q_c = z(R, max(cfg.q_lora, 1), dtype=b16)
+        self.qproj = z(R, m.max_qb, dtype=b16)
+        self.q_abs = z(R, Hh, cfg.kv_lora + cfg.qk_rope, dtype=b16)
+        self.o_lat = z(R, Hh, cfg.kv_lora, dtype=b16)
+        hg = (Hh + 15) // 16
+        self.NS = max(1, min(32, 296 // max(1, R * hg)))
+        self.o_part = z(R, Hh, self.NS, cfg.kv_lora)
+        self.ml_part = z(R, Hh, self.NS, 2)
+        self.attn_v = z(R, Hh * cfg.v_head, dtype=b16)
+        if cfg.has_indexer:
+            P = cfg.index_kpool
+            self.max_entries = (max_ctx + P - 1) // P
+            self.scores = z(R, self.max_entries)
+            self.sel_ld = cfg.index_topk + P
+            self.sel_idx = z(R, self.sel_ld, dtype=i32)
+            self.sel_cnt = z(R, dtype=i32)
+            self.q_idx = z(R, cfg.index_n_heads, cfg.index_head_dim, dtype=b16)
+            self.idx_w = z(R, cfg.index_n_heads)
+        # FFN
+        F = max(cfg.dense_inter, 1)
+        self.gu = z(R, 2 * F)
+        self.act_d = z(R, F, dtype=b16)
+        if cfg.n_routed > 0:
+            S = cfg.top_k + cfg.n_shared
+            E_total = cfg.n_routed + cfg.n_shared
+            self.S = S
+            self.logits_r = z(R, cfg.n_routed)
+            self.ids = z(R, S, dtype=i32); self.wts = z(R, S)
+            self.max_groups = min(R * S, (R * S + 3) // 4 + E_total)
+            self.group_expert = z(self.max_groups, dtype=i32); self.group_n = z(self.max_groups, dtype=i32)
+            self.group_pairs = z(self.max_groups * 4, dtype=i32); self.n_groups = z(1, dtype=i32)
+            self.counts = z(2 * E_total + 2, dtype=i32)
+            self.act = z(R * S, cfg.moe_inter, dtype=b16)
+            self.y = z(R * S, H)
+            self.miss = z(1, dtype=i32)
+        # outputs
+        self.n_logit_rows = n_logit_rows
+        self.logits = z(n_logit_rows, cfg.vocab)
+        self.amax_part = torch.zeros(n_logit_rows, 64, dtype=torch.int64, device=dev)
+        self.out_tok = z(n_logit_rows, dtype=i32)
+        self.out_val = z(n_logit_rows)
+
+
+class DeviceModel:
+    def __init__(self, cfg: ModelConfig, device="cuda", kv_fmt: str = "fp8", page: int = 64):
+        self.cfg, self.device = cfg, torch.device(device)
+        self.kv_fmt, self.page = kv_fmt, page
+        assert page % max(cfg.index_kpool, 1) == 0
+        self.layers: List[dict] = []
+        self.embed = None
+        self.head: Optional[QLinear] = None
+        self.final_norm = None
+        self.max_proj = 1
+        self.max_qb = 1
+        self.kv_row_bytes = nat.call("lsb_kv_row_bytes", KV_FMT[kv_fmt], cfg.kv_lora, cfg.qk_rope)
+        self.idx_row_bytes = nat.call("lsb_indexer_row_bytes")
+        inv = cfg.rope_inv_freq()
+        self.inv_freq = torch.tensor(inv if inv else [0.0], dtype=torch.float32, device=self.device)
+        inv_i = cfg.rope_inv_freq(cfg.index_rope_dim) if cfg.index_rope_dim else [0.0]
+        self.inv_freq_idx = torch.tensor(inv_i, dtype=torch.float32, device=self.device)
+        # caches (allocated by alloc_cache)
+        self.kv_cache: Dict[int, torch.Tensor] = {}
+        self.idx_cache: Dict[int, torch.Tensor] = {}
+        self.idx_tail: Dict[int, torch.Tensor] = {}
+        self.kda_state: Dict[int, torch.Tensor] = {}
+        self.kda_conv: Dict[int, torch.Tensor] = {}
+        self.block_table = None
+        self.kernel_launches = 0
+
+    # ------------------------------------------------------------------ construction
+    def _lin(self, get, name, fmt):
+        return QLinear.from_float(get(name), fmt, self.device)
+
+    @classmethod
+    def from_state_dict(cls, cfg: ModelConfig, w: Dict[str, torch.Tensor], device="cuda", kv_fmt="fp8", page=64,
+                        expert_quant: Optional[str] = None, dense_quant: Optional[str] = None) -> "DeviceModel":
+        m = cls(cfg, device, kv_fmt, page)
+        dev = m.device
+        eq = expert_quant or cfg.expert_quant
+        dq = dense_quant or cfg.dense_quant
+        if eq.startswith("gguf"):
+            eq = "bf16"
+        f32 = lambda t: t.to(dev).float().contiguous()
+        m.embed = w["embed.weight"].to(dev).to(torch.bfloat16).contiguous()
+        m.head = QLinear.from_float(w["head.weight"], "bf16", dev)
+        m.final_norm = f32(w["final_norm.weight"])
+        for i in range(cfg.n_layers):
+            p = f"layers.{i}."
+            L: dict = {"attn_norm": f32(w[p + "attn_norm.weight"]), "ffn_norm": f32(w[p + "ffn_norm.weight"])}
+            if cfg.mhc:
+                for nm in ("hc_attn", "hc_ffn"):
+                    L[nm] = (f32(w[p + nm + ".fn"]), f32(w[p + nm + ".scale"]), f32(w[p + nm + ".base"]))
+            if cfg.is_kda_layer(i):
+                k = p + "kda."
+                L["kda_in"] = QLinear.from_float(torch.cat([w[k + "q"], w[k + "k"], w[k + "v"], w[k + "beta"], w[k + "f_a"], w[k + "g_a"]], 0), dq, dev)
+                L["kda_fb"] = w[k + "f_b"].to(dev).to(torch.bfloat16).contiguous()
+                L["kda_gb"] = w[k + "g_b"].to(dev).to(torch.bfloat16).contiguous()
+                for nm in ("conv_q", "conv_k", "conv_v", "dt_bias", "o_norm"):
+                    L["kda_" + nm] = f32(w[k + nm])
+                L["kda_a_exp"] = torch.exp(f32(w[k + "a_log"]))
+                L["kda_o"] = QLinear.from_float(w[k + "o"], dq, dev)
+            else:
+                a = p + "attn."
+                parts = [w[a + "q_a"], w[a + "kv_a"]]
+                qb_parts = [w[a + "q_b"]]
+                has_idx = cfg.has_indexer and cfg.index_source_layer(i) == i
+                if has_idx:
+                    x = p + "indexer."
+                    parts += [w[x + "wk"], w[x + "weights_proj"]]
+                    if cfg.index_kpool > 1:
+                        parts.append(w[x + "gate"])
+                        L["idx_ape"] = f32(w[x + "ape"])
+                    qb_parts.append(w[x + "wq_b"])
+                    L["idx_ln_w"] = f32(w[x + "k_norm.weight"]); L["idx_ln_b"] = f32(w[x + "k_norm.bias"])
+                L["mla_in"] = QLinear.from_float(torch.cat(parts, 0), dq, dev)
+                L["mla_qb"] = QLinear.from_float(torch.cat(qb_parts, 0), dq, dev)
+                L["qa_norm"] = f32(w[a + "q_a_norm"]); L["kv_norm"] = f32(w[a + "kv_a_norm"])
+                L["k_b"] = w[a + "k_b"].to(dev).to(torch.bfloat16).contiguous()
+                L["v_b"] = w[a + "v_b"].to(dev).to(torch.bfloat16).contiguous()
+                L["mla_o"] = QLinear.from_float(w[a + "o"], dq, dev)
+            if cfg.is_moe_layer(i):
+                mo = p + "moe."
+                L["router"] = QLinear.from_float(w[mo + "router"], "f32", dev)
+                L["router_bias"] = f32(w[mo + "router_bias"]) if (mo + "router_bias") in w else None
+                ef = expert_layout(eq, cfg.hidden, cfg.moe_inter)
+                E_total = cfg.n_routed + cfg.n_shared
+                arena = ExpertArena(ef, E_total, E_total, dev)
+                for e in range(E_total):
+                    nm = mo + (f"experts.{e}." if e < cfg.n_routed else f"shared.{e - cfg.n_routed}.")
+                    arena.write_expert(e, *(QLinear.from_float(w[nm + t], eq, dev) for t in ("gate", "up", "down")))
+                    arena.slot_of[e] = e
+                L["arena"] = arena
+            else:
+                f = p + "mlp."
+                L["mlp_gu"] = QLinear.from_float(torch.cat([w[f + "gate"], w[f + "up"]], 0), dq, dev)
+                L["mlp_down"] = QLinear.from_float(w[f + "down"], dq, dev)
+            m.layers.append(L)
+        m._finish()
+        return m
+
+    @classmethod
+    def random_init(cls, cfg: ModelConfig, device="cuda", kv_fmt="fp8", page=64, seed=0, expert_slots: Optional[int] = None,
+                    embed_on_host: bool = False) -> "DeviceModel":
+        """Random weights generated directly in storage format on the device (full-size models).
+        ``expert_slots`` caps the routed-expert slots per MoE layer (VRAM expert cache); the first
+        slots hold the shared experts followed by routed experts 0..; the rest start non-resident."""
+        m = cls(cfg, device, kv_fmt, page)
+        dev = m.device
+        gen = torch.Generator(device=dev).manual_seed(seed)
+        dq, eq = cfg.dense_quant, cfg.expert_quant
+        if eq.startswith("gguf"):
+            eq = "nvfp4"
+        H = cfg.hidden
+
+        def nrm(n):
+            t = torch.empty(n, dtype=torch.float32, device=dev)
+            t.normal_(1.0, 0.05, generator=gen)
+            return t
+
+        def rnd(*shape, std=0.02, dtype=torch.float32):
+            t = torch.empty(*shape, dtype=dtype, device=dev)
+            t.normal_(0.0, std, generator=gen)
+            return t
+
+        if embed_on_host:
+            e = torch.empty(cfg.vocab, H, dtype=torch.bfloat16).normal_(0.0, 1.0).pin_memory()
+            m.embed = e
+        else:
+            m.embed = rnd(cfg.vocab, H, std=1.0, dtype=torch.bfloat16)
+        m.head = QLinear.random(cfg.vocab, H, "bf16", dev, gen=gen)
+        m.final_norm = nrm(H)
+        n = cfg.hc_mult
+        for i in range(cfg.n_layers):
+            L: dict = {"attn_norm": nrm(H), "ffn_norm": nrm(H)}
+            if cfg.mhc:
+                for nm in ("hc_attn", "hc_ffn"):
+                    L[nm] = (rnd(2 * n + n * n, n * H, std=0.05), torch.ones(3, device=dev), rnd(2 * n + n * n, std=0.5))
+            if cfg.is_kda_layer(i):
+                C = cfg.kda_heads * cfg.kda_head_dim
+                L["kda_in"] = QLinear.random(3 * C + cfg.kda_heads + 2 * cfg.kda_rank, H, dq, dev, std=0.05, gen=gen)
+                L["kda_fb"] = rnd(C, cfg.kda_rank, std=0.2, dtype=torch.bfloat16)
+                L["kda_gb"] = rnd(C, cfg.kda_rank, std=0.2, dtype=torch.bfloat16)
+                for nm in ("conv_q", "conv_k", "conv_v"):
+                    L["kda_" + nm] = torch.empty(C, cfg.kda_conv, device=dev).uniform_(-0.5, 0.5, generator=gen)
+                L["kda_dt_bias"] = torch.empty(cfg.kda_heads, cfg.kda_head_dim, device=dev).uniform_(-1, 1, generator=gen)
+                L["kda_o_norm"] = nrm(cfg.kda_head_dim)
+                L["kda_a_exp"] = torch.exp(torch.empty(cfg.kda_heads, device=dev).uniform_(-1.0, 1.5, generator=gen))
+                L["kda_o"] = QLinear.random(H, C, dq, dev, gen=gen)
+            else:
+                Hh = cfg.n_heads
+                has_idx = cfg.has_indexer and cfg.index_source_layer(i) == i
+                n_in = cfg.q_lora + cfg.kv_lora + cfg.qk_rope
+                n_qb = Hh * cfg.qk_head
+                if has_idx:
+                    n_in += cfg.index_head_dim + cfg.index_n_heads + (cfg.index_head_dim if cfg.index_kpool > 1 else 0)
+                    n_qb += cfg.index_n_heads * cfg.index_head_dim
+                    if cfg.index_kpool > 1:
+                        L["idx_ape"] = rnd(cfg.index_kpool, cfg.index_head_dim, std=0.5)
+                    L["idx_ln_w"] = nrm(cfg.index_head_dim); L["idx_ln_b"] = rnd(cfg.index_head_dim, std=0.1)
+                L["mla_in"] = QLinear.random(_align(n_in, 8), H, dq, dev, std=0.05, gen=gen)
+                L["mla_qb"] = QLinear.random(n_qb, cfg.q_lora, dq, dev, std=0.05, gen=gen)
+                L["qa_norm"] = nrm(cfg.q_lora); L["kv_norm"] = nrm(cfg.kv_lora)
+                L["k_b"] = rnd(Hh, cfg.kv_lora, cfg.qk_nope, std=0.05, dtype=torch.bfloat16)
+                L["v_b"] = rnd(Hh, cfg.v_head, cfg.kv_lora, std=0.05, dtype=torch.bfloat16)
+                L["mla_o"] = QLinear.random(H, Hh * cfg.v_head, dq, dev, gen=gen)
+            if cfg.is_moe_layer(i):
+                L["router"] = QLinear.random(cfg.n_routed, H, "f32", dev, std=0.1, gen=gen)
+                L["router_bias"] = rnd(cfg.n_routed, std=0.05) if cfg.router_bias else None
+                ef = expert_layout(eq, H, cfg.moe_inter)
+                E_total = cfg.n_routed + cfg.n_shared
+                n_slots = E_total if expert_slots is None else min(E_total, expert_slots + cfg.n_shared)
+                arena = ExpertArena(ef, n_slots, E_total, dev)
+                m._random_fill_arena(arena, eq, gen)
+                # shared experts first, then routed experts in id order
+                order = list(range(cfg.n_routed, E_total)) + list(range(cfg.n_routed))
+                so = torch.full((E_total,), -1, dtype=torch.int32)
+                for s_, e in enumerate(order[:n_slots]):
+                    so[e] = s_
+                arena.slot_of.copy_(so)
+                L["arena"] = arena
+            else:
+                L["mlp_gu"] = QLinear.random(2 * cfg.dense_inter, H, dq, dev, gen=gen)
+                L["mlp_down"] = QLinear.random(H, cfg.dense_inter, dq, dev, gen=gen)
+            m.layers.append(L)
+        m._finish()
+        return m
+
+    def _random_fill_arena(self, arena: ExpertArena, eq: str, gen):
+        ef, d = arena.ef, arena.data
+        if eq == "bf16":
+            d.view(torch.bfloat16).normal_(0.0, 0.02, generator=gen)
+        elif eq == "fp8_e4m3":
+            d[:, : ef.off_sg].random_(0, 256, generator=gen)
+            d[:, : ef.off_sg] &= 0xBF
+            d[:, ef.off_sg: ef.off_tail].view(torch.float32).fill_(0.02 / 0.6)
+        else:
+            d[:, : ef.off_sg].random_(0, 256, generator=gen)
+            d[:, ef.off_sg: ef.off_tail].random_(0x30, 0x40, generator=gen)
+            d[:, ef.off_tail: ef.off_tail + 12].view(torch.float32).fill_(0.02 / 2.1)
+
+    def _finish(self):
+        cfg = self.cfg
+        for L in self.layers:
+            if "kda_in" in L:
+                self.max_proj = max(self.max_proj, L["kda_in"].N)
+            if "mla_in" in L:
+                self.max_proj = max(self.max_proj, L["mla_in"].N)
+                self.max_qb = max(self.max_qb, L["mla_qb"].N)
+        self._ef_bytes = {}
+
+    def weight_bytes(self) -> int:
+        tot = self.head.nbytes() + (self.embed.numel() * 2 if self.embed.is_cuda else 0)
+        for L in self.layers:
+            for v in L.values():
+                if isinstance(v, QLinear):
+                    tot += v.nbytes()
+                elif isinstance(v, ExpertArena):
+                    tot += v.data.numel()
+                elif isinstance(v, torch.Tensor):
+                    tot += v.numel() * v.element_size()
+                elif isinstance(v, tuple):
+                    tot += sum(t.numel() * t.element_size() for t in v)
+        return tot
+
+    # ------------------------------------------------------------------ caches
+    def alloc_cache(self, num_pages: int, n_slots: int, max_pages_per_seq: int):
+        cfg, dev = self.cfg, self.device
+        self.num_pages, self.n_slots, self.max_pages = num_pages, n_slots, max_pages_per_seq
+        self.block_table = torch.zeros(n_slots, max_pages_per_seq, dtype=torch.int32, device=dev)
+        P = cfg.index_kpool
+        for i in range(cfg.n_layers):
+            if cfg.is_kda_layer(i):
+                self.kda_state[i] = torch.zeros(n_slots, cfg.kda_heads, cfg.kda_head_dim, cfg.kda_head_dim, dtype=torch.float32, device=dev)
+                self.kda_conv[i] = torch.zeros(n_slots, 3, cfg.kda_heads * cfg.kda_head_dim, 3, dtype=torch.float32, device=dev)
+            else:
+                self.kv_cache[i] = torch.zeros(num_pages, self.page, self.kv_row_bytes, dtype=torch.uint8, device=dev)
+                if cfg.has_indexer and cfg.index_source_layer(i) == i:
+                    self.idx_cache[i] = torch.zeros(num_pages, self.page // P, self.idx_row_bytes, dtype=torch.uint8, device=dev)
+                    if P > 1:
+                        self.idx_tail[i] = torch.zeros(n_slots, P, 2, cfg.index_head_dim, dtype=torch.bfloat16, device=dev)
+
+    def reset_slot(self, slot: int):
+        for t in self.kda_state.values():
+            t[slot].zero_()
+        for t in self.kda_conv.values():
+            t[slot].zero_()
+
+    def cache_bytes_per_token(self) -> int:
+        cfg = self.cfg
+        b = 0
+        for i in cfg.mla_layers():
+            b += self.kv_row_bytes
+            if cfg.has_indexer and cfg.index_source_layer(i) == i:
+                b += self.idx_row_bytes // cfg.index_kpool
+        return b
+
+    # ------------------------------------------------------------------ forward
+    def _ffn(self, i: int, L: dict, ws: Workspace, R: int):
+        cfg = self.cfg
+        if "arena" not in L:
+            L["mlp_gu"](ws.gu, ws.x, R, ldo=2 * cfg.dense_inter)
+            nat.call("lsb_swiglu", ws.act_d, ws.gu, R, cfg.dense_inter, cfg.swiglu_limit)
+            L["mlp_down"](ws.sub, ws.act_d, R)
+            return
+        arena: ExpertArena = L["arena"]
+        S = ws.S
+        E_total = cfg.n_routed + cfg.n_shared
+        L["router"](ws.logits_r, ws.x, R)
+        sc = {"sigmoid": 0, "softmax": 1, "sqrtsoftplus": 2}[cfg.scoring]
+        nat.call("lsb_router_topk", ws.logits_r, L["router_bias"], ws.ids, ws.wts, R, cfg.n_routed, cfg.top_k, cfg.n_group,
+                 cfg.topk_group, sc, int(cfg.norm_topk_prob), cfg.routed_scale, cfg.n_shared, cfg.n_routed)
+        nat.call("lsb_moe_build_groups", ws.ids, R * S, E_total, ws.group_expert, ws.group_n, ws.group_pairs, ws.n_groups, ws.counts)
+        efp = ctypes.addressof(arena.ef)
+        mg = min(ws.max_groups, min(R * S, (R * S + 3) // 4 + E_total))
+        nat.call("lsb_moe_gateup", ws.x, arena.data, arena.slot_of, efp, ws.group_expert, ws.group_n, ws.group_pairs, ws.n_groups,
+                 ws.act, S, mg, cfg.swiglu_limit, ws.miss)
+        nat.call("lsb_moe_down", ws.act, arena.data, arena.slot_of, efp, ws.group_expert, ws.group_n, ws.group_pairs, ws.n_groups,
+                 ws.y, mg)
+        nat.call("lsb_moe_combine", ws.sub, ws.y, ws.wts, ws.ids, arena.slot_of, R, S, cfg.hidden, 0)
+
+    def _kda(self, i: int, L: dict, ws: Workspace, R: int, nseq: int):
+        cfg = self.cfg
+        C = cfg.kda_heads * cfg.kda_head_dim
+        lin: QLinear = L["kda_in"]
+        lin(ws.proj, ws.x, R, ldo=self.max_proj)
+        nat.call("lsb_kda_forward", ws.proj, self.max_proj, 0, C, 2 * C, 3 * C, 3 * C + cfg.kda_heads,
+                 3 * C + cfg.kda_heads + cfg.kda_rank, cfg.kda_rank, L["kda_fb"], L["kda_gb"], L["kda_conv_q"], L["kda_conv_k"],
+                 L["kda_conv_v"], L["kda_a_exp"], L["kda_dt_bias"], L["kda_o_norm"], self.kda_state[i], self.kda_conv[i],
+                 ws.seq_row0, ws.seq_nrows, ws.seq_slot, ws.kda_out, nseq, cfg.kda_heads, cfg.kda_head_dim,
+                 cfg.kda_head_dim ** -0.5, cfg.kda_lower_bound, cfg.rms_eps)
+        L["kda_o"](ws.sub, ws.kda_out, R)
+
+    def _mla(self, i: int, L: dict, ws: Workspace, R: int):
+        cfg = self.cfg
+        Hh, dl, dr, dn, dv = cfg.n_heads, cfg.kv_lora, cfg.qk_rope, cfg.qk_nope, cfg.v_head
+        ldp = self.max_proj
+        off_qa, off_kv = 0, cfg.q_lora
+        off_ik = off_kv + dl + dr
+        off_iw = off_ik + cfg.index_head_dim
+        off_ig = off_iw + cfg.index_n_heads
+        src = cfg.index_source_layer(i) if cfg.has_indexer else -1
+        has_idx = src == i
+        L["mla_in"](ws.proj, ws.x, R, ldo=ldp)
+        P = cfg.index_kpool
+        if has_idx:
+            nat.call("lsb_indexer_k_append", ws.proj, ldp, off_ik, off_ig, L["idx_ln_w"], L["idx_ln_b"], L.get("idx_ape"),
+                     self.inv_freq_idx, cfg.index_rope_dim, self.idx_cache[i], self.block_table, self.max_pages, self.page // P,
+                     self.idx_tail.get(i), ws.row_seq, ws.row_pos, ws.row_slot, R, P, 1e-6)
+        nat.call("lsb_mla_prep", ws.proj, ldp, off_qa, cfg.q_lora, off_kv, dl, dr, L["qa_norm"], L["kv_norm"], self.inv_freq,
+                 ws.q_c, self.kv_cache[i], self.block_table, self.max_pages, ws.row_seq, ws.row_pos, R, self.page,
+                 KV_FMT[self.kv_fmt], cfg.rms_eps)
+        ldq = self.max_qb
+        L["mla_qb"](ws.qproj, ws.q_c, R, ldo=ldq)
+        nat.call("lsb_batched_gemv_bf16", ws.q_abs, ws.qproj, L["k_b"], R, Hh, dl, dn, ldq, dn + dr, Hh * (dl + dr), dl + dr,
+                 dr, self.inv_freq, ws.row_pos)
+        sel_idx = sel_cnt = None
+        sel_ld = 0
+        if cfg.has_indexer:
+            if has_idx:
+                nat.call("lsb_indexer_q_prep", ws.qproj, ldq, Hh * (dn + dr), ws.proj, ldp, off_iw, cfg.index_n_heads,
+                         cfg.index_rope_dim, self.inv_freq_idx, ws.row_pos, ws.q_idx, ws.idx_w, R)
+                nat.call("lsb_indexer_score", ws.q_idx, ws.idx_w, cfg.index_n_heads, self.idx_cache[i], self.block_table,
+                         self.max_pages, self.page // P, ws.row_seq, ws.n_entries, ws.scores, ws.max_entries, R, ws.max_entries)
+                nat.call("lsb_indexer_topk", ws.scores, ws.max_entries, ws.n_entries, ws.row_len, ws.row_seq,
+                         cfg.index_topk // P, P, ws.sel_idx, ws.sel_cnt, ws.sel_ld, R)
+            sel_idx, sel_cnt, sel_ld = ws.sel_idx, ws.sel_cnt, ws.sel_ld
+        nat.call("lsb_mla_decode", ws.q_abs, self.kv_cache[i], self.block_table, self.max_pages, ws.row_seq, ws.row_len,
+                 sel_idx, sel_cnt, sel_ld, ws.o_lat, None, ws.o_part, ws.ml_part, R, Hh, dl, dr, self.page,
+                 KV_FMT[self.kv_fmt], ws.NS, cfg.softmax_scale)
+        nat.call("lsb_batched_gemv_bf16", ws.attn_v, ws.o_lat, L["v_b"], R, Hh, dv, dl, Hh * dl, dl, Hh * dv, dv, 0, None, None)
+        L["mla_o"](ws.sub, ws.attn_v, R)
+
+    def forward(self, ws: Workspace, R: int, nseq: int, logit_row0: int, n_logit_rows: int):
+        """Run one step over the first ``R`` rows of the workspace (inputs already staged in
+        ``ws``).  Writes logits for rows [logit_row0, logit_row0 + n_logit_rows)."""
+        cfg = self.cfg
+        H, n = cfg.hidden, cfg.hc_mult
+        if cfg.mhc:
+            nat.call("lsb_embedding", ws.sub, None, self.embed, ws.tok, R, H, 0, cfg.vocab)
+            for i, L in enumerate(self.layers):
+                fn, sc, base = L["hc_attn"]
+                nat.call("lsb_mhc_post_pre", ws.x, ws.resid, ws.sub, ws.post, ws.comb, fn, sc, base, L["attn_norm"], ws.part, R, H, n,
+                         0 if i == 0 else 1, cfg.hc_sinkhorn_iters, cfg.hc_eps, cfg.rms_eps, cfg.hc_post_mult)
+                if cfg.is_kda_layer(i):
+                    self._kda(i, L, ws, R, nseq)
+                else:
+                    self._mla(i, L, ws, R)
+                fn, sc, base = L["hc_ffn"]
+                nat.call("lsb_mhc_post_pre", ws.x, ws.resid, ws.sub, ws.post, ws.comb, fn, sc, base, L["ffn_norm"], ws.part, R, H, n,
+                         1, cfg.hc_sinkhorn_iters, cfg.hc_eps, cfg.rms_eps, cfg.hc_post_mult)
+                self._ffn(i, L, ws, R)
+            nat.call("lsb_mhc_contract_norm", ws.x, ws.resid, ws.sub, ws.post, ws.comb, self.final_norm, R, H, n, cfg.rms_eps)
+        else:
+            resid = ws.resid.view(-1)[: ws.R * H].view(ws.R, H)
+            nat.call("lsb_embedding", resid, None, self.embed, ws.tok, R, H, 0, cfg.vocab)
+            nat.call("lsb_rmsnorm", ws.x, resid, self.layers[0]["attn_norm"], R, H, H, H, cfg.rms_eps, 1, None)
+            for i, L in enumerate(self.layers):
+                if cfg.is_kda_layer(i):
+                    self._kda(i, L, ws, R, nseq)
+                else:
+                    self._mla(i, L, ws, R)
+                nat.call("lsb_add_rmsnorm", ws.x, resid, ws.sub, L["ffn_norm"], R, H, cfg.rms_eps)
+                self._ffn(i, L, ws, R)
+                nxt = self.layers[i + 1]["attn_norm"] if i + 1 < cfg.n_layers else self.final_norm
+                nat.call("lsb_add_rmsnorm", ws.x, resid, ws.sub, nxt, R, H, cfg.rms_eps)
+        xr = ws.x[logit_row0: logit_row0 + n_logit_rows]
+        self.head(ws.logits, xr, n_logit_rows)
+
+    def argmax(self, ws: Workspace, n_rows: int):
+        nat.call("lsb_argmax", ws.logits, self.cfg.vocab, n_rows, self.cfg.vocab, ws.amax_part, ws.out_tok, ws.out_val, 0)
+
+    # ------------------------------------------------------------------ oracle support
+    def effective_state_dict(self) -> Dict[str, torch.Tensor]:
+        """fp32 CPU state dict of what the device actually computes with (dequantised), in the
+        canonical naming - lets the oracle check the kernels independent of quantisation error."""
+        cfg = self.cfg
+        out: Dict[str, torch.Tensor] = {}
+        cpu = lambda t: t.detach().float().cpu()
+        out["embed.weight"] = cpu(self.embed)
+        out["head.weight"] = cpu(self.head.dequant())
+        out["final_norm.weight"] = cpu(self.final_norm)
+        for i, L in enumerate(self.layers):
+            p = f"layers.{i}."
+            out[p + "attn_norm.weight"] = cpu(L["attn_norm"]); out[p + "ffn_norm.weight"] = cpu(L["ffn_norm"])
+            if cfg.mhc:
+                for nm in ("hc_attn", "hc_ffn"):
+                    out[p + nm + ".fn"], out[p + nm + ".scale"], out[p + nm + ".base"] = (cpu(t) for t in L[nm])
+            if cfg.is_kda_layer(i):
+                C = cfg.kda_heads * cfg.kda_head_dim
+                w = cpu(L["kda_in"].dequant())
+                k = p + "kda."
+                out[k + "q"], out[k + "k"], out[k + "v"] = w[:C], w[C:2 * C], w[2 * C:3 * C]
+                o = 3 * C
+                out[k + "beta"] = w[o: o + cfg.kda_heads]; o += cfg.kda_heads
+                out[k + "f_a"] = w[o: o + cfg.kda_rank]; o += cfg.kda_rank
+                out[k + "g_a"] = w[o: o + cfg.kda_rank]
+                out[k + "f_b"] = cpu(L["kda_fb"]); out[k + "g_b"] = cpu(L["kda_gb"])
+                for nm in ("conv_q", "conv_k", "conv_v", "dt_bias", "o_norm"):
+                    out[k + nm] = cpu(L["kda_" + nm])
+                out[k + "a_log"] = torch.log(cpu(L["kda_a_exp"]))
+                out[k + "o"] = cpu(L["kda_o"].dequant())
+            else:
+                a = p + "attn."
+                w = cpu(L["mla_in"].dequant())
+                out[a + "q_a"] = w[: cfg.q_lora]
+                o = cfg.q_lora
+                out[a + "kv_a"] = w[o: o + cfg.kv_lora + cfg.qk_rope]; o += cfg.kv_lora + cfg.qk_rope
+                wq = cpu(L["mla_qb"].dequant())
+                nq = cfg.n_heads * cfg.qk_head
+                out[a + "q_b"] = wq[:nq]
+                if cfg.has_indexer and cfg.index_source_layer(i) == i:
+                    x = p + "indexer."
+                    out[x + "wk"] = w[o: o + cfg.index_head_dim]; o += cfg.index_head_dim
+                    out[x + "weights_proj"] = w[o: o + cfg.index_n_heads]; o += cfg.index_n_heads
+                    if cfg.index_kpool > 1:
+                        out[x + "gate"] = w[o: o + cfg.index_head_dim]
+                        out[x + "ape"] = cpu(L["idx_ape"])
+                    out[x + "wq_b"] = wq[nq:]
+                    out[x + "k_norm.weight"] = cpu(L["idx_ln_w"]); out[x + "k_norm.bias"] = cpu(L["idx_ln_b"])
+                out[a + "q_a_norm"] = cpu(L["qa_norm"]); out[a + "kv_a_norm"] = cpu(L["kv_norm"])
+                out[a + "k_b"] = cpu(L["k_b"]); out[a + "v_b"] = cpu(L["v_b"])
+                out[a + "o"] = cpu(L["mla_o"].dequant())
+            if "arena" in L:
+                mo = p + "moe."
+                out[mo + "router"] = cpu(L["router"].w)
+                if L["router_bias"] is not None:
+                    out[mo + "router_bias"] = cpu(L["router_bias"])
+                arena: ExpertArena = L["arena"]
+                fmt = {0: "bf16", 1: "fp8_e4m3", 2: "nvfp4"}[arena.ef.fmt]
+                so = arena.slot_of.cpu()
+                for e in range(cfg.n_routed + cfg.n_shared):
+                    nm = mo + (f"experts.{e}." if e < cfg.n_routed else f"shared.{e - cfg.n_routed}.")
+                    g, u, d = arena.read_expert(int(so[e]), fmt)
+                    out[nm + "gate"], out[nm + "up"], out[nm + "down"] = cpu(g), cpu(u), cpu(d)
+            else:
+                f = p + "mlp."
+                w = cpu(L["mlp_gu"].dequant())
+                out[f + "gate"], out[f + "up"] = w[: cfg.dense_inter], w[cfg.dense_inter:]
+                out[f + "down"] = cpu(L["mlp_down"].dequant())
+        return out

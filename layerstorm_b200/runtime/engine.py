@@ -1,0 +1,269 @@
+"""Step engine: sequences, paged-cache bookkeeping, step staging, CUDA-graph decode.
+
+One ``Engine`` drives one ``DeviceModel`` on one GPU.  A step is a batch of rows (decode: one
+row per sequence; prefill: a chunk of consecutive tokens of one sequence; verify: a few
+consecutive rows).  All per-step inputs are packed into one pinned host buffer and copied
+with a single cudaMemcpyAsync; decode steps replay a captured CUDA graph per batch size,
+so the host issues one copy + one graph launch + one 4-byte readback per generated token.
+
+This is the role of the reference's CommandDispatcher + attention driver + sequence table
+(src/daemon/command_dispatcher.h, src/daemon/attention/{attention_driver,kv_metadata,
+page_provision}.cpp) with the ring protocol collapsed into direct calls: the reference's own
+measurements identified per-layer host round trips, not bandwidth, as the decode wall
+(docs/DESIGN-REVISIONS.md:46-54).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from ..models.config import ModelConfig
+from ..models.device_model import DeviceModel, Workspace
+from ..ops import _native as nat
+
+
+class KvPoolExhausted(RuntimeError):
+    """No free KV pages (the reference's kKvPoolExhausted completion error)."""
+
+
+@dataclass
+class SequenceState:
+    slot: int
+    length: int = 0                 # tokens whose KV / recurrent state is committed
+    pages: List[int] = field(default_factory=list)
+    tokens: List[int] = field(default_factory=list)
+
+
+@dataclass
+class SamplingParams:
+    temperature: float = 0.0
+    top_k: int = 0
+    top_p: float = 1.0
+    seed: int = 0
+    max_tokens: int = 16
+
+
+class Engine:
+    def __init__(self, model: DeviceModel, max_seqs: int = 4, max_ctx: int = 4096, prefill_chunk: int = 256,
+                 max_batch: int = 4, num_pages: Optional[int] = None, use_graph: bool = True):
+        self.model, self.cfg = model, model.cfg
+        self.dev = model.device
+        self.page = model.page
+        self.max_ctx = max_ctx
+        self.max_pages = (max_ctx + self.page - 1) // self.page
+        self.num_pages = num_pages if num_pages is not None else self.max_pages * max_seqs
+        self.max_seqs, self.max_batch, self.prefill_chunk = max_seqs, max_batch, prefill_chunk
+        model.alloc_cache(self.num_pages, max_seqs, self.max_pages)
+        self.free_pages = list(range(self.num_pages - 1, -1, -1))
+        self.free_slots = list(range(max_seqs - 1, -1, -1))
+        self.seqs: Dict[int, SequenceState] = {}
+        self.use_graph = use_graph and self.dev.type == "cuda"
+        self.ws_decode: Dict[int, Workspace] = {}
+        self.ws_prefill: Optional[Workspace] = None
+        self.graphs: Dict[int, torch.cuda.CUDAGraph] = {}
+        self.graph_launches: Dict[int, int] = {}
+        Rmax = max(prefill_chunk, max_batch)
+        self.h_bt = torch.zeros(max_seqs, self.max_pages, dtype=torch.int32).pin_memory()
+        self.h_out = torch.zeros(Rmax, dtype=torch.int32).pin_memory()
+        self.stream = torch.cuda.Stream(device=self.dev)
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+        self.kernel_launches = 0
+
+    # ------------------------------------------------------------------ sequences
+    def create_sequence(self) -> int:
+        if not self.free_slots:
+            raise RuntimeError("no free sequence slot")
+        slot = self.free_slots.pop()
+        self.seqs[slot] = SequenceState(slot)
+        with torch.cuda.stream(self.stream):
+            self.model.reset_slot(slot)
+        return slot
+
+    def free_sequence(self, sid: int):
+        s = self.seqs.pop(sid)
+        self.free_pages.extend(reversed(s.pages))
+        self.free_slots.append(s.slot)
+
+    def rewind(self, sid: int, length: int):
+        """Roll the committed frontier back (speculative-verify rejection).  Only valid for models
+        without recurrent (KDA) state, whose state cannot be un-applied."""
+        s = self.seqs[sid]
+        if any(self.cfg.is_kda_layer(i) for i in range(self.cfg.n_layers)) and length < s.length:
+            raise RuntimeError("rewind of a recurrent-state sequence is refused")
+        s.length = length
+        del s.tokens[length:]
+
+    def _ensure_pages(self, s: SequenceState, new_len: int):
+        need = (new_len + self.page - 1) // self.page
+        if need > self.max_pages:
+            raise RuntimeError(f"sequence length {new_len} exceeds max context {self.max_ctx}")
+        changed = False
+        while len(s.pages) < need:
+            if not self.free_pages:
+                raise KvPoolExhausted(f"KV pool exhausted ({self.num_pages} pages)")
+            pg = self.free_pages.pop()
+            self.h_bt[s.slot, len(s.pages)] = pg
+            s.pages.append(pg)
+            changed = True
+        if changed:
+            self.model.block_table[s.slot].copy_(self.h_bt[s.slot], non_blocking=True)
+            self.h2d_bytes += self.max_pages * 4
+
+    # ------------------------------------------------------------------ staging
+    def _stage(self, ws: Workspace, rows: List[tuple], seq_groups: List[tuple]):
+        """rows: (token, slot, pos); seq_groups: (row0, nrows, slot)."""
+        R = len(rows)
+        P = max(self.cfg.index_kpool, 1)
+        if not hasattr(ws, "h_inp"):
+            ws.h_inp = torch.zeros(9, ws.R, dtype=torch.int32).pin_memory()
+        h = ws.h_inp
+        h.zero_()
+        h[1].fill_(-1)
+        for r, (tok, slot, pos) in enumerate(rows):
+            h[0, r] = tok; h[1, r] = slot; h[2, r] = pos; h[3, r] = pos + 1; h[4, r] = slot
+            h[5, r] = (pos + 1) // P
+        for j, (r0, n, slot) in enumerate(seq_groups):
+            h[6, j] = r0; h[7, j] = n; h[8, j] = slot
+        ws.inp.copy_(h, non_blocking=True)
+        self.h2d_bytes += 9 * ws.R * 4
+
+    def _ws_decode(self, B: int) -> Workspace:
+        if B not in self.ws_decode:
+            self.ws_decode[B] = Workspace(self.model, B, B, self.max_ctx)
+        return self.ws_decode[B]
+
+    # ------------------------------------------------------------------ steps
+    def prefill(self, sid: int, tokens: Sequence[int], want_logits: bool = False):
+        """Append ``tokens`` to the sequence in chunks; returns the greedy next token (and the
+        last-position logits when asked)."""
+        s = self.seqs[sid]
+        tokens = [int(t) for t in tokens]
+        if self.ws_prefill is None:
+            self.ws_prefill = Workspace(self.model, self.prefill_chunk, 1, self.max_ctx)
+        ws = self.ws_prefill
+        nxt, logits = None, None
+        with torch.cuda.stream(self.stream):
+            for c0 in range(0, len(tokens), self.prefill_chunk):
+                chunk = tokens[c0: c0 + self.prefill_chunk]
+                R = len(chunk)
+                self._ensure_pages(s, s.length + R)
+                rows = [(t, s.slot, s.length + j) for j, t in enumerate(chunk)]
+                self._stage(ws, rows, [(0, R, s.slot)])
+                n0 = nat.launch_count()
+                self.model.forward(ws, R, 1, R - 1, 1)
+                self.model.argmax(ws, 1)
+                self.kernel_launches += nat.launch_count() - n0
+                s.length += R
+                s.tokens.extend(chunk)
+            self.h_out[:1].copy_(ws.out_tok[:1], non_blocking=True)
+            self.d2h_bytes += 4
+            self.stream.synchronize()
+            nxt = int(self.h_out[0])
+            if want_logits:
+                logits = ws.logits[0].float().cpu()
+        return (nxt, logits) if want_logits else nxt
+
+    def forward_rows(self, sid: int, tokens: Sequence[int], commit: bool = True) -> torch.Tensor:
+        """Run consecutive rows of one sequence and return logits for ALL rows (verify shape)."""
+        s = self.seqs[sid]
+        R = len(tokens)
+        ws = Workspace(self.model, R, R, self.max_ctx)
+        with torch.cuda.stream(self.stream):
+            self._ensure_pages(s, s.length + R)
+            rows = [(int(t), s.slot, s.length + j) for j, t in enumerate(tokens)]
+            self._stage(ws, rows, [(0, R, s.slot)])
+            n0 = nat.launch_count()
+            self.model.forward(ws, R, 1, 0, R)
+            self.kernel_launches += nat.launch_count() - n0
+            self.stream.synchronize()
+        if commit:
+            s.length += R
+            s.tokens.extend(int(t) for t in tokens)
+        return ws.logits[:R].float().cpu()
+
+    def decode(self, sids: Sequence[int], tokens: Sequence[int], return_logits: bool = False):
+        """One decode step for a batch of sequences: feeds ``tokens[i]`` at the frontier of
+        ``sids[i]`` and returns the greedy next token per sequence."""
+        B = len(sids)
+        ws = self._ws_decode(B)
+        with torch.cuda.stream(self.stream):
+            rows, groups = [], []
+            for j, (sid, tok) in enumerate(zip(sids, tokens)):
+                s = self.seqs[sid]
+                self._ensure_pages(s, s.length + 1)
+                rows.append((int(tok), s.slot, s.length))
+                groups.append((j, 1, s.slot))
+            self._stage(ws, rows, groups)
+            if self.use_graph:
+                if B not in self.graphs:
+                    self._capture(B, ws)
+                self.graphs[B].replay()
+                self.kernel_launches += self.graph_launches[B]
+            else:
+                n0 = nat.launch_count()
+                self.model.forward(ws, B, B, 0, B)
+                self.model.argmax(ws, B)
+                self.kernel_launches += nat.launch_count() - n0
+            self.h_out[:B].copy_(ws.out_tok[:B], non_blocking=True)
+            self.d2h_bytes += 4 * B
+            self.stream.synchronize()
+        out = [int(self.h_out[j]) for j in range(B)]
+        for sid, tok in zip(sids, tokens):
+            s = self.seqs[sid]
+            s.length += 1
+            s.tokens.append(int(tok))
+        if return_logits:
+            return out, ws.logits[:B].float().cpu()
+        return out
+
+    def _capture(self, B: int, ws: Workspace):
+        # warm-up run outside capture (sets function attributes, touches every buffer); the KDA
+        # state it perturbs is restored by snapshotting the affected slots first.
+        slots = [int(ws.seq_slot[j]) for j in range(B)]
+        snap = self._snapshot_recurrent(slots)
+        self.model.forward(ws, B, B, 0, B)
+        self.model.argmax(ws, B)
+        self.stream.synchronize()
+        self._restore_recurrent(slots, snap)
+        g = torch.cuda.CUDAGraph()
+        n0 = nat.launch_count()
+        with torch.cuda.graph(g, stream=self.stream):
+            self.model.forward(ws, B, B, 0, B)
+            self.model.argmax(ws, B)
+        self.graph_launches[B] = nat.launch_count() - n0
+        self._restore_recurrent(slots, snap)
+        self.graphs[B] = g
+
+    def _snapshot_recurrent(self, slots):
+        m = self.model
+        return {"state": {i: t[slots].clone() for i, t in m.kda_state.items()},
+                "conv": {i: t[slots].clone() for i, t in m.kda_conv.items()}}
+
+    def _restore_recurrent(self, slots, snap):
+        m = self.model
+        for i, t in m.kda_state.items():
+            t[slots] = snap["state"][i]
+        for i, t in m.kda_conv.items():
+            t[slots] = snap["conv"][i]
+
+    # ------------------------------------------------------------------ user-facing
+    def generate(self, prompt: Sequence[int], max_new_tokens: int = 16, eos: Optional[Sequence[int]] = None,
+                 on_token=None) -> List[int]:
+        """Greedy generation for one prompt (prefill + decode loop)."""
+        sid = self.create_sequence()
+        try:
+            out = []
+            tok = self.prefill(sid, prompt)
+            for _ in range(max_new_tokens):
+                out.append(tok)
+                if on_token:
+                    on_token(tok)
+                if eos and tok in eos:
+                    break
+                tok = self.decode([sid], [tok])[0]
+            return out
+        finally:
+            self.free_sequence(sid)

@@ -1,0 +1,180 @@
+"""Numerics of the decode-path CUDA kernels against plain PyTorch fp32 references."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from layerstorm_b200.formats import quant
+from layerstorm_b200.models import reference as ref
+from layerstorm_b200.models.config import ModelConfig, get_preset
+from layerstorm_b200.ops import _native as nat
+
+DEV = "cuda"
+
+
+def rnd(*shape, s=1.0, dtype=torch.float32, seed=0):
+    g = torch.Generator(device="cpu").manual_seed(seed + sum(shape))
+    return (torch.randn(*shape, generator=g) * s).to(dtype).to(DEV)
+
+
+def close(a, b, rtol, atol, what=""):
+    a, b = a.float().cpu(), b.float().cpu()
+    err = (a - b).abs()
+    lim = atol + rtol * b.abs()
+    bad = err > lim
+    assert not bad.any(), f"{what}: {int(bad.sum())}/{a.numel()} off, max err {float(err.max()):.4g} (ref max {float(b.abs().max()):.4g})"
+
+
+@pytest.mark.parametrize("M", [1, 2, 3, 7])
+@pytest.mark.parametrize("fmt", ["bf16", "f32", "fp8", "nvfp4"])
+def test_gemv_formats(M, fmt):
+    N, K = 200, 512
+    x = rnd(M, K, dtype=torch.bfloat16)
+    w = rnd(N, K, s=0.05, seed=1)
+    out = torch.zeros(M, N, device=DEV)
+    if fmt == "bf16":
+        wq = w.to(torch.bfloat16)
+        nat.call("lsb_gemv_bf16", out, x, wq, None, M, N, K, K, K, N, 1.0, 0)
+        wd = wq.float()
+    elif fmt == "f32":
+        nat.call("lsb_gemv_f32w", out, x, w, None, M, N, K, K, K, N, 1.0, 0)
+        wd = w
+    elif fmt == "fp8":
+        q, s = quant.quantize_fp8_block(w)
+        nat.call("lsb_gemv_fp8b", out, x, q, s, None, M, N, K, K, N, 1.0, 0)
+        wd = quant.dequantize_fp8_block(q, s)
+    else:
+        q, a, gs = quant.quantize_nvfp4(w)
+        nat.call("lsb_gemv_nvfp4", out, x, q, a, None, M, N, K, K, N, gs, 0)
+        wd = quant.dequantize_nvfp4(q, a, gs, N, K)
+        assert (wd - w).abs().max() < 0.3 * w.abs().max()
+    torch.cuda.synchronize()
+    close(out, x.float() @ wd.T, 1e-3, 1e-3, f"gemv {fmt} M={M}")
+
+
+def test_gemv_bf16_out_and_bias():
+    M, N, K = 2, 64, 256
+    x = rnd(M, K, dtype=torch.bfloat16)
+    w = rnd(N, K, s=0.05, dtype=torch.bfloat16)
+    b = rnd(N)
+    out = torch.zeros(M, N, device=DEV, dtype=torch.bfloat16)
+    nat.call("lsb_gemv_bf16", out, x, w, b, M, N, K, K, K, N, 1.0, 1)
+    torch.cuda.synchronize()
+    close(out, x.float() @ w.float().T + b, 1e-2, 1e-2, "gemv bf16 out")
+
+
+def test_rmsnorm_and_add():
+    R, D = 5, 768
+    x = rnd(R, D)
+    w = rnd(D) * 0.1 + 1
+    out = torch.zeros(R, D, device=DEV, dtype=torch.bfloat16)
+    nat.call("lsb_rmsnorm", out, x, w, R, D, D, D, 1e-6, 1, None)
+    torch.cuda.synchronize()
+    close(out, ref.rmsnorm(x.cpu(), w.cpu(), 1e-6), 1e-2, 1e-2, "rmsnorm")
+    resid = rnd(R, D, seed=3)
+    r0 = resid.clone()
+    nat.call("lsb_add_rmsnorm", out, resid, x, w, R, D, 1e-6)
+    torch.cuda.synchronize()
+    close(resid, r0 + x, 1e-6, 1e-6, "resid add")
+    close(out, ref.rmsnorm((r0 + x).cpu(), w.cpu(), 1e-6), 1e-2, 1e-2, "add_rmsnorm")
+
+
+def test_mhc_post_pre_and_contract():
+    cfg = get_preset("tiny-glm5-next")
+    R, H, n = 3, cfg.hidden, cfg.hc_mult
+    o = ref.Oracle(cfg, {})
+    fn, sc, base, nw = rnd(24, n * H, s=0.05), torch.tensor([0.7, 1.1, 1.3], device=DEV), rnd(24, s=0.5), rnd(H) * 0.1 + 1
+    emb = rnd(R, H)
+    resid = torch.zeros(R, n, H, device=DEV)
+    post = torch.zeros(R, n, device=DEV); comb = torch.zeros(R, n, n, device=DEV)
+    part = torch.zeros(R, H // 128, 25, device=DEV)
+    x = torch.zeros(R, H, device=DEV, dtype=torch.bfloat16)
+    args = (cfg.hc_sinkhorn_iters, cfg.hc_eps, cfg.rms_eps, cfg.hc_post_mult)
+    nat.call("lsb_mhc_post_pre", x, resid, emb, post, comb, fn, sc, base, nw, part, R, H, n, 0, *args)
+    torch.cuda.synchronize()
+    r_ref = emb.cpu()[:, None, :].repeat(1, n, 1)
+    p_ref, c_ref, x_ref = o.mhc_pre(r_ref, fn.cpu(), sc.cpu(), base.cpu(), nw.cpu())
+    close(resid, r_ref, 1e-6, 1e-6, "expand")
+    close(post, p_ref, 1e-4, 1e-5, "post")
+    close(comb, c_ref, 1e-4, 1e-5, "comb")
+    close(x, x_ref, 1e-2, 1e-2, "x")
+    sub = rnd(R, H, seed=5)
+    nat.call("lsb_mhc_post_pre", x, resid, sub, post, comb, fn, sc, base, nw, part, R, H, n, 1, *args)
+    torch.cuda.synchronize()
+    r2 = o.mhc_post(sub.cpu(), r_ref, p_ref, c_ref)
+    p2, c2, x2 = o.mhc_pre(r2, fn.cpu(), sc.cpu(), base.cpu(), nw.cpu())
+    close(resid, r2, 1e-4, 1e-5, "post residual")
+    close(comb, c2, 1e-4, 1e-5, "comb2")
+    close(x, x2, 1e-2, 1e-2, "x2")
+    sub2 = rnd(R, H, seed=6)
+    nat.call("lsb_mhc_contract_norm", x, resid, sub2, post, comb, nw, R, H, n, cfg.rms_eps)
+    torch.cuda.synchronize()
+    fin = ref.rmsnorm(o.mhc_post(sub2.cpu(), r2, p2, c2).mean(1), nw.cpu(), cfg.rms_eps)
+    close(x, fin, 1e-2, 1e-2, "contract")
+
+
+@pytest.mark.parametrize("scoring,n_group,topk_group", [("sigmoid", 1, 1), ("softmax", 1, 1), ("sigmoid", 4, 2), ("sqrtsoftplus", 1, 1)])
+def test_router_topk(scoring, n_group, topk_group):
+    E, k, R = 32, 4, 9
+    cfg = ModelConfig(n_routed=E, top_k=k, scoring=scoring, n_group=n_group, topk_group=topk_group, routed_scale=2.5)
+    logits = rnd(R, E)
+    logits[0, 3] = logits[0, 7]           # exact tie -> lower index
+    bias = rnd(E, s=0.1)
+    ids = torch.zeros(R, k + 1, dtype=torch.int32, device=DEV)
+    wts = torch.zeros(R, k + 1, device=DEV)
+    nat.call("lsb_router_topk", logits, bias, ids, wts, R, E, k, n_group, topk_group,
+             {"sigmoid": 0, "softmax": 1, "sqrtsoftplus": 2}[scoring], 1, 2.5, 1, E)
+    torch.cuda.synchronize()
+    rid, rw = ref.route(cfg, logits.cpu(), bias.cpu())
+    assert torch.equal(ids[:, :k].cpu().long(), rid), (ids.cpu(), rid)
+    close(wts[:, :k], rw, 1e-4, 1e-6, "router weights")
+    assert (ids[:, k] == E).all() and (wts[:, k] == 1).all()
+
+
+def test_sampling_kernels():
+    R, V = 4, 5000
+    logits = rnd(R, V, s=3.0)
+    part = torch.zeros(R, 64, dtype=torch.int64, device=DEV)
+    ids = torch.zeros(R, dtype=torch.int32, device=DEV)
+    val = torch.zeros(R, device=DEV)
+    logits[1, 17] = logits[1, 4000] = 50.0
+    nat.call("lsb_argmax", logits, V, R, V, part, ids, val, 0)
+    torch.cuda.synchronize()
+    assert ids.cpu().tolist() == [int(t) for t in logits.cpu().argmax(-1)[:1]] + [17] + [int(t) for t in logits.cpu().argmax(-1)[2:]]
+    close(val, logits.max(-1).values, 0, 0, "argmax value")
+    top1 = torch.zeros(R, device=DEV); ent = torch.zeros(R, device=DEV)
+    nat.call("lsb_confidence", logits, V, R, V, top1, ent)
+    p = torch.softmax(logits.cpu(), -1)
+    torch.cuda.synchronize()
+    close(top1, p.max(-1).values, 1e-3, 1e-6, "top1")
+    close(ent, -(p * torch.log(p.clamp_min(1e-30))).sum(-1) / math.log(V), 1e-3, 1e-5, "entropy")
+    # top-k=1 sampling is argmax; the same seed repeats; top-p keeps the draw inside the nucleus
+    out = torch.zeros(R, dtype=torch.int32, device=DEV)
+    nat.call("lsb_sample", logits, V, R, V, 1.0, 1, 1.0, 123, None, out)
+    torch.cuda.synchronize()
+    assert out.cpu().tolist() == ids.cpu().tolist()
+    a = torch.zeros(R, dtype=torch.int32, device=DEV); b = torch.zeros(R, dtype=torch.int32, device=DEV)
+    nat.call("lsb_sample", logits, V, R, V, 0.8, 50, 0.9, 7, None, a)
+    nat.call("lsb_sample", logits, V, R, V, 0.8, 50, 0.9, 7, None, b)
+    torch.cuda.synchronize()
+    assert torch.equal(a, b)
+    top50 = logits.cpu().topk(50, -1).indices
+    for r in range(R):
+        assert int(a[r]) in top50[r].tolist()
+    # distribution check on a small vocabulary
+    lg = torch.tensor([[0.0, 1.0, 2.0, 3.0]], device=DEV).repeat(2000, 1).contiguous()
+    offs = torch.arange(2000, dtype=torch.int64, device=DEV)
+    o = torch.zeros(2000, dtype=torch.int32, device=DEV)
+    nat.call("lsb_sample", lg, 4, 2000, 4, 1.0, 0, 1.0, 99, offs, o)
+    torch.cuda.synchronize()
+    freq = torch.bincount(o.cpu().long(), minlength=4).float() / 2000
+    close(freq, torch.softmax(lg[0].cpu(), -1), 0.0, 0.04, "sample distribution")
+    # verify
+    d = torch.tensor([5, 6, 7, 8], dtype=torch.int32, device=DEV)
+    t = torch.tensor([5, 6, 9, 8, 1], dtype=torch.int32, device=DEV)
+    res = torch.zeros(2, dtype=torch.int32, device=DEV)
+    nat.call("lsb_spec_verify", d, t, 4, res)
+    torch.cuda.synchronize()
+    assert res.cpu().tolist() == [2, 9]

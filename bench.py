@@ -1,0 +1,231 @@
+#!/usr/bin/env python
+"""Headline benchmark: batch-1 greedy decode tokens/s at 8k context on a GLM-5.3-Flash-shape
+model (glm5_next: 45 layers, hidden 4096, 34 KDA + 11 sparse-MLA layers, mHC x4, 288 routed
+NVFP4 experts top-8 + 1 shared, bf16 attention, FP8 KV cache), random-init weights and
+synthetic token ids.  The reference publishes 24.5 tok/s for this workload on its own
+hardware (README.md:57,124).
+
+    python bench.py --gpus N --steps K --warmup W            # this engine
+    python bench.py --impl reference ...                     # the reference arm
+
+One JSON line is printed by rank 0.  ``value`` times only the device work of the K decode
+steps (CUDA events around each step's graph replay, summed, max over ranks); ``e2e`` times the
+same K steps through the public ``Engine.decode`` call, including each step's host->device
+copy of the inputs from pinned memory and the device->host read of the sampled token.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+BASELINE_DECODE_8K = 24.5      # tok/s, reference README.md:57 (GLM-5.3-Flash, decode @8k)
+
+
+def reference_arm(args):
+    print(json.dumps({
+        "impl": "reference",
+        "unavailable": "reference cannot be installed offline: no setup.py/pyproject.toml (pip: 'not installable'), its CUDA "
+                       "kernel submodules are empty and every CUDA target is compute_120-only",
+    }))
+    return 0
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks / throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.path = f"/tmp/lsb_clocks_{os.getpid()}.csv"
+
+    def start(self):
+        try:
+            self.f = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.gpu)], stdout=self.f, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.f.close()
+        sm, mx, reasons = [], [], set()
+        for line in open(self.path):
+            p = [x.strip() for x in line.split(",")]
+            if len(p) < 9:
+                continue
+            try:
+                sm.append(float(p[1])); mx.append(float(p[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), p[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        try:
+            os.unlink(self.path)
+        except OSError:
+            pass
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--model", default="glm-5.3-flash")
+    ap.add_argument("--ctx", type=int, default=8192)
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--prefill-chunk", type=int, default=256)
+    ap.add_argument("--headroom-gib", type=float, default=6.0, help="HBM left free after weights (caches, workspaces, context)")
+    ap.add_argument("--synthetic-fill", action="store_true", help="skip the real prefill; decode over an uninitialised cache")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    from layerstorm_b200.models.config import get_preset
+    from layerstorm_b200.models.device_model import DeviceModel, expert_layout
+    from layerstorm_b200.runtime.engine import Engine
+
+    cfg = get_preset(args.model)
+    dev = torch.device("cuda", local)
+    t0 = time.time()
+    # expert slots that fit next to the non-expert weights: the rest would stream from pinned host RAM
+    free_b, total_b = torch.cuda.mem_get_info(dev)
+    ef = expert_layout("nvfp4" if cfg.expert_quant.startswith(("nvfp4", "gguf")) else cfg.expert_quant, cfg.hidden, cfg.moe_inter)
+    n_moe = cfg.n_moe_layers()
+    non_expert_est = 19.5e9 if cfg.name == "GLM-5.3-Flash" else 0.15 * total_b
+    budget = free_b - non_expert_est - args.headroom_gib * 2 ** 30
+    slots = int(budget // (ef.stride * max(n_moe, 1))) - cfg.n_shared
+    slots = max(cfg.top_k, min(cfg.n_routed, slots))
+    model = DeviceModel.random_init(cfg, dev, kv_fmt="fp8", page=64, seed=1234 + rank, expert_slots=slots, embed_on_host=True)
+    max_ctx = args.ctx + args.steps + args.warmup + 64
+    eng = Engine(model, max_seqs=args.batch, max_ctx=max_ctx, prefill_chunk=args.prefill_chunk, max_batch=args.batch)
+    torch.cuda.synchronize()
+    t_init = time.time() - t0
+
+    g = torch.Generator().manual_seed(7)
+    prompts = [torch.randint(0, cfg.vocab, (args.ctx,), generator=g).tolist() for _ in range(args.batch)]
+    sids = [eng.create_sequence() for _ in range(args.batch)]
+    t0 = time.time()
+    toks = []
+    if args.synthetic_fill:
+        for sid in sids:
+            s = eng.seqs[sid]
+            eng._ensure_pages(s, args.ctx)
+            s.length = args.ctx
+            toks.append(1)
+    else:
+        for sid, p in zip(sids, prompts):
+            toks.append(eng.prefill(sid, p))
+    torch.cuda.synchronize()
+    t_prefill = time.time() - t0
+    prefill_tps = args.batch * args.ctx / t_prefill if not args.synthetic_fill else None
+
+    # when resident slots < routed experts, restrict routing to resident experts is NOT done: a miss is counted
+    for _ in range(args.warmup):
+        toks = eng.decode(sids, toks)
+
+    # ---- timed region 1: public API end to end (H2D inputs + graph + D2H token per step) ----
+    sampler = ClockSampler(local)
+    sampler.start()
+    h2d0, d2h0, l0 = eng.h2d_bytes, eng.d2h_bytes, eng.kernel_launches
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(eng.stream)
+    for _ in range(args.steps):
+        toks = eng.decode(sids, toks)
+    e1.record(eng.stream)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e2e_ms = e0.elapsed_time(e1)
+    h2d = (eng.h2d_bytes - h2d0) / args.steps
+    d2h = (eng.d2h_bytes - d2h0) / args.steps
+    launches = eng.kernel_launches - l0
+
+    # ---- timed region 2: device time of the step itself (graph replay only) ----
+    B = args.batch
+    graph = eng.graphs[B]
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    torch.cuda.synchronize()
+    with torch.cuda.stream(eng.stream):
+        for a, b in evs:
+            # advance the sequence like decode() does, without the host round trip
+            for sid in sids:
+                s = eng.seqs[sid]
+                eng._ensure_pages(s, s.length + 1)
+            rows = [(int(t), eng.seqs[sid].slot, eng.seqs[sid].length) for sid, t in zip(sids, toks)]
+            eng._stage(eng.ws_decode[B], rows, [(j, 1, eng.seqs[sid].slot) for j, sid in enumerate(sids)])
+            a.record(eng.stream)
+            graph.replay()
+            b.record(eng.stream)
+            for sid in sids:
+                eng.seqs[sid].length += 1
+    torch.cuda.synchronize()
+    dev_ms = sum(a.elapsed_time(b) for a, b in evs)
+    clocks = sampler.stop()
+    miss = int(eng.ws_decode[B].miss[0]) if hasattr(eng.ws_decode[B], "miss") else 0
+
+    if world > 1:
+        t = torch.tensor([dev_ms, e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dev_ms, e2e_ms = float(t[0]), float(t[1])
+    if rank == 0:
+        value = args.batch * args.steps / (dev_ms / 1e3)
+        e2e = args.batch * args.steps / (e2e_ms / 1e3)
+        out = {
+            "metric": "decode tok/s @8k ctx" if args.ctx == 8192 else f"decode tok/s @{args.ctx} ctx",
+            "value": round(value, 3), "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(dev_ms / args.steps, 4), "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": round(value / BASELINE_DECODE_8K, 3) if (args.model == "glm-5.3-flash" and args.ctx == 8192 and B == 1) else None,
+            "dtype": "bf16", "data": "synthetic token ids, random-init weights",
+            "config": {"model": cfg.name + "-shape", "global_batch": B, "seq_len": args.ctx,
+                       "parallelism": f"tp{world}ep{world}" if world > 1 else "single-gpu",
+                       "weights": f"experts {cfg.expert_quant}, attention {cfg.dense_quant}", "kv_cache": "fp8+bf16-rope, 64-token pages",
+                       "l2": "inputs larger than L2 (each step streams ~20 GB of weights)",
+                       "resident_expert_slots_per_layer": slots, "routed_experts": cfg.n_routed, "expert_miss_flag": miss,
+                       "context_fill": "synthetic (uninitialised cache)" if args.synthetic_fill else "real chunked prefill"},
+            "clocks": clocks,
+            "e2e": {"value": round(e2e, 3), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": launches,
+            "extra": {"prefill_tok_s": round(prefill_tps, 1) if prefill_tps else None, "init_s": round(t_init, 1),
+                      "weight_gib": round(model.weight_bytes() / 2 ** 30, 2)},
+        }
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

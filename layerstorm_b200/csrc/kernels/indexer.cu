@@ -61,7 +61,10 @@ struct IdxAppendParams {
     const float* ln_w; const float* ln_b; const float* ape;   // ape [P,128] (kpool only)
     const float* inv_freq; int dr;
     uint8_t* cache; const int* block_table; int max_pages, page;   // entries per page = `page`
-    bf16* tail;               // [slots, P, 2, 128] LayerNormed key | gate of the open pool (kpool only)
+    const bf16* tail;         // [slots, P, 2, 128] LayerNormed key | gate of the open pool (kpool only);
+                              // read-only here: written by indexer_q_prep, which runs after every
+                              // block of this kernel has finished (no in-launch read/write race)
+    bf16* kstash;             // [rows, 128] this launch's LayerNormed keys (kpool only)
     const int* row_seq; const int* row_pos; const int* row_slot;
     int P; float ln_eps;
 };
@@ -93,9 +96,7 @@ __global__ void __launch_bounds__(kID) indexer_k_append_kernel(IdxAppendParams p
         store_entry(p.cache + ((size_t)pg * p.page + pos % p.page) * kIdxRow, __bfloat162float(__float2bfloat16(v)), red, false);
     } else {
         const int slot = p.row_slot[r], j = pos % p.P;
-        bf16* tl = p.tail + ((size_t)slot * p.P + j) * 2 * kID;
-        tl[t] = __float2bfloat16(v);
-        tl[kID + t] = __float2bfloat16(pr[p.off_gate + t]);
+        p.kstash[(size_t)r * kID + t] = __float2bfloat16(v);
         if (j == p.P - 1) {
             // Compose the pooled entry: two-pass softmax over the P slots per dimension.  Slots
             // written by earlier rows of THIS launch are recomputed from their projections (other
@@ -139,10 +140,23 @@ __global__ void __launch_bounds__(kID) indexer_k_append_kernel(IdxAppendParams p
 __global__ void __launch_bounds__(kID) indexer_q_prep_kernel(const bf16* __restrict__ qproj, int ldq, int off_q,
                                                               const float* __restrict__ proj, int ldp, int off_w, int IH, int dr,
                                                               const float* __restrict__ inv_freq, const int* __restrict__ row_pos,
-                                                              bf16* __restrict__ q_idx, float* __restrict__ w_out) {
+                                                              bf16* __restrict__ q_idx, float* __restrict__ w_out,
+                                                              const bf16* __restrict__ kstash, int off_gate, bf16* __restrict__ tail,
+                                                              const int* __restrict__ row_seq, const int* __restrict__ row_slot, int P, int R) {
     __shared__ float buf[kID];
     const int r = blockIdx.x, t = threadIdx.x;
     pdl_wait();
+    if (P > 1 && row_seq[r] >= 0) {
+        // publish this row's key | gate to the sequence's open-pool tail unless the pool is
+        // completed by a later row of this same launch (then nobody will read it)
+        const int ipos = row_pos[r], j = ipos % P, rc = r + (P - 1 - j);
+        const bool completes_here = (j == P - 1) || (rc < R && row_seq[rc] == row_seq[r] && row_pos[rc] == ipos + (P - 1 - j));
+        if (!completes_here) {
+            bf16* tl = tail + ((size_t)row_slot[r] * P + j) * 2 * kID;
+            tl[t] = kstash[(size_t)r * kID + t];
+            tl[kID + t] = __float2bfloat16(proj[(size_t)r * ldp + off_gate + t]);
+        }
+    }
     const float pos = (float)row_pos[r];
     for (int h = 0; h < IH; ++h) {
         float v = __bfloat162float(qproj[(size_t)r * ldq + off_q + h * kID + t]);
@@ -312,24 +326,27 @@ LSB_API int lsb_indexer_row_bytes() { return kIdxRow; }
 
 LSB_API int lsb_indexer_k_append(const void* proj, int ldp, int off_k, int off_gate, const void* ln_w, const void* ln_b,
                                  const void* ape, const void* inv_freq, int dr, void* cache, const void* block_table,
-                                 int max_pages, int page, void* tail, const void* row_seq, const void* row_pos,
-                                 const void* row_slot, int rows, int P, float ln_eps, void* stream) {
+                                 int max_pages, int page, const void* tail, void* kstash, const void* row_seq,
+                                 const void* row_pos, const void* row_slot, int rows, int P, float ln_eps, void* stream) {
     if (P > 8) return -1;
     IdxAppendParams p;
     p.proj = (const float*)proj; p.ldp = ldp; p.off_k = off_k; p.off_gate = off_gate; p.ln_w = (const float*)ln_w;
     p.ln_b = (const float*)ln_b; p.ape = (const float*)ape; p.inv_freq = (const float*)inv_freq; p.dr = dr;
     p.cache = (uint8_t*)cache; p.block_table = (const int*)block_table; p.max_pages = max_pages; p.page = page;
-    p.tail = (bf16*)tail; p.row_seq = (const int*)row_seq; p.row_pos = (const int*)row_pos; p.row_slot = (const int*)row_slot;
+    p.tail = (const bf16*)tail; p.kstash = (bf16*)kstash; p.row_seq = (const int*)row_seq; p.row_pos = (const int*)row_pos; p.row_slot = (const int*)row_slot;
     p.P = P; p.ln_eps = ln_eps;
     indexer_k_append_kernel<<<rows, kID, 0, (cudaStream_t)stream>>>(p);
     LSB_CHECK_LAUNCH();
 }
 
 LSB_API int lsb_indexer_q_prep(const void* qproj, int ldq, int off_q, const void* proj, int ldp, int off_w, int IH, int dr,
-                               const void* inv_freq, const void* row_pos, void* q_idx, void* w_out, int rows, void* stream) {
+                               const void* inv_freq, const void* row_pos, void* q_idx, void* w_out, const void* kstash,
+                               int off_gate, void* tail, const void* row_seq, const void* row_slot, int P, int rows, void* stream) {
     if (IH > kID) return -1;
     indexer_q_prep_kernel<<<rows, kID, 0, (cudaStream_t)stream>>>((const bf16*)qproj, ldq, off_q, (const float*)proj, ldp, off_w, IH, dr,
-                                                                 (const float*)inv_freq, (const int*)row_pos, (bf16*)q_idx, (float*)w_out);
+                                                                 (const float*)inv_freq, (const int*)row_pos, (bf16*)q_idx, (float*)w_out,
+                                                                 (const bf16*)kstash, off_gate, (bf16*)tail, (const int*)row_seq,
+                                                                 (const int*)row_slot, P, rows);
     LSB_CHECK_LAUNCH();
 }
 

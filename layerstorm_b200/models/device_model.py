@@ -251,6 +251,7 @@ class Workspace:
             self.sel_cnt = z(R, dtype=i32)
             self.q_idx = z(R, cfg.index_n_heads, cfg.index_head_dim, dtype=b16)
             self.idx_w = z(R, cfg.index_n_heads)
+            self.kstash = z(R, cfg.index_head_dim, dtype=b16)
         # FFN
         F = max(cfg.dense_inter, 1)
         self.gu = z(R, 2 * F)
@@ -580,7 +581,7 @@ class DeviceModel:
         if has_idx:
             nat.call("lsb_indexer_k_append", ws.proj, ldp, off_ik, off_ig, L["idx_ln_w"], L["idx_ln_b"], L.get("idx_ape"),
                      self.inv_freq_idx, cfg.index_rope_dim, self.idx_cache[i], self.block_table, self.max_pages, self.page // P,
-                     self.idx_tail.get(i), ws.row_seq, ws.row_pos, ws.row_slot, R, P, 1e-6)
+                     self.idx_tail.get(i), ws.kstash, ws.row_seq, ws.row_pos, ws.row_slot, R, P, 1e-6)
         nat.call("lsb_mla_prep", ws.proj, ldp, off_qa, cfg.q_lora, off_kv, dl, dr, L["qa_norm"], L["kv_norm"], self.inv_freq,
                  ws.q_c, self.kv_cache[i], self.block_table, self.max_pages, ws.row_seq, ws.row_pos, R, self.page,
                  KV_FMT[self.kv_fmt], cfg.rms_eps)
@@ -593,7 +594,8 @@ class DeviceModel:
         if cfg.has_indexer:
             if has_idx:
                 nat.call("lsb_indexer_q_prep", ws.qproj, ldq, Hh * (dn + dr), ws.proj, ldp, off_iw, cfg.index_n_heads,
-                         cfg.index_rope_dim, self.inv_freq_idx, ws.row_pos, ws.q_idx, ws.idx_w, R)
+                         cfg.index_rope_dim, self.inv_freq_idx, ws.row_pos, ws.q_idx, ws.idx_w, ws.kstash, off_ig,
+                         self.idx_tail.get(i), ws.row_seq, ws.row_slot, P, R)
                 nat.call("lsb_indexer_score", ws.q_idx, ws.idx_w, cfg.index_n_heads, self.idx_cache[i], self.block_table,
                          self.max_pages, self.page // P, ws.row_seq, ws.n_entries, ws.scores, ws.max_entries, R, ws.max_entries)
                 nat.call("lsb_indexer_topk", ws.scores, ws.max_entries, ws.n_entries, ws.row_len, ws.row_seq,

@@ -117,9 +117,17 @@ class Engine:
         """rows: (token, slot, pos); seq_groups: (row0, nrows, slot)."""
         R = len(rows)
         P = max(self.cfg.index_kpool, 1)
-        if not hasattr(ws, "h_inp"):
-            ws.h_inp = torch.zeros(9, ws.R, dtype=torch.int32).pin_memory()
-        h = ws.h_inp
+        # ring of pinned staging buffers: a buffer is rewritten only after the copy that last
+        # read it has completed, so the host can run ahead of the device by several steps
+        if not hasattr(ws, "h_ring"):
+            ws.h_ring = [torch.zeros(9, ws.R, dtype=torch.int32).pin_memory() for _ in range(4)]
+            ws.h_ev = [None] * 4
+            ws.h_i = 0
+        k = ws.h_i
+        ws.h_i = (k + 1) % 4
+        if ws.h_ev[k] is not None:
+            ws.h_ev[k].synchronize()
+        h = ws.h_ring[k]
         h.zero_()
         h[1].fill_(-1)
         for r, (tok, slot, pos) in enumerate(rows):
@@ -128,6 +136,9 @@ class Engine:
         for j, (r0, n, slot) in enumerate(seq_groups):
             h[6, j] = r0; h[7, j] = n; h[8, j] = slot
         ws.inp.copy_(h, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream())
+        ws.h_ev[k] = ev
         self.h2d_bytes += 9 * ws.R * 4
 
     def _ws_decode(self, B: int) -> Workspace:

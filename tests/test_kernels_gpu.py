@@ -152,6 +152,7 @@ def test_sampling_kernels():
     close(ent, -(p * torch.log(p.clamp_min(1e-30))).sum(-1) / math.log(V), 1e-3, 1e-5, "entropy")
     # top-k=1 sampling is argmax; the same seed repeats; top-p keeps the draw inside the nucleus
     out = torch.zeros(R, dtype=torch.int32, device=DEV)
+    logits[1, 4000] = 49.0               # exact ties at the k-th value are all kept, so break the tie
     nat.call("lsb_sample", logits, V, R, V, 1.0, 1, 1.0, 123, None, out)
     torch.cuda.synchronize()
     assert out.cpu().tolist() == ids.cpu().tolist()

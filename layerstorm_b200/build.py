@@ -78,7 +78,7 @@ def _link(objs, out: Path, kind: str):
     if out.exists() and stamp.exists() and stamp.read_text() == key:
         return
     if kind == "cu":
-        cmd = [NVCC, "-shared", "-o", str(out)] + [str(o) for o in objs] + ["-lcuda"]
+        cmd = [NVCC, "-shared", "-o", str(out)] + [str(o) for o in objs] + []
     else:
         cmd = [CXX, "-shared", "-o", str(out)] + [str(o) for o in objs] + ["-pthread", "-ldl", "-lrt"]
     r = subprocess.run(cmd, capture_output=True, text=True)

@@ -1,0 +1,43 @@
+"""tcgen05 / TMA GEMM against a PyTorch fp32 reference."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from layerstorm_b200.ops import _native as nat
+
+
+def run(M, N, K, out_bf16=False, bias=False, splitk=True, ldx=None, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    ldx = ldx or K
+    x = (torch.randn(M, ldx, generator=g)).to(torch.bfloat16).cuda()
+    w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).cuda()
+    b = torch.randn(N, generator=g).cuda() if bias else None
+    out = torch.zeros(M, N, device="cuda", dtype=torch.bfloat16 if out_bf16 else torch.float32)
+    part = torch.zeros(16 * M * N, device="cuda") if splitk else None
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    nat.call("lsb_gemm_bf16_tc", out, x, w, b, M, N, K, ldx, K, N, int(out_bf16), part, err)
+    torch.cuda.synchronize()
+    assert int(err[0]) == 0, f"kernel reported wait timeout code {int(err[0])}"
+    ref = x[:, :K].float() @ w.float().T
+    if bias:
+        ref = ref + b
+    tol = 2e-2 if out_bf16 else 2e-3
+    e = (out.float() - ref).abs().max() / ref.abs().max()
+    assert float(e) < tol, (M, N, K, float(e))
+
+
+def test_gemm_tc_smallest():
+    run(16, 128, 64, splitk=False)
+
+
+@pytest.mark.parametrize("M,N,K", [(16, 128, 256), (32, 256, 512), (64, 384, 1024), (128, 512, 512), (256, 256, 2048),
+                                   (300, 200, 264), (17, 130, 72), (2048, 1024, 512)])
+def test_gemm_tc_shapes(M, N, K):
+    run(M, N, K, splitk=False)
+
+
+def test_gemm_tc_splitk_bias_bf16():
+    run(32, 256, 4096, splitk=True, bias=True)
+    run(48, 512, 2048, splitk=True, out_bf16=True, bias=True)
+    run(64, 128, 1024, ldx=1032, splitk=True)

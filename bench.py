@@ -92,7 +92,8 @@ def main():
     ap.add_argument("--ctx", type=int, default=8192)
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--prefill-chunk", type=int, default=256)
-    ap.add_argument("--headroom-gib", type=float, default=6.0, help="HBM left free after weights (caches, workspaces, context)")
+    ap.add_argument("--headroom-gib", type=float, default=2.5, help="HBM left free after weights (caches, workspaces, context)")
+    ap.add_argument("--no-graph", action="store_true", help="eager launches (for per-kernel profiling)")
     ap.add_argument("--synthetic-fill", action="store_true", help="skip the real prefill; decode over an uninitialised cache")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -117,17 +118,13 @@ def main():
     cfg = get_preset(args.model)
     dev = torch.device("cuda", local)
     t0 = time.time()
-    # expert slots that fit next to the non-expert weights: the rest would stream from pinned host RAM
-    free_b, total_b = torch.cuda.mem_get_info(dev)
-    ef = expert_layout("nvfp4" if cfg.expert_quant.startswith(("nvfp4", "gguf")) else cfg.expert_quant, cfg.hidden, cfg.moe_inter)
-    n_moe = cfg.n_moe_layers()
-    non_expert_est = 19.5e9 if cfg.name == "GLM-5.3-Flash" else 0.15 * total_b
-    budget = free_b - non_expert_est - args.headroom_gib * 2 ** 30
-    slots = int(budget // (ef.stride * max(n_moe, 1))) - cfg.n_shared
-    slots = max(cfg.top_k, min(cfg.n_routed, slots))
-    model = DeviceModel.random_init(cfg, dev, kv_fmt="fp8", page=64, seed=1234 + rank, expert_slots=slots, embed_on_host=True)
+    # as many routed-expert slots per layer as fit in HBM next to the other weights; any remainder
+    # would be streamed from pinned host RAM by the expert cache
+    model = DeviceModel.random_init(cfg, dev, kv_fmt="fp8", page=64, seed=1234 + rank, expert_slots="auto", embed_on_host=True,
+                                    reserve_bytes=int(args.headroom_gib * 2 ** 30))
+    slots = getattr(model, "expert_slots", cfg.n_routed)
     max_ctx = args.ctx + args.steps + args.warmup + 64
-    eng = Engine(model, max_seqs=args.batch, max_ctx=max_ctx, prefill_chunk=args.prefill_chunk, max_batch=args.batch)
+    eng = Engine(model, max_seqs=args.batch, max_ctx=max_ctx, prefill_chunk=args.prefill_chunk, max_batch=args.batch, use_graph=not args.no_graph)
     torch.cuda.synchronize()
     t_init = time.time() - t0
 
@@ -175,7 +172,13 @@ def main():
 
     # ---- timed region 2: device time of the step itself (graph replay only) ----
     B = args.batch
-    graph = eng.graphs[B]
+    graph = eng.graphs.get(B)
+    if graph is None:      # eager mode: device timing = the same loop
+        class _G:
+            def replay(self_inner):
+                eng.model.forward(eng.ws_decode[B], B, B, 0, B)
+                eng.model.argmax(eng.ws_decode[B], B)
+        graph = _G()
     evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     torch.cuda.synchronize()
     with torch.cuda.stream(eng.stream):

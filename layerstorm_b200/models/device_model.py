@@ -375,11 +375,13 @@ class DeviceModel:
         return m
 
     @classmethod
-    def random_init(cls, cfg: ModelConfig, device="cuda", kv_fmt="fp8", page=64, seed=0, expert_slots: Optional[int] = None,
-                    embed_on_host: bool = False) -> "DeviceModel":
+    def random_init(cls, cfg: ModelConfig, device="cuda", kv_fmt="fp8", page=64, seed=0, expert_slots=None,
+                    embed_on_host: bool = False, reserve_bytes: int = 4 << 30) -> "DeviceModel":
         """Random weights generated directly in storage format on the device (full-size models).
-        ``expert_slots`` caps the routed-expert slots per MoE layer (VRAM expert cache); the first
-        slots hold the shared experts followed by routed experts 0..; the rest start non-resident."""
+        ``expert_slots`` caps the routed-expert slots per MoE layer (VRAM expert cache): an int, None
+        (all experts resident) or "auto" (as many as fit while leaving ``reserve_bytes`` of device
+        memory free for caches and workspaces).  The first slots hold the shared experts followed by
+        routed experts 0..; the rest start non-resident."""
         m = cls(cfg, device, kv_fmt, page)
         dev = m.device
         gen = torch.Generator(device=dev).manual_seed(seed)
@@ -442,22 +444,34 @@ class DeviceModel:
             if cfg.is_moe_layer(i):
                 L["router"] = QLinear.random(cfg.n_routed, H, "f32", dev, std=0.1, gen=gen)
                 L["router_bias"] = rnd(cfg.n_routed, std=0.05) if cfg.router_bias else None
-                ef = expert_layout(eq, H, cfg.moe_inter)
-                E_total = cfg.n_routed + cfg.n_shared
-                n_slots = E_total if expert_slots is None else min(E_total, expert_slots + cfg.n_shared)
-                arena = ExpertArena(ef, n_slots, E_total, dev)
-                m._random_fill_arena(arena, eq, gen)
-                # shared experts first, then routed experts in id order
-                order = list(range(cfg.n_routed, E_total)) + list(range(cfg.n_routed))
-                so = torch.full((E_total,), -1, dtype=torch.int32)
-                for s_, e in enumerate(order[:n_slots]):
-                    so[e] = s_
-                arena.slot_of.copy_(so)
-                L["arena"] = arena
+                L["arena"] = None      # allocated below, once the non-expert footprint is known
             else:
                 L["mlp_gu"] = QLinear.random(2 * cfg.dense_inter, H, dq, dev, gen=gen)
                 L["mlp_down"] = QLinear.random(H, cfg.dense_inter, dq, dev, gen=gen)
             m.layers.append(L)
+        moe_layers = [L for L in m.layers if "arena" in L]
+        if moe_layers:
+            ef = expert_layout(eq, H, cfg.moe_inter)
+            E_total = cfg.n_routed + cfg.n_shared
+            if expert_slots == "auto":
+                free_b, _ = torch.cuda.mem_get_info(dev)
+                free_b += torch.cuda.memory_reserved(dev) - torch.cuda.memory_allocated(dev)
+                fit = int((free_b - reserve_bytes) // (ef.stride * len(moe_layers)))
+                n_slots = max(cfg.top_k + cfg.n_shared, min(E_total, fit))
+            elif expert_slots is None:
+                n_slots = E_total
+            else:
+                n_slots = min(E_total, int(expert_slots) + cfg.n_shared)
+            m.expert_slots = n_slots - cfg.n_shared
+            order = list(range(cfg.n_routed, E_total)) + list(range(cfg.n_routed))
+            so = torch.full((E_total,), -1, dtype=torch.int32)
+            for s_, e in enumerate(order[:n_slots]):
+                so[e] = s_
+            for L in moe_layers:
+                arena = ExpertArena(ef, n_slots, E_total, dev)
+                m._random_fill_arena(arena, eq, gen)
+                arena.slot_of.copy_(so)
+                L["arena"] = arena
         m._finish()
         return m
 

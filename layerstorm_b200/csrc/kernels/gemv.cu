@@ -61,6 +61,44 @@ __global__ void __launch_bounds__(256) gemv_kernel(Mat mat, const bf16* __restri
     pdl_launch_dependents();
 }
 
+// Small-N variant: one block per pair of weight rows, all 256 threads stride over K, partial
+// sums combined through shared memory in warp order.  Keeps every SM busy when N is only a few
+// hundred rows (router, low-rank projections).
+template <class Mat, int MT, bool OUT_BF16>
+__global__ void __launch_bounds__(256) gemv_smalln_kernel(Mat mat, const bf16* __restrict__ x, int ldx, void* __restrict__ out,
+                                                          int ldo, int N, int K, float alpha, const float* __restrict__ bias) {
+    __shared__ float red[8][2 * MT];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * 2;
+    const int n1 = min(n0 + 1, N - 1);
+    float acc0[MT], acc1[MT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) acc0[m] = acc1[m] = 0.f;
+    auto r0 = mat.row(n0);
+    auto r1 = mat.row(n1);
+    pdl_wait();
+    warp_dot2<decltype(r0), MT>(r0, r1, x, ldx, K, acc0, acc1, threadIdx.x, 256);
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+        const float a = warp_sum(acc0[m]), b = warp_sum(acc1[m]);
+        if (lane == 0) { red[warp][2 * m] = a; red[warp][2 * m + 1] = b; }
+    }
+    __syncthreads();
+    if (threadIdx.x < 2 * MT) {
+        float a = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) a += red[w][threadIdx.x];
+        a *= alpha;
+        const int m = threadIdx.x >> 1, n = n0 + (threadIdx.x & 1);
+        if (n < N) {
+            if (bias) a += bias[n];
+            if (OUT_BF16) reinterpret_cast<bf16*>(out)[(size_t)m * ldo + n] = __float2bfloat16(a);
+            else reinterpret_cast<float*>(out)[(size_t)m * ldo + n] = a;
+        }
+    }
+    pdl_launch_dependents();
+}
+
 template <class Mat>
 static int launch_gemv(Mat mat, const bf16* x, int ldx, void* out, int ldo, int M, int N, int K, float alpha,
                        const float* bias, int out_bf16, cudaStream_t st) {
@@ -71,8 +109,11 @@ static int launch_gemv(Mat mat, const bf16* x, int ldx, void* out, int ldo, int 
         const int mt = rem >= 4 ? 4 : (rem >= 2 ? 2 : 1);
         const bf16* xp = x + (size_t)m0 * ldx;
         void* op = reinterpret_cast<char*>(out) + (size_t)m0 * ldo * osz;
-#define LSB_GEMV_CASE(MT_)                                                                                      \
-    if (out_bf16) gemv_kernel<Mat, MT_, true><<<grid, 256, 0, st>>>(mat, xp, ldx, op, ldo, N, K, alpha, bias); \
+#define LSB_GEMV_CASE(MT_)                                                                                                  \
+    if (N <= 1024) {                                                                                                        \
+        if (out_bf16) gemv_smalln_kernel<Mat, MT_, true><<<(N + 1) / 2, 256, 0, st>>>(mat, xp, ldx, op, ldo, N, K, alpha, bias); \
+        else gemv_smalln_kernel<Mat, MT_, false><<<(N + 1) / 2, 256, 0, st>>>(mat, xp, ldx, op, ldo, N, K, alpha, bias);         \
+    } else if (out_bf16) gemv_kernel<Mat, MT_, true><<<grid, 256, 0, st>>>(mat, xp, ldx, op, ldo, N, K, alpha, bias);           \
     else gemv_kernel<Mat, MT_, false><<<grid, 256, 0, st>>>(mat, xp, ldx, op, ldo, N, K, alpha, bias);
         if (mt == 4) { LSB_GEMV_CASE(4) } else if (mt == 2) { LSB_GEMV_CASE(2) } else { LSB_GEMV_CASE(1) }
 #undef LSB_GEMV_CASE

@@ -74,15 +74,113 @@ struct WRowNvfp4 {
     }
 };
 
+// ---- fast NVFP4 path -------------------------------------------------------------------
+// Two E2M1 values per byte convert to an f16x2 with one cvt instruction; products with fp16
+// activations are exact (2 x 8 significant bits), are summed 8 at a time in fp16 and then
+// scaled and accumulated in fp32 per 16-element scale group.
+__device__ __forceinline__ void fp4x8_to_half2x4(uint32_t v, __half2* h) {
+    uint32_t r0, r1, r2, r3;
+    asm("{ .reg .b8 b0, b1, b2, b3;\n mov.b32 {b0, b1, b2, b3}, %4;\n cvt.rn.f16x2.e2m1x2 %0, b0;\n cvt.rn.f16x2.e2m1x2 %1, b1;\n"
+        " cvt.rn.f16x2.e2m1x2 %2, b2;\n cvt.rn.f16x2.e2m1x2 %3, b3;\n}"
+        : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(v));
+    h[0] = *reinterpret_cast<__half2*>(&r0); h[1] = *reinterpret_cast<__half2*>(&r1);
+    h[2] = *reinterpret_cast<__half2*>(&r2); h[3] = *reinterpret_cast<__half2*>(&r3);
+}
+
+// Activation rows staged in shared memory as fp16 in a "part-major" layout so that the 16-byte
+// reads of a warp are bank-conflict free: element k lives at ((k%32)/8 * nchunks + k/32)*8 + k%8.
+__device__ __forceinline__ int xs_index(int k, int nchunks) { return (((k & 31) >> 3) * nchunks + (k >> 5)) * 8 + (k & 7); }
+
+// Stage `nrows` bf16 rows (gathered through row pointers) of length K into xs[m][K] (fp16).
+__device__ __forceinline__ void stage_x_half(__half* xs, const bf16* const* rows, int nrows, int K) {
+    const int nchunks = K >> 5;
+    for (int m = 0; m < nrows; ++m) {
+        const bf16* src = rows[m];
+        for (int k8 = threadIdx.x; k8 < (K >> 3); k8 += blockDim.x) {
+            float f[8];
+            unpack_bf16x8(__ldg(reinterpret_cast<const uint4*>(src + k8 * 8)), f);
+            __half2 h[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+            const int k = k8 * 8;
+            *reinterpret_cast<uint4*>(xs + (size_t)m * K + xs_index(k, nchunks)) = *reinterpret_cast<uint4*>(h);
+        }
+    }
+}
+
+// One 32-element chunk (16 bytes of fp4, two scale groups) of one weight row against MT staged rows.
+template <int MT>
+__device__ __forceinline__ void nvfp4_chunk_dot(const uint4& v, float s0, float s1, const __half* xs, int K, int nchunks, int c, int nvalid,
+                                                float* acc) {
+    __half2 w[16];
+    fp4x8_to_half2x4(v.x, w); fp4x8_to_half2x4(v.y, w + 4); fp4x8_to_half2x4(v.z, w + 8); fp4x8_to_half2x4(v.w, w + 12);
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+        if (m < nvalid) {
+            const __half* xb = xs + (size_t)m * K + c * 8;
+            __half2 a0 = __float2half2_rn(0.f), a1 = a0;
+#pragma unroll
+            for (int part = 0; part < 4; ++part) {
+                const uint4 xv = *reinterpret_cast<const uint4*>(xb + (size_t)part * nchunks * 8);
+                const __half2* x2 = reinterpret_cast<const __half2*>(&xv);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    if (part < 2) a0 = __hfma2(w[part * 4 + i], x2[i], a0);
+                    else a1 = __hfma2(w[part * 4 + i], x2[i], a1);
+                }
+            }
+            const float2 f0 = __half22float2(a0), f1 = __half22float2(a1);
+            acc[m] = fmaf(s0, f0.x + f0.y, acc[m]);
+            acc[m] = fmaf(s1, f1.x + f1.y, acc[m]);
+        }
+    }
+}
+
+// Full row: weight row pointer (K/2 bytes), scale-atom base, row index n.
+template <int MT>
+__device__ __forceinline__ void nvfp4_row_dot(const uint8_t* __restrict__ wrow, const uint8_t* __restrict__ sf, int n, int K,
+                                              const __half* xs, int nvalid, float* acc) {
+    const int lane = threadIdx.x & 31, nchunks = K >> 5, gtiles = ((K >> 4) + 3) >> 2;
+    const size_t sf_row = (size_t)(n >> 7) * gtiles * 512 + (n & 31) * 16 + ((n & 127) >> 5) * 4;
+#pragma unroll 2
+    for (int c = lane; c < nchunks; c += 32) {
+        const uint4 v = ldg_stream(wrow + c * 16);
+        const int g = c * 2;
+        const uint16_t s2 = __ldg(reinterpret_cast<const uint16_t*>(sf + sf_row + (size_t)(g >> 2) * 512 + (g & 3)));
+        nvfp4_chunk_dot<MT>(v, fp8e4m3_to_float((uint8_t)(s2 & 0xff)), fp8e4m3_to_float((uint8_t)(s2 >> 8)), xs, K, nchunks, c, nvalid, acc);
+    }
+}
+
+// Two rows (A, B) in one pass so both rows' loads are in flight together.
+template <int MT>
+__device__ __forceinline__ void nvfp4_row_dot2(const uint8_t* __restrict__ wa, const uint8_t* __restrict__ sfa, int na,
+                                               const uint8_t* __restrict__ wb, const uint8_t* __restrict__ sfb, int nb, int K,
+                                               const __half* xs, int nvalid, float* acca, float* accb) {
+    const int lane = threadIdx.x & 31, nchunks = K >> 5, gtiles = ((K >> 4) + 3) >> 2;
+    const size_t ra = (size_t)(na >> 7) * gtiles * 512 + (na & 31) * 16 + ((na & 127) >> 5) * 4;
+    const size_t rb = (size_t)(nb >> 7) * gtiles * 512 + (nb & 31) * 16 + ((nb & 127) >> 5) * 4;
+#pragma unroll 2
+    for (int c = lane; c < nchunks; c += 32) {
+        const uint4 va = ldg_stream(wa + c * 16);
+        const uint4 vb = ldg_stream(wb + c * 16);
+        const int g = c * 2;
+        const size_t go = (size_t)(g >> 2) * 512 + (g & 3);
+        const uint16_t sa = __ldg(reinterpret_cast<const uint16_t*>(sfa + ra + go));
+        const uint16_t sb = __ldg(reinterpret_cast<const uint16_t*>(sfb + rb + go));
+        nvfp4_chunk_dot<MT>(va, fp8e4m3_to_float((uint8_t)(sa & 0xff)), fp8e4m3_to_float((uint8_t)(sa >> 8)), xs, K, nchunks, c, nvalid, acca);
+        nvfp4_chunk_dot<MT>(vb, fp8e4m3_to_float((uint8_t)(sb & 0xff)), fp8e4m3_to_float((uint8_t)(sb >> 8)), xs, K, nchunks, c, nvalid, accb);
+    }
+}
+
 // acc0[m] += sum_k w0[k]*x[m][k], acc1 likewise for w1.  x is bf16 [MT][ldx].
 // Partial sums stay per-lane; call warp_sum on them afterwards.
 template <class WF, int MT>
 __device__ __forceinline__ void warp_dot2(const WF& w0, const WF& w1, const bf16* __restrict__ x, int ldx, int K,
-                                          float* acc0, float* acc1) {
+                                          float* acc0, float* acc1, int tid = -1, int nthr = 32) {
     constexpr int E = WF::EPL;
-    const int lane = threadIdx.x & 31;
+    const int lane = tid < 0 ? (threadIdx.x & 31) : tid;
 #pragma unroll 2
-    for (int k = lane * E; k + E <= K; k += 32 * E) {
+    for (int k = lane * E; k + E <= K; k += nthr * E) {
         float a[E], b[E];
         w0.load(k, a);
         w1.load(k, b);

@@ -144,9 +144,9 @@ __global__ void __launch_bounds__(kID) indexer_q_prep_kernel(const bf16* __restr
                                                               const bf16* __restrict__ kstash, int off_gate, bf16* __restrict__ tail,
                                                               const int* __restrict__ row_seq, const int* __restrict__ row_slot, int P, int R) {
     __shared__ float buf[kID];
-    const int r = blockIdx.x, t = threadIdx.x;
+    const int r = blockIdx.x, h = blockIdx.y, t = threadIdx.x;
     pdl_wait();
-    if (P > 1 && row_seq[r] >= 0) {
+    if (h == 0 && P > 1 && row_seq[r] >= 0) {
         // publish this row's key | gate to the sequence's open-pool tail unless the pool is
         // completed by a later row of this same launch (then nobody will read it)
         const int ipos = row_pos[r], j = ipos % P, rc = r + (P - 1 - j);
@@ -158,13 +158,13 @@ __global__ void __launch_bounds__(kID) indexer_q_prep_kernel(const bf16* __restr
         }
     }
     const float pos = (float)row_pos[r];
-    for (int h = 0; h < IH; ++h) {
+    {
         float v = __bfloat162float(qproj[(size_t)r * ldq + off_q + h * kID + t]);
         if (dr > 0) rope_first(v, buf, dr, pos, inv_freq);
         v = fwht128(__bfloat162float(__float2bfloat16(v)), buf);
         q_idx[((size_t)r * IH + h) * kID + t] = __float2bfloat16(v);
     }
-    if (t < IH) w_out[(size_t)r * IH + t] = proj[(size_t)r * ldp + off_w + t] * rsqrtf((float)IH) * rsqrtf((float)kID);
+    if (h == 0 && t < IH) w_out[(size_t)r * IH + t] = proj[(size_t)r * ldp + off_w + t] * rsqrtf((float)IH) * rsqrtf((float)kID);
     pdl_launch_dependents();
 }
 
@@ -343,7 +343,7 @@ LSB_API int lsb_indexer_q_prep(const void* qproj, int ldq, int off_q, const void
                                const void* inv_freq, const void* row_pos, void* q_idx, void* w_out, const void* kstash,
                                int off_gate, void* tail, const void* row_seq, const void* row_slot, int P, int rows, void* stream) {
     if (IH > kID) return -1;
-    indexer_q_prep_kernel<<<rows, kID, 0, (cudaStream_t)stream>>>((const bf16*)qproj, ldq, off_q, (const float*)proj, ldp, off_w, IH, dr,
+    indexer_q_prep_kernel<<<dim3(rows, IH), kID, 0, (cudaStream_t)stream>>>((const bf16*)qproj, ldq, off_q, (const float*)proj, ldp, off_w, IH, dr,
                                                                  (const float*)inv_freq, (const int*)row_pos, (bf16*)q_idx, (float*)w_out,
                                                                  (const bf16*)kstash, off_gate, (bf16*)tail, (const int*)row_seq,
                                                                  (const int*)row_slot, P, rows);

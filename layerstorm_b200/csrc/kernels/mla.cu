@@ -294,24 +294,39 @@ __global__ void __launch_bounds__(256) mla_decode_kernel(MlaDecodeParams p) {
     pdl_launch_dependents();
 }
 
-// Merge split partials in split order: out = sum_s exp(m_s - M) acc_s / sum_s exp(m_s - M) l_s.
-__global__ void mla_combine_kernel(bf16* __restrict__ out, float* __restrict__ lse, const float* __restrict__ o_part,
-                                   const float* __restrict__ ml_part, int H, int NS, int dl) {
-    const int r = blockIdx.x, h = blockIdx.y;
+// Merge split partials in split order: out = sum_s exp(m_s - M) acc_s / sum_s exp(m_s - M) l_s.  NS <= 32.
+__global__ void __launch_bounds__(128) mla_combine_kernel(bf16* __restrict__ out, float* __restrict__ lse, const float* __restrict__ o_part,
+                                                          const float* __restrict__ ml_part, int H, int NS, int dl) {
+    __shared__ float w[32];
+    __shared__ float s_invL, s_lse;
+    const int r = blockIdx.x, h = blockIdx.y, t = threadIdx.x;
     pdl_wait();
     const float* ml = ml_part + ((size_t)r * H + h) * NS * 2;
-    float M = -INFINITY;
-    for (int s = 0; s < NS; ++s) M = fmaxf(M, ml[2 * s]);
-    float L = 0.f;
-    for (int s = 0; s < NS; ++s) if (ml[2 * s] > -INFINITY) L += __expf(ml[2 * s] - M) * ml[2 * s + 1];
-    const float invL = L > 0.f ? 1.f / L : 0.f;
-    for (int d = threadIdx.x; d < dl; d += blockDim.x) {
+    if (t < 32) {
+        const float m = t < NS ? ml[2 * t] : -INFINITY;
+        const float l = t < NS ? ml[2 * t + 1] : 0.f;
+        const float M = warp_max(m);
+        const float e = (m > -INFINITY) ? __expf(m - M) : 0.f;
+        w[t] = e;
+        // fixed-order sum over splits (lane 0), so the result does not depend on shuffle order
+        __syncwarp();
+        if (t == 0) {
+            float L = 0.f;
+            for (int s = 0; s < NS; ++s) L += w[s] * ml[2 * s + 1];
+            s_invL = L > 0.f ? 1.f / L : 0.f;
+            s_lse = L > 0.f ? M + logf(L) : -INFINITY;
+        }
+        (void)l;
+    }
+    __syncthreads();
+    const float invL = s_invL;
+    const float* op = o_part + ((size_t)r * H + h) * NS * dl;
+    for (int d = t; d < dl; d += blockDim.x) {
         float a = 0.f;
-        for (int s = 0; s < NS; ++s)
-            if (ml[2 * s] > -INFINITY) a += __expf(ml[2 * s] - M) * o_part[(((size_t)r * H + h) * NS + s) * dl + d];
+        for (int s = 0; s < NS; ++s) a = fmaf(w[s], op[(size_t)s * dl + d], a);
         out[((size_t)r * H + h) * dl + d] = __float2bfloat16(a * invL);
     }
-    if (lse && threadIdx.x == 0) lse[(size_t)r * H + h] = L > 0.f ? M + logf(L) : -INFINITY;
+    if (lse && t == 0) lse[(size_t)r * H + h] = s_lse;
     pdl_launch_dependents();
 }
 
@@ -364,7 +379,7 @@ LSB_API int lsb_mla_decode(const void* q, const void* cache, const void* block_t
                            const void* row_len, const void* sel_idx, const void* sel_cnt, int sel_ld, void* out, void* lse,
                            void* o_part, void* ml_part, int R, int H, int dl, int dr, int page, int kv_fmt, int NS,
                            float scale, void* stream) {
-    if (dl % 16 || dr % 8 || dl > 512) return -1;
+    if (dl % 16 || dr % 8 || dl > 512 || NS > 32) return -1;
     cudaStream_t st = (cudaStream_t)stream;
     MlaDecodeParams p;
     p.q = (const bf16*)q; p.cache = (const uint8_t*)cache; p.block_table = (const int*)block_table; p.max_pages = max_pages;

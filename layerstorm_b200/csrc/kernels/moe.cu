@@ -319,6 +319,108 @@ __global__ void __launch_bounds__(256) moe_down_kernel(const bf16* __restrict__ 
     pdl_launch_dependents();
 }
 
+
+// ---- NVFP4 fast path (hidden and expert width multiples of 128) -----------------------------
+// Row order inside a 128-row tile follows the scale-atom layout: a block covers 4 (gate/up) or 8
+// (down) consecutive values of n%32 for all four 32-row quads, so every 32-byte sector of scale
+// bytes it touches is used completely.
+template <int MT>
+__global__ void __launch_bounds__(256) moe_gateup_fp4_kernel(const bf16* __restrict__ x, const uint8_t* __restrict__ arena,
+                                                             const int* __restrict__ slot_of, ExpertFmt ef,
+                                                             const int* __restrict__ group_expert, const int* __restrict__ group_n,
+                                                             const int* __restrict__ group_pairs, const int* __restrict__ n_groups,
+                                                             bf16* __restrict__ act, int S, float limit, int* __restrict__ miss_flag) {
+    extern __shared__ __align__(16) uint8_t smraw[];
+    __half* xs = reinterpret_cast<__half*>(smraw);
+    __shared__ const bf16* rows[4];
+    pdl_wait();
+    const int g = blockIdx.y;
+    if (g >= (n_groups ? n_groups[0] : (int)gridDim.y)) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int e = group_expert[g];
+    const int n = MT == 1 ? 1 : (group_n ? group_n[g] : 1);
+    const int slot = (e >= 0) ? slot_of[e] : -1;
+    if (slot < 0) { if (e >= 0 && threadIdx.x == 0 && blockIdx.x == 0) atomicExch(miss_flag, e + 1); return; }
+    int pr[MT];
+#pragma unroll
+    for (int i = 0; i < MT; ++i) pr[i] = group_pairs ? group_pairs[g * 4 + min(i, n - 1)] : g;
+    if (threadIdx.x < MT) rows[threadIdx.x] = x + (size_t)(pr[threadIdx.x] / S) * ef.H;
+    __syncthreads();
+    stage_x_half(xs, rows, n, ef.H);
+    __syncthreads();
+    const uint8_t* base = arena + (size_t)slot * ef.stride;
+    const float* tail = reinterpret_cast<const float*>(base + ef.off_tail);
+    const float sg = tail[0], su = tail[1];
+    const int tile = blockIdx.x >> 3, blk = blockIdx.x & 7;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int j = warp * 2 + r;                       // 0..15
+        const int f = tile * 128 + (j >> 2) * 32 + blk * 4 + (j & 3);
+        float ag[MT], au[MT];
+#pragma unroll
+        for (int m = 0; m < MT; ++m) ag[m] = au[m] = 0.f;
+        nvfp4_row_dot2<MT>(base + ef.off_gate + (size_t)f * (ef.H >> 1), base + ef.off_sg, f,
+                           base + ef.off_up + (size_t)f * (ef.H >> 1), base + ef.off_su, f, ef.H, xs, n, ag, au);
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            if (m < n) {
+                float gv = warp_sum(ag[m]) * sg, uv = warp_sum(au[m]) * su;
+                if (limit > 0.f) { gv = fminf(gv, limit); uv = fminf(fmaxf(uv, -limit), limit); }
+                if (lane == 0) act[(size_t)pr[m] * ef.F + f] = __float2bfloat16(siluf_(gv) * uv);
+            }
+        }
+    }
+    pdl_launch_dependents();
+}
+
+template <int MT>
+__global__ void __launch_bounds__(256) moe_down_fp4_kernel(const bf16* __restrict__ act, const uint8_t* __restrict__ arena,
+                                                           const int* __restrict__ slot_of, ExpertFmt ef,
+                                                           const int* __restrict__ group_expert, const int* __restrict__ group_n,
+                                                           const int* __restrict__ group_pairs, const int* __restrict__ n_groups,
+                                                           float* __restrict__ y) {
+    extern __shared__ __align__(16) uint8_t smraw[];
+    __half* xs = reinterpret_cast<__half*>(smraw);
+    __shared__ const bf16* rows[4];
+    pdl_wait();
+    const int g = blockIdx.y;
+    if (g >= (n_groups ? n_groups[0] : (int)gridDim.y)) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int e = group_expert[g];
+    const int n = MT == 1 ? 1 : (group_n ? group_n[g] : 1);
+    const int slot = (e >= 0) ? slot_of[e] : -1;
+    if (slot < 0) return;
+    int pr[MT];
+#pragma unroll
+    for (int i = 0; i < MT; ++i) pr[i] = group_pairs ? group_pairs[g * 4 + min(i, n - 1)] : g;
+    if (threadIdx.x < MT) rows[threadIdx.x] = act + (size_t)pr[threadIdx.x] * ef.F;
+    __syncthreads();
+    stage_x_half(xs, rows, n, ef.F);
+    __syncthreads();
+    const uint8_t* base = arena + (size_t)slot * ef.stride;
+    const float sd = reinterpret_cast<const float*>(base + ef.off_tail)[2];
+    const int tile = blockIdx.x >> 2, blk = blockIdx.x & 3;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int j0 = warp * 4 + r * 2;                  // 0..31, two rows per pass
+        const int h0 = tile * 128 + (j0 >> 3) * 32 + blk * 8 + (j0 & 7);
+        const int h1 = h0 + 1;
+        float a0[MT], a1[MT];
+#pragma unroll
+        for (int m = 0; m < MT; ++m) a0[m] = a1[m] = 0.f;
+        nvfp4_row_dot2<MT>(base + ef.off_down + (size_t)h0 * (ef.F >> 1), base + ef.off_sd, h0,
+                           base + ef.off_down + (size_t)h1 * (ef.F >> 1), base + ef.off_sd, h1, ef.F, xs, n, a0, a1);
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            if (m < n) {
+                const float v0 = warp_sum(a0[m]) * sd, v1 = warp_sum(a1[m]) * sd;
+                if (lane == 0) { y[(size_t)pr[m] * ef.H + h0] = v0; y[(size_t)pr[m] * ef.H + h1] = v1; }
+            }
+        }
+    }
+    pdl_launch_dependents();
+}
+
 // out[r][h] = sum_s w[r][s] * y[r*S+s][h], slots in order; experts that were not resident
 // (slot < 0) contribute nothing.  mode 0: write fp32; mode 1: add into out.
 __global__ void moe_combine_kernel(float* __restrict__ out, const float* __restrict__ y, const float* __restrict__ wts,
@@ -372,12 +474,32 @@ LSB_API int lsb_moe_build_groups(const void* ids, int npairs, int E_total, void*
     LSB_CHECK_LAUNCH();
 }
 
+// Pair mode (group_n == null): every (row, slot) pair is its own group - group_expert is the
+// routing id array itself, group g is pair g; used for small batches where no build pass is needed.
 LSB_API int lsb_moe_gateup(const void* x, const void* arena, const void* slot_of, const void* fmt_struct,
                            const void* group_expert, const void* group_n, const void* group_pairs, const void* n_groups,
                            void* act, int S, int max_groups, float limit, void* miss_flag, void* stream) {
     ExpertFmt ef = *reinterpret_cast<const ExpertFmt*>(fmt_struct);
-    dim3 grid((ef.F + 7) / 8, max_groups);
     cudaStream_t st = (cudaStream_t)stream;
+    if (ef.fmt == 2 && ef.F % 128 == 0 && ef.H % 128 == 0) {
+        dim3 g2(ef.F / 16, max_groups);
+        static bool attr = false;
+        if (!attr) {
+            cudaFuncSetAttribute(moe_gateup_fp4_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+            cudaFuncSetAttribute(moe_gateup_fp4_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+            attr = true;
+        }
+        if (!group_n)
+            moe_gateup_fp4_kernel<1><<<g2, 256, (size_t)ef.H * 2, st>>>((const bf16*)x, (const uint8_t*)arena, (const int*)slot_of, ef, (const int*)group_expert,
+                                                                        nullptr, nullptr, nullptr, (bf16*)act, S, limit, (int*)miss_flag);
+        else
+            moe_gateup_fp4_kernel<4><<<g2, 256, (size_t)ef.H * 8, st>>>((const bf16*)x, (const uint8_t*)arena, (const int*)slot_of, ef, (const int*)group_expert,
+                                                                        (const int*)group_n, (const int*)group_pairs, (const int*)n_groups, (bf16*)act, S, limit,
+                                                                        (int*)miss_flag);
+        LSB_CHECK_LAUNCH();
+    }
+    if (!group_n) return -1;   // pair mode is only implemented for the NVFP4 fast path
+    dim3 grid((ef.F + 7) / 8, max_groups);
 #define ARGS (const bf16*)x, (const uint8_t*)arena, (const int*)slot_of, ef, (const int*)group_expert, (const int*)group_n, \
              (const int*)group_pairs, (const int*)n_groups, (bf16*)act, S, limit, (int*)miss_flag
     if (ef.fmt == 0) moe_gateup_kernel<0><<<grid, 256, 0, st>>>(ARGS);
@@ -392,8 +514,25 @@ LSB_API int lsb_moe_down(const void* act, const void* arena, const void* slot_of
                          const void* group_expert, const void* group_n, const void* group_pairs, const void* n_groups,
                          void* y, int max_groups, void* stream) {
     ExpertFmt ef = *reinterpret_cast<const ExpertFmt*>(fmt_struct);
-    dim3 grid((ef.H + 15) / 16, max_groups);
     cudaStream_t st = (cudaStream_t)stream;
+    if (ef.fmt == 2 && ef.F % 128 == 0 && ef.H % 128 == 0) {
+        dim3 g2(ef.H / 32, max_groups);
+        static bool attr = false;
+        if (!attr) {
+            cudaFuncSetAttribute(moe_down_fp4_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+            cudaFuncSetAttribute(moe_down_fp4_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+            attr = true;
+        }
+        if (!group_n)
+            moe_down_fp4_kernel<1><<<g2, 256, (size_t)ef.F * 2, st>>>((const bf16*)act, (const uint8_t*)arena, (const int*)slot_of, ef, (const int*)group_expert,
+                                                                      nullptr, nullptr, nullptr, (float*)y);
+        else
+            moe_down_fp4_kernel<4><<<g2, 256, (size_t)ef.F * 8, st>>>((const bf16*)act, (const uint8_t*)arena, (const int*)slot_of, ef, (const int*)group_expert,
+                                                                      (const int*)group_n, (const int*)group_pairs, (const int*)n_groups, (float*)y);
+        LSB_CHECK_LAUNCH();
+    }
+    if (!group_n) return -1;
+    dim3 grid((ef.H + 15) / 16, max_groups);
 #define ARGS (const bf16*)act, (const uint8_t*)arena, (const int*)slot_of, ef, (const int*)group_expert, (const int*)group_n, \
              (const int*)group_pairs, (const int*)n_groups, (float*)y
     if (ef.fmt == 0) moe_down_kernel<0><<<grid, 256, 0, st>>>(ARGS);

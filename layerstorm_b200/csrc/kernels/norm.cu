@@ -51,26 +51,37 @@ __global__ void rmsnorm_kernel(bf16* __restrict__ out, const TIn* __restrict__ x
 
 constexpr int kHcMax = 4;           // residual streams
 constexpr int kHcOut = 2 * kHcMax + kHcMax * kHcMax;   // 24 mixing logits
-constexpr int kHcChunk = 128;       // hidden columns per partial block
+constexpr int kHcChunk = 32;        // hidden columns per partial block
+constexpr int kHcPerWarp = 6;       // mixing logits per warp (4 warps x 6 = 24)
 
 // Pass 1 of post+pre.  mode 0: residual[j] = x (replicate, first layer);
 // mode 1: residual[j] = post[j]*x + sum_i comb[i][j]*residual[i].
 // Then partial mixing logits and partial sum of squares of the NEW residual over this
-// block's hidden columns: part[r][chunk][0..23] logits, [24] sum of squares.
-__global__ void __launch_bounds__(kHcChunk) mhc_post_partial_kernel(float* __restrict__ residual, const float* __restrict__ x,
-                                                                    const float* __restrict__ post, const float* __restrict__ comb,
-                                                                    const float* __restrict__ fn, float* __restrict__ part,
-                                                                    int hidden, int n, int mode) {
-    __shared__ float red[4][kHcOut + 1];
-    const int r = blockIdx.x, c = blockIdx.y, h = c * kHcChunk + threadIdx.x;
+// block's 32 hidden columns: part[r][chunk][0..23] logits, [24] sum of squares.
+// Lane = column, warp = a group of 6 mixing logits; every warp recomputes the (cheap) residual
+// update, warp 0 stores it.
+__global__ void __launch_bounds__(128) mhc_post_partial_kernel(float* __restrict__ residual, const float* __restrict__ x,
+                                                               const float* __restrict__ post, const float* __restrict__ comb,
+                                                               const float* __restrict__ fn, float* __restrict__ part,
+                                                               int hidden, int n, int mode) {
+    const int r = blockIdx.x, c = blockIdx.y, lane = threadIdx.x & 31, og = threadIdx.x >> 5;
+    const int h = c * kHcChunk + lane;
     const int nout = 2 * n + n * n;
+    // mixing-matrix rows do not depend on the previous kernel: fetch them before the dependency wait
+    float f[kHcPerWarp][kHcMax];
+#pragma unroll
+    for (int i = 0; i < kHcPerWarp; ++i) {
+        const int o = og * kHcPerWarp + i;
+#pragma unroll
+        for (int j = 0; j < kHcMax; ++j) f[i][j] = (o < nout && j < n) ? __ldg(fn + ((size_t)o * n + j) * hidden + h) : 0.f;
+    }
     pdl_wait();
     float res[kHcMax];
     float* rp = residual + (size_t)r * n * hidden;
     const float xv = x[(size_t)r * hidden + h];
     if (mode == 0) {
 #pragma unroll
-        for (int j = 0; j < kHcMax; ++j) res[j] = xv;
+        for (int j = 0; j < kHcMax; ++j) res[j] = j < n ? xv : 0.f;
     } else {
         float old[kHcMax];
 #pragma unroll
@@ -85,103 +96,87 @@ __global__ void __launch_bounds__(kHcChunk) mhc_post_partial_kernel(float* __res
             res[j] = a;
         }
     }
-    float acc[kHcOut + 1];
-    float ss = 0.f;
+    float* po = part + ((size_t)r * gridDim.y + c) * (kHcOut + 1);
 #pragma unroll
-    for (int j = 0; j < kHcMax; ++j)
-        if (j < n) {
-            rp[(size_t)j * hidden + h] = res[j];
-            ss += res[j] * res[j];
-        }
-#pragma unroll
-    for (int o = 0; o < kHcOut; ++o) {
+    for (int i = 0; i < kHcPerWarp; ++i) {
         float a = 0.f;
-        if (o < nout) {
-            const float* f = fn + (size_t)o * n * hidden + h;
 #pragma unroll
-            for (int j = 0; j < kHcMax; ++j)
-                if (j < n) a += res[j] * f[(size_t)j * hidden];
-        }
-        acc[o] = a;
+        for (int j = 0; j < kHcMax; ++j) a = fmaf(res[j], f[i][j], a);
+        a = warp_sum(a);
+        const int o = og * kHcPerWarp + i;
+        if (lane == 0 && o < kHcOut) po[o] = a;
     }
-    acc[kHcOut] = ss;
-    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    if (og == 0) {
+        float ss = 0.f;
 #pragma unroll
-    for (int o = 0; o <= kHcOut; ++o) {
-        const float v = warp_sum(acc[o]);
-        if (lane == 0) red[w][o] = v;
-    }
-    __syncthreads();
-    if (threadIdx.x <= kHcOut) {
-        const float v = red[0][threadIdx.x] + red[1][threadIdx.x] + red[2][threadIdx.x] + red[3][threadIdx.x];
-        part[((size_t)r * gridDim.y + c) * (kHcOut + 1) + threadIdx.x] = v;
+        for (int j = 0; j < kHcMax; ++j)
+            if (j < n) { rp[(size_t)j * hidden + h] = res[j]; ss += res[j] * res[j]; }
+        ss = warp_sum(ss);
+        if (lane == 0) po[kHcOut] = ss;
     }
     pdl_launch_dependents();
 }
 
-// Pass 2: reduce the partials in chunk order, form pre/post gates and the Sinkhorn-
-// normalised mixing matrix, then out = RMSNorm(sum_j pre[j]*residual[j]) * w (bf16).
-__global__ void mhc_finalize_kernel(bf16* __restrict__ out, const float* __restrict__ residual, const float* __restrict__ part,
-                                    const float* __restrict__ hc_scale, const float* __restrict__ hc_base,
-                                    const float* __restrict__ norm_w, float* __restrict__ post_out, float* __restrict__ comb_out,
-                                    int hidden, int n, int nchunks, int iters, float hc_eps, float rms_eps, float post_mult) {
+// Pass 2: reduce the partials in a fixed order, form pre/post gates and the Sinkhorn-
+// normalised mixing matrix (one matrix element per lane, sums by shuffles), then
+// out = RMSNorm(sum_j pre[j]*residual[j]) * w (bf16).
+__global__ void __launch_bounds__(512) mhc_finalize_kernel(bf16* __restrict__ out, const float* __restrict__ residual, const float* __restrict__ part,
+                                                           const float* __restrict__ hc_scale, const float* __restrict__ hc_base,
+                                                           const float* __restrict__ norm_w, float* __restrict__ post_out, float* __restrict__ comb_out,
+                                                           int hidden, int n, int nchunks, int iters, float hc_eps, float rms_eps, float post_mult) {
     __shared__ float red[33];
     __shared__ float mix[kHcOut + 1];
     __shared__ float pre[kHcMax];
     extern __shared__ float row[];
-    const int r = blockIdx.x;
-    const int nout = 2 * n + n * n;
+    const int r = blockIdx.x, t = threadIdx.x;
     pdl_wait();
-    if (threadIdx.x <= kHcOut) {
+    {
+        const int o = t >> 4, sub = t & 15;
         float a = 0.f;
-        for (int c = 0; c < nchunks; ++c) a += part[((size_t)r * nchunks + c) * (kHcOut + 1) + threadIdx.x];
-        mix[threadIdx.x] = a;
+        if (o <= kHcOut)
+            for (int c = sub; c < nchunks; c += 16) a += part[((size_t)r * nchunks + c) * (kHcOut + 1) + o];
+#pragma unroll
+        for (int d = 8; d > 0; d >>= 1) a += __shfl_xor_sync(0xffffffffu, a, d, 16);
+        if (sub == 0 && o <= kHcOut) mix[o] = a;
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
+    if (t < 32) {
         const float inv = rsqrtf(mix[kHcOut] / (float)(n * hidden) + rms_eps);
-        float m[kHcOut];
-        for (int o = 0; o < nout; ++o) m[o] = mix[o] * inv;
-        for (int j = 0; j < n; ++j) {
-            pre[j] = sigmoidf_(m[j] * hc_scale[0] + hc_base[j]) + hc_eps;
-            post_out[r * n + j] = sigmoidf_(m[n + j] * hc_scale[1] + hc_base[n + j]) * post_mult;
-        }
-        float cm[kHcMax][kHcMax];
-        for (int i = 0; i < n; ++i) {
-            float mx = -INFINITY;
-            for (int j = 0; j < n; ++j) {
-                cm[i][j] = m[2 * n + i * n + j] * hc_scale[2] + hc_base[2 * n + i * n + j];
-                mx = fmaxf(mx, cm[i][j]);
+        if (t < 16) {
+            const int i = t >> 2, j = t & 3;
+            const bool valid = i < n && j < n;
+            float v = valid ? mix[2 * n + i * n + j] * inv * hc_scale[2] + hc_base[2 * n + i * n + j] : -INFINITY;
+            float mx = fmaxf(v, __shfl_xor_sync(0xffffu, v, 1, 16));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffu, mx, 2, 16));
+            float e = valid ? expf(v - mx) : 0.f;
+            float s = e + __shfl_xor_sync(0xffffu, e, 1, 16);
+            s += __shfl_xor_sync(0xffffu, s, 2, 16);
+            float cm = valid ? e / s + hc_eps : 0.f;
+            // column normalise, then (iters-1) x (row normalise, column normalise)
+            float cs = cm + __shfl_xor_sync(0xffffu, cm, 4, 16);
+            cs += __shfl_xor_sync(0xffffu, cs, 8, 16);
+            cm = valid ? cm / (cs + hc_eps) : 0.f;
+            for (int it = 1; it < iters; ++it) {
+                float rs = cm + __shfl_xor_sync(0xffffu, cm, 1, 16);
+                rs += __shfl_xor_sync(0xffffu, rs, 2, 16);
+                cm = valid ? cm / (rs + hc_eps) : 0.f;
+                cs = cm + __shfl_xor_sync(0xffffu, cm, 4, 16);
+                cs += __shfl_xor_sync(0xffffu, cs, 8, 16);
+                cm = valid ? cm / (cs + hc_eps) : 0.f;
             }
-            float s = 0.f;
-            for (int j = 0; j < n; ++j) { cm[i][j] = expf(cm[i][j] - mx); s += cm[i][j]; }
-            for (int j = 0; j < n; ++j) cm[i][j] = cm[i][j] / s + hc_eps;
+            if (valid) comb_out[(r * n + i) * n + j] = cm;
+        } else if (t < 16 + kHcMax) {
+            const int j = t - 16;
+            if (j < n) pre[j] = sigmoidf_(mix[j] * inv * hc_scale[0] + hc_base[j]) + hc_eps;
+        } else if (t < 16 + 2 * kHcMax) {
+            const int j = t - 16 - kHcMax;
+            if (j < n) post_out[r * n + j] = sigmoidf_(mix[n + j] * inv * hc_scale[1] + hc_base[n + j]) * post_mult;
         }
-        // column normalise, then (iters-1) x (row normalise, column normalise)
-        for (int j = 0; j < n; ++j) {
-            float s = 0.f;
-            for (int i = 0; i < n; ++i) s += cm[i][j];
-            for (int i = 0; i < n; ++i) cm[i][j] /= (s + hc_eps);
-        }
-        for (int it = 1; it < iters; ++it) {
-            for (int i = 0; i < n; ++i) {
-                float s = 0.f;
-                for (int j = 0; j < n; ++j) s += cm[i][j];
-                for (int j = 0; j < n; ++j) cm[i][j] /= (s + hc_eps);
-            }
-            for (int j = 0; j < n; ++j) {
-                float s = 0.f;
-                for (int i = 0; i < n; ++i) s += cm[i][j];
-                for (int i = 0; i < n; ++i) cm[i][j] /= (s + hc_eps);
-            }
-        }
-        for (int i = 0; i < n; ++i)
-            for (int j = 0; j < n; ++j) comb_out[(r * n + i) * n + j] = cm[i][j];
     }
     __syncthreads();
     const float* rp = residual + (size_t)r * n * hidden;
     float ss = 0.f;
-    for (int h = threadIdx.x; h < hidden; h += blockDim.x) {
+    for (int h = t; h < hidden; h += blockDim.x) {
         float a = 0.f;
         for (int j = 0; j < n; ++j) a += pre[j] * rp[(size_t)j * hidden + h];
         row[h] = a;
@@ -189,7 +184,7 @@ __global__ void mhc_finalize_kernel(bf16* __restrict__ out, const float* __restr
     }
     ss = block_sum(ss, red);
     const float inv = rsqrtf(ss / (float)hidden + rms_eps);
-    for (int h = threadIdx.x; h < hidden; h += blockDim.x) out[(size_t)r * hidden + h] = __float2bfloat16(row[h] * inv * norm_w[h]);
+    for (int h = t; h < hidden; h += blockDim.x) out[(size_t)r * hidden + h] = __float2bfloat16(row[h] * inv * norm_w[h]);
     pdl_launch_dependents();
 }
 
@@ -248,7 +243,7 @@ LSB_API int lsb_add_rmsnorm(void* out, void* resid, const void* x, const void* w
 
 // residual: fp32 [rows, n, hidden] updated in place; x: fp32 [rows, hidden] sublayer output
 // (or the embedding when mode == 0); post/comb: state from the previous finalize (in) and
-// for the next post (out, same buffers).  part: scratch fp32 [rows, hidden/128, 25].
+// for the next post (out, same buffers).  part: scratch fp32 [rows, hidden/32, 25].
 LSB_API int lsb_mhc_post_pre(void* out_x, void* residual, const void* x, void* post, void* comb, const void* fn,
                              const void* hc_scale, const void* hc_base, const void* norm_w, void* part, int rows,
                              int hidden, int n, int mode, int iters, float hc_eps, float rms_eps, float post_mult,
@@ -256,7 +251,7 @@ LSB_API int lsb_mhc_post_pre(void* out_x, void* residual, const void* x, void* p
     if (hidden % kHcChunk || n > kHcMax) return -1;
     cudaStream_t st = (cudaStream_t)stream;
     const int nchunks = hidden / kHcChunk;
-    mhc_post_partial_kernel<<<dim3(rows, nchunks), kHcChunk, 0, st>>>((float*)residual, (const float*)x, (const float*)post,
+    mhc_post_partial_kernel<<<dim3(rows, nchunks), 128, 0, st>>>((float*)residual, (const float*)x, (const float*)post,
                                                                     (const float*)comb, (const float*)fn, (float*)part, hidden, n, mode);
     mhc_finalize_kernel<<<rows, 512, (size_t)hidden * 4, st>>>((bf16*)out_x, (const float*)residual, (const float*)part,
                                                               (const float*)hc_scale, (const float*)hc_base, (const float*)norm_w,

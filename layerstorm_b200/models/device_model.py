@@ -228,7 +228,7 @@ class Workspace:
         self.sub = z(R, H)
         self.resid = z(R, n, H)
         self.post = z(R, n); self.comb = z(R, n, n)
-        self.part = z(R, max(1, H // 128), 25)
+        self.part = z(R, max(1, H // 32), 25)
         self.proj = z(R, m.max_proj)
         C = cfg.kda_heads * cfg.kda_head_dim
         self.kda_out = z(R, max(C, 1), dtype=b16)
@@ -559,13 +559,20 @@ class DeviceModel:
         sc = {"sigmoid": 0, "softmax": 1, "sqrtsoftplus": 2}[cfg.scoring]
         nat.call("lsb_router_topk", ws.logits_r, L["router_bias"], ws.ids, ws.wts, R, cfg.n_routed, cfg.top_k, cfg.n_group,
                  cfg.topk_group, sc, int(cfg.norm_topk_prob), cfg.routed_scale, cfg.n_shared, cfg.n_routed)
-        nat.call("lsb_moe_build_groups", ws.ids, R * S, E_total, ws.group_expert, ws.group_n, ws.group_pairs, ws.n_groups, ws.counts)
         efp = ctypes.addressof(arena.ef)
-        mg = min(ws.max_groups, min(R * S, (R * S + 3) // 4 + E_total))
-        nat.call("lsb_moe_gateup", ws.x, arena.data, arena.slot_of, efp, ws.group_expert, ws.group_n, ws.group_pairs, ws.n_groups,
-                 ws.act, S, mg, cfg.swiglu_limit, ws.miss)
-        nat.call("lsb_moe_down", ws.act, arena.data, arena.slot_of, efp, ws.group_expert, ws.group_n, ws.group_pairs, ws.n_groups,
-                 ws.y, mg)
+        fast_fp4 = arena.ef.fmt == 2 and cfg.moe_inter % 128 == 0 and cfg.hidden % 128 == 0
+        if fast_fp4 and R * S <= 72:
+            # small batch: every (row, slot) pair streams its expert on its own - no grouping pass
+            nat.call("lsb_moe_gateup", ws.x, arena.data, arena.slot_of, efp, ws.ids, None, None, None,
+                     ws.act, S, R * S, cfg.swiglu_limit, ws.miss)
+            nat.call("lsb_moe_down", ws.act, arena.data, arena.slot_of, efp, ws.ids, None, None, None, ws.y, R * S)
+        else:
+            nat.call("lsb_moe_build_groups", ws.ids, R * S, E_total, ws.group_expert, ws.group_n, ws.group_pairs, ws.n_groups, ws.counts)
+            mg = min(ws.max_groups, min(R * S, (R * S + 3) // 4 + E_total))
+            nat.call("lsb_moe_gateup", ws.x, arena.data, arena.slot_of, efp, ws.group_expert, ws.group_n, ws.group_pairs, ws.n_groups,
+                     ws.act, S, mg, cfg.swiglu_limit, ws.miss)
+            nat.call("lsb_moe_down", ws.act, arena.data, arena.slot_of, efp, ws.group_expert, ws.group_n, ws.group_pairs, ws.n_groups,
+                     ws.y, mg)
         nat.call("lsb_moe_combine", ws.sub, ws.y, ws.wts, ws.ids, arena.slot_of, R, S, cfg.hidden, 0)
 
     def _kda(self, i: int, L: dict, ws: Workspace, R: int, nseq: int):

@@ -89,7 +89,7 @@ def test_mhc_post_pre_and_contract():
     emb = rnd(R, H)
     resid = torch.zeros(R, n, H, device=DEV)
     post = torch.zeros(R, n, device=DEV); comb = torch.zeros(R, n, n, device=DEV)
-    part = torch.zeros(R, H // 128, 25, device=DEV)
+    part = torch.zeros(R, H // 32, 25, device=DEV)
     x = torch.zeros(R, H, device=DEV, dtype=torch.bfloat16)
     args = (cfg.hc_sinkhorn_iters, cfg.hc_eps, cfg.rms_eps, cfg.hc_post_mult)
     nat.call("lsb_mhc_post_pre", x, resid, emb, post, comb, fn, sc, base, nw, part, R, H, n, 0, *args)

@@ -172,6 +172,39 @@ __device__ __forceinline__ void nvfp4_row_dot2(const uint8_t* __restrict__ wa, c
     }
 }
 
+// Same, with the rows' scale bytes pre-staged in shared memory: `sca`/`scb` point at the row's
+// first scale pair; K-tile t (64 columns) is `tile_stride` bytes further (stride chosen odd in
+// words so a warp's reads are bank-conflict free).
+template <int MT>
+__device__ __forceinline__ void nvfp4_row_dot2_sm(const uint8_t* __restrict__ wa, const uint8_t* sca, const uint8_t* __restrict__ wb,
+                                                  const uint8_t* scb, int tile_stride, int K, const __half* xs, int nvalid,
+                                                  float* acca, float* accb) {
+    const int lane = threadIdx.x & 31, nchunks = K >> 5;
+#pragma unroll 2
+    for (int c = lane; c < nchunks; c += 32) {
+        const uint4 va = ldg_stream(wa + c * 16);
+        const uint4 vb = ldg_stream(wb + c * 16);
+        const int so = (c >> 1) * tile_stride + (c & 1) * 2;
+        const uint16_t sa = *reinterpret_cast<const uint16_t*>(sca + so);
+        const uint16_t sb = *reinterpret_cast<const uint16_t*>(scb + so);
+        nvfp4_chunk_dot<MT>(va, fp8e4m3_to_float((uint8_t)(sa & 0xff)), fp8e4m3_to_float((uint8_t)(sa >> 8)), xs, K, nchunks, c, nvalid, acca);
+        nvfp4_chunk_dot<MT>(vb, fp8e4m3_to_float((uint8_t)(sb & 0xff)), fp8e4m3_to_float((uint8_t)(sb >> 8)), xs, K, nchunks, c, nvalid, accb);
+    }
+}
+
+// Cooperative copy of the scale bytes of `rows_per_blk` consecutive n%32 values (all four 32-row
+// quads) of one 128-row tile: per K-tile a contiguous run of rows_per_blk*16 bytes.
+__device__ __forceinline__ void stage_scales(uint8_t* dst, const uint8_t* __restrict__ sf, int tile_n, int blk, int rows_per_blk, int gtiles,
+                                             int tile_stride) {
+    const int parts = rows_per_blk;          // 16-byte pieces per K-tile
+    for (int idx = threadIdx.x; idx < gtiles * parts; idx += blockDim.x) {
+        const int t = idx / parts, part = idx % parts;
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(sf + ((size_t)tile_n * gtiles + t) * 512 + (size_t)(blk * rows_per_blk + part) * 16));
+        uint32_t* d = reinterpret_cast<uint32_t*>(dst + (size_t)t * tile_stride + part * 16);
+        d[0] = v.x; d[1] = v.y; d[2] = v.z; d[3] = v.w;
+    }
+}
+
 // acc0[m] += sum_k w0[k]*x[m][k], acc1 likewise for w1.  x is bf16 [MT][ldx].
 // Partial sums stay per-lane; call warp_sum on them afterwards.
 template <class WF, int MT>

@@ -240,6 +240,15 @@ __global__ void __launch_bounds__(1024) indexer_topk_kernel(const float* __restr
         for (int i = t; i < ne * P; i += blockDim.x) out[i] = i;
         nsel_entries = ne;
     } else {
+        // Keys live in registers when the row has at most 8 entries per thread (context up to 8k
+        // pooled entries); longer rows re-read the scores from memory in every pass.
+        constexpr int KPT = 8;
+        const bool in_regs = ne <= 1024 * KPT;
+        uint32_t key[KPT];
+        if (in_regs) {
+#pragma unroll
+            for (int u = 0; u < KPT; ++u) { const int i = t + u * 1024; key[u] = i < ne ? sortable(sc[i]) : 0u; }
+        }
         // find the key of the budget-th largest element, 8 bits at a time
         if (t == 0) { s_prefix = 0; s_need = budget; }
         __syncthreads();
@@ -248,19 +257,37 @@ __global__ void __launch_bounds__(1024) indexer_topk_kernel(const float* __restr
             __syncthreads();
             const uint32_t prefix = s_prefix;
             const uint32_t mask = shift == 24 ? 0u : (0xffffffffu << (shift + 8));
-            for (int i = t; i < ne; i += blockDim.x) {
-                const uint32_t k = sortable(sc[i]);
-                if ((k & mask) == prefix) atomicAdd(&hist[(k >> shift) & 255], 1);
+            if (in_regs) {
+#pragma unroll
+                for (int u = 0; u < KPT; ++u)
+                    if (t + u * 1024 < ne && (key[u] & mask) == prefix) atomicAdd(&hist[(key[u] >> shift) & 255], 1);
+            } else {
+                for (int i = t; i < ne; i += blockDim.x) {
+                    const uint32_t k = sortable(sc[i]);
+                    if ((k & mask) == prefix) atomicAdd(&hist[(k >> shift) & 255], 1);
+                }
             }
             __syncthreads();
-            if (t == 0) {
-                int need = s_need, b = 255;
-                for (; b > 0; --b) {
-                    if (hist[b] >= need) break;
-                    need -= hist[b];
+            if (t < 32) {
+                // bucket search from the top by one warp: each lane sums 8 buckets, then a serial walk over 32 + 8 items
+                int part = 0;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) part += hist[255 - (t * 8 + j)];
+                int need = s_need, grp = 31;
+                for (int l = 0; l < 32; ++l) {
+                    const int pl = __shfl_sync(0xffffffffu, part, l);
+                    if (pl >= need) { grp = l; break; }
+                    need -= pl;
                 }
-                s_need = need;
-                s_prefix = prefix | ((uint32_t)b << shift);
+                if (t == 0) {
+                    int b = 255 - grp * 8;
+                    for (int j = 0; j < 8; ++j, --b) {
+                        if (hist[b] >= need || b == 0 || j == 7) break;
+                        need -= hist[b];
+                    }
+                    s_need = need;
+                    s_prefix = prefix | ((uint32_t)b << shift);
+                }
             }
             __syncthreads();
         }
@@ -269,10 +296,7 @@ __global__ void __launch_bounds__(1024) indexer_topk_kernel(const float* __restr
         if (t == 0) { s_base = 0; s_eqbase = 0; }
         __syncthreads();
         const int lane = t & 31, w = t >> 5;
-        for (int c0 = 0; c0 < ne; c0 += blockDim.x) {
-            const int i = c0 + t;
-            uint32_t k = 0;
-            if (i < ne) k = sortable(sc[i]);
+        auto emit_chunk = [&](int i, uint32_t k) {
             const int gt = (i < ne && k > T) ? 1 : 0, eq = (i < ne && k == T) ? 1 : 0;
             // block exclusive scan of eq
             int v = eq;
@@ -291,10 +315,10 @@ __global__ void __launch_bounds__(1024) indexer_topk_kernel(const float* __restr
             const int eq_total = s_scan[31];
             const int take = gt | (eq && eq_rank < quota);
             __syncthreads();
-            int u = take;
+            int uu = take;
 #pragma unroll
-            for (int o = 1; o < 32; o <<= 1) { const int n = __shfl_up_sync(0xffffffffu, u, o); if (lane >= o) u += n; }
-            if (lane == 31) s_scan[w] = u;
+            for (int o = 1; o < 32; o <<= 1) { const int n = __shfl_up_sync(0xffffffffu, uu, o); if (lane >= o) uu += n; }
+            if (lane == 31) s_scan[w] = uu;
             __syncthreads();
             if (w == 0) {
                 int x = s_scan[lane];
@@ -303,13 +327,20 @@ __global__ void __launch_bounds__(1024) indexer_topk_kernel(const float* __restr
                 s_scan[lane] = x;
             }
             __syncthreads();
-            const int posn = s_base + (w ? s_scan[w - 1] : 0) + u - take;
+            const int posn = s_base + (w ? s_scan[w - 1] : 0) + uu - take;
             if (take && posn < budget)
                 for (int j = 0; j < P; ++j) out[posn * P + j] = i * P + j;
             const int tot = s_scan[31];
             __syncthreads();
             if (t == 0) { s_base += tot; s_eqbase += eq_total; }
             __syncthreads();
+        };
+        if (in_regs) {
+#pragma unroll
+            for (int u = 0; u < KPT; ++u)
+                if (u * 1024 < ne) emit_chunk(u * 1024 + t, key[u]);
+        } else {
+            for (int c0 = 0; c0 < ne; c0 += blockDim.x) emit_chunk(c0 + t, (c0 + t < ne) ? sortable(sc[c0 + t]) : 0u);
         }
         nsel_entries = budget;
     }

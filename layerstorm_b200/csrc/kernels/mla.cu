@@ -308,22 +308,26 @@ __global__ void __launch_bounds__(128) mla_combine_kernel(bf16* __restrict__ out
         const float M = warp_max(m);
         const float e = (m > -INFINITY) ? __expf(m - M) : 0.f;
         w[t] = e;
-        // fixed-order sum over splits (lane 0), so the result does not depend on shuffle order
-        __syncwarp();
+        // fixed-order sum over splits (ascending lane by shuffle), independent of scheduling
+        float L = 0.f;
+        for (int s = 0; s < NS; ++s) L += __shfl_sync(0xffffffffu, e * l, s);
         if (t == 0) {
-            float L = 0.f;
-            for (int s = 0; s < NS; ++s) L += w[s] * ml[2 * s + 1];
             s_invL = L > 0.f ? 1.f / L : 0.f;
             s_lse = L > 0.f ? M + logf(L) : -INFINITY;
         }
-        (void)l;
     }
     __syncthreads();
     const float invL = s_invL;
     const float* op = o_part + ((size_t)r * H + h) * NS * dl;
     for (int d = t; d < dl; d += blockDim.x) {
         float a = 0.f;
-        for (int s = 0; s < NS; ++s) a = fmaf(w[s], op[(size_t)s * dl + d], a);
+        for (int s0 = 0; s0 < NS; s0 += 8) {
+            float v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = (s0 + u < NS) ? op[(size_t)(s0 + u) * dl + d] : 0.f;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) a = fmaf(w[(s0 + u) & 31], v[u], a);
+        }
         out[((size_t)r * H + h) * dl + d] = __float2bfloat16(a * invL);
     }
     if (lse && t == 0) lse[(size_t)r * H + h] = s_lse;

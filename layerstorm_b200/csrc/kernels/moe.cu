@@ -19,27 +19,24 @@ namespace lsb {
 
 enum { kScoreSigmoid = 0, kScoreSoftmax = 1, kScoreSqrtSoftplus = 2 };
 
-__global__ void router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int* __restrict__ ids,
-                                   float* __restrict__ wts, int E, int topk, int n_group, int topk_group, int scoring,
-                                   int norm_topk, float scale, int n_shared, int ld_logits) {
+// One warp per row: no block-wide barriers, the k selection rounds are shuffle reductions.
+__global__ void __launch_bounds__(32) router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int* __restrict__ ids,
+                                                         float* __restrict__ wts, int E, int topk, int n_group, int topk_group, int scoring,
+                                                         int norm_topk, float scale, int n_shared, int ld_logits) {
     extern __shared__ float sm[];
     float* score = sm;            // [E] unbiased
     float* sel = sm + E;          // [E] biased, -inf when masked/taken
-    __shared__ float red[33];
-    __shared__ int s_best;
-    __shared__ float s_gscore[64];
-    __shared__ int s_pick[64];
-    __shared__ float s_pickw[64];
-    const int r = blockIdx.x, t = threadIdx.x;
+    __shared__ int s_keep[64];
+    const int r = blockIdx.x, lane = threadIdx.x;
     const float* lg = logits + (size_t)r * ld_logits;
     pdl_wait();
     float mx = -INFINITY;
     if (scoring == kScoreSoftmax) {
-        for (int e = t; e < E; e += blockDim.x) mx = fmaxf(mx, lg[e]);
-        mx = block_max(mx, red);
+        for (int e = lane; e < E; e += 32) mx = fmaxf(mx, lg[e]);
+        mx = warp_max(mx);
     }
     float ssum = 0.f;
-    for (int e = t; e < E; e += blockDim.x) {
+    for (int e = lane; e < E; e += 32) {
         const float x = lg[e];
         float s;
         if (scoring == kScoreSigmoid) s = 1.f / (1.f + expf(-x));
@@ -49,44 +46,54 @@ __global__ void router_topk_kernel(const float* __restrict__ logits, const float
         ssum += s;
     }
     if (scoring == kScoreSoftmax) {
-        ssum = block_sum(ssum, red);
-        for (int e = t; e < E; e += blockDim.x) score[e] /= ssum;
+        ssum = warp_sum(ssum);
+        for (int e = lane; e < E; e += 32) score[e] /= ssum;
     }
-    __syncthreads();
-    for (int e = t; e < E; e += blockDim.x) sel[e] = score[e] + (bias ? bias[e] : 0.f);
-    __syncthreads();
+    __syncwarp();
+    for (int e = lane; e < E; e += 32) sel[e] = score[e] + (bias ? bias[e] : 0.f);
+    __syncwarp();
     if (n_group > 1) {
         const int gs = E / n_group;
-        if (t < n_group) {
-            float a = -INFINITY, b = -INFINITY;
-            for (int i = 0; i < gs; ++i) {
-                const float v = sel[t * gs + i];
-                if (v > a) { b = a; a = v; } else if (v > b) b = v;
+        // group score = sum of the two best biased scores; keep topk_group groups (ties -> lower group)
+        for (int g0 = 0; g0 < n_group; g0 += 32) {
+            const int g = g0 + lane;
+            if (g < n_group) {
+                float a = -INFINITY, b2 = -INFINITY;
+                for (int i = 0; i < gs; ++i) {
+                    const float v = sel[g * gs + i];
+                    if (v > a) { b2 = a; a = v; } else if (v > b2) b2 = v;
+                }
+                s_keep[g] = 0;
+                sm[2 * E + g] = a + b2;
             }
-            s_gscore[t] = a + b;
         }
-        __syncthreads();
-        if (t == 0) {
-            // keep topk_group groups: repeatedly take the best, ties to the lower group
-            bool keep[64];
-            for (int g = 0; g < n_group; ++g) keep[g] = false;
-            for (int k = 0; k < topk_group; ++k) {
-                int best = -1; float bv = -INFINITY;
-                for (int g = 0; g < n_group; ++g)
-                    if (!keep[g] && (best < 0 || s_gscore[g] > bv)) { best = g; bv = s_gscore[g]; }
-                keep[best] = true;
+        __syncwarp();
+        float* gscore = sm + 2 * E;
+        for (int k = 0; k < topk_group; ++k) {
+            float bv = -INFINITY; int bi = 0x7fffffff;
+            for (int g = lane; g < n_group; g += 32) {
+                if (s_keep[g]) continue;
+                const float v = gscore[g];
+                if (bi == 0x7fffffff || v > bv || (v == bv && g < bi)) { bv = v; bi = g; }
             }
-            for (int g = 0; g < n_group; ++g) s_pick[g] = keep[g] ? 1 : 0;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) { bv = ov; bi = oi; }
+            }
+            if (lane == 0 && bi != 0x7fffffff) s_keep[bi] = 1;
+            __syncwarp();
         }
-        __syncthreads();
-        for (int e = t; e < E; e += blockDim.x)
-            if (!s_pick[e / gs]) sel[e] = -INFINITY;
-        __syncthreads();
+        for (int e = lane; e < E; e += 32)
+            if (!s_keep[e / gs]) sel[e] = -INFINITY;
+        __syncwarp();
     }
+    float my_w = 0.f; int my_id = 0;     // lane k keeps the k-th pick
+    float tot = 0.f;
     for (int k = 0; k < topk; ++k) {
-        // block argmax, ties to the lower index
         float bv = -INFINITY; int bi = 0x7fffffff;
-        for (int e = t; e < E; e += blockDim.x) {
+        for (int e = lane; e < E; e += 32) {
             const float v = sel[e];
             if (v > bv || (v == bv && e < bi)) { bv = v; bi = e; }
         }
@@ -96,36 +103,21 @@ __global__ void router_topk_kernel(const float* __restrict__ logits, const float
             const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
             if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
         }
-        const int lane = t & 31, w = t >> 5, nw = (blockDim.x + 31) >> 5;
-        __shared__ float wv[32];
-        __shared__ int wi[32];
-        if (lane == 0) { wv[w] = bv; wi[w] = bi; }
-        __syncthreads();
-        if (t == 0) {
-            float v = wv[0]; int i = wi[0];
-            for (int j = 1; j < nw; ++j)
-                if (wv[j] > v || (wv[j] == v && wi[j] < i)) { v = wv[j]; i = wi[j]; }
-            if (i >= E) i = 0;   // all masked (cannot happen with finite logits)
-            s_best = i;
-            s_pick[k] = i;
-            s_pickw[k] = score[i];
-            sel[i] = -INFINITY;
-        }
-        __syncthreads();
-        (void)s_best;
+        if (bi >= E) bi = 0;               // everything masked (cannot happen with finite logits)
+        const float w = score[bi];
+        tot += w;
+        if (lane == (k & 31)) { my_w = w; my_id = bi; }
+        if (lane == 0) sel[bi] = -INFINITY;
+        __syncwarp();
     }
-    if (t == 0) {
-        float tot = 0.f;
-        for (int k = 0; k < topk; ++k) tot += s_pickw[k];
-        const int S = topk + n_shared;
-        for (int k = 0; k < topk; ++k) {
-            float w = s_pickw[k];
-            if (norm_topk) w = w / (tot + 1e-20f);
-            ids[r * S + k] = s_pick[k];
-            wts[r * S + k] = w * scale;
-        }
-        for (int k = 0; k < n_shared; ++k) { ids[r * S + topk + k] = E + k; wts[r * S + topk + k] = 1.f; }
+    const int S = topk + n_shared;
+    if (lane < topk) {
+        float w = my_w;
+        if (norm_topk) w = w / (tot + 1e-20f);
+        ids[r * S + lane] = my_id;
+        wts[r * S + lane] = w * scale;
     }
+    if (lane < n_shared) { ids[r * S + topk + lane] = E + lane; wts[r * S + topk + lane] = 1.f; }
     pdl_launch_dependents();
 }
 
@@ -345,13 +337,19 @@ __global__ void __launch_bounds__(256) moe_gateup_fp4_kernel(const bf16* __restr
 #pragma unroll
     for (int i = 0; i < MT; ++i) pr[i] = group_pairs ? group_pairs[g * 4 + min(i, n - 1)] : g;
     if (threadIdx.x < MT) rows[threadIdx.x] = x + (size_t)(pr[threadIdx.x] / S) * ef.H;
+    const uint8_t* base = arena + (size_t)slot * ef.stride;
+    const int tile = blockIdx.x >> 3, blk = blockIdx.x & 7;
+    const int gtiles = ef.H >> 6;
+    constexpr int kTS = 68;                                // 64 scale bytes per K-tile + 4 pad
+    uint8_t* scg = smraw + (size_t)MT * ef.H * 2;
+    uint8_t* scu = scg + (size_t)gtiles * kTS;
+    stage_scales(scg, base + ef.off_sg, tile, blk, 4, gtiles, kTS);
+    stage_scales(scu, base + ef.off_su, tile, blk, 4, gtiles, kTS);
     __syncthreads();
     stage_x_half(xs, rows, n, ef.H);
     __syncthreads();
-    const uint8_t* base = arena + (size_t)slot * ef.stride;
     const float* tail = reinterpret_cast<const float*>(base + ef.off_tail);
     const float sg = tail[0], su = tail[1];
-    const int tile = blockIdx.x >> 3, blk = blockIdx.x & 7;
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         const int j = warp * 2 + r;                       // 0..15
@@ -359,8 +357,9 @@ __global__ void __launch_bounds__(256) moe_gateup_fp4_kernel(const bf16* __restr
         float ag[MT], au[MT];
 #pragma unroll
         for (int m = 0; m < MT; ++m) ag[m] = au[m] = 0.f;
-        nvfp4_row_dot2<MT>(base + ef.off_gate + (size_t)f * (ef.H >> 1), base + ef.off_sg, f,
-                           base + ef.off_up + (size_t)f * (ef.H >> 1), base + ef.off_su, f, ef.H, xs, n, ag, au);
+        const int so = (j & 3) * 16 + (j >> 2) * 4;
+        nvfp4_row_dot2_sm<MT>(base + ef.off_gate + (size_t)f * (ef.H >> 1), scg + so,
+                              base + ef.off_up + (size_t)f * (ef.H >> 1), scu + so, kTS, ef.H, xs, n, ag, au);
 #pragma unroll
         for (int m = 0; m < MT; ++m) {
             if (m < n) {
@@ -394,12 +393,16 @@ __global__ void __launch_bounds__(256) moe_down_fp4_kernel(const bf16* __restric
 #pragma unroll
     for (int i = 0; i < MT; ++i) pr[i] = group_pairs ? group_pairs[g * 4 + min(i, n - 1)] : g;
     if (threadIdx.x < MT) rows[threadIdx.x] = act + (size_t)pr[threadIdx.x] * ef.F;
+    const uint8_t* base = arena + (size_t)slot * ef.stride;
+    const int tile = blockIdx.x >> 2, blk = blockIdx.x & 3;
+    const int gtiles = ef.F >> 6;
+    constexpr int kTS = 132;                               // 128 scale bytes per K-tile + 4 pad
+    uint8_t* scd = smraw + (size_t)MT * ef.F * 2;
+    stage_scales(scd, base + ef.off_sd, tile, blk, 8, gtiles, kTS);
     __syncthreads();
     stage_x_half(xs, rows, n, ef.F);
     __syncthreads();
-    const uint8_t* base = arena + (size_t)slot * ef.stride;
     const float sd = reinterpret_cast<const float*>(base + ef.off_tail)[2];
-    const int tile = blockIdx.x >> 2, blk = blockIdx.x & 3;
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         const int j0 = warp * 4 + r * 2;                  // 0..31, two rows per pass
@@ -408,8 +411,9 @@ __global__ void __launch_bounds__(256) moe_down_fp4_kernel(const bf16* __restric
         float a0[MT], a1[MT];
 #pragma unroll
         for (int m = 0; m < MT; ++m) a0[m] = a1[m] = 0.f;
-        nvfp4_row_dot2<MT>(base + ef.off_down + (size_t)h0 * (ef.F >> 1), base + ef.off_sd, h0,
-                           base + ef.off_down + (size_t)h1 * (ef.F >> 1), base + ef.off_sd, h1, ef.F, xs, n, a0, a1);
+        const int so = (j0 & 7) * 16 + (j0 >> 3) * 4;
+        nvfp4_row_dot2_sm<MT>(base + ef.off_down + (size_t)h0 * (ef.F >> 1), scd + so,
+                              base + ef.off_down + (size_t)h1 * (ef.F >> 1), scd + so + 16, kTS, ef.F, xs, n, a0, a1);
 #pragma unroll
         for (int m = 0; m < MT; ++m) {
             if (m < n) {
@@ -425,17 +429,26 @@ __global__ void __launch_bounds__(256) moe_down_fp4_kernel(const bf16* __restric
 // (slot < 0) contribute nothing.  mode 0: write fp32; mode 1: add into out.
 __global__ void moe_combine_kernel(float* __restrict__ out, const float* __restrict__ y, const float* __restrict__ wts,
                                    const int* __restrict__ ids, const int* __restrict__ slot_of, int S, int H, int accumulate) {
+    constexpr int kMaxS = 16;
     pdl_wait();
     const int r = blockIdx.y;
     const int h = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
     if (h >= H) return;
+    // routing metadata first (independent loads), then all slot rows in flight together
+    int e[kMaxS];
+    float w[kMaxS];
+#pragma unroll
+    for (int s = 0; s < kMaxS; ++s) { e[s] = s < S ? ids[r * S + s] : -1; w[s] = s < S ? wts[r * S + s] : 0.f; }
+#pragma unroll
+    for (int s = 0; s < kMaxS; ++s) if (e[s] >= 0 && slot_of[e[s]] < 0) e[s] = -1;
+    float4 v[kMaxS];
+#pragma unroll
+    for (int s = 0; s < kMaxS; ++s)
+        v[s] = e[s] >= 0 ? *reinterpret_cast<const float4*>(y + ((size_t)r * S + s) * H + h) : make_float4(0, 0, 0, 0);
     float4 a = make_float4(0, 0, 0, 0);
-    for (int s = 0; s < S; ++s) {
-        const int e = ids[r * S + s];
-        if (e < 0 || slot_of[e] < 0) continue;
-        const float w = wts[r * S + s];
-        const float4 v = *reinterpret_cast<const float4*>(y + ((size_t)r * S + s) * H + h);
-        a.x = fmaf(w, v.x, a.x); a.y = fmaf(w, v.y, a.y); a.z = fmaf(w, v.z, a.z); a.w = fmaf(w, v.w, a.w);
+#pragma unroll
+    for (int s = 0; s < kMaxS; ++s) {
+        if (e[s] >= 0) { a.x = fmaf(w[s], v[s].x, a.x); a.y = fmaf(w[s], v[s].y, a.y); a.z = fmaf(w[s], v[s].z, a.z); a.w = fmaf(w[s], v[s].w, a.w); }
     }
     float4* o = reinterpret_cast<float4*>(out + (size_t)r * H + h);
     if (accumulate) { float4 p = *o; a.x += p.x; a.y += p.y; a.z += p.z; a.w += p.w; }
@@ -460,8 +473,8 @@ using namespace lsb;
 LSB_API int lsb_router_topk(const void* logits, const void* bias, void* ids, void* wts, int rows, int E, int topk,
                             int n_group, int topk_group, int scoring, int norm_topk, float scale, int n_shared,
                             int ld_logits, void* stream) {
-    if (topk > 64 || n_group > 64 || E > 4096) return -1;
-    router_topk_kernel<<<rows, 256, (size_t)E * 8, (cudaStream_t)stream>>>((const float*)logits, (const float*)bias, (int*)ids,
+    if (topk > 32 || n_group > 64 || E > 4096 || n_shared > 32) return -1;
+    router_topk_kernel<<<rows, 32, (size_t)(2 * E + 64) * 4, (cudaStream_t)stream>>>((const float*)logits, (const float*)bias, (int*)ids,
                                                                          (float*)wts, E, topk, n_group, topk_group, scoring,
                                                                          norm_topk, scale, n_shared, ld_logits);
     LSB_CHECK_LAUNCH();
@@ -481,7 +494,7 @@ LSB_API int lsb_moe_gateup(const void* x, const void* arena, const void* slot_of
                            void* act, int S, int max_groups, float limit, void* miss_flag, void* stream) {
     ExpertFmt ef = *reinterpret_cast<const ExpertFmt*>(fmt_struct);
     cudaStream_t st = (cudaStream_t)stream;
-    if (ef.fmt == 2 && ef.F % 128 == 0 && ef.H % 128 == 0) {
+    if (ef.fmt == 2 && ef.F % 128 == 0 && ef.H % 128 == 0) {   // K % 64 == 0 follows
         dim3 g2(ef.F / 16, max_groups);
         static bool attr = false;
         if (!attr) {
@@ -490,10 +503,10 @@ LSB_API int lsb_moe_gateup(const void* x, const void* arena, const void* slot_of
             attr = true;
         }
         if (!group_n)
-            moe_gateup_fp4_kernel<1><<<g2, 256, (size_t)ef.H * 2, st>>>((const bf16*)x, (const uint8_t*)arena, (const int*)slot_of, ef, (const int*)group_expert,
+            moe_gateup_fp4_kernel<1><<<g2, 256, (size_t)ef.H * 2 + 2 * (ef.H / 64) * 68, st>>>((const bf16*)x, (const uint8_t*)arena, (const int*)slot_of, ef, (const int*)group_expert,
                                                                         nullptr, nullptr, nullptr, (bf16*)act, S, limit, (int*)miss_flag);
         else
-            moe_gateup_fp4_kernel<4><<<g2, 256, (size_t)ef.H * 8, st>>>((const bf16*)x, (const uint8_t*)arena, (const int*)slot_of, ef, (const int*)group_expert,
+            moe_gateup_fp4_kernel<4><<<g2, 256, (size_t)ef.H * 8 + 2 * (ef.H / 64) * 68, st>>>((const bf16*)x, (const uint8_t*)arena, (const int*)slot_of, ef, (const int*)group_expert,
                                                                         (const int*)group_n, (const int*)group_pairs, (const int*)n_groups, (bf16*)act, S, limit,
                                                                         (int*)miss_flag);
         LSB_CHECK_LAUNCH();
@@ -524,10 +537,10 @@ LSB_API int lsb_moe_down(const void* act, const void* arena, const void* slot_of
             attr = true;
         }
         if (!group_n)
-            moe_down_fp4_kernel<1><<<g2, 256, (size_t)ef.F * 2, st>>>((const bf16*)act, (const uint8_t*)arena, (const int*)slot_of, ef, (const int*)group_expert,
+            moe_down_fp4_kernel<1><<<g2, 256, (size_t)ef.F * 2 + (ef.F / 64) * 132, st>>>((const bf16*)act, (const uint8_t*)arena, (const int*)slot_of, ef, (const int*)group_expert,
                                                                       nullptr, nullptr, nullptr, (float*)y);
         else
-            moe_down_fp4_kernel<4><<<g2, 256, (size_t)ef.F * 8, st>>>((const bf16*)act, (const uint8_t*)arena, (const int*)slot_of, ef, (const int*)group_expert,
+            moe_down_fp4_kernel<4><<<g2, 256, (size_t)ef.F * 8 + (ef.F / 64) * 132, st>>>((const bf16*)act, (const uint8_t*)arena, (const int*)slot_of, ef, (const int*)group_expert,
                                                                       (const int*)group_n, (const int*)group_pairs, (const int*)n_groups, (float*)y);
         LSB_CHECK_LAUNCH();
     }
@@ -545,9 +558,9 @@ LSB_API int lsb_moe_down(const void* act, const void* arena, const void* slot_of
 
 LSB_API int lsb_moe_combine(void* out, const void* y, const void* wts, const void* ids, const void* slot_of, int rows,
                             int S, int H, int accumulate, void* stream) {
-    if (H % 4) return -1;
-    dim3 grid((H / 4 + 255) / 256, rows);
-    moe_combine_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((float*)out, (const float*)y, (const float*)wts, (const int*)ids,
+    if (H % 4 || S > 16) return -1;
+    dim3 grid((H / 4 + 127) / 128, rows);
+    moe_combine_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>((float*)out, (const float*)y, (const float*)wts, (const int*)ids,
                                                              (const int*)slot_of, S, H, accumulate);
     LSB_CHECK_LAUNCH();
 }

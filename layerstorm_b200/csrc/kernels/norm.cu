@@ -133,8 +133,19 @@ __global__ void __launch_bounds__(512) mhc_finalize_kernel(bf16* __restrict__ ou
     {
         const int o = t >> 4, sub = t & 15;
         float a = 0.f;
-        if (o <= kHcOut)
-            for (int c = sub; c < nchunks; c += 16) a += part[((size_t)r * nchunks + c) * (kHcOut + 1) + o];
+        if (o <= kHcOut) {
+            // batches of 8 independent loads: the adds must not serialise the memory latency
+            for (int c0 = sub; c0 < nchunks; c0 += 128) {
+                float v[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int c = c0 + u * 16;
+                    v[u] = c < nchunks ? part[((size_t)r * nchunks + c) * (kHcOut + 1) + o] : 0.f;
+                }
+#pragma unroll
+                for (int u = 0; u < 8; ++u) a += v[u];
+            }
+        }
 #pragma unroll
         for (int d = 8; d > 0; d >>= 1) a += __shfl_xor_sync(0xffffffffu, a, d, 16);
         if (sub == 0 && o <= kHcOut) mix[o] = a;
@@ -176,11 +187,28 @@ __global__ void __launch_bounds__(512) mhc_finalize_kernel(bf16* __restrict__ ou
     __syncthreads();
     const float* rp = residual + (size_t)r * n * hidden;
     float ss = 0.f;
-    for (int h = t; h < hidden; h += blockDim.x) {
-        float a = 0.f;
-        for (int j = 0; j < n; ++j) a += pre[j] * rp[(size_t)j * hidden + h];
-        row[h] = a;
-        ss += a * a;
+    float pj[kHcMax];
+#pragma unroll
+    for (int j = 0; j < kHcMax; ++j) pj[j] = j < n ? pre[j] : 0.f;
+    for (int h0 = t; h0 < hidden; h0 += blockDim.x * 4) {
+        float v[4][kHcMax];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int h = h0 + u * blockDim.x;
+#pragma unroll
+            for (int j = 0; j < kHcMax; ++j) v[u][j] = (h < hidden && j < n) ? rp[(size_t)j * hidden + h] : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int h = h0 + u * blockDim.x;
+            if (h < hidden) {
+                float a = 0.f;
+#pragma unroll
+                for (int j = 0; j < kHcMax; ++j) a += pj[j] * v[u][j];
+                row[h] = a;
+                ss += a * a;
+            }
+        }
     }
     ss = block_sum(ss, red);
     const float inv = rsqrtf(ss / (float)hidden + rms_eps);

@@ -22,10 +22,8 @@ import torch
 from ..models.config import ModelConfig
 from ..models.device_model import DeviceModel, Workspace
 from ..ops import _native as nat
-
-
-class KvPoolExhausted(RuntimeError):
-    """No free KV pages (the reference's kKvPoolExhausted completion error)."""
+from . import native as rt
+from .native import KvPoolExhausted  # noqa: F401  (re-exported: no free KV pages, the reference's kKvPoolExhausted)
 
 
 @dataclass
@@ -56,7 +54,7 @@ class Engine:
         self.num_pages = num_pages if num_pages is not None else self.max_pages * max_seqs
         self.max_seqs, self.max_batch, self.prefill_chunk = max_seqs, max_batch, prefill_chunk
         model.alloc_cache(self.num_pages, max_seqs, self.max_pages)
-        self.free_pages = list(range(self.num_pages - 1, -1, -1))
+        self.pa = rt.PageAllocator([self.num_pages], self.page)
         self.free_slots = list(range(max_seqs - 1, -1, -1))
         self.seqs: Dict[int, SequenceState] = {}
         self.use_graph = use_graph and self.dev.type == "cuda"
@@ -78,14 +76,53 @@ class Engine:
             raise RuntimeError("no free sequence slot")
         slot = self.free_slots.pop()
         self.seqs[slot] = SequenceState(slot)
+        self.pa.create(slot)
         with torch.cuda.stream(self.stream):
             self.model.reset_slot(slot)
         return slot
 
     def free_sequence(self, sid: int):
         s = self.seqs.pop(sid)
-        self.free_pages.extend(reversed(s.pages))
+        self.pa.destroy(s.slot)
         self.free_slots.append(s.slot)
+
+    def free_page_count(self) -> int:
+        return self.pa.free_pages(0)
+
+    def fork_sequence(self, parent: int, prefix_len: Optional[int] = None) -> int:
+        """Truncating fork: the child shares the parent's KV pages covering ``prefix_len`` tokens
+        (reference counted, copy-on-write on the frontier page).  Recurrent (KDA) state cannot be
+        rolled back, so models with KDA layers only fork at the parent's full length."""
+        ps = self.seqs[parent]
+        prefix_len = ps.length if prefix_len is None else prefix_len
+        has_kda = any(self.cfg.is_kda_layer(i) for i in range(self.cfg.n_layers))
+        if has_kda and prefix_len != ps.length:
+            raise RuntimeError("a sequence with recurrent state can only be forked at its frontier")
+        if self.cfg.index_kpool > 1 and prefix_len % self.cfg.index_kpool and prefix_len != ps.length:
+            raise RuntimeError("fork point must be a multiple of the indexer pool size")
+        if not self.free_slots:
+            raise RuntimeError("no free sequence slot")
+        slot = self.free_slots.pop()
+        self.pa.fork(ps.slot, slot, prefix_len)
+        cs = SequenceState(slot, length=prefix_len, pages=self.pa.pages(slot), tokens=list(ps.tokens[:prefix_len]))
+        self.seqs[slot] = cs
+        with torch.cuda.stream(self.stream):
+            m = self.model
+            for t in list(m.kda_state.values()) + list(m.kda_conv.values()) + list(m.idx_tail.values()):
+                t[slot].copy_(t[ps.slot])
+            self._sync_block_table(cs)
+        return slot
+
+    def _copy_page(self, src: int, dst: int):
+        m = self.model
+        for t in list(m.kv_cache.values()) + list(m.idx_cache.values()):
+            t[dst].copy_(t[src])
+
+    def _sync_block_table(self, s: SequenceState):
+        for j, pg in enumerate(s.pages):
+            self.h_bt[s.slot, j] = pg
+        self.model.block_table[s.slot].copy_(self.h_bt[s.slot], non_blocking=True)
+        self.h2d_bytes += self.max_pages * 4
 
     def rewind(self, sid: int, length: int):
         """Roll the committed frontier back (speculative-verify rejection).  Only valid for models
@@ -95,22 +132,19 @@ class Engine:
             raise RuntimeError("rewind of a recurrent-state sequence is refused")
         s.length = length
         del s.tokens[length:]
+        self.pa.rewind(s.slot, length)
+        s.pages = self.pa.pages(s.slot)
 
     def _ensure_pages(self, s: SequenceState, new_len: int):
-        need = (new_len + self.page - 1) // self.page
-        if need > self.max_pages:
+        if (new_len + self.page - 1) // self.page > self.max_pages:
             raise RuntimeError(f"sequence length {new_len} exceeds max context {self.max_ctx}")
-        changed = False
-        while len(s.pages) < need:
-            if not self.free_pages:
-                raise KvPoolExhausted(f"KV pool exhausted ({self.num_pages} pages)")
-            pg = self.free_pages.pop()
-            self.h_bt[s.slot, len(s.pages)] = pg
-            s.pages.append(pg)
-            changed = True
-        if changed:
-            self.model.block_table[s.slot].copy_(self.h_bt[s.slot], non_blocking=True)
-            self.h2d_bytes += self.max_pages * 4
+        cow = self.pa.cow_frontier(s.slot)          # shared frontier page must become private first
+        if cow is not None:
+            self._copy_page(*cow)
+        new = self.pa.extend(s.slot, new_len)
+        if new or cow is not None:
+            s.pages = self.pa.pages(s.slot)
+            self._sync_block_table(s)
 
     # ------------------------------------------------------------------ staging
     def _stage(self, ws: Workspace, rows: List[tuple], seq_groups: List[tuple]):

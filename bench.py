@@ -120,9 +120,15 @@ def main():
     t0 = time.time()
     # as many routed-expert slots per layer as fit in HBM next to the other weights; any remainder
     # would be streamed from pinned host RAM by the expert cache
-    model = DeviceModel.random_init(cfg, dev, kv_fmt="fp8", page=64, seed=1234 + rank, expert_slots="auto", embed_on_host=True,
-                                    reserve_bytes=int(args.headroom_gib * 2 ** 30))
+    model = DeviceModel.random_init(cfg, dev, kv_fmt="fp8", page=64, seed=1234, expert_slots="auto", embed_on_host=True,
+                                    reserve_bytes=int(args.headroom_gib * 2 ** 30), tp_rank=rank, tp_size=world)
     slots = getattr(model, "expert_slots", cfg.n_routed)
+    if world > 1:
+        # in-kernel NVLink all-reduce buffers (peer-mapped); NCCL only bootstraps and serves prefill chunks
+        from layerstorm_b200.parallel.symm import PeerComm
+        comm = PeerComm(4 * cfg.hidden, dev)
+        comm_amax = PeerComm(2 * max(args.batch, 4), dev)
+        model.attach_comm(comm, comm_amax)
     max_ctx = args.ctx + args.steps + args.warmup + 64
     eng = Engine(model, max_seqs=args.batch, max_ctx=max_ctx, prefill_chunk=args.prefill_chunk, max_batch=args.batch, use_graph=not args.no_graph)
     torch.cuda.synchronize()
@@ -216,7 +222,9 @@ def main():
                        "parallelism": f"tp{world}ep{world}" if world > 1 else "single-gpu",
                        "weights": f"experts {cfg.expert_quant}, attention {cfg.dense_quant}", "kv_cache": "fp8+bf16-rope, 64-token pages",
                        "l2": "inputs larger than L2 (each step streams ~20 GB of weights)",
-                       "resident_expert_slots_per_layer": slots, "routed_experts": cfg.n_routed, "expert_miss_flag": miss,
+                       "resident_expert_slots_per_layer_per_gpu": slots, "routed_experts": cfg.n_routed, "expert_miss_flag": miss,
+                       "collectives": ("fused in-kernel NVLink all-reduce (P2P stores + flags), argmax exchange; NCCL for prefill chunks only"
+                                       if world > 1 else "none"),
                        "context_fill": "synthetic (uninitialised cache)" if args.synthetic_fill else "real chunked prefill"},
             "clocks": clocks,
             "e2e": {"value": round(e2e, 3), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},

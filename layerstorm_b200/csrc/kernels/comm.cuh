@@ -1,0 +1,99 @@
+// In-kernel NVLink collectives over peer-mapped symmetric buffers (no NCCL on these paths).
+//
+// All-reduce of a [rows, hidden] fp32 partial, split between the kernel that PRODUCES the
+// partial and the kernel that CONSUMES the sum:
+//   producer epilogue  every block stores its part of the partial into slot[my_rank] of the
+//                      receive buffer of EVERY rank (plain st.global to peer memory); the last block to
+//                      finish publishes the new epoch to every rank's flag word (st.release.sys).
+//   consumer prologue  waits (bounded) until all ranks' flags carry the epoch, then sums the
+//                      slots in rank order - identical bits on every rank.
+// Receive buffers are double-buffered by epoch parity; a rank can never run two reductions
+// ahead of a peer, because producing epoch e+2 requires having consumed e+1, which requires
+// every rank to have produced e+1 and therefore consumed e.
+//
+// This is the B200 replacement for the reference's per-layer NCCL all-reduces after o_proj and
+// after the expert / dense FFN down projection (src/daemon/attention/arch_mla.cpp:2055,
+// src/daemon/moe/moe_ranks.cpp:682-832; call sites C4-C6 of src/parallelism/dcp_communicator.cpp).
+#pragma once
+#include "common.cuh"
+
+namespace lsb {
+
+constexpr int kMaxRanks = 8;
+
+struct PeerComm {
+    int nranks, rank;
+    long long cap;                   // floats per (parity, source-rank) slot
+    float* recv[kMaxRanks];          // recv[p] = rank p's receive buffer [2][nranks][cap]
+    unsigned* flags[kMaxRanks];      // flags[p] = rank p's flag words [2][nranks]
+    unsigned* epoch;                 // local: reductions completed so far
+    unsigned* cta_done;              // local: blocks of the current producer that have finished
+    int* err;                        // local error word (0 = ok)
+};
+
+__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ unsigned long long comm_now_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Producer side, step 1 (any thread): store one partial value into every rank's slot.
+__device__ __forceinline__ void comm_push(const PeerComm& c, unsigned next_epoch, size_t idx, float v) {
+    const size_t off = ((size_t)(next_epoch & 1u) * c.nranks + c.rank) * (size_t)c.cap + idx;
+#pragma unroll
+    for (int p = 0; p < kMaxRanks; ++p)
+        if (p < c.nranks) c.recv[p][off] = v;
+}
+
+// Producer side, step 2 (whole block, after its pushes): the last block publishes the epoch.
+__device__ __forceinline__ void comm_signal(const PeerComm& c, unsigned next_epoch, unsigned total_blocks) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        const unsigned prev = atomicAdd(c.cta_done, 1u);
+        if (prev == total_blocks - 1) {
+            *c.cta_done = 0;
+            __threadfence_system();
+            for (int p = 0; p < c.nranks; ++p) st_release_sys(c.flags[p] + (next_epoch & 1u) * c.nranks + c.rank, next_epoch);
+            *c.epoch = next_epoch;
+        }
+    }
+}
+
+// Consumer side (whole block): wait for every rank's contribution to `epoch`.  Gives up after
+// ~2 s, records error 100 + missing rank and lets the kernel finish on whatever is there.
+__device__ __forceinline__ void comm_wait(const PeerComm& c, unsigned epoch) {
+    if (threadIdx.x < (unsigned)c.nranks) {
+        const unsigned* f = c.flags[c.rank] + (epoch & 1u) * c.nranks + threadIdx.x;
+        if ((int)(ld_acquire_sys(f) - epoch) < 0) {
+            const unsigned long long t0 = comm_now_ns();
+            unsigned it = 0;
+            while ((int)(ld_acquire_sys(f) - epoch) < 0) {
+                if ((++it & 1023u) == 0 && comm_now_ns() - t0 > 2000000000ull) { atomicCAS(c.err, 0, 100 + (int)threadIdx.x); break; }
+            }
+        }
+    }
+    __syncthreads();
+}
+
+// Sum of the ranks' slots for element idx, in rank order.
+__device__ __forceinline__ float comm_reduce(const PeerComm& c, unsigned epoch, size_t idx) {
+    const float* base = c.recv[c.rank] + (size_t)(epoch & 1u) * c.nranks * (size_t)c.cap + idx;
+    float v[kMaxRanks];
+#pragma unroll
+    for (int p = 0; p < kMaxRanks; ++p) v[p] = p < c.nranks ? __ldcg(base + (size_t)p * c.cap) : 0.f;   // L2 read: peers wrote these lines
+    float a = 0.f;
+#pragma unroll
+    for (int p = 0; p < kMaxRanks; ++p) a += v[p];
+    return a;
+}
+
+}  // namespace lsb

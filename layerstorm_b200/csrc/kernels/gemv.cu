@@ -4,6 +4,7 @@
 // Replaces the reference's CUDA-core GEMV family (src/compute/kernels/sm120/gemm/bf16_gemm.cu:41-156,
 // wq_gemm.cu:84-158) with one templated kernel over four weight formats.
 #include "gemv_core.cuh"
+#include "comm.cuh"
 
 namespace lsb {
 
@@ -30,10 +31,14 @@ struct MatNvfp4 {
 
 template <class Mat, int MT, bool OUT_BF16>
 __global__ void __launch_bounds__(256) gemv_kernel(Mat mat, const bf16* __restrict__ x, int ldx, void* __restrict__ out,
-                                                   int ldo, int N, int K, float alpha, const float* __restrict__ bias) {
+                                                   int ldo, int N, int K, float alpha, const float* __restrict__ bias, PeerComm comm) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = (blockIdx.x * 8 + warp) * 2;
-    if (n0 >= N) return;
+    int n0 = (blockIdx.x * 8 + warp) * 2;
+    const bool active = n0 < N;
+    if (!active) {
+        if (comm.nranks == 0) return;
+        n0 = 0;                       // keep the warp alive for the block-wide signal below
+    }
     const int n1 = min(n0 + 1, N - 1);
     float acc0[MT], acc1[MT];
 #pragma unroll
@@ -41,13 +46,18 @@ __global__ void __launch_bounds__(256) gemv_kernel(Mat mat, const bf16* __restri
     auto r0 = mat.row(n0);
     auto r1 = mat.row(n1);
     pdl_wait();
-    warp_dot2<decltype(r0), MT>(r0, r1, x, ldx, K, acc0, acc1);
+    unsigned next_epoch = 0;
+    if (comm.nranks) next_epoch = *comm.epoch + 1;
+    if (active) warp_dot2<decltype(r0), MT>(r0, r1, x, ldx, K, acc0, acc1);
 #pragma unroll
     for (int m = 0; m < MT; ++m) {
         float a = warp_sum(acc0[m]) * alpha, b = warp_sum(acc1[m]) * alpha;
-        if (lane == 0) {
+        if (lane == 0 && active) {
             if (bias) { a += bias[n0]; b += bias[n1]; }
-            if (OUT_BF16) {
+            if (comm.nranks) {
+                comm_push(comm, next_epoch, (size_t)m * ldo + n0, a);
+                if (n0 + 1 < N) comm_push(comm, next_epoch, (size_t)m * ldo + n0 + 1, b);
+            } else if (OUT_BF16) {
                 bf16* o = reinterpret_cast<bf16*>(out) + (size_t)m * ldo;
                 o[n0] = __float2bfloat16(a);
                 if (n0 + 1 < N) o[n0 + 1] = __float2bfloat16(b);
@@ -58,6 +68,7 @@ __global__ void __launch_bounds__(256) gemv_kernel(Mat mat, const bf16* __restri
             }
         }
     }
+    if (comm.nranks) comm_signal(comm, next_epoch, gridDim.x);
     pdl_launch_dependents();
 }
 
@@ -66,7 +77,7 @@ __global__ void __launch_bounds__(256) gemv_kernel(Mat mat, const bf16* __restri
 // hundred rows (router, low-rank projections).
 template <class Mat, int MT, bool OUT_BF16>
 __global__ void __launch_bounds__(256) gemv_smalln_kernel(Mat mat, const bf16* __restrict__ x, int ldx, void* __restrict__ out,
-                                                          int ldo, int N, int K, float alpha, const float* __restrict__ bias) {
+                                                          int ldo, int N, int K, float alpha, const float* __restrict__ bias, PeerComm comm) {
     __shared__ float red[8][2 * MT];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n0 = blockIdx.x * 2;
@@ -77,6 +88,8 @@ __global__ void __launch_bounds__(256) gemv_smalln_kernel(Mat mat, const bf16* _
     auto r0 = mat.row(n0);
     auto r1 = mat.row(n1);
     pdl_wait();
+    unsigned next_epoch = 0;
+    if (comm.nranks) next_epoch = *comm.epoch + 1;
     warp_dot2<decltype(r0), MT>(r0, r1, x, ldx, K, acc0, acc1, threadIdx.x, 256);
 #pragma unroll
     for (int m = 0; m < MT; ++m) {
@@ -92,16 +105,24 @@ __global__ void __launch_bounds__(256) gemv_smalln_kernel(Mat mat, const bf16* _
         const int m = threadIdx.x >> 1, n = n0 + (threadIdx.x & 1);
         if (n < N) {
             if (bias) a += bias[n];
-            if (OUT_BF16) reinterpret_cast<bf16*>(out)[(size_t)m * ldo + n] = __float2bfloat16(a);
+            if (comm.nranks) comm_push(comm, next_epoch, (size_t)m * ldo + n, a);
+            else if (OUT_BF16) reinterpret_cast<bf16*>(out)[(size_t)m * ldo + n] = __float2bfloat16(a);
             else reinterpret_cast<float*>(out)[(size_t)m * ldo + n] = a;
         }
     }
+    if (comm.nranks) comm_signal(comm, next_epoch, gridDim.x);
     pdl_launch_dependents();
 }
 
 template <class Mat>
 static int launch_gemv(Mat mat, const bf16* x, int ldx, void* out, int ldo, int M, int N, int K, float alpha,
-                       const float* bias, int out_bf16, cudaStream_t st) {
+                       const float* bias, int out_bf16, cudaStream_t st, const void* comm_host = nullptr) {
+    PeerComm comm;
+    comm.nranks = 0;
+    if (comm_host) {
+        comm = *reinterpret_cast<const PeerComm*>(comm_host);
+        if ((M != 1 && M != 2 && M != 4) || out_bf16) return -1;   // the fused epilogue covers one single-pass launch of fp32 rows
+    }
     const int grid = (N + 15) / 16;
     const size_t osz = out_bf16 ? 2 : 4;
     for (int m0 = 0; m0 < M;) {
@@ -111,10 +132,10 @@ static int launch_gemv(Mat mat, const bf16* x, int ldx, void* out, int ldo, int 
         void* op = reinterpret_cast<char*>(out) + (size_t)m0 * ldo * osz;
 #define LSB_GEMV_CASE(MT_)                                                                                                  \
     if (N <= 1024) {                                                                                                        \
-        if (out_bf16) gemv_smalln_kernel<Mat, MT_, true><<<(N + 1) / 2, 256, 0, st>>>(mat, xp, ldx, op, ldo, N, K, alpha, bias); \
-        else gemv_smalln_kernel<Mat, MT_, false><<<(N + 1) / 2, 256, 0, st>>>(mat, xp, ldx, op, ldo, N, K, alpha, bias);         \
-    } else if (out_bf16) gemv_kernel<Mat, MT_, true><<<grid, 256, 0, st>>>(mat, xp, ldx, op, ldo, N, K, alpha, bias);           \
-    else gemv_kernel<Mat, MT_, false><<<grid, 256, 0, st>>>(mat, xp, ldx, op, ldo, N, K, alpha, bias);
+        if (out_bf16) gemv_smalln_kernel<Mat, MT_, true><<<(N + 1) / 2, 256, 0, st>>>(mat, xp, ldx, op, ldo, N, K, alpha, bias, comm); \
+        else gemv_smalln_kernel<Mat, MT_, false><<<(N + 1) / 2, 256, 0, st>>>(mat, xp, ldx, op, ldo, N, K, alpha, bias, comm);         \
+    } else if (out_bf16) gemv_kernel<Mat, MT_, true><<<grid, 256, 0, st>>>(mat, xp, ldx, op, ldo, N, K, alpha, bias, comm);           \
+    else gemv_kernel<Mat, MT_, false><<<grid, 256, 0, st>>>(mat, xp, ldx, op, ldo, N, K, alpha, bias, comm);
         if (mt == 4) { LSB_GEMV_CASE(4) } else if (mt == 2) { LSB_GEMV_CASE(2) } else { LSB_GEMV_CASE(1) }
 #undef LSB_GEMV_CASE
         m0 += mt;
@@ -127,11 +148,12 @@ static int launch_gemv(Mat mat, const bf16* x, int ldx, void* out, int ldo, int 
 using namespace lsb;
 
 // x: bf16 [M, ldx]; W: bf16 [N, ldw]; out fp32 or bf16 [M, ldo]. K % 8 == 0, 16-byte aligned rows.
+// comm: host pointer to a PeerComm (fused all-reduce push of the fp32 output) or null.
 LSB_API int lsb_gemv_bf16(void* out, const void* x, const void* w, const void* bias, int M, int N, int K, int ldx,
-                          int ldw, int ldo, float alpha, int out_bf16, void* stream) {
+                          int ldw, int ldo, float alpha, int out_bf16, const void* comm, void* stream) {
     if (K % 8 || ldw % 8 || ldx % 8) return -1;
     return launch_gemv(MatBf16{(const bf16*)w, ldw}, (const bf16*)x, ldx, out, ldo, M, N, K, alpha, (const float*)bias,
-                       out_bf16, (cudaStream_t)stream);
+                       out_bf16, (cudaStream_t)stream, comm);
 }
 
 // W: fp32 [N, ldw] (router / hyper-connection mixing matrices). K % 4 == 0.
@@ -144,18 +166,18 @@ LSB_API int lsb_gemv_f32w(void* out, const void* x, const void* w, const void* b
 
 // W: e4m3 [N, K] with fp32 scales [ceil(N/128), ceil(K/128)] (128x128 blocks). K % 16 == 0.
 LSB_API int lsb_gemv_fp8b(void* out, const void* x, const void* w, const void* scales, const void* bias, int M, int N,
-                          int K, int ldx, int ldo, float alpha, int out_bf16, void* stream) {
+                          int K, int ldx, int ldo, float alpha, int out_bf16, const void* comm, void* stream) {
     if (K % 16 || ldx % 8) return -1;
     return launch_gemv(MatFp8B{(const uint8_t*)w, K, (const float*)scales, (K + 127) / 128}, (const bf16*)x, ldx, out,
-                       ldo, M, N, K, alpha, (const float*)bias, out_bf16, (cudaStream_t)stream);
+                       ldo, M, N, K, alpha, (const float*)bias, out_bf16, (cudaStream_t)stream, comm);
 }
 
 // W: packed E2M1 [N, K/2] + e4m3 group scales in the 128x4 atom layout; alpha carries the
 // per-tensor scale (weight_scale_2). K % 32 == 0.
 LSB_API int lsb_gemv_nvfp4(void* out, const void* x, const void* w, const void* sf, const void* bias, int M, int N,
-                           int K, int ldx, int ldo, float alpha, int out_bf16, void* stream) {
+                           int K, int ldx, int ldo, float alpha, int out_bf16, const void* comm, void* stream) {
     if (K % 32 || ldx % 8) return -1;
     const int G = K / 16;
     return launch_gemv(MatNvfp4{(const uint8_t*)w, K, (const uint8_t*)sf, (G + 3) / 4}, (const bf16*)x, ldx, out, ldo,
-                       M, N, K, alpha, (const float*)bias, out_bf16, (cudaStream_t)stream);
+                       M, N, K, alpha, (const float*)bias, out_bf16, (cudaStream_t)stream, comm);
 }

@@ -14,6 +14,7 @@
 //  * moe_combine: out[r] = sum over slots in slot order of w[r][s] * y[r][s]  (fp32, fixed
 //    order => placement-invariant; reference: src/core/expert_device.h:31-52).
 #include "gemv_core.cuh"
+#include "comm.cuh"
 
 namespace lsb {
 
@@ -208,7 +209,7 @@ __global__ void __launch_bounds__(256) moe_gateup_kernel(const bf16* __restrict_
     if (f >= ef.F) return;
     const int e = group_expert[g], n = group_n[g];
     const int slot = slot_of[e];
-    if (slot < 0) { if (threadIdx.x == 0 && blockIdx.x == 0) atomicExch(miss_flag, e + 1); return; }
+    if (slot < 0) { if (miss_flag && threadIdx.x == 0 && blockIdx.x == 0) atomicExch(miss_flag, e + 1); return; }
     const uint8_t* base = arena + (size_t)slot * ef.stride;
     auto rg = RowOf<FMT>::make(base + ef.off_gate, base + ef.off_sg, f, ef.H);
     auto ru = RowOf<FMT>::make(base + ef.off_up, base + ef.off_su, f, ef.H);
@@ -332,7 +333,7 @@ __global__ void __launch_bounds__(256) moe_gateup_fp4_kernel(const bf16* __restr
     const int e = group_expert[g];
     const int n = MT == 1 ? 1 : (group_n ? group_n[g] : 1);
     const int slot = (e >= 0) ? slot_of[e] : -1;
-    if (slot < 0) { if (e >= 0 && threadIdx.x == 0 && blockIdx.x == 0) atomicExch(miss_flag, e + 1); return; }
+    if (slot < 0) { if (miss_flag && e >= 0 && threadIdx.x == 0 && blockIdx.x == 0) atomicExch(miss_flag, e + 1); return; }
     int pr[MT];
 #pragma unroll
     for (int i = 0; i < MT; ++i) pr[i] = group_pairs ? group_pairs[g * 4 + min(i, n - 1)] : g;
@@ -428,12 +429,18 @@ __global__ void __launch_bounds__(256) moe_down_fp4_kernel(const bf16* __restric
 // out[r][h] = sum_s w[r][s] * y[r*S+s][h], slots in order; experts that were not resident
 // (slot < 0) contribute nothing.  mode 0: write fp32; mode 1: add into out.
 __global__ void moe_combine_kernel(float* __restrict__ out, const float* __restrict__ y, const float* __restrict__ wts,
-                                   const int* __restrict__ ids, const int* __restrict__ slot_of, int S, int H, int accumulate) {
+                                   const int* __restrict__ ids, const int* __restrict__ slot_of, int S, int H, int accumulate,
+                                   PeerComm comm) {
     constexpr int kMaxS = 16;
     pdl_wait();
     const int r = blockIdx.y;
     const int h = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
-    if (h >= H) return;
+    unsigned next_epoch = 0;
+    if (comm.nranks) next_epoch = *comm.epoch + 1;
+    if (h >= H) {
+        if (comm.nranks) comm_signal(comm, next_epoch, gridDim.x * gridDim.y);
+        return;
+    }
     // routing metadata first (independent loads), then all slot rows in flight together
     int e[kMaxS];
     float w[kMaxS];
@@ -450,9 +457,16 @@ __global__ void moe_combine_kernel(float* __restrict__ out, const float* __restr
     for (int s = 0; s < kMaxS; ++s) {
         if (e[s] >= 0) { a.x = fmaf(w[s], v[s].x, a.x); a.y = fmaf(w[s], v[s].y, a.y); a.z = fmaf(w[s], v[s].z, a.z); a.w = fmaf(w[s], v[s].w, a.w); }
     }
-    float4* o = reinterpret_cast<float4*>(out + (size_t)r * H + h);
-    if (accumulate) { float4 p = *o; a.x += p.x; a.y += p.y; a.z += p.z; a.w += p.w; }
-    *o = a;
+    if (comm.nranks) {
+        const size_t idx = (size_t)r * H + h;
+        comm_push(comm, next_epoch, idx, a.x); comm_push(comm, next_epoch, idx + 1, a.y);
+        comm_push(comm, next_epoch, idx + 2, a.z); comm_push(comm, next_epoch, idx + 3, a.w);
+        comm_signal(comm, next_epoch, gridDim.x * gridDim.y);
+    } else {
+        float4* o = reinterpret_cast<float4*>(out + (size_t)r * H + h);
+        if (accumulate) { float4 p = *o; a.x += p.x; a.y += p.y; a.z += p.z; a.w += p.w; }
+        *o = a;
+    }
     pdl_launch_dependents();
 }
 
@@ -557,11 +571,14 @@ LSB_API int lsb_moe_down(const void* act, const void* arena, const void* slot_of
 }
 
 LSB_API int lsb_moe_combine(void* out, const void* y, const void* wts, const void* ids, const void* slot_of, int rows,
-                            int S, int H, int accumulate, void* stream) {
+                            int S, int H, int accumulate, const void* comm, void* stream) {
+    PeerComm pc;
+    pc.nranks = 0;
+    if (comm) pc = *reinterpret_cast<const PeerComm*>(comm);
     if (H % 4 || S > 16) return -1;
     dim3 grid((H / 4 + 127) / 128, rows);
     moe_combine_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>((float*)out, (const float*)y, (const float*)wts, (const int*)ids,
-                                                             (const int*)slot_of, S, H, accumulate);
+                                                             (const int*)slot_of, S, H, accumulate, pc);
     LSB_CHECK_LAUNCH();
 }
 

@@ -8,6 +8,7 @@
 // are one fused pass: a partial kernel spread over the hidden dimension followed by a
 // one-block-per-token finalize that also applies the sublayer's input RMSNorm.
 #include "common.cuh"
+#include "comm.cuh"
 
 namespace lsb {
 
@@ -23,15 +24,17 @@ __device__ __forceinline__ float ld_as_float<bf16>(const bf16* p, int i) { retur
 template <typename TIn, bool ADD>
 __global__ void rmsnorm_kernel(bf16* __restrict__ out, const TIn* __restrict__ x, float* __restrict__ resid,
                                const float* __restrict__ w, int dim, int ldx, int ldo, int ldr, float eps,
-                               float* __restrict__ out_f32) {
+                               float* __restrict__ out_f32, PeerComm comm) {
     __shared__ float red[33];
     extern __shared__ float row[];
     const int r = blockIdx.x;
     const TIn* xr = x + (size_t)r * ldx;
     pdl_wait();
+    unsigned epoch = 0;
+    if (comm.nranks) { epoch = *comm.epoch; comm_wait(comm, epoch); }
     float ss = 0.f;
     for (int i = threadIdx.x; i < dim; i += blockDim.x) {
-        float v = ld_as_float<TIn>(xr, i);
+        float v = comm.nranks ? comm_reduce(comm, epoch, (size_t)r * ldx + i) : ld_as_float<TIn>(xr, i);
         if (ADD) {
             v += resid[(size_t)r * ldr + i];
             resid[(size_t)r * ldr + i] = v;
@@ -63,7 +66,7 @@ constexpr int kHcPerWarp = 6;       // mixing logits per warp (4 warps x 6 = 24)
 __global__ void __launch_bounds__(128) mhc_post_partial_kernel(float* __restrict__ residual, const float* __restrict__ x,
                                                                const float* __restrict__ post, const float* __restrict__ comb,
                                                                const float* __restrict__ fn, float* __restrict__ part,
-                                                               int hidden, int n, int mode) {
+                                                               int hidden, int n, int mode, PeerComm comm) {
     const int r = blockIdx.x, c = blockIdx.y, lane = threadIdx.x & 31, og = threadIdx.x >> 5;
     const int h = c * kHcChunk + lane;
     const int nout = 2 * n + n * n;
@@ -78,7 +81,14 @@ __global__ void __launch_bounds__(128) mhc_post_partial_kernel(float* __restrict
     pdl_wait();
     float res[kHcMax];
     float* rp = residual + (size_t)r * n * hidden;
-    const float xv = x[(size_t)r * hidden + h];
+    float xv;
+    if (comm.nranks && mode == 1) {
+        const unsigned epoch = *comm.epoch;
+        comm_wait(comm, epoch);
+        xv = comm_reduce(comm, epoch, (size_t)r * hidden + h);
+    } else {
+        xv = x[(size_t)r * hidden + h];
+    }
     if (mode == 0) {
 #pragma unroll
         for (int j = 0; j < kHcMax; ++j) res[j] = j < n ? xv : 0.f;
@@ -219,11 +229,13 @@ __global__ void __launch_bounds__(512) mhc_finalize_kernel(bf16* __restrict__ ou
 // Last layer: out = RMSNorm(mean_j(post[j]*x + sum_i comb[i][j]*residual[i])) * w.
 __global__ void mhc_contract_norm_kernel(bf16* __restrict__ out, const float* __restrict__ residual, const float* __restrict__ x,
                                          const float* __restrict__ post, const float* __restrict__ comb,
-                                         const float* __restrict__ norm_w, int hidden, int n, float rms_eps) {
+                                         const float* __restrict__ norm_w, int hidden, int n, float rms_eps, PeerComm comm) {
     __shared__ float red[33];
     extern __shared__ float row[];
     const int r = blockIdx.x;
     pdl_wait();
+    unsigned epoch = 0;
+    if (comm.nranks) { epoch = *comm.epoch; comm_wait(comm, epoch); }
     const float* rp = residual + (size_t)r * n * hidden;
     float pm = 0.f, cw[kHcMax];
     for (int j = 0; j < n; ++j) pm += post[r * n + j];
@@ -234,7 +246,7 @@ __global__ void mhc_contract_norm_kernel(bf16* __restrict__ out, const float* __
     }
     float ss = 0.f;
     for (int h = threadIdx.x; h < hidden; h += blockDim.x) {
-        float a = pm * x[(size_t)r * hidden + h];
+        float a = pm * (comm.nranks ? comm_reduce(comm, epoch, (size_t)r * hidden + h) : x[(size_t)r * hidden + h]);
         for (int i = 0; i < n; ++i) a += cw[i] * rp[(size_t)i * hidden + h];
         a /= (float)n;
         row[h] = a;
@@ -249,23 +261,34 @@ __global__ void mhc_contract_norm_kernel(bf16* __restrict__ out, const float* __
 }  // namespace lsb
 using namespace lsb;
 
+static PeerComm comm_from_host(const void* h) {
+    PeerComm c;
+    c.nranks = 0;
+    if (h) c = *reinterpret_cast<const PeerComm*>(h);
+    return c;
+}
+
 LSB_API int lsb_rmsnorm(void* out, const void* x, const void* w, int rows, int dim, int ldx, int ldo, float eps,
                         int x_is_f32, void* out_f32, void* stream) {
     cudaStream_t st = (cudaStream_t)stream;
+    PeerComm nocomm;
+    nocomm.nranks = 0;
     const int thr = dim >= 2048 ? 512 : 256;
     const size_t sm = (size_t)dim * 4;
     if (x_is_f32)
-        rmsnorm_kernel<float, false><<<rows, thr, sm, st>>>((bf16*)out, (const float*)x, nullptr, (const float*)w, dim, ldx, ldo, 0, eps, (float*)out_f32);
+        rmsnorm_kernel<float, false><<<rows, thr, sm, st>>>((bf16*)out, (const float*)x, nullptr, (const float*)w, dim, ldx, ldo, 0, eps, (float*)out_f32, nocomm);
     else
-        rmsnorm_kernel<bf16, false><<<rows, thr, sm, st>>>((bf16*)out, (const bf16*)x, nullptr, (const float*)w, dim, ldx, ldo, 0, eps, (float*)out_f32);
+        rmsnorm_kernel<bf16, false><<<rows, thr, sm, st>>>((bf16*)out, (const bf16*)x, nullptr, (const float*)w, dim, ldx, ldo, 0, eps, (float*)out_f32, nocomm);
     LSB_CHECK_LAUNCH();
 }
 
-// resid (fp32, in place) += x (fp32); out = RMSNorm(resid) * w as bf16.
-LSB_API int lsb_add_rmsnorm(void* out, void* resid, const void* x, const void* w, int rows, int dim, float eps, void* stream) {
+// resid (fp32, in place) += x (fp32); out = RMSNorm(resid) * w as bf16.  With `comm`, x is the
+// cross-rank sum of the partials the producing kernel pushed (fused all-reduce).
+LSB_API int lsb_add_rmsnorm(void* out, void* resid, const void* x, const void* w, int rows, int dim, float eps, const void* comm,
+                            void* stream) {
     const int thr = dim >= 2048 ? 512 : 256;
     rmsnorm_kernel<float, true><<<rows, thr, (size_t)dim * 4, (cudaStream_t)stream>>>((bf16*)out, (const float*)x, (float*)resid,
-                                                                                   (const float*)w, dim, dim, dim, dim, eps, nullptr);
+                                                                                   (const float*)w, dim, dim, dim, dim, eps, nullptr, comm_from_host(comm));
     LSB_CHECK_LAUNCH();
 }
 
@@ -275,12 +298,12 @@ LSB_API int lsb_add_rmsnorm(void* out, void* resid, const void* x, const void* w
 LSB_API int lsb_mhc_post_pre(void* out_x, void* residual, const void* x, void* post, void* comb, const void* fn,
                              const void* hc_scale, const void* hc_base, const void* norm_w, void* part, int rows,
                              int hidden, int n, int mode, int iters, float hc_eps, float rms_eps, float post_mult,
-                             void* stream) {
+                             const void* comm, void* stream) {
     if (hidden % kHcChunk || n > kHcMax) return -1;
     cudaStream_t st = (cudaStream_t)stream;
     const int nchunks = hidden / kHcChunk;
     mhc_post_partial_kernel<<<dim3(rows, nchunks), 128, 0, st>>>((float*)residual, (const float*)x, (const float*)post,
-                                                                    (const float*)comb, (const float*)fn, (float*)part, hidden, n, mode);
+                                                                    (const float*)comb, (const float*)fn, (float*)part, hidden, n, mode, comm_from_host(comm));
     mhc_finalize_kernel<<<rows, 512, (size_t)hidden * 4, st>>>((bf16*)out_x, (const float*)residual, (const float*)part,
                                                               (const float*)hc_scale, (const float*)hc_base, (const float*)norm_w,
                                                               (float*)post, (float*)comb, hidden, n, nchunks, iters, hc_eps, rms_eps, post_mult);
@@ -288,9 +311,9 @@ LSB_API int lsb_mhc_post_pre(void* out_x, void* residual, const void* x, void* p
 }
 
 LSB_API int lsb_mhc_contract_norm(void* out, const void* residual, const void* x, const void* post, const void* comb,
-                                  const void* norm_w, int rows, int hidden, int n, float rms_eps, void* stream) {
+                                  const void* norm_w, int rows, int hidden, int n, float rms_eps, const void* comm, void* stream) {
     mhc_contract_norm_kernel<<<rows, 512, (size_t)hidden * 4, (cudaStream_t)stream>>>((bf16*)out, (const float*)residual, (const float*)x,
                                                                                       (const float*)post, (const float*)comb,
-                                                                                      (const float*)norm_w, hidden, n, rms_eps);
+                                                                                      (const float*)norm_w, hidden, n, rms_eps, comm_from_host(comm));
     LSB_CHECK_LAUNCH();
 }

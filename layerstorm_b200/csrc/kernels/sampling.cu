@@ -5,6 +5,7 @@
 // inline Philox-4x32-10), confidence.cu:88, embedding.cu:28, and the orchestrator's acceptance
 // rules (python/orchestrator/orchestrator.py:289-303, 3781-3818).
 #include "common.cuh"
+#include "comm.cuh"
 
 namespace lsb {
 
@@ -56,15 +57,46 @@ __global__ void argmax_partial_kernel(const float* __restrict__ logits, int ld, 
     pdl_launch_dependents();
 }
 
+// Final reduction over the per-block partials.  With `comm` (vocabulary-parallel LM head) the
+// local winner - packed with its GLOBAL token id - is stored into every rank's receive slot and
+// the winners of all ranks are merged, so only 8 bytes per row cross NVLink instead of the
+// logits (the reference all-gathers [B, vocab/tp] fp32 logits: src/daemon/dispatch_forward.cpp:538).
 __global__ void argmax_final_kernel(const unsigned long long* __restrict__ part, int nblk, int* __restrict__ out_ids,
-                                    float* __restrict__ out_val, int base) {
+                                    float* __restrict__ out_val, int base, PeerComm comm) {
+    __shared__ unsigned long long s_best;
     const int r = blockIdx.x;
     pdl_wait();
+    unsigned next_epoch = 0;
+    if (comm.nranks) next_epoch = *comm.epoch + 1;
     if (threadIdx.x == 0) {
         unsigned long long best = 0ull;
         for (int i = 0; i < nblk; ++i) { const unsigned long long k = part[(size_t)r * nblk + i]; best = k > best ? k : best; }
-        const uint32_t idx = 0xffffffffu - (uint32_t)(best & 0xffffffffull);
-        out_ids[r] = (int)idx + base;
+        // re-pack with the global index
+        const uint32_t idx = 0xffffffffu - (uint32_t)(best & 0xffffffffull) + (uint32_t)base;
+        best = (best & 0xffffffff00000000ull) | (unsigned long long)(0xffffffffu - idx);
+        s_best = best;
+        if (comm.nranks) {
+            const size_t off = ((size_t)(next_epoch & 1u) * comm.nranks + comm.rank) * (size_t)comm.cap + (size_t)r * 2;
+            for (int p = 0; p < comm.nranks; ++p) *reinterpret_cast<unsigned long long*>(comm.recv[p] + off) = best;
+        }
+    }
+    if (comm.nranks) {
+        comm_signal(comm, next_epoch, gridDim.x);
+        comm_wait(comm, next_epoch);
+    } else {
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        unsigned long long best = s_best;
+        if (comm.nranks) {
+            best = 0ull;
+            for (int p = 0; p < comm.nranks; ++p) {
+                const size_t off = ((size_t)(next_epoch & 1u) * comm.nranks + p) * (size_t)comm.cap + (size_t)r * 2;
+                const unsigned long long k = __ldcg(reinterpret_cast<const unsigned long long*>(comm.recv[comm.rank] + off));
+                best = k > best ? k : best;
+            }
+        }
+        out_ids[r] = (int)(0xffffffffu - (uint32_t)(best & 0xffffffffull));
         if (out_val) {
             const uint32_t key = (uint32_t)(best >> 32);
             const uint32_t bits = (key & 0x80000000u) ? (key & 0x7fffffffu) : ~key;
@@ -240,10 +272,13 @@ LSB_API int lsb_embedding(void* out_f32, void* out_bf16, const void* table, cons
 
 // part: scratch u64 [rows, 64].  out_val may be null.  `base` is added to the index (vocab shard offset).
 LSB_API int lsb_argmax(const void* logits, int ld, int rows, int V, void* part, void* out_ids, void* out_val, int base,
-                       void* stream) {
+                       const void* comm, void* stream) {
     cudaStream_t st = (cudaStream_t)stream;
+    PeerComm pc;
+    pc.nranks = 0;
+    if (comm) pc = *reinterpret_cast<const PeerComm*>(comm);
     argmax_partial_kernel<<<dim3(64, rows), 256, 0, st>>>((const float*)logits, ld, V, (unsigned long long*)part);
-    argmax_final_kernel<<<rows, 32, 0, st>>>((const unsigned long long*)part, 64, (int*)out_ids, (float*)out_val, base);
+    argmax_final_kernel<<<rows, 32, 0, st>>>((const unsigned long long*)part, 64, (int*)out_ids, (float*)out_val, base, pc);
     LSB_CHECK_LAUNCH();
 }
 

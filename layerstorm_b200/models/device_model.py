@@ -133,18 +133,22 @@ class QLinear:
         return self.w.numel() * self.w.element_size() + (self.scales.numel() * self.scales.element_size() if self.scales is not None else 0)
 
     def __call__(self, out: torch.Tensor, x: torch.Tensor, M: int, ldx: Optional[int] = None, ldo: Optional[int] = None,
-                 bias: Optional[torch.Tensor] = None):
+                 bias: Optional[torch.Tensor] = None, comm: Optional[int] = None):
+        """out[M, N] = x[M, K] @ W^T.  ``comm`` (address of a PeerComm struct) turns the store into the
+        push half of a fused cross-rank all-reduce (row-parallel layers)."""
         ldx = ldx if ldx is not None else self.K
         ldo = ldo if ldo is not None else self.N
         ob = 1 if out.dtype == torch.bfloat16 else 0
+        if comm is not None and M not in (1, 2, 4):
+            raise RuntimeError("the fused all-reduce epilogue covers single-pass shapes (1, 2 or 4 rows)")
         if self.fmt == "bf16":
-            nat.call("lsb_gemv_bf16", out, x, self.w, bias, M, self.N, self.K, ldx, self.K, ldo, 1.0, ob)
+            nat.call("lsb_gemv_bf16", out, x, self.w, bias, M, self.N, self.K, ldx, self.K, ldo, 1.0, ob, comm)
         elif self.fmt == "f32":
             nat.call("lsb_gemv_f32w", out, x, self.w, bias, M, self.N, self.K, ldx, self.K, ldo, 1.0, ob)
         elif self.fmt == "fp8_e4m3":
-            nat.call("lsb_gemv_fp8b", out, x, self.w, self.scales, bias, M, self.N, self.K, ldx, ldo, 1.0, ob)
+            nat.call("lsb_gemv_fp8b", out, x, self.w, self.scales, bias, M, self.N, self.K, ldx, ldo, 1.0, ob, comm)
         else:
-            nat.call("lsb_gemv_nvfp4", out, x, self.w, self.scales, bias, M, self.N, self.K, ldx, ldo, self.alpha, ob)
+            nat.call("lsb_gemv_nvfp4", out, x, self.w, self.scales, bias, M, self.N, self.K, ldx, ldo, self.alpha, ob, comm)
 
 
 @dataclass
@@ -230,9 +234,9 @@ class Workspace:
         self.post = z(R, n); self.comb = z(R, n, n)
         self.part = z(R, max(1, H // 32), 25)
         self.proj = z(R, m.max_proj)
-        C = cfg.kda_heads * cfg.kda_head_dim
+        C = m.Hk * cfg.kda_head_dim
         self.kda_out = z(R, max(C, 1), dtype=b16)
-        Hh = cfg.n_heads
+        Hh = m.Hh
         self.q_c = z(R, max(cfg.q_lora, 1), dtype=b16)
         self.qproj = z(R, m.max_qb, dtype=b16)
         self.q_abs = z(R, Hh, cfg.kv_lora + cfg.qk_rope, dtype=b16)
@@ -253,7 +257,7 @@ class Workspace:
             self.idx_w = z(R, cfg.index_n_heads)
             self.kstash = z(R, cfg.index_head_dim, dtype=b16)
         # FFN
-        F = max(cfg.dense_inter, 1)
+        F = max(m.Fd, 1)
         self.gu = z(R, 2 * F)
         self.act_d = z(R, F, dtype=b16)
         if cfg.n_routed > 0:
@@ -271,17 +275,31 @@ class Workspace:
             self.miss = z(1, dtype=i32)
         # outputs
         self.n_logit_rows = n_logit_rows
-        self.logits = z(n_logit_rows, cfg.vocab)
+        self.logits = z(n_logit_rows, m.V_local)
         self.amax_part = torch.zeros(n_logit_rows, 64, dtype=torch.int64, device=dev)
         self.out_tok = z(n_logit_rows, dtype=i32)
         self.out_val = z(n_logit_rows)
 
 
 class DeviceModel:
-    def __init__(self, cfg: ModelConfig, device="cuda", kv_fmt: str = "fp8", page: int = 64):
+    def __init__(self, cfg: ModelConfig, device="cuda", kv_fmt: str = "fp8", page: int = 64, tp_rank: int = 0, tp_size: int = 1):
         self.cfg, self.device = cfg, torch.device(device)
         self.kv_fmt, self.page = kv_fmt, page
         assert page % max(cfg.index_kpool, 1) == 0
+        # Tensor / expert parallel layout (one process per GPU): attention heads, KDA heads, dense FFN
+        # columns and the LM-head vocabulary are split over the ranks; routed experts are owned by rank
+        # e % tp_size, the shared expert of layer i by rank i % tp_size; small projections are replicated.
+        self.tp_rank, self.tp_size = tp_rank, tp_size
+        for v, nm in ((cfg.n_heads, "n_heads"), (cfg.dense_inter, "dense_inter"), (cfg.vocab, "vocab")):
+            assert v % tp_size == 0, f"{nm}={v} not divisible by tp={tp_size}"
+        assert cfg.kda_heads % tp_size == 0
+        self.Hh = cfg.n_heads // tp_size
+        self.Hk = cfg.kda_heads // tp_size
+        self.Fd = cfg.dense_inter // tp_size
+        self.V_local = cfg.vocab // tp_size
+        self._fused = False
+        self.comm = None          # PeerComm for the fused all-reduces
+        self.comm_amax = None     # PeerComm for the argmax exchange
         self.layers: List[dict] = []
         self.embed = None
         self.head: Optional[QLinear] = None
@@ -303,22 +321,52 @@ class DeviceModel:
         self.block_table = None
         self.kernel_launches = 0
 
+    def attach_comm(self, comm, comm_amax):
+        self.comm, self.comm_amax = comm, comm_amax
+
+    @property
+    def _cp(self):
+        """PeerComm address for the fused all-reduce of the current step, or None (single GPU, or a
+        step shape the fused epilogue does not cover - those use NCCL, see ``_reduce``)."""
+        return self.comm.ptr if (self.comm is not None and self._fused) else None
+
+    def _reduce(self, ws, R):
+        """Row-parallel partial -> full sum when the fused in-kernel path is not in use."""
+        if self.tp_size > 1 and not self._fused:
+            import torch.distributed as dist
+            dist.all_reduce(ws.sub[:R])
+
+    def owns_expert(self, layer: int, e: int) -> bool:
+        if e < self.cfg.n_routed:
+            return e % self.tp_size == self.tp_rank
+        return layer % self.tp_size == self.tp_rank
+
     # ------------------------------------------------------------------ construction
     def _lin(self, get, name, fmt):
         return QLinear.from_float(get(name), fmt, self.device)
 
     @classmethod
     def from_state_dict(cls, cfg: ModelConfig, w: Dict[str, torch.Tensor], device="cuda", kv_fmt="fp8", page=64,
-                        expert_quant: Optional[str] = None, dense_quant: Optional[str] = None) -> "DeviceModel":
-        m = cls(cfg, device, kv_fmt, page)
+                        expert_quant: Optional[str] = None, dense_quant: Optional[str] = None, tp_rank: int = 0,
+                        tp_size: int = 1) -> "DeviceModel":
+        m = cls(cfg, device, kv_fmt, page, tp_rank, tp_size)
         dev = m.device
+        tr, ts = tp_rank, tp_size
+
+        def rows(t, n_units, unit):     # this rank's block of `n_units/ts` units of `unit` rows
+            per = n_units // ts * unit
+            return t[tr * per: (tr + 1) * per]
+
+        def cols(t, n_units, unit):
+            per = n_units // ts * unit
+            return t[:, tr * per: (tr + 1) * per]
         eq = expert_quant or cfg.expert_quant
         dq = dense_quant or cfg.dense_quant
         if eq.startswith("gguf"):
             eq = "bf16"
         f32 = lambda t: t.to(dev).float().contiguous()
         m.embed = w["embed.weight"].to(dev).to(torch.bfloat16).contiguous()
-        m.head = QLinear.from_float(w["head.weight"], "bf16", dev)
+        m.head = QLinear.from_float(rows(w["head.weight"], cfg.vocab, 1), "bf16", dev)
         m.final_norm = f32(w["final_norm.weight"])
         for i in range(cfg.n_layers):
             p = f"layers.{i}."
@@ -328,17 +376,21 @@ class DeviceModel:
                     L[nm] = (f32(w[p + nm + ".fn"]), f32(w[p + nm + ".scale"]), f32(w[p + nm + ".base"]))
             if cfg.is_kda_layer(i):
                 k = p + "kda."
-                L["kda_in"] = QLinear.from_float(torch.cat([w[k + "q"], w[k + "k"], w[k + "v"], w[k + "beta"], w[k + "f_a"], w[k + "g_a"]], 0), dq, dev)
-                L["kda_fb"] = w[k + "f_b"].to(dev).to(torch.bfloat16).contiguous()
-                L["kda_gb"] = w[k + "g_b"].to(dev).to(torch.bfloat16).contiguous()
-                for nm in ("conv_q", "conv_k", "conv_v", "dt_bias", "o_norm"):
-                    L["kda_" + nm] = f32(w[k + nm])
-                L["kda_a_exp"] = torch.exp(f32(w[k + "a_log"]))
-                L["kda_o"] = QLinear.from_float(w[k + "o"], dq, dev)
+                Hk, D = cfg.kda_heads, cfg.kda_head_dim
+                L["kda_in"] = QLinear.from_float(torch.cat([rows(w[k + "q"], Hk, D), rows(w[k + "k"], Hk, D), rows(w[k + "v"], Hk, D),
+                                                            rows(w[k + "beta"], Hk, 1), w[k + "f_a"], w[k + "g_a"]], 0), dq, dev)
+                L["kda_fb"] = rows(w[k + "f_b"], Hk, D).to(dev).to(torch.bfloat16).contiguous()
+                L["kda_gb"] = rows(w[k + "g_b"], Hk, D).to(dev).to(torch.bfloat16).contiguous()
+                for nm in ("conv_q", "conv_k", "conv_v"):
+                    L["kda_" + nm] = f32(rows(w[k + nm], Hk, D))
+                L["kda_dt_bias"] = f32(rows(w[k + "dt_bias"], Hk, 1))
+                L["kda_o_norm"] = f32(w[k + "o_norm"])
+                L["kda_a_exp"] = torch.exp(f32(rows(w[k + "a_log"], Hk, 1)))
+                L["kda_o"] = QLinear.from_float(cols(w[k + "o"], Hk, D), dq, dev)
             else:
                 a = p + "attn."
                 parts = [w[a + "q_a"], w[a + "kv_a"]]
-                qb_parts = [w[a + "q_b"]]
+                qb_parts = [rows(w[a + "q_b"], cfg.n_heads, cfg.qk_head)]
                 has_idx = cfg.has_indexer and cfg.index_source_layer(i) == i
                 if has_idx:
                     x = p + "indexer."
@@ -351,40 +403,42 @@ class DeviceModel:
                 L["mla_in"] = QLinear.from_float(torch.cat(parts, 0), dq, dev)
                 L["mla_qb"] = QLinear.from_float(torch.cat(qb_parts, 0), dq, dev)
                 L["qa_norm"] = f32(w[a + "q_a_norm"]); L["kv_norm"] = f32(w[a + "kv_a_norm"])
-                L["k_b"] = w[a + "k_b"].to(dev).to(torch.bfloat16).contiguous()
-                L["v_b"] = w[a + "v_b"].to(dev).to(torch.bfloat16).contiguous()
-                L["mla_o"] = QLinear.from_float(w[a + "o"], dq, dev)
+                L["k_b"] = rows(w[a + "k_b"], cfg.n_heads, 1).to(dev).to(torch.bfloat16).contiguous()
+                L["v_b"] = rows(w[a + "v_b"], cfg.n_heads, 1).to(dev).to(torch.bfloat16).contiguous()
+                L["mla_o"] = QLinear.from_float(cols(w[a + "o"], cfg.n_heads, cfg.v_head), dq, dev)
             if cfg.is_moe_layer(i):
                 mo = p + "moe."
                 L["router"] = QLinear.from_float(w[mo + "router"], "f32", dev)
                 L["router_bias"] = f32(w[mo + "router_bias"]) if (mo + "router_bias") in w else None
                 ef = expert_layout(eq, cfg.hidden, cfg.moe_inter)
                 E_total = cfg.n_routed + cfg.n_shared
-                arena = ExpertArena(ef, E_total, E_total, dev)
-                for e in range(E_total):
+                mine = [e for e in range(E_total) if m.owns_expert(i, e)]
+                arena = ExpertArena(ef, max(len(mine), 1), E_total, dev)
+                for s_, e in enumerate(mine):
                     nm = mo + (f"experts.{e}." if e < cfg.n_routed else f"shared.{e - cfg.n_routed}.")
-                    arena.write_expert(e, *(QLinear.from_float(w[nm + t], eq, dev) for t in ("gate", "up", "down")))
-                    arena.slot_of[e] = e
+                    arena.write_expert(s_, *(QLinear.from_float(w[nm + t], eq, dev) for t in ("gate", "up", "down")))
+                    arena.slot_of[e] = s_
                 L["arena"] = arena
             else:
                 f = p + "mlp."
-                L["mlp_gu"] = QLinear.from_float(torch.cat([w[f + "gate"], w[f + "up"]], 0), dq, dev)
-                L["mlp_down"] = QLinear.from_float(w[f + "down"], dq, dev)
+                L["mlp_gu"] = QLinear.from_float(torch.cat([rows(w[f + "gate"], cfg.dense_inter, 1), rows(w[f + "up"], cfg.dense_inter, 1)], 0), dq, dev)
+                L["mlp_down"] = QLinear.from_float(cols(w[f + "down"], cfg.dense_inter, 1), dq, dev)
             m.layers.append(L)
         m._finish()
         return m
 
     @classmethod
     def random_init(cls, cfg: ModelConfig, device="cuda", kv_fmt="fp8", page=64, seed=0, expert_slots=None,
-                    embed_on_host: bool = False, reserve_bytes: int = 4 << 30) -> "DeviceModel":
+                    embed_on_host: bool = False, reserve_bytes: int = 4 << 30, tp_rank: int = 0, tp_size: int = 1) -> "DeviceModel":
         """Random weights generated directly in storage format on the device (full-size models).
         ``expert_slots`` caps the routed-expert slots per MoE layer (VRAM expert cache): an int, None
         (all experts resident) or "auto" (as many as fit while leaving ``reserve_bytes`` of device
         memory free for caches and workspaces).  The first slots hold the shared experts followed by
         routed experts 0..; the rest start non-resident."""
-        m = cls(cfg, device, kv_fmt, page)
+        m = cls(cfg, device, kv_fmt, page, tp_rank, tp_size)
         dev = m.device
-        gen = torch.Generator(device=dev).manual_seed(seed)
+        gen = torch.Generator(device=dev).manual_seed(seed)                          # replicated tensors: same on every rank
+        gloc = torch.Generator(device=dev).manual_seed(seed * 7919 + 1 + tp_rank)    # this rank's shards
         dq, eq = cfg.dense_quant, cfg.expert_quant
         if eq.startswith("gguf"):
             eq = "nvfp4"
@@ -401,11 +455,17 @@ class DeviceModel:
             return t
 
         if embed_on_host:
-            e = torch.empty(cfg.vocab, H, dtype=torch.bfloat16).normal_(0.0, 1.0).pin_memory()
+            hg = torch.Generator().manual_seed(seed)
+            e = torch.empty(cfg.vocab, H, dtype=torch.bfloat16).normal_(0.0, 1.0, generator=hg).pin_memory()
             m.embed = e
         else:
             m.embed = rnd(cfg.vocab, H, std=1.0, dtype=torch.bfloat16)
-        m.head = QLinear.random(cfg.vocab, H, "bf16", dev, gen=gen)
+        m.head = QLinear.random(m.V_local, H, "bf16", dev, gen=gloc)
+
+        def overwrite_rows(lin: QLinear, r0: int, std: float):
+            """Re-draw rows [r0:] from the replicated generator (projections every rank must agree on)."""
+            if lin.fmt == "bf16" and r0 < lin.N:
+                lin.w[r0:].normal_(0.0, std, generator=gen)
         m.final_norm = nrm(H)
         n = cfg.hc_mult
         for i in range(cfg.n_layers):
@@ -414,18 +474,19 @@ class DeviceModel:
                 for nm in ("hc_attn", "hc_ffn"):
                     L[nm] = (rnd(2 * n + n * n, n * H, std=0.05), torch.ones(3, device=dev), rnd(2 * n + n * n, std=0.5))
             if cfg.is_kda_layer(i):
-                C = cfg.kda_heads * cfg.kda_head_dim
-                L["kda_in"] = QLinear.random(3 * C + cfg.kda_heads + 2 * cfg.kda_rank, H, dq, dev, std=0.05, gen=gen)
-                L["kda_fb"] = rnd(C, cfg.kda_rank, std=0.2, dtype=torch.bfloat16)
-                L["kda_gb"] = rnd(C, cfg.kda_rank, std=0.2, dtype=torch.bfloat16)
+                C = m.Hk * cfg.kda_head_dim
+                L["kda_in"] = QLinear.random(3 * C + m.Hk + 2 * cfg.kda_rank, H, dq, dev, std=0.05, gen=gloc)
+                overwrite_rows(L["kda_in"], 3 * C + m.Hk, 0.05)
+                L["kda_fb"] = torch.empty(C, cfg.kda_rank, dtype=torch.bfloat16, device=dev).normal_(0.0, 0.2, generator=gloc)
+                L["kda_gb"] = torch.empty(C, cfg.kda_rank, dtype=torch.bfloat16, device=dev).normal_(0.0, 0.2, generator=gloc)
                 for nm in ("conv_q", "conv_k", "conv_v"):
-                    L["kda_" + nm] = torch.empty(C, cfg.kda_conv, device=dev).uniform_(-0.5, 0.5, generator=gen)
-                L["kda_dt_bias"] = torch.empty(cfg.kda_heads, cfg.kda_head_dim, device=dev).uniform_(-1, 1, generator=gen)
+                    L["kda_" + nm] = torch.empty(C, cfg.kda_conv, device=dev).uniform_(-0.5, 0.5, generator=gloc)
+                L["kda_dt_bias"] = torch.empty(m.Hk, cfg.kda_head_dim, device=dev).uniform_(-1, 1, generator=gloc)
                 L["kda_o_norm"] = nrm(cfg.kda_head_dim)
-                L["kda_a_exp"] = torch.exp(torch.empty(cfg.kda_heads, device=dev).uniform_(-1.0, 1.5, generator=gen))
-                L["kda_o"] = QLinear.random(H, C, dq, dev, gen=gen)
+                L["kda_a_exp"] = torch.exp(torch.empty(m.Hk, device=dev).uniform_(-1.0, 1.5, generator=gloc))
+                L["kda_o"] = QLinear.random(H, C, dq, dev, gen=gloc)
             else:
-                Hh = cfg.n_heads
+                Hh = m.Hh
                 has_idx = cfg.has_indexer and cfg.index_source_layer(i) == i
                 n_in = cfg.q_lora + cfg.kv_lora + cfg.qk_rope
                 n_qb = Hh * cfg.qk_head
@@ -436,40 +497,43 @@ class DeviceModel:
                         L["idx_ape"] = rnd(cfg.index_kpool, cfg.index_head_dim, std=0.5)
                     L["idx_ln_w"] = nrm(cfg.index_head_dim); L["idx_ln_b"] = rnd(cfg.index_head_dim, std=0.1)
                 L["mla_in"] = QLinear.random(_align(n_in, 8), H, dq, dev, std=0.05, gen=gen)
-                L["mla_qb"] = QLinear.random(n_qb, cfg.q_lora, dq, dev, std=0.05, gen=gen)
+                L["mla_qb"] = QLinear.random(n_qb, cfg.q_lora, dq, dev, std=0.05, gen=gloc)
+                overwrite_rows(L["mla_qb"], Hh * cfg.qk_head, 0.05)
                 L["qa_norm"] = nrm(cfg.q_lora); L["kv_norm"] = nrm(cfg.kv_lora)
-                L["k_b"] = rnd(Hh, cfg.kv_lora, cfg.qk_nope, std=0.05, dtype=torch.bfloat16)
-                L["v_b"] = rnd(Hh, cfg.v_head, cfg.kv_lora, std=0.05, dtype=torch.bfloat16)
-                L["mla_o"] = QLinear.random(H, Hh * cfg.v_head, dq, dev, gen=gen)
+                L["k_b"] = torch.empty(Hh, cfg.kv_lora, cfg.qk_nope, dtype=torch.bfloat16, device=dev).normal_(0.0, 0.05, generator=gloc)
+                L["v_b"] = torch.empty(Hh, cfg.v_head, cfg.kv_lora, dtype=torch.bfloat16, device=dev).normal_(0.0, 0.05, generator=gloc)
+                L["mla_o"] = QLinear.random(H, Hh * cfg.v_head, dq, dev, gen=gloc)
             if cfg.is_moe_layer(i):
                 L["router"] = QLinear.random(cfg.n_routed, H, "f32", dev, std=0.1, gen=gen)
                 L["router_bias"] = rnd(cfg.n_routed, std=0.05) if cfg.router_bias else None
                 L["arena"] = None      # allocated below, once the non-expert footprint is known
             else:
-                L["mlp_gu"] = QLinear.random(2 * cfg.dense_inter, H, dq, dev, gen=gen)
-                L["mlp_down"] = QLinear.random(H, cfg.dense_inter, dq, dev, gen=gen)
+                L["mlp_gu"] = QLinear.random(2 * m.Fd, H, dq, dev, gen=gloc)
+                L["mlp_down"] = QLinear.random(H, m.Fd, dq, dev, gen=gloc)
             m.layers.append(L)
-        moe_layers = [L for L in m.layers if "arena" in L]
+        moe_layers = [(i, L) for i, L in enumerate(m.layers) if "arena" in L]
         if moe_layers:
             ef = expert_layout(eq, H, cfg.moe_inter)
             E_total = cfg.n_routed + cfg.n_shared
+            max_owned = max(sum(1 for e in range(E_total) if m.owns_expert(i, e)) for i, _ in moe_layers)
             if expert_slots == "auto":
                 free_b, _ = torch.cuda.mem_get_info(dev)
                 free_b += torch.cuda.memory_reserved(dev) - torch.cuda.memory_allocated(dev)
                 fit = int((free_b - reserve_bytes) // (ef.stride * len(moe_layers)))
-                n_slots = max(cfg.top_k + cfg.n_shared, min(E_total, fit))
+                n_slots = max(cfg.top_k // tp_size + cfg.n_shared, min(max_owned, fit))
             elif expert_slots is None:
-                n_slots = E_total
+                n_slots = max_owned
             else:
-                n_slots = min(E_total, int(expert_slots) + cfg.n_shared)
-            m.expert_slots = n_slots - cfg.n_shared
-            order = list(range(cfg.n_routed, E_total)) + list(range(cfg.n_routed))
-            so = torch.full((E_total,), -1, dtype=torch.int32)
-            for s_, e in enumerate(order[:n_slots]):
-                so[e] = s_
-            for L in moe_layers:
+                n_slots = min(max_owned, int(expert_slots) + cfg.n_shared)
+            m.expert_slots = n_slots
+            for i, L in moe_layers:
+                # resident order: this rank's shared expert first, then its routed experts by id
+                order = [e for e in range(cfg.n_routed, E_total) if m.owns_expert(i, e)] + [e for e in range(cfg.n_routed) if m.owns_expert(i, e)]
+                so = torch.full((E_total,), -1, dtype=torch.int32)
+                for s_, e in enumerate(order[:n_slots]):
+                    so[e] = s_
                 arena = ExpertArena(ef, n_slots, E_total, dev)
-                m._random_fill_arena(arena, eq, gen)
+                m._random_fill_arena(arena, eq, gloc)
                 arena.slot_of.copy_(so)
                 L["arena"] = arena
         m._finish()
@@ -520,8 +584,8 @@ class DeviceModel:
         P = cfg.index_kpool
         for i in range(cfg.n_layers):
             if cfg.is_kda_layer(i):
-                self.kda_state[i] = torch.zeros(n_slots, cfg.kda_heads, cfg.kda_head_dim, cfg.kda_head_dim, dtype=torch.float32, device=dev)
-                self.kda_conv[i] = torch.zeros(n_slots, 3, cfg.kda_heads * cfg.kda_head_dim, 3, dtype=torch.float32, device=dev)
+                self.kda_state[i] = torch.zeros(n_slots, self.Hk, cfg.kda_head_dim, cfg.kda_head_dim, dtype=torch.float32, device=dev)
+                self.kda_conv[i] = torch.zeros(n_slots, 3, self.Hk * cfg.kda_head_dim, 3, dtype=torch.float32, device=dev)
             else:
                 self.kv_cache[i] = torch.zeros(num_pages, self.page, self.kv_row_bytes, dtype=torch.uint8, device=dev)
                 if cfg.has_indexer and cfg.index_source_layer(i) == i:
@@ -548,9 +612,10 @@ class DeviceModel:
     def _ffn(self, i: int, L: dict, ws: Workspace, R: int):
         cfg = self.cfg
         if "arena" not in L:
-            L["mlp_gu"](ws.gu, ws.x, R, ldo=2 * cfg.dense_inter)
-            nat.call("lsb_swiglu", ws.act_d, ws.gu, R, cfg.dense_inter, cfg.swiglu_limit)
-            L["mlp_down"](ws.sub, ws.act_d, R)
+            L["mlp_gu"](ws.gu, ws.x, R, ldo=2 * self.Fd)
+            nat.call("lsb_swiglu", ws.act_d, ws.gu, R, self.Fd, cfg.swiglu_limit)
+            L["mlp_down"](ws.sub, ws.act_d, R, comm=self._cp)
+            self._reduce(ws, R)
             return
         arena: ExpertArena = L["arena"]
         S = ws.S
@@ -564,32 +629,34 @@ class DeviceModel:
         if fast_fp4 and R * S <= 72:
             # small batch: every (row, slot) pair streams its expert on its own - no grouping pass
             nat.call("lsb_moe_gateup", ws.x, arena.data, arena.slot_of, efp, ws.ids, None, None, None,
-                     ws.act, S, R * S, cfg.swiglu_limit, ws.miss)
+                     ws.act, S, R * S, cfg.swiglu_limit, ws.miss if self.tp_size == 1 else None)
             nat.call("lsb_moe_down", ws.act, arena.data, arena.slot_of, efp, ws.ids, None, None, None, ws.y, R * S)
         else:
             nat.call("lsb_moe_build_groups", ws.ids, R * S, E_total, ws.group_expert, ws.group_n, ws.group_pairs, ws.n_groups, ws.counts)
             mg = min(ws.max_groups, min(R * S, (R * S + 3) // 4 + E_total))
             nat.call("lsb_moe_gateup", ws.x, arena.data, arena.slot_of, efp, ws.group_expert, ws.group_n, ws.group_pairs, ws.n_groups,
-                     ws.act, S, mg, cfg.swiglu_limit, ws.miss)
+                     ws.act, S, mg, cfg.swiglu_limit, ws.miss if self.tp_size == 1 else None)
             nat.call("lsb_moe_down", ws.act, arena.data, arena.slot_of, efp, ws.group_expert, ws.group_n, ws.group_pairs, ws.n_groups,
                      ws.y, mg)
-        nat.call("lsb_moe_combine", ws.sub, ws.y, ws.wts, ws.ids, arena.slot_of, R, S, cfg.hidden, 0)
+        nat.call("lsb_moe_combine", ws.sub, ws.y, ws.wts, ws.ids, arena.slot_of, R, S, cfg.hidden, 0, self._cp)
+        self._reduce(ws, R)
 
     def _kda(self, i: int, L: dict, ws: Workspace, R: int, nseq: int):
         cfg = self.cfg
-        C = cfg.kda_heads * cfg.kda_head_dim
+        C = self.Hk * cfg.kda_head_dim
         lin: QLinear = L["kda_in"]
         lin(ws.proj, ws.x, R, ldo=self.max_proj)
-        nat.call("lsb_kda_forward", ws.proj, self.max_proj, 0, C, 2 * C, 3 * C, 3 * C + cfg.kda_heads,
-                 3 * C + cfg.kda_heads + cfg.kda_rank, cfg.kda_rank, L["kda_fb"], L["kda_gb"], L["kda_conv_q"], L["kda_conv_k"],
+        nat.call("lsb_kda_forward", ws.proj, self.max_proj, 0, C, 2 * C, 3 * C, 3 * C + self.Hk,
+                 3 * C + self.Hk + cfg.kda_rank, cfg.kda_rank, L["kda_fb"], L["kda_gb"], L["kda_conv_q"], L["kda_conv_k"],
                  L["kda_conv_v"], L["kda_a_exp"], L["kda_dt_bias"], L["kda_o_norm"], self.kda_state[i], self.kda_conv[i],
-                 ws.seq_row0, ws.seq_nrows, ws.seq_slot, ws.kda_out, nseq, cfg.kda_heads, cfg.kda_head_dim,
+                 ws.seq_row0, ws.seq_nrows, ws.seq_slot, ws.kda_out, nseq, self.Hk, cfg.kda_head_dim,
                  cfg.kda_head_dim ** -0.5, cfg.kda_lower_bound, cfg.rms_eps)
-        L["kda_o"](ws.sub, ws.kda_out, R)
+        L["kda_o"](ws.sub, ws.kda_out, R, comm=self._cp)
+        self._reduce(ws, R)
 
     def _mla(self, i: int, L: dict, ws: Workspace, R: int):
         cfg = self.cfg
-        Hh, dl, dr, dn, dv = cfg.n_heads, cfg.kv_lora, cfg.qk_rope, cfg.qk_nope, cfg.v_head
+        Hh, dl, dr, dn, dv = self.Hh, cfg.kv_lora, cfg.qk_rope, cfg.qk_nope, cfg.v_head
         ldp = self.max_proj
         off_qa, off_kv = 0, cfg.q_lora
         off_ik = off_kv + dl + dr
@@ -626,28 +693,30 @@ class DeviceModel:
                  sel_idx, sel_cnt, sel_ld, ws.o_lat, None, ws.o_part, ws.ml_part, R, Hh, dl, dr, self.page,
                  KV_FMT[self.kv_fmt], ws.NS, cfg.softmax_scale)
         nat.call("lsb_batched_gemv_bf16", ws.attn_v, ws.o_lat, L["v_b"], R, Hh, dv, dl, Hh * dl, dl, Hh * dv, dv, 0, None, None)
-        L["mla_o"](ws.sub, ws.attn_v, R)
+        L["mla_o"](ws.sub, ws.attn_v, R, comm=self._cp)
+        self._reduce(ws, R)
 
     def forward(self, ws: Workspace, R: int, nseq: int, logit_row0: int, n_logit_rows: int):
         """Run one step over the first ``R`` rows of the workspace (inputs already staged in
         ``ws``).  Writes logits for rows [logit_row0, logit_row0 + n_logit_rows)."""
         cfg = self.cfg
         H, n = cfg.hidden, cfg.hc_mult
+        self._fused = self.comm is not None and R in (1, 2, 4)
         if cfg.mhc:
             nat.call("lsb_embedding", ws.sub, None, self.embed, ws.tok, R, H, 0, cfg.vocab)
             for i, L in enumerate(self.layers):
                 fn, sc, base = L["hc_attn"]
                 nat.call("lsb_mhc_post_pre", ws.x, ws.resid, ws.sub, ws.post, ws.comb, fn, sc, base, L["attn_norm"], ws.part, R, H, n,
-                         0 if i == 0 else 1, cfg.hc_sinkhorn_iters, cfg.hc_eps, cfg.rms_eps, cfg.hc_post_mult)
+                         0 if i == 0 else 1, cfg.hc_sinkhorn_iters, cfg.hc_eps, cfg.rms_eps, cfg.hc_post_mult, self._cp)
                 if cfg.is_kda_layer(i):
                     self._kda(i, L, ws, R, nseq)
                 else:
                     self._mla(i, L, ws, R)
                 fn, sc, base = L["hc_ffn"]
                 nat.call("lsb_mhc_post_pre", ws.x, ws.resid, ws.sub, ws.post, ws.comb, fn, sc, base, L["ffn_norm"], ws.part, R, H, n,
-                         1, cfg.hc_sinkhorn_iters, cfg.hc_eps, cfg.rms_eps, cfg.hc_post_mult)
+                         1, cfg.hc_sinkhorn_iters, cfg.hc_eps, cfg.rms_eps, cfg.hc_post_mult, self._cp)
                 self._ffn(i, L, ws, R)
-            nat.call("lsb_mhc_contract_norm", ws.x, ws.resid, ws.sub, ws.post, ws.comb, self.final_norm, R, H, n, cfg.rms_eps)
+            nat.call("lsb_mhc_contract_norm", ws.x, ws.resid, ws.sub, ws.post, ws.comb, self.final_norm, R, H, n, cfg.rms_eps, self._cp)
         else:
             resid = ws.resid.view(-1)[: ws.R * H].view(ws.R, H)
             nat.call("lsb_embedding", resid, None, self.embed, ws.tok, R, H, 0, cfg.vocab)
@@ -657,15 +726,18 @@ class DeviceModel:
                     self._kda(i, L, ws, R, nseq)
                 else:
                     self._mla(i, L, ws, R)
-                nat.call("lsb_add_rmsnorm", ws.x, resid, ws.sub, L["ffn_norm"], R, H, cfg.rms_eps)
+                nat.call("lsb_add_rmsnorm", ws.x, resid, ws.sub, L["ffn_norm"], R, H, cfg.rms_eps, self._cp)
                 self._ffn(i, L, ws, R)
                 nxt = self.layers[i + 1]["attn_norm"] if i + 1 < cfg.n_layers else self.final_norm
-                nat.call("lsb_add_rmsnorm", ws.x, resid, ws.sub, nxt, R, H, cfg.rms_eps)
+                nat.call("lsb_add_rmsnorm", ws.x, resid, ws.sub, nxt, R, H, cfg.rms_eps, self._cp)
         xr = ws.x[logit_row0: logit_row0 + n_logit_rows]
         self.head(ws.logits, xr, n_logit_rows)
 
     def argmax(self, ws: Workspace, n_rows: int):
-        nat.call("lsb_argmax", ws.logits, self.cfg.vocab, n_rows, self.cfg.vocab, ws.amax_part, ws.out_tok, ws.out_val, 0)
+        """Greedy token per row; with a vocabulary-parallel head the per-rank winners are exchanged
+        in-kernel over NVLink (8 bytes per row per rank)."""
+        nat.call("lsb_argmax", ws.logits, self.V_local, n_rows, self.V_local, ws.amax_part, ws.out_tok, ws.out_val,
+                 self.tp_rank * self.V_local, self.comm_amax.ptr if self.comm_amax is not None else None)
 
     # ------------------------------------------------------------------ oracle support
     def effective_state_dict(self) -> Dict[str, torch.Tensor]:

@@ -1,0 +1,58 @@
+"""Multi-GPU worker (one process per GPU, launched by torch.distributed.run): tensor/expert-parallel
+engine with the in-kernel NVLink all-reduce vs the single-process fp32 oracle."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from layerstorm_b200.models.config import get_preset
+from layerstorm_b200.models.device_model import DeviceModel
+from layerstorm_b200.models.reference import Oracle
+from layerstorm_b200.models.weights import init_weights, round_weights_bf16
+from layerstorm_b200.parallel.symm import PeerComm
+from layerstorm_b200.runtime.engine import Engine
+
+
+def main():
+    name = sys.argv[1] if len(sys.argv) > 1 else "tiny-glm5-next"
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    cfg = get_preset(name)
+    w = round_weights_bf16(init_weights(cfg, 0))
+    m = DeviceModel.from_state_dict(cfg, w, dev, kv_fmt="bf16", page=16, tp_rank=rank, tp_size=world)
+    comm = PeerComm(4 * cfg.hidden, dev)
+    comm_amax = PeerComm(64, dev)
+    m.attach_comm(comm, comm_amax)
+    oracle = Oracle(cfg, w)
+    T = 24
+    ids = torch.randint(0, cfg.vocab, (T + 6,), generator=torch.Generator().manual_seed(5))
+    ref = oracle.forward(ids)
+    ok = True
+    for use_graph in (False, True):
+        eng = Engine(m, max_seqs=2, max_ctx=128, prefill_chunk=8, max_batch=2, use_graph=use_graph)
+        sid = eng.create_sequence()
+        nxt = eng.prefill(sid, ids[:T].tolist())                 # chunks of 8 rows: NCCL reduce path
+        good = nxt == int(ref[T - 1].argmax())
+        for j in range(6):                                       # single rows: fused in-kernel all-reduce
+            out = eng.decode([sid], [int(ids[T + j])])
+            good = good and out[0] == int(ref[T + j].argmax())
+        err = comm.error() or comm_amax.error()
+        if rank == 0:
+            print(f"graph={use_graph} tokens_match={good} comm_err={err} backend={comm.buf.backend} epochs={comm.epoch()}", flush=True)
+        ok = ok and good and err == 0
+        eng.free_sequence(sid)
+    flag = torch.tensor([1 if ok else 0], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        print("MGPU_OK" if int(flag[0]) == 1 else "MGPU_FAIL", flush=True)
+    dist.destroy_process_group()
+    sys.exit(0 if int(flag[0]) == 1 else 1)
+
+
+if __name__ == "__main__":
+    main()

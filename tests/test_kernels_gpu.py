@@ -36,18 +36,18 @@ def test_gemv_formats(M, fmt):
     out = torch.zeros(M, N, device=DEV)
     if fmt == "bf16":
         wq = w.to(torch.bfloat16)
-        nat.call("lsb_gemv_bf16", out, x, wq, None, M, N, K, K, K, N, 1.0, 0)
+        nat.call("lsb_gemv_bf16", out, x, wq, None, M, N, K, K, K, N, 1.0, 0, None)
         wd = wq.float()
     elif fmt == "f32":
         nat.call("lsb_gemv_f32w", out, x, w, None, M, N, K, K, K, N, 1.0, 0)
         wd = w
     elif fmt == "fp8":
         q, s = quant.quantize_fp8_block(w)
-        nat.call("lsb_gemv_fp8b", out, x, q, s, None, M, N, K, K, N, 1.0, 0)
+        nat.call("lsb_gemv_fp8b", out, x, q, s, None, M, N, K, K, N, 1.0, 0, None)
         wd = quant.dequantize_fp8_block(q, s)
     else:
         q, a, gs = quant.quantize_nvfp4(w)
-        nat.call("lsb_gemv_nvfp4", out, x, q, a, None, M, N, K, K, N, gs, 0)
+        nat.call("lsb_gemv_nvfp4", out, x, q, a, None, M, N, K, K, N, gs, 0, None)
         wd = quant.dequantize_nvfp4(q, a, gs, N, K)
         assert (wd - w).abs().max() < 0.3 * w.abs().max()
     torch.cuda.synchronize()
@@ -60,7 +60,7 @@ def test_gemv_bf16_out_and_bias():
     w = rnd(N, K, s=0.05, dtype=torch.bfloat16)
     b = rnd(N)
     out = torch.zeros(M, N, device=DEV, dtype=torch.bfloat16)
-    nat.call("lsb_gemv_bf16", out, x, w, b, M, N, K, K, K, N, 1.0, 1)
+    nat.call("lsb_gemv_bf16", out, x, w, b, M, N, K, K, K, N, 1.0, 1, None)
     torch.cuda.synchronize()
     close(out, x.float() @ w.float().T + b, 1e-2, 1e-2, "gemv bf16 out")
 
@@ -75,7 +75,7 @@ def test_rmsnorm_and_add():
     close(out, ref.rmsnorm(x.cpu(), w.cpu(), 1e-6), 1e-2, 1e-2, "rmsnorm")
     resid = rnd(R, D, seed=3)
     r0 = resid.clone()
-    nat.call("lsb_add_rmsnorm", out, resid, x, w, R, D, 1e-6)
+    nat.call("lsb_add_rmsnorm", out, resid, x, w, R, D, 1e-6, None)
     torch.cuda.synchronize()
     close(resid, r0 + x, 1e-6, 1e-6, "resid add")
     close(out, ref.rmsnorm((r0 + x).cpu(), w.cpu(), 1e-6), 1e-2, 1e-2, "add_rmsnorm")
@@ -92,7 +92,7 @@ def test_mhc_post_pre_and_contract():
     part = torch.zeros(R, H // 32, 25, device=DEV)
     x = torch.zeros(R, H, device=DEV, dtype=torch.bfloat16)
     args = (cfg.hc_sinkhorn_iters, cfg.hc_eps, cfg.rms_eps, cfg.hc_post_mult)
-    nat.call("lsb_mhc_post_pre", x, resid, emb, post, comb, fn, sc, base, nw, part, R, H, n, 0, *args)
+    nat.call("lsb_mhc_post_pre", x, resid, emb, post, comb, fn, sc, base, nw, part, R, H, n, 0, *args, None)
     torch.cuda.synchronize()
     r_ref = emb.cpu()[:, None, :].repeat(1, n, 1)
     p_ref, c_ref, x_ref = o.mhc_pre(r_ref, fn.cpu(), sc.cpu(), base.cpu(), nw.cpu())
@@ -101,7 +101,7 @@ def test_mhc_post_pre_and_contract():
     close(comb, c_ref, 1e-4, 1e-5, "comb")
     close(x, x_ref, 1e-2, 1e-2, "x")
     sub = rnd(R, H, seed=5)
-    nat.call("lsb_mhc_post_pre", x, resid, sub, post, comb, fn, sc, base, nw, part, R, H, n, 1, *args)
+    nat.call("lsb_mhc_post_pre", x, resid, sub, post, comb, fn, sc, base, nw, part, R, H, n, 1, *args, None)
     torch.cuda.synchronize()
     r2 = o.mhc_post(sub.cpu(), r_ref, p_ref, c_ref)
     p2, c2, x2 = o.mhc_pre(r2, fn.cpu(), sc.cpu(), base.cpu(), nw.cpu())
@@ -109,7 +109,7 @@ def test_mhc_post_pre_and_contract():
     close(comb, c2, 1e-4, 1e-5, "comb2")
     close(x, x2, 1e-2, 1e-2, "x2")
     sub2 = rnd(R, H, seed=6)
-    nat.call("lsb_mhc_contract_norm", x, resid, sub2, post, comb, nw, R, H, n, cfg.rms_eps)
+    nat.call("lsb_mhc_contract_norm", x, resid, sub2, post, comb, nw, R, H, n, cfg.rms_eps, None)
     torch.cuda.synchronize()
     fin = ref.rmsnorm(o.mhc_post(sub2.cpu(), r2, p2, c2).mean(1), nw.cpu(), cfg.rms_eps)
     close(x, fin, 1e-2, 1e-2, "contract")
@@ -140,7 +140,7 @@ def test_sampling_kernels():
     ids = torch.zeros(R, dtype=torch.int32, device=DEV)
     val = torch.zeros(R, device=DEV)
     logits[1, 17] = logits[1, 4000] = 50.0
-    nat.call("lsb_argmax", logits, V, R, V, part, ids, val, 0)
+    nat.call("lsb_argmax", logits, V, R, V, part, ids, val, 0, None)
     torch.cuda.synchronize()
     assert ids.cpu().tolist() == [int(t) for t in logits.cpu().argmax(-1)[:1]] + [17] + [int(t) for t in logits.cpu().argmax(-1)[2:]]
     close(val, logits.max(-1).values, 0, 0, "argmax value")

@@ -1,0 +1,23 @@
+"""Tensor/expert-parallel engine on 2 GPUs: fused in-kernel all-reduce (decode) and the NCCL path
+(prefill chunks) both reproduce the oracle's greedy tokens."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+@pytest.mark.parametrize("name", ["tiny-glm5-next", "tiny-mla-moe"])
+def test_two_rank_engine_matches_oracle(name):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29533", os.path.join(HERE, "mgpu_worker.py"), name]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert "MGPU_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]

@@ -19,7 +19,7 @@ ERR_NAMES = {ERR_ARG: "bad argument", ERR_NOT_FOUND: "not found", ERR_EXISTS: "e
              ERR_FORMAT: "bad format"}
 
 _DECL = re.compile(r'LSB_RT_API\s+([\w\s\*:]+?)\s+(lsb_\w+)\s*\(([^)]*)\)', re.S)
-_CT = {"int": ctypes.c_int, "void": None, "long long": ctypes.c_longlong, "unsigned long long": ctypes.c_ulonglong,
+_CT = {"int": ctypes.c_int, "void": None, "unsigned int": ctypes.c_uint, "char": ctypes.c_char, "bool": ctypes.c_bool, "long long": ctypes.c_longlong, "unsigned long long": ctypes.c_ulonglong,
        "float": ctypes.c_float, "double": ctypes.c_double, "uint64_t": ctypes.c_uint64, "int64_t": ctypes.c_int64,
        "uint32_t": ctypes.c_uint32, "size_t": ctypes.c_size_t}
 

@@ -1,0 +1,90 @@
+"""Checkpoint container and codec tests (CPU)."""
+import numpy as np
+import pytest
+import torch
+
+from layerstorm_b200 import build as _build
+
+_build.build_all(only="runtime")
+
+from layerstorm_b200.formats import gguf, quant, safetensors as st
+
+
+@pytest.mark.parametrize("tname,tol", [("F32", 0.0), ("F16", 1e-3), ("BF16", 8e-3), ("Q8_0", 1e-2), ("Q6_K", 3e-2), ("Q4_K", 0.12)])
+def test_ggml_quant_roundtrip(tname, tol):
+    t = gguf.GGML_TYPES[tname]
+    x = np.random.default_rng(0).standard_normal(4 * 256).astype(np.float32)
+    raw = gguf.quantize(t, x)
+    assert raw.size == gguf.nbytes_for(t, x.size)
+    y = gguf.dequantize(t, raw, x.size)
+    assert np.max(np.abs(x - y)) <= tol * np.max(np.abs(x)) + 1e-7
+
+
+def test_block_sizes_match_spec():
+    spec = {"Q2_K": (256, 84), "Q3_K": (256, 110), "Q4_K": (256, 144), "Q5_K": (256, 176), "Q6_K": (256, 210), "Q8_0": (32, 34), "MXFP4": (32, 17)}
+    for k, (e, b) in spec.items():
+        assert gguf.block_elems(gguf.GGML_TYPES[k]) == e and gguf.block_bytes(gguf.GGML_TYPES[k]) == b
+
+
+def test_hand_built_blocks_decode():
+    # Q5_K: d=1, dmin=0, all sub-scales 1, nibble 3 with the high bit set in the second half of each 64
+    blk = np.zeros(176, dtype=np.uint8)
+    blk[0:2] = np.frombuffer(np.float16(1.0).tobytes(), dtype=np.uint8)
+    blk[4:8] = 1          # scales for sub-blocks 0..3 (6-bit), mins stay 0
+    blk[12:16] = 1        # scales for sub-blocks 4..7 live in the low nibbles of bytes 8..11 of the 12-byte field
+    blk[48:176] = 0x33
+    blk[16:48] = 0xAA     # high bits: odd sub-blocks (u2) set
+    y = gguf.dequantize(gguf.GGML_TYPES["Q5_K"], blk, 256)
+    assert np.all(y[:32] == 3) and np.all(y[32:64] == 19)
+    # MXFP4: scale byte 128 -> 2^1, nibbles (1, 2) -> 0.5*2, 1.0*2
+    m = np.zeros(17, dtype=np.uint8); m[0] = 128; m[1:] = 0x21
+    y = gguf.dequantize(gguf.GGML_TYPES["MXFP4"], m, 32)
+    assert np.all(y[:16] == 1.0) and np.all(y[16:] == 2.0)
+    # Q2_K / Q3_K decode without error and stay finite
+    for name in ("Q2_K", "Q3_K"):
+        raw = np.random.default_rng(1).integers(0, 255, gguf.block_bytes(gguf.GGML_TYPES[name]), dtype=np.uint8)
+        raw[-2:] = np.frombuffer(np.float16(0.5).tobytes(), dtype=np.uint8)
+        if name == "Q2_K":
+            raw[-4:-2] = np.frombuffer(np.float16(0.25).tobytes(), dtype=np.uint8)
+        assert np.all(np.isfinite(gguf.dequantize(gguf.GGML_TYPES[name], raw, 256)))
+
+
+def test_gguf_container_roundtrip(tmp_path):
+    w = gguf.GgufWriter()
+    w.meta("general.architecture", "glm5_next")
+    w.meta("glm5_next.block_count", 45)
+    w.meta("glm5_next.attention.layer_norm_rms_epsilon", 1e-5)
+    a = np.random.default_rng(2).standard_normal((8, 512)).astype(np.float32)
+    b = np.random.default_rng(3).standard_normal((16,)).astype(np.float32)
+    w.add("blk.0.ffn_gate_exps.weight", a, gguf.GGML_TYPES["Q4_K"])
+    w.add("blk.0.attn_norm.weight", b, gguf.GGML_TYPES["F32"])
+    p = str(tmp_path / "m.gguf")
+    w.write(p)
+    r = gguf.GgufReader(p)
+    assert r.version == 3 and r.meta("general.architecture") == "glm5_next" and r.meta("glm5_next.block_count") == 45
+    assert abs(r.meta("glm5_next.attention.layer_norm_rms_epsilon") - 1e-5) < 1e-9
+    assert r.tensors["blk.0.ffn_gate_exps.weight"]["shape"] == (8, 512)
+    assert np.array_equal(r.get("blk.0.attn_norm.weight"), b)
+    assert np.max(np.abs(r.get("blk.0.ffn_gate_exps.weight") - a)) < 0.15 * np.max(np.abs(a))
+    with pytest.raises(Exception):
+        (tmp_path / "bad.gguf").write_bytes(b"NOPE" + b"\0" * 64)
+        gguf.GgufReader(str(tmp_path / "bad.gguf"))
+
+
+def test_safetensors_roundtrip_incl_nvfp4_quartet(tmp_path):
+    w = torch.randn(128, 64)
+    packed, atoms, gs = quant.quantize_nvfp4(w)
+    q8, sc = quant.quantize_fp8_block(w)
+    tensors = {"e.weight": packed, "e.weight_scale": atoms, "e.weight_scale_2": torch.tensor([gs]), "e.input_scale": torch.tensor([1.0]),
+               "a.weight": q8.view(torch.float8_e4m3fn), "a.weight_scale_inv": sc, "n.weight": torch.randn(7).to(torch.bfloat16)}
+    p = str(tmp_path / "m.safetensors")
+    st.write_safetensors(p, tensors, {"format": "pt"})
+    r = st.SafetensorsReader(p)
+    assert set(r.keys()) == set(tensors) and r.metadata["format"] == "pt"
+    for k, v in tensors.items():
+        got = r.get(k)
+        assert got.dtype == v.dtype and got.shape == v.shape and torch.equal(got.view(torch.uint8), v.view(torch.uint8))
+    d = quant.dequantize_nvfp4(r.get("e.weight"), r.get("e.weight_scale"), float(r.get("e.weight_scale_2")), 128, 64)
+    assert (d - w).abs().max() < 0.3 * w.abs().max()
+    assert (quant.dequantize_fp8_block(r.get("a.weight").view(torch.uint8), r.get("a.weight_scale_inv")) - w).abs().max() < 0.07 * w.abs().max()
+    r.close()

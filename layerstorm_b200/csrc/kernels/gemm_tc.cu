@@ -229,9 +229,10 @@ LSB_API int lsb_gemm_tc_workspace_floats(int M, int N, int K) {
 }
 
 // x bf16 [M, ldx], w bf16 [N, ldw], out fp32/bf16 [M, ldo]; K % 8 == 0; ldx, ldw % 8 == 0; pointers 16-byte aligned.
-// partial: fp32 scratch (lsb_gemm_tc_workspace_floats) or null to disable split-K.  err: int error word (0 = ok).
+// partial: fp32 scratch of partial_cap floats (split-K is limited to what fits) or null to disable split-K.
+// err: int error word (0 = ok; 1-3 = a bounded pipeline wait gave up).
 LSB_API int lsb_gemm_bf16_tc(void* out, const void* x, const void* w, const void* bias, int M, int N, int K, int ldx, int ldw,
-                             int ldo, int out_bf16, void* partial, void* err, void* stream) {
+                             int ldo, int out_bf16, void* partial, long long partial_cap, void* err, void* stream) {
     if (K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return -1;
     cudaStream_t st = (cudaStream_t)stream;
     int BN = 16;
@@ -251,6 +252,7 @@ LSB_API int lsb_gemm_bf16_tc(void* out, const void* x, const void* w, const void
         splits = (148 + tiles - 1) / tiles;
         if (splits > 16) splits = 16;
         if (splits > nkb / 4) splits = nkb / 4 > 0 ? nkb / 4 : 1;
+        while (splits > 1 && (long long)splits * M * N > partial_cap) --splits;
     }
     p.kb_per_split = (nkb + splits - 1) / splits;
     p.splits = (nkb + p.kb_per_split - 1) / p.kb_per_split;

@@ -76,8 +76,27 @@ def expert_layout(fmt: str, H: int, F: int) -> ExpertFmt:
     return ef
 
 
+class TcScratch:
+    """Per-device scratch of the tensor-core GEMM: split-K partials and the kernel's error word."""
+    _inst: Dict[int, "TcScratch"] = {}
+
+    def __init__(self, device):
+        self.cap = 16 << 20
+        self.partial = torch.empty(self.cap, dtype=torch.float32, device=device)
+        self.err = torch.zeros(1, dtype=torch.int32, device=device)
+
+    @classmethod
+    def get(cls, device) -> "TcScratch":
+        idx = torch.device(device).index or 0
+        if idx not in cls._inst:
+            cls._inst[idx] = cls(device)
+        return cls._inst[idx]
+
+
 class QLinear:
-    """A weight matrix [N, K] in a device storage format, applied to bf16 activations."""
+    """A weight matrix [N, K] in a device storage format, applied to bf16 activations.
+    Up to 4 rows (decode) stream the weights through the CUDA-core GEMV; larger row counts with
+    bf16 weights run on the tcgen05 tensor-core GEMM."""
 
     def __init__(self, fmt: str, N: int, K: int, w: torch.Tensor, scales: Optional[torch.Tensor] = None, alpha: float = 1.0):
         self.fmt, self.N, self.K, self.w, self.scales, self.alpha = fmt, N, K, w, scales, alpha
@@ -141,7 +160,10 @@ class QLinear:
         ob = 1 if out.dtype == torch.bfloat16 else 0
         if comm is not None and M not in (1, 2, 4):
             raise RuntimeError("the fused all-reduce epilogue covers single-pass shapes (1, 2 or 4 rows)")
-        if self.fmt == "bf16":
+        if self.fmt == "bf16" and M >= 8 and comm is None:
+            sc = TcScratch.get(self.w.device)
+            nat.call("lsb_gemm_bf16_tc", out, x, self.w, bias, M, self.N, self.K, ldx, self.K, ldo, ob, sc.partial, sc.cap, sc.err)
+        elif self.fmt == "bf16":
             nat.call("lsb_gemv_bf16", out, x, self.w, bias, M, self.N, self.K, ldx, self.K, ldo, 1.0, ob, comm)
         elif self.fmt == "f32":
             nat.call("lsb_gemv_f32w", out, x, self.w, bias, M, self.N, self.K, ldx, self.K, ldo, 1.0, ob)

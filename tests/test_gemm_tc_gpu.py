@@ -16,7 +16,7 @@ def run(M, N, K, out_bf16=False, bias=False, splitk=True, ldx=None, seed=0):
     out = torch.zeros(M, N, device="cuda", dtype=torch.bfloat16 if out_bf16 else torch.float32)
     part = torch.zeros(16 * M * N, device="cuda") if splitk else None
     err = torch.zeros(1, dtype=torch.int32, device="cuda")
-    nat.call("lsb_gemm_bf16_tc", out, x, w, b, M, N, K, ldx, K, N, int(out_bf16), part, err)
+    nat.call("lsb_gemm_bf16_tc", out, x, w, b, M, N, K, ldx, K, N, int(out_bf16), part, 16 * M * N if splitk else 0, err)
     torch.cuda.synchronize()
     assert int(err[0]) == 0, f"kernel reported wait timeout code {int(err[0])}"
     ref = x[:, :K].float() @ w.float().T

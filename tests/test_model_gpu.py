@@ -112,5 +112,19 @@ def test_chunking_invariance():
         sid = eng.create_sequence()
         nxt, lg = eng.prefill(sid, prompt, want_logits=True)
         outs.append((nxt, lg))
+    # token identity across execution shapes; logits agree to rounding (rows >= 8 run on the
+    # tensor-core GEMM, smaller chunks on the GEMV, whose summation orders differ)
     assert outs[0][0] == outs[1][0] == outs[2][0]
-    assert torch.equal(outs[0][1], outs[1][1]) and torch.equal(outs[0][1], outs[2][1])
+    for o in outs[1:]:
+        assert rel_err(o[1], outs[0][1]) < 2e-2
+
+
+def test_run_to_run_determinism():
+    cfg, m, _ = build("tiny-glm5-next", eq="nvfp4", kv="fp8")
+    prompt = torch.randint(0, cfg.vocab, (41,), generator=torch.Generator().manual_seed(9)).tolist()
+    res = []
+    for _ in range(2):
+        eng = Engine(m, max_seqs=1, max_ctx=128, prefill_chunk=16, max_batch=1, use_graph=False)
+        sid = eng.create_sequence()
+        res.append(eng.prefill(sid, prompt, want_logits=True))
+    assert res[0][0] == res[1][0] and torch.equal(res[0][1], res[1][1])

@@ -89,6 +89,13 @@ class Engine:
     def free_page_count(self) -> int:
         return self.pa.free_pages(0)
 
+    def seq_len(self, sid: int) -> int:
+        return self.seqs[sid].length
+
+    @property
+    def has_recurrent_state(self) -> bool:
+        return any(self.cfg.is_kda_layer(i) for i in range(self.cfg.n_layers))
+
     def fork_sequence(self, parent: int, prefix_len: Optional[int] = None) -> int:
         """Truncating fork: the child shares the parent's KV pages covering ``prefix_len`` tokens
         (reference counted, copy-on-write on the frontier page).  Recurrent (KDA) state cannot be

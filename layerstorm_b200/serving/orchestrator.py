@@ -1,0 +1,341 @@
+"""Request orchestrator: one generation loop on the main thread, fed by a thread-safe deque.
+
+``submit_request`` is called from the HTTP thread; ``run`` / ``step`` serve requests in FIFO
+order: prefix-cache lookup + fork, chunked prefill, then one of the decode arms (greedy,
+sampled, speculative with a draft proposer, guided).  Tokens stream to the caller through the
+request's ``on_token`` callback.  Pool exhaustion evicts a prefix holder and retries the same
+chunk; cancellation is checked between steps.
+Reference: Orchestrator in python/orchestrator/orchestrator.py:172-4257 (request deque,
+_serve_next, _generate, decode arms, SpecRoundGovernor, RequestStats, _with_pool_evict_retry).
+"""
+from __future__ import annotations
+
+import collections
+import threading
+import time
+from dataclasses import dataclass, field
+from typing import Callable, Deque, Dict, List, Optional, Sequence
+
+import torch
+
+from ..runtime.native import KvPoolExhausted
+from .prefix_cache import PrefixCache, PrefixCacheConfig
+
+
+@dataclass
+class SamplingParams:
+    max_tokens: int = 128
+    temperature: float = 0.0
+    top_k: int = 0
+    top_p: float = 1.0
+    seed: Optional[int] = None
+    stop_token_ids: List[int] = field(default_factory=list)
+    stop: List[str] = field(default_factory=list)
+    logprobs: int = 0
+    ignore_eos: bool = False
+
+    @property
+    def greedy(self) -> bool:
+        return self.temperature <= 0.0 or self.top_k == 1
+
+
+@dataclass
+class RequestStats:
+    prompt_tokens: int = 0
+    cached_tokens: int = 0
+    completion_tokens: int = 0
+    t_submit: float = 0.0
+    t_start: float = 0.0
+    t_first_token: float = 0.0
+    t_done: float = 0.0
+    spec_rounds: int = 0
+    spec_accepted: int = 0
+    pool_evict_retries: int = 0
+
+    @property
+    def ttft_s(self) -> float:
+        return self.t_first_token - self.t_start if self.t_first_token else 0.0
+
+    @property
+    def decode_tok_s(self) -> float:
+        dt = self.t_done - self.t_first_token
+        return (self.completion_tokens - 1) / dt if dt > 0 and self.completion_tokens > 1 else 0.0
+
+
+@dataclass
+class InferenceRequest:
+    request_id: str
+    prompt_ids: List[int]
+    params: SamplingParams = field(default_factory=SamplingParams)
+    on_token: Optional[Callable[[int, Optional[dict]], None]] = None      # (token id, logprob info)
+    on_done: Optional[Callable[["InferenceRequest"], None]] = None
+    logit_mask: Optional[Callable[[List[int]], Optional[torch.Tensor]]] = None   # guided decoding: allowed-token mask
+    output_ids: List[int] = field(default_factory=list)
+    finish_reason: Optional[str] = None
+    error: Optional[str] = None
+    cancelled: threading.Event = field(default_factory=threading.Event)
+    done: threading.Event = field(default_factory=threading.Event)
+    stats: RequestStats = field(default_factory=RequestStats)
+
+
+def splitmix64(seed: int, pos: int) -> int:
+    """Per-position sampling seed: the same request seed gives the same trajectory whether tokens
+    are produced one at a time or accepted in speculative batches."""
+    z = (seed + 0x9E3779B97F4A7C15 * (pos + 1)) & 0xFFFFFFFFFFFFFFFF
+    z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & 0xFFFFFFFFFFFFFFFF
+    z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & 0xFFFFFFFFFFFFFFFF
+    return z ^ (z >> 31)
+
+
+def target_probs(logits: torch.Tensor, p: SamplingParams) -> torch.Tensor:
+    """Target distribution after temperature / top-k / top-p."""
+    lg = logits.float() / max(p.temperature, 1e-6)
+    if p.top_k and p.top_k < lg.numel():
+        kth = torch.topk(lg, p.top_k).values[-1]
+        lg = torch.where(lg < kth, torch.full_like(lg, -float("inf")), lg)
+    pr = torch.softmax(lg, -1)
+    if 0.0 < p.top_p < 1.0:
+        sp, si = torch.sort(pr, descending=True)
+        keep = torch.cumsum(sp, 0) - sp < p.top_p
+        mask = torch.zeros_like(pr, dtype=torch.bool)
+        mask[si[keep]] = True
+        pr = torch.where(mask, pr, torch.zeros_like(pr))
+        pr = pr / pr.sum()
+    return pr
+
+
+def sample_from(pr: torch.Tensor, seed: int, pos: int) -> int:
+    g = torch.Generator().manual_seed(splitmix64(seed, pos) & 0x7FFFFFFFFFFFFFFF)
+    return int(torch.multinomial(pr, 1, generator=g))
+
+
+class SpecRoundGovernor:
+    """EMA of the per-round speculative gain (tokens x plain_ms - round_ms); drafting is suspended
+    while the gain is negative and probed again every ``probe_every`` rounds."""
+
+    def __init__(self, alpha: float = 0.2, probe_every: int = 16, enabled: bool = True):
+        self.alpha, self.probe_every, self.enabled = alpha, probe_every, enabled
+        self.gain_ema = 0.0
+        self.rounds = 0
+        self.plain_ms = None
+
+    def observe_plain(self, ms: float):
+        self.plain_ms = ms if self.plain_ms is None else (1 - self.alpha) * self.plain_ms + self.alpha * ms
+
+    def observe_round(self, tokens: int, round_ms: float):
+        if self.plain_ms is None:
+            return
+        gain = tokens * self.plain_ms - round_ms
+        self.gain_ema = (1 - self.alpha) * self.gain_ema + self.alpha * gain
+
+    def should_draft(self) -> bool:
+        self.rounds += 1
+        if not self.enabled or self.plain_ms is None:
+            return True
+        return self.gain_ema >= 0 or self.rounds % self.probe_every == 0
+
+
+class Orchestrator:
+    """Serves InferenceRequests on one engine.  ``draft`` is an optional proposer with
+    ``propose(context_ids, gamma) -> List[int]`` (speculative decoding)."""
+
+    def __init__(self, engine, eos_token_ids: Sequence[int] = (), prefix_cache: Optional[PrefixCacheConfig] = None,
+                 draft=None, speculation_depth: int = 0, tokenizer=None, governor: Optional[SpecRoundGovernor] = None):
+        self.engine = engine
+        self.eos = set(int(t) for t in eos_token_ids)
+        self.prefix = PrefixCache(engine, prefix_cache or PrefixCacheConfig())
+        self.draft, self.gamma = draft, speculation_depth if draft is not None else 0
+        self.tokenizer = tokenizer
+        self.governor = governor or SpecRoundGovernor(enabled=False)
+        self.queue: Deque[InferenceRequest] = collections.deque()
+        self.lock = threading.Lock()
+        self.wake = threading.Event()
+        self.stop_flag = threading.Event()
+        self.active: Optional[InferenceRequest] = None
+        self.served = 0
+
+    # ---- thread-safe entry points ----
+    def submit_request(self, req: InferenceRequest):
+        req.stats.t_submit = time.time()
+        with self.lock:
+            self.queue.append(req)
+        self.wake.set()
+
+    def cancel_request(self, request_id: str) -> bool:
+        with self.lock:
+            for r in list(self.queue):
+                if r.request_id == request_id:
+                    self.queue.remove(r)
+                    self._finish(r, "cancelled")
+                    return True
+            if self.active is not None and self.active.request_id == request_id:
+                self.active.cancelled.set()
+                return True
+        return False
+
+    def queued(self) -> int:
+        with self.lock:
+            return len(self.queue)
+
+    def shutdown(self):
+        self.stop_flag.set()
+        self.wake.set()
+
+    # ---- main loop ----
+    def run(self, idle_sleep_s: float = 0.0002):
+        while not self.stop_flag.is_set():
+            if not self.step():
+                self.wake.wait(timeout=0.05)
+                self.wake.clear()
+
+    def step(self) -> bool:
+        """Serve one queued request to completion; False when the queue is empty."""
+        with self.lock:
+            if not self.queue:
+                return False
+            req = self.queue.popleft()
+            self.active = req
+        try:
+            self._generate(req)
+        except Exception as exc:  # noqa: BLE001 - a failed request must not kill the serving loop
+            req.error = f"{type(exc).__name__}: {exc}"
+            self._finish(req, "error")
+        finally:
+            with self.lock:
+                self.active = None
+            self.served += 1
+        return True
+
+    def _finish(self, req: InferenceRequest, reason: str):
+        req.finish_reason = req.finish_reason or reason
+        req.stats.t_done = time.time()
+        req.stats.completion_tokens = len(req.output_ids)
+        req.done.set()
+        if req.on_done:
+            req.on_done(req)
+
+    def _with_pool_evict_retry(self, req: InferenceRequest, fn):
+        """Run ``fn``; on KV pool exhaustion evict one prefix holder and retry the identical step."""
+        while True:
+            try:
+                return fn()
+            except KvPoolExhausted:
+                if not self.prefix.evict_one():
+                    raise
+                req.stats.pool_evict_retries += 1
+
+    # ---- one request ----
+    def _emit(self, req: InferenceRequest, tok: int, logits: Optional[torch.Tensor]) -> bool:
+        """Append a token; returns True when generation must stop."""
+        p = req.params
+        if not req.output_ids:
+            req.stats.t_first_token = time.time()
+        req.output_ids.append(tok)
+        info = None
+        if p.logprobs and logits is not None:
+            lp = torch.log_softmax(logits.float(), -1)
+            top = torch.topk(lp, min(p.logprobs, lp.numel()))
+            info = {"logprob": float(lp[tok]), "top": [(int(i), float(v)) for v, i in zip(top.values, top.indices)]}
+        if req.on_token:
+            req.on_token(tok, info)
+        if (not p.ignore_eos and tok in self.eos) or tok in p.stop_token_ids:
+            req.finish_reason = "stop"
+            return True
+        if p.stop and self.tokenizer is not None:
+            text = self.tokenizer.decode(req.output_ids[-32:])
+            if any(s and s in text for s in p.stop):
+                req.finish_reason = "stop"
+                return True
+        if len(req.output_ids) >= p.max_tokens:
+            req.finish_reason = "length"
+            return True
+        return req.cancelled.is_set()
+
+    def _pick(self, req: InferenceRequest, logits: torch.Tensor, pos: int) -> int:
+        p = req.params
+        if req.logit_mask is not None:
+            mask = req.logit_mask(req.output_ids)
+            if mask is not None:
+                logits = torch.where(mask, logits, torch.full_like(logits, -float("inf")))
+        if p.greedy:
+            return int(torch.argmax(logits))
+        return sample_from(target_probs(logits, p), p.seed if p.seed is not None else 0, pos)
+
+    def _generate(self, req: InferenceRequest):
+        eng, p = self.engine, req.params
+        st = req.stats
+        st.t_start = time.time()
+        st.prompt_tokens = len(req.prompt_ids)
+        prompt = list(req.prompt_ids)
+        if not prompt:
+            raise ValueError("empty prompt")
+        sid, cached = self.prefix.fork_from(prompt)
+        if sid is None:
+            sid = self._with_pool_evict_retry(req, eng.create_sequence)
+            cached = 0
+        st.cached_tokens = cached
+        need_logits = (not p.greedy) or p.logprobs > 0 or req.logit_mask is not None
+        try:
+            out = self._with_pool_evict_retry(req, lambda: eng.prefill(sid, prompt[cached:], want_logits=need_logits))
+            self.prefix.register(sid, prompt)
+            tok, logits = out if need_logits else (out, None)
+            if need_logits:
+                tok = self._pick(req, logits, len(prompt))
+            if self._emit(req, tok, logits):
+                return self._finish(req, req.finish_reason or "cancelled")
+            if self.gamma > 0 and not need_logits:
+                self._decode_speculative(req, sid, tok)
+            else:
+                self._decode_plain(req, sid, tok, need_logits)
+            self._finish(req, req.finish_reason or ("cancelled" if req.cancelled.is_set() else "stop"))
+        finally:
+            eng.free_sequence(sid)
+
+    def _decode_plain(self, req: InferenceRequest, sid: int, tok: int, need_logits: bool):
+        eng = self.engine
+        while True:
+            t0 = time.time()
+            if need_logits:
+                outs, lg = self._with_pool_evict_retry(req, lambda: eng.decode([sid], [tok], return_logits=True))
+                logits = lg[0]
+                tok = self._pick(req, logits, len(req.prompt_ids) + len(req.output_ids))
+            else:
+                tok = self._with_pool_evict_retry(req, lambda: eng.decode([sid], [tok]))[0]
+                logits = None
+            self.governor.observe_plain((time.time() - t0) * 1e3)
+            if self._emit(req, tok, logits):
+                return
+
+    def _decode_speculative(self, req: InferenceRequest, sid: int, tok: int):
+        """Greedy lossless speculation: the draft proposes up to gamma tokens after ``tok``; one batched
+        target forward over [tok, d_0..d_{g-1}] gives the target's argmax at every position; the longest
+        agreeing prefix is accepted plus the target's own next token (correction or bonus)."""
+        eng = self.engine
+        recurrent = getattr(eng, "has_recurrent_state", False)
+        while True:
+            if recurrent or not self.governor.should_draft():
+                t0 = time.time()
+                tok = self._with_pool_evict_retry(req, lambda: eng.decode([sid], [tok]))[0]
+                self.governor.observe_plain((time.time() - t0) * 1e3)
+                if self._emit(req, tok, None):
+                    return
+                continue
+            t0 = time.time()
+            ctx = list(req.prompt_ids) + req.output_ids
+            draft = list(self.draft.propose(ctx, self.gamma))[: self.gamma]
+            base_len = eng.seq_len(sid)
+            rows = [tok] + draft
+            logits = self._with_pool_evict_retry(req, lambda: eng.forward_rows(sid, rows, commit=True))
+            target = [int(t) for t in torch.argmax(logits, -1)]
+            n_acc = 0
+            while n_acc < len(draft) and draft[n_acc] == target[n_acc]:
+                n_acc += 1
+            eng.rewind(sid, base_len + 1 + n_acc)          # keep tok + the accepted draft tokens
+            req.stats.spec_rounds += 1
+            req.stats.spec_accepted += n_acc
+            new = draft[:n_acc] + [target[n_acc]]
+            self.governor.observe_round(len(new), (time.time() - t0) * 1e3)
+            for t in new:
+                if self._emit(req, t, None):
+                    return
+            tok = new[-1]

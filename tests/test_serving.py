@@ -1,0 +1,159 @@
+"""Serving stack on the CPU null engine: orchestrator arms, prefix cache, parsers, guided JSON, HTTP API."""
+import json
+import threading
+
+import pytest
+import torch
+
+from layerstorm_b200 import build as _build
+
+_build.build_all(only="runtime")
+
+from layerstorm_b200.runtime.null_engine import NullEngine
+from layerstorm_b200.serving.guided import JsonPrefixValidator, make_logit_mask
+from layerstorm_b200.serving.orchestrator import InferenceRequest, Orchestrator, SamplingParams
+from layerstorm_b200.serving.parsers import (StreamingReasoningSplitter, get_reasoning_parser, get_tool_parser)
+from layerstorm_b200.serving.prefix_cache import PrefixCacheConfig
+from layerstorm_b200.serving.tokenizer import ChatTemplateRenderer, IncrementalDetokenizer, TokenizerWrapper
+
+
+def run(orch, prompt, **kw):
+    req = InferenceRequest("r", list(prompt), SamplingParams(**kw))
+    orch.submit_request(req)
+    assert orch.step()
+    assert req.done.is_set() and req.error is None, req.error
+    return req
+
+
+def test_greedy_matches_plain_loop_and_prefix_cache_is_invisible():
+    prompt = list(range(5, 205))
+    ref_eng = NullEngine()
+    sid = ref_eng.create_sequence()
+    t = ref_eng.prefill(sid, prompt)
+    ref = [t]
+    for _ in range(15):
+        t = ref_eng.decode([sid], [t])[0]
+        ref.append(t)
+    for cache in (False, True):
+        eng = NullEngine()
+        orch = Orchestrator(eng, prefix_cache=PrefixCacheConfig(enabled=cache, grid=64, min_prefix=64))
+        r1 = run(orch, prompt, max_tokens=16, ignore_eos=True)
+        r2 = run(orch, prompt[:150] + [9, 9, 9], max_tokens=4, ignore_eos=True)
+        r3 = run(orch, prompt, max_tokens=16, ignore_eos=True)
+        assert r1.output_ids == ref and r3.output_ids == ref
+        if cache:
+            assert r3.stats.cached_tokens == 192 and r2.stats.cached_tokens == 128
+            assert eng.prefill_tokens == 200 + (153 - 128) + (200 - 192)
+        else:
+            assert r3.stats.cached_tokens == 0
+    # every sequence is released (holders stay): free slots + holders == max_seqs
+    assert len(eng.free_slots) + orch.prefix.holders() == eng.max_seqs
+
+
+def test_speculative_is_lossless_and_pool_evict_retry():
+    prompt = list(range(3, 90))
+
+    class GoodThenBadDraft:
+        def __init__(self, eng): self.eng = eng
+        def propose(self, ctx, gamma):
+            out, c = [], list(ctx)
+            for i in range(gamma):
+                t = self.eng._next(c) if i < 3 else 7      # three right, then wrong
+                out.append(t); c.append(t)
+            return out
+
+    plain = run(Orchestrator(NullEngine()), prompt, max_tokens=24, ignore_eos=True).output_ids
+    eng = NullEngine()
+    orch = Orchestrator(eng, draft=GoodThenBadDraft(eng), speculation_depth=6)
+    r = run(orch, prompt, max_tokens=24, ignore_eos=True)
+    assert r.output_ids == plain
+    assert r.stats.spec_rounds > 0 and r.stats.spec_accepted >= 3 * (r.stats.spec_rounds - 1)
+    # KV pool too small for a holder + a new request: the holder is evicted and the step retried
+    eng = NullEngine(max_seqs=4, max_ctx=256, page=16, num_pages=12)
+    orch = Orchestrator(eng, prefix_cache=PrefixCacheConfig(grid=16, min_prefix=16))
+    run(orch, list(range(100, 200)), max_tokens=2, ignore_eos=True)
+    r = run(orch, list(range(300, 420)), max_tokens=2, ignore_eos=True)
+    assert r.stats.pool_evict_retries >= 1 and r.finish_reason == "length"
+
+
+def test_sampling_is_seeded_and_cancel():
+    orch = Orchestrator(NullEngine())
+    a = run(orch, [1, 2, 3], max_tokens=8, temperature=1.0, top_k=20, top_p=0.9, seed=11, ignore_eos=True)
+    b = run(orch, [1, 2, 3], max_tokens=8, temperature=1.0, top_k=20, top_p=0.9, seed=11, ignore_eos=True)
+    c = run(orch, [1, 2, 3], max_tokens=8, temperature=1.0, top_k=20, top_p=0.9, seed=12, ignore_eos=True)
+    assert a.output_ids == b.output_ids and a.output_ids != c.output_ids
+    req = InferenceRequest("x", [1, 2], SamplingParams(max_tokens=1000, ignore_eos=True))
+    req.on_token = lambda t, i: req.cancelled.set() if len(req.output_ids) >= 5 else None
+    orch.submit_request(req); orch.step()
+    assert req.finish_reason == "cancelled" and len(req.output_ids) == 5
+    q = InferenceRequest("q", [1], SamplingParams())
+    orch.submit_request(q)
+    assert orch.cancel_request("q") and q.finish_reason == "cancelled" and not orch.step()
+
+
+def test_parsers():
+    text = "I will call.<tool_call>get_weather\n<arg_key>city</arg_key>\n<arg_value>Paris</arg_value>\n<arg_key>days</arg_key>\n<arg_value>3</arg_value>\n</tool_call>"
+    rest, calls = get_tool_parser("glm47").parse(text)
+    assert rest == "I will call." and calls[0].name == "get_weather" and json.loads(calls[0].arguments) == {"city": "Paris", "days": 3}
+    ds = '<｜tool▁calls▁begin｜><｜tool▁call▁begin｜>search<｜tool▁sep｜>{"q": "b200"}<｜tool▁call▁end｜><｜tool▁calls▁end｜>'
+    rest, calls = get_tool_parser("deepseek_v4").parse(ds)
+    assert rest == "" and calls[0].name == "search" and json.loads(calls[0].arguments) == {"q": "b200"}
+    rp = get_reasoning_parser("glm45")
+    assert rp.parse("<think>hmm</think>\nanswer") == ("hmm", "answer") and rp.parse("plain") == (None, "plain")
+    sp = StreamingReasoningSplitter(rp)
+    r_all, c_all = "", ""
+    for piece in ["<th", "ink>rea", "son</thi", "nk>\nfi", "nal"]:
+        r, c = sp.push(piece); r_all += r; c_all += c
+    assert (r_all, c_all) == ("reason", "final")
+    with pytest.raises(ValueError):
+        get_tool_parser("nope")
+
+
+def test_guided_json_and_detokenizer():
+    v = JsonPrefixValidator()
+    assert v.feed_text('{"a": [1, 2.5e3, true, null, {"b": "x\\n"}], "c": {}}') and v.complete
+    for bad in ['{"a" 1}', '[1]', '{"a": 01}', '{,}', '{"a": tru }']:
+        assert not JsonPrefixValidator().feed_text(bad), bad
+    tok = TokenizerWrapper()
+    mask = make_logit_mask(tok, {"type": "json_object"})
+    eng = NullEngine(vocab=tok.vocab_size)
+    orch = Orchestrator(eng, eos_token_ids=tok.eos_token_ids, tokenizer=tok)
+    req = InferenceRequest("g", tok.encode("give json"), SamplingParams(max_tokens=200), logit_mask=mask)
+    orch.submit_request(req); orch.step()
+    out = tok.decode(req.output_ids)
+    vv = JsonPrefixValidator()
+    assert vv.feed_text(out)                      # always a valid JSON prefix
+    if req.finish_reason == "stop":
+        json.loads(out)
+    d = IncrementalDetokenizer(tok)
+    s = "".join(d.push(t) for t in tok.encode("héllo ✓ wörld"))
+    assert s == "héllo ✓ wörld"
+    assert "user" in ChatTemplateRenderer().render([{"role": "user", "content": "hi"}])
+
+
+def test_http_api():
+    from fastapi.testclient import TestClient
+    from layerstorm_b200.serving.http_server import LayerStormServer, ServerConfig
+    tok = TokenizerWrapper()
+    eng = NullEngine(vocab=tok.vocab_size)
+    orch = Orchestrator(eng, eos_token_ids=tok.eos_token_ids, tokenizer=tok)
+    th = threading.Thread(target=orch.run, daemon=True)
+    th.start()
+    srv = LayerStormServer(orch, tok, ServerConfig(model_name="m", max_queued_requests=2, reasoning_parser="glm45"))
+    c = TestClient(srv.app)
+    assert c.get("/health").json()["status"] == "ok"
+    assert c.get("/v1/models").json()["data"][0]["id"] == "m"
+    r = c.post("/v1/completions", json={"prompt": "hello", "max_tokens": 5, "ignore_eos": True, "logprobs": 2}).json()
+    assert r["usage"]["completion_tokens"] == 5 and r["choices"][0]["finish_reason"] == "length"
+    assert len(r["choices"][0]["logprobs"]["content"]) == 5
+    r = c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "hi"}], "max_tokens": 6, "ignore_eos": True}).json()
+    assert r["choices"][0]["message"]["role"] == "assistant" and r["usage"]["completion_tokens"] == 6
+    with c.stream("POST", "/v1/chat/completions", json={"messages": [{"role": "user", "content": "hi"}], "max_tokens": 6, "stream": True, "ignore_eos": True}) as s:
+        lines = [l for l in s.iter_lines() if l.startswith("data: ")]
+    assert lines[-1] == "data: [DONE]" and json.loads(lines[-2][6:])["choices"][0]["finish_reason"] == "length"
+    assert c.post("/v1/completions", json={"prompt": 5}).status_code == 400
+    assert c.post("/v1/chat/completions", json={"messages": []}).status_code == 400
+    srv.inflight = 3
+    r = c.post("/v1/completions", json={"prompt": "x"})
+    assert r.status_code == 503 and "Retry-After" in r.headers
+    orch.shutdown()

@@ -204,6 +204,7 @@ def main():
     dev_ms = sum(a.elapsed_time(b) for a, b in evs)
     clocks = sampler.stop()
     miss = int(eng.ws_decode[B].miss[0]) if hasattr(eng.ws_decode[B], "miss") else 0
+    comm_err = (model.comm.error() or model.comm_amax.error()) if model.comm is not None else 0
 
     if world > 1:
         t = torch.tensor([dev_ms, e2e_ms], device=dev)
@@ -222,7 +223,7 @@ def main():
                        "parallelism": f"tp{world}ep{world}" if world > 1 else "single-gpu",
                        "weights": f"experts {cfg.expert_quant}, attention {cfg.dense_quant}", "kv_cache": "fp8+bf16-rope, 64-token pages",
                        "l2": "inputs larger than L2 (each step streams ~20 GB of weights)",
-                       "resident_expert_slots_per_layer_per_gpu": slots, "routed_experts": cfg.n_routed, "expert_miss_flag": miss,
+                       "resident_expert_slots_per_layer_per_gpu": slots, "routed_experts": cfg.n_routed, "expert_miss_flag": miss, "comm_error_word": comm_err,
                        "collectives": ("fused in-kernel NVLink all-reduce (P2P stores + flags), argmax exchange; NCCL for prefill chunks only"
                                        if world > 1 else "none"),
                        "context_fill": "synthetic (uninitialised cache)" if args.synthetic_fill else "real chunked prefill"},

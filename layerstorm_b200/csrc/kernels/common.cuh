@@ -6,6 +6,7 @@
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <utility>
 
 #define LSB_API extern "C" __attribute__((visibility("default")))
 
@@ -121,5 +122,24 @@ __device__ __forceinline__ uint2 ldg_stream8(const void* p) {
 // wait for the previous kernel's memory before touching its outputs.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Kernel launch with programmatic dependent launch: the kernel may become resident while its
+// predecessor in the stream is still running and executes everything up to its
+// griddepcontrol.wait (weight prefetch, barrier set-up) under the predecessor's tail.  Every
+// kernel in this library reads its predecessor's output only after pdl_wait() and performs no
+// global store before it, which is what makes the early start safe.
+inline int& pdl_enabled_flag() { static int v = 1; return v; }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = pdl_enabled_flag() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 }  // namespace lsb

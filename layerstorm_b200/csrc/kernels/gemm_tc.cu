@@ -72,6 +72,7 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
     tc_fence_after();
     const uint32_t tmem_d = *tmem_holder;
     pdl_wait();
+    pdl_launch_dependents();
 
     if (warp == 0 && lane == 0) {
         // ---------------- TMA producer ----------------
@@ -149,6 +150,7 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
 __global__ void splitk_reduce_kernel(void* __restrict__ out, int ldo, const float* __restrict__ partial, const float* __restrict__ bias,
                                      int M, int N, int splits, int out_bf16) {
     pdl_wait();
+    pdl_launch_dependents();
     const int n = blockIdx.x * blockDim.x + threadIdx.x, m = blockIdx.y;
     if (n >= N) return;
     float a = 0.f;
@@ -216,7 +218,7 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const GemmTcP
     static bool attr = false;
     if (!attr) { cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM); attr = true; }
     dim3 grid((p.N + BM - 1) / BM, (p.M + BN - 1) / BN, p.splits);
-    gemm_tc_kernel<BN><<<grid, 192, C::SMEM, st>>>(mw, mx, p);
+    launch_pdl((gemm_tc_kernel<BN>), grid, 192, C::SMEM, st, mw, mx, p);
     return (int)cudaGetLastError();
 }
 
@@ -265,7 +267,7 @@ LSB_API int lsb_gemm_bf16_tc(void* out, const void* x, const void* w, const void
     }
     if (rc) return rc;
     if (p.splits > 1) {
-        splitk_reduce_kernel<<<dim3((N + 255) / 256, M), 256, 0, st>>>(out, ldo, (const float*)partial, (const float*)bias, M, N, p.splits, out_bf16);
+        launch_pdl((splitk_reduce_kernel), dim3((N + 255) / 256, M), 256, 0, st, out, ldo, (const float*)partial, (const float*)bias, M, N, p.splits, out_bf16);
         return (int)cudaGetLastError();
     }
     return 0;

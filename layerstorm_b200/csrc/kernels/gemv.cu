@@ -45,7 +45,16 @@ __global__ void __launch_bounds__(256) gemv_kernel(Mat mat, const bf16* __restri
     for (int m = 0; m < MT; ++m) acc0[m] = acc1[m] = 0.f;
     auto r0 = mat.row(n0);
     auto r1 = mat.row(n1);
+    {   // weights do not depend on the previous kernel: pull the head of both rows into L2 while it finishes
+        constexpr int E = decltype(r0)::EPL;
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+            const int k = (lane + 32 * it) * E;
+            if (k + E <= K) { r0.prefetch(k); r1.prefetch(k); }
+        }
+    }
     pdl_wait();
+    pdl_launch_dependents();
     unsigned next_epoch = 0;
     if (comm.nranks) next_epoch = *comm.epoch + 1;
     if (active) warp_dot2<decltype(r0), MT>(r0, r1, x, ldx, K, acc0, acc1);
@@ -88,6 +97,7 @@ __global__ void __launch_bounds__(256) gemv_smalln_kernel(Mat mat, const bf16* _
     auto r0 = mat.row(n0);
     auto r1 = mat.row(n1);
     pdl_wait();
+    pdl_launch_dependents();
     unsigned next_epoch = 0;
     if (comm.nranks) next_epoch = *comm.epoch + 1;
     warp_dot2<decltype(r0), MT>(r0, r1, x, ldx, K, acc0, acc1, threadIdx.x, 256);
@@ -132,10 +142,10 @@ static int launch_gemv(Mat mat, const bf16* x, int ldx, void* out, int ldo, int 
         void* op = reinterpret_cast<char*>(out) + (size_t)m0 * ldo * osz;
 #define LSB_GEMV_CASE(MT_)                                                                                                  \
     if (N <= 1024) {                                                                                                        \
-        if (out_bf16) gemv_smalln_kernel<Mat, MT_, true><<<(N + 1) / 2, 256, 0, st>>>(mat, xp, ldx, op, ldo, N, K, alpha, bias, comm); \
-        else gemv_smalln_kernel<Mat, MT_, false><<<(N + 1) / 2, 256, 0, st>>>(mat, xp, ldx, op, ldo, N, K, alpha, bias, comm);         \
-    } else if (out_bf16) gemv_kernel<Mat, MT_, true><<<grid, 256, 0, st>>>(mat, xp, ldx, op, ldo, N, K, alpha, bias, comm);           \
-    else gemv_kernel<Mat, MT_, false><<<grid, 256, 0, st>>>(mat, xp, ldx, op, ldo, N, K, alpha, bias, comm);
+        if (out_bf16) launch_pdl((gemv_smalln_kernel<Mat, MT_, true>), (N + 1) / 2, 256, 0, st, mat, xp, ldx, op, ldo, N, K, alpha, bias, comm); \
+        else launch_pdl((gemv_smalln_kernel<Mat, MT_, false>), (N + 1) / 2, 256, 0, st, mat, xp, ldx, op, ldo, N, K, alpha, bias, comm);         \
+    } else if (out_bf16) launch_pdl((gemv_kernel<Mat, MT_, true>), grid, 256, 0, st, mat, xp, ldx, op, ldo, N, K, alpha, bias, comm);           \
+    else launch_pdl((gemv_kernel<Mat, MT_, false>), grid, 256, 0, st, mat, xp, ldx, op, ldo, N, K, alpha, bias, comm);
         if (mt == 4) { LSB_GEMV_CASE(4) } else if (mt == 2) { LSB_GEMV_CASE(2) } else { LSB_GEMV_CASE(1) }
 #undef LSB_GEMV_CASE
         m0 += mt;

@@ -18,9 +18,12 @@
 
 namespace lsb {
 
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+
 struct WRowBf16 {
     static constexpr int EPL = 8;
     const bf16* w;
+    __device__ __forceinline__ void prefetch(int k) const { prefetch_l2(w + k); }
     __device__ __forceinline__ void load(int k, float* f) const {
         uint4 v = ldg_stream(w + k);
         unpack_bf16x8(v, f);
@@ -30,6 +33,7 @@ struct WRowBf16 {
 struct WRowF32 {
     static constexpr int EPL = 4;
     const float* w;
+    __device__ __forceinline__ void prefetch(int k) const { prefetch_l2(w + k); }
     __device__ __forceinline__ void load(int k, float* f) const {
         uint4 v = ldg_stream(w + k);
         f[0] = __uint_as_float(v.x); f[1] = __uint_as_float(v.y);
@@ -41,6 +45,7 @@ struct WRowFp8B {
     static constexpr int EPL = 16;
     const uint8_t* w;     // row start
     const float* scale;   // scale for column block 0 of this row; stride 1 per 128 cols
+    __device__ __forceinline__ void prefetch(int k) const { prefetch_l2(w + k); }
     __device__ __forceinline__ void load(int k, float* f) const {
         uint4 v = ldg_stream(w + k);
         const float s = __ldg(scale + (k >> 7));
@@ -62,6 +67,7 @@ struct WRowNvfp4 {
     const uint8_t* sf;   // base of the scale-atom array for this matrix
     int n;               // row index inside the matrix (selects the atom lane)
     int gtiles;          // ceil(G/4)
+    __device__ __forceinline__ void prefetch(int k) const { prefetch_l2(w + (k >> 1)); }
     __device__ __forceinline__ void load(int k, float* f) const {
         uint4 v = ldg_stream(w + (k >> 1));
         const int g = k >> 4;  // even

@@ -86,6 +86,7 @@ __global__ void __launch_bounds__(kID) indexer_k_append_kernel(IdxAppendParams p
     __shared__ float red[33];
     const int r = blockIdx.x, t = threadIdx.x;
     pdl_wait();
+    pdl_launch_dependents();
     const int seq = p.row_seq[r], pos = p.row_pos[r];
     if (seq < 0) return;
     const float* pr = p.proj + (size_t)r * p.ldp;
@@ -146,6 +147,7 @@ __global__ void __launch_bounds__(kID) indexer_q_prep_kernel(const bf16* __restr
     __shared__ float buf[kID];
     const int r = blockIdx.x, h = blockIdx.y, t = threadIdx.x;
     pdl_wait();
+    pdl_launch_dependents();
     if (h == 0 && P > 1 && row_seq[r] >= 0) {
         // publish this row's key | gate to the sequence's open-pool tail unless the pool is
         // completed by a later row of this same launch (then nobody will read it)
@@ -178,6 +180,7 @@ __global__ void __launch_bounds__(128) indexer_score_kernel(const bf16* __restri
     float* ws = reinterpret_cast<float*>(qs + IH * kID);       // [IH]
     const int r = blockIdx.y, t = threadIdx.x;
     pdl_wait();
+    pdl_launch_dependents();
     const int seq = row_seq[r];
     const int ne = seq < 0 ? 0 : n_entries[r];
     if ((int)(blockIdx.x * blockDim.x) >= ne) return;
@@ -231,6 +234,7 @@ __global__ void __launch_bounds__(1024) indexer_topk_kernel(const float* __restr
     __shared__ int s_need, s_base, s_eqbase;
     const int r = blockIdx.x, t = threadIdx.x;
     pdl_wait();
+    pdl_launch_dependents();
     const int len = row_seq[r] < 0 ? 0 : row_len[r];
     const int ne = row_seq[r] < 0 ? 0 : n_entries[r];
     const float* sc = scores + (size_t)r * ld_scores;
@@ -366,7 +370,7 @@ LSB_API int lsb_indexer_k_append(const void* proj, int ldp, int off_k, int off_g
     p.cache = (uint8_t*)cache; p.block_table = (const int*)block_table; p.max_pages = max_pages; p.page = page;
     p.tail = (const bf16*)tail; p.kstash = (bf16*)kstash; p.row_seq = (const int*)row_seq; p.row_pos = (const int*)row_pos; p.row_slot = (const int*)row_slot;
     p.P = P; p.ln_eps = ln_eps;
-    indexer_k_append_kernel<<<rows, kID, 0, (cudaStream_t)stream>>>(p);
+    launch_pdl((indexer_k_append_kernel), rows, kID, 0, (cudaStream_t)stream, p);
     LSB_CHECK_LAUNCH();
 }
 
@@ -374,7 +378,7 @@ LSB_API int lsb_indexer_q_prep(const void* qproj, int ldq, int off_q, const void
                                const void* inv_freq, const void* row_pos, void* q_idx, void* w_out, const void* kstash,
                                int off_gate, void* tail, const void* row_seq, const void* row_slot, int P, int rows, void* stream) {
     if (IH > kID) return -1;
-    indexer_q_prep_kernel<<<dim3(rows, IH), kID, 0, (cudaStream_t)stream>>>((const bf16*)qproj, ldq, off_q, (const float*)proj, ldp, off_w, IH, dr,
+    launch_pdl((indexer_q_prep_kernel), dim3(rows, IH), kID, 0, (cudaStream_t)stream, (const bf16*)qproj, ldq, off_q, (const float*)proj, ldp, off_w, IH, dr,
                                                                  (const float*)inv_freq, (const int*)row_pos, (bf16*)q_idx, (float*)w_out,
                                                                  (const bf16*)kstash, off_gate, (bf16*)tail, (const int*)row_seq,
                                                                  (const int*)row_slot, P, rows);
@@ -386,7 +390,7 @@ LSB_API int lsb_indexer_score(const void* q_idx, const void* w, int IH, const vo
                               int ld_scores, int rows, int max_entries, void* stream) {
     if (max_entries <= 0) return 0;
     dim3 grid((max_entries + 127) / 128, rows);
-    indexer_score_kernel<<<grid, 128, (size_t)IH * kID * 2 + IH * 4, (cudaStream_t)stream>>>((const bf16*)q_idx, (const float*)w, IH, (const uint8_t*)cache,
+    launch_pdl((indexer_score_kernel), grid, 128, (size_t)IH * kID * 2 + IH * 4, (cudaStream_t)stream, (const bf16*)q_idx, (const float*)w, IH, (const uint8_t*)cache,
                                                                                             (const int*)block_table, max_pages, page, (const int*)row_seq,
                                                                                             (const int*)n_entries, (float*)scores, ld_scores);
     LSB_CHECK_LAUNCH();
@@ -395,7 +399,7 @@ LSB_API int lsb_indexer_score(const void* q_idx, const void* w, int IH, const vo
 LSB_API int lsb_indexer_topk(const void* scores, int ld_scores, const void* n_entries, const void* row_len,
                              const void* row_seq, int budget, int P, void* sel_idx, void* sel_cnt, int sel_ld, int rows,
                              void* stream) {
-    indexer_topk_kernel<<<rows, 1024, 0, (cudaStream_t)stream>>>((const float*)scores, ld_scores, (const int*)n_entries, (const int*)row_len,
+    launch_pdl((indexer_topk_kernel), rows, 1024, 0, (cudaStream_t)stream, (const float*)scores, ld_scores, (const int*)n_entries, (const int*)row_len,
                                                                (const int*)row_seq, budget, P, (int*)sel_idx, (int*)sel_cnt, sel_ld);
     LSB_CHECK_LAUNCH();
 }

@@ -45,6 +45,7 @@ __global__ void __launch_bounds__(kD) kda_kernel(KdaParams p) {
     if (nrows <= 0) return;
     const int C = p.H * kD, ch = h * kD + t;
     pdl_wait();
+    pdl_launch_dependents();
     // state row
     float S[kD];
     float* sp = p.state + (((size_t)slot * p.H + h) * kD + t) * kD;
@@ -135,6 +136,6 @@ LSB_API int lsb_kda_forward(const void* proj, int ldp, int off_q, int off_k, int
     p.state = (float*)state; p.conv_state = (float*)conv_state; p.seq_row0 = (const int*)seq_row0;
     p.seq_nrows = (const int*)seq_nrows; p.seq_slot = (const int*)seq_slot; p.out = (bf16*)out; p.H = H;
     p.scale = scale; p.lower_bound = lower_bound; p.eps = eps;
-    kda_kernel<<<dim3(nseq, H), kD, 0, (cudaStream_t)stream>>>(p);
+    launch_pdl((kda_kernel), dim3(nseq, H), kD, 0, (cudaStream_t)stream, p);
     LSB_CHECK_LAUNCH();
 }

@@ -37,6 +37,7 @@ __global__ void mla_prep_kernel(const float* __restrict__ proj, int ldp, int off
     const int r = blockIdx.x, t = threadIdx.x;
     const float* pr = proj + (size_t)r * ldp;
     pdl_wait();
+    pdl_launch_dependents();
     if (q_lora > 0) {
         float ss = 0.f;
         for (int i = t; i < q_lora; i += blockDim.x) { const float v = pr[off_qa + i]; sm[i] = v; ss += v * v; }
@@ -87,6 +88,7 @@ __global__ void __launch_bounds__(256) batched_gemv_kernel(bf16* __restrict__ ou
     const int b = blockIdx.y;
     const int n0 = (blockIdx.x * 8 + warp) * 2;
     pdl_wait();
+    pdl_launch_dependents();
     if (blockIdx.x == 0 && dr > 0) {
         for (int m = 0; m < MT; ++m)
             for (int i = threadIdx.x; i < dr / 2; i += blockDim.x) {
@@ -145,6 +147,7 @@ __global__ void __launch_bounds__(256) mla_decode_kernel(MlaDecodeParams p) {
     const int r = blockIdx.x, hg = blockIdx.y, sp = blockIdx.z;
     const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
     pdl_wait();
+    pdl_launch_dependents();
     const int seq = p.row_seq[r];
     int n = p.sel_idx ? p.sel_cnt[r] : p.row_len[r];
     if (seq < 0) n = 0;
@@ -301,6 +304,7 @@ __global__ void __launch_bounds__(128) mla_combine_kernel(bf16* __restrict__ out
     __shared__ float s_invL, s_lse;
     const int r = blockIdx.x, h = blockIdx.y, t = threadIdx.x;
     pdl_wait();
+    pdl_launch_dependents();
     const float* ml = ml_part + ((size_t)r * H + h) * NS * 2;
     if (t < 32) {
         const float m = t < NS ? ml[2 * t] : -INFINITY;
@@ -344,7 +348,7 @@ LSB_API int lsb_mla_prep(const void* proj, int ldp, int off_qa, int q_lora, int 
                          const void* block_table, int max_pages, const void* row_seq, const void* row_pos, int rows,
                          int page, int kv_fmt, float eps, void* stream) {
     const int n = q_lora > dl + dr ? q_lora : dl + dr;
-    mla_prep_kernel<<<rows, 256, (size_t)n * 4, (cudaStream_t)stream>>>((const float*)proj, ldp, off_qa, q_lora, off_kv, dl, dr,
+    launch_pdl((mla_prep_kernel), rows, 256, (size_t)n * 4, (cudaStream_t)stream, (const float*)proj, ldp, off_qa, q_lora, off_kv, dl, dr,
                                                                       (const float*)qa_norm_w, (const float*)kv_norm_w,
                                                                       (const float*)inv_freq, (bf16*)q_c, (uint8_t*)cache,
                                                                       (const int*)block_table, max_pages, (const int*)row_seq,
@@ -364,9 +368,9 @@ LSB_API int lsb_batched_gemv_bf16(void* out, const void* x, const void* w, int M
         bf16* o = (bf16*)out + (size_t)m0 * os_m;
         const bf16* xp = (const bf16*)x + (size_t)m0 * xs_m;
 #define ARGS o, xp, (const bf16*)w, N, K, xs_m, xs_b, os_m, os_b, dr, (const float*)inv_freq, (const int*)row_pos, m0
-        if (mt == 4) batched_gemv_kernel<4><<<grid, 256, 0, st>>>(ARGS);
-        else if (mt == 2) batched_gemv_kernel<2><<<grid, 256, 0, st>>>(ARGS);
-        else batched_gemv_kernel<1><<<grid, 256, 0, st>>>(ARGS);
+        if (mt == 4) launch_pdl((batched_gemv_kernel<4>), grid, 256, 0, st, ARGS);
+        else if (mt == 2) launch_pdl((batched_gemv_kernel<2>), grid, 256, 0, st, ARGS);
+        else launch_pdl((batched_gemv_kernel<1>), grid, 256, 0, st, ARGS);
 #undef ARGS
         m0 += mt;
     }
@@ -396,7 +400,7 @@ LSB_API int lsb_mla_decode(const void* q, const void* cache, const void* block_t
         cudaFuncSetAttribute(mla_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         attr_set = true;
     }
-    mla_decode_kernel<<<dim3(R, (H + kHG - 1) / kHG, NS), 256, smem, st>>>(p);
-    mla_combine_kernel<<<dim3(R, H), 128, 0, st>>>((bf16*)out, (float*)lse, (const float*)o_part, (const float*)ml_part, H, NS, dl);
+    launch_pdl((mla_decode_kernel), dim3(R, (H + kHG - 1) / kHG, NS), 256, smem, st, p);
+    launch_pdl((mla_combine_kernel), dim3(R, H), 128, 0, st, (bf16*)out, (float*)lse, (const float*)o_part, (const float*)ml_part, H, NS, dl);
     LSB_CHECK_LAUNCH();
 }

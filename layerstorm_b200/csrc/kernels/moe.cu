@@ -31,6 +31,7 @@ __global__ void __launch_bounds__(32) router_topk_kernel(const float* __restrict
     const int r = blockIdx.x, lane = threadIdx.x;
     const float* lg = logits + (size_t)r * ld_logits;
     pdl_wait();
+    pdl_launch_dependents();
     float mx = -INFINITY;
     if (scoring == kScoreSoftmax) {
         for (int e = lane; e < E; e += 32) mx = fmaxf(mx, lg[e]);
@@ -130,6 +131,7 @@ __global__ void moe_build_groups_kernel(const int* __restrict__ ids, int npairs,
                                         int* __restrict__ group_n, int* __restrict__ group_pairs, int* __restrict__ n_groups,
                                         int* __restrict__ counts /* scratch [E_total*2+1] */) {
     pdl_wait();
+    pdl_launch_dependents();
     int* cnt = counts;             // [E_total]
     int* gbase = counts + E_total; // [E_total+1] first group index per expert
     for (int e = threadIdx.x; e < E_total; e += blockDim.x) cnt[e] = 0;
@@ -202,6 +204,7 @@ __global__ void __launch_bounds__(256) moe_gateup_kernel(const bf16* __restrict_
                                                          const int* __restrict__ group_pairs, const int* __restrict__ n_groups,
                                                          bf16* __restrict__ act, int S, float limit, int* __restrict__ miss_flag) {
     pdl_wait();
+    pdl_launch_dependents();
     const int g = blockIdx.y;
     if (g >= n_groups[0]) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -262,6 +265,7 @@ __global__ void __launch_bounds__(256) moe_down_kernel(const bf16* __restrict__ 
                                                        const int* __restrict__ group_pairs, const int* __restrict__ n_groups,
                                                        float* __restrict__ y) {
     pdl_wait();
+    pdl_launch_dependents();
     const int g = blockIdx.y;
     if (g >= n_groups[0]) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -327,6 +331,7 @@ __global__ void __launch_bounds__(256) moe_gateup_fp4_kernel(const bf16* __restr
     __half* xs = reinterpret_cast<__half*>(smraw);
     __shared__ const bf16* rows[4];
     pdl_wait();
+    pdl_launch_dependents();
     const int g = blockIdx.y;
     if (g >= (n_groups ? n_groups[0] : (int)gridDim.y)) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -383,6 +388,7 @@ __global__ void __launch_bounds__(256) moe_down_fp4_kernel(const bf16* __restric
     __half* xs = reinterpret_cast<__half*>(smraw);
     __shared__ const bf16* rows[4];
     pdl_wait();
+    pdl_launch_dependents();
     const int g = blockIdx.y;
     if (g >= (n_groups ? n_groups[0] : (int)gridDim.y)) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -433,6 +439,7 @@ __global__ void moe_combine_kernel(float* __restrict__ out, const float* __restr
                                    PeerComm comm) {
     constexpr int kMaxS = 16;
     pdl_wait();
+    pdl_launch_dependents();
     const int r = blockIdx.y;
     const int h = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
     unsigned next_epoch = 0;
@@ -473,6 +480,7 @@ __global__ void moe_combine_kernel(float* __restrict__ out, const float* __restr
 // Dense SwiGLU on a fused [rows, 2F] fp32 projection (gate | up) -> bf16 [rows, F].
 __global__ void swiglu_kernel(bf16* __restrict__ out, const float* __restrict__ gu, int F, float limit) {
     pdl_wait();
+    pdl_launch_dependents();
     const int r = blockIdx.y, f = blockIdx.x * blockDim.x + threadIdx.x;
     if (f >= F) return;
     float g = gu[(size_t)r * 2 * F + f], u = gu[(size_t)r * 2 * F + F + f];
@@ -488,7 +496,7 @@ LSB_API int lsb_router_topk(const void* logits, const void* bias, void* ids, voi
                             int n_group, int topk_group, int scoring, int norm_topk, float scale, int n_shared,
                             int ld_logits, void* stream) {
     if (topk > 32 || n_group > 64 || E > 4096 || n_shared > 32) return -1;
-    router_topk_kernel<<<rows, 32, (size_t)(2 * E + 64) * 4, (cudaStream_t)stream>>>((const float*)logits, (const float*)bias, (int*)ids,
+    launch_pdl((router_topk_kernel), rows, 32, (size_t)(2 * E + 64) * 4, (cudaStream_t)stream, (const float*)logits, (const float*)bias, (int*)ids,
                                                                          (float*)wts, E, topk, n_group, topk_group, scoring,
                                                                          norm_topk, scale, n_shared, ld_logits);
     LSB_CHECK_LAUNCH();
@@ -496,7 +504,7 @@ LSB_API int lsb_router_topk(const void* logits, const void* bias, void* ids, voi
 
 LSB_API int lsb_moe_build_groups(const void* ids, int npairs, int E_total, void* group_expert, void* group_n,
                                  void* group_pairs, void* n_groups, void* counts, void* stream) {
-    moe_build_groups_kernel<<<1, 512, 0, (cudaStream_t)stream>>>((const int*)ids, npairs, E_total, (int*)group_expert, (int*)group_n,
+    launch_pdl((moe_build_groups_kernel), 1, 512, 0, (cudaStream_t)stream, (const int*)ids, npairs, E_total, (int*)group_expert, (int*)group_n,
                                                                (int*)group_pairs, (int*)n_groups, (int*)counts);
     LSB_CHECK_LAUNCH();
 }
@@ -517,10 +525,10 @@ LSB_API int lsb_moe_gateup(const void* x, const void* arena, const void* slot_of
             attr = true;
         }
         if (!group_n)
-            moe_gateup_fp4_kernel<1><<<g2, 256, (size_t)ef.H * 2 + 2 * (ef.H / 64) * 68, st>>>((const bf16*)x, (const uint8_t*)arena, (const int*)slot_of, ef, (const int*)group_expert,
+            launch_pdl((moe_gateup_fp4_kernel<1>), g2, 256, (size_t)ef.H * 2 + 2 * (ef.H / 64) * 68, st, (const bf16*)x, (const uint8_t*)arena, (const int*)slot_of, ef, (const int*)group_expert,
                                                                         nullptr, nullptr, nullptr, (bf16*)act, S, limit, (int*)miss_flag);
         else
-            moe_gateup_fp4_kernel<4><<<g2, 256, (size_t)ef.H * 8 + 2 * (ef.H / 64) * 68, st>>>((const bf16*)x, (const uint8_t*)arena, (const int*)slot_of, ef, (const int*)group_expert,
+            launch_pdl((moe_gateup_fp4_kernel<4>), g2, 256, (size_t)ef.H * 8 + 2 * (ef.H / 64) * 68, st, (const bf16*)x, (const uint8_t*)arena, (const int*)slot_of, ef, (const int*)group_expert,
                                                                         (const int*)group_n, (const int*)group_pairs, (const int*)n_groups, (bf16*)act, S, limit,
                                                                         (int*)miss_flag);
         LSB_CHECK_LAUNCH();
@@ -529,9 +537,9 @@ LSB_API int lsb_moe_gateup(const void* x, const void* arena, const void* slot_of
     dim3 grid((ef.F + 7) / 8, max_groups);
 #define ARGS (const bf16*)x, (const uint8_t*)arena, (const int*)slot_of, ef, (const int*)group_expert, (const int*)group_n, \
              (const int*)group_pairs, (const int*)n_groups, (bf16*)act, S, limit, (int*)miss_flag
-    if (ef.fmt == 0) moe_gateup_kernel<0><<<grid, 256, 0, st>>>(ARGS);
-    else if (ef.fmt == 1) moe_gateup_kernel<1><<<grid, 256, 0, st>>>(ARGS);
-    else if (ef.fmt == 2) moe_gateup_kernel<2><<<grid, 256, 0, st>>>(ARGS);
+    if (ef.fmt == 0) launch_pdl((moe_gateup_kernel<0>), grid, 256, 0, st, ARGS);
+    else if (ef.fmt == 1) launch_pdl((moe_gateup_kernel<1>), grid, 256, 0, st, ARGS);
+    else if (ef.fmt == 2) launch_pdl((moe_gateup_kernel<2>), grid, 256, 0, st, ARGS);
     else return -1;
 #undef ARGS
     LSB_CHECK_LAUNCH();
@@ -551,10 +559,10 @@ LSB_API int lsb_moe_down(const void* act, const void* arena, const void* slot_of
             attr = true;
         }
         if (!group_n)
-            moe_down_fp4_kernel<1><<<g2, 256, (size_t)ef.F * 2 + (ef.F / 64) * 132, st>>>((const bf16*)act, (const uint8_t*)arena, (const int*)slot_of, ef, (const int*)group_expert,
+            launch_pdl((moe_down_fp4_kernel<1>), g2, 256, (size_t)ef.F * 2 + (ef.F / 64) * 132, st, (const bf16*)act, (const uint8_t*)arena, (const int*)slot_of, ef, (const int*)group_expert,
                                                                       nullptr, nullptr, nullptr, (float*)y);
         else
-            moe_down_fp4_kernel<4><<<g2, 256, (size_t)ef.F * 8 + (ef.F / 64) * 132, st>>>((const bf16*)act, (const uint8_t*)arena, (const int*)slot_of, ef, (const int*)group_expert,
+            launch_pdl((moe_down_fp4_kernel<4>), g2, 256, (size_t)ef.F * 8 + (ef.F / 64) * 132, st, (const bf16*)act, (const uint8_t*)arena, (const int*)slot_of, ef, (const int*)group_expert,
                                                                       (const int*)group_n, (const int*)group_pairs, (const int*)n_groups, (float*)y);
         LSB_CHECK_LAUNCH();
     }
@@ -562,9 +570,9 @@ LSB_API int lsb_moe_down(const void* act, const void* arena, const void* slot_of
     dim3 grid((ef.H + 15) / 16, max_groups);
 #define ARGS (const bf16*)act, (const uint8_t*)arena, (const int*)slot_of, ef, (const int*)group_expert, (const int*)group_n, \
              (const int*)group_pairs, (const int*)n_groups, (float*)y
-    if (ef.fmt == 0) moe_down_kernel<0><<<grid, 256, 0, st>>>(ARGS);
-    else if (ef.fmt == 1) moe_down_kernel<1><<<grid, 256, 0, st>>>(ARGS);
-    else if (ef.fmt == 2) moe_down_kernel<2><<<grid, 256, 0, st>>>(ARGS);
+    if (ef.fmt == 0) launch_pdl((moe_down_kernel<0>), grid, 256, 0, st, ARGS);
+    else if (ef.fmt == 1) launch_pdl((moe_down_kernel<1>), grid, 256, 0, st, ARGS);
+    else if (ef.fmt == 2) launch_pdl((moe_down_kernel<2>), grid, 256, 0, st, ARGS);
     else return -1;
 #undef ARGS
     LSB_CHECK_LAUNCH();
@@ -577,13 +585,13 @@ LSB_API int lsb_moe_combine(void* out, const void* y, const void* wts, const voi
     if (comm) pc = *reinterpret_cast<const PeerComm*>(comm);
     if (H % 4 || S > 16) return -1;
     dim3 grid((H / 4 + 127) / 128, rows);
-    moe_combine_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>((float*)out, (const float*)y, (const float*)wts, (const int*)ids,
+    launch_pdl((moe_combine_kernel), grid, 128, 0, (cudaStream_t)stream, (float*)out, (const float*)y, (const float*)wts, (const int*)ids,
                                                              (const int*)slot_of, S, H, accumulate, pc);
     LSB_CHECK_LAUNCH();
 }
 
 LSB_API int lsb_swiglu(void* out, const void* gu, int rows, int F, float limit, void* stream) {
     dim3 grid((F + 255) / 256, rows);
-    swiglu_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((bf16*)out, (const float*)gu, F, limit);
+    launch_pdl((swiglu_kernel), grid, 256, 0, (cudaStream_t)stream, (bf16*)out, (const float*)gu, F, limit);
     LSB_CHECK_LAUNCH();
 }

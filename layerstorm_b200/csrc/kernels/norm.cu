@@ -30,6 +30,7 @@ __global__ void rmsnorm_kernel(bf16* __restrict__ out, const TIn* __restrict__ x
     const int r = blockIdx.x;
     const TIn* xr = x + (size_t)r * ldx;
     pdl_wait();
+    pdl_launch_dependents();
     unsigned epoch = 0;
     if (comm.nranks) { epoch = *comm.epoch; comm_wait(comm, epoch); }
     float ss = 0.f;
@@ -79,6 +80,7 @@ __global__ void __launch_bounds__(128) mhc_post_partial_kernel(float* __restrict
         for (int j = 0; j < kHcMax; ++j) f[i][j] = (o < nout && j < n) ? __ldg(fn + ((size_t)o * n + j) * hidden + h) : 0.f;
     }
     pdl_wait();
+    pdl_launch_dependents();
     float res[kHcMax];
     float* rp = residual + (size_t)r * n * hidden;
     float xv;
@@ -140,6 +142,7 @@ __global__ void __launch_bounds__(512) mhc_finalize_kernel(bf16* __restrict__ ou
     extern __shared__ float row[];
     const int r = blockIdx.x, t = threadIdx.x;
     pdl_wait();
+    pdl_launch_dependents();
     {
         const int o = t >> 4, sub = t & 15;
         float a = 0.f;
@@ -234,6 +237,7 @@ __global__ void mhc_contract_norm_kernel(bf16* __restrict__ out, const float* __
     extern __shared__ float row[];
     const int r = blockIdx.x;
     pdl_wait();
+    pdl_launch_dependents();
     unsigned epoch = 0;
     if (comm.nranks) { epoch = *comm.epoch; comm_wait(comm, epoch); }
     const float* rp = residual + (size_t)r * n * hidden;
@@ -276,9 +280,9 @@ LSB_API int lsb_rmsnorm(void* out, const void* x, const void* w, int rows, int d
     const int thr = dim >= 2048 ? 512 : 256;
     const size_t sm = (size_t)dim * 4;
     if (x_is_f32)
-        rmsnorm_kernel<float, false><<<rows, thr, sm, st>>>((bf16*)out, (const float*)x, nullptr, (const float*)w, dim, ldx, ldo, 0, eps, (float*)out_f32, nocomm);
+        launch_pdl((rmsnorm_kernel<float, false>), rows, thr, sm, st, (bf16*)out, (const float*)x, nullptr, (const float*)w, dim, ldx, ldo, 0, eps, (float*)out_f32, nocomm);
     else
-        rmsnorm_kernel<bf16, false><<<rows, thr, sm, st>>>((bf16*)out, (const bf16*)x, nullptr, (const float*)w, dim, ldx, ldo, 0, eps, (float*)out_f32, nocomm);
+        launch_pdl((rmsnorm_kernel<bf16, false>), rows, thr, sm, st, (bf16*)out, (const bf16*)x, nullptr, (const float*)w, dim, ldx, ldo, 0, eps, (float*)out_f32, nocomm);
     LSB_CHECK_LAUNCH();
 }
 
@@ -287,7 +291,7 @@ LSB_API int lsb_rmsnorm(void* out, const void* x, const void* w, int rows, int d
 LSB_API int lsb_add_rmsnorm(void* out, void* resid, const void* x, const void* w, int rows, int dim, float eps, const void* comm,
                             void* stream) {
     const int thr = dim >= 2048 ? 512 : 256;
-    rmsnorm_kernel<float, true><<<rows, thr, (size_t)dim * 4, (cudaStream_t)stream>>>((bf16*)out, (const float*)x, (float*)resid,
+    launch_pdl((rmsnorm_kernel<float, true>), rows, thr, (size_t)dim * 4, (cudaStream_t)stream, (bf16*)out, (const float*)x, (float*)resid,
                                                                                    (const float*)w, dim, dim, dim, dim, eps, nullptr, comm_from_host(comm));
     LSB_CHECK_LAUNCH();
 }
@@ -302,9 +306,9 @@ LSB_API int lsb_mhc_post_pre(void* out_x, void* residual, const void* x, void* p
     if (hidden % kHcChunk || n > kHcMax) return -1;
     cudaStream_t st = (cudaStream_t)stream;
     const int nchunks = hidden / kHcChunk;
-    mhc_post_partial_kernel<<<dim3(rows, nchunks), 128, 0, st>>>((float*)residual, (const float*)x, (const float*)post,
+    launch_pdl((mhc_post_partial_kernel), dim3(rows, nchunks), 128, 0, st, (float*)residual, (const float*)x, (const float*)post,
                                                                     (const float*)comb, (const float*)fn, (float*)part, hidden, n, mode, comm_from_host(comm));
-    mhc_finalize_kernel<<<rows, 512, (size_t)hidden * 4, st>>>((bf16*)out_x, (const float*)residual, (const float*)part,
+    launch_pdl((mhc_finalize_kernel), rows, 512, (size_t)hidden * 4, st, (bf16*)out_x, (const float*)residual, (const float*)part,
                                                               (const float*)hc_scale, (const float*)hc_base, (const float*)norm_w,
                                                               (float*)post, (float*)comb, hidden, n, nchunks, iters, hc_eps, rms_eps, post_mult);
     LSB_CHECK_LAUNCH();
@@ -312,7 +316,7 @@ LSB_API int lsb_mhc_post_pre(void* out_x, void* residual, const void* x, void* p
 
 LSB_API int lsb_mhc_contract_norm(void* out, const void* residual, const void* x, const void* post, const void* comb,
                                   const void* norm_w, int rows, int hidden, int n, float rms_eps, const void* comm, void* stream) {
-    mhc_contract_norm_kernel<<<rows, 512, (size_t)hidden * 4, (cudaStream_t)stream>>>((bf16*)out, (const float*)residual, (const float*)x,
+    launch_pdl((mhc_contract_norm_kernel), rows, 512, (size_t)hidden * 4, (cudaStream_t)stream, (bf16*)out, (const float*)residual, (const float*)x,
                                                                                       (const float*)post, (const float*)comb,
                                                                                       (const float*)norm_w, hidden, n, rms_eps, comm_from_host(comm));
     LSB_CHECK_LAUNCH();

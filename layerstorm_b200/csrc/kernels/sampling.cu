@@ -20,6 +20,7 @@ __global__ void embedding_kernel(float* __restrict__ out_f32, bf16* __restrict__
                                  const int* __restrict__ ids, int hidden, int vocab_lo, int vocab_hi) {
     const int r = blockIdx.x;
     pdl_wait();
+    pdl_launch_dependents();
     const int id = ids[r];
     const bool own = id >= vocab_lo && id < vocab_hi;
     const bf16* src = table + (size_t)(own ? id - vocab_lo : 0) * hidden;
@@ -40,6 +41,7 @@ __global__ void argmax_partial_kernel(const float* __restrict__ logits, int ld, 
     __shared__ unsigned long long sm[32];
     const int r = blockIdx.y;
     pdl_wait();
+    pdl_launch_dependents();
     unsigned long long best = 0ull;
     const float* lg = logits + (size_t)r * ld;
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < V; i += gridDim.x * blockDim.x) {
@@ -66,6 +68,7 @@ __global__ void argmax_final_kernel(const unsigned long long* __restrict__ part,
     __shared__ unsigned long long s_best;
     const int r = blockIdx.x;
     pdl_wait();
+    pdl_launch_dependents();
     unsigned next_epoch = 0;
     if (comm.nranks) next_epoch = *comm.epoch + 1;
     if (threadIdx.x == 0) {
@@ -132,6 +135,7 @@ __global__ void __launch_bounds__(1024) sample_kernel(const float* __restrict__ 
     const int r = blockIdx.x, t = threadIdx.x;
     const float* lg = logits + (size_t)r * ld;
     pdl_wait();
+    pdl_launch_dependents();
     float mx = -INFINITY;
     for (int i = t; i < V; i += blockDim.x) mx = fmaxf(mx, lg[i]);
     mx = block_max(mx, red);
@@ -232,6 +236,7 @@ __global__ void confidence_kernel(const float* __restrict__ logits, int ld, int 
     const int r = blockIdx.x, t = threadIdx.x;
     const float* lg = logits + (size_t)r * ld;
     pdl_wait();
+    pdl_launch_dependents();
     float mx = -INFINITY;
     for (int i = t; i < V; i += blockDim.x) mx = fmaxf(mx, lg[i]);
     mx = block_max(mx, red);
@@ -251,6 +256,7 @@ __global__ void confidence_kernel(const float* __restrict__ logits, int ld, int 
 // next token = target[n_acc] (the correction or the bonus).  out = {n_acc, next_token}.
 __global__ void spec_verify_kernel(const int* __restrict__ draft, const int* __restrict__ target, int gamma, int* __restrict__ out) {
     pdl_wait();
+    pdl_launch_dependents();
     if (threadIdx.x == 0 && blockIdx.x == 0) {
         int n = 0;
         while (n < gamma && draft[n] == target[n]) ++n;
@@ -265,7 +271,7 @@ using namespace lsb;
 
 LSB_API int lsb_embedding(void* out_f32, void* out_bf16, const void* table, const void* ids, int rows, int hidden,
                           int vocab_lo, int vocab_hi, void* stream) {
-    embedding_kernel<<<rows, 256, 0, (cudaStream_t)stream>>>((float*)out_f32, (bf16*)out_bf16, (const bf16*)table, (const int*)ids,
+    launch_pdl((embedding_kernel), rows, 256, 0, (cudaStream_t)stream, (float*)out_f32, (bf16*)out_bf16, (const bf16*)table, (const int*)ids,
                                                            hidden, vocab_lo, vocab_hi);
     LSB_CHECK_LAUNCH();
 }
@@ -277,24 +283,30 @@ LSB_API int lsb_argmax(const void* logits, int ld, int rows, int V, void* part, 
     PeerComm pc;
     pc.nranks = 0;
     if (comm) pc = *reinterpret_cast<const PeerComm*>(comm);
-    argmax_partial_kernel<<<dim3(64, rows), 256, 0, st>>>((const float*)logits, ld, V, (unsigned long long*)part);
-    argmax_final_kernel<<<rows, 32, 0, st>>>((const unsigned long long*)part, 64, (int*)out_ids, (float*)out_val, base, pc);
+    launch_pdl((argmax_partial_kernel), dim3(64, rows), 256, 0, st, (const float*)logits, ld, V, (unsigned long long*)part);
+    launch_pdl((argmax_final_kernel), rows, 32, 0, st, (const unsigned long long*)part, 64, (int*)out_ids, (float*)out_val, base, pc);
     LSB_CHECK_LAUNCH();
 }
 
 LSB_API int lsb_sample(const void* logits, int ld, int rows, int V, float temperature, int top_k, float top_p,
                        unsigned long long seed, const void* offsets, void* out_ids, void* stream) {
-    sample_kernel<<<rows, 1024, 0, (cudaStream_t)stream>>>((const float*)logits, ld, V, temperature, top_k, top_p, seed,
+    launch_pdl((sample_kernel), rows, 1024, 0, (cudaStream_t)stream, (const float*)logits, ld, V, temperature, top_k, top_p, seed,
                                                          (const long long*)offsets, (int*)out_ids);
     LSB_CHECK_LAUNCH();
 }
 
 LSB_API int lsb_confidence(const void* logits, int ld, int rows, int V, void* top1, void* entropy, void* stream) {
-    confidence_kernel<<<rows, 1024, 0, (cudaStream_t)stream>>>((const float*)logits, ld, V, (float*)top1, (float*)entropy);
+    launch_pdl((confidence_kernel), rows, 1024, 0, (cudaStream_t)stream, (const float*)logits, ld, V, (float*)top1, (float*)entropy);
     LSB_CHECK_LAUNCH();
 }
 
 LSB_API int lsb_spec_verify(const void* draft, const void* target, int gamma, void* out, void* stream) {
-    spec_verify_kernel<<<1, 32, 0, (cudaStream_t)stream>>>((const int*)draft, (const int*)target, gamma, (int*)out);
+    launch_pdl((spec_verify_kernel), 1, 32, 0, (cudaStream_t)stream, (const int*)draft, (const int*)target, gamma, (int*)out);
     LSB_CHECK_LAUNCH();
+}
+
+// Process-wide switch for programmatic dependent launch (1 = on, the default).
+LSB_API int lsb_set_pdl(int enabled) {
+    lsb::pdl_enabled_flag() = enabled ? 1 : 0;
+    return 0;
 }

@@ -1,6 +1,6 @@
 // Dense weight-streaming GEMV / skinny GEMM for decode-shaped work (M <= 4 rows per
-// pass): out[m][n] = sum_k x[m][k] * W[n][k].  One warp owns two weight rows, so every
-// weight byte is read exactly once per pass and the kernel runs at HBM speed.
+// pass): out[m][n] = sum_k x[m][k] * W[n][k].  A warp owns (a K slice of) two weight rows, so
+// every weight byte is read exactly once per pass and the kernel runs at HBM speed.
 // Replaces the reference's CUDA-core GEMV family (src/compute/kernels/sm120/gemm/bf16_gemm.cu:41-156,
 // wq_gemm.cu:84-158) with one templated kernel over four weight formats.
 #include "gemv_core.cuh"
@@ -29,99 +29,106 @@ struct MatNvfp4 {
     }
 };
 
-template <class Mat, int MT, bool OUT_BF16>
+// One block = 8 warps = (8 / KS) pairs of weight rows x KS slices of K.  KS = 1 streams whole
+// rows per warp (large N); larger KS splits K across warps so that matrices with few rows still
+// put enough warps - and enough bytes in flight - on every SM.  Slice partials are combined
+// through shared memory in slice order, so the result is deterministic.
+template <class Mat, int MT, bool OUT_BF16, int KS>
 __global__ void __launch_bounds__(256) gemv_kernel(Mat mat, const bf16* __restrict__ x, int ldx, void* __restrict__ out,
                                                    int ldo, int N, int K, float alpha, const float* __restrict__ bias, PeerComm comm) {
+    __shared__ float red[8][2 * MT];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    int n0 = (blockIdx.x * 8 + warp) * 2;
+    constexpr int PAIRS = 8 / KS;
+    const int pair = warp / KS, ks = warp % KS;
+    int n0 = (blockIdx.x * PAIRS + pair) * 2;
     const bool active = n0 < N;
-    if (!active) {
-        if (comm.nranks == 0) return;
-        n0 = 0;                       // keep the warp alive for the block-wide signal below
-    }
+    if (!active) n0 = 0;
     const int n1 = min(n0 + 1, N - 1);
+    using Row = decltype(mat.row(0));
+    constexpr int E = Row::EPL;
+    const int kper = ((K + KS - 1) / KS + 32 * E - 1) / (32 * E) * (32 * E);
+    const int k0 = ks * kper, k1 = min(K, k0 + kper);
     float acc0[MT], acc1[MT];
 #pragma unroll
     for (int m = 0; m < MT; ++m) acc0[m] = acc1[m] = 0.f;
     auto r0 = mat.row(n0);
     auto r1 = mat.row(n1);
-    {   // weights do not depend on the previous kernel: pull the head of both rows into L2 while it finishes
-        constexpr int E = decltype(r0)::EPL;
+    if (active) {   // weights do not depend on the previous kernel: pull the head of both rows into L2 while it finishes
 #pragma unroll
         for (int it = 0; it < 4; ++it) {
-            const int k = (lane + 32 * it) * E;
-            if (k + E <= K) { r0.prefetch(k); r1.prefetch(k); }
+            const int k = k0 + (lane + 32 * it) * E;
+            if (k + E <= k1) { r0.prefetch(k); r1.prefetch(k); }
         }
     }
     pdl_wait();
     pdl_launch_dependents();
     unsigned next_epoch = 0;
     if (comm.nranks) next_epoch = *comm.epoch + 1;
-    if (active) warp_dot2<decltype(r0), MT>(r0, r1, x, ldx, K, acc0, acc1);
+    constexpr int UNR = E <= 8 ? (MT == 1 ? 4 : 2) : (E == 16 ? (MT == 1 ? 2 : 1) : 1);
+    if (active) warp_dot2<Row, MT, UNR>(r0, r1, x, ldx, K, acc0, acc1, lane, 32, k0, k1);
+    float va[MT], vb[MT];
 #pragma unroll
-    for (int m = 0; m < MT; ++m) {
-        float a = warp_sum(acc0[m]) * alpha, b = warp_sum(acc1[m]) * alpha;
-        if (lane == 0 && active) {
-            if (bias) { a += bias[n0]; b += bias[n1]; }
+    for (int m = 0; m < MT; ++m) { va[m] = warp_sum(acc0[m]); vb[m] = warp_sum(acc1[m]); }
+    if (KS > 1) {
+        if (lane == 0) {
+#pragma unroll
+            for (int m = 0; m < MT; ++m) { red[warp][2 * m] = va[m]; red[warp][2 * m + 1] = vb[m]; }
+        }
+        __syncthreads();
+        if (ks == 0 && lane == 0) {
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
+                float a = 0.f, b2 = 0.f;
+#pragma unroll
+                for (int j = 0; j < KS; ++j) { a += red[pair * KS + j][2 * m]; b2 += red[pair * KS + j][2 * m + 1]; }
+                va[m] = a; vb[m] = b2;
+            }
+        }
+    }
+    if (lane == 0 && ks == 0 && active) {
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            float a = va[m] * alpha, b2 = vb[m] * alpha;
+            if (bias) { a += bias[n0]; b2 += bias[n1]; }
             if (comm.nranks) {
                 comm_push(comm, next_epoch, (size_t)m * ldo + n0, a);
-                if (n0 + 1 < N) comm_push(comm, next_epoch, (size_t)m * ldo + n0 + 1, b);
+                if (n0 + 1 < N) comm_push(comm, next_epoch, (size_t)m * ldo + n0 + 1, b2);
             } else if (OUT_BF16) {
                 bf16* o = reinterpret_cast<bf16*>(out) + (size_t)m * ldo;
                 o[n0] = __float2bfloat16(a);
-                if (n0 + 1 < N) o[n0 + 1] = __float2bfloat16(b);
+                if (n0 + 1 < N) o[n0 + 1] = __float2bfloat16(b2);
             } else {
                 float* o = reinterpret_cast<float*>(out) + (size_t)m * ldo;
                 o[n0] = a;
-                if (n0 + 1 < N) o[n0 + 1] = b;
+                if (n0 + 1 < N) o[n0 + 1] = b2;
             }
         }
     }
     if (comm.nranks) comm_signal(comm, next_epoch, gridDim.x);
-    pdl_launch_dependents();
 }
 
-// Small-N variant: one block per pair of weight rows, all 256 threads stride over K, partial
-// sums combined through shared memory in warp order.  Keeps every SM busy when N is only a few
-// hundred rows (router, low-rank projections).
-template <class Mat, int MT, bool OUT_BF16>
-__global__ void __launch_bounds__(256) gemv_smalln_kernel(Mat mat, const bf16* __restrict__ x, int ldx, void* __restrict__ out,
-                                                          int ldo, int N, int K, float alpha, const float* __restrict__ bias, PeerComm comm) {
-    __shared__ float red[8][2 * MT];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * 2;
-    const int n1 = min(n0 + 1, N - 1);
-    float acc0[MT], acc1[MT];
-#pragma unroll
-    for (int m = 0; m < MT; ++m) acc0[m] = acc1[m] = 0.f;
-    auto r0 = mat.row(n0);
-    auto r1 = mat.row(n1);
-    pdl_wait();
-    pdl_launch_dependents();
-    unsigned next_epoch = 0;
-    if (comm.nranks) next_epoch = *comm.epoch + 1;
-    warp_dot2<decltype(r0), MT>(r0, r1, x, ldx, K, acc0, acc1, threadIdx.x, 256);
-#pragma unroll
-    for (int m = 0; m < MT; ++m) {
-        const float a = warp_sum(acc0[m]), b = warp_sum(acc1[m]);
-        if (lane == 0) { red[warp][2 * m] = a; red[warp][2 * m + 1] = b; }
-    }
-    __syncthreads();
-    if (threadIdx.x < 2 * MT) {
-        float a = 0.f;
-#pragma unroll
-        for (int w = 0; w < 8; ++w) a += red[w][threadIdx.x];
-        a *= alpha;
-        const int m = threadIdx.x >> 1, n = n0 + (threadIdx.x & 1);
-        if (n < N) {
-            if (bias) a += bias[n];
-            if (comm.nranks) comm_push(comm, next_epoch, (size_t)m * ldo + n, a);
-            else if (OUT_BF16) reinterpret_cast<bf16*>(out)[(size_t)m * ldo + n] = __float2bfloat16(a);
-            else reinterpret_cast<float*>(out)[(size_t)m * ldo + n] = a;
-        }
-    }
-    if (comm.nranks) comm_signal(comm, next_epoch, gridDim.x);
-    pdl_launch_dependents();
+template <class Mat, int MT, bool OB, int KS>
+static void launch_one(Mat mat, const bf16* xp, int ldx, void* op, int ldo, int N, int K, float alpha, const float* bias, PeerComm comm,
+                       cudaStream_t st) {
+    const int rows_per_block = (8 / KS) * 2;
+    launch_pdl((gemv_kernel<Mat, MT, OB, KS>), (N + rows_per_block - 1) / rows_per_block, 256, 0, st, mat, xp, ldx, op, ldo, N, K, alpha, bias, comm);
+}
+
+template <class Mat, int MT, bool OB>
+static void launch_ks(int ks, Mat mat, const bf16* xp, int ldx, void* op, int ldo, int N, int K, float alpha, const float* bias, PeerComm comm,
+                      cudaStream_t st) {
+    if (ks == 1) launch_one<Mat, MT, OB, 1>(mat, xp, ldx, op, ldo, N, K, alpha, bias, comm, st);
+    else if (ks == 2) launch_one<Mat, MT, OB, 2>(mat, xp, ldx, op, ldo, N, K, alpha, bias, comm, st);
+    else if (ks == 4) launch_one<Mat, MT, OB, 4>(mat, xp, ldx, op, ldo, N, K, alpha, bias, comm, st);
+    else launch_one<Mat, MT, OB, 8>(mat, xp, ldx, op, ldo, N, K, alpha, bias, comm, st);
+}
+
+// K-split so that the grid is at least ~two full waves (148 SMs x 8 resident blocks) while every
+// slice still has a few 32-lane iterations.
+static int choose_ks(int N, int K, int epl) {
+    int ks = 1;
+    while (ks < 8 && (long long)((N + 1) / 2) * ks / 8 < 2368 && K / (ks * 2) >= 32 * epl * 2) ks *= 2;
+    return ks;
 }
 
 template <class Mat>
@@ -133,19 +140,16 @@ static int launch_gemv(Mat mat, const bf16* x, int ldx, void* out, int ldo, int 
         comm = *reinterpret_cast<const PeerComm*>(comm_host);
         if ((M != 1 && M != 2 && M != 4) || out_bf16) return -1;   // the fused epilogue covers one single-pass launch of fp32 rows
     }
-    const int grid = (N + 15) / 16;
     const size_t osz = out_bf16 ? 2 : 4;
+    const int ks = choose_ks(N, K, decltype(mat.row(0))::EPL);
     for (int m0 = 0; m0 < M;) {
         const int rem = M - m0;
         const int mt = rem >= 4 ? 4 : (rem >= 2 ? 2 : 1);
         const bf16* xp = x + (size_t)m0 * ldx;
         void* op = reinterpret_cast<char*>(out) + (size_t)m0 * ldo * osz;
-#define LSB_GEMV_CASE(MT_)                                                                                                  \
-    if (N <= 1024) {                                                                                                        \
-        if (out_bf16) launch_pdl((gemv_smalln_kernel<Mat, MT_, true>), (N + 1) / 2, 256, 0, st, mat, xp, ldx, op, ldo, N, K, alpha, bias, comm); \
-        else launch_pdl((gemv_smalln_kernel<Mat, MT_, false>), (N + 1) / 2, 256, 0, st, mat, xp, ldx, op, ldo, N, K, alpha, bias, comm);         \
-    } else if (out_bf16) launch_pdl((gemv_kernel<Mat, MT_, true>), grid, 256, 0, st, mat, xp, ldx, op, ldo, N, K, alpha, bias, comm);           \
-    else launch_pdl((gemv_kernel<Mat, MT_, false>), grid, 256, 0, st, mat, xp, ldx, op, ldo, N, K, alpha, bias, comm);
+#define LSB_GEMV_CASE(MT_)                                                                              \
+    if (out_bf16) launch_ks<Mat, MT_, true>(ks, mat, xp, ldx, op, ldo, N, K, alpha, bias, comm, st);  \
+    else launch_ks<Mat, MT_, false>(ks, mat, xp, ldx, op, ldo, N, K, alpha, bias, comm, st);
         if (mt == 4) { LSB_GEMV_CASE(4) } else if (mt == 2) { LSB_GEMV_CASE(2) } else { LSB_GEMV_CASE(1) }
 #undef LSB_GEMV_CASE
         m0 += mt;

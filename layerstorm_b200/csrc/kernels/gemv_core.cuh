@@ -211,15 +211,46 @@ __device__ __forceinline__ void stage_scales(uint8_t* dst, const uint8_t* __rest
     }
 }
 
-// acc0[m] += sum_k w0[k]*x[m][k], acc1 likewise for w1.  x is bf16 [MT][ldx].
-// Partial sums stay per-lane; call warp_sum on them afterwards.
-template <class WF, int MT>
+// acc0[m] += sum_k w0[k]*x[m][k], acc1 likewise for w1, over k in [k0, k1).  x is bf16 [MT][ldx].
+// Lane `tid` of `nthr` cooperating threads; partial sums stay per-thread (reduce afterwards).
+// The weight vectors of UNR iterations (both rows) are requested before any of them is used,
+// so each thread keeps 2*UNR 16-byte loads in flight.
+template <class WF, int MT, int UNR = 4>
 __device__ __forceinline__ void warp_dot2(const WF& w0, const WF& w1, const bf16* __restrict__ x, int ldx, int K,
-                                          float* acc0, float* acc1, int tid = -1, int nthr = 32) {
+                                          float* acc0, float* acc1, int tid = -1, int nthr = 32, int k0 = 0, int k1 = -1) {
     constexpr int E = WF::EPL;
     const int lane = tid < 0 ? (threadIdx.x & 31) : tid;
-#pragma unroll 2
-    for (int k = lane * E; k + E <= K; k += nthr * E) {
+    if (k1 < 0 || k1 > K) k1 = K;
+    const int step = nthr * E;
+    int k = k0 + lane * E;
+    for (; k + (UNR - 1) * step + E <= k1; k += UNR * step) {
+        float a[UNR][E], b[UNR][E];
+#pragma unroll
+        for (int u = 0; u < UNR; ++u) { w0.load(k + u * step, a[u]); w1.load(k + u * step, b[u]); }
+#pragma unroll
+        for (int u = 0; u < UNR; ++u) {
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
+                const bf16* xp = x + (size_t)m * ldx + k + u * step;
+#pragma unroll
+                for (int e = 0; e < E; e += 8) {
+                    float xf[8];
+                    if constexpr (E >= 8) {
+                        uint4 xv = __ldg(reinterpret_cast<const uint4*>(xp + e));
+                        unpack_bf16x8(xv, xf);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) { acc0[m] = fmaf(a[u][e + i], xf[i], acc0[m]); acc1[m] = fmaf(b[u][e + i], xf[i], acc1[m]); }
+                    } else {
+                        uint2 xv = __ldg(reinterpret_cast<const uint2*>(xp + e));
+                        xf[0] = bf16_lo(xv.x); xf[1] = bf16_hi(xv.x); xf[2] = bf16_lo(xv.y); xf[3] = bf16_hi(xv.y);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) { acc0[m] = fmaf(a[u][e + i], xf[i], acc0[m]); acc1[m] = fmaf(b[u][e + i], xf[i], acc1[m]); }
+                    }
+                }
+            }
+        }
+    }
+    for (; k + E <= k1; k += step) {
         float a[E], b[E];
         w0.load(k, a);
         w1.load(k, b);
@@ -233,18 +264,12 @@ __device__ __forceinline__ void warp_dot2(const WF& w0, const WF& w1, const bf16
                     uint4 xv = __ldg(reinterpret_cast<const uint4*>(xp + e));
                     unpack_bf16x8(xv, xf);
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        acc0[m] = fmaf(a[e + i], xf[i], acc0[m]);
-                        acc1[m] = fmaf(b[e + i], xf[i], acc1[m]);
-                    }
+                    for (int i = 0; i < 8; ++i) { acc0[m] = fmaf(a[e + i], xf[i], acc0[m]); acc1[m] = fmaf(b[e + i], xf[i], acc1[m]); }
                 } else {
                     uint2 xv = __ldg(reinterpret_cast<const uint2*>(xp + e));
                     xf[0] = bf16_lo(xv.x); xf[1] = bf16_hi(xv.x); xf[2] = bf16_lo(xv.y); xf[3] = bf16_hi(xv.y);
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        acc0[m] = fmaf(a[e + i], xf[i], acc0[m]);
-                        acc1[m] = fmaf(b[e + i], xf[i], acc1[m]);
-                    }
+                    for (int i = 0; i < 4; ++i) { acc0[m] = fmaf(a[e + i], xf[i], acc0[m]); acc1[m] = fmaf(b[e + i], xf[i], acc1[m]); }
                 }
             }
         }

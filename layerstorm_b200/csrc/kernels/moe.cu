@@ -318,7 +318,7 @@ __global__ void __launch_bounds__(256) moe_down_kernel(const bf16* __restrict__ 
 
 
 // ---- NVFP4 fast path (hidden and expert width multiples of 128) -----------------------------
-// Row order inside a 128-row tile follows the scale-atom layout: a block covers 4 (gate/up) or 8
+// Row order inside a 128-row tile follows the scale-atom layout: a block covers 8 (gate/up) or 16
 // (down) consecutive values of n%32 for all four 32-row quads, so every 32-byte sector of scale
 // bytes it touches is used completely.
 template <int MT>
@@ -344,26 +344,26 @@ __global__ void __launch_bounds__(256) moe_gateup_fp4_kernel(const bf16* __restr
     for (int i = 0; i < MT; ++i) pr[i] = group_pairs ? group_pairs[g * 4 + min(i, n - 1)] : g;
     if (threadIdx.x < MT) rows[threadIdx.x] = x + (size_t)(pr[threadIdx.x] / S) * ef.H;
     const uint8_t* base = arena + (size_t)slot * ef.stride;
-    const int tile = blockIdx.x >> 3, blk = blockIdx.x & 7;
+    const int tile = blockIdx.x >> 2, blk = blockIdx.x & 3;
     const int gtiles = ef.H >> 6;
-    constexpr int kTS = 68;                                // 64 scale bytes per K-tile + 4 pad
+    constexpr int kTS = 132;                               // 128 scale bytes per K-tile + 4 pad
     uint8_t* scg = smraw + (size_t)MT * ef.H * 2;
     uint8_t* scu = scg + (size_t)gtiles * kTS;
-    stage_scales(scg, base + ef.off_sg, tile, blk, 4, gtiles, kTS);
-    stage_scales(scu, base + ef.off_su, tile, blk, 4, gtiles, kTS);
+    stage_scales(scg, base + ef.off_sg, tile, blk, 8, gtiles, kTS);
+    stage_scales(scu, base + ef.off_su, tile, blk, 8, gtiles, kTS);
     __syncthreads();
     stage_x_half(xs, rows, n, ef.H);
     __syncthreads();
     const float* tail = reinterpret_cast<const float*>(base + ef.off_tail);
     const float sg = tail[0], su = tail[1];
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        const int j = warp * 2 + r;                       // 0..15
-        const int f = tile * 128 + (j >> 2) * 32 + blk * 4 + (j & 3);
+#pragma unroll 1
+    for (int r = 0; r < 4; ++r) {
+        const int j = warp * 4 + r;                       // 0..31
+        const int f = tile * 128 + (j >> 3) * 32 + blk * 8 + (j & 7);
         float ag[MT], au[MT];
 #pragma unroll
         for (int m = 0; m < MT; ++m) ag[m] = au[m] = 0.f;
-        const int so = (j & 3) * 16 + (j >> 2) * 4;
+        const int so = (j & 7) * 16 + (j >> 3) * 4;
         nvfp4_row_dot2_sm<MT>(base + ef.off_gate + (size_t)f * (ef.H >> 1), scg + so,
                               base + ef.off_up + (size_t)f * (ef.H >> 1), scu + so, kTS, ef.H, xs, n, ag, au);
 #pragma unroll
@@ -401,24 +401,24 @@ __global__ void __launch_bounds__(256) moe_down_fp4_kernel(const bf16* __restric
     for (int i = 0; i < MT; ++i) pr[i] = group_pairs ? group_pairs[g * 4 + min(i, n - 1)] : g;
     if (threadIdx.x < MT) rows[threadIdx.x] = act + (size_t)pr[threadIdx.x] * ef.F;
     const uint8_t* base = arena + (size_t)slot * ef.stride;
-    const int tile = blockIdx.x >> 2, blk = blockIdx.x & 3;
+    const int tile = blockIdx.x >> 1, blk = blockIdx.x & 1;
     const int gtiles = ef.F >> 6;
-    constexpr int kTS = 132;                               // 128 scale bytes per K-tile + 4 pad
+    constexpr int kTS = 260;                               // 256 scale bytes per K-tile + 4 pad
     uint8_t* scd = smraw + (size_t)MT * ef.F * 2;
-    stage_scales(scd, base + ef.off_sd, tile, blk, 8, gtiles, kTS);
+    stage_scales(scd, base + ef.off_sd, tile, blk, 16, gtiles, kTS);
     __syncthreads();
     stage_x_half(xs, rows, n, ef.F);
     __syncthreads();
     const float sd = reinterpret_cast<const float*>(base + ef.off_tail)[2];
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        const int j0 = warp * 4 + r * 2;                  // 0..31, two rows per pass
-        const int h0 = tile * 128 + (j0 >> 3) * 32 + blk * 8 + (j0 & 7);
+#pragma unroll 1
+    for (int r = 0; r < 4; ++r) {
+        const int j0 = warp * 8 + r * 2;                  // 0..63, two rows per pass
+        const int h0 = tile * 128 + (j0 >> 4) * 32 + blk * 16 + (j0 & 15);
         const int h1 = h0 + 1;
         float a0[MT], a1[MT];
 #pragma unroll
         for (int m = 0; m < MT; ++m) a0[m] = a1[m] = 0.f;
-        const int so = (j0 & 7) * 16 + (j0 >> 3) * 4;
+        const int so = (j0 & 15) * 16 + (j0 >> 4) * 4;
         nvfp4_row_dot2_sm<MT>(base + ef.off_down + (size_t)h0 * (ef.F >> 1), scd + so,
                               base + ef.off_down + (size_t)h1 * (ef.F >> 1), scd + so + 16, kTS, ef.F, xs, n, a0, a1);
 #pragma unroll
@@ -517,7 +517,7 @@ LSB_API int lsb_moe_gateup(const void* x, const void* arena, const void* slot_of
     ExpertFmt ef = *reinterpret_cast<const ExpertFmt*>(fmt_struct);
     cudaStream_t st = (cudaStream_t)stream;
     if (ef.fmt == 2 && ef.F % 128 == 0 && ef.H % 128 == 0) {   // K % 64 == 0 follows
-        dim3 g2(ef.F / 16, max_groups);
+        dim3 g2(ef.F / 32, max_groups);
         static bool attr = false;
         if (!attr) {
             cudaFuncSetAttribute(moe_gateup_fp4_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
@@ -525,10 +525,10 @@ LSB_API int lsb_moe_gateup(const void* x, const void* arena, const void* slot_of
             attr = true;
         }
         if (!group_n)
-            launch_pdl((moe_gateup_fp4_kernel<1>), g2, 256, (size_t)ef.H * 2 + 2 * (ef.H / 64) * 68, st, (const bf16*)x, (const uint8_t*)arena, (const int*)slot_of, ef, (const int*)group_expert,
+            launch_pdl((moe_gateup_fp4_kernel<1>), g2, 256, (size_t)ef.H * 2 + 2 * (ef.H / 64) * 132, st, (const bf16*)x, (const uint8_t*)arena, (const int*)slot_of, ef, (const int*)group_expert,
                                                                         nullptr, nullptr, nullptr, (bf16*)act, S, limit, (int*)miss_flag);
         else
-            launch_pdl((moe_gateup_fp4_kernel<4>), g2, 256, (size_t)ef.H * 8 + 2 * (ef.H / 64) * 68, st, (const bf16*)x, (const uint8_t*)arena, (const int*)slot_of, ef, (const int*)group_expert,
+            launch_pdl((moe_gateup_fp4_kernel<4>), g2, 256, (size_t)ef.H * 8 + 2 * (ef.H / 64) * 132, st, (const bf16*)x, (const uint8_t*)arena, (const int*)slot_of, ef, (const int*)group_expert,
                                                                         (const int*)group_n, (const int*)group_pairs, (const int*)n_groups, (bf16*)act, S, limit,
                                                                         (int*)miss_flag);
         LSB_CHECK_LAUNCH();
@@ -551,7 +551,7 @@ LSB_API int lsb_moe_down(const void* act, const void* arena, const void* slot_of
     ExpertFmt ef = *reinterpret_cast<const ExpertFmt*>(fmt_struct);
     cudaStream_t st = (cudaStream_t)stream;
     if (ef.fmt == 2 && ef.F % 128 == 0 && ef.H % 128 == 0) {
-        dim3 g2(ef.H / 32, max_groups);
+        dim3 g2(ef.H / 64, max_groups);
         static bool attr = false;
         if (!attr) {
             cudaFuncSetAttribute(moe_down_fp4_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
@@ -559,10 +559,10 @@ LSB_API int lsb_moe_down(const void* act, const void* arena, const void* slot_of
             attr = true;
         }
         if (!group_n)
-            launch_pdl((moe_down_fp4_kernel<1>), g2, 256, (size_t)ef.F * 2 + (ef.F / 64) * 132, st, (const bf16*)act, (const uint8_t*)arena, (const int*)slot_of, ef, (const int*)group_expert,
+            launch_pdl((moe_down_fp4_kernel<1>), g2, 256, (size_t)ef.F * 2 + (ef.F / 64) * 260, st, (const bf16*)act, (const uint8_t*)arena, (const int*)slot_of, ef, (const int*)group_expert,
                                                                       nullptr, nullptr, nullptr, (float*)y);
         else
-            launch_pdl((moe_down_fp4_kernel<4>), g2, 256, (size_t)ef.F * 8 + (ef.F / 64) * 132, st, (const bf16*)act, (const uint8_t*)arena, (const int*)slot_of, ef, (const int*)group_expert,
+            launch_pdl((moe_down_fp4_kernel<4>), g2, 256, (size_t)ef.F * 8 + (ef.F / 64) * 260, st, (const bf16*)act, (const uint8_t*)arena, (const int*)slot_of, ef, (const int*)group_expert,
                                                                       (const int*)group_n, (const int*)group_pairs, (const int*)n_groups, (float*)y);
         LSB_CHECK_LAUNCH();
     }

@@ -57,9 +57,9 @@ private:
 class StateSnapshot {
 public:
     explicit StateSnapshot(uint32_t bytes) : data_(bytes) {}
-    void begin() { seq_.fetch_add(1, std::memory_order_acq_rel); depth_++; }       // nested transactions publish once
+    void begin() { if (depth_++ == 0) seq_.fetch_add(1, std::memory_order_acq_rel); }   // nested transactions publish once
     void write(uint32_t off, const void* src, uint32_t n) { if (off + n <= data_.size()) std::memcpy(data_.data() + off, src, n); }
-    void end() { if (--depth_ == 0) seq_.fetch_add(1, std::memory_order_acq_rel); else seq_.fetch_sub(1, std::memory_order_acq_rel); }
+    void end() { if (--depth_ == 0) seq_.fetch_add(1, std::memory_order_acq_rel); }
     // Returns the version read, or 0 when no consistent copy was obtained within `tries`.
     uint64_t read(void* out, uint32_t off, uint32_t n, int tries) const {
         for (int i = 0; i < tries; ++i) {

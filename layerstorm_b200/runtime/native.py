@@ -188,3 +188,182 @@ class ExpertCache:
         CB = ctypes.CFUNCTYPE(None, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int)
         self._cb = CB(lambda user, layer, expert, slot, resident: fn(layer, expert, slot, bool(resident)))
         self.lib.lsb_ec_set_listener(self.h, ctypes.cast(self._cb, ctypes.c_void_p), None)
+
+
+def _vp(x):
+    return ctypes.cast(x, ctypes.c_void_p)
+
+
+def _iarr(vals, ct=ctypes.c_int):
+    return (ct * len(vals))(*vals)
+
+
+class ExpertStats:
+    def __init__(self, n: int, alpha: float = 0.05):
+        self.lib, self.n = load(), n
+        self.h = self.lib.lsb_es_create(n, alpha)
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            self.lib.lsb_es_destroy(self.h); self.h = None
+
+    def observe(self, ids, weights=None):
+        a = _iarr(list(ids))
+        w = _iarr(list(weights), ctypes.c_float) if weights is not None else None
+        self.lib.lsb_es_observe(self.h, _vp(a), _vp(w) if w is not None else None, len(ids))
+
+    def frequency(self, e): return self.lib.lsb_es_frequency(self.h, e)
+    def weight(self, e): return self.lib.lsb_es_weight(self.h, e)
+    def autocorr(self, e): return self.lib.lsb_es_autocorr(self.h, e)
+    def recency(self, e): return self.lib.lsb_es_recency(self.h, e)
+
+    def frequencies(self):
+        out = (ctypes.c_float * self.n)()
+        self.lib.lsb_es_frequencies(self.h, _vp(out))
+        return list(out)
+
+
+class CoactivationGraph:
+    def __init__(self, n: int, decay: float = 0.99):
+        self.lib, self.n = load(), n
+        self.h = self.lib.lsb_cg_create(n, decay)
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            self.lib.lsb_cg_destroy(self.h); self.h = None
+
+    def observe(self, ids): self.lib.lsb_cg_observe(self.h, _vp(_iarr(list(ids))), len(ids))
+    def weight(self, a, b): return self.lib.lsb_cg_weight(self.h, a, b)
+
+    def partition(self, parts: int):
+        out = (ctypes.c_int * self.n)()
+        self.lib.lsb_cg_partition(self.h, parts, _vp(out))
+        return list(out)
+
+
+class WorkloadDetector:
+    def __init__(self, n: int, window: int = 256, z: float = 4.0):
+        self.lib = load()
+        self.h = self.lib.lsb_wd_create(n, window, z)
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            self.lib.lsb_wd_destroy(self.h); self.h = None
+
+    def observe(self, freq) -> bool: return bool(self.lib.lsb_wd_observe(self.h, _vp(_iarr(list(freq), ctypes.c_float))))
+    def shifts(self): return self.lib.lsb_wd_shifts(self.h)
+
+
+class AcceptanceTracker:
+    def __init__(self, alpha: float = 0.1, window: int = 64):
+        self.lib = load()
+        self.h = self.lib.lsb_at_create(alpha, window)
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            self.lib.lsb_at_destroy(self.h); self.h = None
+
+    def record(self, request, proposed, accepted): self.lib.lsb_at_record(self.h, request, proposed, accepted)
+    def ema(self): return self.lib.lsb_at_ema(self.h)
+    def global_rate(self): return self.lib.lsb_at_global(self.h)
+    def windowed_rate(self): return self.lib.lsb_at_windowed(self.h)
+    def request_rate(self, r): return self.lib.lsb_at_request(self.h, r)
+    def forget(self, r): self.lib.lsb_at_forget(self.h, r)
+    def expected_tokens(self, gamma): return self.lib.lsb_at_expected_tokens(self.h, gamma)
+
+
+class SpscRing:
+    """Lock-free single-producer/single-consumer ring of fixed-size slots (power-of-two capacity)."""
+
+    def __init__(self, slots: int, slot_bytes: int):
+        self.lib, self.slot_bytes = load(), slot_bytes
+        self.h = self.lib.lsb_ring_create(slots, slot_bytes)
+        if not self.h:
+            raise ValueError("ring capacity must be a power of two")
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            self.lib.lsb_ring_destroy(self.h); self.h = None
+
+    def push(self, data: bytes) -> bool: return bool(self.lib.lsb_ring_push(self.h, ctypes.c_char_p(data), len(data)))
+
+    def pop(self) -> Optional[bytes]:
+        buf = ctypes.create_string_buffer(self.slot_bytes)
+        return buf.raw if self.lib.lsb_ring_pop(self.h, _vp(buf)) else None
+
+    def __len__(self): return int(self.lib.lsb_ring_size(self.h))
+
+
+class StateSnapshot:
+    """Seqlock-published state block: one writer, any number of wait-free readers."""
+
+    def __init__(self, nbytes: int):
+        self.lib, self.nbytes = load(), nbytes
+        self.h = self.lib.lsb_snap_create(nbytes)
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            self.lib.lsb_snap_destroy(self.h); self.h = None
+
+    def begin(self): self.lib.lsb_snap_begin(self.h)
+    def write(self, off: int, data: bytes): self.lib.lsb_snap_write(self.h, off, ctypes.c_char_p(data), len(data))
+    def end(self): self.lib.lsb_snap_end(self.h)
+
+    def read(self, off: int, n: int, tries: int = 64):
+        buf = ctypes.create_string_buffer(n)
+        v = self.lib.lsb_snap_read(self.h, _vp(buf), off, n, tries)
+        return (buf.raw, int(v)) if v else (None, 0)
+
+
+class PerfTrace:
+    """Preallocated ring of 32-byte trace records (see csrc/runtime/ipc.cpp)."""
+
+    def __init__(self, capacity: int = 1 << 20):
+        self.lib = load()
+        self.h = self.lib.lsb_trace_create(capacity)
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            self.lib.lsb_trace_destroy(self.h); self.h = None
+
+    def record(self, stage, gpu=0, cmd_seq=0, key=0, token=0): self.lib.lsb_trace_record(self.h, stage, gpu, cmd_seq, key, token)
+    def count(self): return int(self.lib.lsb_trace_count(self.h))
+    def dropped(self): return int(self.lib.lsb_trace_dropped(self.h))
+    def dump_csv(self, path): _check(self.lib.lsb_trace_dump_csv(self.h, path.encode()), "dump_csv")
+
+    def span_ns(self, begin_stage, end_stage):
+        n = ctypes.c_ulonglong(0)
+        t = self.lib.lsb_trace_span_ns(self.h, begin_stage, end_stage, _vp(ctypes.pointer(n)))
+        return int(t), int(n.value)
+
+
+class LoaderSolver:
+    """Expert placement solver (see csrc/runtime/loader_solver.cpp).  rates in bytes/us, times in ns."""
+
+    def __init__(self, a_ns, b_ns, rate_bpus, lat_ns, egress_bpus, batch_p=64, recon_ns=0, evict_ns=0):
+        self.lib = load()
+        self.M, self.B = len(a_ns), len(egress_bpus)
+        LL = ctypes.c_longlong
+        flat = lambda m: [x for row in m for x in row]
+        self.h = self.lib.lsb_solver_create(self.M, self.B, batch_p, _vp(_iarr(a_ns, LL)), _vp(_iarr(b_ns, LL)), _vp(_iarr(flat(rate_bpus), LL)),
+                                            _vp(_iarr(flat(lat_ns), LL)), _vp(_iarr(egress_bpus, LL)), recon_ns, evict_ns)
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            self.lib.lsb_solver_destroy(self.h); self.h = None
+
+    def _req(self, bank, nbytes, resident, free_slots):
+        n = len(bank)
+        res = (ctypes.c_ubyte * (n * self.M))(*[int(resident[e][m]) for e in range(n) for m in range(self.M)])
+        return n, _iarr(bank), _iarr(nbytes, ctypes.c_longlong), res, _iarr(free_slots)
+
+    def solve(self, bank, nbytes, resident, free_slots, tier=0):
+        n, b, by, res, fs = self._req(bank, nbytes, resident, free_slots)
+        out = (ctypes.c_int * n)()
+        cost = ctypes.c_longlong(0)
+        used = _check(self.lib.lsb_solver_solve(self.h, n, _vp(b), _vp(by), _vp(res), _vp(fs), tier, _vp(out), _vp(ctypes.pointer(cost))), "solve")
+        return list(out), int(cost.value), used
+
+    def evaluate(self, bank, nbytes, resident, free_slots, assign):
+        n, b, by, res, fs = self._req(bank, nbytes, resident, free_slots)
+        return int(self.lib.lsb_solver_evaluate(self.h, n, _vp(b), _vp(by), _vp(res), _vp(fs), _vp(_iarr(assign))))

@@ -92,3 +92,95 @@ def test_expert_cache_two_phase_lock_evict():
         ec.cancel(3, e)
     ec.remove_elastic_zone(gen)
     assert ec.n_slots() == 4 and ec.lookup(0, 5) == s0
+
+
+def test_stats():
+    es = nt.ExpertStats(8, alpha=0.5)
+    for _ in range(6):
+        es.observe([1, 3], [0.7, 0.3])
+    es.observe([2], [1.0])
+    assert es.frequency(1) > 0.4 and es.frequency(5) == 0 and abs(es.weight(1) - 0.7) < 0.05
+    assert es.recency(2) == 1.0 and 0 < es.recency(1) < 1 and es.autocorr(1) > 0.4 and len(es.frequencies()) == 8
+    cg = nt.CoactivationGraph(8, 0.99)
+    for _ in range(10):
+        cg.observe([0, 1]); cg.observe([2, 3]); cg.observe([4, 5, 6, 7])
+    part = cg.partition(4)
+    assert part[0] == part[1] and part[2] == part[3] and sorted(part.count(g) for g in range(4)) == [2, 2, 2, 2]
+    wd = nt.WorkloadDetector(4, z=3.0)
+    base = [0.5, 0.5, 0.0, 0.0]
+    assert not any(wd.observe([b + 0.01 * (i % 3) for b in base]) for i in range(12))
+    assert wd.observe([0.0, 0.0, 0.5, 0.5]) and wd.shifts() == 1
+    at = nt.AcceptanceTracker(0.5, 4)
+    at.record(1, 8, 6); at.record(1, 8, 2); at.record(2, 4, 4)
+    assert abs(at.global_rate() - 0.6) < 1e-6 and abs(at.request_rate(1) - 0.5) < 1e-6 and at.request_rate(2) == 1.0
+    assert 1.0 < at.expected_tokens(4) < 5.0
+    at.forget(1)
+    assert at.request_rate(1) == 0.0
+
+
+def test_ring_snapshot_trace(tmp_path):
+    import threading
+    r = nt.SpscRing(8, 32)
+    with pytest.raises(ValueError):
+        nt.SpscRing(6, 32)
+    assert r.pop() is None
+    for i in range(8):
+        assert r.push(bytes([i]) * 4)
+    assert not r.push(b"x") and len(r) == 8              # full -> back-pressure
+    assert r.pop()[:4] == b"\x00" * 4 and r.push(b"zz") and len(r) == 8
+    got = []
+    ring = nt.SpscRing(64, 16)
+    def consumer():
+        while len(got) < 2000:
+            m = ring.pop()
+            if m is not None:
+                got.append(int.from_bytes(m[:4], "little"))
+    th = threading.Thread(target=consumer); th.start()
+    i = 0
+    while i < 2000:
+        if ring.push(i.to_bytes(4, "little")):
+            i += 1
+    th.join()
+    assert got == list(range(2000))
+    s = nt.StateSnapshot(64)
+    s.begin(); s.write(0, b"abcd"); s.begin(); s.write(4, b"efgh")
+    assert s.read(0, 8)[0] is None                        # writer active: no consistent copy
+    s.end(); assert s.read(0, 8)[0] is None               # nested transaction still open
+    s.end()
+    data, ver = s.read(0, 8)
+    assert data == b"abcdefgh" and ver > 0
+    t = nt.PerfTrace(16)
+    for tok in range(5):
+        t.record(1, token=tok); t.record(2, token=tok)
+    tot, n = t.span_ns(1, 2)
+    assert n == 5 and tot >= 0 and t.count() == 10
+    for _ in range(10):
+        t.record(3)
+    assert t.count() == 16 and t.dropped() == 4
+    t.dump_csv(str(tmp_path / "t.csv"))
+    assert len(open(tmp_path / "t.csv").read().splitlines()) == 17
+
+
+def test_loader_solver_tiers_agree_with_brute_force():
+    import itertools, random
+    M = 3
+    sv = nt.LoaderSolver(a_ns=[16000] * M, b_ns=[64000] * M, rate_bpus=[[50000] * M, [30000] * M], lat_ns=[[9000] * M, [12000] * M],
+                         egress_bpus=[80000, 60000], batch_p=64, recon_ns=20000, evict_ns=30000)
+    rng = random.Random(0)
+    for trial in range(8):
+        n = rng.randint(3, 6)
+        bank = [rng.randint(0, 1) for _ in range(n)]
+        nbytes = [rng.choice([14_000_000, 25_000_000]) for _ in range(n)]
+        resident = [[rng.random() < 0.3 for _ in range(M)] for _ in range(n)]
+        free = [rng.randint(0, 3) for _ in range(M)]
+        assign, cost, tier = sv.solve(bank, nbytes, resident, free, tier=0)
+        assert tier == 1
+        brute = min(sv.evaluate(bank, nbytes, resident, free, list(a)) for a in itertools.product(range(M), repeat=n))
+        assert cost == brute == sv.evaluate(bank, nbytes, resident, free, assign)
+        for t in (2, 3):
+            a2, c2, used = sv.solve(bank, nbytes, resident, free, tier=t)
+            assert used == t and c2 >= brute and c2 == sv.evaluate(bank, nbytes, resident, free, a2)
+            assert c2 <= 2 * brute
+    # a resident expert stays where it is when that is free of charge
+    a, c, _ = sv.solve([0], [14_000_000], [[False, True, False]], [1, 1, 1])
+    assert a == [1] and c == 16000 + 64000

@@ -1,0 +1,64 @@
+"""``python -m layerstorm_b200.cli.autoconfigure`` - derive an engine configuration for a model on this
+machine (or on a described machine) and write it with its explain sidecar.
+
+Reference: python/cli/autoconfigure.py (same levers, pins and refusal behaviour).
+Exit codes: 0 written, 2 bad arguments / config, 3 refused (the message names what to relax).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+from typing import Optional
+
+from ..autoconfig import AutoconfigRefusal, HardwareInfo, Levers, PINNABLE, detect, explain_text, solve, synthetic, write_result
+from ..config import ConfigError
+from .serve import collect_pins, resolve_model
+
+
+def build_parser() -> argparse.ArgumentParser:
+    p = argparse.ArgumentParser(prog="layerstorm_b200.cli.autoconfigure")
+    p.add_argument("--model", required=True, help="checkpoint path or built-in shape name")
+    p.add_argument("--config", help="base configuration to start from")
+    p.add_argument("--output", "-o", default="layerstorm_autoconfig.json")
+    p.add_argument("--prefer", choices=["speed", "balanced", "capacity"], default="balanced")
+    p.add_argument("--accuracy", choices=["compact", "standard", "high", "superior"], default="standard")
+    p.add_argument("--vram-expert-ratio", type=float, default=None)
+    p.add_argument("--total-active-context-tokens", type=int, default=None)
+    p.add_argument("--pin", action="append", default=[], metavar="PATH=VALUE|FILE.json", help="pinnable: " + ", ".join(PINNABLE))
+    p.add_argument("--hardware", help="JSON hardware descriptor to plan for instead of probing this machine")
+    p.add_argument("--assume-gpus", type=int, default=None, help="plan for N B200 GPUs (no probe)")
+    p.add_argument("--print", dest="show", action="store_true", help="print the explanation")
+    return p
+
+
+def main(argv: Optional[list[str]] = None) -> int:
+    args = build_parser().parse_args(argv)
+    try:
+        base = json.load(open(args.config)) if args.config else None
+        shape, _ = resolve_model(args, base)
+        if shape is None:
+            raise ConfigError(["--model: no config.json beside the checkpoint; pass a shape name or a full --config"])
+        if args.hardware:
+            hw = HardwareInfo.from_dict(json.load(open(args.hardware)))
+        elif args.assume_gpus:
+            hw = synthetic(args.assume_gpus)
+        else:
+            hw = detect((base or {}).get("hardware", {}).get("nvme_paths"))
+        res = solve(shape, hw, Levers(args.vram_expert_ratio, args.total_active_context_tokens, args.prefer, args.accuracy),
+                    collect_pins(args.pin), base)
+    except ConfigError as e:
+        print(str(e), file=sys.stderr)
+        return 2
+    except AutoconfigRefusal as e:
+        print(f"autoconfig refused: {e}\n  relax: {e.binding}", file=sys.stderr)
+        return 3
+    cfg_path, side = write_result(res, args.output)
+    if args.show:
+        print(explain_text(res))
+    print(f"wrote {cfg_path} and {side}")
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,252 @@
+"""``python -m layerstorm_b200.cli.serve`` - boot an engine and serve the OpenAI-compatible API.
+
+Boot order: parse flags -> load / autoconfigure the config -> tokenizer -> engine (one process per
+GPU; rank 0 owns the HTTP server, the other ranks follow its step commands) -> orchestrator thread ->
+uvicorn.  ``--test-engine`` swaps the GPU engine for the deterministic null engine, so the whole
+serving stack can be exercised on a machine without a GPU.
+Flag surface follows the reference CLI (python/cli/serve.py:110-217).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import logging
+import os
+import sys
+import threading
+from typing import Any, Optional
+
+from ..config import ConfigError, apply_env, fill_model_from_checkpoint, load_config, model_config_from, parse_pin
+from ..models.config import PRESETS as MODEL_PRESETS, ModelConfig, get_preset
+
+log = logging.getLogger("layerstorm_b200.serve")
+
+
+def build_parser() -> argparse.ArgumentParser:
+    p = argparse.ArgumentParser(prog="layerstorm_b200.cli.serve", description="OpenAI-compatible server for MLA-family MoE models on B200")
+    src = p.add_argument_group("configuration source")
+    src.add_argument("--config", help="engine configuration JSON")
+    src.add_argument("--autoconfig", action="store_true", help="derive the configuration from the model and this machine")
+    src.add_argument("--model", help="checkpoint path (HF safetensors directory or .gguf file) or a built-in shape preset: " + ", ".join(MODEL_PRESETS))
+    src.add_argument("--accuracy", choices=["compact", "standard", "high", "superior"], default=None, help="autoconfig: floor of the attention-backend ladder")
+    src.add_argument("--prefer", choices=["speed", "balanced", "capacity"], default=None, help="autoconfig: sort key over feasible configurations")
+    src.add_argument("--pin", action="append", default=[], metavar="PATH=VALUE|FILE.json", help="autoconfig: hard constraint (repeatable)")
+    src.add_argument("--autoconfig-redetect", action="store_true", help="ignore a stored autoconfig result and probe the machine again")
+    src.add_argument("--vram-expert-ratio", type=float, default=None, help="autoconfig lever: fraction of owned experts resident in HBM")
+    src.add_argument("--total-active-context-tokens", type=int, default=None, help="autoconfig lever: concurrency x sequence length")
+    srv = p.add_argument_group("serving")
+    srv.add_argument("--host", default=None)
+    srv.add_argument("--port", type=int, default=None)
+    srv.add_argument("--model-name", default=None, help="id reported by /v1/models")
+    srv.add_argument("--tokenizer-path", default=None)
+    srv.add_argument("--tokenizer-mode", default=None, choices=["auto", "hf", "byte"])
+    srv.add_argument("--max-concurrent", type=int, default=None)
+    srv.add_argument("--max-queued-requests", type=int, default=None)
+    srv.add_argument("--sse-heartbeat-seconds", type=float, default=None)
+    srv.add_argument("--max-sequence-length", type=int, default=None)
+    srv.add_argument("--tool-call-parser", default=None)
+    srv.add_argument("--enable-auto-tool-choice", action="store_true", default=None)
+    srv.add_argument("--reasoning-parser", default=None)
+    srv.add_argument("--reasoning-config", default=None, help="JSON string or file with the reasoning parser's settings")
+    eng = p.add_argument_group("engine")
+    eng.add_argument("--speculation-depth", type=int, default=None, help="draft tokens per speculative round (0 = off)")
+    eng.add_argument("--cycle-budget-us", type=int, default=None, help="orchestrator idle poll period")
+    eng.add_argument("--random-weights", action="store_true", help="random-init weights of the configured shape (benchmarks, smoke tests)")
+    eng.add_argument("--kv-format", default=None, choices=["fp8", "bf16"])
+    eng.add_argument("--log-level", default="info", choices=["debug", "info", "warning", "error"])
+    eng.add_argument("--test-engine", action="store_true", help="serve from the null engine (no GPU, deterministic tokens)")
+    eng.add_argument("--dry-run", action="store_true", help="resolve and print the configuration, then exit")
+    return p
+
+
+_FLAG_TO_PATH = {
+    "host": "serving.host", "port": "serving.port", "model_name": "serving.model_name", "tokenizer_path": "serving.tokenizer_path",
+    "tokenizer_mode": "serving.tokenizer_mode", "max_concurrent": "serving.max_concurrent_requests",
+    "max_queued_requests": "serving.max_queued_requests", "sse_heartbeat_seconds": "serving.sse_heartbeat_seconds",
+    "max_sequence_length": "serving.max_sequence_length", "tool_call_parser": "serving.tool_call_parser",
+    "enable_auto_tool_choice": "serving.enable_auto_tool_choice", "reasoning_parser": "serving.reasoning_parser",
+    "reasoning_config": "serving.reasoning_config",
+}
+
+
+def overrides_from_args(args: argparse.Namespace) -> dict[str, Any]:
+    out = {}
+    for flag, path in _FLAG_TO_PATH.items():
+        v = getattr(args, flag, None)
+        if v is not None:
+            out[path] = v
+    if args.speculation_depth is not None:
+        out["speculation.enabled"] = args.speculation_depth > 0
+        out["speculation.mtp.max_depth"] = max(1, args.speculation_depth)
+    return out
+
+
+def collect_pins(items: list[str]) -> dict[str, Any]:
+    pins: dict[str, Any] = {}
+    for it in items:
+        if it.endswith(".json") and os.path.exists(it):
+            pins.update(json.load(open(it)))
+        else:
+            k, v = parse_pin(it)
+            pins[k] = v
+    return pins
+
+
+def resolve_model(args: argparse.Namespace, cfg: Optional[dict]) -> tuple[Optional[ModelConfig], Optional[str]]:
+    """(shape, checkpoint path).  ``--model`` wins over ``model.weights_path``."""
+    src = args.model or (cfg or {}).get("model", {}).get("weights_path") or None
+    if src and src.lower() in MODEL_PRESETS:
+        return get_preset(src), None
+    if src and os.path.exists(src):
+        from ..models.config import from_hf_config
+        d = src if os.path.isdir(src) else os.path.dirname(src)
+        cj = os.path.join(d, "config.json")
+        if os.path.exists(cj):
+            return from_hf_config(cj), src
+        return None, src
+    if src:
+        raise ConfigError([f"--model: '{src}' is neither a path nor one of the built-in shapes {sorted(MODEL_PRESETS)}"])
+    return None, None
+
+
+def resolve_config(args: argparse.Namespace) -> tuple[dict, ModelConfig, Optional[str], Optional[str]]:
+    """Returns (config, model shape, checkpoint path or None, autoconfig explanation or None)."""
+    over = overrides_from_args(args)
+    base = json.load(open(args.config)) if args.config else None
+    shape, ckpt = resolve_model(args, base)
+    explain = None
+    if args.autoconfig or (base or {}).get("autoconfig", {}).get("enabled"):
+        from ..autoconfig import Levers, detect, explain_text, solve, synthetic, write_result
+        if shape is None:
+            raise ConfigError(["--autoconfig needs --model (a checkpoint with config.json or a built-in shape)"])
+        ac = (base or {}).get("autoconfig", {})
+        stored = ac.get("output_path") or ""
+        hw = detect((base or {}).get("hardware", {}).get("nvme_paths"))
+        if not hw.gpus and args.test_engine:
+            hw = synthetic(1)
+        if stored and os.path.exists(stored) and not args.autoconfig_redetect:
+            prev = json.load(open(stored))
+            if prev.get("autoconfig", {}).get("fingerprint") == hw.fingerprint():
+                log.info("reusing the stored autoconfig result %s", stored)
+                cfg = load_config(prev, over)
+                return apply_env(cfg), model_config_from(cfg), ckpt, "stored result reused"
+        lv = Levers(vram_expert_ratio=args.vram_expert_ratio if args.vram_expert_ratio is not None else ac.get("vram_expert_ratio"),
+                    total_active_context_tokens=args.total_active_context_tokens or ac.get("total_active_context_tokens"),
+                    prefer=args.prefer or ac.get("prefer", "balanced"), accuracy=args.accuracy or ac.get("accuracy", "standard"))
+        pins = collect_pins(args.pin)
+        for k in ("serving.max_concurrent_requests", "serving.max_sequence_length"):
+            if k in over:
+                pins.setdefault(k, over[k])
+        res = solve(shape, hw, lv, pins, base)
+        explain = explain_text(res)
+        if stored:
+            write_result(res, stored)
+        cfg = load_config(res.config, over)
+    else:
+        cfg = load_config(base, over)
+        if ckpt:
+            cfg["model"]["weights_path"] = ckpt
+            cfg["model"]["weights_format"] = "gguf" if ckpt.endswith(".gguf") else "safetensors"
+        cfg = fill_model_from_checkpoint(cfg)
+        if shape is None:
+            shape = model_config_from(cfg)
+    return apply_env(cfg), shape, ckpt, explain
+
+
+def build_engine(cfg: dict, shape: ModelConfig, ckpt: Optional[str], args: argparse.Namespace):
+    sv = cfg["serving"]
+    page = cfg["memory"]["kv_cache"]["page_size_tokens"]
+    if args.test_engine:
+        from ..runtime.null_engine import NullEngine
+        return NullEngine(vocab=max(512, min(shape.vocab, 65536)), max_seqs=sv["max_concurrent_requests"] + 4,
+                          max_ctx=sv["max_sequence_length"], page=page)
+    import torch
+    from ..models.device_model import DeviceModel
+    from ..runtime.engine import Engine
+    if not torch.cuda.is_available():
+        raise RuntimeError("no CUDA device is visible; use --test-engine to serve from the null engine")
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0)))
+    torch.cuda.set_device(dev)
+    kv_fmt = args.kv_format or {"fp8_e4m3": "fp8", "bf16": "bf16", "fp16": "bf16"}.get(cfg["quantization"]["kv_cache"], "fp8")
+    if ckpt and not args.random_weights:
+        from ..models.checkpoint import open_checkpoint
+        _, w = open_checkpoint(ckpt, shape)
+        model = DeviceModel.from_state_dict(shape, w, dev, kv_fmt, page, tp_rank=rank, tp_size=world)
+    else:
+        log.warning("serving RANDOM weights of shape %s", shape.name)
+        model = DeviceModel.random_init(shape, dev, kv_fmt, page, expert_slots="auto", embed_on_host=shape.vocab * shape.hidden > (1 << 28),
+                                        tp_rank=rank, tp_size=world)
+    max_ctx = sv["max_sequence_length"]
+    pages = cfg["memory"]["kv_cache"]["max_pages_per_gpu"]
+    eng = Engine(model, max_seqs=sv["max_concurrent_requests"] + 4, max_ctx=max_ctx,
+                 prefill_chunk=cfg["orchestrator"]["prefill_chunk_tokens"], max_batch=min(4, cfg["orchestrator"]["max_batch_size"]),
+                 num_pages=None if pages in ("auto", None) else int(pages), use_graph=cfg["compute"]["cuda_graphs"]["enabled"])
+    return eng
+
+
+def build_server(cfg: dict, shape: ModelConfig, ckpt: Optional[str], engine, args: argparse.Namespace):
+    from ..serving.http_server import LayerStormServer, ServerConfig
+    from ..serving.orchestrator import Orchestrator
+    from ..serving.prefix_cache import PrefixCacheConfig
+    from ..serving.tokenizer import TokenizerWrapper, resolve_tokenizer_dir
+    sv = cfg["serving"]
+    tpath = None if sv["tokenizer_mode"] == "byte" else resolve_tokenizer_dir(None if sv["tokenizer_path"] in ("", "auto") else sv["tokenizer_path"], ckpt)
+    tok = TokenizerWrapper(tpath, vocab_limit=getattr(engine, "vocab", None) or shape.vocab)
+    pc = sv["prefix_cache"]
+    pcc = PrefixCacheConfig(enabled=pc["enabled"] and pc["max_entries"] > 0, max_tokens=pc["max_cached_tokens"], max_holders=max(1, pc["max_entries"]))
+    eos = list(shape.eos_token_ids) or ([tok.eos_token_id] if getattr(tok, "eos_token_id", None) is not None else [])
+    draft, depth = None, 0
+    sp = cfg["speculation"]
+    if sp["enabled"] and sp["method"] == "prompt_lookup":
+        from ..speculation.prompt_lookup import PromptLookupDraft
+        pl = sp["prompt_lookup"]
+        draft = PromptLookupDraft(pl["min_ngram_size"], pl["max_ngram_size"], pl["max_continuation_length"])
+        depth = args.speculation_depth if args.speculation_depth is not None else pl["max_continuation_length"]
+    orch = Orchestrator(engine, eos_token_ids=eos, prefix_cache=pcc, draft=draft, speculation_depth=depth, tokenizer=tok)
+    rc = sv["reasoning_config"]
+    if rc:
+        rc = json.load(open(rc)) if os.path.exists(rc) else json.loads(rc)
+    scfg = ServerConfig(model_name=sv["model_name"] or shape.name, max_concurrent=sv["max_concurrent_requests"],
+                        max_queued_requests=sv["max_queued_requests"], sse_heartbeat_seconds=sv["sse_heartbeat_seconds"],
+                        max_sequence_length=sv["max_sequence_length"], tool_call_parser=sv["tool_call_parser"] or None,
+                        enable_auto_tool_choice=sv["enable_auto_tool_choice"], reasoning_parser=sv["reasoning_parser"] or None,
+                        reasoning_config=rc or None)
+    return LayerStormServer(orch, tok, scfg), orch
+
+
+def main(argv: Optional[list[str]] = None) -> int:
+    args = build_parser().parse_args(argv)
+    logging.basicConfig(level=getattr(logging, args.log_level.upper()), format="%(asctime)s %(levelname)s %(name)s: %(message)s")
+    os.environ.setdefault("CUDA_DEVICE_ORDER", "PCI_BUS_ID")
+    try:
+        cfg, shape, ckpt, explain = resolve_config(args)
+    except ConfigError as e:
+        print(str(e), file=sys.stderr)
+        return 2
+    except Exception as e:
+        from ..autoconfig import AutoconfigRefusal
+        if isinstance(e, AutoconfigRefusal):
+            print(f"autoconfig refused: {e}\n  relax: {e.binding}", file=sys.stderr)
+            return 3
+        raise
+    if explain:
+        log.info("%s", explain)
+    if args.dry_run:
+        print(json.dumps(cfg, indent=1))
+        return 0
+    engine = build_engine(cfg, shape, ckpt, args)
+    server, orch = build_server(cfg, shape, ckpt, engine, args)
+    idle = (args.cycle_budget_us or 200) * 1e-6
+    t = threading.Thread(target=orch.run, kwargs={"idle_sleep_s": idle}, name="orchestrator", daemon=True)
+    t.start()
+    try:
+        server.run(cfg["serving"]["host"], cfg["serving"]["port"], args.log_level)
+    finally:
+        orch.shutdown()
+        t.join(timeout=5)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -122,6 +122,26 @@ class GgufReader:
         return dequantize(t["type"], self.raw(name), n).reshape(t["shape"])
 
 
+    def tensor_names(self) -> List[str]:
+        return list(self.tensors)
+
+    def tensor_type(self, name: str) -> int:
+        return self.tensors[name]["type"]
+
+    def tensor_shape(self, name: str) -> Tuple[int, ...]:
+        return self.tensors[name]["shape"]
+
+    def get_slice(self, name: str, elem0: int, n: int) -> np.ndarray:
+        """Dequantise ``n`` consecutive elements starting at ``elem0`` (both multiples of the type's
+        block size), e.g. one expert out of a stacked ``[E, rows, cols]`` tensor."""
+        t = self.tensors[name]
+        be, bb = block_elems(t["type"]), block_bytes(t["type"])
+        if elem0 % be or n % be:
+            raise ValueError(f"slice [{elem0}, +{n}) is not aligned to {be}-element blocks")
+        raw = self.raw(name)[elem0 // be * bb: (elem0 + n) // be * bb]
+        return dequantize(t["type"], raw, n)
+
+
 class GgufWriter:
     def __init__(self):
         self.lib = nt.load()

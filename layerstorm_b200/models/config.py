@@ -269,6 +269,6 @@ def from_hf_config(path_or_dict) -> ModelConfig:
         index_topk_freq=c.get("index_topk_freq", 1) or 1, index_kpool=c.get("index_kpool", 1) or 1,
         index_rope_dim=c.get("qk_rope_head_dim", 0), layer_types=lt, kda_heads=la.get("num_heads", 0),
         kda_head_dim=la.get("head_dim", 128), kda_conv=la.get("short_conv_kernel_size", 4),
-        kda_lower_bound=la.get("gate_lower_bound", -5.0), hc_mult=c.get("hc_mult", 1) if c.get("mhc") else 1,
+        kda_rank=la.get("gate_low_rank", la.get("head_dim", 128)), kda_lower_bound=la.get("gate_lower_bound", -5.0), hc_mult=c.get("hc_mult", 1) if c.get("mhc") else 1,
         hc_eps=c.get("hc_eps", 1e-6), hc_sinkhorn_iters=c.get("hc_sinkhorn_iters", 20),
         eos_token_ids=(c["eos_token_id"] if isinstance(c.get("eos_token_id"), list) else [c.get("eos_token_id", 0)]))

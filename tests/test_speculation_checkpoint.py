@@ -1,0 +1,218 @@
+"""Draft proposers, draft heads, combiner / scorer / calibrator, and the lazy checkpoint readers (CPU)."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from layerstorm_b200.models.checkpoint import (LazyCheckpoint, dequant_nvfp4_rowmajor, export_hf, hf_config_dict, open_checkpoint)
+from layerstorm_b200.models.config import from_hf_config, get_preset, tiny_deepseek_v32, tiny_glm5_next, tiny_mla_moe
+from layerstorm_b200.models.weights import init_weights, round_weights_bf16
+from layerstorm_b200.runtime.null_engine import NullEngine
+from layerstorm_b200.serving.orchestrator import InferenceRequest, Orchestrator, SamplingParams
+from layerstorm_b200.speculation import (ConfidenceHead, DepthCalibrator, DraftCombiner, DraftSource, EngineDraft, IncrementalPromptLookup,
+                                         MarkovHead, PromptLookupDraft, UtilityScorer, draft_shape_for, expected_tokens)
+
+
+# ---------------------------------------------------------------- prompt lookup
+def test_prompt_lookup_prefers_longest_then_most_recent_match():
+    d = PromptLookupDraft(2, 4, 5)
+    ctx = [1, 2, 3, 9, 9, 1, 2, 3, 7, 8, 5, 1, 2, 3]
+    assert d.propose(ctx, 4) == [7, 8, 5, 1]                 # most recent earlier "1 2 3" is followed by 7 8 5 1
+    assert d.propose([4, 5, 6], 4) == []                     # nothing repeats
+    assert d.propose([1, 2, 1, 2], 8) == [1, 2]              # continuation is clipped by the context end
+    assert d.propose(ctx, 0) == []
+    assert PromptLookupDraft(2, 4, 2).propose(ctx, 4) == [7, 8]
+
+
+def test_incremental_prompt_lookup_matches_rescan():
+    g = torch.Generator().manual_seed(3)
+    toks = torch.randint(0, 6, (400,), generator=g).tolist()
+    a, b = PromptLookupDraft(2, 4, 5), IncrementalPromptLookup(2, 4, 5)
+    for n in range(3, 400, 7):
+        assert a.propose(toks[:n], 5) == b.propose(toks[:n], 5), n
+    assert b.propose([9, 9, 9, 9], 3) == a.propose([9, 9, 9, 9], 3)      # a different sequence resets the index
+
+
+# ---------------------------------------------------------------- engine draft
+def test_engine_draft_tracks_context_and_is_lossless_in_the_orchestrator():
+    target = NullEngine(vocab=97, page=16)
+    oracle = NullEngine(vocab=97, page=16)
+    draft = EngineDraft(NullEngine(vocab=97, page=16), max_gamma=4)     # same deterministic model => perfect draft
+    prompt = [5, 6, 7, 8, 9, 10]
+    ref = InferenceRequest("ref", list(prompt), SamplingParams(max_tokens=24, ignore_eos=True))
+    o = Orchestrator(oracle)
+    o.submit_request(ref); o.step()
+    req = InferenceRequest("spec", list(prompt), SamplingParams(max_tokens=24, ignore_eos=True))
+    s = Orchestrator(target, draft=draft, speculation_depth=4)
+    s.submit_request(req); s.step()
+    assert req.output_ids == ref.output_ids
+    assert req.stats.spec_rounds > 0 and req.stats.spec_accepted > 0
+    # the draft cache followed the context without re-prefilling from scratch
+    assert draft.failures == 0 and draft.engine.seq_len(draft.sid) >= len(prompt)
+
+
+def test_engine_draft_rewinds_on_divergent_context_and_fails_closed():
+    e = NullEngine(vocab=50, page=16)
+    d = EngineDraft(e, max_gamma=3)
+    p1 = d.propose([1, 2, 3, 4], 3)
+    assert len(p1) == 3 and e.seq_len(d.sid) == 3
+    p2 = d.propose([1, 2, 9, 9, 9], 3)                    # diverges after two tokens
+    assert len(p2) == 3 and e.seq_len(d.sid) == 4 and d.fed == [1, 2, 9, 9]
+    assert d.propose([1, 2, 3, 4], 3) == p1               # deterministic
+
+    class Broken(NullEngine):
+        def decode(self, *a, **k):
+            raise RuntimeError("draft device lost")
+    b = EngineDraft(Broken(vocab=50, page=16))
+    assert b.propose([1, 2, 3], 2) == [] and b.failures == 1 and b.sid is None
+
+
+def test_draft_shape():
+    t = get_preset("glm-5.3-flash")
+    d = draft_shape_for(t)
+    assert d.n_layers == 2 and d.hidden == t.hidden and d.vocab == t.vocab and d.n_routed == 0 and d.dense_quant == "nvfp4"
+    assert d.first_k_dense == 2 and not d.has_indexer and d.layer_types == ["mla", "mla"]
+
+
+# ---------------------------------------------------------------- heads
+def test_markov_chain_and_confidence_cut():
+    g = torch.Generator().manual_seed(0)
+    V, r, G = 40, 8, 5
+    w1, w2 = torch.randn(V, r, generator=g), torch.randn(V, r, generator=g)
+    base = torch.randn(G, V, generator=g)
+    ids, feats = MarkovHead(w1, w2).chain(base, prev_token=3)
+    x = 3
+    for k in range(G):
+        x = int(torch.argmax(base[k] + w2 @ w1[x]))
+        assert ids[k] == x
+    assert feats.shape == (G, r) and torch.equal(feats[0], w1[3])
+    tie = torch.zeros(1, V)
+    assert MarkovHead(torch.zeros(V, r), torch.zeros(V, r)).chain(tie, 0)[0] == [0]          # lowest index on ties
+    d2t = torch.arange(V) * 0 + 2
+    assert MarkovHead(torch.zeros(V, r), torch.zeros(V, r), d2t=d2t).chain(tie, 0)[0] == [2]  # draft -> target vocabulary
+    ch = ConfidenceHead(torch.ones(4 + r) * 0.0, b=2.0)
+    conf = ch.survival(torch.zeros(G, 4), feats)
+    assert torch.allclose(conf, torch.sigmoid(torch.tensor(2.0)).expand(G))
+    assert ConfidenceHead.cut(torch.tensor([0.9, 0.9, 0.5, 0.9]), 0.5) == 2
+    assert ConfidenceHead.cut(torch.tensor([0.4]), 0.5) == 0
+
+
+# ---------------------------------------------------------------- combiner / scorer / calibrator
+def test_combiner_picks_by_expected_tokens_per_cost_and_learns():
+    class Fixed:
+        def __init__(self, out): self.out, self.calls = out, 0
+        def propose(self, ctx, g): self.calls += 1; return self.out[:g]
+    pl, md = Fixed([]), Fixed([1, 2, 3, 4])
+    c = DraftCombiner([DraftSource("prompt_lookup", pl, cost=0.0), DraftSource("model", md, cost=0.1)])
+    assert c.propose([0], 4) == [1, 2, 3, 4] and c.last.name == "model"
+    pl.out = [7, 7, 7, 7]
+    assert c.propose([0], 4) == [7, 7, 7, 7] and md.calls == 1          # the free full-length proposal short-circuits
+    a0 = c.last.acceptance
+    c.feedback(4, 0)
+    assert c.last.acceptance < a0
+    assert expected_tokens(0.0, 5) == 1.0 and expected_tokens(0.5, 1) == 1.5
+
+
+def test_utility_scorer_strategies():
+    s = UtilityScorer("ema", max_depth=8)
+    assert s.best_depth(0.05) == 0                     # hopeless draft: do not speculate
+    assert s.best_depth(0.9) > s.best_depth(0.6) > 0
+    c = UtilityScorer("cascade", static_depth=3, max_depth=8)
+    assert c.choose(0.95) == 4 and c.choose(0.95) == 5  # one step per adjustment
+    assert UtilityScorer("fixed", static_depth=2).choose(0.1) == 2
+
+
+def test_depth_calibrator_moves_towards_target_and_disables():
+    c = DepthCalibrator(adjustment_interval_tokens=10, depth=3, ema_alpha=1.0)
+    for _ in range(5):
+        c.record(3, 3)
+    assert c.depth == 4 and c.enabled
+    c2 = DepthCalibrator(adjustment_interval_tokens=5, depth=3, ema_alpha=1.0)
+    for _ in range(6):
+        c2.record(3, 0)
+    assert not c2.enabled
+
+
+# ---------------------------------------------------------------- checkpoints
+@pytest.mark.parametrize("make", [tiny_mla_moe, tiny_glm5_next, tiny_deepseek_v32])
+def test_hf_directory_roundtrip(make, tmp_path):
+    cfg = make()
+    w = round_weights_bf16(init_weights(cfg))
+    export_hf(cfg, w, str(tmp_path), shard_bytes=2 << 20)
+    assert len([f for f in os.listdir(tmp_path) if f.endswith(".safetensors")]) > 1
+    cfg2, ck = open_checkpoint(str(tmp_path))
+    for f in ("hidden", "n_layers", "layer_types", "hc_mult", "kda_rank", "index_kpool", "n_routed", "scoring", "router_bias"):
+        assert getattr(cfg2, f) == getattr(cfg, f), f
+    for k, v in w.items():
+        assert k in ck, k
+        got = ck[k]
+        assert got.shape == v.shape and torch.equal(got, v), k
+    assert "layers.0.nope" not in ck
+    with pytest.raises(KeyError):
+        ck["layers.0.nope"]
+
+
+def test_fp8_and_nvfp4_safetensors_linears_are_dequantised(tmp_path):
+    from layerstorm_b200.formats import quant
+    from layerstorm_b200.formats.safetensors import write_safetensors
+    g = torch.Generator().manual_seed(1)
+    w = torch.randn(256, 256, generator=g) * 0.05
+    q8, sc = quant.quantize_fp8_block(w)
+    # NVFP4 in the row-major group-scale layout of ModelOpt checkpoints
+    gs = float(w.abs().max()) / (6.0 * 448.0)
+    blk = w.reshape(256, 16, 16)
+    sf = quant.e4m3_round(blk.abs().amax(-1) / 6.0 / gs).clamp_min(2 ** -9)
+    lut = torch.tensor([0, .5, 1, 1.5, 2, 3, 4, 6])
+    scaled = blk / (sf.unsqueeze(-1) * gs)
+    idx = (scaled.abs().unsqueeze(-1) - lut).abs().argmin(-1)
+    nib = (idx + 8 * (scaled < 0)).to(torch.uint8).reshape(256, 256)
+    packed = nib[:, 0::2] | (nib[:, 1::2] << 4)
+    write_safetensors(str(tmp_path / "model.safetensors"), {
+        "a.weight": q8.view(torch.float8_e4m3fn), "a.weight_scale_inv": sc,
+        "b.weight": packed, "b.weight_scale": sf.to(torch.float8_e4m3fn), "b.weight_scale_2": torch.tensor([gs]),
+        "c.weight": w.to(torch.bfloat16)})
+    from layerstorm_b200.models.checkpoint import SafetensorsSource
+    s = SafetensorsSource(str(tmp_path))
+    assert torch.allclose(s.load("a"), quant.dequantize_fp8_block(q8, sc))
+    assert (s.load("a") - w).abs().max() < 0.02
+    b = s.load("b")
+    assert torch.equal(b, dequant_nvfp4_rowmajor(packed, sf.to(torch.float8_e4m3fn).view(torch.uint8), gs))
+    assert (b - w).abs().mean() < 0.01 and (b - w).abs().max() < 0.06
+    assert torch.equal(s.load("c"), w.to(torch.bfloat16).float())
+
+
+def test_gguf_checkpoint_view(tmp_path):
+    from layerstorm_b200.formats.gguf import GgufWriter
+    cfg = tiny_mla_moe()
+    w = round_weights_bf16(init_weights(cfg))
+    gw = GgufWriter()
+    gw.meta("general.architecture", "deepseek2")
+    f32 = lambda t: t.float().numpy()
+    gw.add("token_embd.weight", f32(w["embed.weight"]))
+    gw.add("output.weight", f32(w["head.weight"]))
+    gw.add("output_norm.weight", f32(w["final_norm.weight"]))
+    i = 1
+    names = {"attn_norm.weight": "attn_norm.weight", "attn.q_a": "attn_q_a.weight", "attn.kv_a": "attn_kv_a_mqa.weight", "attn.o": "attn_output.weight",
+             "moe.router": "ffn_gate_inp.weight", "moe.router_bias": "exp_probs_b.bias"}
+    for k, n in names.items():
+        if f"layers.{i}.{k}" in w:
+            gw.add(f"blk.{i}.{n}", f32(w[f"layers.{i}.{k}"]))
+    kb = w[f"layers.{i}.attn.k_b"]                                # [H, dl, dn]
+    gw.add(f"blk.{i}.attn_k_b.weight", f32(kb.transpose(1, 2).contiguous()))      # stored [H, dn, dl]
+    gw.add(f"blk.{i}.attn_v_b.weight", f32(w[f"layers.{i}.attn.v_b"]))
+    for proj in ("gate", "up", "down"):
+        stack = torch.stack([w[f"layers.{i}.moe.experts.{e}.{proj}"] for e in range(cfg.n_routed)])
+        gw.add(f"blk.{i}.ffn_{proj}_exps.weight", f32(stack), ggml_type=8 if proj != "down" else 0)     # Q8_0 for gate/up
+        gw.add(f"blk.{i}.ffn_{proj}_shexp.weight", f32(w[f"layers.{i}.moe.shared.0.{proj}"]))
+    path = str(tmp_path / "tiny.gguf")
+    gw.write(path)
+    _, ck = open_checkpoint(path, cfg)
+    for k in ("embed.weight", "head.weight", "final_norm.weight", f"layers.{i}.attn.q_a", f"layers.{i}.attn.kv_a", f"layers.{i}.attn.o",
+              f"layers.{i}.attn.k_b", f"layers.{i}.attn.v_b", f"layers.{i}.moe.router", f"layers.{i}.moe.experts.3.down", f"layers.{i}.moe.shared.0.up"):
+        assert torch.equal(ck[k], w[k]), k
+    q = ck[f"layers.{i}.moe.experts.5.gate"]
+    ref = w[f"layers.{i}.moe.experts.5.gate"]
+    assert q.shape == ref.shape and (q - ref).abs().max() < ref.abs().max() / 100          # Q8_0 error
+    assert f"layers.{i}.mlp.gate" not in ck

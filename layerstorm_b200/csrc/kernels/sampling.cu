@@ -310,3 +310,49 @@ LSB_API int lsb_set_pdl(int enabled) {
     lsb::pdl_enabled_flag() = enabled ? 1 : 0;
     return 0;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free argmax (declared in csrc/include/lsb_noalloc.h).
+//
+// Some callers cannot allocate device memory at all: code running while a CUDA memory pool is
+// frozen, plug-ins inside a host process that owns every byte of the device heap, and latency
+// paths where a cudaMalloc (an implicit device synchronisation) is not acceptable.  For them the
+// per-block partial winners live in the fixed file-scope array below instead of a caller buffer.
+// The array costs kNoAllocMaxRows * 64 * 8 bytes = 128 KiB on every GPU that loads this library,
+// for the lifetime of the process.
+constexpr int kNoAllocMaxRows = 256;
+static __device__ __align__(256) unsigned long long g_argmax_scratch[kNoAllocMaxRows * 64];
+
+// The array's name is only a host-side handle; the device address is looked up once per device.
+static unsigned long long* noalloc_scratch_for_current_device(int* rc) {
+    static unsigned long long* ptrs[64] = {nullptr};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= 64) { *rc = e != cudaSuccess ? (int)e : -3; return nullptr; }
+    if (!ptrs[dev]) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_argmax_scratch);
+        if (e != cudaSuccess) { *rc = (int)e; return nullptr; }
+        ptrs[dev] = (unsigned long long*)p;
+    }
+    *rc = 0;
+    return ptrs[dev];
+}
+
+LSB_API int lsb_argmax_noalloc(const float* logits, int ld, int rows, int V, int* out_ids, float* out_val, int base, void* stream) {
+    if (rows <= 0 || V <= 0 || !logits || !out_ids) return -1;
+    if (rows > kNoAllocMaxRows) return -2;          // larger batches must use lsb_argmax with a caller-provided buffer
+    int rc = 0;
+    unsigned long long* part = noalloc_scratch_for_current_device(&rc);
+    if (!part) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    PeerComm pc;
+    pc.nranks = 0;
+    // every [row][block] partial is rewritten by the first kernel before the second reads it, so
+    // nothing left over from an earlier call can leak into this one
+    launch_pdl((argmax_partial_kernel), dim3(64, rows), 256, 0, st, logits, ld, V, part);
+    launch_pdl((argmax_final_kernel), rows, 32, 0, st, (const unsigned long long*)part, 64, out_ids, out_val, base, pc);
+    LSB_CHECK_LAUNCH();
+}
+
+LSB_API int lsb_argmax_noalloc_max_rows() { return kNoAllocMaxRows; }

@@ -15,6 +15,7 @@
 //    order => placement-invariant; reference: src/core/expert_device.h:31-52).
 #include "gemv_core.cuh"
 #include "comm.cuh"
+#include "moe_fmt.cuh"
 
 namespace lsb {
 
@@ -166,15 +167,6 @@ __global__ void moe_build_groups_kernel(const int* __restrict__ ids, int npairs,
     }
     pdl_launch_dependents();
 }
-
-struct ExpertFmt {
-    int fmt;                 // 0 bf16, 1 fp8 block-128, 2 nvfp4
-    int H, F;                // hidden, expert intermediate
-    long long stride;        // bytes between slots
-    long long off_gate, off_up, off_down;        // weights
-    long long off_sg, off_su, off_sd;            // scales (fp8: fp32 block scales; nvfp4: atoms)
-    long long off_tail;                           // nvfp4: 3 fp32 per-tensor scales (gate, up, down)
-};
 
 template <int FMT> struct RowOf;
 template <> struct RowOf<0> {

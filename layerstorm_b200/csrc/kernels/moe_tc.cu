@@ -1,0 +1,448 @@
+// Tensor-core routed-expert FFN for many tokens (prefill chunks, verify batches, large decode
+// batches): a grouped GEMM over expert-sorted token rows with the weight de-quantisation fused
+// into the operand pipeline.
+//
+//   moe_tc_sort     counting sort of (row, slot) pairs by expert + list of [expert, first row, rows]
+//                   token tiles of at most BN rows (device-side, no host round trip)
+//   moe_tc_gather   xs[pos] = fp16(x[pair / S]) in sorted order (the TMA-loadable "B" operand)
+//   moe_tc_ffn      one CTA per (token tile, 128 weight rows):
+//        warp 0      TMA producer for the token tile (cp.async.bulk.tensor, 128-byte swizzle)
+//        warp 1      tensor-memory owner and tcgen05.mma issuer (kind::f16, fp16 x fp16 -> fp32 in TMEM)
+//        warps 2-9   weight converters: stream the expert's NVFP4 / FP8-block / BF16 rows from HBM
+//                    exactly once, expand them to fp16 (group / block scale folded in) and store them
+//                    straight into the 128-byte-swizzled shared-memory tile the MMA reads; warps 2-5
+//                    then run the epilogue (tcgen05.ld -> SwiGLU(+clamp) -> fp16, or -> fp32 rows)
+//     gate and up tiles share one token tile and accumulate into two TMEM regions, so SwiGLU is
+//     fused and the [tokens, 2F] intermediate never exists.
+// Per-tensor NVFP4 scales are applied in the epilogue in fp32.  Every wait is bounded and reports
+// through an error word.
+// Reference seams replaced: moe_permute + external grouped GEMM + fused SwiGLU + unpermute
+// (src/core/expert_device.h:31-52, E/smxx/permute/moe_permute.cu, G/sm120/gemm/grouped).
+#include "tc_common.cuh"
+#include "gemv_core.cuh"
+#include "moe_fmt.cuh"
+
+namespace lsb {
+using namespace tc;
+
+int cached_map_2d(CUtensorMap* out, const void* ptr, CUtensorMapDataType dt, int esize, uint64_t rows, uint64_t cols, uint64_t ld,
+                  uint32_t br, uint32_t bc);
+
+constexpr int kTBM = 128;   // weight rows per UMMA
+constexpr int kTBK = 64;    // fp16 elements per stage row (128 bytes = one swizzle span)
+
+// ------------------------------------------------------------------------------------------ sort
+// Single block.  ids[npairs] = expert of pair i (or < 0 / >= E_total: ignored).
+__global__ void __launch_bounds__(1024) moe_tc_sort_kernel(const int* __restrict__ ids, int npairs, int E_total, int BN,
+                                                           int* __restrict__ sorted_pair, int* __restrict__ tile_expert,
+                                                           int* __restrict__ tile_row0, int* __restrict__ tile_n,
+                                                           int* __restrict__ counters /* [0]=tiles [1]=sorted pairs */) {
+    extern __shared__ int sm[];
+    int* cnt = sm;                  // [E_total]
+    int* off = sm + E_total;        // [E_total + 1]
+    int* tb = off + E_total + 1;    // [E_total + 1]
+    pdl_wait();
+    pdl_launch_dependents();
+    for (int e = threadIdx.x; e < E_total; e += blockDim.x) cnt[e] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < npairs; i += blockDim.x) {
+        const int e = ids[i];
+        if (e >= 0 && e < E_total) atomicAdd(&cnt[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int o = 0, t = 0;
+        for (int e = 0; e < E_total; ++e) { off[e] = o; tb[e] = t; o += cnt[e]; t += (cnt[e] + BN - 1) / BN; }
+        off[E_total] = o; tb[E_total] = t;
+        counters[0] = t; counters[1] = o;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < E_total; e += blockDim.x) {
+        const int c = cnt[e];
+        for (int j = 0, t = tb[e]; j < c; j += BN, ++t) { tile_expert[t] = e; tile_row0[t] = off[e] + j; tile_n[t] = min(BN, c - j); }
+        cnt[e] = 0;                 // reused as the placement cursor
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < npairs; i += blockDim.x) {
+        const int e = ids[i];
+        if (e >= 0 && e < E_total) sorted_pair[off[e] + atomicAdd(&cnt[e], 1)] = i;
+    }
+    pdl_launch_dependents();
+}
+
+// xs[pos][:] = fp16(x[sorted_pair[pos] / S][:])
+__global__ void __launch_bounds__(128) moe_tc_gather_kernel(const bf16* __restrict__ x, const int* __restrict__ sorted_pair,
+                                                            const int* __restrict__ counters, __half* __restrict__ xs, int S, int H) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int pos = blockIdx.x;
+    if (pos >= counters[1]) return;
+    const bf16* src = x + (size_t)(sorted_pair[pos] / S) * H;
+    __half* dst = xs + (size_t)pos * H;
+    for (int k = threadIdx.x * 8; k < H; k += blockDim.x * 8) {
+        float f[8];
+        unpack_bf16x8(__ldg(reinterpret_cast<const uint4*>(src + k)), f);
+        __half2 h[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+        *reinterpret_cast<uint4*>(dst + k) = *reinterpret_cast<uint4*>(h);
+    }
+    pdl_launch_dependents();
+}
+
+// ------------------------------------------------------------------------------------------ converters
+// Address of 16-byte chunk `c` (0..7) of row `r` in a [rows x 64 fp16] tile with 128-byte swizzle.
+__device__ __forceinline__ uint32_t sw128_chunk(uint32_t tile, int r, int c) {
+    return tile + (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4));
+}
+__device__ __forceinline__ void st_shared_16(uint32_t addr, const uint4& v) {
+    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ __half2 e4m3x2_to_half2(uint16_t v) {
+    uint32_t r;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(r) : "h"(v));
+    return *reinterpret_cast<__half2*>(&r);
+}
+
+// One converter thread's share of one pipeline stage: NE = 64 / threads-per-row consecutive K
+// elements of one weight row.  `Raw` holds the bytes fetched from HBM (issued early), `emit`
+// expands them to fp16 and stores the swizzled chunks.
+template <int FMT, int NE> struct Conv;
+constexpr float kFp8Unscale = 1.f / 256.f;
+
+template <int NE> struct Conv<2, NE> {        // NVFP4: NE/2 bytes + one 4-scale word per 64-element stage
+    static constexpr int NV = NE / 32;        // uint4 loads
+    struct Raw { uint4 v[NV]; uint32_t sc; };
+    static __device__ __forceinline__ void load(Raw& r, const uint8_t* w, const uint8_t* sf, int n, int K, int k0, int sub) {
+        const uint8_t* p = w + (size_t)n * (K >> 1) + ((k0 + sub * NE) >> 1);
+#pragma unroll
+        for (int i = 0; i < NV; ++i) r.v[i] = ldg_stream(p + 16 * i);
+        const int gtiles = ((K >> 4) + 3) >> 2;
+        r.sc = __ldg(reinterpret_cast<const uint32_t*>(sf + ((size_t)(n >> 7) * gtiles + (k0 >> 6)) * 512 + (n & 31) * 16 + ((n & 127) >> 5) * 4));
+    }
+    static __device__ __forceinline__ void emit(const Raw& r, uint32_t tile, int row, int sub) {
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const uint32_t wv[4] = {r.v[i].x, r.v[i].y, r.v[i].z, r.v[i].w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {                 // 8 elements = one 16-byte fp16 chunk
+                const int e0 = sub * NE + i * 32 + j * 8; // element offset within the 64-wide stage row
+                __half2 h[4];
+                fp4x8_to_half2x4(wv[j], h);
+                // both halves of s2 = the e4m3 scale of this element's 16-group (byte e0/16 of the scale word)
+                const __half2 s2 = e4m3x2_to_half2((uint16_t)(((r.sc >> ((e0 >> 4) * 8)) & 0xffu) * 0x0101u));
+#pragma unroll
+                for (int q = 0; q < 4; ++q) h[q] = __hmul2(h[q], s2);
+                st_shared_16(sw128_chunk(tile, row, e0 >> 3), *reinterpret_cast<uint4*>(h));
+            }
+        }
+    }
+};
+
+template <int NE> struct Conv<1, NE> {        // FP8 e4m3 with 128x128 block scales: NE bytes
+    static constexpr int NV = NE / 16;
+    struct Raw { uint4 v[NV]; float sc; };
+    static __device__ __forceinline__ void load(Raw& r, const uint8_t* w, const uint8_t* sf, int n, int K, int k0, int sub) {
+        const uint8_t* p = w + (size_t)n * K + k0 + sub * NE;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) r.v[i] = ldg_stream(p + 16 * i);
+        r.sc = __ldg(reinterpret_cast<const float*>(sf) + (size_t)(n >> 7) * ((K + 127) >> 7) + (k0 >> 7));
+    }
+    static __device__ __forceinline__ void emit(const Raw& r, uint32_t tile, int row, int sub) {
+        // block scales of small weights sit near the bottom of the fp16 range: carry them times 2^8 (exact)
+        // and take the factor out again in the fp32 epilogue (kFp8Unscale)
+        const __half2 s2 = __float2half2_rn(r.sc * 256.f);
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const uint32_t wv[4] = {r.v[i].x, r.v[i].y, r.v[i].z, r.v[i].w};
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {                 // 8 bytes -> 8 fp16
+                __half2 h[4];
+                h[0] = __hmul2(e4m3x2_to_half2((uint16_t)(wv[2 * j] & 0xffffu)), s2);
+                h[1] = __hmul2(e4m3x2_to_half2((uint16_t)(wv[2 * j] >> 16)), s2);
+                h[2] = __hmul2(e4m3x2_to_half2((uint16_t)(wv[2 * j + 1] & 0xffffu)), s2);
+                h[3] = __hmul2(e4m3x2_to_half2((uint16_t)(wv[2 * j + 1] >> 16)), s2);
+                const int e0 = sub * NE + i * 16 + j * 8;
+                st_shared_16(sw128_chunk(tile, row, e0 >> 3), *reinterpret_cast<uint4*>(h));
+            }
+        }
+    }
+};
+
+template <int NE> struct Conv<0, NE> {        // BF16: 2*NE bytes
+    static constexpr int NV = NE / 8;
+    struct Raw { uint4 v[NV]; };
+    static __device__ __forceinline__ void load(Raw& r, const uint8_t* w, const uint8_t*, int n, int K, int k0, int sub) {
+        const uint8_t* p = w + ((size_t)n * K + k0 + sub * NE) * 2;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) r.v[i] = ldg_stream(p + 16 * i);
+    }
+    static __device__ __forceinline__ void emit(const Raw& r, uint32_t tile, int row, int sub) {
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            float f[8];
+            unpack_bf16x8(r.v[i], f);
+            __half2 h[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) h[q] = __floats2half2_rn(f[2 * q], f[2 * q + 1]);
+            st_shared_16(sw128_chunk(tile, row, (sub * NE + i * 8) >> 3), *reinterpret_cast<uint4*>(h));
+        }
+    }
+};
+
+// ------------------------------------------------------------------------------------------ main kernel
+struct MoeTcParams {
+    const uint8_t* arena; const int* slot_of; ExpertFmt ef;
+    const int* tile_expert; const int* tile_row0; const int* tile_n; const int* counters;
+    const int* sorted_pair;
+    __half* act;          // gate/up output, [pairs, F] fp16 in sorted order
+    float* y;             // down output, [npairs, H] fp32 in pair order
+    float limit;
+    int* miss_flag; int* err;
+};
+
+template <int BN, bool GATEUP> struct MoeTcCfg {
+    static constexpr int A_TILES = GATEUP ? 2 : 1;
+    static constexpr int A_BYTES = A_TILES * kTBM * kTBK * 2;
+    static constexpr int B_BYTES = BN * kTBK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int STAGES = GATEUP ? 4 : 6;
+    static constexpr int TMEM_COLS = (A_TILES * BN) < 32 ? 32 : A_TILES * BN;
+    static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 256;
+    static constexpr int CONV_WARPS = 8;
+    static constexpr int THREADS = (2 + CONV_WARPS) * 32;
+    static constexpr int TPR = (CONV_WARPS * 32) / (A_TILES * kTBM);     // converter threads per weight row
+    static constexpr int NE = kTBK / TPR;                                 // elements per converter thread per stage
+};
+
+template <int FMT, int BN, bool GATEUP>
+__global__ void __launch_bounds__(MoeTcCfg<BN, GATEUP>::THREADS) moe_tc_ffn_kernel(const __grid_constant__ CUtensorMap map_b, MoeTcParams p) {
+    using C = MoeTcCfg<BN, GATEUP>;
+    using CV = Conv<FMT, C::NE>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
+    uint64_t* empty = full + C::STAGES;
+    uint64_t* acc_full = empty + C::STAGES;
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_full + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int K = GATEUP ? p.ef.H : p.ef.F;          // reduction length
+    const int NOUT = GATEUP ? p.ef.F : p.ef.H;       // weight rows
+    const int n0 = blockIdx.x * kTBM;
+    const int nkb = K / kTBK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1 + C::CONV_WARPS); mbar_init(&empty[s], 1); }
+        mbar_init(acc_full, 1);
+        fence_barrier_init();
+        fence_proxy_async();
+        tma_prefetch_desc(&map_b);
+    }
+    pdl_wait();
+    pdl_launch_dependents();
+    const int t = blockIdx.y;
+    if (t >= p.counters[0]) return;                  // uniform: no tile for this CTA
+    const int e = p.tile_expert[t], row0 = p.tile_row0[t], ncols = p.tile_n[t];
+    const int slot = p.slot_of[e];
+    if (slot < 0) {                                  // expert not resident on this GPU
+        if (p.miss_flag && threadIdx.x == 0 && blockIdx.x == 0) atomicExch(p.miss_flag, e + 1);
+        return;
+    }
+    if (warp == 1) tmem_alloc(tmem_holder, C::TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_d = *tmem_holder;
+    const uint8_t* base = p.arena + (size_t)slot * p.ef.stride;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---------------- TMA producer: token tile ----------------
+            int issued = 0;
+            bool ok = true;
+            for (int it = 0; it < nkb && ok; ++it) {
+                const int s = it % C::STAGES;
+                ok = mbar_wait(&empty[s], ((it / C::STAGES) & 1) ^ 1, p.err, 11);
+                if (!ok) break;
+                mbar_expect_tx(&full[s], C::B_BYTES);
+                tma_load_2d(smem + s * C::STAGE_BYTES + C::A_BYTES, &map_b, &full[s], it * kTBK, row0);
+                ++issued;
+            }
+            if (!ok) {
+                // the loads in flight still write this CTA's shared memory: let them land.  Their barriers may
+                // be short of converter arrivals on this path, so poll the phase with a bound and no error code.
+                for (int it = max(0, issued - C::STAGES); it < issued; ++it) mbar_wait(&full[it % C::STAGES], (it / C::STAGES) & 1, nullptr, 0);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ---------------- MMA issuer ----------------
+            constexpr uint32_t idesc = idesc_f16(kTBM, BN, 0);
+            bool ok = true;
+            for (int it = 0; it < nkb; ++it) {
+                const int s = it % C::STAGES;
+                ok = mbar_wait(&full[s], (it / C::STAGES) & 1, p.err, 12);
+                if (!ok) break;
+                tc_fence_after();
+                const uint8_t* a = smem + s * C::STAGE_BYTES;
+                const uint64_t da0 = smem_desc_sw128(a), db = smem_desc_sw128(a + C::A_BYTES);
+#pragma unroll
+                for (int k = 0; k < kTBK / 16; ++k) {
+                    const uint32_t acc = (it > 0 || k > 0) ? 1u : 0u;
+                    umma_f16(tmem_d, da0 + 2 * k, db + 2 * k, idesc, acc);
+                    if (GATEUP) umma_f16(tmem_d + BN, smem_desc_sw128(a + kTBM * kTBK * 2) + 2 * k, db + 2 * k, idesc, acc);
+                }
+                umma_commit(&empty[s]);
+            }
+            if (ok) umma_commit(acc_full);
+        }
+    } else {
+        // ---------------- weight converters ----------------
+        const int ct = threadIdx.x - 64;                       // 0..255
+        const int row = ct / C::TPR, sub = ct % C::TPR;        // row within the A stage (gate rows, then up rows)
+        const int wrow = n0 + (row & (kTBM - 1));              // weight row in the expert matrix
+        const bool is_up = GATEUP && row >= kTBM;
+        const uint8_t* w = base + (GATEUP ? (is_up ? p.ef.off_up : p.ef.off_gate) : p.ef.off_down);
+        const uint8_t* sf = base + (GATEUP ? (is_up ? p.ef.off_su : p.ef.off_sg) : p.ef.off_sd);
+        constexpr int PF = 2;                                  // stages fetched ahead of the one being converted
+        typename CV::Raw raw[PF];
+#pragma unroll
+        for (int j = 0; j < PF; ++j)
+            if (j < nkb) CV::load(raw[j], w, sf, wrow, K, j * kTBK, sub);
+        bool ok = true;
+        for (int it0 = 0; it0 < nkb && ok; it0 += PF) {
+#pragma unroll
+            for (int j = 0; j < PF; ++j) {
+                const int it = it0 + j;
+                if (it < nkb && ok) {
+                    const int s = it % C::STAGES;
+                    ok = mbar_wait(&empty[s], ((it / C::STAGES) & 1) ^ 1, p.err, 13);
+                    if (ok) {
+                        const uint32_t tile = smem_u32(smem + s * C::STAGE_BYTES) + (is_up ? kTBM * kTBK * 2 : 0);
+                        CV::emit(raw[j], tile, row & (kTBM - 1), sub);
+                        if (it + PF < nkb) CV::load(raw[j], w, sf, wrow, K, (it + PF) * kTBK, sub);
+                        fence_proxy_async();                   // generic-proxy stores -> visible to the MMA's async-proxy reads
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&full[s]);
+                    }
+                }
+            }
+        }
+        // ---------------- epilogue (warps 2-5: one TMEM lane quarter each) ----------------
+        if (warp < 6) {
+            const int q = warp & 3;
+            const int n = n0 + q * 32 + lane;
+            ok = mbar_wait(acc_full, 0, p.err, 14);
+            tc_fence_after();
+            if (ok) {
+                float sg = 1.f, su = 1.f;
+                if (FMT == 2) {
+                    const float* tail = reinterpret_cast<const float*>(base + p.ef.off_tail);
+                    if (GATEUP) { sg = tail[0]; su = tail[1]; } else sg = tail[2];
+                } else if (FMT == 1) {
+                    sg = su = kFp8Unscale;
+                }
+                const uint32_t lane_addr = tmem_d + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 16) {
+                    if (c0 >= ncols) break;
+                    float g[16], u[16];
+                    tmem_ld16(lane_addr + (uint32_t)c0, g);
+                    if (GATEUP) tmem_ld16(lane_addr + (uint32_t)(BN + c0), u);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        if (c0 + j < ncols && n < NOUT) {
+                            if (GATEUP) {
+                                float gv = g[j] * sg, uv = u[j] * su;
+                                if (p.limit > 0.f) { gv = fminf(gv, p.limit); uv = fminf(fmaxf(uv, -p.limit), p.limit); }
+                                p.act[(size_t)(row0 + c0 + j) * NOUT + n] = __float2half_rn(siluf_(gv) * uv);
+                            } else {
+                                p.y[(size_t)p.sorted_pair[row0 + c0 + j] * NOUT + n] = g[j] * sg;
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_d, C::TMEM_COLS);
+    pdl_launch_dependents();
+}
+
+template <int FMT, int BN, bool GATEUP>
+static int launch_moe_tc(const CUtensorMap& mb, const MoeTcParams& p, int nout, int max_tiles, cudaStream_t st) {
+    using C = MoeTcCfg<BN, GATEUP>;
+    static bool attr = false;
+    if (!attr) { cudaFuncSetAttribute(moe_tc_ffn_kernel<FMT, BN, GATEUP>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM); attr = true; }
+    launch_pdl((moe_tc_ffn_kernel<FMT, BN, GATEUP>), dim3(nout / kTBM, max_tiles), C::THREADS, C::SMEM, st, mb, p);
+    return (int)cudaGetLastError();
+}
+
+template <int BN, bool GATEUP>
+static int dispatch_fmt(int fmt, const CUtensorMap& mb, const MoeTcParams& p, int nout, int max_tiles, cudaStream_t st) {
+    switch (fmt) {
+        case 0: return launch_moe_tc<0, BN, GATEUP>(mb, p, nout, max_tiles, st);
+        case 1: return launch_moe_tc<1, BN, GATEUP>(mb, p, nout, max_tiles, st);
+        case 2: return launch_moe_tc<2, BN, GATEUP>(mb, p, nout, max_tiles, st);
+    }
+    return -1;
+}
+
+}  // namespace lsb
+using namespace lsb;
+
+// Tiles of at most `BN` (32, 64 or 128) sorted rows.  tile_* arrays hold npairs / BN + E_total + 1 entries,
+// counters 2 ints, sorted_pair npairs ints.
+LSB_API int lsb_moe_tc_sort(const void* ids, int npairs, int E_total, int BN, void* sorted_pair, void* tile_expert, void* tile_row0,
+                            void* tile_n, void* counters, void* stream) {
+    if (E_total > 4000 || (BN != 32 && BN != 64 && BN != 128)) return -1;
+    launch_pdl((moe_tc_sort_kernel), 1, 1024, (size_t)(3 * E_total + 2) * 4, (cudaStream_t)stream, (const int*)ids, npairs, E_total, BN,
+               (int*)sorted_pair, (int*)tile_expert, (int*)tile_row0, (int*)tile_n, (int*)counters);
+    LSB_CHECK_LAUNCH();
+}
+
+LSB_API int lsb_moe_tc_gather(const void* x, const void* sorted_pair, const void* counters, void* xs, int npairs, int S, int H, void* stream) {
+    if (H % 8) return -1;
+    launch_pdl((moe_tc_gather_kernel), npairs, 128, 0, (cudaStream_t)stream, (const bf16*)x, (const int*)sorted_pair, (const int*)counters,
+               (__half*)xs, S, H);
+    LSB_CHECK_LAUNCH();
+}
+
+// gateup != 0: act[pos][f] = SwiGLU(xs[pos] . Wgate[f], xs[pos] . Wup[f]) for every sorted position (fp16, [cap_rows, F]).
+// gateup == 0: y[pair][h] = act[pos] . Wdown[h]  (fp32, [npairs, H], rows in pair order).
+// `b` is the fp16 token operand ([cap_rows, K], K = H for gate/up and F for down), 16-byte aligned.
+LSB_API int lsb_moe_tc_ffn(int gateup, const void* b, int cap_rows, const void* arena, const void* slot_of, const void* fmt_struct,
+                           const void* tile_expert, const void* tile_row0, const void* tile_n, const void* counters,
+                           const void* sorted_pair, void* out, int BN, int max_tiles, float limit, void* miss_flag, void* err, void* stream) {
+    const ExpertFmt* ef = (const ExpertFmt*)fmt_struct;
+    const int K = gateup ? ef->H : ef->F, nout = gateup ? ef->F : ef->H;
+    if (K % kTBK || nout % kTBM || ((uintptr_t)b & 15)) return -1;
+    if (ef->fmt == 1 && (K % 128)) return -1;
+    CUtensorMap mb;
+    int rc = cached_map_2d(&mb, b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (uint64_t)cap_rows, (uint64_t)K, (uint64_t)K, (uint32_t)BN, kTBK);
+    if (rc) return rc;
+    MoeTcParams p;
+    p.arena = (const uint8_t*)arena; p.slot_of = (const int*)slot_of; p.ef = *ef;
+    p.tile_expert = (const int*)tile_expert; p.tile_row0 = (const int*)tile_row0; p.tile_n = (const int*)tile_n;
+    p.counters = (const int*)counters; p.sorted_pair = (const int*)sorted_pair;
+    p.act = gateup ? (__half*)out : nullptr; p.y = gateup ? nullptr : (float*)out;
+    p.limit = limit; p.miss_flag = (int*)miss_flag; p.err = (int*)err;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (gateup) {
+        switch (BN) {
+            case 32: return dispatch_fmt<32, true>(ef->fmt, mb, p, nout, max_tiles, st);
+            case 64: return dispatch_fmt<64, true>(ef->fmt, mb, p, nout, max_tiles, st);
+            case 128: return dispatch_fmt<128, true>(ef->fmt, mb, p, nout, max_tiles, st);
+        }
+    } else {
+        switch (BN) {
+            case 32: return dispatch_fmt<32, false>(ef->fmt, mb, p, nout, max_tiles, st);
+            case 64: return dispatch_fmt<64, false>(ef->fmt, mb, p, nout, max_tiles, st);
+            case 128: return dispatch_fmt<128, false>(ef->fmt, mb, p, nout, max_tiles, st);
+        }
+    }
+    return -1;
+}

@@ -76,6 +76,9 @@ def expert_layout(fmt: str, H: int, F: int) -> ExpertFmt:
     return ef
 
 
+TC_MOE_MIN_ROWS = 16      # rows per step from which the routed experts run on the tensor-core grouped GEMM
+
+
 class TcScratch:
     """Per-device scratch of the tensor-core GEMM: split-K partials and the kernel's error word."""
     _inst: Dict[int, "TcScratch"] = {}
@@ -295,6 +298,18 @@ class Workspace:
             self.act = z(R * S, cfg.moe_inter, dtype=b16)
             self.y = z(R * S, H)
             self.miss = z(1, dtype=i32)
+            # tensor-core grouped path (many rows): expert-sorted fp16 operands and the device-built tile list
+            self.tc_ok = R >= TC_MOE_MIN_ROWS and H % 64 == 0 and H % 128 == 0 and cfg.moe_inter % 128 == 0
+            if self.tc_ok:
+                P = R * S
+                avg = P / max(1, min(E_total, P))
+                self.tc_bn = 32 if avg <= 32 else (64 if avg <= 96 else 128)
+                self.tc_tiles = P // self.tc_bn + E_total + 1
+                self.tc_sorted = z(P, dtype=i32)
+                self.tc_tile_e = z(self.tc_tiles, dtype=i32); self.tc_tile_r0 = z(self.tc_tiles, dtype=i32)
+                self.tc_tile_n = z(self.tc_tiles, dtype=i32); self.tc_cnt = z(2, dtype=i32)
+                self.tc_xs = z(P, H, dtype=torch.float16)
+                self.tc_act = z(P, cfg.moe_inter, dtype=torch.float16)
         # outputs
         self.n_logit_rows = n_logit_rows
         self.logits = z(n_logit_rows, m.V_local)
@@ -648,7 +663,17 @@ class DeviceModel:
                  cfg.topk_group, sc, int(cfg.norm_topk_prob), cfg.routed_scale, cfg.n_shared, cfg.n_routed)
         efp = ctypes.addressof(arena.ef)
         fast_fp4 = arena.ef.fmt == 2 and cfg.moe_inter % 128 == 0 and cfg.hidden % 128 == 0
-        if fast_fp4 and R * S <= 72:
+        if getattr(ws, "tc_ok", False) and R >= TC_MOE_MIN_ROWS:
+            P = R * S
+            err = TcScratch.get(self.device).err
+            nat.call("lsb_moe_tc_sort", ws.ids, P, E_total, ws.tc_bn, ws.tc_sorted, ws.tc_tile_e, ws.tc_tile_r0, ws.tc_tile_n, ws.tc_cnt)
+            nat.call("lsb_moe_tc_gather", ws.x, ws.tc_sorted, ws.tc_cnt, ws.tc_xs, P, S, cfg.hidden)
+            tiles = min(ws.tc_tiles, P // ws.tc_bn + E_total + 1)
+            nat.call("lsb_moe_tc_ffn", 1, ws.tc_xs, ws.tc_xs.shape[0], arena.data, arena.slot_of, efp, ws.tc_tile_e, ws.tc_tile_r0, ws.tc_tile_n,
+                     ws.tc_cnt, ws.tc_sorted, ws.tc_act, ws.tc_bn, tiles, cfg.swiglu_limit, ws.miss if self.tp_size == 1 else None, err)
+            nat.call("lsb_moe_tc_ffn", 0, ws.tc_act, ws.tc_act.shape[0], arena.data, arena.slot_of, efp, ws.tc_tile_e, ws.tc_tile_r0, ws.tc_tile_n,
+                     ws.tc_cnt, ws.tc_sorted, ws.y, ws.tc_bn, tiles, 0.0, None, err)
+        elif fast_fp4 and R * S <= 72:
             # small batch: every (row, slot) pair streams its expert on its own - no grouping pass
             nat.call("lsb_moe_gateup", ws.x, arena.data, arena.slot_of, efp, ws.ids, None, None, None,
                      ws.act, S, R * S, cfg.swiglu_limit, ws.miss if self.tp_size == 1 else None)

@@ -367,3 +367,343 @@ class LoaderSolver:
     def evaluate(self, bank, nbytes, resident, free_slots, assign):
         n, b, by, res, fs = self._req(bank, nbytes, resident, free_slots)
         return int(self.lib.lsb_solver_evaluate(self.h, n, _vp(b), _vp(by), _vp(res), _vp(fs), _vp(_iarr(assign))))
+
+
+def _out(ct=ctypes.c_int):
+    v = ct(0)
+    return v, _vp(ctypes.pointer(v))
+
+
+class TransferEngine:
+    """Queueing / de-duplication / priority core of the async transfer engine (csrc/runtime/transfer_engine.cpp).
+    dir 0 = host->device, 1 = device->host.  States: 0 queued, 1 in flight, 2 done, 3 cancelled."""
+    H2D, D2H = 0, 1
+
+    def __init__(self, n_gpus: int = 1, levels: int = 3, waterline: int = 4):
+        self.lib = load()
+        self.h = self.lib.lsb_te_create(n_gpus, levels, waterline)
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            self.lib.lsb_te_destroy(self.h); self.h = None
+
+    def submit(self, layer, expert, gpu=0, direction=0, priority=0, nbytes=0) -> int:
+        return int(self.lib.lsb_te_submit(self.h, layer, expert, gpu, direction, priority, nbytes))
+
+    def next_to_issue(self, gpu=0, now_ns=0) -> int: return int(self.lib.lsb_te_next(self.h, gpu, now_ns))
+
+    def info(self, token):
+        vals = [_out() for _ in range(5)]
+        b, bp = _out(ctypes.c_longlong)
+        st, stp = _out()
+        _check(self.lib.lsb_te_info(self.h, token, *(p for _, p in vals), bp, stp), "transfer info")
+        l, e, g, d, pr = (v.value for v, _ in vals)
+        return {"layer": l, "expert": e, "gpu": g, "dir": d, "priority": pr, "bytes": b.value, "state": st.value}
+
+    def complete(self, token, now_ns=0): _check(self.lib.lsb_te_complete(self.h, token, now_ns), "transfer complete")
+    def cancel(self, token) -> int: return _check(self.lib.lsb_te_cancel(self.h, token), "transfer cancel")
+
+    def poll(self, cap: int = 64):
+        toks = (ctypes.c_ulonglong * cap)()
+        arrs = [(ctypes.c_int * cap)() for _ in range(4)]
+        n = self.lib.lsb_te_poll(self.h, _vp(toks), *(_vp(a) for a in arrs), cap)
+        return [(int(toks[i]), arrs[0][i], arrs[1][i], arrs[2][i], arrs[3][i]) for i in range(n)]      # token, state, layer, expert, gpu
+
+    def queued(self, gpu=0): return self.lib.lsb_te_queued(self.h, gpu)
+    def in_flight(self, gpu=0): return self.lib.lsb_te_in_flight(self.h, gpu)
+    def bandwidth_gbs(self, gpu=0, direction=0): return self.lib.lsb_te_bandwidth_gbs(self.h, gpu, direction)
+    def dedup_hits(self): return int(self.lib.lsb_te_dedup_hits(self.h))
+    def find(self, layer, expert, gpu=0, direction=0): return int(self.lib.lsb_te_find(self.h, layer, expert, gpu, direction))
+
+
+def numa_topology(sysfs_root: str = ""):
+    lib = load()
+    cap = 64
+    ids, cpus = (ctypes.c_int * cap)(), (ctypes.c_int * cap)()
+    tot, free = (ctypes.c_longlong * cap)(), (ctypes.c_longlong * cap)()
+    n = min(cap, lib.lsb_numa_topology(sysfs_root.encode(), cap, _vp(ids), _vp(tot), _vp(free), _vp(cpus)))
+    return [{"id": ids[i], "total_bytes": tot[i], "free_bytes": free[i], "n_cpus": cpus[i]} for i in range(n)]
+
+
+SIZING_MODES = {"fraction_free": 0, "fraction_total": 1, "absolute_gb": 2}
+
+
+def host_pool_budget(mode: str, value: float, total_bytes: int, free_bytes: int, reserve_bytes: int = 0) -> int:
+    return int(load().lsb_host_pool_budget(SIZING_MODES[mode], value, total_bytes, free_bytes, reserve_bytes))
+
+
+class HostArena:
+    """Slotted host slab for expert weights (csrc/runtime/host_arena.cpp).  ``tensor()`` exposes the slab as a
+    uint8 torch tensor without copying; ``pin()`` registers it with the CUDA driver."""
+    EMPTY, LOADING, ACTIVE = 0, 1, 2
+
+    def __init__(self, slot_bytes: int, n_slots: int, numa_node: int = -1, memfd: bool = False, thp: bool = True):
+        self.lib = load()
+        self.slot_bytes, self.n_slots = slot_bytes, n_slots
+        self.h = self.lib.lsb_arena_create(slot_bytes, n_slots, numa_node, int(memfd), int(thp))
+        if not self.h:
+            raise MemoryError(f"cannot map a host arena of {slot_bytes * n_slots} bytes")
+        self._tensor = None
+        self._pinned = False
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            self.unpin()
+            self._tensor = None
+            self.lib.lsb_arena_destroy(self.h); self.h = None
+
+    @property
+    def base(self) -> int: return int(self.lib.lsb_arena_base(self.h) or 0)
+    @property
+    def nbytes(self) -> int: return int(self.lib.lsb_arena_bytes(self.h))
+    @property
+    def fd(self) -> int: return self.lib.lsb_arena_fd(self.h)
+    @property
+    def numa_bound(self) -> bool: return bool(self.lib.lsb_arena_numa_bound(self.h))
+
+    def tensor(self):
+        import torch
+        if self._tensor is None:
+            buf = (ctypes.c_uint8 * self.nbytes).from_address(self.base)
+            self._tensor = torch.frombuffer(buf, dtype=torch.uint8).view(self.n_slots, self.slot_bytes)
+        return self._tensor
+
+    def pin(self) -> bool:
+        """Page-lock the slab for asynchronous copies (cudaHostRegister, portable).  False without a CUDA device."""
+        import torch
+        if self._pinned or not torch.cuda.is_available():
+            return self._pinned
+        rc = torch.cuda.cudart().cudaHostRegister(self.base, self.nbytes, 1)
+        self._pinned = int(rc) == 0
+        return self._pinned
+
+    def unpin(self):
+        if self._pinned:
+            import torch
+            torch.cuda.cudart().cudaHostUnregister(self.base)
+            self._pinned = False
+
+    def lookup(self, layer, expert) -> int: return self.lib.lsb_arena_lookup(self.h, layer, expert)
+
+    def begin_load(self, layer, expert):
+        el, elp = _out()
+        ee, eep = _out()
+        slot = _check(self.lib.lsb_arena_begin_load(self.h, layer, expert, elp, eep), "arena begin_load")
+        return slot, ((el.value, ee.value) if el.value >= 0 else None)
+
+    def finish_load(self, slot, ok=True): _check(self.lib.lsb_arena_finish_load(self.h, slot, int(ok)), "arena finish_load")
+    def ref(self, slot, delta=1): return _check(self.lib.lsb_arena_ref(self.h, slot, delta), "arena ref")
+    def wipe(self): _check(self.lib.lsb_arena_wipe(self.h), "arena wipe")
+
+    def stats(self):
+        U = ctypes.c_ulonglong
+        (a, ap), (b, bp), (c, cp) = _out(U), _out(U), _out(U)
+        n, np_ = _out()
+        self.lib.lsb_arena_stats(self.h, ap, bp, cp, np_)
+        return {"hits": a.value, "misses": b.value, "evictions": c.value, "active": n.value}
+
+    def slot_info(self, slot):
+        vals = [_out() for _ in range(4)]
+        _check(self.lib.lsb_arena_slot_info(self.h, slot, *(p for _, p in vals)), "arena slot_info")
+        st, l, e, r = (v.value for v, _ in vals)
+        return {"state": st, "layer": l, "expert": e, "refs": r}
+
+    def save_meta(self, path, tag=0): _check(self.lib.lsb_arena_save_meta(self.h, str(path).encode(), tag), "arena save_meta")
+    def load_meta(self, path, tag=0) -> int: return self.lib.lsb_arena_load_meta(self.h, str(path).encode(), tag)
+
+
+class NvmeTier:
+    def __init__(self, drives, capacity_bytes: int = 0, queue_depth: int = 64, direct_io: bool = False, workers: int = 4):
+        self.lib = load()
+        self.h = self.lib.lsb_nvme_create("\n".join(str(d) for d in drives).encode(), capacity_bytes, queue_depth, int(direct_io), workers)
+        if not self.h:
+            raise ValueError("NvmeTier needs at least one drive path")
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            self.lib.lsb_nvme_destroy(self.h); self.h = None
+
+    def write(self, layer, expert, data: bytes): _check(self.lib.lsb_nvme_write(self.h, layer, expert, ctypes.c_char_p(data), len(data)), "nvme write")
+
+    def write_ptr(self, layer, expert, ptr: int, nbytes: int): _check(self.lib.lsb_nvme_write(self.h, layer, expert, ctypes.c_void_p(ptr), nbytes), "nvme write")
+
+    def read(self, layer, expert, nbytes: int) -> bytes:
+        buf = ctypes.create_string_buffer(nbytes)
+        _check(self.lib.lsb_nvme_read(self.h, layer, expert, _vp(buf), nbytes), "nvme read")
+        return buf.raw
+
+    def read_async(self, layer, expert, dst_ptr: int, nbytes: int) -> int:
+        return int(self.lib.lsb_nvme_read_async(self.h, layer, expert, ctypes.c_void_p(dst_ptr), nbytes))
+
+    def poll(self, cap=64):
+        toks, st = (ctypes.c_ulonglong * cap)(), (ctypes.c_int * cap)()
+        n = self.lib.lsb_nvme_poll(self.h, _vp(toks), _vp(st), cap)
+        return [(int(toks[i]), st[i]) for i in range(n)]
+
+    def size_of(self, layer, expert): return int(self.lib.lsb_nvme_size_of(self.h, layer, expert))
+    def evict(self, layer, expert): _check(self.lib.lsb_nvme_evict(self.h, layer, expert), "nvme evict")
+    def used(self): return int(self.lib.lsb_nvme_used(self.h))
+    def pending(self): return self.lib.lsb_nvme_pending(self.h)
+
+
+class ExpertLifecycle:
+    """Per (layer, expert, gpu) residency state machine (csrc/runtime/lifecycle.cpp)."""
+    COLD, LOADING_TO_RAM, WARM = 0, 1, 2
+    ABSENT, RESERVED, TRANSFERRING, HOT, DRAINING = 0, 1, 2, 3, 4
+    ACT_NONE, ACT_READ_NVME, ACT_RESERVE_SLOT, ACT_START_H2D, ACT_WAIT = 0, 1, 2, 3, 4
+    (EV_NVME_DONE, EV_NVME_FAILED, EV_SLOT_RESERVED, EV_SLOT_DENIED, EV_H2D_STARTED, EV_H2D_DONE, EV_H2D_FAILED, EV_EVICT_REQUESTED,
+     EV_DRAINED, EV_HOST_EVICTED) = range(10)
+
+    def __init__(self):
+        self.lib = load()
+        self.h = self.lib.lsb_elm_create()
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            self.lib.lsb_elm_destroy(self.h); self.h = None
+
+    def set_host_tier(self, layer, expert, tier): self.lib.lsb_elm_set_host_tier(self.h, layer, expert, tier)
+    def begin_host_load(self, layer, expert): self.lib.lsb_elm_begin_host_load(self.h, layer, expert)
+
+    def ensure_resident(self, layer, expert, gpu=0):
+        t, tp = _out(ctypes.c_ulonglong)
+        a = self.lib.lsb_elm_ensure_resident(self.h, layer, expert, gpu, tp)
+        return a, int(t.value)
+
+    def release(self, layer, expert, gpu=0): return self.lib.lsb_elm_release(self.h, layer, expert, gpu)
+    def on_event(self, layer, expert, gpu, ev) -> int: return _check(self.lib.lsb_elm_on_event(self.h, layer, expert, gpu, ev), "lifecycle event")
+
+    def get(self, layer, expert, gpu=0):
+        vals = [_out() for _ in range(3)]
+        self.lib.lsb_elm_get(self.h, layer, expert, gpu, *(p for _, p in vals))
+        return tuple(v.value for v, _ in vals)          # host tier, gpu tier, interest
+
+    def loads(self): return int(self.lib.lsb_elm_loads(self.h))
+    def evictions(self): return int(self.lib.lsb_elm_evictions(self.h))
+
+
+class ZoneRebalancer:
+    NONE, LEND, BEGIN_RECLAIM, FINISH_RECLAIM = range(4)
+
+    def __init__(self, total_kv_pages, pages_per_zone, low_water=0.5, high_water=0.85, max_zones=4):
+        self.lib = load()
+        self.h = self.lib.lsb_zr_create(total_kv_pages, pages_per_zone, low_water, high_water, max_zones)
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            self.lib.lsb_zr_destroy(self.h); self.h = None
+
+    def step(self, kv_used, miss_rate, zone_occupancy=0):
+        g, gp = _out()
+        a = self.lib.lsb_zr_step(self.h, kv_used, miss_rate, zone_occupancy, gp)
+        return a, g.value
+
+    def on_lent(self, gen): self.lib.lsb_zr_on_lent(self.h, gen)
+    def on_reclaimed(self, gen): _check(self.lib.lsb_zr_on_reclaimed(self.h, gen), "zone reclaim")
+    def lent_pages(self): return self.lib.lsb_zr_lent_pages(self.h)
+    def n_zones(self): return self.lib.lsb_zr_n_zones(self.h)
+
+
+class KvTierTable:
+    HOT_PAGE, ROW_CACHE, COLD = 0, 1, 2
+
+    def __init__(self, page_tokens, hot_window_tokens, cold_slots, row_cache_rows=0):
+        self.lib = load()
+        self.h = self.lib.lsb_kvt_create(page_tokens, hot_window_tokens, cold_slots, row_cache_rows)
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            self.lib.lsb_kvt_destroy(self.h); self.h = None
+
+    def create(self, seq): self.lib.lsb_kvt_seq_create(self.h, seq)
+    def fork(self, parent, child, prefix_pages): _check(self.lib.lsb_kvt_seq_fork(self.h, parent, child, prefix_pages), "tier fork")
+    def destroy(self, seq): _check(self.lib.lsb_kvt_seq_destroy(self.h, seq), "tier destroy")
+
+    def demotion_candidates(self, seq, seq_len, cap=256):
+        out = (ctypes.c_int * cap)()
+        n = _check(self.lib.lsb_kvt_demotion_candidates(self.h, seq, seq_len, _vp(out), cap), "tier candidates")
+        return list(out[:n])
+
+    def demote(self, seq, page) -> int: return _check(self.lib.lsb_kvt_demote(self.h, seq, page), "tier demote")
+    def promote(self, seq, page) -> int: return _check(self.lib.lsb_kvt_promote(self.h, seq, page), "tier promote")
+    def truncate(self, seq, new_len): _check(self.lib.lsb_kvt_truncate(self.h, seq, new_len), "tier truncate")
+    def where(self, seq, page) -> int: return self.lib.lsb_kvt_where(self.h, seq, page)
+
+    def classify(self, seq, layer, rows):
+        n = len(rows)
+        kind, ref = (ctypes.c_int * n)(), (ctypes.c_int * n)()
+        cold = _check(self.lib.lsb_kvt_classify(self.h, seq, layer, _vp(_iarr(list(rows))), n, _vp(kind), _vp(ref)), "tier classify")
+        return list(kind), list(ref), cold
+
+    def cache_row(self, seq, layer, row) -> int: return self.lib.lsb_kvt_cache_row(self.h, seq, layer, row)
+    def free_cold_slots(self): return self.lib.lsb_kvt_free_cold_slots(self.h)
+
+    def stats(self):
+        U = ctypes.c_ulonglong
+        vals = [_out(U) for _ in range(4)]
+        self.lib.lsb_kvt_stats(self.h, *(p for _, p in vals))
+        return dict(zip(("demotions", "promotions", "cold_fetches", "row_hits"), (v.value for v, _ in vals)))
+
+
+VRAM_REGIONS = ("weights", "workspace", "kv_spec", "indexer_k", "kv_main", "prefill_scratch", "recurrent", "expert_streaming", "expert_stable", "safety")
+
+
+def vram_plan(total_bytes, weights_bytes, workspace_bytes, kv_bytes_per_page, kv_pages, spec_pool_fraction=0.15, indexer_bytes_per_page=0,
+              indexer_pages=0, prefill_scratch_bytes=0, recurrent_bytes_per_seq=0, recurrent_seqs=0, expert_slot_bytes=0,
+              expert_slots_wanted=0, stable_zone_fraction=0.7, safety_bytes=1 << 30):
+    """Carve one GPU (csrc/runtime/vram_planner.cpp).  Raises NativeError(ERR_FULL) naming the region that does not fit."""
+    inp = (ctypes.c_double * 16)(total_bytes, weights_bytes, workspace_bytes, kv_bytes_per_page, kv_pages, spec_pool_fraction, indexer_bytes_per_page,
+                                 indexer_pages, prefill_scratch_bytes, recurrent_bytes_per_seq, recurrent_seqs, expert_slot_bytes,
+                                 expert_slots_wanted, stable_zone_fraction, safety_bytes, 0)
+    out = (ctypes.c_longlong * 23)()
+    failed = load().lsb_vram_plan(_vp(inp), _vp(out))
+    if failed >= 0:
+        raise NativeError(ERR_FULL, f"VRAM plan: region '{VRAM_REGIONS[failed]}' does not fit")
+    regions = {VRAM_REGIONS[r]: {"offset": out[r], "size": out[10 + r]} for r in range(10)}
+    return {"regions": regions, "kv_spec_pages": out[20], "expert_stable_slots": out[21], "expert_streaming_slots": out[22]}
+
+
+class Determinism:
+    def __init__(self):
+        self.lib = load()
+        self.h = self.lib.lsb_det_create()
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            self.lib.lsb_det_destroy(self.h); self.h = None
+
+    def set_flags(self, deterministic=False, identity=False):
+        buf = ctypes.create_string_buffer(128)
+        rc = self.lib.lsb_det_set_flags(self.h, int(deterministic), int(identity), _vp(buf), 128)
+        if rc < 0:
+            raise NativeError(rc, f"determinism: pinned knob '{buf.value.decode()}' contradicts the requested mode")
+
+    def pin(self, name, value): _check(self.lib.lsb_det_pin(self.h, name.encode(), int(value)), f"determinism pin {name}")
+    def get(self, name) -> int: return _check(self.lib.lsb_det_get(self.h, name.encode()), f"determinism knob {name}")
+
+    def knobs(self):
+        self.lib.lsb_det_name_at.restype = ctypes.c_char_p
+        return [self.lib.lsb_det_name_at(self.h, i).decode() for i in range(self.lib.lsb_det_count(self.h))]
+
+
+class BufferRegistry:
+    def __init__(self):
+        self.lib = load()
+        self.h = self.lib.lsb_bufreg_create()
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            self.lib.lsb_bufreg_destroy(self.h); self.h = None
+
+    def add(self, name, ptr, nbytes, gpu=0) -> int: return _check(self.lib.lsb_bufreg_add(self.h, name.encode(), ptr, nbytes, gpu), f"buffer {name}")
+    def find(self, name) -> int: return _check(self.lib.lsb_bufreg_find(self.h, name.encode()), f"buffer {name}")
+
+    def get(self, bid):
+        U = ctypes.c_ulonglong
+        (p, pp), (b, bp) = _out(U), _out(U)
+        g, gp = _out()
+        _check(self.lib.lsb_bufreg_get(self.h, bid, pp, bp, gp), "buffer id")
+        return p.value, b.value, g.value
+
+    def contains(self, bid, ptr, nbytes) -> bool: return bool(self.lib.lsb_bufreg_contains(self.h, bid, ptr, nbytes))
+    def __len__(self): return self.lib.lsb_bufreg_count(self.h)

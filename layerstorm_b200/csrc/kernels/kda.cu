@@ -118,6 +118,196 @@ __global__ void __launch_bounds__(kD) kda_kernel(KdaParams p) {
     pdl_launch_dependents();
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Many-token path (prefill chunks, verify batches).  Everything that is not part of the
+// recurrence is hoisted out of the token loop and runs in parallel over (row, head):
+//   kda_prep    conv4+SiLU, q/k L2 norms, low-rank gate tails, decay = exp(lb * sigmoid(..)),
+//               output gate sigmoid(g2), beta -> fp32 arrays [rows, C] / [rows, H]
+//   kda_recur   the delta rule only: per token 4 x 128 FMAs per thread on the register-resident
+//               state row; q/k/decay vectors arrive through a double-buffered cp.async pipeline
+//   kda_out     gated RMSNorm of the outputs -> bf16
+// The math per token is the one of kda_kernel above, in the same operation order.
+constexpr int kTCH = 8;       // tokens per shared-memory pipeline stage
+
+struct KdaScratch {
+    float* qn; float* kn; float* vo; float* decay; float* gate;   // [rows, C]  (vo: v in, o out)
+    float* beta;                                                    // [rows, H]
+};
+
+__global__ void __launch_bounds__(kD) kda_prep_kernel(KdaParams p, KdaScratch w, int nseq) {
+    __shared__ float s_fa[128], s_ga[128], s_red[33];
+    const int row = blockIdx.x, h = blockIdx.y, t = threadIdx.x;
+    const int C = p.H * kD, ch = h * kD + t;
+    float wq[4], wk[4], wv[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { wq[j] = p.conv_q[ch * 4 + j]; wk[j] = p.conv_k[ch * 4 + j]; wv[j] = p.conv_v[ch * 4 + j]; }
+    const float a_exp = p.a_exp[h], dtb = p.dt_bias[ch];
+    pdl_wait();
+    pdl_launch_dependents();
+    int row0 = -1, slot = 0;
+    for (int s = 0; s < nseq; ++s) {
+        const int r0 = p.seq_row0[s], n = p.seq_nrows[s];
+        if (row >= r0 && row < r0 + n) { row0 = r0; slot = p.seq_slot[s]; }
+    }
+    if (row0 < 0) return;                                    // row belongs to no sequence of this step
+    const int i = row - row0;
+    float rq[4], rk[4], rv[4];                               // raw taps, oldest first; [3] = this row
+#pragma unroll
+    for (int d = 0; d < 4; ++d) {
+        const int back = 3 - d;                              // tap d is `back` rows before this one
+        if (i - back >= 0) {
+            const float* pr = p.proj + (size_t)(row - back) * p.ldp;
+            rq[d] = pr[p.off_q + ch]; rk[d] = pr[p.off_k + ch]; rv[d] = pr[p.off_v + ch];
+        } else {
+            const int hi = 3 + i - back;                     // 0..2 in the saved history
+            rq[d] = p.conv_state[(((size_t)slot * 3 + 0) * C + ch) * 3 + hi];
+            rk[d] = p.conv_state[(((size_t)slot * 3 + 1) * C + ch) * 3 + hi];
+            rv[d] = p.conv_state[(((size_t)slot * 3 + 2) * C + ch) * 3 + hi];
+        }
+    }
+    const float* pr = p.proj + (size_t)row * p.ldp;
+    float q = rq[0] * wq[0]; q += rq[1] * wq[1]; q += rq[2] * wq[2]; q += rq[3] * wq[3];
+    float k = rk[0] * wk[0]; k += rk[1] * wk[1]; k += rk[2] * wk[2]; k += rk[3] * wk[3];
+    float v = rv[0] * wv[0]; v += rv[1] * wv[1]; v += rv[2] * wv[2]; v += rv[3] * wv[3];
+    q = siluf_(q); k = siluf_(k); v = siluf_(v);
+    if (t < p.rank) { s_fa[t] = pr[p.off_fa + t]; s_ga[t] = pr[p.off_ga + t]; }
+    const float qs = block_sum(q * q, s_red);
+    const float ks = block_sum(k * k, s_red);
+    __syncthreads();
+    const bf16* fb = p.f_b + (size_t)ch * p.rank;
+    const bf16* gb = p.g_b + (size_t)ch * p.rank;
+    float raw_g = 0.f, g2 = 0.f;
+    for (int j = 0; j < p.rank; j += 8) {
+        uint4 a = __ldg(reinterpret_cast<const uint4*>(fb + j));
+        uint4 b = __ldg(reinterpret_cast<const uint4*>(gb + j));
+        float af[8], bfv[8];
+        unpack_bf16x8(a, af); unpack_bf16x8(b, bfv);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) { raw_g = fmaf(af[e], s_fa[j + e], raw_g); g2 = fmaf(bfv[e], s_ga[j + e], g2); }
+    }
+    const size_t o = (size_t)row * C + ch;
+    w.qn[o] = q * rsqrtf(qs + 1e-6f) * p.scale;
+    w.kn[o] = k * rsqrtf(ks + 1e-6f);
+    w.vo[o] = v;
+    w.decay[o] = __expf(p.lower_bound * sigmoidf_(a_exp * (raw_g + dtb)));
+    w.gate[o] = sigmoidf_(g2);
+    if (t == 0) w.beta[(size_t)row * p.H + h] = sigmoidf_(pr[p.off_beta + h]);
+    pdl_launch_dependents();
+}
+
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gsrc) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__global__ void __launch_bounds__(kD) kda_recur_kernel(KdaParams p, KdaScratch w) {
+    __shared__ __align__(16) float sm[2][3][kTCH][kD];       // [buffer][q,k,decay][token][channel]
+    const int seq = blockIdx.x, h = blockIdx.y, t = threadIdx.x;
+    pdl_wait();
+    pdl_launch_dependents();
+    const int row0 = p.seq_row0[seq], nrows = p.seq_nrows[seq], slot = p.seq_slot[seq];
+    if (nrows <= 0) return;
+    const int C = p.H * kD, ch = h * kD + t;
+    float S[kD];
+    float* sp = p.state + (((size_t)slot * p.H + h) * kD + t) * kD;
+#pragma unroll
+    for (int c = 0; c < kD; c += 4) {
+        float4 v = *reinterpret_cast<const float4*>(sp + c);
+        S[c] = v.x; S[c + 1] = v.y; S[c + 2] = v.z; S[c + 3] = v.w;
+    }
+    const int nchunks = (nrows + kTCH - 1) / kTCH;
+    auto issue = [&](int chunk, int buf) {
+        // kTCH tokens x 3 arrays x 128 floats = 768 float4 -> 6 per thread; rows past the end are clamped (unused)
+        for (int idx = t; idx < 3 * kTCH * (kD / 4); idx += kD) {
+            const int arr = idx / (kTCH * (kD / 4)), rem = idx % (kTCH * (kD / 4));
+            const int tok = rem / (kD / 4), c4 = rem % (kD / 4);
+            const int row = row0 + min(chunk * kTCH + tok, nrows - 1);
+            const float* src = (arr == 0 ? w.qn : (arr == 1 ? w.kn : w.decay)) + (size_t)row * C + h * kD + c4 * 4;
+            cp_async_16(&sm[buf][arr][tok][c4 * 4], src);
+        }
+        cp_async_commit();
+    };
+    issue(0, 0);
+    for (int chunk = 0; chunk < nchunks; ++chunk) {
+        const int buf = chunk & 1;
+        if (chunk + 1 < nchunks) issue(chunk + 1, buf ^ 1); else cp_async_commit();
+        // this thread's v and beta for the chunk
+        float vv[kTCH], bb[kTCH];
+#pragma unroll
+        for (int j = 0; j < kTCH; ++j) {
+            const int row = row0 + min(chunk * kTCH + j, nrows - 1);
+            vv[j] = w.vo[(size_t)row * C + ch];
+            bb[j] = w.beta[(size_t)row * p.H + h];
+        }
+        cp_async_wait<1>();
+        __syncthreads();
+        const int ntok = min(kTCH, nrows - chunk * kTCH);
+#pragma unroll 1
+        for (int j = 0; j < ntok; ++j) {
+            const float4* q4 = reinterpret_cast<const float4*>(sm[buf][0][j]);
+            const float4* k4 = reinterpret_cast<const float4*>(sm[buf][1][j]);
+            const float4* d4 = reinterpret_cast<const float4*>(sm[buf][2][j]);
+            float sk = 0.f;
+#pragma unroll
+            for (int c = 0; c < kD / 4; ++c) {
+                const float4 d = d4[c], k = k4[c];
+                S[4 * c] *= d.x; sk = fmaf(S[4 * c], k.x, sk);
+                S[4 * c + 1] *= d.y; sk = fmaf(S[4 * c + 1], k.y, sk);
+                S[4 * c + 2] *= d.z; sk = fmaf(S[4 * c + 2], k.z, sk);
+                S[4 * c + 3] *= d.w; sk = fmaf(S[4 * c + 3], k.w, sk);
+            }
+            float vj = vv[0], bj = bb[0];
+#pragma unroll
+            for (int u = 1; u < kTCH; ++u) if (u == j) { vj = vv[u]; bj = bb[u]; }
+            const float err = (vj - sk) * bj;
+            float o = 0.f;
+#pragma unroll
+            for (int c = 0; c < kD / 4; ++c) {
+                const float4 k = k4[c], q = q4[c];
+                S[4 * c] = fmaf(err, k.x, S[4 * c]); o = fmaf(S[4 * c], q.x, o);
+                S[4 * c + 1] = fmaf(err, k.y, S[4 * c + 1]); o = fmaf(S[4 * c + 1], q.y, o);
+                S[4 * c + 2] = fmaf(err, k.z, S[4 * c + 2]); o = fmaf(S[4 * c + 2], q.z, o);
+                S[4 * c + 3] = fmaf(err, k.w, S[4 * c + 3]); o = fmaf(S[4 * c + 3], q.w, o);
+            }
+            w.vo[(size_t)(row0 + chunk * kTCH + j) * C + ch] = o;
+        }
+        __syncthreads();                                     // everyone is done with `buf` before it is refilled
+    }
+    cp_async_wait<0>();
+#pragma unroll
+    for (int c = 0; c < kD; c += 4) *reinterpret_cast<float4*>(sp + c) = make_float4(S[c], S[c + 1], S[c + 2], S[c + 3]);
+    // conv history = the last three raw rows (older taps come from the previous history when the step was short)
+#pragma unroll
+    for (int a = 0; a < 3; ++a) {
+        float* cs = p.conv_state + (((size_t)slot * 3 + a) * C + ch) * 3;
+        const int off = a == 0 ? p.off_q : (a == 1 ? p.off_k : p.off_v);
+        float nh[3];
+#pragma unroll
+        for (int d = 0; d < 3; ++d) {
+            const int i = nrows - 3 + d;                     // row index inside the step for new tap d
+            nh[d] = i >= 0 ? p.proj[(size_t)(row0 + i) * p.ldp + off + ch] : cs[3 + i];
+        }
+#pragma unroll
+        for (int d = 0; d < 3; ++d) cs[d] = nh[d];
+    }
+    pdl_launch_dependents();
+}
+
+__global__ void __launch_bounds__(kD) kda_out_kernel(KdaParams p, KdaScratch w) {
+    __shared__ float s_red[33];
+    const int row = blockIdx.x, h = blockIdx.y, t = threadIdx.x;
+    const int C = p.H * kD, ch = h * kD + t;
+    const float ow = p.onorm_w[t];
+    pdl_wait();
+    pdl_launch_dependents();
+    const float o = w.vo[(size_t)row * C + ch];
+    const float os = block_sum(o * o, s_red);
+    p.out[(size_t)row * C + ch] = __float2bfloat16(o * rsqrtf(os / (float)kD + p.eps) * ow * w.gate[(size_t)row * C + ch]);
+    pdl_launch_dependents();
+}
+
 }  // namespace lsb
 using namespace lsb;
 
@@ -126,7 +316,7 @@ LSB_API int lsb_kda_forward(const void* proj, int ldp, int off_q, int off_k, int
                             const void* conv_k, const void* conv_v, const void* a_exp, const void* dt_bias,
                             const void* onorm_w, void* state, void* conv_state, const void* seq_row0,
                             const void* seq_nrows, const void* seq_slot, void* out, int nseq, int H, int head_dim,
-                            float scale, float lower_bound, float eps, void* stream) {
+                            float scale, float lower_bound, float eps, int total_rows, void* scratch, void* stream) {
     if (head_dim != kD || rank > 128 || rank % 8) return -1;
     KdaParams p;
     p.proj = (const float*)proj; p.ldp = ldp; p.off_q = off_q; p.off_k = off_k; p.off_v = off_v; p.off_beta = off_beta;
@@ -136,6 +326,17 @@ LSB_API int lsb_kda_forward(const void* proj, int ldp, int off_q, int off_k, int
     p.state = (float*)state; p.conv_state = (float*)conv_state; p.seq_row0 = (const int*)seq_row0;
     p.seq_nrows = (const int*)seq_nrows; p.seq_slot = (const int*)seq_slot; p.out = (bf16*)out; p.H = H;
     p.scale = scale; p.lower_bound = lower_bound; p.eps = eps;
-    launch_pdl((kda_kernel), dim3(nseq, H), kD, 0, (cudaStream_t)stream, p);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (scratch && total_rows >= 8) {
+        // scratch: fp32 [5][total_rows][H*128] followed by [total_rows][H]
+        const size_t n = (size_t)total_rows * H * kD;
+        float* b = (float*)scratch;
+        KdaScratch w{b, b + n, b + 2 * n, b + 3 * n, b + 4 * n, b + 5 * n};
+        launch_pdl((kda_prep_kernel), dim3(total_rows, H), kD, 0, st, p, w, nseq);
+        launch_pdl((kda_recur_kernel), dim3(nseq, H), kD, 0, st, p, w);
+        launch_pdl((kda_out_kernel), dim3(total_rows, H), kD, 0, st, p, w);
+    } else {
+        launch_pdl((kda_kernel), dim3(nseq, H), kD, 0, st, p);
+    }
     LSB_CHECK_LAUNCH();
 }

@@ -119,6 +119,22 @@ __global__ void __launch_bounds__(256) batched_gemv_kernel(bf16* __restrict__ ou
     pdl_launch_dependents();
 }
 
+// RoPE of the query rope half for the many-row path (the GEMM part runs on the tensor cores).
+__global__ void rope_tail_kernel(bf16* __restrict__ out, const bf16* __restrict__ x, int N, int K, long long xs_m, long long xs_b,
+                                 long long os_m, long long os_b, int dr, const float* __restrict__ inv_freq, const int* __restrict__ row_pos) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int m = blockIdx.x, b = blockIdx.y;
+    const bf16* xp = x + (size_t)m * xs_m + (size_t)b * xs_b + K;
+    bf16* o = out + (size_t)m * os_m + (size_t)b * os_b + N;
+    for (int i = threadIdx.x; i < dr / 2; i += blockDim.x) {
+        float a0 = __bfloat162float(xp[2 * i]), a1 = __bfloat162float(xp[2 * i + 1]);
+        rope_pair(a0, a1, (float)row_pos[m], inv_freq[i]);
+        o[2 * i] = __float2bfloat16(a0); o[2 * i + 1] = __float2bfloat16(a1);
+    }
+    pdl_launch_dependents();
+}
+
 constexpr int kHG = 16;   // heads per block
 constexpr int kTK = 32;   // cache rows per tile
 
@@ -341,6 +357,9 @@ __global__ void __launch_bounds__(128) mla_combine_kernel(bf16* __restrict__ out
 }  // namespace lsb
 using namespace lsb;
 
+extern "C" int lsb_gemm_bf16_tc(void* out, const void* x, const void* w, const void* bias, int M, int N, int K, int ldx, int ldw,
+                                int ldo, int out_bf16, void* partial, long long partial_cap, void* err, void* stream);
+
 LSB_API int lsb_kv_row_bytes(int fmt, int dl, int dr) { return kv_row_bytes(fmt, dl, dr); }
 
 LSB_API int lsb_mla_prep(const void* proj, int ldp, int off_qa, int q_lora, int off_kv, int dl, int dr,
@@ -363,6 +382,18 @@ LSB_API int lsb_batched_gemv_bf16(void* out, const void* x, const void* w, int M
     if (K % 8 || xs_m % 8 || xs_b % 8) return -1;
     cudaStream_t st = (cudaStream_t)stream;
     dim3 grid((N + 15) / 16, B);
+    if (M >= 32 && K % 8 == 0 && xs_m % 8 == 0 && xs_b % 8 == 0 && os_b % 8 == 0 && (((uintptr_t)x | (uintptr_t)w) & 15) == 0) {
+        // many rows: one tensor-core GEMM per head ([M, K] x [N, K]^T), the rope tail on the side
+        for (int b = 0; b < B; ++b) {
+            const int rc = lsb_gemm_bf16_tc((bf16*)out + (size_t)b * os_b, (const bf16*)x + (size_t)b * xs_b, (const bf16*)w + (size_t)b * N * K, nullptr,
+                                            M, N, K, (int)xs_m, K, (int)os_m, 1, nullptr, 0, nullptr, stream);
+            if (rc) return rc;
+        }
+        if (dr > 0)
+            launch_pdl((rope_tail_kernel), dim3(M, B), 32, 0, st, (bf16*)out, (const bf16*)x, N, K, xs_m, xs_b, os_m, os_b, dr, (const float*)inv_freq,
+                       (const int*)row_pos);
+        LSB_CHECK_LAUNCH();
+    }
     for (int m0 = 0; m0 < M;) {
         const int rem = M - m0, mt = rem >= 4 ? 4 : (rem >= 2 ? 2 : 1);
         bf16* o = (bf16*)out + (size_t)m0 * os_m;

@@ -67,8 +67,8 @@ constexpr int kHcPerWarp = 6;       // mixing logits per warp (4 warps x 6 = 24)
 __global__ void __launch_bounds__(128) mhc_post_partial_kernel(float* __restrict__ residual, const float* __restrict__ x,
                                                                const float* __restrict__ post, const float* __restrict__ comb,
                                                                const float* __restrict__ fn, float* __restrict__ part,
-                                                               int hidden, int n, int mode, PeerComm comm) {
-    const int r = blockIdx.x, c = blockIdx.y, lane = threadIdx.x & 31, og = threadIdx.x >> 5;
+                                                               int hidden, int n, int mode, int rows, int rows_per_block, PeerComm comm) {
+    const int c = blockIdx.y, lane = threadIdx.x & 31, og = threadIdx.x >> 5;
     const int h = c * kHcChunk + lane;
     const int nout = 2 * n + n * n;
     // mixing-matrix rows do not depend on the previous kernel: fetch them before the dependency wait
@@ -81,50 +81,51 @@ __global__ void __launch_bounds__(128) mhc_post_partial_kernel(float* __restrict
     }
     pdl_wait();
     pdl_launch_dependents();
-    float res[kHcMax];
-    float* rp = residual + (size_t)r * n * hidden;
-    float xv;
+    unsigned epoch = 0;
     if (comm.nranks && mode == 1) {
-        const unsigned epoch = *comm.epoch;
+        epoch = *comm.epoch;
         comm_wait(comm, epoch);
-        xv = comm_reduce(comm, epoch, (size_t)r * hidden + h);
-    } else {
-        xv = x[(size_t)r * hidden + h];
     }
-    if (mode == 0) {
+    // a block serves `rows_per_block` consecutive rows with the same register-resident mixing rows
+    for (int r = blockIdx.x * rows_per_block; r < min(rows, (int)(blockIdx.x + 1) * rows_per_block); ++r) {
+        float res[kHcMax];
+        float* rp = residual + (size_t)r * n * hidden;
+        const float xv = (comm.nranks && mode == 1) ? comm_reduce(comm, epoch, (size_t)r * hidden + h) : x[(size_t)r * hidden + h];
+        if (mode == 0) {
 #pragma unroll
-        for (int j = 0; j < kHcMax; ++j) res[j] = j < n ? xv : 0.f;
-    } else {
-        float old[kHcMax];
+            for (int j = 0; j < kHcMax; ++j) res[j] = j < n ? xv : 0.f;
+        } else {
+            float old[kHcMax];
 #pragma unroll
-        for (int i = 0; i < kHcMax; ++i) old[i] = i < n ? rp[(size_t)i * hidden + h] : 0.f;
+            for (int i = 0; i < kHcMax; ++i) old[i] = i < n ? rp[(size_t)i * hidden + h] : 0.f;
 #pragma unroll
-        for (int j = 0; j < kHcMax; ++j) {
-            float a = 0.f;
-            if (j < n) {
-                a = post[r * n + j] * xv;
-                for (int i = 0; i < n; ++i) a += comb[(r * n + i) * n + j] * old[i];
+            for (int j = 0; j < kHcMax; ++j) {
+                float a = 0.f;
+                if (j < n) {
+                    a = post[r * n + j] * xv;
+                    for (int i = 0; i < n; ++i) a += comb[(r * n + i) * n + j] * old[i];
+                }
+                res[j] = a;
             }
-            res[j] = a;
         }
-    }
-    float* po = part + ((size_t)r * gridDim.y + c) * (kHcOut + 1);
+        float* po = part + ((size_t)r * gridDim.y + c) * (kHcOut + 1);
 #pragma unroll
-    for (int i = 0; i < kHcPerWarp; ++i) {
-        float a = 0.f;
+        for (int i = 0; i < kHcPerWarp; ++i) {
+            float a = 0.f;
 #pragma unroll
-        for (int j = 0; j < kHcMax; ++j) a = fmaf(res[j], f[i][j], a);
-        a = warp_sum(a);
-        const int o = og * kHcPerWarp + i;
-        if (lane == 0 && o < kHcOut) po[o] = a;
-    }
-    if (og == 0) {
-        float ss = 0.f;
+            for (int j = 0; j < kHcMax; ++j) a = fmaf(res[j], f[i][j], a);
+            a = warp_sum(a);
+            const int o = og * kHcPerWarp + i;
+            if (lane == 0 && o < kHcOut) po[o] = a;
+        }
+        if (og == 0) {
+            float ss = 0.f;
 #pragma unroll
-        for (int j = 0; j < kHcMax; ++j)
-            if (j < n) { rp[(size_t)j * hidden + h] = res[j]; ss += res[j] * res[j]; }
-        ss = warp_sum(ss);
-        if (lane == 0) po[kHcOut] = ss;
+            for (int j = 0; j < kHcMax; ++j)
+                if (j < n) { rp[(size_t)j * hidden + h] = res[j]; ss += res[j] * res[j]; }
+            ss = warp_sum(ss);
+            if (lane == 0) po[kHcOut] = ss;
+        }
     }
     pdl_launch_dependents();
 }
@@ -306,8 +307,9 @@ LSB_API int lsb_mhc_post_pre(void* out_x, void* residual, const void* x, void* p
     if (hidden % kHcChunk || n > kHcMax) return -1;
     cudaStream_t st = (cudaStream_t)stream;
     const int nchunks = hidden / kHcChunk;
-    launch_pdl((mhc_post_partial_kernel), dim3(rows, nchunks), 128, 0, st, (float*)residual, (const float*)x, (const float*)post,
-                                                                    (const float*)comb, (const float*)fn, (float*)part, hidden, n, mode, comm_from_host(comm));
+    const int rpb = rows >= 64 ? 16 : 1;      // many rows: amortise the mixing-matrix loads over 16 rows per block
+    launch_pdl((mhc_post_partial_kernel), dim3((rows + rpb - 1) / rpb, nchunks), 128, 0, st, (float*)residual, (const float*)x, (const float*)post,
+                                                                    (const float*)comb, (const float*)fn, (float*)part, hidden, n, mode, rows, rpb, comm_from_host(comm));
     launch_pdl((mhc_finalize_kernel), rows, 512, (size_t)hidden * 4, st, (bf16*)out_x, (const float*)residual, (const float*)part,
                                                               (const float*)hc_scale, (const float*)hc_base, (const float*)norm_w,
                                                               (float*)post, (float*)comb, hidden, n, nchunks, iters, hc_eps, rms_eps, post_mult);

@@ -261,6 +261,8 @@ class Workspace:
         self.proj = z(R, m.max_proj)
         C = m.Hk * cfg.kda_head_dim
         self.kda_out = z(R, max(C, 1), dtype=b16)
+        # many-row KDA path: q / k / v->o / decay / gate [R, C] and beta [R, heads], fp32
+        self.kda_scratch = z(5 * R * C + R * m.Hk) if (C > 0 and R >= 8) else None
         Hh = m.Hh
         self.q_c = z(R, max(cfg.q_lora, 1), dtype=b16)
         self.qproj = z(R, m.max_qb, dtype=b16)
@@ -697,7 +699,7 @@ class DeviceModel:
                  3 * C + self.Hk + cfg.kda_rank, cfg.kda_rank, L["kda_fb"], L["kda_gb"], L["kda_conv_q"], L["kda_conv_k"],
                  L["kda_conv_v"], L["kda_a_exp"], L["kda_dt_bias"], L["kda_o_norm"], self.kda_state[i], self.kda_conv[i],
                  ws.seq_row0, ws.seq_nrows, ws.seq_slot, ws.kda_out, nseq, self.Hk, cfg.kda_head_dim,
-                 cfg.kda_head_dim ** -0.5, cfg.kda_lower_bound, cfg.rms_eps)
+                 cfg.kda_head_dim ** -0.5, cfg.kda_lower_bound, cfg.rms_eps, R, ws.kda_scratch)
         L["kda_o"](ws.sub, ws.kda_out, R, comm=self._cp)
         self._reduce(ws, R)
 

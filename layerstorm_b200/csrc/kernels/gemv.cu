@@ -170,10 +170,74 @@ LSB_API int lsb_gemv_bf16(void* out, const void* x, const void* w, const void* b
                        out_bf16, (cudaStream_t)stream, comm);
 }
 
+namespace lsb {
+// Many-row product with fp32 weights (router logits of a prefill chunk): out[m][n] = alpha * sum_k x[m][k] * W[n][k] + bias[n].
+// 64 x 64 output tile per block, 4 x 4 outputs per thread, K in steps of 16 through shared memory; fp32 FMAs in a fixed
+// k order (the routing decision must not depend on the launch shape).
+__global__ void __launch_bounds__(256) sgemm_f32w_kernel(void* __restrict__ out, const bf16* __restrict__ x, const float* __restrict__ w,
+                                                         const float* __restrict__ bias, int M, int N, int K, int ldx, int ldw, int ldo,
+                                                         float alpha, int out_bf16) {
+    __shared__ float xs[16][64 + 4], ws[16][64 + 4];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64, t = threadIdx.x;
+    const int tm = (t >> 4) * 4, tn = (t & 15) * 4;
+    const int lr = t >> 2, lk = (t & 3) * 4;                 // loader: row lr (0..63), 4 consecutive k
+    float acc[4][4] = {};
+    for (int k0 = 0; k0 < K; k0 += 16) {
+        {
+            const int m = m0 + lr, n = n0 + lr;
+            float xv[4] = {0, 0, 0, 0}, wv[4] = {0, 0, 0, 0};
+            if (m < M && k0 + lk < K) {
+                const uint2 u = *reinterpret_cast<const uint2*>(x + (size_t)m * ldx + k0 + lk);
+                xv[0] = bf16_lo(u.x); xv[1] = bf16_hi(u.x); xv[2] = bf16_lo(u.y); xv[3] = bf16_hi(u.y);
+            }
+            if (n < N && k0 + lk < K) {
+                const float4 f = *reinterpret_cast<const float4*>(w + (size_t)n * ldw + k0 + lk);
+                wv[0] = f.x; wv[1] = f.y; wv[2] = f.z; wv[3] = f.w;
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { xs[lk + i][lr] = xv[i]; ws[lk + i][lr] = wv[i]; }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+            const float4 a = *reinterpret_cast<const float4*>(&xs[k][tm]);
+            const float4 b = *reinterpret_cast<const float4*>(&ws[k][tn]);
+            const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int m = m0 + tm + i;
+        if (m >= M) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tn + j;
+            if (n >= N) continue;
+            const float v = acc[i][j] * alpha + (bias ? bias[n] : 0.f);
+            if (out_bf16) reinterpret_cast<bf16*>(out)[(size_t)m * ldo + n] = __float2bfloat16(v);
+            else reinterpret_cast<float*>(out)[(size_t)m * ldo + n] = v;
+        }
+    }
+    pdl_launch_dependents();
+}
+}  // namespace lsb
+
 // W: fp32 [N, ldw] (router / hyper-connection mixing matrices). K % 4 == 0.
 LSB_API int lsb_gemv_f32w(void* out, const void* x, const void* w, const void* bias, int M, int N, int K, int ldx,
                           int ldw, int ldo, float alpha, int out_bf16, void* stream) {
     if (K % 4 || ldw % 4 || ldx % 4) return -1;
+    if (M >= 16) {
+        launch_pdl((sgemm_f32w_kernel), dim3((N + 63) / 64, (M + 63) / 64), 256, 0, (cudaStream_t)stream, out, (const bf16*)x, (const float*)w,
+                   (const float*)bias, M, N, K, ldx, ldw, ldo, alpha, out_bf16);
+        LSB_CHECK_LAUNCH();
+    }
     return launch_gemv(MatF32{(const float*)w, ldw}, (const bf16*)x, ldx, out, ldo, M, N, K, alpha, (const float*)bias,
                        out_bf16, (cudaStream_t)stream);
 }

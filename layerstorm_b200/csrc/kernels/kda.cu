@@ -135,64 +135,78 @@ struct KdaScratch {
     float* beta;                                                    // [rows, H]
 };
 
-__global__ void __launch_bounds__(kD) kda_prep_kernel(KdaParams p, KdaScratch w, int nseq) {
+constexpr int kPrepRows = 16;   // rows per prep block (amortises staging the head's low-rank matrices)
+
+__global__ void __launch_bounds__(kD) kda_prep_kernel(KdaParams p, KdaScratch w, int nseq, int total_rows) {
+    extern __shared__ __align__(16) uint8_t prep_sm[];
+    bf16* s_fb = reinterpret_cast<bf16*>(prep_sm);            // [rank][128] transposed: lane-contiguous reads
+    bf16* s_gb = s_fb + (size_t)p.rank * kD;
     __shared__ float s_fa[128], s_ga[128], s_red[33];
-    const int row = blockIdx.x, h = blockIdx.y, t = threadIdx.x;
+    const int h = blockIdx.y, t = threadIdx.x;
     const int C = p.H * kD, ch = h * kD + t;
     float wq[4], wk[4], wv[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) { wq[j] = p.conv_q[ch * 4 + j]; wk[j] = p.conv_k[ch * 4 + j]; wv[j] = p.conv_v[ch * 4 + j]; }
     const float a_exp = p.a_exp[h], dtb = p.dt_bias[ch];
-    pdl_wait();
-    pdl_launch_dependents();
-    int row0 = -1, slot = 0;
-    for (int s = 0; s < nseq; ++s) {
-        const int r0 = p.seq_row0[s], n = p.seq_nrows[s];
-        if (row >= r0 && row < r0 + n) { row0 = r0; slot = p.seq_slot[s]; }
-    }
-    if (row0 < 0) return;                                    // row belongs to no sequence of this step
-    const int i = row - row0;
-    float rq[4], rk[4], rv[4];                               // raw taps, oldest first; [3] = this row
+    {   // weights do not depend on the previous kernel: stage them before the dependency wait
+        const bf16* fb = p.f_b + (size_t)ch * p.rank;
+        const bf16* gb = p.g_b + (size_t)ch * p.rank;
+        for (int j = 0; j < p.rank; j += 8) {
+            const uint4 a = __ldg(reinterpret_cast<const uint4*>(fb + j)), b = __ldg(reinterpret_cast<const uint4*>(gb + j));
+            const bf16* ap = reinterpret_cast<const bf16*>(&a);
+            const bf16* bp = reinterpret_cast<const bf16*>(&b);
 #pragma unroll
-    for (int d = 0; d < 4; ++d) {
-        const int back = 3 - d;                              // tap d is `back` rows before this one
-        if (i - back >= 0) {
-            const float* pr = p.proj + (size_t)(row - back) * p.ldp;
-            rq[d] = pr[p.off_q + ch]; rk[d] = pr[p.off_k + ch]; rv[d] = pr[p.off_v + ch];
-        } else {
-            const int hi = 3 + i - back;                     // 0..2 in the saved history
-            rq[d] = p.conv_state[(((size_t)slot * 3 + 0) * C + ch) * 3 + hi];
-            rk[d] = p.conv_state[(((size_t)slot * 3 + 1) * C + ch) * 3 + hi];
-            rv[d] = p.conv_state[(((size_t)slot * 3 + 2) * C + ch) * 3 + hi];
+            for (int e = 0; e < 8; ++e) { s_fb[(size_t)(j + e) * kD + t] = ap[e]; s_gb[(size_t)(j + e) * kD + t] = bp[e]; }
         }
     }
-    const float* pr = p.proj + (size_t)row * p.ldp;
-    float q = rq[0] * wq[0]; q += rq[1] * wq[1]; q += rq[2] * wq[2]; q += rq[3] * wq[3];
-    float k = rk[0] * wk[0]; k += rk[1] * wk[1]; k += rk[2] * wk[2]; k += rk[3] * wk[3];
-    float v = rv[0] * wv[0]; v += rv[1] * wv[1]; v += rv[2] * wv[2]; v += rv[3] * wv[3];
-    q = siluf_(q); k = siluf_(k); v = siluf_(v);
-    if (t < p.rank) { s_fa[t] = pr[p.off_fa + t]; s_ga[t] = pr[p.off_ga + t]; }
-    const float qs = block_sum(q * q, s_red);
-    const float ks = block_sum(k * k, s_red);
-    __syncthreads();
-    const bf16* fb = p.f_b + (size_t)ch * p.rank;
-    const bf16* gb = p.g_b + (size_t)ch * p.rank;
-    float raw_g = 0.f, g2 = 0.f;
-    for (int j = 0; j < p.rank; j += 8) {
-        uint4 a = __ldg(reinterpret_cast<const uint4*>(fb + j));
-        uint4 b = __ldg(reinterpret_cast<const uint4*>(gb + j));
-        float af[8], bfv[8];
-        unpack_bf16x8(a, af); unpack_bf16x8(b, bfv);
+    pdl_wait();
+    pdl_launch_dependents();
+    for (int row = blockIdx.x * kPrepRows; row < min(total_rows, (int)(blockIdx.x + 1) * kPrepRows); ++row) {
+        int row0 = -1, slot = 0;
+        for (int s = 0; s < nseq; ++s) {
+            const int r0 = p.seq_row0[s], n = p.seq_nrows[s];
+            if (row >= r0 && row < r0 + n) { row0 = r0; slot = p.seq_slot[s]; }
+        }
+        if (row0 < 0) continue;                              // row belongs to no sequence of this step (uniform per block)
+        const int i = row - row0;
+        float rq[4], rk[4], rv[4];                           // raw taps, oldest first; [3] = this row
 #pragma unroll
-        for (int e = 0; e < 8; ++e) { raw_g = fmaf(af[e], s_fa[j + e], raw_g); g2 = fmaf(bfv[e], s_ga[j + e], g2); }
+        for (int d = 0; d < 4; ++d) {
+            const int back = 3 - d;                          // tap d is `back` rows before this one
+            if (i - back >= 0) {
+                const float* pr = p.proj + (size_t)(row - back) * p.ldp;
+                rq[d] = pr[p.off_q + ch]; rk[d] = pr[p.off_k + ch]; rv[d] = pr[p.off_v + ch];
+            } else {
+                const int hi = 3 + i - back;                 // 0..2 in the saved history
+                rq[d] = p.conv_state[(((size_t)slot * 3 + 0) * C + ch) * 3 + hi];
+                rk[d] = p.conv_state[(((size_t)slot * 3 + 1) * C + ch) * 3 + hi];
+                rv[d] = p.conv_state[(((size_t)slot * 3 + 2) * C + ch) * 3 + hi];
+            }
+        }
+        const float* pr = p.proj + (size_t)row * p.ldp;
+        float q = rq[0] * wq[0]; q += rq[1] * wq[1]; q += rq[2] * wq[2]; q += rq[3] * wq[3];
+        float k = rk[0] * wk[0]; k += rk[1] * wk[1]; k += rk[2] * wk[2]; k += rk[3] * wk[3];
+        float v = rv[0] * wv[0]; v += rv[1] * wv[1]; v += rv[2] * wv[2]; v += rv[3] * wv[3];
+        q = siluf_(q); k = siluf_(k); v = siluf_(v);
+        __syncthreads();                                     // previous row's readers are done with s_fa / s_ga
+        if (t < p.rank) { s_fa[t] = pr[p.off_fa + t]; s_ga[t] = pr[p.off_ga + t]; }
+        const float qs = block_sum(q * q, s_red);
+        const float ks = block_sum(k * k, s_red);
+        __syncthreads();
+        float raw_g = 0.f, g2 = 0.f;
+#pragma unroll 8
+        for (int j = 0; j < p.rank; ++j) {
+            raw_g = fmaf(__bfloat162float(s_fb[(size_t)j * kD + t]), s_fa[j], raw_g);
+            g2 = fmaf(__bfloat162float(s_gb[(size_t)j * kD + t]), s_ga[j], g2);
+        }
+        const size_t o = (size_t)row * C + ch;
+        w.qn[o] = q * rsqrtf(qs + 1e-6f) * p.scale;
+        w.kn[o] = k * rsqrtf(ks + 1e-6f);
+        w.vo[o] = v;
+        w.decay[o] = __expf(p.lower_bound * sigmoidf_(a_exp * (raw_g + dtb)));
+        w.gate[o] = sigmoidf_(g2);
+        if (t == 0) w.beta[(size_t)row * p.H + h] = sigmoidf_(pr[p.off_beta + h]);
     }
-    const size_t o = (size_t)row * C + ch;
-    w.qn[o] = q * rsqrtf(qs + 1e-6f) * p.scale;
-    w.kn[o] = k * rsqrtf(ks + 1e-6f);
-    w.vo[o] = v;
-    w.decay[o] = __expf(p.lower_bound * sigmoidf_(a_exp * (raw_g + dtb)));
-    w.gate[o] = sigmoidf_(g2);
-    if (t == 0) w.beta[(size_t)row * p.H + h] = sigmoidf_(pr[p.off_beta + h]);
     pdl_launch_dependents();
 }
 
@@ -249,28 +263,32 @@ __global__ void __launch_bounds__(kD) kda_recur_kernel(KdaParams p, KdaScratch w
             const float4* q4 = reinterpret_cast<const float4*>(sm[buf][0][j]);
             const float4* k4 = reinterpret_cast<const float4*>(sm[buf][1][j]);
             const float4* d4 = reinterpret_cast<const float4*>(sm[buf][2][j]);
-            float sk = 0.f;
+            // four independent accumulation chains per reduction: one warp per scheduler cannot hide a 128-long
+            // dependent FMA chain otherwise
+            float sk0 = 0.f, sk1 = 0.f, sk2 = 0.f, sk3 = 0.f;
 #pragma unroll
             for (int c = 0; c < kD / 4; ++c) {
                 const float4 d = d4[c], k = k4[c];
-                S[4 * c] *= d.x; sk = fmaf(S[4 * c], k.x, sk);
-                S[4 * c + 1] *= d.y; sk = fmaf(S[4 * c + 1], k.y, sk);
-                S[4 * c + 2] *= d.z; sk = fmaf(S[4 * c + 2], k.z, sk);
-                S[4 * c + 3] *= d.w; sk = fmaf(S[4 * c + 3], k.w, sk);
+                S[4 * c] *= d.x; sk0 = fmaf(S[4 * c], k.x, sk0);
+                S[4 * c + 1] *= d.y; sk1 = fmaf(S[4 * c + 1], k.y, sk1);
+                S[4 * c + 2] *= d.z; sk2 = fmaf(S[4 * c + 2], k.z, sk2);
+                S[4 * c + 3] *= d.w; sk3 = fmaf(S[4 * c + 3], k.w, sk3);
             }
+            const float sk = (sk0 + sk1) + (sk2 + sk3);
             float vj = vv[0], bj = bb[0];
 #pragma unroll
             for (int u = 1; u < kTCH; ++u) if (u == j) { vj = vv[u]; bj = bb[u]; }
             const float err = (vj - sk) * bj;
-            float o = 0.f;
+            float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
             for (int c = 0; c < kD / 4; ++c) {
                 const float4 k = k4[c], q = q4[c];
-                S[4 * c] = fmaf(err, k.x, S[4 * c]); o = fmaf(S[4 * c], q.x, o);
-                S[4 * c + 1] = fmaf(err, k.y, S[4 * c + 1]); o = fmaf(S[4 * c + 1], q.y, o);
-                S[4 * c + 2] = fmaf(err, k.z, S[4 * c + 2]); o = fmaf(S[4 * c + 2], q.z, o);
-                S[4 * c + 3] = fmaf(err, k.w, S[4 * c + 3]); o = fmaf(S[4 * c + 3], q.w, o);
+                S[4 * c] = fmaf(err, k.x, S[4 * c]); o0 = fmaf(S[4 * c], q.x, o0);
+                S[4 * c + 1] = fmaf(err, k.y, S[4 * c + 1]); o1 = fmaf(S[4 * c + 1], q.y, o1);
+                S[4 * c + 2] = fmaf(err, k.z, S[4 * c + 2]); o2 = fmaf(S[4 * c + 2], q.z, o2);
+                S[4 * c + 3] = fmaf(err, k.w, S[4 * c + 3]); o3 = fmaf(S[4 * c + 3], q.w, o3);
             }
+            const float o = (o0 + o1) + (o2 + o3);
             w.vo[(size_t)(row0 + chunk * kTCH + j) * C + ch] = o;
         }
         __syncthreads();                                     // everyone is done with `buf` before it is refilled
@@ -332,7 +350,10 @@ LSB_API int lsb_kda_forward(const void* proj, int ldp, int off_q, int off_k, int
         const size_t n = (size_t)total_rows * H * kD;
         float* b = (float*)scratch;
         KdaScratch w{b, b + n, b + 2 * n, b + 3 * n, b + 4 * n, b + 5 * n};
-        launch_pdl((kda_prep_kernel), dim3(total_rows, H), kD, 0, st, p, w, nseq);
+        const size_t prep_smem = (size_t)2 * rank * kD * sizeof(bf16);
+        static bool prep_attr = false;
+        if (!prep_attr) { cudaFuncSetAttribute(kda_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * 128 * kD * (int)sizeof(bf16)); prep_attr = true; }
+        launch_pdl((kda_prep_kernel), dim3((total_rows + kPrepRows - 1) / kPrepRows, H), kD, prep_smem, st, p, w, nseq, total_rows);
         launch_pdl((kda_recur_kernel), dim3(nseq, H), kD, 0, st, p, w);
         launch_pdl((kda_out_kernel), dim3(total_rows, H), kD, 0, st, p, w);
     } else {

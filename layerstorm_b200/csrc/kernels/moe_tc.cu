@@ -19,8 +19,10 @@
 // Reference seams replaced: moe_permute + external grouped GEMM + fused SwiGLU + unpermute
 // (src/core/expert_device.h:31-52, E/smxx/permute/moe_permute.cu, G/sm120/gemm/grouped).
 #include "tc_common.cuh"
+#include <cstring>
 #include "gemv_core.cuh"
 #include "moe_fmt.cuh"
+#include "ep_comm.cuh"
 
 namespace lsb {
 using namespace tc;
@@ -199,6 +201,9 @@ struct MoeTcParams {
     float* y;             // down output, [npairs, H] fp32 in pair order
     float limit;
     int* miss_flag; int* err;
+    // expert-parallel mode (ep.nranks > 0): the gate/up kernel waits for the peers' token rows (phase 1) before its
+    // first load, the down kernel stores its rows straight into the token owners' buffers and publishes phase 2
+    EpComm ep;
 };
 
 template <int BN, bool GATEUP> struct MoeTcCfg {
@@ -241,12 +246,23 @@ __global__ void __launch_bounds__(MoeTcCfg<BN, GATEUP>::THREADS) moe_tc_ffn_kern
     }
     pdl_wait();
     pdl_launch_dependents();
+    const bool ep_mode = p.ep.nranks > 0;
+    const unsigned ep_epoch = ep_mode ? *p.ep.epoch + 1u : 0u;
+    const unsigned ep_blocks = gridDim.x * gridDim.y;
+    if (ep_mode && GATEUP) {
+        ep_wait(p.ep, 1, ep_epoch);                  // peers' rows have landed in this rank's staging buffer
+        asm volatile("fence.proxy.async;" ::: "memory");   // ... and are ordered before the TMA (async proxy) reads
+    }
     const int t = blockIdx.y;
-    if (t >= p.counters[0]) return;                  // uniform: no tile for this CTA
+    if (t >= p.counters[0]) {                        // uniform: no tile for this CTA
+        if (ep_mode && !GATEUP) ep_signal(p.ep, 2, ep_epoch, ep_blocks);
+        return;
+    }
     const int e = p.tile_expert[t], row0 = p.tile_row0[t], ncols = p.tile_n[t];
     const int slot = p.slot_of[e];
     if (slot < 0) {                                  // expert not resident on this GPU
         if (p.miss_flag && threadIdx.x == 0 && blockIdx.x == 0) atomicExch(p.miss_flag, e + 1);
+        if (ep_mode && !GATEUP) ep_signal(p.ep, 2, ep_epoch, ep_blocks);
         return;
     }
     if (warp == 1) tmem_alloc(tmem_holder, C::TMEM_COLS);
@@ -305,7 +321,9 @@ __global__ void __launch_bounds__(MoeTcCfg<BN, GATEUP>::THREADS) moe_tc_ffn_kern
         const bool is_up = GATEUP && row >= kTBM;
         const uint8_t* w = base + (GATEUP ? (is_up ? p.ef.off_up : p.ef.off_gate) : p.ef.off_down);
         const uint8_t* sf = base + (GATEUP ? (is_up ? p.ef.off_su : p.ef.off_sg) : p.ef.off_sd);
-        constexpr int PF = 2;                                  // stages fetched ahead of the one being converted
+        // stages fetched ahead of the one being converted: enough bytes in flight per SM to cover HBM latency
+        // (nvfp4: 6 x 8 KB, fp8: 3 x 16 KB, bf16: 2 x 32 KB per CTA)
+        constexpr int PF = FMT == 2 ? 6 : (FMT == 1 ? 3 : 2);
         typename CV::Raw raw[PF];
 #pragma unroll
         for (int j = 0; j < PF; ++j)
@@ -357,6 +375,9 @@ __global__ void __launch_bounds__(MoeTcCfg<BN, GATEUP>::THREADS) moe_tc_ffn_kern
                                 float gv = g[j] * sg, uv = u[j] * su;
                                 if (p.limit > 0.f) { gv = fminf(gv, p.limit); uv = fminf(fmaxf(uv, -p.limit), p.limit); }
                                 p.act[(size_t)(row0 + c0 + j) * NOUT + n] = __float2half_rn(siluf_(gv) * uv);
+                            } else if (ep_mode) {
+                                const int2 ra = p.ep.ret[p.ep.rank][row0 + c0 + j];      // (token owner, pair index there)
+                                p.ep.y[ra.x][(size_t)ra.y * NOUT + n] = g[j] * sg;        // NVLink store into the owner's buffer
                             } else {
                                 p.y[(size_t)p.sorted_pair[row0 + c0 + j] * NOUT + n] = g[j] * sg;
                             }
@@ -369,6 +390,7 @@ __global__ void __launch_bounds__(MoeTcCfg<BN, GATEUP>::THREADS) moe_tc_ffn_kern
     tc_fence_before();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem_d, C::TMEM_COLS);
+    if (ep_mode && !GATEUP) ep_signal(p.ep, 2, ep_epoch, ep_blocks);
     pdl_launch_dependents();
 }
 
@@ -416,7 +438,8 @@ LSB_API int lsb_moe_tc_gather(const void* x, const void* sorted_pair, const void
 // `b` is the fp16 token operand ([cap_rows, K], K = H for gate/up and F for down), 16-byte aligned.
 LSB_API int lsb_moe_tc_ffn(int gateup, const void* b, int cap_rows, const void* arena, const void* slot_of, const void* fmt_struct,
                            const void* tile_expert, const void* tile_row0, const void* tile_n, const void* counters,
-                           const void* sorted_pair, void* out, int BN, int max_tiles, float limit, void* miss_flag, void* err, void* stream) {
+                           const void* sorted_pair, void* out, int BN, int max_tiles, float limit, void* miss_flag, void* err,
+                           const void* ep, void* stream) {
     const ExpertFmt* ef = (const ExpertFmt*)fmt_struct;
     const int K = gateup ? ef->H : ef->F, nout = gateup ? ef->F : ef->H;
     if (K % kTBK || nout % kTBM || ((uintptr_t)b & 15)) return -1;
@@ -430,6 +453,7 @@ LSB_API int lsb_moe_tc_ffn(int gateup, const void* b, int cap_rows, const void* 
     p.counters = (const int*)counters; p.sorted_pair = (const int*)sorted_pair;
     p.act = gateup ? (__half*)out : nullptr; p.y = gateup ? nullptr : (float*)out;
     p.limit = limit; p.miss_flag = (int*)miss_flag; p.err = (int*)err;
+    if (ep) p.ep = *(const EpComm*)ep; else { memset(&p.ep, 0, sizeof(p.ep)); }
     cudaStream_t st = (cudaStream_t)stream;
     if (gateup) {
         switch (BN) {

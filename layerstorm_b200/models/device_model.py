@@ -672,9 +672,9 @@ class DeviceModel:
             nat.call("lsb_moe_tc_gather", ws.x, ws.tc_sorted, ws.tc_cnt, ws.tc_xs, P, S, cfg.hidden)
             tiles = min(ws.tc_tiles, P // ws.tc_bn + E_total + 1)
             nat.call("lsb_moe_tc_ffn", 1, ws.tc_xs, ws.tc_xs.shape[0], arena.data, arena.slot_of, efp, ws.tc_tile_e, ws.tc_tile_r0, ws.tc_tile_n,
-                     ws.tc_cnt, ws.tc_sorted, ws.tc_act, ws.tc_bn, tiles, cfg.swiglu_limit, ws.miss if self.tp_size == 1 else None, err)
+                     ws.tc_cnt, ws.tc_sorted, ws.tc_act, ws.tc_bn, tiles, cfg.swiglu_limit, ws.miss if self.tp_size == 1 else None, err, None)
             nat.call("lsb_moe_tc_ffn", 0, ws.tc_act, ws.tc_act.shape[0], arena.data, arena.slot_of, efp, ws.tc_tile_e, ws.tc_tile_r0, ws.tc_tile_n,
-                     ws.tc_cnt, ws.tc_sorted, ws.y, ws.tc_bn, tiles, 0.0, None, err)
+                     ws.tc_cnt, ws.tc_sorted, ws.y, ws.tc_bn, tiles, 0.0, None, err, None)
         elif fast_fp4 and R * S <= 72:
             # small batch: every (row, slot) pair streams its expert on its own - no grouping pass
             nat.call("lsb_moe_gateup", ws.x, arena.data, arena.slot_of, efp, ws.ids, None, None, None,

@@ -52,8 +52,8 @@ def test_grouped_ffn_matches_reference(fmt, BN, R):
     for _ in range(2):                                  # twice: barriers, TMEM and scratch are reusable
         nat.call("lsb_moe_tc_sort", ids, P, E, BN, srt, te, tr, tn, cnt)
         nat.call("lsb_moe_tc_gather", x, srt, cnt, xs, P, S, H)
-        nat.call("lsb_moe_tc_ffn", 1, xs, P, arena.data, arena.slot_of, efp, te, tr, tn, cnt, srt, act, BN, tiles, limit, miss, err)
-        nat.call("lsb_moe_tc_ffn", 0, act, P, arena.data, arena.slot_of, efp, te, tr, tn, cnt, srt, y, BN, tiles, 0.0, None, err)
+        nat.call("lsb_moe_tc_ffn", 1, xs, P, arena.data, arena.slot_of, efp, te, tr, tn, cnt, srt, act, BN, tiles, limit, miss, err, None)
+        nat.call("lsb_moe_tc_ffn", 0, act, P, arena.data, arena.slot_of, efp, te, tr, tn, cnt, srt, y, BN, tiles, 0.0, None, err, None)
     torch.cuda.synchronize()
     assert int(err) == 0
     assert int(miss) == 1                               # expert 0 (+1) was routed to but is not resident

@@ -21,3 +21,16 @@ def test_two_rank_engine_matches_oracle(name):
            "--master-port", "29533", os.path.join(HERE, "mgpu_worker.py"), name]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert "MGPU_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+@pytest.mark.parametrize("fmt", ["fp8_e4m3", "nvfp4"])
+def test_fused_expert_parallel_ffn(fmt):
+    """Dispatch and combine as P2P stores inside the kernels == fp32 reference == NCCL all-to-all baseline."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    n = 4 if torch.cuda.device_count() >= 4 else 2
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
+           "--master-port", "29537", os.path.join(HERE, "ep_worker.py"), fmt]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert "EP_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]

@@ -91,7 +91,7 @@ def main():
     ap.add_argument("--model", default="glm-5.3-flash")
     ap.add_argument("--ctx", type=int, default=8192)
     ap.add_argument("--batch", type=int, default=1)
-    ap.add_argument("--prefill-chunk", type=int, default=256)
+    ap.add_argument("--prefill-chunk", type=int, default=2048)
     ap.add_argument("--headroom-gib", type=float, default=2.5, help="HBM left free after weights (caches, workspaces, context)")
     ap.add_argument("--no-graph", action="store_true", help="eager launches (for per-kernel profiling)")
     ap.add_argument("--synthetic-fill", action="store_true", help="skip the real prefill; decode over an uninitialised cache")
@@ -126,7 +126,7 @@ def main():
     if world > 1:
         # in-kernel NVLink all-reduce buffers (peer-mapped); NCCL only bootstraps and serves prefill chunks
         from layerstorm_b200.parallel.symm import PeerComm
-        comm = PeerComm(4 * cfg.hidden, dev)
+        comm = PeerComm(max(4, args.batch, args.prefill_chunk) * cfg.hidden, dev)
         comm_amax = PeerComm(2 * max(args.batch, 4), dev)
         model.attach_comm(comm, comm_amax)
     max_ctx = args.ctx + args.steps + args.warmup + 64
@@ -224,7 +224,7 @@ def main():
                        "weights": f"experts {cfg.expert_quant}, attention {cfg.dense_quant}", "kv_cache": "fp8+bf16-rope, 64-token pages",
                        "l2": "inputs larger than L2 (each step streams ~20 GB of weights)",
                        "resident_expert_slots_per_layer_per_gpu": slots, "routed_experts": cfg.n_routed, "expert_miss_flag": miss, "comm_error_word": comm_err,
-                       "collectives": ("fused in-kernel NVLink all-reduce (P2P stores + flags), argmax exchange; NCCL for prefill chunks only"
+                       "collectives": ("fused in-kernel NVLink all-reduce (P2P stores + flags) in the GEMV / tcgen05-GEMM / MoE-combine epilogues, argmax exchange; no NCCL on the step path"
                                        if world > 1 else "none"),
                        "context_fill": "synthetic (uninitialised cache)" if args.synthetic_fill else "real chunked prefill"},
             "clocks": clocks,

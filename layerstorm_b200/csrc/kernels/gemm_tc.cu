@@ -13,6 +13,7 @@
 // This replaces the reference's CUDA-core tiled GEMM (src/compute/kernels/sm120/gemm/bf16_gemm.cu:156)
 // and the external FP8 GEMM launcher (G/sm120/gemm/fp8/fp8_gemm.h) for every M > 4.
 #include "tc_common.cuh"
+#include "comm.cuh"
 
 #include <map>
 #include <mutex>
@@ -30,6 +31,11 @@ struct GemmTcParams {
     const float* bias;             // [N] or null
     int M, N, K, out_bf16, splits, kb_per_split;
     int* err;
+    long long out_bs;              // batched mode: elements between consecutive batches of `out` (blockIdx.z = batch)
+    // fused all-reduce epilogue (row-parallel layers under tensor parallelism): instead of a local store, every tile of
+    // the fp32 partial is stored into this rank's slot of every peer's receive buffer over NVLink; the last CTA
+    // publishes the epoch.  The consuming kernel sums the slots in rank order.
+    PeerComm comm;
 };
 
 template <int BN> struct TcCfg {
@@ -41,7 +47,7 @@ template <int BN> struct TcCfg {
     static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 };
 
-template <int BN>
+template <int BN, bool BATCHED = false>
 __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, GemmTcParams p) {
     using C = TcCfg<BN>;
     extern __shared__ uint8_t smem_raw[];
@@ -52,7 +58,8 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_full + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * BM, m0 = blockIdx.y * BN, split = blockIdx.z;
+    const int n0 = blockIdx.x * BM, m0 = blockIdx.y * BN;
+    const int split = BATCHED ? 0 : blockIdx.z, batch = BATCHED ? blockIdx.z : 0;
     const int nkb_total = (p.K + BK - 1) / BK;
     const int kb0 = split * p.kb_per_split;
     const int kb1 = min(nkb_total, kb0 + p.kb_per_split);
@@ -73,6 +80,7 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
     const uint32_t tmem_d = *tmem_holder;
     pdl_wait();
     pdl_launch_dependents();
+    const unsigned next_epoch = p.comm.nranks ? *p.comm.epoch + 1u : 0u;
 
     if (warp == 0 && lane == 0) {
         // ---------------- TMA producer ----------------
@@ -85,8 +93,13 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
             if (!ok) break;
             uint8_t* a = smem + s * C::STAGE_BYTES;
             mbar_expect_tx(&full[s], C::STAGE_BYTES);
-            tma_load_2d(a, &map_w, &full[s], (kb0 + it) * BK, n0);
-            tma_load_2d(a + C::A_BYTES, &map_x, &full[s], (kb0 + it) * BK, m0);
+            if (BATCHED) {
+                tma_load_3d(a, &map_w, &full[s], (kb0 + it) * BK, n0, batch);
+                tma_load_3d(a + C::A_BYTES, &map_x, &full[s], (kb0 + it) * BK, m0, batch);
+            } else {
+                tma_load_2d(a, &map_w, &full[s], (kb0 + it) * BK, n0);
+                tma_load_2d(a + C::A_BYTES, &map_x, &full[s], (kb0 + it) * BK, m0);
+            }
             ++issued;
         }
         if (!ok) {
@@ -131,9 +144,10 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
                     for (int j = 0; j < 16; ++j) {
                         const int m = m0 + c0 + j;
                         if (m < p.M) {
-                            if (p.splits > 1) p.partial[((size_t)split * p.M + m) * p.N + n] = v[j];
-                            else if (p.out_bf16) reinterpret_cast<bf16*>(p.out)[(size_t)m * p.ldo + n] = __float2bfloat16(v[j] + b);
-                            else reinterpret_cast<float*>(p.out)[(size_t)m * p.ldo + n] = v[j] + b;
+                            if (p.comm.nranks) comm_push(p.comm, next_epoch, (size_t)m * p.ldo + n, v[j]);
+                            else if (p.splits > 1) p.partial[((size_t)split * p.M + m) * p.N + n] = v[j];
+                            else if (p.out_bf16) reinterpret_cast<bf16*>(p.out)[(size_t)batch * p.out_bs + (size_t)m * p.ldo + n] = __float2bfloat16(v[j] + b);
+                            else reinterpret_cast<float*>(p.out)[(size_t)batch * p.out_bs + (size_t)m * p.ldo + n] = v[j] + b;
                         }
                     }
                 }
@@ -143,6 +157,7 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
     tc_fence_before();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem_d, C::TMEM_COLS);
+    if (p.comm.nranks) comm_signal(p.comm, next_epoch, gridDim.x * gridDim.y * gridDim.z);
     pdl_launch_dependents();
 }
 
@@ -190,6 +205,20 @@ int make_map_2d(CUtensorMap* map, const void* ptr, CUtensorMapDataType dt, int e
     return r == CUDA_SUCCESS ? 0 : -3;
 }
 
+// 3-D view [batch][rows][cols] with element strides (batch_stride, ld, 1); box [1][box_rows][box_cols].
+int make_map_3d(CUtensorMap* map, const void* ptr, CUtensorMapDataType dt, int esize, uint64_t rows, uint64_t cols, uint64_t ld_elems,
+                uint64_t batch, uint64_t batch_stride_elems, uint32_t box_rows, uint32_t box_cols) {
+    EncodeTiledFn enc = get_encode();
+    if (!enc) return -2;
+    cuuint64_t gdim[3] = {cols, rows, batch};
+    cuuint64_t gstr[2] = {ld_elems * (uint64_t)esize, batch_stride_elems * (uint64_t)esize};
+    cuuint32_t box[3] = {box_cols, box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(map, dt, 3, const_cast<void*>(ptr), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : -3;
+}
+
 struct MapKey {
     const void* p; uint64_t rows, cols, ld; uint32_t br, bc; int dt;
     bool operator<(const MapKey& o) const { return std::tie(p, rows, cols, ld, br, bc, dt) < std::tie(o.p, o.rows, o.cols, o.ld, o.br, o.bc, o.dt); }
@@ -222,8 +251,58 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const GemmTcP
     return (int)cudaGetLastError();
 }
 
+template <int BN>
+static int launch_tc_batched(const CUtensorMap& mw, const CUtensorMap& mx, const GemmTcParams& p, int batch, cudaStream_t st) {
+    using C = TcCfg<BN>;
+    static bool attr = false;
+    if (!attr) { cudaFuncSetAttribute(gemm_tc_kernel<BN, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM); attr = true; }
+    dim3 grid((p.N + BM - 1) / BM, (p.M + BN - 1) / BN, batch);
+    launch_pdl((gemm_tc_kernel<BN, true>), grid, 192, C::SMEM, st, mw, mx, p);
+    return (int)cudaGetLastError();
+}
+
 }  // namespace lsb
 using namespace lsb;
+
+// Batched product for b in [0, B): out[b][m][n] = sum_k x[b][m][k] * w[b][n][k] with element strides
+// x: (xs_b, ldx, 1), w: (ws_b, ldw, 1), out: (os_b, ldo, 1).  One launch, grid.z = batch.  Strides % 8 == 0.
+LSB_API int lsb_gemm_bf16_tc_batched(void* out, const void* x, const void* w, int M, int N, int K, int B, int ldx, long long xs_b, int ldw,
+                                     long long ws_b, int ldo, long long os_b, int out_bf16, void* err, void* stream) {
+    if (K % 8 || ldx % 8 || ldw % 8 || xs_b % 8 || ws_b % 8 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || B < 1 || B > 65535) return -1;
+    int BN = 16;
+    while (BN < 256 && BN < M) BN <<= 1;
+    static std::map<std::tuple<const void*, int, int, int, long long, int, int>, CUtensorMap> cache;      // per (ptr, rows, cols, ld, batch stride, B, box rows)
+    static std::mutex mu;
+    auto get = [&](const void* ptr, int rows, int cols, int ld, long long bs, int box_rows, CUtensorMap* o) -> int {
+        std::lock_guard<std::mutex> g(mu);
+        const auto key = std::make_tuple(ptr, rows, cols, ld, bs, B, box_rows);
+        auto it = cache.find(key);
+        if (it != cache.end()) { *o = it->second; return 0; }
+        CUtensorMap m;
+        const int rc = make_map_3d(&m, ptr, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows, cols, ld, B, bs, box_rows, BK);
+        if (rc) return rc;
+        if (cache.size() > 4096) cache.clear();
+        cache[key] = m;
+        *o = m;
+        return 0;
+    };
+    CUtensorMap mw, mx;
+    int rc = get(w, N, K, ldw, ws_b, BM, &mw);
+    if (rc) return rc;
+    rc = get(x, M, K, ldx, xs_b, BN, &mx);
+    if (rc) return rc;
+    GemmTcParams p;
+    p.out = out; p.ldo = ldo; p.partial = nullptr; p.bias = nullptr; p.M = M; p.N = N; p.K = K; p.out_bf16 = out_bf16; p.err = (int*)err;
+    p.splits = 1; p.kb_per_split = (K + BK - 1) / BK; p.out_bs = os_b; p.comm.nranks = 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (BN) {
+        case 16: return launch_tc_batched<16>(mw, mx, p, B, st);
+        case 32: return launch_tc_batched<32>(mw, mx, p, B, st);
+        case 64: return launch_tc_batched<64>(mw, mx, p, B, st);
+        case 128: return launch_tc_batched<128>(mw, mx, p, B, st);
+        default: return launch_tc_batched<256>(mw, mx, p, B, st);
+    }
+}
 
 LSB_API int lsb_gemm_tc_workspace_floats(int M, int N, int K) {
     // upper bound on split-K partial storage: at most 16 splits
@@ -234,8 +313,9 @@ LSB_API int lsb_gemm_tc_workspace_floats(int M, int N, int K) {
 // partial: fp32 scratch of partial_cap floats (split-K is limited to what fits) or null to disable split-K.
 // err: int error word (0 = ok; 1-3 = a bounded pipeline wait gave up).
 LSB_API int lsb_gemm_bf16_tc(void* out, const void* x, const void* w, const void* bias, int M, int N, int K, int ldx, int ldw,
-                             int ldo, int out_bf16, void* partial, long long partial_cap, void* err, void* stream) {
+                             int ldo, int out_bf16, void* partial, long long partial_cap, void* err, const void* comm, void* stream) {
     if (K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return -1;
+    if (comm) { partial = nullptr; if (out_bf16 || bias || (long long)M * ldo > ((const PeerComm*)comm)->cap) return -1; }
     cudaStream_t st = (cudaStream_t)stream;
     int BN = 16;
     while (BN < 256 && BN < M) BN <<= 1;
@@ -246,7 +326,8 @@ LSB_API int lsb_gemm_bf16_tc(void* out, const void* x, const void* w, const void
     if (rc) return rc;
     GemmTcParams p;
     p.out = out; p.ldo = ldo; p.partial = (float*)partial; p.bias = (const float*)bias; p.M = M; p.N = N; p.K = K;
-    p.out_bf16 = out_bf16; p.err = (int*)err;
+    p.out_bf16 = out_bf16; p.err = (int*)err; p.out_bs = 0;
+    if (comm) p.comm = *(const PeerComm*)comm; else p.comm.nranks = 0;
     const int nkb = (K + BK - 1) / BK;
     const int tiles = ((N + BM - 1) / BM) * ((M + BN - 1) / BN);
     int splits = 1;

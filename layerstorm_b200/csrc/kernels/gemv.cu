@@ -22,6 +22,10 @@ struct MatFp8B {
         return WRowFp8B{w + (size_t)n * ldw, scales + (size_t)(n >> 7) * kblocks};
     }
 };
+struct MatQ4K {
+    const uint8_t* w; int K;
+    __device__ __forceinline__ WRowQ4K row(int n) const { return WRowQ4K{w + (size_t)n * (K >> 8) * 144}; }
+};
 struct MatNvfp4 {
     const uint8_t* w; int K; const uint8_t* sf; int gtiles;
     __device__ __forceinline__ WRowNvfp4 row(int n) const {
@@ -258,4 +262,12 @@ LSB_API int lsb_gemv_nvfp4(void* out, const void* x, const void* w, const void* 
     const int G = K / 16;
     return launch_gemv(MatNvfp4{(const uint8_t*)w, K, (const uint8_t*)sf, (G + 3) / 4}, (const bf16*)x, ldx, out, ldo,
                        M, N, K, alpha, (const float*)bias, out_bf16, (cudaStream_t)stream, comm);
+}
+
+// W: GGUF Q4_K blocks, [N] rows of K/256 x 144 bytes.  K % 256 == 0.
+LSB_API int lsb_gemv_q4k(void* out, const void* x, const void* w, const void* bias, int M, int N, int K, int ldx, int ldo, float alpha,
+                         int out_bf16, const void* comm, void* stream) {
+    if (K % 256 || ldx % 8) return -1;
+    return launch_gemv(MatQ4K{(const uint8_t*)w, K}, (const bf16*)x, ldx, out, ldo, M, N, K, alpha, (const float*)bias, out_bf16,
+                       (cudaStream_t)stream, comm);
 }

@@ -80,6 +80,47 @@ struct WRowNvfp4 {
     }
 };
 
+// GGUF Q4_K: super-blocks of 256 weights in 144 bytes: fp16 d, fp16 dmin, 12 bytes of packed 6-bit (scale, min) pairs for 8
+// sub-blocks of 32, then 128 bytes of 4-bit quants (bytes 32j..32j+31: low nibbles = sub-block 2j, high nibbles = 2j+1).
+// w = d * scale_s * q - dmin * min_s.  Layout reference: src/model/quantization/gguf_kquant.h:49-57 (block sizes) and the
+// ggml k-quant definition; the container reader's CPU codec (csrc/runtime/gguf.cpp) is the oracle for this decoder.
+__device__ __forceinline__ void q4k_scale_min(const uint8_t* q, int j, float& sc, float& mn) {
+    if (j < 4) { sc = (float)(q[j] & 63); mn = (float)(q[j + 4] & 63); }
+    else { sc = (float)((q[j + 4] & 0xF) | ((q[j - 4] >> 6) << 4)); mn = (float)((q[j + 4] >> 4) | ((q[j] >> 6) << 4)); }
+}
+struct Q4KHeader { float d, dmin; uint8_t sc[12]; };
+__device__ __forceinline__ Q4KHeader q4k_header(const uint8_t* blk) {
+    const uint4 h = __ldg(reinterpret_cast<const uint4*>(blk));
+    Q4KHeader o;
+    const __half2 dd = *reinterpret_cast<const __half2*>(&h.x);
+    o.d = __low2float(dd); o.dmin = __high2float(dd);
+    const uint32_t w[3] = {h.y, h.z, h.w};
+#pragma unroll
+    for (int i = 0; i < 12; ++i) o.sc[i] = (uint8_t)(w[i >> 2] >> (8 * (i & 3)));
+    return o;
+}
+struct WRowQ4K {
+    static constexpr int EPL = 32;
+    const uint8_t* w;    // row start: K/256 blocks of 144 bytes
+    __device__ __forceinline__ void prefetch(int k) const { prefetch_l2(w + (size_t)(k >> 8) * 144); }
+    __device__ __forceinline__ void load(int k, float* f) const {
+        const uint8_t* blk = w + (size_t)(k >> 8) * 144;
+        const int sub = (k & 255) >> 5;
+        const Q4KHeader h = q4k_header(blk);
+        float sc, mn;
+        q4k_scale_min(h.sc, sub, sc, mn);
+        const float a = h.d * sc, b = h.dmin * mn;
+        const uint8_t* qs = blk + 16 + (sub >> 1) * 32;
+        const uint4 v0 = ldg_stream(qs), v1 = ldg_stream(qs + 16);
+        const uint32_t wv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+        const int sh = (sub & 1) * 4;
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) f[4 * i + c] = a * (float)((wv[i] >> (8 * c + sh)) & 0xFu) - b;
+    }
+};
+
 // ---- fast NVFP4 path -------------------------------------------------------------------
 // Two E2M1 values per byte convert to an f16x2 with one cvt instruction; products with fp16
 // activations are exact (2 x 8 significant bits), are summed 8 at a time in fp16 and then

@@ -357,8 +357,8 @@ __global__ void __launch_bounds__(128) mla_combine_kernel(bf16* __restrict__ out
 }  // namespace lsb
 using namespace lsb;
 
-extern "C" int lsb_gemm_bf16_tc(void* out, const void* x, const void* w, const void* bias, int M, int N, int K, int ldx, int ldw,
-                                int ldo, int out_bf16, void* partial, long long partial_cap, void* err, void* stream);
+extern "C" int lsb_gemm_bf16_tc_batched(void* out, const void* x, const void* w, int M, int N, int K, int B, int ldx, long long xs_b, int ldw,
+                                        long long ws_b, int ldo, long long os_b, int out_bf16, void* err, void* stream);
 
 LSB_API int lsb_kv_row_bytes(int fmt, int dl, int dr) { return kv_row_bytes(fmt, dl, dr); }
 
@@ -384,11 +384,8 @@ LSB_API int lsb_batched_gemv_bf16(void* out, const void* x, const void* w, int M
     dim3 grid((N + 15) / 16, B);
     if (M >= 32 && K % 8 == 0 && xs_m % 8 == 0 && xs_b % 8 == 0 && os_b % 8 == 0 && (((uintptr_t)x | (uintptr_t)w) & 15) == 0) {
         // many rows: one tensor-core GEMM per head ([M, K] x [N, K]^T), the rope tail on the side
-        for (int b = 0; b < B; ++b) {
-            const int rc = lsb_gemm_bf16_tc((bf16*)out + (size_t)b * os_b, (const bf16*)x + (size_t)b * xs_b, (const bf16*)w + (size_t)b * N * K, nullptr,
-                                            M, N, K, (int)xs_m, K, (int)os_m, 1, nullptr, 0, nullptr, stream);
-            if (rc) return rc;
-        }
+        const int rc = lsb_gemm_bf16_tc_batched(out, x, w, M, N, K, B, (int)xs_m, xs_b, K, (long long)N * K, (int)os_m, os_b, 1, nullptr, stream);
+        if (rc) return rc;
         if (dr > 0)
             launch_pdl((rope_tail_kernel), dim3(M, B), 32, 0, st, (bf16*)out, (const bf16*)x, N, K, xs_m, xs_b, os_m, os_b, dr, (const float*)inv_freq,
                        (const int*)row_pos);

@@ -188,6 +188,13 @@ template <> struct RowOf<2> {
     }
 };
 
+template <> struct RowOf<3> {
+    using T = WRowQ4K;
+    static __device__ __forceinline__ T make(const uint8_t* w, const uint8_t*, int n, int K) {
+        return T{w + (size_t)n * (K >> 8) * 144};
+    }
+};
+
 // act[pair][f] = silu(min(g,limit)) * clamp(u) ; g = x[row] . Wgate[f], u = x[row] . Wup[f]
 template <int FMT>
 __global__ void __launch_bounds__(256) moe_gateup_kernel(const bf16* __restrict__ x, const uint8_t* __restrict__ arena,
@@ -532,6 +539,7 @@ LSB_API int lsb_moe_gateup(const void* x, const void* arena, const void* slot_of
     if (ef.fmt == 0) launch_pdl((moe_gateup_kernel<0>), grid, 256, 0, st, ARGS);
     else if (ef.fmt == 1) launch_pdl((moe_gateup_kernel<1>), grid, 256, 0, st, ARGS);
     else if (ef.fmt == 2) launch_pdl((moe_gateup_kernel<2>), grid, 256, 0, st, ARGS);
+    else if (ef.fmt == 3) launch_pdl((moe_gateup_kernel<3>), grid, 256, 0, st, ARGS);
     else return -1;
 #undef ARGS
     LSB_CHECK_LAUNCH();
@@ -565,6 +573,7 @@ LSB_API int lsb_moe_down(const void* act, const void* arena, const void* slot_of
     if (ef.fmt == 0) launch_pdl((moe_down_kernel<0>), grid, 256, 0, st, ARGS);
     else if (ef.fmt == 1) launch_pdl((moe_down_kernel<1>), grid, 256, 0, st, ARGS);
     else if (ef.fmt == 2) launch_pdl((moe_down_kernel<2>), grid, 256, 0, st, ARGS);
+    else if (ef.fmt == 3) launch_pdl((moe_down_kernel<3>), grid, 256, 0, st, ARGS);
     else return -1;
 #undef ARGS
     LSB_CHECK_LAUNCH();

@@ -6,7 +6,7 @@
 namespace lsb {
 
 struct ExpertFmt {
-    int fmt;                 // 0 bf16, 1 fp8 block-128, 2 nvfp4
+    int fmt;                 // 0 bf16, 1 fp8 block-128, 2 nvfp4, 3 GGUF Q4_K
     int H, F;                // hidden, expert intermediate
     long long stride;        // bytes between slots
     long long off_gate, off_up, off_down;        // weights

@@ -171,6 +171,47 @@ template <int NE> struct Conv<1, NE> {        // FP8 e4m3 with 128x128 block sca
     }
 };
 
+template <int NE> struct Conv<3, NE> {        // GGUF Q4_K: a 64-element stage = one (low, high) nibble pair of 32 quant bytes
+    struct Raw { uint4 hdr; uint4 q[2]; };
+    static __device__ __forceinline__ void load(Raw& r, const uint8_t* w, const uint8_t*, int n, int K, int k0, int) {
+        const uint8_t* blk = w + ((size_t)n * (K >> 8) + (k0 >> 8)) * 144;
+        r.hdr = __ldg(reinterpret_cast<const uint4*>(blk));
+        const uint8_t* qs = blk + 16 + ((k0 & 255) >> 6) * 32;
+        r.q[0] = ldg_stream(qs); r.q[1] = ldg_stream(qs + 16);
+    }
+    // NE = 64: this thread emits both sub-blocks (low then high nibbles); NE = 32: sub-block `sub` only.
+    static __device__ __forceinline__ void emit(const Raw& r, uint32_t tile, int row, int sub, int k0 = 0) {
+        const __half2 dd = *reinterpret_cast<const __half2*>(&r.hdr.x);
+        const float d = __low2float(dd), dmin = __high2float(dd);
+        uint8_t sc12[12];
+        const uint32_t hw[3] = {r.hdr.y, r.hdr.z, r.hdr.w};
+#pragma unroll
+        for (int i = 0; i < 12; ++i) sc12[i] = (uint8_t)(hw[i >> 2] >> (8 * (i & 3)));
+        const uint32_t wv[8] = {r.q[0].x, r.q[0].y, r.q[0].z, r.q[0].w, r.q[1].x, r.q[1].y, r.q[1].z, r.q[1].w};
+        const int j2 = ((k0 & 255) >> 6) * 2;                      // first sub-block of this stage
+#pragma unroll
+        for (int half_i = 0; half_i < 2; ++half_i) {
+            if (NE == 32 && half_i != sub) continue;
+            float sc, mn;
+            q4k_scale_min(sc12, j2 + half_i, sc, mn);
+            const __half2 a2 = __float2half2_rn(d * sc), b2 = __float2half2_rn(-dmin * mn);
+#pragma unroll
+            for (int c8 = 0; c8 < 4; ++c8) {                       // 8 elements = bytes 8*c8 .. 8*c8+7 -> words 2*c8, 2*c8+1
+                __half2 h[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const uint32_t wq = wv[2 * c8 + (q >> 1)] >> ((q & 1) * 16 + half_i * 4);
+                    // two consecutive bytes -> two 4-bit values as exact fp16 integers (1024 + v) - 1024
+                    const uint32_t bits = 0x64006400u | (wq & 0xFu) | (((wq >> 8) & 0xFu) << 16);
+                    const __half2 v = __hsub2(*reinterpret_cast<const __half2*>(&bits), __float2half2_rn(1024.f));
+                    h[q] = __hfma2(v, a2, b2);
+                }
+                st_shared_16(sw128_chunk(tile, row, half_i * 4 + c8), *reinterpret_cast<uint4*>(h));
+            }
+        }
+    }
+};
+
 template <int NE> struct Conv<0, NE> {        // BF16: 2*NE bytes
     static constexpr int NV = NE / 8;
     struct Raw { uint4 v[NV]; };
@@ -204,6 +245,9 @@ struct MoeTcParams {
     // expert-parallel mode (ep.nranks > 0): the gate/up kernel waits for the peers' token rows (phase 1) before its
     // first load, the down kernel stores its rows straight into the token owners' buffers and publishes phase 2
     EpComm ep;
+    // dense-linear mode of the down kernel (one "expert" = the whole matrix): row stride and type of the output and the
+    // per-tensor scale (0 = read it from the slot tail)
+    int ldo, out_bf16; float down_scale;
 };
 
 template <int BN, bool GATEUP> struct MoeTcCfg {
@@ -323,7 +367,7 @@ __global__ void __launch_bounds__(MoeTcCfg<BN, GATEUP>::THREADS) moe_tc_ffn_kern
         const uint8_t* sf = base + (GATEUP ? (is_up ? p.ef.off_su : p.ef.off_sg) : p.ef.off_sd);
         // stages fetched ahead of the one being converted: enough bytes in flight per SM to cover HBM latency
         // (nvfp4: 6 x 8 KB, fp8: 3 x 16 KB, bf16: 2 x 32 KB per CTA)
-        constexpr int PF = FMT == 2 ? 6 : (FMT == 1 ? 3 : 2);
+        constexpr int PF = FMT == 2 ? 6 : (FMT == 0 ? 2 : 3);
         typename CV::Raw raw[PF];
 #pragma unroll
         for (int j = 0; j < PF; ++j)
@@ -338,7 +382,8 @@ __global__ void __launch_bounds__(MoeTcCfg<BN, GATEUP>::THREADS) moe_tc_ffn_kern
                     ok = mbar_wait(&empty[s], ((it / C::STAGES) & 1) ^ 1, p.err, 13);
                     if (ok) {
                         const uint32_t tile = smem_u32(smem + s * C::STAGE_BYTES) + (is_up ? kTBM * kTBK * 2 : 0);
-                        CV::emit(raw[j], tile, row & (kTBM - 1), sub);
+                        if constexpr (FMT == 3) CV::emit(raw[j], tile, row & (kTBM - 1), sub, it * kTBK);
+                        else CV::emit(raw[j], tile, row & (kTBM - 1), sub);
                         if (it + PF < nkb) CV::load(raw[j], w, sf, wrow, K, (it + PF) * kTBK, sub);
                         fence_proxy_async();                   // generic-proxy stores -> visible to the MMA's async-proxy reads
                         __syncwarp();
@@ -355,9 +400,11 @@ __global__ void __launch_bounds__(MoeTcCfg<BN, GATEUP>::THREADS) moe_tc_ffn_kern
             tc_fence_after();
             if (ok) {
                 float sg = 1.f, su = 1.f;
-                if (FMT == 2) {
+                if (FMT == 2 && (GATEUP || p.down_scale == 0.f)) {
                     const float* tail = reinterpret_cast<const float*>(base + p.ef.off_tail);
-                    if (GATEUP) { sg = tail[0]; su = tail[1]; } else sg = tail[2];
+                    if (GATEUP) { sg = tail[0]; su = tail[1]; } else sg = p.down_scale != 0.f ? p.down_scale : tail[2];
+                } else if (FMT == 2) {
+                    sg = p.down_scale;
                 } else if (FMT == 1) {
                     sg = su = kFp8Unscale;
                 }
@@ -378,8 +425,10 @@ __global__ void __launch_bounds__(MoeTcCfg<BN, GATEUP>::THREADS) moe_tc_ffn_kern
                             } else if (ep_mode) {
                                 const int2 ra = p.ep.ret[p.ep.rank][row0 + c0 + j];      // (token owner, pair index there)
                                 p.ep.y[ra.x][(size_t)ra.y * NOUT + n] = g[j] * sg;        // NVLink store into the owner's buffer
+                            } else if (p.out_bf16) {
+                                reinterpret_cast<bf16*>(p.y)[(size_t)p.sorted_pair[row0 + c0 + j] * p.ldo + n] = __float2bfloat16(g[j] * sg);
                             } else {
-                                p.y[(size_t)p.sorted_pair[row0 + c0 + j] * NOUT + n] = g[j] * sg;
+                                p.y[(size_t)p.sorted_pair[row0 + c0 + j] * p.ldo + n] = g[j] * sg;
                             }
                         }
                     }
@@ -409,6 +458,7 @@ static int dispatch_fmt(int fmt, const CUtensorMap& mb, const MoeTcParams& p, in
         case 0: return launch_moe_tc<0, BN, GATEUP>(mb, p, nout, max_tiles, st);
         case 1: return launch_moe_tc<1, BN, GATEUP>(mb, p, nout, max_tiles, st);
         case 2: return launch_moe_tc<2, BN, GATEUP>(mb, p, nout, max_tiles, st);
+        case 3: return launch_moe_tc<3, BN, GATEUP>(mb, p, nout, max_tiles, st);
     }
     return -1;
 }
@@ -444,6 +494,7 @@ LSB_API int lsb_moe_tc_ffn(int gateup, const void* b, int cap_rows, const void* 
     const int K = gateup ? ef->H : ef->F, nout = gateup ? ef->F : ef->H;
     if (K % kTBK || nout % kTBM || ((uintptr_t)b & 15)) return -1;
     if (ef->fmt == 1 && (K % 128)) return -1;
+    if (ef->fmt == 3 && (K % 256)) return -1;
     CUtensorMap mb;
     int rc = cached_map_2d(&mb, b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (uint64_t)cap_rows, (uint64_t)K, (uint64_t)K, (uint32_t)BN, kTBK);
     if (rc) return rc;
@@ -454,6 +505,7 @@ LSB_API int lsb_moe_tc_ffn(int gateup, const void* b, int cap_rows, const void* 
     p.act = gateup ? (__half*)out : nullptr; p.y = gateup ? nullptr : (float*)out;
     p.limit = limit; p.miss_flag = (int*)miss_flag; p.err = (int*)err;
     if (ep) p.ep = *(const EpComm*)ep; else { memset(&p.ep, 0, sizeof(p.ep)); }
+    p.ldo = nout; p.out_bf16 = 0; p.down_scale = 0.f;
     cudaStream_t st = (cudaStream_t)stream;
     if (gateup) {
         switch (BN) {
@@ -467,6 +519,37 @@ LSB_API int lsb_moe_tc_ffn(int gateup, const void* b, int cap_rows, const void* 
             case 64: return dispatch_fmt<64, false>(ef->fmt, mb, p, nout, max_tiles, st);
             case 128: return dispatch_fmt<128, false>(ef->fmt, mb, p, nout, max_tiles, st);
         }
+    }
+    return -1;
+}
+
+// Dense linear layer with quantised weights on the tensor cores: out[m][n] = alpha * sum_k x16[m][k] * W[n][k].
+// x16: fp16 [M, K] contiguous; W in storage format `fmt` (0 bf16, 1 fp8 e4m3 + 128x128 block scales, 2 nvfp4 + group-scale
+// atoms) with `scales`; out fp32 or bf16 with row stride ldo.  The caller provides the (constant per M) tile description:
+// tile_expert = 0, tile_row0 = t*BN, tile_n, counters = {tiles, M}, ident[m] = m, slot0 = {0}.
+LSB_API int lsb_gemm_q_tc(void* out, const void* x16, const void* w, const void* scales, int fmt, int M, int N, int K, int ldo, int out_bf16,
+                          float alpha, const void* tile_expert, const void* tile_row0, const void* tile_n, const void* counters,
+                          const void* ident, const void* slot0, int BN, int n_tiles, void* err, void* stream) {
+    if (K % kTBK || N % kTBM || ((uintptr_t)x16 & 15) || fmt < 0 || fmt > 3) return -1;
+    if ((fmt == 1 && (K % 128)) || (fmt == 3 && (K % 256))) return -1;
+    CUtensorMap mb;
+    int rc = cached_map_2d(&mb, x16, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (uint64_t)M, (uint64_t)K, (uint64_t)K, (uint32_t)BN, kTBK);
+    if (rc) return rc;
+    MoeTcParams p;
+    memset(&p, 0, sizeof(p));
+    p.arena = (const uint8_t*)w; p.slot_of = (const int*)slot0;
+    p.ef.fmt = fmt; p.ef.H = N; p.ef.F = K; p.ef.stride = 0; p.ef.off_down = 0;
+    p.ef.off_sd = scales ? (long long)((const uint8_t*)scales - (const uint8_t*)w) : 0;
+    p.tile_expert = (const int*)tile_expert; p.tile_row0 = (const int*)tile_row0; p.tile_n = (const int*)tile_n;
+    p.counters = (const int*)counters; p.sorted_pair = (const int*)ident;
+    p.y = (float*)out; p.err = (int*)err; p.ldo = ldo; p.out_bf16 = out_bf16;
+    p.down_scale = fmt == 2 ? alpha : 0.f;
+    if (fmt != 2 && alpha != 1.0f) return -1;
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (BN) {
+        case 32: return dispatch_fmt<32, false>(fmt, mb, p, N, n_tiles, st);
+        case 64: return dispatch_fmt<64, false>(fmt, mb, p, N, n_tiles, st);
+        case 128: return dispatch_fmt<128, false>(fmt, mb, p, N, n_tiles, st);
     }
     return -1;
 }

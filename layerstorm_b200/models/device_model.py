@@ -24,7 +24,7 @@ from ..ops import _native as nat
 from .config import ModelConfig
 
 KV_FMT = {"bf16": 0, "fp8": 1}
-EXPERT_FMT = {"bf16": 0, "fp8_e4m3": 1, "nvfp4": 2}
+EXPERT_FMT = {"bf16": 0, "fp8_e4m3": 1, "nvfp4": 2, "gguf_q4_k": 3}
 
 
 class ExpertFmt(ctypes.Structure):
@@ -70,6 +70,13 @@ def expert_layout(fmt: str, H: int, F: int) -> ExpertFmt:
         ef.off_sd = ef.off_su + sgu
         ef.off_tail = ef.off_sd + sd
         end = ef.off_tail + 32
+    elif fmt == "gguf_q4_k":
+        if H % 256 or F % 256:
+            raise ValueError("Q4_K experts need hidden and intermediate sizes that are multiples of 256")
+        wb = H * F // 256 * 144
+        ef.off_gate, ef.off_up, ef.off_down = 0, wb, 2 * wb
+        ef.off_sg = ef.off_su = ef.off_sd = ef.off_tail = 3 * wb
+        end = 3 * wb
     else:
         raise ValueError(fmt)
     ef.stride = _align(end, 4096)
@@ -77,6 +84,12 @@ def expert_layout(fmt: str, H: int, F: int) -> ExpertFmt:
 
 
 TC_MOE_MIN_ROWS = 16      # rows per step from which the routed experts run on the tensor-core grouped GEMM
+
+
+def _dequant_q4k(raw: torch.Tensor, N: int, K: int) -> torch.Tensor:
+    from ..formats import gguf as _gguf
+    out = _gguf.dequantize(_gguf.GGML_TYPES["Q4_K"], raw.detach().cpu().numpy().reshape(-1), N * K)
+    return torch.from_numpy(out).view(N, K).to(raw.device)
 
 
 class TcScratch:
@@ -118,6 +131,10 @@ class QLinear:
         if fmt == "nvfp4":
             q, a, gs = quant.quantize_nvfp4(wf)
             return QLinear("nvfp4", N, K, q, a, gs)
+        if fmt == "gguf_q4_k":
+            from ..formats import gguf as _gguf
+            raw = _gguf.quantize(_gguf.GGML_TYPES["Q4_K"], wf.float().cpu().numpy())
+            return QLinear("gguf_q4_k", N, K, torch.from_numpy(raw).to(device).view(N, K // 256 * 144))
         raise ValueError(fmt)
 
     @staticmethod
@@ -142,13 +159,47 @@ class QLinear:
             a = torch.empty(quant.sf_atom_size(N, K), dtype=torch.uint8, device=device)
             gs = quant.random_nvfp4_(w, a, gen) * (std / 0.02)
             return QLinear("nvfp4", N, K, w, a, gs)
+        if fmt == "gguf_q4_k":
+            # random quants and 6-bit scales; d / dmin fixed so that weights ~ U(-c, c) with standard deviation `std`
+            blocks = torch.empty(N * K // 256, 144, dtype=torch.uint8, device=device)
+            blocks.random_(0, 256, generator=gen)
+            c = std * 3 ** 0.5
+            d = torch.tensor([c / 7.5 / 32.0, c / 32.0], dtype=torch.float16).view(torch.uint8).to(device)      # d*sc*q - dmin*m with sc~32, m~32
+            blocks[:, :4] = d
+            blocks[:, 4:16] = (blocks[:, 4:16] & 0x1F) | 0x10      # scales and mins in 16..31, top bits clear
+            return QLinear("gguf_q4_k", N, K, blocks.view(N, K // 256 * 144))
         raise ValueError(fmt)
+
+    _tiles: Dict[tuple, dict] = {}
+    _x16: Dict[int, torch.Tensor] = {}
+
+    @classmethod
+    def _dense_tiles(cls, device, M: int) -> dict:
+        """Tile description of a dense [M, K] operand for the grouped tensor-core kernel (constant per M) and the shared
+        fp16 staging buffer for the activations."""
+        idx = torch.device(device).index or 0
+        key = (idx, M)
+        if key not in cls._tiles:
+            bn = 32 if M <= 32 else (64 if M <= 64 else 128)
+            n = (M + bn - 1) // bn
+            i32 = dict(dtype=torch.int32, device=device)
+            r0 = torch.arange(n, **i32) * bn
+            cls._tiles[key] = {"bn": bn, "n": n, "te": torch.zeros(n, **i32), "tr": r0, "tn": torch.clamp(M - r0, max=bn).int(),
+                               "cnt": torch.tensor([n, M], **i32), "ident": torch.arange(M, **i32), "slot0": torch.zeros(1, **i32)}
+        t = cls._tiles[key]
+        need = M * 32768
+        if idx not in cls._x16 or cls._x16[idx].numel() < need:
+            cls._x16[idx] = torch.empty(max(need, 4096 * 32768), dtype=torch.float16, device=device)
+        t["x16"] = cls._x16[idx]
+        return t
 
     def dequant(self) -> torch.Tensor:
         if self.fmt in ("bf16", "f32"):
             return self.w.float()
         if self.fmt == "fp8_e4m3":
             return quant.dequantize_fp8_block(self.w, self.scales)
+        if self.fmt == "gguf_q4_k":
+            return _dequant_q4k(self.w, self.N, self.K)
         return quant.dequantize_nvfp4(self.w, self.scales, self.alpha, self.N, self.K)
 
     def nbytes(self) -> int:
@@ -161,15 +212,25 @@ class QLinear:
         ldx = ldx if ldx is not None else self.K
         ldo = ldo if ldo is not None else self.N
         ob = 1 if out.dtype == torch.bfloat16 else 0
-        if comm is not None and M not in (1, 2, 4):
-            raise RuntimeError("the fused all-reduce epilogue covers single-pass shapes (1, 2 or 4 rows)")
-        if self.fmt == "bf16" and M >= 8 and comm is None:
+        if comm is not None and M not in (1, 2, 4) and not (self.fmt == "bf16" and M >= 8 and bias is None and not ob):
+            raise RuntimeError("the fused all-reduce epilogue covers 1, 2 or 4 rows (GEMV) or >= 8 rows of a bf16 layer (GEMM)")
+        if self.fmt == "bf16" and M >= 8:
             sc = TcScratch.get(self.w.device)
-            nat.call("lsb_gemm_bf16_tc", out, x, self.w, bias, M, self.N, self.K, ldx, self.K, ldo, ob, sc.partial, sc.cap, sc.err)
+            nat.call("lsb_gemm_bf16_tc", out, x, self.w, bias, M, self.N, self.K, ldx, self.K, ldo, ob, sc.partial, sc.cap, sc.err, comm)
+        elif (self.fmt in ("fp8_e4m3", "nvfp4", "gguf_q4_k") and M >= 16 and comm is None and bias is None and ldx == self.K and self.K % 64 == 0
+              and self.N % 128 == 0 and (self.fmt != "fp8_e4m3" or self.K % 128 == 0) and (self.fmt != "gguf_q4_k" or self.K % 256 == 0)):
+            # many rows over quantised weights: de-quantisation fused into the tcgen05 operand pipeline
+            t = QLinear._dense_tiles(self.w.device, M)
+            nat.call("lsb_moe_tc_gather", x, t["ident"], t["cnt"], t["x16"], M, 1, self.K)
+            nat.call("lsb_gemm_q_tc", out, t["x16"], self.w, self.scales, EXPERT_FMT[self.fmt], M, self.N, self.K, ldo, ob,
+                     self.alpha if self.fmt == "nvfp4" else 1.0, t["te"], t["tr"], t["tn"], t["cnt"], t["ident"], t["slot0"], t["bn"], t["n"],
+                     TcScratch.get(self.w.device).err)
         elif self.fmt == "bf16":
             nat.call("lsb_gemv_bf16", out, x, self.w, bias, M, self.N, self.K, ldx, self.K, ldo, 1.0, ob, comm)
         elif self.fmt == "f32":
             nat.call("lsb_gemv_f32w", out, x, self.w, bias, M, self.N, self.K, ldx, self.K, ldo, 1.0, ob)
+        elif self.fmt == "gguf_q4_k":
+            nat.call("lsb_gemv_q4k", out, x, self.w, bias, M, self.N, self.K, ldx, ldo, 1.0, ob, comm)
         elif self.fmt == "fp8_e4m3":
             nat.call("lsb_gemv_fp8b", out, x, self.w, self.scales, bias, M, self.N, self.K, ldx, ldo, 1.0, ob, comm)
         else:
@@ -223,6 +284,8 @@ class ExpertArena:
                                    ("down", (H, F), ef.off_down, ef.off_sd)):
             if fmt == "bf16":
                 out.append(v[ow: ow + N * K * 2].view(torch.bfloat16).view(N, K).float())
+            elif fmt == "gguf_q4_k":
+                out.append(_dequant_q4k(v[ow: ow + N * K // 256 * 144], N, K))
             elif fmt == "fp8_e4m3":
                 nb = ((N + 127) // 128) * ((K + 127) // 128)
                 s = v[os_: os_ + nb * 4].view(torch.float32).view((N + 127) // 128, (K + 127) // 128)
@@ -402,7 +465,8 @@ class DeviceModel:
         eq = expert_quant or cfg.expert_quant
         dq = dense_quant or cfg.dense_quant
         if eq.startswith("gguf"):
-            eq = "bf16"
+            # GGUF expert tensors: Q4_K runs natively; the other ggml types are expanded at load time
+            eq = "gguf_q4_k" if (eq in ("gguf", "gguf_q4_k") and cfg.hidden % 256 == 0 and cfg.moe_inter % 256 == 0) else "bf16"
         f32 = lambda t: t.to(dev).float().contiguous()
         m.embed = w["embed.weight"].to(dev).to(torch.bfloat16).contiguous()
         m.head = QLinear.from_float(rows(w["head.weight"], cfg.vocab, 1), "bf16", dev)
@@ -480,7 +544,7 @@ class DeviceModel:
         gloc = torch.Generator(device=dev).manual_seed(seed * 7919 + 1 + tp_rank)    # this rank's shards
         dq, eq = cfg.dense_quant, cfg.expert_quant
         if eq.startswith("gguf"):
-            eq = "nvfp4"
+            eq = "gguf_q4_k" if (cfg.hidden % 256 == 0 and cfg.moe_inter % 256 == 0) else "nvfp4"
         H = cfg.hidden
 
         def nrm(n):
@@ -586,6 +650,12 @@ class DeviceModel:
             d[:, : ef.off_sg].random_(0, 256, generator=gen)
             d[:, : ef.off_sg] &= 0xBF
             d[:, ef.off_sg: ef.off_tail].view(torch.float32).fill_(0.02 / 0.6)
+        elif eq == "gguf_q4_k":
+            blocks = d[:, : ef.off_tail].view(d.shape[0], -1, 144)
+            blocks.random_(0, 256, generator=gen)
+            c = 0.02 * 3 ** 0.5
+            blocks[:, :, :4] = torch.tensor([c / 7.5 / 24.0, c / 24.0], dtype=torch.float16).view(torch.uint8).to(d.device)
+            blocks[:, :, 4:16] = (blocks[:, :, 4:16] & 0x0F) | 0x10
         else:
             d[:, : ef.off_sg].random_(0, 256, generator=gen)
             d[:, ef.off_sg: ef.off_tail].random_(0x30, 0x40, generator=gen)
@@ -750,7 +820,9 @@ class DeviceModel:
         ``ws``).  Writes logits for rows [logit_row0, logit_row0 + n_logit_rows)."""
         cfg = self.cfg
         H, n = cfg.hidden, cfg.hc_mult
-        self._fused = self.comm is not None and R in (1, 2, 4)
+        # fused in-kernel all-reduce: GEMV epilogues cover 1, 2 or 4 rows; the tcgen05 GEMM epilogue covers any larger
+        # step with bf16 dense weights, as long as the step fits the peers' receive slots
+        self._fused = self.comm is not None and (R in (1, 2, 4) or (R >= 8 and cfg.dense_quant == "bf16" and R * H <= self.comm.cap))
         if cfg.mhc:
             nat.call("lsb_embedding", ws.sub, None, self.embed, ws.tok, R, H, 0, cfg.vocab)
             for i, L in enumerate(self.layers):
@@ -845,7 +917,7 @@ class DeviceModel:
                 if L["router_bias"] is not None:
                     out[mo + "router_bias"] = cpu(L["router_bias"])
                 arena: ExpertArena = L["arena"]
-                fmt = {0: "bf16", 1: "fp8_e4m3", 2: "nvfp4"}[arena.ef.fmt]
+                fmt = {v: k for k, v in EXPERT_FMT.items()}[arena.ef.fmt]
                 so = arena.slot_of.cpu()
                 for e in range(cfg.n_routed + cfg.n_shared):
                     nm = mo + (f"experts.{e}." if e < cfg.n_routed else f"shared.{e - cfg.n_routed}.")

@@ -25,7 +25,7 @@ def main():
     cfg = get_preset(name)
     w = round_weights_bf16(init_weights(cfg, 0))
     m = DeviceModel.from_state_dict(cfg, w, dev, kv_fmt="bf16", page=16, tp_rank=rank, tp_size=world)
-    comm = PeerComm(4 * cfg.hidden, dev)
+    comm = PeerComm(16 * cfg.hidden, dev)       # 16 rows: the 8-row prefill chunks go through the fused GEMM epilogue
     comm_amax = PeerComm(64, dev)
     m.attach_comm(comm, comm_amax)
     oracle = Oracle(cfg, w)
@@ -36,7 +36,7 @@ def main():
     for use_graph in (False, True):
         eng = Engine(m, max_seqs=2, max_ctx=128, prefill_chunk=8, max_batch=2, use_graph=use_graph)
         sid = eng.create_sequence()
-        nxt = eng.prefill(sid, ids[:T].tolist())                 # chunks of 8 rows: NCCL reduce path
+        nxt = eng.prefill(sid, ids[:T].tolist())                 # chunks of 8 rows: tcgen05 GEMM with the fused all-reduce epilogue
         good = nxt == int(ref[T - 1].argmax())
         for j in range(6):                                       # single rows: fused in-kernel all-reduce
             out = eng.decode([sid], [int(ids[T + j])])

@@ -179,3 +179,22 @@ def test_sampling_kernels():
     nat.call("lsb_spec_verify", d, t, 4, res)
     torch.cuda.synchronize()
     assert res.cpu().tolist() == [2, 9]
+
+
+@pytest.mark.parametrize("M", [1, 4, 40])
+def test_q4k_linear_gemv_and_tensor_core(M):
+    """GGUF Q4_K weights: decode GEMV (M <= 4) and the tensor-core path (M >= 16) against the container codec's dequantisation."""
+    from layerstorm_b200.models.device_model import QLinear
+    g = torch.Generator().manual_seed(21)
+    N, K = 256, 512
+    lin = QLinear.from_float(torch.randn(N, K, generator=g) * 0.05, "gguf_q4_k", "cuda")
+    assert lin.w.shape == (N, K // 256 * 144)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
+    ref = x.float() @ lin.dequant().float().T
+    out = torch.zeros(M, N, device="cuda")
+    lin(out, x, M)
+    torch.cuda.synchronize()
+    assert float((out - ref).abs().max() / ref.abs().max()) < 3e-3
+    rnd = QLinear.random(N, K, "gguf_q4_k", "cuda")
+    wd = rnd.dequant()
+    assert torch.isfinite(wd).all() and 0.005 < float(wd.std()) < 0.08

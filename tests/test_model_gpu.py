@@ -84,6 +84,26 @@ def test_quantised_formats_match_oracle(eq, dq, kv):
     assert rel_err(lg, ref_logits[-1]) < 6e-2, rel_err(lg, ref_logits[-1])
 
 
+def test_gguf_q4k_experts_decode_and_prefill_match_oracle():
+    """Q4_K expert slots: weight-streaming kernels (short chunks / decode) and the tensor-core grouped path (long chunk)."""
+    import dataclasses
+    cfg = dataclasses.replace(get_preset("tiny-mla-moe"), moe_inter=256, name="tiny-q4k")
+    w = init_weights(cfg, 3)
+    m = DeviceModel.from_state_dict(cfg, w, "cuda", kv_fmt="bf16", page=16, expert_quant="gguf_q4_k")
+    assert m.layers[1]["arena"].ef.fmt == 3
+    oracle = Oracle(cfg, m.effective_state_dict())
+    ids = torch.randint(0, cfg.vocab, (26,), generator=torch.Generator().manual_seed(2))
+    ref_logits = oracle.forward(ids)
+    for chunk in (8, 32):
+        eng = Engine(m, max_seqs=1, max_ctx=128, prefill_chunk=chunk, max_batch=1, use_graph=False)
+        sid = eng.create_sequence()
+        _, lg = eng.prefill(sid, ids[:24].tolist(), want_logits=True)
+        assert rel_err(lg, ref_logits[23]) < 3e-2, (chunk, rel_err(lg, ref_logits[23]))
+        out, lg = eng.decode([sid], [int(ids[24])], return_logits=True)
+        assert rel_err(lg[0], ref_logits[24]) < 3e-2 and out[0] == int(ref_logits[24].argmax())
+        eng.free_sequence(sid)
+
+
 def test_graph_decode_equals_eager_and_batched():
     cfg, m, _ = build("tiny-glm5-next")
     prompt_a = torch.randint(0, cfg.vocab, (20,), generator=torch.Generator().manual_seed(3)).tolist()

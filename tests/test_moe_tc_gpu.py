@@ -27,12 +27,12 @@ def _setup(fmt, H, F, E, n_missing, seed):
     return arena, ref
 
 
-@pytest.mark.parametrize("fmt", ["nvfp4", "fp8_e4m3", "bf16"])
+@pytest.mark.parametrize("fmt", ["nvfp4", "fp8_e4m3", "bf16", "gguf_q4_k"])
 @pytest.mark.parametrize("BN,R", [(32, 40), (64, 150), (128, 300)])
 def test_grouped_ffn_matches_reference(fmt, BN, R):
     from layerstorm_b200.ops import _native as nat
     dev = torch.device("cuda")
-    H, F, E, S, limit = 256, 128, 6, 3, 7.0
+    H, F, E, S, limit = 256, (256 if fmt == "gguf_q4_k" else 128), 6, 3, 7.0
     arena, ref = _setup(fmt, H, F, E, n_missing=1, seed=1)
     g = torch.Generator(device="cpu").manual_seed(2)
     x = (torch.randn(R, H, generator=g) * 1.5).to(torch.bfloat16).to(dev)

@@ -256,14 +256,19 @@ template <int BN, bool GATEUP> struct MoeTcCfg {
     static constexpr int B_BYTES = BN * kTBK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int STAGES = GATEUP ? 4 : 6;
-    static constexpr int TMEM_COLS = (A_TILES * BN) < 32 ? 32 : A_TILES * BN;
+    static constexpr int ACC_COLS = A_TILES * BN;                         // one accumulator set (gate [+ up])
+    static constexpr int TMEM_COLS = (2 * ACC_COLS) < 32 ? 32 : 2 * ACC_COLS;   // double-buffered: epilogue of tile i overlaps tile i+1
     static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 256;
     static constexpr int CONV_WARPS = 8;
-    static constexpr int THREADS = (2 + CONV_WARPS) * 32;
+    static constexpr int EPI_WARPS = 4;
+    static constexpr int THREADS = (2 + CONV_WARPS + EPI_WARPS) * 32;
     static constexpr int TPR = (CONV_WARPS * 32) / (A_TILES * kTBM);     // converter threads per weight row
     static constexpr int NE = kTBK / TPR;                                 // elements per converter thread per stage
 };
 
+// Persistent kernel: one CTA per SM walks the work list (token tile x 128-row weight tile, weight tile fastest so
+// that concurrently running CTAs share a token tile); the shared-memory ring, its barrier phases and the two TMEM
+// accumulator sets carry over from one work item to the next.
 template <int FMT, int BN, bool GATEUP>
 __global__ void __launch_bounds__(MoeTcCfg<BN, GATEUP>::THREADS) moe_tc_ffn_kernel(const __grid_constant__ CUtensorMap map_b, MoeTcParams p) {
     using C = MoeTcCfg<BN, GATEUP>;
@@ -272,175 +277,211 @@ __global__ void __launch_bounds__(MoeTcCfg<BN, GATEUP>::THREADS) moe_tc_ffn_kern
     uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
     uint64_t* empty = full + C::STAGES;
-    uint64_t* acc_full = empty + C::STAGES;
-    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_full + 1);
+    uint64_t* acc_full = empty + C::STAGES;      // [2]
+    uint64_t* acc_empty = acc_full + 2;          // [2]
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int K = GATEUP ? p.ef.H : p.ef.F;          // reduction length
     const int NOUT = GATEUP ? p.ef.F : p.ef.H;       // weight rows
-    const int n0 = blockIdx.x * kTBM;
+    const int NT = NOUT / kTBM;
     const int nkb = K / kTBK;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1 + C::CONV_WARPS); mbar_init(&empty[s], 1); }
-        mbar_init(acc_full, 1);
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], C::EPI_WARPS); }
         fence_barrier_init();
         fence_proxy_async();
         tma_prefetch_desc(&map_b);
-    }
-    pdl_wait();
-    pdl_launch_dependents();
-    const bool ep_mode = p.ep.nranks > 0;
-    const unsigned ep_epoch = ep_mode ? *p.ep.epoch + 1u : 0u;
-    const unsigned ep_blocks = gridDim.x * gridDim.y;
-    if (ep_mode && GATEUP) {
-        ep_wait(p.ep, 1, ep_epoch);                  // peers' rows have landed in this rank's staging buffer
-        asm volatile("fence.proxy.async;" ::: "memory");   // ... and are ordered before the TMA (async proxy) reads
-    }
-    const int t = blockIdx.y;
-    if (t >= p.counters[0]) {                        // uniform: no tile for this CTA
-        if (ep_mode && !GATEUP) ep_signal(p.ep, 2, ep_epoch, ep_blocks);
-        return;
-    }
-    const int e = p.tile_expert[t], row0 = p.tile_row0[t], ncols = p.tile_n[t];
-    const int slot = p.slot_of[e];
-    if (slot < 0) {                                  // expert not resident on this GPU
-        if (p.miss_flag && threadIdx.x == 0 && blockIdx.x == 0) atomicExch(p.miss_flag, e + 1);
-        if (ep_mode && !GATEUP) ep_signal(p.ep, 2, ep_epoch, ep_blocks);
-        return;
     }
     if (warp == 1) tmem_alloc(tmem_holder, C::TMEM_COLS);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_d = *tmem_holder;
-    const uint8_t* base = p.arena + (size_t)slot * p.ef.stride;
+    pdl_wait();
+    pdl_launch_dependents();
+    const bool ep_mode = p.ep.nranks > 0;
+    const unsigned ep_epoch = ep_mode ? *p.ep.epoch + 1u : 0u;
+    if (ep_mode && GATEUP) {
+        ep_wait(p.ep, 1, ep_epoch);                  // peers' rows have landed in this rank's staging buffer
+        asm volatile("fence.proxy.async;" ::: "memory");   // ... and are ordered before the TMA (async proxy) reads
+    }
+    const int total = p.counters[0] * NT;
 
     if (warp == 0) {
         if (lane == 0) {
-            // ---------------- TMA producer: token tile ----------------
-            int issued = 0;
+            // ---------------- TMA producer: token tiles ----------------
+            uint32_t g = 0;
             bool ok = true;
-            for (int it = 0; it < nkb && ok; ++it) {
-                const int s = it % C::STAGES;
-                ok = mbar_wait(&empty[s], ((it / C::STAGES) & 1) ^ 1, p.err, 11);
-                if (!ok) break;
-                mbar_expect_tx(&full[s], C::B_BYTES);
-                tma_load_2d(smem + s * C::STAGE_BYTES + C::A_BYTES, &map_b, &full[s], it * kTBK, row0);
-                ++issued;
+            for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
+                const int t = w / NT;
+                const int e = p.tile_expert[t];
+                if (p.slot_of[e] < 0) {              // expert not resident on this GPU: every role skips the item
+                    if (GATEUP && p.miss_flag && (w % NT) == 0) atomicExch(p.miss_flag, e + 1);
+                    continue;
+                }
+                const int row0 = p.tile_row0[t];
+                for (int it = 0; it < nkb; ++it, ++g) {
+                    const int s = g % C::STAGES;
+                    ok = mbar_wait(&empty[s], ((g / C::STAGES) & 1) ^ 1, p.err, 11);
+                    if (!ok) break;
+                    mbar_expect_tx(&full[s], C::B_BYTES);
+                    tma_load_2d(smem + s * C::STAGE_BYTES + C::A_BYTES, &map_b, &full[s], it * kTBK, row0);
+                }
             }
             if (!ok) {
-                // the loads in flight still write this CTA's shared memory: let them land.  Their barriers may
-                // be short of converter arrivals on this path, so poll the phase with a bound and no error code.
-                for (int it = max(0, issued - C::STAGES); it < issued; ++it) mbar_wait(&full[it % C::STAGES], (it / C::STAGES) & 1, nullptr, 0);
+                // loads in flight still write this CTA's shared memory: let them land (bounded, no error code)
+                for (uint32_t i = g > (uint32_t)C::STAGES ? g - C::STAGES : 0; i < g; ++i) mbar_wait(&full[i % C::STAGES], (i / C::STAGES) & 1, nullptr, 0);
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             // ---------------- MMA issuer ----------------
             constexpr uint32_t idesc = idesc_f16(kTBM, BN, 0);
+            uint32_t g = 0, lt = 0;
             bool ok = true;
-            for (int it = 0; it < nkb; ++it) {
-                const int s = it % C::STAGES;
-                ok = mbar_wait(&full[s], (it / C::STAGES) & 1, p.err, 12);
+            for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
+                if (p.slot_of[p.tile_expert[w / NT]] < 0) continue;
+                const uint32_t buf = lt & 1u;
+                ok = mbar_wait(&acc_empty[buf], ((lt >> 1) & 1u) ^ 1u, p.err, 15);     // epilogue has drained this accumulator set
                 if (!ok) break;
                 tc_fence_after();
-                const uint8_t* a = smem + s * C::STAGE_BYTES;
-                const uint64_t da0 = smem_desc_sw128(a), db = smem_desc_sw128(a + C::A_BYTES);
+                const uint32_t acc = tmem_d + buf * C::ACC_COLS;
+                for (int it = 0; it < nkb; ++it, ++g) {
+                    const int s = g % C::STAGES;
+                    ok = mbar_wait(&full[s], (g / C::STAGES) & 1, p.err, 12);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint8_t* a = smem + s * C::STAGE_BYTES;
+                    const uint64_t da0 = smem_desc_sw128(a), db = smem_desc_sw128(a + C::A_BYTES);
 #pragma unroll
-                for (int k = 0; k < kTBK / 16; ++k) {
-                    const uint32_t acc = (it > 0 || k > 0) ? 1u : 0u;
-                    umma_f16(tmem_d, da0 + 2 * k, db + 2 * k, idesc, acc);
-                    if (GATEUP) umma_f16(tmem_d + BN, smem_desc_sw128(a + kTBM * kTBK * 2) + 2 * k, db + 2 * k, idesc, acc);
+                    for (int k = 0; k < kTBK / 16; ++k) {
+                        const uint32_t accum = (it > 0 || k > 0) ? 1u : 0u;
+                        umma_f16(acc, da0 + 2 * k, db + 2 * k, idesc, accum);
+                        if (GATEUP) umma_f16(acc + BN, smem_desc_sw128(a + kTBM * kTBK * 2) + 2 * k, db + 2 * k, idesc, accum);
+                    }
+                    umma_commit(&empty[s]);
                 }
-                umma_commit(&empty[s]);
+                if (ok) umma_commit(&acc_full[buf]);
+                ++lt;
             }
-            if (ok) umma_commit(acc_full);
         }
-    } else {
+    } else if (warp < 2 + C::CONV_WARPS) {
         // ---------------- weight converters ----------------
         const int ct = threadIdx.x - 64;                       // 0..255
         const int row = ct / C::TPR, sub = ct % C::TPR;        // row within the A stage (gate rows, then up rows)
-        const int wrow = n0 + (row & (kTBM - 1));              // weight row in the expert matrix
         const bool is_up = GATEUP && row >= kTBM;
-        const uint8_t* w = base + (GATEUP ? (is_up ? p.ef.off_up : p.ef.off_gate) : p.ef.off_down);
-        const uint8_t* sf = base + (GATEUP ? (is_up ? p.ef.off_su : p.ef.off_sg) : p.ef.off_sd);
         // stages fetched ahead of the one being converted: enough bytes in flight per SM to cover HBM latency
-        // (nvfp4: 6 x 8 KB, fp8: 3 x 16 KB, bf16: 2 x 32 KB per CTA)
+        // (nvfp4: 6 x 8 KB, fp8 / q4_k: 3 x 16 KB / 3 x 10 KB, bf16: 2 x 32 KB per CTA)
         constexpr int PF = FMT == 2 ? 6 : (FMT == 0 ? 2 : 3);
-        typename CV::Raw raw[PF];
-#pragma unroll
-        for (int j = 0; j < PF; ++j)
-            if (j < nkb) CV::load(raw[j], w, sf, wrow, K, j * kTBK, sub);
+        uint32_t g = 0;
         bool ok = true;
-        for (int it0 = 0; it0 < nkb && ok; it0 += PF) {
+        for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
+            const int slot = p.slot_of[p.tile_expert[w / NT]];
+            if (slot < 0) continue;
+            const uint8_t* base = p.arena + (size_t)slot * p.ef.stride;
+            const int wrow = (w % NT) * kTBM + (row & (kTBM - 1));      // weight row in the expert matrix
+            const uint8_t* wp = base + (GATEUP ? (is_up ? p.ef.off_up : p.ef.off_gate) : p.ef.off_down);
+            const uint8_t* sf = base + (GATEUP ? (is_up ? p.ef.off_su : p.ef.off_sg) : p.ef.off_sd);
+            typename CV::Raw raw[PF];
 #pragma unroll
-            for (int j = 0; j < PF; ++j) {
-                const int it = it0 + j;
-                if (it < nkb && ok) {
-                    const int s = it % C::STAGES;
-                    ok = mbar_wait(&empty[s], ((it / C::STAGES) & 1) ^ 1, p.err, 13);
-                    if (ok) {
-                        const uint32_t tile = smem_u32(smem + s * C::STAGE_BYTES) + (is_up ? kTBM * kTBK * 2 : 0);
-                        if constexpr (FMT == 3) CV::emit(raw[j], tile, row & (kTBM - 1), sub, it * kTBK);
-                        else CV::emit(raw[j], tile, row & (kTBM - 1), sub);
-                        if (it + PF < nkb) CV::load(raw[j], w, sf, wrow, K, (it + PF) * kTBK, sub);
-                        fence_proxy_async();                   // generic-proxy stores -> visible to the MMA's async-proxy reads
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(&full[s]);
-                    }
-                }
-            }
-        }
-        // ---------------- epilogue (warps 2-5: one TMEM lane quarter each) ----------------
-        if (warp < 6) {
-            const int q = warp & 3;
-            const int n = n0 + q * 32 + lane;
-            ok = mbar_wait(acc_full, 0, p.err, 14);
-            tc_fence_after();
-            if (ok) {
-                float sg = 1.f, su = 1.f;
-                if (FMT == 2 && (GATEUP || p.down_scale == 0.f)) {
-                    const float* tail = reinterpret_cast<const float*>(base + p.ef.off_tail);
-                    if (GATEUP) { sg = tail[0]; su = tail[1]; } else sg = p.down_scale != 0.f ? p.down_scale : tail[2];
-                } else if (FMT == 2) {
-                    sg = p.down_scale;
-                } else if (FMT == 1) {
-                    sg = su = kFp8Unscale;
-                }
-                const uint32_t lane_addr = tmem_d + ((uint32_t)(q * 32) << 16);
-#pragma unroll 1
-                for (int c0 = 0; c0 < BN; c0 += 16) {
-                    if (c0 >= ncols) break;
-                    float g[16], u[16];
-                    tmem_ld16(lane_addr + (uint32_t)c0, g);
-                    if (GATEUP) tmem_ld16(lane_addr + (uint32_t)(BN + c0), u);
+            for (int j = 0; j < PF; ++j)
+                if (j < nkb) CV::load(raw[j], wp, sf, wrow, K, j * kTBK, sub);
+            for (int it0 = 0; it0 < nkb && ok; it0 += PF) {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        if (c0 + j < ncols && n < NOUT) {
-                            if (GATEUP) {
-                                float gv = g[j] * sg, uv = u[j] * su;
-                                if (p.limit > 0.f) { gv = fminf(gv, p.limit); uv = fminf(fmaxf(uv, -p.limit), p.limit); }
-                                p.act[(size_t)(row0 + c0 + j) * NOUT + n] = __float2half_rn(siluf_(gv) * uv);
-                            } else if (ep_mode) {
-                                const int2 ra = p.ep.ret[p.ep.rank][row0 + c0 + j];      // (token owner, pair index there)
-                                p.ep.y[ra.x][(size_t)ra.y * NOUT + n] = g[j] * sg;        // NVLink store into the owner's buffer
-                            } else if (p.out_bf16) {
-                                reinterpret_cast<bf16*>(p.y)[(size_t)p.sorted_pair[row0 + c0 + j] * p.ldo + n] = __float2bfloat16(g[j] * sg);
-                            } else {
-                                p.y[(size_t)p.sorted_pair[row0 + c0 + j] * p.ldo + n] = g[j] * sg;
-                            }
+                for (int j = 0; j < PF; ++j) {
+                    const int it = it0 + j;
+                    if (it < nkb && ok) {
+                        const int s = g % C::STAGES;
+                        ok = mbar_wait(&empty[s], ((g / C::STAGES) & 1) ^ 1, p.err, 13);
+                        if (ok) {
+                            const uint32_t tile = smem_u32(smem + s * C::STAGE_BYTES) + (is_up ? kTBM * kTBK * 2 : 0);
+                            if constexpr (FMT == 3) CV::emit(raw[j], tile, row & (kTBM - 1), sub, it * kTBK);
+                            else CV::emit(raw[j], tile, row & (kTBM - 1), sub);
+                            if (it + PF < nkb) CV::load(raw[j], wp, sf, wrow, K, (it + PF) * kTBK, sub);
+                            fence_proxy_async();               // generic-proxy stores -> visible to the MMA's async-proxy reads
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(&full[s]);
+                            ++g;
                         }
                     }
                 }
             }
         }
+    } else {
+        // ---------------- epilogue (4 warps: one TMEM lane quarter each) ----------------
+        const int q = warp & 3;
+        uint32_t lt = 0;
+        bool ok = true;
+        for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
+            const int t = w / NT;
+            const int e = p.tile_expert[t];
+            const int slot = p.slot_of[e];
+            if (slot < 0) continue;
+            const int row0 = p.tile_row0[t], ncols = p.tile_n[t];
+            const int n = (w % NT) * kTBM + q * 32 + lane;
+            const uint8_t* base = p.arena + (size_t)slot * p.ef.stride;
+            const uint32_t buf = lt & 1u;
+            ok = mbar_wait(&acc_full[buf], (lt >> 1) & 1u, p.err, 14);
+            tc_fence_after();
+            if (ok) {
+                float sg = 1.f, su = 1.f;
+                if (FMT == 2 && (GATEUP || p.down_scale == 0.f)) {
+                    const float* tail = reinterpret_cast<const float*>(base + p.ef.off_tail);
+                    if (GATEUP) { sg = tail[0]; su = tail[1]; } else sg = tail[2];
+                } else if (FMT == 2) {
+                    sg = p.down_scale;
+                } else if (FMT == 1) {
+                    sg = su = kFp8Unscale;
+                }
+                const uint32_t lane_addr = tmem_d + buf * C::ACC_COLS + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 16) {
+                    if (c0 >= ncols) break;
+                    float gq[16], uq[16];
+                    tmem_ld16(lane_addr + (uint32_t)c0, gq);
+                    if (GATEUP) tmem_ld16(lane_addr + (uint32_t)(BN + c0), uq);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        if (c0 + j < ncols && n < NOUT) {
+                            if (GATEUP) {
+                                float gv = gq[j] * sg, uv = uq[j] * su;
+                                if (p.limit > 0.f) { gv = fminf(gv, p.limit); uv = fminf(fmaxf(uv, -p.limit), p.limit); }
+                                p.act[(size_t)(row0 + c0 + j) * NOUT + n] = __float2half_rn(siluf_(gv) * uv);
+                            } else if (ep_mode) {
+                                const int2 ra = p.ep.ret[p.ep.rank][row0 + c0 + j];      // (token owner, pair index there)
+                                p.ep.y[ra.x][(size_t)ra.y * NOUT + n] = gq[j] * sg;       // NVLink store into the owner's buffer
+                            } else if (p.out_bf16) {
+                                reinterpret_cast<bf16*>(p.y)[(size_t)p.sorted_pair[row0 + c0 + j] * p.ldo + n] = __float2bfloat16(gq[j] * sg);
+                            } else {
+                                p.y[(size_t)p.sorted_pair[row0 + c0 + j] * p.ldo + n] = gq[j] * sg;
+                            }
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);       // the MMA issuer may overwrite this accumulator set
+            ++lt;
+        }
     }
     tc_fence_before();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem_d, C::TMEM_COLS);
-    if (ep_mode && !GATEUP) ep_signal(p.ep, 2, ep_epoch, ep_blocks);
+    if (ep_mode && !GATEUP) ep_signal(p.ep, 2, ep_epoch, gridDim.x);
     pdl_launch_dependents();
+}
+
+static int sm_count() {
+    static int n = 0;
+    if (!n) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    }
+    return n;
 }
 
 template <int FMT, int BN, bool GATEUP>
@@ -448,7 +489,9 @@ static int launch_moe_tc(const CUtensorMap& mb, const MoeTcParams& p, int nout, 
     using C = MoeTcCfg<BN, GATEUP>;
     static bool attr = false;
     if (!attr) { cudaFuncSetAttribute(moe_tc_ffn_kernel<FMT, BN, GATEUP>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM); attr = true; }
-    launch_pdl((moe_tc_ffn_kernel<FMT, BN, GATEUP>), dim3(nout / kTBM, max_tiles), C::THREADS, C::SMEM, st, mb, p);
+    const long long work = (long long)(nout / kTBM) * max_tiles;
+    const int grid = (int)(work < sm_count() ? (work > 0 ? work : 1) : sm_count());
+    launch_pdl((moe_tc_ffn_kernel<FMT, BN, GATEUP>), grid, C::THREADS, C::SMEM, st, mb, p);
     return (int)cudaGetLastError();
 }
 

@@ -400,6 +400,7 @@ class DeviceModel:
         self.Fd = cfg.dense_inter // tp_size
         self.V_local = cfg.vocab // tp_size
         self._fused = False
+        self.streamer = None      # ExpertStreamer when the VRAM expert cache is capped (runtime/streaming.py)
         self.comm = None          # PeerComm for the fused all-reduces
         self.comm_amax = None     # PeerComm for the argmax exchange
         self.layers: List[dict] = []
@@ -728,37 +729,64 @@ class DeviceModel:
             return
         arena: ExpertArena = L["arena"]
         S = ws.S
-        E_total = cfg.n_routed + cfg.n_shared
         L["router"](ws.logits_r, ws.x, R)
         sc = {"sigmoid": 0, "softmax": 1, "sqrtsoftplus": 2}[cfg.scoring]
         nat.call("lsb_router_topk", ws.logits_r, L["router_bias"], ws.ids, ws.wts, R, cfg.n_routed, cfg.top_k, cfg.n_group,
                  cfg.topk_group, sc, int(cfg.norm_topk_prob), cfg.routed_scale, cfg.n_shared, cfg.n_routed)
-        efp = ctypes.addressof(arena.ef)
-        fast_fp4 = arena.ef.fmt == 2 and cfg.moe_inter % 128 == 0 and cfg.hidden % 128 == 0
+        if self.streamer is not None:
+            # capped expert cache: experts are brought in from pinned host memory in waves; every wave runs the
+            # expert kernels over what is resident, the combine runs once at the end over all slots
+            present = self.streamer.run_layer(self, i, arena, ws, R)
+        else:
+            self._moe_prepare(arena, ws, R)
+            self._moe_experts(arena, ws, R, ws.miss if self.tp_size == 1 else None)
+            present = arena.slot_of
+        nat.call("lsb_moe_combine", ws.sub, ws.y, ws.wts, ws.ids, present, R, S, cfg.hidden, 0, self._cp)
+        self._reduce(ws, R)
+
+    def _moe_mode(self, arena: ExpertArena, ws: Workspace, R: int) -> str:
+        cfg = self.cfg
         if getattr(ws, "tc_ok", False) and R >= TC_MOE_MIN_ROWS:
+            return "tc"
+        fast_fp4 = arena.ef.fmt == 2 and cfg.moe_inter % 128 == 0 and cfg.hidden % 128 == 0
+        return "pairs" if (fast_fp4 and R * ws.S <= 72) else "groups"
+
+    def _moe_prepare(self, arena: ExpertArena, ws: Workspace, R: int):
+        """Group the step's (row, slot) pairs by expert (once per layer, independent of residency)."""
+        cfg, S = self.cfg, ws.S
+        E_total = cfg.n_routed + cfg.n_shared
+        mode = self._moe_mode(arena, ws, R)
+        if mode == "tc":
             P = R * S
-            err = TcScratch.get(self.device).err
             nat.call("lsb_moe_tc_sort", ws.ids, P, E_total, ws.tc_bn, ws.tc_sorted, ws.tc_tile_e, ws.tc_tile_r0, ws.tc_tile_n, ws.tc_cnt)
             nat.call("lsb_moe_tc_gather", ws.x, ws.tc_sorted, ws.tc_cnt, ws.tc_xs, P, S, cfg.hidden)
+        elif mode == "groups":
+            nat.call("lsb_moe_build_groups", ws.ids, R * S, E_total, ws.group_expert, ws.group_n, ws.group_pairs, ws.n_groups, ws.counts)
+
+    def _moe_experts(self, arena: ExpertArena, ws: Workspace, R: int, miss):
+        """gate/up + SwiGLU and down projections of every pair whose expert is resident (``arena.slot_of[e] >= 0``)."""
+        cfg, S = self.cfg, ws.S
+        E_total = cfg.n_routed + cfg.n_shared
+        efp = ctypes.addressof(arena.ef)
+        mode = self._moe_mode(arena, ws, R)
+        if mode == "tc":
+            P = R * S
+            err = TcScratch.get(self.device).err
             tiles = min(ws.tc_tiles, P // ws.tc_bn + E_total + 1)
             nat.call("lsb_moe_tc_ffn", 1, ws.tc_xs, ws.tc_xs.shape[0], arena.data, arena.slot_of, efp, ws.tc_tile_e, ws.tc_tile_r0, ws.tc_tile_n,
-                     ws.tc_cnt, ws.tc_sorted, ws.tc_act, ws.tc_bn, tiles, cfg.swiglu_limit, ws.miss if self.tp_size == 1 else None, err, None)
+                     ws.tc_cnt, ws.tc_sorted, ws.tc_act, ws.tc_bn, tiles, cfg.swiglu_limit, miss, err, None)
             nat.call("lsb_moe_tc_ffn", 0, ws.tc_act, ws.tc_act.shape[0], arena.data, arena.slot_of, efp, ws.tc_tile_e, ws.tc_tile_r0, ws.tc_tile_n,
                      ws.tc_cnt, ws.tc_sorted, ws.y, ws.tc_bn, tiles, 0.0, None, err, None)
-        elif fast_fp4 and R * S <= 72:
+        elif mode == "pairs":
             # small batch: every (row, slot) pair streams its expert on its own - no grouping pass
-            nat.call("lsb_moe_gateup", ws.x, arena.data, arena.slot_of, efp, ws.ids, None, None, None,
-                     ws.act, S, R * S, cfg.swiglu_limit, ws.miss if self.tp_size == 1 else None)
+            nat.call("lsb_moe_gateup", ws.x, arena.data, arena.slot_of, efp, ws.ids, None, None, None, ws.act, S, R * S, cfg.swiglu_limit, miss)
             nat.call("lsb_moe_down", ws.act, arena.data, arena.slot_of, efp, ws.ids, None, None, None, ws.y, R * S)
         else:
-            nat.call("lsb_moe_build_groups", ws.ids, R * S, E_total, ws.group_expert, ws.group_n, ws.group_pairs, ws.n_groups, ws.counts)
             mg = min(ws.max_groups, min(R * S, (R * S + 3) // 4 + E_total))
             nat.call("lsb_moe_gateup", ws.x, arena.data, arena.slot_of, efp, ws.group_expert, ws.group_n, ws.group_pairs, ws.n_groups,
-                     ws.act, S, mg, cfg.swiglu_limit, ws.miss if self.tp_size == 1 else None)
+                     ws.act, S, mg, cfg.swiglu_limit, miss)
             nat.call("lsb_moe_down", ws.act, arena.data, arena.slot_of, efp, ws.group_expert, ws.group_n, ws.group_pairs, ws.n_groups,
                      ws.y, mg)
-        nat.call("lsb_moe_combine", ws.sub, ws.y, ws.wts, ws.ids, arena.slot_of, R, S, cfg.hidden, 0, self._cp)
-        self._reduce(ws, R)
 
     def _kda(self, i: int, L: dict, ws: Workspace, R: int, nseq: int):
         cfg = self.cfg

@@ -47,9 +47,7 @@ class EpMoE:
         self.max_pairs = max_tokens * top_k
         # worst case every pair of every rank lands on one owner; capacity_factor x the average is the allocation
         self.cap_rows = min(self.world * self.max_pairs, int(capacity_factor * self.max_pairs) + 128 * n_experts // self.world)
-        avg = self.max_pairs / max(1, min(n_experts // self.world, self.max_pairs))
-        self.BN = 32 if avg <= 32 else (64 if avg <= 96 else 128)
-        self.max_tiles = self.cap_rows // self.BN + n_experts // self.world + 2
+        self.max_tiles = self.cap_rows // 32 + n_experts // self.world + 2      # sized for the smallest token tile
         sizes = {"cnt_all": self.world * n_experts * 4, "xs": self.cap_rows * hidden * 2, "ret": self.cap_rows * 8,
                  "y": self.max_pairs * hidden * 4, "flags": 3 * self.world * 4}
         offs, cur = {}, 0
@@ -88,12 +86,18 @@ class EpMoE:
     def rows_received(self) -> int:
         return int(self.counters[1])
 
+    def _bn(self, R: int) -> int:
+        """Token-tile width from the expected rows per owned expert (every rank must pick the same value)."""
+        avg = R * self.S * self.world / self.E
+        return 32 if avg <= 32 else (64 if avg <= 96 else 128)
+
     # ------------------------------------------------------------------ fused path
     def forward(self, x: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, out: torch.Tensor, accumulate: bool = False):
         """x bf16 [R, H]; ids int32 [R, S] (expert per slot, < 0 = none); wts fp32 [R, S]; out fp32 [R, H]."""
         R = x.shape[0]
         assert R * self.S <= self.max_pairs and ids.dtype == torch.int32 and x.dtype == torch.bfloat16
         efp = ctypes.addressof(self.arena.ef)
+        self.BN = self._bn(R)
         nat.call("lsb_ep_dispatch", x, ids, R * self.S, self.S, self.BN, self.dst_off, self.cursor, self.tile_e, self.tile_r0, self.tile_n,
                  self.counters, self.max_tiles, self.ptr)
         for gateup, b, o, lim in ((1, self.xs_local, self.act, self.limit), (0, self.act, self.y_local, 0.0)):
@@ -106,7 +110,7 @@ class EpMoE:
     def _nccl_buffers(self):
         if getattr(self, "_nb", None) is None:
             dev, i32 = self.dev, dict(dtype=torch.int32, device=self.dev)
-            tiles = self.cap_rows // self.BN + self.E + 2
+            tiles = self.cap_rows // 32 + self.E + 2
             self._nb = dict(srt=torch.zeros(self.cap_rows, **i32), te=torch.zeros(tiles, **i32), tr=torch.zeros(tiles, **i32),
                             tn=torch.zeros(tiles, **i32), cnt=torch.zeros(2, **i32), xs=torch.zeros(self.cap_rows, self.H, dtype=torch.float16, device=dev),
                             y=torch.zeros(self.cap_rows, self.H, device=dev), tiles=tiles)
@@ -133,6 +137,7 @@ class EpMoE:
         dist.all_to_all_single(recv_e, send_e, rc, sc, group=self.group)
         nb = self._nccl_buffers()
         efp = ctypes.addressof(self.arena.ef)
+        self.BN = self._bn(R)
         if n_recv:
             nat.call("lsb_moe_tc_sort", recv_e, n_recv, self.E, self.BN, nb["srt"], nb["te"], nb["tr"], nb["tn"], nb["cnt"])
             nat.call("lsb_moe_tc_gather", recv_x, nb["srt"], nb["cnt"], nb["xs"], n_recv, 1, H)

@@ -52,7 +52,7 @@ def build_parser() -> argparse.ArgumentParser:
     eng.add_argument("--speculation-depth", type=int, default=None, help="draft tokens per speculative round (0 = off)")
     eng.add_argument("--cycle-budget-us", type=int, default=None, help="orchestrator idle poll period")
     eng.add_argument("--random-weights", action="store_true", help="random-init weights of the configured shape (benchmarks, smoke tests)")
-    eng.add_argument("--kv-format", default=None, choices=["fp8", "bf16"])
+    eng.add_argument("--kv-format", default=None, choices=["fp8", "bf16", "tq4"])
     eng.add_argument("--log-level", default="info", choices=["debug", "info", "warning", "error"])
     eng.add_argument("--test-engine", action="store_true", help="serve from the null engine (no GPU, deterministic tokens)")
     eng.add_argument("--dry-run", action="store_true", help="resolve and print the configuration, then exit")
@@ -168,7 +168,7 @@ def build_engine(cfg: dict, shape: ModelConfig, ckpt: Optional[str], args: argpa
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0)))
     torch.cuda.set_device(dev)
-    kv_fmt = args.kv_format or {"fp8_e4m3": "fp8", "bf16": "bf16", "fp16": "bf16"}.get(cfg["quantization"]["kv_cache"], "fp8")
+    kv_fmt = args.kv_format or {"fp8_e4m3": "fp8", "bf16": "bf16", "fp16": "bf16", "turboquant4": "tq4"}.get(cfg["quantization"]["kv_cache"], "fp8")
     if ckpt and not args.random_weights:
         from ..models.checkpoint import open_checkpoint
         _, w = open_checkpoint(ckpt, shape)

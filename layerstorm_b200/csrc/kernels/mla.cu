@@ -11,13 +11,20 @@
 //   0  bf16: (d_c + d_rope) bf16
 //   1  fp8 : d_c e4m3 bytes | fp32 per-token scale (+12 pad bytes) | d_rope bf16
 //          (the reference's FP8+BF16-RoPE row: docs/DESIGN.md:126, K/sm120/prep/fused_k_append.cu)
+//   2  tq4 : d_c / 2 bytes of 4-bit codes (low nibble = even index) | fp32 row scale (+12 pad bytes) | d_rope bf16
+//          TurboQuant: the latent is L2-normalised, rotated by a fixed per-layer orthogonal matrix and every coordinate
+//          (times sqrt(d_c), ~N(0,1)) is replaced by the nearest of 16 Lloyd-Max centroids; row scale = norm / sqrt(d_c).
+//          Attention runs in the rotated space: the rotation is folded into W_UK / W_UV when the weights are loaded, so
+//          decode only swaps the row loader (reference: 386-byte TurboQuant rows, src/compute/tq_init.h, docs/INTERNALS.md:8-9).
 // Pages hold `page` consecutive tokens; a sequence's pages are listed in its block table.
 #include "common.cuh"
 #include "gemv_core.cuh"
 
 namespace lsb {
 
-__host__ __device__ inline int kv_row_bytes(int fmt, int dl, int dr) { return fmt == 0 ? (dl + dr) * 2 : dl + 16 + dr * 2; }
+__host__ __device__ inline int kv_row_bytes(int fmt, int dl, int dr) {
+    return fmt == 0 ? (dl + dr) * 2 : (fmt == 1 ? dl + 16 + dr * 2 : dl / 2 + 16 + dr * 2);
+}
 
 __device__ __forceinline__ void rope_pair(float& a, float& b, float pos, float inv_freq) {
     float s, c;
@@ -31,7 +38,8 @@ __global__ void mla_prep_kernel(const float* __restrict__ proj, int ldp, int off
                                 const float* __restrict__ qa_norm_w, const float* __restrict__ kv_norm_w,
                                 const float* __restrict__ inv_freq, bf16* __restrict__ q_c, uint8_t* __restrict__ cache,
                                 const int* __restrict__ block_table, int max_pages, const int* __restrict__ row_seq,
-                                const int* __restrict__ row_pos, int page, int kv_fmt, float eps) {
+                                const int* __restrict__ row_pos, int page, int kv_fmt, float eps,
+                                const bf16* __restrict__ tq_rot_t, const float* __restrict__ tq_centroids) {
     __shared__ float red[33];
     extern __shared__ float sm[];   // [max(q_lora, dl + dr)]
     const int r = blockIdx.x, t = threadIdx.x;
@@ -66,6 +74,35 @@ __global__ void mla_prep_kernel(const float* __restrict__ proj, int ldp, int off
     if (kv_fmt == 0) {
         bf16* o = reinterpret_cast<bf16*>(row);
         for (int i = t; i < dl + dr; i += blockDim.x) o[i] = __float2bfloat16(sm[i]);
+    } else if (kv_fmt == 2) {
+        // rotated unit vector u' = Pi (c / |c|); tq_rot_t is Pi transposed, so consecutive threads read consecutive bytes
+        float n2 = 0.f;
+        for (int i = t; i < dl; i += blockDim.x) n2 += sm[i] * sm[i];
+        n2 = block_sum(n2, red);
+        const float norm = sqrtf(fmaxf(n2, 1e-30f));
+        const float up = sqrtf((float)dl) / norm;                 // coordinates of the unit vector times sqrt(d): ~N(0,1)
+        float cent[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) cent[j] = tq_centroids[j];
+        for (int i0 = 2 * t; i0 < dl; i0 += 2 * blockDim.x) {    // two coordinates -> one byte
+            float a0 = 0.f, a1 = 0.f;
+            for (int k = 0; k < dl; ++k) {
+                const bf162 w2 = *reinterpret_cast<const bf162*>(tq_rot_t + (size_t)k * dl + i0);
+                const float ck = sm[k];
+                a0 = fmaf(__low2float(w2), ck, a0); a1 = fmaf(__high2float(w2), ck, a1);
+            }
+            a0 *= up; a1 *= up;
+            int c0 = 0, c1 = 0;
+#pragma unroll
+            for (int j = 1; j < 16; ++j) {                        // centroids ascend: count the midpoints below the value
+                const float mid = 0.5f * (cent[j - 1] + cent[j]);
+                c0 += a0 > mid; c1 += a1 > mid;
+            }
+            row[i0 >> 1] = (uint8_t)(c0 | (c1 << 4));
+        }
+        if (t == 0) *reinterpret_cast<float*>(row + dl / 2) = norm / sqrtf((float)dl);
+        bf16* o = reinterpret_cast<bf16*>(row + dl / 2 + 16);
+        for (int i = t; i < dr; i += blockDim.x) o[i] = __float2bfloat16(sm[dl + i]);
     } else {
         const float scale = fmaxf(amax, 1e-10f) / 448.f;
         const float inv_s = 1.f / scale;
@@ -147,6 +184,7 @@ struct MlaDecodeParams {
     float* o_part; float* ml_part;              // [R,H,NS,dl], [R,H,NS,2]
     int H, dl, dr, page, kv_fmt, NS;
     float scale;
+    const float* tq_centroids;   // kv_fmt 2: the 16 reconstruction levels
 };
 
 __global__ void __launch_bounds__(256) mla_decode_kernel(MlaDecodeParams p) {
@@ -204,6 +242,39 @@ __global__ void __launch_bounds__(256) mla_decode_kernel(MlaDecodeParams p) {
                 *reinterpret_cast<uint4*>(Ks + j * DP + c * 8) = v;
             }
             if (t < kTK) sc[t] = 1.f;
+        } else if (p.kv_fmt == 2) {
+            const int c32 = p.dl / 32, cr = p.dr / 8, cpr = c32 + cr;   // 16 bytes = 32 codes
+            for (int i = t; i < kTK * cpr; i += blockDim.x) {
+                const int j = i / cpr, c = i % cpr, tok = s_tok[j];
+                const uint8_t* row = nullptr;
+                if (tok >= 0) {
+                    const int pg = p.block_table[(size_t)seq * p.max_pages + tok / p.page];
+                    row = p.cache + ((size_t)pg * p.page + tok % p.page) * rb;
+                }
+                if (c < c32) {
+                    const uint4 v = row ? *reinterpret_cast<const uint4*>(row + c * 16) : make_uint4(0x77777777u, 0x77777777u, 0x77777777u, 0x77777777u);
+                    const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
+                    bf162* o = reinterpret_cast<bf162*>(Ks + j * DP + c * 32);
+#pragma unroll
+                    for (int b = 0; b < 16; ++b) {
+                        const uint32_t byte = (wv[b >> 2] >> (8 * (b & 3))) & 0xffu;
+                        o[b] = __floats2bfloat162_rn(row ? __ldg(p.tq_centroids + (byte & 15u)) : 0.f, row ? __ldg(p.tq_centroids + (byte >> 4)) : 0.f);
+                    }
+                } else {
+                    const int cc = c - c32;
+                    uint4 v = row ? *reinterpret_cast<const uint4*>(row + p.dl / 2 + 16 + cc * 16) : make_uint4(0, 0, 0, 0);
+                    *reinterpret_cast<uint4*>(Ks + j * DP + p.dl + cc * 8) = v;
+                }
+            }
+            if (t < kTK) {
+                const int tok = s_tok[t];
+                float s = 0.f;
+                if (tok >= 0) {
+                    const int pg = p.block_table[(size_t)seq * p.max_pages + tok / p.page];
+                    s = *reinterpret_cast<const float*>(p.cache + ((size_t)pg * p.page + tok % p.page) * rb + p.dl / 2);
+                }
+                sc[t] = s;
+            }
         } else {
             const int c8 = p.dl / 16, cr = p.dr / 8, cpr = c8 + cr;
             for (int i = t; i < kTK * cpr; i += blockDim.x) {
@@ -365,13 +436,15 @@ LSB_API int lsb_kv_row_bytes(int fmt, int dl, int dr) { return kv_row_bytes(fmt,
 LSB_API int lsb_mla_prep(const void* proj, int ldp, int off_qa, int q_lora, int off_kv, int dl, int dr,
                          const void* qa_norm_w, const void* kv_norm_w, const void* inv_freq, void* q_c, void* cache,
                          const void* block_table, int max_pages, const void* row_seq, const void* row_pos, int rows,
-                         int page, int kv_fmt, float eps, void* stream) {
+                         int page, int kv_fmt, float eps, const void* tq_rot_t, const void* tq_centroids, void* stream) {
+    if (kv_fmt == 2 && (!tq_rot_t || !tq_centroids || dl % 32)) return -1;
     const int n = q_lora > dl + dr ? q_lora : dl + dr;
     launch_pdl((mla_prep_kernel), rows, 256, (size_t)n * 4, (cudaStream_t)stream, (const float*)proj, ldp, off_qa, q_lora, off_kv, dl, dr,
                                                                       (const float*)qa_norm_w, (const float*)kv_norm_w,
                                                                       (const float*)inv_freq, (bf16*)q_c, (uint8_t*)cache,
                                                                       (const int*)block_table, max_pages, (const int*)row_seq,
-                                                                      (const int*)row_pos, page, kv_fmt, eps);
+                                                                      (const int*)row_pos, page, kv_fmt, eps, (const bf16*)tq_rot_t,
+                                                                      (const float*)tq_centroids);
     LSB_CHECK_LAUNCH();
 }
 
@@ -414,14 +487,15 @@ LSB_API int lsb_mla_decode_smem_bytes(int dl, int dr) {
 LSB_API int lsb_mla_decode(const void* q, const void* cache, const void* block_table, int max_pages, const void* row_seq,
                            const void* row_len, const void* sel_idx, const void* sel_cnt, int sel_ld, void* out, void* lse,
                            void* o_part, void* ml_part, int R, int H, int dl, int dr, int page, int kv_fmt, int NS,
-                           float scale, void* stream) {
+                           float scale, const void* tq_centroids, void* stream) {
     if (dl % 16 || dr % 8 || dl > 512 || NS > 32) return -1;
+    if (kv_fmt == 2 && (!tq_centroids || dl % 32)) return -1;
     cudaStream_t st = (cudaStream_t)stream;
     MlaDecodeParams p;
     p.q = (const bf16*)q; p.cache = (const uint8_t*)cache; p.block_table = (const int*)block_table; p.max_pages = max_pages;
     p.row_seq = (const int*)row_seq; p.row_len = (const int*)row_len; p.sel_idx = (const int*)sel_idx; p.sel_cnt = (const int*)sel_cnt;
     p.sel_ld = sel_ld; p.o_part = (float*)o_part; p.ml_part = (float*)ml_part; p.H = H; p.dl = dl; p.dr = dr; p.page = page;
-    p.kv_fmt = kv_fmt; p.NS = NS; p.scale = scale;
+    p.kv_fmt = kv_fmt; p.NS = NS; p.scale = scale; p.tq_centroids = (const float*)tq_centroids;
     const int smem = lsb_mla_decode_smem_bytes(dl, dr);
     static bool attr_set = false;
     if (!attr_set) {

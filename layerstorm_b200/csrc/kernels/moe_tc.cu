@@ -106,130 +106,115 @@ __device__ __forceinline__ __half2 e4m3x2_to_half2(uint16_t v) {
     return *reinterpret_cast<__half2*>(&r);
 }
 
-// One converter thread's share of one pipeline stage: NE = 64 / threads-per-row consecutive K
-// elements of one weight row.  `Raw` holds the bytes fetched from HBM (issued early), `emit`
-// expands them to fp16 and stores the swizzled chunks.
-template <int FMT, int NE> struct Conv;
+// Weight conversion works in 16-byte "pieces" of raw weight bytes.  Consecutive converter threads take consecutive
+// pieces along a weight row and then the next row, so every 32-byte memory sector a warp touches is consumed
+// completely by that one load instruction (a row-per-thread mapping would fetch each sector twice).  A piece
+// expands to 8..32 fp16 values = 1..4 sixteen-byte chunks of the swizzled operand tile.
+//   Conv<FMT>::PPR   pieces per weight row per 64-element pipeline stage
+//   load(raw, w, sf, n, K, k0, c)   fetch piece c of matrix row n at reduction offset k0 (issued early)
+//   emit(raw, tile, row, c, k0)     expand and store it into row `row` of the operand tile
+template <int FMT> struct Conv;
 constexpr float kFp8Unscale = 1.f / 256.f;
 
-template <int NE> struct Conv<2, NE> {        // NVFP4: NE/2 bytes + one 4-scale word per 64-element stage
-    static constexpr int NV = NE / 32;        // uint4 loads
-    struct Raw { uint4 v[NV]; uint32_t sc; };
-    static __device__ __forceinline__ void load(Raw& r, const uint8_t* w, const uint8_t* sf, int n, int K, int k0, int sub) {
-        const uint8_t* p = w + (size_t)n * (K >> 1) + ((k0 + sub * NE) >> 1);
-#pragma unroll
-        for (int i = 0; i < NV; ++i) r.v[i] = ldg_stream(p + 16 * i);
+template <> struct Conv<2> {                  // NVFP4: 32 bytes per row-stage; 4 group scales in one word
+    static constexpr int PPR = 2;
+    struct Raw { uint4 v; uint32_t sc; };
+    static __device__ __forceinline__ void load(Raw& r, const uint8_t* w, const uint8_t* sf, int n, int K, int k0, int c) {
+        r.v = ldg_stream(w + (size_t)n * (K >> 1) + (k0 >> 1) + 16 * c);
         const int gtiles = ((K >> 4) + 3) >> 2;
         r.sc = __ldg(reinterpret_cast<const uint32_t*>(sf + ((size_t)(n >> 7) * gtiles + (k0 >> 6)) * 512 + (n & 31) * 16 + ((n & 127) >> 5) * 4));
     }
-    static __device__ __forceinline__ void emit(const Raw& r, uint32_t tile, int row, int sub) {
+    static __device__ __forceinline__ void emit(const Raw& r, uint32_t tile, int row, int c, int) {
+        const uint32_t wv[4] = {r.v.x, r.v.y, r.v.z, r.v.w};
 #pragma unroll
-        for (int i = 0; i < NV; ++i) {
-            const uint32_t wv[4] = {r.v[i].x, r.v[i].y, r.v[i].z, r.v[i].w};
+        for (int j = 0; j < 4; ++j) {                 // 8 elements = one 16-byte fp16 chunk
+            __half2 h[4];
+            fp4x8_to_half2x4(wv[j], h);
+            // both halves of s2 = the e4m3 scale of this chunk's 16-group (byte 2c + j/2 of the scale word)
+            const __half2 s2 = e4m3x2_to_half2((uint16_t)(((r.sc >> ((2 * c + (j >> 1)) * 8)) & 0xffu) * 0x0101u));
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {                 // 8 elements = one 16-byte fp16 chunk
-                const int e0 = sub * NE + i * 32 + j * 8; // element offset within the 64-wide stage row
-                __half2 h[4];
-                fp4x8_to_half2x4(wv[j], h);
-                // both halves of s2 = the e4m3 scale of this element's 16-group (byte e0/16 of the scale word)
-                const __half2 s2 = e4m3x2_to_half2((uint16_t)(((r.sc >> ((e0 >> 4) * 8)) & 0xffu) * 0x0101u));
-#pragma unroll
-                for (int q = 0; q < 4; ++q) h[q] = __hmul2(h[q], s2);
-                st_shared_16(sw128_chunk(tile, row, e0 >> 3), *reinterpret_cast<uint4*>(h));
-            }
+            for (int q = 0; q < 4; ++q) h[q] = __hmul2(h[q], s2);
+            st_shared_16(sw128_chunk(tile, row, 4 * c + j), *reinterpret_cast<uint4*>(h));
         }
     }
 };
 
-template <int NE> struct Conv<1, NE> {        // FP8 e4m3 with 128x128 block scales: NE bytes
-    static constexpr int NV = NE / 16;
-    struct Raw { uint4 v[NV]; float sc; };
-    static __device__ __forceinline__ void load(Raw& r, const uint8_t* w, const uint8_t* sf, int n, int K, int k0, int sub) {
-        const uint8_t* p = w + (size_t)n * K + k0 + sub * NE;
-#pragma unroll
-        for (int i = 0; i < NV; ++i) r.v[i] = ldg_stream(p + 16 * i);
+template <> struct Conv<1> {                  // FP8 e4m3 with 128x128 block scales: 64 bytes per row-stage
+    static constexpr int PPR = 4;
+    struct Raw { uint4 v; float sc; };
+    static __device__ __forceinline__ void load(Raw& r, const uint8_t* w, const uint8_t* sf, int n, int K, int k0, int c) {
+        r.v = ldg_stream(w + (size_t)n * K + k0 + 16 * c);
         r.sc = __ldg(reinterpret_cast<const float*>(sf) + (size_t)(n >> 7) * ((K + 127) >> 7) + (k0 >> 7));
     }
-    static __device__ __forceinline__ void emit(const Raw& r, uint32_t tile, int row, int sub) {
+    static __device__ __forceinline__ void emit(const Raw& r, uint32_t tile, int row, int c, int) {
         // block scales of small weights sit near the bottom of the fp16 range: carry them times 2^8 (exact)
         // and take the factor out again in the fp32 epilogue (kFp8Unscale)
         const __half2 s2 = __float2half2_rn(r.sc * 256.f);
+        const uint32_t wv[4] = {r.v.x, r.v.y, r.v.z, r.v.w};
 #pragma unroll
-        for (int i = 0; i < NV; ++i) {
-            const uint32_t wv[4] = {r.v[i].x, r.v[i].y, r.v[i].z, r.v[i].w};
-#pragma unroll
-            for (int j = 0; j < 2; ++j) {                 // 8 bytes -> 8 fp16
-                __half2 h[4];
-                h[0] = __hmul2(e4m3x2_to_half2((uint16_t)(wv[2 * j] & 0xffffu)), s2);
-                h[1] = __hmul2(e4m3x2_to_half2((uint16_t)(wv[2 * j] >> 16)), s2);
-                h[2] = __hmul2(e4m3x2_to_half2((uint16_t)(wv[2 * j + 1] & 0xffffu)), s2);
-                h[3] = __hmul2(e4m3x2_to_half2((uint16_t)(wv[2 * j + 1] >> 16)), s2);
-                const int e0 = sub * NE + i * 16 + j * 8;
-                st_shared_16(sw128_chunk(tile, row, e0 >> 3), *reinterpret_cast<uint4*>(h));
-            }
+        for (int j = 0; j < 2; ++j) {                 // 8 bytes -> 8 fp16
+            __half2 h[4];
+            h[0] = __hmul2(e4m3x2_to_half2((uint16_t)(wv[2 * j] & 0xffffu)), s2);
+            h[1] = __hmul2(e4m3x2_to_half2((uint16_t)(wv[2 * j] >> 16)), s2);
+            h[2] = __hmul2(e4m3x2_to_half2((uint16_t)(wv[2 * j + 1] & 0xffffu)), s2);
+            h[3] = __hmul2(e4m3x2_to_half2((uint16_t)(wv[2 * j + 1] >> 16)), s2);
+            st_shared_16(sw128_chunk(tile, row, 2 * c + j), *reinterpret_cast<uint4*>(h));
         }
     }
 };
 
-template <int NE> struct Conv<3, NE> {        // GGUF Q4_K: a 64-element stage = one (low, high) nibble pair of 32 quant bytes
-    struct Raw { uint4 hdr; uint4 q[2]; };
-    static __device__ __forceinline__ void load(Raw& r, const uint8_t* w, const uint8_t*, int n, int K, int k0, int) {
+template <> struct Conv<3> {                  // GGUF Q4_K: 32 quant bytes per row-stage = one (low, high) nibble pair of sub-blocks
+    static constexpr int PPR = 2;
+    struct Raw { uint4 hdr; uint4 q; };
+    static __device__ __forceinline__ void load(Raw& r, const uint8_t* w, const uint8_t*, int n, int K, int k0, int c) {
         const uint8_t* blk = w + ((size_t)n * (K >> 8) + (k0 >> 8)) * 144;
         r.hdr = __ldg(reinterpret_cast<const uint4*>(blk));
-        const uint8_t* qs = blk + 16 + ((k0 & 255) >> 6) * 32;
-        r.q[0] = ldg_stream(qs); r.q[1] = ldg_stream(qs + 16);
+        r.q = ldg_stream(blk + 16 + ((k0 & 255) >> 6) * 32 + 16 * c);
     }
-    // NE = 64: this thread emits both sub-blocks (low then high nibbles); NE = 32: sub-block `sub` only.
-    static __device__ __forceinline__ void emit(const Raw& r, uint32_t tile, int row, int sub, int k0 = 0) {
+    static __device__ __forceinline__ void emit(const Raw& r, uint32_t tile, int row, int c, int k0) {
         const __half2 dd = *reinterpret_cast<const __half2*>(&r.hdr.x);
         const float d = __low2float(dd), dmin = __high2float(dd);
         uint8_t sc12[12];
         const uint32_t hw[3] = {r.hdr.y, r.hdr.z, r.hdr.w};
 #pragma unroll
         for (int i = 0; i < 12; ++i) sc12[i] = (uint8_t)(hw[i >> 2] >> (8 * (i & 3)));
-        const uint32_t wv[8] = {r.q[0].x, r.q[0].y, r.q[0].z, r.q[0].w, r.q[1].x, r.q[1].y, r.q[1].z, r.q[1].w};
+        const uint32_t wv[4] = {r.q.x, r.q.y, r.q.z, r.q.w};
         const int j2 = ((k0 & 255) >> 6) * 2;                      // first sub-block of this stage
 #pragma unroll
-        for (int half_i = 0; half_i < 2; ++half_i) {
-            if (NE == 32 && half_i != sub) continue;
+        for (int half_i = 0; half_i < 2; ++half_i) {               // low nibbles: sub-block j2, high nibbles: j2 + 1
             float sc, mn;
             q4k_scale_min(sc12, j2 + half_i, sc, mn);
             const __half2 a2 = __float2half2_rn(d * sc), b2 = __float2half2_rn(-dmin * mn);
 #pragma unroll
-            for (int c8 = 0; c8 < 4; ++c8) {                       // 8 elements = bytes 8*c8 .. 8*c8+7 -> words 2*c8, 2*c8+1
+            for (int cc = 0; cc < 2; ++cc) {                       // bytes 8cc..8cc+7 of the piece -> elements 16c + 8cc ..
                 __half2 h[4];
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
-                    const uint32_t wq = wv[2 * c8 + (q >> 1)] >> ((q & 1) * 16 + half_i * 4);
+                    const uint32_t wq = wv[2 * cc + (q >> 1)] >> ((q & 1) * 16 + half_i * 4);
                     // two consecutive bytes -> two 4-bit values as exact fp16 integers (1024 + v) - 1024
                     const uint32_t bits = 0x64006400u | (wq & 0xFu) | (((wq >> 8) & 0xFu) << 16);
                     const __half2 v = __hsub2(*reinterpret_cast<const __half2*>(&bits), __float2half2_rn(1024.f));
                     h[q] = __hfma2(v, a2, b2);
                 }
-                st_shared_16(sw128_chunk(tile, row, half_i * 4 + c8), *reinterpret_cast<uint4*>(h));
+                st_shared_16(sw128_chunk(tile, row, half_i * 4 + 2 * c + cc), *reinterpret_cast<uint4*>(h));
             }
         }
     }
 };
 
-template <int NE> struct Conv<0, NE> {        // BF16: 2*NE bytes
-    static constexpr int NV = NE / 8;
-    struct Raw { uint4 v[NV]; };
-    static __device__ __forceinline__ void load(Raw& r, const uint8_t* w, const uint8_t*, int n, int K, int k0, int sub) {
-        const uint8_t* p = w + ((size_t)n * K + k0 + sub * NE) * 2;
-#pragma unroll
-        for (int i = 0; i < NV; ++i) r.v[i] = ldg_stream(p + 16 * i);
+template <> struct Conv<0> {                  // BF16: 128 bytes per row-stage
+    static constexpr int PPR = 8;
+    struct Raw { uint4 v; };
+    static __device__ __forceinline__ void load(Raw& r, const uint8_t* w, const uint8_t*, int n, int K, int k0, int c) {
+        r.v = ldg_stream(w + ((size_t)n * K + k0 + 8 * c) * 2);
     }
-    static __device__ __forceinline__ void emit(const Raw& r, uint32_t tile, int row, int sub) {
+    static __device__ __forceinline__ void emit(const Raw& r, uint32_t tile, int row, int c, int) {
+        float f[8];
+        unpack_bf16x8(r.v, f);
+        __half2 h[4];
 #pragma unroll
-        for (int i = 0; i < NV; ++i) {
-            float f[8];
-            unpack_bf16x8(r.v[i], f);
-            __half2 h[4];
-#pragma unroll
-            for (int q = 0; q < 4; ++q) h[q] = __floats2half2_rn(f[2 * q], f[2 * q + 1]);
-            st_shared_16(sw128_chunk(tile, row, (sub * NE + i * 8) >> 3), *reinterpret_cast<uint4*>(h));
-        }
+        for (int q = 0; q < 4; ++q) h[q] = __floats2half2_rn(f[2 * q], f[2 * q + 1]);
+        st_shared_16(sw128_chunk(tile, row, c), *reinterpret_cast<uint4*>(h));
     }
 };
 
@@ -262,9 +247,22 @@ template <int BN, bool GATEUP> struct MoeTcCfg {
     static constexpr int CONV_WARPS = 8;
     static constexpr int EPI_WARPS = 4;
     static constexpr int THREADS = (2 + CONV_WARPS + EPI_WARPS) * 32;
-    static constexpr int TPR = (CONV_WARPS * 32) / (A_TILES * kTBM);     // converter threads per weight row
-    static constexpr int NE = kTBK / TPR;                                 // elements per converter thread per stage
+    static constexpr int CONV_THREADS = CONV_WARPS * 32;
+    static constexpr int ROWS = A_TILES * kTBM;                           // weight rows per stage (gate rows, then up rows)
 };
+
+// Work item w -> (token tile t, weight tile j).  Items are grouped by kTileGroup consecutive token tiles (tiles are sorted
+// by expert, so a group mostly belongs to one expert); inside a group the token tile runs fastest, so the CTAs that
+// are in flight together read the same 128 weight rows and all but the first hit L2.
+constexpr int kTileGroup = 8;
+__device__ __forceinline__ void work_item(int w, int ntiles, int NT, int& t, int& j) {
+    const int per = kTileGroup * NT;
+    const int gi = w / per, r = w % per;
+    const int t0 = gi * kTileGroup;
+    const int gsz = min(kTileGroup, ntiles - t0);
+    t = t0 + r % gsz;
+    j = r / gsz;
+}
 
 // Persistent kernel: one CTA per SM walks the work list (token tile x 128-row weight tile, weight tile fastest so
 // that concurrently running CTAs share a token tile); the shared-memory ring, its barrier phases and the two TMEM
@@ -272,7 +270,7 @@ template <int BN, bool GATEUP> struct MoeTcCfg {
 template <int FMT, int BN, bool GATEUP>
 __global__ void __launch_bounds__(MoeTcCfg<BN, GATEUP>::THREADS) moe_tc_ffn_kernel(const __grid_constant__ CUtensorMap map_b, MoeTcParams p) {
     using C = MoeTcCfg<BN, GATEUP>;
-    using CV = Conv<FMT, C::NE>;
+    using CV = Conv<FMT>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
@@ -307,7 +305,8 @@ __global__ void __launch_bounds__(MoeTcCfg<BN, GATEUP>::THREADS) moe_tc_ffn_kern
         ep_wait(p.ep, 1, ep_epoch);                  // peers' rows have landed in this rank's staging buffer
         asm volatile("fence.proxy.async;" ::: "memory");   // ... and are ordered before the TMA (async proxy) reads
     }
-    const int total = p.counters[0] * NT;
+    const int ntiles = p.counters[0];
+    const int total = ntiles * NT;
 
     if (warp == 0) {
         if (lane == 0) {
@@ -315,10 +314,11 @@ __global__ void __launch_bounds__(MoeTcCfg<BN, GATEUP>::THREADS) moe_tc_ffn_kern
             uint32_t g = 0;
             bool ok = true;
             for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
-                const int t = w / NT;
+                int t, jn;
+                work_item(w, ntiles, NT, t, jn);
                 const int e = p.tile_expert[t];
                 if (p.slot_of[e] < 0) {              // expert not resident on this GPU: every role skips the item
-                    if (GATEUP && p.miss_flag && (w % NT) == 0) atomicExch(p.miss_flag, e + 1);
+                    if (GATEUP && p.miss_flag && jn == 0) atomicExch(p.miss_flag, e + 1);
                     continue;
                 }
                 const int row0 = p.tile_row0[t];
@@ -342,7 +342,9 @@ __global__ void __launch_bounds__(MoeTcCfg<BN, GATEUP>::THREADS) moe_tc_ffn_kern
             uint32_t g = 0, lt = 0;
             bool ok = true;
             for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
-                if (p.slot_of[p.tile_expert[w / NT]] < 0) continue;
+                int t, jn;
+                work_item(w, ntiles, NT, t, jn);
+                if (p.slot_of[p.tile_expert[t]] < 0) continue;
                 const uint32_t buf = lt & 1u;
                 ok = mbar_wait(&acc_empty[buf], ((lt >> 1) & 1u) ^ 1u, p.err, 15);     // epilogue has drained this accumulator set
                 if (!ok) break;
@@ -370,36 +372,55 @@ __global__ void __launch_bounds__(MoeTcCfg<BN, GATEUP>::THREADS) moe_tc_ffn_kern
     } else if (warp < 2 + C::CONV_WARPS) {
         // ---------------- weight converters ----------------
         const int ct = threadIdx.x - 64;                       // 0..255
-        const int row = ct / C::TPR, sub = ct % C::TPR;        // row within the A stage (gate rows, then up rows)
-        const bool is_up = GATEUP && row >= kTBM;
+        constexpr int NP = C::ROWS * CV::PPR / C::CONV_THREADS;   // pieces per thread per stage
         // stages fetched ahead of the one being converted: enough bytes in flight per SM to cover HBM latency
-        // (nvfp4: 6 x 8 KB, fp8 / q4_k: 3 x 16 KB / 3 x 10 KB, bf16: 2 x 32 KB per CTA)
         constexpr int PF = FMT == 2 ? 6 : (FMT == 0 ? 2 : 3);
+        int prow[NP], pc[NP];                                  // piece -> row inside the stage tile, piece inside the row
+#pragma unroll
+        for (int i = 0; i < NP; ++i) { const int pid = i * C::CONV_THREADS + ct; prow[i] = pid / CV::PPR; pc[i] = pid % CV::PPR; }
         uint32_t g = 0;
         bool ok = true;
         for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
-            const int slot = p.slot_of[p.tile_expert[w / NT]];
+            int t, jn;
+            work_item(w, ntiles, NT, t, jn);
+            const int slot = p.slot_of[p.tile_expert[t]];
             if (slot < 0) continue;
             const uint8_t* base = p.arena + (size_t)slot * p.ef.stride;
-            const int wrow = (w % NT) * kTBM + (row & (kTBM - 1));      // weight row in the expert matrix
-            const uint8_t* wp = base + (GATEUP ? (is_up ? p.ef.off_up : p.ef.off_gate) : p.ef.off_down);
-            const uint8_t* sf = base + (GATEUP ? (is_up ? p.ef.off_su : p.ef.off_sg) : p.ef.off_sd);
-            typename CV::Raw raw[PF];
+            const uint8_t* wp[NP];
+            const uint8_t* sfp[NP];
+            int wrow[NP];
+#pragma unroll
+            for (int i = 0; i < NP; ++i) {
+                const bool up = GATEUP && prow[i] >= kTBM;
+                wp[i] = base + (GATEUP ? (up ? p.ef.off_up : p.ef.off_gate) : p.ef.off_down);
+                sfp[i] = base + (GATEUP ? (up ? p.ef.off_su : p.ef.off_sg) : p.ef.off_sd);
+                wrow[i] = jn * kTBM + (prow[i] & (kTBM - 1));   // weight row in the expert matrix
+            }
+            typename CV::Raw raw[PF][NP];
 #pragma unroll
             for (int j = 0; j < PF; ++j)
-                if (j < nkb) CV::load(raw[j], wp, sf, wrow, K, j * kTBK, sub);
+                if (j < nkb) {
+#pragma unroll
+                    for (int i = 0; i < NP; ++i) CV::load(raw[j][i], wp[i], sfp[i], wrow[i], K, j * kTBK, pc[i]);
+                }
             for (int it0 = 0; it0 < nkb && ok; it0 += PF) {
 #pragma unroll
                 for (int j = 0; j < PF; ++j) {
                     const int it = it0 + j;
                     if (it < nkb && ok) {
                         const int s = g % C::STAGES;
-                        ok = mbar_wait(&empty[s], ((g / C::STAGES) & 1) ^ 1, p.err, 13);
+                        // one lane polls the barrier, the warp sleeps at the sync: waiting warps leave the issue slots alone
+                        int okw = 1;
+                        if (lane == 0) okw = mbar_wait(&empty[s], ((g / C::STAGES) & 1) ^ 1, p.err, 13) ? 1 : 0;
+                        ok = __shfl_sync(0xffffffffu, okw, 0) != 0;
                         if (ok) {
-                            const uint32_t tile = smem_u32(smem + s * C::STAGE_BYTES) + (is_up ? kTBM * kTBK * 2 : 0);
-                            if constexpr (FMT == 3) CV::emit(raw[j], tile, row & (kTBM - 1), sub, it * kTBK);
-                            else CV::emit(raw[j], tile, row & (kTBM - 1), sub);
-                            if (it + PF < nkb) CV::load(raw[j], wp, sf, wrow, K, (it + PF) * kTBK, sub);
+                            const uint32_t st_base = smem_u32(smem + s * C::STAGE_BYTES);
+#pragma unroll
+                            for (int i = 0; i < NP; ++i) {
+                                const uint32_t tile = st_base + ((GATEUP && prow[i] >= kTBM) ? kTBM * kTBK * 2 : 0);
+                                CV::emit(raw[j][i], tile, prow[i] & (kTBM - 1), pc[i], it * kTBK);
+                                if (it + PF < nkb) CV::load(raw[j][i], wp[i], sfp[i], wrow[i], K, (it + PF) * kTBK, pc[i]);
+                            }
                             fence_proxy_async();               // generic-proxy stores -> visible to the MMA's async-proxy reads
                             __syncwarp();
                             if (lane == 0) mbar_arrive(&full[s]);
@@ -415,15 +436,18 @@ __global__ void __launch_bounds__(MoeTcCfg<BN, GATEUP>::THREADS) moe_tc_ffn_kern
         uint32_t lt = 0;
         bool ok = true;
         for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
-            const int t = w / NT;
+            int t, jn;
+            work_item(w, ntiles, NT, t, jn);
             const int e = p.tile_expert[t];
             const int slot = p.slot_of[e];
             if (slot < 0) continue;
             const int row0 = p.tile_row0[t], ncols = p.tile_n[t];
-            const int n = (w % NT) * kTBM + q * 32 + lane;
+            const int n = jn * kTBM + q * 32 + lane;
             const uint8_t* base = p.arena + (size_t)slot * p.ef.stride;
             const uint32_t buf = lt & 1u;
-            ok = mbar_wait(&acc_full[buf], (lt >> 1) & 1u, p.err, 14);
+            int okw = 1;
+            if (lane == 0) okw = mbar_wait(&acc_full[buf], (lt >> 1) & 1u, p.err, 14) ? 1 : 0;
+            ok = __shfl_sync(0xffffffffu, okw, 0) != 0;
             tc_fence_after();
             if (ok) {
                 float sg = 1.f, su = 1.f;

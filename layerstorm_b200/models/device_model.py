@@ -23,7 +23,7 @@ from ..formats import quant
 from ..ops import _native as nat
 from .config import ModelConfig
 
-KV_FMT = {"bf16": 0, "fp8": 1}
+KV_FMT = {"bf16": 0, "fp8": 1, "tq4": 2}
 EXPERT_FMT = {"bf16": 0, "fp8_e4m3": 1, "nvfp4": 2, "gguf_q4_k": 3}
 
 
@@ -401,6 +401,7 @@ class DeviceModel:
         self.V_local = cfg.vocab // tp_size
         self._fused = False
         self.streamer = None      # ExpertStreamer when the VRAM expert cache is capped (runtime/streaming.py)
+        self.tq_centroids = None  # TurboQuant reconstruction levels (kv_fmt "tq4")
         self.comm = None          # PeerComm for the fused all-reduces
         self.comm_amax = None     # PeerComm for the argmax exchange
         self.layers: List[dict] = []
@@ -662,8 +663,25 @@ class DeviceModel:
             d[:, ef.off_sg: ef.off_tail].random_(0x30, 0x40, generator=gen)
             d[:, ef.off_tail: ef.off_tail + 12].view(torch.float32).fill_(0.02 / 2.1)
 
+    def _fold_turboquant(self):
+        """4-bit KV: attention runs in a rotated latent space.  The per-layer rotation is folded into W_UK / W_UV here, so
+        the only run-time cost is the rotation of each new latent row when it is appended."""
+        from ..formats import turboquant as tq
+        cfg = self.cfg
+        self.tq_centroids = tq.lloyd_max_gaussian(16).to(self.device)
+        for i, L in enumerate(self.layers):
+            if "k_b" not in L or "tq_rot_t" in L:
+                continue
+            rot = tq.rotation(cfg.kv_lora, i).to(self.device)
+            L["k_b_orig"], L["v_b_orig"] = L["k_b"], L["v_b"]
+            L["k_b"] = torch.einsum("ij,hjn->hin", rot, L["k_b"].float()).to(torch.bfloat16).contiguous()      # Pi @ W_UK[h]
+            L["v_b"] = torch.einsum("hdl,il->hdi", L["v_b"].float(), rot).to(torch.bfloat16).contiguous()      # W_UV[h] @ Pi^T
+            L["tq_rot_t"] = rot.T.contiguous().to(torch.bfloat16)
+
     def _finish(self):
         cfg = self.cfg
+        if self.kv_fmt == "tq4":
+            self._fold_turboquant()
         for L in self.layers:
             if "kda_in" in L:
                 self.max_proj = max(self.max_proj, L["kda_in"].N)
@@ -819,7 +837,7 @@ class DeviceModel:
                      self.idx_tail.get(i), ws.kstash, ws.row_seq, ws.row_pos, ws.row_slot, R, P, 1e-6)
         nat.call("lsb_mla_prep", ws.proj, ldp, off_qa, cfg.q_lora, off_kv, dl, dr, L["qa_norm"], L["kv_norm"], self.inv_freq,
                  ws.q_c, self.kv_cache[i], self.block_table, self.max_pages, ws.row_seq, ws.row_pos, R, self.page,
-                 KV_FMT[self.kv_fmt], cfg.rms_eps)
+                 KV_FMT[self.kv_fmt], cfg.rms_eps, L.get("tq_rot_t"), self.tq_centroids)
         ldq = self.max_qb
         L["mla_qb"](ws.qproj, ws.q_c, R, ldo=ldq)
         nat.call("lsb_batched_gemv_bf16", ws.q_abs, ws.qproj, L["k_b"], R, Hh, dl, dn, ldq, dn + dr, Hh * (dl + dr), dl + dr,
@@ -838,7 +856,7 @@ class DeviceModel:
             sel_idx, sel_cnt, sel_ld = ws.sel_idx, ws.sel_cnt, ws.sel_ld
         nat.call("lsb_mla_decode", ws.q_abs, self.kv_cache[i], self.block_table, self.max_pages, ws.row_seq, ws.row_len,
                  sel_idx, sel_cnt, sel_ld, ws.o_lat, None, ws.o_part, ws.ml_part, R, Hh, dl, dr, self.page,
-                 KV_FMT[self.kv_fmt], ws.NS, cfg.softmax_scale)
+                 KV_FMT[self.kv_fmt], ws.NS, cfg.softmax_scale, self.tq_centroids)
         nat.call("lsb_batched_gemv_bf16", ws.attn_v, ws.o_lat, L["v_b"], R, Hh, dv, dl, Hh * dl, dl, Hh * dv, dv, 0, None, None)
         L["mla_o"](ws.sub, ws.attn_v, R, comm=self._cp)
         self._reduce(ws, R)
@@ -937,7 +955,7 @@ class DeviceModel:
                     out[x + "wq_b"] = wq[nq:]
                     out[x + "k_norm.weight"] = cpu(L["idx_ln_w"]); out[x + "k_norm.bias"] = cpu(L["idx_ln_b"])
                 out[a + "q_a_norm"] = cpu(L["qa_norm"]); out[a + "kv_a_norm"] = cpu(L["kv_norm"])
-                out[a + "k_b"] = cpu(L["k_b"]); out[a + "v_b"] = cpu(L["v_b"])
+                out[a + "k_b"] = cpu(L.get("k_b_orig", L["k_b"])); out[a + "v_b"] = cpu(L.get("v_b_orig", L["v_b"]))
                 out[a + "o"] = cpu(L["mla_o"].dequant())
             if "arena" in L:
                 mo = p + "moe."

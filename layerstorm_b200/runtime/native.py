@@ -707,3 +707,46 @@ class BufferRegistry:
 
     def contains(self, bid, ptr, nbytes) -> bool: return bool(self.lib.lsb_bufreg_contains(self.h, bid, ptr, nbytes))
     def __len__(self): return self.lib.lsb_bufreg_count(self.h)
+
+
+class CpuExperts:
+    """Host execution of expert FFNs from the GPU's slot images (csrc/runtime/cpu_experts.cpp)."""
+
+    def __init__(self, threads: int = 0, cpus: Optional[List[int]] = None):
+        import os
+        self.lib = load()
+        n = threads or max(1, min(32, os.cpu_count() or 1))
+        arr = _iarr(list(cpus)) if cpus else None
+        self.h = self.lib.lsb_cpu_pool_create(n, _vp(arr) if arr is not None else None, len(cpus) if cpus else 0)
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            self.lib.lsb_cpu_pool_destroy(self.h); self.h = None
+
+    @property
+    def threads(self) -> int: return self.lib.lsb_cpu_pool_size(self.h)
+
+    def ffn(self, ef_struct_addr: int, slot, x, limit: float = 0.0, scale=None, out=None, accumulate: bool = False):
+        """``slot``: uint8 CPU tensor (one slot image); ``x``: fp32 CPU [n, H]."""
+        import torch
+        x = x.contiguous().float()
+        n, H = x.shape
+        out = torch.zeros(n, H) if out is None else out
+        sc = scale.contiguous().float() if scale is not None else None
+        _check(self.lib.lsb_cpu_expert_ffn(self.h, ctypes.c_void_p(ef_struct_addr), ctypes.c_void_p(slot.data_ptr()), ctypes.c_void_p(x.data_ptr()), n,
+                                           float(limit), ctypes.c_void_p(sc.data_ptr()) if sc is not None else None,
+                                           ctypes.c_void_p(out.data_ptr()), int(accumulate)), "cpu expert ffn")
+        return out
+
+    def moe_layer(self, ef_struct_addr: int, slots: dict, n_experts: int, x, ids, wts, limit: float = 0.0):
+        """``slots``: expert id -> uint8 CPU tensor.  Returns fp32 [tokens, H]."""
+        import torch
+        x, ids, wts = x.contiguous().float(), ids.contiguous().int(), wts.contiguous().float()
+        T, H = x.shape
+        S = ids.shape[1]
+        ptrs = (ctypes.c_void_p * n_experts)(*[ctypes.c_void_p(slots[e].data_ptr()) if e in slots else None for e in range(n_experts)])
+        out = torch.zeros(T, H)
+        _check(self.lib.lsb_cpu_moe_layer(self.h, ctypes.c_void_p(ef_struct_addr), _vp(ptrs), n_experts, ctypes.c_void_p(x.data_ptr()),
+                                          ctypes.c_void_p(ids.data_ptr()), ctypes.c_void_p(wts.data_ptr()), T, S, float(limit),
+                                          ctypes.c_void_p(out.data_ptr())), "cpu moe layer")
+        return out

@@ -132,15 +132,26 @@ class ExpertStreamer:
         while todo:
             wave: List[int] = []
             fetched: List[int] = []
+            locked = set()
+
+            def lock_landed():
+                # a copy that has landed is evictable until it is locked: pin this wave's experts as soon as they are ready
+                for f in fetched:
+                    if f not in locked and cache.is_ready(li, f):
+                        cache.lock(li, f)
+                        locked.add(f)
+
             for e in todo:
                 if len(wave) == arena.n_slots:
                     break
                 if cache.lookup(li, e) >= 0 and not cache.is_ready(li, e):
                     self._issue()                                # a prefetch of this expert is still on its way
                     self._settle()
+                    lock_landed()
                 if cache.lookup(li, e) >= 0:
                     self.stats["hits"] += 1
                     cache.lock(li, e)
+                    locked.add(e)
                 elif self._reserve(li, st, e):
                     self.stats["misses"] += 1
                     fetched.append(e)
@@ -151,8 +162,7 @@ class ExpertStreamer:
                 raise RuntimeError(f"layer {li}: no expert slot can be freed")
             self._issue()
             self._settle()
-            for e in fetched:
-                cache.lock(li, e)
+            lock_landed()
             so = torch.full_like(st["slot_of_host"], -1)
             for e in wave:
                 cache.touch(li, e, need[e])

@@ -148,3 +148,31 @@ def test_run_to_run_determinism():
         sid = eng.create_sequence()
         res.append(eng.prefill(sid, prompt, want_logits=True))
     assert res[0][0] == res[1][0] and torch.equal(res[0][1], res[1][1])
+
+
+def test_turboquant_kv_rows_match_reference_quantiser_and_oracle():
+    """4-bit TurboQuant KV: the cached codes equal the PyTorch reference quantiser's, and the logits stay close to the fp32 oracle."""
+    from layerstorm_b200.formats import turboquant as tq
+    cfg, m, oracle = build("tiny-mla-moe", kv="tq4")
+    assert m.kv_row_bytes == cfg.kv_lora // 2 + 16 + 2 * cfg.qk_rope
+    eng = Engine(m, max_seqs=1, max_ctx=128, prefill_chunk=8, max_batch=1, use_graph=False)
+    ids = torch.randint(0, cfg.vocab, (30,), generator=torch.Generator().manual_seed(8))
+    ref_logits = oracle.forward(ids)
+    sid = eng.create_sequence()
+    _, lg = eng.prefill(sid, ids[:28].tolist(), want_logits=True)
+    assert rel_err(lg, ref_logits[27]) < 0.25                      # 4-bit cache: coarse, but the same distribution
+    out, lg2 = eng.decode([sid], [int(ids[28])], return_logits=True)
+    assert rel_err(lg2[0], ref_logits[28]) < 0.25
+    # codes in the cache reproduce: quantise(dequantise(row)) is a fixed point of the reference quantiser
+    li = cfg.mla_layers()[0]
+    dl = cfg.kv_lora
+    page0 = m.kv_cache[li][int(m.block_table[eng.seqs[sid].slot, 0])].cpu()            # [page, row_bytes]
+    codes_b = page0[:8, : dl // 2]
+    codes = torch.stack([codes_b & 15, codes_b >> 4], -1).reshape(8, dl)
+    scale = page0[:8, dl // 2: dl // 2 + 4].contiguous().view(torch.float32).reshape(8)
+    levels, rot = tq.lloyd_max_gaussian(16), tq.rotation(dl, li)
+    c_hat = tq.dequantise(codes, scale, rot, levels)
+    codes2, scale2 = tq.quantise(c_hat, rot, levels)
+    assert float((codes2 == codes).float().mean()) > 0.97          # re-quantising the reconstruction gives the same codes (up to bf16 rotation rounding)
+    assert torch.all(scale > 0) and levels.numel() == 16 and torch.allclose(levels, -levels.flip(0), atol=1e-5)
+    assert torch.allclose(rot @ rot.T, torch.eye(dl), atol=1e-4)

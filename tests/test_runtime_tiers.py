@@ -262,3 +262,43 @@ def test_buffer_registry():
         b.add("logits", 0, 1)
     with pytest.raises(rt.NativeError):
         b.find("nope")
+
+
+# ---------------------------------------------------------------- CPU expert kernels
+@pytest.mark.parametrize("fmt,H,F", [("bf16", 64, 48), ("fp8_e4m3", 256, 128), ("nvfp4", 256, 128), ("gguf_q4_k", 256, 256)])
+def test_cpu_expert_ffn_reads_gpu_slot_images(fmt, H, F):
+    import ctypes
+    import torch
+    from layerstorm_b200.models.device_model import ExpertArena, QLinear, expert_layout
+    cpu = rt.CpuExperts(3)
+    assert cpu.threads == 3
+    g = torch.Generator().manual_seed(0)
+    E, S, T = 4, 2, 7
+    ef = expert_layout(fmt, H, F)
+    ar = ExpertArena(ef, E, E, "cpu")
+    deq = {}
+    for e in range(E):
+        mats = [torch.randn(F, H, generator=g) * 0.05, torch.randn(F, H, generator=g) * 0.05, torch.randn(H, F, generator=g) * 0.05]
+        ar.write_expert(e, *(QLinear.from_float(m, fmt, "cpu") for m in mats))
+        deq[e] = [m.double() for m in ar.read_expert(e, fmt)]
+    x = torch.randn(T, H, generator=g)
+
+    def ref_ffn(e, xv, limit):
+        gate, up, down = deq[e]
+        gv, uv = torch.clamp(xv.double() @ gate.T, max=limit), torch.clamp(xv.double() @ up.T, -limit, limit)
+        return (torch.nn.functional.silu(gv) * uv) @ down.T
+
+    y = cpu.ffn(ctypes.addressof(ef), ar.data[1], x, limit=3.0)
+    want = ref_ffn(1, x, 3.0)
+    assert float((y.double() - want).abs().max() / want.abs().max()) < 1e-5
+    ids = torch.randint(0, E, (T, S), generator=g).int()
+    ids[2, 1] = 3
+    wts = torch.rand(T, S, generator=g)
+    slots = {e: ar.data[e] for e in range(E) if e != 3}            # expert 3 is not available on the host
+    out = cpu.moe_layer(ctypes.addressof(ef), slots, E, x, ids, wts, limit=3.0)
+    want = torch.zeros(T, H, dtype=torch.float64)
+    for t in range(T):
+        for s in range(S):
+            if int(ids[t, s]) != 3:
+                want[t] += float(wts[t, s]) * ref_ffn(int(ids[t, s]), x[t:t + 1], 3.0)[0]
+    assert float((out.double() - want).abs().max() / want.abs().max()) < 1e-5

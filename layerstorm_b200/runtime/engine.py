@@ -82,6 +82,9 @@ class Engine:
         return slot
 
     def free_sequence(self, sid: int):
+        if getattr(self, "hibernated", None) and sid in self.hibernated:
+            self.hibernated.pop(sid)
+            self.tier.destroy(sid)
         s = self.seqs.pop(sid)
         self.pa.destroy(s.slot)
         self.free_slots.append(s.slot)
@@ -119,6 +122,67 @@ class Engine:
                 t[slot].copy_(t[ps.slot])
             self._sync_block_table(cs)
         return slot
+
+    # ------------------------------------------------------------------ KV tiering (hibernate / resume)
+    def enable_kv_tiering(self, cold_pages: int):
+        """Reserve a pinned host pool of ``cold_pages`` KV pages (all attention layers of a page travel together).
+        A hibernated sequence gives its HBM pages back to the pool and keeps only host copies; its slot (recurrent
+        state, indexer tail) stays.  The native tier table tracks which logical page sits in which cold slot."""
+        m = self.model
+        self.cold_pages = cold_pages
+        self.tier = rt.KvTierTable(self.page, 0, cold_pages, 0)
+        self.cold_kv = {i: torch.empty(cold_pages, *t.shape[1:], dtype=t.dtype).pin_memory() for i, t in m.kv_cache.items()}
+        self.cold_idx = {i: torch.empty(cold_pages, *t.shape[1:], dtype=t.dtype).pin_memory() for i, t in m.idx_cache.items()}
+        self.hibernated: Dict[int, List[int]] = {}
+        self.copy_stream = torch.cuda.Stream(device=self.dev)
+
+    def hibernate(self, sid: int) -> int:
+        """Move every KV page of the sequence to pinned host memory and free its HBM pages.  Returns the pages freed.
+        Shared (forked) pages are copied too: the sequence becomes independent of its relatives."""
+        s = self.seqs[sid]
+        if sid in self.hibernated:
+            return 0
+        n = len(s.pages)
+        if n > self.tier.free_cold_slots():
+            raise RuntimeError(f"cold pool full: need {n} pages, {self.tier.free_cold_slots()} free")
+        self.tier.create(sid)
+        self.tier.demotion_candidates(sid, n * self.page + self.page)          # sizes the per-sequence table
+        slots = [self.tier.demote(sid, p) for p in range(n)]
+        self.stream.synchronize()                                              # the pages are final
+        with torch.cuda.stream(self.copy_stream):
+            for p, (pg, cs) in enumerate(zip(s.pages, slots)):
+                for i, t in self.model.kv_cache.items():
+                    self.cold_kv[i][cs].copy_(t[pg], non_blocking=True)
+                for i, t in self.model.idx_cache.items():
+                    self.cold_idx[i][cs].copy_(t[pg], non_blocking=True)
+            self.d2h_bytes += n * sum(t[0].numel() * t.element_size() for t in list(self.model.kv_cache.values()) + list(self.model.idx_cache.values()))
+        self.copy_stream.synchronize()
+        self.pa.rewind(s.slot, 0)                                              # HBM pages go back to the allocator
+        self.hibernated[sid] = slots
+        s.pages = []
+        return n
+
+    def resume(self, sid: int):
+        """Bring a hibernated sequence back: allocate pages, copy host -> device, rebuild the block table."""
+        slots = self.hibernated.pop(sid)
+        s = self.seqs[sid]
+        self.pa.extend(s.slot, s.length)                                       # may raise KvPoolExhausted: the caller evicts and retries
+        s.pages = self.pa.pages(s.slot)
+        with torch.cuda.stream(self.copy_stream):
+            for pg, cs in zip(s.pages, slots):
+                for i, t in self.model.kv_cache.items():
+                    t[pg].copy_(self.cold_kv[i][cs], non_blocking=True)
+                for i, t in self.model.idx_cache.items():
+                    t[pg].copy_(self.cold_idx[i][cs], non_blocking=True)
+            self.h2d_bytes += len(slots) * sum(t[0].numel() * t.element_size() for t in list(self.model.kv_cache.values()) + list(self.model.idx_cache.values()))
+        self.copy_stream.synchronize()
+        self.tier.destroy(sid)
+        with torch.cuda.stream(self.stream):
+            self._sync_block_table(s)
+
+    def _require_hot(self, sid: int):
+        if getattr(self, "hibernated", None) and sid in self.hibernated:
+            self.resume(sid)
 
     def _copy_page(self, src: int, dst: int):
         m = self.model
@@ -191,6 +255,7 @@ class Engine:
     def prefill(self, sid: int, tokens: Sequence[int], want_logits: bool = False):
         """Append ``tokens`` to the sequence in chunks; returns the greedy next token (and the
         last-position logits when asked)."""
+        self._require_hot(sid)
         s = self.seqs[sid]
         tokens = [int(t) for t in tokens]
         if self.ws_prefill is None:
@@ -220,6 +285,7 @@ class Engine:
 
     def forward_rows(self, sid: int, tokens: Sequence[int], commit: bool = True) -> torch.Tensor:
         """Run consecutive rows of one sequence and return logits for ALL rows (verify shape)."""
+        self._require_hot(sid)
         s = self.seqs[sid]
         R = len(tokens)
         ws = Workspace(self.model, R, R, self.max_ctx)
@@ -240,6 +306,8 @@ class Engine:
         """One decode step for a batch of sequences: feeds ``tokens[i]`` at the frontier of
         ``sids[i]`` and returns the greedy next token per sequence."""
         B = len(sids)
+        for sid in sids:
+            self._require_hot(sid)
         ws = self._ws_decode(B)
         with torch.cuda.stream(self.stream):
             rows, groups = [], []

@@ -88,3 +88,46 @@ def test_safetensors_roundtrip_incl_nvfp4_quartet(tmp_path):
     assert (d - w).abs().max() < 0.3 * w.abs().max()
     assert (quant.dequantize_fp8_block(r.get("a.weight").view(torch.uint8), r.get("a.weight_scale_inv")) - w).abs().max() < 0.07 * w.abs().max()
     r.close()
+
+
+def test_prepacked_store_roundtrip_resume_and_verify(tmp_path):
+    import os
+    import torch
+    from layerstorm_b200.formats.prepacked import PrepackedSource, PrepackWriter, load_experts, prepack_model
+    from layerstorm_b200.models.checkpoint import export_hf
+    from layerstorm_b200.models.config import get_preset
+    from layerstorm_b200.models.device_model import ExpertArena, QLinear, expert_layout
+    from layerstorm_b200.models.weights import init_weights, round_weights_bf16
+    cfg = get_preset("tiny-mla-moe")
+    w = round_weights_bf16(init_weights(cfg, 4))
+    d = str(tmp_path / "store")
+    wr = prepack_model(cfg, w, d, "nvfp4")
+    n_exp = cfg.n_moe_layers() * (cfg.n_routed + cfg.n_shared)
+    assert wr.written == n_exp and wr.skipped == 0
+    wr2 = prepack_model(cfg, w, d, "nvfp4")                     # resume: nothing to do
+    assert wr2.written == 0 and wr2.skipped == n_exp
+    src = PrepackedSource(d, mode="pread")
+    src.check_shape(cfg, "nvfp4")
+    assert src.verify_all() == (n_exp, 0)
+    # the image is byte-identical to what the arena writer produces
+    ef = expert_layout("nvfp4", cfg.hidden, cfg.moe_inter)
+    ar = ExpertArena(ef, 1, 1, "cpu")
+    ar.data.zero_()
+    nm = "layers.2.moe.experts.5."
+    ar.write_expert(0, *(QLinear.from_float(w[nm + t], "nvfp4", "cpu") for t in ("gate", "up", "down")))
+    buf = torch.empty(src.stride, dtype=torch.uint8)
+    for mode in ("mmap", "pread", "direct"):
+        PrepackedSource(d, mode=mode).read_into(2, 5, buf, verify=True)
+        assert torch.equal(buf, ar.data[0])
+    # corruption is detected
+    p = src.path(1, 0)
+    raw = bytearray(open(p, "rb").read())
+    raw[100] ^= 0xFF
+    open(p, "wb").write(raw)
+    assert PrepackedSource(d).verify_all() == (n_exp, 1)
+    # CLI on an exported checkpoint
+    from layerstorm_b200.cli import prepack
+    hf = str(tmp_path / "hf")
+    export_hf(cfg, w, hf)
+    assert prepack.main(["--model", hf, "--out", str(tmp_path / "s2"), "--quant", "fp8_e4m3", "--verify"]) == 0
+    assert os.path.exists(tmp_path / "s2" / "manifest.json")

@@ -176,3 +176,36 @@ def test_turboquant_kv_rows_match_reference_quantiser_and_oracle():
     assert float((codes2 == codes).float().mean()) > 0.97          # re-quantising the reconstruction gives the same codes (up to bf16 rotation rounding)
     assert torch.all(scale > 0) and levels.numel() == 16 and torch.allclose(levels, -levels.flip(0), atol=1e-5)
     assert torch.allclose(rot @ rot.T, torch.eye(dl), atol=1e-4)
+
+
+@pytest.mark.parametrize("name", ["tiny-glm5-next", "tiny-deepseek-v32"])
+def test_hibernate_resume_is_bit_identical_and_frees_pages(name):
+    """KV tiering at sequence granularity: pages move to pinned host memory and back; tokens and logits are unchanged and
+    another sequence can use the freed HBM pages in between."""
+    cfg, m, _ = build(name, kv="fp8")
+    eng = Engine(m, max_seqs=3, max_ctx=128, prefill_chunk=16, max_batch=1, num_pages=12, use_graph=False)
+    eng.enable_kv_tiering(cold_pages=16)
+    g = torch.Generator().manual_seed(11)
+    pa = torch.randint(0, cfg.vocab, (70,), generator=g).tolist()
+    pb = torch.randint(0, cfg.vocab, (90,), generator=g).tolist()
+
+    def run(hib):
+        a = eng.create_sequence()
+        ta = [eng.prefill(a, pa)]
+        free0 = eng.free_page_count()
+        if hib:
+            assert eng.hibernate(a) == 5 and eng.free_page_count() == free0 + 5 and eng.hibernate(a) == 0
+            b = eng.create_sequence()                      # needs 6 pages: only fits because a's pages were released
+            eng.prefill(b, pb)
+            eng.free_sequence(b)
+        lgs = []
+        for _ in range(4):                                 # the first decode resumes the sequence transparently
+            out, lg = eng.decode([a], [ta[-1]], return_logits=True)
+            ta.append(out[0]); lgs.append(lg[0].clone())
+        eng.free_sequence(a)
+        return ta, torch.stack(lgs)
+
+    t0, l0 = run(False)
+    t1, l1 = run(True)
+    assert t0 == t1 and torch.equal(l0, l1)
+    assert eng.d2h_bytes > 0 and not eng.hibernated

@@ -302,3 +302,26 @@ def test_cpu_expert_ffn_reads_gpu_slot_images(fmt, H, F):
             if int(ids[t, s]) != 3:
                 want[t] += float(wts[t, s]) * ref_ffn(int(ids[t, s]), x[t:t + 1], 3.0)[0]
     assert float((out.double() - want).abs().max() / want.abs().max()) < 1e-5
+
+
+def test_calibration_fit_document_and_solver(tmp_path):
+    import json
+    from layerstorm_b200.runtime import calibration as cal
+    counts = [1, 2, 4, 8, 16, 64, 65, 128]
+    a, b, P = 9000.0, 30000.0, 64
+    times = [a * c + b * -(-c // P) for c in counts]
+    fa, fb = cal.fit_compute_curve(counts, times, P)
+    assert abs(fa - a) / a < 1e-6 and abs(fb - b) / b < 1e-6
+    doc = {"version": 2, "batch_p": P, "devices": [{"a_ns": fa, "b_ns": fb}, {"a_ns": 2 * fa, "b_ns": fb}],
+           "banks": [{"rate_bytes_per_us": [50000, 25000], "latency_ns": [8000, 9000], "egress_bytes_per_us": 60000}],
+           "recon_ns": 12000, "evict_ns": 4000}
+    p = tmp_path / "cal.json"
+    p.write_text(json.dumps(doc))
+    assert cal.calibrate(mode="loaded", path=str(p))["devices"][1]["a_ns"] == 2 * fa
+    (tmp_path / "old.json").write_text(json.dumps({"version": 1}))
+    with pytest.raises(ValueError):
+        cal.calibrate(mode="loaded", path=str(tmp_path / "old.json"))
+    solver = cal.solver_from_calibration(doc)
+    assign, cost, tier = solver.solve([0] * 6, [14 << 20] * 6, [[1, 0]] * 3 + [[0, 0]] * 3, [4, 4])
+    assert len(assign) == 6 and cost > 0 and tier == 1
+    assert all(x == 0 for x in assign[:3])                 # resident experts stay on the device that holds them

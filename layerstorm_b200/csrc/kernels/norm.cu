@@ -230,6 +230,186 @@ __global__ void __launch_bounds__(512) mhc_finalize_kernel(bf16* __restrict__ ou
     pdl_launch_dependents();
 }
 
+
+// ---- few-row (decode) variant: two launches instead of partial + one-block-per-row finalize -------------------------------
+// mhc_post_fused: same residual update and partial mixing logits as mhc_post_partial, plus the partial Gram matrix
+// G[j][j'] = sum_h res_j[h] res_j'[h] of the new residual streams.  The last block of a row to finish (atomic counter)
+// reduces the partials in chunk order, forms pre / post and the Sinkhorn-normalised mixing matrix, and gets the RMS of the
+// contracted vector algebraically:  sum_h (sum_j pre_j res_j[h])^2 = pre^T G pre  - no second pass over the hidden dimension.
+// mhc_contract: out[h] = inv_rms * w[h] * sum_j pre_j res_j[h], fully parallel over the hidden dimension.
+constexpr int kHcGram = kHcMax * (kHcMax + 1) / 2;         // 10
+constexpr int kHcPart2 = kHcOut + kHcGram + 2;             // 36 floats per (row, chunk)
+
+__global__ void __launch_bounds__(128) mhc_post_fused_kernel(float* __restrict__ residual, const float* __restrict__ x,
+                                                             float* __restrict__ post, float* __restrict__ comb,
+                                                             const float* __restrict__ fn, const float* __restrict__ hc_scale,
+                                                             const float* __restrict__ hc_base, float* __restrict__ part,
+                                                             unsigned* __restrict__ done, float* __restrict__ prex, int hidden, int n, int mode,
+                                                             int iters, float hc_eps, float rms_eps, float post_mult, PeerComm comm) {
+    __shared__ float mix[kHcPart2];
+    __shared__ int s_last;
+    const int r = blockIdx.x, c = blockIdx.y, lane = threadIdx.x & 31, og = threadIdx.x >> 5, t = threadIdx.x;
+    const int nchunks = gridDim.y;
+    const int h = c * kHcChunk + lane;
+    const int nout = 2 * n + n * n;
+    float f[kHcPerWarp][kHcMax];
+#pragma unroll
+    for (int i = 0; i < kHcPerWarp; ++i) {
+        const int o = og * kHcPerWarp + i;
+#pragma unroll
+        for (int j = 0; j < kHcMax; ++j) f[i][j] = (o < nout && j < n) ? __ldg(fn + ((size_t)o * n + j) * hidden + h) : 0.f;
+    }
+    pdl_wait();
+    pdl_launch_dependents();
+    float res[kHcMax];
+    float* rp = residual + (size_t)r * n * hidden;
+    float xv;
+    if (comm.nranks && mode == 1) {
+        const unsigned epoch = *comm.epoch;
+        comm_wait(comm, epoch);
+        xv = comm_reduce(comm, epoch, (size_t)r * hidden + h);
+    } else {
+        xv = x[(size_t)r * hidden + h];
+    }
+    if (mode == 0) {
+#pragma unroll
+        for (int j = 0; j < kHcMax; ++j) res[j] = j < n ? xv : 0.f;
+    } else {
+        float old[kHcMax];
+#pragma unroll
+        for (int i = 0; i < kHcMax; ++i) old[i] = i < n ? rp[(size_t)i * hidden + h] : 0.f;
+#pragma unroll
+        for (int j = 0; j < kHcMax; ++j) {
+            float a = 0.f;
+            if (j < n) {
+                a = post[r * n + j] * xv;
+                for (int i = 0; i < n; ++i) a += comb[(r * n + i) * n + j] * old[i];
+            }
+            res[j] = a;
+        }
+    }
+    float* po = part + ((size_t)r * nchunks + c) * kHcPart2;
+#pragma unroll
+    for (int i = 0; i < kHcPerWarp; ++i) {
+        float a = 0.f;
+#pragma unroll
+        for (int j = 0; j < kHcMax; ++j) a = fmaf(res[j], f[i][j], a);
+        a = warp_sum(a);
+        const int o = og * kHcPerWarp + i;
+        if (lane == 0 && o < kHcOut) po[o] = a;
+    }
+    // Gram entries (j <= j'), spread over the four warps: warp w takes entries w, w+4, w+8
+    {
+        int e = 0;
+#pragma unroll
+        for (int j = 0; j < kHcMax; ++j)
+#pragma unroll
+            for (int k = j; k < kHcMax; ++k, ++e)
+                if ((e & 3) == og) {
+                    const float g = warp_sum(res[j] * res[k]);
+                    if (lane == 0) po[kHcOut + e] = g;
+                }
+    }
+    if (og == 0) {
+#pragma unroll
+        for (int j = 0; j < kHcMax; ++j)
+            if (j < n) rp[(size_t)j * hidden + h] = res[j];
+    }
+    // ---- last block of this row finishes the job ----
+    __threadfence();
+    __syncthreads();
+    if (t == 0) s_last = atomicAdd(done + r, 1u) == (unsigned)(nchunks - 1);
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    if (t < kHcOut + kHcGram) {                       // 34 threads, each sums one column over the chunks in chunk order
+        float a = 0.f;
+        for (int c0 = 0; c0 < nchunks; c0 += 8) {
+            float v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = c0 + u < nchunks ? __ldcg(part + ((size_t)r * nchunks + c0 + u) * kHcPart2 + t) : 0.f;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) a += v[u];
+        }
+        mix[t] = a;
+    }
+    __syncthreads();
+    if (t < 32) {
+        // sum of squares of the residual streams = trace of the Gram matrix (diagonal entries 0, 4, 7, 9 for n = 4)
+        float tr = 0.f;
+        { int e = 0; for (int j = 0; j < kHcMax; ++j) for (int k = j; k < kHcMax; ++k, ++e) if (k == j && j < n) tr += mix[kHcOut + e]; }
+        const float inv = rsqrtf(tr / (float)(n * hidden) + rms_eps);
+        float cm = 0.f;
+        const int i = (t & 15) >> 2, j = t & 3;
+        const bool valid = t < 16 && i < n && j < n;
+        {
+            float v = valid ? mix[2 * n + i * n + j] * inv * hc_scale[2] + hc_base[2 * n + i * n + j] : -INFINITY;
+            float mx = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            float e = valid ? expf(v - mx) : 0.f;
+            float sm = e + __shfl_xor_sync(0xffffffffu, e, 1);
+            sm += __shfl_xor_sync(0xffffffffu, sm, 2);
+            cm = valid ? e / sm + hc_eps : 0.f;
+            float cs = cm + __shfl_xor_sync(0xffffffffu, cm, 4);
+            cs += __shfl_xor_sync(0xffffffffu, cs, 8);
+            cm = valid ? cm / (cs + hc_eps) : 0.f;
+            for (int it = 1; it < iters; ++it) {
+                float rs = cm + __shfl_xor_sync(0xffffffffu, cm, 1);
+                rs += __shfl_xor_sync(0xffffffffu, rs, 2);
+                cm = valid ? cm / (rs + hc_eps) : 0.f;
+                cs = cm + __shfl_xor_sync(0xffffffffu, cm, 4);
+                cs += __shfl_xor_sync(0xffffffffu, cs, 8);
+                cm = valid ? cm / (cs + hc_eps) : 0.f;
+            }
+        }
+        if (valid) comb[(r * n + i) * n + j] = cm;
+        // pre gates on lanes 16..19, post gates on lanes 20..23
+        float pre_v = 0.f;
+        if (t >= 16 && t < 16 + kHcMax && t - 16 < n) pre_v = sigmoidf_(mix[t - 16] * inv * hc_scale[0] + hc_base[t - 16]) + hc_eps;
+        if (t >= 20 && t < 20 + kHcMax && t - 20 < n) post[r * n + (t - 20)] = sigmoidf_(mix[n + t - 20] * inv * hc_scale[1] + hc_base[n + t - 20]) * post_mult;
+        float pj[kHcMax];
+#pragma unroll
+        for (int q = 0; q < kHcMax; ++q) pj[q] = __shfl_sync(0xffffffffu, pre_v, 16 + q);
+        if (t == 0) {
+            float quad = 0.f;
+            int e = 0;
+            for (int a = 0; a < kHcMax; ++a)
+                for (int b = a; b < kHcMax; ++b, ++e) quad += (a == b ? 1.f : 2.f) * pj[a] * pj[b] * mix[kHcOut + e];
+            float* px = prex + (size_t)r * 8;
+#pragma unroll
+            for (int q = 0; q < kHcMax; ++q) px[q] = pj[q];
+            px[4] = rsqrtf(fmaxf(quad, 0.f) / (float)hidden + rms_eps);
+            done[r] = 0;
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256) mhc_contract_kernel(bf16* __restrict__ out, const float* __restrict__ residual, const float* __restrict__ prex,
+                                                           const float* __restrict__ norm_w, int hidden, int n) {
+    const int r = blockIdx.x;
+    const int h = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
+    float4 w4 = make_float4(0, 0, 0, 0);
+    if (h < hidden) w4 = *reinterpret_cast<const float4*>(norm_w + h);
+    pdl_wait();
+    pdl_launch_dependents();
+    if (h >= hidden) return;
+    const float* px = prex + (size_t)r * 8;
+    const float* rp = residual + (size_t)r * n * hidden + h;
+    float4 a = make_float4(0, 0, 0, 0), v[kHcMax];
+#pragma unroll
+    for (int j = 0; j < kHcMax; ++j) v[j] = j < n ? *reinterpret_cast<const float4*>(rp + (size_t)j * hidden) : make_float4(0, 0, 0, 0);
+#pragma unroll
+    for (int j = 0; j < kHcMax; ++j) {
+        const float p = j < n ? px[j] : 0.f;
+        a.x = fmaf(p, v[j].x, a.x); a.y = fmaf(p, v[j].y, a.y); a.z = fmaf(p, v[j].z, a.z); a.w = fmaf(p, v[j].w, a.w);
+    }
+    const float inv = px[4];
+    bf162 o0 = __floats2bfloat162_rn(a.x * inv * w4.x, a.y * inv * w4.y), o1 = __floats2bfloat162_rn(a.z * inv * w4.z, a.w * inv * w4.w);
+    uint2 pk;
+    pk.x = *reinterpret_cast<uint32_t*>(&o0); pk.y = *reinterpret_cast<uint32_t*>(&o1);
+    *reinterpret_cast<uint2*>(out + (size_t)r * hidden + h) = pk;
+}
+
 // Last layer: out = RMSNorm(mean_j(post[j]*x + sum_i comb[i][j]*residual[i])) * w.
 __global__ void mhc_contract_norm_kernel(bf16* __restrict__ out, const float* __restrict__ residual, const float* __restrict__ x,
                                          const float* __restrict__ post, const float* __restrict__ comb,
@@ -303,10 +483,20 @@ LSB_API int lsb_add_rmsnorm(void* out, void* resid, const void* x, const void* w
 LSB_API int lsb_mhc_post_pre(void* out_x, void* residual, const void* x, void* post, void* comb, const void* fn,
                              const void* hc_scale, const void* hc_base, const void* norm_w, void* part, int rows,
                              int hidden, int n, int mode, int iters, float hc_eps, float rms_eps, float post_mult,
-                             const void* comm, void* stream) {
+                             void* done, void* prex, const void* comm, void* stream) {
     if (hidden % kHcChunk || n > kHcMax) return -1;
     cudaStream_t st = (cudaStream_t)stream;
     const int nchunks = hidden / kHcChunk;
+    if (done && prex && rows < 64 && hidden % 4 == 0) {
+        // few rows: partials + finalize in one launch (last block per row), then a fully parallel contraction.
+        // part must hold rows * nchunks * 36 floats, done rows zero-initialised counters, prex rows * 8 floats.
+        launch_pdl((mhc_post_fused_kernel), dim3(rows, nchunks), 128, 0, st, (float*)residual, (const float*)x, (float*)post, (float*)comb,
+                   (const float*)fn, (const float*)hc_scale, (const float*)hc_base, (float*)part, (unsigned*)done, (float*)prex, hidden, n, mode,
+                   iters, hc_eps, rms_eps, post_mult, comm_from_host(comm));
+        launch_pdl((mhc_contract_kernel), dim3(rows, (hidden / 4 + 255) / 256), 256, 0, st, (bf16*)out_x, (const float*)residual, (const float*)prex,
+                   (const float*)norm_w, hidden, n);
+        LSB_CHECK_LAUNCH();
+    }
     const int rpb = rows >= 64 ? 16 : 1;      // many rows: amortise the mixing-matrix loads over 16 rows per block
     launch_pdl((mhc_post_partial_kernel), dim3((rows + rpb - 1) / rpb, nchunks), 128, 0, st, (float*)residual, (const float*)x, (const float*)post,
                                                                     (const float*)comb, (const float*)fn, (float*)part, hidden, n, mode, rows, rpb, comm_from_host(comm));

@@ -29,6 +29,7 @@
 
 #include <fcntl.h>
 #include <sys/mman.h>
+#include <sys/stat.h>
 #include <sys/syscall.h>
 #include <unistd.h>
 
@@ -107,6 +108,17 @@ public:
             // MPOL_BIND = 2; failure (no NUMA support, container restrictions) is not fatal: placement is a hint
             bound_ = syscall(SYS_mbind, base_, bytes_, 2, mask, sizeof(mask) * 8, 0u) == 0;
         }
+    }
+    // Attach to a slab that already exists (an fd kept alive by the arena holder process): contents and, with load_meta,
+    // the slot table survive an engine restart.
+    HostArena(int64_t slot_bytes, int n_slots, int existing_fd)
+        : slot_bytes_(slot_bytes), n_(n_slots), slots_(n_slots) {
+        bytes_ = (size_t)slot_bytes * (size_t)n_slots;
+        struct stat st;
+        if (existing_fd < 0 || fstat(existing_fd, &st) != 0 || (size_t)st.st_size < bytes_) return;
+        fd_ = dup(existing_fd);
+        base_ = mmap(nullptr, bytes_, PROT_READ | PROT_WRITE, MAP_SHARED, fd_, 0);
+        if (base_ == MAP_FAILED) base_ = nullptr;
     }
     ~HostArena() {
         if (base_) munmap(base_, bytes_);
@@ -245,6 +257,12 @@ LSB_RT_API long long lsb_host_pool_budget(int mode, double value, long long tota
 LSB_RT_API void* lsb_arena_create(long long slot_bytes, int n_slots, int numa_node, int use_memfd, int thp) {
     if (slot_bytes <= 0 || n_slots <= 0) return nullptr;
     auto* a = new HostArena(slot_bytes, n_slots, numa_node, use_memfd != 0, thp != 0);
+    if (!a->ok()) { delete a; return nullptr; }
+    return a;
+}
+LSB_RT_API void* lsb_arena_attach(long long slot_bytes, int n_slots, int fd) {
+    if (slot_bytes <= 0 || n_slots <= 0) return nullptr;
+    auto* a = new HostArena(slot_bytes, n_slots, fd);
     if (!a->ok()) { delete a; return nullptr; }
     return a;
 }

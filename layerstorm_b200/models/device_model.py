@@ -320,7 +320,9 @@ class Workspace:
         self.sub = z(R, H)
         self.resid = z(R, n, H)
         self.post = z(R, n); self.comb = z(R, n, n)
-        self.part = z(R, max(1, H // 32), 25)
+        self.part = z(R, max(1, H // 32), 36)
+        self.hc_done = z(max(R, 1), dtype=i32)
+        self.hc_pre = z(max(R, 1), 8)
         self.proj = z(R, m.max_proj)
         C = m.Hk * cfg.kda_head_dim
         self.kda_out = z(R, max(C, 1), dtype=b16)
@@ -874,14 +876,14 @@ class DeviceModel:
             for i, L in enumerate(self.layers):
                 fn, sc, base = L["hc_attn"]
                 nat.call("lsb_mhc_post_pre", ws.x, ws.resid, ws.sub, ws.post, ws.comb, fn, sc, base, L["attn_norm"], ws.part, R, H, n,
-                         0 if i == 0 else 1, cfg.hc_sinkhorn_iters, cfg.hc_eps, cfg.rms_eps, cfg.hc_post_mult, self._cp)
+                         0 if i == 0 else 1, cfg.hc_sinkhorn_iters, cfg.hc_eps, cfg.rms_eps, cfg.hc_post_mult, ws.hc_done, ws.hc_pre, self._cp)
                 if cfg.is_kda_layer(i):
                     self._kda(i, L, ws, R, nseq)
                 else:
                     self._mla(i, L, ws, R)
                 fn, sc, base = L["hc_ffn"]
                 nat.call("lsb_mhc_post_pre", ws.x, ws.resid, ws.sub, ws.post, ws.comb, fn, sc, base, L["ffn_norm"], ws.part, R, H, n,
-                         1, cfg.hc_sinkhorn_iters, cfg.hc_eps, cfg.rms_eps, cfg.hc_post_mult, self._cp)
+                         1, cfg.hc_sinkhorn_iters, cfg.hc_eps, cfg.rms_eps, cfg.hc_post_mult, ws.hc_done, ws.hc_pre, self._cp)
                 self._ffn(i, L, ws, R)
             nat.call("lsb_mhc_contract_norm", ws.x, ws.resid, ws.sub, ws.post, ws.comb, self.final_norm, R, H, n, cfg.rms_eps, self._cp)
         else:

@@ -437,10 +437,13 @@ class HostArena:
     uint8 torch tensor without copying; ``pin()`` registers it with the CUDA driver."""
     EMPTY, LOADING, ACTIVE = 0, 1, 2
 
-    def __init__(self, slot_bytes: int, n_slots: int, numa_node: int = -1, memfd: bool = False, thp: bool = True):
+    def __init__(self, slot_bytes: int, n_slots: int, numa_node: int = -1, memfd: bool = False, thp: bool = True, attach_fd: int = -1):
         self.lib = load()
         self.slot_bytes, self.n_slots = slot_bytes, n_slots
-        self.h = self.lib.lsb_arena_create(slot_bytes, n_slots, numa_node, int(memfd), int(thp))
+        if attach_fd >= 0:
+            self.h = self.lib.lsb_arena_attach(slot_bytes, n_slots, attach_fd)
+        else:
+            self.h = self.lib.lsb_arena_create(slot_bytes, n_slots, numa_node, int(memfd), int(thp))
         if not self.h:
             raise MemoryError(f"cannot map a host arena of {slot_bytes * n_slots} bytes")
         self._tensor = None

@@ -81,7 +81,8 @@ def test_rmsnorm_and_add():
     close(out, ref.rmsnorm((r0 + x).cpu(), w.cpu(), 1e-6), 1e-2, 1e-2, "add_rmsnorm")
 
 
-def test_mhc_post_pre_and_contract():
+@pytest.mark.parametrize("fused", [False, True])
+def test_mhc_post_pre_and_contract(fused):
     cfg = get_preset("tiny-glm5-next")
     R, H, n = 3, cfg.hidden, cfg.hc_mult
     o = ref.Oracle(cfg, {})
@@ -89,10 +90,13 @@ def test_mhc_post_pre_and_contract():
     emb = rnd(R, H)
     resid = torch.zeros(R, n, H, device=DEV)
     post = torch.zeros(R, n, device=DEV); comb = torch.zeros(R, n, n, device=DEV)
-    part = torch.zeros(R, H // 32, 25, device=DEV)
+    part = torch.zeros(R, H // 32, 36, device=DEV)
+    # fused = the few-row path (last block finalises, RMS from the Gram matrix); otherwise partial + per-row finalize
+    done = torch.zeros(R, dtype=torch.int32, device=DEV) if fused else None
+    prex = torch.zeros(R, 8, device=DEV) if fused else None
     x = torch.zeros(R, H, device=DEV, dtype=torch.bfloat16)
     args = (cfg.hc_sinkhorn_iters, cfg.hc_eps, cfg.rms_eps, cfg.hc_post_mult)
-    nat.call("lsb_mhc_post_pre", x, resid, emb, post, comb, fn, sc, base, nw, part, R, H, n, 0, *args, None)
+    nat.call("lsb_mhc_post_pre", x, resid, emb, post, comb, fn, sc, base, nw, part, R, H, n, 0, *args, done, prex, None)
     torch.cuda.synchronize()
     r_ref = emb.cpu()[:, None, :].repeat(1, n, 1)
     p_ref, c_ref, x_ref = o.mhc_pre(r_ref, fn.cpu(), sc.cpu(), base.cpu(), nw.cpu())
@@ -101,7 +105,7 @@ def test_mhc_post_pre_and_contract():
     close(comb, c_ref, 1e-4, 1e-5, "comb")
     close(x, x_ref, 1e-2, 1e-2, "x")
     sub = rnd(R, H, seed=5)
-    nat.call("lsb_mhc_post_pre", x, resid, sub, post, comb, fn, sc, base, nw, part, R, H, n, 1, *args, None)
+    nat.call("lsb_mhc_post_pre", x, resid, sub, post, comb, fn, sc, base, nw, part, R, H, n, 1, *args, done, prex, None)
     torch.cuda.synchronize()
     r2 = o.mhc_post(sub.cpu(), r_ref, p_ref, c_ref)
     p2, c2, x2 = o.mhc_pre(r2, fn.cpu(), sc.cpu(), base.cpu(), nw.cpu())

@@ -325,3 +325,41 @@ def test_calibration_fit_document_and_solver(tmp_path):
     assign, cost, tier = solver.solve([0] * 6, [14 << 20] * 6, [[1, 0]] * 3 + [[0, 0]] * 3, [4, 4])
     assert len(assign) == 6 and cost > 0 and tier == 1
     assert all(x == 0 for x in assign[:3])                 # resident experts stay on the device that holds them
+
+
+def test_arena_holder_keeps_slab_across_clients(tmp_path):
+    import subprocess, sys, time as _t
+    import torch
+    from layerstorm_b200.runtime.arena_holder import HolderClient
+    sock = str(tmp_path / "holder.sock")
+    proc = subprocess.Popen([sys.executable, "-m", "layerstorm_b200.runtime.arena_holder", "serve", "--socket", sock],
+                            cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    try:
+        c = HolderClient(sock)
+        for _ in range(100):
+            if c.alive():
+                break
+            _t.sleep(0.05)
+        assert c.alive()
+        ar = rt.HostArena(4096, 4, memfd=True, thp=False)
+        s, _ = ar.begin_load(3, 9)
+        ar.tensor()[s].fill_(0x5A)
+        ar.finish_load(s)
+        ar.save_meta(tmp_path / "meta", tag=7)
+        c.put("gpu0", ar, tag=7)
+        del ar                                                  # the engine process goes away; the holder keeps the slab
+        got = HolderClient(sock).get("gpu0")
+        assert got is not None
+        ar2, tag = got
+        assert tag == 7 and ar2.load_meta(tmp_path / "meta", tag=7) == 1
+        s2 = ar2.lookup(3, 9)
+        assert s2 == s and int(ar2.tensor()[s2][100]) == 0x5A   # contents survived
+        st = c.status()
+        assert st["arenas"]["gpu0"]["n_slots"] == 4
+        with pytest.raises(ValueError):
+            c.wipe("gpu0", " ")
+        assert c.wipe("gpu0", "test teardown") and HolderClient(sock).get("gpu0") is None
+        assert c.status()["wipes"][-1]["reason"] == "test teardown"
+    finally:
+        HolderClient(sock).shutdown()
+        proc.wait(timeout=10)

@@ -177,15 +177,41 @@ class ExpertStreamer:
             todo = [e for e in todo if e not in done]
             self.stats["waves"] += 1
         if self.prefetch:
-            self._prefetch_next(li, list(need))
+            self._prefetch_next(model, li, ws, R, list(need))
         return st["present"]
 
-    def _prefetch_next(self, li: int, experts: List[int]):
-        """Same-index heuristic: request this step's experts for the next MoE layer at the lowest priority."""
+    def _prescope(self, model, nxt: int, ws, R: int) -> List[int]:
+        """Pre-gating ("prescope"): run the NEXT MoE layer's router on this layer's input.  The residual stream changes
+        slowly from layer to layer, so the experts it picks predict the real routing well; the prediction only steers
+        prefetch, never the computation."""
+        cfg = model.cfg
+        L = model.layers[nxt]
+        if not hasattr(ws, "_pre"):
+            dev = model.device
+            ws._pre = (torch.zeros(ws.R, cfg.n_routed, device=dev), torch.zeros(ws.R, ws.S, dtype=torch.int32, device=dev), torch.zeros(ws.R, ws.S, device=dev))
+        lg, ids, wts = ws._pre
+        from ..ops import _native as nat
+        L["router"](lg, ws.x, R)
+        sc = {"sigmoid": 0, "softmax": 1, "sqrtsoftplus": 2}[cfg.scoring]
+        nat.call("lsb_router_topk", lg, L["router_bias"], ids, wts, R, cfg.n_routed, cfg.top_k, cfg.n_group, cfg.topk_group, sc,
+                 int(cfg.norm_topk_prob), cfg.routed_scale, cfg.n_shared, cfg.n_routed)
+        flat = ids[:R].reshape(-1).cpu().tolist()
+        seen, out = set(), []
+        for e in flat:
+            if e >= 0 and e not in seen:
+                seen.add(e)
+                out.append(e)
+        return out
+
+    def _prefetch_next(self, model, li: int, ws, R: int, fallback: List[int]):
+        """Request the experts the next MoE layer will probably route to, at the lowest priority, so their copies overlap
+        this layer's combine and the next layer's attention."""
         nxt = min((j for j in self.layers if j > li), default=None)
         if nxt is None:
             return
         st = self.layers[nxt]
+        experts = self._prescope(model, nxt, ws, R) if R <= 4 else fallback
+        self.stats["prefetch_requests"] = self.stats.get("prefetch_requests", 0) + len(experts)
         for e in experts[: max(0, st["arena"].n_slots // 2)]:
             if e in st["mine"] and st["cache"].lookup(nxt, e) < 0:
                 if not self._reserve(nxt, st, e, priority=2):

@@ -285,6 +285,8 @@ class Orchestrator:
                 return self._finish(req, req.finish_reason or "cancelled")
             if self.gamma > 0 and not need_logits:
                 self._decode_speculative(req, sid, tok)
+            elif self.gamma > 0 and not getattr(eng, "has_recurrent_state", False):
+                self._decode_speculative_logits(req, sid, tok)
             else:
                 self._decode_plain(req, sid, tok, need_logits)
             self._finish(req, req.finish_reason or ("cancelled" if req.cancelled.is_set() else "stop"))
@@ -304,6 +306,50 @@ class Orchestrator:
                 logits = None
             self.governor.observe_plain((time.time() - t0) * 1e3)
             if self._emit(req, tok, logits):
+                return
+
+    def _decode_speculative_logits(self, req: InferenceRequest, sid: int, tok: int):
+        """Lossless speculation for requests that need the logits of every step (sampling, guided decoding, logprobs).
+        The draft is a point mass, so exact rejection sampling reduces to equality coupling: draw s_k from the target
+        distribution of row k (temperature / top-k / top-p / mask applied, RNG keyed by the absolute position) and accept
+        the draft token iff s_k equals it; on a mismatch s_k itself is the correct next token.  One RNG draw per committed
+        token at its own position => the same trajectory as plain sampled decoding for a fixed seed.
+        Reference behaviour: python/orchestrator/orchestrator.py:3781-3818 (_decode_speculative_sampled), guided variant
+        :4079-4237."""
+        eng = self.engine
+        while True:
+            t0 = time.time()
+            if not self.governor.should_draft():
+                lg = self._with_pool_evict_retry(req, lambda: eng.decode([sid], [tok], return_logits=True))[1][0]
+                tok = self._pick(req, lg, len(req.prompt_ids) + len(req.output_ids))
+                self.governor.observe_plain((time.time() - t0) * 1e3)
+                if self._emit(req, tok, lg):
+                    return
+                continue
+            ctx = list(req.prompt_ids) + req.output_ids
+            draft = list(self.draft.propose(ctx, self.gamma))[: self.gamma]
+            base_len = eng.seq_len(sid)
+            rows = [tok] + draft
+            logits = self._with_pool_evict_retry(req, lambda: eng.forward_rows(sid, rows, commit=True))
+            n_acc, n_new, stop = 0, 0, False
+            for k in range(len(rows)):
+                t = self._pick(req, logits[k], len(req.prompt_ids) + len(req.output_ids))
+                n_new += 1
+                tok = t
+                if self._emit(req, t, logits[k]):
+                    stop = True
+                    break
+                if k < len(draft) and t == draft[k]:
+                    n_acc += 1
+                    continue
+                break
+            eng.rewind(sid, base_len + 1 + n_acc)
+            req.stats.spec_rounds += 1
+            req.stats.spec_accepted += n_acc
+            self.governor.observe_round(n_new, (time.time() - t0) * 1e3)
+            if hasattr(self.draft, "feedback"):
+                self.draft.feedback(len(draft), n_acc)
+            if stop:
                 return
 
     def _decode_speculative(self, req: InferenceRequest, sid: int, tok: int):

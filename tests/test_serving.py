@@ -157,3 +157,33 @@ def test_http_api():
     r = c.post("/v1/completions", json={"prompt": "x"})
     assert r.status_code == 503 and "Retry-After" in r.headers
     orch.shutdown()
+
+
+def test_sampled_and_guided_speculation_follow_the_plain_trajectory():
+    """Equality coupling: with a fixed seed, speculative sampled decoding emits exactly the tokens of plain sampled decoding,
+    whatever the draft proposes; a logit mask (guided decoding) composes with it."""
+    from layerstorm_b200.speculation import EngineDraft, PromptLookupDraft
+    prompt = [5, 6, 7, 8, 5, 6, 7, 8, 5, 6]
+
+    def run(draft, gamma, mask=None, **sp):
+        eng = NullEngine(vocab=64, page=16)
+        o = Orchestrator(eng, draft=draft, speculation_depth=gamma)
+        req = InferenceRequest("r", list(prompt), SamplingParams(max_tokens=24, ignore_eos=True, **sp))
+        req.logit_mask = mask
+        o.submit_request(req); o.step()
+        return req
+
+    plain = run(None, 0, temperature=0.9, top_k=20, seed=1234)
+    good = run(EngineDraft(NullEngine(vocab=64, page=16), 4), 4, temperature=0.9, top_k=20, seed=1234)
+    lookup = run(PromptLookupDraft(2, 4, 4), 4, temperature=0.9, top_k=20, seed=1234)
+    assert good.output_ids == plain.output_ids == lookup.output_ids
+    assert good.stats.spec_rounds > 0 and lookup.stats.spec_rounds > 0
+    other = run(None, 0, temperature=0.9, top_k=20, seed=99)
+    assert other.output_ids != plain.output_ids                 # the seed matters, i.e. the requests really sample
+    even = torch.arange(64) % 2 == 0
+    mask = lambda out: even                                      # guided: only even token ids are legal
+    g_plain = run(None, 0, mask=mask, temperature=0.7, seed=7)
+    g_spec = run(EngineDraft(NullEngine(vocab=64, page=16), 3), 3, mask=mask, temperature=0.7, seed=7)
+    assert g_spec.output_ids == g_plain.output_ids and all(t % 2 == 0 for t in g_spec.output_ids)
+    lp = run(EngineDraft(NullEngine(vocab=64, page=16), 3), 3, logprobs=2)      # greedy + logprobs also takes the logits path
+    assert lp.output_ids == run(None, 0, logprobs=2).output_ids

@@ -116,13 +116,30 @@ __device__ __forceinline__ __half2 e4m3x2_to_half2(uint16_t v) {
 template <int FMT> struct Conv;
 constexpr float kFp8Unscale = 1.f / 256.f;
 
+// Raw weight bytes travel HBM -> shared memory with cp.async (no registers held while they are in flight, so the ring can be
+// deep enough to cover DRAM latency); the thread that issued a piece's copy is the one that later expands it.
+__device__ __forceinline__ void cpa16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cpa4(void* dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cpa_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cpa_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 template <> struct Conv<2> {                  // NVFP4: 32 bytes per row-stage; 4 group scales in one word
     static constexpr int PPR = 2;
     struct Raw { uint4 v; uint32_t sc; };
-    static __device__ __forceinline__ void load(Raw& r, const uint8_t* w, const uint8_t* sf, int n, int K, int k0, int c) {
-        r.v = ldg_stream(w + (size_t)n * (K >> 1) + (k0 >> 1) + 16 * c);
+    static constexpr int AUX = 4;             // bytes of side data per piece in the raw ring (the scale word)
+    static __device__ __forceinline__ void issue(void* a, void* b, const uint8_t* w, const uint8_t* sf, int n, int K, int k0, int c) {
+        cpa16(a, w + (size_t)n * (K >> 1) + (k0 >> 1) + 16 * c);
         const int gtiles = ((K >> 4) + 3) >> 2;
-        r.sc = __ldg(reinterpret_cast<const uint32_t*>(sf + ((size_t)(n >> 7) * gtiles + (k0 >> 6)) * 512 + (n & 31) * 16 + ((n & 127) >> 5) * 4));
+        cpa4(b, sf + ((size_t)(n >> 7) * gtiles + (k0 >> 6)) * 512 + (n & 31) * 16 + ((n & 127) >> 5) * 4);
+    }
+    static __device__ __forceinline__ float side(const uint8_t*, int, int, int) { return 0.f; }
+    static __device__ __forceinline__ void fetch(Raw& r, const void* a, const void* b, float) {
+        r.v = *reinterpret_cast<const uint4*>(a);
+        r.sc = *reinterpret_cast<const uint32_t*>(b);
     }
     static __device__ __forceinline__ void emit(const Raw& r, uint32_t tile, int row, int c, int) {
         const uint32_t wv[4] = {r.v.x, r.v.y, r.v.z, r.v.w};
@@ -142,9 +159,17 @@ template <> struct Conv<2> {                  // NVFP4: 32 bytes per row-stage; 
 template <> struct Conv<1> {                  // FP8 e4m3 with 128x128 block scales: 64 bytes per row-stage
     static constexpr int PPR = 4;
     struct Raw { uint4 v; float sc; };
-    static __device__ __forceinline__ void load(Raw& r, const uint8_t* w, const uint8_t* sf, int n, int K, int k0, int c) {
-        r.v = ldg_stream(w + (size_t)n * K + k0 + 16 * c);
-        r.sc = __ldg(reinterpret_cast<const float*>(sf) + (size_t)(n >> 7) * ((K + 127) >> 7) + (k0 >> 7));
+    static constexpr int AUX = 0;
+    static __device__ __forceinline__ void issue(void* a, void*, const uint8_t* w, const uint8_t*, int n, int K, int k0, int c) {
+        cpa16(a, w + (size_t)n * K + k0 + 16 * c);
+    }
+    // one float per 128 x 128 block: read (a cache hit) one stage before it is needed, so no load sits in the conversion
+    static __device__ __forceinline__ float side(const uint8_t* sf, int n, int K, int k0) {
+        return __ldg(reinterpret_cast<const float*>(sf) + (size_t)(n >> 7) * ((K + 127) >> 7) + (k0 >> 7));
+    }
+    static __device__ __forceinline__ void fetch(Raw& r, const void* a, const void*, float sd) {
+        r.v = *reinterpret_cast<const uint4*>(a);
+        r.sc = sd;
     }
     static __device__ __forceinline__ void emit(const Raw& r, uint32_t tile, int row, int c, int) {
         // block scales of small weights sit near the bottom of the fp16 range: carry them times 2^8 (exact)
@@ -166,10 +191,16 @@ template <> struct Conv<1> {                  // FP8 e4m3 with 128x128 block sca
 template <> struct Conv<3> {                  // GGUF Q4_K: 32 quant bytes per row-stage = one (low, high) nibble pair of sub-blocks
     static constexpr int PPR = 2;
     struct Raw { uint4 hdr; uint4 q; };
-    static __device__ __forceinline__ void load(Raw& r, const uint8_t* w, const uint8_t*, int n, int K, int k0, int c) {
+    static constexpr int AUX = 16;            // the super-block header (d, dmin, 12 scale bytes)
+    static __device__ __forceinline__ void issue(void* a, void* b, const uint8_t* w, const uint8_t*, int n, int K, int k0, int c) {
         const uint8_t* blk = w + ((size_t)n * (K >> 8) + (k0 >> 8)) * 144;
-        r.hdr = __ldg(reinterpret_cast<const uint4*>(blk));
-        r.q = ldg_stream(blk + 16 + ((k0 & 255) >> 6) * 32 + 16 * c);
+        cpa16(b, blk);
+        cpa16(a, blk + 16 + ((k0 & 255) >> 6) * 32 + 16 * c);
+    }
+    static __device__ __forceinline__ float side(const uint8_t*, int, int, int) { return 0.f; }
+    static __device__ __forceinline__ void fetch(Raw& r, const void* a, const void* b, float) {
+        r.q = *reinterpret_cast<const uint4*>(a);
+        r.hdr = *reinterpret_cast<const uint4*>(b);
     }
     static __device__ __forceinline__ void emit(const Raw& r, uint32_t tile, int row, int c, int k0) {
         const __half2 dd = *reinterpret_cast<const __half2*>(&r.hdr.x);
@@ -205,8 +236,13 @@ template <> struct Conv<3> {                  // GGUF Q4_K: 32 quant bytes per r
 template <> struct Conv<0> {                  // BF16: 128 bytes per row-stage
     static constexpr int PPR = 8;
     struct Raw { uint4 v; };
-    static __device__ __forceinline__ void load(Raw& r, const uint8_t* w, const uint8_t*, int n, int K, int k0, int c) {
-        r.v = ldg_stream(w + ((size_t)n * K + k0 + 8 * c) * 2);
+    static constexpr int AUX = 0;
+    static __device__ __forceinline__ void issue(void* a, void*, const uint8_t* w, const uint8_t*, int n, int K, int k0, int c) {
+        cpa16(a, w + ((size_t)n * K + k0 + 8 * c) * 2);
+    }
+    static __device__ __forceinline__ float side(const uint8_t*, int, int, int) { return 0.f; }
+    static __device__ __forceinline__ void fetch(Raw& r, const void* a, const void*, float) {
+        r.v = *reinterpret_cast<const uint4*>(a);
     }
     static __device__ __forceinline__ void emit(const Raw& r, uint32_t tile, int row, int c, int) {
         float f[8];
@@ -235,20 +271,39 @@ struct MoeTcParams {
     int ldo, out_bf16; float down_scale;
 };
 
-template <int BN, bool GATEUP> struct MoeTcCfg {
+template <int FMT, int BN, bool GATEUP> struct MoeTcCfg {
     static constexpr int A_TILES = GATEUP ? 2 : 1;
     static constexpr int A_BYTES = A_TILES * kTBM * kTBK * 2;
     static constexpr int B_BYTES = BN * kTBK * 2;
-    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int STAGES = GATEUP ? 4 : 6;
+    // Two operand rings with their own barriers: converted weight tiles (SA stages, filled by the converter warps)
+    // and token tiles (SB stages, TMA).  The token ring runs further ahead, so a TMA round trip never sits between
+    // the MMA freeing a weight stage and the converters refilling it.
+    static constexpr int SA = GATEUP ? 2 : 3;
+    static constexpr int SB = 4;
+    static constexpr int OP_BYTES = SA * A_BYTES + SB * B_BYTES;
     static constexpr int ACC_COLS = A_TILES * BN;                         // one accumulator set (gate [+ up])
     static constexpr int TMEM_COLS = (2 * ACC_COLS) < 32 ? 32 : 2 * ACC_COLS;   // double-buffered: epilogue of tile i overlaps tile i+1
-    static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 256;
-    static constexpr int CONV_WARPS = 8;
+#ifndef LSB_MOE_RELAX
+#define LSB_MOE_RELAX 1
+#endif
+#ifndef LSB_MOE_CONV_WARPS
+#define LSB_MOE_CONV_WARPS 8
+#endif
+    static constexpr int PIECES = (GATEUP ? 2 : 1) * kTBM * Conv<FMT>::PPR;   // 16-byte pieces per stage
+    static constexpr int CONV_WARPS = (PIECES / 32) < LSB_MOE_CONV_WARPS ? (PIECES / 32) : LSB_MOE_CONV_WARPS;
     static constexpr int EPI_WARPS = 4;
     static constexpr int THREADS = (2 + CONV_WARPS + EPI_WARPS) * 32;
     static constexpr int CONV_THREADS = CONV_WARPS * 32;
     static constexpr int ROWS = A_TILES * kTBM;                           // weight rows per stage (gate rows, then up rows)
+    // raw ring: RD stages of not yet converted weight bytes in flight per CTA (up to ~128 KB)
+    static constexpr int NP = ROWS * Conv<FMT>::PPR / CONV_THREADS;       // 16-byte pieces per converter thread per stage
+    static constexpr int RAW_STAGE = NP * CONV_THREADS * (16 + Conv<FMT>::AUX);
+    static constexpr int RAW_BUDGET = 227 * 1024 - 1024 - 256 - OP_BYTES > 128 * 1024 ? 128 * 1024 : 227 * 1024 - 1024 - 256 - OP_BYTES;
+    static constexpr int RD_FIT = RAW_BUDGET / RAW_STAGE;
+    static constexpr int RD = RD_FIT > 12 ? 12 : (RD_FIT < 3 ? 3 : RD_FIT);
+    static constexpr int BAR_BYTES = 256;
+    static constexpr int SMEM = OP_BYTES + BAR_BYTES + RD * RAW_STAGE + 1024;
+    static_assert(SMEM <= 227 * 1024, "shared memory budget");
 };
 
 // Work item w -> (token tile t, weight tile j).  Items are grouped by kTileGroup consecutive token tiles (tiles are sorted
@@ -268,14 +323,18 @@ __device__ __forceinline__ void work_item(int w, int ntiles, int NT, int& t, int
 // that concurrently running CTAs share a token tile); the shared-memory ring, its barrier phases and the two TMEM
 // accumulator sets carry over from one work item to the next.
 template <int FMT, int BN, bool GATEUP>
-__global__ void __launch_bounds__(MoeTcCfg<BN, GATEUP>::THREADS) moe_tc_ffn_kernel(const __grid_constant__ CUtensorMap map_b, MoeTcParams p) {
-    using C = MoeTcCfg<BN, GATEUP>;
+__global__ void __launch_bounds__(MoeTcCfg<FMT, BN, GATEUP>::THREADS) moe_tc_ffn_kernel(const __grid_constant__ CUtensorMap map_b, MoeTcParams p) {
+    using C = MoeTcCfg<FMT, BN, GATEUP>;
     using CV = Conv<FMT>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
-    uint64_t* empty = full + C::STAGES;
-    uint64_t* acc_full = empty + C::STAGES;      // [2]
+    uint8_t* smem_a = smem;                                   // [SA] converted weight tiles (gate [+ up])
+    uint8_t* smem_b = smem + C::SA * C::A_BYTES;              // [SB] token tiles
+    uint64_t* full_a = reinterpret_cast<uint64_t*>(smem + C::OP_BYTES);
+    uint64_t* empty_a = full_a + C::SA;
+    uint64_t* full_b = empty_a + C::SA;
+    uint64_t* empty_b = full_b + C::SB;
+    uint64_t* acc_full = empty_b + C::SB;        // [2]
     uint64_t* acc_empty = acc_full + 2;          // [2]
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + 2);
 
@@ -286,7 +345,8 @@ __global__ void __launch_bounds__(MoeTcCfg<BN, GATEUP>::THREADS) moe_tc_ffn_kern
     const int nkb = K / kTBK;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1 + C::CONV_WARPS); mbar_init(&empty[s], 1); }
+        for (int s = 0; s < C::SA; ++s) { mbar_init(&full_a[s], C::CONV_WARPS); mbar_init(&empty_a[s], 1); }
+        for (int s = 0; s < C::SB; ++s) { mbar_init(&full_b[s], 1); mbar_init(&empty_b[s], 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], C::EPI_WARPS); }
         fence_barrier_init();
         fence_proxy_async();
@@ -323,16 +383,16 @@ __global__ void __launch_bounds__(MoeTcCfg<BN, GATEUP>::THREADS) moe_tc_ffn_kern
                 }
                 const int row0 = p.tile_row0[t];
                 for (int it = 0; it < nkb; ++it, ++g) {
-                    const int s = g % C::STAGES;
-                    ok = mbar_wait(&empty[s], ((g / C::STAGES) & 1) ^ 1, p.err, 11);
+                    const int s = g % C::SB;
+                    ok = mbar_wait(&empty_b[s], ((g / C::SB) & 1) ^ 1, p.err, 11);
                     if (!ok) break;
-                    mbar_expect_tx(&full[s], C::B_BYTES);
-                    tma_load_2d(smem + s * C::STAGE_BYTES + C::A_BYTES, &map_b, &full[s], it * kTBK, row0);
+                    mbar_expect_tx(&full_b[s], C::B_BYTES);
+                    tma_load_2d(smem_b + s * C::B_BYTES, &map_b, &full_b[s], it * kTBK, row0);
                 }
             }
             if (!ok) {
                 // loads in flight still write this CTA's shared memory: let them land (bounded, no error code)
-                for (uint32_t i = g > (uint32_t)C::STAGES ? g - C::STAGES : 0; i < g; ++i) mbar_wait(&full[i % C::STAGES], (i / C::STAGES) & 1, nullptr, 0);
+                for (uint32_t i = g > (uint32_t)C::SB ? g - C::SB : 0; i < g; ++i) mbar_wait(&full_b[i % C::SB], (i / C::SB) & 1, nullptr, 0);
             }
         }
     } else if (warp == 1) {
@@ -351,19 +411,20 @@ __global__ void __launch_bounds__(MoeTcCfg<BN, GATEUP>::THREADS) moe_tc_ffn_kern
                 tc_fence_after();
                 const uint32_t acc = tmem_d + buf * C::ACC_COLS;
                 for (int it = 0; it < nkb; ++it, ++g) {
-                    const int s = g % C::STAGES;
-                    ok = mbar_wait(&full[s], (g / C::STAGES) & 1, p.err, 12);
+                    const int sa = g % C::SA, sb = g % C::SB;
+                    ok = mbar_wait(&full_b[sb], (g / C::SB) & 1, p.err, 12) && mbar_wait(&full_a[sa], (g / C::SA) & 1, p.err, 12);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint8_t* a = smem + s * C::STAGE_BYTES;
-                    const uint64_t da0 = smem_desc_sw128(a), db = smem_desc_sw128(a + C::A_BYTES);
+                    const uint8_t* a = smem_a + sa * C::A_BYTES;
+                    const uint64_t da0 = smem_desc_sw128(a), db = smem_desc_sw128(smem_b + sb * C::B_BYTES);
 #pragma unroll
                     for (int k = 0; k < kTBK / 16; ++k) {
                         const uint32_t accum = (it > 0 || k > 0) ? 1u : 0u;
                         umma_f16(acc, da0 + 2 * k, db + 2 * k, idesc, accum);
                         if (GATEUP) umma_f16(acc + BN, smem_desc_sw128(a + kTBM * kTBK * 2) + 2 * k, db + 2 * k, idesc, accum);
                     }
-                    umma_commit(&empty[s]);
+                    umma_commit(&empty_a[sa]);
+                    umma_commit(&empty_b[sb]);
                 }
                 if (ok) umma_commit(&acc_full[buf]);
                 ++lt;
@@ -371,10 +432,10 @@ __global__ void __launch_bounds__(MoeTcCfg<BN, GATEUP>::THREADS) moe_tc_ffn_kern
         }
     } else if (warp < 2 + C::CONV_WARPS) {
         // ---------------- weight converters ----------------
-        const int ct = threadIdx.x - 64;                       // 0..255
-        constexpr int NP = C::ROWS * CV::PPR / C::CONV_THREADS;   // pieces per thread per stage
-        // stages fetched ahead of the one being converted: enough bytes in flight per SM to cover HBM latency
-        constexpr int PF = FMT == 2 ? 6 : (FMT == 0 ? 2 : 3);
+        const int ct = threadIdx.x - 64;                       // converter thread index
+        constexpr int NP = C::NP, RD = C::RD;
+        uint8_t* rawA = smem + C::OP_BYTES + C::BAR_BYTES;                                 // [RD][NP][threads] x 16 bytes
+        uint8_t* rawB = rawA + (size_t)RD * NP * C::CONV_THREADS * 16;                     // [RD][NP][threads] x AUX bytes
         int prow[NP], pc[NP];                                  // piece -> row inside the stage tile, piece inside the row
 #pragma unroll
         for (int i = 0; i < NP; ++i) { const int pid = i * C::CONV_THREADS + ct; prow[i] = pid / CV::PPR; pc[i] = pid % CV::PPR; }
@@ -396,39 +457,57 @@ __global__ void __launch_bounds__(MoeTcCfg<BN, GATEUP>::THREADS) moe_tc_ffn_kern
                 sfp[i] = base + (GATEUP ? (up ? p.ef.off_su : p.ef.off_sg) : p.ef.off_sd);
                 wrow[i] = jn * kTBM + (prow[i] & (kTBM - 1));   // weight row in the expert matrix
             }
-            typename CV::Raw raw[PF][NP];
+            auto issue_stage = [&](int it) {
+                const int ring = it % RD;
 #pragma unroll
-            for (int j = 0; j < PF; ++j)
-                if (j < nkb) {
-#pragma unroll
-                    for (int i = 0; i < NP; ++i) CV::load(raw[j][i], wp[i], sfp[i], wrow[i], K, j * kTBK, pc[i]);
+                for (int i = 0; i < NP; ++i) {
+                    const size_t idx = (size_t)(ring * NP + i) * C::CONV_THREADS + ct;
+                    CV::issue(rawA + idx * 16, rawB + idx * CV::AUX, wp[i], sfp[i], wrow[i], K, it * kTBK, pc[i]);
                 }
-            for (int it0 = 0; it0 < nkb && ok; it0 += PF) {
+            };
+            float sd[NP];
 #pragma unroll
-                for (int j = 0; j < PF; ++j) {
-                    const int it = it0 + j;
-                    if (it < nkb && ok) {
-                        const int s = g % C::STAGES;
-                        // one lane polls the barrier, the warp sleeps at the sync: waiting warps leave the issue slots alone
-                        int okw = 1;
-                        if (lane == 0) okw = mbar_wait(&empty[s], ((g / C::STAGES) & 1) ^ 1, p.err, 13) ? 1 : 0;
-                        ok = __shfl_sync(0xffffffffu, okw, 0) != 0;
-                        if (ok) {
-                            const uint32_t st_base = smem_u32(smem + s * C::STAGE_BYTES);
+            for (int i = 0; i < NP; ++i) sd[i] = CV::side(sfp[i], wrow[i], K, 0);
+            // prologue: RD - 1 stages in flight (one commit group per stage, empty groups keep the count uniform)
+#pragma unroll 1
+            for (int j = 0; j < RD - 1; ++j) {
+                if (j < nkb) issue_stage(j);
+                cpa_commit();
+            }
+#pragma unroll 1
+            for (int it = 0; it < nkb && ok; ++it) {
+                float sdn[NP];
 #pragma unroll
-                            for (int i = 0; i < NP; ++i) {
-                                const uint32_t tile = st_base + ((GATEUP && prow[i] >= kTBM) ? kTBM * kTBK * 2 : 0);
-                                CV::emit(raw[j][i], tile, prow[i] & (kTBM - 1), pc[i], it * kTBK);
-                                if (it + PF < nkb) CV::load(raw[j][i], wp[i], sfp[i], wrow[i], K, (it + PF) * kTBK, pc[i]);
-                            }
-                            fence_proxy_async();               // generic-proxy stores -> visible to the MMA's async-proxy reads
-                            __syncwarp();
-                            if (lane == 0) mbar_arrive(&full[s]);
-                            ++g;
-                        }
+                for (int i = 0; i < NP; ++i) sdn[i] = (it + 1 < nkb) ? CV::side(sfp[i], wrow[i], K, (it + 1) * kTBK) : 0.f;
+                cpa_wait<RD - 2>();                            // this thread's pieces of stage `it` have landed
+                const int s = g % C::SA;
+                // one lane polls the barrier, the warp sleeps at the sync: waiting warps leave the issue slots alone
+                int okw = 1;
+                if (lane == 0) okw = mbar_wait(&empty_a[s], ((g / C::SA) & 1) ^ 1, p.err, 13) ? 1 : 0;
+                ok = __shfl_sync(0xffffffffu, okw, 0) != 0;
+                if (ok) {
+                    const uint32_t st_base = smem_u32(smem_a + s * C::A_BYTES);
+                    const int ring = it % RD;
+#pragma unroll
+                    for (int i = 0; i < NP; ++i) {
+                        const size_t idx = (size_t)(ring * NP + i) * C::CONV_THREADS + ct;
+                        typename CV::Raw raw;
+                        CV::fetch(raw, rawA + idx * 16, rawB + idx * CV::AUX, sd[i]);
+                        const uint32_t tile = st_base + ((GATEUP && prow[i] >= kTBM) ? kTBM * kTBK * 2 : 0);
+                        CV::emit(raw, tile, prow[i] & (kTBM - 1), pc[i], it * kTBK);
                     }
+                    // refill the ring slot that was consumed one iteration ago
+                    if (it + RD - 1 < nkb) issue_stage(it + RD - 1);
+                    cpa_commit();
+                    fence_proxy_async();                       // generic-proxy stores -> visible to the MMA's async-proxy reads
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&full_a[s]);
+                    ++g;
+#pragma unroll
+                    for (int i = 0; i < NP; ++i) sd[i] = sdn[i];
                 }
             }
+            cpa_wait<0>();                                     // nothing of this item is left in flight
         }
     } else {
         // ---------------- epilogue (4 warps: one TMEM lane quarter each) ----------------
@@ -446,7 +525,7 @@ __global__ void __launch_bounds__(MoeTcCfg<BN, GATEUP>::THREADS) moe_tc_ffn_kern
             const uint8_t* base = p.arena + (size_t)slot * p.ef.stride;
             const uint32_t buf = lt & 1u;
             int okw = 1;
-            if (lane == 0) okw = mbar_wait(&acc_full[buf], (lt >> 1) & 1u, p.err, 14) ? 1 : 0;
+            if (lane == 0) okw = (LSB_MOE_RELAX ? mbar_wait_relaxed(&acc_full[buf], (lt >> 1) & 1u, p.err, 14) : mbar_wait(&acc_full[buf], (lt >> 1) & 1u, p.err, 14)) ? 1 : 0;
             ok = __shfl_sync(0xffffffffu, okw, 0) != 0;
             tc_fence_after();
             if (ok) {
@@ -510,7 +589,7 @@ static int sm_count() {
 
 template <int FMT, int BN, bool GATEUP>
 static int launch_moe_tc(const CUtensorMap& mb, const MoeTcParams& p, int nout, int max_tiles, cudaStream_t st) {
-    using C = MoeTcCfg<BN, GATEUP>;
+    using C = MoeTcCfg<FMT, BN, GATEUP>;
     static bool attr = false;
     if (!attr) { cudaFuncSetAttribute(moe_tc_ffn_kernel<FMT, BN, GATEUP>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM); attr = true; }
     const long long work = (long long)(nout / kTBM) * max_tiles;

@@ -38,12 +38,29 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
 }
 constexpr uint64_t kWaitLimitNs = 2000000000ull;   // 2 s: far beyond any legitimate wait in these kernels
 // Returns false (and records `code` in *err) when the barrier did not flip in time.
+#ifndef LSB_RELAXED_SLEEP_NS
+#define LSB_RELAXED_SLEEP_NS 200
+#endif
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err, int code) {
     if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = globaltimer_ns();
     for (uint32_t i = 0; i < (1u << 30); ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 255u) == 255u && globaltimer_ns() - t0 > kWaitLimitNs) break;
+    }
+    if (err) atomicCAS(err, 0, code);
+    return false;
+}
+
+// Same contract for waits that are long and off the critical path (an epilogue warp waiting for a whole tile): sleeping
+// between polls leaves the issue slots to the warps that are working.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, int* err, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = globaltimer_ns();
+    for (uint32_t i = 0; i < (1u << 30); ++i) {
+        __nanosleep(LSB_RELAXED_SLEEP_NS);
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 63u) == 63u && globaltimer_ns() - t0 > kWaitLimitNs) break;
     }
     if (err) atomicCAS(err, 0, code);
     return false;

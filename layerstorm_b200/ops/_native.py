@@ -16,7 +16,8 @@ from pathlib import Path
 import torch
 
 _LIB = None
-_LIB_PATH = Path(__file__).resolve().parent.parent / "_lib" / "liblsb200_kernels.so"
+# LSB200_KERNELS_LIB: load another build of the kernel library (kernel tuning experiments).
+_LIB_PATH = Path(os.environ.get("LSB200_KERNELS_LIB") or Path(__file__).resolve().parent.parent / "_lib" / "liblsb200_kernels.so")
 
 # signature letters: p pointer, i int32, l int64, f float, u uint64; the trailing stream is appended.
 _DECL = re.compile(r'LSB_API\s+int\s+(lsb_\w+)\s*\(([^)]*)\)', re.S)

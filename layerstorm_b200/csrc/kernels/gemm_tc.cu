@@ -219,6 +219,24 @@ int make_map_3d(CUtensorMap* map, const void* ptr, CUtensorMapDataType dt, int e
     return r == CUDA_SUCCESS ? 0 : -3;
 }
 
+// 3-D byte view [slot][row][byte] of quantised weight matrices that sit at the same offset in every slot of an arena
+// (strides: slot_stride, pitch, 1 bytes); box [1][box_rows][box_bytes] with the swizzle mode that matches box_bytes
+// (32, 64 or 128), so that a thread reading its own row of the box hits every bank once.
+int make_map_bytes_3d(CUtensorMap* map, const void* ptr, uint64_t pitch, uint64_t rows, uint64_t slot_stride, uint64_t nslots,
+                      uint32_t box_bytes, uint32_t box_rows) {
+    EncodeTiledFn enc = get_encode();
+    if (!enc) return -2;
+    if (((uintptr_t)ptr & 15) || (pitch & 15) || (slot_stride & 15)) return -4;
+    cuuint64_t gdim[3] = {pitch, rows, nslots};
+    cuuint64_t gstr[2] = {pitch, slot_stride};
+    cuuint32_t box[3] = {box_bytes, box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    const CUtensorMapSwizzle sw = box_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : (box_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(ptr), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : -3;
+}
+
 struct MapKey {
     const void* p; uint64_t rows, cols, ld; uint32_t br, bc; int dt;
     bool operator<(const MapKey& o) const { return std::tie(p, rows, cols, ld, br, bc, dt) < std::tie(o.p, o.rows, o.cols, o.ld, o.br, o.bc, o.dt); }

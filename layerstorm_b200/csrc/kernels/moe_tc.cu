@@ -5,13 +5,14 @@
 //   moe_tc_sort     counting sort of (row, slot) pairs by expert + list of [expert, first row, rows]
 //                   token tiles of at most BN rows (device-side, no host round trip)
 //   moe_tc_gather   xs[pos] = fp16(x[pair / S]) in sorted order (the TMA-loadable "B" operand)
-//   moe_tc_ffn      one CTA per (token tile, 128 weight rows):
-//        warp 0      TMA producer for the token tile (cp.async.bulk.tensor, 128-byte swizzle)
-//        warp 1      tensor-memory owner and tcgen05.mma issuer (kind::f16, fp16 x fp16 -> fp32 in TMEM)
-//        warps 2-9   weight converters: stream the expert's NVFP4 / FP8-block / BF16 rows from HBM
-//                    exactly once, expand them to fp16 (group / block scale folded in) and store them
-//                    straight into the 128-byte-swizzled shared-memory tile the MMA reads; warps 2-5
-//                    then run the epilogue (tcgen05.ld -> SwiGLU(+clamp) -> fp16, or -> fp32 rows)
+//   moe_tc_ffn      persistent, one CTA per SM walking (token tile, 128 weight rows) work items:
+//        warp 0      TMA producer for the token tiles (cp.async.bulk.tensor, 128-byte swizzle, 8-stage ring)
+//        warp 1      tensor-memory owner and tcgen05.mma issuer (kind::f16, fp16 x fp16 -> fp32 in TMEM,
+//                    A = weights read from tensor memory, B = tokens read from shared memory)
+//        warps 2-9   weight converters: stream the expert's NVFP4 / FP8-block / Q4_K / BF16 rows from HBM
+//                    exactly once into registers, expand them to fp16 (group / block scale folded in) and
+//                    write them with tcgen05.st into a ring of operand stages in tensor memory
+//        warps 10-13 epilogue (tcgen05.ld -> SwiGLU(+clamp) -> fp16, or -> fp32 / bf16 rows, or NVLink stores)
 //     gate and up tiles share one token tile and accumulate into two TMEM regions, so SwiGLU is
 //     fused and the [tokens, 2F] intermediate never exists.
 // Per-tensor NVFP4 scales are applied in the epilogue in fp32.  Every wait is bounded and reports
@@ -20,6 +21,9 @@
 // (src/core/expert_device.h:31-52, E/smxx/permute/moe_permute.cu, G/sm120/gemm/grouped).
 #include "tc_common.cuh"
 #include <cstring>
+#include <map>
+#include <mutex>
+#include <tuple>
 #include "gemv_core.cuh"
 #include "moe_fmt.cuh"
 #include "ep_comm.cuh"
@@ -93,164 +97,138 @@ __global__ void __launch_bounds__(128) moe_tc_gather_kernel(const bf16* __restri
 }
 
 // ------------------------------------------------------------------------------------------ converters
-// Address of 16-byte chunk `c` (0..7) of row `r` in a [rows x 64 fp16] tile with 128-byte swizzle.
-__device__ __forceinline__ uint32_t sw128_chunk(uint32_t tile, int r, int c) {
-    return tile + (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4));
-}
-__device__ __forceinline__ void st_shared_16(uint32_t addr, const uint4& v) {
-    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-}
 __device__ __forceinline__ __half2 e4m3x2_to_half2(uint16_t v) {
     uint32_t r;
     asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(r) : "h"(v));
     return *reinterpret_cast<__half2*>(&r);
 }
+__device__ __forceinline__ uint32_t h2_bits(const __half2& h) { return *reinterpret_cast<const uint32_t*>(&h); }
 
-// Weight conversion works in 16-byte "pieces" of raw weight bytes.  Consecutive converter threads take consecutive
-// pieces along a weight row and then the next row, so every 32-byte memory sector a warp touches is consumed
-// completely by that one load instruction (a row-per-thread mapping would fetch each sector twice).  A piece
-// expands to 8..32 fp16 values = 1..4 sixteen-byte chunks of the swizzled operand tile.
-//   Conv<FMT>::PPR   pieces per weight row per 64-element pipeline stage
-//   load(raw, w, sf, n, K, k0, c)   fetch piece c of matrix row n at reduction offset k0 (issued early)
-//   emit(raw, tile, row, c, k0)     expand and store it into row `row` of the operand tile
-template <int FMT> struct Conv;
+// Weight path of the grouped GEMM:  HBM --TMA--> raw ring in shared memory --ld.shared--> registers --convert-->
+// tcgen05.st --> operand ring in tensor memory --> tcgen05.mma (A from TMEM).
+// A pipeline stage is 64 reduction elements of 128 weight rows per matrix = one TMA box of SBYTES x 128 bytes of the
+// [slot][row][byte] view of the arena, written with the swizzle mode of width SBYTES.  One converter thread owns one
+// weight row (TMEM lane = row) and 64 / NH consecutive elements of the stage: it reads its 16-byte chunks from the
+// swizzled box (conflict free: the 8 lanes of a quarter-warp phase hit 8 different 16-byte bank groups), expands
+// them to fp16 pairs with the group / block scale folded in and writes them into its TMEM lane with one tcgen05.st.
+// The converted operand never exists in shared memory, which carries only raw bytes (once in, once out) and the
+// token tiles; staging fp16 weight tiles there would cost about four times the shared-memory bandwidth.
+//   RowConv<FMT, NH>::SBYTES                   raw bytes per row and stage
+//   stage_x(it)                                byte offset of stage `it` inside a weight row
+//   fetch(raw, tile, r, h)                     read this thread's chunks of row r (part h of NH) from the box at `tile`
+//   convert(raw, out, k0, h)                   expand to 32 / NH packed fp16 pairs
 constexpr float kFp8Unscale = 1.f / 256.f;
-
-// Raw weight bytes travel HBM -> shared memory with cp.async (no registers held while they are in flight, so the ring can be
-// deep enough to cover DRAM latency); the thread that issued a piece's copy is the one that later expands it.
-__device__ __forceinline__ void cpa16(void* dst, const void* src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+template <int SBYTES> __device__ __forceinline__ uint32_t swz_chunk(uint32_t tile, int r, int c) {
+    if (SBYTES == 128) return tile + (uint32_t)(r * 128 + ((c ^ (r & 7)) << 4));
+    if (SBYTES == 64) return tile + (uint32_t)(r * 64 + ((c ^ ((r >> 1) & 3)) << 4));
+    return tile + (uint32_t)(r * 32 + ((c ^ ((r >> 2) & 1)) << 4));
 }
-__device__ __forceinline__ void cpa4(void* dst, const void* src) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cpa_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void cpa_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+template <int FMT, int NH> struct RowConv;
 
-template <> struct Conv<2> {                  // NVFP4: 32 bytes per row-stage; 4 group scales in one word
-    static constexpr int PPR = 2;
-    struct Raw { uint4 v; uint32_t sc; };
-    static constexpr int AUX = 4;             // bytes of side data per piece in the raw ring (the scale word)
-    static __device__ __forceinline__ void issue(void* a, void* b, const uint8_t* w, const uint8_t* sf, int n, int K, int k0, int c) {
-        cpa16(a, w + (size_t)n * (K >> 1) + (k0 >> 1) + 16 * c);
-        const int gtiles = ((K >> 4) + 3) >> 2;
-        cpa4(b, sf + ((size_t)(n >> 7) * gtiles + (k0 >> 6)) * 512 + (n & 31) * 16 + ((n & 127) >> 5) * 4);
-    }
-    static __device__ __forceinline__ float side(const uint8_t*, int, int, int) { return 0.f; }
-    static __device__ __forceinline__ void fetch(Raw& r, const void* a, const void* b, float) {
-        r.v = *reinterpret_cast<const uint4*>(a);
-        r.sc = *reinterpret_cast<const uint32_t*>(b);
-    }
-    static __device__ __forceinline__ void emit(const Raw& r, uint32_t tile, int row, int c, int) {
-        const uint32_t wv[4] = {r.v.x, r.v.y, r.v.z, r.v.w};
+template <int NH> struct RowConv<2, NH> {     // NVFP4: 32 bytes per row-stage; 4 group scales in one word
+    static constexpr int SBYTES = 32, NV = 2 / NH, AUX = 512;              // AUX: the stage's 128 x 4 scale atom
+    struct Raw { uint4 v[NV]; uint32_t sc; };
+    static __device__ __forceinline__ int pitch(int K) { return K >> 1; }
+    static __device__ __forceinline__ int stage_x(int it) { return it * 32; }
+    static __device__ __forceinline__ void fetch(Raw& r, uint32_t tile, int row, int h) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {                 // 8 elements = one 16-byte fp16 chunk
-            __half2 h[4];
-            fp4x8_to_half2x4(wv[j], h);
-            // both halves of s2 = the e4m3 scale of this chunk's 16-group (byte 2c + j/2 of the scale word)
-            const __half2 s2 = e4m3x2_to_half2((uint16_t)(((r.sc >> ((2 * c + (j >> 1)) * 8)) & 0xffu) * 0x0101u));
+        for (int i = 0; i < NV; ++i) r.v[i] = ld_shared_16(swz_chunk<32>(tile, row, h * NV + i));
+    }
+    static __device__ __forceinline__ void convert(const Raw& r, uint32_t* out, int, int h) {
 #pragma unroll
-            for (int q = 0; q < 4; ++q) h[q] = __hmul2(h[q], s2);
-            st_shared_16(sw128_chunk(tile, row, 4 * c + j), *reinterpret_cast<uint4*>(h));
+        for (int i = 0; i < NV; ++i) {
+            const uint32_t wv[4] = {r.v[i].x, r.v[i].y, r.v[i].z, r.v[i].w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {             // one word = 8 elements; 16-group index = word / 2
+                __half2 hh[4];
+                fp4x8_to_half2x4(wv[j], hh);
+                const int word = (NH == 1 ? 0 : 4 * h) + 4 * i + j;
+                const __half2 s2 = e4m3x2_to_half2((uint16_t)(((r.sc >> ((word >> 1) * 8)) & 0xffu) * 0x0101u));
+#pragma unroll
+                for (int q = 0; q < 4; ++q) out[(4 * i + j) * 4 + q] = h2_bits(__hmul2(hh[q], s2));
+            }
         }
     }
 };
 
-template <> struct Conv<1> {                  // FP8 e4m3 with 128x128 block scales: 64 bytes per row-stage
-    static constexpr int PPR = 4;
-    struct Raw { uint4 v; float sc; };
-    static constexpr int AUX = 0;
-    static __device__ __forceinline__ void issue(void* a, void*, const uint8_t* w, const uint8_t*, int n, int K, int k0, int c) {
-        cpa16(a, w + (size_t)n * K + k0 + 16 * c);
+template <int NH> struct RowConv<1, NH> {     // FP8 e4m3 with 128 x 128 block scales: 64 bytes per row-stage
+    static constexpr int SBYTES = 64, NV = 4 / NH, AUX = 0;
+    struct Raw { uint4 v[NV]; float sc; };
+    static __device__ __forceinline__ int pitch(int K) { return K; }
+    static __device__ __forceinline__ int stage_x(int it) { return it * 64; }
+    static __device__ __forceinline__ void fetch(Raw& r, uint32_t tile, int row, int h) {
+#pragma unroll
+        for (int i = 0; i < NV; ++i) r.v[i] = ld_shared_16(swz_chunk<64>(tile, row, h * NV + i));
     }
-    // one float per 128 x 128 block: read (a cache hit) one stage before it is needed, so no load sits in the conversion
-    static __device__ __forceinline__ float side(const uint8_t* sf, int n, int K, int k0) {
-        return __ldg(reinterpret_cast<const float*>(sf) + (size_t)(n >> 7) * ((K + 127) >> 7) + (k0 >> 7));
-    }
-    static __device__ __forceinline__ void fetch(Raw& r, const void* a, const void*, float sd) {
-        r.v = *reinterpret_cast<const uint4*>(a);
-        r.sc = sd;
-    }
-    static __device__ __forceinline__ void emit(const Raw& r, uint32_t tile, int row, int c, int) {
+    static __device__ __forceinline__ void convert(const Raw& r, uint32_t* out, int, int) {
         // block scales of small weights sit near the bottom of the fp16 range: carry them times 2^8 (exact)
         // and take the factor out again in the fp32 epilogue (kFp8Unscale)
         const __half2 s2 = __float2half2_rn(r.sc * 256.f);
-        const uint32_t wv[4] = {r.v.x, r.v.y, r.v.z, r.v.w};
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {                 // 8 bytes -> 8 fp16
-            __half2 h[4];
-            h[0] = __hmul2(e4m3x2_to_half2((uint16_t)(wv[2 * j] & 0xffffu)), s2);
-            h[1] = __hmul2(e4m3x2_to_half2((uint16_t)(wv[2 * j] >> 16)), s2);
-            h[2] = __hmul2(e4m3x2_to_half2((uint16_t)(wv[2 * j + 1] & 0xffffu)), s2);
-            h[3] = __hmul2(e4m3x2_to_half2((uint16_t)(wv[2 * j + 1] >> 16)), s2);
-            st_shared_16(sw128_chunk(tile, row, 2 * c + j), *reinterpret_cast<uint4*>(h));
+        for (int i = 0; i < NV; ++i) {
+            const uint32_t wv[4] = {r.v[i].x, r.v[i].y, r.v[i].z, r.v[i].w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                out[(4 * i + j) * 2 + 0] = h2_bits(__hmul2(e4m3x2_to_half2((uint16_t)(wv[j] & 0xffffu)), s2));
+                out[(4 * i + j) * 2 + 1] = h2_bits(__hmul2(e4m3x2_to_half2((uint16_t)(wv[j] >> 16)), s2));
+            }
         }
     }
 };
 
-template <> struct Conv<3> {                  // GGUF Q4_K: 32 quant bytes per row-stage = one (low, high) nibble pair of sub-blocks
-    static constexpr int PPR = 2;
-    struct Raw { uint4 hdr; uint4 q; };
-    static constexpr int AUX = 16;            // the super-block header (d, dmin, 12 scale bytes)
-    static __device__ __forceinline__ void issue(void* a, void* b, const uint8_t* w, const uint8_t*, int n, int K, int k0, int c) {
-        const uint8_t* blk = w + ((size_t)n * (K >> 8) + (k0 >> 8)) * 144;
-        cpa16(b, blk);
-        cpa16(a, blk + 16 + ((k0 & 255) >> 6) * 32 + 16 * c);
+template <int NH> struct RowConv<3, NH> {     // GGUF Q4_K: a stage = 32 quant bytes: low nibbles = sub-block 2s, high nibbles = 2s + 1
+    static constexpr int SBYTES = 32, AUX = 0;
+    struct Raw { uint4 hdr; uint4 q[2]; };
+    static __device__ __forceinline__ int pitch(int K) { return (K >> 8) * 144; }
+    static __device__ __forceinline__ int stage_x(int it) { return (it >> 2) * 144 + 16 + (it & 3) * 32; }
+    static __device__ __forceinline__ void fetch(Raw& r, uint32_t tile, int row, int) {
+        r.q[0] = ld_shared_16(swz_chunk<32>(tile, row, 0));
+        r.q[1] = ld_shared_16(swz_chunk<32>(tile, row, 1));
     }
-    static __device__ __forceinline__ float side(const uint8_t*, int, int, int) { return 0.f; }
-    static __device__ __forceinline__ void fetch(Raw& r, const void* a, const void* b, float) {
-        r.q = *reinterpret_cast<const uint4*>(a);
-        r.hdr = *reinterpret_cast<const uint4*>(b);
-    }
-    static __device__ __forceinline__ void emit(const Raw& r, uint32_t tile, int row, int c, int k0) {
+    static __device__ __forceinline__ void convert(const Raw& r, uint32_t* out, int k0, int h) {
         const __half2 dd = *reinterpret_cast<const __half2*>(&r.hdr.x);
         const float d = __low2float(dd), dmin = __high2float(dd);
         uint8_t sc12[12];
         const uint32_t hw[3] = {r.hdr.y, r.hdr.z, r.hdr.w};
 #pragma unroll
         for (int i = 0; i < 12; ++i) sc12[i] = (uint8_t)(hw[i >> 2] >> (8 * (i & 3)));
-        const uint32_t wv[4] = {r.q.x, r.q.y, r.q.z, r.q.w};
+        const uint32_t wv[8] = {r.q[0].x, r.q[0].y, r.q[0].z, r.q[0].w, r.q[1].x, r.q[1].y, r.q[1].z, r.q[1].w};
         const int j2 = ((k0 & 255) >> 6) * 2;                      // first sub-block of this stage
 #pragma unroll
-        for (int half_i = 0; half_i < 2; ++half_i) {               // low nibbles: sub-block j2, high nibbles: j2 + 1
+        for (int hi = 0; hi < 2 / NH; ++hi) {                      // which nibble: elements 32 * nib .. 32 * nib + 31
+            const int nib = NH == 1 ? hi : h;
             float sc, mn;
-            q4k_scale_min(sc12, j2 + half_i, sc, mn);
+            q4k_scale_min(sc12, j2 + nib, sc, mn);
             const __half2 a2 = __float2half2_rn(d * sc), b2 = __float2half2_rn(-dmin * mn);
 #pragma unroll
-            for (int cc = 0; cc < 2; ++cc) {                       // bytes 8cc..8cc+7 of the piece -> elements 16c + 8cc ..
-                __half2 h[4];
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const uint32_t wq = wv[2 * cc + (q >> 1)] >> ((q & 1) * 16 + half_i * 4);
-                    // two consecutive bytes -> two 4-bit values as exact fp16 integers (1024 + v) - 1024
-                    const uint32_t bits = 0x64006400u | (wq & 0xFu) | (((wq >> 8) & 0xFu) << 16);
-                    const __half2 v = __hsub2(*reinterpret_cast<const __half2*>(&bits), __float2half2_rn(1024.f));
-                    h[q] = __hfma2(v, a2, b2);
-                }
-                st_shared_16(sw128_chunk(tile, row, half_i * 4 + 2 * c + cc), *reinterpret_cast<uint4*>(h));
+            for (int pr = 0; pr < 16; ++pr) {                      // byte pair (2 pr, 2 pr + 1) -> two consecutive elements
+                const uint32_t wq = wv[pr >> 1] >> ((pr & 1) * 16 + nib * 4);
+                // two 4-bit values as exact fp16 integers (1024 + v) - 1024
+                const uint32_t bits = 0x64006400u | (wq & 0xFu) | (((wq >> 8) & 0xFu) << 16);
+                const __half2 v = __hsub2(*reinterpret_cast<const __half2*>(&bits), __float2half2_rn(1024.f));
+                out[hi * 16 + pr] = h2_bits(__hfma2(v, a2, b2));
             }
         }
     }
 };
 
-template <> struct Conv<0> {                  // BF16: 128 bytes per row-stage
-    static constexpr int PPR = 8;
-    struct Raw { uint4 v; };
-    static constexpr int AUX = 0;
-    static __device__ __forceinline__ void issue(void* a, void*, const uint8_t* w, const uint8_t*, int n, int K, int k0, int c) {
-        cpa16(a, w + ((size_t)n * K + k0 + 8 * c) * 2);
-    }
-    static __device__ __forceinline__ float side(const uint8_t*, int, int, int) { return 0.f; }
-    static __device__ __forceinline__ void fetch(Raw& r, const void* a, const void*, float) {
-        r.v = *reinterpret_cast<const uint4*>(a);
-    }
-    static __device__ __forceinline__ void emit(const Raw& r, uint32_t tile, int row, int c, int) {
-        float f[8];
-        unpack_bf16x8(r.v, f);
-        __half2 h[4];
+template <int NH> struct RowConv<0, NH> {     // BF16: 128 bytes per row-stage
+    static constexpr int SBYTES = 128, NV = 8 / NH, AUX = 0;
+    struct Raw { uint4 v[NV]; };
+    static __device__ __forceinline__ int pitch(int K) { return K * 2; }
+    static __device__ __forceinline__ int stage_x(int it) { return it * 128; }
+    static __device__ __forceinline__ void fetch(Raw& r, uint32_t tile, int row, int h) {
 #pragma unroll
-        for (int q = 0; q < 4; ++q) h[q] = __floats2half2_rn(f[2 * q], f[2 * q + 1]);
-        st_shared_16(sw128_chunk(tile, row, c), *reinterpret_cast<uint4*>(h));
+        for (int i = 0; i < NV; ++i) r.v[i] = ld_shared_16(swz_chunk<128>(tile, row, h * NV + i));
+    }
+    static __device__ __forceinline__ void convert(const Raw& r, uint32_t* out, int, int) {
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            float f[8];
+            unpack_bf16x8(r.v[i], f);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) out[4 * i + q] = h2_bits(__floats2half2_rn(f[2 * q], f[2 * q + 1]));
+        }
     }
 };
 
@@ -273,38 +251,39 @@ struct MoeTcParams {
 
 template <int FMT, int BN, bool GATEUP> struct MoeTcCfg {
     static constexpr int A_TILES = GATEUP ? 2 : 1;
-    static constexpr int A_BYTES = A_TILES * kTBM * kTBK * 2;
+    static constexpr int NH = GATEUP ? 1 : 2;                             // converter threads per (row, stage): gate/up = one per matrix
+    using CV = RowConv<FMT, NH>;
     static constexpr int B_BYTES = BN * kTBK * 2;
-    // Two operand rings with their own barriers: converted weight tiles (SA stages, filled by the converter warps)
-    // and token tiles (SB stages, TMA).  The token ring runs further ahead, so a TMA round trip never sits between
-    // the MMA freeing a weight stage and the converters refilling it.
-    static constexpr int SA = GATEUP ? 2 : 3;
-    static constexpr int SB = 4;
-    static constexpr int OP_BYTES = SA * A_BYTES + SB * B_BYTES;
+    static constexpr int SB = 4;                                          // token-tile ring (shared memory, TMA)
     static constexpr int ACC_COLS = A_TILES * BN;                         // one accumulator set (gate [+ up])
-    static constexpr int TMEM_COLS = (2 * ACC_COLS) < 32 ? 32 : 2 * ACC_COLS;   // double-buffered: epilogue of tile i overlaps tile i+1
-#ifndef LSB_MOE_RELAX
-#define LSB_MOE_RELAX 1
-#endif
-#ifndef LSB_MOE_CONV_WARPS
-#define LSB_MOE_CONV_WARPS 8
-#endif
-    static constexpr int PIECES = (GATEUP ? 2 : 1) * kTBM * Conv<FMT>::PPR;   // 16-byte pieces per stage
-    static constexpr int CONV_WARPS = (PIECES / 32) < LSB_MOE_CONV_WARPS ? (PIECES / 32) : LSB_MOE_CONV_WARPS;
+    // Tensor memory (512 columns): accumulator sets first, then the ring of converted weight stages
+    // (32 columns = 64 fp16 per matrix and stage).  Two accumulator sets let the epilogue of one item overlap the
+    // main loop of the next; at ACC_COLS = 256 only one fits beside the weight ring.
+    static constexpr int NBUF = ACC_COLS > 128 ? 1 : 2;
+    static constexpr int A_COLS = 32 * A_TILES;
+    static constexpr int A_BASE = NBUF * ACC_COLS;
+    static constexpr int SA_FIT = (512 - A_BASE) / A_COLS;
+    static constexpr int SA = SA_FIT > 8 ? 8 : SA_FIT;                    // weight stages in TMEM
+    static constexpr int TMEM_COLS = 512;
+    static constexpr int CONV_WARPS = 8;
     static constexpr int EPI_WARPS = 4;
-    static constexpr int THREADS = (2 + CONV_WARPS + EPI_WARPS) * 32;
-    static constexpr int CONV_THREADS = CONV_WARPS * 32;
-    static constexpr int ROWS = A_TILES * kTBM;                           // weight rows per stage (gate rows, then up rows)
-    // raw ring: RD stages of not yet converted weight bytes in flight per CTA (up to ~128 KB)
-    static constexpr int NP = ROWS * Conv<FMT>::PPR / CONV_THREADS;       // 16-byte pieces per converter thread per stage
-    static constexpr int RAW_STAGE = NP * CONV_THREADS * (16 + Conv<FMT>::AUX);
-    static constexpr int RAW_BUDGET = 227 * 1024 - 1024 - 256 - OP_BYTES > 128 * 1024 ? 128 * 1024 : 227 * 1024 - 1024 - 256 - OP_BYTES;
-    static constexpr int RD_FIT = RAW_BUDGET / RAW_STAGE;
-    static constexpr int RD = RD_FIT > 12 ? 12 : (RD_FIT < 3 ? 3 : RD_FIT);
-    static constexpr int BAR_BYTES = 256;
-    static constexpr int SMEM = OP_BYTES + BAR_BYTES + RD * RAW_STAGE + 1024;
-    static_assert(SMEM <= 227 * 1024, "shared memory budget");
+    static constexpr int RAW_WARP = 2 + CONV_WARPS + EPI_WARPS;           // last warp: TMA producer of the raw weight ring
+    static constexpr int THREADS = (RAW_WARP + 1) * 32;
+    // raw weight ring (shared memory): per stage one SBYTES x 128 box per matrix (+ the NVFP4 scale atoms)
+    static constexpr int W_TILE = kTBM * CV::SBYTES;
+    static constexpr int RAW_STAGE = A_TILES * (W_TILE + CV::AUX);
+    static constexpr int BAR_BYTES = 512;
+    static constexpr int RAW_BUDGET = 224 * 1024 - SB * B_BYTES - BAR_BYTES - 1024;
+    static constexpr int RD_FIT = (RAW_BUDGET > 144 * 1024 ? 144 * 1024 : RAW_BUDGET) / RAW_STAGE;
+    static constexpr int RD = RD_FIT > 12 ? 12 : RD_FIT;
+    // One CTA per SM by construction (the CTA owns all of tensor memory): ask for more than half of the SM's shared memory.
+    static constexpr int SMEM_NEED = SB * B_BYTES + RD * RAW_STAGE + BAR_BYTES + 1024;
+    static constexpr int SMEM = SMEM_NEED < 120 * 1024 ? 120 * 1024 : SMEM_NEED;
+    static_assert(SA >= 3 && A_BASE + SA * A_COLS <= 512, "tensor memory budget");
+    static_assert(RD >= 3 && SMEM <= 227 * 1024, "shared memory budget");
+    static_assert((2 * SA + 2 * SB + 2 * RD + 4) * 8 + 8 <= BAR_BYTES, "barrier area");
 };
+constexpr int kMaxSlots = 1 << 16;               // slot extent of the weight tensor maps
 
 // Work item w -> (token tile t, weight tile j).  Items are grouped by kTileGroup consecutive token tiles (tiles are sorted
 // by expert, so a group mostly belongs to one expert); inside a group the token tile runs fastest, so the CTAs that
@@ -319,23 +298,27 @@ __device__ __forceinline__ void work_item(int w, int ntiles, int NT, int& t, int
     j = r / gsz;
 }
 
-// Persistent kernel: one CTA per SM walks the work list (token tile x 128-row weight tile, weight tile fastest so
-// that concurrently running CTAs share a token tile); the shared-memory ring, its barrier phases and the two TMEM
-// accumulator sets carry over from one work item to the next.
+// Persistent kernel: one CTA per SM walks the work list (token tile x 128-row weight tile); the rings, their barrier
+// phases and the accumulator sets carry over from one work item to the next, so the producers run ahead across
+// item boundaries.
 template <int FMT, int BN, bool GATEUP>
-__global__ void __launch_bounds__(MoeTcCfg<FMT, BN, GATEUP>::THREADS) moe_tc_ffn_kernel(const __grid_constant__ CUtensorMap map_b, MoeTcParams p) {
+__global__ void __launch_bounds__(MoeTcCfg<FMT, BN, GATEUP>::THREADS) moe_tc_ffn_kernel(const __grid_constant__ CUtensorMap map_b,
+                                                                                       const __grid_constant__ CUtensorMap map_w0,
+                                                                                       const __grid_constant__ CUtensorMap map_w1, MoeTcParams p) {
     using C = MoeTcCfg<FMT, BN, GATEUP>;
-    using CV = Conv<FMT>;
+    using CV = typename C::CV;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint8_t* smem_a = smem;                                   // [SA] converted weight tiles (gate [+ up])
-    uint8_t* smem_b = smem + C::SA * C::A_BYTES;              // [SB] token tiles
-    uint64_t* full_a = reinterpret_cast<uint64_t*>(smem + C::OP_BYTES);
+    uint8_t* smem_b = smem;                                   // [SB] token tiles
+    uint8_t* smem_r = smem + C::SB * C::B_BYTES;              // [RD] raw weight stages
+    uint64_t* full_a = reinterpret_cast<uint64_t*>(smem_r + C::RD * C::RAW_STAGE);
     uint64_t* empty_a = full_a + C::SA;
     uint64_t* full_b = empty_a + C::SA;
     uint64_t* empty_b = full_b + C::SB;
-    uint64_t* acc_full = empty_b + C::SB;        // [2]
-    uint64_t* acc_empty = acc_full + 2;          // [2]
+    uint64_t* full_r = empty_b + C::SB;
+    uint64_t* empty_r = full_r + C::RD;
+    uint64_t* acc_full = empty_r + C::RD;        // [NBUF]
+    uint64_t* acc_empty = acc_full + 2;          // [NBUF]
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_empty + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -347,10 +330,13 @@ __global__ void __launch_bounds__(MoeTcCfg<FMT, BN, GATEUP>::THREADS) moe_tc_ffn
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::SA; ++s) { mbar_init(&full_a[s], C::CONV_WARPS); mbar_init(&empty_a[s], 1); }
         for (int s = 0; s < C::SB; ++s) { mbar_init(&full_b[s], 1); mbar_init(&empty_b[s], 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], C::EPI_WARPS); }
+        for (int s = 0; s < C::RD; ++s) { mbar_init(&full_r[s], 1); mbar_init(&empty_r[s], C::CONV_WARPS); }
+        for (int b = 0; b < C::NBUF; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], C::EPI_WARPS); }
         fence_barrier_init();
         fence_proxy_async();
         tma_prefetch_desc(&map_b);
+        tma_prefetch_desc(&map_w0);
+        if (GATEUP) tma_prefetch_desc(&map_w1);
     }
     if (warp == 1) tmem_alloc(tmem_holder, C::TMEM_COLS);
     tc_fence_before();
@@ -367,6 +353,8 @@ __global__ void __launch_bounds__(MoeTcCfg<FMT, BN, GATEUP>::THREADS) moe_tc_ffn
     }
     const int ntiles = p.counters[0];
     const int total = ntiles * NT;
+    // an expert that is not resident on this GPU (or a slot the weight maps do not cover): every role skips the item
+    auto slot_ok = [&](int slot) { return slot >= 0 && slot < kMaxSlots; };
 
     if (warp == 0) {
         if (lane == 0) {
@@ -377,7 +365,7 @@ __global__ void __launch_bounds__(MoeTcCfg<FMT, BN, GATEUP>::THREADS) moe_tc_ffn
                 int t, jn;
                 work_item(w, ntiles, NT, t, jn);
                 const int e = p.tile_expert[t];
-                if (p.slot_of[e] < 0) {              // expert not resident on this GPU: every role skips the item
+                if (!slot_ok(p.slot_of[e])) {
                     if (GATEUP && p.miss_flag && jn == 0) atomicExch(p.miss_flag, e + 1);
                     continue;
                 }
@@ -395,18 +383,52 @@ __global__ void __launch_bounds__(MoeTcCfg<FMT, BN, GATEUP>::THREADS) moe_tc_ffn
                 for (uint32_t i = g > (uint32_t)C::SB ? g - C::SB : 0; i < g; ++i) mbar_wait(&full_b[i % C::SB], (i / C::SB) & 1, nullptr, 0);
             }
         }
+    } else if (warp == C::RAW_WARP) {
+        if (lane == 0) {
+            // ---------------- TMA producer: raw weight bytes (and NVFP4 scale atoms) ----------------
+            uint32_t g = 0;
+            bool ok = true;
+            for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
+                int t, jn;
+                work_item(w, ntiles, NT, t, jn);
+                const int slot = p.slot_of[p.tile_expert[t]];
+                if (!slot_ok(slot)) continue;
+                const uint8_t* base = p.arena + (size_t)slot * p.ef.stride;
+                const uint8_t* sf0 = base + (GATEUP ? p.ef.off_sg : p.ef.off_sd);
+                const uint8_t* sf1 = base + p.ef.off_su;
+                const int gtiles = ((K >> 4) + 3) >> 2;        // NVFP4: 512-byte scale atoms per 128-row tile
+                for (int it = 0; it < nkb; ++it, ++g) {
+                    const int s = g % C::RD;
+                    ok = mbar_wait(&empty_r[s], ((g / C::RD) & 1) ^ 1, p.err, 16);
+                    if (!ok) break;
+                    uint8_t* dst = smem_r + s * C::RAW_STAGE;
+                    mbar_expect_tx(&full_r[s], C::RAW_STAGE);
+                    const int x = CV::stage_x(it);
+                    tma_load_3d(dst, &map_w0, &full_r[s], x, jn * kTBM, slot);
+                    if (GATEUP) tma_load_3d(dst + C::W_TILE, &map_w1, &full_r[s], x, jn * kTBM, slot);
+                    if (CV::AUX) {
+                        const size_t so = ((size_t)jn * gtiles + it) * 512;
+                        bulk_load_1d(dst + C::A_TILES * C::W_TILE, sf0 + so, 512, &full_r[s]);
+                        if (GATEUP) bulk_load_1d(dst + C::A_TILES * C::W_TILE + 512, sf1 + so, 512, &full_r[s]);
+                    }
+                }
+            }
+            if (!ok) {
+                for (uint32_t i = g > (uint32_t)C::RD ? g - C::RD : 0; i < g; ++i) mbar_wait(&full_r[i % C::RD], (i / C::RD) & 1, nullptr, 0);
+            }
+        }
     } else if (warp == 1) {
         if (lane == 0) {
-            // ---------------- MMA issuer ----------------
+            // ---------------- MMA issuer: A (weights) from tensor memory, B (tokens) from shared memory ----------------
             constexpr uint32_t idesc = idesc_f16(kTBM, BN, 0);
             uint32_t g = 0, lt = 0;
             bool ok = true;
             for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
                 int t, jn;
                 work_item(w, ntiles, NT, t, jn);
-                if (p.slot_of[p.tile_expert[t]] < 0) continue;
-                const uint32_t buf = lt & 1u;
-                ok = mbar_wait(&acc_empty[buf], ((lt >> 1) & 1u) ^ 1u, p.err, 15);     // epilogue has drained this accumulator set
+                if (!slot_ok(p.slot_of[p.tile_expert[t]])) continue;
+                const uint32_t buf = lt % C::NBUF;
+                ok = mbar_wait(&acc_empty[buf], ((lt / C::NBUF) & 1u) ^ 1u, p.err, 15);   // epilogue has drained this accumulator set
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t acc = tmem_d + buf * C::ACC_COLS;
@@ -415,13 +437,13 @@ __global__ void __launch_bounds__(MoeTcCfg<FMT, BN, GATEUP>::THREADS) moe_tc_ffn
                     ok = mbar_wait(&full_b[sb], (g / C::SB) & 1, p.err, 12) && mbar_wait(&full_a[sa], (g / C::SA) & 1, p.err, 12);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint8_t* a = smem_a + sa * C::A_BYTES;
-                    const uint64_t da0 = smem_desc_sw128(a), db = smem_desc_sw128(smem_b + sb * C::B_BYTES);
+                    const uint32_t a_t = tmem_d + C::A_BASE + sa * C::A_COLS;
+                    const uint64_t db = smem_desc_sw128(smem_b + sb * C::B_BYTES);
 #pragma unroll
                     for (int k = 0; k < kTBK / 16; ++k) {
                         const uint32_t accum = (it > 0 || k > 0) ? 1u : 0u;
-                        umma_f16(acc, da0 + 2 * k, db + 2 * k, idesc, accum);
-                        if (GATEUP) umma_f16(acc + BN, smem_desc_sw128(a + kTBM * kTBK * 2) + 2 * k, db + 2 * k, idesc, accum);
+                        umma_f16_ts(acc, a_t + 8 * k, db + 2 * k, idesc, accum);
+                        if (GATEUP) umma_f16_ts(acc + BN, a_t + 32 + 8 * k, db + 2 * k, idesc, accum);
                     }
                     umma_commit(&empty_a[sa]);
                     umma_commit(&empty_b[sb]);
@@ -432,82 +454,76 @@ __global__ void __launch_bounds__(MoeTcCfg<FMT, BN, GATEUP>::THREADS) moe_tc_ffn
         }
     } else if (warp < 2 + C::CONV_WARPS) {
         // ---------------- weight converters ----------------
-        const int ct = threadIdx.x - 64;                       // converter thread index
-        constexpr int NP = C::NP, RD = C::RD;
-        uint8_t* rawA = smem + C::OP_BYTES + C::BAR_BYTES;                                 // [RD][NP][threads] x 16 bytes
-        uint8_t* rawB = rawA + (size_t)RD * NP * C::CONV_THREADS * 16;                     // [RD][NP][threads] x AUX bytes
-        int prow[NP], pc[NP];                                  // piece -> row inside the stage tile, piece inside the row
-#pragma unroll
-        for (int i = 0; i < NP; ++i) { const int pid = i * C::CONV_THREADS + ct; prow[i] = pid / CV::PPR; pc[i] = pid % CV::PPR; }
+        constexpr int NC = 32 / C::NH;
+        const int q = warp & 3;                                // TMEM lane quarter this warp may access
+        const int part = (warp - 2) >> 2;                      // gate/up: matrix (0 gate, 1 up); down: half of the stage's K range
+        const int row = q * 32 + lane;                         // row of the 128-row weight tile = TMEM lane
+        const int h = GATEUP ? 0 : part;
+        const int mat = GATEUP ? part : 0;
+        const uint32_t t_lane = tmem_d + C::A_BASE + ((uint32_t)(q * 32) << 16) + (GATEUP ? part * 32 : part * NC);
         uint32_t g = 0;
         bool ok = true;
         for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
             int t, jn;
             work_item(w, ntiles, NT, t, jn);
             const int slot = p.slot_of[p.tile_expert[t]];
-            if (slot < 0) continue;
+            if (!slot_ok(slot)) continue;
             const uint8_t* base = p.arena + (size_t)slot * p.ef.stride;
-            const uint8_t* wp[NP];
-            const uint8_t* sfp[NP];
-            int wrow[NP];
-#pragma unroll
-            for (int i = 0; i < NP; ++i) {
-                const bool up = GATEUP && prow[i] >= kTBM;
-                wp[i] = base + (GATEUP ? (up ? p.ef.off_up : p.ef.off_gate) : p.ef.off_down);
-                sfp[i] = base + (GATEUP ? (up ? p.ef.off_su : p.ef.off_sg) : p.ef.off_sd);
-                wrow[i] = jn * kTBM + (prow[i] & (kTBM - 1));   // weight row in the expert matrix
-            }
-            auto issue_stage = [&](int it) {
-                const int ring = it % RD;
-#pragma unroll
-                for (int i = 0; i < NP; ++i) {
-                    const size_t idx = (size_t)(ring * NP + i) * C::CONV_THREADS + ct;
-                    CV::issue(rawA + idx * 16, rawB + idx * CV::AUX, wp[i], sfp[i], wrow[i], K, it * kTBK, pc[i]);
-                }
-            };
-            float sd[NP];
-#pragma unroll
-            for (int i = 0; i < NP; ++i) sd[i] = CV::side(sfp[i], wrow[i], K, 0);
-            // prologue: RD - 1 stages in flight (one commit group per stage, empty groups keep the count uniform)
-#pragma unroll 1
-            for (int j = 0; j < RD - 1; ++j) {
-                if (j < nkb) issue_stage(j);
-                cpa_commit();
-            }
+            const uint8_t* wm = base + (GATEUP ? (part ? p.ef.off_up : p.ef.off_gate) : p.ef.off_down);
+            const uint8_t* sf = base + (GATEUP ? (part ? p.ef.off_su : p.ef.off_sg) : p.ef.off_sd);
+            const int n = jn * kTBM + row;                     // weight row in the expert matrix
+            // side data that does not travel through the ring: the FP8 block scale (one float per 128 x 128 block, the
+            // same for the whole tile) and the Q4_K super-block header (16 bytes per row and 256 elements), both read
+            // ahead of their use
+            const float* fsc = reinterpret_cast<const float*>(sf) + (size_t)(n >> 7) * ((K + 127) >> 7);
+            float sc_next = 0.f;
+            uint4 hdr_cur = make_uint4(0, 0, 0, 0), hdr_next = hdr_cur;
+            if (FMT == 1) sc_next = __ldg(fsc);
+            if (FMT == 3) hdr_next = __ldg(reinterpret_cast<const uint4*>(wm + (size_t)n * CV::pitch(K)));
 #pragma unroll 1
             for (int it = 0; it < nkb && ok; ++it) {
-                float sdn[NP];
-#pragma unroll
-                for (int i = 0; i < NP; ++i) sdn[i] = (it + 1 < nkb) ? CV::side(sfp[i], wrow[i], K, (it + 1) * kTBK) : 0.f;
-                cpa_wait<RD - 2>();                            // this thread's pieces of stage `it` have landed
-                const int s = g % C::SA;
+                typename CV::Raw raw;
+                if constexpr (FMT == 1) {
+                    raw.sc = sc_next;
+                    if (it + 1 < nkb) sc_next = __ldg(fsc + ((it + 1) >> 1));
+                }
+                if constexpr (FMT == 3) {
+                    if ((it & 3) == 0) {
+                        hdr_cur = hdr_next;
+                        if (it + 4 < nkb) hdr_next = __ldg(reinterpret_cast<const uint4*>(wm + (size_t)n * CV::pitch(K) + (size_t)((it >> 2) + 1) * 144));
+                    }
+                    raw.hdr = hdr_cur;
+                }
+                const int rs = g % C::RD, s = g % C::SA;
                 // one lane polls the barrier, the warp sleeps at the sync: waiting warps leave the issue slots alone
                 int okw = 1;
-                if (lane == 0) okw = mbar_wait(&empty_a[s], ((g / C::SA) & 1) ^ 1, p.err, 13) ? 1 : 0;
+                if (lane == 0) okw = mbar_wait(&full_r[rs], (g / C::RD) & 1, p.err, 17) ? 1 : 0;
                 ok = __shfl_sync(0xffffffffu, okw, 0) != 0;
-                if (ok) {
-                    const uint32_t st_base = smem_u32(smem_a + s * C::A_BYTES);
-                    const int ring = it % RD;
-#pragma unroll
-                    for (int i = 0; i < NP; ++i) {
-                        const size_t idx = (size_t)(ring * NP + i) * C::CONV_THREADS + ct;
-                        typename CV::Raw raw;
-                        CV::fetch(raw, rawA + idx * 16, rawB + idx * CV::AUX, sd[i]);
-                        const uint32_t tile = st_base + ((GATEUP && prow[i] >= kTBM) ? kTBM * kTBK * 2 : 0);
-                        CV::emit(raw, tile, prow[i] & (kTBM - 1), pc[i], it * kTBK);
-                    }
-                    // refill the ring slot that was consumed one iteration ago
-                    if (it + RD - 1 < nkb) issue_stage(it + RD - 1);
-                    cpa_commit();
-                    fence_proxy_async();                       // generic-proxy stores -> visible to the MMA's async-proxy reads
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&full_a[s]);
-                    ++g;
-#pragma unroll
-                    for (int i = 0; i < NP; ++i) sd[i] = sdn[i];
+                if (!ok) break;
+                const uint32_t stage = smem_u32(smem_r + rs * C::RAW_STAGE);
+                CV::fetch(raw, stage + mat * C::W_TILE, row, h);
+                if constexpr (FMT == 2) {
+                    // scale atom of the 128-row tile: word (row % 32) * 4 + row / 32
+                    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(raw.sc) : "r"(stage + C::A_TILES * C::W_TILE + mat * 512 + lane * 16 + q * 4) : "memory");
                 }
+                uint32_t out[NC];
+                CV::convert(raw, out, it * kTBK, h);           // consumes every byte read above
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(&empty_r[rs]);                 // the raw stage may be refilled
+                    okw = mbar_wait(&empty_a[s], ((g / C::SA) & 1) ^ 1, p.err, 13) ? 1 : 0;
+                }
+                ok = __shfl_sync(0xffffffffu, okw, 0) != 0;
+                if (!ok) break;
+                tc_fence_after();                              // the MMAs that read this operand stage have completed
+                if (NC == 32) tmem_st32(t_lane + s * C::A_COLS, out);
+                else tmem_st16(t_lane + s * C::A_COLS, out);
+                tmem_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&full_a[s]);
+                ++g;
             }
-            cpa_wait<0>();                                     // nothing of this item is left in flight
         }
     } else {
         // ---------------- epilogue (4 warps: one TMEM lane quarter each) ----------------
@@ -519,13 +535,13 @@ __global__ void __launch_bounds__(MoeTcCfg<FMT, BN, GATEUP>::THREADS) moe_tc_ffn
             work_item(w, ntiles, NT, t, jn);
             const int e = p.tile_expert[t];
             const int slot = p.slot_of[e];
-            if (slot < 0) continue;
+            if (!slot_ok(slot)) continue;
             const int row0 = p.tile_row0[t], ncols = p.tile_n[t];
             const int n = jn * kTBM + q * 32 + lane;
             const uint8_t* base = p.arena + (size_t)slot * p.ef.stride;
-            const uint32_t buf = lt & 1u;
+            const uint32_t buf = lt % C::NBUF;
             int okw = 1;
-            if (lane == 0) okw = (LSB_MOE_RELAX ? mbar_wait_relaxed(&acc_full[buf], (lt >> 1) & 1u, p.err, 14) : mbar_wait(&acc_full[buf], (lt >> 1) & 1u, p.err, 14)) ? 1 : 0;
+            if (lane == 0) okw = mbar_wait_relaxed(&acc_full[buf], (lt / C::NBUF) & 1u, p.err, 14) ? 1 : 0;
             ok = __shfl_sync(0xffffffffu, okw, 0) != 0;
             tc_fence_after();
             if (ok) {
@@ -577,6 +593,28 @@ __global__ void __launch_bounds__(MoeTcCfg<FMT, BN, GATEUP>::THREADS) moe_tc_ffn
     pdl_launch_dependents();
 }
 
+int make_map_bytes_3d(CUtensorMap* map, const void* ptr, uint64_t pitch, uint64_t rows, uint64_t slot_stride, uint64_t nslots,
+                      uint32_t box_bytes, uint32_t box_rows);
+static int cached_map_w(CUtensorMap* out, const void* ptr, uint64_t pitch, uint64_t rows, uint64_t sstride, uint64_t nslots, int sbytes) {
+    struct Key {
+        const void* p; uint64_t pitch, rows, ss, ns; int sb;
+        bool operator<(const Key& o) const { return std::tie(p, pitch, rows, ss, ns, sb) < std::tie(o.p, o.pitch, o.rows, o.ss, o.ns, o.sb); }
+    };
+    static std::map<Key, CUtensorMap> cache;
+    static std::mutex mu;
+    std::lock_guard<std::mutex> g(mu);
+    const Key k{ptr, pitch, rows, sstride, nslots, sbytes};
+    auto it = cache.find(k);
+    if (it != cache.end()) { *out = it->second; return 0; }
+    CUtensorMap m;
+    const int rc = make_map_bytes_3d(&m, ptr, pitch, rows, sstride, nslots, (uint32_t)sbytes, (uint32_t)kTBM);
+    if (rc) return rc;
+    if (cache.size() > 65536) cache.clear();
+    cache[k] = m;
+    *out = m;
+    return 0;
+}
+
 static int sm_count() {
     static int n = 0;
     if (!n) {
@@ -589,12 +627,26 @@ static int sm_count() {
 
 template <int FMT, int BN, bool GATEUP>
 static int launch_moe_tc(const CUtensorMap& mb, const MoeTcParams& p, int nout, int max_tiles, cudaStream_t st) {
+    using CVt = typename MoeTcCfg<FMT, BN, GATEUP>::CV;
+    const int Kred = GATEUP ? p.ef.H : p.ef.F;
+    CUtensorMap mw0, mw1;
+    {
+        // byte views of the weight matrices over every slot of the arena (dense mode: one "slot")
+        const uint64_t pitch = (uint64_t)(FMT == 0 ? Kred * 2 : FMT == 1 ? Kred : FMT == 2 ? Kred / 2 : Kred / 256 * 144);
+        const bool dense = p.ef.stride == 0;
+        const uint64_t sstride = dense ? pitch * (uint64_t)nout : (uint64_t)p.ef.stride;
+        const uint64_t nslots = dense ? 1 : (uint64_t)kMaxSlots;
+        int rc = cached_map_w(&mw0, p.arena + (GATEUP ? p.ef.off_gate : p.ef.off_down), pitch, (uint64_t)nout, sstride, nslots, CVt::SBYTES);
+        if (rc) return rc;
+        if (GATEUP) { rc = cached_map_w(&mw1, p.arena + p.ef.off_up, pitch, (uint64_t)nout, sstride, nslots, CVt::SBYTES); if (rc) return rc; }
+        else mw1 = mw0;
+    }
     using C = MoeTcCfg<FMT, BN, GATEUP>;
     static bool attr = false;
     if (!attr) { cudaFuncSetAttribute(moe_tc_ffn_kernel<FMT, BN, GATEUP>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM); attr = true; }
     const long long work = (long long)(nout / kTBM) * max_tiles;
     const int grid = (int)(work < sm_count() ? (work > 0 ? work : 1) : sm_count());
-    launch_pdl((moe_tc_ffn_kernel<FMT, BN, GATEUP>), grid, C::THREADS, C::SMEM, st, mb, p);
+    launch_pdl((moe_tc_ffn_kernel<FMT, BN, GATEUP>), grid, C::THREADS, C::SMEM, st, mb, mw0, mw1, p);
     return (int)cudaGetLastError();
 }
 

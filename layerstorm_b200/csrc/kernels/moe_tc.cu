@@ -254,18 +254,29 @@ template <int FMT, int BN, bool GATEUP> struct MoeTcCfg {
     static constexpr int NH = GATEUP ? 1 : 2;                             // converter threads per (row, stage): gate/up = one per matrix
     using CV = RowConv<FMT, NH>;
     static constexpr int B_BYTES = BN * kTBK * 2;
-    static constexpr int SB = 4;                                          // token-tile ring (shared memory, TMA)
+
     static constexpr int ACC_COLS = A_TILES * BN;                         // one accumulator set (gate [+ up])
     // Tensor memory (512 columns): accumulator sets first, then the ring of converted weight stages
     // (32 columns = 64 fp16 per matrix and stage).  Two accumulator sets let the epilogue of one item overlap the
     // main loop of the next; at ACC_COLS = 256 only one fits beside the weight ring.
-    static constexpr int NBUF = ACC_COLS > 128 ? 1 : 2;
+#ifndef LSB_MOE_NBUF1_COLS
+#define LSB_MOE_NBUF1_COLS 128
+#endif
+    static constexpr int NBUF = ACC_COLS > LSB_MOE_NBUF1_COLS ? 1 : 2;
     static constexpr int A_COLS = 32 * A_TILES;
     static constexpr int A_BASE = NBUF * ACC_COLS;
     static constexpr int SA_FIT = (512 - A_BASE) / A_COLS;
-    static constexpr int SA = SA_FIT > 8 ? 8 : SA_FIT;                    // weight stages in TMEM
+    static constexpr int SA = SA_FIT > 8 ? 8 : SA_FIT;                    // converted weight stages in TMEM
+    static constexpr int SB = 4;                                          // token-tile ring (shared memory, TMA)
     static constexpr int TMEM_COLS = 512;
-    static constexpr int CONV_WARPS = 8;
+    // 8 converter warps cover one stage (4 lane quarters x 2 parts); CONV_GROUPS such sets take the stages round-robin, so
+    // a warp has CONV_GROUPS stage times for its serial wait -> read -> convert -> store -> signal chain.
+#ifndef LSB_MOE_CONV_GROUPS
+#define LSB_MOE_CONV_GROUPS 1
+#endif
+    static constexpr int CONV_GROUPS = LSB_MOE_CONV_GROUPS;
+    static constexpr int STAGE_WARPS = 8;
+    static constexpr int CONV_WARPS = STAGE_WARPS * CONV_GROUPS;
     static constexpr int EPI_WARPS = 4;
     static constexpr int RAW_WARP = 2 + CONV_WARPS + EPI_WARPS;           // last warp: TMA producer of the raw weight ring
     static constexpr int THREADS = (RAW_WARP + 1) * 32;
@@ -283,7 +294,21 @@ template <int FMT, int BN, bool GATEUP> struct MoeTcCfg {
     static_assert(RD >= 3 && SMEM <= 227 * 1024, "shared memory budget");
     static_assert((2 * SA + 2 * SB + 2 * RD + 4) * 8 + 8 <= BAR_BYTES, "barrier area");
 };
-constexpr int kMaxSlots = 1 << 16;               // slot extent of the weight tensor maps
+constexpr int kMaxSlots = 1 << 16;
+// Role-level time breakdown for tuning builds (-DLSB_MOE_PROFILE): block 0 accumulates the cycles each role spends
+// waiting on each barrier and working; lsb_moe_tc_prof_read copies the table out.
+#ifdef LSB_MOE_PROFILE
+__device__ unsigned long long g_moe_prof[32];
+#define PROF_DECL() long long _pacc[4] = {0, 0, 0, 0}; const long long _pt0 = clock64()
+#define PROF_SCOPE(j, stmt) do { const long long _t = clock64(); stmt; _pacc[j] += clock64() - _t; } while (0)
+#define PROF_FLUSH(j, i) do { if (blockIdx.x == 0) g_moe_prof[i] += (unsigned long long)_pacc[j]; } while (0)
+#define PROF_TOTAL(i) do { if (blockIdx.x == 0) g_moe_prof[i] += (unsigned long long)(clock64() - _pt0); } while (0)
+#else
+#define PROF_DECL()
+#define PROF_SCOPE(j, stmt) do { stmt; } while (0)
+#define PROF_FLUSH(j, i)
+#define PROF_TOTAL(i)
+#endif               // slot extent of the weight tensor maps
 
 // Work item w -> (token tile t, weight tile j).  Items are grouped by kTileGroup consecutive token tiles (tiles are sorted
 // by expert, so a group mostly belongs to one expert); inside a group the token tile runs fastest, so the CTAs that
@@ -328,9 +353,9 @@ __global__ void __launch_bounds__(MoeTcCfg<FMT, BN, GATEUP>::THREADS) moe_tc_ffn
     const int nkb = K / kTBK;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < C::SA; ++s) { mbar_init(&full_a[s], C::CONV_WARPS); mbar_init(&empty_a[s], 1); }
+        for (int s = 0; s < C::SA; ++s) { mbar_init(&full_a[s], C::STAGE_WARPS); mbar_init(&empty_a[s], 1); }
         for (int s = 0; s < C::SB; ++s) { mbar_init(&full_b[s], 1); mbar_init(&empty_b[s], 1); }
-        for (int s = 0; s < C::RD; ++s) { mbar_init(&full_r[s], 1); mbar_init(&empty_r[s], C::CONV_WARPS); }
+        for (int s = 0; s < C::RD; ++s) { mbar_init(&full_r[s], 1); mbar_init(&empty_r[s], C::STAGE_WARPS); }
         for (int b = 0; b < C::NBUF; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], C::EPI_WARPS); }
         fence_barrier_init();
         fence_proxy_async();
@@ -361,6 +386,7 @@ __global__ void __launch_bounds__(MoeTcCfg<FMT, BN, GATEUP>::THREADS) moe_tc_ffn
             // ---------------- TMA producer: token tiles ----------------
             uint32_t g = 0;
             bool ok = true;
+            PROF_DECL();
             for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
                 int t, jn;
                 work_item(w, ntiles, NT, t, jn);
@@ -372,12 +398,13 @@ __global__ void __launch_bounds__(MoeTcCfg<FMT, BN, GATEUP>::THREADS) moe_tc_ffn
                 const int row0 = p.tile_row0[t];
                 for (int it = 0; it < nkb; ++it, ++g) {
                     const int s = g % C::SB;
-                    ok = mbar_wait(&empty_b[s], ((g / C::SB) & 1) ^ 1, p.err, 11);
+                    PROF_SCOPE(0, ok = mbar_wait(&empty_b[s], ((g / C::SB) & 1) ^ 1, p.err, 11));
                     if (!ok) break;
                     mbar_expect_tx(&full_b[s], C::B_BYTES);
                     tma_load_2d(smem_b + s * C::B_BYTES, &map_b, &full_b[s], it * kTBK, row0);
                 }
             }
+            PROF_FLUSH(0, 1);
             if (!ok) {
                 // loads in flight still write this CTA's shared memory: let them land (bounded, no error code)
                 for (uint32_t i = g > (uint32_t)C::SB ? g - C::SB : 0; i < g; ++i) mbar_wait(&full_b[i % C::SB], (i / C::SB) & 1, nullptr, 0);
@@ -388,6 +415,7 @@ __global__ void __launch_bounds__(MoeTcCfg<FMT, BN, GATEUP>::THREADS) moe_tc_ffn
             // ---------------- TMA producer: raw weight bytes (and NVFP4 scale atoms) ----------------
             uint32_t g = 0;
             bool ok = true;
+            PROF_DECL();
             for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
                 int t, jn;
                 work_item(w, ntiles, NT, t, jn);
@@ -399,7 +427,7 @@ __global__ void __launch_bounds__(MoeTcCfg<FMT, BN, GATEUP>::THREADS) moe_tc_ffn
                 const int gtiles = ((K >> 4) + 3) >> 2;        // NVFP4: 512-byte scale atoms per 128-row tile
                 for (int it = 0; it < nkb; ++it, ++g) {
                     const int s = g % C::RD;
-                    ok = mbar_wait(&empty_r[s], ((g / C::RD) & 1) ^ 1, p.err, 16);
+                    PROF_SCOPE(0, ok = mbar_wait(&empty_r[s], ((g / C::RD) & 1) ^ 1, p.err, 16));
                     if (!ok) break;
                     uint8_t* dst = smem_r + s * C::RAW_STAGE;
                     mbar_expect_tx(&full_r[s], C::RAW_STAGE);
@@ -413,6 +441,7 @@ __global__ void __launch_bounds__(MoeTcCfg<FMT, BN, GATEUP>::THREADS) moe_tc_ffn
                     }
                 }
             }
+            PROF_FLUSH(0, 0);
             if (!ok) {
                 for (uint32_t i = g > (uint32_t)C::RD ? g - C::RD : 0; i < g; ++i) mbar_wait(&full_r[i % C::RD], (i / C::RD) & 1, nullptr, 0);
             }
@@ -423,22 +452,25 @@ __global__ void __launch_bounds__(MoeTcCfg<FMT, BN, GATEUP>::THREADS) moe_tc_ffn
             constexpr uint32_t idesc = idesc_f16(kTBM, BN, 0);
             uint32_t g = 0, lt = 0;
             bool ok = true;
+            PROF_DECL();
             for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
                 int t, jn;
                 work_item(w, ntiles, NT, t, jn);
                 if (!slot_ok(p.slot_of[p.tile_expert[t]])) continue;
                 const uint32_t buf = lt % C::NBUF;
-                ok = mbar_wait(&acc_empty[buf], ((lt / C::NBUF) & 1u) ^ 1u, p.err, 15);   // epilogue has drained this accumulator set
+                PROF_SCOPE(0, ok = mbar_wait(&acc_empty[buf], ((lt / C::NBUF) & 1u) ^ 1u, p.err, 15));   // epilogue has drained this accumulator set
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t acc = tmem_d + buf * C::ACC_COLS;
                 for (int it = 0; it < nkb; ++it, ++g) {
                     const int sa = g % C::SA, sb = g % C::SB;
-                    ok = mbar_wait(&full_b[sb], (g / C::SB) & 1, p.err, 12) && mbar_wait(&full_a[sa], (g / C::SA) & 1, p.err, 12);
+                    PROF_SCOPE(1, ok = mbar_wait(&full_b[sb], (g / C::SB) & 1, p.err, 12));
+                    if (ok) PROF_SCOPE(2, ok = mbar_wait(&full_a[sa], (g / C::SA) & 1, p.err, 12));
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t a_t = tmem_d + C::A_BASE + sa * C::A_COLS;
                     const uint64_t db = smem_desc_sw128(smem_b + sb * C::B_BYTES);
+                    PROF_SCOPE(3, {
 #pragma unroll
                     for (int k = 0; k < kTBK / 16; ++k) {
                         const uint32_t accum = (it > 0 || k > 0) ? 1u : 0u;
@@ -446,23 +478,26 @@ __global__ void __launch_bounds__(MoeTcCfg<FMT, BN, GATEUP>::THREADS) moe_tc_ffn
                         if (GATEUP) umma_f16_ts(acc + BN, a_t + 32 + 8 * k, db + 2 * k, idesc, accum);
                     }
                     umma_commit(&empty_a[sa]);
-                    umma_commit(&empty_b[sb]);
+                    umma_commit(&empty_b[sb]); });
                 }
                 if (ok) umma_commit(&acc_full[buf]);
                 ++lt;
             }
+            PROF_FLUSH(0, 4); PROF_FLUSH(1, 2); PROF_FLUSH(2, 3); PROF_FLUSH(3, 14); PROF_TOTAL(5);
         }
     } else if (warp < 2 + C::CONV_WARPS) {
         // ---------------- weight converters ----------------
         constexpr int NC = 32 / C::NH;
         const int q = warp & 3;                                // TMEM lane quarter this warp may access
-        const int part = (warp - 2) >> 2;                      // gate/up: matrix (0 gate, 1 up); down: half of the stage's K range
+        const int part = ((warp - 2) >> 2) & 1;                // gate/up: matrix (0 gate, 1 up); down: half of the stage's K range
+        const int grp = (warp - 2) >> 3;                       // this warp converts the stages with g % CONV_GROUPS == grp
         const int row = q * 32 + lane;                         // row of the 128-row weight tile = TMEM lane
         const int h = GATEUP ? 0 : part;
         const int mat = GATEUP ? part : 0;
         const uint32_t t_lane = tmem_d + C::A_BASE + ((uint32_t)(q * 32) << 16) + (GATEUP ? part * 32 : part * NC);
         uint32_t g = 0;
         bool ok = true;
+        PROF_DECL();
         for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
             int t, jn;
             work_item(w, ntiles, NT, t, jn);
@@ -474,30 +509,31 @@ __global__ void __launch_bounds__(MoeTcCfg<FMT, BN, GATEUP>::THREADS) moe_tc_ffn
             const int n = jn * kTBM + row;                     // weight row in the expert matrix
             // side data that does not travel through the ring: the FP8 block scale (one float per 128 x 128 block, the
             // same for the whole tile) and the Q4_K super-block header (16 bytes per row and 256 elements), both read
-            // ahead of their use
+            // one handled stage ahead of their use
             const float* fsc = reinterpret_cast<const float*>(sf) + (size_t)(n >> 7) * ((K + 127) >> 7);
+            const uint8_t* qrow = wm + (size_t)n * CV::pitch(K);
+            const int it_first = (int)((grp + C::CONV_GROUPS - g % C::CONV_GROUPS) % C::CONV_GROUPS);   // first stage of this item that is ours
             float sc_next = 0.f;
-            uint4 hdr_cur = make_uint4(0, 0, 0, 0), hdr_next = hdr_cur;
-            if (FMT == 1) sc_next = __ldg(fsc);
-            if (FMT == 3) hdr_next = __ldg(reinterpret_cast<const uint4*>(wm + (size_t)n * CV::pitch(K)));
+            uint4 hdr_next = make_uint4(0, 0, 0, 0);
+            if (FMT == 1 && it_first < nkb) sc_next = __ldg(fsc + (it_first >> 1));
+            if (FMT == 3 && it_first < nkb) hdr_next = __ldg(reinterpret_cast<const uint4*>(qrow + (size_t)(it_first >> 2) * 144));
 #pragma unroll 1
             for (int it = 0; it < nkb && ok; ++it) {
+                if ((int)(g % C::CONV_GROUPS) != grp) { ++g; continue; }
                 typename CV::Raw raw;
+                const int itn = it + C::CONV_GROUPS;               // next stage of this item that is ours
                 if constexpr (FMT == 1) {
                     raw.sc = sc_next;
-                    if (it + 1 < nkb) sc_next = __ldg(fsc + ((it + 1) >> 1));
+                    if (itn < nkb) sc_next = __ldg(fsc + (itn >> 1));
                 }
                 if constexpr (FMT == 3) {
-                    if ((it & 3) == 0) {
-                        hdr_cur = hdr_next;
-                        if (it + 4 < nkb) hdr_next = __ldg(reinterpret_cast<const uint4*>(wm + (size_t)n * CV::pitch(K) + (size_t)((it >> 2) + 1) * 144));
-                    }
-                    raw.hdr = hdr_cur;
+                    raw.hdr = hdr_next;
+                    if (itn < nkb) hdr_next = __ldg(reinterpret_cast<const uint4*>(qrow + (size_t)(itn >> 2) * 144));
                 }
                 const int rs = g % C::RD, s = g % C::SA;
                 // one lane polls the barrier, the warp sleeps at the sync: waiting warps leave the issue slots alone
                 int okw = 1;
-                if (lane == 0) okw = mbar_wait(&full_r[rs], (g / C::RD) & 1, p.err, 17) ? 1 : 0;
+                if (lane == 0) { if (warp == 2) PROF_SCOPE(0, okw = mbar_wait(&full_r[rs], (g / C::RD) & 1, p.err, 17) ? 1 : 0); else okw = mbar_wait(&full_r[rs], (g / C::RD) & 1, p.err, 17) ? 1 : 0; }
                 ok = __shfl_sync(0xffffffffu, okw, 0) != 0;
                 if (!ok) break;
                 const uint32_t stage = smem_u32(smem_r + rs * C::RAW_STAGE);
@@ -511,25 +547,28 @@ __global__ void __launch_bounds__(MoeTcCfg<FMT, BN, GATEUP>::THREADS) moe_tc_ffn
                 __syncwarp();
                 if (lane == 0) {
                     mbar_arrive(&empty_r[rs]);                 // the raw stage may be refilled
-                    okw = mbar_wait(&empty_a[s], ((g / C::SA) & 1) ^ 1, p.err, 13) ? 1 : 0;
+                    if (warp == 2) PROF_SCOPE(1, okw = mbar_wait(&empty_a[s], ((g / C::SA) & 1) ^ 1, p.err, 13) ? 1 : 0); else okw = mbar_wait(&empty_a[s], ((g / C::SA) & 1) ^ 1, p.err, 13) ? 1 : 0;
                 }
                 ok = __shfl_sync(0xffffffffu, okw, 0) != 0;
                 if (!ok) break;
                 tc_fence_after();                              // the MMAs that read this operand stage have completed
-                if (NC == 32) tmem_st32(t_lane + s * C::A_COLS, out);
-                else tmem_st16(t_lane + s * C::A_COLS, out);
-                tmem_wait_st();
+                PROF_SCOPE(3, {
+                    if (NC == 32) tmem_st32(t_lane + s * C::A_COLS, out);
+                    else tmem_st16(t_lane + s * C::A_COLS, out);
+                    tmem_wait_st(); });
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&full_a[s]);
                 ++g;
             }
         }
+        if (warp == 2 && lane == 0) { PROF_FLUSH(0, 6); PROF_FLUSH(1, 8); PROF_FLUSH(2, 7); PROF_FLUSH(3, 9); PROF_TOTAL(10); }
     } else {
         // ---------------- epilogue (4 warps: one TMEM lane quarter each) ----------------
         const int q = warp & 3;
         uint32_t lt = 0;
         bool ok = true;
+        PROF_DECL();
         for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
             int t, jn;
             work_item(w, ntiles, NT, t, jn);
@@ -541,7 +580,7 @@ __global__ void __launch_bounds__(MoeTcCfg<FMT, BN, GATEUP>::THREADS) moe_tc_ffn
             const uint8_t* base = p.arena + (size_t)slot * p.ef.stride;
             const uint32_t buf = lt % C::NBUF;
             int okw = 1;
-            if (lane == 0) okw = mbar_wait_relaxed(&acc_full[buf], (lt / C::NBUF) & 1u, p.err, 14) ? 1 : 0;
+            if (lane == 0) { if (q == 0) PROF_SCOPE(0, okw = mbar_wait_relaxed(&acc_full[buf], (lt / C::NBUF) & 1u, p.err, 14) ? 1 : 0); else okw = mbar_wait_relaxed(&acc_full[buf], (lt / C::NBUF) & 1u, p.err, 14) ? 1 : 0; }
             ok = __shfl_sync(0xffffffffu, okw, 0) != 0;
             tc_fence_after();
             if (ok) {
@@ -585,6 +624,7 @@ __global__ void __launch_bounds__(MoeTcCfg<FMT, BN, GATEUP>::THREADS) moe_tc_ffn
             if (lane == 0) mbar_arrive(&acc_empty[buf]);       // the MMA issuer may overwrite this accumulator set
             ++lt;
         }
+        if (q == 0 && lane == 0) { PROF_FLUSH(0, 11); PROF_TOTAL(13); }
     }
     tc_fence_before();
     __syncthreads();
@@ -663,6 +703,20 @@ static int dispatch_fmt(int fmt, const CUtensorMap& mb, const MoeTcParams& p, in
 
 }  // namespace lsb
 using namespace lsb;
+
+// Role-level cycle table of tuning builds (see PROF_SCOPE); -1 in a normal build.
+LSB_API int lsb_moe_tc_prof_read(void* out32, int reset, void* stream) {
+    (void)stream;
+#ifdef LSB_MOE_PROFILE
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(out32, g_moe_prof, sizeof(unsigned long long) * 32);
+    if (reset) { unsigned long long z[32] = {0}; cudaMemcpyToSymbol(g_moe_prof, z, sizeof(z)); }
+    return 0;
+#else
+    (void)out32; (void)reset;
+    return -1;
+#endif
+}
 
 // Tiles of at most `BN` (32, 64 or 128) sorted rows.  tile_* arrays hold npairs / BN + E_total + 1 entries,
 // counters 2 ints, sorted_pair npairs ints.

@@ -58,7 +58,9 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_full + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * BM, m0 = blockIdx.y * BN;
+    // token-row tiles are the fastest grid dimension: the blocks that share a weight tile run together, so the weight
+    // matrix streams from DRAM once and the (much smaller) activation tiles stay in L2
+    const int n0 = blockIdx.y * BM, m0 = blockIdx.x * BN;
     const int split = BATCHED ? 0 : blockIdx.z, batch = BATCHED ? blockIdx.z : 0;
     const int nkb_total = (p.K + BK - 1) / BK;
     const int kb0 = split * p.kb_per_split;
@@ -264,7 +266,7 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const GemmTcP
     using C = TcCfg<BN>;
     static bool attr = false;
     if (!attr) { cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM); attr = true; }
-    dim3 grid((p.N + BM - 1) / BM, (p.M + BN - 1) / BN, p.splits);
+    dim3 grid((p.M + BN - 1) / BN, (p.N + BM - 1) / BM, p.splits);
     launch_pdl((gemm_tc_kernel<BN>), grid, 192, C::SMEM, st, mw, mx, p);
     return (int)cudaGetLastError();
 }
@@ -274,7 +276,7 @@ static int launch_tc_batched(const CUtensorMap& mw, const CUtensorMap& mx, const
     using C = TcCfg<BN>;
     static bool attr = false;
     if (!attr) { cudaFuncSetAttribute(gemm_tc_kernel<BN, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM); attr = true; }
-    dim3 grid((p.N + BM - 1) / BM, (p.M + BN - 1) / BN, batch);
+    dim3 grid((p.M + BN - 1) / BN, (p.N + BM - 1) / BM, batch);
     launch_pdl((gemm_tc_kernel<BN, true>), grid, 192, C::SMEM, st, mw, mx, p);
     return (int)cudaGetLastError();
 }

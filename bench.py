@@ -95,6 +95,7 @@ def main():
     ap.add_argument("--headroom-gib", type=float, default=2.5, help="HBM left free after weights (caches, workspaces, context)")
     ap.add_argument("--no-graph", action="store_true", help="eager launches (for per-kernel profiling)")
     ap.add_argument("--synthetic-fill", action="store_true", help="skip the real prefill; decode over an uninitialised cache")
+    ap.add_argument("--layers", type=int, default=0, help="smoke runs only: keep the first N layers (the JSON line is then marked invalid)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -116,6 +117,9 @@ def main():
     from layerstorm_b200.runtime.engine import Engine
 
     cfg = get_preset(args.model)
+    if args.layers and args.layers < cfg.n_layers:
+        import dataclasses
+        cfg = dataclasses.replace(cfg, n_layers=args.layers, **({"layer_types": list(cfg.layer_types[:args.layers])} if cfg.layer_types else {}))
     dev = torch.device("cuda", local)
     t0 = time.time()
     # as many routed-expert slots per layer as fit in HBM next to the other weights; any remainder
@@ -230,6 +234,7 @@ def main():
             "clocks": clocks,
             "e2e": {"value": round(e2e, 3), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": launches,
+            **({"invalid": f"depth reduced to {args.layers} layers (smoke run)"} if args.layers else {}),
             "extra": {"prefill_tok_s": round(prefill_tps, 1) if prefill_tps else None, "init_s": round(t_init, 1),
                       "weight_gib": round(model.weight_bytes() / 2 ** 30, 2)},
         }

@@ -187,6 +187,90 @@ struct MlaDecodeParams {
     const float* tq_centroids;   // kv_fmt 2: the 16 reconstruction levels
 };
 
+// Loads KT cache rows (token positions s_tok[0..KT), -1 = none) into the bf16 tile Ks[KT][DP]: latent part expanded
+// from the cache format (bf16 copy, FP8 e4m3 -> bf16 exactly, TurboQuant codes -> centroids), rope part copied, the
+// per-row latent scale into sc[].
+__device__ __forceinline__ void mla_load_tile(const MlaDecodeParams& p, int seq, int rb, const int* s_tok, bf16* Ks, float* sc, int DP, int D,
+                                              int t, int nthr, int KT) {
+    if (p.kv_fmt == 0) {
+        const int cpr = D / 8;
+        for (int i = t; i < KT * cpr; i += nthr) {
+            const int j = i / cpr, c = i % cpr, tok = s_tok[j];
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (tok >= 0) {
+                const int pg = p.block_table[(size_t)seq * p.max_pages + tok / p.page];
+                v = *reinterpret_cast<const uint4*>(p.cache + ((size_t)pg * p.page + tok % p.page) * rb + c * 16);
+            }
+            *reinterpret_cast<uint4*>(Ks + j * DP + c * 8) = v;
+        }
+        if (t < KT) sc[t] = 1.f;
+    } else if (p.kv_fmt == 2) {
+        const int c32 = p.dl / 32, cr = p.dr / 8, cpr = c32 + cr;   // 16 bytes = 32 codes
+        for (int i = t; i < KT * cpr; i += nthr) {
+            const int j = i / cpr, c = i % cpr, tok = s_tok[j];
+            const uint8_t* row = nullptr;
+            if (tok >= 0) {
+                const int pg = p.block_table[(size_t)seq * p.max_pages + tok / p.page];
+                row = p.cache + ((size_t)pg * p.page + tok % p.page) * rb;
+            }
+            if (c < c32) {
+                const uint4 v = row ? *reinterpret_cast<const uint4*>(row + c * 16) : make_uint4(0x77777777u, 0x77777777u, 0x77777777u, 0x77777777u);
+                const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
+                bf162* o = reinterpret_cast<bf162*>(Ks + j * DP + c * 32);
+#pragma unroll
+                for (int b = 0; b < 16; ++b) {
+                    const uint32_t byte = (wv[b >> 2] >> (8 * (b & 3))) & 0xffu;
+                    o[b] = __floats2bfloat162_rn(row ? __ldg(p.tq_centroids + (byte & 15u)) : 0.f, row ? __ldg(p.tq_centroids + (byte >> 4)) : 0.f);
+                }
+            } else {
+                const int cc = c - c32;
+                uint4 v = row ? *reinterpret_cast<const uint4*>(row + p.dl / 2 + 16 + cc * 16) : make_uint4(0, 0, 0, 0);
+                *reinterpret_cast<uint4*>(Ks + j * DP + p.dl + cc * 8) = v;
+            }
+        }
+        if (t < KT) {
+            const int tok = s_tok[t];
+            float s = 0.f;
+            if (tok >= 0) {
+                const int pg = p.block_table[(size_t)seq * p.max_pages + tok / p.page];
+                s = *reinterpret_cast<const float*>(p.cache + ((size_t)pg * p.page + tok % p.page) * rb + p.dl / 2);
+            }
+            sc[t] = s;
+        }
+    } else {
+        const int c8 = p.dl / 16, cr = p.dr / 8, cpr = c8 + cr;
+        for (int i = t; i < KT * cpr; i += nthr) {
+            const int j = i / cpr, c = i % cpr, tok = s_tok[j];
+            const uint8_t* row = nullptr;
+            if (tok >= 0) {
+                const int pg = p.block_table[(size_t)seq * p.max_pages + tok / p.page];
+                row = p.cache + ((size_t)pg * p.page + tok % p.page) * rb;
+            }
+            if (c < c8) {
+                uint4 v = row ? *reinterpret_cast<const uint4*>(row + c * 16) : make_uint4(0, 0, 0, 0);
+                float f[16];
+                unpack_fp8x4(v.x, f); unpack_fp8x4(v.y, f + 4); unpack_fp8x4(v.z, f + 8); unpack_fp8x4(v.w, f + 12);
+                bf162* o = reinterpret_cast<bf162*>(Ks + j * DP + c * 16);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) o[e] = __floats2bfloat162_rn(f[2 * e], f[2 * e + 1]);   // e4m3 -> bf16 is exact
+            } else {
+                const int cc = c - c8;
+                uint4 v = row ? *reinterpret_cast<const uint4*>(row + p.dl + 16 + cc * 16) : make_uint4(0, 0, 0, 0);
+                *reinterpret_cast<uint4*>(Ks + j * DP + p.dl + cc * 8) = v;
+            }
+        }
+        if (t < KT) {
+            const int tok = s_tok[t];
+            float s = 0.f;
+            if (tok >= 0) {
+                const int pg = p.block_table[(size_t)seq * p.max_pages + tok / p.page];
+                s = *reinterpret_cast<const float*>(p.cache + ((size_t)pg * p.page + tok % p.page) * rb + p.dl);
+            }
+            sc[t] = s;
+        }
+    }
+}
+
 __global__ void __launch_bounds__(256) mla_decode_kernel(MlaDecodeParams p) {
     extern __shared__ __align__(16) uint8_t smraw[];
     const int D = p.dl + p.dr, DP = D + 8;     // padded bf16 row (16 B mod 128 B => conflict-free 128-bit reads)
@@ -229,84 +313,7 @@ __global__ void __launch_bounds__(256) mla_decode_kernel(MlaDecodeParams p) {
             s_tok[t] = tok;
         }
         __syncthreads();
-        // load tile
-        if (p.kv_fmt == 0) {
-            const int cpr = D / 8;
-            for (int i = t; i < kTK * cpr; i += blockDim.x) {
-                const int j = i / cpr, c = i % cpr, tok = s_tok[j];
-                uint4 v = make_uint4(0, 0, 0, 0);
-                if (tok >= 0) {
-                    const int pg = p.block_table[(size_t)seq * p.max_pages + tok / p.page];
-                    v = *reinterpret_cast<const uint4*>(p.cache + ((size_t)pg * p.page + tok % p.page) * rb + c * 16);
-                }
-                *reinterpret_cast<uint4*>(Ks + j * DP + c * 8) = v;
-            }
-            if (t < kTK) sc[t] = 1.f;
-        } else if (p.kv_fmt == 2) {
-            const int c32 = p.dl / 32, cr = p.dr / 8, cpr = c32 + cr;   // 16 bytes = 32 codes
-            for (int i = t; i < kTK * cpr; i += blockDim.x) {
-                const int j = i / cpr, c = i % cpr, tok = s_tok[j];
-                const uint8_t* row = nullptr;
-                if (tok >= 0) {
-                    const int pg = p.block_table[(size_t)seq * p.max_pages + tok / p.page];
-                    row = p.cache + ((size_t)pg * p.page + tok % p.page) * rb;
-                }
-                if (c < c32) {
-                    const uint4 v = row ? *reinterpret_cast<const uint4*>(row + c * 16) : make_uint4(0x77777777u, 0x77777777u, 0x77777777u, 0x77777777u);
-                    const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
-                    bf162* o = reinterpret_cast<bf162*>(Ks + j * DP + c * 32);
-#pragma unroll
-                    for (int b = 0; b < 16; ++b) {
-                        const uint32_t byte = (wv[b >> 2] >> (8 * (b & 3))) & 0xffu;
-                        o[b] = __floats2bfloat162_rn(row ? __ldg(p.tq_centroids + (byte & 15u)) : 0.f, row ? __ldg(p.tq_centroids + (byte >> 4)) : 0.f);
-                    }
-                } else {
-                    const int cc = c - c32;
-                    uint4 v = row ? *reinterpret_cast<const uint4*>(row + p.dl / 2 + 16 + cc * 16) : make_uint4(0, 0, 0, 0);
-                    *reinterpret_cast<uint4*>(Ks + j * DP + p.dl + cc * 8) = v;
-                }
-            }
-            if (t < kTK) {
-                const int tok = s_tok[t];
-                float s = 0.f;
-                if (tok >= 0) {
-                    const int pg = p.block_table[(size_t)seq * p.max_pages + tok / p.page];
-                    s = *reinterpret_cast<const float*>(p.cache + ((size_t)pg * p.page + tok % p.page) * rb + p.dl / 2);
-                }
-                sc[t] = s;
-            }
-        } else {
-            const int c8 = p.dl / 16, cr = p.dr / 8, cpr = c8 + cr;
-            for (int i = t; i < kTK * cpr; i += blockDim.x) {
-                const int j = i / cpr, c = i % cpr, tok = s_tok[j];
-                const uint8_t* row = nullptr;
-                if (tok >= 0) {
-                    const int pg = p.block_table[(size_t)seq * p.max_pages + tok / p.page];
-                    row = p.cache + ((size_t)pg * p.page + tok % p.page) * rb;
-                }
-                if (c < c8) {
-                    uint4 v = row ? *reinterpret_cast<const uint4*>(row + c * 16) : make_uint4(0, 0, 0, 0);
-                    float f[16];
-                    unpack_fp8x4(v.x, f); unpack_fp8x4(v.y, f + 4); unpack_fp8x4(v.z, f + 8); unpack_fp8x4(v.w, f + 12);
-                    bf162* o = reinterpret_cast<bf162*>(Ks + j * DP + c * 16);
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) o[e] = __floats2bfloat162_rn(f[2 * e], f[2 * e + 1]);   // e4m3 -> bf16 is exact
-                } else {
-                    const int cc = c - c8;
-                    uint4 v = row ? *reinterpret_cast<const uint4*>(row + p.dl + 16 + cc * 16) : make_uint4(0, 0, 0, 0);
-                    *reinterpret_cast<uint4*>(Ks + j * DP + p.dl + cc * 8) = v;
-                }
-            }
-            if (t < kTK) {
-                const int tok = s_tok[t];
-                float s = 0.f;
-                if (tok >= 0) {
-                    const int pg = p.block_table[(size_t)seq * p.max_pages + tok / p.page];
-                    s = *reinterpret_cast<const float*>(p.cache + ((size_t)pg * p.page + tok % p.page) * rb + p.dl);
-                }
-                sc[t] = s;
-            }
-        }
+        mla_load_tile(p, seq, rb, s_tok, Ks, sc, DP, D, t, blockDim.x, kTK);
         __syncthreads();
         // scores: warp -> heads (2w, 2w+1); lane -> cache row
         {
@@ -375,6 +382,173 @@ __global__ void __launch_bounds__(256) mla_decode_kernel(MlaDecodeParams p) {
                 float* o = p.o_part + (((size_t)r * p.H + hh) * p.NS + sp) * p.dl + 2 * t;
                 o[0] = acc[h][0]; o[1] = acc[h][1];
             }
+        }
+    }
+    if (t < kHG && hg * kHG + t < p.H) {
+        float* ml = p.ml_part + (((size_t)r * p.H + hg * kHG + t) * p.NS + sp) * 2;
+        ml[0] = s_m[t]; ml[1] = s_l[t];
+    }
+    pdl_launch_dependents();
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// Many-row variant (prefill chunks, verify batches, large decode batches): same contract as mla_decode_kernel
+// (grid = rows x head groups x splits, same partial outputs), but the two contractions run on the tensor
+// cores: warp-level mma.sync m16n8k16 (bf16 x bf16 -> fp32) with the 16 heads of the group as the M dimension.
+//   scores  S[16 heads x 64 keys]  = Q[16 x D] . K^T      warp w owns keys 8w .. 8w+7 (one n-tile), all of D
+//   values  O[16 heads x dl]      += P[16 x 64] . V        warp w owns dl / 8 latent columns, all 64 keys
+// K tile rows double as V rows (absorbed MLA: the value is the latent itself), so a tile is gathered and
+// de-quantised once.  The softmax statistics are exchanged between the warps through shared memory.
+// (The 5th-generation tensor path needs M = 128 rows per instruction; with 16-64 heads per query row and a
+// private key set per row that shape does not occur here.)
+constexpr int kTKM = 64;   // cache rows per tile of the tensor-core variant
+
+__device__ __forceinline__ uint32_t smem_addr_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x2(uint32_t addr, uint32_t& r0, uint32_t& r1) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x2_trans(uint32_t addr, uint32_t& r0, uint32_t& r1) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16_16816(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+LSB_API int lsb_mla_decode_mma_smem_bytes(int dl, int dr) {
+    const int DP = dl + dr + 8;
+    return (kTKM + kHG) * DP * 2 + kHG * (kTKM + 8) * 2 + kTKM * 4 + kTKM * 4 + (3 * kHG + 2 * 8 * kHG) * 4;
+}
+
+__global__ void __launch_bounds__(256) mla_decode_mma_kernel(MlaDecodeParams p) {
+    extern __shared__ __align__(16) uint8_t smraw[];
+    const int D = p.dl + p.dr, DP = D + 8;     // padded bf16 row: 16 bytes past a multiple of 128 => conflict-free ldmatrix rows
+    constexpr int PP = kTKM + 8;               // padded P row
+    bf16* Ks = reinterpret_cast<bf16*>(smraw);                 // [kTKM][DP]
+    bf16* Qs = Ks + kTKM * DP;                                  // [kHG][DP]
+    bf16* Ps = Qs + kHG * DP;                                   // [kHG][PP]  probabilities (x row scale), bf16
+    float* sc = reinterpret_cast<float*>(Ps + kHG * PP);        // [kTKM] row scales
+    int* s_tok = reinterpret_cast<int*>(sc + kTKM);             // [kTKM]
+    float* s_m = reinterpret_cast<float*>(s_tok + kTKM);        // [kHG] running max
+    float* s_l = s_m + kHG;                                     // [kHG] running sum
+    float* s_alpha = s_l + kHG;                                 // [kHG]
+    float* s_pmax = s_alpha + kHG;                              // [8 warps][kHG]
+    float* s_psum = s_pmax + 8 * kHG;                           // [8 warps][kHG]
+    const int r = blockIdx.x, hg = blockIdx.y, sp = blockIdx.z;
+    const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+    const int g = lane >> 2, tq = lane & 3;                     // fragment row / column-pair index
+    pdl_wait();
+    pdl_launch_dependents();
+    const int seq = p.row_seq[r];
+    int n = p.sel_idx ? p.sel_cnt[r] : p.row_len[r];
+    if (seq < 0) n = 0;
+    const int per = (((n + p.NS - 1) / p.NS) + kTKM - 1) / kTKM * kTKM;
+    const int beg = sp * per, end = min(n, beg + per);
+    for (int i = t; i < kHG * (D / 8); i += blockDim.x) {
+        const int h = i / (D / 8), c = i % (D / 8);
+        const int hh = hg * kHG + h;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (hh < p.H) v = *reinterpret_cast<const uint4*>(p.q + ((size_t)r * p.H + hh) * D + c * 8);
+        *reinterpret_cast<uint4*>(Qs + h * DP + c * 8) = v;
+    }
+    if (t < kHG) { s_m[t] = -INFINITY; s_l[t] = 0.f; }
+    const int ncol = p.dl / 8;                 // latent columns per warp in the PV product (multiple of 8: dl % 64 == 0)
+    const int ntile = ncol / 8;                // n-tiles per warp, <= 8
+    float o[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+    const int rb = kv_row_bytes(p.kv_fmt, p.dl, p.dr);
+    const uint32_t q_addr = smem_addr_u32(Qs) + (uint32_t)((((lane & 7) + ((lane >> 3) & 1) * 8) * DP + (lane >> 4) * 8) * 2);
+    const uint32_t k_addr = smem_addr_u32(Ks) + (uint32_t)(((warp * 8 + (lane & 7)) * DP + ((lane >> 3) & 1) * 8) * 2);
+    const uint32_t p_addr = smem_addr_u32(Ps) + (uint32_t)((((lane & 7) + ((lane >> 3) & 1) * 8) * PP + (lane >> 4) * 8) * 2);
+    const uint32_t v_addr = smem_addr_u32(Ks) + (uint32_t)((((lane & 7) + ((lane >> 3) & 1) * 8) * DP + warp * ncol) * 2);
+    for (int t0 = beg; t0 < end; t0 += kTKM) {
+        __syncthreads();                                       // previous tile fully consumed
+        if (t < kTKM) {
+            const int i = t0 + t;
+            int tok = -1;
+            if (i < end) tok = p.sel_idx ? p.sel_idx[(size_t)r * p.sel_ld + i] : i;
+            s_tok[t] = tok;
+        }
+        __syncthreads();
+        mla_load_tile(p, seq, rb, s_tok, Ks, sc, DP, D, t, blockDim.x, kTKM);
+        __syncthreads();
+        // ---- scores of keys 8 warp .. 8 warp + 7 for the 16 heads ----
+        float cl[4] = {0.f, 0.f, 0.f, 0.f}, cr[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int d = 0; d < p.dl; d += 16) {
+            uint32_t a0, a1, a2, a3, b0, b1;
+            ldsm_x4(q_addr + d * 2, a0, a1, a2, a3);
+            ldsm_x2(k_addr + d * 2, b0, b1);
+            mma_bf16_16816(cl, a0, a1, a2, a3, b0, b1);
+        }
+        for (int d = p.dl; d < D; d += 16) {
+            uint32_t a0, a1, a2, a3, b0, b1;
+            ldsm_x4(q_addr + d * 2, a0, a1, a2, a3);
+            ldsm_x2(k_addr + d * 2, b0, b1);
+            mma_bf16_16816(cr, a0, a1, a2, a3, b0, b1);
+        }
+        // this thread: heads g, g + 8; keys 8 warp + 2 tq, + 1
+        const int key0 = warp * 8 + 2 * tq;
+        const bool v0 = s_tok[key0] >= 0, v1 = s_tok[key0 + 1] >= 0;
+        const float rs0 = sc[key0], rs1 = sc[key0 + 1];
+        float s00 = v0 ? (cl[0] * rs0 + cr[0]) * p.scale : -INFINITY, s01 = v1 ? (cl[1] * rs1 + cr[1]) * p.scale : -INFINITY;
+        float s10 = v0 ? (cl[2] * rs0 + cr[2]) * p.scale : -INFINITY, s11 = v1 ? (cl[3] * rs1 + cr[3]) * p.scale : -INFINITY;
+        float mx0 = fmaxf(s00, s01), mx1 = fmaxf(s10, s11);
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        if (tq == 0) { s_pmax[warp * kHG + g] = mx0; s_pmax[warp * kHG + g + 8] = mx1; }
+        __syncthreads();
+        float m0 = s_m[g], m1 = s_m[g + 8];
+#pragma unroll
+        for (int w = 0; w < 8; ++w) { m0 = fmaxf(m0, s_pmax[w * kHG + g]); m1 = fmaxf(m1, s_pmax[w * kHG + g + 8]); }
+        const float p00 = v0 ? __expf(s00 - m0) : 0.f, p01 = v1 ? __expf(s01 - m0) : 0.f;
+        const float p10 = v0 ? __expf(s10 - m1) : 0.f, p11 = v1 ? __expf(s11 - m1) : 0.f;
+        float l0 = p00 + p01, l1 = p10 + p11;
+        l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+        if (tq == 0) { s_psum[warp * kHG + g] = l0; s_psum[warp * kHG + g + 8] = l1; }
+        // the value row is the scaled latent: fold the row scale into P for the PV product
+        *reinterpret_cast<bf162*>(Ps + g * PP + key0) = __floats2bfloat162_rn(p00 * rs0, p01 * rs1);
+        *reinterpret_cast<bf162*>(Ps + (g + 8) * PP + key0) = __floats2bfloat162_rn(p10 * rs0, p11 * rs1);
+        // every thread holds the new maxima of its two heads; rescale its accumulators
+        const float al0 = (m0 == -INFINITY) ? 1.f : __expf(s_m[g] - m0), al1 = (m1 == -INFINITY) ? 1.f : __expf(s_m[g + 8] - m1);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { o[j][0] *= al0; o[j][1] *= al0; o[j][2] *= al1; o[j][3] *= al1; }
+        __syncthreads();                                       // P and the partial sums are complete; all reads of s_m are done
+        if (t < kHG) {
+            float mm = s_m[t], ll = 0.f;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) { mm = fmaxf(mm, s_pmax[w * kHG + t]); ll += s_psum[w * kHG + t]; }
+            const float a = (mm == -INFINITY) ? 1.f : __expf(s_m[t] - mm);
+            s_l[t] = s_l[t] * a + ll;
+            s_m[t] = mm;
+        }
+        // ---- O += P . V over this warp's latent columns ----
+#pragma unroll
+        for (int ks = 0; ks < kTKM / 16; ++ks) {
+            uint32_t a0, a1, a2, a3;
+            ldsm_x4(p_addr + ks * 32, a0, a1, a2, a3);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if (j < ntile) {
+                    uint32_t b0, b1;
+                    ldsm_x2_trans(v_addr + (uint32_t)((ks * 16 * DP + j * 8) * 2), b0, b1);
+                    mma_bf16_16816(o[j], a0, a1, a2, a3, b0, b1);
+                }
+            }
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        if (j < ntile) {
+            const int col = warp * ncol + j * 8 + 2 * tq;
+            const int h0 = hg * kHG + g, h1 = h0 + 8;
+            if (h0 < p.H) { float* op = p.o_part + (((size_t)r * p.H + h0) * p.NS + sp) * p.dl + col; op[0] = o[j][0]; op[1] = o[j][1]; }
+            if (h1 < p.H) { float* op = p.o_part + (((size_t)r * p.H + h1) * p.NS + sp) * p.dl + col; op[0] = o[j][2]; op[1] = o[j][3]; }
         }
     }
     if (t < kHG && hg * kHG + t < p.H) {
@@ -500,9 +674,15 @@ LSB_API int lsb_mla_decode(const void* q, const void* cache, const void* block_t
     static bool attr_set = false;
     if (!attr_set) {
         cudaFuncSetAttribute(mla_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaFuncSetAttribute(mla_decode_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         attr_set = true;
     }
-    launch_pdl((mla_decode_kernel), dim3(R, (H + kHG - 1) / kHG, NS), 256, smem, st, p);
+    // many rows (prefill chunks, verify batches, large batches): tensor-core variant; few rows: the latency-tuned CUDA-core one
+    if (R >= 16 && dl % 64 == 0 && dl <= 512 && dr % 16 == 0) {
+        launch_pdl((mla_decode_mma_kernel), dim3(R, (H + kHG - 1) / kHG, NS), 256, (size_t)lsb_mla_decode_mma_smem_bytes(dl, dr), st, p);
+    } else {
+        launch_pdl((mla_decode_kernel), dim3(R, (H + kHG - 1) / kHG, NS), 256, smem, st, p);
+    }
     launch_pdl((mla_combine_kernel), dim3(R, H), 128, 0, st, (bf16*)out, (float*)lse, (const float*)o_part, (const float*)ml_part, H, NS, dl);
     LSB_CHECK_LAUNCH();
 }

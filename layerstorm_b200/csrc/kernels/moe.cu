@@ -124,6 +124,51 @@ __global__ void __launch_bounds__(32) router_topk_kernel(const float* __restrict
     pdl_launch_dependents();
 }
 
+// Hash-layer gating (DeepSeek-V4 hash layers): the experts of a row come from a table indexed by the row's token id
+// (tid2eid[token * topk + k], table order kept), the weights are the scores of exactly those experts - no selection
+// bias - optionally renormalised and scaled.  A token id outside the table or a table entry outside [0, E) yields
+// expert -1 with weight 0 (the slot is dropped by the expert kernels).  One warp per row.
+// Reference semantics: src/compute/kernels/moe/hash_gating.h:1-16.
+__global__ void __launch_bounds__(32) router_hash_kernel(const float* __restrict__ logits, const int* __restrict__ tid2eid,
+                                                         const int* __restrict__ token_ids, int* __restrict__ ids, float* __restrict__ wts,
+                                                         int E, int topk, int vocab, int scoring, int norm_topk, float scale, int n_shared,
+                                                         int ld_logits) {
+    const int r = blockIdx.x, lane = threadIdx.x;
+    const float* lg = logits + (size_t)r * ld_logits;
+    pdl_wait();
+    pdl_launch_dependents();
+    float mx = -INFINITY, den = 1.f;
+    if (scoring == kScoreSoftmax) {                  // the only scoring that needs the whole row
+        for (int e = lane; e < E; e += 32) mx = fmaxf(mx, lg[e]);
+        mx = warp_max(mx);
+        float sum = 0.f;
+        for (int e = lane; e < E; e += 32) sum += expf(lg[e] - mx);
+        den = warp_sum(sum);
+    }
+    const int tok = token_ids[r];
+    int id = -1;
+    float w = 0.f;
+    if (lane < topk && tok >= 0 && tok < vocab) {
+        const int e = tid2eid[(size_t)tok * topk + lane];
+        if (e >= 0 && e < E) {
+            const float x = lg[e];
+            id = e;
+            if (scoring == kScoreSigmoid) w = 1.f / (1.f + expf(-x));
+            else if (scoring == kScoreSoftmax) w = expf(x - mx) / den;
+            else w = sqrtf(x > 20.f ? x : log1pf(expf(x)));
+        }
+    }
+    const float tot = warp_sum(w);
+    const int S = topk + n_shared;
+    if (lane < topk) {
+        if (norm_topk) w = w / (tot + 1e-20f);
+        ids[r * S + lane] = id;
+        wts[r * S + lane] = id >= 0 ? w * scale : 0.f;
+    }
+    if (lane < n_shared) { ids[r * S + topk + lane] = E + lane; wts[r * S + topk + lane] = 1.f; }
+    pdl_launch_dependents();
+}
+
 // Groups: for every expert (routed and shared) with at least one (row,slot) pair, its pairs
 // in ascending pair order are cut into groups of <= 4.  Output:
 //   group_expert[g], group_n[g], group_pairs[g*4 + i] (pair = row*S + slot), n_groups[0].
@@ -498,6 +543,15 @@ LSB_API int lsb_router_topk(const void* logits, const void* bias, void* ids, voi
     launch_pdl((router_topk_kernel), rows, 32, (size_t)(2 * E + 64) * 4, (cudaStream_t)stream, (const float*)logits, (const float*)bias, (int*)ids,
                                                                          (float*)wts, E, topk, n_group, topk_group, scoring,
                                                                          norm_topk, scale, n_shared, ld_logits);
+    LSB_CHECK_LAUNCH();
+}
+
+// Hash-layer routing: ids[r][k] = tid2eid[token_ids[r]][k], weights from the logits of those experts.
+LSB_API int lsb_router_hash(const void* logits, const void* tid2eid, const void* token_ids, void* ids, void* wts, int rows, int E, int topk,
+                            int vocab, int scoring, int norm_topk, float scale, int n_shared, int ld_logits, void* stream) {
+    if (topk > 32 || n_shared > 32 || E <= 0) return -1;
+    launch_pdl((router_hash_kernel), rows, 32, 0, (cudaStream_t)stream, (const float*)logits, (const int*)tid2eid, (const int*)token_ids, (int*)ids,
+               (float*)wts, E, topk, vocab, scoring, norm_topk, scale, n_shared, ld_logits);
     LSB_CHECK_LAUNCH();
 }
 

@@ -443,6 +443,21 @@ __global__ void mhc_contract_norm_kernel(bf16* __restrict__ out, const float* __
     pdl_launch_dependents();
 }
 
+
+// Producer half of the in-kernel all-reduce for partials that a kernel without a fused epilogue has already written to
+// local memory: stores x[m][n] (fp32, row stride ld) into slot[this rank] of every rank's receive buffer and publishes
+// the epoch.  The consumer (add_rmsnorm / mHC kernels with `comm`) sums the slots in rank order.
+__global__ void __launch_bounds__(256) comm_push_rows_kernel(const float* __restrict__ x, int ld, int N, long long total, PeerComm c) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const unsigned next_epoch = *c.epoch + 1u;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long m = i / N;
+        comm_push(c, next_epoch, (size_t)i, x[m * ld + (i - m * N)]);
+    }
+    comm_signal(c, next_epoch, gridDim.x);
+    pdl_launch_dependents();
+}
 }  // namespace lsb
 using namespace lsb;
 
@@ -451,6 +466,17 @@ static PeerComm comm_from_host(const void* h) {
     c.nranks = 0;
     if (h) c = *reinterpret_cast<const PeerComm*>(h);
     return c;
+}
+
+// Push a locally computed fp32 partial [M, N] (row stride ld) as this rank's contribution to the next all-reduce epoch.
+LSB_API int lsb_comm_push_rows(const void* x, int M, int N, int ld, const void* comm, void* stream) {
+    if (!comm) return -1;
+    const PeerComm c = comm_from_host(comm);
+    const long long total = (long long)M * N;
+    if (c.nranks <= 0 || total > c.cap) return -2;
+    const int grid = (int)((total + 256 * 8 - 1) / (256 * 8) < 592 ? (total + 256 * 8 - 1) / (256 * 8) : 592);
+    launch_pdl((comm_push_rows_kernel), grid > 0 ? grid : 1, 256, 0, (cudaStream_t)stream, (const float*)x, ld, N, total, c);
+    LSB_CHECK_LAUNCH();
 }
 
 LSB_API int lsb_rmsnorm(void* out, const void* x, const void* w, int rows, int dim, int ldx, int ldo, float eps,

@@ -213,7 +213,12 @@ class QLinear:
         ldo = ldo if ldo is not None else self.N
         ob = 1 if out.dtype == torch.bfloat16 else 0
         if comm is not None and M not in (1, 2, 4) and not (self.fmt == "bf16" and M >= 8 and bias is None and not ob):
-            raise RuntimeError("the fused all-reduce epilogue covers 1, 2 or 4 rows (GEMV) or >= 8 rows of a bf16 layer (GEMM)")
+            # no fused epilogue for this shape / format: compute the partial locally, then push it to the peers with a copy kernel
+            if ob:
+                raise RuntimeError("the cross-rank reduction needs an fp32 partial")
+            self(out, x, M, ldx, ldo, bias, None)
+            nat.call("lsb_comm_push_rows", out, M, self.N, ldo, comm)
+            return
         if self.fmt == "bf16" and M >= 8:
             sc = TcScratch.get(self.w.device)
             nat.call("lsb_gemm_bf16_tc", out, x, self.w, bias, M, self.N, self.K, ldx, self.K, ldo, ob, sc.partial, sc.cap, sc.err, comm)
@@ -870,7 +875,9 @@ class DeviceModel:
         H, n = cfg.hidden, cfg.hc_mult
         # fused in-kernel all-reduce: GEMV epilogues cover 1, 2 or 4 rows; the tcgen05 GEMM epilogue covers any larger
         # step with bf16 dense weights, as long as the step fits the peers' receive slots
-        self._fused = self.comm is not None and (R in (1, 2, 4) or (R >= 8 and cfg.dense_quant == "bf16" and R * H <= self.comm.cap))
+        # in-kernel NVLink all-reduce whenever the partial fits the peer buffers (fused GEMV / GEMM epilogues where they exist,
+        # a push kernel after the layer otherwise); NCCL only beyond that
+        self._fused = self.comm is not None and R * H <= self.comm.cap
         if cfg.mhc:
             nat.call("lsb_embedding", ws.sub, None, self.embed, ws.tok, R, H, 0, cfg.vocab)
             for i, L in enumerate(self.layers):

@@ -80,6 +80,27 @@ def route(cfg: ModelConfig, logits, bias):
     return ids, w * cfg.routed_scale
 
 
+def route_hash(cfg: ModelConfig, logits, tid2eid, token_ids):
+    """Hash-layer routing (DeepSeek-V4): the experts of a row are the table row of its token id (table order), the
+    weights the scores of those experts without selection bias.  Entries outside the table or the expert range give
+    id -1 / weight 0.  Reference semantics: src/compute/kernels/moe/hash_gating.h:1-16."""
+    if cfg.scoring == "sigmoid":
+        score = torch.sigmoid(logits)
+    elif cfg.scoring == "softmax":
+        score = torch.softmax(logits, -1)
+    else:
+        score = torch.sqrt(torch.nn.functional.softplus(logits))
+    T, E = score.shape
+    tok = token_ids.long()
+    ok_tok = (tok >= 0) & (tok < tid2eid.shape[0])
+    ids = tid2eid[tok.clamp(0, tid2eid.shape[0] - 1)].long()
+    ok = ok_tok[:, None] & (ids >= 0) & (ids < E)
+    w = torch.where(ok, torch.gather(score, 1, ids.clamp(0, E - 1)), torch.zeros(()))
+    if cfg.norm_topk_prob:
+        w = w / (w.sum(-1, keepdim=True) + 1e-20)
+    return torch.where(ok, ids, torch.full_like(ids, -1)), w * cfg.routed_scale
+
+
 class Oracle:
     def __init__(self, cfg: ModelConfig, weights: Dict[str, torch.Tensor]):
         self.cfg = cfg

@@ -46,6 +46,21 @@ def main():
             print(f"graph={use_graph} tokens_match={good} comm_err={err} backend={comm.buf.backend} epochs={comm.epoch()}", flush=True)
         ok = ok and good and err == 0
         eng.free_sequence(sid)
+    # three sequences decoded together: 3 rows have no fused GEMV epilogue, the partials go through the push kernel
+    seqs = [torch.randint(0, cfg.vocab, (12 + 5,), generator=torch.Generator().manual_seed(40 + b)) for b in range(3)]
+    refs = [oracle.forward(s_) for s_ in seqs]
+    eng = Engine(m, max_seqs=3, max_ctx=128, prefill_chunk=8, max_batch=3, use_graph=True)
+    sids = [eng.create_sequence() for _ in range(3)]
+    good = True
+    for sid, s_, r_ in zip(sids, seqs, refs):
+        good = good and eng.prefill(sid, s_[:12].tolist()) == int(r_[11].argmax())
+    for j in range(5):
+        out = eng.decode(sids, [int(s_[12 + j]) for s_ in seqs])
+        good = good and all(o == int(r_[12 + j].argmax()) for o, r_ in zip(out, refs))
+    err = comm.error() or comm_amax.error()
+    if rank == 0:
+        print(f"batch3 tokens_match={good} comm_err={err}", flush=True)
+    ok = ok and good and err == 0
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     if rank == 0:

@@ -137,6 +137,66 @@ def test_router_topk(scoring, n_group, topk_group):
     assert (ids[:, k] == E).all() and (wts[:, k] == 1).all()
 
 
+@pytest.mark.parametrize("scoring", ["sigmoid", "softmax", "sqrtsoftplus"])
+def test_router_hash(scoring):
+    E, k, R, V = 48, 6, 7, 100
+    cfg = ModelConfig(n_routed=E, top_k=k, scoring=scoring, routed_scale=1.5)
+    logits = rnd(R, E)
+    g = torch.Generator().manual_seed(3)
+    table = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(V)]).int()
+    table[5, 2] = E + 3                     # entry outside the expert range -> dropped slot
+    toks = torch.tensor([0, 5, 17, 99, 100, 42, 5], dtype=torch.int32)    # 100 is outside the table
+    ids = torch.zeros(R, k + 1, dtype=torch.int32, device=DEV)
+    wts = torch.zeros(R, k + 1, device=DEV)
+    nat.call("lsb_router_hash", logits, table.to(DEV), toks.to(DEV), ids, wts, R, E, k, V,
+             {"sigmoid": 0, "softmax": 1, "sqrtsoftplus": 2}[scoring], 1, 1.5, 1, E)
+    torch.cuda.synchronize()
+    rid, rw = ref.route_hash(cfg, logits.cpu(), table, toks)
+    assert torch.equal(ids[:, :k].cpu().long(), rid), (ids.cpu(), rid)
+    close(wts[:, :k], rw, 1e-4, 1e-6, "hash router weights")
+    assert (ids[4, :k] == -1).all() and (wts[4, :k] == 0).all() and int(ids[1, 2]) == -1
+    assert (ids[:, k] == E).all() and (wts[:, k] == 1).all()
+
+
+@pytest.mark.parametrize("R,sparse", [(4, False), (20, False), (20, True), (33, True)])
+def test_mla_decode_attention(R, sparse):
+    """Absorbed MLA attention over a paged bf16 cache against an fp32 reference; R >= 16 takes the tensor-core
+    (mma) variant, smaller R the CUDA-core one; sparse = per-row selected positions (the indexer's output)."""
+    H, dl, dr, page, NS = 24, 128, 16, 16, 2
+    D = dl + dr
+    n_seq, max_pages, ctx = 2, 8, 100
+    g = torch.Generator().manual_seed(11)
+    cache = (torch.randn(n_seq * max_pages * page, D, generator=g) * 0.5).to(torch.bfloat16)
+    bt = torch.arange(n_seq * max_pages, dtype=torch.int32).view(n_seq, max_pages).flip(1).contiguous()   # pages out of order
+    q = (torch.randn(R, H, D, generator=g) * 0.5).to(torch.bfloat16)
+    row_seq = torch.tensor([i % n_seq for i in range(R)], dtype=torch.int32)
+    row_len = torch.tensor([1 + (7 * i) % ctx for i in range(R)], dtype=torch.int32)
+    sel_ld = 48
+    sel_idx = torch.full((R, sel_ld), -1, dtype=torch.int32)
+    sel_cnt = torch.zeros(R, dtype=torch.int32)
+    if sparse:
+        for i in range(R):
+            n = int(row_len[i])
+            pick = torch.randperm(n, generator=g)[: min(n, 5 + (3 * i) % 40)]
+            sel_idx[i, : len(pick)] = pick.int()
+            sel_cnt[i] = len(pick)
+    out = torch.zeros(R, H, dl, dtype=torch.bfloat16, device=DEV)
+    o_part = torch.zeros(R, H, NS, dl, device=DEV)
+    ml_part = torch.zeros(R, H, NS, 2, device=DEV)
+    scale = D ** -0.5
+    nat.call("lsb_mla_decode", q.to(DEV), cache.to(DEV).view(torch.uint8), bt.to(DEV), max_pages, row_seq.to(DEV), row_len.to(DEV),
+             sel_idx.to(DEV) if sparse else None, sel_cnt.to(DEV) if sparse else None, sel_ld if sparse else 0, out, None, o_part, ml_part,
+             R, H, dl, dr, page, 0, NS, scale, None)
+    torch.cuda.synchronize()
+    cf, qf = cache.float(), q.float()
+    for i in range(R):
+        pos = sel_idx[i, : int(sel_cnt[i])].long() if sparse else torch.arange(int(row_len[i]))
+        rows = bt[int(row_seq[i])].long()[pos // page] * page + pos % page
+        k = cf[rows]
+        pr = torch.softmax(qf[i] @ k.T * scale, -1)
+        close(out[i], pr @ k[:, :dl], 2e-2, 2e-2, f"mla attention row {i}")
+
+
 def test_sampling_kernels():
     R, V = 4, 5000
     logits = rnd(R, V, s=3.0)

@@ -130,6 +130,91 @@ __global__ void __launch_bounds__(128) mhc_post_partial_kernel(float* __restrict
     pdl_launch_dependents();
 }
 
+// Many-row variant of the pass above: a block covers 128 hidden columns (4 consecutive columns per lane, 16-byte
+// loads and stores), so the 25 warp reductions per (row, block) amortise over four times the columns - with 2048-row
+// prefill chunks the narrow kernel is bound by its shuffles, not by memory.  part[r][chunk128][0..24].
+constexpr int kHcWide = 128;
+__global__ void __launch_bounds__(128) mhc_post_partial_wide_kernel(float* __restrict__ residual, const float* __restrict__ x,
+                                                                    const float* __restrict__ post, const float* __restrict__ comb,
+                                                                    const float* __restrict__ fn, float* __restrict__ part,
+                                                                    int hidden, int n, int mode, int rows, int rows_per_block, PeerComm comm) {
+    const int c = blockIdx.y, lane = threadIdx.x & 31, og = threadIdx.x >> 5;
+    const int h = c * kHcWide + lane * 4;
+    const int nout = 2 * n + n * n;
+    float4 f[kHcPerWarp][kHcMax];
+#pragma unroll
+    for (int i = 0; i < kHcPerWarp; ++i) {
+        const int o = og * kHcPerWarp + i;
+#pragma unroll
+        for (int j = 0; j < kHcMax; ++j)
+            f[i][j] = (o < nout && j < n) ? __ldg(reinterpret_cast<const float4*>(fn + ((size_t)o * n + j) * hidden + h)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    pdl_wait();
+    pdl_launch_dependents();
+    unsigned epoch = 0;
+    if (comm.nranks && mode == 1) {
+        epoch = *comm.epoch;
+        comm_wait(comm, epoch);
+    }
+    for (int r = blockIdx.x * rows_per_block; r < min(rows, (int)(blockIdx.x + 1) * rows_per_block); ++r) {
+        float4 res[kHcMax];
+        float* rp = residual + (size_t)r * n * hidden;
+        float4 xv;
+        if (comm.nranks && mode == 1) {
+            const size_t b = (size_t)r * hidden + h;
+            xv = make_float4(comm_reduce(comm, epoch, b), comm_reduce(comm, epoch, b + 1), comm_reduce(comm, epoch, b + 2), comm_reduce(comm, epoch, b + 3));
+        } else {
+            xv = *reinterpret_cast<const float4*>(x + (size_t)r * hidden + h);
+        }
+        if (mode == 0) {
+#pragma unroll
+            for (int j = 0; j < kHcMax; ++j) res[j] = j < n ? xv : make_float4(0.f, 0.f, 0.f, 0.f);
+        } else {
+            float4 old[kHcMax];
+#pragma unroll
+            for (int i = 0; i < kHcMax; ++i) old[i] = i < n ? *reinterpret_cast<const float4*>(rp + (size_t)i * hidden + h) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int j = 0; j < kHcMax; ++j) {
+                float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (j < n) {
+                    const float pj = post[r * n + j];
+                    a = make_float4(pj * xv.x, pj * xv.y, pj * xv.z, pj * xv.w);
+                    for (int i = 0; i < n; ++i) {
+                        const float cj = comb[(r * n + i) * n + j];
+                        a.x += cj * old[i].x; a.y += cj * old[i].y; a.z += cj * old[i].z; a.w += cj * old[i].w;
+                    }
+                }
+                res[j] = a;
+            }
+        }
+        float* po = part + ((size_t)r * gridDim.y + c) * (kHcOut + 1);
+#pragma unroll
+        for (int i = 0; i < kHcPerWarp; ++i) {
+            float a = 0.f;
+#pragma unroll
+            for (int j = 0; j < kHcMax; ++j) {
+                a = fmaf(res[j].x, f[i][j].x, a); a = fmaf(res[j].y, f[i][j].y, a);
+                a = fmaf(res[j].z, f[i][j].z, a); a = fmaf(res[j].w, f[i][j].w, a);
+            }
+            a = warp_sum(a);
+            const int o = og * kHcPerWarp + i;
+            if (lane == 0 && o < kHcOut) po[o] = a;
+        }
+        if (og == 0) {
+            float ss = 0.f;
+#pragma unroll
+            for (int j = 0; j < kHcMax; ++j)
+                if (j < n) {
+                    *reinterpret_cast<float4*>(rp + (size_t)j * hidden + h) = res[j];
+                    ss += res[j].x * res[j].x + res[j].y * res[j].y + res[j].z * res[j].z + res[j].w * res[j].w;
+                }
+            ss = warp_sum(ss);
+            if (lane == 0) po[kHcOut] = ss;
+        }
+    }
+    pdl_launch_dependents();
+}
+
 // Pass 2: reduce the partials in a fixed order, form pre/post gates and the Sinkhorn-
 // normalised mixing matrix (one matrix element per lane, sums by shuffles), then
 // out = RMSNorm(sum_j pre[j]*residual[j]) * w (bf16).
@@ -524,11 +609,18 @@ LSB_API int lsb_mhc_post_pre(void* out_x, void* residual, const void* x, void* p
         LSB_CHECK_LAUNCH();
     }
     const int rpb = rows >= 64 ? 16 : 1;      // many rows: amortise the mixing-matrix loads over 16 rows per block
-    launch_pdl((mhc_post_partial_kernel), dim3((rows + rpb - 1) / rpb, nchunks), 128, 0, st, (float*)residual, (const float*)x, (const float*)post,
-                                                                    (const float*)comb, (const float*)fn, (float*)part, hidden, n, mode, rows, rpb, comm_from_host(comm));
+    int nparts = nchunks;
+    if (rows >= 64 && hidden % kHcWide == 0) {
+        nparts = hidden / kHcWide;
+        launch_pdl((mhc_post_partial_wide_kernel), dim3((rows + rpb - 1) / rpb, nparts), 128, 0, st, (float*)residual, (const float*)x, (const float*)post,
+                   (const float*)comb, (const float*)fn, (float*)part, hidden, n, mode, rows, rpb, comm_from_host(comm));
+    } else {
+        launch_pdl((mhc_post_partial_kernel), dim3((rows + rpb - 1) / rpb, nchunks), 128, 0, st, (float*)residual, (const float*)x, (const float*)post,
+                   (const float*)comb, (const float*)fn, (float*)part, hidden, n, mode, rows, rpb, comm_from_host(comm));
+    }
     launch_pdl((mhc_finalize_kernel), rows, 512, (size_t)hidden * 4, st, (bf16*)out_x, (const float*)residual, (const float*)part,
                                                               (const float*)hc_scale, (const float*)hc_base, (const float*)norm_w,
-                                                              (float*)post, (float*)comb, hidden, n, nchunks, iters, hc_eps, rms_eps, post_mult);
+                                                              (float*)post, (float*)comb, hidden, n, nparts, iters, hc_eps, rms_eps, post_mult);
     LSB_CHECK_LAUNCH();
 }
 

@@ -558,6 +558,174 @@ __global__ void __launch_bounds__(256) mla_decode_mma_kernel(MlaDecodeParams p) 
     pdl_launch_dependents();
 }
 
+// Head-group-shared variant: one block serves NG groups of 16 heads of a query row (4 warps per group), so a K tile is
+// gathered and de-quantised once per row instead of once per 16 heads.  Per group: warp s of 4 owns keys 16 s .. 16 s + 15
+// (two n-tiles) in the score product and dl / 4 latent columns in the value product.
+template <int NG>
+__global__ void __launch_bounds__(NG * 128) mla_decode_mma_shared_kernel(MlaDecodeParams p) {
+    extern __shared__ __align__(16) uint8_t smraw[];
+    constexpr int NH = NG * kHG;               // heads per block
+    const int D = p.dl + p.dr, DP = D + 8;
+    constexpr int PP = kTKM + 8;
+    bf16* Ks = reinterpret_cast<bf16*>(smraw);                 // [kTKM][DP]
+    bf16* Qs = Ks + kTKM * DP;                                  // [NH][DP]
+    bf16* Ps = Qs + NH * DP;                                    // [NH][PP]
+    float* sc = reinterpret_cast<float*>(Ps + NH * PP);         // [kTKM]
+    int* s_tok = reinterpret_cast<int*>(sc + kTKM);             // [kTKM]
+    float* s_m = reinterpret_cast<float*>(s_tok + kTKM);        // [NH]
+    float* s_l = s_m + NH;                                      // [NH]
+    float* s_pmax = s_l + NH;                                   // [4][NH]
+    float* s_psum = s_pmax + 4 * NH;                            // [4][NH]
+    const int r = blockIdx.x, hb = blockIdx.y * NH, sp = blockIdx.z;
+    const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+    const int grp = warp >> 2, sw = warp & 3;                   // head group inside the block, warp inside the group
+    const int g = lane >> 2, tq = lane & 3;
+    const int hl0 = grp * kHG + g, hl1 = hl0 + 8;               // this thread's two heads (block-local)
+    pdl_wait();
+    pdl_launch_dependents();
+    const int seq = p.row_seq[r];
+    int n = p.sel_idx ? p.sel_cnt[r] : p.row_len[r];
+    if (seq < 0) n = 0;
+    const int per = (((n + p.NS - 1) / p.NS) + kTKM - 1) / kTKM * kTKM;
+    const int beg = sp * per, end = min(n, beg + per);
+    for (int i = t; i < NH * (D / 8); i += blockDim.x) {
+        const int h = i / (D / 8), c = i % (D / 8);
+        const int hh = hb + h;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (hh < p.H) v = *reinterpret_cast<const uint4*>(p.q + ((size_t)r * p.H + hh) * D + c * 8);
+        *reinterpret_cast<uint4*>(Qs + h * DP + c * 8) = v;
+    }
+    if (t < NH) { s_m[t] = -INFINITY; s_l[t] = 0.f; }
+    const int ncol = p.dl / 4;                 // latent columns per warp in the PV product (multiple of 16: dl % 64 == 0)
+    const int ntile = ncol / 8;                // n-tiles per warp, <= 16
+    float o[16][4];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+    const int rb = kv_row_bytes(p.kv_fmt, p.dl, p.dr);
+    const int arow = (lane & 7) + ((lane >> 3) & 1) * 8;        // ldmatrix.x4 row of an A tile
+    const uint32_t q_addr = smem_addr_u32(Qs) + (uint32_t)(((grp * kHG + arow) * DP + (lane >> 4) * 8) * 2);
+    const uint32_t k_addr = smem_addr_u32(Ks) + (uint32_t)(((sw * 16 + (lane & 7)) * DP + ((lane >> 3) & 1) * 8) * 2);
+    const uint32_t p_addr = smem_addr_u32(Ps) + (uint32_t)(((grp * kHG + arow) * PP + (lane >> 4) * 8) * 2);
+    const uint32_t v_addr = smem_addr_u32(Ks) + (uint32_t)((arow * DP + sw * ncol) * 2);
+    for (int t0 = beg; t0 < end; t0 += kTKM) {
+        __syncthreads();
+        if (t < kTKM) {
+            const int i = t0 + t;
+            int tok = -1;
+            if (i < end) tok = p.sel_idx ? p.sel_idx[(size_t)r * p.sel_ld + i] : i;
+            s_tok[t] = tok;
+        }
+        __syncthreads();
+        mla_load_tile(p, seq, rb, s_tok, Ks, sc, DP, D, t, blockDim.x, kTKM);
+        __syncthreads();
+        // ---- scores: keys 16 sw .. 16 sw + 15 (n-tiles u = 0, 1) for this group's 16 heads ----
+        float cl[2][4], cr[2][4];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) { cl[u][0] = cl[u][1] = cl[u][2] = cl[u][3] = 0.f; cr[u][0] = cr[u][1] = cr[u][2] = cr[u][3] = 0.f; }
+        for (int d = 0; d < p.dl; d += 16) {
+            uint32_t a0, a1, a2, a3, b0, b1;
+            ldsm_x4(q_addr + d * 2, a0, a1, a2, a3);
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                ldsm_x2(k_addr + (uint32_t)((u * 8 * DP + d) * 2), b0, b1);
+                mma_bf16_16816(cl[u], a0, a1, a2, a3, b0, b1);
+            }
+        }
+        for (int d = p.dl; d < D; d += 16) {
+            uint32_t a0, a1, a2, a3, b0, b1;
+            ldsm_x4(q_addr + d * 2, a0, a1, a2, a3);
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                ldsm_x2(k_addr + (uint32_t)((u * 8 * DP + d) * 2), b0, b1);
+                mma_bf16_16816(cr[u], a0, a1, a2, a3, b0, b1);
+            }
+        }
+        float s[2][4];                                         // [n-tile][head g: keys 2tq, 2tq+1; head g+8: same keys]
+        bool vld[2][2];
+        float rsv[2][2];
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int key0 = sw * 16 + u * 8 + 2 * tq;
+            vld[u][0] = s_tok[key0] >= 0; vld[u][1] = s_tok[key0 + 1] >= 0;
+            rsv[u][0] = sc[key0]; rsv[u][1] = sc[key0 + 1];
+            s[u][0] = vld[u][0] ? (cl[u][0] * rsv[u][0] + cr[u][0]) * p.scale : -INFINITY;
+            s[u][1] = vld[u][1] ? (cl[u][1] * rsv[u][1] + cr[u][1]) * p.scale : -INFINITY;
+            s[u][2] = vld[u][0] ? (cl[u][2] * rsv[u][0] + cr[u][2]) * p.scale : -INFINITY;
+            s[u][3] = vld[u][1] ? (cl[u][3] * rsv[u][1] + cr[u][3]) * p.scale : -INFINITY;
+            mx0 = fmaxf(mx0, fmaxf(s[u][0], s[u][1]));
+            mx1 = fmaxf(mx1, fmaxf(s[u][2], s[u][3]));
+        }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        if (tq == 0) { s_pmax[sw * NH + hl0] = mx0; s_pmax[sw * NH + hl1] = mx1; }
+        __syncthreads();
+        float m0 = s_m[hl0], m1 = s_m[hl1];
+#pragma unroll
+        for (int w = 0; w < 4; ++w) { m0 = fmaxf(m0, s_pmax[w * NH + hl0]); m1 = fmaxf(m1, s_pmax[w * NH + hl1]); }
+        float l0 = 0.f, l1 = 0.f;
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int key0 = sw * 16 + u * 8 + 2 * tq;
+            const float p00 = vld[u][0] ? __expf(s[u][0] - m0) : 0.f, p01 = vld[u][1] ? __expf(s[u][1] - m0) : 0.f;
+            const float p10 = vld[u][0] ? __expf(s[u][2] - m1) : 0.f, p11 = vld[u][1] ? __expf(s[u][3] - m1) : 0.f;
+            l0 += p00 + p01; l1 += p10 + p11;
+            // the value row is the scaled latent: fold the row scale into P for the PV product
+            *reinterpret_cast<bf162*>(Ps + hl0 * PP + key0) = __floats2bfloat162_rn(p00 * rsv[u][0], p01 * rsv[u][1]);
+            *reinterpret_cast<bf162*>(Ps + hl1 * PP + key0) = __floats2bfloat162_rn(p10 * rsv[u][0], p11 * rsv[u][1]);
+        }
+        l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+        if (tq == 0) { s_psum[sw * NH + hl0] = l0; s_psum[sw * NH + hl1] = l1; }
+        const float al0 = (m0 == -INFINITY) ? 1.f : __expf(s_m[hl0] - m0), al1 = (m1 == -INFINITY) ? 1.f : __expf(s_m[hl1] - m1);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) { o[j][0] *= al0; o[j][1] *= al0; o[j][2] *= al1; o[j][3] *= al1; }
+        __syncthreads();                                       // P and the partial sums are complete; all reads of s_m are done
+        if (t < NH) {
+            float mm = s_m[t], ll = 0.f;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) { mm = fmaxf(mm, s_pmax[w * NH + t]); ll += s_psum[w * NH + t]; }
+            const float a = (mm == -INFINITY) ? 1.f : __expf(s_m[t] - mm);
+            s_l[t] = s_l[t] * a + ll;
+            s_m[t] = mm;
+        }
+        // ---- O += P . V over this warp's latent columns ----
+#pragma unroll
+        for (int ks = 0; ks < kTKM / 16; ++ks) {
+            uint32_t a0, a1, a2, a3;
+            ldsm_x4(p_addr + ks * 32, a0, a1, a2, a3);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                if (j < ntile) {
+                    uint32_t b0, b1;
+                    ldsm_x2_trans(v_addr + (uint32_t)((ks * 16 * DP + j * 8) * 2), b0, b1);
+                    mma_bf16_16816(o[j], a0, a1, a2, a3, b0, b1);
+                }
+            }
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        if (j < ntile) {
+            const int col = sw * ncol + j * 8 + 2 * tq;
+            const int h0 = hb + hl0, h1 = hb + hl1;
+            if (h0 < p.H) { float* op = p.o_part + (((size_t)r * p.H + h0) * p.NS + sp) * p.dl + col; op[0] = o[j][0]; op[1] = o[j][1]; }
+            if (h1 < p.H) { float* op = p.o_part + (((size_t)r * p.H + h1) * p.NS + sp) * p.dl + col; op[0] = o[j][2]; op[1] = o[j][3]; }
+        }
+    }
+    if (t < NH && hb + t < p.H) {
+        float* ml = p.ml_part + (((size_t)r * p.H + hb + t) * p.NS + sp) * 2;
+        ml[0] = s_m[t]; ml[1] = s_l[t];
+    }
+    pdl_launch_dependents();
+}
+
+static int mla_mma_shared_smem_bytes(int dl, int dr, int ng) {
+    const int DP = dl + dr + 8, NH = ng * kHG;
+    return (kTKM + NH) * DP * 2 + NH * (kTKM + 8) * 2 + kTKM * 4 + kTKM * 4 + (2 * NH + 8 * NH) * 4;
+}
+
 // Merge split partials in split order: out = sum_s exp(m_s - M) acc_s / sum_s exp(m_s - M) l_s.  NS <= 32.
 __global__ void __launch_bounds__(128) mla_combine_kernel(bf16* __restrict__ out, float* __restrict__ lse, const float* __restrict__ o_part,
                                                           const float* __restrict__ ml_part, int H, int NS, int dl) {
@@ -675,11 +843,19 @@ LSB_API int lsb_mla_decode(const void* q, const void* cache, const void* block_t
     if (!attr_set) {
         cudaFuncSetAttribute(mla_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         cudaFuncSetAttribute(mla_decode_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaFuncSetAttribute(mla_decode_mma_shared_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaFuncSetAttribute(mla_decode_mma_shared_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         attr_set = true;
     }
     // many rows (prefill chunks, verify batches, large batches): tensor-core variant; few rows: the latency-tuned CUDA-core one
     if (R >= 16 && dl % 64 == 0 && dl <= 512 && dr % 16 == 0) {
-        launch_pdl((mla_decode_mma_kernel), dim3(R, (H + kHG - 1) / kHG, NS), 256, (size_t)lsb_mla_decode_mma_smem_bytes(dl, dr), st, p);
+        // more than one 16-head group per query row: the groups of a row share each gathered K tile
+        if (H > 2 * kHG && mla_mma_shared_smem_bytes(dl, dr, 4) <= 200 * 1024)
+            launch_pdl((mla_decode_mma_shared_kernel<4>), dim3(R, (H + 4 * kHG - 1) / (4 * kHG), NS), 512, (size_t)mla_mma_shared_smem_bytes(dl, dr, 4), st, p);
+        else if (H > kHG && mla_mma_shared_smem_bytes(dl, dr, 2) <= 200 * 1024)
+            launch_pdl((mla_decode_mma_shared_kernel<2>), dim3(R, (H + 2 * kHG - 1) / (2 * kHG), NS), 256, (size_t)mla_mma_shared_smem_bytes(dl, dr, 2), st, p);
+        else
+            launch_pdl((mla_decode_mma_kernel), dim3(R, (H + kHG - 1) / kHG, NS), 256, (size_t)lsb_mla_decode_mma_smem_bytes(dl, dr), st, p);
     } else {
         launch_pdl((mla_decode_kernel), dim3(R, (H + kHG - 1) / kHG, NS), 256, smem, st, p);
     }

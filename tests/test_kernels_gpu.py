@@ -158,11 +158,11 @@ def test_router_hash(scoring):
     assert (ids[:, k] == E).all() and (wts[:, k] == 1).all()
 
 
-@pytest.mark.parametrize("R,sparse", [(4, False), (20, False), (20, True), (33, True)])
-def test_mla_decode_attention(R, sparse):
+@pytest.mark.parametrize("R,sparse,H", [(4, False, 24), (20, False, 24), (20, True, 24), (33, True, 24), (18, True, 12), (20, True, 72)])
+def test_mla_decode_attention(R, sparse, H):
     """Absorbed MLA attention over a paged bf16 cache against an fp32 reference; R >= 16 takes the tensor-core
     (mma) variant, smaller R the CUDA-core one; sparse = per-row selected positions (the indexer's output)."""
-    H, dl, dr, page, NS = 24, 128, 16, 16, 2
+    dl, dr, page, NS = 128, 16, 16, 2           # 12 heads: one 16-head group; 24: two share a K tile; 72: four + a partial block
     D = dl + dr
     n_seq, max_pages, ctx = 2, 8, 100
     g = torch.Generator().manual_seed(11)

@@ -25,7 +25,7 @@ def main():
     cfg = get_preset(name)
     w = round_weights_bf16(init_weights(cfg, 0))
     m = DeviceModel.from_state_dict(cfg, w, dev, kv_fmt="bf16", page=16, tp_rank=rank, tp_size=world)
-    comm = PeerComm(16 * cfg.hidden, dev)       # 16 rows: the 8-row prefill chunks go through the fused GEMM epilogue
+    comm = PeerComm(64 * cfg.hidden, dev)       # 64 rows: 8-row prefill chunks (fused GEMM epilogue) and one 64-row chunk (many-row kernels)
     comm_amax = PeerComm(64, dev)
     m.attach_comm(comm, comm_amax)
     oracle = Oracle(cfg, w)
@@ -60,6 +60,16 @@ def main():
     err = comm.error() or comm_amax.error()
     if rank == 0:
         print(f"batch3 tokens_match={good} comm_err={err}", flush=True)
+    ok = ok and good and err == 0
+    # one 64-row prefill chunk: the many-row kernels (wide mHC partials, tensor-core attention) consume the cross-rank sums
+    long_ids = torch.randint(0, cfg.vocab, (80,), generator=torch.Generator().manual_seed(77))
+    long_ref = oracle.forward(long_ids)
+    eng = Engine(m, max_seqs=1, max_ctx=128, prefill_chunk=64, max_batch=1, use_graph=False)
+    sid = eng.create_sequence()
+    good = eng.prefill(sid, long_ids.tolist()) == int(long_ref[79].argmax())
+    err = comm.error() or comm_amax.error()
+    if rank == 0:
+        print(f"chunk64 tokens_match={good} comm_err={err}", flush=True)
     ok = ok and good and err == 0
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)

@@ -81,10 +81,10 @@ def test_rmsnorm_and_add():
     close(out, ref.rmsnorm((r0 + x).cpu(), w.cpu(), 1e-6), 1e-2, 1e-2, "add_rmsnorm")
 
 
-@pytest.mark.parametrize("fused", [False, True])
-def test_mhc_post_pre_and_contract(fused):
+@pytest.mark.parametrize("fused,R", [(False, 3), (True, 3), (False, 70)])     # 70 rows: the wide many-row partial kernel
+def test_mhc_post_pre_and_contract(fused, R):
     cfg = get_preset("tiny-glm5-next")
-    R, H, n = 3, cfg.hidden, cfg.hc_mult
+    H, n = cfg.hidden, cfg.hc_mult
     o = ref.Oracle(cfg, {})
     fn, sc, base, nw = rnd(24, n * H, s=0.05), torch.tensor([0.7, 1.1, 1.3], device=DEV), rnd(24, s=0.5), rnd(H) * 0.1 + 1
     emb = rnd(R, H)

@@ -133,7 +133,29 @@ constexpr int kTCH = 8;       // tokens per shared-memory pipeline stage
 struct KdaScratch {
     float* qn; float* kn; float* vo; float* decay; float* gate;   // [rows, C]  (vo: v in, o out)
     float* beta;                                                    // [rows, H]
+    // optional: the two low-rank gate products of every row, computed beforehand by the tensor-core GEMM
+    // (raw_g = f_a . f_b^T, g2 = g_a . g_b^T, [rows, C]); null = the prep kernel computes them itself
+    const float* rawg; const float* g2;
 };
+
+// fp32 low-rank activations -> bf16 (hi | lo) pairs, so that the bf16 tensor-core product with the duplicated weight
+// [W | W] reproduces the fp32-activation product to ~2^-16: xs[row][which][0..rank) = hi, [rank..2 rank) = v - hi.
+__global__ void __launch_bounds__(128) kda_split_kernel(const float* __restrict__ proj, int ldp, int off_fa, int off_ga, int rank,
+                                                        bf16* __restrict__ xs) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int row = blockIdx.x;
+    const float* pr = proj + (size_t)row * ldp;
+    for (int j = threadIdx.x; j < 2 * rank; j += blockDim.x) {
+        const int which = j / rank, jj = j - which * rank;
+        const float v = pr[(which ? off_ga : off_fa) + jj];
+        const bf16 hi = __float2bfloat16(v);
+        bf16* o = xs + ((size_t)row * 2 + which) * 2 * rank;
+        o[jj] = hi;
+        o[rank + jj] = __float2bfloat16(v - __bfloat162float(hi));
+    }
+    pdl_launch_dependents();
+}
 
 constexpr int kPrepRows = 16;   // rows per prep block (amortises staging the head's low-rank matrices)
 
@@ -148,7 +170,8 @@ __global__ void __launch_bounds__(kD) kda_prep_kernel(KdaParams p, KdaScratch w,
 #pragma unroll
     for (int j = 0; j < 4; ++j) { wq[j] = p.conv_q[ch * 4 + j]; wk[j] = p.conv_k[ch * 4 + j]; wv[j] = p.conv_v[ch * 4 + j]; }
     const float a_exp = p.a_exp[h], dtb = p.dt_bias[ch];
-    {   // weights do not depend on the previous kernel: stage them before the dependency wait
+    const bool pre = w.rawg != nullptr;
+    if (!pre) {   // weights do not depend on the previous kernel: stage them before the dependency wait
         const bf16* fb = p.f_b + (size_t)ch * p.rank;
         const bf16* gb = p.g_b + (size_t)ch * p.rank;
         for (int j = 0; j < p.rank; j += 8) {
@@ -189,17 +212,22 @@ __global__ void __launch_bounds__(kD) kda_prep_kernel(KdaParams p, KdaScratch w,
         float v = rv[0] * wv[0]; v += rv[1] * wv[1]; v += rv[2] * wv[2]; v += rv[3] * wv[3];
         q = siluf_(q); k = siluf_(k); v = siluf_(v);
         __syncthreads();                                     // previous row's readers are done with s_fa / s_ga
-        if (t < p.rank) { s_fa[t] = pr[p.off_fa + t]; s_ga[t] = pr[p.off_ga + t]; }
+        if (!pre && t < p.rank) { s_fa[t] = pr[p.off_fa + t]; s_ga[t] = pr[p.off_ga + t]; }
         const float qs = block_sum(q * q, s_red);
         const float ks = block_sum(k * k, s_red);
         __syncthreads();
-        float raw_g = 0.f, g2 = 0.f;
-#pragma unroll 8
-        for (int j = 0; j < p.rank; ++j) {
-            raw_g = fmaf(__bfloat162float(s_fb[(size_t)j * kD + t]), s_fa[j], raw_g);
-            g2 = fmaf(__bfloat162float(s_gb[(size_t)j * kD + t]), s_ga[j], g2);
-        }
         const size_t o = (size_t)row * C + ch;
+        float raw_g = 0.f, g2 = 0.f;
+        if (pre) {
+            raw_g = w.rawg[o];
+            g2 = w.g2[o];
+        } else {
+#pragma unroll 8
+            for (int j = 0; j < p.rank; ++j) {
+                raw_g = fmaf(__bfloat162float(s_fb[(size_t)j * kD + t]), s_fa[j], raw_g);
+                g2 = fmaf(__bfloat162float(s_gb[(size_t)j * kD + t]), s_ga[j], g2);
+            }
+        }
         w.qn[o] = q * rsqrtf(qs + 1e-6f) * p.scale;
         w.kn[o] = k * rsqrtf(ks + 1e-6f);
         w.vo[o] = v;
@@ -329,8 +357,11 @@ __global__ void __launch_bounds__(kD) kda_out_kernel(KdaParams p, KdaScratch w) 
 }  // namespace lsb
 using namespace lsb;
 
+LSB_API int lsb_gemm_bf16_tc(void* out, const void* x, const void* w, const void* bias, int M, int N, int K, int ldx, int ldw,
+                             int ldo, int out_bf16, void* partial, long long partial_cap, void* err, const void* comm, void* stream);
+
 LSB_API int lsb_kda_forward(const void* proj, int ldp, int off_q, int off_k, int off_v, int off_beta, int off_fa,
-                            int off_ga, int rank, const void* f_b, const void* g_b, const void* conv_q,
+                            int off_ga, int rank, const void* f_b, const void* g_b, const void* f_b2, const void* g_b2, const void* conv_q,
                             const void* conv_k, const void* conv_v, const void* a_exp, const void* dt_bias,
                             const void* onorm_w, void* state, void* conv_state, const void* seq_row0,
                             const void* seq_nrows, const void* seq_slot, void* out, int nseq, int H, int head_dim,
@@ -346,10 +377,24 @@ LSB_API int lsb_kda_forward(const void* proj, int ldp, int off_q, int off_k, int
     p.scale = scale; p.lower_bound = lower_bound; p.eps = eps;
     cudaStream_t st = (cudaStream_t)stream;
     if (scratch && total_rows >= 8) {
-        // scratch: fp32 [5][total_rows][H*128] followed by [total_rows][H]
+        // scratch: fp32 [5][total_rows][H*128], [total_rows][H]; with the duplicated gate weights (f_b2 / g_b2 = [W | W],
+        // [C, 2 rank]) also [2][total_rows][H*128] gate products, the bf16 (hi | lo) activations [rows][2][2 rank] and an error word
         const size_t n = (size_t)total_rows * H * kD;
         float* b = (float*)scratch;
-        KdaScratch w{b, b + n, b + 2 * n, b + 3 * n, b + 4 * n, b + 5 * n};
+        KdaScratch w{b, b + n, b + 2 * n, b + 3 * n, b + 4 * n, b + 5 * n, nullptr, nullptr};
+        if (f_b2 && g_b2 && total_rows >= 64 && rank % 8 == 0) {
+            float* rawg = b + 5 * n + (((size_t)total_rows * H + 3) & ~(size_t)3);     // keep 16-byte alignment for the GEMM operands
+            float* g2 = rawg + n;
+            bf16* xs = reinterpret_cast<bf16*>(g2 + n);
+            int* gerr = reinterpret_cast<int*>(g2 + n + (size_t)total_rows * 2 * rank);
+            launch_pdl((kda_split_kernel), total_rows, 128, 0, st, (const float*)proj, ldp, off_fa, off_ga, rank, xs);
+            const int C = H * kD;
+            int rc = lsb_gemm_bf16_tc(rawg, xs, f_b2, nullptr, total_rows, C, 2 * rank, 4 * rank, 2 * rank, C, 0, nullptr, 0, gerr, nullptr, stream);
+            if (rc) return rc;
+            rc = lsb_gemm_bf16_tc(g2, xs + 2 * rank, g_b2, nullptr, total_rows, C, 2 * rank, 4 * rank, 2 * rank, C, 0, nullptr, 0, gerr, nullptr, stream);
+            if (rc) return rc;
+            w.rawg = rawg; w.g2 = g2;
+        }
         const size_t prep_smem = (size_t)2 * rank * kD * sizeof(bf16);
         static bool prep_attr = false;
         if (!prep_attr) { cudaFuncSetAttribute(kda_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * 128 * kD * (int)sizeof(bf16)); prep_attr = true; }

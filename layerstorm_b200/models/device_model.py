@@ -332,7 +332,8 @@ class Workspace:
         C = m.Hk * cfg.kda_head_dim
         self.kda_out = z(R, max(C, 1), dtype=b16)
         # many-row KDA path: q / k / v->o / decay / gate [R, C] and beta [R, heads], fp32
-        self.kda_scratch = z(5 * R * C + R * m.Hk) if (C > 0 and R >= 8) else None
+        # KDA chunk path: 5 + 2 per-channel arrays, beta, the bf16 (hi | lo) gate activations and an error word
+        self.kda_scratch = z(7 * R * C + R * m.Hk + 2 * R * m.cfg.kda_rank + 16) if (C > 0 and R >= 8) else None
         Hh = m.Hh
         self.q_c = z(R, max(cfg.q_lora, 1), dtype=b16)
         self.qproj = z(R, m.max_qb, dtype=b16)
@@ -687,6 +688,11 @@ class DeviceModel:
 
     def _finish(self):
         cfg = self.cfg
+        for L in self.layers:
+            if "kda_fb" in L and "kda_fb2" not in L:
+                # [W | W]: the many-row KDA path computes the low-rank gates on the tensor cores with bf16 (hi | lo) activations
+                L["kda_fb2"] = torch.cat([L["kda_fb"], L["kda_fb"]], 1).contiguous()
+                L["kda_gb2"] = torch.cat([L["kda_gb"], L["kda_gb"]], 1).contiguous()
         if self.kv_fmt == "tq4":
             self._fold_turboquant()
         for L in self.layers:
@@ -819,7 +825,7 @@ class DeviceModel:
         lin: QLinear = L["kda_in"]
         lin(ws.proj, ws.x, R, ldo=self.max_proj)
         nat.call("lsb_kda_forward", ws.proj, self.max_proj, 0, C, 2 * C, 3 * C, 3 * C + self.Hk,
-                 3 * C + self.Hk + cfg.kda_rank, cfg.kda_rank, L["kda_fb"], L["kda_gb"], L["kda_conv_q"], L["kda_conv_k"],
+                 3 * C + self.Hk + cfg.kda_rank, cfg.kda_rank, L["kda_fb"], L["kda_gb"], L.get("kda_fb2"), L.get("kda_gb2"), L["kda_conv_q"], L["kda_conv_k"],
                  L["kda_conv_v"], L["kda_a_exp"], L["kda_dt_bias"], L["kda_o_norm"], self.kda_state[i], self.kda_conv[i],
                  ws.seq_row0, ws.seq_nrows, ws.seq_slot, ws.kda_out, nseq, self.Hk, cfg.kda_head_dim,
                  cfg.kda_head_dim ** -0.5, cfg.kda_lower_bound, cfg.rms_eps, R, ws.kda_scratch)

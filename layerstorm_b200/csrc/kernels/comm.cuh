@@ -53,6 +53,58 @@ __device__ __forceinline__ void comm_push(const PeerComm& c, unsigned next_epoch
         if (p < c.nranks) c.recv[p][off] = v;
 }
 
+// Four consecutive values with one 16-byte store per rank (idx and cap multiples of 4).
+__device__ __forceinline__ void comm_push4(const PeerComm& c, unsigned next_epoch, size_t idx, float4 v) {
+    const size_t off = ((size_t)(next_epoch & 1u) * c.nranks + c.rank) * (size_t)c.cap + idx;
+#pragma unroll
+    for (int p = 0; p < kMaxRanks; ++p)
+        if (p < c.nranks) *reinterpret_cast<float4*>(c.recv[p] + off) = v;
+}
+
+// Producer side for few-row partials (whole block, instead of per-element pushes + comm_signal): every block has stored
+// its part of the [M, N] partial to LOCAL memory `buf` (row stride ld == the consumer's row stride); the last block to
+// arrive copies the whole partial into every rank's slot with 16-byte stores and publishes the epoch.  One
+// system-scope fence per collective instead of one per block, and NVLink sees full 128-byte packets instead of
+// thousands of 4-byte stores.
+__device__ __forceinline__ void comm_finish_local(const PeerComm& c, unsigned next_epoch, unsigned total_blocks, const float* buf, int M, int N,
+                                                  int ld) {
+    __shared__ int s_last;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();                                   // this block's local stores before its arrival
+        s_last = atomicAdd(c.cta_done, 1u) == total_blocks - 1 ? 1 : 0;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();                                       // the other blocks' stores are visible to this block
+    const size_t off = ((size_t)(next_epoch & 1u) * c.nranks + c.rank) * (size_t)c.cap;
+    if (((N | ld) & 3) == 0 && (c.cap & 3) == 0) {
+        const int n4 = N >> 2;
+        for (int i = threadIdx.x; i < M * n4; i += blockDim.x) {
+            const int m = i / n4, n = (i - m * n4) << 2;
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(buf + (size_t)m * ld + n));
+#pragma unroll
+            for (int p = 0; p < kMaxRanks; ++p)
+                if (p < c.nranks) *reinterpret_cast<float4*>(c.recv[p] + off + (size_t)m * ld + n) = v;
+        }
+    } else {
+        for (int i = threadIdx.x; i < M * N; i += blockDim.x) {
+            const int m = i / N, n = i - m * N;
+            const float v = __ldcg(buf + (size_t)m * ld + n);
+#pragma unroll
+            for (int p = 0; p < kMaxRanks; ++p)
+                if (p < c.nranks) c.recv[p][off + (size_t)m * ld + n] = v;
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        *c.cta_done = 0;
+        for (int p = 0; p < c.nranks; ++p) st_release_sys(c.flags[p] + (next_epoch & 1u) * c.nranks + c.rank, next_epoch);
+        *c.epoch = next_epoch;
+    }
+}
+
 // Producer side, step 2 (whole block, after its pushes): the last block publishes the epoch.
 __device__ __forceinline__ void comm_signal(const PeerComm& c, unsigned next_epoch, unsigned total_blocks) {
     __syncthreads();

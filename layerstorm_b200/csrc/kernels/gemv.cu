@@ -94,10 +94,7 @@ __global__ void __launch_bounds__(256) gemv_kernel(Mat mat, const bf16* __restri
         for (int m = 0; m < MT; ++m) {
             float a = va[m] * alpha, b2 = vb[m] * alpha;
             if (bias) { a += bias[n0]; b2 += bias[n1]; }
-            if (comm.nranks) {
-                comm_push(comm, next_epoch, (size_t)m * ldo + n0, a);
-                if (n0 + 1 < N) comm_push(comm, next_epoch, (size_t)m * ldo + n0 + 1, b2);
-            } else if (OUT_BF16) {
+            if (OUT_BF16 && !comm.nranks) {
                 bf16* o = reinterpret_cast<bf16*>(out) + (size_t)m * ldo;
                 o[n0] = __float2bfloat16(a);
                 if (n0 + 1 < N) o[n0 + 1] = __float2bfloat16(b2);
@@ -108,7 +105,8 @@ __global__ void __launch_bounds__(256) gemv_kernel(Mat mat, const bf16* __restri
             }
         }
     }
-    if (comm.nranks) comm_signal(comm, next_epoch, gridDim.x);
+    // cross-rank reduction: the partial is in local memory now; the last block ships it to the peers
+    if (comm.nranks) comm_finish_local(comm, next_epoch, gridDim.x, reinterpret_cast<const float*>(out), MT, N, ldo);
 }
 
 template <class Mat, int MT, bool OB, int KS>

@@ -510,8 +510,12 @@ __global__ void moe_combine_kernel(float* __restrict__ out, const float* __restr
     }
     if (comm.nranks) {
         const size_t idx = (size_t)r * H + h;
-        comm_push(comm, next_epoch, idx, a.x); comm_push(comm, next_epoch, idx + 1, a.y);
-        comm_push(comm, next_epoch, idx + 2, a.z); comm_push(comm, next_epoch, idx + 3, a.w);
+        if ((comm.cap & 3) == 0) {
+            comm_push4(comm, next_epoch, idx, a);
+        } else {
+            comm_push(comm, next_epoch, idx, a.x); comm_push(comm, next_epoch, idx + 1, a.y);
+            comm_push(comm, next_epoch, idx + 2, a.z); comm_push(comm, next_epoch, idx + 3, a.w);
+        }
         comm_signal(comm, next_epoch, gridDim.x * gridDim.y);
     } else {
         float4* o = reinterpret_cast<float4*>(out + (size_t)r * H + h);

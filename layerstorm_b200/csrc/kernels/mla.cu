@@ -859,6 +859,7 @@ LSB_API int lsb_mla_decode(const void* q, const void* cache, const void* block_t
     } else {
         launch_pdl((mla_decode_kernel), dim3(R, (H + kHG - 1) / kHG, NS), 256, smem, st, p);
     }
-    launch_pdl((mla_combine_kernel), dim3(R, H), 128, 0, st, (bf16*)out, (float*)lse, (const float*)o_part, (const float*)ml_part, H, NS, dl);
+    // out == null: the caller merges the partials itself (context-parallel attention combines them across ranks)
+    if (out) launch_pdl((mla_combine_kernel), dim3(R, H), 128, 0, st, (bf16*)out, (float*)lse, (const float*)o_part, (const float*)ml_part, H, NS, dl);
     LSB_CHECK_LAUNCH();
 }

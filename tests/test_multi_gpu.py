@@ -34,3 +34,16 @@ def test_fused_expert_parallel_ffn(fmt):
            "--master-port", "29537", os.path.join(HERE, "ep_worker.py"), fmt]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert "EP_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+def test_context_parallel_attention():
+    """Token-sharded KV cache: all-gather of the queries, local split-KV attention and the cross-rank log-sum-exp merge, all by
+    P2P stores from inside the kernels == fp32 attention over the whole cache."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    n = 4 if torch.cuda.device_count() >= 4 else 2
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
+           "--master-port", "29539", os.path.join(HERE, "dcp_worker.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert "DCP_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]

@@ -18,6 +18,7 @@
 //          decode only swaps the row loader (reference: 386-byte TurboQuant rows, src/compute/tq_init.h, docs/INTERNALS.md:8-9).
 // Pages hold `page` consecutive tokens; a sequence's pages are listed in its block table.
 #include "common.cuh"
+#include <cstdlib>
 #include "gemv_core.cuh"
 
 namespace lsb {
@@ -848,7 +849,9 @@ LSB_API int lsb_mla_decode(const void* q, const void* cache, const void* block_t
         attr_set = true;
     }
     // many rows (prefill chunks, verify batches, large batches): tensor-core variant; few rows: the latency-tuned CUDA-core one
-    if (R >= 16 && dl % 64 == 0 && dl <= 512 && dr % 16 == 0) {
+    // LSB_MLA_MMA_MIN_ROWS: step size from which the tensor-core variant is used (tuning knob, default 16)
+    static const int mma_min_rows = [] { const char* e = getenv("LSB_MLA_MMA_MIN_ROWS"); return e ? atoi(e) : 16; }();
+    if (R >= mma_min_rows && dl % 64 == 0 && dl <= 512 && dr % 16 == 0) {
         // more than one 16-head group per query row: the groups of a row share each gathered K tile
         if (H > 2 * kHG && mla_mma_shared_smem_bytes(dl, dr, 4) <= 200 * 1024)
             launch_pdl((mla_decode_mma_shared_kernel<4>), dim3(R, (H + 4 * kHG - 1) / (4 * kHG), NS), 512, (size_t)mla_mma_shared_smem_bytes(dl, dr, 4), st, p);

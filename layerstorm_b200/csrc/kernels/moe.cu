@@ -21,26 +21,22 @@ namespace lsb {
 
 enum { kScoreSigmoid = 0, kScoreSoftmax = 1, kScoreSqrtSoftplus = 2 };
 
-// One warp per row: no block-wide barriers, the k selection rounds are shuffle reductions.
-__global__ void __launch_bounds__(32) router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int* __restrict__ ids,
-                                                         float* __restrict__ wts, int E, int topk, int n_group, int topk_group, int scoring,
-                                                         int norm_topk, float scale, int n_shared, int ld_logits) {
-    extern __shared__ float sm[];
+// Scores, grouped selection and top-k of ONE row by ONE warp (`lane`): no block-wide barriers, the k selection rounds are
+// shuffle reductions.  sm: 2 E + 64 floats of shared memory, s_keep: 64 ints, both private to the warp.
+__device__ __forceinline__ void router_topk_row(const float* __restrict__ logits, const float* __restrict__ bias, int* __restrict__ ids,
+                                                float* __restrict__ wts, int E, int topk, int n_group, int topk_group, int scoring,
+                                                int norm_topk, float scale, int n_shared, int ld_logits, int r, int lane, float* sm, int* s_keep) {
     float* score = sm;            // [E] unbiased
     float* sel = sm + E;          // [E] biased, -inf when masked/taken
-    __shared__ int s_keep[64];
-    const int r = blockIdx.x, lane = threadIdx.x;
-    const float* lg = logits + (size_t)r * ld_logits;
-    pdl_wait();
-    pdl_launch_dependents();
+    const float* lg = logits + (size_t)r * ld_logits;     // read through L2: the fused kernel's last block reads what other blocks wrote
     float mx = -INFINITY;
     if (scoring == kScoreSoftmax) {
-        for (int e = lane; e < E; e += 32) mx = fmaxf(mx, lg[e]);
+        for (int e = lane; e < E; e += 32) mx = fmaxf(mx, __ldcg(lg + e));
         mx = warp_max(mx);
     }
     float ssum = 0.f;
     for (int e = lane; e < E; e += 32) {
-        const float x = lg[e];
+        const float x = __ldcg(lg + e);
         float s;
         if (scoring == kScoreSigmoid) s = 1.f / (1.f + expf(-x));
         else if (scoring == kScoreSoftmax) s = expf(x - mx);
@@ -121,6 +117,76 @@ __global__ void __launch_bounds__(32) router_topk_kernel(const float* __restrict
         wts[r * S + lane] = w * scale;
     }
     if (lane < n_shared) { ids[r * S + topk + lane] = E + lane; wts[r * S + topk + lane] = 1.f; }
+}
+
+// One warp per row.
+__global__ void __launch_bounds__(32) router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int* __restrict__ ids,
+                                                         float* __restrict__ wts, int E, int topk, int n_group, int topk_group, int scoring,
+                                                         int norm_topk, float scale, int n_shared, int ld_logits) {
+    extern __shared__ float sm[];
+    __shared__ int s_keep[64];
+    pdl_wait();
+    pdl_launch_dependents();
+    router_topk_row(logits, bias, ids, wts, E, topk, n_group, topk_group, scoring, norm_topk, scale, n_shared, ld_logits, blockIdx.x, threadIdx.x, sm, s_keep);
+    pdl_launch_dependents();
+}
+
+// Router projection and top-k in one launch for decode-sized steps (rows <= 8): every warp computes the fp32 logit of one
+// expert for all rows (fp32 router weights [E, H], bf16 activations), the last block to finish runs the top-k of each row
+// (one warp per row).  Saves a launch and a dependent-kernel hand-off per MoE layer.
+constexpr int kRouterMaxRows = 8;
+__global__ void __launch_bounds__(128) router_fused_kernel(const float* __restrict__ w, const bf16* __restrict__ x, float* __restrict__ logits,
+                                                           const float* __restrict__ bias, int* __restrict__ ids, float* __restrict__ wts,
+                                                           unsigned* __restrict__ done, int rows, int H, int E, int topk, int n_group,
+                                                           int topk_group, int scoring, int norm_topk, float scale, int n_shared) {
+    extern __shared__ float sm[];                // last block: rows x (2 E + 64) floats, then rows x 64 ints
+    __shared__ int s_last;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int e = blockIdx.x * 4 + warp;
+    const float* wr = w + (size_t)e * H;
+    if (e < E) {                                 // weights do not depend on the previous kernel
+        for (int k = lane * 4; k < H; k += 32 * 4 * 4) asm volatile("prefetch.global.L2 [%0];" ::"l"(wr + k));
+    }
+    pdl_wait();
+    pdl_launch_dependents();
+    if (e < E) {
+        float acc[kRouterMaxRows];
+#pragma unroll
+        for (int m = 0; m < kRouterMaxRows; ++m) acc[m] = 0.f;
+        for (int k = lane * 4; k < H; k += 128) {
+            const float4 wv = __ldg(reinterpret_cast<const float4*>(wr + k));
+#pragma unroll
+            for (int m = 0; m < kRouterMaxRows; ++m) {
+                if (m < rows) {
+                    const uint2 xv = *reinterpret_cast<const uint2*>(x + (size_t)m * H + k);
+                    const float2 x01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xv.x));
+                    const float2 x23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xv.y));
+                    acc[m] = fmaf(wv.x, x01.x, acc[m]); acc[m] = fmaf(wv.y, x01.y, acc[m]);
+                    acc[m] = fmaf(wv.z, x23.x, acc[m]); acc[m] = fmaf(wv.w, x23.y, acc[m]);
+                }
+            }
+        }
+#pragma unroll
+        for (int m = 0; m < kRouterMaxRows; ++m) {
+            if (m < rows) {
+                const float v = warp_sum(acc[m]);
+                if (lane == 0) logits[(size_t)m * E + e] = v;
+            }
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        s_last = atomicAdd(done, 1u) == gridDim.x - 1 ? 1 : 0;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    if (threadIdx.x == 0) *done = 0;
+    __threadfence();
+    int* keep = reinterpret_cast<int*>(sm + (size_t)rows * (2 * E + 64));
+    for (int r = warp; r < rows; r += 4)
+        router_topk_row(logits, bias, ids, wts, E, topk, n_group, topk_group, scoring, norm_topk, scale, n_shared, E, r, lane,
+                        sm + (size_t)r * (2 * E + 64), keep + r * 64);
     pdl_launch_dependents();
 }
 
@@ -547,6 +613,18 @@ LSB_API int lsb_router_topk(const void* logits, const void* bias, void* ids, voi
     launch_pdl((router_topk_kernel), rows, 32, (size_t)(2 * E + 64) * 4, (cudaStream_t)stream, (const float*)logits, (const float*)bias, (int*)ids,
                                                                          (float*)wts, E, topk, n_group, topk_group, scoring,
                                                                          norm_topk, scale, n_shared, ld_logits);
+    LSB_CHECK_LAUNCH();
+}
+
+// Router projection + top-k in one launch (rows <= 8, H % 128 == 0).  w: fp32 [E, H]; x: bf16 [rows, H]; logits: fp32 scratch
+// [rows, E]; done: one zero-initialised counter.
+LSB_API int lsb_router_fused(const void* w, const void* x, void* logits, const void* bias, void* ids, void* wts, void* done, int rows, int H,
+                             int E, int topk, int n_group, int topk_group, int scoring, int norm_topk, float scale, int n_shared, void* stream) {
+    if (rows > kRouterMaxRows || H % 128 || topk > 32 || n_group > 64 || E > 4096 || n_shared > 32) return -1;
+    const size_t smem = (size_t)rows * ((2 * E + 64) * 4 + 64 * 4);
+    if (smem > 48 * 1024) return -1;
+    launch_pdl((router_fused_kernel), (E + 3) / 4, 128, smem, (cudaStream_t)stream, (const float*)w, (const bf16*)x, (float*)logits, (const float*)bias,
+               (int*)ids, (float*)wts, (unsigned*)done, rows, H, E, topk, n_group, topk_group, scoring, norm_topk, scale, n_shared);
     LSB_CHECK_LAUNCH();
 }
 

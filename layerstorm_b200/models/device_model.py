@@ -333,6 +333,7 @@ class Workspace:
         self.kda_out = z(R, max(C, 1), dtype=b16)
         # many-row KDA path: q / k / v->o / decay / gate [R, C] and beta [R, heads], fp32
         # KDA chunk path: 5 + 2 per-channel arrays, beta, the bf16 (hi | lo) gate activations and an error word
+        self.router_done = torch.zeros(1, dtype=i32, device=dev)
         self.kda_scratch = z(7 * R * C + R * m.Hk + 2 * R * m.cfg.kda_rank + 16) if (C > 0 and R >= 8) else None
         Hh = m.Hh
         self.q_c = z(R, max(cfg.q_lora, 1), dtype=b16)
@@ -760,10 +761,15 @@ class DeviceModel:
             return
         arena: ExpertArena = L["arena"]
         S = ws.S
-        L["router"](ws.logits_r, ws.x, R)
         sc = {"sigmoid": 0, "softmax": 1, "sqrtsoftplus": 2}[cfg.scoring]
-        nat.call("lsb_router_topk", ws.logits_r, L["router_bias"], ws.ids, ws.wts, R, cfg.n_routed, cfg.top_k, cfg.n_group,
-                 cfg.topk_group, sc, int(cfg.norm_topk_prob), cfg.routed_scale, cfg.n_shared, cfg.n_routed)
+        if R <= 8 and cfg.hidden % 128 == 0 and R * (2 * cfg.n_routed + 128) * 4 <= 48 * 1024:
+            # decode-sized steps: projection and top-k in one launch (the last block selects)
+            nat.call("lsb_router_fused", L["router"].w, ws.x, ws.logits_r, L["router_bias"], ws.ids, ws.wts, ws.router_done, R, cfg.hidden,
+                     cfg.n_routed, cfg.top_k, cfg.n_group, cfg.topk_group, sc, int(cfg.norm_topk_prob), cfg.routed_scale, cfg.n_shared)
+        else:
+            L["router"](ws.logits_r, ws.x, R)
+            nat.call("lsb_router_topk", ws.logits_r, L["router_bias"], ws.ids, ws.wts, R, cfg.n_routed, cfg.top_k, cfg.n_group,
+                     cfg.topk_group, sc, int(cfg.norm_topk_prob), cfg.routed_scale, cfg.n_shared, cfg.n_routed)
         if self.streamer is not None:
             # capped expert cache: experts are brought in from pinned host memory in waves; every wave runs the
             # expert kernels over what is resident, the combine runs once at the end over all slots

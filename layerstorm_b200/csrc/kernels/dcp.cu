@@ -26,7 +26,7 @@ struct DcpComm {
     int nranks, rank, H, Hh;         // heads in total / per rank
     int D, dl, NS, max_rows;         // q row width (dl + dr), latent width, splits per rank, rows per call
     bf16* q_all[kMaxRanks];          // rank p's gathered queries [max_rows][H][D]
-    float* part[kMaxRanks];          // rank p's incoming partials [nranks][max_rows][Hh][NS][dl + 2]  (o, m, l)
+    float* part[kMaxRanks];          // rank p's incoming partials [nranks][max_rows][Hh][NS][dl + 4]  (o, m, l, pad: rows stay 16-byte aligned)
     unsigned* flags[kMaxRanks];      // rank p's flag words [2][nranks]
     unsigned* epoch;                 // local: calls completed
     unsigned* cta_done;              // local: [2] finished-block counters
@@ -121,7 +121,7 @@ __global__ void __launch_bounds__(128) dcp_scatter_kernel(const float* __restric
     const unsigned epoch = *c.epoch + 1u;
     const int r = blockIdx.x, h = blockIdx.y;
     const int owner = h / c.Hh, hl = h - owner * c.Hh;
-    const int W = c.dl + 2;
+    const int W = c.dl + 4;
     float* dst = c.part[owner] + ((((size_t)c.rank * c.max_rows + r) * c.Hh + hl) * c.NS) * W;
     for (int s = 0; s < c.NS; ++s) {
         const float* o = o_part + (((size_t)r * c.H + h) * c.NS + s) * c.dl;
@@ -141,7 +141,7 @@ __global__ void __launch_bounds__(128) dcp_combine_kernel(bf16* __restrict__ out
     const unsigned epoch = *c.epoch + 1u;
     const bool ok = dcp_wait(c, 1, epoch);
     const int r = blockIdx.x, hl = blockIdx.y, t = threadIdx.x;
-    const int W = c.dl + 2, NP = c.nranks * c.NS;
+    const int W = c.dl + 4, NP = c.nranks * c.NS;
     auto slot = [&](int i) {                                      // partial i = (source rank, split)
         const int src = i / c.NS, s = i - src * c.NS;
         return c.part[c.rank] + ((((size_t)src * c.max_rows + r) * c.Hh + hl) * c.NS + s) * W;

@@ -55,7 +55,7 @@ class DcpAttention:
         assert self.world <= K_MAX_RANKS and n_heads % self.world == 0
         self.H, self.Hh, self.dl, self.dr, self.D = n_heads, n_heads // self.world, dl, dr, dl + dr
         self.max_rows, self.NS, self.chunk, self.dev = max_rows, n_splits, chunk, device
-        sizes = {"q_all": max_rows * self.H * self.D * 2, "part": self.world * max_rows * self.Hh * self.NS * (dl + 2) * 4,
+        sizes = {"q_all": max_rows * self.H * self.D * 2, "part": self.world * max_rows * self.Hh * self.NS * (dl + 4) * 4,
                  "flags": 2 * self.world * 4}
         offs, cur = {}, 0
         for k, v in sizes.items():

@@ -12,6 +12,7 @@
 // RMSNorm; src/compute/kernels/sm120/attention/kda_linear.h); here thread v owns state row
 // S[v][:] in registers, so the token loop needs no cross-thread reduction except the norms.
 #include "common.cuh"
+#include <cstdlib>
 
 namespace lsb {
 
@@ -238,6 +239,82 @@ __global__ void __launch_bounds__(kD) kda_prep_kernel(KdaParams p, KdaScratch w,
     pdl_launch_dependents();
 }
 
+// Many-row prep when the gate products are precomputed: one WARP per row (lane = 4 consecutive channels of the head, 16-byte
+// loads and stores, norms by warp shuffles), four rows in flight per block - no block-wide barrier per row.
+__global__ void __launch_bounds__(128) kda_prep_rows_kernel(KdaParams p, KdaScratch w, int nseq, int total_rows) {
+    const int h = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int C = p.H * kD, ch = h * kD + lane * 4;
+    float wq[4][4], wk[4][4], wv[4][4];                      // [channel][tap]
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        const float4 a = *reinterpret_cast<const float4*>(p.conv_q + (size_t)(ch + c) * 4);
+        const float4 b = *reinterpret_cast<const float4*>(p.conv_k + (size_t)(ch + c) * 4);
+        const float4 d = *reinterpret_cast<const float4*>(p.conv_v + (size_t)(ch + c) * 4);
+        wq[c][0] = a.x; wq[c][1] = a.y; wq[c][2] = a.z; wq[c][3] = a.w;
+        wk[c][0] = b.x; wk[c][1] = b.y; wk[c][2] = b.z; wk[c][3] = b.w;
+        wv[c][0] = d.x; wv[c][1] = d.y; wv[c][2] = d.z; wv[c][3] = d.w;
+    }
+    const float4 dt4 = *reinterpret_cast<const float4*>(p.dt_bias + ch);
+    const float dtb[4] = {dt4.x, dt4.y, dt4.z, dt4.w};
+    const float a_exp = p.a_exp[h];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int row_end = min(total_rows, (int)(blockIdx.x + 1) * kPrepRows);
+    for (int row = blockIdx.x * kPrepRows + warp; row < row_end; row += 4) {
+        int row0 = -1, slot = 0;
+        for (int s = 0; s < nseq; ++s) {
+            const int r0 = p.seq_row0[s], n = p.seq_nrows[s];
+            if (row >= r0 && row < r0 + n) { row0 = r0; slot = p.seq_slot[s]; }
+        }
+        if (row0 < 0) continue;
+        const int i = row - row0;
+        float q[4] = {0.f, 0.f, 0.f, 0.f}, k[4] = {0.f, 0.f, 0.f, 0.f}, v[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int d = 0; d < 4; ++d) {                        // tap d is `3 - d` rows before this one (oldest first)
+            const int back = 3 - d;
+            float rq[4], rk[4], rv[4];
+            if (i - back >= 0) {
+                const float* pr = p.proj + (size_t)(row - back) * p.ldp;
+                const float4 a = *reinterpret_cast<const float4*>(pr + p.off_q + ch);
+                const float4 b = *reinterpret_cast<const float4*>(pr + p.off_k + ch);
+                const float4 e = *reinterpret_cast<const float4*>(pr + p.off_v + ch);
+                rq[0] = a.x; rq[1] = a.y; rq[2] = a.z; rq[3] = a.w;
+                rk[0] = b.x; rk[1] = b.y; rk[2] = b.z; rk[3] = b.w;
+                rv[0] = e.x; rv[1] = e.y; rv[2] = e.z; rv[3] = e.w;
+            } else {
+                const int hi = 3 + i - back;                 // 0..2 in the saved history
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    rq[c] = p.conv_state[(((size_t)slot * 3 + 0) * C + ch + c) * 3 + hi];
+                    rk[c] = p.conv_state[(((size_t)slot * 3 + 1) * C + ch + c) * 3 + hi];
+                    rv[c] = p.conv_state[(((size_t)slot * 3 + 2) * C + ch + c) * 3 + hi];
+                }
+            }
+#pragma unroll
+            for (int c = 0; c < 4; ++c) { q[c] += rq[c] * wq[c][d]; k[c] += rk[c] * wk[c][d]; v[c] += rv[c] * wv[c][d]; }
+        }
+        float qs = 0.f, ks = 0.f;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) { q[c] = siluf_(q[c]); k[c] = siluf_(k[c]); v[c] = siluf_(v[c]); qs += q[c] * q[c]; ks += k[c] * k[c]; }
+        qs = warp_sum(qs);
+        ks = warp_sum(ks);
+        const float qi = rsqrtf(qs + 1e-6f) * p.scale, ki = rsqrtf(ks + 1e-6f);
+        const size_t o = (size_t)row * C + ch;
+        const float4 rg = *reinterpret_cast<const float4*>(w.rawg + o), g2 = *reinterpret_cast<const float4*>(w.g2 + o);
+        const float rgv[4] = {rg.x, rg.y, rg.z, rg.w}, g2v[4] = {g2.x, g2.y, g2.z, g2.w};
+        float dec[4], gat[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) { dec[c] = __expf(p.lower_bound * sigmoidf_(a_exp * (rgv[c] + dtb[c]))); gat[c] = sigmoidf_(g2v[c]); }
+        *reinterpret_cast<float4*>(w.qn + o) = make_float4(q[0] * qi, q[1] * qi, q[2] * qi, q[3] * qi);
+        *reinterpret_cast<float4*>(w.kn + o) = make_float4(k[0] * ki, k[1] * ki, k[2] * ki, k[3] * ki);
+        *reinterpret_cast<float4*>(w.vo + o) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4*>(w.decay + o) = make_float4(dec[0], dec[1], dec[2], dec[3]);
+        *reinterpret_cast<float4*>(w.gate + o) = make_float4(gat[0], gat[1], gat[2], gat[3]);
+        if (lane == 0) w.beta[(size_t)row * p.H + h] = sigmoidf_(p.proj[(size_t)row * p.ldp + p.off_beta + h]);
+    }
+    pdl_launch_dependents();
+}
+
 __device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gsrc) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gsrc) : "memory");
 }
@@ -398,7 +475,12 @@ LSB_API int lsb_kda_forward(const void* proj, int ldp, int off_q, int off_k, int
         const size_t prep_smem = (size_t)2 * rank * kD * sizeof(bf16);
         static bool prep_attr = false;
         if (!prep_attr) { cudaFuncSetAttribute(kda_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * 128 * kD * (int)sizeof(bf16)); prep_attr = true; }
-        launch_pdl((kda_prep_kernel), dim3((total_rows + kPrepRows - 1) / kPrepRows, H), kD, prep_smem, st, p, w, nseq, total_rows);
+        // LSB_KDA_PREP_ROWS=0 keeps the block-per-16-rows prep kernel
+        static const bool prep_rows = [] { const char* e = getenv("LSB_KDA_PREP_ROWS"); return e ? atoi(e) != 0 : false; }();
+        if (prep_rows && w.rawg && ldp % 4 == 0 && off_q % 4 == 0 && off_k % 4 == 0 && off_v % 4 == 0 && ((uintptr_t)proj & 15) == 0)
+            launch_pdl((kda_prep_rows_kernel), dim3((total_rows + kPrepRows - 1) / kPrepRows, H), 128, 0, st, p, w, nseq, total_rows);
+        else
+            launch_pdl((kda_prep_kernel), dim3((total_rows + kPrepRows - 1) / kPrepRows, H), kD, prep_smem, st, p, w, nseq, total_rows);
         launch_pdl((kda_recur_kernel), dim3(nseq, H), kD, 0, st, p, w);
         launch_pdl((kda_out_kernel), dim3(total_rows, H), kD, 0, st, p, w);
     } else {

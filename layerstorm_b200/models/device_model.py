@@ -12,6 +12,8 @@ src/daemon/moe/moe_driver.cpp:382-1745.
 """
 from __future__ import annotations
 
+import os
+
 import ctypes
 import math
 from dataclasses import dataclass
@@ -83,7 +85,9 @@ def expert_layout(fmt: str, H: int, F: int) -> ExpertFmt:
     return ef
 
 
-TC_MOE_MIN_ROWS = 16      # rows per step from which the routed experts run on the tensor-core grouped GEMM
+TC_MOE_MIN_ROWS = 16
+# router projection + top-k in one launch for decode-sized steps (LSB_ROUTER_FUSED=0 falls back to two kernels)
+ROUTER_FUSED = os.environ.get("LSB_ROUTER_FUSED", "0") != "0"      # rows per step from which the routed experts run on the tensor-core grouped GEMM
 
 
 def _dequant_q4k(raw: torch.Tensor, N: int, K: int) -> torch.Tensor:
@@ -762,7 +766,7 @@ class DeviceModel:
         arena: ExpertArena = L["arena"]
         S = ws.S
         sc = {"sigmoid": 0, "softmax": 1, "sqrtsoftplus": 2}[cfg.scoring]
-        if R <= 8 and cfg.hidden % 128 == 0 and R * (2 * cfg.n_routed + 128) * 4 <= 48 * 1024:
+        if ROUTER_FUSED and R <= 8 and cfg.hidden % 128 == 0 and R * (2 * cfg.n_routed + 128) * 4 <= 48 * 1024:
             # decode-sized steps: projection and top-k in one launch (the last block selects)
             nat.call("lsb_router_fused", L["router"].w, ws.x, ws.logits_r, L["router_bias"], ws.ids, ws.wts, ws.router_done, R, cfg.hidden,
                      cfg.n_routed, cfg.top_k, cfg.n_group, cfg.topk_group, sc, int(cfg.norm_topk_prob), cfg.routed_scale, cfg.n_shared)

@@ -85,9 +85,9 @@ def expert_layout(fmt: str, H: int, F: int) -> ExpertFmt:
     return ef
 
 
-TC_MOE_MIN_ROWS = 16
-# router projection + top-k in one launch for decode-sized steps (LSB_ROUTER_FUSED=0 falls back to two kernels)
-ROUTER_FUSED = os.environ.get("LSB_ROUTER_FUSED", "0") != "0"      # rows per step from which the routed experts run on the tensor-core grouped GEMM
+TC_MOE_MIN_ROWS = 16      # rows per step from which the routed experts run on the tensor-core grouped GEMM
+# router projection + top-k in one launch for decode-sized steps (switch: LSB_ROUTER_FUSED=1)
+ROUTER_FUSED = os.environ.get("LSB_ROUTER_FUSED", "0") != "0"
 
 
 def _dequant_q4k(raw: torch.Tensor, N: int, K: int) -> torch.Tensor:

@@ -476,7 +476,7 @@ LSB_API int lsb_kda_forward(const void* proj, int ldp, int off_q, int off_k, int
         static bool prep_attr = false;
         if (!prep_attr) { cudaFuncSetAttribute(kda_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * 128 * kD * (int)sizeof(bf16)); prep_attr = true; }
         // LSB_KDA_PREP_ROWS=0 keeps the block-per-16-rows prep kernel
-        static const bool prep_rows = [] { const char* e = getenv("LSB_KDA_PREP_ROWS"); return e ? atoi(e) != 0 : false; }();
+        static const bool prep_rows = [] { const char* e = getenv("LSB_KDA_PREP_ROWS"); return e ? atoi(e) != 0 : true; }();
         if (prep_rows && w.rawg && ldp % 4 == 0 && off_q % 4 == 0 && off_k % 4 == 0 && off_v % 4 == 0 && ((uintptr_t)proj & 15) == 0)
             launch_pdl((kda_prep_rows_kernel), dim3((total_rows + kPrepRows - 1) / kPrepRows, H), 128, 0, st, p, w, nseq, total_rows);
         else

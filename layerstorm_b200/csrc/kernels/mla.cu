@@ -10,7 +10,7 @@
 // Cache row formats (kv_fmt):
 //   0  bf16: (d_c + d_rope) bf16
 //   1  fp8 : d_c e4m3 bytes | fp32 per-token scale (+12 pad bytes) | d_rope bf16
-//          (the reference's FP8+BF16-RoPE row: docs/DESIGN.md:126, K/sm120/prep/fused_k_append.cu)
+//          (the reference's FP8+BF16-RoPE row: its design document under docs/, line 126; K/sm120/prep/fused_k_append.cu)
 //   2  tq4 : d_c / 2 bytes of 4-bit codes (low nibble = even index) | fp32 row scale (+12 pad bytes) | d_rope bf16
 //          TurboQuant: the latent is L2-normalised, rotated by a fixed per-layer orthogonal matrix and every coordinate
 //          (times sqrt(d_c), ~N(0,1)) is replaced by the nearest of 16 Lloyd-Max centroids; row scale = norm / sqrt(d_c).

@@ -131,9 +131,9 @@ __global__ void __launch_bounds__(32) router_topk_kernel(const float* __restrict
     pdl_launch_dependents();
 }
 
-// Router projection and top-k in one launch for decode-sized steps (rows <= 8): every warp computes the fp32 logit of one
-// expert for all rows (fp32 router weights [E, H], bf16 activations), the last block to finish runs the top-k of each row
-// (one warp per row).  Saves a launch and a dependent-kernel hand-off per MoE layer.
+// Router projection and top-k in one launch for decode-sized steps (rows <= 8): one block per expert computes its fp32 logit
+// for all rows (fp32 router weights [E, H], bf16 activations, the reduction split over the block's 4 warps); the last block to
+// finish runs the top-k of each row (one warp per row).  Saves a launch and a dependent-kernel hand-off per MoE layer.
 constexpr int kRouterMaxRows = 8;
 __global__ void __launch_bounds__(128) router_fused_kernel(const float* __restrict__ w, const bf16* __restrict__ x, float* __restrict__ logits,
                                                            const float* __restrict__ bias, int* __restrict__ ids, float* __restrict__ wts,
@@ -141,39 +141,41 @@ __global__ void __launch_bounds__(128) router_fused_kernel(const float* __restri
                                                            int topk_group, int scoring, int norm_topk, float scale, int n_shared) {
     extern __shared__ float sm[];                // last block: rows x (2 E + 64) floats, then rows x 64 ints
     __shared__ int s_last;
+    __shared__ float s_part[4][kRouterMaxRows];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int e = blockIdx.x * 4 + warp;
-    const float* wr = w + (size_t)e * H;
-    if (e < E) {                                 // weights do not depend on the previous kernel
-        for (int k = lane * 4; k < H; k += 32 * 4 * 4) asm volatile("prefetch.global.L2 [%0];" ::"l"(wr + k));
-    }
+    const int e = blockIdx.x;                    // one expert per block, the reduction split over the 4 warps
+    const int kq = H >> 2;                       // columns per warp (a multiple of 4)
+    const float* wr = w + (size_t)e * H + warp * kq;
+    // weights do not depend on the previous kernel: have them on their way before the dependency wait
+    for (int k = lane * 32; k < kq; k += 32 * 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(wr + k));
     pdl_wait();
     pdl_launch_dependents();
-    if (e < E) {
-        float acc[kRouterMaxRows];
+    float acc[kRouterMaxRows];
 #pragma unroll
-        for (int m = 0; m < kRouterMaxRows; ++m) acc[m] = 0.f;
-        for (int k = lane * 4; k < H; k += 128) {
-            const float4 wv = __ldg(reinterpret_cast<const float4*>(wr + k));
-#pragma unroll
-            for (int m = 0; m < kRouterMaxRows; ++m) {
-                if (m < rows) {
-                    const uint2 xv = *reinterpret_cast<const uint2*>(x + (size_t)m * H + k);
-                    const float2 x01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xv.x));
-                    const float2 x23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xv.y));
-                    acc[m] = fmaf(wv.x, x01.x, acc[m]); acc[m] = fmaf(wv.y, x01.y, acc[m]);
-                    acc[m] = fmaf(wv.z, x23.x, acc[m]); acc[m] = fmaf(wv.w, x23.y, acc[m]);
-                }
-            }
-        }
+    for (int m = 0; m < kRouterMaxRows; ++m) acc[m] = 0.f;
+#pragma unroll 4
+    for (int k = lane * 4; k < kq; k += 128) {
+        const float4 wv = __ldg(reinterpret_cast<const float4*>(wr + k));
 #pragma unroll
         for (int m = 0; m < kRouterMaxRows; ++m) {
             if (m < rows) {
-                const float v = warp_sum(acc[m]);
-                if (lane == 0) logits[(size_t)m * E + e] = v;
+                const uint2 xv = *reinterpret_cast<const uint2*>(x + (size_t)m * H + warp * kq + k);
+                const float2 x01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xv.x));
+                const float2 x23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xv.y));
+                acc[m] = fmaf(wv.x, x01.x, acc[m]); acc[m] = fmaf(wv.y, x01.y, acc[m]);
+                acc[m] = fmaf(wv.z, x23.x, acc[m]); acc[m] = fmaf(wv.w, x23.y, acc[m]);
             }
         }
     }
+#pragma unroll
+    for (int m = 0; m < kRouterMaxRows; ++m) {
+        if (m < rows) {
+            const float v = warp_sum(acc[m]);
+            if (lane == 0) s_part[warp][m] = v;
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x < rows) logits[(size_t)threadIdx.x * E + e] = (s_part[0][threadIdx.x] + s_part[1][threadIdx.x]) + (s_part[2][threadIdx.x] + s_part[3][threadIdx.x]);
     __syncthreads();
     if (threadIdx.x == 0) {
         __threadfence();
@@ -616,14 +618,14 @@ LSB_API int lsb_router_topk(const void* logits, const void* bias, void* ids, voi
     LSB_CHECK_LAUNCH();
 }
 
-// Router projection + top-k in one launch (rows <= 8, H % 128 == 0).  w: fp32 [E, H]; x: bf16 [rows, H]; logits: fp32 scratch
+// Router projection + top-k in one launch (rows <= 8, H % 16 == 0).  w: fp32 [E, H]; x: bf16 [rows, H]; logits: fp32 scratch
 // [rows, E]; done: one zero-initialised counter.
 LSB_API int lsb_router_fused(const void* w, const void* x, void* logits, const void* bias, void* ids, void* wts, void* done, int rows, int H,
                              int E, int topk, int n_group, int topk_group, int scoring, int norm_topk, float scale, int n_shared, void* stream) {
-    if (rows > kRouterMaxRows || H % 128 || topk > 32 || n_group > 64 || E > 4096 || n_shared > 32) return -1;
+    if (rows > kRouterMaxRows || H % 16 || topk > 32 || n_group > 64 || E > 4096 || n_shared > 32) return -1;
     const size_t smem = (size_t)rows * ((2 * E + 64) * 4 + 64 * 4);
     if (smem > 48 * 1024) return -1;
-    launch_pdl((router_fused_kernel), (E + 3) / 4, 128, smem, (cudaStream_t)stream, (const float*)w, (const bf16*)x, (float*)logits, (const float*)bias,
+    launch_pdl((router_fused_kernel), E, 128, smem, (cudaStream_t)stream, (const float*)w, (const bf16*)x, (float*)logits, (const float*)bias,
                (int*)ids, (float*)wts, (unsigned*)done, rows, H, E, topk, n_group, topk_group, scoring, norm_topk, scale, n_shared);
     LSB_CHECK_LAUNCH();
 }

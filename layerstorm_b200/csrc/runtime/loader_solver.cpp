@@ -9,7 +9,7 @@
 // per-device part of the objective followed by a full re-evaluation, and greedy longest-
 // processing-time placement; the best candidate under the full objective is returned.
 // Reference component: LoaderSolver (src/core/gpu_loader/loader_solver.h:93-165, math in
-// docs/DESIGN.md:305-413): same objective shape and tiering, re-derived for NVLink-class devices.
+// the reference's design document under docs/, lines 305-413): same objective shape and tiering, re-derived for NVLink-class devices.
 #include <algorithm>
 #include <climits>
 #include <cstdint>

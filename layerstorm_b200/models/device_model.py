@@ -767,7 +767,7 @@ class DeviceModel:
         arena: ExpertArena = L["arena"]
         S = ws.S
         sc = {"sigmoid": 0, "softmax": 1, "sqrtsoftplus": 2}[cfg.scoring]
-        if ROUTER_FUSED and R <= 8 and cfg.hidden % 128 == 0 and R * (2 * cfg.n_routed + 128) * 4 <= 48 * 1024:
+        if ROUTER_FUSED and R <= 8 and cfg.hidden % 16 == 0 and R * (2 * cfg.n_routed + 128) * 4 <= 48 * 1024:
             # decode-sized steps: projection and top-k in one launch (the last block selects)
             nat.call("lsb_router_fused", L["router"].w, ws.x, ws.logits_r, L["router_bias"], ws.ids, ws.wts, ws.router_done, R, cfg.hidden,
                      cfg.n_routed, cfg.top_k, cfg.n_group, cfg.topk_group, sc, int(cfg.norm_topk_prob), cfg.routed_scale, cfg.n_shared)

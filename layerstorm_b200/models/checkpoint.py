@@ -297,6 +297,35 @@ class LazyCheckpoint(Mapping):
             return lambda: s.load(name).reshape(c.kda_heads, -1)
         return lambda: s.load(name)
 
+    def native_q4k(self, key: str) -> Optional[torch.Tensor]:
+        """Raw Q4_K super-blocks ([rows, cols / 256 * 144] uint8) of an expert matrix whose GGUF tensor is stored as Q4_K, else
+        None.  Lets the device model take such experts bit-exactly instead of de-quantising and re-quantising them."""
+        if self.kind != "gguf":
+            return None
+        m = _LAYER_RE.match(key)
+        if not m:
+            return None
+        e = _EXPERT_RE.match(m.group(2))
+        if not e:
+            return None
+        kind, idx, proj = e.group(1), int(e.group(2)), e.group(3)
+        name = f"blk.{int(m.group(1))}.ffn_{proj}_{'exps' if kind == 'experts' else 'shexp'}.weight"
+        s: GgufSource = self.src
+        if not s.has(name):
+            return None
+        from ..formats import gguf as _g
+        if s.ggml_type(name) != _g.GGML_TYPES["Q4_K"]:
+            return None
+        r = s.where[name]
+        shape = r.tensor_shape(name)                       # [E, rows, cols] or [rows, cols]
+        rows, cols = int(shape[-2]), int(shape[-1])
+        if cols % 256:
+            return None
+        per = rows * cols // 256 * 144
+        raw = r.raw(name)
+        off = idx * per if (kind == "experts" and len(shape) == 3) else 0
+        return torch.from_numpy(np.ascontiguousarray(raw[off: off + per])).view(rows, cols // 256 * 144)
+
     def _expert_slice(self, name: str, e: int) -> torch.Tensor:
         """One expert's matrix out of a stacked [E, rows, cols] GGUF tensor, dequantising only its blocks."""
         s: GgufSource = self.src

@@ -461,6 +461,15 @@ class DeviceModel:
         return layer % self.tp_size == self.tp_rank
 
     # ------------------------------------------------------------------ construction
+    def _expert_lin(self, w, name: str, eq: str) -> QLinear:
+        """One expert matrix in the arena's storage format.  Q4_K tensors of a GGUF checkpoint are taken as they are (bit-exact
+        super-blocks); everything else goes through the float path (de-quantise, quantise to the arena format)."""
+        if eq == "gguf_q4_k" and hasattr(w, "native_q4k"):
+            raw = w.native_q4k(name)
+            if raw is not None:
+                return QLinear("gguf_q4_k", raw.shape[0], raw.shape[1] // 144 * 256, raw.to(self.device).contiguous())
+        return QLinear.from_float(w[name], eq, self.device)
+
     def _lin(self, get, name, fmt):
         return QLinear.from_float(get(name), fmt, self.device)
 
@@ -536,7 +545,7 @@ class DeviceModel:
                 arena = ExpertArena(ef, max(len(mine), 1), E_total, dev)
                 for s_, e in enumerate(mine):
                     nm = mo + (f"experts.{e}." if e < cfg.n_routed else f"shared.{e - cfg.n_routed}.")
-                    arena.write_expert(s_, *(QLinear.from_float(w[nm + t], eq, dev) for t in ("gate", "up", "down")))
+                    arena.write_expert(s_, *(m._expert_lin(w, nm + t, eq) for t in ("gate", "up", "down")))
                     arena.slot_of[e] = s_
                 L["arena"] = arena
             else:

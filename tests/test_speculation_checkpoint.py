@@ -216,3 +216,29 @@ def test_gguf_checkpoint_view(tmp_path):
     ref = w[f"layers.{i}.moe.experts.5.gate"]
     assert q.shape == ref.shape and (q - ref).abs().max() < ref.abs().max() / 100          # Q8_0 error
     assert f"layers.{i}.mlp.gate" not in ck
+
+
+def test_gguf_q4k_experts_pass_through_bit_exact(tmp_path):
+    """Experts stored as Q4_K reach the device format as the file's own super-blocks (no de-quantise / re-quantise round trip)."""
+    from layerstorm_b200.formats import gguf as g
+    rows, cols, E = 8, 512, 3
+    stack = (torch.randn(E, rows, cols, generator=torch.Generator().manual_seed(1)) * 0.05).numpy()
+    gw = g.GgufWriter()
+    gw.meta("general.architecture", "deepseek2")
+    t = g.GGML_TYPES["Q4_K"]
+    gw.add("blk.1.ffn_gate_exps.weight", stack, ggml_type=t)
+    gw.add("blk.1.ffn_up_exps.weight", stack, ggml_type=g.GGML_TYPES["Q8_0"])
+    gw.add("blk.1.ffn_down_shexp.weight", stack[0], ggml_type=t)
+    path = str(tmp_path / "q4k.gguf")
+    gw.write(path)
+    _, ck = open_checkpoint(path, tiny_mla_moe())
+    raw = ck.native_q4k("layers.1.moe.experts.2.gate")
+    assert raw is not None and tuple(raw.shape) == (rows, cols // 256 * 144) and raw.dtype == torch.uint8
+    want = g.quantize(t, stack[2])                                   # the writer's own quantisation of that expert
+    assert bytes(raw.numpy().tobytes()) == bytes(want.tobytes())
+    deq = torch.from_numpy(g.dequantize(t, raw.numpy().reshape(-1), rows * cols)).reshape(rows, cols)
+    assert torch.equal(deq, ck["layers.1.moe.experts.2.gate"])      # same values as the float view
+    assert ck.native_q4k("layers.1.moe.experts.2.up") is None        # Q8_0: float path
+    sh = ck.native_q4k("layers.1.moe.shared.0.down")
+    assert sh is not None and tuple(sh.shape) == (rows, cols // 256 * 144)
+    assert ck.native_q4k("layers.1.attn.q_a") is None

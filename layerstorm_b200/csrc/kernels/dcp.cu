@@ -114,6 +114,20 @@ __global__ void __launch_bounds__(32) dcp_localize_kernel(const int* __restrict_
     if (lane == 0) loc_cnt[r] = base;
 }
 
+// Per step row: where this rank stores the new token (index inside its shard, -1 = not its token) and how many of the
+// visible positions [0, len) it owns.
+__global__ void dcp_rows_kernel(const int* __restrict__ row_pos, const int* __restrict__ row_len, int* __restrict__ row_store,
+                                int* __restrict__ row_len_local, int R, int chunk, int nranks, int rank) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= R) return;
+    const int pos = row_pos[r], len = row_len[r];
+    row_store[r] = (pos >= 0 && (pos / chunk) % nranks == rank) ? (pos / (chunk * nranks)) * chunk + pos % chunk : -1;
+    const int span = chunk * nranks, full = len / span, rem = len - full * span;
+    row_len_local[r] = full * chunk + min(max(rem - rank * chunk, 0), chunk);
+}
+
 // o_part: fp32 [R][H][NS][dl], ml_part: fp32 [R][H][NS][2] (local partials of all heads).  grid = (R, H), 128 threads.
 __global__ void __launch_bounds__(128) dcp_scatter_kernel(const float* __restrict__ o_part, const float* __restrict__ ml_part, int R, DcpComm c) {
     pdl_wait();
@@ -198,6 +212,14 @@ LSB_API int lsb_dcp_localize(const void* sel_idx, const void* sel_cnt, int sel_l
     if (chunk <= 0 || nranks <= 0) return -1;
     launch_pdl((dcp_localize_kernel), R, 32, 0, (cudaStream_t)stream, (const int*)sel_idx, (const int*)sel_cnt, sel_ld, (int*)loc_idx, (int*)loc_cnt,
                chunk, nranks, rank);
+    LSB_CHECK_LAUNCH();
+}
+
+LSB_API int lsb_dcp_rows(const void* row_pos, const void* row_len, void* row_store, void* row_len_local, int R, int chunk, int nranks,
+                         int rank, void* stream) {
+    if (chunk <= 0 || nranks <= 0) return -1;
+    launch_pdl((dcp_rows_kernel), (R + 127) / 128, 128, 0, (cudaStream_t)stream, (const int*)row_pos, (const int*)row_len, (int*)row_store,
+               (int*)row_len_local, R, chunk, nranks, rank);
     LSB_CHECK_LAUNCH();
 }
 

@@ -40,7 +40,8 @@ __global__ void mla_prep_kernel(const float* __restrict__ proj, int ldp, int off
                                 const float* __restrict__ inv_freq, bf16* __restrict__ q_c, uint8_t* __restrict__ cache,
                                 const int* __restrict__ block_table, int max_pages, const int* __restrict__ row_seq,
                                 const int* __restrict__ row_pos, int page, int kv_fmt, float eps,
-                                const bf16* __restrict__ tq_rot_t, const float* __restrict__ tq_centroids) {
+                                const bf16* __restrict__ tq_rot_t, const float* __restrict__ tq_centroids,
+                                const int* __restrict__ row_store) {
     __shared__ float red[33];
     extern __shared__ float sm[];   // [max(q_lora, dl + dr)]
     const int r = blockIdx.x, t = threadIdx.x;
@@ -68,10 +69,13 @@ __global__ void mla_prep_kernel(const float* __restrict__ proj, int ldp, int off
         sm[dl + 2 * i] = a; sm[dl + 2 * i + 1] = b;
     }
     amax = block_max(amax, red);   // also orders the shared-memory writes above
-    if (seq < 0) return;
-    const int pg = block_table[(size_t)seq * max_pages + pos / page];
+    // row_store (context-parallel cache shards): index of this row inside the local shard, < 0 = another rank stores it;
+    // the rotary phase above always uses the global position
+    const int spos = row_store ? row_store[r] : pos;
+    if (seq < 0 || spos < 0) return;
+    const int pg = block_table[(size_t)seq * max_pages + spos / page];
     const int rb = kv_row_bytes(kv_fmt, dl, dr);
-    uint8_t* row = cache + ((size_t)pg * page + (pos % page)) * rb;
+    uint8_t* row = cache + ((size_t)pg * page + (spos % page)) * rb;
     if (kv_fmt == 0) {
         bf16* o = reinterpret_cast<bf16*>(row);
         for (int i = t; i < dl + dr; i += blockDim.x) o[i] = __float2bfloat16(sm[i]);
@@ -779,7 +783,8 @@ LSB_API int lsb_kv_row_bytes(int fmt, int dl, int dr) { return kv_row_bytes(fmt,
 LSB_API int lsb_mla_prep(const void* proj, int ldp, int off_qa, int q_lora, int off_kv, int dl, int dr,
                          const void* qa_norm_w, const void* kv_norm_w, const void* inv_freq, void* q_c, void* cache,
                          const void* block_table, int max_pages, const void* row_seq, const void* row_pos, int rows,
-                         int page, int kv_fmt, float eps, const void* tq_rot_t, const void* tq_centroids, void* stream) {
+                         int page, int kv_fmt, float eps, const void* tq_rot_t, const void* tq_centroids, const void* row_store,
+                         void* stream) {
     if (kv_fmt == 2 && (!tq_rot_t || !tq_centroids || dl % 32)) return -1;
     const int n = q_lora > dl + dr ? q_lora : dl + dr;
     launch_pdl((mla_prep_kernel), rows, 256, (size_t)n * 4, (cudaStream_t)stream, (const float*)proj, ldp, off_qa, q_lora, off_kv, dl, dr,
@@ -787,7 +792,7 @@ LSB_API int lsb_mla_prep(const void* proj, int ldp, int off_qa, int q_lora, int 
                                                                       (const float*)inv_freq, (bf16*)q_c, (uint8_t*)cache,
                                                                       (const int*)block_table, max_pages, (const int*)row_seq,
                                                                       (const int*)row_pos, page, kv_fmt, eps, (const bf16*)tq_rot_t,
-                                                                      (const float*)tq_centroids);
+                                                                      (const float*)tq_centroids, (const int*)row_store);
     LSB_CHECK_LAUNCH();
 }
 

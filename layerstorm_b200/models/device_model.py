@@ -340,6 +340,8 @@ class Workspace:
         # many-row KDA path: q / k / v->o / decay / gate [R, C] and beta [R, heads], fp32
         # KDA chunk path: 5 + 2 per-channel arrays, beta, the bf16 (hi | lo) gate activations and an error word
         self.router_done = torch.zeros(1, dtype=i32, device=dev)
+        self.row_store = torch.zeros(R, dtype=i32, device=dev)          # context-parallel KV: shard index of each new row (-1: not ours)
+        self.row_len_local = torch.zeros(R, dtype=i32, device=dev)      # ... and the number of visible positions this rank stores
         self.kda_scratch = z(7 * R * C + R * m.Hk + 2 * R * m.cfg.kda_rank + 16) if (C > 0 and R >= 8) else None
         Hh = m.Hh
         self.q_c = z(R, max(cfg.q_lora, 1), dtype=b16)
@@ -415,6 +417,7 @@ class DeviceModel:
         self.Fd = cfg.dense_inter // tp_size
         self.V_local = cfg.vocab // tp_size
         self._fused = False
+        self.dcp = None
         self.streamer = None      # ExpertStreamer when the VRAM expert cache is capped (runtime/streaming.py)
         self.tq_centroids = None  # TurboQuant reconstruction levels (kv_fmt "tq4")
         self.comm = None          # PeerComm for the fused all-reduces
@@ -448,6 +451,16 @@ class DeviceModel:
         """PeerComm address for the fused all-reduce of the current step, or None (single GPU, or a
         step shape the fused epilogue does not cover - those use NCCL, see ``_reduce``)."""
         return self.comm.ptr if (self.comm is not None and self._fused) else None
+
+    def enable_dcp(self, dcp):
+        """Shard the latent KV cache by token position over the tensor-parallel ranks (``dcp``: a ``parallel.dcp.DcpAttention`` for
+        this model's heads).  Every rank then stores only its own tokens; the engine allocates pages for the local share.  Layers
+        with a DSA indexer keep position-addressed side caches and are not supported in this mode."""
+        if self.cfg.has_indexer:
+            raise ValueError("sharded KV is not wired for models with a DSA indexer")
+        if dcp.world != self.tp_size or dcp.H != self.Hh * self.tp_size or dcp.dl != self.cfg.kv_lora or dcp.dr != self.cfg.qk_rope:
+            raise ValueError("DcpAttention does not match this model's heads / latent sizes / ranks")
+        self.dcp = dcp
 
     def _reduce(self, ws, R):
         """Row-parallel partial -> full sum when the fused in-kernel path is not in use."""
@@ -871,7 +884,7 @@ class DeviceModel:
                      self.idx_tail.get(i), ws.kstash, ws.row_seq, ws.row_pos, ws.row_slot, R, P, 1e-6)
         nat.call("lsb_mla_prep", ws.proj, ldp, off_qa, cfg.q_lora, off_kv, dl, dr, L["qa_norm"], L["kv_norm"], self.inv_freq,
                  ws.q_c, self.kv_cache[i], self.block_table, self.max_pages, ws.row_seq, ws.row_pos, R, self.page,
-                 KV_FMT[self.kv_fmt], cfg.rms_eps, L.get("tq_rot_t"), self.tq_centroids)
+                 KV_FMT[self.kv_fmt], cfg.rms_eps, L.get("tq_rot_t"), self.tq_centroids, ws.row_store if self.dcp is not None else None)
         ldq = self.max_qb
         L["mla_qb"](ws.qproj, ws.q_c, R, ldo=ldq)
         nat.call("lsb_batched_gemv_bf16", ws.q_abs, ws.qproj, L["k_b"], R, Hh, dl, dn, ldq, dn + dr, Hh * (dl + dr), dl + dr,
@@ -888,9 +901,14 @@ class DeviceModel:
                 nat.call("lsb_indexer_topk", ws.scores, ws.max_entries, ws.n_entries, ws.row_len, ws.row_seq,
                          cfg.index_topk // P, P, ws.sel_idx, ws.sel_cnt, ws.sel_ld, R)
             sel_idx, sel_cnt, sel_ld = ws.sel_idx, ws.sel_cnt, ws.sel_ld
-        nat.call("lsb_mla_decode", ws.q_abs, self.kv_cache[i], self.block_table, self.max_pages, ws.row_seq, ws.row_len,
-                 sel_idx, sel_cnt, sel_ld, ws.o_lat, None, ws.o_part, ws.ml_part, R, Hh, dl, dr, self.page,
-                 KV_FMT[self.kv_fmt], ws.NS, cfg.softmax_scale, self.tq_centroids)
+        if self.dcp is not None:
+            # sharded KV: gather the queries of all heads, attend over this rank's token shard, merge on the head owners
+            self.dcp.forward(ws.q_abs, self.kv_cache[i], self.block_table, self.max_pages, ws.row_seq, ws.row_len_local, ws.o_lat, self.page,
+                             KV_FMT[self.kv_fmt], cfg.softmax_scale, tq_centroids=self.tq_centroids, rows=R)
+        else:
+            nat.call("lsb_mla_decode", ws.q_abs, self.kv_cache[i], self.block_table, self.max_pages, ws.row_seq, ws.row_len,
+                     sel_idx, sel_cnt, sel_ld, ws.o_lat, None, ws.o_part, ws.ml_part, R, Hh, dl, dr, self.page,
+                     KV_FMT[self.kv_fmt], ws.NS, cfg.softmax_scale, self.tq_centroids)
         nat.call("lsb_batched_gemv_bf16", ws.attn_v, ws.o_lat, L["v_b"], R, Hh, dv, dl, Hh * dl, dl, Hh * dv, dv, 0, None, None)
         L["mla_o"](ws.sub, ws.attn_v, R, comm=self._cp)
         self._reduce(ws, R)
@@ -905,6 +923,8 @@ class DeviceModel:
         # in-kernel NVLink all-reduce whenever the partial fits the peer buffers (fused GEMV / GEMM epilogues where they exist,
         # a push kernel after the layer otherwise); NCCL only beyond that
         self._fused = self.comm is not None and R * H <= self.comm.cap
+        if self.dcp is not None:
+            nat.call("lsb_dcp_rows", ws.row_pos, ws.row_len, ws.row_store, ws.row_len_local, R, self.dcp.chunk, self.tp_size, self.tp_rank)
         if cfg.mhc:
             nat.call("lsb_embedding", ws.sub, None, self.embed, ws.tok, R, H, 0, cfg.vocab)
             for i, L in enumerate(self.layers):

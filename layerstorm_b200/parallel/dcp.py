@@ -88,11 +88,12 @@ class DcpAttention:
 
     def forward(self, q_local: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, max_pages: int, row_seq: torch.Tensor,
                 row_len_local: torch.Tensor, out: torch.Tensor, page: int, kv_fmt: int, scale: float, sel_idx: Optional[torch.Tensor] = None,
-                sel_cnt: Optional[torch.Tensor] = None, tq_centroids: Optional[torch.Tensor] = None, lse: Optional[torch.Tensor] = None):
+                sel_cnt: Optional[torch.Tensor] = None, tq_centroids: Optional[torch.Tensor] = None, lse: Optional[torch.Tensor] = None,
+                rows: Optional[int] = None):
         """q_local bf16 [R, Hh, D] (this rank's heads); cache / block_table: this rank's token shard; row_len_local int32 [R]:
         owned positions visible to each row (``local_length``); sel_idx / sel_cnt: the indexer's GLOBAL positions (sparse
         layers) or None; out bf16 [R, Hh, dl]."""
-        R = q_local.shape[0]
+        R = rows if rows is not None else q_local.shape[0]          # `rows`: only the first rows of a larger static buffer are live
         assert R <= self.max_rows and q_local.dtype == torch.bfloat16 and q_local.is_contiguous()
         nat.call("lsb_dcp_gather_q", q_local, R, self.ptr)
         li = lc = None

@@ -103,6 +103,8 @@ class Engine:
         """Truncating fork: the child shares the parent's KV pages covering ``prefix_len`` tokens
         (reference counted, copy-on-write on the frontier page).  Recurrent (KDA) state cannot be
         rolled back, so models with KDA layers only fork at the parent's full length."""
+        if getattr(self.model, "dcp", None) is not None:
+            raise NotImplementedError("not available with a sharded KV cache")
         ps = self.seqs[parent]
         prefix_len = ps.length if prefix_len is None else prefix_len
         has_kda = any(self.cfg.is_kda_layer(i) for i in range(self.cfg.n_layers))
@@ -139,6 +141,8 @@ class Engine:
     def hibernate(self, sid: int) -> int:
         """Move every KV page of the sequence to pinned host memory and free its HBM pages.  Returns the pages freed.
         Shared (forked) pages are copied too: the sequence becomes independent of its relatives."""
+        if getattr(self.model, "dcp", None) is not None:
+            raise NotImplementedError("not available with a sharded KV cache")
         s = self.seqs[sid]
         if sid in self.hibernated:
             return 0
@@ -198,6 +202,8 @@ class Engine:
     def rewind(self, sid: int, length: int):
         """Roll the committed frontier back (speculative-verify rejection).  Only valid for models
         without recurrent (KDA) state, whose state cannot be un-applied."""
+        if getattr(self.model, "dcp", None) is not None:
+            raise NotImplementedError("not available with a sharded KV cache")
         s = self.seqs[sid]
         if any(self.cfg.is_kda_layer(i) for i in range(self.cfg.n_layers)) and length < s.length:
             raise RuntimeError("rewind of a recurrent-state sequence is refused")
@@ -212,6 +218,11 @@ class Engine:
         cow = self.pa.cow_frontier(s.slot)          # shared frontier page must become private first
         if cow is not None:
             self._copy_page(*cow)
+        dcp = getattr(self.model, "dcp", None)
+        if dcp is not None:
+            # sharded KV: this rank stores (and pages) only its share of the positions
+            from ..parallel.dcp import local_length
+            new_len = local_length(new_len, dcp.chunk, dcp.world, dcp.rank)
         new = self.pa.extend(s.slot, new_len)
         if new or cow is not None:
             s.pages = self.pa.pages(s.slot)

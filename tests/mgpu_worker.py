@@ -71,6 +71,26 @@ def main():
     if rank == 0:
         print(f"chunk64 tokens_match={good} comm_err={err}", flush=True)
     ok = ok and good and err == 0
+    # sharded KV (context parallel): every rank stores only its token positions; same greedy tokens as the oracle
+    if not cfg.has_indexer:
+        from layerstorm_b200.parallel.dcp import DcpAttention, local_length
+        dcp = DcpAttention(cfg.n_heads, cfg.kv_lora, cfg.qk_rope, max_rows=8, device=dev, chunk=4, n_splits=2)
+        m.enable_dcp(dcp)
+        good = True
+        for use_graph in (False, True):
+            eng = Engine(m, max_seqs=2, max_ctx=128, prefill_chunk=8, max_batch=2, use_graph=use_graph)
+            sid = eng.create_sequence()
+            good = good and eng.prefill(sid, ids[:T].tolist()) == int(ref[T - 1].argmax())
+            for j in range(6):
+                good = good and eng.decode([sid], [int(ids[T + j])])[0] == int(ref[T + j].argmax())
+            pages = len(eng.seqs[sid].pages)
+            good = good and pages == (local_length(T + 6, 4, world, rank) + 15) // 16       # pages for the local share only
+            eng.free_sequence(sid)
+        err = comm.error() or comm_amax.error() or dcp.error()
+        if rank == 0:
+            print(f"sharded_kv tokens_match={good} err={err} local_pages={pages}", flush=True)
+        ok = ok and good and err == 0
+        m.dcp = None
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     if rank == 0:

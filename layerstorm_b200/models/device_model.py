@@ -454,10 +454,9 @@ class DeviceModel:
 
     def enable_dcp(self, dcp):
         """Shard the latent KV cache by token position over the tensor-parallel ranks (``dcp``: a ``parallel.dcp.DcpAttention`` for
-        this model's heads).  Every rank then stores only its own tokens; the engine allocates pages for the local share.  Layers
-        with a DSA indexer keep position-addressed side caches and are not supported in this mode."""
-        if self.cfg.has_indexer:
-            raise ValueError("sharded KV is not wired for models with a DSA indexer")
+        this model's heads).  Every rank then stores only its own tokens; the engine allocates pages for the local share.  The DSA
+        indexer's key cache (its rows are 128-byte class, addressed by global position) stays replicated with a page table of its own.
+        Call before the engine allocates the caches."""
         if dcp.world != self.tp_size or dcp.H != self.Hh * self.tp_size or dcp.dl != self.cfg.kv_lora or dcp.dr != self.cfg.qk_rope:
             raise ValueError("DcpAttention does not match this model's heads / latent sizes / ranks")
         self.dcp = dcp
@@ -751,6 +750,13 @@ class DeviceModel:
         cfg, dev = self.cfg, self.device
         self.num_pages, self.n_slots, self.max_pages = num_pages, n_slots, max_pages_per_seq
         self.block_table = torch.zeros(n_slots, max_pages_per_seq, dtype=torch.int32, device=dev)
+        # the indexer's key cache is addressed by GLOBAL position: with a sharded KV cache it stays replicated and gets its own
+        # identity page table (slot-major, full length per slot); otherwise it shares the sequence's pages
+        self.idx_block_table = self.block_table
+        idx_pages = num_pages
+        if self.dcp is not None and cfg.has_indexer:
+            idx_pages = n_slots * max_pages_per_seq
+            self.idx_block_table = torch.arange(idx_pages, dtype=torch.int32, device=dev).view(n_slots, max_pages_per_seq).contiguous()
         P = cfg.index_kpool
         for i in range(cfg.n_layers):
             if cfg.is_kda_layer(i):
@@ -759,7 +765,7 @@ class DeviceModel:
             else:
                 self.kv_cache[i] = torch.zeros(num_pages, self.page, self.kv_row_bytes, dtype=torch.uint8, device=dev)
                 if cfg.has_indexer and cfg.index_source_layer(i) == i:
-                    self.idx_cache[i] = torch.zeros(num_pages, self.page // P, self.idx_row_bytes, dtype=torch.uint8, device=dev)
+                    self.idx_cache[i] = torch.zeros(idx_pages, self.page // P, self.idx_row_bytes, dtype=torch.uint8, device=dev)
                     if P > 1:
                         self.idx_tail[i] = torch.zeros(n_slots, P, 2, cfg.index_head_dim, dtype=torch.bfloat16, device=dev)
 
@@ -880,7 +886,7 @@ class DeviceModel:
         P = cfg.index_kpool
         if has_idx:
             nat.call("lsb_indexer_k_append", ws.proj, ldp, off_ik, off_ig, L["idx_ln_w"], L["idx_ln_b"], L.get("idx_ape"),
-                     self.inv_freq_idx, cfg.index_rope_dim, self.idx_cache[i], self.block_table, self.max_pages, self.page // P,
+                     self.inv_freq_idx, cfg.index_rope_dim, self.idx_cache[i], self.idx_block_table, self.max_pages, self.page // P,
                      self.idx_tail.get(i), ws.kstash, ws.row_seq, ws.row_pos, ws.row_slot, R, P, 1e-6)
         nat.call("lsb_mla_prep", ws.proj, ldp, off_qa, cfg.q_lora, off_kv, dl, dr, L["qa_norm"], L["kv_norm"], self.inv_freq,
                  ws.q_c, self.kv_cache[i], self.block_table, self.max_pages, ws.row_seq, ws.row_pos, R, self.page,
@@ -896,7 +902,7 @@ class DeviceModel:
                 nat.call("lsb_indexer_q_prep", ws.qproj, ldq, Hh * (dn + dr), ws.proj, ldp, off_iw, cfg.index_n_heads,
                          cfg.index_rope_dim, self.inv_freq_idx, ws.row_pos, ws.q_idx, ws.idx_w, ws.kstash, off_ig,
                          self.idx_tail.get(i), ws.row_seq, ws.row_slot, P, R)
-                nat.call("lsb_indexer_score", ws.q_idx, ws.idx_w, cfg.index_n_heads, self.idx_cache[i], self.block_table,
+                nat.call("lsb_indexer_score", ws.q_idx, ws.idx_w, cfg.index_n_heads, self.idx_cache[i], self.idx_block_table,
                          self.max_pages, self.page // P, ws.row_seq, ws.n_entries, ws.scores, ws.max_entries, R, ws.max_entries)
                 nat.call("lsb_indexer_topk", ws.scores, ws.max_entries, ws.n_entries, ws.row_len, ws.row_seq,
                          cfg.index_topk // P, P, ws.sel_idx, ws.sel_cnt, ws.sel_ld, R)
@@ -904,7 +910,7 @@ class DeviceModel:
         if self.dcp is not None:
             # sharded KV: gather the queries of all heads, attend over this rank's token shard, merge on the head owners
             self.dcp.forward(ws.q_abs, self.kv_cache[i], self.block_table, self.max_pages, ws.row_seq, ws.row_len_local, ws.o_lat, self.page,
-                             KV_FMT[self.kv_fmt], cfg.softmax_scale, tq_centroids=self.tq_centroids, rows=R)
+                             KV_FMT[self.kv_fmt], cfg.softmax_scale, sel_idx=sel_idx, sel_cnt=sel_cnt, tq_centroids=self.tq_centroids, rows=R)
         else:
             nat.call("lsb_mla_decode", ws.q_abs, self.kv_cache[i], self.block_table, self.max_pages, ws.row_seq, ws.row_len,
                      sel_idx, sel_cnt, sel_ld, ws.o_lat, None, ws.o_part, ws.ml_part, R, Hh, dl, dr, self.page,

@@ -72,7 +72,7 @@ def main():
         print(f"chunk64 tokens_match={good} comm_err={err}", flush=True)
     ok = ok and good and err == 0
     # sharded KV (context parallel): every rank stores only its token positions; same greedy tokens as the oracle
-    if not cfg.has_indexer:
+    if True:
         from layerstorm_b200.parallel.dcp import DcpAttention, local_length
         dcp = DcpAttention(cfg.n_heads, cfg.kv_lora, cfg.qk_rope, max_rows=8, device=dev, chunk=4, n_splits=2)
         m.enable_dcp(dcp)

@@ -97,6 +97,8 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="eager launches (for per-kernel profiling)")
     ap.add_argument("--synthetic-fill", action="store_true", help="skip the real prefill; decode over an uninitialised cache")
     ap.add_argument("--extra-batches", default="", help="comma-separated batch sizes measured after the main case in the same process (one more JSON line each)")
+    ap.add_argument("--dcp-chunk", type=int, default=0,
+                    help="N > 1 GPUs: shard the latent KV cache over the ranks in chunks of this many tokens (context parallel); 0 = replicated")
     ap.add_argument("--layers", type=int, default=0, help="smoke runs only: keep the first N layers (the JSON line is then marked invalid)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -138,6 +140,10 @@ def main():
         comm = PeerComm(max(4, bmax, args.prefill_chunk) * cfg.hidden, dev)
         comm_amax = PeerComm(2 * max(bmax, 4), dev)
         model.attach_comm(comm, comm_amax)
+        if args.dcp_chunk > 0:
+            from layerstorm_b200.parallel.dcp import DcpAttention
+            model.enable_dcp(DcpAttention(cfg.n_heads, cfg.kv_lora, cfg.qk_rope, max_rows=max(bmax, args.prefill_chunk), device=dev,
+                                          chunk=args.dcp_chunk, n_splits=4))
     extra = [int(x) for x in args.extra_batches.split(",") if x.strip()]
     cases = [(args.batch, args.synthetic_fill)] + [(b_, True) for b_ in extra]
     eng = None
@@ -238,7 +244,8 @@ def main():
                 "dtype": "bf16", "data": "synthetic token ids, random-init weights",
                 "config": {"model": cfg.name + "-shape", "global_batch": B, "seq_len": args.ctx,
                            "parallelism": f"tp{world}ep{world}" if world > 1 else "single-gpu",
-                           "weights": f"experts {cfg.expert_quant}, attention {cfg.dense_quant}", "kv_cache": "fp8+bf16-rope, 64-token pages",
+                           "weights": f"experts {cfg.expert_quant}, attention {cfg.dense_quant}",
+                       "kv_cache": "fp8+bf16-rope, 64-token pages" + (f", sharded over the ranks in {args.dcp_chunk}-token chunks" if (world > 1 and args.dcp_chunk > 0) else ""),
                            "l2": "inputs larger than L2 (each step streams ~20 GB of weights)",
                            "resident_expert_slots_per_layer_per_gpu": slots, "routed_experts": cfg.n_routed, "expert_miss_flag": miss, "comm_error_word": comm_err,
                            "collectives": ("fused in-kernel NVLink all-reduce (P2P stores + flags) in the GEMV / tcgen05-GEMM / MoE-combine epilogues, argmax exchange; no NCCL on the step path"

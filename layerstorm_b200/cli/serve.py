@@ -166,6 +166,10 @@ def build_engine(cfg: dict, shape: ModelConfig, ckpt: Optional[str], args: argpa
     if not torch.cuda.is_available():
         raise RuntimeError("no CUDA device is visible; use --test-engine to serve from the null engine")
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    if world > 1:
+        # the tensor / expert-parallel engine is SPMD (every rank must issue the same engine calls); the server process has no
+        # follower loop that mirrors the orchestrator's calls on the other ranks yet
+        raise RuntimeError("serve.py drives a single-GPU engine; multi-GPU engines run through bench.py / the parallel tests (one process per GPU)")
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0)))
     torch.cuda.set_device(dev)
     kv_fmt = args.kv_format or {"fp8_e4m3": "fp8", "bf16": "bf16", "fp16": "bf16", "turboquant4": "tq4"}.get(cfg["quantization"]["kv_cache"], "fp8")

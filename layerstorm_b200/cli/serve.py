@@ -166,12 +166,13 @@ def build_engine(cfg: dict, shape: ModelConfig, ckpt: Optional[str], args: argpa
     if not torch.cuda.is_available():
         raise RuntimeError("no CUDA device is visible; use --test-engine to serve from the null engine")
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
-    if world > 1:
-        # the tensor / expert-parallel engine is SPMD (every rank must issue the same engine calls); the server process has no
-        # follower loop that mirrors the orchestrator's calls on the other ranks yet
-        raise RuntimeError("serve.py drives a single-GPU engine; multi-GPU engines run through bench.py / the parallel tests (one process per GPU)")
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0)))
     torch.cuda.set_device(dev)
+    if world > 1:
+        # one process per GPU (torchrun): tensor / expert parallel model shards, in-kernel NVLink collectives
+        import torch.distributed as dist
+        if not dist.is_initialized():
+            dist.init_process_group("nccl", device_id=dev)
     kv_fmt = args.kv_format or {"fp8_e4m3": "fp8", "bf16": "bf16", "fp16": "bf16", "turboquant4": "tq4"}.get(cfg["quantization"]["kv_cache"], "fp8")
     if ckpt and not args.random_weights:
         from ..models.checkpoint import open_checkpoint
@@ -182,6 +183,16 @@ def build_engine(cfg: dict, shape: ModelConfig, ckpt: Optional[str], args: argpa
         model = DeviceModel.random_init(shape, dev, kv_fmt, page, expert_slots="auto", embed_on_host=shape.vocab * shape.hidden > (1 << 28),
                                         tp_rank=rank, tp_size=world)
     max_ctx = sv["max_sequence_length"]
+    if world > 1:
+        from ..parallel.symm import PeerComm
+        chunk_rows = max(4, cfg["orchestrator"]["prefill_chunk_tokens"], cfg["orchestrator"]["max_batch_size"])
+        model.attach_comm(PeerComm(chunk_rows * shape.hidden, dev), PeerComm(2 * max(4, cfg["orchestrator"]["max_batch_size"]), dev))
+        pc_on = sv["prefix_cache"]["enabled"] and sv["prefix_cache"]["max_entries"] > 0
+        if cfg["hardware"].get("dcp_kv_mode") == "sharded" and cfg["hardware"].get("dcp_enabled", True) and not pc_on and not cfg["speculation"]["enabled"]:
+            # context-parallel KV shards (no fork / rewind in this mode, hence only without prefix cache and speculation)
+            from ..parallel.dcp import DcpAttention
+            model.enable_dcp(DcpAttention(shape.n_heads, shape.kv_lora, shape.qk_rope, max_rows=chunk_rows, device=dev,
+                                          chunk=int(cfg["memory"]["kv_cache"].get("dcp_chunk_size", 64))))
     pages = cfg["memory"]["kv_cache"]["max_pages_per_gpu"]
     eng = Engine(model, max_seqs=sv["max_concurrent_requests"] + 4, max_ctx=max_ctx,
                  prefill_chunk=cfg["orchestrator"]["prefill_chunk_tokens"], max_batch=min(4, cfg["orchestrator"]["max_batch_size"]),
@@ -240,6 +251,15 @@ def main(argv: Optional[list[str]] = None) -> int:
         print(json.dumps(cfg, indent=1))
         return 0
     engine = build_engine(cfg, shape, ckpt, args)
+    world = int(os.environ.get("WORLD_SIZE", 1)) if not args.test_engine else 1
+    if world > 1:
+        # SPMD: rank 0 runs the orchestrator and the HTTP server and announces every engine call; the other ranks replay them
+        from ..runtime.spmd import SpmdLeader, control_group, follower_loop
+        grp = control_group()
+        if int(os.environ.get("RANK", 0)) != 0:
+            follower_loop(engine, grp)
+            return 0
+        engine = SpmdLeader(engine, grp)
     server, orch = build_server(cfg, shape, ckpt, engine, args)
     idle = (args.cycle_budget_us or 200) * 1e-6
     t = threading.Thread(target=orch.run, kwargs={"idle_sleep_s": idle}, name="orchestrator", daemon=True)
@@ -249,6 +269,8 @@ def main(argv: Optional[list[str]] = None) -> int:
     finally:
         orch.shutdown()
         t.join(timeout=5)
+        if world > 1:
+            engine.shutdown()
     return 0
 
 

@@ -47,3 +47,14 @@ def test_context_parallel_attention():
            "--master-port", "29539", os.path.join(HERE, "dcp_worker.py")]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert "DCP_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+def test_spmd_leader_and_followers_drive_the_parallel_engine():
+    """Rank 0 issues the engine calls (as the server's orchestrator does), the other ranks replay the announced call stream."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29541", os.path.join(HERE, "spmd_gpu_worker.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert "SPMD_GPU_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]

@@ -134,7 +134,7 @@ def main():
                                     reserve_bytes=int(args.headroom_gib * 2 ** 30), tp_rank=rank, tp_size=world)
     slots = getattr(model, "expert_slots", cfg.n_routed)
     if world > 1:
-        # in-kernel NVLink all-reduce buffers (peer-mapped); NCCL only bootstraps and serves prefill chunks
+        # in-kernel NVLink all-reduce buffers (peer-mapped) sized for the largest step (a prefill chunk); NCCL only bootstraps
         from layerstorm_b200.parallel.symm import PeerComm
         bmax = max([args.batch] + [int(x) for x in args.extra_batches.split(",") if x.strip()])
         comm = PeerComm(max(4, bmax, args.prefill_chunk) * cfg.hidden, dev)

@@ -1,0 +1,22 @@
+"""The benchmark's command-line contract that does not need a GPU: the reference arm and the argument surface."""
+import json
+import os
+import subprocess
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_reference_arm_prints_unavailable_and_exits_zero():
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "1", "--steps", "4", "--warmup", "3"],
+                       capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, r.stderr[-500:]
+    d = json.loads(r.stdout.strip().splitlines()[-1])
+    assert d["impl"] == "reference" and isinstance(d["unavailable"], str) and d["unavailable"]
+
+
+def test_arguments_named_by_the_contract_exist():
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--help"], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0
+    for flag in ("--gpus", "--steps", "--warmup", "--impl", "--model", "--batch", "--ctx", "--prefill-chunk", "--extra-batches", "--dcp-chunk"):
+        assert flag in r.stdout, flag

@@ -257,7 +257,9 @@ def main(argv: Optional[list[str]] = None) -> int:
         from ..runtime.spmd import SpmdLeader, control_group, follower_loop
         grp = control_group()
         if int(os.environ.get("RANK", 0)) != 0:
-            follower_loop(engine, grp)
+            # an engine call that fails (e.g. KV pool exhausted) fails the same way on every rank; the leader's orchestrator handles
+            # it (evict / retry / degrade), the followers just log it and wait for the next call
+            follower_loop(engine, grp, on_error=lambda name, e: log.warning("replayed %s raised %s: %s", name, type(e).__name__, e))
             return 0
         engine = SpmdLeader(engine, grp)
     server, orch = build_server(cfg, shape, ckpt, engine, args)

@@ -31,3 +31,20 @@ def test_two_process_command_stream():
            "--master-port", "29571", os.path.join(HERE, "spmd_worker.py")]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env)
     assert "SPMD_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+def test_follower_reports_mirrored_failures_and_keeps_going():
+    q = collections.deque()
+    eng_l, eng_f = NullEngine(vocab=100, max_seqs=2, max_ctx=64), NullEngine(vocab=100, max_seqs=2, max_ctx=64)
+    lead = SpmdLeader(eng_l, broadcast=q.append)
+    sid = lead.create_sequence()
+    try:
+        lead.free_sequence(sid + 7)                       # fails on the leader ...
+        raised = False
+    except Exception:
+        raised = True
+    lead.prefill(sid, [1, 2])
+    lead.shutdown()
+    seen = []
+    n = follower_loop(eng_f, receive=q.popleft, on_error=lambda name, e: seen.append(name))
+    assert raised and seen == ["free_sequence"] and n == 3 and eng_f.seq_len(sid) == 2     # ... and the same way on the follower

@@ -262,6 +262,12 @@ def main(argv: Optional[list[str]] = None) -> int:
             follower_loop(engine, grp, on_error=lambda name, e: log.warning("replayed %s raised %s: %s", name, type(e).__name__, e))
             return 0
         engine = SpmdLeader(engine, grp)
+    tracer = None
+    from ..utils import perf_trace
+    if perf_trace.enabled():
+        # LS_PERF_TRACE: begin / end records around every engine call, dumped with a report at shutdown
+        tracer = perf_trace.Tracer(gpu=int(os.environ.get("LOCAL_RANK", 0)))
+        engine = perf_trace.TracedEngine(engine, tracer)
     server, orch = build_server(cfg, shape, ckpt, engine, args)
     idle = (args.cycle_budget_us or 200) * 1e-6
     t = threading.Thread(target=orch.run, kwargs={"idle_sleep_s": idle}, name="orchestrator", daemon=True)
@@ -273,6 +279,9 @@ def main(argv: Optional[list[str]] = None) -> int:
         t.join(timeout=5)
         if world > 1:
             engine.shutdown()
+        if tracer is not None:
+            rep = tracer.dump(perf_trace.out_path())
+            log.info("perf trace: %d records -> %s\n%s", rep["records"], perf_trace.out_path(), perf_trace.format_table(rep))
     return 0
 
 

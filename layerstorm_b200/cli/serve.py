@@ -230,6 +230,15 @@ def build_server(cfg: dict, shape: ModelConfig, ckpt: Optional[str], engine, arg
     return LayerStormServer(orch, tok, scfg), orch
 
 
+def apply_live_changes(changes, orch) -> None:
+    """Push hot-reloaded fields into the running orchestrator.  The config tree itself is already updated in place; components that
+    read it per decision (eviction weights, batching waits) need nothing more."""
+    for path, old, new in changes:
+        log.info("config hot reload: %s %r -> %r", path, old, new)
+        if path == "speculation.mtp.max_depth" and getattr(orch, "draft", None) is not None:
+            orch.gamma = max(0, int(new))
+
+
 def main(argv: Optional[list[str]] = None) -> int:
     args = build_parser().parse_args(argv)
     logging.basicConfig(level=getattr(logging, args.log_level.upper()), format="%(asctime)s %(levelname)s %(name)s: %(message)s")
@@ -269,12 +278,20 @@ def main(argv: Optional[list[str]] = None) -> int:
         tracer = perf_trace.Tracer(gpu=int(os.environ.get("LOCAL_RANK", 0)))
         engine = perf_trace.TracedEngine(engine, tracer)
     server, orch = build_server(cfg, shape, ckpt, engine, args)
+    reloader = None
+    if args.config and not args.autoconfig:
+        # hot reload of the live-changeable fields; everything else in an edited file is reported and waits for a restart
+        from ..config.hot_reload import ConfigHotReloader
+        reloader = ConfigHotReloader(args.config, cfg, overrides_from_args(args), on_apply=lambda ch: apply_live_changes(ch, orch))
+        reloader.start()
     idle = (args.cycle_budget_us or 200) * 1e-6
     t = threading.Thread(target=orch.run, kwargs={"idle_sleep_s": idle}, name="orchestrator", daemon=True)
     t.start()
     try:
         server.run(cfg["serving"]["host"], cfg["serving"]["port"], args.log_level)
     finally:
+        if reloader is not None:
+            reloader.stop()
         orch.shutdown()
         t.join(timeout=5)
         if world > 1:

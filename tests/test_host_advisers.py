@@ -1,0 +1,100 @@
+"""Config hot reload, GPU load balancer and prefetch fuser (host-side, CPU only)."""
+import json
+import os
+
+import numpy as np
+
+from layerstorm_b200.config.hot_reload import ConfigHotReloader, diff_configs
+from layerstorm_b200.config.loader import get_path, load_config
+from layerstorm_b200.runtime.balancer import GpuLoadBalancer, PrefetchFuser
+
+
+def _write(path, tree, bump):
+    with open(path, "w") as fh:
+        json.dump(tree, fh)
+    os.utime(path, ns=(bump, bump))          # distinct mtime even on coarse clocks
+
+
+def test_hot_reload_applies_only_live_fields(tmp_path):
+    p = str(tmp_path / "cfg.json")
+    _write(p, {}, 1_000_000_000)
+    cfg = load_config(p)
+    holder = cfg["memory"]["expert_cache"]                       # a component keeps a reference into the tree
+    seen = []
+    r = ConfigHotReloader(p, cfg, on_apply=seen.append)
+    assert r.poll() == []                                        # unchanged file
+    _write(p, {"memory": {"expert_cache": {"eviction_policy": "lru"}}, "orchestrator": {"max_batch_size": 7},
+               "model": {"use_mmap": False}}, 2_000_000_000)
+    applied = r.poll()
+    assert {c[0] for c in applied} == {"memory.expert_cache.eviction_policy", "orchestrator.max_batch_size"}
+    assert holder["eviction_policy"] == "lru" and get_path(cfg, "orchestrator.max_batch_size") == 7
+    assert get_path(cfg, "model.use_mmap") is True               # not live: kept until restart, reported
+    assert [c[0] for c in r.ignored] == ["model.use_mmap"]
+    assert seen == [applied]
+    assert r.poll() == []
+
+
+def test_hot_reload_keeps_config_on_invalid_file(tmp_path):
+    p = str(tmp_path / "cfg.json")
+    _write(p, {}, 1_000_000_000)
+    cfg = load_config(p)
+    before = json.dumps(cfg, sort_keys=True)
+    r = ConfigHotReloader(p, cfg)
+    with open(p, "w") as fh:
+        fh.write("{ not json")
+    os.utime(p, ns=(3_000_000_000, 3_000_000_000))
+    assert r.poll() == [] and r.last_error
+    _write(p, {"orchestrator": {"max_batch_size": -5}}, 4_000_000_000)
+    assert r.poll() == [] and r.last_error
+    assert json.dumps(cfg, sort_keys=True) == before
+    _write(p, {"orchestrator": {"max_batch_size": 3}}, 5_000_000_000)
+    assert [c[0] for c in r.poll()] == ["orchestrator.max_batch_size"] and r.last_error is None
+
+
+def test_diff_configs_lists_changed_leaves():
+    a = load_config(None)
+    b = load_config(None, {"speculation.mtp.max_depth": 9})
+    assert diff_configs(a, b) == [("speculation.mtp.max_depth", get_path(a, "speculation.mtp.max_depth"), 9)]
+
+
+def test_load_balancer_reduces_the_busiest_gpu():
+    rng = np.random.default_rng(0)
+    bal = GpuLoadBalancer(n_layers=2, n_experts=16, n_gpus=4, decay=1.0, threshold=1.1, max_moves=8)
+    hot = [0, 4, 8, 12]                                          # all on GPU 0 under the default placement
+    for _ in range(200):
+        bal.observe(0, list(rng.choice(hot, 2, replace=False)) + list(rng.integers(0, 16, 2)))
+        bal.observe(1, rng.integers(0, 16, 4))                   # balanced layer
+    before = bal.imbalance(0)
+    assert before > 1.5 and bal.imbalance(1) < 1.3
+    moves = bal.propose()
+    assert moves and all(m.layer == 0 and m.src == 0 and m.gain > 0 for m in moves[:1])
+    bal.apply(moves)
+    assert bal.imbalance(0) < before
+    assert bal.gpu_loads(0).sum() == bal.load[0].sum()           # nothing lost
+    # no free slot on any target: nothing proposed
+    bal2 = GpuLoadBalancer(1, 8, 2, decay=1.0)
+    for _ in range(50):
+        bal2.observe(0, [0, 2, 4])
+    assert bal2.propose(slots_free=[0, 0]) == []
+    assert bal2.propose(slots_free=[0, 1])
+
+
+def test_load_balancer_quiet_when_balanced():
+    bal = GpuLoadBalancer(1, 8, 2, decay=1.0)
+    for _ in range(10):
+        bal.observe(0, range(8))
+    assert bal.propose() == []
+
+
+def test_prefetch_fuser_merges_sources_under_a_budget():
+    f = PrefetchFuser(slot_bytes=100, budget_bytes=350)
+    sug = {"prescope": [(3, 5, 0.9), (3, 6, 0.2), (3, 9, 0.5)],
+           "ridge": [(3, 6, 0.9), (4, 1, 0.8), (3, 7, 1.0)],
+           "draft": [(3, 7, 0.5), (3, -1, 1.0)]}
+    out = f.fuse(sug, resident={(3, 9)}, in_flight={(4, 1)})
+    assert len(out) == 3                                         # budget: 3 slots
+    assert [(j, e) for j, e, _ in out] == [(3, 5), (3, 7), (3, 6)]
+    s = dict(((j, e), v) for j, e, v in out)
+    assert abs(s[(3, 7)] - (1 - (1 - 0.5) * (1 - 0.4))) < 1e-6   # two sources agree: combined as independent evidence
+    assert abs(s[(3, 6)] - (1 - (1 - 0.2) * (1 - 0.45))) < 1e-6
+    assert PrefetchFuser(100, 0).fuse(sug) == []

@@ -1,0 +1,133 @@
+"""Hidden-state expert predictors, verification planning, STS calibration and the small speculation policies (CPU only)."""
+import numpy as np
+
+from layerstorm_b200.config.loader import load_config
+from layerstorm_b200.speculation.hidden_predictors import MoeSpeq, Probe
+from layerstorm_b200.speculation.policies import (LayerSkipPolicy, PerformanceObjective, ReasoningMode, SelfSpeculativePlan, ThinkTracker,
+                                                   cosine)
+from layerstorm_b200.speculation.verify_plan import (adaptive_topk, cumulative_survival_ece, fit_sts_temperatures, plan_verification)
+
+H, E, K = 32, 16, 2
+
+
+def _router(rng, n_layers):
+    return [rng.standard_normal((H, E)).astype(np.float32) for _ in range(n_layers)]
+
+
+def _drive(pred, routers, layers, steps, rng, drift=0.05):
+    for _ in range(steps):
+        h = rng.standard_normal(H).astype(np.float32)
+        for l in range(len(routers)):
+            pred.observe_hidden(l, h)
+            if l in layers:
+                pred.observe_routing(l, np.argsort(-(h @ routers[l]))[:K])
+            h = h + drift * rng.standard_normal(H).astype(np.float32)      # the residual stream changes slowly
+        pred.end_step()
+
+
+def test_moe_speq_learns_next_layer_routing():
+    rng = np.random.default_rng(1)
+    layers = [1, 2, 3, 4]
+    routers = _router(rng, 5)
+    p = MoeSpeq(H, E, K, layers, lookahead=2, feat=128, lr=0.5, train_interval=16, train_steps=16, warm_samples=64, confidence_threshold=0.2, seed=3)
+    assert set(p.heads) == {(1, 2), (1, 3), (2, 3), (2, 4), (3, 4)}
+    p.observe_hidden(1, rng.standard_normal(H))
+    assert p.predict(1) == []                                              # cold: no hints
+    _drive(p, routers, layers, 600, rng)
+    assert p.is_warm(1, 2)
+    chance = 2 * K / E
+    assert p.recall(1, 2) > chance + 0.3 and p.recall(2, 4) > chance + 0.2
+    h = rng.standard_normal(H).astype(np.float32)
+    p.observe_hidden(1, h)
+    hints = p.predict(1)
+    assert hints and all(t in (2, 3) and 0 <= e < E and 0.2 <= c <= 1 for t, e, c in hints)
+    truth = set(np.argsort(-(h @ routers[2]))[:K])
+    assert truth & {e for t, e, _ in hints if t == 2}
+
+
+def test_probe_predicts_all_later_layers_from_probe_points():
+    rng = np.random.default_rng(2)
+    layers = list(range(1, 8))
+    routers = _router(rng, 8)
+    p = Probe(H, E, K, layers, n_layers=8, probe_points=(0.25, 0.5), feat=128, lr=0.5, train_interval=16, train_steps=16, warm_samples=64, seed=5)
+    assert p.probe_layers == [2, 4]
+    assert {t for s, t in p.heads if s == 4} == {5, 6, 7} and {t for s, t in p.heads if s == 2} == {3, 4, 5, 6, 7}
+    _drive(p, routers, layers, 500, rng, drift=0.02)
+    assert p.recall(4, 7) > 2 * K / E + 0.3
+    assert p.source_layers() == [2, 4]
+
+
+def test_adaptive_topk_and_verification_plan():
+    w = np.array([0.5, 0.3, 0.1, 0.06, 0.04])
+    assert adaptive_topk(w, 0.75, 8) == [0, 1] and adaptive_topk(w, 0.95, 8) == [0, 1, 2, 3] and adaptive_topk(w, 0.95, 2) == [0, 1]
+    one = lambda *ids: np.bincount(ids, minlength=8).astype(float)
+    gating = {(0, 0): one(1, 2), (0, 1): one(3, 4), (1, 0): one(1, 5), (1, 1): one(3, 6), (2, 0): one(7, 2), (2, 1): one(0, 4)}
+    resident = {(0, 1), (0, 2), (1, 3), (1, 4)}
+    plan = plan_verification(gating, resident, slot_bytes=10_000_000, bandwidth_gbs=10.0, layer_ms=1.0, threshold=0.99, k_max=2, start_ms=1.0)
+    assert plan.transfers == [(0, 5), (1, 6), (0, 7), (1, 0)]              # by first position needed, then layer
+    assert plan.required[0] == {(0, 1), (0, 2), (1, 3), (1, 4)}
+    # 1 ms per transfer; layer 0 starts at 1 ms, layer 1 at 2 ms: position 1's (0,5)@1ms and (1,6)@2ms arrive in time, position 2's (0,7)@3ms does not
+    assert plan.max_depth == 2
+    assert plan_verification(gating, resident, 10_000_000, 10.0, 1.0, 0.99, 2, start_ms=0.0).max_depth == 1
+    assert plan_verification(gating, resident, 10_000_000, 1000.0, 1.0, 0.99, 2, start_ms=1.0).max_depth == 3
+
+
+def test_sts_calibrates_overconfident_survival():
+    rng = np.random.default_rng(0)
+    g, rounds = 4, []
+    true_p = np.array([0.85, 0.8, 0.75, 0.7])
+    for _ in range(4000):
+        p = np.clip(true_p + 0.05 * rng.standard_normal(g), 0.05, 0.95)
+        ok = rng.random(g) < p
+        accepted = int(np.argmin(ok)) if not ok.all() else g
+        raw = 1 / (1 + np.exp(-2.0 * np.log(p / (1 - p))))               # over-confident head: logits doubled
+        rounds.append((raw, accepted))
+    temps = fit_sts_temperatures(rounds, g)
+    assert all(1.4 < t < 2.9 for t in temps), temps                        # recovers the logit scale
+    before, after = cumulative_survival_ece(rounds, [1.0] * g), cumulative_survival_ece(rounds, temps)
+    assert all(a < b for a, b in zip(after, before)) and max(after) < 0.04
+
+
+def test_reasoning_mode_and_think_tracker():
+    cfg = load_config(None, {"speculation.reasoning_mode.enabled": True})["speculation"]["reasoning_mode"]
+    rm, tr = ReasoningMode(cfg), ThinkTracker([7, 8], [9])
+    states = [tr.feed(t) for t in [1, 7, 8, 2, 3, 9, 4]]
+    assert states == [False, False, True, True, True, False, False]
+    ov = rm.overrides(True)
+    assert ov.active and rm.depth(3, ov) == 6 and ov.adaptive_topk_threshold == 0.85 and ov.sparse_verification
+    off = rm.overrides(False)
+    assert not off.active and rm.depth(3, off) == 3
+    assert not ReasoningMode({"enabled": False}).overrides(True).active
+
+
+def test_performance_objective_normalises():
+    po = PerformanceObjective(3, 1)
+    assert abs(po.latency_weight - 0.75) < 1e-12 and po.latency_dominant and abs(po.score(1.0, 0.0) - 0.75) < 1e-12
+    assert PerformanceObjective(0, 0).latency_weight == 0.5
+    assert PerformanceObjective.from_config(load_config(None)).latency_weight > 0
+
+
+def test_layer_skip_policy_gates():
+    cfg = {"enabled": True, "threshold": 0.99, "no_skip_first": 2, "no_skip_last": 2, "min_contiguous": 2, "product_window": 1,
+           "min_acceptance_rate_to_enable": 0.5, "target_skip_fraction": 0.5}
+    pol = LayerSkipPolicy(cfg, 12)
+    sim = {l: 0.999 for l in range(12)}
+    sim[6] = 0.9
+    s = pol.skip_set(sim)
+    assert s == {4, 5, 6, 9}                                               # needs 2 similar skippable layers below; 7, 8 broken by layer 6
+    assert not ({0, 1, 10, 11} & s)
+    assert pol.active(0.6) and not pol.active(0.4)
+    pol2 = LayerSkipPolicy(dict(cfg, min_contiguous=1, product_window=3, product_threshold=0.995), 12)
+    assert 8 not in pol2.skip_set(sim) and 9 not in pol2.skip_set(sim) and 10 not in pol2.skip_set(sim)
+    assert abs(cosine([1, 0], [1, 0]) - 1) < 1e-12 and cosine([0, 0], [1, 0]) == 0.0
+
+
+def test_self_speculative_plan():
+    sp = SelfSpeculativePlan({"draft_expert_count": 1, "draft_confidence_threshold": 0.4}, moe_layers=range(1, 6), n_layers=6, model_top_k=8, max_depth=3)
+    plan = sp.plan({3})
+    assert [p.experts for p in plan] == [0, 1, 1, 0, 1, 1] and plan[3].skip
+    assert abs(sp.expert_fraction(8, {3}) - 4 / 40) < 1e-12
+    assert sp.should_continue(1, 0.5) and not sp.should_continue(1, 0.3) and not sp.should_continue(3, 0.9)
+    sp.record(3, 2)
+    sp.record(3, 1)
+    assert abs(sp.acceptance_rate - 0.5) < 1e-12

@@ -230,13 +230,17 @@ def build_server(cfg: dict, shape: ModelConfig, ckpt: Optional[str], engine, arg
     return LayerStormServer(orch, tok, scfg), orch
 
 
-def apply_live_changes(changes, orch) -> None:
-    """Push hot-reloaded fields into the running orchestrator.  The config tree itself is already updated in place; components that
-    read it per decision (eviction weights, batching waits) need nothing more."""
+def apply_live_changes(changes, orch, cfg: Optional[dict] = None) -> None:
+    """Push hot-reloaded fields into the running components.  The config tree itself is already updated in place."""
+    evict = False
     for path, old, new in changes:
         log.info("config hot reload: %s %r -> %r", path, old, new)
         if path == "speculation.mtp.max_depth" and getattr(orch, "draft", None) is not None:
             orch.gamma = max(0, int(new))
+        evict |= path.startswith("memory.expert_cache.eviction_")
+    streamer = getattr(getattr(getattr(orch, "engine", None), "model", None), "streamer", None)
+    if evict and cfg is not None and streamer is not None:
+        streamer.configure_eviction(cfg["memory"]["expert_cache"])
 
 
 def main(argv: Optional[list[str]] = None) -> int:
@@ -282,7 +286,7 @@ def main(argv: Optional[list[str]] = None) -> int:
     if args.config and not args.autoconfig:
         # hot reload of the live-changeable fields; everything else in an edited file is reported and waits for a restart
         from ..config.hot_reload import ConfigHotReloader
-        reloader = ConfigHotReloader(args.config, cfg, overrides_from_args(args), on_apply=lambda ch: apply_live_changes(ch, orch))
+        reloader = ConfigHotReloader(args.config, cfg, overrides_from_args(args), on_apply=lambda ch: apply_live_changes(ch, orch, cfg))
         reloader.start()
     idle = (args.cycle_budget_us or 200) * 1e-6
     t = threading.Thread(target=orch.run, kwargs={"idle_sleep_s": idle}, name="orchestrator", daemon=True)

@@ -8,6 +8,14 @@
 // impact_weighted_lru | lru | lfu with +1000 duplicate and +500 streaming penalties;
 // ExpertCache::reserve never evicts on its own - callers make room explicitly,
 // src/daemon/moe/moe_progressive.cpp:441-453).
+//
+// Weighted scoring (set_weights): keep-value = -alpha*recency + beta*frequency + gamma*routing_weight +
+// delta*temporal_autocorrelation + epsilon*coactivation + zeta*prefetch_score + eta*hysteresis, every
+// term in [0, 1]; the lowest keep-value is evicted first.  frequency / autocorrelation are per-step
+// EMAs maintained by end_step(); coactivation and prefetch score are hints from the advisers;
+// hysteresis is a small per-slot state machine with asymmetric promote / demote thresholds over the
+// activations of a window of steps, which keeps a briefly idle hot expert from being thrashed.
+// Reference: python/orchestrator/eviction_policy.py (7-term impact-weighted score, HysteresisTracker).
 #include <algorithm>
 #include <cstdint>
 #include <cstring>
@@ -31,6 +39,14 @@ struct Slot {
     uint64_t last_use = 0;
     uint64_t uses = 0;
     float impact = 0.f;      // mean routing weight observed (impact-weighted LRU)
+    float freq = 0.f;        // EMA over steps of "was routed in the step"
+    float autocorr = 0.f;    // EMA over steps of "was routed in this step and the one before"
+    float coact = 0.f;       // hint: co-activation with the experts of the current working set
+    float prefetch = 0.f;    // hint: fused prefetch score (likely needed soon)
+    int step_uses = 0;       // touches since the last end_step()
+    int window_uses = 0;     // touches in the current hysteresis window
+    int hyst = 0;            // hysteresis stage, 0 .. hyst_stages
+    bool prev_step = false;  // routed in the previous step
     int elastic_gen = 0;     // 0 = permanent slot, otherwise the generation of its elastic zone
 };
 
@@ -63,6 +79,8 @@ public:
         if (s < 0) return LSB_ERR_FULL;
         Slot& sl = slots_[s];
         sl.state = kReserved; sl.key = make_key(layer, expert); sl.locks = 0; sl.uses = 0; sl.impact = 0.f;
+        sl.freq = sl.autocorr = sl.coact = sl.prefetch = 0.f;
+        sl.step_uses = sl.window_uses = sl.hyst = 0; sl.prev_step = false;
         sl.last_use = ++tick_;
         map_[sl.key] = s;
         return s;
@@ -102,6 +120,8 @@ public:
         Slot& sl = slots_[s];
         sl.last_use = ++tick_;
         sl.uses++;
+        sl.step_uses++;
+        sl.window_uses++;
         sl.impact += (weight - sl.impact) / (float)std::min<uint64_t>(sl.uses, 64);
     }
     int evict(int layer, int expert) {
@@ -116,12 +136,64 @@ public:
     // another GPU too) are preferred victims.
     double score(const Slot& sl, bool duplicate) const {
         double base;
+        if (weighted_ && policy_ == kImpactWeightedLru) {
+            double recency = (double)(tick_ - sl.last_use) / (double)(tick_ + 1);
+            double hyst = hyst_stages_ > 0 ? (double)sl.hyst / hyst_stages_ : 0.0;
+            base = -w_[0] * recency + w_[1] * sl.freq + w_[2] * std::min(1.f, sl.impact) + w_[3] * sl.autocorr + w_[4] * sl.coact +
+                   w_[5] * sl.prefetch + w_[6] * hyst;
+            if (duplicate) base -= 1000.0;
+            if (sl.zone == kStreaming) base -= 500.0;
+            return base;
+        }
         if (policy_ == kLru) base = (double)sl.last_use;
         else if (policy_ == kLfu) base = (double)sl.uses;
         else base = (double)sl.last_use * (0.25 + (double)sl.impact);
         if (duplicate) base -= 1000.0;
         if (sl.zone == kStreaming) base -= 500.0;
         return base;
+    }
+    // Live-changeable: policy and the seven weights (alpha .. eta).  Switches the impact-weighted policy to the weighted score.
+    void set_weights(int policy, const float* w7) {
+        policy_ = policy;
+        for (int i = 0; i < 7; ++i) w_[i] = w7[i];
+        weighted_ = true;
+    }
+    void set_hysteresis(int stages, int up, int down, int window_steps, float ema) {
+        hyst_stages_ = stages; hyst_up_ = up; hyst_down_ = down; hyst_window_ = std::max(1, window_steps);
+        ema_ = ema;
+    }
+    int set_hint(int layer, int expert, float coactivation, float prefetch_score) {
+        int s = lookup(layer, expert);
+        if (s < 0) return LSB_ERR_NOT_FOUND;
+        if (coactivation >= 0.f) slots_[s].coact = std::min(1.f, coactivation);
+        if (prefetch_score >= 0.f) slots_[s].prefetch = std::min(1.f, prefetch_score);
+        return 0;
+    }
+    // Once per decode step / prefill chunk: fold the step's touches into the per-slot statistics.
+    void end_step() {
+        ++steps_;
+        bool close_window = steps_ % hyst_window_ == 0;
+        for (auto& sl : slots_) {
+            if (sl.state != kReady) continue;
+            bool on = sl.step_uses > 0;
+            sl.freq += ema_ * ((on ? 1.f : 0.f) - sl.freq);
+            sl.autocorr += ema_ * ((on && sl.prev_step ? 1.f : 0.f) - sl.autocorr);
+            sl.prev_step = on;
+            sl.step_uses = 0;
+            if (close_window) {
+                int diff = sl.window_uses - sl.hyst;
+                if (diff >= hyst_up_) sl.hyst = std::min(hyst_stages_, sl.hyst + 1);
+                else if (-diff >= hyst_down_) sl.hyst = std::max(0, sl.hyst - 1);
+                sl.window_uses = 0;
+            }
+        }
+    }
+    int slot_stats(int slot, float* out7) const {
+        if (slot < 0 || slot >= (int)slots_.size()) return LSB_ERR_ARG;
+        const Slot& sl = slots_[slot];
+        out7[0] = (float)((double)(tick_ - sl.last_use) / (double)(tick_ + 1)); out7[1] = sl.freq; out7[2] = sl.impact; out7[3] = sl.autocorr;
+        out7[4] = sl.coact; out7[5] = sl.prefetch; out7[6] = hyst_stages_ > 0 ? (float)sl.hyst / hyst_stages_ : 0.f;
+        return 0;
     }
     // Picks an unlocked ready victim in `zone` (-1 = any); returns slot or -1 and its key.
     int pick_victim(int zone, const uint8_t* duplicate_flags, int n_flags, int* layer, int* expert) const {
@@ -199,7 +271,11 @@ private:
     std::vector<Slot> slots_;
     std::unordered_map<int64_t, int> map_;
     int n_stable_ = 0, policy_ = 0, generation_ = 0;
-    uint64_t tick_ = 0;
+    uint64_t tick_ = 0, steps_ = 0;
+    bool weighted_ = false;
+    float w_[7] = {0.4f, 0.35f, 0.25f, 0.f, 0.f, 0.f, 0.f};
+    int hyst_stages_ = 5, hyst_up_ = 5, hyst_down_ = 1, hyst_window_ = 16;
+    float ema_ = 0.1f;
     ResidencyCb cb_ = nullptr;
     void* user_ = nullptr;
 };
@@ -229,5 +305,12 @@ LSB_RT_API int lsb_ec_count(void* h, int zone, int state) { return ((ExpertCache
 LSB_RT_API int lsb_ec_slot_info(void* h, int slot, int* state, int* zone, int* layer, int* expert, int* locks) {
     return ((ExpertCache*)h)->slot_info(slot, state, zone, layer, expert, locks);
 }
+LSB_RT_API void lsb_ec_set_weights(void* h, int policy, const float* w7) { ((ExpertCache*)h)->set_weights(policy, w7); }
+LSB_RT_API void lsb_ec_set_hysteresis(void* h, int stages, int up, int down, int window_steps, float ema) {
+    ((ExpertCache*)h)->set_hysteresis(stages, up, down, window_steps, ema);
+}
+LSB_RT_API int lsb_ec_set_hint(void* h, int layer, int expert, float coact, float prefetch) { return ((ExpertCache*)h)->set_hint(layer, expert, coact, prefetch); }
+LSB_RT_API void lsb_ec_end_step(void* h) { ((ExpertCache*)h)->end_step(); }
+LSB_RT_API int lsb_ec_slot_stats(void* h, int slot, float* out7) { return ((ExpertCache*)h)->slot_stats(slot, out7); }
 LSB_RT_API void lsb_ec_set_listener(void* h, lsb::ResidencyCb cb, void* user) { ((ExpertCache*)h)->set_listener(cb, user); }
 }

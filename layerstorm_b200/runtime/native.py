@@ -184,6 +184,31 @@ class ExpertCache:
         _check(self.lib.lsb_ec_slot_info(self.h, slot, *[ctypes.cast(ctypes.pointer(x), ctypes.c_void_p) for x in v]), "slot_info")
         return dict(zip(("state", "zone", "layer", "expert", "locks"), (x.value for x in v)))
 
+    WEIGHT_FIELDS = ("eviction_alpha_recency", "eviction_beta_frequency", "eviction_gamma_routing_weight", "eviction_delta_temporal_autocorr",
+                     "eviction_epsilon_coactivation", "eviction_zeta_prefetch_score", "eviction_eta_hysteresis")
+
+    def set_weights(self, policy: str, weights):
+        """Policy + the seven score weights (alpha .. eta); may be called at any time (configuration hot reload)."""
+        w = (ctypes.c_float * 7)(*[float(x) for x in weights])
+        self.lib.lsb_ec_set_weights(self.h, POLICY[policy], ctypes.cast(w, ctypes.c_void_p))
+
+    def configure(self, section: dict):
+        """``section`` = the ``memory.expert_cache`` configuration section."""
+        self.set_weights(section.get("eviction_policy", "impact_weighted_lru"), [section.get(k, 0.0) for k in self.WEIGHT_FIELDS])
+
+    def set_hysteresis(self, stages=5, up=5, down=1, window_steps=16, ema=0.1):
+        self.lib.lsb_ec_set_hysteresis(self.h, stages, up, down, window_steps, float(ema))
+
+    def set_hint(self, layer, expert, coactivation=-1.0, prefetch_score=-1.0):
+        return self.lib.lsb_ec_set_hint(self.h, layer, expert, float(coactivation), float(prefetch_score)) == 0
+
+    def end_step(self): self.lib.lsb_ec_end_step(self.h)
+
+    def slot_stats(self, slot):
+        out = (ctypes.c_float * 7)()
+        _check(self.lib.lsb_ec_slot_stats(self.h, slot, ctypes.cast(out, ctypes.c_void_p)), "slot_stats")
+        return dict(zip(("recency", "frequency", "routing_weight", "temporal_autocorr", "coactivation", "prefetch_score", "hysteresis"), out))
+
     def set_listener(self, fn):
         CB = ctypes.CFUNCTYPE(None, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int)
         self._cb = CB(lambda user, layer, expert, slot, resident: fn(layer, expert, slot, bool(resident)))

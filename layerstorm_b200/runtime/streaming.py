@@ -36,6 +36,7 @@ class ExpertStreamer:
         self.te = rt.TransferEngine(n_gpus=1, levels=3, waterline=waterline)
         self.layers: Dict[int, dict] = {}
         self.prefetch = prefetch
+        self.weighted = False                                    # True once configure_eviction() has installed the weighted score
         self.stats = {"hits": 0, "misses": 0, "waves": 0, "bytes_h2d": 0}
         self._issued: List[tuple] = []
         cfg = model.cfg
@@ -176,6 +177,8 @@ class ExpertStreamer:
             done = set(wave)
             todo = [e for e in todo if e not in done]
             self.stats["waves"] += 1
+        if self.weighted:
+            cache.end_step()                                     # fold this pass's touches into frequency / autocorrelation / hysteresis
         if self.prefetch:
             self._prefetch_next(model, li, ws, R, list(need))
         return st["present"]
@@ -217,6 +220,13 @@ class ExpertStreamer:
                 if not self._reserve(nxt, st, e, priority=2):
                     break
         self._issue()                                            # copies overlap the rest of this layer and the next attention
+
+    def configure_eviction(self, section: dict):
+        """Switch every layer's cache to the weighted eviction score of the ``memory.expert_cache`` configuration section (policy + the
+        seven weights).  May be called again at any time: the fields are live-changeable."""
+        self.weighted = True
+        for st in self.layers.values():
+            st["cache"].configure(section)
 
     def summary(self) -> dict:
         tot = max(1, self.stats["hits"] + self.stats["misses"])

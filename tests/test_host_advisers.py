@@ -98,3 +98,41 @@ def test_prefetch_fuser_merges_sources_under_a_budget():
     assert abs(s[(3, 7)] - (1 - (1 - 0.5) * (1 - 0.4))) < 1e-6   # two sources agree: combined as independent evidence
     assert abs(s[(3, 6)] - (1 - (1 - 0.2) * (1 - 0.45))) < 1e-6
     assert PrefetchFuser(100, 0).fuse(sug) == []
+
+
+def test_expert_cache_weighted_score_and_hysteresis():
+    from layerstorm_b200.runtime import native as rt
+    ec = rt.ExpertCache(4, 0)
+    for e in range(4):
+        ec.reserve(0, e)
+        ec.mark_ready(0, e)
+    section = load_config(None)["memory"]["expert_cache"]
+    ec.configure(dict(section, eviction_alpha_recency=0.0, eviction_beta_frequency=1.0, eviction_gamma_routing_weight=0.0))
+    ec.set_hysteresis(stages=3, up=2, down=1, window_steps=4, ema=0.25)
+    for step in range(16):                                   # expert 0 every step, 1 every other step, 2 once, 3 never
+        ec.touch(0, 0, 0.5)
+        if step % 2 == 0:
+            ec.touch(0, 1, 0.2)
+        if step == 3:
+            ec.touch(0, 2, 0.9)
+        ec.end_step()
+    st = [ec.slot_stats(ec.lookup(0, e)) for e in range(4)]
+    assert st[0]["frequency"] > st[1]["frequency"] > st[2]["frequency"] > st[3]["frequency"] == 0.0
+    assert st[0]["temporal_autocorr"] > 0.9 * st[0]["frequency"] and st[1]["temporal_autocorr"] == 0.0
+    assert st[0]["hysteresis"] == 1.0 and st[3]["hysteresis"] == 0.0
+    assert ec.pick_victim()[2] == 3                          # frequency only: the never-used expert goes first
+    ec.touch(0, 3, 0.1)                                      # most recent now, still the least frequent
+    assert ec.pick_victim()[2] == 3
+    ec.set_weights("impact_weighted_lru", [1.0, 0, 0, 0, 0, 0, 0])     # hot reload: recency only
+    assert ec.pick_victim()[2] == 2
+    ec.set_weights("impact_weighted_lru", [0.0, 0, 0, 0, 0, 1.0, 0])   # prefetch score protects an expert the advisers expect
+    for e in (0, 1, 3):
+        assert ec.set_hint(0, e, prefetch_score=0.5)
+    assert ec.pick_victim()[2] == 2
+    assert ec.set_hint(0, 2, prefetch_score=0.9) and ec.pick_victim()[2] in (0, 1, 3)
+    assert not ec.set_hint(5, 5, 0.1, 0.1)
+    # hysteresis: an idle window demotes one stage at a time
+    ec.set_weights("impact_weighted_lru", [0, 0, 0, 0, 0, 0, 1.0])
+    for _ in range(4):
+        ec.end_step()
+    assert abs(ec.slot_stats(ec.lookup(0, 0))["hysteresis"] - 2 / 3) < 1e-6

@@ -171,3 +171,50 @@ class SelfSpeculativePlan:
     @property
     def acceptance_rate(self) -> float:
         return self.accepted / self.steps if self.steps else 0.0
+
+
+# --------------------------------------------------------------------------------------------------------- MTP planner
+@dataclass
+class MtpStep:
+    step: int
+    layer: int            # index of the MTP block to run: n_layers + step % n_mtp_layers (blocks are reused cyclically)
+    input_token: int      # -1: the token sampled by the previous step
+
+
+class MtpDraftPlanner:
+    """Planner of a multi-token-prediction draft: which MTP block each draft step runs, when to stop, acceptance statistics.
+    Step k combines the previous hidden state with the embedding of token k, runs MTP block ``k % n_mtp`` and the shared output head.
+    Reference: python/orchestrator/mtp_draft.py (cyclic block reuse, dynamic depth gating on draft confidence, acceptance tracking)."""
+
+    def __init__(self, cfg: dict, n_layers: int, n_mtp_layers: int):
+        """``cfg`` = the ``speculation.mtp`` section."""
+        self.enabled = bool(cfg.get("enabled", True)) and n_mtp_layers > 0
+        self.max_depth = int(cfg.get("max_depth", 3))
+        self.dynamic = bool(cfg.get("dynamic_depth", True))
+        self.conf_thr = float(cfg.get("confidence_threshold", 0.4))
+        self.batched_verify = bool(cfg.get("batched_verify", True))
+        self.L, self.M = n_layers, n_mtp_layers
+        self.drafts = self.steps = self.accepted = 0
+
+    def layer_of(self, step: int) -> int:
+        return self.L + step % self.M
+
+    def plan(self, first_token: int, depth: Optional[int] = None) -> List[MtpStep]:
+        if not self.enabled:
+            return []
+        d = self.max_depth if depth is None else min(depth, self.max_depth)
+        return [MtpStep(k, self.layer_of(k), first_token if k == 0 else -1) for k in range(d)]
+
+    def should_continue(self, step: int, confidence: float) -> bool:
+        if step + 1 >= self.max_depth:
+            return False
+        return not self.dynamic or confidence >= self.conf_thr
+
+    def record(self, drafted: int, accepted: int):
+        self.drafts += 1
+        self.steps += drafted
+        self.accepted += accepted
+
+    @property
+    def acceptance_rate(self) -> float:
+        return self.accepted / self.steps if self.steps else 0.0

@@ -123,3 +123,43 @@ def cumulative_survival_ece(rounds, temps: Sequence[float]) -> List[float]:
         label = np.array([1.0 if a > k else 0.0 for _, a in use])
         out.append(expected_calibration_error(pred, label))
     return out
+
+
+# ---------------------------------------------------------------------------------------------------------------- coverage
+@dataclass
+class CoverageReport:
+    per_position_min: List[float]            # lowest per-layer coverage of each drafted position
+    per_position_mode: List[int]             # 0 = every selected expert resident, 1 = some missing (fetch before verifying)
+    depth: int                               # longest prefix whose every layer meets the floor
+    truncation_reason: str = ""
+
+
+def coverage_depth(draft_gating: np.ndarray, resident: Set[Tuple[int, int]], moe_layers: Sequence[int], floor: float = 0.85,
+                   threshold: float = 0.92, k_max: int = 8) -> CoverageReport:
+    """Residency coverage of a drafted block: ``draft_gating`` is [positions, moe layers, experts].  Coverage of (position, layer) =
+    gating weight of the selected experts that are resident / weight of all selected experts.  The verification pass of this engine
+    always runs every selected expert (missing ones are fetched first), so the depth is advice on how much of the draft can be verified
+    WITHOUT waiting for transfers, not a licence to mask experts.
+    Reference: python/orchestrator/verifier.py (analyze_moe_coverage / compute_verifiable_depth with the verification quality floor)."""
+    g = np.asarray(draft_gating, np.float64)
+    mins, modes, depth, reason, open_ = [], [], 0, "", True
+    for d in range(g.shape[0]):
+        lo, mode = 1.0, 0
+        for m, layer in enumerate(moe_layers):
+            sel = adaptive_topk(g[d, m], threshold, k_max)
+            tot = sum(g[d, m, e] for e in sel)
+            res = sum(g[d, m, e] for e in sel if (layer, e) in resident)
+            cov = res / tot if tot > 0 else 0.0
+            if cov < 1.0:
+                mode = 1
+            if cov < lo:
+                lo = cov
+                if cov < floor and open_ and not reason:
+                    reason = f"coverage {cov:.2f} below floor at position {d}, layer {layer}"
+        mins.append(lo)
+        modes.append(mode)
+        if open_ and lo >= floor:
+            depth += 1
+        else:
+            open_ = False
+    return CoverageReport(mins, modes, depth, reason if depth < g.shape[0] else "")

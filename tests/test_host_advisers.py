@@ -136,3 +136,38 @@ def test_expert_cache_weighted_score_and_hysteresis():
     for _ in range(4):
         ec.end_step()
     assert abs(ec.slot_stats(ec.lookup(0, 0))["hysteresis"] - 2 / 3) < 1e-6
+
+
+def test_work_queue_orders_and_cancels():
+    from layerstorm_b200.runtime.scheduling import DONE, PENDING, READY, RUNNING, WorkQueue
+    q = WorkQueue()
+    q.insert(("a", 0, "attn"), 1.0)
+    q.insert(("a", 1, "moe"), 5.0)
+    q.insert(("b", 0, "attn"), 5.0)
+    q.insert(("b", 1, "moe"), 9.0, status=PENDING)
+    assert q.pop().key == ("a", 1, "moe")                        # highest priority, FIFO among equals; PENDING is not handed out
+    assert q.get(("a", 1, "moe")).status == RUNNING
+    q.update_priority(("a", 0, "attn"), 7.0)
+    assert q.pop().key == ("a", 0, "attn")
+    q.update_status(("b", 1, "moe"), READY)
+    assert q.pop().key == ("b", 1, "moe")
+    q.update_status(("a", 1, "moe"), DONE)
+    assert len(q) == 3 and q.cancel_by_request("b") == 2 and len(q) == 1
+    assert q.pop() is None and [i.key for i in q.by_status(RUNNING)] == [("a", 0, "attn")]
+    q.insert(("c", 0, "x"), 1.0)
+    q.insert(("c", 1, "x"), 2.0)
+    assert [i.key[1] for i in q.pop_n(5)] == [1, 0]
+
+
+def test_transfer_planner_budget_dedup_and_zones():
+    from layerstorm_b200.runtime.scheduling import Candidate, TransferPlanner, ZONE_STABLE, ZONE_STREAMING
+    tp = TransferPlanner(n_gpus=2, expert_bytes=20_000_000, link_gbs=[50.0, 50.0], cycle_budget_us=1000.0, max_inflight_per_gpu=3)
+    # 50 GB/s * 1 ms = 50 MB per cycle and GPU: two experts of 20 MB fit
+    cands = [Candidate(1, 1, 0, 0.9, needed_in_us=5000), Candidate(1, 2, 0, 0.5), Candidate(1, 3, 0, 0.4), Candidate(1, 4, 0, 0.001),
+             Candidate(2, 1, 1, 0.8), Candidate(2, 2, 1, 0.75), Candidate(2, 3, 1, 0.6), Candidate(2, 1, 1, 0.3), Candidate(9, 9, 5, 1.0)]
+    plan = tp.plan_transfers(cands, resident={1: {(2, 1)}}, in_flight={1: {(2, 2)}}, transfer_latency_us={0: 400.0})
+    got = [(t.gpu, t.layer, t.expert) for t in plan]
+    assert got == [(0, 1, 1), (1, 2, 3), (0, 1, 2)]              # resident, in flight, below threshold, bad GPU and over budget are skipped
+    assert plan[0].zone == ZONE_STABLE and plan[0].start_delay_us == 4600.0 and plan[2].zone == ZONE_STREAMING and plan[2].start_delay_us == 0.0
+    ev = tp.plan_evictions({0: 3, 1: 1}, {0: 1, 1: 4}, victims_of=lambda g, n: [(7, i) for i in range(10)])
+    assert ev == {0: [(7, 0), (7, 1)]}

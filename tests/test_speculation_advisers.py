@@ -131,3 +131,50 @@ def test_self_speculative_plan():
     sp.record(3, 2)
     sp.record(3, 1)
     assert abs(sp.acceptance_rate - 0.5) < 1e-12
+
+
+def test_coverage_depth_truncates_at_the_floor():
+    from layerstorm_b200.speculation.verify_plan import coverage_depth
+    g = np.zeros((3, 2, 8))
+    g[0, 0, [1, 2]] = [0.6, 0.4]; g[0, 1, [3, 4]] = [0.5, 0.5]
+    g[1, 0, [1, 5]] = [0.9, 0.1]; g[1, 1, [3, 4]] = [0.5, 0.5]
+    g[2, 0, [6, 7]] = [0.5, 0.5]; g[2, 1, [3, 4]] = [0.5, 0.5]
+    resident = {(10, 1), (10, 2), (11, 3), (11, 4)}
+    rep = coverage_depth(g, resident, moe_layers=[10, 11], floor=0.85, threshold=0.99)
+    assert rep.depth == 2 and rep.per_position_mode == [0, 1, 1]
+    assert abs(rep.per_position_min[1] - 0.9) < 1e-9 and rep.per_position_min[2] == 0.0
+    assert "position 2, layer 10" in rep.truncation_reason
+    assert coverage_depth(g, resident | {(10, 6), (10, 7)}, [10, 11], 0.85, 0.99).depth == 3
+
+
+def test_mtp_planner_cycles_blocks_and_gates_depth():
+    from layerstorm_b200.speculation.policies import MtpDraftPlanner
+    cfg = load_config(None)["speculation"]["mtp"]
+    p = MtpDraftPlanner(dict(cfg, max_depth=5), n_layers=61, n_mtp_layers=2)
+    steps = p.plan(first_token=42)
+    assert [s.layer for s in steps] == [61, 62, 61, 62, 61] and steps[0].input_token == 42 and steps[1].input_token == -1
+    assert len(p.plan(1, depth=2)) == 2
+    assert p.should_continue(0, 0.9) and not p.should_continue(0, 0.1) and not p.should_continue(4, 0.99)
+    p.record(5, 3)
+    assert abs(p.acceptance_rate - 0.6) < 1e-12
+    assert MtpDraftPlanner(cfg, 61, 0).plan(1) == []
+
+
+def test_residual_correction_learns_the_missing_experts():
+    from layerstorm_b200.speculation.residual_correction import ResidualCorrection
+    rng = np.random.default_rng(0)
+    Hh, Ee = 16, 8
+    A, B = 0.3 * rng.standard_normal((Hh, Hh)).astype(np.float32), rng.standard_normal((Ee, Hh)).astype(np.float32)
+    rc = ResidualCorrection(Hh, Ee, mlp_hidden=48, lr=0.1, train_interval=16, train_steps=32, warm_samples=64, seed=1)
+    assert not rc.predict(3, np.zeros(Hh), np.zeros(Ee)).any()                 # cold: zero correction
+    for _ in range(1500):
+        top1 = rng.standard_normal(Hh).astype(np.float32)
+        gate = rng.dirichlet(np.ones(Ee)).astype(np.float32)
+        full = top1 + np.tanh(top1 @ A) + gate @ B
+        rc.record(3, top1, gate, full)
+        rc.end_step()
+    assert rc.is_warm(3) and rc.error_reduction(3) > 0.6
+    top1, gate = rng.standard_normal((4, Hh)).astype(np.float32), rng.dirichlet(np.ones(Ee), 4).astype(np.float32)
+    target = np.tanh(top1 @ A) + gate @ B
+    pred = rc.predict(3, top1, gate)
+    assert pred.shape == (4, Hh) and ((pred - target) ** 2).sum() < 0.5 * (target ** 2).sum()

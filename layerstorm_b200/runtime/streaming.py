@@ -17,6 +17,7 @@ Reference behaviour: progressive FETCH_AND_RUN_MOE waves with an explicit evict 
 """
 from __future__ import annotations
 
+import os
 import time
 from typing import Dict, List, Optional
 
@@ -36,6 +37,8 @@ class ExpertStreamer:
         self.te = rt.TransferEngine(n_gpus=1, levels=3, waterline=waterline)
         self.layers: Dict[int, dict] = {}
         self.prefetch = prefetch
+        self.trace = open(os.environ["LS_ROUTING_TRACE"], "w") if os.environ.get("LS_ROUTING_TRACE") else None
+        self.trace_step = 0
         self.weighted = False                                    # True once configure_eviction() has installed the weighted score
         self.stats = {"hits": 0, "misses": 0, "waves": 0, "bytes_h2d": 0}
         self._issued: List[tuple] = []
@@ -62,6 +65,7 @@ class ExpertStreamer:
             del old
         torch.cuda.synchronize(self.dev)
         torch.cuda.empty_cache()
+        self._last_layer = max(self.layers) if self.layers else -1
         model.streamer = self
 
     # ------------------------------------------------------------------ residency
@@ -128,6 +132,10 @@ class ExpertStreamer:
             if e in st["mine"]:
                 need[e] = need.get(e, 0.0) + w
         todo = sorted(need, key=lambda e: -need[e])              # heaviest experts first
+        if self.trace is not None:                               # LS_ROUTING_TRACE: input of the offline cache replay (utils/cache_sim.py)
+            self.trace.write(f"{self.trace_step} {li} {' '.join(str(e) for e in todo)}\n")
+            if li == self._last_layer:
+                self.trace_step += 1
         model._moe_prepare(arena, ws, R)
         st["present"].fill_(-1)
         while todo:

@@ -419,6 +419,7 @@ class DeviceModel:
         self._fused = False
         self.dcp = None
         self.streamer = None      # ExpertStreamer when the VRAM expert cache is capped (runtime/streaming.py)
+        self.drift = None         # dict: eager steps store every layer's output rows here (input of utils/determinism_probe.py drift)
         self.tq_centroids = None  # TurboQuant reconstruction levels (kv_fmt "tq4")
         self.comm = None          # PeerComm for the fused all-reduces
         self.comm_amax = None     # PeerComm for the argmax exchange
@@ -945,6 +946,8 @@ class DeviceModel:
                 nat.call("lsb_mhc_post_pre", ws.x, ws.resid, ws.sub, ws.post, ws.comb, fn, sc, base, L["ffn_norm"], ws.part, R, H, n,
                          1, cfg.hc_sinkhorn_iters, cfg.hc_eps, cfg.rms_eps, cfg.hc_post_mult, ws.hc_done, ws.hc_pre, self._cp)
                 self._ffn(i, L, ws, R)
+                if self.drift is not None:
+                    self.drift[f"layer{i:03d}.ffn_out"] = ws.sub[:R].float().cpu()
             nat.call("lsb_mhc_contract_norm", ws.x, ws.resid, ws.sub, ws.post, ws.comb, self.final_norm, R, H, n, cfg.rms_eps, self._cp)
         else:
             resid = ws.resid.view(-1)[: ws.R * H].view(ws.R, H)
@@ -959,8 +962,13 @@ class DeviceModel:
                 self._ffn(i, L, ws, R)
                 nxt = self.layers[i + 1]["attn_norm"] if i + 1 < cfg.n_layers else self.final_norm
                 nat.call("lsb_add_rmsnorm", ws.x, resid, ws.sub, nxt, R, H, cfg.rms_eps, self._cp)
+                if self.drift is not None:
+                    self.drift[f"layer{i:03d}.resid"] = resid[:R].float().cpu()
         xr = ws.x[logit_row0: logit_row0 + n_logit_rows]
         self.head(ws.logits, xr, n_logit_rows)
+        if self.drift is not None:
+            self.drift["final_norm_out"] = xr.float().cpu()
+            self.drift["logits"] = ws.logits[:n_logit_rows].float().cpu()
 
     def argmax(self, ws: Workspace, n_rows: int):
         """Greedy token per row; with a vocabulary-parallel head the per-rank winners are exchanged

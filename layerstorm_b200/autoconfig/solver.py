@@ -24,7 +24,7 @@ from typing import Any
 
 from ..config.loader import ConfigError, deep_merge, get_path, load_config, model_section_from, set_path, validate
 from ..models.config import ModelConfig
-from . import sizing
+from . import sizing, templates
 from .hwdetect import HardwareInfo
 
 PINNABLE = (
@@ -180,7 +180,8 @@ def solve(mc: ModelConfig, hw: HardwareInfo, levers: Levers | None = None, pins:
     idx_modes = ["replicated", "local"] if mc.has_indexer else ["replicated"]
     if "hardware.dcp_indexer_mode" in pins:
         idx_modes = [pins["hardware.dcp_indexer_mode"]]
-    chunk = pins.get("orchestrator.prefill_chunk_tokens", 256)
+    base_chunk = (base or {}).get("orchestrator", {}).get("prefill_chunk_tokens")
+    chunk = pins.get("orchestrator.prefill_chunk_tokens", base_chunk or templates.prefill_chunk_for(conc0))
     min_ratio = levers.vram_expert_ratio or 0.0
 
     # E1: the lattice, in relaxation order
@@ -299,6 +300,10 @@ def solve(mc: ModelConfig, hw: HardwareInfo, levers: Levers | None = None, pins:
     cfg["autoconfig"].update({"enabled": True, "vram_expert_ratio": round(rep.vram_expert_ratio, 4),
                               "total_active_context_tokens": best.concurrency * best.seq_len, "prefer": levers.prefer,
                               "accuracy": levers.accuracy, "fingerprint": hw.fingerprint()})
+    # T1: family template for what neither geometry nor hardware decides; the base configuration and pins win
+    user_set = {p for p, _ in templates._leaves(base or {})} | set(pins)
+    copied = templates.apply_template(cfg, mc.architecture, user_set)
+    step("T1", {"family": templates.family_of(mc.architecture), "copied": copied}, "family template (kind = template); base configuration and pins win")
     for p, v in pins.items():
         set_path(cfg, p, v)
     step("M1", {"expert_slots_per_layer_per_gpu": rep.expert_slots_per_layer, "owned_experts_per_gpu": rep.expert_slots_wanted,

@@ -29,11 +29,20 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--hardware", help="JSON hardware descriptor to plan for instead of probing this machine")
     p.add_argument("--assume-gpus", type=int, default=None, help="plan for N B200 GPUs (no probe)")
     p.add_argument("--print", dest="show", action="store_true", help="print the explanation")
+    p.add_argument("--probe-only", action="store_true", help="print what the model path is (format, shape, quantisation, size) and exit")
     return p
 
 
 def main(argv: Optional[list[str]] = None) -> int:
     args = build_parser().parse_args(argv)
+    if args.probe_only:
+        from ..autoconfig.modelprobe import probe
+        try:
+            print(json.dumps(probe(args.model).to_dict(), indent=1))
+        except (OSError, ValueError) as e:
+            print(f"--model: {e}", file=sys.stderr)
+            return 2
+        return 0
     try:
         base = json.load(open(args.config)) if args.config else None
         shape, _ = resolve_model(args, base)

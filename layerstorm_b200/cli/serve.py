@@ -103,6 +103,12 @@ def resolve_model(args: argparse.Namespace, cfg: Optional[dict]) -> tuple[Option
         cj = os.path.join(d, "config.json")
         if os.path.exists(cj):
             return from_hf_config(cj), src
+        if src.endswith(".gguf") or os.path.isdir(src):
+            from ..autoconfig.modelprobe import probe
+            try:
+                return probe(src).shape, src                     # GGUF metadata carries the shape
+            except ValueError:
+                pass
         return None, src
     if src:
         raise ConfigError([f"--model: '{src}' is neither a path nor one of the built-in shapes {sorted(MODEL_PRESETS)}"])

@@ -341,9 +341,11 @@ def open_checkpoint(path: str, cfg: Optional[ModelConfig] = None) -> tuple[Model
         src = GgufSource(path)
         if cfg is None:
             cj = os.path.join(os.path.dirname(path), "config.json")
-            if not os.path.exists(cj):
-                raise FileNotFoundError("a GGUF checkpoint needs an explicit ModelConfig or a config.json beside it")
-            cfg = from_hf_config(cj)
+            if os.path.exists(cj):
+                cfg = from_hf_config(cj)
+            else:
+                from ..autoconfig.modelprobe import shape_from_gguf
+                cfg = shape_from_gguf(src)                      # llama.cpp metadata keys of the file itself
         return cfg, LazyCheckpoint(cfg, src, "gguf")
     d = path if os.path.isdir(path) else os.path.dirname(path)
     if cfg is None:

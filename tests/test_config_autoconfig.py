@@ -236,3 +236,37 @@ def test_serve_cli_builds_a_working_server_on_the_null_engine():
     finally:
         orch.shutdown()
         t.join(timeout=5)
+
+
+def test_family_template_is_copied_and_pins_win():
+    from layerstorm_b200.autoconfig import Levers, solve, synthetic, templates
+    from layerstorm_b200.models.config import glm_5_3_flash, deepseek_v3_2
+    res = solve(glm_5_3_flash(), synthetic(8), Levers(None, None, "balanced", "standard"), {"serving.max_concurrent_requests": 4})
+    assert res.config["serving"]["tool_call_parser"] == "glm47" and res.config["serving"]["reasoning_parser"] == "glm45"
+    assert res.config["orchestrator"]["prefill_chunk_tokens"] == 2048          # few concurrent requests: throughput-sized chunks
+    t1 = [s for s in res.explain["steps"] if s["step"] == "T1"][0]
+    assert t1["decision"]["family"] == "glm5_next" and "serving.tool_call_parser" in t1["decision"]["copied"]
+    res2 = solve(deepseek_v3_2(), synthetic(8), Levers(None, None, "balanced", "standard"), {},
+                 {"serving": {"reasoning_parser": "glm45", "tool_call_parser": "hermes"}})
+    assert res2.config["serving"]["tool_call_parser"] == "hermes" and res2.config["serving"]["reasoning_parser"] == "glm45"
+    t1 = [s for s in res2.explain["steps"] if s["step"] == "T1"][0]
+    assert "serving.reasoning_parser" not in t1["decision"]["copied"] and "serving.tool_call_parser" not in t1["decision"]["copied"]
+    assert res2.config["orchestrator"]["prefill_chunk_tokens"] == 256           # default concurrency 32
+    assert templates.family_of("unknown") == "mla_dsa" and templates.template_for("deepseek_v4")["serving"]["tool_call_parser"] == "deepseek_v4"
+
+
+def test_champion_comparison(tmp_path):
+    from layerstorm_b200.autoconfig import compare as cmp
+    champ = {"metric": "decode_tok_s", "value": 100.0, "higher_is_better": True, "e2e": {"value": 95.0}, "extra": {"ttft_ms": 400.0, "prefill_tok_s": 5000.0}}
+    cand = {"metric": "decode_tok_s", "value": 98.0, "higher_is_better": True, "e2e": {"value": 96.0}, "extra": {"ttft_ms": 380.0, "prefill_tok_s": 5100.0}}
+    rep = cmp.compare(champ, cand, 0.03)
+    assert rep["pass"] and {r["metric"] for r in rep["metrics"]} == {"decode_tok_s", "e2e", "ttft_ms", "prefill_tok_s"}
+    slow = dict(cand, extra={"ttft_ms": 500.0, "prefill_tok_s": 5100.0})
+    rep = cmp.compare(champ, slow, 0.03)
+    assert not rep["pass"] and [r["metric"] for r in rep["metrics"] if not r["pass"]] == ["ttft_ms"]
+    assert not cmp.compare(champ, {"metric": "decode_tok_s", "value": 100.0}, 0.03)["pass"]      # sub-metrics missing
+    a, b = tmp_path / "a.log", tmp_path / "b.json"
+    a.write_text("warming up\n" + json.dumps(champ) + "\n")
+    b.write_text(json.dumps(cand))
+    assert cmp.main([str(a), str(b)]) == 0
+    assert cmp.config_diff({"x": {"y": 1, "z": 2}}, {"x": {"y": 1, "z": 3}, "w": 0}) == [("w", None, 0), ("x.z", 2, 3)]

@@ -62,7 +62,7 @@ def compare(champion: dict, candidate: dict, tolerance: float = 0.03) -> dict:
             ok = False
             continue
         (va, hib), (vb, _) = a[name], b[name]
-        ratio = (vb / va if hib else va / vb) if va and vb else 0.0          # > 1 = candidate better
+        ratio = 1.0 if va == vb else ((vb / va if hib else va / vb) if va and vb else 0.0)      # > 1 = candidate better
         passed = ratio >= 1.0 - tolerance
         ok &= passed
         rows.append({"metric": name, "champion": va, "candidate": vb, "ratio": round(ratio, 4), "higher_is_better": hib, "pass": passed})

@@ -28,6 +28,7 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--pin", action="append", default=[], metavar="PATH=VALUE|FILE.json", help="pinnable: " + ", ".join(PINNABLE))
     p.add_argument("--hardware", help="JSON hardware descriptor to plan for instead of probing this machine")
     p.add_argument("--assume-gpus", type=int, default=None, help="plan for N B200 GPUs (no probe)")
+    p.add_argument("--calibration", help="loader calibration or measured-peaks JSON: replaces the default bandwidths of the step-time model")
     p.add_argument("--print", dest="show", action="store_true", help="print the explanation")
     p.add_argument("--probe-only", action="store_true", help="print what the model path is (format, shape, quantisation, size) and exit")
     return p
@@ -54,6 +55,11 @@ def main(argv: Optional[list[str]] = None) -> int:
             hw = synthetic(args.assume_gpus)
         else:
             hw = detect((base or {}).get("hardware", {}).get("nvme_paths"))
+        if args.calibration:
+            from ..autoconfig.calibration import apply_calibration
+            hw, notes = apply_calibration(hw, json.load(open(args.calibration)))
+            for n in notes:
+                print("calibration:", n, file=sys.stderr)
         res = solve(shape, hw, Levers(args.vram_expert_ratio, args.total_active_context_tokens, args.prefer, args.accuracy),
                     collect_pins(args.pin), base)
     except ConfigError as e:

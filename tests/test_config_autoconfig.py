@@ -270,3 +270,36 @@ def test_champion_comparison(tmp_path):
     b.write_text(json.dumps(cand))
     assert cmp.main([str(a), str(b)]) == 0
     assert cmp.config_diff({"x": {"y": 1, "z": 2}}, {"x": {"y": 1, "z": 3}, "w": 0}) == [("w", None, 0), ("x.z", 2, 3)]
+
+
+def test_calibration_replaces_default_bandwidths(tmp_path):
+    from layerstorm_b200.autoconfig import synthetic
+    from layerstorm_b200.autoconfig.calibration import apply_calibration
+    from layerstorm_b200.cli import autoconfigure
+    hw = synthetic(8)
+    doc = {"version": 1, "devices": [{"a_ns": 30000, "b_ns": 2500}], "banks": [{"rate_bytes_per_us": [48000, 52000], "latency_ns": [9000, 9000]}],
+           "hbm_gbs": 7100.0, "nvlink_gbs": 5.0}
+    hw2, notes = apply_calibration(hw, doc)
+    assert hw2.h2d_gbs == 48.0 and hw2.hbm_gbs == 7100.0 and hw2.nvlink_gbs == hw.nvlink_gbs and hw.h2d_gbs == 55.0
+    assert any("ignored" in n and "nvlink" in n for n in notes) and any("cost curve" in n for n in notes)
+    p = tmp_path / "cal.json"
+    p.write_text(json.dumps(doc))
+    out = tmp_path / "cfg.json"
+    assert autoconfigure.main(["--model", "glm-5.3-flash", "--assume-gpus", "8", "--calibration", str(p), "-o", str(out)]) == 0
+    assert json.load(open(out))["serving"]["tool_call_parser"] == "glm47"
+
+
+def test_benchmark_mode_on_the_null_engine(tmp_path, capsys):
+    from layerstorm_b200 import build as _build
+    _build.build_all(only="runtime")
+    from layerstorm_b200.autoconfig import benchmark, compare
+    out = tmp_path / "rep.json"
+    rc = benchmark.main(["--prompt-len", "300", "--gen", "8", "--requests", "2", "--out", str(out), "--",
+                         "--model", "tiny-mla-moe", "--test-engine"])
+    assert rc == 0
+    rep = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert rep == json.load(open(out)) and rep["metric"] == "decode_tok_s" and rep["value"] > 0
+    assert rep["extra"]["prefill_tok_s"] > 0 and rep["extra"]["ttft_ms"] > 0 and rep["config"]["model"]
+    assert compare.compare(rep, rep)["pass"]
+    # too long for the configured sequence length: refused before anything is built
+    assert benchmark.main(["--prompt-len", "100000000", "--", "--model", "tiny-mla-moe", "--test-engine"]) == 2

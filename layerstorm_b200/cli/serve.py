@@ -206,6 +206,47 @@ def build_engine(cfg: dict, shape: ModelConfig, ckpt: Optional[str], args: argpa
     return eng
 
 
+def build_model_draft(cfg: dict, shape: ModelConfig, engine, args: argparse.Namespace):
+    """(draft, depth) for the model-backed speculation methods.
+    ``self_speculative``: the target drafts for itself with ``speculation.self_speculative.draft_expert_count`` routed experts per token.
+    ``dspark``: a small draft model on its own engine - ``speculation.dspark.checkpoint_path`` when given, else (random-weight runs) the
+    default 2-layer draft shape of the target's width.  Returns (None, 0) when the engine at hand cannot host the draft."""
+    from ..speculation.model_draft import EngineDraft, draft_shape_for
+    sp = cfg["speculation"]
+    target = getattr(engine, "_engine", engine)                  # unwrap tracing / SPMD facades
+    if sp["method"] == "self_speculative":
+        from ..speculation.self_draft import SelfSpeculativeDraft
+        depth = args.speculation_depth if args.speculation_depth is not None else sp["mtp"]["max_depth"]
+        try:
+            return SelfSpeculativeDraft(target, sp["self_speculative"], max_gamma=max(1, depth)), depth
+        except (TypeError, NotImplementedError) as e:
+            log.warning("self-speculative draft unavailable (%s); serving without speculation", e)
+            return None, 0
+    ds = sp["dspark"]
+    depth = args.speculation_depth if args.speculation_depth is not None else ds["speculative_tokens"]
+    if args.test_engine:
+        from ..runtime.null_engine import NullEngine
+        return EngineDraft(NullEngine(vocab=target.vocab, max_seqs=2, max_ctx=target.max_ctx), max_gamma=depth), depth
+    if int(os.environ.get("WORLD_SIZE", 1)) > 1:
+        log.warning("model draft with tensor-parallel serving is not wired; serving without speculation")
+        return None, 0
+    import torch
+    from ..models.device_model import DeviceModel
+    from ..runtime.engine import Engine
+    dev = torch.device("cuda", int(ds["draft_gpus"][0]) if ds["draft_gpus"] else int(os.environ.get("LOCAL_RANK", 0)))
+    page = cfg["memory"]["kv_cache"]["page_size_tokens"]
+    if ds["checkpoint_path"]:
+        from ..models.checkpoint import open_checkpoint
+        dshape, w = open_checkpoint(ds["checkpoint_path"])
+        dm = DeviceModel.from_state_dict(dshape, w, dev, "bf16", page)
+    else:
+        dshape = draft_shape_for(shape, quant="nvfp4" if ds["draft_weights_quant"] in ("nvfp4", "auto") else "bf16")
+        log.warning("speculation.dspark.checkpoint_path is empty: RANDOM draft weights of shape %s", dshape.name)
+        dm = DeviceModel.random_init(dshape, dev, "bf16", page)
+    ctx = min(cfg["serving"]["max_sequence_length"], max(ds["draft_context_capacity_tokens"], 1024))
+    return EngineDraft(Engine(dm, max_seqs=2, max_ctx=ctx, prefill_chunk=cfg["orchestrator"]["prefill_chunk_tokens"], max_batch=1), max_gamma=depth), depth
+
+
 def build_server(cfg: dict, shape: ModelConfig, ckpt: Optional[str], engine, args: argparse.Namespace):
     from ..serving.http_server import LayerStormServer, ServerConfig
     from ..serving.orchestrator import Orchestrator
@@ -224,6 +265,8 @@ def build_server(cfg: dict, shape: ModelConfig, ckpt: Optional[str], engine, arg
         pl = sp["prompt_lookup"]
         draft = PromptLookupDraft(pl["min_ngram_size"], pl["max_ngram_size"], pl["max_continuation_length"])
         depth = args.speculation_depth if args.speculation_depth is not None else pl["max_continuation_length"]
+    elif sp["enabled"] and sp["method"] in ("dspark", "self_speculative"):
+        draft, depth = build_model_draft(cfg, shape, engine, args)
     orch = Orchestrator(engine, eos_token_ids=eos, prefix_cache=pcc, draft=draft, speculation_depth=depth, tokenizer=tok)
     rc = sv["reasoning_config"]
     if rc:

@@ -238,7 +238,7 @@ SCHEMA: dict[str, Any] = {
     },
     "speculation": {
         "enabled": F(bool, True),
-        "method": F(str, "none", enum=("none", "null", "mtp", "prompt_lookup", "dspark")),
+        "method": F(str, "none", enum=("none", "null", "mtp", "prompt_lookup", "dspark", "self_speculative")),
         "mtp": {"enabled": F(bool, True), "max_depth": F(int, 3, lo=1, live=True), "dynamic_depth": F(bool, True),
                 "confidence_threshold": F(float, 0.4, live=True), "batched_verify": F(bool, True)},
         "dspark": {

@@ -447,6 +447,22 @@ class DeviceModel:
     def attach_comm(self, comm, comm_amax):
         self.comm, self.comm_amax = comm, comm_amax
 
+    def reduced_expert_view(self, top_k: int) -> "DeviceModel":
+        """A second model over the SAME weight tensors that routes to ``top_k`` experts per token (own KV / recurrent caches, to be
+        allocated by the engine that takes it): the draft side of self-speculative decoding.  Single-GPU models with fully resident
+        experts only - the in-kernel collectives' buffers and the expert streamer's slots belong to the full model's step."""
+        import copy
+        import dataclasses
+        if self.tp_size != 1 or self.streamer is not None:
+            raise NotImplementedError("reduced-expert view needs tp_size == 1 and fully resident experts")
+        v = copy.copy(self)
+        v.cfg = dataclasses.replace(self.cfg, top_k=max(1, min(top_k, self.cfg.top_k)))
+        v.kv_cache, v.idx_cache, v.idx_tail, v.kda_state, v.kda_conv = {}, {}, {}, {}, {}
+        v.block_table = None
+        v.drift = None
+        v.kernel_launches = 0
+        return v
+
     @property
     def _cp(self):
         """PeerComm address for the fused all-reduce of the current step, or None (single GPU, or a

@@ -67,6 +67,19 @@ class CpuEngine:
         self._next = 0
         self.forward_seconds = 0.0
 
+    def reduced_expert_view(self, top_k: int) -> "CpuEngine":
+        """A second engine over the SAME weights that routes to ``top_k`` experts per token instead of the model's (own sequences):
+        the draft side of self-speculative decoding."""
+        import copy
+        import dataclasses
+        view = copy.copy(self)
+        view.cfg = dataclasses.replace(self.cfg, top_k=max(1, min(top_k, self.cfg.top_k)))
+        view.model = copy.copy(self.model)
+        view.model.cfg = view.cfg
+        view.model.sel_log = {}
+        view.seqs, view._next, view.forward_seconds = {}, 0, 0.0
+        return view
+
     # ---- sequences ----
     def create_sequence(self) -> int:
         if len(self.seqs) >= self.max_seqs:

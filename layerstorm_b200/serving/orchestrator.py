@@ -381,6 +381,8 @@ class Orchestrator:
             req.stats.spec_accepted += n_acc
             new = draft[:n_acc] + [target[n_acc]]
             self.governor.observe_round(len(new), (time.time() - t0) * 1e3)
+            if hasattr(self.draft, "feedback"):
+                self.draft.feedback(len(draft), n_acc)
             for t in new:
                 if self._emit(req, t, None):
                     return

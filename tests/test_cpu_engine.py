@@ -46,3 +46,44 @@ def test_orchestrator_on_cpu_engine():
     orch.submit_request(req)
     orch.step()
     assert len(req.output_ids) == 5 and req.finish_reason == "length"
+
+
+def test_self_speculative_draft_is_lossless_on_the_cpu_engine():
+    from layerstorm_b200.speculation.self_draft import SelfSpeculativeDraft
+    cfg = get_preset("tiny-mla-moe")
+    w = init_weights(cfg, 3)
+    prompt = list(range(7, 31))
+    plain = CpuEngine(cfg, w, native_experts=False)
+    req0 = InferenceRequest("p", prompt, SamplingParams(max_tokens=12, ignore_eos=True))
+    o0 = Orchestrator(plain)
+    o0.submit_request(req0)
+    assert o0.step() and req0.error is None
+    eng = CpuEngine(cfg, w, native_experts=False)
+    draft = SelfSpeculativeDraft(eng, {"draft_expert_count": 2, "adaptive_exit_enabled": False}, max_gamma=3)
+    assert draft.engine.cfg.top_k == 2 and eng.cfg.top_k == cfg.top_k and draft.engine.model.w is eng.model.w      # same weights, fewer experts
+    assert abs(draft.expert_fraction - 2 / cfg.top_k) < 1e-9
+    orch = Orchestrator(eng, draft=draft, speculation_depth=3)
+    req = InferenceRequest("s", prompt, SamplingParams(max_tokens=12, ignore_eos=True))
+    orch.submit_request(req)
+    assert orch.step() and req.error is None
+    assert req.output_ids == req0.output_ids                     # verification by the full model: same tokens as plain greedy
+    assert req.stats.spec_rounds > 0 and draft.plan.steps > 0 and draft.failures == 0
+    assert 0.0 <= draft.plan.acceptance_rate <= 1.0
+
+
+def test_serve_builds_model_drafts_on_the_test_engine():
+    from layerstorm_b200.cli import serve
+    from layerstorm_b200.speculation.model_draft import EngineDraft
+    args = serve.build_parser().parse_args(["--model", "tiny-mla-moe", "--test-engine", "--tokenizer-mode", "byte", "--speculation-depth", "4"])
+    cfg, shape, ckpt, _ = serve.resolve_config(args)
+    cfg["speculation"]["enabled"], cfg["speculation"]["method"] = True, "dspark"
+    eng = serve.build_engine(cfg, shape, ckpt, args)
+    _, orch = serve.build_server(cfg, shape, ckpt, eng, args)
+    assert isinstance(orch.draft, EngineDraft) and orch.gamma == 4
+    req = InferenceRequest("d", list(range(5, 40)), SamplingParams(max_tokens=10, ignore_eos=True))
+    orch.submit_request(req)
+    assert orch.step() and req.error is None and len(req.output_ids) == 10 and req.stats.spec_accepted > 0
+    # the null engine cannot draft for itself: self_speculative degrades to plain decoding with a warning
+    cfg["speculation"]["method"] = "self_speculative"
+    _, orch2 = serve.build_server(cfg, shape, ckpt, serve.build_engine(cfg, shape, ckpt, args), args)
+    assert orch2.draft is None and orch2.gamma == 0

@@ -225,13 +225,18 @@ class Oracle:
         decay = torch.exp(cfg.kda_lower_bound * torch.sigmoid(a_exp[None, :, None] * (raw_g + w[p + "dt_bias"][None])))
         qn = q / torch.sqrt((q * q).sum(-1, keepdim=True) + 1e-6) * (D ** -0.5)
         kn = k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)
-        S = torch.zeros(Hk, D, D)
-        core = torch.empty(T, Hk, D)
-        for t in range(T):
-            S = S * decay[t][:, None, :]
-            err = (v[t] - (S * kn[t][:, None, :]).sum(-1)) * beta[t][:, None]
-            S = S + err[:, :, None] * kn[t][:, None, :]
-            core[t] = (S * qn[t][:, None, :]).sum(-1)
+        if getattr(self, "kda_chunk", 0):
+            # chunk-parallel form (models/kda_chunked.py): same result, the algorithm of a tensor-core prefill kernel
+            from .kda_chunked import kda_chunked
+            core, _ = kda_chunked(qn, kn, v, beta, decay, None, chunk=self.kda_chunk, blockwise=True)
+        else:
+            S = torch.zeros(Hk, D, D)
+            core = torch.empty(T, Hk, D)
+            for t in range(T):
+                S = S * decay[t][:, None, :]
+                err = (v[t] - (S * kn[t][:, None, :]).sum(-1)) * beta[t][:, None]
+                S = S + err[:, :, None] * kn[t][:, None, :]
+                core[t] = (S * qn[t][:, None, :]).sum(-1)
         on = core * torch.rsqrt(core.pow(2).mean(-1, keepdim=True) + cfg.rms_eps) * w[p + "o_norm"][None, None] * torch.sigmoid(g2)
         return on.reshape(T, Hk * D) @ w[p + "o"].T
 

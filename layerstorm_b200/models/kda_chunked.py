@@ -71,6 +71,51 @@ def _pair_matrices(qc, kc, G, blockwise: bool, sub: int, operand_dtype):
     return A, B
 
 
+def kda_chunk_prepare(q, k, beta, decay, chunk: int = 64, blockwise: bool = True, sub: int = 16, operand_dtype: Optional[torch.dtype] = None):
+    """Phase 1, independent of the state and therefore parallel over (chunk, head): for every chunk
+        W  = (I + diag(beta) tril(A, -1))^-1 diag(beta)      [C, C]   (so that U = W (V - Kp S0^T))
+        Bm = tril(B)                                          [C, C]
+        Qp = Q * exp(G), Kp = K * exp(G)                      [C, Dk]  read keys / queries seen from the chunk start
+        Km = K * exp(G_C - G)                                 [C, Dk]  write keys seen from the chunk end
+        gC = exp(G_C)                                         [Dk]     decay of the carried state over the whole chunk
+    Returns a list over chunks of dicts of tensors with a leading head dimension."""
+    T, H, Dk = k.shape
+    logd = torch.log(decay)
+    out = []
+    for c0 in range(0, T, chunk):
+        c1 = min(c0 + chunk, T)
+        C = c1 - c0
+        G = torch.cumsum(logd[c0:c1], 0)
+        eye = torch.eye(C, dtype=q.dtype)
+        W, Bm = torch.empty(H, C, C, dtype=q.dtype), torch.empty(H, C, C, dtype=q.dtype)
+        for h in range(H):
+            A, B = _pair_matrices(q[c0:c1, h], k[c0:c1, h], G[:, h], blockwise, sub, operand_dtype)
+            bc = beta[c0:c1, h]
+            W[h] = torch.linalg.solve_triangular(eye + bc[:, None] * torch.tril(A, -1), torch.diag(bc), upper=False)
+            Bm[h] = torch.tril(B)
+        eg = torch.exp(G).transpose(0, 1)                                               # [H, C, Dk]
+        kh, qh = k[c0:c1].transpose(0, 1), q[c0:c1].transpose(0, 1)
+        out.append({"rows": (c0, c1), "W": W, "B": Bm, "Qp": qh * eg, "Kp": kh * eg,
+                    "Km": kh * torch.exp(G[-1][None] - G).transpose(0, 1), "gC": torch.exp(G[-1])})
+    return out
+
+
+def kda_chunk_scan(prep, v, S0=None, operand_dtype: Optional[torch.dtype] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Phase 2, sequential over chunks, independent per (head, value channel): four small matrix products per chunk."""
+    T, H, Dv = v.shape
+    Dk = prep[0]["Kp"].shape[-1]
+    S = torch.zeros(H, Dv, Dk, dtype=v.dtype) if S0 is None else S0.clone()
+    out = torch.empty(T, H, Dv, dtype=v.dtype)
+    mm = lambda a, b: _mm(a, b, operand_dtype)
+    for p in prep:
+        c0, c1 = p["rows"]
+        St = S.transpose(1, 2)                                                          # [H, Dk, Dv]
+        U = mm(p["W"], v[c0:c1].transpose(0, 1) - mm(p["Kp"], St))                       # [H, C, Dv]
+        out[c0:c1] = (mm(p["Qp"], St) + mm(p["B"], U)).transpose(0, 1)
+        S = S * p["gC"][:, None, :] + mm(U.transpose(1, 2), p["Km"])
+    return out, S
+
+
 def kda_chunked(q, k, v, beta, decay, S0=None, chunk: int = 64, blockwise: bool = False, sub: int = 16,
                 operand_dtype: Optional[torch.dtype] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     T, H, Dk = k.shape

@@ -67,3 +67,16 @@ def test_oracle_with_chunked_kda_matches_the_sequential_oracle():
     b = o.forward(toks)
     assert (a - b).abs().max() < 2e-4 * a.abs().max()
     assert torch.equal(a.argmax(-1), b.argmax(-1))
+
+
+def test_two_phase_form_equals_the_recurrence():
+    from layerstorm_b200.models.kda_chunked import kda_chunk_prepare, kda_chunk_scan
+    q, k, v, beta, decay = _inputs(150, 3, 32, 40, torch.float64, 5)
+    S0 = torch.randn(3, 40, 32, dtype=torch.float64, generator=torch.Generator().manual_seed(1))
+    o_ref, S_ref = kda_sequential(q, k, v, beta, decay, S0)
+    prep = kda_chunk_prepare(q, k, beta, decay, chunk=64)          # no state, no values: parallel over chunks and heads
+    o, S = kda_chunk_scan(prep, v, S0)
+    assert (o - o_ref).abs().max() < 1e-10 and (S - S_ref).abs().max() < 1e-10
+    # value channels are independent in the scan: any slice of them gives that slice of the result
+    o_s, S_s = kda_chunk_scan(prep, v[..., 8:24].contiguous(), S0[:, 8:24].contiguous())
+    assert (o_s - o_ref[..., 8:24]).abs().max() < 1e-10 and (S_s - S_ref[:, 8:24]).abs().max() < 1e-10

@@ -90,6 +90,10 @@ TC_MOE_MIN_ROWS = 16      # rows per step from which the routed experts run on t
 # GLM-5.3-Flash shape the fused kernel (one block per expert, last block selects) gives 7.21 ms per decode step against 7.12 ms for
 # the split-K GEMV + top-k pair, whose second launch already overlaps the first through programmatic dependent launch
 ROUTER_FUSED = os.environ.get("LSB_ROUTER_FUSED", "0") != "0"
+# LSB_KDA_CHUNKED=1: prefill chunks of one sequence (>= 128 rows) run the KDA recurrence chunk-parallel (kda_chunk_prep / kda_chunk_scan)
+# instead of token by token.  Off by default: the kernels compile and their algorithm is verified on the CPU (models/kda_chunked.py),
+# but they have not been run on a GPU yet.
+KDA_CHUNKED = os.environ.get("LSB_KDA_CHUNKED", "0") not in ("", "0")
 
 
 def _dequant_q4k(raw: torch.Tensor, N: int, K: int) -> torch.Tensor:
@@ -343,6 +347,8 @@ class Workspace:
         self.row_store = torch.zeros(R, dtype=i32, device=dev)          # context-parallel KV: shard index of each new row (-1: not ours)
         self.row_len_local = torch.zeros(R, dtype=i32, device=dev)      # ... and the number of visible positions this rank stores
         self.kda_scratch = z(7 * R * C + R * m.Hk + 2 * R * m.cfg.kda_rank + 16) if (C > 0 and R >= 8) else None
+        # workspace of the chunk-parallel KDA recurrence (W, tril(B) and the chunk decays of every 64-token chunk); opt-in
+        self.kda_chunk_ws = z(((R + 63) // 64) * m.Hk * (2 * 64 * 64 + 128)) if (KDA_CHUNKED and C > 0 and R >= 128) else None
         Hh = m.Hh
         self.q_c = z(R, max(cfg.q_lora, 1), dtype=b16)
         self.qproj = z(R, m.max_qb, dtype=b16)
@@ -881,11 +887,15 @@ class DeviceModel:
         C = self.Hk * cfg.kda_head_dim
         lin: QLinear = L["kda_in"]
         lin(ws.proj, ws.x, R, ldo=self.max_proj)
-        nat.call("lsb_kda_forward", ws.proj, self.max_proj, 0, C, 2 * C, 3 * C, 3 * C + self.Hk,
-                 3 * C + self.Hk + cfg.kda_rank, cfg.kda_rank, L["kda_fb"], L["kda_gb"], L.get("kda_fb2"), L.get("kda_gb2"), L["kda_conv_q"], L["kda_conv_k"],
-                 L["kda_conv_v"], L["kda_a_exp"], L["kda_dt_bias"], L["kda_o_norm"], self.kda_state[i], self.kda_conv[i],
-                 ws.seq_row0, ws.seq_nrows, ws.seq_slot, ws.kda_out, nseq, self.Hk, cfg.kda_head_dim,
-                 cfg.kda_head_dim ** -0.5, cfg.kda_lower_bound, cfg.rms_eps, R, ws.kda_scratch)
+        args = (ws.proj, self.max_proj, 0, C, 2 * C, 3 * C, 3 * C + self.Hk,
+                3 * C + self.Hk + cfg.kda_rank, cfg.kda_rank, L["kda_fb"], L["kda_gb"], L.get("kda_fb2"), L.get("kda_gb2"), L["kda_conv_q"], L["kda_conv_k"],
+                L["kda_conv_v"], L["kda_a_exp"], L["kda_dt_bias"], L["kda_o_norm"], self.kda_state[i], self.kda_conv[i],
+                ws.seq_row0, ws.seq_nrows, ws.seq_slot, ws.kda_out, nseq, self.Hk, cfg.kda_head_dim,
+                cfg.kda_head_dim ** -0.5, cfg.kda_lower_bound, cfg.rms_eps, R, ws.kda_scratch)
+        if ws.kda_chunk_ws is not None and nseq == 1 and R >= 128:
+            nat.call("lsb_kda_forward_chunked", *args, ws.kda_chunk_ws, ws.kda_chunk_ws.numel())
+        else:
+            nat.call("lsb_kda_forward", *args)
         L["kda_o"](ws.sub, ws.kda_out, R, comm=self._cp)
         self._reduce(ws, R)
 

@@ -209,3 +209,26 @@ def test_hibernate_resume_is_bit_identical_and_frees_pages(name):
     t1, l1 = run(True)
     assert t0 == t1 and torch.equal(l0, l1)
     assert eng.d2h_bytes > 0 and not eng.hibernated
+
+
+@pytest.mark.skipif(__import__("os").environ.get("LSB_KDA_CHUNKED", "0") in ("", "0"),
+                    reason="the chunk-parallel KDA recurrence is opt-in (LSB_KDA_CHUNKED=1)")
+def test_kda_chunked_prefill_matches_token_recurrence():
+    """Single-sequence steps of >= 128 rows run kda_chunk_prep / kda_chunk_scan; shorter steps run the token-by-token kernel.
+    Both must give the same logits, the same next token and the same carried state (checked through the following decode steps)."""
+    cfg, m, oracle = build("tiny-glm5-next")
+    prompt = torch.randint(0, cfg.vocab, (200,), generator=torch.Generator().manual_seed(11)).tolist()      # 3 full chunks + 8 tokens
+    res = []
+    for chunk in (200, 100):
+        eng = Engine(m, max_seqs=1, max_ctx=256, prefill_chunk=chunk, max_batch=1, use_graph=False)
+        sid = eng.create_sequence()
+        nxt, lg = eng.prefill(sid, prompt, want_logits=True)
+        steps = [eng.decode([sid], [t], return_logits=True)[1][0].clone() for t in (5, 9, 2)]
+        res.append((nxt, lg.clone(), steps))
+        eng.free_sequence(sid)
+    assert res[0][0] == res[1][0]
+    assert rel_err(res[0][1], res[1][1]) < 2e-3, rel_err(res[0][1], res[1][1])
+    for a, b in zip(res[0][2], res[1][2]):
+        assert rel_err(a, b) < 2e-3, rel_err(a, b)
+    ref = oracle.forward(torch.tensor(prompt))[-1]
+    assert rel_err(res[0][1], ref) < 3e-2 and res[0][0] == int(ref.argmax())

@@ -220,9 +220,11 @@ class Engine:
             self._copy_page(*cow)
         dcp = getattr(self.model, "dcp", None)
         if dcp is not None:
-            # sharded KV: this rank stores (and pages) only its share of the positions
+            # sharded KV: a rank stores only its share of the positions.  Every rank pages for the LARGEST share (rank 0's, at most
+            # one chunk more than its own), so that the allocators of all ranks stay in the same state and a pool-exhausted error
+            # is raised by every rank in the same call - the ranks of a multi-process server must fail together or not at all
             from ..parallel.dcp import local_length
-            new_len = local_length(new_len, dcp.chunk, dcp.world, dcp.rank)
+            new_len = local_length(new_len, dcp.chunk, dcp.world, 0)
         new = self.pa.extend(s.slot, new_len)
         if new or cow is not None:
             s.pages = self.pa.pages(s.slot)

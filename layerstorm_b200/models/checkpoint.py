@@ -42,6 +42,8 @@ _HF_LAYER = {
     "hc_ffn.fn": "hc_ffn_fn", "hc_ffn.scale": "hc_ffn_scale", "hc_ffn.base": "hc_ffn_base",
     "mlp.gate": "mlp.gate_proj", "mlp.up": "mlp.up_proj", "mlp.down": "mlp.down_proj",
     "moe.router": "mlp.gate.weight", "moe.router_bias": "mlp.gate.e_score_correction_bias",
+    # multi-token-prediction blocks (layer ids >= num_hidden_layers)
+    "mtp.enorm": "enorm.weight", "mtp.hnorm": "hnorm.weight", "mtp.eh_proj": "eh_proj", "mtp.final_norm": "shared_head.norm.weight",
 }
 _GGUF_LAYER = {
     "attn_norm.weight": "attn_norm.weight", "ffn_norm.weight": "ffn_norm.weight",
@@ -58,6 +60,8 @@ _GGUF_LAYER = {
     "hc_ffn.fn": "hc_ffn_fn.weight", "hc_ffn.scale": "hc_ffn_scale.weight", "hc_ffn.base": "hc_ffn_base.weight",
     "mlp.gate": "ffn_gate.weight", "mlp.up": "ffn_up.weight", "mlp.down": "ffn_down.weight",
     "moe.router": "ffn_gate_inp.weight", "moe.router_bias": "exp_probs_b.bias",
+    "mtp.enorm": "nextn.enorm.weight", "mtp.hnorm": "nextn.hnorm.weight", "mtp.eh_proj": "nextn.eh_proj.weight",
+    "mtp.final_norm": "nextn.shared_head_norm.weight",
 }
 _LAYER_RE = re.compile(r"^layers\.(\d+)\.(.+)$")
 _EXPERT_RE = re.compile(r"^moe\.(experts|shared)\.(\d+)\.(gate|up|down)$")
@@ -404,7 +408,8 @@ def export_hf(cfg: ModelConfig, w: Dict[str, torch.Tensor], directory: str, dtyp
 
 def hf_config_dict(c: ModelConfig) -> dict:
     mt = {"deepseek_v3": "deepseek_v3", "glm_moe_dsa": "glm_moe_dsa", "glm5_next": "glm5_next", "kimi_k25": "kimi_k25", "deepseek_v4": "deepseek_v4"}[c.architecture]
-    d = {"model_type": mt, "hidden_size": c.hidden, "num_hidden_layers": c.n_layers, "vocab_size": c.vocab, "rms_norm_eps": c.rms_eps,
+    d = {"model_type": mt, "hidden_size": c.hidden, "num_hidden_layers": c.n_layers, "num_nextn_predict_layers": c.n_mtp, "vocab_size": c.vocab,
+         "rms_norm_eps": c.rms_eps,
          "num_attention_heads": c.n_heads, "q_lora_rank": c.q_lora, "kv_lora_rank": c.kv_lora, "qk_nope_head_dim": c.qk_nope,
          "qk_rope_head_dim": c.qk_rope, "v_head_dim": c.v_head, "rope_theta": c.rope_theta, "max_position_embeddings": c.max_position,
          "intermediate_size": c.dense_inter, "first_k_dense_replace": c.first_k_dense, "n_routed_experts": c.n_routed,

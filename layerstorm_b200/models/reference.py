@@ -262,7 +262,7 @@ class Oracle:
 
     # ---------------- full forward ----------------
     def forward(self, ids: torch.Tensor, pos: Optional[torch.Tensor] = None, sel_override: Optional[dict] = None,
-                trace: Optional[list] = None) -> torch.Tensor:
+                trace: Optional[list] = None, return_hidden: bool = False):
         cfg, w = self.cfg, self.w
         ids = torch.as_tensor(ids, dtype=torch.long)
         T = ids.shape[0]
@@ -297,7 +297,8 @@ class Oracle:
                 if trace is not None:
                     trace.append(resid.clone())
             final = resid
-        return rmsnorm(final, w["final_norm.weight"], cfg.rms_eps) @ w["head.weight"].T
+        logits = rmsnorm(final, w["final_norm.weight"], cfg.rms_eps) @ w["head.weight"].T
+        return (logits, final) if return_hidden else logits        # ``final``: the stream before the output norm (input of the MTP blocks)
 
     def greedy(self, prompt, n_new: int) -> List[int]:
         """Greedy decode by re-running the full forward (O(T^2); fine for the tiny model)."""

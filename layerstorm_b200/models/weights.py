@@ -108,6 +108,44 @@ def init_weights(cfg: ModelConfig, seed: int = 0, std: float = 0.02) -> Dict[str
             w[f + "gate"] = mat(cfg.dense_inter, H)
             w[f + "up"] = mat(cfg.dense_inter, H)
             w[f + "down"] = mat(H, cfg.dense_inter)
+    # multi-token-prediction blocks: an MLA + FFN decoder layer each (dense attention), plus the input norms / projection and output norm
+    for k in range(cfg.n_mtp):
+        L = cfg.n_layers + k
+        p = f"layers.{L}."
+        a = p + "attn."
+        Hh = cfg.n_heads
+        w[p + "attn_norm.weight"] = norm(H)
+        w[p + "ffn_norm.weight"] = norm(H)
+        w[a + "q_a"] = mat(cfg.q_lora, H, s=0.05)
+        w[a + "q_a_norm"] = norm(cfg.q_lora)
+        w[a + "q_b"] = mat(Hh * cfg.qk_head, cfg.q_lora, s=0.05)
+        w[a + "kv_a"] = mat(cfg.kv_lora + cfg.qk_rope, H, s=0.05)
+        w[a + "kv_a_norm"] = norm(cfg.kv_lora)
+        w[a + "k_b"] = mat(Hh, cfg.kv_lora, cfg.qk_nope, s=0.05)
+        w[a + "v_b"] = mat(Hh, cfg.v_head, cfg.kv_lora, s=0.05)
+        w[a + "o"] = mat(H, Hh * cfg.v_head)
+        if cfg.is_moe_layer(L):
+            m = p + "moe."
+            w[m + "router"] = mat(cfg.n_routed, H, s=0.1)
+            if cfg.router_bias:
+                w[m + "router_bias"] = mat(cfg.n_routed, s=0.05)
+            for e in range(cfg.n_routed):
+                w[m + f"experts.{e}.gate"] = mat(cfg.moe_inter, H)
+                w[m + f"experts.{e}.up"] = mat(cfg.moe_inter, H)
+                w[m + f"experts.{e}.down"] = mat(H, cfg.moe_inter)
+            for s_ in range(cfg.n_shared):
+                w[m + f"shared.{s_}.gate"] = mat(cfg.moe_inter, H)
+                w[m + f"shared.{s_}.up"] = mat(cfg.moe_inter, H)
+                w[m + f"shared.{s_}.down"] = mat(H, cfg.moe_inter)
+        else:
+            f = p + "mlp."
+            w[f + "gate"] = mat(cfg.dense_inter, H)
+            w[f + "up"] = mat(cfg.dense_inter, H)
+            w[f + "down"] = mat(H, cfg.dense_inter)
+        w[p + "mtp.enorm"] = norm(H)
+        w[p + "mtp.hnorm"] = norm(H)
+        w[p + "mtp.eh_proj"] = mat(H, 2 * H, s=0.05)
+        w[p + "mtp.final_norm"] = norm(H)
     return w
 
 

@@ -87,3 +87,41 @@ def test_serve_builds_model_drafts_on_the_test_engine():
     cfg["speculation"]["method"] = "self_speculative"
     _, orch2 = serve.build_server(cfg, shape, ckpt, serve.build_engine(cfg, shape, ckpt, args), args)
     assert orch2.draft is None and orch2.gamma == 0
+
+
+def test_mtp_blocks_and_lossless_mtp_speculation():
+    import dataclasses
+    from layerstorm_b200.models.mtp import mtp_block, mtp_draft_tokens
+    from layerstorm_b200.speculation.mtp_draft import MtpDraft
+    base = get_preset("tiny-mla-moe")
+    cfg = dataclasses.replace(base, n_mtp=1)
+    w = init_weights(cfg, 5)
+    w0 = init_weights(base, 5)
+    assert all(torch.equal(w[k], w0[k]) for k in w0) and f"layers.{cfg.n_layers}.mtp.eh_proj" in w        # main weights unchanged by the extra blocks
+    eng = CpuEngine(cfg, w, native_experts=False)
+    orc = eng.model
+    ids = list(range(9, 33))
+    logits, hidden = orc.forward(torch.tensor(ids), return_hidden=True)
+    assert hidden.shape == (len(ids), cfg.hidden) and torch.equal(logits, orc.forward(torch.tensor(ids)))
+    # causality of the block: position i does not depend on later positions
+    la, ha = mtp_block(orc, 0, hidden[:-1], ids[1:])
+    lb, hb = mtp_block(orc, 0, hidden[:10], ids[1:11])
+    assert torch.allclose(la[:10], lb, atol=1e-5) and torch.allclose(ha[:10], hb, atol=1e-5)
+    toks, conf = mtp_draft_tokens(orc, ids, 3)                     # one block, three depths: cyclic reuse
+    assert len(toks) == 3 and all(0 <= t < cfg.vocab for t in toks) and all(0 < c <= 1 for c in conf)
+    assert mtp_draft_tokens(orc, ids, 3, stop=lambda s, c: True)[0] == toks[:1]
+    # through the orchestrator: random MTP weights draft badly, the output must still equal plain greedy decoding
+    plain = CpuEngine(cfg, w, native_experts=False)
+    r0 = InferenceRequest("p", ids, SamplingParams(max_tokens=8, ignore_eos=True))
+    o0 = Orchestrator(plain)
+    o0.submit_request(r0)
+    assert o0.step() and r0.error is None
+    draft = MtpDraft(eng, {"enabled": True, "max_depth": 2, "dynamic_depth": False})
+    orch = Orchestrator(eng, draft=draft, speculation_depth=2)
+    r1 = InferenceRequest("m", ids, SamplingParams(max_tokens=8, ignore_eos=True))
+    orch.submit_request(r1)
+    assert orch.step() and r1.error is None
+    assert r1.output_ids == r0.output_ids and r1.stats.spec_rounds > 0 and draft.planner.steps > 0
+    import pytest
+    with pytest.raises(ValueError):
+        MtpDraft(CpuEngine(base, w0, native_experts=False), {})

@@ -242,3 +242,16 @@ def test_gguf_q4k_experts_pass_through_bit_exact(tmp_path):
     sh = ck.native_q4k("layers.1.moe.shared.0.down")
     assert sh is not None and tuple(sh.shape) == (rows, cols // 256 * 144)
     assert ck.native_q4k("layers.1.attn.q_a") is None
+
+
+def test_mtp_block_weights_roundtrip_through_an_hf_checkpoint(tmp_path):
+    import dataclasses
+    cfg = dataclasses.replace(tiny_mla_moe(), n_mtp=1)
+    w = round_weights_bf16(init_weights(cfg))
+    export_hf(cfg, w, str(tmp_path))
+    cfg2, ck = open_checkpoint(str(tmp_path))
+    assert cfg2.n_mtp == 1
+    L = cfg.n_layers
+    for k in (f"layers.{L}.mtp.enorm", f"layers.{L}.mtp.hnorm", f"layers.{L}.mtp.eh_proj", f"layers.{L}.mtp.final_norm", f"layers.{L}.attn.q_a",
+              f"layers.{L}.attn.k_b", f"layers.{L}.attn_norm.weight", f"layers.{L}.moe.router", f"layers.{L}.moe.experts.2.up"):
+        assert torch.equal(ck[k], w[k]), k

@@ -187,3 +187,28 @@ def test_sampled_and_guided_speculation_follow_the_plain_trajectory():
     assert g_spec.output_ids == g_plain.output_ids and all(t % 2 == 0 for t in g_spec.output_ids)
     lp = run(EngineDraft(NullEngine(vocab=64, page=16), 3), 3, logprobs=2)      # greedy + logprobs also takes the logits path
     assert lp.output_ids == run(None, 0, logprobs=2).output_ids
+
+
+def test_randomised_requests_with_shared_prefixes_under_pool_pressure():
+    """Many requests with overlapping prefixes through a small KV pool: every output equals the plain run of the same prompt, and no
+    sequence slot or page leaks however the prefix cache forked, evicted and retried."""
+    import random
+    rng = random.Random(7)
+    stems = [[rng.randrange(4, 500) for _ in range(rng.randrange(40, 120))] for _ in range(4)]
+    eng = NullEngine(max_seqs=6, max_ctx=256, page=16, num_pages=40)
+    orch = Orchestrator(eng, prefix_cache=PrefixCacheConfig(grid=16, min_prefix=16, max_holders=3))
+    total_pages = eng.free_page_count()
+    cached = retries = 0
+    for n in range(40):
+        stem = rng.choice(stems)
+        prompt = stem[: rng.randrange(20, len(stem) + 1)] + [rng.randrange(4, 500) for _ in range(rng.randrange(0, 30))]
+        gen = rng.randrange(1, 12)
+        want = run(Orchestrator(NullEngine(max_ctx=256)), prompt, max_tokens=gen, ignore_eos=True).output_ids
+        r = run(orch, prompt, max_tokens=gen, ignore_eos=True)
+        assert r.output_ids == want, n
+        cached += r.stats.cached_tokens
+        retries += r.stats.pool_evict_retries
+        assert len(eng.free_slots) + orch.prefix.holders() == eng.max_seqs
+    assert cached > 0                                             # the shared stems were reused
+    orch.prefix.clear()
+    assert len(eng.free_slots) == eng.max_seqs and eng.free_page_count() == total_pages

@@ -287,9 +287,9 @@ def apply_live_changes(changes, orch, cfg: Optional[dict] = None) -> None:
         if path == "speculation.mtp.max_depth" and getattr(orch, "draft", None) is not None:
             orch.gamma = max(0, int(new))
         evict |= path.startswith("memory.expert_cache.eviction_")
-    streamer = getattr(getattr(getattr(orch, "engine", None), "model", None), "streamer", None)
-    if evict and cfg is not None and streamer is not None:
-        streamer.configure_eviction(cfg["memory"]["expert_cache"])
+    engine = getattr(orch, "engine", None)
+    if evict and cfg is not None and hasattr(engine, "configure_expert_cache"):
+        engine.configure_expert_cache(cfg["memory"]["expert_cache"])      # through the SPMD facade: every rank's cache takes it
 
 
 def main(argv: Optional[list[str]] = None) -> int:

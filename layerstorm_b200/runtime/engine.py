@@ -92,6 +92,15 @@ class Engine:
     def free_page_count(self) -> int:
         return self.pa.free_pages(0)
 
+    def configure_expert_cache(self, section: dict) -> bool:
+        """Apply the ``memory.expert_cache`` eviction policy and weights to the capped expert cache, if this engine streams experts
+        (live-changeable; mirrored to every rank of a multi-process server).  Returns whether a cache took them."""
+        streamer = getattr(self.model, "streamer", None)
+        if streamer is None:
+            return False
+        streamer.configure_eviction(section)
+        return True
+
     def seq_len(self, sid: int) -> int:
         return self.seqs[sid].length
 

@@ -14,7 +14,7 @@ from typing import Any, Optional
 
 # engine methods that change device or sequence state and therefore must run on every rank, in the same order
 MIRRORED = ("create_sequence", "free_sequence", "fork_sequence", "rewind", "prefill", "forward_rows", "decode", "generate",
-            "enable_kv_tiering", "hibernate", "resume")
+            "enable_kv_tiering", "hibernate", "resume", "configure_expert_cache")
 _STOP = "__stop__"
 
 

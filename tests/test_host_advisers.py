@@ -171,3 +171,25 @@ def test_transfer_planner_budget_dedup_and_zones():
     assert plan[0].zone == ZONE_STABLE and plan[0].start_delay_us == 4600.0 and plan[2].zone == ZONE_STREAMING and plan[2].start_delay_us == 0.0
     ev = tp.plan_evictions({0: 3, 1: 1}, {0: 1, 1: 4}, victims_of=lambda g, n: [(7, i) for i in range(10)])
     assert ev == {0: [(7, 0), (7, 1)]}
+
+
+def test_live_eviction_change_reaches_the_engine_through_the_spmd_facade():
+    from layerstorm_b200.cli.serve import apply_live_changes
+    from layerstorm_b200.runtime.spmd import MIRRORED, SpmdLeader
+    calls, sent = [], []
+
+    class Eng:
+        def configure_expert_cache(self, section):
+            calls.append(section["eviction_policy"])
+            return True
+
+    class Orch:
+        draft, gamma = object(), 3
+        engine = SpmdLeader(Eng(), broadcast=sent.append)
+
+    cfg = load_config(None, {"memory.expert_cache.eviction_policy": "lfu"})
+    apply_live_changes([("memory.expert_cache.eviction_policy", "impact_weighted_lru", "lfu"), ("speculation.mtp.max_depth", 3, 5)], Orch, cfg)
+    assert calls == ["lfu"] and Orch.gamma == 5
+    assert "configure_expert_cache" in MIRRORED and sent and sent[0][0] == "configure_expert_cache"      # announced to the other ranks
+    apply_live_changes([("orchestrator.max_batch_size", 4, 8)], Orch, cfg)
+    assert calls == ["lfu"]

@@ -69,8 +69,10 @@ class GpuLoadBalancer:
                 if not cand:
                     break
                 e = min(cand, key=lambda x: abs(self.load[j, x] - gap / 2))       # the expert that best halves the gap
-                new_max = max(g[src] - self.load[j, e], g[dst] + self.load[j, e], *(g[k] for k in range(self.G) if k not in (src, dst))) \
-                    if self.G > 2 else max(g[src] - self.load[j, e], g[dst] + self.load[j, e])
+                after = g.copy()
+                after[src] -= self.load[j, e]
+                after[dst] += self.load[j, e]
+                new_max = after.max()
                 if new_max >= g.max():
                     break
                 moves.append(Move(j, e, src, dst, float(g.max() - new_max)))

@@ -144,7 +144,7 @@ class TransferPlanner:
         self.G, self.nbytes = n_gpus, expert_bytes
         self.max_inflight, self.min_priority, self.stable_thr = max_inflight_per_gpu, min_priority, stable_zone_threshold
         bw = [link_gbs[g] if g < len(link_gbs) else default_link_gbs for g in range(n_gpus)]
-        self.budget = [int(b * 1e3 * cycle_budget_us) for b in bw]    # GB/s * us = kB
+        self.budget = [int(b * 1e3 * cycle_budget_us) for b in bw]    # bytes per planning cycle: GB/s x us = 1e3 bytes
 
     def plan_transfers(self, candidates: Iterable[Candidate], resident: Dict[int, Set[Tuple[int, int]]], in_flight: Dict[int, Set[Tuple[int, int]]],
                        transfer_latency_us: Optional[Dict[int, float]] = None) -> List[PlannedTransfer]:

@@ -279,6 +279,26 @@ def build_server(cfg: dict, shape: ModelConfig, ckpt: Optional[str], engine, arg
     return LayerStormServer(orch, tok, scfg), orch
 
 
+def start_rank_liveness(world: int):
+    """Heartbeats of every rank through the job's rendezvous store; on rank 0 also the monitor that SpmdLeader asks before each step
+    (LS_RANK_TIMEOUT_S, default 10 s; 0 disables).  Returns (monitor or None, heartbeat or None)."""
+    timeout = float(os.environ.get("LS_RANK_TIMEOUT_S", "10"))
+    if timeout <= 0:
+        return None, None
+    try:
+        import torch.distributed as dist
+        from torch.distributed.distributed_c10d import _get_default_store
+        store = dist.PrefixStore("lsb200_hb", _get_default_store())
+    except Exception as e:            # noqa: BLE001 - liveness is an extra; serving works without it
+        log.warning("rank liveness disabled: no rendezvous store (%s)", e)
+        return None, None
+    from ..runtime.heartbeat import Heartbeat, RankMonitor
+    rank = int(os.environ.get("RANK", 0))
+    beat = Heartbeat(store, rank, interval_s=min(1.0, timeout / 5)).start()
+    monitor = RankMonitor(store, list(range(1, world)), timeout_s=timeout).start(interval_s=min(1.0, timeout / 5)) if rank == 0 else None
+    return monitor, beat
+
+
 def apply_live_changes(changes, orch, cfg: Optional[dict] = None) -> None:
     """Push hot-reloaded fields into the running components.  The config tree itself is already updated in place."""
     evict = False
@@ -318,12 +338,15 @@ def main(argv: Optional[list[str]] = None) -> int:
         # SPMD: rank 0 runs the orchestrator and the HTTP server and announces every engine call; the other ranks replay them
         from ..runtime.spmd import SpmdLeader, control_group, follower_loop
         grp = control_group()
+        monitor, beat = start_rank_liveness(world)
         if int(os.environ.get("RANK", 0)) != 0:
             # an engine call that fails (e.g. KV pool exhausted) fails the same way on every rank; the leader's orchestrator handles
             # it (evict / retry / degrade), the followers just log it and wait for the next call
             follower_loop(engine, grp, on_error=lambda name, e: log.warning("replayed %s raised %s: %s", name, type(e).__name__, e))
+            if beat is not None:
+                beat.stop(goodbye=True)
             return 0
-        engine = SpmdLeader(engine, grp)
+        engine = SpmdLeader(engine, grp, monitor=monitor)
     tracer = None
     from ..utils import perf_trace
     if perf_trace.enabled():

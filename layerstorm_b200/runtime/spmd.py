@@ -27,16 +27,19 @@ def control_group():
 class SpmdLeader:
     """Engine facade for rank 0.  Attribute reads go straight to the engine; mirrored methods are announced first."""
 
-    def __init__(self, engine, group=None, broadcast=None):
+    def __init__(self, engine, group=None, broadcast=None, monitor=None):
         object.__setattr__(self, "_engine", engine)
         object.__setattr__(self, "_group", group)
         object.__setattr__(self, "_broadcast", broadcast or _broadcast_from(0, group))
+        object.__setattr__(self, "_monitor", monitor)            # runtime/heartbeat.py RankMonitor: refuse to start a step a dead rank cannot join
         object.__setattr__(self, "calls_announced", 0)
 
     def __getattr__(self, name: str) -> Any:
         attr = getattr(self._engine, name)
         if name in MIRRORED and callable(attr):
             def mirrored(*args, **kwargs):
+                if self._monitor is not None:
+                    self._monitor.check()                        # raises RankFailure: nothing is announced, no kernel waits on the dead rank
                 self._broadcast([name, args, kwargs])
                 object.__setattr__(self, "calls_announced", self.calls_announced + 1)
                 return attr(*args, **kwargs)

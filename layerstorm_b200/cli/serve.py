@@ -334,6 +334,7 @@ def main(argv: Optional[list[str]] = None) -> int:
         return 0
     engine = build_engine(cfg, shape, ckpt, args)
     world = int(os.environ.get("WORLD_SIZE", 1)) if not args.test_engine else 1
+    monitor = None
     if world > 1:
         # SPMD: rank 0 runs the orchestrator and the HTTP server and announces every engine call; the other ranks replay them
         from ..runtime.spmd import SpmdLeader, control_group, follower_loop
@@ -354,6 +355,8 @@ def main(argv: Optional[list[str]] = None) -> int:
         tracer = perf_trace.Tracer(gpu=int(os.environ.get("LOCAL_RANK", 0)))
         engine = perf_trace.TracedEngine(engine, tracer)
     server, orch = build_server(cfg, shape, ckpt, engine, args)
+    if world > 1 and monitor is not None:
+        server.failed_ranks = lambda: dict(monitor.failed)       # /health answers 503 while a rank is down
     reloader = None
     if args.config and not args.autoconfig:
         # hot reload of the live-changeable fields; everything else in an edited file is reported and waits for a restart

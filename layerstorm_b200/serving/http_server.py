@@ -76,6 +76,10 @@ class LayerStormServer:
 
     # ---- simple routes ----
     async def health(self):
+        # a multi-process server is healthy only while every rank is alive (set by the CLI: () -> {rank: reason} of failed ranks)
+        failed = self.failed_ranks() if getattr(self, "failed_ranks", None) else None
+        if failed:
+            return _error(503, "rank(s) down: " + "; ".join(f"{r}: {why}" for r, why in sorted(failed.items())), "server_error")
         return {"status": "ok", "uptime_s": round(time.time() - self.started, 1), "queued": self.orch.queued(), "served": self.orch.served}
 
     async def models(self):

@@ -156,6 +156,11 @@ def test_http_api():
     srv.inflight = 3
     r = c.post("/v1/completions", json={"prompt": "x"})
     assert r.status_code == 503 and "Retry-After" in r.headers
+    srv.failed_ranks = lambda: {}                                  # multi-process server: every rank alive
+    assert c.get("/health").status_code == 200
+    srv.failed_ranks = lambda: {3: "sent no heartbeat for 12.0 s"}
+    r = c.get("/health")
+    assert r.status_code == 503 and "3: sent no heartbeat" in r.json()["error"]["message"]
     orch.shutdown()
 
 

@@ -113,7 +113,37 @@ def build_all(verbose: bool = False, only: str | None = None) -> dict:
     return out
 
 
+def build_sanitized(sanitizers: str = "address,undefined") -> Path:
+    """The host runtime built with -fsanitize=<sanitizers> into ``_lib/liblsb200_runtime_san.so`` (the production library is not touched).
+    Load it with ``LSB200_RUNTIME_LIB=<path>`` and the sanitizer runtime preloaded (``LD_PRELOAD=$(gcc -print-file-name=libasan.so)``):
+    ``tests/test_runtime_sanitized.py`` runs the native-runtime tests that way.  The kernels library has no sanitized build
+    (compute-sanitizer is the tool for device code)."""
+    obj = OBJ / ("san_" + sanitizers.replace(",", "_"))
+    obj.mkdir(parents=True, exist_ok=True)
+    cxx = os.environ.get("LSB200_SAN_CXX") or shutil.which("g++") or CXX        # the distribution's compiler ships the sanitizer runtimes
+    flags = [f for f in CXX_FLAGS if not f.startswith("-O")] + ["-O1", "-g", "-fno-omit-frame-pointer", f"-fsanitize={sanitizers}"]
+    objs = []
+    for src in sorted((CSRC / "runtime").glob("*.cpp")):
+        o = obj / f"{src.stem}.{_hash([src] + _headers(), flags)}.o"
+        if not o.exists():
+            for old in obj.glob(f"{src.stem}.*.o"):
+                old.unlink()
+            r = subprocess.run([cxx] + flags + ["-c", str(src), "-o", str(o)], capture_output=True, text=True)
+            if r.returncode != 0:
+                raise RuntimeError(f"compile failed: {src}\n{r.stderr}")
+        objs.append(o)
+    out = LIB / "liblsb200_runtime_san.so"
+    r = subprocess.run([cxx, "-shared", f"-fsanitize={sanitizers}", "-o", str(out)] + [str(o) for o in objs] + ["-pthread", "-ldl", "-lrt"],
+                       capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"link failed\n{r.stderr}")
+    return out
+
+
 if __name__ == "__main__":
+    if "--sanitize" in sys.argv:
+        print("runtime (sanitized)", build_sanitized(sys.argv[sys.argv.index("--sanitize") + 1] if len(sys.argv) > sys.argv.index("--sanitize") + 1 else "address,undefined"))
+        sys.exit(0)
     res = build_all(verbose="-v" in sys.argv)
     for k, v in res.items():
         print(k, v)

@@ -6,12 +6,14 @@ in C++ (page allocator, expert cache, placement solver, rings, statistics, traci
 from __future__ import annotations
 
 import ctypes
+import os
 import re
 from pathlib import Path
 from typing import List, Optional, Tuple
 
 _LIB = None
-_LIB_PATH = Path(__file__).resolve().parent.parent / "_lib" / "liblsb200_runtime.so"
+# LSB200_RUNTIME_LIB: another build of the runtime library (the sanitized one of ``build.build_sanitized``)
+_LIB_PATH = Path(os.environ.get("LSB200_RUNTIME_LIB") or Path(__file__).resolve().parent.parent / "_lib" / "liblsb200_runtime.so")
 
 OK, ERR_ARG, ERR_NOT_FOUND, ERR_EXISTS, ERR_POOL_EXHAUSTED, ERR_FROZEN, ERR_SHARED, ERR_FULL, ERR_BUSY, ERR_IO, ERR_FORMAT = range(0, -11, -1)
 ERR_NAMES = {ERR_ARG: "bad argument", ERR_NOT_FOUND: "not found", ERR_EXISTS: "exists", ERR_POOL_EXHAUSTED: "kv pool exhausted",

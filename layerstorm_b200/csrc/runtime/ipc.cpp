@@ -54,18 +54,33 @@ private:
     alignas(64) std::atomic<uint64_t> tail_{0};
 };
 
+// The payload of a seqlock is read while it may be written: the reader throws a torn copy away, but the accesses themselves must not be
+// data races, so both sides move the shared bytes with relaxed atomic accesses (words when aligned, bytes otherwise).
+static inline void copy_to_shared(uint8_t* shared, const uint8_t* src, uint32_t n) {
+    uint32_t i = 0;
+    if (((uintptr_t)shared & 7) == 0)
+        for (; i + 8 <= n; i += 8) { uint64_t v; std::memcpy(&v, src + i, 8); __atomic_store_n((uint64_t*)(shared + i), v, __ATOMIC_RELAXED); }
+    for (; i < n; ++i) __atomic_store_n(shared + i, src[i], __ATOMIC_RELAXED);
+}
+static inline void copy_from_shared(uint8_t* dst, const uint8_t* shared, uint32_t n) {
+    uint32_t i = 0;
+    if (((uintptr_t)shared & 7) == 0)
+        for (; i + 8 <= n; i += 8) { const uint64_t v = __atomic_load_n((const uint64_t*)(shared + i), __ATOMIC_RELAXED); std::memcpy(dst + i, &v, 8); }
+    for (; i < n; ++i) dst[i] = __atomic_load_n(shared + i, __ATOMIC_RELAXED);
+}
+
 class StateSnapshot {
 public:
     explicit StateSnapshot(uint32_t bytes) : data_(bytes) {}
     void begin() { if (depth_++ == 0) seq_.fetch_add(1, std::memory_order_acq_rel); }   // nested transactions publish once
-    void write(uint32_t off, const void* src, uint32_t n) { if (off + n <= data_.size()) std::memcpy(data_.data() + off, src, n); }
+    void write(uint32_t off, const void* src, uint32_t n) { if (off + n <= data_.size()) copy_to_shared(data_.data() + off, (const uint8_t*)src, n); }
     void end() { if (--depth_ == 0) seq_.fetch_add(1, std::memory_order_acq_rel); }
     // Returns the version read, or 0 when no consistent copy was obtained within `tries`.
     uint64_t read(void* out, uint32_t off, uint32_t n, int tries) const {
         for (int i = 0; i < tries; ++i) {
             const uint64_t a = seq_.load(std::memory_order_acquire);
             if (a & 1) continue;
-            std::memcpy(out, data_.data() + off, n);
+            copy_from_shared((uint8_t*)out, data_.data() + off, n);
             std::atomic_thread_fence(std::memory_order_acquire);
             if (seq_.load(std::memory_order_acquire) == a) return a + 2;   // +2 so that version 0 can mean failure
         }

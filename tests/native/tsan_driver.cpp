@@ -1,5 +1,5 @@
 // ThreadSanitizer driver for the host-runtime components that are touched by two threads by design: the SPSC ring (one producer, one
-// consumer), the seqlock state snapshot (one writer, any readers) and the NVMe tier (caller + its worker pool).  Linked against the
+// consumer), the seqlock state snapshot (one writer, any readers), the NVMe tier (caller + its worker pool) and the host arena (loaders).  Linked against the
 // runtime sources compiled with -fsanitize=thread; exits 0 when the functional checks hold (TSAN reports make the process exit 66).
 #include <atomic>
 #include <cstdint>
@@ -27,6 +27,14 @@ int lsb_nvme_write(void* h, int layer, int expert, const void* src, long long by
 unsigned long long lsb_nvme_read_async(void* h, int layer, int expert, void* dst, long long bytes);
 int lsb_nvme_poll(void* h, unsigned long long* tokens, int* status, int cap);
 int lsb_nvme_pending(void* h);
+void* lsb_arena_create(long long slot_bytes, int n_slots, int numa_node, int use_memfd, int thp);
+void lsb_arena_destroy(void* h);
+void* lsb_arena_base(void* h);
+int lsb_arena_lookup(void* h, int layer, int expert);
+int lsb_arena_begin_load(void* h, int layer, int expert, int* ev_layer, int* ev_expert);
+int lsb_arena_finish_load(void* h, int slot, int success);
+int lsb_arena_ref(void* h, int slot, int delta);
+void lsb_arena_stats(void* h, unsigned long long* hits, unsigned long long* misses, unsigned long long* evictions, int* active);
 }
 
 static int check(bool ok, const char* what) {
@@ -104,6 +112,42 @@ int main(int argc, char** argv) {
             for (int e = 0; e < 12; ++e) same &= src[e] == dst[e];
             bad += check(same, "nvme data");
             lsb_nvme_destroy(t);
+        }
+    }
+    // 4. host arena: four loader threads claim, fill and publish slots of a small arena (evicting each other's unreferenced experts)
+    {
+        const long long B = 4096;
+        void* a = lsb_arena_create(B, 8, -1, 0, 0);
+        bad += check(a != nullptr, "arena create");
+        if (a) {
+            std::atomic<int> loads{0}, wrong{0};
+            auto worker = [&](int id) {
+                unsigned char* base = (unsigned char*)lsb_arena_base(a);
+                for (int it = 0; it < 400; ++it) {
+                    const int layer = id & 1, expert = (it * 7 + id * 3) % 24;
+                    int slot = lsb_arena_lookup(a, layer, expert);
+                    if (slot >= 0 && lsb_arena_ref(a, slot, +1) >= 0) {
+                        // (lookup and ref are two calls: the slot may have been re-used in between; the tag written below tells)
+                        const unsigned char tag = base[(long long)slot * B];
+                        if (lsb_arena_lookup(a, layer, expert) == slot) wrong += tag != (unsigned char)(layer * 24 + expert);
+                        lsb_arena_ref(a, slot, -1);
+                        continue;
+                    }
+                    int evl = -1, eve = -1;
+                    slot = lsb_arena_begin_load(a, layer, expert, &evl, &eve);
+                    if (slot < 0) continue;                                   // being loaded by another thread, or nothing evictable
+                    std::memset(base + (long long)slot * B, layer * 24 + expert, B);
+                    lsb_arena_finish_load(a, slot, 1);
+                    ++loads;
+                }
+            };
+            std::vector<std::thread> th;
+            for (int i = 0; i < 4; ++i) th.emplace_back(worker, i);
+            for (auto& t : th) t.join();
+            unsigned long long hits = 0, misses = 0, ev = 0; int active = 0;
+            lsb_arena_stats(a, &hits, &misses, &ev, &active);
+            bad += check(loads > 0 && wrong == 0 && active <= 8, "arena consistency");
+            lsb_arena_destroy(a);
         }
     }
     printf(bad ? "TSAN_DRIVER_FAIL\n" : "TSAN_DRIVER_OK\n");

@@ -135,7 +135,15 @@ static void dequant_row(int fmt, const uint8_t* w, const uint8_t* sf, float ts, 
     }
 }
 
-__attribute__((target_clones("avx512f", "avx2", "default")))
+// Function multiversioning resolves through an ifunc that runs before a ThreadSanitizer runtime is initialised (the process crashes at
+// start-up), so the clones are left out of -fsanitize=thread builds.
+#if defined(__SANITIZE_THREAD__)
+#define LSB_TARGET_CLONES
+#else
+#define LSB_TARGET_CLONES __attribute__((target_clones("avx512f", "avx2", "default")))
+#endif
+
+LSB_TARGET_CLONES
 static float dot_f32(const float* a, const float* b, int n) {
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     int i = 0;

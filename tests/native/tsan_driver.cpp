@@ -1,7 +1,9 @@
 // ThreadSanitizer driver for the host-runtime components that are touched by two threads by design: the SPSC ring (one producer, one
 // consumer), the seqlock state snapshot (one writer, any readers), the NVMe tier (caller + its worker pool) and the host arena (loaders).  Linked against the
 // runtime sources compiled with -fsanitize=thread; exits 0 when the functional checks hold (TSAN reports make the process exit 66).
+#include <algorithm>
 #include <atomic>
+#include <cmath>
 #include <cstdint>
 #include <cstdio>
 #include <cstdlib>
@@ -35,6 +37,10 @@ int lsb_arena_begin_load(void* h, int layer, int expert, int* ev_layer, int* ev_
 int lsb_arena_finish_load(void* h, int slot, int success);
 int lsb_arena_ref(void* h, int slot, int delta);
 void lsb_arena_stats(void* h, unsigned long long* hits, unsigned long long* misses, unsigned long long* evictions, int* active);
+void* lsb_cpu_pool_create(int threads, const int* cpus, int n_cpus);
+void lsb_cpu_pool_destroy(void* h);
+int lsb_cpu_expert_ffn(void* pool, const void* fmt_struct, const void* slot, const float* x, int n, float limit, const float* scale, float* y,
+                       int accumulate);
 }
 
 static int check(bool ok, const char* what) {
@@ -149,6 +155,39 @@ int main(int argc, char** argv) {
             bad += check(loads > 0 && wrong == 0 && active <= 8, "arena consistency");
             lsb_arena_destroy(a);
         }
+    }
+    // 5. CPU expert kernels: the fork-join pool runs an expert FFN (bf16 slot image) over several tokens; compared with a serial evaluation
+    {
+        struct Raw { int fmt, H, F; long long stride, og, ou, od, sg, su, sd, tail; };
+        const int H = 64, F = 96, n = 5;
+        Raw f{0, H, F, (long long)3 * H * F * 2, 0, (long long)H * F * 2, (long long)2 * H * F * 2, 0, 0, 0, 0};
+        std::vector<uint16_t> slot((size_t)3 * H * F);
+        auto bf = [](float v) { uint32_t u; std::memcpy(&u, &v, 4); return (uint16_t)((u + 0x7FFF + ((u >> 16) & 1)) >> 16); };
+        auto fb = [](uint16_t b) { uint32_t u = (uint32_t)b << 16; float v; std::memcpy(&v, &u, 4); return v; };
+        uint32_t seed = 12345;
+        auto rnd = [&] { seed = seed * 1664525u + 1013904223u; return ((seed >> 8) & 0xFFFF) / 65536.f - 0.5f; };
+        for (auto& w : slot) w = bf(0.2f * rnd());
+        std::vector<float> x((size_t)n * H), y((size_t)n * H, 0.f), ref((size_t)n * H, 0.f);
+        for (auto& v : x) v = rnd();
+        void* pool = lsb_cpu_pool_create(4, nullptr, 0);
+        bad += check(pool && lsb_cpu_expert_ffn(pool, &f, slot.data(), x.data(), n, 0.f, nullptr, y.data(), 0) == 0, "cpu expert ffn");
+        for (int t = 0; t < n; ++t) {
+            std::vector<float> act(F);
+            for (int j = 0; j < F; ++j) {
+                float g = 0, u = 0;
+                for (int k = 0; k < H; ++k) { g += fb(slot[(size_t)j * H + k]) * x[(size_t)t * H + k]; u += fb(slot[(size_t)H * F + (size_t)j * H + k]) * x[(size_t)t * H + k]; }
+                act[j] = g / (1.f + expf(-g)) * u;
+            }
+            for (int o = 0; o < H; ++o) {
+                float acc = 0;
+                for (int j = 0; j < F; ++j) acc += fb(slot[(size_t)2 * H * F + (size_t)o * F + j]) * act[j];
+                ref[(size_t)t * H + o] = acc;
+            }
+        }
+        float err = 0, mx = 0;
+        for (size_t i = 0; i < ref.size(); ++i) { err = std::max(err, std::fabs(ref[i] - y[i])); mx = std::max(mx, std::fabs(ref[i])); }
+        bad += check(mx > 0 && err < 1e-3f * mx + 1e-6f, "cpu expert ffn values");
+        if (pool) lsb_cpu_pool_destroy(pool);
     }
     printf(bad ? "TSAN_DRIVER_FAIL\n" : "TSAN_DRIVER_OK\n");
     return bad ? 1 : 0;

@@ -1,4 +1,4 @@
-"""ThreadSanitizer over the host-runtime components shared between two threads (SPSC ring, seqlock snapshot, NVMe tier worker pool, host arena with concurrent loaders):
+"""ThreadSanitizer over the host-runtime components shared between two threads (SPSC ring, seqlock snapshot, NVMe tier worker pool, host arena with concurrent loaders, CPU expert fork-join pool):
 a small C++ driver is built with -fsanitize=thread from the runtime sources and run; any TSAN report fails it."""
 import shutil
 import subprocess
@@ -19,7 +19,7 @@ def test_shared_runtime_components_are_race_free(tmp_path):
         pytest.skip("the compiler ships no ThreadSanitizer runtime")
     exe = tmp_path / "tsan_driver"
     r = subprocess.run([gxx, "-O1", "-g", "-std=c++20", "-fsanitize=thread", "-pthread", "-w", "-I", str(RUNTIME.parent / "include"), "-I", str(RUNTIME),
-                        str(ROOT / "native" / "tsan_driver.cpp"), str(RUNTIME / "ipc.cpp"), str(RUNTIME / "nvme_tier.cpp"), str(RUNTIME / "host_arena.cpp"), "-o", str(exe)],
+                        str(ROOT / "native" / "tsan_driver.cpp"), str(RUNTIME / "ipc.cpp"), str(RUNTIME / "nvme_tier.cpp"), str(RUNTIME / "host_arena.cpp"), str(RUNTIME / "cpu_experts.cpp"), str(RUNTIME / "gguf.cpp"), "-o", str(exe)],
                        capture_output=True, text=True)
     assert r.returncode == 0, r.stderr[-2000:]
     store = tmp_path / "nvme"

@@ -116,3 +116,77 @@ def test_expert_cache_random_walk(seed):
         for k, st in state.items():
             assert ec.lookup(*k) >= 0 and ec.is_ready(*k) == (st == "ready")
         assert ec.count(-1, rt.SLOT_READY) == sum(1 for st in state.values() if st == "ready")
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_transfer_engine_random_walk(seed):
+    """Submissions de-duplicate on (layer, expert, gpu, direction); at most ``waterline`` transfers are in flight per GPU; every
+    transfer is reported by poll exactly once, as done or cancelled; the queue drains."""
+    rng = random.Random(200 + seed)
+    W = 3
+    te = rt.TransferEngine(n_gpus=2, levels=3, waterline=W)
+    live = {}                                                    # token -> key of transfers not yet reported
+    active = set()                                               # tokens still queued or in flight (what a new request can ride on)
+    flying = {0: set(), 1: set()}
+    reported = {}
+    now = 0
+
+    def drain_poll():
+        for tok, state, layer, expert, gpu in te.poll(64):
+            assert tok not in reported and state in (2, 3), (tok, state)
+            reported[tok] = state
+            assert live.pop(tok) == (layer, expert, gpu)
+            flying[gpu].discard(tok)
+
+    for _ in range(800):
+        now += 1000
+        op = rng.choice(["submit", "submit", "issue", "issue", "complete", "cancel", "poll"])
+        if op == "submit":
+            key = (rng.randint(0, 2), rng.randint(0, 7), rng.randint(0, 1))
+            before = te.dedup_hits()
+            tok = te.submit(key[0], key[1], key[2], 0, rng.randint(0, 2), 1 << 20)
+            assert tok != 0
+            dup = [t for t, k in live.items() if k == key and t in active]
+            if dup:
+                assert tok == dup[0] and te.dedup_hits() == before + 1      # the same expert to the same GPU rides on the first request
+            else:
+                live[tok] = key
+                active.add(tok)
+            assert te.find(key[0], key[1], key[2], 0) == tok
+        elif op == "issue":
+            g = rng.randint(0, 1)
+            tok = te.next_to_issue(g, now)
+            if tok:
+                assert tok in live and live[tok][2] == g and te.info(tok)["state"] == 1
+                flying[g].add(tok)
+            else:
+                assert te.in_flight(g) >= W or te.queued(g) == 0
+        elif op == "complete":
+            g = rng.randint(0, 1)
+            if flying[g]:
+                tok = rng.choice(sorted(flying[g]))
+                te.complete(tok, now)                            # the copy has landed (a cancel of an in-flight transfer waits for this)
+                flying[g].discard(tok)
+                active.discard(tok)
+        elif op == "cancel" and active:
+            tok = rng.choice(sorted(active))
+            if te.cancel(tok) == 1:                              # queued: gone at once; in flight (2): cancelled when its copy completes
+                active.discard(tok)
+        else:
+            drain_poll()
+        for g in (0, 1):
+            assert te.in_flight(g) <= W
+    # finish everything that is left
+    for _ in range(200):
+        for g in (0, 1):
+            tok = te.next_to_issue(g, now)
+            if tok:
+                flying[g].add(tok)
+            for t in sorted(flying[g]):
+                te.complete(t, now)
+                flying[g].discard(t)
+                active.discard(t)
+        drain_poll()
+        if not live:
+            break
+    assert not live and te.queued(0) == te.queued(1) == 0 and te.in_flight(0) == te.in_flight(1) == 0

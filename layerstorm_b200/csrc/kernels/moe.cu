@@ -16,108 +16,9 @@
 #include "gemv_core.cuh"
 #include "comm.cuh"
 #include "moe_fmt.cuh"
+#include "router_core.cuh"
 
 namespace lsb {
-
-enum { kScoreSigmoid = 0, kScoreSoftmax = 1, kScoreSqrtSoftplus = 2 };
-
-// Scores, grouped selection and top-k of ONE row by ONE warp (`lane`): no block-wide barriers, the k selection rounds are
-// shuffle reductions.  sm: 2 E + 64 floats of shared memory, s_keep: 64 ints, both private to the warp.
-__device__ __forceinline__ void router_topk_row(const float* __restrict__ logits, const float* __restrict__ bias, int* __restrict__ ids,
-                                                float* __restrict__ wts, int E, int topk, int n_group, int topk_group, int scoring,
-                                                int norm_topk, float scale, int n_shared, int ld_logits, int r, int lane, float* sm, int* s_keep) {
-    float* score = sm;            // [E] unbiased
-    float* sel = sm + E;          // [E] biased, -inf when masked/taken
-    const float* lg = logits + (size_t)r * ld_logits;     // read through L2: the fused kernel's last block reads what other blocks wrote
-    float mx = -INFINITY;
-    if (scoring == kScoreSoftmax) {
-        for (int e = lane; e < E; e += 32) mx = fmaxf(mx, __ldcg(lg + e));
-        mx = warp_max(mx);
-    }
-    float ssum = 0.f;
-    for (int e = lane; e < E; e += 32) {
-        const float x = __ldcg(lg + e);
-        float s;
-        if (scoring == kScoreSigmoid) s = 1.f / (1.f + expf(-x));
-        else if (scoring == kScoreSoftmax) s = expf(x - mx);
-        else s = sqrtf(x > 20.f ? x : log1pf(expf(x)));
-        score[e] = s;
-        ssum += s;
-    }
-    if (scoring == kScoreSoftmax) {
-        ssum = warp_sum(ssum);
-        for (int e = lane; e < E; e += 32) score[e] /= ssum;
-    }
-    __syncwarp();
-    for (int e = lane; e < E; e += 32) sel[e] = score[e] + (bias ? bias[e] : 0.f);
-    __syncwarp();
-    if (n_group > 1) {
-        const int gs = E / n_group;
-        // group score = sum of the two best biased scores; keep topk_group groups (ties -> lower group)
-        for (int g0 = 0; g0 < n_group; g0 += 32) {
-            const int g = g0 + lane;
-            if (g < n_group) {
-                float a = -INFINITY, b2 = -INFINITY;
-                for (int i = 0; i < gs; ++i) {
-                    const float v = sel[g * gs + i];
-                    if (v > a) { b2 = a; a = v; } else if (v > b2) b2 = v;
-                }
-                s_keep[g] = 0;
-                sm[2 * E + g] = a + b2;
-            }
-        }
-        __syncwarp();
-        float* gscore = sm + 2 * E;
-        for (int k = 0; k < topk_group; ++k) {
-            float bv = -INFINITY; int bi = 0x7fffffff;
-            for (int g = lane; g < n_group; g += 32) {
-                if (s_keep[g]) continue;
-                const float v = gscore[g];
-                if (bi == 0x7fffffff || v > bv || (v == bv && g < bi)) { bv = v; bi = g; }
-            }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-                if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) { bv = ov; bi = oi; }
-            }
-            if (lane == 0 && bi != 0x7fffffff) s_keep[bi] = 1;
-            __syncwarp();
-        }
-        for (int e = lane; e < E; e += 32)
-            if (!s_keep[e / gs]) sel[e] = -INFINITY;
-        __syncwarp();
-    }
-    float my_w = 0.f; int my_id = 0;     // lane k keeps the k-th pick
-    float tot = 0.f;
-    for (int k = 0; k < topk; ++k) {
-        float bv = -INFINITY; int bi = 0x7fffffff;
-        for (int e = lane; e < E; e += 32) {
-            const float v = sel[e];
-            if (v > bv || (v == bv && e < bi)) { bv = v; bi = e; }
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
-        }
-        if (bi >= E) bi = 0;               // everything masked (cannot happen with finite logits)
-        const float w = score[bi];
-        tot += w;
-        if (lane == (k & 31)) { my_w = w; my_id = bi; }
-        if (lane == 0) sel[bi] = -INFINITY;
-        __syncwarp();
-    }
-    const int S = topk + n_shared;
-    if (lane < topk) {
-        float w = my_w;
-        if (norm_topk) w = w / (tot + 1e-20f);
-        ids[r * S + lane] = my_id;
-        wts[r * S + lane] = w * scale;
-    }
-    if (lane < n_shared) { ids[r * S + topk + lane] = E + lane; wts[r * S + topk + lane] = 1.f; }
-}
 
 // One warp per row.
 __global__ void __launch_bounds__(32) router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int* __restrict__ ids,
@@ -127,7 +28,8 @@ __global__ void __launch_bounds__(32) router_topk_kernel(const float* __restrict
     __shared__ int s_keep[64];
     pdl_wait();
     pdl_launch_dependents();
-    router_topk_row(logits, bias, ids, wts, E, topk, n_group, topk_group, scoring, norm_topk, scale, n_shared, ld_logits, blockIdx.x, threadIdx.x, sm, s_keep);
+    router_topk_row(logits + (size_t)blockIdx.x * ld_logits, bias, ids + (size_t)blockIdx.x * (topk + n_shared), wts + (size_t)blockIdx.x * (topk + n_shared), E, topk,
+                    n_group, topk_group, scoring, norm_topk, scale, n_shared, threadIdx.x, sm, s_keep);
     pdl_launch_dependents();
 }
 
@@ -187,8 +89,8 @@ __global__ void __launch_bounds__(128) router_fused_kernel(const float* __restri
     __threadfence();
     int* keep = reinterpret_cast<int*>(sm + (size_t)rows * (2 * E + 64));
     for (int r = warp; r < rows; r += 4)
-        router_topk_row(logits, bias, ids, wts, E, topk, n_group, topk_group, scoring, norm_topk, scale, n_shared, E, r, lane,
-                        sm + (size_t)r * (2 * E + 64), keep + r * 64);
+        router_topk_row(logits + (size_t)r * E, bias, ids + (size_t)r * (topk + n_shared), wts + (size_t)r * (topk + n_shared), E, topk, n_group,
+                        topk_group, scoring, norm_topk, scale, n_shared, lane, sm + (size_t)r * (2 * E + 64), keep + r * 64);
     pdl_launch_dependents();
 }
 

@@ -94,6 +94,8 @@ ROUTER_FUSED = os.environ.get("LSB_ROUTER_FUSED", "0") != "0"
 # instead of token by token.  Off by default: the kernels compile and their algorithm is verified on the CPU (models/kda_chunked.py),
 # but they have not been run on a GPU yet.
 KDA_CHUNKED = os.environ.get("LSB_KDA_CHUNKED", "0") not in ("", "0")
+# LSB_MHC_CLUSTER=0: decode-sized hyper-connection passes fall back to the two-launch path (partials + last-block finalize, contraction)
+MHC_CLUSTER = os.environ.get("LSB_MHC_CLUSTER", "1") not in ("", "0")
 
 
 def _dequant_q4k(raw: torch.Tensor, N: int, K: int) -> torch.Tensor:
@@ -808,7 +810,9 @@ class DeviceModel:
         return b
 
     # ------------------------------------------------------------------ forward
-    def _ffn(self, i: int, L: dict, ws: Workspace, R: int):
+    def _ffn(self, i: int, L: dict, ws: Workspace, R: int, routed: bool = False, defer_combine: bool = False):
+        """FFN sublayer into ``ws.sub``.  ``routed``: ids / weights of this layer are already in the workspace.  ``defer_combine``: leave the
+        weighted sum of the expert outputs to the next hyper-connection kernel (returns True when it did so)."""
         cfg = self.cfg
         if "arena" not in L:
             L["mlp_gu"](ws.gu, ws.x, R, ldo=2 * self.Fd)
@@ -819,7 +823,9 @@ class DeviceModel:
         arena: ExpertArena = L["arena"]
         S = ws.S
         sc = {"sigmoid": 0, "softmax": 1, "sqrtsoftplus": 2}[cfg.scoring]
-        if ROUTER_FUSED and R <= 8 and cfg.hidden % 16 == 0 and R * (2 * cfg.n_routed + 128) * 4 <= 48 * 1024:
+        if routed:
+            pass        # the hyper-connection kernel in front of this layer already projected and selected (ws.ids / ws.wts)
+        elif ROUTER_FUSED and R <= 8 and cfg.hidden % 16 == 0 and R * (2 * cfg.n_routed + 128) * 4 <= 48 * 1024:
             # decode-sized steps: projection and top-k in one launch (the last block selects)
             nat.call("lsb_router_fused", L["router"].w, ws.x, ws.logits_r, L["router_bias"], ws.ids, ws.wts, ws.router_done, R, cfg.hidden,
                      cfg.n_routed, cfg.top_k, cfg.n_group, cfg.topk_group, sc, int(cfg.norm_topk_prob), cfg.routed_scale, cfg.n_shared)
@@ -835,8 +841,11 @@ class DeviceModel:
             self._moe_prepare(arena, ws, R)
             self._moe_experts(arena, ws, R, ws.miss if self.tp_size == 1 else None)
             present = arena.slot_of
+        if defer_combine and self.streamer is None and self._cp is None and self.tp_size == 1:
+            return True
         nat.call("lsb_moe_combine", ws.sub, ws.y, ws.wts, ws.ids, present, R, S, cfg.hidden, 0, self._cp)
         self._reduce(ws, R)
+        return False
 
     def _moe_mode(self, arena: ExpertArena, ws: Workspace, R: int) -> str:
         cfg = self.cfg
@@ -946,6 +955,39 @@ class DeviceModel:
         L["mla_o"](ws.sub, ws.attn_v, R, comm=self._cp)
         self._reduce(ws, R)
 
+    def _mhc_cluster_ok(self) -> bool:
+        """Whether the one-launch cluster kernel covers this model's hyper-connection pass on this device (asked once)."""
+        if not hasattr(self, "_mhc_clus"):
+            self._mhc_clus = MHC_CLUSTER and nat.call("lsb_mhc_cluster_width", self.cfg.hidden, self.cfg.hc_mult) > 0
+        return self._mhc_clus
+
+    def _router_foldable(self, ws: "Workspace") -> bool:
+        cfg = self.cfg
+        return cfg.n_routed <= 2048 and cfg.top_k <= 32 and cfg.n_group <= 64 and cfg.n_shared <= 32
+
+    def _hc_pass(self, hc, norm_w, ws: "Workspace", R: int, mode: int, clus: bool, pending, route):
+        """post of the previous sublayer + pre of the next one: residual streams, mixing gates, contracted and normalised input
+        ``ws.x``.  ``pending``: slot table of a MoE layer whose expert outputs (``ws.y``) still have to be combined;
+        ``route``: the MoE layer whose router runs on the new ``ws.x`` inside the same kernel."""
+        cfg = self.cfg
+        fn, sc, base = hc
+        H, n = cfg.hidden, cfg.hc_mult
+        if clus:
+            S = getattr(ws, "S", 0)
+            rs = {"sigmoid": 0, "softmax": 1, "sqrtsoftplus": 2}[cfg.scoring]
+            nat.call("lsb_mhc_cluster", ws.x, ws.resid, ws.sub, ws.post, ws.comb, fn, sc, base, norm_w, R, H, n, mode, cfg.hc_sinkhorn_iters,
+                     cfg.hc_eps, cfg.rms_eps, cfg.hc_post_mult,
+                     ws.y if pending is not None else None, ws.wts if pending is not None else None, ws.ids if pending is not None else None,
+                     pending, S,
+                     route["router"].w if route is not None else None, route["router_bias"] if route is not None else None,
+                     ws.logits_r if route is not None else None, ws.ids if route is not None else None, ws.wts if route is not None else None,
+                     cfg.n_routed, cfg.top_k, cfg.n_group, cfg.topk_group, rs, int(cfg.norm_topk_prob), cfg.routed_scale, cfg.n_shared,
+                     self._cp if pending is None else None)
+            return
+        assert pending is None and route is None
+        nat.call("lsb_mhc_post_pre", ws.x, ws.resid, ws.sub, ws.post, ws.comb, fn, sc, base, norm_w, ws.part, R, H, n,
+                 mode, cfg.hc_sinkhorn_iters, cfg.hc_eps, cfg.rms_eps, cfg.hc_post_mult, ws.hc_done, ws.hc_pre, self._cp)
+
     def forward(self, ws: Workspace, R: int, nseq: int, logit_row0: int, n_logit_rows: int):
         """Run one step over the first ``R`` rows of the workspace (inputs already staged in
         ``ws``).  Writes logits for rows [logit_row0, logit_row0 + n_logit_rows)."""
@@ -960,18 +1002,21 @@ class DeviceModel:
             nat.call("lsb_dcp_rows", ws.row_pos, ws.row_len, ws.row_store, ws.row_len_local, R, self.dcp.chunk, self.tp_size, self.tp_rank)
         if cfg.mhc:
             nat.call("lsb_embedding", ws.sub, None, self.embed, ws.tok, R, H, 0, cfg.vocab)
+            # decode-sized steps: one cluster kernel per post -> pre pass, with the MoE combine folded in front and the router behind
+            clus = R < 64 and self._mhc_cluster_ok()
+            pending = None         # slot table of the MoE layer whose combine the next pass performs
             for i, L in enumerate(self.layers):
-                fn, sc, base = L["hc_attn"]
-                nat.call("lsb_mhc_post_pre", ws.x, ws.resid, ws.sub, ws.post, ws.comb, fn, sc, base, L["attn_norm"], ws.part, R, H, n,
-                         0 if i == 0 else 1, cfg.hc_sinkhorn_iters, cfg.hc_eps, cfg.rms_eps, cfg.hc_post_mult, ws.hc_done, ws.hc_pre, self._cp)
+                self._hc_pass(L["hc_attn"], L["attn_norm"], ws, R, 0 if i == 0 else 1, clus, pending, None)
+                pending = None
                 if cfg.is_kda_layer(i):
                     self._kda(i, L, ws, R, nseq)
                 else:
                     self._mla(i, L, ws, R)
-                fn, sc, base = L["hc_ffn"]
-                nat.call("lsb_mhc_post_pre", ws.x, ws.resid, ws.sub, ws.post, ws.comb, fn, sc, base, L["ffn_norm"], ws.part, R, H, n,
-                         1, cfg.hc_sinkhorn_iters, cfg.hc_eps, cfg.rms_eps, cfg.hc_post_mult, ws.hc_done, ws.hc_pre, self._cp)
-                self._ffn(i, L, ws, R)
+                route = L if (clus and "arena" in L and self._router_foldable(ws)) else None
+                self._hc_pass(L["hc_ffn"], L["ffn_norm"], ws, R, 1, clus, None, route)
+                last = i + 1 == len(self.layers)
+                if self._ffn(i, L, ws, R, routed=route is not None, defer_combine=clus and not last and self.drift is None):
+                    pending = L["arena"].slot_of
                 if self.drift is not None:
                     self.drift[f"layer{i:03d}.ffn_out"] = ws.sub[:R].float().cpu()
             nat.call("lsb_mhc_contract_norm", ws.x, ws.resid, ws.sub, ws.post, ws.comb, self.final_norm, R, H, n, cfg.rms_eps, self._cp)

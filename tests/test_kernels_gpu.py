@@ -119,6 +119,65 @@ def test_mhc_post_pre_and_contract(fused, R):
     close(x, fin, 1e-2, 1e-2, "contract")
 
 
+@pytest.mark.parametrize("H,E,k,R", [(256, 16, 4, 3), (4096, 288, 8, 1), (4096, 288, 8, 5), (2048, 64, 6, 2)])
+def test_mhc_cluster_kernel_with_folded_combine_and_router(H, E, k, R):
+    """The one-launch cluster form of the hyper-connection pass: plain, with the MoE combine folded in front, and with the router
+    projection + top-k folded behind, against the oracle and the stand-alone router / combine arithmetic."""
+    import dataclasses
+    cfg = dataclasses.replace(get_preset("tiny-glm5-next"), hidden=H, n_routed=E, top_k=k, hc_sinkhorn_iters=20)
+    n = cfg.hc_mult
+    if nat.call("lsb_mhc_cluster_width", H, n) <= 0:
+        pytest.skip("no cluster shape for this hidden size on this device")
+    o = ref.Oracle(cfg, {})
+    fn, sc, base, nw = rnd(24, n * H, s=0.05), torch.tensor([0.7, 1.1, 1.3], device=DEV), rnd(24, s=0.5), rnd(H) * 0.1 + 1
+    S = k + 1
+    rw, rb = rnd(E, H, s=0.1, seed=9), rnd(E, s=0.05, seed=10)
+    resid = torch.zeros(R, n, H, device=DEV)
+    post = torch.zeros(R, n, device=DEV); comb = torch.zeros(R, n, n, device=DEV)
+    x = torch.zeros(R, H, device=DEV, dtype=torch.bfloat16)
+    ids = torch.zeros(R, S, dtype=torch.int32, device=DEV); wts = torch.zeros(R, S, device=DEV)
+    logits = torch.zeros(R, E, device=DEV)
+    hc = (cfg.hc_sinkhorn_iters, cfg.hc_eps, cfg.rms_eps, cfg.hc_post_mult)
+    rt = (E, k, 1, 1, 0, 1, 2.5, 1)
+
+    def run(sub, mode, y=None, cw=None, ci=None, so=None, route=False):
+        nat.call("lsb_mhc_cluster", x, resid, sub, post, comb, fn, sc, base, nw, R, H, n, mode, *hc, y, cw, ci, so, S,
+                 rw if route else None, rb if route else None, logits if route else None, ids if route else None, wts if route else None, *rt, None)
+        torch.cuda.synchronize()
+
+    emb = rnd(R, H)
+    run(emb, 0)
+    r_ref = emb.cpu()[:, None, :].repeat(1, n, 1)
+    p_ref, c_ref, x_ref = o.mhc_pre(r_ref, fn.cpu(), sc.cpu(), base.cpu(), nw.cpu())
+    close(resid, r_ref, 1e-6, 1e-6, "expand")
+    close(post, p_ref, 1e-4, 1e-5, "post"); close(comb, c_ref, 1e-4, 1e-5, "comb"); close(x, x_ref, 1e-2, 1e-2, "x")
+    # post of a plain sublayer output, router folded behind
+    sub = rnd(R, H, seed=5)
+    run(sub, 1, route=True)
+    r2 = o.mhc_post(sub.cpu(), r_ref, p_ref, c_ref)
+    p2, c2, x2 = o.mhc_pre(r2, fn.cpu(), sc.cpu(), base.cpu(), nw.cpu())
+    close(resid, r2, 1e-4, 1e-5, "post residual"); close(comb, c2, 1e-4, 1e-5, "comb2"); close(x, x2, 1e-2, 1e-2, "x2")
+    lg_ref = x.float().cpu() @ rw.cpu().T                      # the router consumes the bf16-rounded activations
+    close(logits, lg_ref, 1e-4, 1e-4, "router logits")
+    ids2 = torch.zeros_like(ids); wts2 = torch.zeros_like(wts)
+    nat.call("lsb_router_topk", logits, rb, ids2, wts2, R, E, k, 1, 1, 0, 1, 2.5, 1, E)
+    torch.cuda.synchronize()
+    assert torch.equal(ids, ids2) and torch.equal(wts, wts2), "folded router differs from the stand-alone top-k on the same logits"
+    rid, rwt = ref.route(dataclasses.replace(cfg, routed_scale=2.5), logits.cpu(), rb.cpu())
+    assert torch.equal(ids[:, :k].cpu().long(), rid)
+    # post with the MoE combine folded in front: one expert marked non-resident
+    y = rnd(R * S, H, seed=6)
+    so = torch.arange(E + 1, dtype=torch.int32, device=DEV)
+    so[int(ids[0, 1])] = -1
+    want = torch.zeros(R, H, device=DEV)
+    nat.call("lsb_moe_combine", want, y, wts, ids, so, R, S, H, 0, None)
+    torch.cuda.synchronize()
+    run(None, 1, y=y, cw=wts, ci=ids, so=so)
+    r3 = o.mhc_post(want.cpu(), r2, p2, c2)
+    p3, c3, x3 = o.mhc_pre(r3, fn.cpu(), sc.cpu(), base.cpu(), nw.cpu())
+    close(resid, r3, 1e-4, 1e-5, "post residual after combine"); close(post, p3, 1e-4, 1e-5, "post3"); close(x, x3, 1e-2, 1e-2, "x3")
+
+
 @pytest.mark.parametrize("scoring,n_group,topk_group", [("sigmoid", 1, 1), ("softmax", 1, 1), ("sigmoid", 4, 2), ("sqrtsoftplus", 1, 1)])
 def test_router_topk(scoring, n_group, topk_group):
     E, k, R = 32, 4, 9

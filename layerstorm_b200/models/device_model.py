@@ -96,6 +96,9 @@ ROUTER_FUSED = os.environ.get("LSB_ROUTER_FUSED", "0") != "0"
 KDA_CHUNKED = os.environ.get("LSB_KDA_CHUNKED", "0") not in ("", "0")
 # LSB_MHC_CLUSTER=0: decode-sized hyper-connection passes fall back to the two-launch path (partials + last-block finalize, contraction)
 MHC_CLUSTER = os.environ.get("LSB_MHC_CLUSTER", "1") not in ("", "0")
+# ablation switches of the two folds of the cluster kernel (router behind, MoE combine in front)
+MHC_FOLD_ROUTER = os.environ.get("LSB_MHC_FOLD_ROUTER", "1") not in ("", "0")
+MHC_FOLD_COMBINE = os.environ.get("LSB_MHC_FOLD_COMBINE", "1") not in ("", "0")
 
 
 def _dequant_q4k(raw: torch.Tensor, N: int, K: int) -> torch.Tensor:
@@ -963,7 +966,7 @@ class DeviceModel:
 
     def _router_foldable(self, ws: "Workspace") -> bool:
         cfg = self.cfg
-        return cfg.n_routed <= 2048 and cfg.top_k <= 32 and cfg.n_group <= 64 and cfg.n_shared <= 32
+        return MHC_FOLD_ROUTER and cfg.n_routed <= 2048 and cfg.top_k <= 32 and cfg.n_group <= 64 and cfg.n_shared <= 32
 
     def _hc_pass(self, hc, norm_w, ws: "Workspace", R: int, mode: int, clus: bool, pending, route):
         """post of the previous sublayer + pre of the next one: residual streams, mixing gates, contracted and normalised input
@@ -1015,7 +1018,7 @@ class DeviceModel:
                 route = L if (clus and "arena" in L and self._router_foldable(ws)) else None
                 self._hc_pass(L["hc_ffn"], L["ffn_norm"], ws, R, 1, clus, None, route)
                 last = i + 1 == len(self.layers)
-                if self._ffn(i, L, ws, R, routed=route is not None, defer_combine=clus and not last and self.drift is None):
+                if self._ffn(i, L, ws, R, routed=route is not None, defer_combine=MHC_FOLD_COMBINE and clus and not last and self.drift is None):
                     pending = L["arena"].slot_of
                 if self.drift is not None:
                     self.drift[f"layer{i:03d}.ffn_out"] = ws.sub[:R].float().cpu()

@@ -118,9 +118,53 @@ __device__ __forceinline__ uint2 ldg_stream8(const void* p) {
     return v;
 }
 
+// Asks the memory system to bring [p, p + bytes) into L2 (one instruction for the whole span; p and bytes multiples of 16).
+// Used to start a weight stream before the data dependency of a kernel has resolved, or one kernel ahead of its consumer.
+__device__ __forceinline__ void l2_prefetch_span(const void* p, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+// The share of thread `i` of `n` cooperating threads of a span cut into pieces of `piece` bytes (a multiple of 16).
+__device__ __forceinline__ void l2_prefetch_split(const uint8_t* base, long long bytes, long long piece, int i, int n) {
+    for (long long o = (long long)i * piece; o < bytes; o += (long long)n * piece) {
+        const long long len = bytes - o < piece ? bytes - o : piece;
+        l2_prefetch_span(base + o, (uint32_t)(len & ~15ll));
+    }
+}
+
 // Programmatic dependent launch: let the next kernel's prologue start early, and
 // wait for the previous kernel's memory before touching its outputs.
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Optional step trace: when a trace buffer is installed (lsb_trace_set_* of every translation unit, see utils/step_trace.py), thread 0
+// of block (0,0,0) of EVERY kernel records the time it reached its dependency wait and the time the wait returned - the moment the
+// previous kernel in the stream has completed.  Consecutive "wait returned" stamps are the critical path of a step kernel by kernel,
+// measured inside the CUDA graph with programmatic dependent launch active.  buf[0] = records so far, buf[1] = capacity, then 4
+// words per record: t_reached_wait, t_wait_returned, gridDim.x | gridDim.y << 32, blockDim.x | gridDim.z << 32.
+static __device__ unsigned long long* lsb_trace_buf = nullptr;
+
+__device__ __forceinline__ void pdl_wait() {
+    unsigned long long* tb = nullptr;
+    unsigned long long t0 = 0;
+    if ((blockIdx.x | blockIdx.y | blockIdx.z | threadIdx.x | threadIdx.y) == 0) {
+        tb = lsb_trace_buf;
+        if (tb) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (tb) {
+        unsigned long long t1;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+        const unsigned long long i = atomicAdd(tb, 1ull);
+        if (i < tb[1]) {
+            unsigned long long* r = tb + 2 + 4 * i;
+            r[0] = t0; r[1] = t1;
+            r[2] = (unsigned long long)gridDim.x | ((unsigned long long)gridDim.y << 32);
+            r[3] = (unsigned long long)blockDim.x | ((unsigned long long)gridDim.z << 32);
+        }
+    }
+}
+// Installs the trace buffer of this translation unit (every .cu file exports one setter built from this).
+static inline int lsb_trace_install(void* buf) {
+    unsigned long long* p = reinterpret_cast<unsigned long long*>(buf);
+    return (int)cudaMemcpyToSymbol(lsb_trace_buf, &p, sizeof(p));
+}
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // Kernel launch with programmatic dependent launch: the kernel may become resident while its

@@ -230,3 +230,5 @@ LSB_API int lsb_dcp_scatter_combine(const void* o_part, const void* ml_part, voi
     launch_pdl((dcp_combine_kernel), dim3(R, c.Hh), 128, 0, (cudaStream_t)stream, (bf16*)out, (float*)lse, R, c);
     LSB_CHECK_LAUNCH();
 }
+
+LSB_API int lsb_trace_set_dcp(void* buf) { return lsb_trace_install(buf); }

@@ -174,3 +174,5 @@ LSB_API int lsb_ep_combine(void* out, const void* wts, const void* ids, int rows
                (const int*)ids, S, accumulate, c);
     LSB_CHECK_LAUNCH();
 }
+
+LSB_API int lsb_trace_set_ep_moe(void* buf) { return lsb_trace_install(buf); }

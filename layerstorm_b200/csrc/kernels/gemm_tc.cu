@@ -373,3 +373,5 @@ LSB_API int lsb_gemm_bf16_tc(void* out, const void* x, const void* w, const void
     }
     return 0;
 }
+
+LSB_API int lsb_trace_set_gemm_tc(void* buf) { return lsb_trace_install(buf); }

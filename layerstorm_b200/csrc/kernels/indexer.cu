@@ -403,3 +403,5 @@ LSB_API int lsb_indexer_topk(const void* scores, int ld_scores, const void* n_en
                                                                (const int*)row_seq, budget, P, (int*)sel_idx, (int*)sel_cnt, sel_ld);
     LSB_CHECK_LAUNCH();
 }
+
+LSB_API int lsb_trace_set_indexer(void* buf) { return lsb_trace_install(buf); }

@@ -18,14 +18,33 @@ namespace lsb {
 
 #include "kda_types.cuh"
 
+// Shared-memory row stride (bytes) of the staged low-rank gate rows: 16 bytes of padding make the per-thread 16-byte reads
+// of 32 different rows conflict-free.
+__host__ __device__ constexpr int kda_gate_row_bytes(int rank) { return rank * 2 + 16; }
+
 __global__ void __launch_bounds__(kD) kda_kernel(KdaParams p) {
-    __shared__ float s_q[kD], s_k[kD], s_fa[128], s_ga[128], s_red[33];
+    __shared__ float s_q[kD], s_k[kD], s_fa[128], s_ga[128], s_red[2][33];
+    extern __shared__ __align__(16) uint8_t s_gate[];          // [2][kD] rows of rank bf16 (+ pad): f_b, g_b of this head
     const int seq = blockIdx.x, h = blockIdx.y, t = threadIdx.x;
+    // everything read before the dependency wait is written by the host or by the PREVIOUS step, never by the predecessor kernel
     const int row0 = p.seq_row0[seq], nrows = p.seq_nrows[seq], slot = p.seq_slot[seq];
     if (nrows <= 0) return;
     const int C = p.H * kD, ch = h * kD + t;
-    pdl_wait();
-    pdl_launch_dependents();
+    const int grb = kda_gate_row_bytes(p.rank);
+    {
+        // low-rank gate rows of this head -> shared memory (coalesced 16-byte pieces, asynchronously)
+        const int per_row = p.rank / 8;                          // 16-byte pieces per row
+        const uint8_t* fsrc = reinterpret_cast<const uint8_t*>(p.f_b + (size_t)h * kD * p.rank);
+        const uint8_t* gsrc = reinterpret_cast<const uint8_t*>(p.g_b + (size_t)h * kD * p.rank);
+        for (int idx = t; idx < kD * per_row; idx += kD) {
+            const int rr = idx / per_row, pc = idx - rr * per_row;
+            const uint32_t df = (uint32_t)__cvta_generic_to_shared(s_gate + (size_t)rr * grb + pc * 16);
+            const uint32_t dg = (uint32_t)__cvta_generic_to_shared(s_gate + (size_t)(kD + rr) * grb + pc * 16);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(df), "l"(fsrc + (size_t)idx * 16) : "memory");
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dg), "l"(gsrc + (size_t)idx * 16) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
     // state row
     float S[kD];
     float* sp = p.state + (((size_t)slot * p.H + h) * kD + t) * kD;
@@ -34,7 +53,11 @@ __global__ void __launch_bounds__(kD) kda_kernel(KdaParams p) {
         float4 v = *reinterpret_cast<const float4*>(sp + c);
         S[c] = v.x; S[c + 1] = v.y; S[c + 2] = v.z; S[c + 3] = v.w;
     }
-    // conv history (3 raw taps, oldest first) and taps
+    const uint8_t* fb = s_gate + (size_t)t * grb;
+    const uint8_t* gb = s_gate + (size_t)(kD + t) * grb;
+    pdl_wait();
+    pdl_launch_dependents();
+    // conv history (3 raw taps, oldest first) and taps: small, in flight together with the first projection row
     float hq[3], hk[3], hv[3], wq[4], wk[4], wv[4];
     float* csq = p.conv_state + (((size_t)slot * 3 + 0) * C + ch) * 3;
     float* csk = p.conv_state + (((size_t)slot * 3 + 1) * C + ch) * 3;
@@ -44,12 +67,12 @@ __global__ void __launch_bounds__(kD) kda_kernel(KdaParams p) {
 #pragma unroll
     for (int j = 0; j < 4; ++j) { wq[j] = p.conv_q[ch * 4 + j]; wk[j] = p.conv_k[ch * 4 + j]; wv[j] = p.conv_v[ch * 4 + j]; }
     const float a_exp = p.a_exp[h], dtb = p.dt_bias[ch], ow = p.onorm_w[t];
-    const bf16* fb = p.f_b + (size_t)ch * p.rank;
-    const bf16* gb = p.g_b + (size_t)ch * p.rank;
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
 
     for (int i = 0; i < nrows; ++i) {
         const float* pr = p.proj + (size_t)(row0 + i) * p.ldp;
         const float rq = pr[p.off_q + ch], rk = pr[p.off_k + ch], rv = pr[p.off_v + ch];
+        const float beta = sigmoidf_(pr[p.off_beta + h]);
         float q = hq[0] * wq[0]; q += hq[1] * wq[1]; q += hq[2] * wq[2]; q += rq * wq[3];
         float k = hk[0] * wk[0]; k += hk[1] * wk[1]; k += hk[2] * wk[2]; k += rk * wk[3];
         float v = hv[0] * wv[0]; v += hv[1] * wv[1]; v += hv[2] * wv[2]; v += rv * wv[3];
@@ -58,16 +81,19 @@ __global__ void __launch_bounds__(kD) kda_kernel(KdaParams p) {
         hv[0] = hv[1]; hv[1] = hv[2]; hv[2] = rv;
         q = siluf_(q); k = siluf_(k); v = siluf_(v);
         if (t < p.rank) { s_fa[t] = pr[p.off_fa + t]; s_ga[t] = pr[p.off_ga + t]; }
-        const float qs = block_sum(q * q, s_red);
-        const float ks = block_sum(k * k, s_red);
+        // both squared norms in one pass over the block (fixed order: warp tree, then warp 0 over the warp partials)
+        float qs = warp_sum(q * q), ks = warp_sum(k * k);
+        if ((t & 31) == 0) { s_red[0][t >> 5] = qs; s_red[1][t >> 5] = ks; }
+        __syncthreads();                                       // also publishes s_fa / s_ga and the staged gate rows
+        qs = (s_red[0][0] + s_red[0][1]) + (s_red[0][2] + s_red[0][3]);
+        ks = (s_red[1][0] + s_red[1][1]) + (s_red[1][2] + s_red[1][3]);
         s_q[t] = q * rsqrtf(qs + 1e-6f) * p.scale;
         s_k[t] = k * rsqrtf(ks + 1e-6f);
-        __syncthreads();
         // low-rank tails: raw_g (per key channel t) and g2 (per value channel t)
         float raw_g = 0.f, g2 = 0.f;
         for (int j = 0; j < p.rank; j += 8) {
-            uint4 a = __ldg(reinterpret_cast<const uint4*>(fb + j));
-            uint4 b = __ldg(reinterpret_cast<const uint4*>(gb + j));
+            const uint4 a = *reinterpret_cast<const uint4*>(fb + j * 2);
+            const uint4 b = *reinterpret_cast<const uint4*>(gb + j * 2);
             float af[8], bfv[8];
             unpack_bf16x8(a, af); unpack_bf16x8(b, bfv);
 #pragma unroll
@@ -78,15 +104,30 @@ __global__ void __launch_bounds__(kD) kda_kernel(KdaParams p) {
         __syncthreads();
         s_fa[t] = decay_t;
         __syncthreads();
-        const float beta = sigmoidf_(pr[p.off_beta + h]);
-        float sk = 0.f;
+        // four independent accumulation chains per reduction (a single 128-long dependent FMA chain would bound the step)
+        float sk0 = 0.f, sk1 = 0.f, sk2 = 0.f, sk3 = 0.f;
 #pragma unroll
-        for (int c = 0; c < kD; ++c) { S[c] *= s_fa[c]; sk = fmaf(S[c], s_k[c], sk); }
-        const float err = (v - sk) * beta;
-        float o = 0.f;
+        for (int c = 0; c < kD; c += 4) {
+            S[c] *= s_fa[c]; sk0 = fmaf(S[c], s_k[c], sk0);
+            S[c + 1] *= s_fa[c + 1]; sk1 = fmaf(S[c + 1], s_k[c + 1], sk1);
+            S[c + 2] *= s_fa[c + 2]; sk2 = fmaf(S[c + 2], s_k[c + 2], sk2);
+            S[c + 3] *= s_fa[c + 3]; sk3 = fmaf(S[c + 3], s_k[c + 3], sk3);
+        }
+        const float err = (v - ((sk0 + sk1) + (sk2 + sk3))) * beta;
+        float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
-        for (int c = 0; c < kD; ++c) { S[c] = fmaf(err, s_k[c], S[c]); o = fmaf(S[c], s_q[c], o); }
-        const float os = block_sum(o * o, s_red);
+        for (int c = 0; c < kD; c += 4) {
+            S[c] = fmaf(err, s_k[c], S[c]); o0 = fmaf(S[c], s_q[c], o0);
+            S[c + 1] = fmaf(err, s_k[c + 1], S[c + 1]); o1 = fmaf(S[c + 1], s_q[c + 1], o1);
+            S[c + 2] = fmaf(err, s_k[c + 2], S[c + 2]); o2 = fmaf(S[c + 2], s_q[c + 2], o2);
+            S[c + 3] = fmaf(err, s_k[c + 3], S[c + 3]); o3 = fmaf(S[c + 3], s_q[c + 3], o3);
+        }
+        const float o = (o0 + o1) + (o2 + o3);
+        float os = warp_sum(o * o);
+        __syncthreads();                                       // s_red is free again
+        if ((t & 31) == 0) s_red[0][t >> 5] = os;
+        __syncthreads();
+        os = (s_red[0][0] + s_red[0][1]) + (s_red[0][2] + s_red[0][3]);
         const float y = o * rsqrtf(os / (float)kD + p.eps) * ow * sigmoidf_(g2);
         p.out[(size_t)(row0 + i) * C + ch] = __float2bfloat16(y);
         __syncthreads();
@@ -95,7 +136,6 @@ __global__ void __launch_bounds__(kD) kda_kernel(KdaParams p) {
     for (int c = 0; c < kD; c += 4) *reinterpret_cast<float4*>(sp + c) = make_float4(S[c], S[c + 1], S[c + 2], S[c + 3]);
 #pragma unroll
     for (int j = 0; j < 3; ++j) { csq[j] = hq[j]; csk[j] = hk[j]; csv[j] = hv[j]; }
-    pdl_launch_dependents();
 }
 
 
@@ -462,7 +502,10 @@ static int kda_forward_impl(const void* proj, int ldp, int off_q, int off_k, int
         }
         launch_pdl((kda_out_kernel), dim3(total_rows, H), kD, 0, st, p, w);
     } else {
-        launch_pdl((kda_kernel), dim3(nseq, H), kD, 0, st, p);
+        const int gate_smem = 2 * kD * kda_gate_row_bytes(rank);
+        static bool gate_attr = false;
+        if (!gate_attr) { cudaFuncSetAttribute(kda_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * kD * kda_gate_row_bytes(128)); gate_attr = true; }
+        launch_pdl((kda_kernel), dim3(nseq, H), kD, (size_t)gate_smem, st, p);
     }
     LSB_CHECK_LAUNCH();
 }
@@ -491,3 +534,5 @@ LSB_API int lsb_kda_forward_chunked(const void* proj, int ldp, int off_q, int of
                             dt_bias, onorm_w, state, conv_state, seq_row0, seq_nrows, seq_slot, out, nseq, H, head_dim, scale, lower_bound,
                             eps, total_rows, scratch, chunk_ws, chunk_ws_floats, stream);
 }
+
+LSB_API int lsb_trace_set_kda(void* buf) { return lsb_trace_install(buf); }

@@ -872,3 +872,5 @@ LSB_API int lsb_mla_decode(const void* q, const void* cache, const void* block_t
     if (out) launch_pdl((mla_combine_kernel), dim3(R, H), 128, 0, st, (bf16*)out, (float*)lse, (const float*)o_part, (const float*)ml_part, H, NS, dl);
     LSB_CHECK_LAUNCH();
 }
+
+LSB_API int lsb_trace_set_mla(void* buf) { return lsb_trace_install(buf); }

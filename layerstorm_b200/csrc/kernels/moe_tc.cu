@@ -805,3 +805,5 @@ LSB_API int lsb_gemm_q_tc(void* out, const void* x16, const void* w, const void*
     }
     return -1;
 }
+
+LSB_API int lsb_trace_set_moe_tc(void* buf) { return lsb_trace_install(buf); }

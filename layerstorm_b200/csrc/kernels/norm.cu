@@ -631,3 +631,5 @@ LSB_API int lsb_mhc_contract_norm(void* out, const void* residual, const void* x
                                                                                       (const float*)norm_w, hidden, n, rms_eps, comm_from_host(comm));
     LSB_CHECK_LAUNCH();
 }
+
+LSB_API int lsb_trace_set_norm(void* buf) { return lsb_trace_install(buf); }

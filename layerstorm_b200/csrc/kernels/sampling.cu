@@ -356,3 +356,5 @@ LSB_API int lsb_argmax_noalloc(const float* logits, int ld, int rows, int V, int
 }
 
 LSB_API int lsb_argmax_noalloc_max_rows() { return kNoAllocMaxRows; }
+
+LSB_API int lsb_trace_set_sampling(void* buf) { return lsb_trace_install(buf); }

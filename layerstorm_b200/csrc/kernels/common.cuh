@@ -118,19 +118,6 @@ __device__ __forceinline__ uint2 ldg_stream8(const void* p) {
     return v;
 }
 
-// Asks the memory system to bring [p, p + bytes) into L2 (one instruction for the whole span; p and bytes multiples of 16).
-// Used to start a weight stream before the data dependency of a kernel has resolved, or one kernel ahead of its consumer.
-__device__ __forceinline__ void l2_prefetch_span(const void* p, uint32_t bytes) {
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
-}
-// The share of thread `i` of `n` cooperating threads of a span cut into pieces of `piece` bytes (a multiple of 16).
-__device__ __forceinline__ void l2_prefetch_split(const uint8_t* base, long long bytes, long long piece, int i, int n) {
-    for (long long o = (long long)i * piece; o < bytes; o += (long long)n * piece) {
-        const long long len = bytes - o < piece ? bytes - o : piece;
-        l2_prefetch_span(base + o, (uint32_t)(len & ~15ll));
-    }
-}
-
 // Programmatic dependent launch: let the next kernel's prologue start early, and
 // wait for the previous kernel's memory before touching its outputs.
 // Optional step trace: when a trace buffer is installed (lsb_trace_set_* of every translation unit, see utils/step_trace.py), thread 0

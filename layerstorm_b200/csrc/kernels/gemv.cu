@@ -40,8 +40,7 @@ struct MatNvfp4 {
 // through shared memory in slice order, so the result is deterministic.
 template <class Mat, int MT, bool OUT_BF16, int KS>
 __global__ void __launch_bounds__(256) gemv_kernel(Mat mat, const bf16* __restrict__ x, int ldx, void* __restrict__ out,
-                                                   int ldo, int N, int K, float alpha, const float* __restrict__ bias, PeerComm comm,
-                                                   const uint8_t* __restrict__ pf_base, long long pf_bytes) {
+                                                   int ldo, int N, int K, float alpha, const float* __restrict__ bias, PeerComm comm) {
     __shared__ float red[8][2 * MT];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     constexpr int PAIRS = 8 / KS;
@@ -59,12 +58,7 @@ __global__ void __launch_bounds__(256) gemv_kernel(Mat mat, const bf16* __restri
     for (int m = 0; m < MT; ++m) acc0[m] = acc1[m] = 0.f;
     auto r0 = mat.row(n0);
     auto r1 = mat.row(n1);
-    if (pf_bytes > 0) {
-        // contiguous weights that fit L2: the blocks that become resident under the predecessor's tail ask for the WHOLE matrix
-        // (or its head) before the dependency resolves, so the stream is not bounded by what one wave of blocks can request
-        const int nb = min((int)gridDim.x, 592);
-        if ((int)blockIdx.x < nb && threadIdx.x < 4) l2_prefetch_split(pf_base, pf_bytes, 16384, (int)blockIdx.x * 4 + (int)threadIdx.x, nb * 4);
-    } else if (active) {   // weights do not depend on the previous kernel: pull the head of both rows into L2 while it finishes
+    if (active) {   // weights do not depend on the previous kernel: pull the head of both rows into L2 while it finishes
 #pragma unroll
         for (int it = 0; it < 4; ++it) {
             const int k = k0 + (lane + 32 * it) * E;
@@ -118,35 +112,27 @@ __global__ void __launch_bounds__(256) gemv_kernel(Mat mat, const bf16* __restri
 
 template <class Mat, int MT, bool OB, int KS>
 static void launch_one(Mat mat, const bf16* xp, int ldx, void* op, int ldo, int N, int K, float alpha, const float* bias, PeerComm comm,
-                       cudaStream_t st, const uint8_t* pf_base, long long pf_bytes) {
+                       cudaStream_t st) {
     const int rows_per_block = (8 / KS) * 2;
     // The kernel streams its weights past L1 (no-allocate loads) and keeps only the activation row there, so it asks for the
-    // largest shared-memory carve-out: a following kernel that stages tens of KB in shared memory (the hyper-connection cluster
-    // kernel, the KDA step) can then become resident on an SM that still runs the tail of this one.  LSB_GEMV_CARVEOUT=-1: leave the default.
+    // largest shared-memory carve-out: a following kernel that stages tens of KB in shared memory (the KDA step) can then become
+    // resident on an SM that still runs the tail of this one (measured: KDA step 14.4 -> 9.6 us).  LSB_GEMV_CARVEOUT=-1: leave the default.
     static bool once = false;
     if (!once) {
         static const int carve = [] { const char* e = getenv("LSB_GEMV_CARVEOUT"); return e ? atoi(e) : 100; }();
         if (carve >= 0) cudaFuncSetAttribute(gemv_kernel<Mat, MT, OB, KS>, cudaFuncAttributePreferredSharedMemoryCarveout, carve);
         once = true;
     }
-    launch_pdl((gemv_kernel<Mat, MT, OB, KS>), (N + rows_per_block - 1) / rows_per_block, 256, 0, st, mat, xp, ldx, op, ldo, N, K, alpha, bias, comm,
-               pf_base, pf_bytes);
+    launch_pdl((gemv_kernel<Mat, MT, OB, KS>), (N + rows_per_block - 1) / rows_per_block, 256, 0, st, mat, xp, ldx, op, ldo, N, K, alpha, bias, comm);
 }
 
 template <class Mat, int MT, bool OB>
 static void launch_ks(int ks, Mat mat, const bf16* xp, int ldx, void* op, int ldo, int N, int K, float alpha, const float* bias, PeerComm comm,
-                      cudaStream_t st, const uint8_t* pf_base, long long pf_bytes) {
-    if (ks == 1) launch_one<Mat, MT, OB, 1>(mat, xp, ldx, op, ldo, N, K, alpha, bias, comm, st, pf_base, pf_bytes);
-    else if (ks == 2) launch_one<Mat, MT, OB, 2>(mat, xp, ldx, op, ldo, N, K, alpha, bias, comm, st, pf_base, pf_bytes);
-    else if (ks == 4) launch_one<Mat, MT, OB, 4>(mat, xp, ldx, op, ldo, N, K, alpha, bias, comm, st, pf_base, pf_bytes);
-    else launch_one<Mat, MT, OB, 8>(mat, xp, ldx, op, ldo, N, K, alpha, bias, comm, st, pf_base, pf_bytes);
-}
-
-// LSB_GEMV_PF_MB: largest span (MiB) of a contiguous weight matrix requested into L2 before the dependency wait (0 = only the
-// per-row heads, as for the block-scaled formats).  Matrices beyond it get their first rows requested.
-static long long gemv_prefetch_budget() {
-    static const long long b = [] { const char* e = getenv("LSB_GEMV_PF_MB"); return (long long)(e ? atoi(e) : 64) << 20; }();
-    return b;
+                      cudaStream_t st) {
+    if (ks == 1) launch_one<Mat, MT, OB, 1>(mat, xp, ldx, op, ldo, N, K, alpha, bias, comm, st);
+    else if (ks == 2) launch_one<Mat, MT, OB, 2>(mat, xp, ldx, op, ldo, N, K, alpha, bias, comm, st);
+    else if (ks == 4) launch_one<Mat, MT, OB, 4>(mat, xp, ldx, op, ldo, N, K, alpha, bias, comm, st);
+    else launch_one<Mat, MT, OB, 8>(mat, xp, ldx, op, ldo, N, K, alpha, bias, comm, st);
 }
 
 // K-split so that the grid is at least ~two full waves (148 SMs x 8 resident blocks) while every
@@ -159,8 +145,7 @@ static int choose_ks(int N, int K, int epl) {
 
 template <class Mat>
 static int launch_gemv(Mat mat, const bf16* x, int ldx, void* out, int ldo, int M, int N, int K, float alpha,
-                       const float* bias, int out_bf16, cudaStream_t st, const void* comm_host = nullptr, const void* pf_base = nullptr,
-                       long long pf_total = 0) {
+                       const float* bias, int out_bf16, cudaStream_t st, const void* comm_host = nullptr) {
     PeerComm comm;
     comm.nranks = 0;
     if (comm_host) {
@@ -169,16 +154,14 @@ static int launch_gemv(Mat mat, const bf16* x, int ldx, void* out, int ldo, int 
     }
     const size_t osz = out_bf16 ? 2 : 4;
     const int ks = choose_ks(N, K, decltype(mat.row(0))::EPL);
-    const long long pf_bytes = (pf_base && ((uintptr_t)pf_base & 15) == 0) ? (pf_total < gemv_prefetch_budget() ? pf_total : gemv_prefetch_budget()) & ~15ll : 0;
-    const uint8_t* pfb = reinterpret_cast<const uint8_t*>(pf_base);
     for (int m0 = 0; m0 < M;) {
         const int rem = M - m0;
         const int mt = rem >= 4 ? 4 : (rem >= 2 ? 2 : 1);
         const bf16* xp = x + (size_t)m0 * ldx;
         void* op = reinterpret_cast<char*>(out) + (size_t)m0 * ldo * osz;
 #define LSB_GEMV_CASE(MT_)                                                                              \
-    if (out_bf16) launch_ks<Mat, MT_, true>(ks, mat, xp, ldx, op, ldo, N, K, alpha, bias, comm, st, pfb, m0 == 0 ? pf_bytes : 0);  \
-    else launch_ks<Mat, MT_, false>(ks, mat, xp, ldx, op, ldo, N, K, alpha, bias, comm, st, pfb, m0 == 0 ? pf_bytes : 0);
+    if (out_bf16) launch_ks<Mat, MT_, true>(ks, mat, xp, ldx, op, ldo, N, K, alpha, bias, comm, st);  \
+    else launch_ks<Mat, MT_, false>(ks, mat, xp, ldx, op, ldo, N, K, alpha, bias, comm, st);
         if (mt == 4) { LSB_GEMV_CASE(4) } else if (mt == 2) { LSB_GEMV_CASE(2) } else { LSB_GEMV_CASE(1) }
 #undef LSB_GEMV_CASE
         m0 += mt;
@@ -196,7 +179,7 @@ LSB_API int lsb_gemv_bf16(void* out, const void* x, const void* w, const void* b
                           int ldw, int ldo, float alpha, int out_bf16, const void* comm, void* stream) {
     if (K % 8 || ldw % 8 || ldx % 8) return -1;
     return launch_gemv(MatBf16{(const bf16*)w, ldw}, (const bf16*)x, ldx, out, ldo, M, N, K, alpha, (const float*)bias,
-                       out_bf16, (cudaStream_t)stream, comm, ldw == K ? w : nullptr, (long long)N * K * 2);
+                       out_bf16, (cudaStream_t)stream, comm);
 }
 
 namespace lsb {
@@ -268,7 +251,7 @@ LSB_API int lsb_gemv_f32w(void* out, const void* x, const void* w, const void* b
         LSB_CHECK_LAUNCH();
     }
     return launch_gemv(MatF32{(const float*)w, ldw}, (const bf16*)x, ldx, out, ldo, M, N, K, alpha, (const float*)bias,
-                       out_bf16, (cudaStream_t)stream, nullptr, ldw == K ? w : nullptr, (long long)N * K * 4);
+                       out_bf16, (cudaStream_t)stream);
 }
 
 // W: e4m3 [N, K] with fp32 scales [ceil(N/128), ceil(K/128)] (128x128 blocks). K % 16 == 0.

@@ -64,52 +64,60 @@ struct MhcClusterArgs {
     PeerComm comm;
 };
 
-// Column layout of a CTA: `groups` column groups of 128 columns (4 consecutive columns per lane); a column group is served
-// by four warps, warp og of them owning mixing logits 6 og .. 6 og + 5.  The CTA's slice of the mixing rows `fn`
-// (24 x n x cols fp32, 96 KB at 256 columns) is staged in shared memory by asynchronous copies issued BEFORE the dependency
-// wait, and the thread count / register need is kept small (256 threads), so that the CTAs of a cluster can become resident
-// next to the tail of the preceding weight-streaming kernel and have the slice in place when the dependency resolves.
-constexpr int kCVec = 4;
-constexpr int kCGroupCols = 32 * kCVec;                  // 128
+template <int VEC> struct VecT;
+template <> struct VecT<1> { using T = float; };
+template <> struct VecT<2> { using T = float2; };
 
-__device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+template <int VEC> __device__ __forceinline__ typename VecT<VEC>::T vld(const float* p);
+template <> __device__ __forceinline__ float vld<1>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float2 vld<2>(const float* p) { return *reinterpret_cast<const float2*>(p); }
+template <int VEC> __device__ __forceinline__ typename VecT<VEC>::T vldg(const float* p);
+template <> __device__ __forceinline__ float vldg<1>(const float* p) { return __ldg(p); }
+template <> __device__ __forceinline__ float2 vldg<2>(const float* p) { return __ldg(reinterpret_cast<const float2*>(p)); }
 
-__global__ void __launch_bounds__(256, 1) mhc_cluster_kernel(const __grid_constant__ MhcClusterArgs a) {
+template <int VEC>
+__global__ void __launch_bounds__(512, 1) mhc_cluster_kernel(const __grid_constant__ MhcClusterArgs a) {
     cg::cluster_group cluster = cg::this_cluster();
     const unsigned crank = cluster.block_rank(), csize = cluster.num_blocks();
-    __shared__ float s_part[2][kCSum];
-    __shared__ float s_all[kCMaxCluster][kCSum + 2];          // partial sums of every CTA of the cluster (pushed by their owners)
+    __shared__ float s_part[4][kCSum];
+    __shared__ float s_cta[kCSum + 2];
     __shared__ float mix[kCSum + 2];
     __shared__ float s_pre[8];
-    __shared__ __align__(16) float xs[2 * kCGroupCols];
-    extern __shared__ __align__(16) float dyn[];              // [kCOut][n][cols] mixing rows, then the router scratch
+    __shared__ float xs[4 * 32 * VEC];
+    extern __shared__ float dyn[];                  // router: [E] partial logits, [E] logits, top-k scratch
     const int t = threadIdx.x, lane = t & 31, w = t >> 5, og = w & 3, grp = w >> 2;
     const int groups = blockDim.x >> 7;
     const int r = blockIdx.y;
     const int n = a.n, hidden = a.hidden;
-    const int cols = groups * kCGroupCols;                    // columns of this CTA
+    const int cols = groups * 32 * VEC;             // columns of this CTA
     const int c0 = (int)crank * cols;
-    const int hl = grp * kCGroupCols + lane * kCVec;          // column inside the CTA slice
+    const int hl = grp * 32 * VEC + lane * VEC;     // column inside the CTA slice
     const int h = c0 + hl;
     const int nout = 2 * n + n * n;
-    float* sf = dyn;
-    float* rdyn = dyn + (size_t)kCOut * kCMax * cols;
 
-    // first half of a start-up barrier: a CTA's shared memory may be written by its peers only once it is known to run
-    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-    // mixing rows of this CTA's columns -> shared memory; independent of the previous kernel
-    {
-        const int per_row = cols >> 2;                        // 16-byte pieces per (logit, stream) row
-        const int total = nout * n * per_row;
-        for (int idx = t; idx < total; idx += blockDim.x) {
-            const int row = idx / per_row, pc = idx - row * per_row;          // row = o * n + j
-            const uint32_t dst = (uint32_t)__cvta_generic_to_shared(sf + (size_t)row * cols + pc * 4);
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(a.fn + (size_t)row * hidden + c0 + pc * 4) : "memory");
+    // mixing rows: independent of the previous kernel
+    float f[kCPerWarp][kCMax][VEC];
+#pragma unroll
+    for (int i = 0; i < kCPerWarp; ++i) {
+        const int o = og * kCPerWarp + i;
+#pragma unroll
+        for (int j = 0; j < kCMax; ++j) {
+            if (o < nout && j < n) {
+                const typename VecT<VEC>::T v = vldg<VEC>(a.fn + ((size_t)o * n + j) * hidden + h);
+                memcpy(f[i][j], &v, sizeof(v));
+            } else {
+#pragma unroll
+                for (int u = 0; u < VEC; ++u) f[i][j][u] = 0.f;
+            }
         }
-        asm volatile("cp.async.commit_group;" ::: "memory");
     }
-    const float4 nw4 = __ldg(reinterpret_cast<const float4*>(a.norm_w + h));
+    float nw[VEC];
+    {
+        const typename VecT<VEC>::T v = vldg<VEC>(a.norm_w + h);
+        memcpy(nw, &v, sizeof(v));
+    }
     if (a.router_w) {
+        // the router rows of this CTA's column slice: start them towards L2 under the predecessor's tail
         for (int e = w; e < a.E; e += (int)(blockDim.x >> 5))
             for (int k = lane * 32; k < cols; k += 32 * 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(a.router_w + (size_t)e * hidden + c0 + k));
     }
@@ -117,12 +125,12 @@ __global__ void __launch_bounds__(256, 1) mhc_cluster_kernel(const __grid_consta
     pdl_launch_dependents();
 
     // ---- sublayer output for this thread's columns ----
-    float xv[kCVec];
+    float xv[VEC];
     if (a.comm.nranks && a.mode == 1) {
         const unsigned epoch = *a.comm.epoch;
         comm_wait(a.comm, epoch);
 #pragma unroll
-        for (int u = 0; u < kCVec; ++u) xv[u] = comm_reduce(a.comm, epoch, (size_t)r * hidden + h + u);
+        for (int u = 0; u < VEC; ++u) xv[u] = comm_reduce(a.comm, epoch, (size_t)r * hidden + h + u);
     } else if (a.y) {
         int e[kCMaxS];
         float wt[kCMaxS];
@@ -130,71 +138,80 @@ __global__ void __launch_bounds__(256, 1) mhc_cluster_kernel(const __grid_consta
         for (int s = 0; s < kCMaxS; ++s) { e[s] = s < a.S ? a.cids[r * a.S + s] : -1; wt[s] = s < a.S ? a.cwts[r * a.S + s] : 0.f; }
 #pragma unroll
         for (int s = 0; s < kCMaxS; ++s) if (e[s] >= 0 && a.slot_of[e[s]] < 0) e[s] = -1;
-        float4 v[kCMaxS];
+        float v[kCMaxS][VEC];
 #pragma unroll
-        for (int s = 0; s < kCMaxS; ++s) v[s] = e[s] >= 0 ? ld4(a.y + ((size_t)r * a.S + s) * hidden + h) : make_float4(0.f, 0.f, 0.f, 0.f);
-        xv[0] = xv[1] = xv[2] = xv[3] = 0.f;
+        for (int s = 0; s < kCMaxS; ++s) {
+            if (e[s] >= 0) {
+                const typename VecT<VEC>::T q = vld<VEC>(a.y + ((size_t)r * a.S + s) * hidden + h);
+                memcpy(v[s], &q, sizeof(q));
+            } else {
+#pragma unroll
+                for (int u = 0; u < VEC; ++u) v[s][u] = 0.f;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < VEC; ++u) xv[u] = 0.f;
 #pragma unroll
         for (int s = 0; s < kCMaxS; ++s)
             if (e[s] >= 0) {
-                xv[0] = fmaf(wt[s], v[s].x, xv[0]); xv[1] = fmaf(wt[s], v[s].y, xv[1]);
-                xv[2] = fmaf(wt[s], v[s].z, xv[2]); xv[3] = fmaf(wt[s], v[s].w, xv[3]);
+#pragma unroll
+                for (int u = 0; u < VEC; ++u) xv[u] = fmaf(wt[s], v[s][u], xv[u]);
             }
     } else {
-        const float4 q = ld4(a.x + (size_t)r * hidden + h);
-        xv[0] = q.x; xv[1] = q.y; xv[2] = q.z; xv[3] = q.w;
+        const typename VecT<VEC>::T q = vld<VEC>(a.x + (size_t)r * hidden + h);
+        memcpy(xv, &q, sizeof(q));
     }
 
     // ---- new residual streams (every warp of a column group recomputes them; warp og 0 stores) ----
-    float res[kCMax][kCVec];
+    float res[kCMax][VEC];
     float* rp = a.residual + (size_t)r * n * hidden;
     if (a.mode == 0) {
 #pragma unroll
         for (int j = 0; j < kCMax; ++j)
 #pragma unroll
-            for (int u = 0; u < kCVec; ++u) res[j][u] = j < n ? xv[u] : 0.f;
+            for (int u = 0; u < VEC; ++u) res[j][u] = j < n ? xv[u] : 0.f;
     } else {
-        float old[kCMax][kCVec];
+        float old[kCMax][VEC];
 #pragma unroll
         for (int i = 0; i < kCMax; ++i) {
-            const float4 q = i < n ? ld4(rp + (size_t)i * hidden + h) : make_float4(0.f, 0.f, 0.f, 0.f);
-            old[i][0] = q.x; old[i][1] = q.y; old[i][2] = q.z; old[i][3] = q.w;
+            if (i < n) {
+                const typename VecT<VEC>::T q = vld<VEC>(rp + (size_t)i * hidden + h);
+                memcpy(old[i], &q, sizeof(q));
+            } else {
+#pragma unroll
+                for (int u = 0; u < VEC; ++u) old[i][u] = 0.f;
+            }
         }
 #pragma unroll
         for (int j = 0; j < kCMax; ++j) {
-            float acc[kCVec] = {0.f, 0.f, 0.f, 0.f};
+            float acc[VEC];
+#pragma unroll
+            for (int u = 0; u < VEC; ++u) acc[u] = 0.f;
             if (j < n) {
                 const float pj = a.post[r * n + j];
 #pragma unroll
-                for (int u = 0; u < kCVec; ++u) acc[u] = pj * xv[u];
+                for (int u = 0; u < VEC; ++u) acc[u] = pj * xv[u];
                 for (int i = 0; i < n; ++i) {
                     const float cj = a.comb[(r * n + i) * n + j];
 #pragma unroll
-                    for (int u = 0; u < kCVec; ++u) acc[u] += cj * old[i][u];
+                    for (int u = 0; u < VEC; ++u) acc[u] += cj * old[i][u];
                 }
             }
 #pragma unroll
-            for (int u = 0; u < kCVec; ++u) res[j][u] = acc[u];
+            for (int u = 0; u < VEC; ++u) res[j][u] = acc[u];
         }
     }
 
     // ---- partial mixing logits and Gram entries over this warp's columns ----
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
-    __syncthreads();                                 // the staged mixing rows of all threads are visible
 #pragma unroll
     for (int i = 0; i < kCPerWarp; ++i) {
-        const int o = og * kCPerWarp + i;
         float acc = 0.f;
-        if (o < nout) {
 #pragma unroll
-            for (int j = 0; j < kCMax; ++j)
-                if (j < n) {
-                    const float4 f4 = ld4(sf + (size_t)(o * n + j) * cols + hl);
-                    acc = fmaf(res[j][0], f4.x, acc); acc = fmaf(res[j][1], f4.y, acc);
-                    acc = fmaf(res[j][2], f4.z, acc); acc = fmaf(res[j][3], f4.w, acc);
-                }
-        }
+        for (int j = 0; j < kCMax; ++j)
+#pragma unroll
+            for (int u = 0; u < VEC; ++u) acc = fmaf(res[j][u], f[i][j][u], acc);
         acc = warp_sum(acc);
+        const int o = og * kCPerWarp + i;
         if (lane == 0 && o < kCOut) s_part[grp][o] = acc;
     }
     {
@@ -206,89 +223,76 @@ __global__ void __launch_bounds__(256, 1) mhc_cluster_kernel(const __grid_consta
                 if ((e & 3) == og) {
                     float g = 0.f;
 #pragma unroll
-                    for (int u = 0; u < kCVec; ++u) g = fmaf(res[j][u], res[k][u], g);
+                    for (int u = 0; u < VEC; ++u) g = fmaf(res[j][u], res[k][u], g);
                     g = warp_sum(g);
                     if (lane == 0) s_part[grp][kCOut + e] = g;
                 }
     }
     __syncthreads();                                 // every warp has read the old residual; partials are in shared memory
-    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");      // second half: every CTA of the cluster has started (long since)
-    // push this CTA's 34 sums into slot [crank] of EVERY CTA of the cluster (distributed shared memory stores)
-    for (int i = t; i < kCSum * (int)csize; i += blockDim.x) {
-        const int c = i / kCSum, k = i - c * kCSum;
+    if (t < kCSum) {
         float acc = 0.f;
-        for (int g = 0; g < groups; ++g) acc += s_part[g][k];
-        *cluster.map_shared_rank(&s_all[crank][k], c) = acc;
+        for (int g = 0; g < groups; ++g) acc += s_part[g][t];
+        s_cta[t] = acc;
     }
     if (og == 0) {
 #pragma unroll
         for (int j = 0; j < kCMax; ++j)
-            if (j < n) *reinterpret_cast<float4*>(rp + (size_t)j * hidden + h) = make_float4(res[j][0], res[j][1], res[j][2], res[j][3]);
+            if (j < n) {
+                typename VecT<VEC>::T q;
+                memcpy(&q, res[j], sizeof(q));
+                *reinterpret_cast<typename VecT<VEC>::T*>(rp + (size_t)j * hidden + h) = q;
+            }
     }
-    cluster.sync();                                  // the only cluster barrier of the plain pass: all slices have arrived everywhere
+    cluster.sync();                                  // #1: all slices published
 
     if (t < kCSum) {
+        float v[kCMaxCluster];
+#pragma unroll
+        for (int c = 0; c < kCMaxCluster; ++c) v[c] = c < (int)csize ? *cluster.map_shared_rank(&s_cta[t], c) : 0.f;
         float acc = 0.f;
-        for (int c = 0; c < (int)csize; ++c) acc += s_all[c][t];           // CTA order: the same bits in every CTA
+#pragma unroll
+        for (int c = 0; c < kCMaxCluster; ++c) acc += v[c];
         mix[t] = acc;
     }
     __syncthreads();
     if (w == 0) {
-        // all lanes compute the same gates and the Sinkhorn normalisation in registers (no shuffles on the dependent chain)
+        // sum of squares of the residual streams = trace of the Gram matrix
         float tr = 0.f;
         { int e = 0; for (int j = 0; j < kCMax; ++j) for (int k = j; k < kCMax; ++k, ++e) if (k == j && j < n) tr += mix[kCOut + e]; }
         const float inv = rsqrtf(tr / (float)(n * hidden) + a.rms_eps);
-        float cm[kCMax][kCMax];
-        const float s2 = a.hc_scale[2];
-#pragma unroll
-        for (int i = 0; i < kCMax; ++i) {
-            float v[kCMax], mx = -INFINITY;
-#pragma unroll
-            for (int j = 0; j < kCMax; ++j) {
-                v[j] = (i < n && j < n) ? mix[2 * n + i * n + j] * inv * s2 + a.hc_base[2 * n + i * n + j] : -INFINITY;
-                mx = fmaxf(mx, v[j]);
-            }
-            float e[kCMax], sm = 0.f;
-#pragma unroll
-            for (int j = 0; j < kCMax; ++j) { e[j] = (i < n && j < n) ? expf(v[j] - mx) : 0.f; }
-            sm = (e[0] + e[1]) + (e[2] + e[3]);
-#pragma unroll
-            for (int j = 0; j < kCMax; ++j) cm[i][j] = (i < n && j < n) ? e[j] / sm + a.hc_eps : 0.f;
-        }
-        // column normalise, then (iters - 1) x (row normalise, column normalise)
-#pragma unroll
-        for (int j = 0; j < kCMax; ++j) {
-            const float cs = (cm[0][j] + cm[2][j]) + (cm[1][j] + cm[3][j]);
-#pragma unroll
-            for (int i = 0; i < kCMax; ++i) cm[i][j] = (i < n && j < n) ? cm[i][j] / (cs + a.hc_eps) : 0.f;
-        }
-        for (int it = 1; it < a.iters; ++it) {
-#pragma unroll
-            for (int i = 0; i < kCMax; ++i) {
-                const float rs = (cm[i][0] + cm[i][1]) + (cm[i][2] + cm[i][3]);
-#pragma unroll
-                for (int j = 0; j < kCMax; ++j) cm[i][j] = (i < n && j < n) ? cm[i][j] / (rs + a.hc_eps) : 0.f;
-            }
-#pragma unroll
-            for (int j = 0; j < kCMax; ++j) {
-                const float cs = (cm[0][j] + cm[2][j]) + (cm[1][j] + cm[3][j]);
-#pragma unroll
-                for (int i = 0; i < kCMax; ++i) cm[i][j] = (i < n && j < n) ? cm[i][j] / (cs + a.hc_eps) : 0.f;
+        float cm = 0.f;
+        const int i = (t & 15) >> 2, j = t & 3;
+        const bool valid = t < 16 && i < n && j < n;
+        {
+            float v = valid ? mix[2 * n + i * n + j] * inv * a.hc_scale[2] + a.hc_base[2 * n + i * n + j] : -INFINITY;
+            float mx = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            float e = valid ? expf(v - mx) : 0.f;
+            float sm = e + __shfl_xor_sync(0xffffffffu, e, 1);
+            sm += __shfl_xor_sync(0xffffffffu, sm, 2);
+            cm = valid ? e / sm + a.hc_eps : 0.f;
+            float cs = cm + __shfl_xor_sync(0xffffffffu, cm, 4);
+            cs += __shfl_xor_sync(0xffffffffu, cs, 8);
+            cm = valid ? cm / (cs + a.hc_eps) : 0.f;
+            for (int it = 1; it < a.iters; ++it) {
+                float rs = cm + __shfl_xor_sync(0xffffffffu, cm, 1);
+                rs += __shfl_xor_sync(0xffffffffu, rs, 2);
+                cm = valid ? cm / (rs + a.hc_eps) : 0.f;
+                cs = cm + __shfl_xor_sync(0xffffffffu, cm, 4);
+                cs += __shfl_xor_sync(0xffffffffu, cs, 8);
+                cm = valid ? cm / (cs + a.hc_eps) : 0.f;
             }
         }
+        if (valid && crank == 0) a.comb[(r * n + i) * n + j] = cm;
+        // pre gates on lanes 16..19, post gates on lanes 20..23
+        float pre_v = 0.f;
+        if (t >= 16 && t < 16 + kCMax && t - 16 < n) pre_v = sigmoidf_(mix[t - 16] * inv * a.hc_scale[0] + a.hc_base[t - 16]) + a.hc_eps;
+        if (crank == 0 && t >= 20 && t < 20 + kCMax && t - 20 < n)
+            a.post[r * n + (t - 20)] = sigmoidf_(mix[n + t - 20] * inv * a.hc_scale[1] + a.hc_base[n + t - 20]) * a.post_mult;
         float pj[kCMax];
 #pragma unroll
-        for (int q = 0; q < kCMax; ++q) pj[q] = q < n ? sigmoidf_(mix[q] * inv * a.hc_scale[0] + a.hc_base[q]) + a.hc_eps : 0.f;
-        if (crank == 0) {
-#pragma unroll
-            for (int i = 0; i < kCMax; ++i)
-#pragma unroll
-                for (int j = 0; j < kCMax; ++j)
-                    if (lane == i * kCMax + j && i < n && j < n) a.comb[(r * n + i) * n + j] = cm[i][j];
-            if (lane >= 16 && lane < 16 + kCMax && lane - 16 < n)
-                a.post[r * n + (lane - 16)] = sigmoidf_(mix[n + lane - 16] * inv * a.hc_scale[1] + a.hc_base[n + lane - 16]) * a.post_mult;
-        }
-        if (lane == 0) {
+        for (int q = 0; q < kCMax; ++q) pj[q] = __shfl_sync(0xffffffffu, pre_v, 16 + q);
+        if (t == 0) {
             float quad = 0.f;
             int e = 0;
             for (int p = 0; p < kCMax; ++p)
@@ -303,28 +307,34 @@ __global__ void __launch_bounds__(256, 1) mhc_cluster_kernel(const __grid_consta
     // ---- contraction + RMSNorm of this CTA's columns ----
     if (og == 0) {
         const float inv = s_pre[4];
-        const float nwv[kCVec] = {nw4.x, nw4.y, nw4.z, nw4.w};
-        float o[kCVec];
+        float o[VEC];
 #pragma unroll
-        for (int u = 0; u < kCVec; ++u) {
+        for (int u = 0; u < VEC; ++u) {
             float acc = 0.f;
 #pragma unroll
             for (int j = 0; j < kCMax; ++j) acc = fmaf(j < n ? s_pre[j] : 0.f, res[j][u], acc);
-            o[u] = acc * inv * nwv[u];
+            o[u] = acc * inv * nw[u];
         }
-        const bf162 p0 = __floats2bfloat162_rn(o[0], o[1]), p1 = __floats2bfloat162_rn(o[2], o[3]);
-        uint2 pk;
-        pk.x = *reinterpret_cast<const uint32_t*>(&p0); pk.y = *reinterpret_cast<const uint32_t*>(&p1);
-        *reinterpret_cast<uint2*>(a.out + (size_t)r * hidden + h) = pk;
-        const float2 b0 = __bfloat1622float2(p0), b1 = __bfloat1622float2(p1);
-        *reinterpret_cast<float4*>(xs + hl) = make_float4(b0.x, b0.y, b1.x, b1.y);
+        if (VEC == 2) {
+            const bf162 p = __floats2bfloat162_rn(o[0], o[VEC - 1]);
+            *reinterpret_cast<bf162*>(a.out + (size_t)r * hidden + h) = p;
+            const float2 back = __bfloat1622float2(p);
+            xs[hl] = back.x; xs[hl + VEC - 1] = back.y;
+        } else {
+            const bf16 p = __float2bfloat16(o[0]);
+            a.out[(size_t)r * hidden + h] = p;
+            xs[hl] = __bfloat162float(p);
+        }
     }
-    if (!a.router_w) return;                         // nothing reads a peer's shared memory after the barrier above
+    if (!a.router_w) {
+        cluster.sync();                              // #2: nobody leaves while a peer may still read its partial sums
+        return;
+    }
 
     // ---- folded router: partial logits over this CTA's columns, summed over the cluster in CTA order ----
     __syncthreads();
     const int E = a.E, nwarps = blockDim.x >> 5;
-    float* s_rl = rdyn;
+    float* s_rl = dyn;
     for (int e0 = w; e0 < E; e0 += nwarps * 4) {
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -346,8 +356,8 @@ __global__ void __launch_bounds__(256, 1) mhc_cluster_kernel(const __grid_consta
             if (lane == 0 && e < E) s_rl[e] = v;
         }
     }
-    cluster.sync();                                  // partial logits published
-    float* lg = rdyn + E;                            // full logits of the row, CTA 0 only
+    cluster.sync();                                  // #2: partial logits published (and all reads of the partial sums done)
+    float* lg = dyn + E;                             // full logits of the row, CTA 0 only
     if (crank == 0) {
         for (int e = t; e < E; e += blockDim.x) {
             float v[kCMaxCluster];
@@ -360,7 +370,7 @@ __global__ void __launch_bounds__(256, 1) mhc_cluster_kernel(const __grid_consta
             if (a.logits) a.logits[(size_t)r * E + e] = acc;
         }
     }
-    cluster.sync();                                  // CTA 0 has read every peer's partial logits
+    cluster.sync();                                  // #3: CTA 0 has read every peer's partial logits
     if (crank != 0) return;
     router_topk_block<false>(lg, a.router_bias, a.ids_out + (size_t)r * (a.topk + a.n_shared), a.wts_out + (size_t)r * (a.topk + a.n_shared), E, a.topk,
                              a.n_group, a.topk_group, a.scoring, a.norm_topk, a.scale, a.n_shared, lg + E);
@@ -369,26 +379,23 @@ __global__ void __launch_bounds__(256, 1) mhc_cluster_kernel(const __grid_consta
 static int g_cluster_ok[64] = {0};      // per device: 0 unknown, 1 usable, -1 not usable
 
 // Cluster width (CTAs per row) and column groups per CTA for a hidden size, or 0 when this kernel does not cover it.
-static int mhc_cluster_shape(int hidden, int* groups) {
-    if (hidden % kCGroupCols) return 0;
-    const int units = hidden / kCGroupCols;             // column groups in a row
-    int cs = kCMaxCluster;
-    while (cs > 1 && (units % cs || units / cs > 2)) cs >>= 1;
-    if (units % cs || units / cs > 2) return 0;
-    while (cs > 1 && units / cs < 1) cs >>= 1;
-    *groups = units / cs;
-    return cs;
-}
-
-static size_t mhc_cluster_smem(int groups, int E_router) {
-    size_t b = (size_t)kCOut * kCMax * groups * kCGroupCols * 4;
-    if (E_router) b += (size_t)(2 * E_router + router_topk_smem_floats(E_router)) * 4;
-    return b;
+static int mhc_cluster_shape(int hidden, int* groups, int* vec) {
+    if (hidden % 32) return 0;
+    for (int v = 2; v >= 1; --v) {
+        const int unit = 32 * v;                    // columns of one column group
+        if (hidden % unit) continue;
+        int cs = kCMaxCluster;
+        while (cs > 1 && (hidden % (cs * unit) || hidden / (cs * unit) < 1)) cs >>= 1;
+        const int g = hidden / (cs * unit);
+        if (hidden % (cs * unit) == 0 && g >= 1 && g <= 4) { *groups = g; *vec = v; return cs; }
+    }
+    return 0;
 }
 
 }  // namespace lsb
 using namespace lsb;
 
+template <int VEC>
 static cudaError_t launch_mhc_cluster(const MhcClusterArgs& a, int rows, int csize, int groups, size_t smem, cudaStream_t st) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(csize, rows);
@@ -402,33 +409,33 @@ static cudaError_t launch_mhc_cluster(const MhcClusterArgs& a, int rows, int csi
     at[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at;
     cfg.numAttrs = pdl_enabled_flag() ? 2 : 1;
-    return cudaLaunchKernelEx(&cfg, mhc_cluster_kernel, a);
+    return cudaLaunchKernelEx(&cfg, mhc_cluster_kernel<VEC>, a);
 }
 
 // Cluster width this device would use for `hidden` (0: not covered - use lsb_mhc_post_pre).  The first call per device asks
 // the driver whether a cluster of that width can become resident (16 CTAs per cluster is beyond the portable limit of 8).
 LSB_API int lsb_mhc_cluster_width(int hidden, int n) {
-    int groups = 0;
-    const int cs = mhc_cluster_shape(hidden, &groups);
+    int groups = 0, vec = 0;
+    const int cs = mhc_cluster_shape(hidden, &groups, &vec);
     if (!cs || n > kCMax) return 0;
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
     if (g_cluster_ok[dev] == 0) {
         bool ok = true;
-        ok = ok && cudaFuncSetAttribute(mhc_cluster_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
-        ok = ok && cudaFuncSetAttribute(mhc_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) == cudaSuccess;
+        ok = ok && cudaFuncSetAttribute(mhc_cluster_kernel<1>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
+        ok = ok && cudaFuncSetAttribute(mhc_cluster_kernel<2>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
         if (ok) {
             cudaLaunchConfig_t cfg = {};
             cfg.gridDim = dim3(kCMaxCluster, 1);
-            cfg.blockDim = dim3(256);
-            cfg.dynamicSmemBytes = mhc_cluster_smem(2, 512);
+            cfg.blockDim = dim3(512);
+            cfg.dynamicSmemBytes = 16 * 1024;
             cudaLaunchAttribute at[1];
             at[0].id = cudaLaunchAttributeClusterDimension;
             at[0].val.clusterDim.x = kCMaxCluster; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
             cfg.attrs = at;
             cfg.numAttrs = 1;
             int nclusters = 0;
-            ok = cudaOccupancyMaxActiveClusters(&nclusters, mhc_cluster_kernel, &cfg) == cudaSuccess && nclusters >= 1;
+            ok = cudaOccupancyMaxActiveClusters(&nclusters, mhc_cluster_kernel<2>, &cfg) == cudaSuccess && nclusters >= 1;
         }
         cudaGetLastError();
         g_cluster_ok[dev] = ok ? 1 : -1;
@@ -445,12 +452,11 @@ LSB_API int lsb_mhc_cluster(void* out_x, void* residual, const void* x, void* po
                             const void* router_w, const void* router_bias, void* logits, void* ids_out, void* wts_out, int E, int topk,
                             int n_group, int topk_group, int scoring, int norm_topk, float scale, int n_shared, const void* comm,
                             void* stream) {
-    int groups = 0;
+    int groups = 0, vec = 0;
     const int cs = lsb_mhc_cluster_width(hidden, n);
-    if (!cs || !mhc_cluster_shape(hidden, &groups)) return -1;
+    if (!cs || !mhc_cluster_shape(hidden, &groups, &vec)) return -1;
     if (y && (S > kCMaxS || comm)) return -1;
-    if (router_w && (topk > 32 || n_group > 64 || E > 2048 || n_shared > 32)) return -1;
-    if ((((uintptr_t)fn | (uintptr_t)residual | (uintptr_t)x | (uintptr_t)y | (uintptr_t)norm_w | (uintptr_t)router_w) & 15) || ((uintptr_t)out_x & 7)) return -1;
+    if (router_w && (topk > 32 || n_group > 64 || E > 2048 || n_shared > 32 || (groups * 32 * vec) % 4)) return -1;
     MhcClusterArgs a;
     a.out = (bf16*)out_x; a.residual = (float*)residual; a.x = (const float*)x; a.post = (float*)post; a.comb = (float*)comb;
     a.fn = (const float*)fn; a.hc_scale = (const float*)hc_scale; a.hc_base = (const float*)hc_base; a.norm_w = (const float*)norm_w;
@@ -462,9 +468,10 @@ LSB_API int lsb_mhc_cluster(void* out_x, void* residual, const void* x, void* po
     a.n_shared = n_shared; a.scale = scale;
     a.comm.nranks = 0;
     if (comm) a.comm = *reinterpret_cast<const PeerComm*>(comm);
-    const size_t smem = mhc_cluster_smem(groups, router_w ? E : 0);
-    if (smem > 160 * 1024) return -1;
-    cudaError_t e = launch_mhc_cluster(a, rows, cs, groups, smem, (cudaStream_t)stream);
+    const size_t smem = router_w ? (size_t)(2 * E + router_topk_smem_floats(E)) * 4 : 0;
+    if (smem > 48 * 1024) return -1;
+    cudaError_t e = vec == 2 ? launch_mhc_cluster<2>(a, rows, cs, groups, smem, (cudaStream_t)stream)
+                             : launch_mhc_cluster<1>(a, rows, cs, groups, smem, (cudaStream_t)stream);
     if (e != cudaSuccess) return (int)e;
     LSB_CHECK_LAUNCH();
 }

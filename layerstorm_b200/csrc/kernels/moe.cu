@@ -21,45 +21,15 @@
 
 namespace lsb {
 
-// Optional second job of the router kernels: as soon as a row's experts are known, ask for their gate / up weights (and
-// scales) to be brought into L2, one kernel ahead of the expert GEMV that streams them.  arena == null: off.
-struct ExpertPf {
-    const uint8_t* arena;
-    const int* slot_of;
-    long long stride;
-    long long off0, len0;     // weights of the first expert GEMV
-    long long off1, len1;     // their scales (len1 == 0: none)
-};
-
-__device__ __forceinline__ void router_prefetch_experts(const ExpertPf& pf, const int* __restrict__ ids, int S) {
-    if (!pf.arena) return;
-    constexpr long long kPiece = 65536;
-    const int per0 = (int)((pf.len0 + kPiece - 1) / kPiece), per1 = (int)((pf.len1 + kPiece - 1) / kPiece);
-    const int per = per0 + per1;
-    for (int i = threadIdx.x; i < S * per; i += blockDim.x) {
-        const int s = i / per, j = i - s * per;
-        const int e = ids[s];
-        if (e < 0) continue;
-        const int slot = pf.slot_of[e];
-        if (slot < 0) continue;
-        const uint8_t* base = pf.arena + (size_t)slot * pf.stride;
-        const long long off = j < per0 ? pf.off0 + (long long)j * kPiece : pf.off1 + (long long)(j - per0) * kPiece;
-        const long long end = j < per0 ? pf.off0 + pf.len0 : pf.off1 + pf.len1;
-        const long long len = end - off < kPiece ? end - off : kPiece;
-        l2_prefetch_span(base + off, (uint32_t)(len & ~15ll));
-    }
-}
-
 // One block per row.
 __global__ void __launch_bounds__(1024) router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int* __restrict__ ids,
                                                            float* __restrict__ wts, int E, int topk, int n_group, int topk_group, int scoring,
-                                                           int norm_topk, float scale, int n_shared, int ld_logits, ExpertPf pf) {
+                                                           int norm_topk, float scale, int n_shared, int ld_logits) {
     extern __shared__ float sm[];
     pdl_wait();
     pdl_launch_dependents();
     router_topk_block<false>(logits + (size_t)blockIdx.x * ld_logits, bias, ids + (size_t)blockIdx.x * (topk + n_shared),
                              wts + (size_t)blockIdx.x * (topk + n_shared), E, topk, n_group, topk_group, scoring, norm_topk, scale, n_shared, sm);
-    router_prefetch_experts(pf, ids + (size_t)blockIdx.x * (topk + n_shared), topk + n_shared);
 }
 
 // Router projection and top-k in one launch for decode-sized steps (rows <= 8): one block per expert computes its fp32 logit
@@ -69,7 +39,7 @@ constexpr int kRouterMaxRows = 8;
 __global__ void __launch_bounds__(128) router_fused_kernel(const float* __restrict__ w, const bf16* __restrict__ x, float* __restrict__ logits,
                                                            const float* __restrict__ bias, int* __restrict__ ids, float* __restrict__ wts,
                                                            unsigned* __restrict__ done, int rows, int H, int E, int topk, int n_group,
-                                                           int topk_group, int scoring, int norm_topk, float scale, int n_shared, ExpertPf pf) {
+                                                           int topk_group, int scoring, int norm_topk, float scale, int n_shared) {
     extern __shared__ float sm[];                // last block: scratch of the top-k selection
     __shared__ int s_last;
     __shared__ float s_part[4][kRouterMaxRows];
@@ -116,11 +86,9 @@ __global__ void __launch_bounds__(128) router_fused_kernel(const float* __restri
     if (!s_last) return;
     if (threadIdx.x == 0) *done = 0;
     __threadfence();
-    for (int r = 0; r < rows; ++r) {
+    for (int r = 0; r < rows; ++r)
         router_topk_block<true>(logits + (size_t)r * E, bias, ids + (size_t)r * (topk + n_shared), wts + (size_t)r * (topk + n_shared), E, topk, n_group,
                                 topk_group, scoring, norm_topk, scale, n_shared, sm);
-        router_prefetch_experts(pf, ids + (size_t)r * (topk + n_shared), topk + n_shared);
-    }
 }
 
 // Hash-layer gating (DeepSeek-V4 hash layers): the experts of a row come from a table indexed by the row's token id
@@ -369,7 +337,7 @@ __global__ void __launch_bounds__(256) moe_gateup_fp4_kernel(const bf16* __restr
                                                              const int* __restrict__ slot_of, ExpertFmt ef,
                                                              const int* __restrict__ group_expert, const int* __restrict__ group_n,
                                                              const int* __restrict__ group_pairs, const int* __restrict__ n_groups,
-                                                             bf16* __restrict__ act, int S, float limit, int* __restrict__ miss_flag, int pf_down) {
+                                                             bf16* __restrict__ act, int S, float limit, int* __restrict__ miss_flag) {
     extern __shared__ __align__(16) uint8_t smraw[];
     __half* xs = reinterpret_cast<__half*>(smraw);
     __shared__ const bf16* rows[4];
@@ -387,15 +355,6 @@ __global__ void __launch_bounds__(256) moe_gateup_fp4_kernel(const bf16* __restr
     for (int i = 0; i < MT; ++i) pr[i] = group_pairs ? group_pairs[g * 4 + min(i, n - 1)] : g;
     if (threadIdx.x < MT) rows[threadIdx.x] = x + (size_t)(pr[threadIdx.x] / S) * ef.H;
     const uint8_t* base = arena + (size_t)slot * ef.stride;
-    if (pf_down && threadIdx.x < 2) {
-        // the down projection of this expert is the next kernel's stream: every block of the expert asks for its share now
-        const long long wb = ef.off_sg - ef.off_down < (long long)ef.H * (ef.F >> 1) ? ef.off_sg - ef.off_down : (long long)ef.H * (ef.F >> 1);
-        const long long sb = ef.off_tail - ef.off_sd;
-        const long long tot = threadIdx.x == 0 ? wb : sb, off = threadIdx.x == 0 ? ef.off_down : ef.off_sd;
-        const long long share = ((tot + gridDim.x - 1) / gridDim.x + 15) & ~15ll;
-        const long long o = (long long)blockIdx.x * share;
-        if (o < tot) l2_prefetch_span(base + off + o, (uint32_t)(((tot - o < share ? tot - o : share)) & ~15ll));
-    }
     const int tile = blockIdx.x >> 2, blk = blockIdx.x & 3;
     const int gtiles = ef.H >> 6;
     constexpr int kTS = 132;                               // 128 scale bytes per K-tile + 4 pad
@@ -548,48 +507,26 @@ __global__ void swiglu_kernel(bf16* __restrict__ out, const float* __restrict__ 
 }  // namespace lsb
 using namespace lsb;
 
-// Gate / up weights (+ scales) of the experts a decode-sized step is about to stream, as an L2 request descriptor for the
-// router kernels.  LSB_MOE_PF bit 0 switches it off (bit 1: the down-projection request made by the gate / up kernel).
-static int moe_pf_mode() {
-    static const int m = [] { const char* e = getenv("LSB_MOE_PF"); return e ? atoi(e) : 3; }();
-    return m;
-}
-static ExpertPf make_expert_pf(const void* arena, const void* slot_of, const void* fmt_struct, int rows) {
-    ExpertPf pf = {};
-    if (!arena || !slot_of || !fmt_struct || rows > 4 || !(moe_pf_mode() & 1)) return pf;
-    const ExpertFmt ef = *reinterpret_cast<const ExpertFmt*>(fmt_struct);
-    if (((uintptr_t)arena & 15) || (ef.stride & 15) || (ef.off_gate & 15) || (ef.off_sg & 15)) return pf;
-    pf.arena = (const uint8_t*)arena; pf.slot_of = (const int*)slot_of; pf.stride = ef.stride;
-    pf.off0 = ef.off_gate; pf.len0 = ef.off_down - ef.off_gate;               // gate | up are adjacent
-    pf.off1 = ef.off_sg; pf.len1 = ef.off_sd > ef.off_sg ? ef.off_sd - ef.off_sg : 0;
-    return pf;
-}
-
-// pf_arena / pf_slot_of / pf_fmt (optional, decode-sized steps): expert arena of the layer, so that the selected experts'
-// gate / up weights are requested into L2 as soon as they are known.
 LSB_API int lsb_router_topk(const void* logits, const void* bias, void* ids, void* wts, int rows, int E, int topk,
                             int n_group, int topk_group, int scoring, int norm_topk, float scale, int n_shared,
-                            int ld_logits, const void* pf_arena, const void* pf_slot_of, const void* pf_fmt, void* stream) {
+                            int ld_logits, void* stream) {
     if (topk > 32 || n_group > 64 || E > 4096 || n_shared > 32) return -1;
     int threads = (E + 31) / 32 * 32;
     threads = threads < 64 ? 64 : (threads > 1024 ? 1024 : threads);
     launch_pdl((router_topk_kernel), rows, threads, (size_t)router_topk_smem_floats(E) * 4, (cudaStream_t)stream, (const float*)logits, (const float*)bias,
-               (int*)ids, (float*)wts, E, topk, n_group, topk_group, scoring, norm_topk, scale, n_shared, ld_logits,
-               make_expert_pf(pf_arena, pf_slot_of, pf_fmt, rows));
+               (int*)ids, (float*)wts, E, topk, n_group, topk_group, scoring, norm_topk, scale, n_shared, ld_logits);
     LSB_CHECK_LAUNCH();
 }
 
 // Router projection + top-k in one launch (rows <= 8, H % 16 == 0).  w: fp32 [E, H]; x: bf16 [rows, H]; logits: fp32 scratch
 // [rows, E]; done: one zero-initialised counter.
 LSB_API int lsb_router_fused(const void* w, const void* x, void* logits, const void* bias, void* ids, void* wts, void* done, int rows, int H,
-                             int E, int topk, int n_group, int topk_group, int scoring, int norm_topk, float scale, int n_shared,
-                             const void* pf_arena, const void* pf_slot_of, const void* pf_fmt, void* stream) {
+                             int E, int topk, int n_group, int topk_group, int scoring, int norm_topk, float scale, int n_shared, void* stream) {
     if (rows > kRouterMaxRows || H % 16 || topk > 32 || n_group > 64 || E > 4096 || n_shared > 32) return -1;
     const size_t smem = (size_t)router_topk_smem_floats(E) * 4;
     if (smem > 48 * 1024) return -1;
     launch_pdl((router_fused_kernel), E, 128, smem, (cudaStream_t)stream, (const float*)w, (const bf16*)x, (float*)logits, (const float*)bias,
-               (int*)ids, (float*)wts, (unsigned*)done, rows, H, E, topk, n_group, topk_group, scoring, norm_topk, scale, n_shared,
-               make_expert_pf(pf_arena, pf_slot_of, pf_fmt, rows));
+               (int*)ids, (float*)wts, (unsigned*)done, rows, H, E, topk, n_group, topk_group, scoring, norm_topk, scale, n_shared);
     LSB_CHECK_LAUNCH();
 }
 
@@ -626,12 +563,11 @@ LSB_API int lsb_moe_gateup(const void* x, const void* arena, const void* slot_of
         }
         if (!group_n)
             launch_pdl((moe_gateup_fp4_kernel<1>), g2, 256, (size_t)ef.H * 2 + 2 * (ef.H / 64) * 132, st, (const bf16*)x, (const uint8_t*)arena, (const int*)slot_of, ef, (const int*)group_expert,
-                                                                        nullptr, nullptr, nullptr, (bf16*)act, S, limit, (int*)miss_flag,
-                                                                        (moe_pf_mode() & 2) && max_groups <= 40 && (ef.off_down & 15) == 0 && (ef.off_sd & 15) == 0 && (ef.stride & 15) == 0 ? 1 : 0);
+                                                                        nullptr, nullptr, nullptr, (bf16*)act, S, limit, (int*)miss_flag);
         else
             launch_pdl((moe_gateup_fp4_kernel<4>), g2, 256, (size_t)ef.H * 8 + 2 * (ef.H / 64) * 132, st, (const bf16*)x, (const uint8_t*)arena, (const int*)slot_of, ef, (const int*)group_expert,
                                                                         (const int*)group_n, (const int*)group_pairs, (const int*)n_groups, (bf16*)act, S, limit,
-                                                                        (int*)miss_flag, 0);
+                                                                        (int*)miss_flag);
         LSB_CHECK_LAUNCH();
     }
     if (!group_n) return -1;   // pair mode is only implemented for the NVFP4 fast path

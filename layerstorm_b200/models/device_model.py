@@ -826,18 +826,16 @@ class DeviceModel:
         arena: ExpertArena = L["arena"]
         S = ws.S
         sc = {"sigmoid": 0, "softmax": 1, "sqrtsoftplus": 2}[cfg.scoring]
-        # decode-sized steps over resident experts: the router kernel also requests the selected experts' gate / up weights into L2
-        pf = (arena.data, arena.slot_of, ctypes.addressof(arena.ef)) if (R <= 4 and self.streamer is None) else (None, None, None)
         if routed:
             pass        # the hyper-connection kernel in front of this layer already projected and selected (ws.ids / ws.wts)
         elif ROUTER_FUSED and R <= 8 and cfg.hidden % 16 == 0 and R * (2 * cfg.n_routed + 128) * 4 <= 48 * 1024:
             # decode-sized steps: projection and top-k in one launch (the last block selects)
             nat.call("lsb_router_fused", L["router"].w, ws.x, ws.logits_r, L["router_bias"], ws.ids, ws.wts, ws.router_done, R, cfg.hidden,
-                     cfg.n_routed, cfg.top_k, cfg.n_group, cfg.topk_group, sc, int(cfg.norm_topk_prob), cfg.routed_scale, cfg.n_shared, *pf)
+                     cfg.n_routed, cfg.top_k, cfg.n_group, cfg.topk_group, sc, int(cfg.norm_topk_prob), cfg.routed_scale, cfg.n_shared)
         else:
             L["router"](ws.logits_r, ws.x, R)
             nat.call("lsb_router_topk", ws.logits_r, L["router_bias"], ws.ids, ws.wts, R, cfg.n_routed, cfg.top_k, cfg.n_group,
-                     cfg.topk_group, sc, int(cfg.norm_topk_prob), cfg.routed_scale, cfg.n_shared, cfg.n_routed, *pf)
+                     cfg.topk_group, sc, int(cfg.norm_topk_prob), cfg.routed_scale, cfg.n_shared, cfg.n_routed)
         if self.streamer is not None:
             # capped expert cache: experts are brought in from pinned host memory in waves; every wave runs the
             # expert kernels over what is resident, the combine runs once at the end over all slots

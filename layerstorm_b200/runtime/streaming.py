@@ -205,7 +205,7 @@ class ExpertStreamer:
         L["router"](lg, ws.x, R)
         sc = {"sigmoid": 0, "softmax": 1, "sqrtsoftplus": 2}[cfg.scoring]
         nat.call("lsb_router_topk", lg, L["router_bias"], ids, wts, R, cfg.n_routed, cfg.top_k, cfg.n_group, cfg.topk_group, sc,
-                 int(cfg.norm_topk_prob), cfg.routed_scale, cfg.n_shared, cfg.n_routed, None, None, None)
+                 int(cfg.norm_topk_prob), cfg.routed_scale, cfg.n_shared, cfg.n_routed)
         flat = ids[:R].reshape(-1).cpu().tolist()
         seen, out = set(), []
         for e in flat:

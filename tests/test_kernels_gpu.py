@@ -160,7 +160,7 @@ def test_mhc_cluster_kernel_with_folded_combine_and_router(H, E, k, R):
     lg_ref = x.float().cpu() @ rw.cpu().T                      # the router consumes the bf16-rounded activations
     close(logits, lg_ref, 1e-4, 1e-4, "router logits")
     ids2 = torch.zeros_like(ids); wts2 = torch.zeros_like(wts)
-    nat.call("lsb_router_topk", logits, rb, ids2, wts2, R, E, k, 1, 1, 0, 1, 2.5, 1, E, None, None, None)
+    nat.call("lsb_router_topk", logits, rb, ids2, wts2, R, E, k, 1, 1, 0, 1, 2.5, 1, E)
     torch.cuda.synchronize()
     assert torch.equal(ids, ids2) and torch.equal(wts, wts2), "folded router differs from the stand-alone top-k on the same logits"
     rid, rwt = ref.route(dataclasses.replace(cfg, routed_scale=2.5), logits.cpu(), rb.cpu())
@@ -188,7 +188,7 @@ def test_router_topk(scoring, n_group, topk_group):
     ids = torch.zeros(R, k + 1, dtype=torch.int32, device=DEV)
     wts = torch.zeros(R, k + 1, device=DEV)
     nat.call("lsb_router_topk", logits, bias, ids, wts, R, E, k, n_group, topk_group,
-             {"sigmoid": 0, "softmax": 1, "sqrtsoftplus": 2}[scoring], 1, 2.5, 1, E, None, None, None)
+             {"sigmoid": 0, "softmax": 1, "sqrtsoftplus": 2}[scoring], 1, 2.5, 1, E)
     torch.cuda.synchronize()
     rid, rw = ref.route(cfg, logits.cpu(), bias.cpu())
     assert torch.equal(ids[:, :k].cpu().long(), rid), (ids.cpu(), rid)
@@ -197,11 +197,9 @@ def test_router_topk(scoring, n_group, topk_group):
 
 
 @pytest.mark.parametrize("E,k,n_group,topk_group,R", [(288, 8, 1, 1, 1), (256, 8, 8, 4, 3), (48, 6, 1, 1, 8)])
-def test_router_fused_projection_topk_and_expert_prefetch(E, k, n_group, topk_group, R):
-    """Router projection + rank-based top-k in one launch (with the L2 request for the selected experts' weights armed) against
-    the fp32 reference routing; the two-launch form must give the same bits on the same logits."""
-    from layerstorm_b200.models.device_model import ExpertArena, expert_layout
-    import ctypes
+def test_router_fused_projection_and_topk(E, k, n_group, topk_group, R):
+    """Router projection + rank-based top-k in one launch against the fp32 reference routing; the two-launch form must give the
+    same bits on the same logits."""
     H = 512
     cfg = ModelConfig(n_routed=E, top_k=k, scoring="sigmoid", n_group=n_group, topk_group=topk_group, routed_scale=2.5)
     w = rnd(E, H, s=0.1, seed=3)
@@ -210,11 +208,7 @@ def test_router_fused_projection_topk_and_expert_prefetch(E, k, n_group, topk_gr
     ids = torch.zeros(R, k + 1, dtype=torch.int32, device=DEV); wts = torch.zeros(R, k + 1, device=DEV)
     logits = torch.zeros(R, E, device=DEV)
     done = torch.zeros(1, dtype=torch.int32, device=DEV)
-    arena = ExpertArena(expert_layout("nvfp4", H, 256), E + 1, E + 1, DEV)
-    arena.slot_of.copy_(torch.arange(E + 1, dtype=torch.int32))
-    arena.slot_of[5] = -1                                     # a non-resident expert is skipped by the request
-    pf = (arena.data, arena.slot_of, ctypes.addressof(arena.ef))
-    nat.call("lsb_router_fused", w, x, logits, bias, ids, wts, done, R, H, E, k, n_group, topk_group, 0, 1, 2.5, 1, *pf)
+    nat.call("lsb_router_fused", w, x, logits, bias, ids, wts, done, R, H, E, k, n_group, topk_group, 0, 1, 2.5, 1)
     torch.cuda.synchronize()
     close(logits, x.float().cpu() @ w.cpu().T, 1e-4, 1e-4, "router logits")
     rid, rw = ref.route(cfg, logits.cpu(), bias.cpu())
@@ -222,7 +216,7 @@ def test_router_fused_projection_topk_and_expert_prefetch(E, k, n_group, topk_gr
     close(wts[:, :k], rw, 1e-4, 1e-6, "router weights")
     assert (ids[:, k] == E).all() and (wts[:, k] == 1).all() and int(done[0]) == 0
     ids2 = torch.zeros_like(ids); wts2 = torch.zeros_like(wts)
-    nat.call("lsb_router_topk", logits, bias, ids2, wts2, R, E, k, n_group, topk_group, 0, 1, 2.5, 1, E, *pf)
+    nat.call("lsb_router_topk", logits, bias, ids2, wts2, R, E, k, n_group, topk_group, 0, 1, 2.5, 1, E)
     torch.cuda.synchronize()
     assert torch.equal(ids, ids2) and torch.equal(wts, wts2)
 

@@ -48,7 +48,9 @@ __global__ void mla_prep_kernel(const float* __restrict__ proj, int ldp, int off
     const float* pr = proj + (size_t)r * ldp;
     pdl_wait();
     pdl_launch_dependents();
-    if (q_lora > 0) {
+    // two blocks per row (gridDim.y == 2): block y = 0 normalises the query latent, block y = 1 does the KV row - the two chains of
+    // dependent reductions and memory round trips run side by side instead of back to back
+    if (q_lora > 0 && (gridDim.y == 1 || blockIdx.y == 0)) {
         float ss = 0.f;
         for (int i = t; i < q_lora; i += blockDim.x) { const float v = pr[off_qa + i]; sm[i] = v; ss += v * v; }
         ss = block_sum(ss, red);
@@ -56,6 +58,7 @@ __global__ void mla_prep_kernel(const float* __restrict__ proj, int ldp, int off
         for (int i = t; i < q_lora; i += blockDim.x) q_c[(size_t)r * q_lora + i] = __float2bfloat16(sm[i] * inv * qa_norm_w[i]);
         __syncthreads();
     }
+    if (gridDim.y == 2 && blockIdx.y == 0) return;
     float ss = 0.f;
     for (int i = t; i < dl; i += blockDim.x) { const float v = pr[off_kv + i]; sm[i] = v; ss += v * v; }
     ss = block_sum(ss, red);
@@ -732,7 +735,9 @@ static int mla_mma_shared_smem_bytes(int dl, int dr, int ng) {
 }
 
 // Merge split partials in split order: out = sum_s exp(m_s - M) acc_s / sum_s exp(m_s - M) l_s.  NS <= 32.
-__global__ void __launch_bounds__(128) mla_combine_kernel(bf16* __restrict__ out, float* __restrict__ lse, const float* __restrict__ o_part,
+// One thread per latent column with all NS partials of the column requested before the first is used (a dependent
+// batch per 8 splits made this kernel a chain of L2 round trips).
+__global__ void __launch_bounds__(512) mla_combine_kernel(bf16* __restrict__ out, float* __restrict__ lse, const float* __restrict__ o_part,
                                                           const float* __restrict__ ml_part, int H, int NS, int dl) {
     __shared__ float w[32];
     __shared__ float s_invL, s_lse;
@@ -740,6 +745,11 @@ __global__ void __launch_bounds__(128) mla_combine_kernel(bf16* __restrict__ out
     pdl_wait();
     pdl_launch_dependents();
     const float* ml = ml_part + ((size_t)r * H + h) * NS * 2;
+    const float* op = o_part + ((size_t)r * H + h) * NS * dl;
+    float v[32];
+    const bool col = t < dl;
+#pragma unroll
+    for (int s = 0; s < 32; ++s) v[s] = (col && s < NS) ? op[(size_t)s * dl + t] : 0.f;
     if (t < 32) {
         const float m = t < NS ? ml[2 * t] : -INFINITY;
         const float l = t < NS ? ml[2 * t + 1] : 0.f;
@@ -756,20 +766,18 @@ __global__ void __launch_bounds__(128) mla_combine_kernel(bf16* __restrict__ out
     }
     __syncthreads();
     const float invL = s_invL;
-    const float* op = o_part + ((size_t)r * H + h) * NS * dl;
-    for (int d = t; d < dl; d += blockDim.x) {
+    if (col) {
         float a = 0.f;
-        for (int s0 = 0; s0 < NS; s0 += 8) {
-            float v[8];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) v[u] = (s0 + u < NS) ? op[(size_t)(s0 + u) * dl + d] : 0.f;
-#pragma unroll
-            for (int u = 0; u < 8; ++u) a = fmaf(w[(s0 + u) & 31], v[u], a);
-        }
+        for (int s = 0; s < 32; ++s) a = fmaf(w[s], v[s], a);      // w[s] = 0 beyond NS
+        out[((size_t)r * H + h) * dl + t] = __float2bfloat16(a * invL);
+    }
+    for (int d = blockDim.x + t; d < dl; d += blockDim.x) {        // latent widths beyond the block size
+        float a = 0.f;
+        for (int s = 0; s < NS; ++s) a = fmaf(w[s], op[(size_t)s * dl + d], a);
         out[((size_t)r * H + h) * dl + d] = __float2bfloat16(a * invL);
     }
     if (lse && t == 0) lse[(size_t)r * H + h] = s_lse;
-    pdl_launch_dependents();
 }
 
 }  // namespace lsb
@@ -787,7 +795,7 @@ LSB_API int lsb_mla_prep(const void* proj, int ldp, int off_qa, int q_lora, int 
                          void* stream) {
     if (kv_fmt == 2 && (!tq_rot_t || !tq_centroids || dl % 32)) return -1;
     const int n = q_lora > dl + dr ? q_lora : dl + dr;
-    launch_pdl((mla_prep_kernel), rows, 256, (size_t)n * 4, (cudaStream_t)stream, (const float*)proj, ldp, off_qa, q_lora, off_kv, dl, dr,
+    launch_pdl((mla_prep_kernel), dim3(rows, q_lora > 0 && rows <= 64 ? 2 : 1), 256, (size_t)n * 4, (cudaStream_t)stream, (const float*)proj, ldp, off_qa, q_lora, off_kv, dl, dr,
                                                                       (const float*)qa_norm_w, (const float*)kv_norm_w,
                                                                       (const float*)inv_freq, (bf16*)q_c, (uint8_t*)cache,
                                                                       (const int*)block_table, max_pages, (const int*)row_seq,
@@ -869,7 +877,7 @@ LSB_API int lsb_mla_decode(const void* q, const void* cache, const void* block_t
         launch_pdl((mla_decode_kernel), dim3(R, (H + kHG - 1) / kHG, NS), 256, smem, st, p);
     }
     // out == null: the caller merges the partials itself (context-parallel attention combines them across ranks)
-    if (out) launch_pdl((mla_combine_kernel), dim3(R, H), 128, 0, st, (bf16*)out, (float*)lse, (const float*)o_part, (const float*)ml_part, H, NS, dl);
+    if (out) launch_pdl((mla_combine_kernel), dim3(R, H), dl >= 512 ? 512 : (dl >= 256 ? 256 : 128), 0, st, (bf16*)out, (float*)lse, (const float*)o_part, (const float*)ml_part, H, NS, dl);
     LSB_CHECK_LAUNCH();
 }
 

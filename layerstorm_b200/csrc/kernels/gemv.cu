@@ -4,7 +4,9 @@
 // Replaces the reference's CUDA-core GEMV family (src/compute/kernels/sm120/gemm/bf16_gemm.cu:41-156,
 // wq_gemm.cu:84-158) with one templated kernel over four weight formats.
 #include <cstdlib>
+#include <type_traits>
 #include "gemv_core.cuh"
+#include "tc_common.cuh"
 #include "comm.cuh"
 
 namespace lsb {
@@ -110,6 +112,129 @@ __global__ void __launch_bounds__(256) gemv_kernel(Mat mat, const bf16* __restri
     if (comm.nranks) comm_finish_local(comm, next_epoch, gridDim.x, reinterpret_cast<const float*>(out), MT, N, ldo);
 }
 
+// A bf16 weight-row slice that a bulk copy has placed in shared memory; `w + k` addresses column k of the row.
+struct WRowBf16S {
+    static constexpr int EPL = 8;
+    const bf16* w;
+    __device__ __forceinline__ void load(int k, float* f) const {
+        const uint4 v = tc::ld_shared_16((uint32_t)__cvta_generic_to_shared(w + k));
+        unpack_bf16x8(v, f);
+    }
+};
+
+static __device__ int g_gemv_err = 0;      // first bulk-copy wait that ran out (0 = none); read through lsb_gemv_error
+
+// bf16 weights, same work split as gemv_kernel, but every warp asks the copy engine for its two row slices (<= 4 KB each) with
+// one bulk copy per row BEFORE the dependency wait and computes out of shared memory.  Blocks that become resident under the
+// predecessor's tail therefore hold their weights on chip when the activations arrive, and a resident block keeps
+// 8 x 8 KB of the stream in flight without spending registers on it.
+template <int MT, bool OUT_BF16, int KS>
+__global__ void __launch_bounds__(256) gemv_bf16_bulk_kernel(MatBf16 mat, const bf16* __restrict__ x, int ldx, void* __restrict__ out,
+                                                             int ldo, int N, int K, int kper, float alpha, const float* __restrict__ bias,
+                                                             PeerComm comm) {
+    __shared__ float red[8][2 * MT];
+    __shared__ __align__(8) uint64_t bars[8];
+    extern __shared__ __align__(128) uint8_t slices[];       // [8 warps][2 rows][kper] bf16
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int PAIRS = 8 / KS;
+    const int pair = warp / KS, ks = warp % KS;
+    int n0 = (blockIdx.x * PAIRS + pair) * 2;
+    const bool active = n0 < N;
+    if (!active) n0 = 0;
+    const int n1 = min(n0 + 1, N - 1);
+    const int k0 = ks * kper, k1 = min(K, k0 + kper);
+    const bool work = active && k0 < k1;
+    bf16* s0 = reinterpret_cast<bf16*>(slices) + (size_t)warp * 2 * kper;
+    bf16* s1 = s0 + kper;
+    if (work && lane == 0) {
+        const uint32_t bytes = (uint32_t)(k1 - k0) * 2u;
+        tc::mbar_init(&bars[warp], 1);
+        tc::fence_barrier_init();
+        tc::mbar_expect_tx(&bars[warp], 2u * bytes);
+        tc::bulk_load_1d(s0, mat.w + (size_t)n0 * mat.ldw + k0, bytes, &bars[warp]);
+        tc::bulk_load_1d(s1, mat.w + (size_t)n1 * mat.ldw + k0, bytes, &bars[warp]);
+    }
+    __syncwarp();
+    pdl_wait();
+    pdl_launch_dependents();
+    unsigned next_epoch = 0;
+    if (comm.nranks) next_epoch = *comm.epoch + 1;
+    float acc0[MT], acc1[MT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) acc0[m] = acc1[m] = 0.f;
+    if (work) {
+        // the copies always complete (static, valid weights); the bounded wait only guards against a protocol error
+        if (!tc::mbar_wait(&bars[warp], 0, &g_gemv_err, 1)) tc::mbar_wait(&bars[warp], 0, &g_gemv_err, 2);
+        constexpr int UNR = MT == 1 ? 4 : 2;
+        warp_dot2<WRowBf16S, MT, UNR>(WRowBf16S{s0 - k0}, WRowBf16S{s1 - k0}, x, ldx, K, acc0, acc1, lane, 32, k0, k1);
+    }
+    float va[MT], vb[MT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) { va[m] = warp_sum(acc0[m]); vb[m] = warp_sum(acc1[m]); }
+    if (KS > 1) {
+        if (lane == 0) {
+#pragma unroll
+            for (int m = 0; m < MT; ++m) { red[warp][2 * m] = va[m]; red[warp][2 * m + 1] = vb[m]; }
+        }
+        __syncthreads();
+        if (ks == 0 && lane == 0) {
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
+                float a = 0.f, b2 = 0.f;
+#pragma unroll
+                for (int j = 0; j < KS; ++j) { a += red[pair * KS + j][2 * m]; b2 += red[pair * KS + j][2 * m + 1]; }
+                va[m] = a; vb[m] = b2;
+            }
+        }
+    }
+    if (lane == 0 && ks == 0 && active) {
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            float a = va[m] * alpha, b2 = vb[m] * alpha;
+            if (bias) { a += bias[n0]; b2 += bias[n1]; }
+            if (OUT_BF16 && !comm.nranks) {
+                bf16* o = reinterpret_cast<bf16*>(out) + (size_t)m * ldo;
+                o[n0] = __float2bfloat16(a);
+                if (n0 + 1 < N) o[n0 + 1] = __float2bfloat16(b2);
+            } else {
+                float* o = reinterpret_cast<float*>(out) + (size_t)m * ldo;
+                o[n0] = a;
+                if (n0 + 1 < N) o[n0 + 1] = b2;
+            }
+        }
+    }
+    if (comm.nranks) comm_finish_local(comm, next_epoch, gridDim.x, reinterpret_cast<const float*>(out), MT, N, ldo);
+}
+
+template <int MT, bool OB, int KS>
+static void launch_bulk_one(MatBf16 mat, const bf16* xp, int ldx, void* op, int ldo, int N, int K, int kper, float alpha, const float* bias,
+                            PeerComm comm, cudaStream_t st) {
+    const int rows_per_block = (8 / KS) * 2;
+    static bool once = false;
+    if (!once) {
+        cudaFuncSetAttribute(gemv_bf16_bulk_kernel<MT, OB, KS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+        cudaFuncSetAttribute(gemv_bf16_bulk_kernel<MT, OB, KS>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+        once = true;
+    }
+    launch_pdl((gemv_bf16_bulk_kernel<MT, OB, KS>), (N + rows_per_block - 1) / rows_per_block, 256, (size_t)16 * kper * 2, st, mat, xp, ldx, op, ldo,
+               N, K, kper, alpha, bias, comm);
+}
+
+template <int MT, bool OB>
+static void launch_bulk_ks(int ks, MatBf16 mat, const bf16* xp, int ldx, void* op, int ldo, int N, int K, int kper, float alpha, const float* bias,
+                           PeerComm comm, cudaStream_t st) {
+    if (ks == 1) launch_bulk_one<MT, OB, 1>(mat, xp, ldx, op, ldo, N, K, kper, alpha, bias, comm, st);
+    else if (ks == 2) launch_bulk_one<MT, OB, 2>(mat, xp, ldx, op, ldo, N, K, kper, alpha, bias, comm, st);
+    else if (ks == 4) launch_bulk_one<MT, OB, 4>(mat, xp, ldx, op, ldo, N, K, kper, alpha, bias, comm, st);
+    else launch_bulk_one<MT, OB, 8>(mat, xp, ldx, op, ldo, N, K, kper, alpha, bias, comm, st);
+}
+
+// LSB_GEMV_BULK=0: bf16 GEMVs keep the register-streaming kernel
+static bool gemv_bulk_enabled() {
+    static const bool b = [] { const char* e = getenv("LSB_GEMV_BULK"); return e ? atoi(e) != 0 : true; }();
+    return b;
+}
+
 template <class Mat, int MT, bool OB, int KS>
 static void launch_one(Mat mat, const bf16* xp, int ldx, void* op, int ldo, int N, int K, float alpha, const float* bias, PeerComm comm,
                        cudaStream_t st) {
@@ -153,13 +278,31 @@ static int launch_gemv(Mat mat, const bf16* x, int ldx, void* out, int ldo, int 
         if ((M != 1 && M != 2 && M != 4) || out_bf16) return -1;   // the fused epilogue covers one single-pass launch of fp32 rows
     }
     const size_t osz = out_bf16 ? 2 : 4;
-    const int ks = choose_ks(N, K, decltype(mat.row(0))::EPL);
+    int ks = choose_ks(N, K, decltype(mat.row(0))::EPL);
+    int bulk_kper = 0;
+    if constexpr (std::is_same<Mat, MatBf16>::value) {
+        // bulk-copy variant: a warp's row slice must fit 4 KB of shared memory; split K further when it does not
+        if (gemv_bulk_enabled() && K % 8 == 0 && mat.ldw % 8 == 0 && (reinterpret_cast<uintptr_t>(mat.w) & 15) == 0) {
+            int kb = ks;
+            while (kb < 8 && (K + kb - 1) / kb > 2048) kb *= 2;
+            const int kper = ((K + kb - 1) / kb + 255) / 256 * 256;
+            if (kper <= 2048) { ks = kb; bulk_kper = kper; }
+        }
+    }
     for (int m0 = 0; m0 < M;) {
         const int rem = M - m0;
         const int mt = rem >= 4 ? 4 : (rem >= 2 ? 2 : 1);
         const bf16* xp = x + (size_t)m0 * ldx;
         void* op = reinterpret_cast<char*>(out) + (size_t)m0 * ldo * osz;
 #define LSB_GEMV_CASE(MT_)                                                                              \
+    if constexpr (std::is_same<Mat, MatBf16>::value) {                                                  \
+        if (bulk_kper) {                                                                                \
+            if (out_bf16) launch_bulk_ks<MT_, true>(ks, mat, xp, ldx, op, ldo, N, K, bulk_kper, alpha, bias, comm, st);  \
+            else launch_bulk_ks<MT_, false>(ks, mat, xp, ldx, op, ldo, N, K, bulk_kper, alpha, bias, comm, st);          \
+            m0 += mt;                                                                                   \
+            continue;                                                                                   \
+        }                                                                                               \
+    }                                                                                                   \
     if (out_bf16) launch_ks<Mat, MT_, true>(ks, mat, xp, ldx, op, ldo, N, K, alpha, bias, comm, st);  \
     else launch_ks<Mat, MT_, false>(ks, mat, xp, ldx, op, ldo, N, K, alpha, bias, comm, st);
         if (mt == 4) { LSB_GEMV_CASE(4) } else if (mt == 2) { LSB_GEMV_CASE(2) } else { LSB_GEMV_CASE(1) }
@@ -172,6 +315,13 @@ static int launch_gemv(Mat mat, const bf16* x, int ldx, void* out, int ldo, int 
 }  // namespace lsb
 
 using namespace lsb;
+
+// First bulk-copy wait of the bf16 GEMV that gave up since the library was loaded on the current device (0 = none).
+LSB_API int lsb_gemv_error() {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_gemv_err, sizeof(v)) != cudaSuccess) return -1;
+    return v;
+}
 
 // x: bf16 [M, ldx]; W: bf16 [N, ldw]; out fp32 or bf16 [M, ldo]. K % 8 == 0, 16-byte aligned rows.
 // comm: host pointer to a PeerComm (fused all-reduce push of the fp32 output) or null.

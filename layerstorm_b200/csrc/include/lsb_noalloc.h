@@ -15,7 +15,9 @@ extern "C" {
 // fixed 128 KiB array inside the library instead of a caller-provided buffer.
 //
 //  * rows must not exceed lsb_argmax_noalloc_max_rows() (256); more rows return -2 and nothing
-//    is launched.  -1 = bad argument, > 0 = a CUDA error code, 0 = launched.
+//    is launched.  -1 = bad argument (null pointer, rows or V <= 0, ld < V), -3 = the current device
+//    index is beyond the 64 devices this entry point keeps an address for, > 0 = a CUDA error
+//    code, 0 = launched.
 //  * The first call on each device looks up the array's device address (with that device
 //    current).  Make that first call before any CUDA stream capture begins.
 //  * All calls on a device share the one array.  Two calls whose kernels can overlap on the GPU

@@ -212,11 +212,17 @@ static void launch_bulk_one(MatBf16 mat, const bf16* xp, int ldx, void* op, int 
     const int rows_per_block = (8 / KS) * 2;
     static bool once = false;
     if (!once) {
-        cudaFuncSetAttribute(gemv_bf16_bulk_kernel<MT, OB, KS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+        cudaFuncSetAttribute(gemv_bf16_bulk_kernel<MT, OB, KS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);
         cudaFuncSetAttribute(gemv_bf16_bulk_kernel<MT, OB, KS>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
         once = true;
     }
-    launch_pdl((gemv_bf16_bulk_kernel<MT, OB, KS>), (N + rows_per_block - 1) / rows_per_block, 256, (size_t)16 * kper * 2, st, mat, xp, ldx, op, ldo,
+    // LSB_GEMV_BULK_PAD_KB: extra shared memory requested by the 64 KB variant, to keep it two blocks deep per SM so that a
+    // follower which stages ~70 KB itself can become resident under this kernel's tail.  Default 0: measured on the
+    // GLM-5.3-Flash decode step, two blocks per SM cost the GEMVs more (130 us per step) than the KDA step gained.
+    static const int pad_kb = [] { const char* e = getenv("LSB_GEMV_BULK_PAD_KB"); return e ? atoi(e) : 0; }();
+    size_t smem = (size_t)16 * kper * 2;
+    if (smem >= 64 * 1024) smem += (size_t)pad_kb * 1024;
+    launch_pdl((gemv_bf16_bulk_kernel<MT, OB, KS>), (N + rows_per_block - 1) / rows_per_block, 256, smem, st, mat, xp, ldx, op, ldo,
                N, K, kper, alpha, bias, comm);
 }
 

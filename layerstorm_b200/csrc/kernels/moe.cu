@@ -337,8 +337,7 @@ __global__ void __launch_bounds__(256) moe_gateup_fp4_kernel(const bf16* __restr
                                                              const int* __restrict__ slot_of, ExpertFmt ef,
                                                              const int* __restrict__ group_expert, const int* __restrict__ group_n,
                                                              const int* __restrict__ group_pairs, const int* __restrict__ n_groups,
-                                                             bf16* __restrict__ act, int S, float limit, int* __restrict__ miss_flag,
-                                                             __half* __restrict__ act_h) {
+                                                             bf16* __restrict__ act, int S, float limit, int* __restrict__ miss_flag) {
     extern __shared__ __align__(16) uint8_t smraw[];
     __half* xs = reinterpret_cast<__half*>(smraw);
     __shared__ const bf16* rows[4];
@@ -383,98 +382,11 @@ __global__ void __launch_bounds__(256) moe_gateup_fp4_kernel(const bf16* __restr
             if (m < n) {
                 float gv = warp_sum(ag[m]) * sg, uv = warp_sum(au[m]) * su;
                 if (limit > 0.f) { gv = fminf(gv, limit); uv = fminf(fmaxf(uv, -limit), limit); }
-                if (lane == 0) {
-                    const float av = siluf_(gv) * uv;
-                    act[(size_t)pr[m] * ef.F + f] = __float2bfloat16(av);
-                    if (act_h) act_h[(size_t)pr[m] * ef.F + f] = __float2half(av);      // input of the fused down + combine kernel
-                }
+                if (lane == 0) act[(size_t)pr[m] * ef.F + f] = __float2bfloat16(siluf_(gv) * uv);
             }
         }
     }
     pdl_launch_dependents();
-}
-
-// One 32-element chunk of an NVFP4 row (16 bytes, two scale groups) against 32 consecutive fp16 activations read from global memory.
-__device__ __forceinline__ float nvfp4_chunk_dot_g(const uint4& v, uint32_t s2, const __half* __restrict__ x) {
-    __half2 w[16];
-    fp4x8_to_half2x4(v.x, w); fp4x8_to_half2x4(v.y, w + 4); fp4x8_to_half2x4(v.z, w + 8); fp4x8_to_half2x4(v.w, w + 12);
-    __half2 a0 = __float2half2_rn(0.f), a1 = a0;
-#pragma unroll
-    for (int part = 0; part < 4; ++part) {
-        const uint4 xv = __ldg(reinterpret_cast<const uint4*>(x + part * 8));
-        const __half2* x2 = reinterpret_cast<const __half2*>(&xv);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            if (part < 2) a0 = __hfma2(w[part * 4 + i], x2[i], a0);
-            else a1 = __hfma2(w[part * 4 + i], x2[i], a1);
-        }
-    }
-    const float2 f0 = __half22float2(a0), f1 = __half22float2(a1);
-    return fmaf(fp8e4m3_to_float((uint8_t)(s2 & 0xff)), f0.x + f0.y, fp8e4m3_to_float((uint8_t)(s2 >> 8)) * (f1.x + f1.y));
-}
-
-// Down projection of ALL routing slots of a row and their weighted sum in one kernel (decode-sized steps, NVFP4 experts):
-//   out[r][h] = sum over slots s in slot order of  wts[r][s] * (act[r*S+s] . Wdown_{e(r,s)}[h])
-// A warp owns one output column h and holds that row of every selected expert's down matrix in registers (S x F/2 bytes).
-// The expert ids were written by the selection kernel two launches back and are final when this kernel can start, so the
-// weight and scale loads are issued BEFORE the dependency wait: while the gate / up kernel still runs, the resident warps of
-// this kernel already have their part of the down matrices on their way, and only the activations are read after the wait.
-// Slots of experts that are not resident on this GPU (slot_of < 0: expert-parallel peers, capped caches) contribute nothing.
-// SMAX: slots per row covered (registers); CH: 32-element chunks per lane (F <= 1024 CH).
-template <int SMAX, int CH>
-__global__ void __launch_bounds__(128) moe_down_combine_fp4_kernel(const __half* __restrict__ act_h, const uint8_t* __restrict__ arena,
-                                                                   const int* __restrict__ slot_of, ExpertFmt ef, const int* __restrict__ ids,
-                                                                   const float* __restrict__ wts, float* __restrict__ out, int S, PeerComm comm) {
-    const int r = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int h = (blockIdx.x >> 5) * 128 + warp * 32 + (blockIdx.x & 31);
-    const int nchunks = ef.F >> 5, gtiles = ef.F >> 6;
-    const size_t sf_row = (size_t)(h >> 7) * gtiles * 512 + (h & 31) * 16 + ((h & 127) >> 5) * 4;
-    uint4 wv[SMAX][CH];
-    uint32_t sc[SMAX][CH];
-    float coef[SMAX];
-#pragma unroll
-    for (int s = 0; s < SMAX; ++s) {
-        const int e = s < S ? ids[r * S + s] : -1;
-        const int slot = e >= 0 ? slot_of[e] : -1;
-        coef[s] = 0.f;
-#pragma unroll
-        for (int i = 0; i < CH; ++i) { wv[s][i] = make_uint4(0u, 0u, 0u, 0u); sc[s][i] = 0u; }
-        if (slot >= 0) {
-            const uint8_t* base = arena + (size_t)slot * ef.stride;
-            const uint8_t* row = base + ef.off_down + (size_t)h * (ef.F >> 1);
-            const uint8_t* sf = base + ef.off_sd + sf_row;
-#pragma unroll
-            for (int i = 0; i < CH; ++i) {
-                const int c = lane + 32 * i;
-                if (c < nchunks) {
-                    wv[s][i] = ldg_stream(row + c * 16);
-                    sc[s][i] = __ldg(reinterpret_cast<const uint16_t*>(sf + (size_t)(c >> 1) * 512 + (c & 1) * 2));
-                }
-            }
-            coef[s] = wts[r * S + s] * reinterpret_cast<const float*>(base + ef.off_tail)[2];
-        }
-    }
-    pdl_wait();
-    pdl_launch_dependents();
-    unsigned next_epoch = 0;
-    if (comm.nranks) next_epoch = *comm.epoch + 1;
-    float tot = 0.f;
-#pragma unroll
-    for (int s = 0; s < SMAX; ++s) {
-        if (coef[s] != 0.f) {                       // warp-uniform
-            const __half* xr = act_h + (size_t)(r * S + s) * ef.F;
-            float a = 0.f;
-#pragma unroll
-            for (int i = 0; i < CH; ++i) {
-                const int c = lane + 32 * i;
-                if (c < nchunks) a += nvfp4_chunk_dot_g(wv[s][i], sc[s][i], xr + c * 32);
-            }
-            tot = fmaf(coef[s], a, tot);
-        }
-    }
-    tot = warp_sum(tot);
-    if (lane == 0) out[(size_t)r * ef.H + h] = tot;
-    if (comm.nranks) comm_finish_local(comm, next_epoch, gridDim.x * gridDim.y, out, gridDim.y, ef.H, ef.H);
 }
 
 template <int MT>
@@ -638,7 +550,7 @@ LSB_API int lsb_moe_build_groups(const void* ids, int npairs, int E_total, void*
 // routing id array itself, group g is pair g; used for small batches where no build pass is needed.
 LSB_API int lsb_moe_gateup(const void* x, const void* arena, const void* slot_of, const void* fmt_struct,
                            const void* group_expert, const void* group_n, const void* group_pairs, const void* n_groups,
-                           void* act, int S, int max_groups, float limit, void* miss_flag, void* act_h, void* stream) {
+                           void* act, int S, int max_groups, float limit, void* miss_flag, void* stream) {
     ExpertFmt ef = *reinterpret_cast<const ExpertFmt*>(fmt_struct);
     cudaStream_t st = (cudaStream_t)stream;
     if (ef.fmt == 2 && ef.F % 128 == 0 && ef.H % 128 == 0) {   // K % 64 == 0 follows
@@ -651,11 +563,11 @@ LSB_API int lsb_moe_gateup(const void* x, const void* arena, const void* slot_of
         }
         if (!group_n)
             launch_pdl((moe_gateup_fp4_kernel<1>), g2, 256, (size_t)ef.H * 2 + 2 * (ef.H / 64) * 132, st, (const bf16*)x, (const uint8_t*)arena, (const int*)slot_of, ef, (const int*)group_expert,
-                                                                        nullptr, nullptr, nullptr, (bf16*)act, S, limit, (int*)miss_flag, (__half*)act_h);
+                                                                        nullptr, nullptr, nullptr, (bf16*)act, S, limit, (int*)miss_flag);
         else
             launch_pdl((moe_gateup_fp4_kernel<4>), g2, 256, (size_t)ef.H * 8 + 2 * (ef.H / 64) * 132, st, (const bf16*)x, (const uint8_t*)arena, (const int*)slot_of, ef, (const int*)group_expert,
                                                                         (const int*)group_n, (const int*)group_pairs, (const int*)n_groups, (bf16*)act, S, limit,
-                                                                        (int*)miss_flag, (__half*)act_h);
+                                                                        (int*)miss_flag);
         LSB_CHECK_LAUNCH();
     }
     if (!group_n) return -1;   // pair mode is only implemented for the NVFP4 fast path
@@ -702,28 +614,6 @@ LSB_API int lsb_moe_down(const void* act, const void* arena, const void* slot_of
     else if (ef.fmt == 3) launch_pdl((moe_down_kernel<3>), grid, 256, 0, st, ARGS);
     else return -1;
 #undef ARGS
-    LSB_CHECK_LAUNCH();
-}
-
-// Fused down projection + weighted combine for decode-sized steps over NVFP4 experts.  act_h: fp16 [rows * S, F] written by
-// lsb_moe_gateup (pair mode); ids / wts [rows, S]; out fp32 [rows, H] (with `comm`: this rank's partial, pushed to the peers).
-// Returns -1 when the shape is not covered (F > 2048, S > 12, sizes not multiples of 128): use lsb_moe_down + lsb_moe_combine.
-LSB_API int lsb_moe_down_combine(const void* act_h, const void* arena, const void* slot_of, const void* fmt_struct, const void* ids,
-                                 const void* wts, void* out, int rows, int S, const void* comm, void* stream) {
-    const ExpertFmt ef = *reinterpret_cast<const ExpertFmt*>(fmt_struct);
-    if (ef.fmt != 2 || ef.F % 128 || ef.H % 128 || ef.F > 2048 || S > 12 || rows > 8) return -1;
-    PeerComm pc;
-    pc.nranks = 0;
-    if (comm) pc = *reinterpret_cast<const PeerComm*>(comm);
-    cudaStream_t st = (cudaStream_t)stream;
-    dim3 grid(ef.H / 4, rows);
-#define LSB_DC(SM_, CH_) launch_pdl((moe_down_combine_fp4_kernel<SM_, CH_>), grid, 128, 0, st, (const __half*)act_h, (const uint8_t*)arena, \
-                                    (const int*)slot_of, ef, (const int*)ids, (const float*)wts, (float*)out, S, pc)
-    const int ch = ef.F > 1024 ? 2 : 1;
-    if (S <= 5) { if (ch == 2) LSB_DC(5, 2); else LSB_DC(5, 1); }
-    else if (S <= 9) { if (ch == 2) LSB_DC(9, 2); else LSB_DC(9, 1); }
-    else { if (ch == 2) LSB_DC(12, 2); else LSB_DC(12, 1); }
-#undef LSB_DC
     LSB_CHECK_LAUNCH();
 }
 

@@ -4,6 +4,7 @@
 // Reference behaviour: src/compute/kernels/sm120/sampling/sampling.cu:229-269 (one block per token,
 // inline Philox-4x32-10), confidence.cu:88, embedding.cu:28, and the orchestrator's acceptance
 // rules (python/orchestrator/orchestrator.py:289-303, 3781-3818).
+#include <atomic>
 #include "common.cuh"
 #include "comm.cuh"
 
@@ -324,23 +325,27 @@ constexpr int kNoAllocMaxRows = 256;
 static __device__ __align__(256) unsigned long long g_argmax_scratch[kNoAllocMaxRows * 64];
 
 // The array's name is only a host-side handle; the device address is looked up once per device.
+// The per-device cache is atomic: first calls for the same device may come from several host threads at once (they all
+// store the same value).
 static unsigned long long* noalloc_scratch_for_current_device(int* rc) {
-    static unsigned long long* ptrs[64] = {nullptr};
+    static std::atomic<unsigned long long*> ptrs[64];
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess || dev < 0 || dev >= 64) { *rc = e != cudaSuccess ? (int)e : -3; return nullptr; }
-    if (!ptrs[dev]) {
-        void* p = nullptr;
-        e = cudaGetSymbolAddress(&p, g_argmax_scratch);
+    unsigned long long* p = ptrs[dev].load(std::memory_order_acquire);
+    if (!p) {
+        void* q = nullptr;
+        e = cudaGetSymbolAddress(&q, g_argmax_scratch);
         if (e != cudaSuccess) { *rc = (int)e; return nullptr; }
-        ptrs[dev] = (unsigned long long*)p;
+        p = (unsigned long long*)q;
+        ptrs[dev].store(p, std::memory_order_release);
     }
     *rc = 0;
-    return ptrs[dev];
+    return p;
 }
 
 LSB_API int lsb_argmax_noalloc(const float* logits, int ld, int rows, int V, int* out_ids, float* out_val, int base, void* stream) {
-    if (rows <= 0 || V <= 0 || !logits || !out_ids) return -1;
+    if (rows <= 0 || V <= 0 || ld < V || !logits || !out_ids) return -1;     // ld < V would read past the end of a row
     if (rows > kNoAllocMaxRows) return -2;          // larger batches must use lsb_argmax with a caller-provided buffer
     int rc = 0;
     unsigned long long* part = noalloc_scratch_for_current_device(&rc);

@@ -90,17 +90,15 @@ TC_MOE_MIN_ROWS = 16      # rows per step from which the routed experts run on t
 # GLM-5.3-Flash shape the fused kernel (one block per expert, last block selects) gives 7.21 ms per decode step against 7.12 ms for
 # the split-K GEMV + top-k pair, whose second launch already overlaps the first through programmatic dependent launch
 ROUTER_FUSED = os.environ.get("LSB_ROUTER_FUSED", "0") != "0"
-# LSB_KDA_CHUNKED=1: prefill chunks of one sequence (>= 128 rows) run the KDA recurrence chunk-parallel (kda_chunk_prep / kda_chunk_scan)
-# instead of token by token.  Off by default: the kernels compile and their algorithm is verified on the CPU (models/kda_chunked.py),
-# but they have not been run on a GPU yet.
-KDA_CHUNKED = os.environ.get("LSB_KDA_CHUNKED", "0") not in ("", "0")
+# LSB_KDA_CHUNKED=0: prefill chunks of one sequence (>= 128 rows) run the KDA recurrence token by token instead of chunk-parallel
+# (kda_chunk_prep / kda_chunk_scan).  Chunk-parallel is the default: on a B200 its logits are as close to the fp32 oracle as the token
+# recurrence's (1.1e-3 .. 1.8e-3 relative on the tiny model against 1.1e-3 .. 8.6e-3) and a 2048-token chunk is faster.
+KDA_CHUNKED = os.environ.get("LSB_KDA_CHUNKED", "1") not in ("", "0")
 # LSB_MHC_CLUSTER=0: decode-sized hyper-connection passes fall back to the two-launch path (partials + last-block finalize, contraction)
 MHC_CLUSTER = os.environ.get("LSB_MHC_CLUSTER", "1") not in ("", "0")
 # ablation switches of the two folds of the cluster kernel (router behind, MoE combine in front)
 MHC_FOLD_ROUTER = os.environ.get("LSB_MHC_FOLD_ROUTER", "0") not in ("", "0")
 MHC_FOLD_COMBINE = os.environ.get("LSB_MHC_FOLD_COMBINE", "0") not in ("", "0")
-# LSB_MOE_DOWN_COMBINE=0: decode-sized NVFP4 MoE steps keep separate down-projection and combine launches
-MOE_DOWN_COMBINE = os.environ.get("LSB_MOE_DOWN_COMBINE", "1") not in ("", "0")
 
 
 def _dequant_q4k(raw: torch.Tensor, N: int, K: int) -> torch.Tensor:
@@ -391,7 +389,6 @@ class Workspace:
             self.group_pairs = z(self.max_groups * 4, dtype=i32); self.n_groups = z(1, dtype=i32)
             self.counts = z(2 * E_total + 2, dtype=i32)
             self.act = z(R * S, cfg.moe_inter, dtype=b16)
-            self.act_h = z(R * S, cfg.moe_inter, dtype=torch.float16) if R <= 8 else None     # fp16 copy for the fused down + combine kernel
             self.y = z(R * S, H)
             self.miss = z(1, dtype=i32)
             # tensor-core grouped path (many rows): expert-sorted fp16 operands and the device-built tile list
@@ -845,8 +842,7 @@ class DeviceModel:
             present = self.streamer.run_layer(self, i, arena, ws, R)
         else:
             self._moe_prepare(arena, ws, R)
-            if self._moe_experts(arena, ws, R, ws.miss if self.tp_size == 1 else None, fuse_combine=not defer_combine):
-                return False         # layer output already combined into ws.sub (and pushed to the peers)
+            self._moe_experts(arena, ws, R, ws.miss if self.tp_size == 1 else None)
             present = arena.slot_of
         if defer_combine and self.streamer is None and self._cp is None and self.tp_size == 1:
             return True
@@ -873,13 +869,9 @@ class DeviceModel:
         elif mode == "groups":
             nat.call("lsb_moe_build_groups", ws.ids, R * S, E_total, ws.group_expert, ws.group_n, ws.group_pairs, ws.n_groups, ws.counts)
 
-    def _moe_experts(self, arena: ExpertArena, ws: Workspace, R: int, miss, fuse_combine: bool = False):
-        """gate/up + SwiGLU and down projections of every pair whose expert is resident (``arena.slot_of[e] >= 0``).
-        ``fuse_combine``: the caller allows the fused down + combine kernel, which leaves the layer output (or this rank's partial
-        of it) in ``ws.sub``; returns True when it was used, i.e. when no separate combine must follow."""
+    def _moe_experts(self, arena: ExpertArena, ws: Workspace, R: int, miss):
+        """gate/up + SwiGLU and down projections of every pair whose expert is resident (``arena.slot_of[e] >= 0``)."""
         cfg, S = self.cfg, ws.S
-        fuse_combine = (fuse_combine and MOE_DOWN_COMBINE and R <= 8 and S <= 12 and cfg.moe_inter <= 2048 and arena.ef.fmt == 2
-                        and (self.tp_size == 1 or self._cp is not None))
         E_total = cfg.n_routed + cfg.n_shared
         efp = ctypes.addressof(arena.ef)
         mode = self._moe_mode(arena, ws, R)
@@ -893,21 +885,14 @@ class DeviceModel:
                      ws.tc_cnt, ws.tc_sorted, ws.y, ws.tc_bn, tiles, 0.0, None, err, None)
         elif mode == "pairs":
             # small batch: every (row, slot) pair streams its expert on its own - no grouping pass
-            if fuse_combine:
-                # decode-sized steps: the down projections of all slots and their weighted sum in one kernel, straight into ws.sub
-                nat.call("lsb_moe_gateup", ws.x, arena.data, arena.slot_of, efp, ws.ids, None, None, None, ws.act, S, R * S, cfg.swiglu_limit, miss,
-                         ws.act_h)
-                nat.call("lsb_moe_down_combine", ws.act_h, arena.data, arena.slot_of, efp, ws.ids, ws.wts, ws.sub, R, S, self._cp)
-                return True
-            nat.call("lsb_moe_gateup", ws.x, arena.data, arena.slot_of, efp, ws.ids, None, None, None, ws.act, S, R * S, cfg.swiglu_limit, miss, None)
+            nat.call("lsb_moe_gateup", ws.x, arena.data, arena.slot_of, efp, ws.ids, None, None, None, ws.act, S, R * S, cfg.swiglu_limit, miss)
             nat.call("lsb_moe_down", ws.act, arena.data, arena.slot_of, efp, ws.ids, None, None, None, ws.y, R * S)
         else:
             mg = min(ws.max_groups, min(R * S, (R * S + 3) // 4 + E_total))
             nat.call("lsb_moe_gateup", ws.x, arena.data, arena.slot_of, efp, ws.group_expert, ws.group_n, ws.group_pairs, ws.n_groups,
-                     ws.act, S, mg, cfg.swiglu_limit, miss, None)
+                     ws.act, S, mg, cfg.swiglu_limit, miss)
             nat.call("lsb_moe_down", ws.act, arena.data, arena.slot_of, efp, ws.group_expert, ws.group_n, ws.group_pairs, ws.n_groups,
                      ws.y, mg)
-        return False
 
     def _kda(self, i: int, L: dict, ws: Workspace, R: int, nseq: int):
         cfg = self.cfg

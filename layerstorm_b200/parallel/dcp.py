@@ -86,6 +86,10 @@ class DcpAttention:
     def error(self) -> int:
         return int(self.state[3])
 
+    def error_word(self) -> torch.Tensor:
+        """One-element view of the kernels' error word (read back by the engine with every step's tokens)."""
+        return self.state[3:4]
+
     def forward(self, q_local: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, max_pages: int, row_seq: torch.Tensor,
                 row_len_local: torch.Tensor, out: torch.Tensor, page: int, kv_fmt: int, scale: float, sel_idx: Optional[torch.Tensor] = None,
                 sel_cnt: Optional[torch.Tensor] = None, tq_centroids: Optional[torch.Tensor] = None, lse: Optional[torch.Tensor] = None,

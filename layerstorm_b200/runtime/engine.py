@@ -26,6 +26,24 @@ from . import native as rt
 from .native import KvPoolExhausted  # noqa: F401  (re-exported: no free KV pages, the reference's kKvPoolExhausted)
 
 
+class DeviceWaitError(RuntimeError):
+    """A bounded device-side wait gave up during the step (a peer's flag never arrived, a tensor-core pipeline barrier never
+    flipped): the step's output was computed from partial data and is withheld.  ``source`` names the error word
+    ("tp_allreduce", "argmax_exchange", "context_parallel", "tensor_core"), ``code`` is the recorded value
+    (collectives: 100 + the rank whose contribution was missing).  The word is sticky until :meth:`Engine.clear_device_errors`."""
+
+    def __init__(self, source: str, code: int):
+        super().__init__(f"device wait timed out: {source} error word = {code}" + (f" (rank {code - 100} did not arrive)" if code >= 100 else ""))
+        self.source, self.code = source, code
+
+
+def raise_on_error_words(names, values) -> None:
+    """Host half of the per-step error check: ``values[i]`` is the error word read back for source ``names[i]``."""
+    for name, v in zip(names, values):
+        if int(v) != 0:
+            raise DeviceWaitError(name, int(v))
+
+
 @dataclass
 class SequenceState:
     slot: int
@@ -66,9 +84,44 @@ class Engine:
         self.h_bt = torch.zeros(max_seqs, self.max_pages, dtype=torch.int32).pin_memory()
         self.h_out = torch.zeros(Rmax, dtype=torch.int32).pin_memory()
         self.stream = torch.cuda.Stream(device=self.dev)
+        self.h_err = torch.zeros(8, dtype=torch.int32).pin_memory()      # error words of the step, read back with the sampled tokens
         self.h2d_bytes = 0
         self.d2h_bytes = 0
         self.kernel_launches = 0
+
+    # ------------------------------------------------------------------ device error words
+    def _error_sources(self):
+        """(name, int32 tensor view of one word) for every bounded-wait error word the model's kernels can set."""
+        from ..models.device_model import TcScratch
+        m = self.model
+        src = [("tensor_core", TcScratch.get(self.dev).err[0:1])]
+        if getattr(m, "comm", None) is not None:
+            src.append(("tp_allreduce", m.comm.local_state[2:3]))
+        if getattr(m, "comm_amax", None) is not None:
+            src.append(("argmax_exchange", m.comm_amax.local_state[2:3]))
+        dcp = getattr(m, "dcp", None)
+        if dcp is not None and hasattr(dcp, "error_word"):
+            src.append(("context_parallel", dcp.error_word()))
+        return src
+
+    def _queue_error_readback(self):
+        """Called on the engine stream before the step's synchronize: the error words travel in the same device->host batch
+        as the sampled tokens (4 bytes each)."""
+        self._err_names = []
+        for j, (name, t) in enumerate(self._error_sources()):
+            self.h_err[j: j + 1].copy_(t, non_blocking=True)
+            self._err_names.append(name)
+        self.d2h_bytes += 4 * len(self._err_names)
+
+    def _check_errors(self):
+        raise_on_error_words(self._err_names, self.h_err[: len(self._err_names)].tolist())
+
+    def clear_device_errors(self):
+        """Reset the sticky error words after the cause (a dead or late rank) has been dealt with."""
+        with torch.cuda.stream(self.stream):
+            for _, t in self._error_sources():
+                t.zero_()
+        self.stream.synchronize()
 
     # ------------------------------------------------------------------ sequences
     def create_sequence(self) -> int:
@@ -177,9 +230,10 @@ class Engine:
 
     def resume(self, sid: int):
         """Bring a hibernated sequence back: allocate pages, copy host -> device, rebuild the block table."""
-        slots = self.hibernated.pop(sid)
+        slots = self.hibernated[sid]
         s = self.seqs[sid]
         self.pa.extend(s.slot, s.length)                                       # may raise KvPoolExhausted: the caller evicts and retries
+        self.hibernated.pop(sid)                                               # only now: a failed extend leaves the sequence hibernated, cold slots intact
         s.pages = self.pa.pages(s.slot)
         with torch.cuda.stream(self.copy_stream):
             for pg, cs in zip(s.pages, slots):
@@ -285,10 +339,12 @@ class Engine:
         ws = self.ws_prefill
         nxt, logits = None, None
         with torch.cuda.stream(self.stream):
+            # all pages of the call up front: running out of pages must fail BEFORE the first chunk is committed, because the
+            # caller evicts and calls again with the same tokens (a failure after chunk c would append chunks 0..c twice)
+            self._ensure_pages(s, s.length + len(tokens))
             for c0 in range(0, len(tokens), self.prefill_chunk):
                 chunk = tokens[c0: c0 + self.prefill_chunk]
                 R = len(chunk)
-                self._ensure_pages(s, s.length + R)
                 rows = [(t, s.slot, s.length + j) for j, t in enumerate(chunk)]
                 self._stage(ws, rows, [(0, R, s.slot)])
                 n0 = nat.launch_count()
@@ -299,7 +355,9 @@ class Engine:
                 s.tokens.extend(chunk)
             self.h_out[:1].copy_(ws.out_tok[:1], non_blocking=True)
             self.d2h_bytes += 4
+            self._queue_error_readback()
             self.stream.synchronize()
+            self._check_errors()
             nxt = int(self.h_out[0])
             if want_logits:
                 logits = ws.logits[0].float().cpu()
@@ -318,7 +376,9 @@ class Engine:
             n0 = nat.launch_count()
             self.model.forward(ws, R, 1, 0, R)
             self.kernel_launches += nat.launch_count() - n0
+            self._queue_error_readback()
             self.stream.synchronize()
+            self._check_errors()
         if commit:
             s.length += R
             s.tokens.extend(int(t) for t in tokens)
@@ -351,7 +411,9 @@ class Engine:
                 self.kernel_launches += nat.launch_count() - n0
             self.h_out[:B].copy_(ws.out_tok[:B], non_blocking=True)
             self.d2h_bytes += 4 * B
+            self._queue_error_readback()
             self.stream.synchronize()
+            self._check_errors()
         out = [int(self.h_out[j]) for j in range(B)]
         for sid, tok in zip(sids, tokens):
             s = self.seqs[sid]

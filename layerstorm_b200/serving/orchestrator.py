@@ -276,7 +276,9 @@ class Orchestrator:
         st.cached_tokens = cached
         need_logits = (not p.greedy) or p.logprobs > 0 or req.logit_mask is not None
         try:
-            out = self._with_pool_evict_retry(req, lambda: eng.prefill(sid, prompt[cached:], want_logits=need_logits))
+            # every attempt feeds what is still missing (the engine's prefill reserves its pages up front and fails before it
+            # commits anything, and even an engine that failed mid-prompt is continued, never re-fed)
+            out = self._with_pool_evict_retry(req, lambda: eng.prefill(sid, prompt[max(cached, eng.seq_len(sid)):], want_logits=need_logits))
             self.prefix.register(sid, prompt)
             tok, logits = out if need_logits else (out, None)
             if need_logits:

@@ -18,5 +18,5 @@ def test_reference_arm_prints_unavailable_and_exits_zero():
 def test_arguments_named_by_the_contract_exist():
     r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--help"], capture_output=True, text=True, timeout=120)
     assert r.returncode == 0
-    for flag in ("--gpus", "--steps", "--warmup", "--impl", "--model", "--batch", "--ctx", "--prefill-chunk", "--extra-batches", "--dcp-chunk"):
+    for flag in ("--gpus", "--steps", "--warmup", "--impl", "--model", "--batch", "--ctx", "--prefill-chunk", "--extra-batches", "--dcp-chunk", "--tp", "--ep", "--long-prompt"):
         assert flag in r.stdout, flag

@@ -221,49 +221,6 @@ def test_router_fused_projection_and_topk(E, k, n_group, topk_group, R):
     assert torch.equal(ids, ids2) and torch.equal(wts, wts2)
 
 
-@pytest.mark.parametrize("H,F,E,k,R", [(1024, 2048, 12, 8, 1), (256, 256, 8, 4, 3), (512, 1024, 16, 11, 2)])
-def test_moe_fused_down_combine_matches_two_kernel_path(H, F, E, k, R):
-    """Pair-mode NVFP4 experts: gate / up + (down and weighted combine in one kernel, weights requested before the dependency wait)
-    against gate / up + down + combine as separate kernels and against fp32 math on the de-quantised expert weights."""
-    import ctypes
-    from layerstorm_b200.models.device_model import ExpertArena, QLinear, expert_layout
-    S = k + 1
-    g = torch.Generator().manual_seed(5)
-    arena = ExpertArena(expert_layout("nvfp4", H, F), E + 1, E + 1, DEV)
-    mats = []
-    for e in range(E + 1):
-        gate, up, down = (QLinear.from_float(torch.randn(n_, k_, generator=g) * 0.05, "nvfp4", DEV) for n_, k_ in ((F, H), (F, H), (H, F)))
-        arena.write_expert(e, gate, up, down)
-        arena.slot_of[e] = e
-        mats.append((gate.dequant().cpu(), up.dequant().cpu(), down.dequant().cpu()))
-    efp = ctypes.addressof(arena.ef)
-    x = rnd(R, H, dtype=torch.bfloat16, seed=8)
-    ids = torch.stack([torch.cat([torch.randperm(E, generator=g)[:k], torch.tensor([E])]) for _ in range(R)]).int().to(DEV)
-    wts = (torch.rand(R, S, generator=g) + 0.1).to(DEV)
-    arena.slot_of[int(ids[0, 1])] = -1                     # one selected expert is not resident: its slot contributes nothing
-    act = torch.zeros(R * S, F, dtype=torch.bfloat16, device=DEV); act_h = torch.zeros(R * S, F, dtype=torch.float16, device=DEV)
-    y = torch.zeros(R * S, H, device=DEV); two = torch.zeros(R, H, device=DEV); one = torch.zeros(R, H, device=DEV)
-    nat.call("lsb_moe_gateup", x, arena.data, arena.slot_of, efp, ids, None, None, None, act, S, R * S, 10.0, None, act_h)
-    nat.call("lsb_moe_down", act, arena.data, arena.slot_of, efp, ids, None, None, None, y, R * S)
-    nat.call("lsb_moe_combine", two, y, wts, ids, arena.slot_of, R, S, H, 0, None)
-    nat.call("lsb_moe_down_combine", act_h, arena.data, arena.slot_of, efp, ids, wts, one, R, S, None)
-    torch.cuda.synchronize()
-    so = arena.slot_of.cpu()
-    want = torch.zeros(R, H)
-    xf = x.float().cpu()
-    for r in range(R):
-        for s_ in range(S):
-            e = int(ids[r, s_])
-            if so[e] < 0:
-                continue
-            gm, um, dm = mats[e]
-            gv, uv = (xf[r] @ gm.T).clamp(max=10.0), (xf[r] @ um.T).clamp(-10.0, 10.0)
-            want[r] += float(wts[r, s_]) * ((torch.nn.functional.silu(gv) * uv) @ dm.T)
-    close(two, want, 2e-2, 2e-2 * float(want.abs().max()), "two-kernel path vs fp32")
-    close(one, want, 2e-2, 2e-2 * float(want.abs().max()), "fused down + combine vs fp32")
-    close(one, two, 1e-2, 1e-2 * float(want.abs().max()), "fused vs two-kernel path")
-
-
 @pytest.mark.parametrize("scoring", ["sigmoid", "softmax", "sqrtsoftplus"])
 def test_router_hash(scoring):
     E, k, R, V = 48, 6, 7, 100

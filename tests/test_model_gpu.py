@@ -211,24 +211,75 @@ def test_hibernate_resume_is_bit_identical_and_frees_pages(name):
     assert eng.d2h_bytes > 0 and not eng.hibernated
 
 
-@pytest.mark.skipif(__import__("os").environ.get("LSB_KDA_CHUNKED", "0") in ("", "0"),
-                    reason="the chunk-parallel KDA recurrence is opt-in (LSB_KDA_CHUNKED=1)")
-def test_kda_chunked_prefill_matches_token_recurrence():
+def test_kda_chunked_prefill_matches_token_recurrence(monkeypatch):
     """Single-sequence steps of >= 128 rows run kda_chunk_prep / kda_chunk_scan; shorter steps run the token-by-token kernel.
-    Both must give the same logits, the same next token and the same carried state (checked through the following decode steps)."""
+    Both must give the same next token, and logits as close to the fp32 oracle as the token recurrence gives - at the prompt's
+    last position and, through the carried state, at the decode steps that follow."""
+    from layerstorm_b200.models import device_model as dm
+    monkeypatch.setattr(dm, "KDA_CHUNKED", True)
     cfg, m, oracle = build("tiny-glm5-next")
     prompt = torch.randint(0, cfg.vocab, (200,), generator=torch.Generator().manual_seed(11)).tolist()      # 3 full chunks + 8 tokens
+    cont = [5, 9, 2]
+    refs = [oracle.forward(torch.tensor(prompt + cont[:j]))[-1] for j in range(len(cont) + 1)]
     res = []
     for chunk in (200, 100):
         eng = Engine(m, max_seqs=1, max_ctx=256, prefill_chunk=chunk, max_batch=1, use_graph=False)
+        assert (eng.ws_prefill is None)
         sid = eng.create_sequence()
         nxt, lg = eng.prefill(sid, prompt, want_logits=True)
-        steps = [eng.decode([sid], [t], return_logits=True)[1][0].clone() for t in (5, 9, 2)]
-        res.append((nxt, lg.clone(), steps))
+        assert (eng.ws_prefill.kda_chunk_ws is not None) == (chunk >= 128)
+        steps = [eng.decode([sid], [t], return_logits=True)[1][0].clone() for t in cont]
+        res.append((nxt, [lg.clone()] + steps))
         eng.free_sequence(sid)
-    assert res[0][0] == res[1][0]
-    assert rel_err(res[0][1], res[1][1]) < 2e-3, rel_err(res[0][1], res[1][1])
-    for a, b in zip(res[0][2], res[1][2]):
-        assert rel_err(a, b) < 2e-3, rel_err(a, b)
-    ref = oracle.forward(torch.tensor(prompt))[-1]
-    assert rel_err(res[0][1], ref) < 3e-2 and res[0][0] == int(ref.argmax())
+    assert res[0][0] == res[1][0] == int(refs[0].argmax())
+    for j, ref in enumerate(refs):
+        e_chunk, e_tok = rel_err(res[0][1][j], ref), rel_err(res[1][1][j], ref)
+        print(f"position {j}: chunk-parallel {e_chunk:.4g}, token recurrence {e_tok:.4g} (relative to the oracle)")
+        assert e_chunk < 3e-2 and e_chunk < 2.0 * e_tok + 5e-3, (j, e_chunk, e_tok)
+
+
+def test_resume_that_runs_out_of_pages_keeps_the_sequence_hibernated():
+    """A resume that cannot get its pages fails cleanly: the cold copy and the hibernated state stay, and after room has been
+    made the same resume gives bit-identical logits (the sequence never decodes on fresh, uninitialised pages)."""
+    from layerstorm_b200.runtime.engine import KvPoolExhausted
+    cfg, m, _ = build("tiny-deepseek-v32", kv="fp8")
+    eng = Engine(m, max_seqs=3, max_ctx=128, prefill_chunk=16, max_batch=1, num_pages=10, use_graph=False)
+    eng.enable_kv_tiering(cold_pages=16)
+    g = torch.Generator().manual_seed(3)
+    pa = torch.randint(0, cfg.vocab, (70,), generator=g).tolist()
+    pb = torch.randint(0, cfg.vocab, (100,), generator=g).tolist()
+    a = eng.create_sequence()
+    ta = eng.prefill(a, pa)
+    ref_tok, ref_lg = eng.decode([a], [ta], return_logits=True)
+    eng.free_sequence(a)
+    a = eng.create_sequence()
+    assert eng.prefill(a, pa) == ta
+    eng.hibernate(a)
+    b = eng.create_sequence()
+    eng.prefill(b, pb)                                       # 7 of the 10 pages: a's 5 pages no longer fit
+    with pytest.raises(KvPoolExhausted):
+        eng.decode([a], [ta])                                # resumes first: no room
+    assert a in eng.hibernated and eng.seqs[a].pages == []
+    eng.free_sequence(b)
+    tok, lg = eng.decode([a], [ta], return_logits=True)
+    assert tok == ref_tok and torch.equal(lg, ref_lg)
+
+
+def test_a_set_error_word_withholds_the_step_output():
+    """The bounded device waits report through error words; the engine reads them back with every step's tokens and raises a
+    typed error instead of returning a token computed from partial data.  The word is set by hand here (nothing is made to
+    hang); it is sticky until cleared."""
+    from layerstorm_b200.models.device_model import TcScratch
+    from layerstorm_b200.runtime.engine import DeviceWaitError
+    cfg, m, _ = build("tiny-mla-moe")
+    eng = Engine(m, max_seqs=1, max_ctx=64, prefill_chunk=16, max_batch=1, use_graph=False)
+    sid = eng.create_sequence()
+    t = eng.prefill(sid, list(range(3, 20)))
+    TcScratch.get(m.device).err.fill_(7)
+    with pytest.raises(DeviceWaitError) as ei:
+        eng.decode([sid], [t])
+    assert ei.value.source == "tensor_core" and ei.value.code == 7
+    with pytest.raises(DeviceWaitError):
+        eng.decode([sid], [t])
+    eng.clear_device_errors()
+    assert isinstance(eng.decode([sid], [t])[0], int)

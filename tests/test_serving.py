@@ -217,3 +217,50 @@ def test_randomised_requests_with_shared_prefixes_under_pool_pressure():
     assert cached > 0                                             # the shared stems were reused
     orch.prefix.clear()
     assert len(eng.free_slots) == eng.max_seqs and eng.free_page_count() == total_pages
+
+
+def test_pool_exhaustion_in_the_middle_of_a_chunked_prefill_does_not_duplicate_the_prefix():
+    """An engine whose prefill commits chunk by chunk and runs out of pages at a later chunk: the orchestrator evicts a prefix
+    holder and continues from the committed frontier - it must not feed the committed chunks a second time."""
+    from layerstorm_b200.runtime.native import KvPoolExhausted
+
+    class ChunkedEngine(NullEngine):
+        chunk = 32
+        failures = 0
+
+        def prefill(self, sid, tokens, want_logits=False):
+            tokens = [int(t) for t in tokens]
+            out = None
+            for c0 in range(0, len(tokens), self.chunk):
+                try:
+                    out = NullEngine.prefill(self, sid, tokens[c0: c0 + self.chunk], want_logits)
+                except KvPoolExhausted:
+                    ChunkedEngine.failures += 1
+                    raise
+            return out
+
+    prompt_a, prompt_b = list(range(10, 138)), list(range(300, 460))
+    ref_eng = NullEngine()
+    sid = ref_eng.create_sequence()
+    t = ref_eng.prefill(sid, prompt_b)
+    ref = [t]
+    for _ in range(7):
+        t = ref_eng.decode([sid], [t])[0]
+        ref.append(t)
+    # 14 pages of 16 tokens: request A (128 tokens + 8 generated) leaves a holder of 8 pages; request B needs 11 pages, so its
+    # prefill runs out of pages after a few chunks, the holder is evicted and the prefill goes on
+    eng = ChunkedEngine(max_seqs=4, max_ctx=512, page=16, num_pages=14)
+    orch = Orchestrator(eng, prefix_cache=PrefixCacheConfig(enabled=True, grid=64, min_prefix=64))
+    run(orch, prompt_a, max_tokens=8, ignore_eos=True)
+    assert orch.prefix.holders() >= 1
+    rb = run(orch, prompt_b, max_tokens=8, ignore_eos=True)
+    assert ChunkedEngine.failures >= 1, "the scenario must exhaust the pool in the middle of the prompt"
+    assert rb.output_ids == ref
+
+
+def test_device_error_words_raise_a_typed_error():
+    from layerstorm_b200.runtime.engine import DeviceWaitError, raise_on_error_words
+    raise_on_error_words(["tensor_core", "tp_allreduce"], [0, 0])
+    with pytest.raises(DeviceWaitError) as ei:
+        raise_on_error_words(["tensor_core", "tp_allreduce"], [0, 103])
+    assert ei.value.source == "tp_allreduce" and ei.value.code == 103 and "rank 3" in str(ei.value)

@@ -23,7 +23,7 @@ def test_noalloc_argmax_matches_regular_entry_point_twice():
     max_rows = lib.lsb_argmax_noalloc_max_rows()
     assert max_rows == 256
     st = torch.cuda.current_stream().cuda_stream
-    for call, (rows, V) in enumerate([(7, 50021), (3, 1031)]):
+    for call, (rows, V) in enumerate([(7, 50021), (3, 1031), (max_rows, 257)]):     # the last case touches the whole fixed array
         g = torch.Generator().manual_seed(100 + call)
         logits = (torch.randn(rows, V, generator=g) * 3).cuda()
         logits[0, 5] = logits[0, V - 2] = 99.0                 # tie: the lower index must win
@@ -39,6 +39,8 @@ def test_noalloc_argmax_matches_regular_entry_point_twice():
         assert torch.equal(ids, ref_ids) and torch.equal(val, ref_val)
         assert int(ids[0]) == 11 + 5
         assert torch.equal(ids[1:].cpu().long() - 11, logits[1:].cpu().argmax(-1))
+    # a row stride shorter than the row is refused
+    assert fn(logits.data_ptr(), V - 1, rows, V, ids.data_ptr(), None, 0, st) == -1
     # beyond the fixed scratch size the call is refused and nothing runs
     big = torch.zeros(max_rows + 1, 8, device="cuda")
     out = torch.full((max_rows + 1,), -7, dtype=torch.int32, device="cuda")

@@ -29,6 +29,8 @@ struct PeerComm {
     unsigned* epoch;                 // local: reductions completed so far
     unsigned* cta_done;              // local: blocks of the current producer that have finished
     int* err;                        // local error word (0 = ok)
+    int xchg;                        // 1: few-row step - producers keep their partial local and only count the epoch, the
+                                     //    consuming kernel exchanges it (comm_xchg_* below); 0: producers push
 };
 
 __device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
@@ -68,6 +70,10 @@ __device__ __forceinline__ void comm_push4(const PeerComm& c, unsigned next_epoc
 // thousands of 4-byte stores.
 __device__ __forceinline__ void comm_finish_local(const PeerComm& c, unsigned next_epoch, unsigned total_blocks, const float* buf, int M, int N,
                                                   int ld) {
+    if (c.xchg) {      // consumer-side exchange: the partial stays where it is; one thread of the grid counts the reduction
+        if ((blockIdx.x | blockIdx.y | blockIdx.z | threadIdx.x) == 0) *c.epoch = next_epoch;
+        return;
+    }
     __shared__ int s_last;
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -134,6 +140,62 @@ __device__ __forceinline__ void comm_wait(const PeerComm& c, unsigned epoch) {
         }
     }
     __syncthreads();
+}
+
+// ---- consumer-side exchange (few rows) ---------------------------------------------------------------------------------
+// For decode-sized steps the producer's push costs more than the data movement: every block of a weight-streaming kernel
+// arrives on one atomic counter and the last one copies the whole partial to every peer.  In this mode the producer keeps
+// its partial in LOCAL memory and the kernel that consumes the sum does the exchange itself, slice by slice: each of its
+// CTAs stores the slice it is about to use into every peer's slot, publishes ONE flag per CTA, waits for the same CTA of
+// every peer and sums in rank order.  No atomics, no serial copy; a CTA only waits for the columns it needs.
+// Flag words: flags[p][(parity * nranks + src) * kXchgCtas + cta]  (the first 2 * nranks words are the producer-push flags).
+constexpr int kXchgCtas = 128;
+__device__ __forceinline__ unsigned* comm_xchg_flag(const PeerComm& c, int peer, unsigned epoch, int src, int cta) {
+    return c.flags[peer] + 2 * kMaxRanks + ((epoch & 1u) * c.nranks + src) * kXchgCtas + cta;
+}
+// Phase 1 (every thread that owns values): store VEC consecutive values of this rank's partial into every peer's slot.
+template <int VEC>
+__device__ __forceinline__ void comm_xchg_put(const PeerComm& c, unsigned epoch, size_t idx, const float* v) {
+    const size_t off = ((size_t)(epoch & 1u) * c.nranks + c.rank) * (size_t)c.cap + idx;
+#pragma unroll
+    for (int p = 0; p < kMaxRanks; ++p) {
+        if (p < c.nranks && p != c.rank) {
+            if (VEC == 4) *reinterpret_cast<float4*>(c.recv[p] + off) = make_float4(v[0], v[1], v[2], v[3]);
+            else if (VEC == 2) *reinterpret_cast<float2*>(c.recv[p] + off) = make_float2(v[0], v[VEC > 1 ? 1 : 0]);
+            else c.recv[p][off] = v[0];
+        }
+    }
+}
+// Phase 2 (whole block): publish this CTA's flag to every peer, then wait (bounded, ~2 s) for the same CTA of every peer.
+__device__ __forceinline__ void comm_xchg_sync(const PeerComm& c, unsigned epoch, int cta) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        for (int p = 0; p < c.nranks; ++p)
+            if (p != c.rank) st_release_sys(comm_xchg_flag(c, p, epoch, c.rank, cta), epoch);
+    }
+    if (threadIdx.x < (unsigned)c.nranks && (int)threadIdx.x != c.rank) {
+        const unsigned* f = comm_xchg_flag(c, c.rank, epoch, (int)threadIdx.x, cta);
+        if ((int)(ld_acquire_sys(f) - epoch) < 0) {
+            const unsigned long long t0 = comm_now_ns();
+            unsigned it = 0;
+            while ((int)(ld_acquire_sys(f) - epoch) < 0) {
+                if ((++it & 1023u) == 0 && comm_now_ns() - t0 > 2000000000ull) { atomicCAS(c.err, 0, 100 + (int)threadIdx.x); break; }
+            }
+        }
+    }
+    __syncthreads();
+}
+// Phase 3: the sum over ranks in rank order of element idx; this rank's own value comes from the caller (same bits on every rank).
+__device__ __forceinline__ float comm_xchg_get(const PeerComm& c, unsigned epoch, size_t idx, float own) {
+    const float* base = c.recv[c.rank] + (size_t)(epoch & 1u) * c.nranks * (size_t)c.cap + idx;
+    float v[kMaxRanks];
+#pragma unroll
+    for (int p = 0; p < kMaxRanks; ++p) v[p] = (p < c.nranks && p != c.rank) ? __ldcg(base + (size_t)p * c.cap) : 0.f;
+    float a = 0.f;
+#pragma unroll
+    for (int p = 0; p < kMaxRanks; ++p) a += (p == c.rank) ? own : v[p];
+    return a;
 }
 
 // Sum of the ranks' slots for element idx, in rank order.

@@ -126,7 +126,18 @@ __global__ void __launch_bounds__(512, 1) mhc_cluster_kernel(const __grid_consta
 
     // ---- sublayer output for this thread's columns ----
     float xv[VEC];
-    if (a.comm.nranks && a.mode == 1) {
+    if (a.comm.nranks && a.mode == 1 && a.comm.xchg) {
+        // consumer-side exchange: this CTA ships its columns of the local partial to the peers, publishes one flag and waits for
+        // the same CTA of every peer - no producer-side copy, and a CTA only waits for the columns it needs
+        const unsigned epoch = *a.comm.epoch;
+        const typename VecT<VEC>::T q = vld<VEC>(a.x + (size_t)r * hidden + h);
+        float own[VEC];
+        memcpy(own, &q, sizeof(q));
+        if (og == 0) comm_xchg_put<VEC>(a.comm, epoch, (size_t)r * hidden + h, own);
+        comm_xchg_sync(a.comm, epoch, (int)(blockIdx.y * gridDim.x + blockIdx.x));
+#pragma unroll
+        for (int u = 0; u < VEC; ++u) xv[u] = comm_xchg_get(a.comm, epoch, (size_t)r * hidden + h + u, own[u]);
+    } else if (a.comm.nranks && a.mode == 1) {
         const unsigned epoch = *a.comm.epoch;
         comm_wait(a.comm, epoch);
 #pragma unroll

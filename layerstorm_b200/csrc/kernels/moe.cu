@@ -455,8 +455,10 @@ __global__ void moe_combine_kernel(float* __restrict__ out, const float* __restr
     const int h = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
     unsigned next_epoch = 0;
     if (comm.nranks) next_epoch = *comm.epoch + 1;
+    const bool push = comm.nranks && !comm.xchg;      // xchg: this rank's partial stays local, the consuming kernel exchanges it
+    if (comm.nranks && comm.xchg && (blockIdx.x | blockIdx.y | threadIdx.x) == 0) *comm.epoch = next_epoch;
     if (h >= H) {
-        if (comm.nranks) comm_signal(comm, next_epoch, gridDim.x * gridDim.y);
+        if (push) comm_signal(comm, next_epoch, gridDim.x * gridDim.y);
         return;
     }
     // routing metadata first (independent loads), then all slot rows in flight together
@@ -475,7 +477,7 @@ __global__ void moe_combine_kernel(float* __restrict__ out, const float* __restr
     for (int s = 0; s < kMaxS; ++s) {
         if (e[s] >= 0) { a.x = fmaf(w[s], v[s].x, a.x); a.y = fmaf(w[s], v[s].y, a.y); a.z = fmaf(w[s], v[s].z, a.z); a.w = fmaf(w[s], v[s].w, a.w); }
     }
-    if (comm.nranks) {
+    if (push) {
         const size_t idx = (size_t)r * H + h;
         if ((comm.cap & 3) == 0) {
             comm_push4(comm, next_epoch, idx, a);

@@ -32,10 +32,20 @@ __global__ void rmsnorm_kernel(bf16* __restrict__ out, const TIn* __restrict__ x
     pdl_wait();
     pdl_launch_dependents();
     unsigned epoch = 0;
-    if (comm.nranks) { epoch = *comm.epoch; comm_wait(comm, epoch); }
+    if (comm.nranks) {
+        epoch = *comm.epoch;
+        if (comm.xchg) {
+            // consumer-side exchange: this block ships its row of the local partial to the peers, then waits for theirs
+            for (int i = threadIdx.x; i < dim; i += blockDim.x) { const float v = ld_as_float<TIn>(xr, i); comm_xchg_put<1>(comm, epoch, (size_t)r * ldx + i, &v); }
+            comm_xchg_sync(comm, epoch, r);
+        } else {
+            comm_wait(comm, epoch);
+        }
+    }
     float ss = 0.f;
     for (int i = threadIdx.x; i < dim; i += blockDim.x) {
-        float v = comm.nranks ? comm_reduce(comm, epoch, (size_t)r * ldx + i) : ld_as_float<TIn>(xr, i);
+        float v = comm.nranks ? (comm.xchg ? comm_xchg_get(comm, epoch, (size_t)r * ldx + i, ld_as_float<TIn>(xr, i)) : comm_reduce(comm, epoch, (size_t)r * ldx + i))
+                              : ld_as_float<TIn>(xr, i);
         if (ADD) {
             v += resid[(size_t)r * ldr + i];
             resid[(size_t)r * ldr + i] = v;
@@ -505,7 +515,15 @@ __global__ void mhc_contract_norm_kernel(bf16* __restrict__ out, const float* __
     pdl_wait();
     pdl_launch_dependents();
     unsigned epoch = 0;
-    if (comm.nranks) { epoch = *comm.epoch; comm_wait(comm, epoch); }
+    if (comm.nranks) {
+        epoch = *comm.epoch;
+        if (comm.xchg) {
+            for (int h = threadIdx.x; h < hidden; h += blockDim.x) { const float v = x[(size_t)r * hidden + h]; comm_xchg_put<1>(comm, epoch, (size_t)r * hidden + h, &v); }
+            comm_xchg_sync(comm, epoch, r);
+        } else {
+            comm_wait(comm, epoch);
+        }
+    }
     const float* rp = residual + (size_t)r * n * hidden;
     float pm = 0.f, cw[kHcMax];
     for (int j = 0; j < n; ++j) pm += post[r * n + j];
@@ -516,7 +534,9 @@ __global__ void mhc_contract_norm_kernel(bf16* __restrict__ out, const float* __
     }
     float ss = 0.f;
     for (int h = threadIdx.x; h < hidden; h += blockDim.x) {
-        float a = pm * (comm.nranks ? comm_reduce(comm, epoch, (size_t)r * hidden + h) : x[(size_t)r * hidden + h]);
+        float a = pm * (comm.nranks ? (comm.xchg ? comm_xchg_get(comm, epoch, (size_t)r * hidden + h, x[(size_t)r * hidden + h])
+                                                  : comm_reduce(comm, epoch, (size_t)r * hidden + h))
+                                    : x[(size_t)r * hidden + h]);
         for (int i = 0; i < n; ++i) a += cw[i] * rp[(size_t)i * hidden + h];
         a /= (float)n;
         row[h] = a;
@@ -536,6 +556,10 @@ __global__ void __launch_bounds__(256) comm_push_rows_kernel(const float* __rest
     pdl_wait();
     pdl_launch_dependents();
     const unsigned next_epoch = *c.epoch + 1u;
+    if (c.xchg) {          // the consuming kernel exchanges the (already local) partial itself
+        if ((blockIdx.x | threadIdx.x) == 0) *c.epoch = next_epoch;
+        return;
+    }
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const long long m = i / N;
         comm_push(c, next_epoch, (size_t)i, x[m * ld + (i - m * N)]);

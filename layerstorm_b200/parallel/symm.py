@@ -23,7 +23,7 @@ K_MAX_RANKS = 8
 class PeerCommStruct(ctypes.Structure):
     _fields_ = [("nranks", ctypes.c_int), ("rank", ctypes.c_int), ("cap", ctypes.c_longlong),
                 ("recv", ctypes.c_void_p * K_MAX_RANKS), ("flags", ctypes.c_void_p * K_MAX_RANKS),
-                ("epoch", ctypes.c_void_p), ("cta_done", ctypes.c_void_p), ("err", ctypes.c_void_p)]
+                ("epoch", ctypes.c_void_p), ("cta_done", ctypes.c_void_p), ("err", ctypes.c_void_p), ("xchg", ctypes.c_int)]
 
 
 class SymmetricBuffer:
@@ -78,7 +78,8 @@ class PeerComm:
         cap_floats = (cap_floats + 3) // 4 * 4
         self.cap = cap_floats
         recv_bytes = 2 * self.world * cap_floats * 4
-        flag_bytes = 256
+        # producer-push flags [2][8] + consumer-exchange flags [2][8 ranks][128 CTAs] (see csrc/kernels/comm.cuh)
+        flag_bytes = (2 * K_MAX_RANKS + 2 * K_MAX_RANKS * 128) * 4
         self.buf = SymmetricBuffer(recv_bytes + flag_bytes, device, group)
         self.local_state = torch.zeros(16, dtype=torch.int32, device=device)   # epoch, cta_done, err
         s = PeerCommStruct()
@@ -88,6 +89,7 @@ class PeerComm:
             s.flags[p] = self.buf.ptrs[p] + recv_bytes
         base = self.local_state.data_ptr()
         s.epoch, s.cta_done, s.err = base, base + 4, base + 8
+        s.xchg = 0
         self.struct = s
 
     @property

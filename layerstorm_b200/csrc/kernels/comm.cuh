@@ -29,8 +29,11 @@ struct PeerComm {
     unsigned* epoch;                 // local: reductions completed so far
     unsigned* cta_done;              // local: blocks of the current producer that have finished
     int* err;                        // local error word (0 = ok)
-    int xchg;                        // 1: few-row step - producers keep their partial local and only count the epoch, the
-                                     //    consuming kernel exchanges it (comm_xchg_* below); 0: producers push
+    int xchg;                        // few-row step: producers keep their partial local and only count the epoch, the consuming
+                                     //    kernel exchanges it - 1: data + one flag per CTA (comm_xchg_*), 2: flag-in-data words
+                                     //    (comm_ll_*); 0: producers push
+    long long ll_cap;                // elements per (parity, source-rank) slot of the flag-in-data buffers
+    unsigned long long* ll[kMaxRanks];   // ll[p] = rank p's flag-in-data receive buffer [2][nranks][ll_cap] of (value, epoch) pairs
 };
 
 __device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
@@ -196,6 +199,75 @@ __device__ __forceinline__ float comm_xchg_get(const PeerComm& c, unsigned epoch
 #pragma unroll
     for (int p = 0; p < kMaxRanks; ++p) a += (p == c.rank) ? own : v[p];
     return a;
+}
+
+// ---- flag-in-data exchange (lowest latency) ------------------------------------------------------------------------------
+// Every element travels as one 8-byte word (fp32 value, epoch): the store that delivers the value also announces it, so the
+// receiver needs no fence, no separate flag and no block-wide barrier - it polls the words it is about to use until they carry
+// the current epoch.  8-byte stores arrive whole over NVLink; the epoch never repeats, so a stale word cannot be mistaken.
+template <int VEC>
+__device__ __forceinline__ void comm_ll_put(const PeerComm& c, unsigned epoch, size_t idx, const float* v) {
+    const size_t off = ((size_t)(epoch & 1u) * c.nranks + c.rank) * (size_t)c.ll_cap + idx;
+#pragma unroll
+    for (int p = 0; p < kMaxRanks; ++p) {
+        if (p < c.nranks && p != c.rank) {
+            unsigned long long* d = c.ll[p] + off;
+            if (VEC == 2) {
+                asm volatile("st.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(d), "r"(__float_as_uint(v[0])), "r"(epoch),
+                             "r"(__float_as_uint(v[VEC > 1 ? 1 : 0])), "r"(epoch) : "memory");
+            } else {
+#pragma unroll
+                for (int u = 0; u < VEC; ++u)
+                    asm volatile("st.global.v2.u32 [%0], {%1, %2};" ::"l"(d + u), "r"(__float_as_uint(v[u])), "r"(epoch) : "memory");
+            }
+        }
+    }
+}
+// VEC consecutive elements: out[u] = sum over ranks in rank order (own[u] at this rank's position).  Polls (bounded, ~2 s).
+template <int VEC>
+__device__ __forceinline__ void comm_ll_get(const PeerComm& c, unsigned epoch, size_t idx, const float* own, float* out) {
+    const unsigned long long* base = c.ll[c.rank] + (size_t)(epoch & 1u) * c.nranks * (size_t)c.ll_cap + idx;
+    float v[kMaxRanks][VEC];
+#pragma unroll
+    for (int p = 0; p < kMaxRanks; ++p) {
+#pragma unroll
+        for (int u = 0; u < VEC; ++u) v[p][u] = 0.f;
+        if (p < c.nranks && p != c.rank) {
+            const unsigned long long* src = base + (size_t)p * c.ll_cap;
+            unsigned long long t0 = 0;
+            unsigned it = 0;
+            while (true) {
+                bool ok = true;
+                if (VEC == 2) {
+                    unsigned a, ea, b, eb;
+                    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(a), "=r"(ea), "=r"(b), "=r"(eb) : "l"(src) : "memory");
+                    ok = ea == epoch && eb == epoch;
+                    v[p][0] = __uint_as_float(a); v[p][VEC > 1 ? 1 : 0] = __uint_as_float(b);
+                } else {
+#pragma unroll
+                    for (int u = 0; u < VEC; ++u) {
+                        unsigned a, ea;
+                        asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(a), "=r"(ea) : "l"(src + u) : "memory");
+                        ok = ok && ea == epoch;
+                        v[p][u] = __uint_as_float(a);
+                    }
+                }
+                if (ok) break;
+                if ((++it & 255u) == 0) {
+                    const unsigned long long now = comm_now_ns();
+                    if (t0 == 0) t0 = now;
+                    else if (now - t0 > 2000000000ull) { atomicCAS(c.err, 0, 100 + p); break; }
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < VEC; ++u) {
+        float a = 0.f;
+#pragma unroll
+        for (int p = 0; p < kMaxRanks; ++p) a += (p == c.rank) ? own[u] : v[p][u];
+        out[u] = a;
+    }
 }
 
 // Sum of the ranks' slots for element idx, in rank order.

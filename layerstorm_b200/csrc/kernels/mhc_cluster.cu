@@ -133,10 +133,16 @@ __global__ void __launch_bounds__(512, 1) mhc_cluster_kernel(const __grid_consta
         const typename VecT<VEC>::T q = vld<VEC>(a.x + (size_t)r * hidden + h);
         float own[VEC];
         memcpy(own, &q, sizeof(q));
-        if (og == 0) comm_xchg_put<VEC>(a.comm, epoch, (size_t)r * hidden + h, own);
-        comm_xchg_sync(a.comm, epoch, (int)(blockIdx.y * gridDim.x + blockIdx.x));
+        if (a.comm.xchg == 2) {
+            // flag-in-data words: no fence, no flag, no barrier - every warp polls the words of its own columns
+            if (og == 0) comm_ll_put<VEC>(a.comm, epoch, (size_t)r * hidden + h, own);
+            comm_ll_get<VEC>(a.comm, epoch, (size_t)r * hidden + h, own, xv);
+        } else {
+            if (og == 0) comm_xchg_put<VEC>(a.comm, epoch, (size_t)r * hidden + h, own);
+            comm_xchg_sync(a.comm, epoch, (int)(blockIdx.y * gridDim.x + blockIdx.x));
 #pragma unroll
-        for (int u = 0; u < VEC; ++u) xv[u] = comm_xchg_get(a.comm, epoch, (size_t)r * hidden + h + u, own[u]);
+            for (int u = 0; u < VEC; ++u) xv[u] = comm_xchg_get(a.comm, epoch, (size_t)r * hidden + h + u, own[u]);
+        }
     } else if (a.comm.nranks && a.mode == 1) {
         const unsigned epoch = *a.comm.epoch;
         comm_wait(a.comm, epoch);

@@ -36,16 +36,22 @@ __global__ void rmsnorm_kernel(bf16* __restrict__ out, const TIn* __restrict__ x
         epoch = *comm.epoch;
         if (comm.xchg) {
             // consumer-side exchange: this block ships its row of the local partial to the peers, then waits for theirs
-            for (int i = threadIdx.x; i < dim; i += blockDim.x) { const float v = ld_as_float<TIn>(xr, i); comm_xchg_put<1>(comm, epoch, (size_t)r * ldx + i, &v); }
-            comm_xchg_sync(comm, epoch, r);
+            for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+                const float v = ld_as_float<TIn>(xr, i);
+                if (comm.xchg == 2) comm_ll_put<1>(comm, epoch, (size_t)r * ldx + i, &v);
+                else comm_xchg_put<1>(comm, epoch, (size_t)r * ldx + i, &v);
+            }
+            if (comm.xchg != 2) comm_xchg_sync(comm, epoch, r);
         } else {
             comm_wait(comm, epoch);
         }
     }
     float ss = 0.f;
     for (int i = threadIdx.x; i < dim; i += blockDim.x) {
-        float v = comm.nranks ? (comm.xchg ? comm_xchg_get(comm, epoch, (size_t)r * ldx + i, ld_as_float<TIn>(xr, i)) : comm_reduce(comm, epoch, (size_t)r * ldx + i))
-                              : ld_as_float<TIn>(xr, i);
+        float v;
+        if (comm.nranks && comm.xchg == 2) { const float own = ld_as_float<TIn>(xr, i); comm_ll_get<1>(comm, epoch, (size_t)r * ldx + i, &own, &v); }
+        else v = comm.nranks ? (comm.xchg ? comm_xchg_get(comm, epoch, (size_t)r * ldx + i, ld_as_float<TIn>(xr, i)) : comm_reduce(comm, epoch, (size_t)r * ldx + i))
+                             : ld_as_float<TIn>(xr, i);
         if (ADD) {
             v += resid[(size_t)r * ldr + i];
             resid[(size_t)r * ldr + i] = v;
@@ -518,8 +524,12 @@ __global__ void mhc_contract_norm_kernel(bf16* __restrict__ out, const float* __
     if (comm.nranks) {
         epoch = *comm.epoch;
         if (comm.xchg) {
-            for (int h = threadIdx.x; h < hidden; h += blockDim.x) { const float v = x[(size_t)r * hidden + h]; comm_xchg_put<1>(comm, epoch, (size_t)r * hidden + h, &v); }
-            comm_xchg_sync(comm, epoch, r);
+            for (int h = threadIdx.x; h < hidden; h += blockDim.x) {
+                const float v = x[(size_t)r * hidden + h];
+                if (comm.xchg == 2) comm_ll_put<1>(comm, epoch, (size_t)r * hidden + h, &v);
+                else comm_xchg_put<1>(comm, epoch, (size_t)r * hidden + h, &v);
+            }
+            if (comm.xchg != 2) comm_xchg_sync(comm, epoch, r);
         } else {
             comm_wait(comm, epoch);
         }
@@ -534,9 +544,12 @@ __global__ void mhc_contract_norm_kernel(bf16* __restrict__ out, const float* __
     }
     float ss = 0.f;
     for (int h = threadIdx.x; h < hidden; h += blockDim.x) {
-        float a = pm * (comm.nranks ? (comm.xchg ? comm_xchg_get(comm, epoch, (size_t)r * hidden + h, x[(size_t)r * hidden + h])
-                                                  : comm_reduce(comm, epoch, (size_t)r * hidden + h))
-                                    : x[(size_t)r * hidden + h]);
+        float xs_;
+        if (comm.nranks && comm.xchg == 2) { const float own = x[(size_t)r * hidden + h]; comm_ll_get<1>(comm, epoch, (size_t)r * hidden + h, &own, &xs_); }
+        else xs_ = comm.nranks ? (comm.xchg ? comm_xchg_get(comm, epoch, (size_t)r * hidden + h, x[(size_t)r * hidden + h])
+                                            : comm_reduce(comm, epoch, (size_t)r * hidden + h))
+                               : x[(size_t)r * hidden + h];
+        float a = pm * xs_;
         for (int i = 0; i < n; ++i) a += cw[i] * rp[(size_t)i * hidden + h];
         a /= (float)n;
         row[h] = a;

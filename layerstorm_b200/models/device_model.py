@@ -99,8 +99,9 @@ MHC_CLUSTER = os.environ.get("LSB_MHC_CLUSTER", "1") not in ("", "0")
 # ablation switches of the two folds of the cluster kernel (router behind, MoE combine in front)
 MHC_FOLD_ROUTER = os.environ.get("LSB_MHC_FOLD_ROUTER", "0") not in ("", "0")
 MHC_FOLD_COMBINE = os.environ.get("LSB_MHC_FOLD_COMBINE", "0") not in ("", "0")
-# LSB_COMM_XCHG=0: few-row steps keep the producer-side push of the fused all-reduce
-COMM_XCHG = os.environ.get("LSB_COMM_XCHG", "1") not in ("", "0")
+# LSB_COMM_XCHG: how few-row steps do the fused all-reduce - 0 the producer's last block pushes the partial, 1 the consuming kernel
+# exchanges it with one flag per CTA, 2 (default) the consuming kernel exchanges flag-in-data words (no fence, no flag, no barrier)
+COMM_XCHG = int(os.environ.get("LSB_COMM_XCHG", "2") or 0)
 
 
 def _dequant_q4k(raw: torch.Tensor, N: int, K: int) -> torch.Tensor:
@@ -1006,7 +1007,10 @@ class DeviceModel:
         if self.comm is not None:
             # fewer than 8 rows: the kernel that consumes a cross-rank sum exchanges the partials itself (one flag per CTA) instead of
             # the producer's last block copying them to every peer; needs the cluster form of the hyper-connection pass where there is one
-            self.comm.struct.xchg = int(COMM_XCHG and self._fused and R < 8 and self.dcp is None and (not cfg.mhc or self._mhc_cluster_ok()))
+            xchg = COMM_XCHG if (self._fused and R < 8 and self.dcp is None and (not cfg.mhc or self._mhc_cluster_ok())) else 0
+            if xchg == 2 and R * H > self.comm.ll_cap:
+                xchg = 1
+            self.comm.struct.xchg = xchg
         if self.dcp is not None:
             nat.call("lsb_dcp_rows", ws.row_pos, ws.row_len, ws.row_store, ws.row_len_local, R, self.dcp.chunk, self.tp_size, self.tp_rank)
         if cfg.mhc:

@@ -18,12 +18,14 @@ import torch
 import torch.distributed as dist
 
 K_MAX_RANKS = 8
+LL_ELEMS = 65536     # elements per slot of the flag-in-data exchange buffers (8 rows of hidden 8192), see PeerComm
 
 
 class PeerCommStruct(ctypes.Structure):
     _fields_ = [("nranks", ctypes.c_int), ("rank", ctypes.c_int), ("cap", ctypes.c_longlong),
                 ("recv", ctypes.c_void_p * K_MAX_RANKS), ("flags", ctypes.c_void_p * K_MAX_RANKS),
-                ("epoch", ctypes.c_void_p), ("cta_done", ctypes.c_void_p), ("err", ctypes.c_void_p), ("xchg", ctypes.c_int)]
+                ("epoch", ctypes.c_void_p), ("cta_done", ctypes.c_void_p), ("err", ctypes.c_void_p), ("xchg", ctypes.c_int),
+                ("ll_cap", ctypes.c_longlong), ("ll", ctypes.c_void_p * K_MAX_RANKS)]
 
 
 class SymmetricBuffer:
@@ -80,16 +82,21 @@ class PeerComm:
         recv_bytes = 2 * self.world * cap_floats * 4
         # producer-push flags [2][8] + consumer-exchange flags [2][8 ranks][128 CTAs] (see csrc/kernels/comm.cuh)
         flag_bytes = (2 * K_MAX_RANKS + 2 * K_MAX_RANKS * 128) * 4
-        self.buf = SymmetricBuffer(recv_bytes + flag_bytes, device, group)
+        # flag-in-data buffers of the few-row exchange: [2 parities][ranks][ll_cap] words of (value, epoch), 8 bytes each
+        self.ll_cap = (min(cap_floats, LL_ELEMS) + 3) // 4 * 4
+        ll_bytes = 2 * self.world * self.ll_cap * 8
+        self.buf = SymmetricBuffer(recv_bytes + flag_bytes + ll_bytes, device, group)
         self.local_state = torch.zeros(16, dtype=torch.int32, device=device)   # epoch, cta_done, err
         s = PeerCommStruct()
         s.nranks, s.rank, s.cap = self.world, self.rank, cap_floats
         for p in range(self.world):
             s.recv[p] = self.buf.ptrs[p]
             s.flags[p] = self.buf.ptrs[p] + recv_bytes
+            s.ll[p] = self.buf.ptrs[p] + recv_bytes + flag_bytes
         base = self.local_state.data_ptr()
         s.epoch, s.cta_done, s.err = base, base + 4, base + 8
         s.xchg = 0
+        s.ll_cap = self.ll_cap
         self.struct = s
 
     @property

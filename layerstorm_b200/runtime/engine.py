@@ -262,18 +262,67 @@ class Engine:
         self.model.block_table[s.slot].copy_(self.h_bt[s.slot], non_blocking=True)
         self.h2d_bytes += self.max_pages * 4
 
+    # ------------------------------------------------------------------ recurrent-state anchors
+    def anchor(self, sid: int):
+        """Snapshot the recurrent state of a sequence (KDA state and convolution history, the indexer's open-pool tail) at its
+        current frontier.  ``rewind`` to a later-or-equal position restores the snapshot and replays the tokens after it, which is
+        how a partly rejected speculative round is undone on models whose state cannot be un-applied (the reference's KDA anchor
+        snapshot / restore, src/daemon/ipc_protocol.h:214-216).  One anchor per engine (requests are served one at a time)."""
+        s = self.seqs[sid]
+        m = self.model
+        if not hasattr(self, "_anchor_buf"):
+            self._anchor_buf = {"state": {i: torch.empty_like(t[0]) for i, t in m.kda_state.items()},
+                                "conv": {i: torch.empty_like(t[0]) for i, t in m.kda_conv.items()},
+                                "tail": {i: torch.empty_like(t[0]) for i, t in m.idx_tail.items()}}
+        with torch.cuda.stream(self.stream):
+            for key, src in (("state", m.kda_state), ("conv", m.kda_conv), ("tail", m.idx_tail)):
+                for i, t in src.items():
+                    self._anchor_buf[key][i].copy_(t[s.slot], non_blocking=True)
+        self._anchor_of = (sid, s.length)
+
+    def _restore_anchor(self, s: SequenceState):
+        m = self.model
+        for key, dst in (("state", m.kda_state), ("conv", m.kda_conv), ("tail", m.idx_tail)):
+            for i, t in dst.items():
+                t[s.slot].copy_(self._anchor_buf[key][i], non_blocking=True)
+
+    def _ws_rows(self, R: int) -> Workspace:
+        """Cached workspace for verify / replay steps of R consecutive rows of one sequence (logits for every row)."""
+        if not hasattr(self, "ws_verify"):
+            self.ws_verify: Dict[int, Workspace] = {}
+        if R not in self.ws_verify:
+            self.ws_verify[R] = Workspace(self.model, R, R, self.max_ctx)
+        return self.ws_verify[R]
+
     def rewind(self, sid: int, length: int):
-        """Roll the committed frontier back (speculative-verify rejection).  Only valid for models
-        without recurrent (KDA) state, whose state cannot be un-applied."""
+        """Roll the committed frontier back (speculative-verify rejection).  Models with recurrent (KDA) state need an anchor
+        taken at or before ``length`` (:meth:`anchor`): the state is restored from it and the tokens between the anchor and
+        ``length`` are replayed."""
         if getattr(self.model, "dcp", None) is not None:
             raise NotImplementedError("not available with a sharded KV cache")
         s = self.seqs[sid]
-        if any(self.cfg.is_kda_layer(i) for i in range(self.cfg.n_layers)) and length < s.length:
-            raise RuntimeError("rewind of a recurrent-state sequence is refused")
+        if length == s.length:
+            return
+        replay: List[int] = []
+        if self.has_recurrent_state and length < s.length:
+            a_sid, a_len = getattr(self, "_anchor_of", (None, -1))
+            if a_sid != sid or a_len > length or a_len < 0:
+                raise RuntimeError("rewind of a recurrent-state sequence needs an anchor at or before the target position")
+            replay = list(s.tokens[a_len:length])
+            length_after = length
+            length = a_len
+            with torch.cuda.stream(self.stream):
+                self._restore_anchor(s)
         s.length = length
+        del_tokens = s.tokens[length:]
         del s.tokens[length:]
         self.pa.rewind(s.slot, length)
         s.pages = self.pa.pages(s.slot)
+        if replay:
+            # teacher-forced replay of the accepted tokens rebuilds the recurrent state (and rewrites the same KV rows)
+            self.forward_rows(sid, replay, commit=True, want_logits=False)
+            assert s.length == length_after
+        del del_tokens
 
     def _ensure_pages(self, s: SequenceState, new_len: int):
         if (new_len + self.page - 1) // self.page > self.max_pages:
@@ -363,12 +412,27 @@ class Engine:
                 logits = ws.logits[0].float().cpu()
         return (nxt, logits) if want_logits else nxt
 
-    def forward_rows(self, sid: int, tokens: Sequence[int], commit: bool = True) -> torch.Tensor:
+    def sample_last_prefill(self, sid: int, sample) -> int:
+        """Draw the first generated token of a sampled request from the logits the sequence's prefill left in the prefill
+        workspace (the last prompt position), on the device."""
+        ws = self.ws_prefill
+        s = self.seqs[sid]
+        temperature, top_k, top_p, seed = sample
+        with torch.cuda.stream(self.stream):
+            offs = torch.tensor([s.length - 1], dtype=torch.int64, device=self.dev)
+            nat.call("lsb_sample", ws.logits, ws.logits.shape[1], 1, ws.logits.shape[1], float(temperature), int(top_k), float(top_p),
+                     int(seed) & 0x7FFFFFFFFFFFFFFF, offs, ws.out_tok)
+            self.h_out[:1].copy_(ws.out_tok[:1], non_blocking=True)
+            self.d2h_bytes += 4
+            self.stream.synchronize()
+        return int(self.h_out[0])
+
+    def forward_rows(self, sid: int, tokens: Sequence[int], commit: bool = True, want_logits: bool = True) -> Optional[torch.Tensor]:
         """Run consecutive rows of one sequence and return logits for ALL rows (verify shape)."""
         self._require_hot(sid)
         s = self.seqs[sid]
         R = len(tokens)
-        ws = Workspace(self.model, R, R, self.max_ctx)
+        ws = self._ws_rows(R)
         with torch.cuda.stream(self.stream):
             self._ensure_pages(s, s.length + R)
             rows = [(int(t), s.slot, s.length + j) for j, t in enumerate(tokens)]
@@ -382,11 +446,64 @@ class Engine:
         if commit:
             s.length += R
             s.tokens.extend(int(t) for t in tokens)
+        else:
+            self.pa.rewind(s.slot, s.length)
+            s.pages = self.pa.pages(s.slot)
+        if not want_logits:
+            return None
+        self.d2h_bytes += R * ws.logits.shape[1] * 4
         return ws.logits[:R].float().cpu()
 
-    def decode(self, sids: Sequence[int], tokens: Sequence[int], return_logits: bool = False):
+    def verify_greedy(self, sid: int, tok: int, draft: Sequence[int]):
+        """One speculative round decided on the device: feeds ``[tok] + draft`` as consecutive rows, takes the target's arg-max at
+        every row, counts the agreeing draft prefix with ``lsb_spec_verify`` and reads back 8 bytes: (accepted draft tokens, the
+        target's own next token).  ``tok`` and the accepted tokens are committed; on a partial acceptance the rest is rolled back
+        (recurrent models: anchor + replay).  Returns ``(n_accepted, next_token)``."""
+        self._require_hot(sid)
+        s = self.seqs[sid]
+        draft = [int(t) for t in draft]
+        rows_tok = [int(tok)] + draft
+        R, gamma = len(rows_tok), len(draft)
+        ws = self._ws_rows(R)
+        if not hasattr(ws, "verify_out"):
+            ws.verify_out = torch.zeros(2, dtype=torch.int32, device=self.dev)
+        ca = getattr(self.model, "comm_amax", None)
+        if ca is not None and 2 * R > ca.cap:
+            raise RuntimeError(f"the arg-max exchange buffer holds {ca.cap // 2} rows, the verify step has {R}")
+        if self.has_recurrent_state and gamma > 0:
+            self.anchor(sid)
+        with torch.cuda.stream(self.stream):
+            self._ensure_pages(s, s.length + R)
+            rows = [(t, s.slot, s.length + j) for j, t in enumerate(rows_tok)]
+            self._stage(ws, rows, [(0, R, s.slot)])
+            n0 = nat.launch_count()
+            self.model.forward(ws, R, 1, 0, R)
+            self.model.argmax(ws, R)
+            # rows 1..gamma of the staged token ids ARE the draft; out_tok[k] is the target's choice after row k
+            nat.call("lsb_spec_verify", ws.tok[1:] if gamma else ws.tok, ws.out_tok, gamma, ws.verify_out)
+            self.kernel_launches += nat.launch_count() - n0
+            self.h_out[:2].copy_(ws.verify_out, non_blocking=True)
+            self.d2h_bytes += 8
+            self._queue_error_readback()
+            self.stream.synchronize()
+            self._check_errors()
+        n_acc, nxt = int(self.h_out[0]), int(self.h_out[1])
+        s.length += R
+        s.tokens.extend(rows_tok)
+        if n_acc < gamma:
+            self.rewind(sid, s.length - (gamma - n_acc))
+        return n_acc, nxt
+
+    @property
+    def supports_device_sampling(self) -> bool:
+        """Whether ``decode(..., sample=...)`` can draw the next token on the device (needs the whole vocabulary on this GPU)."""
+        return self.model.tp_size == 1
+
+    def decode(self, sids: Sequence[int], tokens: Sequence[int], return_logits: bool = False, sample=None):
         """One decode step for a batch of sequences: feeds ``tokens[i]`` at the frontier of
-        ``sids[i]`` and returns the greedy next token per sequence."""
+        ``sids[i]`` and returns the next token per sequence - the arg-max, or with ``sample = (temperature, top_k, top_p,
+        seed)`` a draw from the filtered distribution made on the device (Philox stream keyed by the seed and the token's
+        position, so a fixed seed reproduces the trajectory); either way only 4 bytes per row come back."""
         B = len(sids)
         for sid in sids:
             self._require_hot(sid)
@@ -409,6 +526,14 @@ class Engine:
                 self.model.forward(ws, B, B, 0, B)
                 self.model.argmax(ws, B)
                 self.kernel_launches += nat.launch_count() - n0
+            if sample is not None:
+                if not self.supports_device_sampling:
+                    raise RuntimeError("device sampling needs the full vocabulary on one GPU")
+                temperature, top_k, top_p, seed = sample
+                offs = ws.row_pos[:B].to(torch.int64)
+                nat.call("lsb_sample", ws.logits, ws.logits.shape[1], B, ws.logits.shape[1], float(temperature), int(top_k), float(top_p),
+                         int(seed) & 0x7FFFFFFFFFFFFFFF, offs, ws.out_tok)
+                self.kernel_launches += 1
             self.h_out[:B].copy_(ws.out_tok[:B], non_blocking=True)
             self.d2h_bytes += 4 * B
             self._queue_error_readback()

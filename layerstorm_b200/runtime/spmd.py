@@ -14,7 +14,8 @@ from typing import Any, Optional
 
 # engine methods that change device or sequence state and therefore must run on every rank, in the same order
 MIRRORED = ("create_sequence", "free_sequence", "fork_sequence", "rewind", "prefill", "forward_rows", "decode", "generate",
-            "enable_kv_tiering", "hibernate", "resume", "configure_expert_cache")
+            "enable_kv_tiering", "hibernate", "resume", "configure_expert_cache", "verify_greedy", "anchor", "sample_last_prefill",
+            "clear_device_errors")
 _STOP = "__stop__"
 
 

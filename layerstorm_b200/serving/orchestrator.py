@@ -274,7 +274,10 @@ class Orchestrator:
             sid = self._with_pool_evict_retry(req, eng.create_sequence)
             cached = 0
         st.cached_tokens = cached
-        need_logits = (not p.greedy) or p.logprobs > 0 or req.logit_mask is not None
+        # sampled requests without a logit mask or logprobs draw on the device when the engine can (4 bytes per token come back
+        # instead of the vocabulary's logits)
+        dev_sample = (not p.greedy) and p.logprobs == 0 and req.logit_mask is None and getattr(eng, "supports_device_sampling", False)
+        need_logits = ((not p.greedy) and not dev_sample) or p.logprobs > 0 or req.logit_mask is not None
         try:
             # every attempt feeds what is still missing (the engine's prefill reserves its pages up front and fails before it
             # commits anything, and even an engine that failed mid-prompt is continued, never re-fed)
@@ -283,9 +286,14 @@ class Orchestrator:
             tok, logits = out if need_logits else (out, None)
             if need_logits:
                 tok = self._pick(req, logits, len(prompt))
+            elif dev_sample:
+                # the prompt's last position: rewind one token and let the sampled decode step produce the first token
+                tok = self._first_sampled_token(req, sid, prompt)
             if self._emit(req, tok, logits):
                 return self._finish(req, req.finish_reason or "cancelled")
-            if self.gamma > 0 and not need_logits:
+            if dev_sample:
+                self._decode_plain(req, sid, tok, False, sample=self._sample_args(req))
+            elif self.gamma > 0 and not need_logits:
                 self._decode_speculative(req, sid, tok)
             elif self.gamma > 0 and not getattr(eng, "has_recurrent_state", False):
                 self._decode_speculative_logits(req, sid, tok)
@@ -295,11 +303,24 @@ class Orchestrator:
         finally:
             eng.free_sequence(sid)
 
-    def _decode_plain(self, req: InferenceRequest, sid: int, tok: int, need_logits: bool):
+    def _sample_args(self, req: InferenceRequest):
+        p = req.params
+        return (p.temperature, p.top_k, p.top_p, p.seed if p.seed is not None else 0)
+
+    def _first_sampled_token(self, req: InferenceRequest, sid: int, prompt: List[int]) -> int:
+        """Device-sampled requests: the prefill returned the greedy token of the last prompt position; the sampled one is drawn
+        from that position's logits, which are still in the engine's prefill workspace."""
+        eng = self.engine
+        return eng.sample_last_prefill(sid, self._sample_args(req))
+
+    def _decode_plain(self, req: InferenceRequest, sid: int, tok: int, need_logits: bool, sample=None):
         eng = self.engine
         while True:
             t0 = time.time()
-            if need_logits:
+            if sample is not None:
+                tok = self._with_pool_evict_retry(req, lambda: eng.decode([sid], [tok], sample=sample))[0]
+                logits = None
+            elif need_logits:
                 outs, lg = self._with_pool_evict_retry(req, lambda: eng.decode([sid], [tok], return_logits=True))
                 logits = lg[0]
                 tok = self._pick(req, logits, len(req.prompt_ids) + len(req.output_ids))
@@ -359,7 +380,8 @@ class Orchestrator:
         target forward over [tok, d_0..d_{g-1}] gives the target's argmax at every position; the longest
         agreeing prefix is accepted plus the target's own next token (correction or bonus)."""
         eng = self.engine
-        recurrent = getattr(eng, "has_recurrent_state", False)
+        dev_verify = hasattr(eng, "verify_greedy")            # decides on the device, rolls recurrent state back through anchors
+        recurrent = getattr(eng, "has_recurrent_state", False) and not dev_verify
         while True:
             if recurrent or not self.governor.should_draft():
                 t0 = time.time()
@@ -373,15 +395,19 @@ class Orchestrator:
             draft = list(self.draft.propose(ctx, self.gamma))[: self.gamma]
             base_len = eng.seq_len(sid)
             rows = [tok] + draft
-            logits = self._with_pool_evict_retry(req, lambda: eng.forward_rows(sid, rows, commit=True))
-            target = [int(t) for t in torch.argmax(logits, -1)]
-            n_acc = 0
-            while n_acc < len(draft) and draft[n_acc] == target[n_acc]:
-                n_acc += 1
-            eng.rewind(sid, base_len + 1 + n_acc)          # keep tok + the accepted draft tokens
+            if dev_verify:
+                n_acc, nxt = self._with_pool_evict_retry(req, lambda: eng.verify_greedy(sid, tok, draft))
+            else:
+                logits = self._with_pool_evict_retry(req, lambda: eng.forward_rows(sid, rows, commit=True))
+                target = [int(t) for t in torch.argmax(logits, -1)]
+                n_acc = 0
+                while n_acc < len(draft) and draft[n_acc] == target[n_acc]:
+                    n_acc += 1
+                nxt = target[n_acc]
+                eng.rewind(sid, base_len + 1 + n_acc)          # keep tok + the accepted draft tokens
             req.stats.spec_rounds += 1
             req.stats.spec_accepted += n_acc
-            new = draft[:n_acc] + [target[n_acc]]
+            new = draft[:n_acc] + [nxt]
             self.governor.observe_round(len(new), (time.time() - t0) * 1e3)
             if hasattr(self.draft, "feedback"):
                 self.draft.feedback(len(draft), n_acc)

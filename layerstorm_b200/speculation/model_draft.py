@@ -67,8 +67,13 @@ class EngineDraft:
         while common < lim and want[common] == self.fed[common]:
             common += 1
         if common < len(self.fed):
-            eng.rewind(self.sid, common)
-            self.fed = self.fed[:common]
+            if getattr(eng, "has_recurrent_state", False):
+                # recurrent draft state cannot be cut at an arbitrary earlier position: start the draft sequence over
+                eng.free_sequence(self.sid)
+                self.sid, self.fed, common = eng.create_sequence(), [], 0
+            else:
+                eng.rewind(self.sid, common)
+                self.fed = self.fed[:common]
         if len(want) > common:
             eng.prefill(self.sid, want[common:], want_logits=False)
             self.fed = want
@@ -83,6 +88,8 @@ class EngineDraft:
             eng, sid = self.engine, self.sid
             tok = int(context[-1])
             out: List[int] = []
+            if getattr(eng, "has_recurrent_state", False) and hasattr(eng, "anchor"):
+                eng.anchor(sid)            # the drafted tokens are rolled back through this snapshot
             for _ in range(g):
                 tok = int(eng.decode([sid], [tok])[0])
                 out.append(tok)

@@ -86,3 +86,51 @@ def test_prefix_cache_hit_on_the_gpu_engine():
     req = InferenceRequest("cold", base + [10, 11], SamplingParams(max_tokens=6, ignore_eos=True))
     cold.submit_request(req); cold.step()
     assert req.output_ids == outs[2][0]                          # cache on == cache off
+
+
+def test_speculation_on_a_recurrent_state_model_is_lossless_and_decided_on_the_device():
+    """glm5_next (KDA layers): a speculative round is verified on the device (arg-max per row + prefix count, 8 bytes back) and a
+    partly rejected round is undone through the recurrent-state anchor + replay.  Tokens equal plain greedy decoding whatever
+    the draft proposes; with a perfect draft every round accepts all drafted tokens."""
+    from layerstorm_b200.serving.orchestrator import InferenceRequest, Orchestrator, SamplingParams
+    from layerstorm_b200.speculation import EngineDraft
+    cfg, target = _engine("tiny-glm5-next", seed=3, use_graph=False)
+    assert target.has_recurrent_state
+    _, same = _engine("tiny-glm5-next", seed=3, use_graph=False)
+    _, other = _engine("tiny-glm5-next", seed=4, use_graph=False)
+    prompt = torch.randint(0, cfg.vocab, (40,), generator=torch.Generator().manual_seed(1)).tolist()
+    ref = InferenceRequest("ref", list(prompt), SamplingParams(max_tokens=24, ignore_eos=True))
+    o = Orchestrator(target)
+    o.submit_request(ref); o.step()
+    for name, de in (("same", same), ("other", other)):
+        d2h0 = target.d2h_bytes
+        req = InferenceRequest(name, list(prompt), SamplingParams(max_tokens=24, ignore_eos=True))
+        s = Orchestrator(target, draft=EngineDraft(de, 4), speculation_depth=4)
+        s.submit_request(req); s.step()
+        assert req.error is None, req.error
+        assert req.output_ids == ref.output_ids, name
+        assert req.stats.spec_rounds > 0
+        assert target.d2h_bytes - d2h0 < 64 * (req.stats.spec_rounds + 30), "verify rounds must not copy logits to the host"
+        if name == "same":
+            assert req.stats.spec_accepted >= 3 * req.stats.spec_rounds - 4
+        else:
+            assert req.stats.spec_accepted < 4 * req.stats.spec_rounds           # some round was rolled back through the anchor
+
+
+def test_sampled_requests_draw_on_the_device_and_repeat_for_a_fixed_seed():
+    from layerstorm_b200.serving.orchestrator import InferenceRequest, Orchestrator, SamplingParams
+    cfg, eng = _engine("tiny-glm5-next", seed=6, use_graph=True)
+    orch = Orchestrator(eng)
+    prompt = torch.randint(0, cfg.vocab, (20,), generator=torch.Generator().manual_seed(4)).tolist()
+    outs = []
+    for seed in (11, 11, 12):
+        d2h0 = eng.d2h_bytes
+        req = InferenceRequest(f"s{seed}", list(prompt), SamplingParams(max_tokens=16, ignore_eos=True, temperature=1.0, top_k=40, top_p=0.95, seed=seed))
+        orch.submit_request(req); orch.step()
+        assert req.error is None, req.error
+        assert eng.d2h_bytes - d2h0 < 16 * 64, "sampled decode must not copy the vocabulary's logits to the host"
+        outs.append(req.output_ids)
+    assert outs[0] == outs[1] and outs[0] != outs[2] and len(outs[0]) == 16
+    greedy = InferenceRequest("g", list(prompt), SamplingParams(max_tokens=16, ignore_eos=True))
+    orch.submit_request(greedy); orch.step()
+    assert greedy.output_ids != outs[0]

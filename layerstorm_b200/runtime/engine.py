@@ -84,10 +84,44 @@ class Engine:
         self.h_bt = torch.zeros(max_seqs, self.max_pages, dtype=torch.int32).pin_memory()
         self.h_out = torch.zeros(Rmax, dtype=torch.int32).pin_memory()
         self.stream = torch.cuda.Stream(device=self.dev)
+        self.vram_plan = self._carve_report()
         self.h_err = torch.zeros(8, dtype=torch.int32).pin_memory()      # error words of the step, read back with the sampled tokens
         self.h2d_bytes = 0
         self.d2h_bytes = 0
         self.kernel_launches = 0
+
+    # ------------------------------------------------------------------ boot-time memory carve
+    def _carve_report(self) -> dict:
+        """The GPU's memory as the native planner carves it for what this engine has just allocated (weights, KV pages, indexer
+        pages, recurrent state, step workspaces, expert slots): logged once at boot and kept as ``engine.vram_plan``.  The planner
+        raises when a region does not fit, which turns an allocation that only succeeded by eating the safety margin into a
+        visible boot error.  Reference: VramAllocator's boot carve log (src/core/memory/vram_allocator.h:19)."""
+        import logging
+        m, cfg = self.model, self.cfg
+        if self.dev.type != "cuda":
+            return {}
+        free_b, total_b = torch.cuda.mem_get_info(self.dev)
+        kv_page = sum(t[0].numel() * t.element_size() for t in m.kv_cache.values())
+        idx_page = sum(t[0].numel() * t.element_size() for t in m.idx_cache.values())
+        rec_seq = sum(t[0].numel() * t.element_size() for t in list(m.kda_state.values()) + list(m.kda_conv.values()) + list(m.idx_tail.values()))
+        arenas = [L["arena"] for L in m.layers if L.get("arena") is not None]
+        slot_b = arenas[0].ef.stride if arenas else 0
+        slots = sum(a.n_slots for a in arenas)
+        weights = m.weight_bytes() - slot_b * slots
+        try:
+            plan = rt.vram_plan(total_b, weights, workspace_bytes=256 << 20, kv_bytes_per_page=kv_page, kv_pages=self.num_pages, spec_pool_fraction=0.0,
+                                indexer_bytes_per_page=idx_page, indexer_pages=self.num_pages if idx_page else 0,
+                                recurrent_bytes_per_seq=rec_seq, recurrent_seqs=self.max_seqs, expert_slot_bytes=slot_b, expert_slots_wanted=slots,
+                                stable_zone_fraction=1.0, safety_bytes=256 << 20)
+        except rt.NativeError as e:
+            logging.getLogger("layerstorm_b200.engine").warning("VRAM carve: %s (device has %.1f GiB, %.1f GiB free after allocation)",
+                                                                e, total_b / 2 ** 30, free_b / 2 ** 30)
+            return {"error": str(e)}
+        plan["free_after_alloc_bytes"], plan["total_bytes"] = free_b, total_b
+        gib = {k: round(v["size"] / 2 ** 30, 2) for k, v in plan["regions"].items() if v["size"]}
+        logging.getLogger("layerstorm_b200.engine").info("VRAM carve (GiB): %s; %d KV pages of %d tokens, %d expert slots, %.1f GiB free",
+                                                         gib, self.num_pages, self.page, plan["expert_stable_slots"], free_b / 2 ** 30)
+        return plan
 
     # ------------------------------------------------------------------ device error words
     def _error_sources(self):

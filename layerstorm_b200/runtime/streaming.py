@@ -2,14 +2,19 @@
 
 Each MoE layer keeps ``slots_per_layer`` expert slots in HBM; every expert's slot image lives in a
 pinned host store.  Per layer and step:
-  1. the routed expert ids come back to the host (one small D2H copy, the only host round trip),
+  1. the routed expert ids come back to the host through a pinned buffer (the only host wait of the layer),
   2. missing experts are fetched host->device with pinned ``cudaMemcpyAsync`` on a side stream -
      what is fetched when is decided by the native ``TransferEngine`` (de-duplication, priorities,
      in-flight waterline) and where it lands by the native ``ExpertCache`` (impact-weighted LRU,
      locked while in use),
-  3. the compute stream waits on the copies' event and runs the expert kernels over the resident
-     experts; when a step needs more experts than the layer has slots (prefill chunks) this repeats
-     in waves, and the combine runs once at the end.
+  3. the copies are gated on the DEVICE: the side stream records an event after the wave's copies, the compute stream
+     waits for it (``cudaStreamWaitEvent``; the reference's ``record_h2d_barrier``, src/core/transfer/transfer_engine.h:159,223)
+     and runs the expert kernels; the side stream in turn waits for the kernels' event before it overwrites a slot.  The host
+     does not wait for a copy.  When a step needs more experts than the layer has slots (prefill chunks) this repeats in
+     waves, and the combine runs once at the end.
+With ``fetch_deadline_ms`` set, the host polls the wave's copy event up to the deadline; experts whose copies have not
+landed by then are left out of this step (the step finishes DEGRADED, the combine skips their slots) and are ready for the
+next one - the reference's deadline -> degraded -> retry (src/daemon/moe/moe_progressive.cpp:579-586).
 Prefetch: the experts a step used at layer i are requested for layer i+1 at low priority while
 layer i computes ("same-index" heuristic), and dropped if the router disagrees.
 Reference behaviour: progressive FETCH_AND_RUN_MOE waves with an explicit evict map
@@ -27,7 +32,8 @@ from . import native as rt
 
 
 class ExpertStreamer:
-    def __init__(self, model, slots_per_layer: int, policy: str = "impact_weighted_lru", waterline: int = 4, prefetch: bool = False):
+    def __init__(self, model, slots_per_layer: int, policy: str = "impact_weighted_lru", waterline: int = 4, prefetch: bool = False,
+                 fetch_deadline_ms: Optional[float] = None, numa_node: int = -1):
         """Takes a fully resident ``DeviceModel`` (every MoE layer's arena holds all of this rank's experts), moves
         the slot images to pinned host memory and shrinks every arena to ``slots_per_layer`` slots."""
         from ..models.device_model import ExpertArena
@@ -40,8 +46,13 @@ class ExpertStreamer:
         self.trace = open(os.environ["LS_ROUTING_TRACE"], "w") if os.environ.get("LS_ROUTING_TRACE") else None
         self.trace_step = 0
         self.weighted = False                                    # True once configure_eviction() has installed the weighted score
-        self.stats = {"hits": 0, "misses": 0, "waves": 0, "bytes_h2d": 0}
+        self.stats = {"hits": 0, "misses": 0, "waves": 0, "bytes_h2d": 0, "degraded_steps": 0, "late_experts": 0, "host_waits": 0}
         self._issued: List[tuple] = []
+        self.fetch_deadline_ms = fetch_deadline_ms
+        self._copy_done = lambda ev: ev.query()                  # tests replace this to stall a completion on the host side
+        self._late: List[tuple] = []                              # copies that missed a deadline: (event, token, layer, expert, slot)
+        self._slot_free_ev = None                                 # compute-stream event after the last expert kernels that read the slots
+        self.h_ids = None
         cfg = model.cfg
         E_total = cfg.n_routed + cfg.n_shared
         for i, L in enumerate(model.layers):
@@ -50,16 +61,32 @@ class ExpertStreamer:
             old: ExpertArena = L["arena"]
             so = old.slot_of.cpu().tolist()
             mine = [e for e in range(E_total) if so[e] >= 0]
-            host = torch.empty(len(mine), old.ef.stride, dtype=torch.uint8).pin_memory()
+            # backing store: the native host arena (NUMA-bound slab, page-locked with cudaHostRegister); plain pinned memory if the
+            # slab cannot be mapped or registered
+            harena = None
+            try:
+                harena = rt.HostArena(old.ef.stride, len(mine), numa_node=numa_node)
+                if not harena.pin():
+                    harena = None
+            except (MemoryError, OSError):
+                harena = None
+            host = harena.tensor() if harena is not None else torch.empty(len(mine), old.ef.stride, dtype=torch.uint8).pin_memory()
             host_row = {}
             for r, e in enumerate(mine):
-                host[r].copy_(old.data[so[e]])
-                host_row[e] = r
+                if harena is not None:
+                    slot_h, _ = harena.begin_load(i, e)
+                    host[slot_h].copy_(old.data[so[e]])
+                    harena.finish_load(slot_h, True)
+                    host_row[e] = slot_h
+                else:
+                    host[r].copy_(old.data[so[e]])
+                    host_row[e] = r
             n = min(slots_per_layer, len(mine))
             assert n >= min(len(mine), cfg.top_k + cfg.n_shared), "the layer needs room for one token's experts"
             new = ExpertArena(old.ef, n, E_total, self.dev)
             L["arena"] = new
-            self.layers[i] = {"host": host, "host_row": host_row, "cache": rt.ExpertCache(0, n, policy), "arena": new,
+            self.layers[i] = {"host": host, "host_row": host_row, "host_arena": harena, "cache": rt.ExpertCache(0, n, policy), "arena": new,
+                              "expert_stats": rt.ExpertStats(E_total),
                               "slot_of_host": torch.full((E_total,), -1, dtype=torch.int32).pin_memory(),
                               "present": torch.zeros(E_total, dtype=torch.int32, device=self.dev), "mine": set(mine), "pending": {}}
             del old
@@ -93,31 +120,74 @@ class ExpertStreamer:
             tok = self.te.next_to_issue(0, now)
             if not tok:
                 if self.te.queued(0) and self.te.in_flight(0):
-                    self._settle()                               # waterline reached: drain, then continue issuing
-                    continue
-                break
+                    before = self.te.in_flight(0)
+                    self._settle()                               # waterline reached: gate what is out, then continue issuing
+                    if self.te.in_flight(0) < before:
+                        continue
+                break                                            # nothing more to issue (or only stalled copies are in flight)
             info = self.te.info(tok)
             lst = self.layers[info["layer"]]
             e, slot = lst["pending"][tok]
             with torch.cuda.stream(self.copy_stream):
+                if self._slot_free_ev is not None:
+                    self.copy_stream.wait_event(self._slot_free_ev)  # the kernels that last read this layer's slots have finished (device side)
                 lst["arena"].data[slot].copy_(lst["host"][lst["host_row"][e]], non_blocking=True)
             self.stats["bytes_h2d"] += lst["arena"].ef.stride
             self._issued.append((tok, info["layer"], e, slot))
 
-    def _settle(self):
-        """Wait for the side stream; every issued copy has landed: mark it ready and publish its slot."""
+    def _mark_landed(self, tok, li, e, slot, now):
+        lst = self.layers[li]
+        self.te.complete(tok, now)
+        lst["pending"].pop(tok, None)
+        lst["cache"].mark_ready(li, e)
+        lst["slot_of_host"][e] = slot
+
+    def _settle(self) -> List[tuple]:
+        """Gate the issued copies on the device and publish their slots.  Without a deadline the compute stream is made to wait
+        for the copies' event and the host goes on at once.  With ``fetch_deadline_ms`` the host polls the event up to the
+        deadline; copies that have not landed are returned as late [(layer, expert)] - their slots stay reserved, they are
+        published by a later call, and the caller runs this step without them."""
+        self._retire_late()
         if not self._issued:
-            return
-        self.copy_stream.synchronize()
+            return []
+        ev = torch.cuda.Event()
+        ev.record(self.copy_stream)
+        late: List[tuple] = []
         now = time.monotonic_ns()
+        if self.fetch_deadline_ms is not None:
+            t_end = time.monotonic() + self.fetch_deadline_ms / 1e3
+            done = self._copy_done(ev)
+            while not done and time.monotonic() < t_end:
+                time.sleep(20e-6)
+                done = self._copy_done(ev)
+            self.stats["host_waits"] += 1
+            if not done:
+                for tok, li, e, slot in self._issued:
+                    self._late.append((ev, tok, li, e, slot))
+                    late.append((li, e))
+                self.stats["late_experts"] += len(late)
+                self._issued = []
+                return late
+        torch.cuda.current_stream(self.dev).wait_event(ev)       # device-side gate: kernels launched from here on see the copies
         for tok, li, e, slot in self._issued:
-            lst = self.layers[li]
-            self.te.complete(tok, now)
-            lst["pending"].pop(tok, None)
-            lst["cache"].mark_ready(li, e)
-            lst["slot_of_host"][e] = slot
+            self._mark_landed(tok, li, e, slot, now)
         self._issued = []
         self.te.poll()
+        return late
+
+    def _retire_late(self):
+        """Copies that missed an earlier deadline and have landed since become ready now (the retry half of deadline -> degraded -> retry)."""
+        if not self._late:
+            return
+        keep = []
+        now = time.monotonic_ns()
+        for ev, tok, li, e, slot in self._late:
+            if self._copy_done(ev):
+                torch.cuda.current_stream(self.dev).wait_event(ev)
+                self._mark_landed(tok, li, e, slot, now)
+            else:
+                keep.append((ev, tok, li, e, slot))
+        self._late = keep
 
     # ------------------------------------------------------------------ per-layer driver
     def run_layer(self, model, li: int, arena, ws, R: int):
@@ -125,8 +195,18 @@ class ExpertStreamer:
         experts' outputs exist (0 for this rank's experts that were computed, -1 otherwise)."""
         st = self.layers[li]
         cache: rt.ExpertCache = st["cache"]
-        ids = ws.ids[:R].reshape(-1).cpu()                       # the one host round trip: which experts does the step need?
-        wts = ws.wts[:R].reshape(-1).cpu()
+        # the one host wait of the layer: which experts does the step need?  (ids | weights through one pinned buffer)
+        n_pairs = R * ws.S
+        if self.h_ids is None or self.h_ids.numel() < 2 * n_pairs:
+            self.h_ids = torch.zeros(2 * max(n_pairs, 64), dtype=torch.int32).pin_memory()
+        cur = torch.cuda.current_stream(self.dev)
+        self.h_ids[:n_pairs].copy_(ws.ids[:R].reshape(-1), non_blocking=True)
+        self.h_ids[n_pairs: 2 * n_pairs].copy_(ws.wts[:R].reshape(-1).view(torch.int32), non_blocking=True)
+        ev_ids = torch.cuda.Event()
+        ev_ids.record(cur)
+        ev_ids.synchronize()
+        ids = self.h_ids[:n_pairs]
+        wts = self.h_ids[n_pairs: 2 * n_pairs].view(torch.float32)
         need: Dict[int, float] = {}
         for e, w in zip(ids.tolist(), wts.tolist()):
             if e in st["mine"]:
@@ -136,12 +216,15 @@ class ExpertStreamer:
             self.trace.write(f"{self.trace_step} {li} {' '.join(str(e) for e in todo)}\n")
             if li == self._last_layer:
                 self.trace_step += 1
+        st["expert_stats"].observe(todo, [need[e] for e in todo])
         model._moe_prepare(arena, ws, R)
         st["present"].fill_(-1)
+        degraded = False
         while todo:
             wave: List[int] = []
             fetched: List[int] = []
             locked = set()
+            late_pre = set()
 
             def lock_landed():
                 # a copy that has landed is evictable until it is locked: pin this wave's experts as soon as they are ready
@@ -157,6 +240,9 @@ class ExpertStreamer:
                     self._issue()                                # a prefetch of this expert is still on its way
                     self._settle()
                     lock_landed()
+                    if not cache.is_ready(li, e):                # ... and missed the deadline: this step goes on without it
+                        late_pre.add(e)
+                        continue
                 if cache.lookup(li, e) >= 0:
                     self.stats["hits"] += 1
                     cache.lock(li, e)
@@ -167,24 +253,33 @@ class ExpertStreamer:
                 else:
                     break                                        # nothing evictable any more: run what is resident
                 wave.append(e)
-            if not wave:
+            if not wave and not late_pre:
                 raise RuntimeError(f"layer {li}: no expert slot can be freed")
             self._issue()
-            self._settle()
+            late = {e for (l_, e) in self._settle() if l_ == li} | late_pre
             lock_landed()
+            if late:
+                # deadline missed: this step runs without those experts (degraded); their copies keep going and are published later
+                degraded = True
+                wave = [e for e in wave if e not in late]
             so = torch.full_like(st["slot_of_host"], -1)
             for e in wave:
                 cache.touch(li, e, need[e])
                 so[e] = st["slot_of_host"][e]
-            arena.slot_of.copy_(so)                              # only this wave's experts are visible to the kernels
-            model._moe_experts(arena, ws, R, None)
-            st["present"][torch.tensor(wave, dtype=torch.long, device=self.dev)] = 0
-            torch.cuda.current_stream(self.dev).synchronize()    # slots may be reused by the next wave / layer
+            arena.slot_of.copy_(so, non_blocking=True)           # only this wave's experts are visible to the kernels
+            if wave:
+                model._moe_experts(arena, ws, R, None)
+                st["present"][torch.tensor(wave, dtype=torch.long, device=self.dev)] = 0
+            # slots may be reused by the next wave / layer: the side stream waits for these kernels on the device, the host does not
+            self._slot_free_ev = torch.cuda.Event()
+            self._slot_free_ev.record(torch.cuda.current_stream(self.dev))
             for e in wave:
                 cache.unlock(li, e)
-            done = set(wave)
+            done = set(wave) | late
             todo = [e for e in todo if e not in done]
             self.stats["waves"] += 1
+        if degraded:
+            self.stats["degraded_steps"] += 1
         if self.weighted:
             cache.end_step()                                     # fold this pass's touches into frequency / autocorrelation / hysteresis
         if self.prefetch:
@@ -238,4 +333,9 @@ class ExpertStreamer:
 
     def summary(self) -> dict:
         tot = max(1, self.stats["hits"] + self.stats["misses"])
-        return dict(self.stats, hit_rate=self.stats["hits"] / tot, h2d_gbs=self.te.bandwidth_gbs(0, 0))
+        return dict(self.stats, hit_rate=self.stats["hits"] / tot, h2d_gbs=self.te.bandwidth_gbs(0, 0),
+                    numa_bound_layers=sum(1 for st in self.layers.values() if st["host_arena"] is not None and st["host_arena"].numa_bound))
+
+    def expert_frequencies(self, li: int):
+        """Decayed per-expert selection frequency of one layer (native ``ExpertStats``, fed by every step's routing)."""
+        return self.layers[li]["expert_stats"].frequencies()

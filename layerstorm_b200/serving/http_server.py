@@ -80,7 +80,10 @@ class LayerStormServer:
         failed = self.failed_ranks() if getattr(self, "failed_ranks", None) else None
         if failed:
             return _error(503, "rank(s) down: " + "; ".join(f"{r}: {why}" for r, why in sorted(failed.items())), "server_error")
-        return {"status": "ok", "uptime_s": round(time.time() - self.started, 1), "queued": self.orch.queued(), "served": self.orch.served}
+        # engine-side numbers come from the orchestrator's published state block (seqlock snapshot written by the serving thread)
+        state = self.orch.published_state() if hasattr(self.orch, "published_state") else {}
+        return {"status": "ok", "uptime_s": round(time.time() - self.started, 1), "queued": self.orch.queued(), "served": self.orch.served,
+                "engine": state}
 
     async def models(self):
         return {"object": "list", "data": [{"id": self.cfg.model_name, "object": "model", "created": int(self.started), "owned_by": "layerstorm-b200",

@@ -153,6 +153,36 @@ class Orchestrator:
         self.stop_flag = threading.Event()
         self.active: Optional[InferenceRequest] = None
         self.served = 0
+        # native statistics of the speculation rounds (global / windowed / per-request acceptance, expected tokens per round) and
+        # a seqlock-published state block that other threads (the HTTP server's /health) read without taking the serving lock
+        from ..runtime import native as _rt
+        self.acceptance = _rt.AcceptanceTracker()
+        self._state = _rt.StateSnapshot(64)
+        self._gen_tokens = 0
+        self._publish_state()
+
+    # ---- published state (single writer: the serving thread; any number of readers) ----
+    _STATE_FMT = "<qqqqdd"      # served, queued, generated tokens, free KV pages, acceptance (windowed), wall time of the last update
+
+    def _publish_state(self):
+        import struct
+        free_pages = -1
+        try:
+            free_pages = int(self.engine.free_page_count())
+        except Exception:      # engines without a page pool
+            pass
+        blob = struct.pack(self._STATE_FMT, self.served, len(self.queue), self._gen_tokens, free_pages, float(self.acceptance.windowed_rate()), time.time())
+        self._state.begin(); self._state.write(0, blob); self._state.end()
+
+    def published_state(self) -> dict:
+        """A consistent copy of the last published state block (lock-free read; retried while the writer is mid-update)."""
+        import struct
+        raw, version = self._state.read(0, struct.calcsize(self._STATE_FMT))
+        if raw is None:
+            return {}
+        served, queued, gen, free_pages, acc, t = struct.unpack(self._STATE_FMT, raw)
+        return {"served": served, "queued": queued, "generated_tokens": gen, "free_kv_pages": free_pages, "spec_acceptance_windowed": round(acc, 4),
+                "state_age_s": round(max(0.0, time.time() - t), 3)}
 
     # ---- thread-safe entry points ----
     def submit_request(self, req: InferenceRequest):
@@ -210,6 +240,9 @@ class Orchestrator:
         req.finish_reason = req.finish_reason or reason
         req.stats.t_done = time.time()
         req.stats.completion_tokens = len(req.output_ids)
+        self._gen_tokens += len(req.output_ids)
+        self.acceptance.forget(hash(req.request_id) & 0x7FFFFFFF)
+        self._publish_state()
         req.done.set()
         if req.on_done:
             req.on_done(req)
@@ -369,6 +402,7 @@ class Orchestrator:
             eng.rewind(sid, base_len + 1 + n_acc)
             req.stats.spec_rounds += 1
             req.stats.spec_accepted += n_acc
+            self.acceptance.record(hash(req.request_id) & 0x7FFFFFFF, len(draft), n_acc)
             self.governor.observe_round(n_new, (time.time() - t0) * 1e3)
             if hasattr(self.draft, "feedback"):
                 self.draft.feedback(len(draft), n_acc)
@@ -407,6 +441,7 @@ class Orchestrator:
                 eng.rewind(sid, base_len + 1 + n_acc)          # keep tok + the accepted draft tokens
             req.stats.spec_rounds += 1
             req.stats.spec_accepted += n_acc
+            self.acceptance.record(hash(req.request_id) & 0x7FFFFFFF, len(draft), n_acc)
             new = draft[:n_acc] + [nxt]
             self.governor.observe_round(len(new), (time.time() - t0) * 1e3)
             if hasattr(self.draft, "feedback"):

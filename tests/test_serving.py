@@ -264,3 +264,23 @@ def test_device_error_words_raise_a_typed_error():
     with pytest.raises(DeviceWaitError) as ei:
         raise_on_error_words(["tensor_core", "tp_allreduce"], [0, 103])
     assert ei.value.source == "tp_allreduce" and ei.value.code == 103 and "rank 3" in str(ei.value)
+
+
+def test_published_state_and_acceptance_statistics():
+    """The serving thread publishes a seqlock state block (read lock-free by /health) and feeds the native acceptance tracker."""
+    eng = NullEngine()
+
+    class RightDraft:
+        def propose(self, ctx, gamma):
+            out, c = [], list(ctx)
+            for _ in range(gamma):
+                c.append(eng._next(c)); out.append(c[-1])
+            return out
+
+    orch = Orchestrator(eng, draft=RightDraft(), speculation_depth=3)
+    assert orch.published_state()["served"] == 0
+    r = run(orch, list(range(5, 60)), max_tokens=12, ignore_eos=True)
+    st = orch.published_state()
+    assert st["generated_tokens"] == len(r.output_ids) == 12 and st["free_kv_pages"] > 0 and st["state_age_s"] < 60
+    assert r.stats.spec_rounds > 0 and orch.acceptance.global_rate() > 0.9 and st["spec_acceptance_windowed"] > 0.9
+    assert orch.acceptance.expected_tokens(3) > 3.0

@@ -40,3 +40,41 @@ def test_streamed_experts_match_resident_model(name, eq):
         for li, lst in st.layers.items():
             assert lst["arena"].n_slots == cfg.top_k + cfg.n_shared + 1
             assert lst["host"].is_pinned()
+
+
+def test_fetch_deadline_finishes_the_step_degraded_and_recovers():
+    """A copy whose completion is stalled (injected on the host: the completion query is made to answer 'not yet') misses the
+    fetch deadline: the step finishes without that expert instead of waiting, the streamer counts it, and once the stall is
+    lifted the late copy is published and the outputs equal the resident model's again."""
+    cfg = get_preset("tiny-mla-moe")
+    w = init_weights(cfg, 9)
+    prompt = torch.randint(0, cfg.vocab, (24,), generator=torch.Generator().manual_seed(4)).tolist()
+
+    def build(streamed):
+        m = DeviceModel.from_state_dict(cfg, w, "cuda", kv_fmt="bf16", page=16, expert_quant="bf16")
+        st = ExpertStreamer(m, slots_per_layer=cfg.top_k + cfg.n_shared + 1, fetch_deadline_ms=2.0) if streamed else None
+        return Engine(m, max_seqs=1, max_ctx=128, prefill_chunk=8, max_batch=1, use_graph=False), st
+
+    ref_eng, _ = build(False)
+    sid = ref_eng.create_sequence()
+    ref = [ref_eng.prefill(sid, prompt)]
+    for _ in range(4):
+        ref.append(ref_eng.decode([sid], [ref[-1]])[0])
+
+    eng, st = build(True)
+    sid = eng.create_sequence()
+    got = [eng.prefill(sid, prompt)]
+    assert got == ref[:1] and st.summary()["degraded_steps"] == 0 and st.summary()["host_waits"] > 0
+    real = st._copy_done
+    st._copy_done = lambda ev: False                       # every completion now looks stalled
+    eng.decode([sid], [got[-1]])                           # must return (degraded), not hang
+    s = st.summary()
+    stalled = s["late_experts"]
+    st._copy_done = real                                    # the stall is lifted: late copies are published on the next use
+    eng.free_sequence(sid)
+    sid = eng.create_sequence()
+    again = [eng.prefill(sid, prompt)]
+    for _ in range(4):
+        again.append(eng.decode([sid], [again[-1]])[0])
+    assert again == ref
+    assert not st._late and (stalled == 0 or s["degraded_steps"] >= 1)

@@ -401,7 +401,10 @@ __global__ void __launch_bounds__(256) sgemm_f32w_kernel(void* __restrict__ out,
 LSB_API int lsb_gemv_f32w(void* out, const void* x, const void* w, const void* bias, int M, int N, int K, int ldx,
                           int ldw, int ldo, float alpha, int out_bf16, void* stream) {
     if (K % 4 || ldw % 4 || ldx % 4) return -1;
-    if (M >= 16) {
+    // The tiled SGEMM pays off from about a hundred rows; below that (decode batches, verify steps) its grid is a handful of
+    // blocks (5 blocks for 288 router rows and 32 tokens: 378 us measured), while passes of the weight-streaming kernel over
+    // four rows at a time keep the whole GPU busy (about 3 us per pass).
+    if (M >= 128) {
         launch_pdl((sgemm_f32w_kernel), dim3((N + 63) / 64, (M + 63) / 64), 256, 0, (cudaStream_t)stream, out, (const bf16*)x, (const float*)w,
                    (const float*)bias, M, N, K, ldx, ldw, ldo, alpha, out_bf16);
         LSB_CHECK_LAUNCH();

@@ -122,6 +122,8 @@ public:
         c.frozen = frozen;
         int n = pages_for(prefix_len);
         auto& pl = pools_[p.pool];
+        for (int i = 0; i < n; ++i)
+            if (p.pages[i] < 0) return LSB_ERR_ARG;         // swapped-out pages cannot be shared: promote them first
         for (int i = 0; i < n; ++i) { c.pages.push_back(p.pages[i]); pl.refcnt[p.pages[i]] += 1; }
         seqs_[child] = std::move(c);
         return 0;
@@ -146,6 +148,31 @@ public:
         return 0;
     }
 
+    // KV tiering of an ACTIVE sequence: logical page `idx` gives its HBM page back to the pool (its rows live in the cold tier
+    // from now on; the block-table entry becomes -1), and takes a fresh HBM page again when it is promoted.  Only private,
+    // completely filled pages behind the frontier may be swapped out.  Returns the released / newly attached physical page.
+    int swap_out(int seq, int idx) {
+        auto it = seqs_.find(seq);
+        if (it == seqs_.end()) return LSB_ERR_NOT_FOUND;
+        Seq& s = it->second;
+        if (idx < 0 || idx >= (int)s.pages.size() || (idx + 1) * page_tokens_ > s.length) return LSB_ERR_ARG;
+        const int pg = s.pages[idx];
+        if (pg < 0) return LSB_ERR_ARG;
+        if (pools_[s.pool].refcnt[pg] != 1) return LSB_ERR_SHARED;
+        release(s.pool, pg);
+        s.pages[idx] = -1;
+        return pg;
+    }
+    int swap_in(int seq, int idx) {
+        auto it = seqs_.find(seq);
+        if (it == seqs_.end()) return LSB_ERR_NOT_FOUND;
+        Seq& s = it->second;
+        if (idx < 0 || idx >= (int)s.pages.size() || s.pages[idx] >= 0) return LSB_ERR_ARG;
+        if (available(s.pool, true) < 1) return LSB_ERR_POOL_EXHAUSTED;
+        s.pages[idx] = take(s.pool);
+        return s.pages[idx];
+    }
+
     // Metadata-only move of a sequence's accounting to another pool of the same geometry (the
     // speculation pool's accepted tokens become main-pool tokens).  Pools must share storage.
     int promote(int seq, int to_pool) {
@@ -157,6 +184,7 @@ public:
         auto& to = pools_[to_pool];
         if ((int)s.pages.size() > available(to_pool, true)) return LSB_ERR_POOL_EXHAUSTED;
         for (auto& pg : s.pages) {
+            if (pg < 0) return LSB_ERR_ARG;
             if (from.refcnt[pg] != 1) return LSB_ERR_SHARED;
         }
         for (auto& pg : s.pages) {
@@ -220,6 +248,7 @@ private:
         return pg;
     }
     void release(int pool, int pg) {
+        if (pg < 0) return;                 // a swapped-out page holds no HBM
         auto& pl = pools_[pool];
         if (--pl.refcnt[pg] == 0) pl.free_list.push_back(pg);
     }
@@ -254,6 +283,8 @@ LSB_RT_API int lsb_pa_fork(void* h, int parent, int child, int prefix_len, int f
 LSB_RT_API int lsb_pa_rewind(void* h, int seq, int new_len) { return ((PageAllocator*)h)->rewind(seq, new_len); }
 LSB_RT_API int lsb_pa_seq_destroy(void* h, int seq) { return ((PageAllocator*)h)->destroy(seq); }
 LSB_RT_API int lsb_pa_promote(void* h, int seq, int to_pool) { return ((PageAllocator*)h)->promote(seq, to_pool); }
+LSB_RT_API int lsb_pa_swap_out(void* h, int seq, int idx) { return ((PageAllocator*)h)->swap_out(seq, idx); }
+LSB_RT_API int lsb_pa_swap_in(void* h, int seq, int idx) { return ((PageAllocator*)h)->swap_in(seq, idx); }
 LSB_RT_API int lsb_pa_seq_length(void* h, int seq) { return ((PageAllocator*)h)->length(seq); }
 LSB_RT_API int lsb_pa_seq_pages(void* h, int seq, int* out, int cap) { return ((PageAllocator*)h)->copy_pages(seq, out, cap); }
 LSB_RT_API int lsb_pa_refcount(void* h, int pool, int page) { return ((PageAllocator*)h)->refcount(pool, page); }

@@ -96,6 +96,9 @@ ROUTER_FUSED = os.environ.get("LSB_ROUTER_FUSED", "0") != "0"
 KDA_CHUNKED = os.environ.get("LSB_KDA_CHUNKED", "1") not in ("", "0")
 # LSB_MHC_CLUSTER=0: decode-sized hyper-connection passes fall back to the two-launch path (partials + last-block finalize, contraction)
 MHC_CLUSTER = os.environ.get("LSB_MHC_CLUSTER", "1") not in ("", "0")
+# rows of a step up to which the cluster kernel (one cluster per row) is used; above it the partial + last-block-finalize kernels, which
+# tile better over many rows (32 rows on a B200: 32.6 us per pass against 55.2 us for 32 clusters)
+MHC_CLUSTER_MAX_ROWS = int(os.environ.get("LSB_MHC_CLUSTER_MAX_ROWS", "8"))
 # ablation switches of the two folds of the cluster kernel (router behind, MoE combine in front)
 MHC_FOLD_ROUTER = os.environ.get("LSB_MHC_FOLD_ROUTER", "0") not in ("", "0")
 MHC_FOLD_COMBINE = os.environ.get("LSB_MHC_FOLD_COMBINE", "0") not in ("", "0")
@@ -362,8 +365,10 @@ class Workspace:
         self.qproj = z(R, m.max_qb, dtype=b16)
         self.q_abs = z(R, Hh, cfg.kv_lora + cfg.qk_rope, dtype=b16)
         self.o_lat = z(R, Hh, cfg.kv_lora, dtype=b16)
-        hg = (Hh + 15) // 16
-        self.NS = max(1, min(32, 296 // max(1, R * hg)))
+        # KV splits: enough blocks for two per SM.  Blocks per query row follow the kernel variant lsb_mla_decode picks (one block
+        # serves four 16-head groups above 32 heads, two above 16)
+        hb = (Hh + 63) // 64 if Hh > 32 else ((Hh + 31) // 32 if Hh > 16 else 1)
+        self.NS = max(1, min(32, 296 // max(1, R * hb)))
         self.o_part = z(R, Hh, self.NS, cfg.kv_lora)
         self.ml_part = z(R, Hh, self.NS, 2)
         self.attn_v = z(R, Hh * cfg.v_head, dtype=b16)
@@ -432,6 +437,8 @@ class DeviceModel:
         self.V_local = cfg.vocab // tp_size
         self._fused = False
         self.dcp = None
+        self.idx_identity = False  # the indexer's key cache keeps a page table of its own (row-granular KV tiering: its pages never leave HBM)
+        self.row_tier = None      # RowTiering (runtime/kv_tiering.py) when old KV pages of active sequences live in pinned host memory
         self.streamer = None      # ExpertStreamer when the VRAM expert cache is capped (runtime/streaming.py)
         self.drift = None         # dict: eager steps store every layer's output rows here (input of utils/determinism_probe.py drift)
         self.tq_centroids = None  # TurboQuant reconstruction levels (kv_fmt "tq4")
@@ -785,7 +792,7 @@ class DeviceModel:
         # identity page table (slot-major, full length per slot); otherwise it shares the sequence's pages
         self.idx_block_table = self.block_table
         idx_pages = num_pages
-        if self.dcp is not None and cfg.has_indexer:
+        if (self.dcp is not None or self.idx_identity) and cfg.has_indexer:
             idx_pages = n_slots * max_pages_per_seq
             self.idx_block_table = torch.arange(idx_pages, dtype=torch.int32, device=dev).view(n_slots, max_pages_per_seq).contiguous()
         P = cfg.index_kpool
@@ -953,6 +960,11 @@ class DeviceModel:
             # sharded KV: gather the queries of all heads, attend over this rank's token shard, merge on the head owners
             self.dcp.forward(ws.q_abs, self.kv_cache[i], self.block_table, self.max_pages, ws.row_seq, ws.row_len_local, ws.o_lat, self.page,
                              KV_FMT[self.kv_fmt], cfg.softmax_scale, sel_idx=sel_idx, sel_cnt=sel_cnt, tq_centroids=self.tq_centroids, rows=R)
+        elif self.row_tier is not None and sel_idx is not None:
+            # tiered KV: the selected rows (hot pages and cold tier alike) are materialised in a dense buffer, attention runs over that
+            cache_m, bt_m, pm, seq_m, sel_m = self.row_tier.materialise(i, ws, R, sel_idx, sel_cnt, sel_ld)
+            nat.call("lsb_mla_decode", ws.q_abs, cache_m, bt_m, pm, seq_m, sel_cnt, sel_m, sel_cnt, sel_ld, ws.o_lat, None, ws.o_part, ws.ml_part,
+                     R, Hh, dl, dr, self.page, KV_FMT[self.kv_fmt], ws.NS, cfg.softmax_scale, self.tq_centroids)
         else:
             nat.call("lsb_mla_decode", ws.q_abs, self.kv_cache[i], self.block_table, self.max_pages, ws.row_seq, ws.row_len,
                      sel_idx, sel_cnt, sel_ld, ws.o_lat, None, ws.o_part, ws.ml_part, R, Hh, dl, dr, self.page,
@@ -1007,7 +1019,7 @@ class DeviceModel:
         if self.comm is not None:
             # fewer than 8 rows: the kernel that consumes a cross-rank sum exchanges the partials itself (one flag per CTA) instead of
             # the producer's last block copying them to every peer; needs the cluster form of the hyper-connection pass where there is one
-            xchg = COMM_XCHG if (self._fused and R < 8 and self.dcp is None and (not cfg.mhc or self._mhc_cluster_ok())) else 0
+            xchg = COMM_XCHG if (self._fused and R < 8 and R <= MHC_CLUSTER_MAX_ROWS and self.dcp is None and (not cfg.mhc or self._mhc_cluster_ok())) else 0
             if xchg == 2 and R * H > self.comm.ll_cap:
                 xchg = 1
             self.comm.struct.xchg = xchg
@@ -1016,7 +1028,7 @@ class DeviceModel:
         if cfg.mhc:
             nat.call("lsb_embedding", ws.sub, None, self.embed, ws.tok, R, H, 0, cfg.vocab)
             # decode-sized steps: one cluster kernel per post -> pre pass, with the MoE combine folded in front and the router behind
-            clus = R < 64 and self._mhc_cluster_ok()
+            clus = R <= MHC_CLUSTER_MAX_ROWS and self._mhc_cluster_ok()
             pending = None         # slot table of the MoE layer whose combine the next pass performs
             for i, L in enumerate(self.layers):
                 self._hc_pass(L["hc_attn"], L["attn_norm"], ws, R, 0 if i == 0 else 1, clus, pending, None)

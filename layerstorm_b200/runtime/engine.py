@@ -63,8 +63,13 @@ class SamplingParams:
 
 class Engine:
     def __init__(self, model: DeviceModel, max_seqs: int = 4, max_ctx: int = 4096, prefill_chunk: int = 256,
-                 max_batch: int = 4, num_pages: Optional[int] = None, use_graph: bool = True):
+                 max_batch: int = 4, num_pages: Optional[int] = None, use_graph: bool = True, row_tiering: Optional[dict] = None):
+        """``row_tiering``: ``{"hot_window_tokens": n, "cold_pages": m}`` keeps only the last n tokens of every sequence in HBM pages;
+        older pages move to pinned host memory and single rows come back when the indexer selects them (eager steps, sparse-attention
+        models; see runtime/kv_tiering.py).  ``num_pages`` can then be far below ``max_seqs * max_ctx / page``."""
         self.model, self.cfg = model, model.cfg
+        if row_tiering:
+            model.idx_identity = True                      # before the caches are allocated: indexer keys stay resident
         self.dev = model.device
         self.page = model.page
         self.max_ctx = max_ctx
@@ -84,6 +89,12 @@ class Engine:
         self.h_bt = torch.zeros(max_seqs, self.max_pages, dtype=torch.int32).pin_memory()
         self.h_out = torch.zeros(Rmax, dtype=torch.int32).pin_memory()
         self.stream = torch.cuda.Stream(device=self.dev)
+        self.row_tier = None
+        if row_tiering:
+            from .kv_tiering import RowTiering
+            self.row_tier = RowTiering(self, int(row_tiering["hot_window_tokens"]), int(row_tiering["cold_pages"]))
+            model.row_tier = self.row_tier
+            self.use_graph = False                         # a tiered attention layer has a host round trip: eager steps
         self.vram_plan = self._carve_report()
         self.h_err = torch.zeros(8, dtype=torch.int32).pin_memory()      # error words of the step, read back with the sampled tokens
         self.h2d_bytes = 0
@@ -164,6 +175,8 @@ class Engine:
         slot = self.free_slots.pop()
         self.seqs[slot] = SequenceState(slot)
         self.pa.create(slot)
+        if self.row_tier is not None:
+            self.row_tier.on_create(slot)
         with torch.cuda.stream(self.stream):
             self.model.reset_slot(slot)
         return slot
@@ -173,6 +186,8 @@ class Engine:
             self.hibernated.pop(sid)
             self.tier.destroy(sid)
         s = self.seqs.pop(sid)
+        if self.row_tier is not None:
+            self.row_tier.on_free(sid)
         self.pa.destroy(s.slot)
         self.free_slots.append(s.slot)
 
@@ -240,6 +255,8 @@ class Engine:
         if getattr(self.model, "dcp", None) is not None:
             raise NotImplementedError("not available with a sharded KV cache")
         s = self.seqs[sid]
+        if self.row_tier is not None:
+            raise NotImplementedError("whole-sequence hibernation and row-granular tiering are alternatives: this engine tiers rows")
         if sid in self.hibernated:
             return 0
         n = len(s.pages)
@@ -337,6 +354,8 @@ class Engine:
         s = self.seqs[sid]
         if length == s.length:
             return
+        if self.row_tier is not None and length < self.row_tier.next_page.get(sid, 0) * self.page:
+            raise RuntimeError("rewind into the cold part of a tiered sequence is refused")
         replay: List[int] = []
         if self.has_recurrent_state and length < s.length:
             a_sid, a_len = getattr(self, "_anchor_of", (None, -1))
@@ -381,6 +400,8 @@ class Engine:
         """rows: (token, slot, pos); seq_groups: (row0, nrows, slot)."""
         R = len(rows)
         P = max(self.cfg.index_kpool, 1)
+        if self.row_tier is not None:
+            self.row_tier.step_sids = [slot for (_, slot, _) in rows]      # sequence id == slot id in this engine
         # ring of pinned staging buffers: a buffer is rewritten only after the copy that last
         # read it has completed, so the host can run ahead of the device by several steps
         if not hasattr(ws, "h_ring"):
@@ -444,6 +465,8 @@ class Engine:
             nxt = int(self.h_out[0])
             if want_logits:
                 logits = ws.logits[0].float().cpu()
+        if self.row_tier is not None:
+            self.row_tier.slide_window(sid)
         return (nxt, logits) if want_logits else nxt
 
     def sample_last_prefill(self, sid: int, sample) -> int:
@@ -578,6 +601,8 @@ class Engine:
             s = self.seqs[sid]
             s.length += 1
             s.tokens.append(int(tok))
+            if self.row_tier is not None and s.length % self.page == 0:
+                self.row_tier.slide_window(sid)
         if return_logits:
             return out, ws.logits[:B].float().cpu()
         return out

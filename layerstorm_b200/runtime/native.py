@@ -117,6 +117,8 @@ class PageAllocator:
     def destroy(self, seq): _check(self.lib.lsb_pa_seq_destroy(self.h, seq), "seq_destroy")
     def promote(self, seq, to_pool): _check(self.lib.lsb_pa_promote(self.h, seq, to_pool), "promote")
     def length(self, seq): return self.lib.lsb_pa_seq_length(self.h, seq)
+    def swap_out(self, seq, idx) -> int: return _check(self.lib.lsb_pa_swap_out(self.h, seq, idx), "swap_out")
+    def swap_in(self, seq, idx) -> int: return _check(self.lib.lsb_pa_swap_in(self.h, seq, idx), "swap_in")
 
     def pages(self, seq: int) -> List[int]:
         cap = 1 << 16
@@ -509,8 +511,11 @@ class HostArena:
 
     def unpin(self):
         if self._pinned:
-            import torch
-            torch.cuda.cudart().cudaHostUnregister(self.base)
+            try:
+                import torch
+                torch.cuda.cudart().cudaHostUnregister(self.base)
+            except ImportError:          # interpreter shutdown: the driver releases the registration with the process
+                pass
             self._pinned = False
 
     def lookup(self, layer, expert) -> int: return self.lib.lsb_arena_lookup(self.h, layer, expert)

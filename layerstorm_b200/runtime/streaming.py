@@ -256,10 +256,12 @@ class ExpertStreamer:
             if not wave and not late_pre:
                 raise RuntimeError(f"layer {li}: no expert slot can be freed")
             self._issue()
-            late = {e for (l_, e) in self._settle() if l_ == li} | late_pre
+            self._settle()
             lock_landed()
+            # with a fetch deadline some of the wave's copies may not have landed (stalled, or still queued behind stalled ones):
+            # this step runs without those experts (degraded); their copies keep going and are published by a later call
+            late = {e for e in wave if not cache.is_ready(li, e)} | late_pre
             if late:
-                # deadline missed: this step runs without those experts (degraded); their copies keep going and are published later
                 degraded = True
                 wave = [e for e in wave if e not in late]
             so = torch.full_like(st["slot_of_host"], -1)

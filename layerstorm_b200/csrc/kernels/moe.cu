@@ -337,7 +337,7 @@ __global__ void __launch_bounds__(256) moe_gateup_fp4_kernel(const bf16* __restr
                                                              const int* __restrict__ slot_of, ExpertFmt ef,
                                                              const int* __restrict__ group_expert, const int* __restrict__ group_n,
                                                              const int* __restrict__ group_pairs, const int* __restrict__ n_groups,
-                                                             bf16* __restrict__ act, int S, float limit, int* __restrict__ miss_flag) {
+                                                             bf16* __restrict__ act, int S, float limit, int* __restrict__ miss_flag, int run) {
     extern __shared__ __align__(16) uint8_t smraw[];
     __half* xs = reinterpret_cast<__half*>(smraw);
     __shared__ const bf16* rows[4];
@@ -355,26 +355,31 @@ __global__ void __launch_bounds__(256) moe_gateup_fp4_kernel(const bf16* __restr
     for (int i = 0; i < MT; ++i) pr[i] = group_pairs ? group_pairs[g * 4 + min(i, n - 1)] : g;
     if (threadIdx.x < MT) rows[threadIdx.x] = x + (size_t)(pr[threadIdx.x] / S) * ef.H;
     const uint8_t* base = arena + (size_t)slot * ef.stride;
-    const int tile = blockIdx.x >> 2, blk = blockIdx.x & 3;
+    // a block covers `run` consecutive values of n % 32 for all four 32-row quads of a 128-row tile (4 * run rows, run / 2 passes of
+    // one row per warp): run = 8 streams most per block, smaller runs spread an expert over more blocks and shorten the chain of
+    // dependent passes when a GPU holds only a few of the step's experts
+    const int bpt = 32 / run;                              // blocks per 128-row tile
+    const int tile = blockIdx.x / bpt, blk = blockIdx.x - tile * bpt;
     const int gtiles = ef.H >> 6;
-    constexpr int kTS = 132;                               // 128 scale bytes per K-tile + 4 pad
+    const int kTS = run * 16 + 4;                          // scale bytes per K-tile + 4 pad (odd number of words: conflict-free)
     uint8_t* scg = smraw + (size_t)MT * ef.H * 2;
     uint8_t* scu = scg + (size_t)gtiles * kTS;
-    stage_scales(scg, base + ef.off_sg, tile, blk, 8, gtiles, kTS);
-    stage_scales(scu, base + ef.off_su, tile, blk, 8, gtiles, kTS);
+    stage_scales(scg, base + ef.off_sg, tile, blk, run, gtiles, kTS);
+    stage_scales(scu, base + ef.off_su, tile, blk, run, gtiles, kTS);
     __syncthreads();
     stage_x_half(xs, rows, n, ef.H);
     __syncthreads();
     const float* tail = reinterpret_cast<const float*>(base + ef.off_tail);
     const float sg = tail[0], su = tail[1];
 #pragma unroll 1
-    for (int r = 0; r < 4; ++r) {
-        const int j = warp * 4 + r;                       // 0..31
-        const int f = tile * 128 + (j >> 3) * 32 + blk * 8 + (j & 7);
+    for (int r = 0; r < run / 2; ++r) {
+        const int j = r * 8 + warp;                       // 0 .. 4 run - 1
+        const int quad = j / run, i = j - quad * run;
+        const int f = tile * 128 + quad * 32 + blk * run + i;
         float ag[MT], au[MT];
 #pragma unroll
         for (int m = 0; m < MT; ++m) ag[m] = au[m] = 0.f;
-        const int so = (j & 7) * 16 + (j >> 3) * 4;
+        const int so = i * 16 + quad * 4;
         nvfp4_row_dot2_sm<MT>(base + ef.off_gate + (size_t)f * (ef.H >> 1), scg + so,
                               base + ef.off_up + (size_t)f * (ef.H >> 1), scu + so, kTS, ef.H, xs, n, ag, au);
 #pragma unroll
@@ -394,7 +399,7 @@ __global__ void __launch_bounds__(256) moe_down_fp4_kernel(const bf16* __restric
                                                            const int* __restrict__ slot_of, ExpertFmt ef,
                                                            const int* __restrict__ group_expert, const int* __restrict__ group_n,
                                                            const int* __restrict__ group_pairs, const int* __restrict__ n_groups,
-                                                           float* __restrict__ y) {
+                                                           float* __restrict__ y, int run) {
     extern __shared__ __align__(16) uint8_t smraw[];
     __half* xs = reinterpret_cast<__half*>(smraw);
     __shared__ const bf16* rows[4];
@@ -412,24 +417,26 @@ __global__ void __launch_bounds__(256) moe_down_fp4_kernel(const bf16* __restric
     for (int i = 0; i < MT; ++i) pr[i] = group_pairs ? group_pairs[g * 4 + min(i, n - 1)] : g;
     if (threadIdx.x < MT) rows[threadIdx.x] = act + (size_t)pr[threadIdx.x] * ef.F;
     const uint8_t* base = arena + (size_t)slot * ef.stride;
-    const int tile = blockIdx.x >> 1, blk = blockIdx.x & 1;
+    const int bpt = 32 / run;                              // see moe_gateup_fp4_kernel: 4 * run rows per block, two rows per warp and pass
+    const int tile = blockIdx.x / bpt, blk = blockIdx.x - tile * bpt;
     const int gtiles = ef.F >> 6;
-    constexpr int kTS = 260;                               // 256 scale bytes per K-tile + 4 pad
+    const int kTS = run * 16 + 4;
     uint8_t* scd = smraw + (size_t)MT * ef.F * 2;
-    stage_scales(scd, base + ef.off_sd, tile, blk, 16, gtiles, kTS);
+    stage_scales(scd, base + ef.off_sd, tile, blk, run, gtiles, kTS);
     __syncthreads();
     stage_x_half(xs, rows, n, ef.F);
     __syncthreads();
     const float sd = reinterpret_cast<const float*>(base + ef.off_tail)[2];
 #pragma unroll 1
-    for (int r = 0; r < 4; ++r) {
-        const int j0 = warp * 8 + r * 2;                  // 0..63, two rows per pass
-        const int h0 = tile * 128 + (j0 >> 4) * 32 + blk * 16 + (j0 & 15);
+    for (int r = 0; r < run / 4; ++r) {
+        const int j0 = r * 16 + warp * 2;                 // 0 .. 4 run - 2, two rows per pass
+        const int quad = j0 / run, i = j0 - quad * run;
+        const int h0 = tile * 128 + quad * 32 + blk * run + i;
         const int h1 = h0 + 1;
         float a0[MT], a1[MT];
 #pragma unroll
         for (int m = 0; m < MT; ++m) a0[m] = a1[m] = 0.f;
-        const int so = (j0 & 15) * 16 + (j0 >> 4) * 4;
+        const int so = i * 16 + quad * 4;
         nvfp4_row_dot2_sm<MT>(base + ef.off_down + (size_t)h0 * (ef.F >> 1), scd + so,
                               base + ef.off_down + (size_t)h1 * (ef.F >> 1), scd + so + 16, kTS, ef.F, xs, n, a0, a1);
 #pragma unroll
@@ -552,11 +559,14 @@ LSB_API int lsb_moe_build_groups(const void* ids, int npairs, int E_total, void*
 // routing id array itself, group g is pair g; used for small batches where no build pass is needed.
 LSB_API int lsb_moe_gateup(const void* x, const void* arena, const void* slot_of, const void* fmt_struct,
                            const void* group_expert, const void* group_n, const void* group_pairs, const void* n_groups,
-                           void* act, int S, int max_groups, float limit, void* miss_flag, void* stream) {
+                           void* act, int S, int max_groups, float limit, void* miss_flag, int run, void* stream) {
     ExpertFmt ef = *reinterpret_cast<const ExpertFmt*>(fmt_struct);
     cudaStream_t st = (cudaStream_t)stream;
     if (ef.fmt == 2 && ef.F % 128 == 0 && ef.H % 128 == 0) {   // K % 64 == 0 follows
-        dim3 g2(ef.F / 32, max_groups);
+        // run: values of n % 32 per block (8, 4 or 2; 0 = 8) - see the kernel
+        if (run != 2 && run != 4) run = 8;
+        dim3 g2(ef.F / (4 * run), max_groups);
+        const size_t sc_bytes = (size_t)2 * (ef.H / 64) * (run * 16 + 4);
         static bool attr = false;
         if (!attr) {
             cudaFuncSetAttribute(moe_gateup_fp4_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
@@ -564,12 +574,12 @@ LSB_API int lsb_moe_gateup(const void* x, const void* arena, const void* slot_of
             attr = true;
         }
         if (!group_n)
-            launch_pdl((moe_gateup_fp4_kernel<1>), g2, 256, (size_t)ef.H * 2 + 2 * (ef.H / 64) * 132, st, (const bf16*)x, (const uint8_t*)arena, (const int*)slot_of, ef, (const int*)group_expert,
-                                                                        nullptr, nullptr, nullptr, (bf16*)act, S, limit, (int*)miss_flag);
+            launch_pdl((moe_gateup_fp4_kernel<1>), g2, 256, (size_t)ef.H * 2 + sc_bytes, st, (const bf16*)x, (const uint8_t*)arena, (const int*)slot_of, ef, (const int*)group_expert,
+                                                                        nullptr, nullptr, nullptr, (bf16*)act, S, limit, (int*)miss_flag, run);
         else
-            launch_pdl((moe_gateup_fp4_kernel<4>), g2, 256, (size_t)ef.H * 8 + 2 * (ef.H / 64) * 132, st, (const bf16*)x, (const uint8_t*)arena, (const int*)slot_of, ef, (const int*)group_expert,
+            launch_pdl((moe_gateup_fp4_kernel<4>), g2, 256, (size_t)ef.H * 8 + sc_bytes, st, (const bf16*)x, (const uint8_t*)arena, (const int*)slot_of, ef, (const int*)group_expert,
                                                                         (const int*)group_n, (const int*)group_pairs, (const int*)n_groups, (bf16*)act, S, limit,
-                                                                        (int*)miss_flag);
+                                                                        (int*)miss_flag, run);
         LSB_CHECK_LAUNCH();
     }
     if (!group_n) return -1;   // pair mode is only implemented for the NVFP4 fast path
@@ -587,11 +597,13 @@ LSB_API int lsb_moe_gateup(const void* x, const void* arena, const void* slot_of
 
 LSB_API int lsb_moe_down(const void* act, const void* arena, const void* slot_of, const void* fmt_struct,
                          const void* group_expert, const void* group_n, const void* group_pairs, const void* n_groups,
-                         void* y, int max_groups, void* stream) {
+                         void* y, int max_groups, int run, void* stream) {
     ExpertFmt ef = *reinterpret_cast<const ExpertFmt*>(fmt_struct);
     cudaStream_t st = (cudaStream_t)stream;
     if (ef.fmt == 2 && ef.F % 128 == 0 && ef.H % 128 == 0) {
-        dim3 g2(ef.H / 64, max_groups);
+        if (run != 4 && run != 8) run = 16;                  // values of n % 32 per block (16, 8 or 4; 0 = 16)
+        dim3 g2(ef.H / (4 * run), max_groups);
+        const size_t sc_bytes = (size_t)(ef.F / 64) * (run * 16 + 4);
         static bool attr = false;
         if (!attr) {
             cudaFuncSetAttribute(moe_down_fp4_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
@@ -599,11 +611,11 @@ LSB_API int lsb_moe_down(const void* act, const void* arena, const void* slot_of
             attr = true;
         }
         if (!group_n)
-            launch_pdl((moe_down_fp4_kernel<1>), g2, 256, (size_t)ef.F * 2 + (ef.F / 64) * 260, st, (const bf16*)act, (const uint8_t*)arena, (const int*)slot_of, ef, (const int*)group_expert,
-                                                                      nullptr, nullptr, nullptr, (float*)y);
+            launch_pdl((moe_down_fp4_kernel<1>), g2, 256, (size_t)ef.F * 2 + sc_bytes, st, (const bf16*)act, (const uint8_t*)arena, (const int*)slot_of, ef, (const int*)group_expert,
+                                                                      nullptr, nullptr, nullptr, (float*)y, run);
         else
-            launch_pdl((moe_down_fp4_kernel<4>), g2, 256, (size_t)ef.F * 8 + (ef.F / 64) * 260, st, (const bf16*)act, (const uint8_t*)arena, (const int*)slot_of, ef, (const int*)group_expert,
-                                                                      (const int*)group_n, (const int*)group_pairs, (const int*)n_groups, (float*)y);
+            launch_pdl((moe_down_fp4_kernel<4>), g2, 256, (size_t)ef.F * 8 + sc_bytes, st, (const bf16*)act, (const uint8_t*)arena, (const int*)slot_of, ef, (const int*)group_expert,
+                                                                      (const int*)group_n, (const int*)group_pairs, (const int*)n_groups, (float*)y, run);
         LSB_CHECK_LAUNCH();
     }
     if (!group_n) return -1;

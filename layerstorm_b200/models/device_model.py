@@ -102,6 +102,9 @@ MHC_CLUSTER_MAX_ROWS = int(os.environ.get("LSB_MHC_CLUSTER_MAX_ROWS", "8"))
 # ablation switches of the two folds of the cluster kernel (router behind, MoE combine in front)
 MHC_FOLD_ROUTER = os.environ.get("LSB_MHC_FOLD_ROUTER", "0") not in ("", "0")
 MHC_FOLD_COMBINE = os.environ.get("LSB_MHC_FOLD_COMBINE", "0") not in ("", "0")
+# LSB_MOE_RUN_GU / LSB_MOE_RUN_DN: rows of n % 32 per block of the pair-mode NVFP4 expert kernels (gate/up: 8, 4, 2; down: 16, 8, 4); 0 = by GPU count
+MOE_RUN_GU = int(os.environ.get("LSB_MOE_RUN_GU", "0") or 0)
+MOE_RUN_DN = int(os.environ.get("LSB_MOE_RUN_DN", "0") or 0)
 # LSB_COMM_XCHG: how few-row steps do the fused all-reduce - 0 the producer's last block pushes the partial, 1 the consuming kernel
 # exchanges it with one flag per CTA, 2 (default) the consuming kernel exchanges flag-in-data words (no fence, no flag, no barrier)
 COMM_XCHG = int(os.environ.get("LSB_COMM_XCHG", "2") or 0)
@@ -895,14 +898,17 @@ class DeviceModel:
                      ws.tc_cnt, ws.tc_sorted, ws.y, ws.tc_bn, tiles, 0.0, None, err, None)
         elif mode == "pairs":
             # small batch: every (row, slot) pair streams its expert on its own - no grouping pass
-            nat.call("lsb_moe_gateup", ws.x, arena.data, arena.slot_of, efp, ws.ids, None, None, None, ws.act, S, R * S, cfg.swiglu_limit, miss)
-            nat.call("lsb_moe_down", ws.act, arena.data, arena.slot_of, efp, ws.ids, None, None, None, ws.y, R * S)
+            # blocks per expert: finer when this GPU holds only a share of the step's experts (expert parallel), see the kernels
+            run_gu = MOE_RUN_GU or (8 if self.tp_size == 1 else (4 if self.tp_size == 2 else 2))
+            run_dn = MOE_RUN_DN or (16 if self.tp_size == 1 else (8 if self.tp_size == 2 else 4))
+            nat.call("lsb_moe_gateup", ws.x, arena.data, arena.slot_of, efp, ws.ids, None, None, None, ws.act, S, R * S, cfg.swiglu_limit, miss, run_gu)
+            nat.call("lsb_moe_down", ws.act, arena.data, arena.slot_of, efp, ws.ids, None, None, None, ws.y, R * S, run_dn)
         else:
             mg = min(ws.max_groups, min(R * S, (R * S + 3) // 4 + E_total))
             nat.call("lsb_moe_gateup", ws.x, arena.data, arena.slot_of, efp, ws.group_expert, ws.group_n, ws.group_pairs, ws.n_groups,
-                     ws.act, S, mg, cfg.swiglu_limit, miss)
+                     ws.act, S, mg, cfg.swiglu_limit, miss, 0)
             nat.call("lsb_moe_down", ws.act, arena.data, arena.slot_of, efp, ws.group_expert, ws.group_n, ws.group_pairs, ws.n_groups,
-                     ws.y, mg)
+                     ws.y, mg, 0)
 
     def _kda(self, i: int, L: dict, ws: Workspace, R: int, nseq: int):
         cfg = self.cfg

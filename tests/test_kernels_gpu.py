@@ -221,6 +221,43 @@ def test_router_fused_projection_and_topk(E, k, n_group, topk_group, R):
     assert torch.equal(ids, ids2) and torch.equal(wts, wts2)
 
 
+def test_moe_pair_kernels_give_the_same_bits_for_every_block_shape():
+    """Pair-mode NVFP4 expert kernels: the rows of an expert can be cut into blocks of 32 / 16 / 8 (gate, up) and 64 / 32 / 16 (down)
+    rows; the per-row arithmetic does not depend on the cut, so all shapes give identical bits, and they match fp32 math."""
+    import ctypes
+    from layerstorm_b200.models.device_model import ExpertArena, QLinear, expert_layout
+    H, F, E, k, R = 512, 768, 6, 3, 2
+    S = k + 1
+    g = torch.Generator().manual_seed(7)
+    arena = ExpertArena(expert_layout("nvfp4", H, F), E + 1, E + 1, DEV)
+    mats = []
+    for e in range(E + 1):
+        gate, up, down = (QLinear.from_float(torch.randn(n_, k_, generator=g) * 0.05, "nvfp4", DEV) for n_, k_ in ((F, H), (F, H), (H, F)))
+        arena.write_expert(e, gate, up, down)
+        arena.slot_of[e] = e
+        mats.append((gate.dequant().cpu(), up.dequant().cpu(), down.dequant().cpu()))
+    efp = ctypes.addressof(arena.ef)
+    x = rnd(R, H, dtype=torch.bfloat16, seed=8)
+    ids = torch.stack([torch.cat([torch.randperm(E, generator=g)[:k], torch.tensor([E])]) for _ in range(R)]).int().to(DEV)
+    outs = []
+    for run_gu, run_dn in ((8, 16), (4, 8), (2, 4)):
+        act = torch.zeros(R * S, F, dtype=torch.bfloat16, device=DEV)
+        y = torch.zeros(R * S, H, device=DEV)
+        nat.call("lsb_moe_gateup", x, arena.data, arena.slot_of, efp, ids, None, None, None, act, S, R * S, 10.0, None, run_gu)
+        nat.call("lsb_moe_down", act, arena.data, arena.slot_of, efp, ids, None, None, None, y, R * S, run_dn)
+        torch.cuda.synchronize()
+        outs.append((act.clone(), y.clone()))
+    for a, y in outs[1:]:
+        assert torch.equal(a, outs[0][0]) and torch.equal(y, outs[0][1])
+    xf = x.float().cpu()
+    for r in range(R):
+        for s_ in range(S):
+            gm, um, dm = mats[int(ids[r, s_])]
+            gv, uv = (xf[r] @ gm.T).clamp(max=10.0), (xf[r] @ um.T).clamp(-10.0, 10.0)
+            want = (torch.nn.functional.silu(gv) * uv).to(torch.bfloat16).float() @ dm.T
+            close(outs[0][1][r * S + s_], want, 2e-2, 2e-2 * float(want.abs().max()), "expert output")
+
+
 @pytest.mark.parametrize("scoring", ["sigmoid", "softmax", "sqrtsoftplus"])
 def test_router_hash(scoring):
     E, k, R, V = 48, 6, 7, 100

@@ -184,3 +184,33 @@ def test_loader_solver_tiers_agree_with_brute_force():
     # a resident expert stays where it is when that is free of charge
     a, c, _ = sv.solve([0], [14_000_000], [[False, True, False]], [1, 1, 1])
     assert a == [1] and c == 16000 + 64000
+
+
+def test_page_swap_out_and_in_for_kv_tiering():
+    """Tiering of an active sequence: a completely filled private page behind the frontier gives its HBM page back (block-table
+    entry -1) and gets a fresh one on promotion; shared pages, the frontier page and holes cannot be swapped or forked."""
+    from layerstorm_b200.runtime import native as rt
+    pa = rt.PageAllocator([6], 16)
+    pa.create(0)
+    pa.extend(0, 40)                                   # pages 0, 1 full, page 2 holds 8 tokens
+    assert pa.free_pages() == 3
+    released = pa.swap_out(0, 0)
+    assert pa.pages(0)[0] == -1 and pa.free_pages() == 4 and released >= 0
+    with pytest.raises(rt.NativeError):
+        pa.swap_out(0, 0)                              # already out
+    with pytest.raises(rt.NativeError):
+        pa.swap_out(0, 2)                              # the frontier page is not full
+    with pytest.raises(rt.NativeError):
+        pa.fork(0, 1, 32)                              # a hole cannot be shared
+    pa.extend(0, 64)                                   # growing past a hole works
+    assert len(pa.pages(0)) == 4 and pa.pages(0)[0] == -1
+    pg = pa.swap_in(0, 0)
+    assert pa.pages(0)[0] == pg >= 0
+    pa.fork(0, 1, 32)
+    with pytest.raises(rt.NativeError):
+        pa.swap_out(0, 1)                              # shared with the fork
+    pa.destroy(1)
+    pa.swap_out(0, 1)
+    pa.rewind(0, 8)                                    # releasing a range that contains a hole
+    pa.destroy(0)
+    assert pa.free_pages() == 6

@@ -97,7 +97,8 @@ def streamed_bytes_per_step(model, batch: int) -> int:
             if isinstance(v, QLinear):
                 tot += v.nbytes()
             elif isinstance(v, ExpertArena):
-                per_rank = (min(cfg.n_routed, batch * cfg.top_k) + model.tp_size - 1) // model.tp_size + cfg.n_shared
+                hit = min(cfg.n_routed, batch * cfg.top_k)
+                per_rank = hit + cfg.n_shared if model.expert_shard == "tp" else (hit + model.tp_size - 1) // model.tp_size + cfg.n_shared
                 tot += min(v.n_slots, per_rank) * v.ef.stride
             elif hasattr(v, "numel") and not isinstance(v, tuple):
                 tot += v.numel() * v.element_size()
@@ -125,6 +126,8 @@ def main():
     ap.add_argument("--tp", type=int, default=0, help="tensor-parallel degree (0 = the number of GPUs; other values are refused: attention, "
                                                       "KDA and dense FFN are sharded over all ranks of the job)")
     ap.add_argument("--ep", type=int, default=0, help="expert-parallel degree (0 = the number of GPUs; other values are refused)")
+    ap.add_argument("--expert-shard", default=None, choices=["ep", "tp"],
+                    help="N > 1 GPUs: 'ep' = whole experts, expert e on GPU e %% N; 'tp' = every GPU holds a 1/N slice of every expert (default: tp)")
     ap.add_argument("--dcp-chunk", type=int, default=0,
                     help="N > 1 GPUs: shard the latent KV cache over the ranks in chunks of this many tokens (context parallel); 0 = replicated")
     ap.add_argument("--layers", type=int, default=0, help="smoke runs only: keep the first N layers (the JSON line is then marked invalid)")
@@ -177,7 +180,7 @@ def main():
     # as many routed-expert slots per layer as fit in HBM next to the other weights; any remainder
     # would be streamed from pinned host RAM by the expert cache
     model = DeviceModel.random_init(cfg, dev, kv_fmt="fp8", page=64, seed=1234, expert_slots="auto", embed_on_host=True,
-                                    reserve_bytes=headroom, tp_rank=rank, tp_size=world)
+                                    reserve_bytes=headroom, tp_rank=rank, tp_size=world, expert_shard=args.expert_shard)
     slots = getattr(model, "expert_slots", cfg.n_routed)
     owned = max(sum(1 for e in range(cfg.n_routed + cfg.n_shared) if model.owns_expert(i, e)) for i in range(cfg.n_layers) if cfg.is_moe_layer(i)) \
         if cfg.n_routed else 0
@@ -192,7 +195,7 @@ def main():
         extra, bmax = [], args.batch
         headroom = fixed + per_seq * bmax + int(0.04 * 2 ** 30) * bmax
         model = DeviceModel.random_init(cfg, dev, kv_fmt="fp8", page=64, seed=1234, expert_slots="auto", embed_on_host=True,
-                                        reserve_bytes=headroom, tp_rank=rank, tp_size=world)
+                                        reserve_bytes=headroom, tp_rank=rank, tp_size=world, expert_shard=args.expert_shard)
         slots = getattr(model, "expert_slots", cfg.n_routed)
     if world > 1:
         # in-kernel NVLink all-reduce buffers (peer-mapped) sized for the largest step (a prefill chunk); NCCL only bootstraps
@@ -333,7 +336,7 @@ def main():
             "vs_baseline": round(main_r["tok_s"] / BASELINE_DECODE_8K, 3) if headline else None,
             "dtype": "bf16", "data": "synthetic token ids, random-init weights",
             "config": {"model": cfg.name + "-shape", "global_batch": args.batch, "seq_len": args.ctx,
-                       "parallelism": f"tp{world}ep{world}" if world > 1 else "single-gpu",
+                       "parallelism": (f"tp{world}" + (f"ep{world}" if model.expert_shard == "ep" else f" (experts sliced over the {world} GPUs)")) if world > 1 else "single-gpu",
                        "weights": f"experts {cfg.expert_quant}, attention {cfg.dense_quant}",
                        "kv_cache": "fp8+bf16-rope, 64-token pages" + (f", sharded over the ranks in {args.dcp_chunk}-token chunks" if (world > 1 and args.dcp_chunk > 0) else ""),
                        "l2": f"inputs larger than L2 (each step streams {main_r['weights_streamed_gb_per_step_per_gpu']} GB of weights per GPU; L2 is 0.126 GB)",

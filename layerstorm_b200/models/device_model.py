@@ -403,7 +403,7 @@ class Workspace:
             self.y = z(R * S, H)
             self.miss = z(1, dtype=i32)
             # tensor-core grouped path (many rows): expert-sorted fp16 operands and the device-built tile list
-            self.tc_ok = R >= TC_MOE_MIN_ROWS and H % 64 == 0 and H % 128 == 0 and cfg.moe_inter % 128 == 0
+            self.tc_ok = R >= TC_MOE_MIN_ROWS and H % 64 == 0 and H % 128 == 0 and m.Fe % 128 == 0
             if self.tc_ok:
                 P = R * S
                 avg = P / max(1, min(E_total, P))
@@ -423,8 +423,20 @@ class Workspace:
 
 
 class DeviceModel:
-    def __init__(self, cfg: ModelConfig, device="cuda", kv_fmt: str = "fp8", page: int = 64, tp_rank: int = 0, tp_size: int = 1):
+    def __init__(self, cfg: ModelConfig, device="cuda", kv_fmt: str = "fp8", page: int = 64, tp_rank: int = 0, tp_size: int = 1,
+                 expert_shard: Optional[str] = None):
+        """``expert_shard``: how the experts are spread over ``tp_size`` GPUs - ``"ep"`` routed expert e lives whole on GPU e % N (the
+        shared expert of layer i on GPU i % N), ``"tp"`` every GPU holds a 1/N slice of EVERY expert (gate / up rows, down columns).
+        Both end in the same cross-rank sum.  ``"tp"`` gives every GPU the same work whatever the router picks, which is what a
+        decode step wants (with ``"ep"`` a token's 8 experts land 4-0-3-1 on 4 GPUs and the step waits for the fullest one);
+        default: ``LSB_EXPERT_SHARD``, else ``"tp"`` whenever the expert width divides into slices of 128."""
         self.cfg, self.device = cfg, torch.device(device)
+        if expert_shard is None:
+            expert_shard = os.environ.get("LSB_EXPERT_SHARD") or ("tp" if (tp_size > 1 and cfg.n_routed and cfg.moe_inter % (128 * tp_size) == 0) else "ep")
+        if expert_shard == "tp" and (tp_size == 1 or cfg.moe_inter % tp_size):
+            expert_shard = "ep"
+        self.expert_shard = expert_shard
+        self.Fe = cfg.moe_inter // tp_size if expert_shard == "tp" else cfg.moe_inter        # expert width held by this GPU
         self.kv_fmt, self.page = kv_fmt, page
         assert page % max(cfg.index_kpool, 1) == 0
         # Tensor / expert parallel layout (one process per GPU): attention heads, KDA heads, dense FFN
@@ -509,6 +521,8 @@ class DeviceModel:
             dist.all_reduce(ws.sub[:R])
 
     def owns_expert(self, layer: int, e: int) -> bool:
+        if self.expert_shard == "tp":
+            return True                      # a slice of every expert
         if e < self.cfg.n_routed:
             return e % self.tp_size == self.tp_rank
         return layer % self.tp_size == self.tp_rank
@@ -529,8 +543,8 @@ class DeviceModel:
     @classmethod
     def from_state_dict(cls, cfg: ModelConfig, w: Dict[str, torch.Tensor], device="cuda", kv_fmt="fp8", page=64,
                         expert_quant: Optional[str] = None, dense_quant: Optional[str] = None, tp_rank: int = 0,
-                        tp_size: int = 1) -> "DeviceModel":
-        m = cls(cfg, device, kv_fmt, page, tp_rank, tp_size)
+                        tp_size: int = 1, expert_shard: Optional[str] = None) -> "DeviceModel":
+        m = cls(cfg, device, kv_fmt, page, tp_rank, tp_size, expert_shard)
         dev = m.device
         tr, ts = tp_rank, tp_size
 
@@ -545,7 +559,7 @@ class DeviceModel:
         dq = dense_quant or cfg.dense_quant
         if eq.startswith("gguf"):
             # GGUF expert tensors: Q4_K runs natively; the other ggml types are expanded at load time
-            eq = "gguf_q4_k" if (eq in ("gguf", "gguf_q4_k") and cfg.hidden % 256 == 0 and cfg.moe_inter % 256 == 0) else "bf16"
+            eq = "gguf_q4_k" if (eq in ("gguf", "gguf_q4_k") and cfg.hidden % 256 == 0 and m.Fe % 256 == 0 and m.expert_shard != "tp") else "bf16"
         f32 = lambda t: t.to(dev).float().contiguous()
         m.embed = w["embed.weight"].to(dev).to(torch.bfloat16).contiguous()
         m.head = QLinear.from_float(rows(w["head.weight"], cfg.vocab, 1), "bf16", dev)
@@ -592,13 +606,20 @@ class DeviceModel:
                 mo = p + "moe."
                 L["router"] = QLinear.from_float(w[mo + "router"], "f32", dev)
                 L["router_bias"] = f32(w[mo + "router_bias"]) if (mo + "router_bias") in w else None
-                ef = expert_layout(eq, cfg.hidden, cfg.moe_inter)
+                ef = expert_layout(eq, cfg.hidden, m.Fe)
                 E_total = cfg.n_routed + cfg.n_shared
                 mine = [e for e in range(E_total) if m.owns_expert(i, e)]
                 arena = ExpertArena(ef, max(len(mine), 1), E_total, dev)
                 for s_, e in enumerate(mine):
                     nm = mo + (f"experts.{e}." if e < cfg.n_routed else f"shared.{e - cfg.n_routed}.")
-                    arena.write_expert(s_, *(m._expert_lin(w, nm + t, eq) for t in ("gate", "up", "down")))
+                    if m.expert_shard == "tp":
+                        # this GPU's slice of the expert: rows of gate / up, columns of down
+                        f0, f1 = tr * m.Fe, (tr + 1) * m.Fe
+                        parts = (QLinear.from_float(w[nm + "gate"][f0:f1], eq, dev), QLinear.from_float(w[nm + "up"][f0:f1], eq, dev),
+                                 QLinear.from_float(w[nm + "down"][:, f0:f1].contiguous(), eq, dev))
+                        arena.write_expert(s_, *parts)
+                    else:
+                        arena.write_expert(s_, *(m._expert_lin(w, nm + t, eq) for t in ("gate", "up", "down")))
                     arena.slot_of[e] = s_
                 L["arena"] = arena
             else:
@@ -611,19 +632,20 @@ class DeviceModel:
 
     @classmethod
     def random_init(cls, cfg: ModelConfig, device="cuda", kv_fmt="fp8", page=64, seed=0, expert_slots=None,
-                    embed_on_host: bool = False, reserve_bytes: int = 4 << 30, tp_rank: int = 0, tp_size: int = 1) -> "DeviceModel":
+                    embed_on_host: bool = False, reserve_bytes: int = 4 << 30, tp_rank: int = 0, tp_size: int = 1,
+                    expert_shard: Optional[str] = None) -> "DeviceModel":
         """Random weights generated directly in storage format on the device (full-size models).
         ``expert_slots`` caps the routed-expert slots per MoE layer (VRAM expert cache): an int, None
         (all experts resident) or "auto" (as many as fit while leaving ``reserve_bytes`` of device
         memory free for caches and workspaces).  The first slots hold the shared experts followed by
         routed experts 0..; the rest start non-resident."""
-        m = cls(cfg, device, kv_fmt, page, tp_rank, tp_size)
+        m = cls(cfg, device, kv_fmt, page, tp_rank, tp_size, expert_shard)
         dev = m.device
         gen = torch.Generator(device=dev).manual_seed(seed)                          # replicated tensors: same on every rank
         gloc = torch.Generator(device=dev).manual_seed(seed * 7919 + 1 + tp_rank)    # this rank's shards
         dq, eq = cfg.dense_quant, cfg.expert_quant
         if eq.startswith("gguf"):
-            eq = "gguf_q4_k" if (cfg.hidden % 256 == 0 and cfg.moe_inter % 256 == 0) else "nvfp4"
+            eq = "gguf_q4_k" if (cfg.hidden % 256 == 0 and m.Fe % 256 == 0) else "nvfp4"
         H = cfg.hidden
 
         def nrm(n):
@@ -695,14 +717,14 @@ class DeviceModel:
             m.layers.append(L)
         moe_layers = [(i, L) for i, L in enumerate(m.layers) if "arena" in L]
         if moe_layers:
-            ef = expert_layout(eq, H, cfg.moe_inter)
+            ef = expert_layout(eq, H, m.Fe)
             E_total = cfg.n_routed + cfg.n_shared
             max_owned = max(sum(1 for e in range(E_total) if m.owns_expert(i, e)) for i, _ in moe_layers)
             if expert_slots == "auto":
                 free_b, _ = torch.cuda.mem_get_info(dev)
                 free_b += torch.cuda.memory_reserved(dev) - torch.cuda.memory_allocated(dev)
                 fit = int((free_b - reserve_bytes) // (ef.stride * len(moe_layers)))
-                n_slots = max(cfg.top_k // tp_size + cfg.n_shared, min(max_owned, fit))
+                n_slots = max((cfg.top_k if m.expert_shard == "tp" else cfg.top_k // tp_size) + cfg.n_shared, min(max_owned, fit))
             elif expert_slots is None:
                 n_slots = max_owned
             else:
@@ -867,7 +889,7 @@ class DeviceModel:
         cfg = self.cfg
         if getattr(ws, "tc_ok", False) and R >= TC_MOE_MIN_ROWS:
             return "tc"
-        fast_fp4 = arena.ef.fmt == 2 and cfg.moe_inter % 128 == 0 and cfg.hidden % 128 == 0
+        fast_fp4 = arena.ef.fmt == 2 and self.Fe % 128 == 0 and cfg.hidden % 128 == 0
         return "pairs" if (fast_fp4 and R * ws.S <= 72) else "groups"
 
     def _moe_prepare(self, arena: ExpertArena, ws: Workspace, R: int):

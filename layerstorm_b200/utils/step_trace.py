@@ -43,6 +43,7 @@ def main(argv=None) -> int:
     ap.add_argument("--prefill", action="store_true", help="compute the context with chunked prefill instead of marking it filled")
     ap.add_argument("--prefill-chunk", type=int, default=2048)
     ap.add_argument("--headroom-gib", type=float, default=4.0)
+    ap.add_argument("--expert-shard", default=None, choices=["ep", "tp"])
     ap.add_argument("--by-call", action="store_true", help="aggregate by launcher call only (not by grid shape)")
     ap.add_argument("--sequence", action="store_true", help="also print the kernels of one step in launch order")
     a = ap.parse_args(argv)
@@ -69,7 +70,7 @@ def main(argv=None) -> int:
             repl["layer_types"] = list(cfg.layer_types[:a.layers])
         cfg = dataclasses.replace(cfg, **repl)
     model = DeviceModel.random_init(cfg, dev, kv_fmt="fp8", page=64, seed=1234, expert_slots="auto", embed_on_host=True,
-                                    reserve_bytes=int(a.headroom_gib * 2 ** 30), tp_rank=rank, tp_size=world)
+                                    reserve_bytes=int(a.headroom_gib * 2 ** 30), tp_rank=rank, tp_size=world, expert_shard=a.expert_shard)
     if world > 1:
         from ..parallel.symm import PeerComm
         model.attach_comm(PeerComm(max(4, a.batch, a.prefill_chunk if a.prefill else 4) * cfg.hidden, dev), PeerComm(2 * max(a.batch, 4), dev))

@@ -12,11 +12,12 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-@pytest.mark.parametrize("name", ["tiny-glm5-next", "tiny-mla-moe"])
-def test_two_rank_engine_matches_oracle(name):
+@pytest.mark.parametrize("name,shard", [("tiny-glm5-next", "ep"), ("tiny-mla-moe", "ep"), ("tiny-glm5-next", "tp"), ("tiny-mla-moe", "tp")])
+def test_two_rank_engine_matches_oracle(name, shard):
+    """``shard``: whole experts per GPU (expert parallel) or a slice of every expert on every GPU (tensor parallel experts)."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", LSB_EXPERT_SHARD=shard)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
            "--master-port", "29533", os.path.join(HERE, "mgpu_worker.py"), name]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)

@@ -921,8 +921,10 @@ class DeviceModel:
         elif mode == "pairs":
             # small batch: every (row, slot) pair streams its expert on its own - no grouping pass
             # blocks per expert: finer when this GPU holds only a share of the step's experts (expert parallel), see the kernels
+            # (sliced experts keep every expert on every GPU with 1/N of the rows of gate / up and 1/N of the columns of down: the
+            # down projection keeps its row count, so it keeps the widest block)
             run_gu = MOE_RUN_GU or (8 if self.tp_size == 1 else (4 if self.tp_size == 2 else 2))
-            run_dn = MOE_RUN_DN or (16 if self.tp_size == 1 else (8 if self.tp_size == 2 else 4))
+            run_dn = MOE_RUN_DN or (16 if self.tp_size == 1 or self.expert_shard == "tp" else (8 if self.tp_size == 2 else 4))
             nat.call("lsb_moe_gateup", ws.x, arena.data, arena.slot_of, efp, ws.ids, None, None, None, ws.act, S, R * S, cfg.swiglu_limit, miss, run_gu)
             nat.call("lsb_moe_down", ws.act, arena.data, arena.slot_of, efp, ws.ids, None, None, None, ws.y, R * S, run_dn)
         else:

@@ -94,6 +94,9 @@ ROUTER_FUSED = os.environ.get("LSB_ROUTER_FUSED", "0") != "0"
 # (kda_chunk_prep / kda_chunk_scan).  Chunk-parallel is the default: on a B200 its logits are as close to the fp32 oracle as the token
 # recurrence's (1.1e-3 .. 1.8e-3 relative on the tiny model against 1.1e-3 .. 8.6e-3) and a 2048-token chunk is faster.
 KDA_CHUNKED = os.environ.get("LSB_KDA_CHUNKED", "1") not in ("", "0")
+# LSB_MOE_BLOCK_SCALED=1: many-row steps over NVFP4 experts quantise the activations to NVFP4 (one scale per 16 elements and
+# one per row) and run the block-scaled tensor-core kernel (4-bit x 4-bit) instead of expanding the weights to fp16
+MOE_BLOCK_SCALED = os.environ.get("LSB_MOE_BLOCK_SCALED", "0") not in ("", "0")
 # LSB_MHC_CLUSTER=0: decode-sized hyper-connection passes fall back to the two-launch path (partials + last-block finalize, contraction)
 MHC_CLUSTER = os.environ.get("LSB_MHC_CLUSTER", "1") not in ("", "0")
 # rows of a step up to which the cluster kernel (one cluster per row) is used; above it the partial + last-block-finalize kernels, which
@@ -412,8 +415,18 @@ class Workspace:
                 self.tc_sorted = z(P, dtype=i32)
                 self.tc_tile_e = z(self.tc_tiles, dtype=i32); self.tc_tile_r0 = z(self.tc_tiles, dtype=i32)
                 self.tc_tile_n = z(self.tc_tiles, dtype=i32); self.tc_cnt = z(2, dtype=i32)
-                self.tc_xs = z(P, H, dtype=torch.float16)
-                self.tc_act = z(P, cfg.moe_inter, dtype=torch.float16)
+                # block-scaled path (NVFP4 experts): both operands stay 4-bit, the activations are quantised in tile order
+                fmts = {L["arena"].ef.fmt for L in m.layers if L.get("arena") is not None}
+                self.bs_ok = MOE_BLOCK_SCALED and fmts == {2} and H % 256 == 0 and m.Fe % 256 == 0 and H <= 8192 and m.Fe <= 8192
+                if self.bs_ok:
+                    rows = self.tc_tiles * self.tc_bn
+                    u8 = torch.uint8
+                    self.bs_xq = z(rows, H // 2, dtype=u8); self.bs_xsf = z(self.tc_tiles * (H // 64) * 512, dtype=u8); self.bs_xa = z(rows)
+                    self.bs_act = z(rows, m.Fe, dtype=torch.float16)
+                    self.bs_aq = z(rows, m.Fe // 2, dtype=u8); self.bs_asf = z(self.tc_tiles * (m.Fe // 64) * 512, dtype=u8); self.bs_aa = z(rows)
+                else:
+                    self.tc_xs = z(P, H, dtype=torch.float16)
+                    self.tc_act = z(P, cfg.moe_inter, dtype=torch.float16)
         # outputs
         self.n_logit_rows = n_logit_rows
         self.logits = z(n_logit_rows, m.V_local)
@@ -900,7 +913,11 @@ class DeviceModel:
         if mode == "tc":
             P = R * S
             nat.call("lsb_moe_tc_sort", ws.ids, P, E_total, ws.tc_bn, ws.tc_sorted, ws.tc_tile_e, ws.tc_tile_r0, ws.tc_tile_n, ws.tc_cnt)
-            nat.call("lsb_moe_tc_gather", ws.x, ws.tc_sorted, ws.tc_cnt, ws.tc_xs, P, S, cfg.hidden)
+            if ws.bs_ok:
+                nat.call("lsb_quant_nvfp4_tiles", ws.x, 0, ws.tc_sorted, ws.tc_tile_r0, ws.tc_tile_n, ws.tc_cnt, S, cfg.hidden, ws.tc_bn,
+                         min(ws.tc_tiles, P // ws.tc_bn + E_total + 1), ws.bs_xq, ws.bs_xsf, ws.bs_xa)
+            else:
+                nat.call("lsb_moe_tc_gather", ws.x, ws.tc_sorted, ws.tc_cnt, ws.tc_xs, P, S, cfg.hidden)
         elif mode == "groups":
             nat.call("lsb_moe_build_groups", ws.ids, R * S, E_total, ws.group_expert, ws.group_n, ws.group_pairs, ws.n_groups, ws.counts)
 
@@ -914,6 +931,13 @@ class DeviceModel:
             P = R * S
             err = TcScratch.get(self.device).err
             tiles = min(ws.tc_tiles, P // ws.tc_bn + E_total + 1)
+            if ws.bs_ok:
+                a = (arena.data, arena.slot_of, efp, ws.tc_tile_e, ws.tc_tile_r0, ws.tc_tile_n, ws.tc_cnt, ws.tc_sorted)
+                nat.call("lsb_moe_bs_ffn", 1, ws.bs_xq, ws.bs_xsf, ws.bs_xa, *a, ws.bs_act, ws.tc_bn, tiles, cfg.swiglu_limit, miss, err)
+                nat.call("lsb_quant_nvfp4_tiles", ws.bs_act, 1, None, ws.tc_tile_r0, ws.tc_tile_n, ws.tc_cnt, S, self.Fe, ws.tc_bn, tiles,
+                         ws.bs_aq, ws.bs_asf, ws.bs_aa)
+                nat.call("lsb_moe_bs_ffn", 0, ws.bs_aq, ws.bs_asf, ws.bs_aa, *a, ws.y, ws.tc_bn, tiles, 0.0, None, err)
+                return
             nat.call("lsb_moe_tc_ffn", 1, ws.tc_xs, ws.tc_xs.shape[0], arena.data, arena.slot_of, efp, ws.tc_tile_e, ws.tc_tile_r0, ws.tc_tile_n,
                      ws.tc_cnt, ws.tc_sorted, ws.tc_act, ws.tc_bn, tiles, cfg.swiglu_limit, miss, err, None)
             nat.call("lsb_moe_tc_ffn", 0, ws.tc_act, ws.tc_act.shape[0], arena.data, arena.slot_of, efp, ws.tc_tile_e, ws.tc_tile_r0, ws.tc_tile_n,

@@ -128,12 +128,17 @@ def main():
     ap.add_argument("--ep", type=int, default=0, help="expert-parallel degree (0 = the number of GPUs; other values are refused)")
     ap.add_argument("--expert-shard", default=None, choices=["ep", "tp"],
                     help="N > 1 GPUs: 'ep' = whole experts, expert e on GPU e %% N; 'tp' = every GPU holds a 1/N slice of every expert (default: tp)")
+    ap.add_argument("--moe-block-scaled", action="store_true",
+                    help="many-row steps (prefill chunks, batch >= 16) quantise the expert activations to NVFP4 and run the 4-bit x 4-bit "
+                         "block-scaled tensor-core kernel (the reference's NVFP4 expert path does the same); default: bf16 -> fp16 activations")
     ap.add_argument("--dcp-chunk", type=int, default=0,
                     help="N > 1 GPUs: shard the latent KV cache over the ranks in chunks of this many tokens (context parallel); 0 = replicated")
     ap.add_argument("--layers", type=int, default=0, help="smoke runs only: keep the first N layers (the JSON line is then marked invalid)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
+    if args.moe_block_scaled:
+        os.environ["LSB_MOE_BLOCK_SCALED"] = "1"
     if args.warmup < 3:
         args.warmup = 3
     extra = [int(x) for x in args.extra_batches.split(",") if x.strip() and int(x) != args.batch]
@@ -338,6 +343,7 @@ def main():
             "config": {"model": cfg.name + "-shape", "global_batch": args.batch, "seq_len": args.ctx,
                        "parallelism": (f"tp{world}" + (f"ep{world}" if model.expert_shard == "ep" else f" (experts sliced over the {world} GPUs)")) if world > 1 else "single-gpu",
                        "weights": f"experts {cfg.expert_quant}, attention {cfg.dense_quant}",
+                       "expert_activations_many_rows": "nvfp4 (block-scaled 4-bit x 4-bit MMA)" if os.environ.get("LSB_MOE_BLOCK_SCALED", "0") not in ("", "0") else "fp16",
                        "kv_cache": "fp8+bf16-rope, 64-token pages" + (f", sharded over the ranks in {args.dcp_chunk}-token chunks" if (world > 1 and args.dcp_chunk > 0) else ""),
                        "l2": f"inputs larger than L2 (each step streams {main_r['weights_streamed_gb_per_step_per_gpu']} GB of weights per GPU; L2 is 0.126 GB)",
                        "resident_expert_slots_per_layer_per_gpu": slots, "routed_experts": cfg.n_routed, "expert_miss_flag": main_r["expert_miss_flag"],

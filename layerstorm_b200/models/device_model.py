@@ -220,6 +220,19 @@ class QLinear:
         t["x16"] = cls._x16[idx]
         return t
 
+    _bsbuf: Dict[tuple, tuple] = {}
+
+    @classmethod
+    def _bs_operand(cls, device, rows: int, ntiles: int, K: int):
+        """Scratch for the NVFP4 image of a dense activation operand: packed values, scale atoms, per-row scales."""
+        key = (torch.device(device).index or 0, rows, ntiles, K)
+        if key not in cls._bsbuf:
+            if len(cls._bsbuf) > 64:
+                cls._bsbuf.clear()
+            cls._bsbuf[key] = (torch.zeros(rows, K // 2, dtype=torch.uint8, device=device),
+                               torch.zeros(ntiles * (K // 64) * 512, dtype=torch.uint8, device=device), torch.zeros(rows, device=device))
+        return cls._bsbuf[key]
+
     def dequant(self) -> torch.Tensor:
         if self.fmt in ("bf16", "f32"):
             return self.w.float()
@@ -249,6 +262,14 @@ class QLinear:
         if self.fmt == "bf16" and M >= 8:
             sc = TcScratch.get(self.w.device)
             nat.call("lsb_gemm_bf16_tc", out, x, self.w, bias, M, self.N, self.K, ldx, self.K, ldo, ob, sc.partial, sc.cap, sc.err, comm)
+        elif (self.fmt == "nvfp4" and MOE_BLOCK_SCALED and M >= 16 and comm is None and bias is None and ldx == self.K and self.K % 256 == 0
+              and self.K <= 8192 and self.N % 128 == 0):
+            # many rows over NVFP4 weights, block-scaled mode: the rows are quantised to NVFP4 and both operands stay 4-bit
+            t = QLinear._dense_tiles(self.w.device, M)
+            q, sf, al = QLinear._bs_operand(self.w.device, t["n"] * t["bn"], t["n"], self.K)
+            nat.call("lsb_quant_nvfp4_tiles", x, 2, None, t["tr"], t["tn"], t["cnt"], 1, self.K, t["bn"], t["n"], q, sf, al)
+            nat.call("lsb_gemm_nvfp4_bs", out, q, sf, al, self.w, self.scales, self.alpha, self.N, self.K, ldo, ob, t["tr"], t["tn"], t["cnt"],
+                     t["bn"], t["n"], TcScratch.get(self.w.device).err)
         elif (self.fmt in ("fp8_e4m3", "nvfp4", "gguf_q4_k") and M >= 16 and comm is None and bias is None and ldx == self.K and self.K % 64 == 0
               and self.N % 128 == 0 and (self.fmt != "fp8_e4m3" or self.K % 128 == 0) and (self.fmt != "gguf_q4_k" or self.K % 256 == 0)):
             # many rows over quantised weights: de-quantisation fused into the tcgen05 operand pipeline

@@ -172,3 +172,32 @@ def test_grouped_block_scaled_expert_ffn(R, BN):
         assert (y[pairs].double() - ref_y).abs().max().item() < 1e-4 * ref_y.abs().max().item() + 1e-6
         checked += tn_h[t]
     assert checked > 0
+
+
+def test_model_prefill_with_block_scaled_experts_stays_within_quantisation_noise(monkeypatch):
+    """The same NVFP4-expert model prefills a prompt with the fp16-operand path and with the block-scaled path: the logits differ
+    by the activation quantisation only, and the block-scaled kernels really ran (launcher count)."""
+    _need_gpu()
+    import dataclasses
+
+    from layerstorm_b200.models import device_model as dm
+    from layerstorm_b200.models.config import get_preset
+    from layerstorm_b200.models.weights import init_weights
+    from layerstorm_b200.ops import _native as nat
+    from layerstorm_b200.runtime.engine import Engine
+    cfg = dataclasses.replace(get_preset("tiny-glm5-next"), moe_inter=256)
+    w = init_weights(cfg, 0)
+    m = dm.DeviceModel.from_state_dict(cfg, w, "cuda", kv_fmt="bf16", page=16, expert_quant="nvfp4")
+    ids = torch.randint(0, cfg.vocab, (48,), generator=torch.Generator().manual_seed(11)).tolist()
+    out = {}
+    for flag in (False, True):
+        monkeypatch.setattr(dm, "MOE_BLOCK_SCALED", flag)
+        eng = Engine(m, max_seqs=1, max_ctx=128, prefill_chunk=32, max_batch=1, use_graph=False)
+        sid = eng.create_sequence()
+        _, lg = eng.prefill(sid, ids, want_logits=True)
+        assert eng.ws_prefill.bs_ok == flag
+        out[flag] = lg.float().cpu()
+        eng.free_sequence(sid)
+    assert torch.isfinite(out[True]).all()
+    rel = float((out[True] - out[False]).norm() / out[False].norm())
+    assert 0 < rel < 0.12, rel

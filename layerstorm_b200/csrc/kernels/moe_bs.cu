@@ -10,8 +10,9 @@
 //        warp 1      tensor-memory owner; one thread copies the stage's scale atoms shared memory -> tensor memory
 //                    (tcgen05.cp 32x128b.warpx4: 128 rows x 4 group scales become 4 columns, replicated over the four
 //                    lane quarters) and issues 4 (gate/up: 8) block-scaled MMAs of K = 64 per stage
-//        warps 2-5   epilogue: tcgen05.ld, per-tensor weight scale x per-row activation scale, SwiGLU(+clamp) -> fp16
-//                    rows in tile order, or fp32 rows scattered back to pair order
+//        warps 2-9   epilogue (two warps per lane quarter, half of the token columns each): tcgen05.ld, per-tensor weight
+//                    scale x per-row activation scale, SwiGLU(+clamp) -> fp16 rows in tile order, or fp32 rows scattered
+//                    back to pair order
 // The weight bytes and their scale atoms are used exactly as they sit in the expert arena (the arena's NVFP4 scale layout
 // is the tensor core's).  Every wait is bounded and reports through an error word.
 // Reference seams replaced: BF16 -> NVFP4 activation quantisation + NVFP4 grouped GEMM over scattered expert pointers +
@@ -176,7 +177,8 @@ template <int BN, bool GATEUP> struct MoeBsCfg {
     static constexpr int TMEM_COLS = 512;
     static constexpr int BAR_BYTES = 256;
     static constexpr int SMEM = STAGES * STAGE + BAR_BYTES + 1024;
-    static constexpr int THREADS = 6 * 32;
+    static constexpr int EPI_WARPS = 8;                          // two per tensor-memory lane quarter, half of the columns each
+    static constexpr int THREADS = (2 + EPI_WARPS) * 32;
     static_assert(SF_BASE + 2 * SF_COLS <= 512, "tensor memory budget");
     static_assert(STAGES >= 3 && SMEM <= 227 * 1024, "shared memory budget");
 };
@@ -214,7 +216,7 @@ __global__ void __launch_bounds__(MoeBsCfg<BN, GATEUP>::THREADS) moe_bs_ffn_kern
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], C::EPI_WARPS); }
         fence_barrier_init();
         fence_proxy_async();
         tma_prefetch_desc(&map_b);
@@ -317,6 +319,8 @@ __global__ void __launch_bounds__(MoeBsCfg<BN, GATEUP>::THREADS) moe_bs_ffn_kern
     } else {
         // ---------------- epilogue (4 warps: one tensor-memory lane quarter each) ----------------
         const int q = warp & 3;
+        const int chalf = (warp - 2) >> 2;                 // which half of the token columns this warp drains
+        constexpr int CH = BN >= 32 ? BN / 2 : BN;
         uint32_t lt = 0;
         bool ok = true;
         for (int w = blockIdx.x; w < total && ok; w += gridDim.x) {
@@ -342,23 +346,29 @@ __global__ void __launch_bounds__(MoeBsCfg<BN, GATEUP>::THREADS) moe_bs_ffn_kern
                 const uint32_t lane_addr = tmem_d + buf * C::ACC_COLS + ((uint32_t)(q * 32) << 16);
                 const float* xa = p.xalpha + (size_t)t * BN;
 #pragma unroll 1
-                for (int c0 = 0; c0 < BN; c0 += 16) {
+                for (int c0 = chalf * CH; c0 < (chalf + 1) * CH; c0 += 16) {
                     if (c0 >= ncols) break;
+                    // the 16 columns' row scales and output rows: one lane each, handed round by shuffles (the stores below
+                    // may alias anything as far as the compiler knows, so loads inside the store loop would serialise)
+                    const int cl = c0 + (lane & 15);
+                    const float ax_l = cl < ncols ? xa[cl] : 0.f;
+                    int orow_l = row0 + cl;
+                    if (!GATEUP && p.sorted_pair && cl < ncols) orow_l = p.sorted_pair[row0 + cl];
                     float gq[16], uq[16];
                     tmem_ld16(lane_addr + (uint32_t)c0, gq);
                     if (GATEUP) tmem_ld16(lane_addr + (uint32_t)(BN + c0), uq);
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
+                        const float ax = __shfl_sync(0xffffffffu, ax_l, j);
+                        const int orow = __shfl_sync(0xffffffffu, orow_l, j);
                         if (c0 + j < ncols && n < NOUT) {
-                            const float ax = xa[c0 + j];
                             if (GATEUP) {
                                 float gv = gq[j] * sg * ax, uv = uq[j] * su * ax;
                                 if (p.limit > 0.f) { gv = fminf(gv, p.limit); uv = fminf(fmaxf(uv, -p.limit), p.limit); }
                                 p.act[((size_t)t * BN + c0 + j) * NOUT + n] = __float2half_rn(siluf_(gv) * uv);
                             } else {
-                                const size_t orow = p.sorted_pair ? (size_t)p.sorted_pair[row0 + c0 + j] : (size_t)(row0 + c0 + j);
-                                if (p.out_bf16) reinterpret_cast<bf16*>(p.y)[orow * p.ldo + n] = __float2bfloat16(gq[j] * sg * ax);
-                                else reinterpret_cast<float*>(p.y)[orow * p.ldo + n] = gq[j] * sg * ax;
+                                if (p.out_bf16) reinterpret_cast<bf16*>(p.y)[(size_t)orow * p.ldo + n] = __float2bfloat16(gq[j] * sg * ax);
+                                else reinterpret_cast<float*>(p.y)[(size_t)orow * p.ldo + n] = gq[j] * sg * ax;
                             }
                         }
                     }

@@ -29,6 +29,18 @@ struct MatQ4K {
     const uint8_t* w; int K;
     __device__ __forceinline__ WRowQ4K row(int n) const { return WRowQ4K{w + (size_t)n * (K >> 8) * 144}; }
 };
+struct MatQ5K {
+    const uint8_t* w; int K;
+    __device__ __forceinline__ WRowQ5K row(int n) const { return WRowQ5K{w + (size_t)n * (K >> 8) * 176}; }
+};
+struct MatQ6K {
+    const uint8_t* w; int K;
+    __device__ __forceinline__ WRowQ6K row(int n) const { return WRowQ6K{w + (size_t)n * (K >> 8) * kQ6KDevBlock}; }
+};
+struct MatQ80 {
+    const uint8_t* w; int K;
+    __device__ __forceinline__ WRowQ80 row(int n) const { return WRowQ80{w + (size_t)n * (K + (K >> 4)), K}; }
+};
 struct MatNvfp4 {
     const uint8_t* w; int K; const uint8_t* sf; int gtiles;
     __device__ __forceinline__ WRowNvfp4 row(int n) const {
@@ -437,6 +449,57 @@ LSB_API int lsb_gemv_q4k(void* out, const void* x, const void* w, const void* bi
     if (K % 256 || ldx % 8) return -1;
     return launch_gemv(MatQ4K{(const uint8_t*)w, K}, (const bf16*)x, ldx, out, ldo, M, N, K, alpha, (const float*)bias, out_bf16,
                        (cudaStream_t)stream, comm);
+}
+
+// out[n][k] = bf16(W[n][k]) for a GGUF block-type matrix in its device layout: one thread per 32 consecutive elements.
+template <class Mat>
+__global__ void __launch_bounds__(256) gguf_dequant_bf16_kernel(Mat mat, bf16* __restrict__ out, int N, int K) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int n = blockIdx.y;
+    const int k = (blockIdx.x * blockDim.x + threadIdx.x) * 32;
+    if (n >= N || k >= K) return;
+    float f[32];
+    mat.row(n).load(k, f);
+    bf16* o = out + (size_t)n * K + k;
+#pragma unroll
+    for (int i = 0; i < 32; i += 8) {
+        __nv_bfloat162 h[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(f[i + 2 * j], f[i + 2 * j + 1]);
+        *reinterpret_cast<uint4*>(o + i) = *reinterpret_cast<uint4*>(h);
+    }
+}
+
+LSB_API int lsb_gguf_dequant_bf16(void* out, const void* w, int ggml_type, int N, int K, void* stream) {
+    if (K % 256 || ((uintptr_t)w & 15) || ((uintptr_t)out & 15)) return -1;
+    dim3 grid((K / 32 + 255) / 256, N);
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (ggml_type) {
+        case 12: launch_pdl((gguf_dequant_bf16_kernel<MatQ4K>), grid, 256, 0, st, MatQ4K{(const uint8_t*)w, K}, (bf16*)out, N, K); break;
+        case 13: launch_pdl((gguf_dequant_bf16_kernel<MatQ5K>), grid, 256, 0, st, MatQ5K{(const uint8_t*)w, K}, (bf16*)out, N, K); break;
+        case 14: launch_pdl((gguf_dequant_bf16_kernel<MatQ6K>), grid, 256, 0, st, MatQ6K{(const uint8_t*)w, K}, (bf16*)out, N, K); break;
+        case 8: launch_pdl((gguf_dequant_bf16_kernel<MatQ80>), grid, 256, 0, st, MatQ80{(const uint8_t*)w, K}, (bf16*)out, N, K); break;
+        default: return -1;
+    }
+    LSB_CHECK_LAUNCH();
+}
+
+// W: another GGUF block type in its device layout (see gemv_core.cuh): ggml_type 13 = Q5_K (176-byte blocks as in the file),
+// 14 = Q6_K (blocks padded to 224 bytes), 8 = Q8_0 (per row: K quants, then K/32 fp16 scales).  K % 256 == 0.
+LSB_API int lsb_gemv_gguf(void* out, const void* x, const void* w, int ggml_type, const void* bias, int M, int N, int K, int ldx, int ldo,
+                          float alpha, int out_bf16, const void* comm, void* stream) {
+    if (K % 256 || ldx % 8 || ((uintptr_t)w & 15)) return -1;
+    const bf16* xb = (const bf16*)x;
+    const float* bs = (const float*)bias;
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (ggml_type) {
+        case 12: return launch_gemv(MatQ4K{(const uint8_t*)w, K}, xb, ldx, out, ldo, M, N, K, alpha, bs, out_bf16, st, comm);
+        case 13: return launch_gemv(MatQ5K{(const uint8_t*)w, K}, xb, ldx, out, ldo, M, N, K, alpha, bs, out_bf16, st, comm);
+        case 14: return launch_gemv(MatQ6K{(const uint8_t*)w, K}, xb, ldx, out, ldo, M, N, K, alpha, bs, out_bf16, st, comm);
+        case 8: return launch_gemv(MatQ80{(const uint8_t*)w, K}, xb, ldx, out, ldo, M, N, K, alpha, bs, out_bf16, st, comm);
+    }
+    return -1;
 }
 
 LSB_API int lsb_trace_set_gemv(void* buf) { return lsb_trace_install(buf); }

@@ -121,6 +121,90 @@ struct WRowQ4K {
     }
 };
 
+// GGUF Q5_K: 176-byte super-blocks of 256 weights: fp16 d, fp16 dmin, 12 bytes of packed 6-bit (scale, min) pairs (as Q4_K),
+// 32 bytes of fifth bits (bit s of byte l belongs to element l of sub-block s), 128 bytes of low nibbles (as Q4_K).
+// w = d * scale_s * (q4 + 16 * bit) - dmin * min_s.  The block is a multiple of 16 bytes: used as it sits in the file.
+struct WRowQ5K {
+    static constexpr int EPL = 32;
+    const uint8_t* w;    // row start: K/256 blocks of 176 bytes
+    __device__ __forceinline__ void prefetch(int k) const { prefetch_l2(w + (size_t)(k >> 8) * 176); }
+    __device__ __forceinline__ void load(int k, float* f) const {
+        const uint8_t* blk = w + (size_t)(k >> 8) * 176;
+        const int sub = (k & 255) >> 5;
+        const Q4KHeader h = q4k_header(blk);
+        float sc, mn;
+        q4k_scale_min(h.sc, sub, sc, mn);
+        const float a = h.d * sc, b = h.dmin * mn;
+        const uint4 h0 = ldg_stream(blk + 16), h1 = ldg_stream(blk + 32);
+        const uint8_t* qs = blk + 48 + (sub >> 1) * 32;
+        const uint4 v0 = ldg_stream(qs), v1 = ldg_stream(qs + 16);
+        const uint32_t wv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+        const uint32_t hv[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+        const int sh = (sub & 1) * 4;
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const uint32_t q = ((wv[i] >> (8 * c + sh)) & 0xFu) | (((hv[i] >> (8 * c + sub)) & 1u) << 4);
+                f[4 * i + c] = a * (float)q - b;
+            }
+    }
+};
+
+// GGUF Q6_K, device layout: the file's 210-byte super-block (128 bytes of low nibbles, 64 bytes of 2-bit high parts, 16 int8
+// scales of 16 weights each, fp16 d) padded to 224 bytes so that every field is 16-byte aligned; values are untouched.
+// Element y = 128 h + 32 j + l (h half, j quarter, l 0..31): low nibble of ql[64 h + 32 (j & 1) + l] (high nibble for j >= 2),
+// bits 2j, 2j+1 of qh[32 h + l]; w = d * scale[8 h + 2 j + l / 16] * (q - 32).
+constexpr int kQ6KDevBlock = 224;
+struct WRowQ6K {
+    static constexpr int EPL = 32;
+    const uint8_t* w;    // row start: K/256 blocks of 224 bytes
+    __device__ __forceinline__ void prefetch(int k) const { prefetch_l2(w + (size_t)(k >> 8) * kQ6KDevBlock); }
+    __device__ __forceinline__ void load(int k, float* f) const {
+        const uint8_t* blk = w + (size_t)(k >> 8) * kQ6KDevBlock;
+        const int h = (k & 255) >> 7, j = (k & 127) >> 5;
+        const uint8_t* ql = blk + h * 64 + (j & 1) * 32;
+        const uint8_t* qh = blk + 128 + h * 32;
+        const uint4 l0 = ldg_stream(ql), l1 = ldg_stream(ql + 16);
+        const uint4 h0 = ldg_stream(qh), h1 = ldg_stream(qh + 16);
+        const uint4 tail = __ldg(reinterpret_cast<const uint4*>(blk + 192));              // 16 int8 scales
+        const __half dh = __ushort_as_half(__ldg(reinterpret_cast<const unsigned short*>(blk + 208)));
+        const float d = __half2float(dh);
+        const uint32_t scw[4] = {tail.x, tail.y, tail.z, tail.w};
+        const int si = h * 8 + j * 2;
+        const float s0 = d * (float)(int8_t)((scw[si >> 2] >> (8 * (si & 3))) & 0xffu);
+        const float s1 = d * (float)(int8_t)((scw[(si + 1) >> 2] >> (8 * ((si + 1) & 3))) & 0xffu);
+        const uint32_t lv[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
+        const uint32_t hv[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+        const int nsh = (j >> 1) * 4, hsh = j * 2;
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int q = (int)(((lv[i] >> (8 * c + nsh)) & 0xFu) | (((hv[i] >> (8 * c + hsh)) & 3u) << 4)) - 32;
+                f[4 * i + c] = (i < 4 ? s0 : s1) * (float)q;
+            }
+    }
+};
+
+// GGUF Q8_0, device layout per row: K int8 quants, then K/32 fp16 block scales (the file interleaves a scale in front of every
+// 32 quants, which leaves the quants 2-byte aligned; values are untouched).  K % 32 == 0, row pitch K + K/16.
+struct WRowQ80 {
+    static constexpr int EPL = 32;
+    const uint8_t* w;    // row start
+    int K;
+    __device__ __forceinline__ void prefetch(int k) const { prefetch_l2(w + k); }
+    __device__ __forceinline__ void load(int k, float* f) const {
+        const uint4 v0 = ldg_stream(w + k), v1 = ldg_stream(w + k + 16);
+        const float d = __half2float(__ushort_as_half(__ldg(reinterpret_cast<const unsigned short*>(w + K) + (k >> 5))));
+        const uint32_t wv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) f[4 * i + c] = d * (float)(int8_t)((wv[i] >> (8 * c)) & 0xffu);
+    }
+};
+
 // ---- fast NVFP4 path -------------------------------------------------------------------
 // Two E2M1 values per byte convert to an f16x2 with one cvt instruction; products with fp16
 // activations are exact (2 x 8 significant bits), are summed 8 at a time in fp16 and then

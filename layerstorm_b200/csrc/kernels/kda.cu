@@ -28,7 +28,7 @@ __global__ void __launch_bounds__(kD) kda_kernel(KdaParams p) {
     const int seq = blockIdx.x, h = blockIdx.y, t = threadIdx.x;
     // everything read before the dependency wait is written by the host or by the PREVIOUS step, never by the predecessor kernel
     const int row0 = p.seq_row0[seq], nrows = p.seq_nrows[seq], slot = p.seq_slot[seq];
-    if (nrows <= 0) return;
+
     const int C = p.H * kD, ch = h * kD + t;
     const int grb = kda_gate_row_bytes(p.rank);
     {
@@ -45,18 +45,26 @@ __global__ void __launch_bounds__(kD) kda_kernel(KdaParams p) {
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     }
-    // state row
+    // state row (an unused sequence slot of the step: nothing to load, and the block leaves only AFTER the dependency wait - a
+    // grid whose blocks all exit before it would let its successor overtake the predecessor)
+    const bool live = nrows > 0 && slot >= 0;
     float S[kD];
-    float* sp = p.state + (((size_t)slot * p.H + h) * kD + t) * kD;
+    float* sp = p.state + (((size_t)(live ? slot : 0) * p.H + h) * kD + t) * kD;
+    if (live) {
 #pragma unroll
-    for (int c = 0; c < kD; c += 4) {
-        float4 v = *reinterpret_cast<const float4*>(sp + c);
-        S[c] = v.x; S[c + 1] = v.y; S[c + 2] = v.z; S[c + 3] = v.w;
+        for (int c = 0; c < kD; c += 4) {
+            float4 v = *reinterpret_cast<const float4*>(sp + c);
+            S[c] = v.x; S[c + 1] = v.y; S[c + 2] = v.z; S[c + 3] = v.w;
+        }
     }
     const uint8_t* fb = s_gate + (size_t)t * grb;
     const uint8_t* gb = s_gate + (size_t)(kD + t) * grb;
     pdl_wait();
     pdl_launch_dependents();
+    if (!live) {
+        asm volatile("cp.async.wait_group 0;" ::: "memory");     // the gate rows in flight target this block's shared memory
+        return;
+    }
     // conv history (3 raw taps, oldest first) and taps: small, in flight together with the first projection row
     float hq[3], hk[3], hv[3], wq[4], wk[4], wv[4];
     float* csq = p.conv_state + (((size_t)slot * 3 + 0) * C + ch) * 3;
@@ -339,7 +347,7 @@ __global__ void __launch_bounds__(kD) kda_recur_kernel(KdaParams p, KdaScratch w
     pdl_wait();
     pdl_launch_dependents();
     const int row0 = p.seq_row0[seq], nrows = p.seq_nrows[seq], slot = p.seq_slot[seq];
-    if (nrows <= 0) return;
+
     const int C = p.H * kD, ch = h * kD + t;
     float S[kD];
     float* sp = p.state + (((size_t)slot * p.H + h) * kD + t) * kD;

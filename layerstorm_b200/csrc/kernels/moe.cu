@@ -207,6 +207,19 @@ template <> struct RowOf<3> {
     }
 };
 
+template <> struct RowOf<4> {
+    using T = WRowQ5K;
+    static __device__ __forceinline__ T make(const uint8_t* w, const uint8_t*, int n, int K) { return T{w + (size_t)n * (K >> 8) * 176}; }
+};
+template <> struct RowOf<5> {
+    using T = WRowQ6K;
+    static __device__ __forceinline__ T make(const uint8_t* w, const uint8_t*, int n, int K) { return T{w + (size_t)n * (K >> 8) * kQ6KDevBlock}; }
+};
+template <> struct RowOf<6> {
+    using T = WRowQ80;
+    static __device__ __forceinline__ T make(const uint8_t* w, const uint8_t*, int n, int K) { return T{w + (size_t)n * (K + (K >> 4)), K}; }
+};
+
 // act[pair][f] = silu(min(g,limit)) * clamp(u) ; g = x[row] . Wgate[f], u = x[row] . Wup[f]
 template <int FMT>
 __global__ void __launch_bounds__(256) moe_gateup_kernel(const bf16* __restrict__ x, const uint8_t* __restrict__ arena,
@@ -590,6 +603,9 @@ LSB_API int lsb_moe_gateup(const void* x, const void* arena, const void* slot_of
     else if (ef.fmt == 1) launch_pdl((moe_gateup_kernel<1>), grid, 256, 0, st, ARGS);
     else if (ef.fmt == 2) launch_pdl((moe_gateup_kernel<2>), grid, 256, 0, st, ARGS);
     else if (ef.fmt == 3) launch_pdl((moe_gateup_kernel<3>), grid, 256, 0, st, ARGS);
+    else if (ef.fmt == 4) launch_pdl((moe_gateup_kernel<4>), grid, 256, 0, st, ARGS);
+    else if (ef.fmt == 5) launch_pdl((moe_gateup_kernel<5>), grid, 256, 0, st, ARGS);
+    else if (ef.fmt == 6) launch_pdl((moe_gateup_kernel<6>), grid, 256, 0, st, ARGS);
     else return -1;
 #undef ARGS
     LSB_CHECK_LAUNCH();
@@ -600,7 +616,7 @@ LSB_API int lsb_moe_down(const void* act, const void* arena, const void* slot_of
                          void* y, int max_groups, int run, void* stream) {
     ExpertFmt ef = *reinterpret_cast<const ExpertFmt*>(fmt_struct);
     cudaStream_t st = (cudaStream_t)stream;
-    if (ef.fmt == 2 && ef.F % 128 == 0 && ef.H % 128 == 0) {
+    if (ef.down_fmt() == 2 && ef.F % 128 == 0 && ef.H % 128 == 0) {
         if (run != 4 && run != 8) run = 16;                  // values of n % 32 per block (16, 8 or 4; 0 = 16)
         dim3 g2(ef.H / (4 * run), max_groups);
         const size_t sc_bytes = (size_t)(ef.F / 64) * (run * 16 + 4);
@@ -622,10 +638,14 @@ LSB_API int lsb_moe_down(const void* act, const void* arena, const void* slot_of
     dim3 grid((ef.H + 15) / 16, max_groups);
 #define ARGS (const bf16*)act, (const uint8_t*)arena, (const int*)slot_of, ef, (const int*)group_expert, (const int*)group_n, \
              (const int*)group_pairs, (const int*)n_groups, (float*)y
-    if (ef.fmt == 0) launch_pdl((moe_down_kernel<0>), grid, 256, 0, st, ARGS);
-    else if (ef.fmt == 1) launch_pdl((moe_down_kernel<1>), grid, 256, 0, st, ARGS);
-    else if (ef.fmt == 2) launch_pdl((moe_down_kernel<2>), grid, 256, 0, st, ARGS);
-    else if (ef.fmt == 3) launch_pdl((moe_down_kernel<3>), grid, 256, 0, st, ARGS);
+    const int df = ef.down_fmt();
+    if (df == 0) launch_pdl((moe_down_kernel<0>), grid, 256, 0, st, ARGS);
+    else if (df == 1) launch_pdl((moe_down_kernel<1>), grid, 256, 0, st, ARGS);
+    else if (df == 2) launch_pdl((moe_down_kernel<2>), grid, 256, 0, st, ARGS);
+    else if (df == 3) launch_pdl((moe_down_kernel<3>), grid, 256, 0, st, ARGS);
+    else if (df == 4) launch_pdl((moe_down_kernel<4>), grid, 256, 0, st, ARGS);
+    else if (df == 5) launch_pdl((moe_down_kernel<5>), grid, 256, 0, st, ARGS);
+    else if (df == 6) launch_pdl((moe_down_kernel<6>), grid, 256, 0, st, ARGS);
     else return -1;
 #undef ARGS
     LSB_CHECK_LAUNCH();

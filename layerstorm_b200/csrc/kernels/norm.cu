@@ -134,6 +134,7 @@ __global__ void __launch_bounds__(128) mhc_post_partial_kernel(float* __restrict
             const int o = og * kHcPerWarp + i;
             if (lane == 0 && o < kHcOut) po[o] = a;
         }
+        __syncthreads();                              // every warp has read the old streams of this row (in-place update by warp 0)
         if (og == 0) {
             float ss = 0.f;
 #pragma unroll
@@ -216,6 +217,9 @@ __global__ void __launch_bounds__(128) mhc_post_partial_wide_kernel(float* __res
             const int o = og * kHcPerWarp + i;
             if (lane == 0 && o < kHcOut) po[o] = a;
         }
+        // the residual is updated in place by warp 0 while every warp of the block read the old streams of this row above:
+        // all of them must have done so before the store (warps drift apart over the row loop)
+        __syncthreads();
         if (og == 0) {
             float ss = 0.f;
 #pragma unroll
@@ -411,6 +415,7 @@ __global__ void __launch_bounds__(128) mhc_post_fused_kernel(float* __restrict__
                     if (lane == 0) po[kHcOut + e] = g;
                 }
     }
+    __syncthreads();                                  // every warp has read the old streams (in-place update by warp 0)
     if (og == 0) {
 #pragma unroll
         for (int j = 0; j < kHcMax; ++j)

@@ -50,6 +50,59 @@ def quantize(t: int, x: np.ndarray) -> np.ndarray:
     return out
 
 
+# ---- block types the GPU kernels read without re-quantisation, and their device layouts ------------------------------
+# Q4_K and Q5_K blocks are multiples of 16 bytes and are used as they sit in the file.  Q6_K blocks (210 bytes) are padded
+# to 224 so that every field is 16-byte aligned; Q8_0 rows are split into a plane of quants and a plane of fp16 scales (the
+# file puts a 2-byte scale in front of every 32 quants).  Both re-layouts move bytes only: values are bit-identical.
+DEVICE_NATIVE = {12: "gguf_q4_k", 13: "gguf_q5_k", 14: "gguf_q6_k", 8: "gguf_q8_0"}
+DEVICE_TYPE_OF = {v: k for k, v in DEVICE_NATIVE.items()}
+Q6K_DEVICE_BLOCK = 224
+
+
+def device_row_bytes(t: int, K: int) -> int:
+    if t == 12:
+        return K // 256 * 144
+    if t == 13:
+        return K // 256 * 176
+    if t == 14:
+        return K // 256 * Q6K_DEVICE_BLOCK
+    if t == 8:
+        return K + K // 16
+    raise ValueError(f"ggml type {t} has no device layout")
+
+
+def to_device_layout(t: int, raw: np.ndarray, N: int, K: int) -> np.ndarray:
+    """File-order blocks of an [N, K] tensor -> uint8 [N, device_row_bytes]."""
+    raw = np.ascontiguousarray(raw).view(np.uint8).reshape(-1)
+    if K % 256:
+        raise ValueError("device layouts need K % 256 == 0")
+    if t in (12, 13):
+        return raw.reshape(N, -1)
+    if t == 14:
+        nb = N * K // 256
+        out = np.zeros((nb, Q6K_DEVICE_BLOCK), dtype=np.uint8)
+        out[:, :210] = raw.reshape(nb, 210)
+        return out.reshape(N, -1)
+    if t == 8:
+        b = raw.reshape(N, K // 32, 34)
+        return np.ascontiguousarray(np.concatenate([b[:, :, 2:].reshape(N, K), b[:, :, :2].reshape(N, K // 16)], axis=1))
+    raise ValueError(f"ggml type {t} has no device layout")
+
+
+def from_device_layout(t: int, dev: np.ndarray, N: int, K: int) -> np.ndarray:
+    """Inverse of :func:`to_device_layout`: flat file-order blocks."""
+    dev = np.ascontiguousarray(dev).view(np.uint8).reshape(N, -1)
+    if t in (12, 13):
+        return dev.reshape(-1)
+    if t == 14:
+        return np.ascontiguousarray(dev.reshape(-1, Q6K_DEVICE_BLOCK)[:, :210]).reshape(-1)
+    if t == 8:
+        q = dev[:, :K].reshape(N, K // 32, 32)
+        d = dev[:, K:].reshape(N, K // 32, 2)
+        return np.ascontiguousarray(np.concatenate([d, q], axis=2)).reshape(-1)
+    raise ValueError(f"ggml type {t} has no device layout")
+
+
 class GgufReader:
     def __init__(self, path: str):
         self.lib = nt.load()

@@ -301,6 +301,37 @@ class LazyCheckpoint(Mapping):
             return lambda: s.load(name).reshape(c.kda_heads, -1)
         return lambda: s.load(name)
 
+    def native_ggml(self, key: str):
+        """(ggml type, file-order blocks as a flat uint8 array, rows, cols) of an expert matrix whose GGUF tensor is stored in a
+        block type the GPU kernels read natively (Q4_K, Q5_K, Q6_K, Q8_0), else None.  Lets the device model take such experts
+        bit-exactly instead of de-quantising and re-quantising them."""
+        if self.kind != "gguf":
+            return None
+        m = _LAYER_RE.match(key)
+        if not m:
+            return None
+        e = _EXPERT_RE.match(m.group(2))
+        if not e:
+            return None
+        kind, idx, proj = e.group(1), int(e.group(2)), e.group(3)
+        name = f"blk.{int(m.group(1))}.ffn_{proj}_{'exps' if kind == 'experts' else 'shexp'}.weight"
+        s: GgufSource = self.src
+        if not s.has(name):
+            return None
+        from ..formats import gguf as _g
+        t = s.ggml_type(name)
+        if t not in _g.DEVICE_NATIVE:
+            return None
+        r = s.where[name]
+        shape = r.tensor_shape(name)                       # [E, rows, cols] or [rows, cols]
+        rows, cols = int(shape[-2]), int(shape[-1])
+        if cols % 256:
+            return None
+        per = _g.nbytes_for(t, rows * cols)
+        raw = r.raw(name)
+        off = idx * per if (kind == "experts" and len(shape) == 3) else 0
+        return t, np.ascontiguousarray(raw[off: off + per]), rows, cols
+
     def native_q4k(self, key: str) -> Optional[torch.Tensor]:
         """Raw Q4_K super-blocks ([rows, cols / 256 * 144] uint8) of an expert matrix whose GGUF tensor is stored as Q4_K, else
         None.  Lets the device model take such experts bit-exactly instead of de-quantising and re-quantising them."""

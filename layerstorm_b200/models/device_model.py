@@ -26,7 +26,9 @@ from ..ops import _native as nat
 from .config import ModelConfig
 
 KV_FMT = {"bf16": 0, "fp8": 1, "tq4": 2}
-EXPERT_FMT = {"bf16": 0, "fp8_e4m3": 1, "nvfp4": 2, "gguf_q4_k": 3}
+EXPERT_FMT = {"bf16": 0, "fp8_e4m3": 1, "nvfp4": 2, "gguf_q4_k": 3, "gguf_q5_k": 4, "gguf_q6_k": 5, "gguf_q8_0": 6}
+_FMT_NAME = {v: k for k, v in EXPERT_FMT.items()}
+GGML_OF = {"gguf_q4_k": 12, "gguf_q5_k": 13, "gguf_q6_k": 14, "gguf_q8_0": 8}      # storage formats that are GGUF block types
 
 
 class ExpertFmt(ctypes.Structure):
@@ -34,19 +36,34 @@ class ExpertFmt(ctypes.Structure):
                 ("stride", ctypes.c_longlong),
                 ("off_gate", ctypes.c_longlong), ("off_up", ctypes.c_longlong), ("off_down", ctypes.c_longlong),
                 ("off_sg", ctypes.c_longlong), ("off_su", ctypes.c_longlong), ("off_sd", ctypes.c_longlong),
-                ("off_tail", ctypes.c_longlong)]
+                ("off_tail", ctypes.c_longlong), ("fmt_down1", ctypes.c_int)]
 
 
 def _align(x, a):
     return (x + a - 1) // a * a
 
 
-def expert_layout(fmt: str, H: int, F: int) -> ExpertFmt:
+def expert_layout(fmt: str, H: int, F: int, down_fmt: Optional[str] = None) -> ExpertFmt:
     """Byte layout of one expert slot (gate | up | down weights, then their scales, then a tail
     of per-tensor scales), slot stride 4096-aligned like the reference's prepacked slots
-    (src/model/weight_pipeline/prepacked_format.h:44-52)."""
+    (src/model/weight_pipeline/prepacked_format.h:44-52).  ``down_fmt``: GGUF files mix block types per tensor; the down
+    matrix may be another GGUF block type than gate / up."""
     ef = ExpertFmt()
     ef.fmt, ef.H, ef.F = EXPERT_FMT[fmt], H, F
+    if fmt in GGML_OF and (fmt != "gguf_q4_k" or (down_fmt or fmt) != fmt):
+        from ..formats import gguf as _gguf
+        dfmt = down_fmt or fmt
+        if dfmt not in GGML_OF or H % 256 or F % 256:
+            raise ValueError("GGUF block-type experts need hidden and intermediate sizes that are multiples of 256 and a GGUF block type for the down matrix")
+        gu = _align(F * _gguf.device_row_bytes(GGML_OF[fmt], H), 256)
+        dn = _align(H * _gguf.device_row_bytes(GGML_OF[dfmt], F), 256)
+        ef.off_gate, ef.off_up, ef.off_down = 0, gu, 2 * gu
+        ef.off_sg = ef.off_su = ef.off_sd = ef.off_tail = 2 * gu + dn
+        ef.fmt_down1 = 0 if dfmt == fmt else EXPERT_FMT[dfmt] + 1
+        ef.stride = _align(2 * gu + dn, 4096)
+        return ef
+    if down_fmt not in (None, fmt):
+        raise ValueError("a separate down format is only supported between GGUF block types")
     if fmt == "bf16":
         wb = H * F * 2
         ef.off_gate, ef.off_up, ef.off_down = 0, wb, 2 * wb
@@ -113,6 +130,13 @@ MOE_RUN_DN = int(os.environ.get("LSB_MOE_RUN_DN", "0") or 0)
 COMM_XCHG = int(os.environ.get("LSB_COMM_XCHG", "2") or 0)
 
 
+def _dequant_ggml(t: int, dev_rows: torch.Tensor, N: int, K: int) -> torch.Tensor:
+    """fp32 [N, K] of a matrix stored in the device layout of GGUF block type ``t`` (CPU codec: the oracle of the GPU decoders)."""
+    from ..formats import gguf as _gguf
+    raw = _gguf.from_device_layout(t, dev_rows.detach().cpu().numpy(), N, K)
+    return torch.from_numpy(_gguf.dequantize(t, raw, N * K)).view(N, K).to(dev_rows.device)
+
+
 def _dequant_q4k(raw: torch.Tensor, N: int, K: int) -> torch.Tensor:
     from ..formats import gguf as _gguf
     out = _gguf.dequantize(_gguf.GGML_TYPES["Q4_K"], raw.detach().cpu().numpy().reshape(-1), N * K)
@@ -162,7 +186,20 @@ class QLinear:
             from ..formats import gguf as _gguf
             raw = _gguf.quantize(_gguf.GGML_TYPES["Q4_K"], wf.float().cpu().numpy())
             return QLinear("gguf_q4_k", N, K, torch.from_numpy(raw).to(device).view(N, K // 256 * 144))
+        if fmt in ("gguf_q6_k", "gguf_q8_0"):
+            from ..formats import gguf as _gguf
+            t = GGML_OF[fmt]
+            return QLinear.from_ggml(t, _gguf.quantize(t, wf.float().cpu().numpy()), N, K, device)
         raise ValueError(fmt)
+
+    @staticmethod
+    def from_ggml(t: int, raw, N: int, K: int, device) -> "QLinear":
+        """File-order GGUF blocks of type ``t`` (Q4_K, Q5_K, Q6_K, Q8_0) -> the device layout of that type, values untouched."""
+        from ..formats import gguf as _gguf
+        import numpy as _np
+        raw = raw.cpu().numpy() if isinstance(raw, torch.Tensor) else _np.asarray(raw)
+        d = _gguf.to_device_layout(t, raw, N, K)
+        return QLinear(_gguf.DEVICE_NATIVE[t], N, K, torch.from_numpy(_np.ascontiguousarray(d)).to(device))
 
     @staticmethod
     def random(N: int, K: int, fmt: str, device, std: float = 0.02, gen=None) -> "QLinear":
@@ -195,6 +232,24 @@ class QLinear:
             blocks[:, :4] = d
             blocks[:, 4:16] = (blocks[:, 4:16] & 0x1F) | 0x10      # scales and mins in 16..31, top bits clear
             return QLinear("gguf_q4_k", N, K, blocks.view(N, K // 256 * 144))
+        if fmt in ("gguf_q5_k", "gguf_q6_k", "gguf_q8_0"):
+            # random quants in file order with fixed block scales, then the device layout
+            c = std * 3 ** 0.5
+            if fmt == "gguf_q5_k":
+                blocks = torch.empty(N * K // 256, 176, dtype=torch.uint8, device=device)
+                blocks.random_(0, 256, generator=gen)
+                blocks[:, :4] = torch.tensor([c / 15.5 / 32.0, c / 32.0], dtype=torch.float16).view(torch.uint8).to(device)
+                blocks[:, 4:16] = (blocks[:, 4:16] & 0x1F) | 0x10
+            elif fmt == "gguf_q6_k":
+                blocks = torch.empty(N * K // 256, 210, dtype=torch.uint8, device=device)
+                blocks.random_(0, 256, generator=gen)
+                blocks[:, 192:208] = (blocks[:, 192:208] & 0x3F) | 0x20          # int8 scales 32..95
+                blocks[:, 208:210] = torch.tensor([c / 32.0 / 64.0], dtype=torch.float16).view(torch.uint8).to(device)
+            else:
+                blocks = torch.empty(N * K // 32, 34, dtype=torch.uint8, device=device)
+                blocks.random_(0, 256, generator=gen)
+                blocks[:, :2] = torch.tensor([c / 127.0], dtype=torch.float16).view(torch.uint8).to(device)
+            return QLinear.from_ggml(GGML_OF[fmt], blocks, N, K, device)
         raise ValueError(fmt)
 
     _tiles: Dict[tuple, dict] = {}
@@ -220,6 +275,15 @@ class QLinear:
         t["x16"] = cls._x16[idx]
         return t
 
+    _bf16: Dict[int, torch.Tensor] = {}
+
+    @classmethod
+    def _bf16_scratch(cls, device, n: int) -> torch.Tensor:
+        idx = torch.device(device).index or 0
+        if idx not in cls._bf16 or cls._bf16[idx].numel() < n:
+            cls._bf16[idx] = torch.empty(n, dtype=torch.bfloat16, device=device)
+        return cls._bf16[idx]
+
     _bsbuf: Dict[tuple, tuple] = {}
 
     @classmethod
@@ -238,8 +302,8 @@ class QLinear:
             return self.w.float()
         if self.fmt == "fp8_e4m3":
             return quant.dequantize_fp8_block(self.w, self.scales)
-        if self.fmt == "gguf_q4_k":
-            return _dequant_q4k(self.w, self.N, self.K)
+        if self.fmt in GGML_OF:
+            return _dequant_ggml(GGML_OF[self.fmt], self.w, self.N, self.K)
         return quant.dequantize_nvfp4(self.w, self.scales, self.alpha, self.N, self.K)
 
     def nbytes(self) -> int:
@@ -284,6 +348,15 @@ class QLinear:
             nat.call("lsb_gemv_f32w", out, x, self.w, bias, M, self.N, self.K, ldx, self.K, ldo, 1.0, ob)
         elif self.fmt == "gguf_q4_k":
             nat.call("lsb_gemv_q4k", out, x, self.w, bias, M, self.N, self.K, ldx, ldo, 1.0, ob, comm)
+        elif self.fmt in GGML_OF:
+            if M >= 16 and comm is None and ldx == self.K:
+                # many rows: expand the blocks to bf16 once per call (scratch shared by all layers) and run the tensor-core GEMM
+                scr = QLinear._bf16_scratch(self.w.device, self.N * self.K)
+                nat.call("lsb_gguf_dequant_bf16", scr, self.w, GGML_OF[self.fmt], self.N, self.K)
+                sc = TcScratch.get(self.w.device)
+                nat.call("lsb_gemm_bf16_tc", out, x, scr, bias, M, self.N, self.K, ldx, self.K, ldo, ob, sc.partial, sc.cap, sc.err, None)
+            else:
+                nat.call("lsb_gemv_gguf", out, x, self.w, GGML_OF[self.fmt], bias, M, self.N, self.K, ldx, ldo, 1.0, ob, comm)
         elif self.fmt == "fp8_e4m3":
             nat.call("lsb_gemv_fp8b", out, x, self.w, self.scales, bias, M, self.N, self.K, ldx, ldo, 1.0, ob, comm)
         else:
@@ -337,8 +410,11 @@ class ExpertArena:
                                    ("down", (H, F), ef.off_down, ef.off_sd)):
             if fmt == "bf16":
                 out.append(v[ow: ow + N * K * 2].view(torch.bfloat16).view(N, K).float())
-            elif fmt == "gguf_q4_k":
-                out.append(_dequant_q4k(v[ow: ow + N * K // 256 * 144], N, K))
+            elif fmt in GGML_OF:
+                from ..formats import gguf as _gguf
+                t = GGML_OF[fmt] if (nm != "down" or not ef.fmt_down1) else GGML_OF[_FMT_NAME[ef.fmt_down1 - 1]]
+                rb = _gguf.device_row_bytes(t, K)
+                out.append(_dequant_ggml(t, v[ow: ow + N * rb].view(N, rb), N, K))
             elif fmt == "fp8_e4m3":
                 nb = ((N + 127) // 128) * ((K + 127) // 128)
                 s = v[os_: os_ + nb * 4].view(torch.float32).view((N + 127) // 128, (K + 127) // 128)
@@ -565,11 +641,23 @@ class DeviceModel:
     def _expert_lin(self, w, name: str, eq: str) -> QLinear:
         """One expert matrix in the arena's storage format.  Q4_K tensors of a GGUF checkpoint are taken as they are (bit-exact
         super-blocks); everything else goes through the float path (de-quantise, quantise to the arena format)."""
-        if eq == "gguf_q4_k" and hasattr(w, "native_q4k"):
-            raw = w.native_q4k(name)
-            if raw is not None:
-                return QLinear("gguf_q4_k", raw.shape[0], raw.shape[1] // 144 * 256, raw.to(self.device).contiguous())
+        if eq in GGML_OF and hasattr(w, "native_ggml"):
+            nv = w.native_ggml(name)
+            if nv is not None and nv[0] == GGML_OF[eq]:
+                return QLinear.from_ggml(nv[0], nv[1], nv[2], nv[3], self.device)
         return QLinear.from_float(w[name], eq, self.device)
+
+    def _gguf_layer_formats(self, w, prefix: str, e0: int):
+        """(gate / up format, down format) when expert ``e0`` of this layer is stored in block types the kernels read natively
+        (gate and up in the same type), else None."""
+        if not hasattr(w, "native_ggml") or self.cfg.hidden % 256 or self.Fe % 256 or self.expert_shard == "tp":
+            return None
+        from ..formats import gguf as _gguf
+        nm = prefix + (f"experts.{e0}." if e0 < self.cfg.n_routed else f"shared.{e0 - self.cfg.n_routed}.")
+        ts = [w.native_ggml(nm + t) for t in ("gate", "up", "down")]
+        if any(t is None for t in ts) or ts[0][0] != ts[1][0]:
+            return None
+        return _gguf.DEVICE_NATIVE[ts[0][0]], _gguf.DEVICE_NATIVE[ts[2][0]]
 
     def _lin(self, get, name, fmt):
         return QLinear.from_float(get(name), fmt, self.device)
@@ -591,9 +679,14 @@ class DeviceModel:
             return t[:, tr * per: (tr + 1) * per]
         eq = expert_quant or cfg.expert_quant
         dq = dense_quant or cfg.dense_quant
+        gguf_experts = eq == "gguf"
         if eq.startswith("gguf"):
-            # GGUF expert tensors: Q4_K runs natively; the other ggml types are expanded at load time
-            eq = "gguf_q4_k" if (eq in ("gguf", "gguf_q4_k") and cfg.hidden % 256 == 0 and m.Fe % 256 == 0 and m.expert_shard != "tp") else "bf16"
+            # GGUF expert tensors: "gguf" = per layer the block types of the file where the kernels read them natively (Q4_K, Q5_K,
+            # Q6_K, Q8_0, the down matrix possibly in another type than gate / up), else Q4_K; a named type = that type for all
+            ok = cfg.hidden % 256 == 0 and m.Fe % 256 == 0 and m.expert_shard != "tp"
+            eq = ("gguf_q4_k" if eq == "gguf" else eq) if ok else "bf16"
+            if eq not in EXPERT_FMT or (eq == "gguf_q5_k" and not hasattr(w, "native_ggml")):
+                eq = "gguf_q4_k"                    # types without a GPU decoder, or without a quantiser from float weights
         f32 = lambda t: t.to(dev).float().contiguous()
         m.embed = w["embed.weight"].to(dev).to(torch.bfloat16).contiguous()
         m.head = QLinear.from_float(rows(w["head.weight"], cfg.vocab, 1), "bf16", dev)
@@ -640,9 +733,16 @@ class DeviceModel:
                 mo = p + "moe."
                 L["router"] = QLinear.from_float(w[mo + "router"], "f32", dev)
                 L["router_bias"] = f32(w[mo + "router_bias"]) if (mo + "router_bias") in w else None
-                ef = expert_layout(eq, cfg.hidden, m.Fe)
                 E_total = cfg.n_routed + cfg.n_shared
                 mine = [e for e in range(E_total) if m.owns_expert(i, e)]
+                eq_l, eq_dn = eq, eq
+                if gguf_experts and mine:
+                    # a GGUF checkpoint: this layer's experts in the block types of the file when the kernels read them natively
+                    # (every expert of a layer shares its tensors' types; the shared expert may differ and is then converted)
+                    nf = m._gguf_layer_formats(w, mo, mine[0])
+                    if nf is not None:
+                        eq_l, eq_dn = nf
+                ef = expert_layout(eq_l, cfg.hidden, m.Fe, eq_dn)
                 arena = ExpertArena(ef, max(len(mine), 1), E_total, dev)
                 for s_, e in enumerate(mine):
                     nm = mo + (f"experts.{e}." if e < cfg.n_routed else f"shared.{e - cfg.n_routed}.")
@@ -653,7 +753,7 @@ class DeviceModel:
                                  QLinear.from_float(w[nm + "down"][:, f0:f1].contiguous(), eq, dev))
                         arena.write_expert(s_, *parts)
                     else:
-                        arena.write_expert(s_, *(m._expert_lin(w, nm + t, eq) for t in ("gate", "up", "down")))
+                        arena.write_expert(s_, m._expert_lin(w, nm + "gate", eq_l), m._expert_lin(w, nm + "up", eq_l), m._expert_lin(w, nm + "down", eq_dn))
                     arena.slot_of[e] = s_
                 L["arena"] = arena
             else:
@@ -921,7 +1021,7 @@ class DeviceModel:
 
     def _moe_mode(self, arena: ExpertArena, ws: Workspace, R: int) -> str:
         cfg = self.cfg
-        if getattr(ws, "tc_ok", False) and R >= TC_MOE_MIN_ROWS:
+        if getattr(ws, "tc_ok", False) and R >= TC_MOE_MIN_ROWS and arena.ef.fmt <= 3 and not arena.ef.fmt_down1:
             return "tc"
         fast_fp4 = arena.ef.fmt == 2 and self.Fe % 128 == 0 and cfg.hidden % 128 == 0
         return "pairs" if (fast_fp4 and R * ws.S <= 72) else "groups"
@@ -1035,7 +1135,8 @@ class DeviceModel:
             # sharded KV: gather the queries of all heads, attend over this rank's token shard, merge on the head owners
             self.dcp.forward(ws.q_abs, self.kv_cache[i], self.block_table, self.max_pages, ws.row_seq, ws.row_len_local, ws.o_lat, self.page,
                              KV_FMT[self.kv_fmt], cfg.softmax_scale, sel_idx=sel_idx, sel_cnt=sel_cnt, tq_centroids=self.tq_centroids, rows=R)
-        elif self.row_tier is not None and sel_idx is not None:
+        elif self.row_tier is not None and sel_idx is not None and self.row_tier.step_has_cold(R):
+            # (a step none of whose sequences has a page in the cold tier - e.g. the prefill of a fresh prompt - reads the paged cache directly)
             # tiered KV: the selected rows (hot pages and cold tier alike) are materialised in a dense buffer, attention runs over that
             cache_m, bt_m, pm, seq_m, sel_m = self.row_tier.materialise(i, ws, R, sel_idx, sel_cnt, sel_ld)
             nat.call("lsb_mla_decode", ws.q_abs, cache_m, bt_m, pm, seq_m, sel_cnt, sel_m, sel_cnt, sel_ld, ws.o_lat, None, ws.o_part, ws.ml_part,

@@ -65,6 +65,10 @@ class RowTiering:
     def has_cold(self, sid: int) -> bool:
         return self.next_page.get(sid, 0) > 0
 
+    def step_has_cold(self, R: int) -> bool:
+        """Whether any row of the running step belongs to a sequence with pages in the cold tier."""
+        return any(self.has_cold(sid) for sid in self.step_sids[:R])
+
     # ------------------------------------------------------------------ demotion
     def slide_window(self, sid: int) -> int:
         """Demote every page of the sequence that lies completely behind the hot window.  Returns the HBM pages released."""

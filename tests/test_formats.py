@@ -131,3 +131,17 @@ def test_prepacked_store_roundtrip_resume_and_verify(tmp_path):
     export_hf(cfg, w, hf)
     assert prepack.main(["--model", hf, "--out", str(tmp_path / "s2"), "--quant", "fp8_e4m3", "--verify"]) == 0
     assert os.path.exists(tmp_path / "s2" / "manifest.json")
+
+
+def test_gguf_device_layouts_hold_the_file_blocks_unchanged():
+    """Q6_K blocks padded to 224 bytes and Q8_0 rows split into a quant plane and a scale plane give back the file's bytes."""
+    import numpy as np
+    from layerstorm_b200.formats import gguf as g
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal((6, 512)).astype(np.float32)
+    for t in (g.GGML_TYPES["Q4_K"], g.GGML_TYPES["Q6_K"], g.GGML_TYPES["Q8_0"]):
+        raw = g.quantize(t, x)
+        d = g.to_device_layout(t, raw, 6, 512)
+        assert d.shape == (6, g.device_row_bytes(t, 512))
+        assert np.array_equal(g.from_device_layout(t, d, 6, 512), raw)
+    assert g.device_row_bytes(g.GGML_TYPES["Q5_K"], 512) == 2 * 176

@@ -383,3 +383,25 @@ def test_q4k_linear_gemv_and_tensor_core(M):
     rnd = QLinear.random(N, K, "gguf_q4_k", "cuda")
     wd = rnd.dequant()
     assert torch.isfinite(wd).all() and 0.005 < float(wd.std()) < 0.08
+
+
+def test_mhc_many_row_pass_is_reproducible_run_to_run():
+    """The many-row hyper-connection pass updates the residual streams in place while all four warps of a block read them: the same
+    inputs must give the same bits every time (a missing block barrier showed up as a handful of differing rows per 2048-row chunk)."""
+    cfg = get_preset("tiny-glm5-next")
+    H, n, R = 1024, cfg.hc_mult, 1024
+    fn, sc, base, nw = rnd(24, n * H, s=0.05), torch.tensor([0.7, 1.1, 1.3], device=DEV), rnd(24, s=0.5), rnd(H) * 0.1 + 1
+    sub = rnd(R, H)
+    resid0, post0, comb0 = rnd(R, n, H), torch.rand(R, n, device=DEV), torch.rand(R, n, n, device=DEV)
+    part = torch.zeros(R, H // 32, 36, device=DEV)
+    args = (cfg.hc_sinkhorn_iters, cfg.hc_eps, cfg.rms_eps, cfg.hc_post_mult)
+    outs = []
+    for _ in range(12):
+        resid, post, comb = resid0.clone(), post0.clone(), comb0.clone()
+        x = torch.zeros(R, H, device=DEV, dtype=torch.bfloat16)
+        nat.call("lsb_mhc_post_pre", x, resid, sub, post, comb, fn, sc, base, nw, part, R, H, n, 1, *args, None, None, None)
+        torch.cuda.synchronize()
+        outs.append((x.clone(), resid, post, comb))
+    for o_ in outs[1:]:
+        for a, b in zip(outs[0], o_):
+            assert torch.equal(a, b)

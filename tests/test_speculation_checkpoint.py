@@ -242,6 +242,13 @@ def test_gguf_q4k_experts_pass_through_bit_exact(tmp_path):
     sh = ck.native_q4k("layers.1.moe.shared.0.down")
     assert sh is not None and tuple(sh.shape) == (rows, cols // 256 * 144)
     assert ck.native_q4k("layers.1.attn.q_a") is None
+    # the general accessor: every block type the GPU kernels decode (here Q4_K and Q8_0), file-order bytes
+    t2, raw2, r2, c2 = ck.native_ggml("layers.1.moe.experts.1.up")
+    assert (t2, r2, c2) == (g.GGML_TYPES["Q8_0"], rows, cols)
+    assert bytes(raw2.tobytes()) == bytes(g.quantize(t2, stack[1]).tobytes())
+    t3, raw3, _, _ = ck.native_ggml("layers.1.moe.experts.2.gate")
+    assert t3 == t and bytes(raw3.tobytes()) == bytes(want.tobytes())
+    assert ck.native_ggml("layers.1.attn.q_a") is None
 
 
 def test_mtp_block_weights_roundtrip_through_an_hf_checkpoint(tmp_path):

@@ -9,6 +9,7 @@
            CUDA graph, 1 GPU vs N GPUs, two builds) start to differ.
 
     python -m layerstorm_b200.utils.determinism_probe probe --model tiny-mla-moe --prompt-len 512 --gen 16 --reps 3
+    python -m layerstorm_b200.utils.determinism_probe probe --model glm-5.3-flash --layers 8 --prompt-len 4096 --gen 8   # full-width slice
     python -m layerstorm_b200.utils.determinism_probe drift a.npz b.npz --rtol 1e-3
 
 Reference counterparts: tools/serve_determinism_probe.py (warm-up, identical greedy repetitions, pairwise first divergence, verdict) and
@@ -86,6 +87,8 @@ def main(argv: Optional[List[str]] = None) -> int:
     p.add_argument("--reps", type=int, default=3)
     p.add_argument("--warmup-len", type=int, default=64)
     p.add_argument("--prefix-cache", action="store_true")
+    p.add_argument("--layers", type=int, default=0, help="keep the first N layers of the model shape at full width (a slice of a large model)")
+    p.add_argument("--prefill-chunk", type=int, default=2048)
     d = sub.add_parser("drift")
     d.add_argument("a")
     d.add_argument("b")
@@ -110,8 +113,13 @@ def main(argv: Optional[List[str]] = None) -> int:
         from ..models.device_model import DeviceModel
         from ..runtime.engine import Engine
         shape = get_preset(a.model)
+        if a.layers and a.layers < shape.n_layers:
+            import dataclasses
+            shape = dataclasses.replace(shape, n_layers=a.layers, **({"layer_types": list(shape.layer_types[:a.layers])} if shape.layer_types else {}))
         dev = torch.device("cuda", 0)
-        eng = Engine(DeviceModel.random_init(shape, dev, "fp8", 64, expert_slots="auto"), max_seqs=8, max_ctx=a.prompt_len + a.gen + 64)
+        eng = Engine(DeviceModel.random_init(shape, dev, "fp8", 64, expert_slots="auto", embed_on_host=shape.vocab * shape.hidden > 2 ** 28,
+                                             reserve_bytes=8 << 30),
+                     max_seqs=8, max_ctx=a.prompt_len + a.gen + 64, prefill_chunk=a.prefill_chunk)
         vocab = shape.vocab
     orch = Orchestrator(eng, prefix_cache=PrefixCacheConfig(enabled=a.prefix_cache))
     prompt = [(7 + 13 * i) % (vocab - 8) + 4 for i in range(a.prompt_len)]

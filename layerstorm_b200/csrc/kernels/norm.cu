@@ -155,7 +155,7 @@ __global__ void __launch_bounds__(128) mhc_post_partial_wide_kernel(float* __res
                                                                     const float* __restrict__ post, const float* __restrict__ comb,
                                                                     const float* __restrict__ fn, float* __restrict__ part,
                                                                     int hidden, int n, int mode, int rows, int rows_per_block, PeerComm comm) {
-    const int c = blockIdx.y, lane = threadIdx.x & 31, og = threadIdx.x >> 5;
+    const int c = blockIdx.x, lane = threadIdx.x & 31, og = threadIdx.x >> 5;
     const int h = c * kHcWide + lane * 4;
     const int nout = 2 * n + n * n;
     float4 f[kHcPerWarp][kHcMax];
@@ -173,38 +173,59 @@ __global__ void __launch_bounds__(128) mhc_post_partial_wide_kernel(float* __res
         epoch = *comm.epoch;
         comm_wait(comm, epoch);
     }
-    for (int r = blockIdx.x * rows_per_block; r < min(rows, (int)(blockIdx.x + 1) * rows_per_block); ++r) {
-        float4 res[kHcMax];
-        float* rp = residual + (size_t)r * n * hidden;
-        float4 xv;
+    // The rows of a block are independent but each one is a chain load -> mix -> 7 warp reductions -> store: with one row in
+    // flight the block waits a DRAM round trip per row (16 per block).  The next row's operands (x, the four old streams, its
+    // post / comb gates: 10 16-byte loads) are therefore requested before the current row is worked on.
+    struct RowIn { float4 xv; float4 old[kHcMax]; float pj[kHcMax]; float cj[kHcMax][kHcMax]; };
+    const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    auto load_row = [&](int r, RowIn& in) {
+        const float* rp = residual + (size_t)r * n * hidden;
         if (comm.nranks && mode == 1) {
             const size_t b = (size_t)r * hidden + h;
-            xv = make_float4(comm_reduce(comm, epoch, b), comm_reduce(comm, epoch, b + 1), comm_reduce(comm, epoch, b + 2), comm_reduce(comm, epoch, b + 3));
+            in.xv = make_float4(comm_reduce(comm, epoch, b), comm_reduce(comm, epoch, b + 1), comm_reduce(comm, epoch, b + 2), comm_reduce(comm, epoch, b + 3));
         } else {
-            xv = *reinterpret_cast<const float4*>(x + (size_t)r * hidden + h);
+            in.xv = *reinterpret_cast<const float4*>(x + (size_t)r * hidden + h);
         }
-        if (mode == 0) {
+        if (mode != 0) {
 #pragma unroll
-            for (int j = 0; j < kHcMax; ++j) res[j] = j < n ? xv : make_float4(0.f, 0.f, 0.f, 0.f);
-        } else {
-            float4 old[kHcMax];
-#pragma unroll
-            for (int i = 0; i < kHcMax; ++i) old[i] = i < n ? *reinterpret_cast<const float4*>(rp + (size_t)i * hidden + h) : make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int i = 0; i < kHcMax; ++i) in.old[i] = i < n ? *reinterpret_cast<const float4*>(rp + (size_t)i * hidden + h) : z4;
 #pragma unroll
             for (int j = 0; j < kHcMax; ++j) {
-                float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+                in.pj[j] = j < n ? post[r * n + j] : 0.f;
+#pragma unroll
+                for (int i = 0; i < kHcMax; ++i) in.cj[i][j] = (i < n && j < n) ? comb[(r * n + i) * n + j] : 0.f;
+            }
+        }
+    };
+    const int r_begin = blockIdx.y * rows_per_block, r_end = min(rows, (int)(blockIdx.y + 1) * rows_per_block);
+    RowIn cur, nxt;
+    if (r_begin < r_end) load_row(r_begin, cur);
+    for (int r = r_begin; r < r_end; ++r) {
+        if (r + 1 < r_end) load_row(r + 1, nxt);      // (rows are disjoint: the in-place store of row r below never touches row r + 1)
+        float4 res[kHcMax];
+        float* rp = residual + (size_t)r * n * hidden;
+        if (mode == 0) {
+#pragma unroll
+            for (int j = 0; j < kHcMax; ++j) res[j] = j < n ? cur.xv : z4;
+        } else {
+#pragma unroll
+            for (int j = 0; j < kHcMax; ++j) {
+                float4 a = z4;
                 if (j < n) {
-                    const float pj = post[r * n + j];
-                    a = make_float4(pj * xv.x, pj * xv.y, pj * xv.z, pj * xv.w);
-                    for (int i = 0; i < n; ++i) {
-                        const float cj = comb[(r * n + i) * n + j];
-                        a.x += cj * old[i].x; a.y += cj * old[i].y; a.z += cj * old[i].z; a.w += cj * old[i].w;
+                    const float pj = cur.pj[j];
+                    a = make_float4(pj * cur.xv.x, pj * cur.xv.y, pj * cur.xv.z, pj * cur.xv.w);
+#pragma unroll
+                    for (int i = 0; i < kHcMax; ++i) {
+                        if (i < n) {
+                            const float cj = cur.cj[i][j];
+                            a.x += cj * cur.old[i].x; a.y += cj * cur.old[i].y; a.z += cj * cur.old[i].z; a.w += cj * cur.old[i].w;
+                        }
                     }
                 }
                 res[j] = a;
             }
         }
-        float* po = part + ((size_t)r * gridDim.y + c) * (kHcOut + 1);
+        float* po = part + ((size_t)r * gridDim.x + c) * (kHcOut + 1);
 #pragma unroll
         for (int i = 0; i < kHcPerWarp; ++i) {
             float a = 0.f;
@@ -231,6 +252,7 @@ __global__ void __launch_bounds__(128) mhc_post_partial_wide_kernel(float* __res
             ss = warp_sum(ss);
             if (lane == 0) po[kHcOut] = ss;
         }
+        cur = nxt;
     }
     pdl_launch_dependents();
 }
@@ -654,7 +676,9 @@ LSB_API int lsb_mhc_post_pre(void* out_x, void* residual, const void* x, void* p
     int nparts = nchunks;
     if (rows >= 64 && hidden % kHcWide == 0) {
         nparts = hidden / kHcWide;
-        launch_pdl((mhc_post_partial_wide_kernel), dim3((rows + rpb - 1) / rpb, nparts), 128, 0, st, (float*)residual, (const float*)x, (const float*)post,
+        // hidden parts are the fastest grid dimension: the blocks that run together read whole rows of the residual streams (16 KB
+        // runs) instead of 512-byte pieces 64 KB apart
+        launch_pdl((mhc_post_partial_wide_kernel), dim3(nparts, (rows + rpb - 1) / rpb), 128, 0, st, (float*)residual, (const float*)x, (const float*)post,
                    (const float*)comb, (const float*)fn, (float*)part, hidden, n, mode, rows, rpb, comm_from_host(comm));
     } else {
         launch_pdl((mhc_post_partial_kernel), dim3((rows + rpb - 1) / rpb, nchunks), 128, 0, st, (float*)residual, (const float*)x, (const float*)post,

@@ -102,6 +102,7 @@ def expert_layout(fmt: str, H: int, F: int, down_fmt: Optional[str] = None) -> E
     return ef
 
 
+F32_SPLIT_MIN_ROWS = 128  # rows from which an fp32 matrix (the router) runs as a split-bf16 tensor-core GEMM instead of the CUDA-core SGEMM
 TC_MOE_MIN_ROWS = 16      # rows per step from which the routed experts run on the tensor-core grouped GEMM
 # router projection + top-k in one launch for decode-sized steps (switch: LSB_ROUTER_FUSED=1).  Off by default: measured on the
 # GLM-5.3-Flash shape the fused kernel (one block per expert, last block selects) gives 7.21 ms per decode step against 7.12 ms for
@@ -275,6 +276,15 @@ class QLinear:
         t["x16"] = cls._x16[idx]
         return t
 
+    _f32s: Dict[int, torch.Tensor] = {}
+
+    @classmethod
+    def _f32_scratch(cls, device, n: int) -> torch.Tensor:
+        idx = torch.device(device).index or 0
+        if idx not in cls._f32s or cls._f32s[idx].numel() < n:
+            cls._f32s[idx] = torch.empty(n, dtype=torch.float32, device=device)
+        return cls._f32s[idx][:n]
+
     _bf16: Dict[int, torch.Tensor] = {}
 
     @classmethod
@@ -344,6 +354,17 @@ class QLinear:
                      TcScratch.get(self.w.device).err)
         elif self.fmt == "bf16":
             nat.call("lsb_gemv_bf16", out, x, self.w, bias, M, self.N, self.K, ldx, self.K, ldo, 1.0, ob, comm)
+        elif self.fmt == "f32" and M >= F32_SPLIT_MIN_ROWS and bias is None and not ob and ldx == self.K and ldo == self.N and self.K % 64 == 0:
+            # many rows over an fp32 matrix (the router of a prefill chunk): w = hi + lo with both halves bf16 (exact to 2^-17
+            # relative), ONE tensor-core GEMM over the stacked [hi; lo] rows, then the two halves of the result are added
+            if getattr(self, "_hilo", None) is None:
+                hi = self.w.to(torch.bfloat16)
+                lo = (self.w - hi.float()).to(torch.bfloat16)
+                self._hilo = torch.cat([hi, lo], 0).contiguous()
+            tmp = QLinear._f32_scratch(self.w.device, M * 2 * self.N).view(M, 2 * self.N)
+            sc = TcScratch.get(self.w.device)
+            nat.call("lsb_gemm_bf16_tc", tmp, x, self._hilo, None, M, 2 * self.N, self.K, ldx, self.K, 2 * self.N, 0, sc.partial, sc.cap, sc.err, None)
+            torch.add(tmp[:, : self.N], tmp[:, self.N:], out=out[:M].view(M, self.N) if out.dim() == 2 else out.view(-1)[: M * self.N].view(M, self.N))
         elif self.fmt == "f32":
             nat.call("lsb_gemv_f32w", out, x, self.w, bias, M, self.N, self.K, ldx, self.K, ldo, 1.0, ob)
         elif self.fmt == "gguf_q4_k":

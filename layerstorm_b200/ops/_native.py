@@ -80,6 +80,31 @@ def load():
 
 
 _launches = 0
+_timer = None          # list of (launcher, start event, end event) while a call_timer() is active
+
+
+class call_timer:
+    """``with call_timer() as t: ...`` brackets every launcher call made on the current stream with CUDA events (eager steps: the launchers'
+    kernels run back to back, so a call's span is its kernels' device time plus the launch gap).  ``t.summary()`` -> {launcher: (calls, ms)}."""
+
+    def __enter__(self):
+        global _timer
+        self.rec = []
+        _timer = self.rec
+        return self
+
+    def __exit__(self, *exc):
+        global _timer
+        _timer = None
+        return False
+
+    def summary(self) -> dict:
+        torch.cuda.synchronize()
+        out = {}
+        for name, e0, e1 in self.rec:
+            c, ms = out.get(name, (0, 0.0))
+            out[name] = (c + 1, ms + e0.elapsed_time(e1))
+        return out
 
 
 def launch_count() -> int:
@@ -112,7 +137,14 @@ def call(name: str, *args, stream=None):
     if not has_stream:
         return getattr(lib, name)(*conv)
     st = stream if stream is not None else torch.cuda.current_stream().cuda_stream
-    rc = getattr(lib, name)(*conv, st)
+    if _timer is not None:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        rc = getattr(lib, name)(*conv, st)
+        e1.record()
+        _timer.append((name, e0, e1))
+    else:
+        rc = getattr(lib, name)(*conv, st)
     _launches += 1
     if rc != 0:
         raise RuntimeError(f"{name} failed with status {rc}")

@@ -32,6 +32,9 @@ def main(argv=None) -> int:
     ap.add_argument("--prefill-chunk", type=int, default=2048)
     ap.add_argument("--kv-format", default="fp8", choices=["fp8", "bf16", "tq4"])
     ap.add_argument("--expert-quant", default=None)
+    ap.add_argument("--time-calls", action="store_true",
+                    help="with --prefill: after the context is filled, run ONE more prefill chunk with CUDA events around every kernel-launcher "
+                         "call and print the table (device time per launcher; the chunk's kernels are long, the event overhead is not)")
     a = ap.parse_args(argv)
 
     import torch
@@ -51,7 +54,7 @@ def main(argv=None) -> int:
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     model = DeviceModel.random_init(cfg, dev, kv_fmt=a.kv_format, page=64, seed=1234, embed_on_host=True)
-    eng = Engine(model, max_seqs=a.batch, max_ctx=a.ctx + a.steps + 64, prefill_chunk=a.prefill_chunk, max_batch=a.batch, use_graph=False)
+    eng = Engine(model, max_seqs=a.batch, max_ctx=a.ctx + a.steps + 64 + (a.prefill_chunk if a.time_calls else 0), prefill_chunk=a.prefill_chunk, max_batch=a.batch, use_graph=False)
     g = torch.Generator().manual_seed(7)
     sids = [eng.create_sequence() for _ in range(a.batch)]
     toks = []
@@ -67,6 +70,18 @@ def main(argv=None) -> int:
             toks.append(1)
     torch.cuda.synchronize()
     t_fill = time.time() - t0
+    if a.time_calls:
+        from ..ops import _native as nat
+        chunk = torch.randint(0, cfg.vocab, (a.prefill_chunk,), generator=g).tolist()
+        with nat.call_timer() as tm:
+            eng.prefill(sids[0], chunk)
+        rows = sorted(tm.summary().items(), key=lambda kv: -kv[1][1])
+        total = sum(ms for _, (_, ms) in rows)
+        print(f"# one {a.prefill_chunk}-token prefill chunk at context {a.ctx}, {L} layers ({', '.join(getattr(cfg, 'layer_types', []) or [])}): "
+              f"{total:.2f} ms in launcher calls")
+        print("| launcher | calls | ms | share |\n|---|---|---|---|")
+        for name, (c, ms) in rows:
+            print(f"| `{name}` | {c} | {ms:.3f} | {100 * ms / total:.1f}% |")
     times = []
     for _ in range(a.steps):
         t0 = time.time()

@@ -405,3 +405,22 @@ def test_mhc_many_row_pass_is_reproducible_run_to_run():
     for o_ in outs[1:]:
         for a, b in zip(outs[0], o_):
             assert torch.equal(a, b)
+
+
+def test_many_row_fp32_matrix_runs_as_split_bf16_tensor_core_gemm():
+    """The router projection of a prefill chunk: fp32 weights split into bf16 hi + lo halves, one tcgen05 GEMM over the stacked halves.
+    Must agree with the fp32 product far below the spacing of router logits (the few-row path reads the fp32 weights directly)."""
+    from layerstorm_b200.models.device_model import QLinear
+    N, K, M = 288, 1024, 300
+    W = QLinear("f32", N, K, rnd(N, K, s=0.1))
+    x = rnd(M, K).to(torch.bfloat16)
+    out = torch.zeros(M, N, device=DEV)
+    W(out, x, M)
+    torch.cuda.synchronize()
+    assert getattr(W, "_hilo", None) is not None and tuple(W._hilo.shape) == (2 * N, K)       # the tensor-core path ran
+    ref = x.double() @ W.w.double().t()
+    assert (out.double() - ref).abs().max().item() < 2e-5 * ref.abs().max().item()
+    few = torch.zeros(4, N, device=DEV)
+    W(few, x[:4].contiguous(), 4)
+    torch.cuda.synchronize()
+    assert (few - out[:4]).abs().max().item() < 2e-5 * ref.abs().max().item()

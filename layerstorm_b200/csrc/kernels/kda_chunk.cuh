@@ -10,7 +10,9 @@
 constexpr int kCh = 64;            // tokens per chunk
 constexpr int kLdK = kD + 4;       // shared-memory row stride (floats) of [*, 128] tiles: 16-byte aligned rows, conflict-free float4 columns
 constexpr int kLdC = kCh + 4;      // row stride of [*, 64] tiles
-constexpr size_t kChunkPrepSmem = (size_t)(3 * kCh * kLdK + 3 * kCh * kLdC + kCh) * sizeof(float);
+constexpr int kSub = 16;           // tokens per sub-chunk of the A / B factorisation
+constexpr int kLdR = kD + 1;       // odd row stride of the rescaled tiles: lanes that read different rows at the same column hit different banks
+constexpr size_t kChunkPrepSmem = (size_t)(3 * kCh * kLdK + 3 * kCh * kLdC + kCh + (2 * kSub + kCh - kSub) * kLdR) * sizeof(float);
 constexpr size_t kChunkScanSmem = (size_t)(4 * kCh * kLdK + 4 * kCh * kLdC) * sizeof(float);
 
 struct KdaChunkWs {
@@ -28,6 +30,9 @@ __global__ void __launch_bounds__(256) kda_chunk_prep_kernel(KdaParams p, KdaScr
     float* sB = sA + kCh * kLdC;
     float* sW = sB + kCh * kLdC;
     float* sBeta = sW + kCh * kLdC;
+    float* sLk = sBeta + kCh;                                 // [16][kLdR] k rows of the current sub-chunk times exp(G - G_ref)
+    float* sLq = sLk + kSub * kLdR;                           // [16][kLdR] q rows, same factor
+    float* sR = sLq + kSub * kLdR;                            // [48][kLdR] earlier k rows times exp(G_ref - G)
     const int chunk = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     pdl_wait();
     pdl_launch_dependents();
@@ -60,14 +65,24 @@ __global__ void __launch_bounds__(256) kda_chunk_prep_kernel(KdaParams p, KdaScr
         for (int t = 0; t < kCh; ++t) { acc += sG[t * kLdK + tid]; sG[t * kLdK + tid] = acc; }
     }
     __syncthreads();
-    // 3. A and B, one warp per (t, s <= t), four channels per lane
-    for (int t = 0; t < cc; ++t) {
-        const float4 kt = *reinterpret_cast<const float4*>(sK + t * kLdK + lane * 4);
-        const float4 qt = *reinterpret_cast<const float4*>(sQ + t * kLdK + lane * 4);
-        const float4 gt = *reinterpret_cast<const float4*>(sG + t * kLdK + lane * 4);
-        for (int s = warp; s <= t; s += 8) {
-            const float4 ks = *reinterpret_cast<const float4*>(sK + s * kLdK + lane * 4);
-            const float4 gs = *reinterpret_cast<const float4*>(sG + s * kLdK + lane * 4);
+    // 3. A and B.  The 64 tokens are four sub-chunks of 16.  Pairs inside a sub-chunk keep the exact form (one warp per pair, one exponential
+    // per channel).  Pairs (t in sub-chunk I, s before it) factor through the first token of I:
+    //     exp(G_t - G_s) = exp(G_t - G_ref) * exp(G_ref - G_s),   G_ref = G[16 I]:   both exponents <= 0 (G is non-increasing),
+    // so the block is a plain product of two rescaled tiles (L = rows of I times exp(G - G_ref), R = earlier rows times exp(G_ref - G))
+    // with no exponential in the inner loop: 12k exponentials per block for the tiles instead of 190k for the pairs.
+    for (int I = 0; I < kCh / kSub; ++I) {
+        const int t0 = I * kSub;
+        if (t0 >= cc) break;                                  // block-uniform
+        for (int pidx = warp; pidx < kSub * (kSub + 1) / 2; pidx += 8) {
+            int dt = 0, ds = pidx;
+            while (ds > dt) { ds -= dt + 1; ++dt; }
+            const int t = t0 + dt, s_ = t0 + ds;
+            if (t >= cc) continue;                            // warp-uniform
+            const float4 kt = *reinterpret_cast<const float4*>(sK + t * kLdK + lane * 4);
+            const float4 qt = *reinterpret_cast<const float4*>(sQ + t * kLdK + lane * 4);
+            const float4 gt = *reinterpret_cast<const float4*>(sG + t * kLdK + lane * 4);
+            const float4 ks = *reinterpret_cast<const float4*>(sK + s_ * kLdK + lane * 4);
+            const float4 gs = *reinterpret_cast<const float4*>(sG + s_ * kLdK + lane * 4);
             const float e0 = __expf(fminf(gt.x - gs.x, 0.f)), e1 = __expf(fminf(gt.y - gs.y, 0.f));
             const float e2 = __expf(fminf(gt.z - gs.z, 0.f)), e3 = __expf(fminf(gt.w - gs.w, 0.f));
             const float k0 = ks.x * e0, k1 = ks.y * e1, k2 = ks.z * e2, k3 = ks.w * e3;
@@ -78,8 +93,37 @@ __global__ void __launch_bounds__(256) kda_chunk_prep_kernel(KdaParams p, KdaScr
                 a += __shfl_xor_sync(0xffffffffu, a, o);
                 b += __shfl_xor_sync(0xffffffffu, b, o);
             }
-            if (lane == 0) { sA[t * kLdC + s] = a; sB[t * kLdC + s] = b; }
+            if (lane == 0) { sA[t * kLdC + s_] = a; sB[t * kLdC + s_] = b; }
         }
+        if (I == 0) continue;
+        const float* gref = sG + t0 * kLdK;
+        for (int idx = tid; idx < kSub * kD; idx += 256) {
+            const int tt = idx / kD, c = idx % kD;
+            const float e = __expf(fminf(sG[(t0 + tt) * kLdK + c] - gref[c], 0.f));
+            sLk[tt * kLdR + c] = sK[(t0 + tt) * kLdK + c] * e;
+            sLq[tt * kLdR + c] = sQ[(t0 + tt) * kLdK + c] * e;
+        }
+        for (int idx = tid; idx < t0 * kD; idx += 256) {
+            const int s_ = idx / kD, c = idx % kD;
+            sR[s_ * kLdR + c] = sK[s_ * kLdK + c] * __expf(fminf(gref[c] - sG[s_ * kLdK + c], 0.f));
+        }
+        __syncthreads();
+        // one thread per (t, s): consecutive lanes take consecutive s (odd row stride: conflict free), t is warp-uniform or nearly
+        for (int o = tid; o < kSub * t0; o += 256) {
+            const int tt = o / t0, s_ = o - tt * t0;
+            const float* lk = sLk + tt * kLdR;
+            const float* lq = sLq + tt * kLdR;
+            const float* rr = sR + s_ * kLdR;
+            float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
+#pragma unroll 8
+            for (int c = 0; c < kD; c += 2) {
+                const float r0 = rr[c], r1 = rr[c + 1];
+                a0 = fmaf(lk[c], r0, a0); a1 = fmaf(lk[c + 1], r1, a1);
+                b0 = fmaf(lq[c], r0, b0); b1 = fmaf(lq[c + 1], r1, b1);
+            }
+            if (t0 + tt < cc) { sA[(t0 + tt) * kLdC + s_] = a0 + a1; sB[(t0 + tt) * kLdC + s_] = b0 + b1; }
+        }
+        __syncthreads();                                      // the tiles are rebuilt for the next sub-chunk
     }
     __syncthreads();
     // 4. W row by row (forward substitution): W[t][j] = beta_t ((j == t) - sum_{j <= s < t} A[t][s] W[s][j]); thread j owns column j

@@ -255,7 +255,27 @@ def main():
         eng.free_sequence(sid)
         long_case = {"prompt_tokens": args.long_prompt, "chunk": args.prefill_chunk, "prefill_tok_s": round(args.long_prompt / (ms / 1e3), 1),
                      "ttft_ms": round(ms, 2), "vs_baseline_prefill": round(args.long_prompt / (ms / 1e3) / BASELINE_PREFILL_27K, 2)
-                     if (args.model == "glm-5.3-flash" and args.long_prompt == 27000 and args.prefill_chunk == 2048) else None}
+                     if (args.model == "glm-5.3-flash" and args.long_prompt == 27000 and args.prefill_chunk == 2048) else None,
+                     "expert_activations": "nvfp4 (block-scaled)" if getattr(eng.ws_prefill, "bs_ok", False) else "fp16"}
+        # the same prompt once more with the other many-row expert path (NVFP4 activations on the block-scaled 4-bit x 4-bit kernel, as the
+        # reference's NVFP4 expert path computes): a second, separately labelled number; the headline keys above stay on the default path
+        ws_p = eng.ws_prefill
+        if ws_p is not None and getattr(ws_p, "bs_can", False) and not ws_p.bs_ok:
+            try:
+                ws_p.set_block_scaled(True)
+                sid = eng.create_sequence()
+                eng.prefill(sid, prompt[: args.prefill_chunk])         # first use of the path's buffers and tensor maps
+                eng.free_sequence(sid)
+                sid = eng.create_sequence()
+                _, ms2 = timed_prefill(sid, prompt)
+                eng.free_sequence(sid)
+                long_case["block_scaled_experts"] = {"prefill_tok_s": round(args.long_prompt / (ms2 / 1e3), 1), "ttft_ms": round(ms2, 2),
+                                                     "expert_activations": "nvfp4, tcgen05.mma kind::mxf4nvf4.block_scale"}
+            except RuntimeError as e:                                   # no room for the second path's buffers beside the weights
+                long_case["block_scaled_experts"] = {"unavailable": str(e).splitlines()[0][:160]}
+                torch.cuda.empty_cache()
+            finally:
+                ws_p.set_block_scaled(False)
 
     # ---- cases 2..: decode at the context length, main batch first, then the extra batches on top of the same sequences ----
     sids, toks, results = [], [], []

@@ -535,22 +535,39 @@ class Workspace:
                 self.tc_tile_n = z(self.tc_tiles, dtype=i32); self.tc_cnt = z(2, dtype=i32)
                 # block-scaled path (NVFP4 experts): both operands stay 4-bit, the activations are quantised in tile order
                 fmts = {L["arena"].ef.fmt for L in m.layers if L.get("arena") is not None}
-                self.bs_ok = MOE_BLOCK_SCALED and fmts == {2} and H % 256 == 0 and m.Fe % 256 == 0 and H <= 8192 and m.Fe <= 8192
-                if self.bs_ok:
-                    rows = self.tc_tiles * self.tc_bn
-                    u8 = torch.uint8
-                    self.bs_xq = z(rows, H // 2, dtype=u8); self.bs_xsf = z(self.tc_tiles * (H // 64) * 512, dtype=u8); self.bs_xa = z(rows)
-                    self.bs_act = z(rows, m.Fe, dtype=torch.float16)
-                    self.bs_aq = z(rows, m.Fe // 2, dtype=u8); self.bs_asf = z(self.tc_tiles * (m.Fe // 64) * 512, dtype=u8); self.bs_aa = z(rows)
-                else:
-                    self.tc_xs = z(P, H, dtype=torch.float16)
-                    self.tc_act = z(P, cfg.moe_inter, dtype=torch.float16)
+                self.bs_can = fmts == {2} and H % 256 == 0 and m.Fe % 256 == 0 and H <= 8192 and m.Fe <= 8192
+                self.bs_ok = False
+                self._m, self._z = m, z
         # outputs
         self.n_logit_rows = n_logit_rows
         self.logits = z(n_logit_rows, m.V_local)
         self.amax_part = torch.zeros(n_logit_rows, 64, dtype=torch.int64, device=dev)
         self.out_tok = z(n_logit_rows, dtype=i32)
         self.out_val = z(n_logit_rows)
+
+        if getattr(self, "tc_ok", False):
+            self.set_block_scaled(MOE_BLOCK_SCALED)
+
+    def set_block_scaled(self, on: bool) -> bool:
+        """Switch this workspace's many-row expert path between fp16 activations (weights expanded in the operand pipeline) and NVFP4
+        activations on the block-scaled tensor-core kernel.  The buffers of a path are allocated the first time it is switched on;
+        not while a CUDA graph that uses the workspace exists.  Returns whether the block-scaled path is now active."""
+        if not getattr(self, "tc_ok", False):
+            return False
+        on = bool(on) and self.bs_can
+        m, z, H = self._m, self._z, self._m.cfg.hidden
+        if on and not hasattr(self, "bs_xq"):
+            rows = self.tc_tiles * self.tc_bn
+            u8 = torch.uint8
+            self.bs_xq = z(rows, H // 2, dtype=u8); self.bs_xsf = z(self.tc_tiles * (H // 64) * 512, dtype=u8); self.bs_xa = z(rows)
+            self.bs_act = z(rows, m.Fe, dtype=torch.float16)
+            self.bs_aq = z(rows, m.Fe // 2, dtype=u8); self.bs_asf = z(self.tc_tiles * (m.Fe // 64) * 512, dtype=u8); self.bs_aa = z(rows)
+        if not on and not hasattr(self, "tc_xs"):
+            P = self.tc_sorted.shape[0]
+            self.tc_xs = z(P, H, dtype=torch.float16)
+            self.tc_act = z(P, m.cfg.moe_inter, dtype=torch.float16)
+        self.bs_ok = on
+        return on
 
 
 class DeviceModel:

@@ -114,6 +114,8 @@ ROUTER_FUSED = os.environ.get("LSB_ROUTER_FUSED", "0") != "0"
 KDA_CHUNKED = os.environ.get("LSB_KDA_CHUNKED", "1") not in ("", "0")
 # LSB_MOE_BLOCK_SCALED=1: many-row steps over NVFP4 experts quantise the activations to NVFP4 (one scale per 16 elements and
 # one per row) and run the block-scaled tensor-core kernel (4-bit x 4-bit) instead of expanding the weights to fp16
+# LSB_INDEXER_TC=0: score prefill chunks with the CUDA-core indexer kernel instead of the tcgen05 one
+INDEXER_TC = os.environ.get("LSB_INDEXER_TC", "1") not in ("", "0")
 MOE_BLOCK_SCALED = os.environ.get("LSB_MOE_BLOCK_SCALED", "0") not in ("", "0")
 # LSB_MHC_CLUSTER=0: decode-sized hyper-connection passes fall back to the two-launch path (partials + last-block finalize, contraction)
 MHC_CLUSTER = os.environ.get("LSB_MHC_CLUSTER", "1") not in ("", "0")
@@ -504,6 +506,13 @@ class Workspace:
             self.sel_idx = z(R, self.sel_ld, dtype=i32)
             self.sel_cnt = z(R, dtype=i32)
             self.q_idx = z(R, cfg.index_n_heads, cfg.index_head_dim, dtype=b16)
+            # tensor-core scoring of single-sequence chunks: the sequence's index keys as a dense bf16 operand + their scales
+            self.idx_tc = (INDEXER_TC and R >= 64 and cfg.index_head_dim == 128 and 256 % cfg.index_n_heads == 0)
+            if self.idx_tc:
+                self.idx_kbf_rows = (self.max_entries + 127) // 128 * 128
+                self.idx_kbf = z(self.idx_kbf_rows, 128, dtype=b16)
+                self.idx_kscale = z(self.idx_kbf_rows)
+            self.ne_hint, self.single_seq = 0, False
             self.idx_w = z(R, cfg.index_n_heads)
             self.kstash = z(R, cfg.index_head_dim, dtype=b16)
         # FFN
@@ -1164,8 +1173,14 @@ class DeviceModel:
                 nat.call("lsb_indexer_q_prep", ws.qproj, ldq, Hh * (dn + dr), ws.proj, ldp, off_iw, cfg.index_n_heads,
                          cfg.index_rope_dim, self.inv_freq_idx, ws.row_pos, ws.q_idx, ws.idx_w, ws.kstash, off_ig,
                          self.idx_tail.get(i), ws.row_seq, ws.row_slot, P, R)
-                nat.call("lsb_indexer_score", ws.q_idx, ws.idx_w, cfg.index_n_heads, self.idx_cache[i], self.idx_block_table,
-                         self.max_pages, self.page // P, ws.row_seq, ws.n_entries, ws.scores, ws.max_entries, R, ws.max_entries)
+                if getattr(ws, "idx_tc", False) and ws.single_seq and R >= 64 and 0 < ws.ne_hint <= ws.idx_kbf_rows:
+                    # a prefill chunk: every row scores the same sequence's keys - one GEMM on the tensor cores
+                    nat.call("lsb_indexer_score_tc", ws.q_idx, ws.idx_w, cfg.index_n_heads, self.idx_cache[i], self.idx_block_table,
+                             self.max_pages, self.page // P, ws.row_seq, ws.n_entries, ws.scores, ws.max_entries, R, ws.ne_hint,
+                             ws.idx_kbf, ws.idx_kbf_rows, ws.idx_kscale, TcScratch.get(self.device).err)
+                else:
+                    nat.call("lsb_indexer_score", ws.q_idx, ws.idx_w, cfg.index_n_heads, self.idx_cache[i], self.idx_block_table,
+                             self.max_pages, self.page // P, ws.row_seq, ws.n_entries, ws.scores, ws.max_entries, R, ws.max_entries)
                 nat.call("lsb_indexer_topk", ws.scores, ws.max_entries, ws.n_entries, ws.row_len, ws.row_seq,
                          cfg.index_topk // P, P, ws.sel_idx, ws.sel_cnt, ws.sel_ld, R)
             sel_idx, sel_cnt, sel_ld = ws.sel_idx, ws.sel_cnt, ws.sel_ld

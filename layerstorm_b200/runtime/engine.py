@@ -420,6 +420,9 @@ class Engine:
             h[5, r] = (pos + 1) // P
         for j, (r0, n, slot) in enumerate(seq_groups):
             h[6, j] = r0; h[7, j] = n; h[8, j] = slot
+        # host-side facts about the step that size kernels' grids: the largest index-entry count of a row, one sequence or several
+        ws.ne_hint = max((pos + 1) // P for (_, _, pos) in rows) if rows else 0
+        ws.single_seq = len(seq_groups) == 1 and len({slot for (_, slot, _) in rows}) == 1
         ws.inp.copy_(h, non_blocking=True)
         ev = torch.cuda.Event()
         ev.record(torch.cuda.current_stream())

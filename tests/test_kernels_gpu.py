@@ -424,3 +424,39 @@ def test_many_row_fp32_matrix_runs_as_split_bf16_tensor_core_gemm():
     W(few, x[:4].contiguous(), 4)
     torch.cuda.synchronize()
     assert (few - out[:4]).abs().max().item() < 2e-5 * ref.abs().max().item()
+
+
+@pytest.mark.parametrize("R,IH,pos0", [(200, 32, 2000), (130, 4, 37), (70, 64, 900), (2048, 32, 6144)])
+def test_indexer_scores_on_tensor_cores_match_the_cuda_core_kernel(R, IH, pos0):
+    """A single-sequence prefill chunk: the tcgen05 scoring (keys gathered to bf16, one GEMM, ReLU / head weights / head sum in the
+    epilogue) against the one-thread-per-(row, entry) kernel on the same paged FP8 index cache, for every causal (row, entry)."""
+    from layerstorm_b200.models.device_model import TcScratch
+    P, page_e = 4, 16                                        # 4 tokens per pooled entry, 16 entries per page
+    g = torch.Generator(device=DEV).manual_seed(R + IH)
+    ne = torch.tensor([(pos0 + r + 1) // P for r in range(R)], dtype=torch.int32, device=DEV)
+    ne_max = int(ne[-1])
+    n_pages = (ne_max + page_e - 1) // page_e + 2
+    cache = torch.zeros(n_pages, page_e, 144, dtype=torch.uint8, device=DEV)
+    cache[:, :, :128] = torch.randint(0, 256, (n_pages, page_e, 128), device=DEV, generator=g, dtype=torch.uint8) & 0x77   # finite e4m3
+    cache[:, :, 128:132] = (torch.rand(n_pages, page_e, 1, device=DEV, generator=g) * 0.05 + 0.01).view(torch.uint8)
+    perm = torch.randperm(n_pages, device=DEV, generator=g).int()
+    bt = perm.view(1, n_pages).contiguous()                  # one sequence, scattered pages
+    q = rnd(R, IH, 128).to(torch.bfloat16)
+    w = rnd(R, IH)
+    row_seq = torch.zeros(R, dtype=torch.int32, device=DEV)
+    ld = (ne_max + 127) // 128 * 128 + 64
+    ref = torch.full((R, ld), -7.0, device=DEV)
+    out = torch.full((R, ld), -7.0, device=DEV)
+    nat.call("lsb_indexer_score", q, w, IH, cache, bt, n_pages, page_e, row_seq, ne, ref, ld, R, ld)
+    kbf_rows = (ld + 127) // 128 * 128
+    kbf = torch.zeros(kbf_rows, 128, dtype=torch.bfloat16, device=DEV)
+    ksc = torch.zeros(kbf_rows, device=DEV)
+    err = TcScratch.get(DEV).err
+    err.zero_()
+    nat.call("lsb_indexer_score_tc", q, w, IH, cache, bt, n_pages, page_e, row_seq, ne, out, ld, R, ne_max, kbf, kbf_rows, ksc, err)
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+    mask = torch.arange(ld, device=DEV)[None, :] < ne[:, None]
+    assert torch.equal(out[~mask], ref[~mask])              # nothing written beyond a row's causal frontier
+    d = (out[mask] - ref[mask]).abs().max().item()
+    assert d < 2e-4 * ref[mask].abs().max().item() + 1e-6, d

@@ -244,7 +244,11 @@ def build_model_draft(cfg: dict, shape: ModelConfig, engine, args: argparse.Name
         log.warning("speculation.dspark.checkpoint_path is empty: RANDOM draft weights of shape %s", dshape.name)
         dm = DeviceModel.random_init(dshape, dev, "bf16", page)
     ctx = min(cfg["serving"]["max_sequence_length"], max(ds["draft_context_capacity_tokens"], 1024))
-    return EngineDraft(Engine(dm, max_seqs=2, max_ctx=ctx, prefill_chunk=cfg["orchestrator"]["prefill_chunk_tokens"], max_batch=1), max_gamma=depth), depth
+    # speculation.dspark.confidence_enabled: stop drafting at the first token the draft model itself gives less than
+    # confidence_threshold (top-1 probability, computed on the device next to the token)
+    min_conf = float(ds["confidence_threshold"]) if ds.get("confidence_enabled") else 0.0
+    return EngineDraft(Engine(dm, max_seqs=2, max_ctx=ctx, prefill_chunk=cfg["orchestrator"]["prefill_chunk_tokens"], max_batch=1), max_gamma=depth,
+                       min_confidence=min_conf), depth
 
 
 def build_server(cfg: dict, shape: ModelConfig, ckpt: Optional[str], engine, args: argparse.Namespace):

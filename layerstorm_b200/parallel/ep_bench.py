@@ -101,13 +101,17 @@ def main():
         t_link = link_pairs * (H * 2 + H * 4) / (NVLINK_GBS * 1e9) * 1e3 if world > 1 else 0.0
         t_hbm = touched_max * ef.stride / (hbm_gbs * 1e9) * 1e3
         roof = max(t_compute, t_link, t_hbm)
+        # two library baselines: fixed-capacity slabs (no host round trip; the fair comparison) and exact splits (one .tolist() per call)
         nccl_ms = None if (a.skip_nccl or world == 1) else timed(lambda: ep.forward_nccl(x, ids, wts, out), max(2, a.iters // 2))
+        nccl_var_ms = None if (a.skip_nccl or world == 1) else timed(lambda: ep.forward_nccl_variable(x, ids, wts, out), max(2, a.iters // 2))
         err = torch.tensor([ep.error()], device=dev)
         dist.all_reduce(err, op=dist.ReduceOp.MAX)
         if rank == 0:
             print(json.dumps({"bench": "ep_fused_dispatch_gemm_combine", "n_gpus": world, "tokens_per_rank": T, "fmt": a.fmt, "hidden": H, "experts": E,
                               "top_k": S, "inter": F, "fused_ms": round(fused_ms, 4), "nccl_ms": None if nccl_ms is None else round(nccl_ms, 4),
                               "speedup_vs_nccl": None if nccl_ms is None else round(nccl_ms / fused_ms, 3),
+                              "nccl_baseline": "fixed-capacity all_to_all_single, no host synchronisation",
+                              "nccl_variable_splits_ms": None if nccl_var_ms is None else round(nccl_var_ms, 4),
                               "roofline_ms": {"compute": round(t_compute, 4), "nvlink": round(t_link, 4), "hbm": round(t_hbm, 4)},
                               "roofline_fraction": round(roof / fused_ms, 3), "roofline_basis": tag, "rows_on_busiest_rank": int(rows_max),
                               "experts_touched_on_busiest_rank": int(touched_max), "error_word": int(err)}), flush=True)

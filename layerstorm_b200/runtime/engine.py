@@ -559,7 +559,12 @@ class Engine:
         """Whether ``decode(..., sample=...)`` can draw the next token on the device (needs the whole vocabulary on this GPU)."""
         return self.model.tp_size == 1
 
-    def decode(self, sids: Sequence[int], tokens: Sequence[int], return_logits: bool = False, sample=None):
+    @property
+    def supports_confidence(self) -> bool:
+        """Whether ``decode(confidence=True)`` can report the step's top-1 probability (the whole vocabulary on this GPU)."""
+        return self.model.tp_size == 1
+
+    def decode(self, sids: Sequence[int], tokens: Sequence[int], return_logits: bool = False, sample=None, confidence: bool = False):
         """One decode step for a batch of sequences: feeds ``tokens[i]`` at the frontier of
         ``sids[i]`` and returns the next token per sequence - the arg-max, or with ``sample = (temperature, top_k, top_p,
         seed)`` a draw from the filtered distribution made on the device (Philox stream keyed by the seed and the token's
@@ -596,10 +601,24 @@ class Engine:
                 self.kernel_launches += 1
             self.h_out[:B].copy_(ws.out_tok[:B], non_blocking=True)
             self.d2h_bytes += 4 * B
+            if confidence:
+                # top-1 probability and entropy of every row's distribution, computed on the device: 8 more bytes per row come back
+                if not self.supports_confidence:
+                    raise RuntimeError("step confidence needs the full vocabulary on one GPU")
+                if not hasattr(ws, "conf"):
+                    ws.conf = torch.zeros(2, ws.R, device=self.dev)
+                    ws.h_conf = torch.zeros(2, ws.R).pin_memory()
+                V = ws.logits.shape[1]
+                nat.call("lsb_confidence", ws.logits, V, B, V, ws.conf[0], ws.conf[1])
+                self.kernel_launches += 1
+                ws.h_conf.copy_(ws.conf, non_blocking=True)
+                self.d2h_bytes += 8 * B
             self._queue_error_readback()
             self.stream.synchronize()
             self._check_errors()
         out = [int(self.h_out[j]) for j in range(B)]
+        if confidence:
+            conf = [(float(ws.h_conf[0, j]), float(ws.h_conf[1, j])) for j in range(B)]
         for sid, tok in zip(sids, tokens):
             s = self.seqs[sid]
             s.length += 1
@@ -608,6 +627,8 @@ class Engine:
                 self.row_tier.slide_window(sid)
         if return_logits:
             return out, ws.logits[:B].float().cpu()
+        if confidence:
+            return out, conf
         return out
 
     def _capture(self, B: int, ws: Workspace):

@@ -39,9 +39,14 @@ def draft_shape_for(target: ModelConfig, n_layers: int = 2, quant: str = "nvfp4"
 class EngineDraft:
     """``propose(context, gamma)`` backed by an engine (GPU ``Engine`` or the null engine)."""
 
-    def __init__(self, engine, max_gamma: int = 8):
+    def __init__(self, engine, max_gamma: int = 8, min_confidence: float = 0.0):
+        """``min_confidence`` > 0: drafting stops at the first token whose top-1 probability under the draft model is below it (that
+        token is not proposed).  The probability comes from the device with the token (``Engine.decode(confidence=True)``); engines that
+        cannot report it draft the full depth."""
         self.engine = engine
         self.max_gamma = max_gamma
+        self.min_confidence = float(min_confidence)
+        self.early_stops = 0
         self.sid: Optional[int] = None
         self.fed: List[int] = []           # tokens whose KV rows are in the draft cache
         self.failures = 0
@@ -90,8 +95,19 @@ class EngineDraft:
             out: List[int] = []
             if getattr(eng, "has_recurrent_state", False) and hasattr(eng, "anchor"):
                 eng.anchor(sid)            # the drafted tokens are rolled back through this snapshot
+            gate = self.min_confidence > 0.0 and getattr(eng, "supports_confidence", False)
+            fed = 0
             for _ in range(g):
-                tok = int(eng.decode([sid], [tok])[0])
+                if gate:
+                    toks, conf = eng.decode([sid], [tok], confidence=True)
+                    fed += 1
+                    if conf[0][0] < self.min_confidence:
+                        self.early_stops += 1
+                        break
+                    tok = int(toks[0])
+                else:
+                    tok = int(eng.decode([sid], [tok])[0])
+                    fed += 1
                 out.append(tok)
             eng.rewind(sid, len(context) - 1)
             return out

@@ -42,8 +42,13 @@ def main():
         ep.forward(x, ids, wts, out)
         torch.cuda.synchronize()
         base = torch.zeros(R, H, device=dev)
-        ep.forward_nccl(x, ids, wts, base)
+        ep.forward_nccl(x, ids, wts, base)                     # fixed-capacity slabs, no host round trip
+        base2 = torch.zeros(R, H, device=dev)
+        ep.forward_nccl_variable(x, ids, wts, base2)           # exact split sizes through the host
         torch.cuda.synchronize()
+        if not torch.allclose(base, base2, rtol=1e-5, atol=1e-6):
+            print(f"rank {rank} call {it}: the two library baselines disagree (a slab overflowed?)", flush=True)
+            ok = False
         xd, want = x.double().cpu(), torch.zeros(R, H, dtype=torch.float64)
         for r in range(R):
             for s in range(S):

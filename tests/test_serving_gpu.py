@@ -134,3 +134,33 @@ def test_sampled_requests_draw_on_the_device_and_repeat_for_a_fixed_seed():
     greedy = InferenceRequest("g", list(prompt), SamplingParams(max_tokens=16, ignore_eos=True))
     orch.submit_request(greedy); orch.step()
     assert greedy.output_ids != outs[0]
+
+
+def test_decode_reports_the_steps_confidence_from_the_device():
+    """``Engine.decode(confidence=True)``: top-1 probability and entropy of the step's distribution come back with the token (8 bytes per row)
+    and equal the softmax of the logits; a confidence-gated draft stops at the first token below its threshold."""
+    import torch
+    from layerstorm_b200.models.config import get_preset
+    from layerstorm_b200.models.device_model import DeviceModel
+    from layerstorm_b200.models.weights import init_weights
+    from layerstorm_b200.runtime.engine import Engine
+    from layerstorm_b200.speculation.model_draft import EngineDraft
+    cfg = get_preset("tiny-mla-moe")
+    m = DeviceModel.from_state_dict(cfg, init_weights(cfg, 5), "cuda", kv_fmt="bf16", page=16)
+    eng = Engine(m, max_seqs=2, max_ctx=128, prefill_chunk=16, max_batch=1, use_graph=True)
+    assert eng.supports_confidence
+    sid = eng.create_sequence()
+    prompt = torch.randint(0, cfg.vocab, (20,), generator=torch.Generator().manual_seed(1)).tolist()
+    tok = eng.prefill(sid, prompt)
+    toks, conf = eng.decode([sid], [tok], confidence=True)
+    lg = eng.ws_decode[1].logits[0].float()
+    p = torch.softmax(lg, 0)
+    assert abs(conf[0][0] - float(p.max())) < 1e-4
+    assert abs(conf[0][1] - float(-(p * torch.log(p.clamp_min(1e-30))).sum())) < 1e-3
+    assert toks[0] == int(lg.argmax())
+    # gated drafting: an impossible threshold stops at once, a zero threshold drafts the full depth
+    ctx = prompt + [tok]
+    d_all = EngineDraft(Engine(m, max_seqs=2, max_ctx=128, prefill_chunk=16, max_batch=1), max_gamma=4, min_confidence=0.0)
+    d_none = EngineDraft(Engine(m, max_seqs=2, max_ctx=128, prefill_chunk=16, max_batch=1), max_gamma=4, min_confidence=1.1)
+    assert len(d_all.propose(ctx, 4)) == 4
+    assert d_none.propose(ctx, 4) == [] and d_none.early_stops == 1

@@ -262,3 +262,46 @@ def test_mtp_block_weights_roundtrip_through_an_hf_checkpoint(tmp_path):
     for k in (f"layers.{L}.mtp.enorm", f"layers.{L}.mtp.hnorm", f"layers.{L}.mtp.eh_proj", f"layers.{L}.mtp.final_norm", f"layers.{L}.attn.q_a",
               f"layers.{L}.attn.k_b", f"layers.{L}.attn_norm.weight", f"layers.{L}.moe.router", f"layers.{L}.moe.experts.2.up"):
         assert torch.equal(ck[k], w[k]), k
+
+
+def test_engine_draft_stops_at_the_first_low_confidence_token():
+    """Confidence-gated drafting against an engine that reports a top-1 probability with every token: the draft ends BEFORE the
+    first token below the threshold, the engine is rewound to the context, and engines without the capability draft the full depth."""
+    from layerstorm_b200.speculation.model_draft import EngineDraft
+
+    class Eng:
+        supports_confidence = True
+        has_recurrent_state = False
+
+        def __init__(self, confs):
+            self.confs, self.calls, self.len, self.rewound = list(confs), 0, 0, None
+
+        def create_sequence(self):
+            return 0
+
+        def free_sequence(self, sid):
+            pass
+
+        def prefill(self, sid, toks, want_logits=False):
+            self.len += len(toks)
+
+        def decode(self, sids, toks, confidence=False):
+            c = self.confs[self.calls]
+            self.calls += 1
+            self.len += 1
+            out = [100 + self.calls]
+            return (out, [(c, 0.0)]) if confidence else out
+
+        def rewind(self, sid, n):
+            self.rewound, self.len = n, n
+
+    ctx = [1, 2, 3, 4]
+    e = Eng([0.9, 0.8, 0.2, 0.9])
+    d = EngineDraft(e, max_gamma=4, min_confidence=0.5)
+    assert d.propose(ctx, 4) == [101, 102]                 # the third token (0.2) and everything after it is not proposed
+    assert e.calls == 3 and e.rewound == len(ctx) - 1 and d.early_stops == 1
+    e2 = Eng([0.1] * 4)
+    assert EngineDraft(e2, max_gamma=4, min_confidence=0.0).propose(ctx, 4) == [101, 102, 103, 104]
+    e3 = Eng([0.1] * 4)
+    e3.supports_confidence = False
+    assert EngineDraft(e3, max_gamma=4, min_confidence=0.5).propose(ctx, 4) == [101, 102, 103, 104]

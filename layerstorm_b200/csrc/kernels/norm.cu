@@ -698,4 +698,28 @@ LSB_API int lsb_mhc_contract_norm(void* out, const void* residual, const void* x
     LSB_CHECK_LAUNCH();
 }
 
+// out[r] = cos(a[r], b[r]) over `dim` bf16 elements (0 when either vector is all zero): how much a layer changed its input.
+__global__ void __launch_bounds__(256) cosine_sim_kernel(const bf16* __restrict__ a, const bf16* __restrict__ b, int dim, int lda, int ldb,
+                                                         float* __restrict__ out) {
+    __shared__ float red[3][33];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int r = blockIdx.x;
+    float ab = 0.f, aa = 0.f, bb = 0.f;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+        const float x = __bfloat162float(a[(size_t)r * lda + i]), y = __bfloat162float(b[(size_t)r * ldb + i]);
+        ab = fmaf(x, y, ab); aa = fmaf(x, x, aa); bb = fmaf(y, y, bb);
+    }
+    ab = block_sum(ab, red[0]); aa = block_sum(aa, red[1]); bb = block_sum(bb, red[2]);
+    if (threadIdx.x == 0) out[r] = (aa > 0.f && bb > 0.f) ? ab * rsqrtf(aa) * rsqrtf(bb) : 0.f;
+}
+
+// Cosine similarity of `rows` pairs of bf16 vectors (layer skipping: the input of a layer against the input of the next one).
+// Reference: src/compute/kernels/similarity/cosine_sim.h (one pair per call, output on the device).
+LSB_API int lsb_cosine_sim(const void* a, const void* b, int rows, int dim, int lda, int ldb, void* out, void* stream) {
+    if (rows <= 0 || dim <= 0) return -1;
+    launch_pdl((cosine_sim_kernel), rows, 256, 0, (cudaStream_t)stream, (const bf16*)a, (const bf16*)b, dim, lda, ldb, (float*)out);
+    LSB_CHECK_LAUNCH();
+}
+
 LSB_API int lsb_trace_set_norm(void* buf) { return lsb_trace_install(buf); }

@@ -610,6 +610,8 @@ class DeviceModel:
         self._fused = False
         self.dcp = None
         self.idx_identity = False  # the indexer's key cache keeps a page table of its own (row-granular KV tiering: its pages never leave HBM)
+        self.skip_layers = frozenset()   # layers whose attention + FFN a step leaves out (self-speculative drafting; never the first or last)
+        self.probe = None                # {"prev": bf16 [1, hidden], "sims": fp32 [n_layers]} while layer-input similarities are recorded
         self.row_tier = None      # RowTiering (runtime/kv_tiering.py) when old KV pages of active sequences live in pinned host memory
         self.streamer = None      # ExpertStreamer when the VRAM expert cache is capped (runtime/streaming.py)
         self.drift = None         # dict: eager steps store every layer's output rows here (input of utils/determinism_probe.py drift)
@@ -1235,6 +1237,30 @@ class DeviceModel:
         nat.call("lsb_mhc_post_pre", ws.x, ws.resid, ws.sub, ws.post, ws.comb, fn, sc, base, norm_w, ws.part, R, H, n,
                  mode, cfg.hc_sinkhorn_iters, cfg.hc_eps, cfg.rms_eps, cfg.hc_post_mult, ws.hc_done, ws.hc_pre, self._cp)
 
+    def set_layer_skip(self, skip=(), probe: bool = False):
+        """Layer skipping for draft passes: ``skip`` = layers to leave out (the first and the last layer are never skipped), ``probe`` =
+        record, per executed layer l, the cosine similarity between the normalised input of l and of the next executed layer (row 0 of
+        the step) in ``self.probe["sims"][l]`` - "how much did layer l change its input".  Reference: layer skip during the
+        self-speculative draft (python/orchestrator/layer_skip.py; src/compute/kernels/similarity/cosine_sim.h)."""
+        n = self.cfg.n_layers
+        self.skip_layers = frozenset(int(l) for l in skip if 0 < int(l) < n - 1)
+        if probe and self.probe is None:
+            self.probe = {"prev": torch.zeros(1, self.cfg.hidden, dtype=torch.bfloat16, device=self.device),
+                          "sims": torch.zeros(n, dtype=torch.float32, device=self.device)}
+        if not probe:
+            self.probe = None
+
+    def _probe_input(self, i: int, ws: Workspace, last: int) -> int:
+        """Called when ``ws.x`` holds the input of layer i; ``last`` = the previously executed layer (-1 for none)."""
+        pr = self.probe
+        if pr is None:
+            return i
+        H = self.cfg.hidden
+        if last >= 0:
+            nat.call("lsb_cosine_sim", pr["prev"], ws.x, 1, H, H, H, pr["sims"][last: last + 1])
+        pr["prev"].copy_(ws.x[:1])
+        return i
+
     def forward(self, ws: Workspace, R: int, nseq: int, logit_row0: int, n_logit_rows: int):
         """Run one step over the first ``R`` rows of the workspace (inputs already staged in
         ``ws``).  Writes logits for rows [logit_row0, logit_row0 + n_logit_rows)."""
@@ -1259,9 +1285,13 @@ class DeviceModel:
             # decode-sized steps: one cluster kernel per post -> pre pass, with the MoE combine folded in front and the router behind
             clus = R <= MHC_CLUSTER_MAX_ROWS and self._mhc_cluster_ok()
             pending = None         # slot table of the MoE layer whose combine the next pass performs
+            last_run = -1
             for i, L in enumerate(self.layers):
+                if i in self.skip_layers:
+                    continue                 # the pending sublayer output, its gates and the residual streams wait for the next executed pass
                 self._hc_pass(L["hc_attn"], L["attn_norm"], ws, R, 0 if i == 0 else 1, clus, pending, None)
                 pending = None
+                last_run = self._probe_input(i, ws, last_run)
                 if cfg.is_kda_layer(i):
                     self._kda(i, L, ws, R, nseq)
                 else:
@@ -1278,14 +1308,20 @@ class DeviceModel:
             resid = ws.resid.view(-1)[: ws.R * H].view(ws.R, H)
             nat.call("lsb_embedding", resid, None, self.embed, ws.tok, R, H, 0, cfg.vocab)
             nat.call("lsb_rmsnorm", ws.x, resid, self.layers[0]["attn_norm"], R, H, H, H, cfg.rms_eps, 1, None)
+            last_run = -1
             for i, L in enumerate(self.layers):
+                nxt = self.layers[i + 1]["attn_norm"] if i + 1 < cfg.n_layers else self.final_norm
+                if i in self.skip_layers:
+                    # the residual stays as it is; only the normalisation weights change to the next layer's
+                    nat.call("lsb_rmsnorm", ws.x, resid, nxt, R, H, H, H, cfg.rms_eps, 1, None)
+                    continue
+                last_run = self._probe_input(i, ws, last_run)
                 if cfg.is_kda_layer(i):
                     self._kda(i, L, ws, R, nseq)
                 else:
                     self._mla(i, L, ws, R)
                 nat.call("lsb_add_rmsnorm", ws.x, resid, ws.sub, L["ffn_norm"], R, H, cfg.rms_eps, self._cp)
                 self._ffn(i, L, ws, R)
-                nxt = self.layers[i + 1]["attn_norm"] if i + 1 < cfg.n_layers else self.final_norm
                 nat.call("lsb_add_rmsnorm", ws.x, resid, ws.sub, nxt, R, H, cfg.rms_eps, self._cp)
                 if self.drift is not None:
                     self.drift[f"layer{i:03d}.resid"] = resid[:R].float().cpu()

@@ -559,6 +559,21 @@ class Engine:
         """Whether ``decode(..., sample=...)`` can draw the next token on the device (needs the whole vocabulary on this GPU)."""
         return self.model.tp_size == 1
 
+    def set_layer_skip(self, skip=(), probe: bool = False):
+        """Draft-pass layer skipping (see ``DeviceModel.set_layer_skip``); applies to the following steps of this engine."""
+        self.model.set_layer_skip(skip, probe)
+
+    def layer_similarities(self) -> Dict[int, float]:
+        """Per executed layer of the last probed step: cosine similarity between the layer's input and the next executed layer's input
+        (one small D2H read; only while probing is on)."""
+        pr = self.model.probe
+        if pr is None:
+            return {}
+        with torch.cuda.stream(self.stream):
+            v = pr["sims"].cpu()
+        run = [i for i in range(self.cfg.n_layers) if i not in self.model.skip_layers]
+        return {l: float(v[l]) for l in run[:-1]}
+
     @property
     def supports_confidence(self) -> bool:
         """Whether ``decode(confidence=True)`` can report the step's top-1 probability (the whole vocabulary on this GPU)."""
@@ -582,10 +597,14 @@ class Engine:
                 groups.append((j, 1, s.slot))
             self._stage(ws, rows, groups)
             if self.use_graph:
-                if B not in self.graphs:
-                    self._capture(B, ws)
-                self.graphs[B].replay()
-                self.kernel_launches += self.graph_launches[B]
+                # one graph per batch size and per set of skipped layers (a draft pass that leaves layers out replays its own graph)
+                gk = B if not (self.model.skip_layers or self.model.probe is not None) else (B, self.model.skip_layers, self.model.probe is not None)
+                if gk not in self.graphs:
+                    if len(self.graphs) > 64:
+                        raise RuntimeError("too many captured decode graphs (layer-skip sets): clear Engine.graphs")
+                    self._capture(B, ws, gk)
+                self.graphs[gk].replay()
+                self.kernel_launches += self.graph_launches[gk]
             else:
                 n0 = nat.launch_count()
                 self.model.forward(ws, B, B, 0, B)
@@ -631,7 +650,8 @@ class Engine:
             return out, conf
         return out
 
-    def _capture(self, B: int, ws: Workspace):
+    def _capture(self, B: int, ws: Workspace, gk=None):
+        gk = B if gk is None else gk
         # warm-up run outside capture (sets function attributes, touches every buffer); the KDA
         # state it perturbs is restored by snapshotting the affected slots first.
         slots = [int(ws.seq_slot[j]) for j in range(B)]
@@ -645,9 +665,9 @@ class Engine:
         with torch.cuda.graph(g, stream=self.stream):
             self.model.forward(ws, B, B, 0, B)
             self.model.argmax(ws, B)
-        self.graph_launches[B] = nat.launch_count() - n0
+        self.graph_launches[gk] = nat.launch_count() - n0
         self._restore_recurrent(slots, snap)
-        self.graphs[B] = g
+        self.graphs[gk] = g
 
     def _snapshot_recurrent(self, slots):
         m = self.model

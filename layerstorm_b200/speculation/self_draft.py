@@ -5,8 +5,11 @@ tensors, ``k`` routed experts per token instead of the model's top-k, own KV cac
 model (``EngineDraft``: incremental sync of the draft cache, ``gamma`` greedy steps, rewind).  The expert bytes streamed per drafted
 token fall by top_k / k in the MoE layers while attention and the shared expert stay exact, so acceptance is high where the top expert
 dominates the mixture.  Verification by the full model is the ordinary lossless path of the orchestrator.
-``plan`` (``policies.SelfSpeculativePlan``) supplies the early-exit rule and the acceptance statistics; layer skipping is not applied
-by the engines (the policy object exists, no engine has a skip path).
+``plan`` (``policies.SelfSpeculativePlan``) supplies the early-exit rule and the acceptance statistics.  With a ``layer_skip`` section
+(``speculation.layer_skip_draft``) and a draft engine that can leave layers out (``Engine.set_layer_skip``) the draft passes also skip
+layers: every draft step records, on the device, the cosine similarity between each executed layer's input and the next one's; once the
+draft's acceptance rate allows it, ``policies.LayerSkipPolicy`` turns the last step's similarities into the set of layers the NEXT
+round's draft steps leave out (protected first / last layers, contiguity and product gates, a cap on the skipped fraction).
 Reference counterpart: python/orchestrator/self_speculative.py (reduced-expert full-model draft pass, third draft source after prompt
 lookup and MTP).
 """
@@ -19,11 +22,16 @@ from .policies import SelfSpeculativePlan
 
 
 class SelfSpeculativeDraft(EngineDraft):
-    def __init__(self, engine, cfg: dict, max_gamma: int = 8):
-        """``engine``: the TARGET engine (or its model holder) offering ``reduced_expert_view``; ``cfg``: ``speculation.self_speculative``."""
+    def __init__(self, engine, cfg: dict, max_gamma: int = 8, layer_skip: dict = None):
+        """``engine``: the TARGET engine (or its model holder) offering ``reduced_expert_view``; ``cfg``: ``speculation.self_speculative``;
+        ``layer_skip``: ``speculation.layer_skip_draft`` (optional)."""
+        from .policies import LayerSkipPolicy
         k = max(1, int(cfg.get("draft_expert_count", 1)))
         super().__init__(make_reduced_engine(engine, k), max_gamma)
         mc = engine.cfg if hasattr(engine, "cfg") else engine.model.cfg
+        self.skip_policy = LayerSkipPolicy(layer_skip or {}, mc.n_layers)
+        self.skip_set = set()
+        self.skipped_layer_steps = 0
         moe = [i for i in range(mc.n_layers) if mc.is_moe_layer(i)]
         self.plan = SelfSpeculativePlan(cfg, moe, mc.n_layers, mc.top_k, max_depth=max_gamma)
         self.expert_fraction = self.plan.expert_fraction(mc.top_k)
@@ -31,7 +39,18 @@ class SelfSpeculativeDraft(EngineDraft):
     def propose(self, context: Sequence[int], gamma: int) -> List[int]:
         if not self.plan.enabled:
             return []
-        return super().propose(context, min(gamma, self.plan.max_depth))
+        eng = self.engine
+        skipping = self.skip_policy.enabled and hasattr(eng, "set_layer_skip")
+        if skipping:
+            use = self.skip_set if self.skip_policy.active(self.plan.acceptance_rate) else set()
+            eng.set_layer_skip(use, probe=True)
+        out = super().propose(context, min(gamma, self.plan.max_depth))
+        if skipping:
+            self.skipped_layer_steps += len(eng.model.skip_layers) * len(out)
+            sims = eng.layer_similarities()              # of the round's last draft step
+            if sims:
+                self.skip_set = self.skip_policy.skip_set(sims)
+        return out
 
     def feedback(self, proposed: int, accepted: int):
         self.plan.record(proposed, accepted)

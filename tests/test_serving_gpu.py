@@ -164,3 +164,54 @@ def test_decode_reports_the_steps_confidence_from_the_device():
     d_none = EngineDraft(Engine(m, max_seqs=2, max_ctx=128, prefill_chunk=16, max_batch=1), max_gamma=4, min_confidence=1.1)
     assert len(d_all.propose(ctx, 4)) == 4
     assert d_none.propose(ctx, 4) == [] and d_none.early_stops == 1
+
+
+@pytest.mark.parametrize("name", ["tiny-mla-moe", "tiny-glm5-next"])
+def test_self_speculative_draft_with_layer_skipping_is_lossless_on_the_gpu(name):
+    """The target drafts for itself with fewer experts AND with layers left out; the skip set comes from the cosine similarities the draft
+    steps record on the device.  Verification by the full model keeps the output identical to plain greedy decoding."""
+    from layerstorm_b200.models.config import get_preset
+    from layerstorm_b200.models.device_model import DeviceModel
+    from layerstorm_b200.models.weights import init_weights
+    from layerstorm_b200.runtime.engine import Engine
+    from layerstorm_b200.serving.orchestrator import InferenceRequest, Orchestrator, SamplingParams
+    from layerstorm_b200.speculation.self_draft import SelfSpeculativeDraft
+    cfg = get_preset(name)
+    m = DeviceModel.from_state_dict(cfg, init_weights(cfg, 3), "cuda", kv_fmt="bf16", page=16)
+    prompt = list(range(7, 31))
+
+    def run(draft_for=None):
+        eng = Engine(m, max_seqs=2, max_ctx=128, prefill_chunk=16, max_batch=1)
+        draft = draft_for(eng) if draft_for else None
+        orch = Orchestrator(eng, draft=draft, speculation_depth=3) if draft else Orchestrator(eng)
+        req = InferenceRequest("r", prompt, SamplingParams(max_tokens=14, ignore_eos=True))
+        orch.submit_request(req)
+        assert orch.step() and req.error is None
+        return req, draft
+
+    plain, _ = run()
+    # a threshold below any cosine: every unprotected layer the policy may skip is skipped from the second round on
+    skip_cfg = {"enabled": True, "threshold": -1.0, "min_acceptance_rate_to_enable": 0.0, "no_skip_first": 1, "no_skip_last": 1,
+                "target_skip_fraction": 0.5}
+    spec, draft = run(lambda eng: SelfSpeculativeDraft(eng, {"draft_expert_count": 2, "adaptive_exit_enabled": False}, max_gamma=3, layer_skip=skip_cfg))
+    assert spec.output_ids == plain.output_ids
+    assert spec.stats.spec_rounds > 0 and draft.failures == 0
+    assert draft.skip_set and draft.skipped_layer_steps > 0                 # layers were really left out of draft steps
+    assert all(0 < l < cfg.n_layers - 1 for l in draft.skip_set)
+    sims = draft.engine.layer_similarities()
+    assert sims and all(-1.001 <= v <= 1.001 for v in sims.values())
+
+
+def test_cosine_similarity_kernel():
+    from layerstorm_b200.ops import _native as nat
+    g = torch.Generator(device="cuda").manual_seed(2)
+    a = torch.randn(5, 1000, device="cuda", generator=g).to(torch.bfloat16)
+    b = (a.float() * 0.7 + torch.randn(5, 1000, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+    b[3] = 0
+    out = torch.full((5,), 9.0, device="cuda")
+    nat.call("lsb_cosine_sim", a, b, 5, 1000, 1000, 1000, out)
+    torch.cuda.synchronize()
+    ref = torch.nn.functional.cosine_similarity(a.float(), b.float(), dim=1)
+    assert float(out[3]) == 0.0
+    keep = torch.tensor([0, 1, 2, 4], device="cuda")
+    assert torch.allclose(out[keep], ref[keep], atol=1e-5)

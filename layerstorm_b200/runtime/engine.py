@@ -621,7 +621,7 @@ class Engine:
             self.h_out[:B].copy_(ws.out_tok[:B], non_blocking=True)
             self.d2h_bytes += 4 * B
             if confidence:
-                # top-1 probability and entropy of every row's distribution, computed on the device: 8 more bytes per row come back
+                # top-1 probability and normalised entropy (H / ln V) of every row's distribution, computed on the device: 8 more bytes per row
                 if not self.supports_confidence:
                     raise RuntimeError("step confidence needs the full vocabulary on one GPU")
                 if not hasattr(ws, "conf"):

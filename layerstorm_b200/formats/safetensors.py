@@ -37,6 +37,10 @@ class SafetensorsReader:
     def keys(self) -> Iterable[str]:
         return self.header.keys()
 
+    def header_items(self) -> dict:
+        """{tensor name: (safetensors dtype string, shape)} of this file."""
+        return {k: (e["dtype"], tuple(e["shape"])) for k, e in self.header.items()}
+
     def info(self, name: str) -> Tuple[str, Tuple[int, ...], int]:
         e = self.header[name]
         return e["dtype"], tuple(e["shape"]), e["data_offsets"][1] - e["data_offsets"][0]

@@ -370,6 +370,92 @@ class LazyCheckpoint(Mapping):
         return torch.from_numpy(np.ascontiguousarray(r.get_slice(name, e * per, per))).float().reshape(shape[1:])
 
 
+class QuantSkipList:
+    """The modules a mixed-precision (FP8) HuggingFace checkpoint keeps unquantised: ``quantization_config.modules_to_not_convert`` of
+    its ``config.json``.  This loader never converts dtypes (the safetensors header is the authority), so the list is a correctness
+    cross-check: every matrix-shaped weight must be FP8 exactly when it is NOT on the list.
+
+    The list names MODULE paths of the loaded model (``model.layers.N...``, ``visual...``) while multimodal checkpoints store their
+    TENSORS under a wrapper (``model.language_model.layers.N...``, ``model.visual...``): a literal comparison matches nothing.  Both
+    sides are therefore brought into one namespace first (wrapper prefixes and the role suffix ``.weight`` / ``.weight_scale`` /
+    ``.weight_scale_inv`` / ``.bias`` stripped).  An entry matches a tensor when it equals the tensor's module path or is a whole-path
+    prefix of it (``model.layers.3.self_attn`` covers ``model.layers.3.self_attn.kv_b_proj.weight``).
+    Reference: src/model/weight_loader/quant_skip_list.h (same cross-check, fails the load on disagreement or on a list that matches
+    no tensor)."""
+    _ROLES = (".weight_scale_inv", ".weight_scale_2", ".weight_scale", ".weight", ".bias")
+
+    def __init__(self, entries, quant_method: str = ""):
+        self.quant_method = quant_method
+        self.entries = sorted({self.canonical(e) for e in entries if e})
+
+    @staticmethod
+    def canonical(name: str) -> str:
+        n = name.strip()
+        for r in QuantSkipList._ROLES:
+            if n.endswith(r):
+                n = n[: -len(r)]
+                break
+        for pre in ("model.language_model.", "language_model.model.", "language_model."):
+            if n.startswith(pre):
+                n = "model." + n[len(pre):]
+                break
+        if n == "visual" or n.startswith("visual."):
+            n = "model." + n
+        return n
+
+    @classmethod
+    def from_model_dir(cls, directory: str) -> Optional["QuantSkipList"]:
+        cj = os.path.join(directory, "config.json")
+        if not os.path.exists(cj):
+            return None
+        c = json.load(open(cj))
+        qc = c.get("quantization_config") or (c.get("text_config") or {}).get("quantization_config")
+        if not isinstance(qc, dict) or "modules_to_not_convert" not in qc:
+            return None
+        ents = qc["modules_to_not_convert"]
+        if ents is not None and not isinstance(ents, list):
+            raise ValueError("quantization_config.modules_to_not_convert must be a list")
+        return cls(ents or [], str(qc.get("quant_method", "")))
+
+    def matches(self, tensor_name: str) -> bool:
+        n = self.canonical(tensor_name)
+        import bisect
+        i = bisect.bisect_right(self.entries, n)
+        if i and self.entries[i - 1] == n:
+            return True
+        # a prefix entry sorts before the name; walk the path upwards instead of scanning the list
+        parts = n.split(".")
+        for k in range(len(parts) - 1, 0, -1):
+            pre = ".".join(parts[:k])
+            j = bisect.bisect_left(self.entries, pre)
+            if j < len(self.entries) and self.entries[j] == pre:
+                return True
+        return False
+
+    def cross_check(self, dtype_of: Dict[str, str], shape_of: Dict[str, tuple]) -> dict:
+        """``dtype_of`` / ``shape_of``: safetensors dtype string and shape per tensor name.  Raises ``ValueError`` when an FP8 matrix is
+        on the list, a listed-free matrix with a scale companion is not FP8, or a non-empty list matches no tensor at all."""
+        fp8 = {"F8_E4M3", "F8_E5M2"}
+        matched = 0
+        bad = []
+        for name, dt in dtype_of.items():
+            if not name.endswith(".weight") or len(shape_of.get(name, ())) < 2:
+                continue
+            listed = self.matches(name)
+            matched += listed
+            is_fp8 = dt in fp8
+            has_scale = (name[: -len(".weight")] + ".weight_scale_inv") in dtype_of or (name[: -len(".weight")] + ".weight_scale") in dtype_of
+            if listed and is_fp8:
+                bad.append(f"{name}: FP8 although its module is listed as not converted")
+            elif not listed and not is_fp8 and has_scale:
+                bad.append(f"{name}: carries a quantisation scale but is stored as {dt}")
+        if self.entries and matched == 0:
+            bad.append(f"none of the {len(self.entries)} modules_to_not_convert entries matches a tensor of this checkpoint (namespace mismatch?)")
+        if bad:
+            raise ValueError("quantisation skip list disagrees with the checkpoint: " + "; ".join(bad[:6]) + (f" (+{len(bad) - 6} more)" if len(bad) > 6 else ""))
+        return {"entries": len(self.entries), "matrices_kept": matched}
+
+
 def open_checkpoint(path: str, cfg: Optional[ModelConfig] = None) -> tuple[ModelConfig, LazyCheckpoint]:
     """``path`` = HF directory, a ``.safetensors`` file inside one, or a ``.gguf`` file (first shard)."""
     if path.endswith(".gguf"):
@@ -385,7 +471,18 @@ def open_checkpoint(path: str, cfg: Optional[ModelConfig] = None) -> tuple[Model
     d = path if os.path.isdir(path) else os.path.dirname(path)
     if cfg is None:
         cfg = from_hf_config(os.path.join(d, "config.json"))
-    return cfg, LazyCheckpoint(cfg, SafetensorsSource(d), "hf")
+    src = SafetensorsSource(d)
+    skip = QuantSkipList.from_model_dir(d)
+    if skip is not None and skip.quant_method in ("fp8", ""):
+        dts, shp = {}, {}
+        for fname in sorted(set(src.where.values())):
+            for name, (dt, shape) in src._reader(fname).header_items().items():
+                dts[name], shp[name] = dt, shape
+        if any(dt in ("F8_E4M3", "F8_E5M2") for dt in dts.values()):
+            skip.cross_check(dts, shp)                       # load-stopping on disagreement
+    ck = LazyCheckpoint(cfg, src, "hf")
+    ck.quant_skip = skip
+    return cfg, ck
 
 
 def export_hf(cfg: ModelConfig, w: Dict[str, torch.Tensor], directory: str, dtype=torch.bfloat16, shard_bytes: int = 1 << 30):

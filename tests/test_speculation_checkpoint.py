@@ -305,3 +305,32 @@ def test_engine_draft_stops_at_the_first_low_confidence_token():
     e3 = Eng([0.1] * 4)
     e3.supports_confidence = False
     assert EngineDraft(e3, max_gamma=4, min_confidence=0.5).propose(ctx, 4) == [101, 102, 103, 104]
+
+
+def test_quant_skip_list_matches_across_namespaces_and_cross_checks(tmp_path):
+    """``modules_to_not_convert`` names module paths, multimodal checkpoints store tensors under a wrapper prefix: both are brought into
+    one namespace; a list that matches nothing, an FP8 tensor on the list or a scaled non-FP8 tensor off it stop the load."""
+    import json as _json
+    from layerstorm_b200.models.checkpoint import QuantSkipList
+    sk = QuantSkipList(["model.layers.3.self_attn", "lm_head", "visual", "model.layers.5.mlp.gate"], "fp8")
+    assert sk.matches("model.language_model.layers.3.self_attn.kv_b_proj.weight")          # wrapper prefix + prefix entry
+    assert sk.matches("model.layers.3.self_attn.q_a_proj.weight_scale_inv")                # role suffix stripped
+    assert sk.matches("lm_head.weight") and sk.matches("model.visual.blocks.0.attn.qkv.weight")
+    assert sk.matches("model.layers.5.mlp.gate.weight") and not sk.matches("model.layers.5.mlp.gate_proj.weight")   # whole path components only
+    assert not sk.matches("model.layers.30.self_attn.o_proj.weight")
+    shapes = {"model.language_model.layers.3.self_attn.o_proj.weight": (8, 8), "model.language_model.layers.4.mlp.down_proj.weight": (8, 8),
+              "model.language_model.layers.4.mlp.down_proj.weight_scale_inv": (1, 1), "model.language_model.norm.weight": (8,)}
+    good = {"model.language_model.layers.3.self_attn.o_proj.weight": "BF16", "model.language_model.layers.4.mlp.down_proj.weight": "F8_E4M3",
+            "model.language_model.layers.4.mlp.down_proj.weight_scale_inv": "F32", "model.language_model.norm.weight": "BF16"}
+    assert sk.cross_check(good, shapes) == {"entries": 4, "matrices_kept": 1}
+    with pytest.raises(ValueError, match="FP8 although"):
+        sk.cross_check(dict(good, **{"model.language_model.layers.3.self_attn.o_proj.weight": "F8_E4M3"}), shapes)
+    with pytest.raises(ValueError, match="carries a quantisation scale"):
+        sk.cross_check(dict(good, **{"model.language_model.layers.4.mlp.down_proj.weight": "BF16"}), shapes)
+    with pytest.raises(ValueError, match="matches a tensor"):
+        QuantSkipList(["transformer.h.0"], "fp8").cross_check(good, shapes)
+    (tmp_path / "config.json").write_text(_json.dumps({"text_config": {"quantization_config": {"quant_method": "fp8", "modules_to_not_convert": ["lm_head"]}}}))
+    got = QuantSkipList.from_model_dir(str(tmp_path))
+    assert got is not None and got.entries == ["lm_head"] and got.quant_method == "fp8"
+    (tmp_path / "config.json").write_text("{}")
+    assert QuantSkipList.from_model_dir(str(tmp_path)) is None

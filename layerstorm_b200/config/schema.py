@@ -407,3 +407,54 @@ def json_schema(node: Any = None) -> dict:
     else:
         out["additionalProperties"] = False
     return out
+
+
+def markdown_reference() -> str:
+    """One table row per leaf: path, type, default, constraints, whether it can change on a running engine."""
+    rows = ["| field | type | default | constraints | live |", "|---|---|---|---|---|"]
+    for path, f in leaf_paths():
+        ts = f.type if isinstance(f.type, tuple) else (f.type,)
+        cons = []
+        if f.enum:
+            cons.append("one of " + ", ".join(repr(e) for e in f.enum))
+        if f.lo is not None:
+            cons.append(f">= {f.lo}")
+        if f.hi is not None:
+            cons.append(f"<= {f.hi}")
+        rows.append(f"| `{path}` | {' / '.join(t.__name__ for t in ts)}{' / null' if f.nullable else ''} | `{f.default!r}` | {'; '.join(cons)} | {'yes' if f.live else ''} |")
+    return "\n".join(rows)
+
+
+def main(argv=None) -> int:
+    """``python -m layerstorm_b200.config --emit json-schema|defaults|live-fields|markdown``: everything that is GENERATED from the
+    schema tree (the reference generates its parser, defaults and live-field list from ``config/schema.json`` with tools/gen_config.mjs;
+    here the tree is interpreted at run time and these are its exports for editors, external validators and documentation).
+    ``--check FILE`` validates a configuration document against the tree and exits 1 with the problems listed."""
+    import argparse
+    import json
+    import sys
+    ap = argparse.ArgumentParser(description="exports of the configuration schema")
+    ap.add_argument("--emit", choices=["json-schema", "defaults", "live-fields", "markdown"], default=None)
+    ap.add_argument("--check", default=None, metavar="FILE")
+    a = ap.parse_args(argv)
+    if a.check:
+        from .loader import load_config
+        try:
+            load_config(a.check)
+        except Exception as e:                       # the loader reports every problem of the document in its message
+            print(f"{a.check}: {e}", file=sys.stderr)
+            return 1
+        print(f"{a.check}: ok")
+        return 0
+    if a.emit == "json-schema":
+        print(json.dumps(json_schema(), indent=1))
+    elif a.emit == "defaults":
+        print(json.dumps(defaults(), indent=1))
+    elif a.emit == "live-fields":
+        print("\n".join(live_changeable_fields()))
+    elif a.emit == "markdown":
+        print(markdown_reference())
+    else:
+        ap.print_help()
+    return 0
+

@@ -303,3 +303,25 @@ def test_benchmark_mode_on_the_null_engine(tmp_path, capsys):
     assert compare.compare(rep, rep)["pass"]
     # too long for the configured sequence length: refused before anything is built
     assert benchmark.main(["--prompt-len", "100000000", "--", "--model", "tiny-mla-moe", "--test-engine"]) == 2
+
+
+def test_schema_exports_and_check_cli(tmp_path, capsys):
+    """Everything generated from the schema tree: JSON-Schema, defaults, live-changeable fields, the markdown field reference, and the
+    document check used from the command line."""
+    import json
+    from layerstorm_b200.config import schema
+    assert schema.main(["--emit", "json-schema"]) == 0
+    js = json.loads(capsys.readouterr().out)
+    assert js["type"] == "object" and "serving" in js["properties"] and js["$schema"].startswith("https://json-schema.org")
+    assert schema.main(["--emit", "live-fields"]) == 0
+    live = capsys.readouterr().out.split()
+    assert live == schema.live_changeable_fields() and "memory.expert_cache.eviction_policy" in live
+    assert schema.main(["--emit", "markdown"]) == 0
+    md = capsys.readouterr().out
+    assert md.count("\n") >= len(list(schema.leaf_paths())) and "| `preset` | str |" in md
+    good = tmp_path / "good.json"
+    good.write_text(json.dumps({"preset": "min_latency"}))
+    assert schema.main(["--check", str(good)]) == 0
+    bad = tmp_path / "bad.json"
+    bad.write_text(json.dumps({"serving": {"port": "x"}}))
+    assert schema.main(["--check", str(bad)]) == 1

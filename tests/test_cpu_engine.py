@@ -125,3 +125,14 @@ def test_mtp_blocks_and_lossless_mtp_speculation():
     import pytest
     with pytest.raises(ValueError):
         MtpDraft(CpuEngine(base, w0, native_experts=False), {})
+
+
+def test_cpu_expert_bench_runs_every_slot_format(capsys):
+    """The stand-alone CPU expert benchmark: every device slot format decodes to finite outputs and reports a rate."""
+    import json
+    from layerstorm_b200.utils import cpu_expert_bench
+    assert cpu_expert_bench.main(["--hidden", "256", "--inter", "256", "--tokens", "1,4", "--reps", "2", "--threads", "2"]) == 0
+    rep = json.loads(capsys.readouterr().out)
+    assert rep["threads"] == 2 and len(rep["rows"]) == 8
+    assert {r["format"] for r in rep["rows"]} == {"bf16", "fp8_e4m3", "nvfp4", "gguf_q4_k"}
+    assert all(r["finite"] and r["ms"] > 0 and r["gflop_s"] > 0 for r in rep["rows"])

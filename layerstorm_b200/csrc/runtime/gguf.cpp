@@ -25,7 +25,7 @@
 
 namespace lsb {
 
-enum GgmlType { T_F32 = 0, T_F16 = 1, T_Q8_0 = 8, T_Q2_K = 10, T_Q3_K = 11, T_Q4_K = 12, T_Q5_K = 13, T_Q6_K = 14, T_BF16 = 30, T_MXFP4 = 39 };
+enum GgmlType { T_F32 = 0, T_F16 = 1, T_Q8_0 = 8, T_Q2_K = 10, T_Q3_K = 11, T_Q4_K = 12, T_Q5_K = 13, T_Q6_K = 14, T_I32 = 26, T_BF16 = 30, T_MXFP4 = 39 };
 
 static inline float h2f(uint16_t h) {
     const uint32_t s = (h & 0x8000u) << 16, e = (h >> 10) & 0x1f, m = h & 0x3ff;
@@ -69,7 +69,7 @@ static inline uint16_t f2h(float f) {
 
 int type_block_elems(int t) {
     switch (t) {
-        case T_F32: case T_F16: case T_BF16: return 1;
+        case T_F32: case T_F16: case T_BF16: case T_I32: return 1;
         case T_Q8_0: case T_MXFP4: return 32;
         case T_Q2_K: case T_Q3_K: case T_Q4_K: case T_Q5_K: case T_Q6_K: return 256;
         default: return 0;
@@ -77,7 +77,7 @@ int type_block_elems(int t) {
 }
 int type_block_bytes(int t) {
     switch (t) {
-        case T_F32: return 4;
+        case T_F32: case T_I32: return 4;
         case T_F16: case T_BF16: return 2;
         case T_Q8_0: return 34;
         case T_MXFP4: return 17;
@@ -103,6 +103,7 @@ int dequantize(int type, const uint8_t* src, float* y, int64_t n) {
     const int64_t nb = n / be;
     switch (type) {
         case T_F32: std::memcpy(y, src, n * 4); return 0;
+        case T_I32: for (int64_t i = 0; i < n; ++i) { int32_t v; std::memcpy(&v, src + 4 * i, 4); y[i] = (float)v; } return 0;   // integer tables (exact below 2^24)
         case T_F16: for (int64_t i = 0; i < n; ++i) { uint16_t h; std::memcpy(&h, src + 2 * i, 2); y[i] = h2f(h); } return 0;
         case T_BF16: for (int64_t i = 0; i < n; ++i) { uint16_t h; std::memcpy(&h, src + 2 * i, 2); uint32_t u = (uint32_t)h << 16; std::memcpy(&y[i], &u, 4); } return 0;
         case T_Q8_0:

@@ -13,7 +13,7 @@ import numpy as np
 
 from ..runtime import native as nt
 
-GGML_TYPES = {"F32": 0, "F16": 1, "Q8_0": 8, "Q2_K": 10, "Q3_K": 11, "Q4_K": 12, "Q5_K": 13, "Q6_K": 14, "BF16": 30, "MXFP4": 39}
+GGML_TYPES = {"F32": 0, "F16": 1, "Q8_0": 8, "Q2_K": 10, "Q3_K": 11, "Q4_K": 12, "Q5_K": 13, "Q6_K": 14, "I32": 26, "BF16": 30, "MXFP4": 39}
 GGML_NAMES = {v: k for k, v in GGML_TYPES.items()}
 
 
@@ -42,6 +42,8 @@ def dequantize(t: int, raw: np.ndarray, n_elements: int) -> np.ndarray:
 
 
 def quantize(t: int, x: np.ndarray) -> np.ndarray:
+    if t == GGML_TYPES["I32"]:
+        return np.ascontiguousarray(np.asarray(x).astype(np.int32).reshape(-1)).view(np.uint8)
     x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1)
     out = np.empty(nbytes_for(t, x.size), dtype=np.uint8)
     rc = nt.load().lsb_ggml_quantize(t, x.ctypes.data, out.ctypes.data, x.size)
@@ -172,6 +174,8 @@ class GgufReader:
         """Dequantised fp32 tensor in NumPy (row-major) shape."""
         t = self.tensors[name]
         n = int(np.prod(t["shape"])) if t["shape"] else 1
+        if t["type"] == GGML_TYPES["I32"]:                     # integer tables (hash-layer token -> expert ids) pass through
+            return self.raw(name).view(np.int32).reshape(t["shape"]).copy()
         return dequantize(t["type"], self.raw(name), n).reshape(t["shape"])
 
 

@@ -41,7 +41,7 @@ _HF_LAYER = {
     "hc_attn.fn": "hc_attn_fn", "hc_attn.scale": "hc_attn_scale", "hc_attn.base": "hc_attn_base",
     "hc_ffn.fn": "hc_ffn_fn", "hc_ffn.scale": "hc_ffn_scale", "hc_ffn.base": "hc_ffn_base",
     "mlp.gate": "mlp.gate_proj", "mlp.up": "mlp.up_proj", "mlp.down": "mlp.down_proj",
-    "moe.router": "mlp.gate.weight", "moe.router_bias": "mlp.gate.e_score_correction_bias",
+    "moe.router": "mlp.gate.weight", "moe.router_bias": "mlp.gate.e_score_correction_bias", "moe.tid2eid": "mlp.gate.tid2eid",
     # multi-token-prediction blocks (layer ids >= num_hidden_layers)
     "mtp.enorm": "enorm.weight", "mtp.hnorm": "hnorm.weight", "mtp.eh_proj": "eh_proj", "mtp.final_norm": "shared_head.norm.weight",
 }
@@ -59,7 +59,7 @@ _GGUF_LAYER = {
     "hc_attn.fn": "hc_attn_fn.weight", "hc_attn.scale": "hc_attn_scale.weight", "hc_attn.base": "hc_attn_base.weight",
     "hc_ffn.fn": "hc_ffn_fn.weight", "hc_ffn.scale": "hc_ffn_scale.weight", "hc_ffn.base": "hc_ffn_base.weight",
     "mlp.gate": "ffn_gate.weight", "mlp.up": "ffn_up.weight", "mlp.down": "ffn_down.weight",
-    "moe.router": "ffn_gate_inp.weight", "moe.router_bias": "exp_probs_b.bias",
+    "moe.router": "ffn_gate_inp.weight", "moe.router_bias": "exp_probs_b.bias", "moe.tid2eid": "ffn_gate_tid2eid.weight",
     "mtp.enorm": "nextn.enorm.weight", "mtp.hnorm": "nextn.hnorm.weight", "mtp.eh_proj": "nextn.eh_proj.weight",
     "mtp.final_norm": "nextn.shared_head_norm.weight",
 }
@@ -509,7 +509,7 @@ def export_hf(cfg: ModelConfig, w: Dict[str, torch.Tensor], directory: str, dtyp
             continue
         hp = _HF_LAYER[rest]
         full = L + hp
-        is_tensor_name = hp.endswith((".weight", ".bias")) or hp.split(".")[-1] in ("A_log", "dt_bias") or hp.startswith("hc_")
+        is_tensor_name = hp.endswith((".weight", ".bias")) or hp.split(".")[-1] in ("A_log", "dt_bias", "tid2eid") or hp.startswith("hc_")
         out[full if is_tensor_name else full + ".weight"] = v
     for i, d in kvb.items():
         kb = d["attn.k_b"].transpose(1, 2)                  # [H, dn, dl]
@@ -519,7 +519,10 @@ def export_hf(cfg: ModelConfig, w: Dict[str, torch.Tensor], directory: str, dtyp
     size = 0
     for k in sorted(out):
         t = out[k].contiguous()
-        t = t.float() if any(s in k for s in keep32) else t.to(dtype)
+        if k.endswith("tid2eid"):
+            t = t.to(torch.int32)                            # integer table: stays integer in the file
+        else:
+            t = t.float() if any(s in k for s in keep32) else t.to(dtype)
         if size + t.numel() * t.element_size() > shard_bytes and shards[-1]:
             shards.append({})
             size = 0
@@ -553,6 +556,8 @@ def hf_config_dict(c: ModelConfig) -> dict:
         d["layer_types"] = ["linear_attention" if t == "kda" else "deepseek_sparse_attention" for t in c.layer_types]
         d["linear_attn_config"] = {"num_heads": c.kda_heads, "head_dim": c.kda_head_dim, "short_conv_kernel_size": c.kda_conv,
                                    "gate_low_rank": c.kda_rank, "gate_lower_bound": c.kda_lower_bound}
+    if c.num_hash_layers:
+        d["num_hash_layers"] = c.num_hash_layers
     if c.mhc:
         d.update({"mhc": True, "hc_mult": c.hc_mult, "hc_eps": c.hc_eps, "hc_sinkhorn_iters": c.hc_sinkhorn_iters})
     return d

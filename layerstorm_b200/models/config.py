@@ -48,6 +48,7 @@ class ModelConfig:
     top_k: int = 4
     n_mtp: int = 0                      # multi-token-prediction blocks after the main stack (layer ids n_layers .. n_layers + n_mtp - 1)
     n_shared: int = 1
+    num_hash_layers: int = 0            # MoE layers with index < this route by a token-id table (`moe.tid2eid`, DeepSeek-V4 hash layers) instead of top-k
     moe_inter: int = 128
     scoring: str = "softmax"          # sigmoid | softmax | sqrtsoftplus
     n_group: int = 1
@@ -102,6 +103,10 @@ class ModelConfig:
 
     def is_moe_layer(self, i: int) -> bool:
         return i >= self.first_k_dense and self.n_routed > 0
+
+    def is_hash_layer(self, i: int) -> bool:
+        """The layer's experts come from the token id (table row), not from a top-k over the router scores."""
+        return self.is_moe_layer(i) and i < self.num_hash_layers
 
     def is_kda_layer(self, i: int) -> bool:
         return i < len(self.layer_types) and self.layer_types[i] == "kda"       # multi-token-prediction blocks (i >= n_layers) are MLA layers
@@ -262,7 +267,7 @@ def from_hf_config(path_or_dict) -> ModelConfig:
         rope_yarn_mscale_all_dim=float(rs.get("mscale_all_dim", 0.0)), max_position=c.get("max_position_embeddings", 8192),
         dense_inter=c["intermediate_size"], first_k_dense=c.get("first_k_dense_replace", 0),
         n_routed=c.get("n_routed_experts", 0), top_k=c.get("num_experts_per_tok", 0), n_shared=c.get("n_shared_experts", 0),
-        n_mtp=int(c.get("num_nextn_predict_layers", 0) or 0),
+        n_mtp=int(c.get("num_nextn_predict_layers", 0) or 0), num_hash_layers=int(c.get("num_hash_layers", 0) or 0),
         moe_inter=c.get("moe_intermediate_size", 0), scoring=c.get("scoring_func", "softmax"), n_group=c.get("n_group", 1),
         topk_group=c.get("topk_group", 1), routed_scale=c.get("routed_scaling_factor", 1.0),
         norm_topk_prob=c.get("norm_topk_prob", True), router_bias=c.get("topk_method") == "noaux_tc",

@@ -782,6 +782,8 @@ class DeviceModel:
                 mo = p + "moe."
                 L["router"] = QLinear.from_float(w[mo + "router"], "f32", dev)
                 L["router_bias"] = f32(w[mo + "router_bias"]) if (mo + "router_bias") in w else None
+                if cfg.is_hash_layer(i):
+                    L["tid2eid"] = w[mo + "tid2eid"].to(dev).to(torch.int32).contiguous()     # [vocab, top_k]
                 E_total = cfg.n_routed + cfg.n_shared
                 mine = [e for e in range(E_total) if m.owns_expert(i, e)]
                 eq_l, eq_dn = eq, eq
@@ -893,6 +895,9 @@ class DeviceModel:
             if cfg.is_moe_layer(i):
                 L["router"] = QLinear.random(cfg.n_routed, H, "f32", dev, std=0.1, gen=gen)
                 L["router_bias"] = rnd(cfg.n_routed, std=0.05) if cfg.router_bias else None
+                if cfg.is_hash_layer(i):
+                    # top_k distinct experts per token id: the first top_k columns of a row-wise random ranking
+                    L["tid2eid"] = torch.rand(cfg.vocab, cfg.n_routed, device=dev, generator=gen).argsort(dim=1)[:, :cfg.top_k].to(torch.int32).contiguous()
                 L["arena"] = None      # allocated below, once the non-expert footprint is known
             else:
                 L["mlp_gu"] = QLinear.random(2 * m.Fd, H, dq, dev, gen=gloc)
@@ -1046,6 +1051,11 @@ class DeviceModel:
         sc = {"sigmoid": 0, "softmax": 1, "sqrtsoftplus": 2}[cfg.scoring]
         if routed:
             pass        # the hyper-connection kernel in front of this layer already projected and selected (ws.ids / ws.wts)
+        elif "tid2eid" in L:
+            # hash layer: the experts are the table row of the row's token id, the weights their (unbiased) scores
+            L["router"](ws.logits_r, ws.x, R)
+            nat.call("lsb_router_hash", ws.logits_r, L["tid2eid"], ws.tok, ws.ids, ws.wts, R, cfg.n_routed, cfg.top_k, cfg.vocab,
+                     sc, int(cfg.norm_topk_prob), cfg.routed_scale, cfg.n_shared, cfg.n_routed)
         elif ROUTER_FUSED and R <= 8 and cfg.hidden % 16 == 0 and R * (2 * cfg.n_routed + 128) * 4 <= 48 * 1024:
             # decode-sized steps: projection and top-k in one launch (the last block selects)
             nat.call("lsb_router_fused", L["router"].w, ws.x, ws.logits_r, L["router_bias"], ws.ids, ws.wts, ws.router_done, R, cfg.hidden,
@@ -1296,7 +1306,7 @@ class DeviceModel:
                     self._kda(i, L, ws, R, nseq)
                 else:
                     self._mla(i, L, ws, R)
-                route = L if (clus and "arena" in L and self._router_foldable(ws)) else None
+                route = L if (clus and "arena" in L and "tid2eid" not in L and self._router_foldable(ws)) else None
                 self._hc_pass(L["hc_ffn"], L["ffn_norm"], ws, R, 1, clus, None, route)
                 last = i + 1 == len(self.layers)
                 if self._ffn(i, L, ws, R, routed=route is not None, defer_combine=MHC_FOLD_COMBINE and clus and not last and self.drift is None):
@@ -1393,6 +1403,8 @@ class DeviceModel:
                 out[mo + "router"] = cpu(L["router"].w)
                 if L["router_bias"] is not None:
                     out[mo + "router_bias"] = cpu(L["router_bias"])
+                if "tid2eid" in L:
+                    out[mo + "tid2eid"] = L["tid2eid"].cpu()
                 arena: ExpertArena = L["arena"]
                 fmt = {v: k for k, v in EXPERT_FMT.items()}[arena.ef.fmt]
                 so = arena.slot_of.cpu()

@@ -104,7 +104,9 @@ def route_hash(cfg: ModelConfig, logits, tid2eid, token_ids):
 class Oracle:
     def __init__(self, cfg: ModelConfig, weights: Dict[str, torch.Tensor]):
         self.cfg = cfg
-        self.w = {k: v.float() for k, v in weights.items()}
+        self.w = {k: v.float() for k, v in weights.items() if not k.endswith(".tid2eid")}
+        self.tables = {k: v.long() for k, v in weights.items() if k.endswith(".tid2eid")}       # integer tables stay integers
+        self._tok = None
         self.sel_log: Dict[int, List] = {}
 
     # ---------------- sublayers ----------------
@@ -115,12 +117,20 @@ class Oracle:
             return swiglu(x @ w[p + "mlp.gate"].T, x @ w[p + "mlp.up"].T, cfg.swiglu_limit) @ w[p + "mlp.down"].T
         m = p + "moe."
         logits = x @ w[m + "router"].T
-        ids, wt = route(cfg, logits, w.get(m + "router_bias"))
+        if cfg.is_hash_layer(i) and (m + "tid2eid") in self.tables:
+            # hash layer: the experts are the table row of the token id, the weights their unbiased scores; -1 = dropped
+            if self._tok is None or self._tok.shape[0] != x.shape[0]:
+                raise RuntimeError("a hash layer needs the token ids of the rows (Oracle.forward sets them)")
+            ids, wt = route_hash(cfg, logits, self.tables[m + "tid2eid"], self._tok)
+        else:
+            ids, wt = route(cfg, logits, w.get(m + "router_bias"))
         self.last_route = (ids, wt)
         out = torch.zeros_like(x)
         for t in range(x.shape[0]):
             for k in range(cfg.top_k):
                 e = int(ids[t, k])
+                if e < 0:
+                    continue                                      # a dropped slot of a hash layer
                 h = swiglu(x[t] @ w[m + f"experts.{e}.gate"].T, x[t] @ w[m + f"experts.{e}.up"].T, cfg.swiglu_limit)
                 out[t] += wt[t, k] * (h @ w[m + f"experts.{e}.down"].T)
         for s in range(cfg.n_shared):
@@ -266,6 +276,7 @@ class Oracle:
         cfg, w = self.cfg, self.w
         ids = torch.as_tensor(ids, dtype=torch.long)
         T = ids.shape[0]
+        self._tok = ids                                           # hash layers route by token id
         pos = torch.arange(T) if pos is None else torch.as_tensor(pos)
         self.sel_log = {}
         h = w["embed.weight"][ids]

@@ -95,6 +95,9 @@ def init_weights(cfg: ModelConfig, seed: int = 0, std: float = 0.02) -> Dict[str
             w[m + "router"] = mat(cfg.n_routed, H, s=0.1)
             if cfg.router_bias:
                 w[m + "router_bias"] = mat(cfg.n_routed, s=0.05)
+            if cfg.is_hash_layer(i):
+                # token id -> its top_k experts (distinct per row), int32 [vocab, top_k]
+                w[m + "tid2eid"] = torch.stack([torch.randperm(cfg.n_routed, generator=g)[: cfg.top_k] for _ in range(cfg.vocab)]).int()
             for e in range(cfg.n_routed):
                 w[m + f"experts.{e}.gate"] = mat(cfg.moe_inter, H)
                 w[m + f"experts.{e}.up"] = mat(cfg.moe_inter, H)
@@ -129,6 +132,9 @@ def init_weights(cfg: ModelConfig, seed: int = 0, std: float = 0.02) -> Dict[str
             w[m + "router"] = mat(cfg.n_routed, H, s=0.1)
             if cfg.router_bias:
                 w[m + "router_bias"] = mat(cfg.n_routed, s=0.05)
+            if cfg.is_hash_layer(L):
+                # token id -> its top_k experts (distinct per row), int32 [vocab, top_k]
+                w[m + "tid2eid"] = torch.stack([torch.randperm(cfg.n_routed, generator=g)[: cfg.top_k] for _ in range(cfg.vocab)]).int()
             for e in range(cfg.n_routed):
                 w[m + f"experts.{e}.gate"] = mat(cfg.moe_inter, H)
                 w[m + f"experts.{e}.up"] = mat(cfg.moe_inter, H)
@@ -154,7 +160,7 @@ def round_weights_bf16(w: Dict[str, torch.Tensor], keep_fp32=("router", "hc_", "
     engine start from identical values."""
     out = {}
     for k, v in w.items():
-        if any(t in k for t in keep_fp32):
+        if any(t in k for t in keep_fp32) or not v.is_floating_point():
             out[k] = v.clone()
         else:
             out[k] = v.to(torch.bfloat16).to(torch.float32)

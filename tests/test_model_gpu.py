@@ -315,3 +315,37 @@ def test_row_granular_kv_tiering_is_bit_identical_and_frees_pages(kv):
     st = tier.stats
     assert st["demoted_pages"] >= 6 and st["cold_rows_fetched"] > 0 and st["bytes_h2d"] > 0, st
     assert free1 >= free0 + st["demoted_pages"] - 1                 # the demoted pages went back to the pool
+
+
+@pytest.mark.parametrize("name", ["tiny-mla-moe", "tiny-glm5-next"])
+def test_hash_layers_match_oracle_in_prefill_and_graph_decode(name):
+    """MoE layers below ``num_hash_layers`` take their experts from the token-id table (DeepSeek-V4 hash layers): the engine's
+    chunked prefill, eager decode and graph decode agree with the fp32 oracle, which routes the same rows through the same table."""
+    import dataclasses
+    cfg = dataclasses.replace(get_preset(name), num_hash_layers=3)
+    assert sum(cfg.is_hash_layer(i) for i in range(cfg.n_layers)) >= 2
+    w = init_weights(cfg, 0)
+    m = DeviceModel.from_state_dict(cfg, w, "cuda", kv_fmt="bf16", page=16, expert_quant="bf16", dense_quant="bf16")
+    assert any("tid2eid" in L for L in m.layers)
+    oracle = Oracle(cfg, m.effective_state_dict())
+    g = torch.Generator().manual_seed(9)
+    T = 28
+    ids = torch.randint(0, cfg.vocab, (T + 4,), generator=g)
+    ref = oracle.forward(ids)
+    for use_graph in (False, True):
+        eng = Engine(m, max_seqs=2, max_ctx=256, prefill_chunk=16, max_batch=2, use_graph=use_graph)
+        sid = eng.create_sequence()
+        nxt, lg = eng.prefill(sid, ids[:T].tolist(), want_logits=True)
+        assert rel_err(lg, ref[T - 1]) < 3e-2, rel_err(lg, ref[T - 1])
+        assert nxt == int(ref[T - 1].argmax())
+        for j in range(4):
+            out, lg = eng.decode([sid], [int(ids[T + j])], return_logits=True)
+            assert rel_err(lg[0], ref[T + j]) < 3e-2, (use_graph, j)
+            assert out[0] == int(ref[T + j].argmax())
+    # the table decides: another table gives other logits for the same tokens
+    hashed = next(L for L in m.layers if "tid2eid" in L)
+    hashed["tid2eid"].copy_(hashed["tid2eid"].roll(1, 0))
+    eng = Engine(m, max_seqs=1, max_ctx=256, prefill_chunk=16, max_batch=1, use_graph=False)
+    sid = eng.create_sequence()
+    _, lg2 = eng.prefill(sid, ids[:T].tolist(), want_logits=True)
+    assert rel_err(lg2, ref[T - 1]) > 1e-3

@@ -334,3 +334,50 @@ def test_quant_skip_list_matches_across_namespaces_and_cross_checks(tmp_path):
     assert got is not None and got.entries == ["lm_head"] and got.quant_method == "fp8"
     (tmp_path / "config.json").write_text("{}")
     assert QuantSkipList.from_model_dir(str(tmp_path)) is None
+
+
+def test_hash_layers_route_by_the_token_table_and_survive_both_checkpoint_formats(tmp_path):
+    """Hash layers (DeepSeek-V4): the experts of a row are its token id's table row, the weights their unbiased scores.
+    Reference: src/compute/kernels/moe/hash_gating.h:1-16; table tensor ffn_gate_tid2eid (I32)."""
+    import dataclasses
+    from layerstorm_b200.formats.gguf import GGML_TYPES, GgufReader, GgufWriter
+    from layerstorm_b200.models.reference import Oracle, route_hash
+    cfg = dataclasses.replace(tiny_mla_moe(), num_hash_layers=2)
+    hashed = [i for i in range(cfg.n_layers) if cfg.is_hash_layer(i)]
+    assert hashed and all(cfg.is_moe_layer(i) and i < 2 for i in hashed)
+    w = round_weights_bf16(init_weights(cfg))
+    tab = w[f"layers.{hashed[0]}.moe.tid2eid"]
+    assert tab.dtype == torch.int32 and tab.shape == (cfg.vocab, cfg.top_k)
+    assert all(len(set(r.tolist())) == cfg.top_k for r in tab[:64])                  # distinct experts per token
+    # routing: ids are the table rows in table order; out-of-range entries are dropped with weight 0
+    logits = torch.randn(3, cfg.n_routed)
+    t2 = tab.clone().long()
+    t2[5, 1] = cfg.n_routed + 3
+    ids, wt = route_hash(cfg, logits, t2, torch.tensor([5, 7, cfg.vocab + 1]))
+    assert ids[0].tolist() == [int(t2[5, 0]), -1] + t2[5, 2:].tolist() and wt[0, 1] == 0
+    assert ids[1].tolist() == t2[7].tolist() and ids[2].tolist() == [-1] * cfg.top_k and float(wt[2].abs().sum()) == 0
+    # the oracle's output depends on the token ids through the table: same hidden rows, other ids -> other experts
+    o = Oracle(cfg, w)
+    tok = torch.randint(0, cfg.vocab, (6,), generator=torch.Generator().manual_seed(1))
+    o.forward(tok)
+    sel = o.last_route[0]
+    last_hashed = max(hashed)
+    if last_hashed == cfg.n_layers - 1:
+        assert torch.equal(sel, w[f"layers.{last_hashed}.moe.tid2eid"].long()[tok])
+    # HuggingFace directory
+    export_hf(cfg, w, str(tmp_path / "hf"))
+    cfg2, ck = open_checkpoint(str(tmp_path / "hf"))
+    assert cfg2.num_hash_layers == 2
+    for i in hashed:
+        assert torch.equal(ck[f"layers.{i}.moe.tid2eid"].long(), w[f"layers.{i}.moe.tid2eid"].long())
+    assert f"layers.{cfg.n_layers - 1}.moe.tid2eid" not in ck or cfg.is_hash_layer(cfg.n_layers - 1)
+    # GGUF: an I32 tensor passes through as integers
+    gw = GgufWriter()
+    gw.meta("general.architecture", "deepseek4")
+    gw.add(f"blk.{hashed[0]}.ffn_gate_tid2eid.weight", tab.numpy(), ggml_type=GGML_TYPES["I32"])
+    gw.write(str(tmp_path / "t.gguf"))
+    r = GgufReader(str(tmp_path / "t.gguf"))
+    got = r.get(f"blk.{hashed[0]}.ffn_gate_tid2eid.weight")
+    assert got.dtype == np.int32 and np.array_equal(got, tab.numpy())
+    _, ck2 = open_checkpoint(str(tmp_path / "t.gguf"), cfg)
+    assert torch.equal(ck2[f"layers.{hashed[0]}.moe.tid2eid"].long(), tab.long())

@@ -354,6 +354,233 @@ __global__ void __launch_bounds__(1024) indexer_topk_kernel(const float* __restr
     pdl_launch_dependents();
 }
 
+
+// ---- the same selection spread over many blocks (few rows, long rows) ------------------------------------------------------
+// One block per row walks a 262k-entry row (a 1M-token context pooled by 4) in ~600 us: four passes over the row and 256
+// emit rounds of six block barriers each.  Here every block owns 2048 consecutive entries of a row and the row's blocks meet in
+// global memory: three histogram launches (11 + 11 + 10 key bits; the block that arrives last picks the bucket and leaves the
+// histogram and the ticket zeroed for the next launch), one counting launch (entries above / equal to the threshold per block;
+// the last block turns the counts into output offsets) and one emit launch.  Integer atomics only: the result does not depend on
+// the order in which blocks run, and it is the single-block kernel's result entry for entry (ascending, ties to the lower index).
+constexpr int kTkChunk = 2048;
+constexpr int kTkThreads = 256;
+constexpr int kTkBins = 2048;
+struct TopkSplitRow {
+    int hist[kTkBins];
+    uint32_t prefix;      // the key bits decided so far
+    int need;             // how many entries are still to be taken from the bucket of `prefix`
+    unsigned ticket;
+    int pad;
+};
+
+// Exclusive prefix sum over the block's 256 threads; `total` = the block's sum.  s_w: 8 ints of shared memory.
+__device__ __forceinline__ int block_excl_scan_256(int v, int* s_w, int& total) {
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    int x = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) { const int n = __shfl_up_sync(0xffffffffu, x, o); if (lane >= o) x += n; }
+    __syncthreads();                       // s_w may still be read from a previous scan
+    if (lane == 31) s_w[w] = x;
+    __syncthreads();
+    int base = 0, tot = 0;
+#pragma unroll
+    for (int j = 0; j < kTkThreads / 32; ++j) { const int sw = s_w[j]; if (j < w) base += sw; tot += sw; }
+    total = tot;
+    return base + x - v;
+}
+
+// true in exactly one block of the row: the one that took the last of `nb` tickets (all its threads return the same value)
+__device__ __forceinline__ bool last_block_of_row(unsigned* ticket, int nb, int* s_flag) {
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) *s_flag = (atomicAdd(ticket, 1u) == (unsigned)(nb - 1)) ? 1 : 0;
+    __syncthreads();
+    const bool last = *s_flag != 0;
+    if (last) __threadfence();
+    return last;
+}
+
+template <int LEVEL>
+__global__ void __launch_bounds__(kTkThreads) indexer_topk_hist_kernel(const float* __restrict__ scores, int ld_scores,
+                                                                       const int* __restrict__ n_entries, const int* __restrict__ row_seq,
+                                                                       int budget, TopkSplitRow* __restrict__ st_all) {
+    constexpr int shift = LEVEL == 0 ? 21 : (LEVEL == 1 ? 10 : 0);
+    constexpr int nbins = LEVEL == 2 ? 1024 : 2048;
+    __shared__ int hist[kTkBins];
+    __shared__ int s_w[kTkThreads / 32];
+    __shared__ int s_flag;
+    const int r = blockIdx.y, b = blockIdx.x, t = threadIdx.x;
+    pdl_wait();
+    pdl_launch_dependents();
+    const int ne = row_seq[r] < 0 ? 0 : n_entries[r];
+    if (ne <= budget || b * kTkChunk >= ne) return;            // short rows are taken whole by the emit kernel
+    TopkSplitRow& st = st_all[r];
+    const int nb = (ne + kTkChunk - 1) / kTkChunk;
+    for (int i = t; i < nbins; i += kTkThreads) hist[i] = 0;
+    __syncthreads();
+    const uint32_t prefix = LEVEL == 0 ? 0u : st.prefix;
+    const int need_in = LEVEL == 0 ? budget : st.need;
+    const float* sc = scores + (size_t)r * ld_scores;
+#pragma unroll
+    for (int u = 0; u < kTkChunk / kTkThreads; ++u) {
+        const int i = b * kTkChunk + u * kTkThreads + t;
+        if (i < ne) {
+            const uint32_t k = sortable(sc[i]);
+            if (LEVEL == 0 || (k >> (shift + (LEVEL == 1 ? 11 : 10))) == (prefix >> (shift + (LEVEL == 1 ? 11 : 10))))
+                atomicAdd(&hist[(k >> shift) & (nbins - 1)], 1);
+        }
+    }
+    __syncthreads();
+    for (int i = t; i < nbins; i += kTkThreads) { const int h = hist[i]; if (h) atomicAdd(&st.hist[i], h); }
+    if (!last_block_of_row(&st.ticket, nb, &s_flag)) return;
+    // the row's histogram is complete: find the bucket that holds the need_in-th largest key, walking from the top
+    int part = 0, mine[8];
+    constexpr int per = nbins / kTkThreads;                     // 8 or 4 buckets per thread, thread 0 owns the top ones
+#pragma unroll
+    for (int j = 0; j < per; ++j) {
+        const int bin = nbins - 1 - (t * per + j);
+        mine[j] = __ldcg(&st.hist[bin]);
+        st.hist[bin] = 0;                                       // left zeroed for the next launch
+        part += mine[j];
+    }
+    int total;
+    const int before = block_excl_scan_256(part, s_w, total);
+    if (before < need_in && before + part >= need_in) {
+        int need = need_in - before, bin = nbins - 1 - t * per;
+#pragma unroll
+        for (int j = 0; j < per; ++j, --bin) {
+            if (mine[j] >= need || j == per - 1) break;
+            need -= mine[j];
+        }
+        st.prefix = prefix | ((uint32_t)bin << shift);
+        st.need = need;
+    }
+    if (t == 0) st.ticket = 0;
+}
+
+// Per block: how many of its entries lie above / on the threshold; the last block turns the counts into the blocks' first output
+// position (blk[2 * nblk + b]) and the number of threshold-equal entries in front of the block (blk[3 * nblk + b]).
+__global__ void __launch_bounds__(kTkThreads) indexer_topk_count_kernel(const float* __restrict__ scores, int ld_scores,
+                                                                        const int* __restrict__ n_entries, const int* __restrict__ row_seq,
+                                                                        int budget, TopkSplitRow* __restrict__ st_all, int* __restrict__ blk_all,
+                                                                        int nblk) {
+    __shared__ int s_w[kTkThreads / 32];
+    __shared__ int s_flag;
+    const int r = blockIdx.y, b = blockIdx.x, t = threadIdx.x;
+    pdl_wait();
+    pdl_launch_dependents();
+    const int ne = row_seq[r] < 0 ? 0 : n_entries[r];
+    if (ne <= budget || b * kTkChunk >= ne) return;
+    TopkSplitRow& st = st_all[r];
+    int* blk = blk_all + (size_t)r * 4 * nblk;
+    const int nb = (ne + kTkChunk - 1) / kTkChunk;
+    const uint32_t T = st.prefix;
+    const int quota = st.need;
+    const float* sc = scores + (size_t)r * ld_scores;
+    int gt = 0, eq = 0;
+#pragma unroll
+    for (int u = 0; u < kTkChunk / kTkThreads; ++u) {
+        const int i = b * kTkChunk + u * kTkThreads + t;
+        if (i < ne) { const uint32_t k = sortable(sc[i]); gt += k > T; eq += k == T; }
+    }
+    int tot_gt, tot_eq;
+    block_excl_scan_256(gt, s_w, tot_gt);
+    block_excl_scan_256(eq, s_w, tot_eq);
+    if (t == 0) { blk[b] = tot_gt; blk[nblk + b] = tot_eq; }
+    if (!last_block_of_row(&st.ticket, nb, &s_flag)) return;
+    // thread t owns blocks [t * per, (t + 1) * per): equal entries in front first, then the taken entries in front
+    const int per = (nb + kTkThreads - 1) / kTkThreads;
+    int sum_eq = 0;
+    for (int j = 0; j < per; ++j) { const int bb = t * per + j; if (bb < nb) sum_eq += __ldcg(&blk[nblk + bb]); }
+    int dummy;
+    int eq_before = block_excl_scan_256(sum_eq, s_w, dummy);
+    int sum_take = 0;
+    for (int j = 0; j < per; ++j) {
+        const int bb = t * per + j;
+        if (bb < nb) {
+            const int e = __ldcg(&blk[nblk + bb]);
+            blk[3 * nblk + bb] = eq_before;
+            sum_take += __ldcg(&blk[bb]) + min(e, max(0, quota - eq_before));
+            eq_before += e;
+        }
+    }
+    int pos = block_excl_scan_256(sum_take, s_w, dummy);
+    for (int j = 0; j < per; ++j) {
+        const int bb = t * per + j;
+        if (bb < nb) {
+            blk[2 * nblk + bb] = pos;
+            pos += __ldcg(&blk[bb]) + min(__ldcg(&blk[nblk + bb]), max(0, quota - blk[3 * nblk + bb]));
+        }
+    }
+    if (t == 0) st.ticket = 0;
+}
+
+__global__ void __launch_bounds__(kTkThreads) indexer_topk_emit_kernel(const float* __restrict__ scores, int ld_scores,
+                                                                       const int* __restrict__ n_entries, const int* __restrict__ row_len,
+                                                                       const int* __restrict__ row_seq, int budget, int P,
+                                                                       const TopkSplitRow* __restrict__ st_all, const int* __restrict__ blk_all, int nblk,
+                                                                       int* __restrict__ sel_idx, int* __restrict__ sel_cnt, int sel_ld) {
+    constexpr int per = kTkChunk / kTkThreads;                  // 8 consecutive entries per thread: output order = index order
+    __shared__ uint32_t s_key[kTkChunk + kTkThreads];           // padded: thread t reads words t * 9 ..
+    __shared__ int s_w[kTkThreads / 32];
+    const int r = blockIdx.y, b = blockIdx.x, t = threadIdx.x;
+    pdl_wait();
+    pdl_launch_dependents();
+    const int len = row_seq[r] < 0 ? 0 : row_len[r];
+    const int ne = row_seq[r] < 0 ? 0 : n_entries[r];
+    int* out = sel_idx + (size_t)r * sel_ld;
+    const int nsel_entries = ne <= budget ? ne : budget;
+    if (b == 0) {                                               // the always-selected tail and the count
+        const int tail0 = ne * P;
+        for (int i = tail0 + t; i < len; i += kTkThreads) out[nsel_entries * P + (i - tail0)] = i;
+        if (t == 0) sel_cnt[r] = nsel_entries * P + max(0, len - tail0);
+    }
+    if (b * kTkChunk >= ne) return;
+    if (ne <= budget) {
+        const int hi = min(ne, (b + 1) * kTkChunk) * P;
+        for (int i = b * kTkChunk * P + t; i < hi; i += kTkThreads) out[i] = i;
+        return;
+    }
+    const TopkSplitRow& st = st_all[r];
+    const int* blk = blk_all + (size_t)r * 4 * nblk;
+    const uint32_t T = st.prefix;
+    const int quota = st.need;
+    const float* sc = scores + (size_t)r * ld_scores;
+#pragma unroll
+    for (int u = 0; u < per; ++u) {
+        const int j = u * kTkThreads + t, i = b * kTkChunk + j;
+        s_key[j + j / per] = i < ne ? sortable(sc[i]) : 0u;      // entry j of the block sits at word j + j / 8
+    }
+    __syncthreads();
+    uint32_t key[per];
+    int n_eq = 0;
+#pragma unroll
+    for (int u = 0; u < per; ++u) {
+        key[u] = s_key[t * (per + 1) + u];
+        n_eq += (b * kTkChunk + t * per + u < ne) && key[u] == T;
+    }
+    int dummy;
+    int eq_rank = blk[3 * nblk + b] + block_excl_scan_256(n_eq, s_w, dummy);
+    unsigned take = 0;
+#pragma unroll
+    for (int u = 0; u < per; ++u) {
+        const bool in = b * kTkChunk + t * per + u < ne;
+        if (in && key[u] > T) take |= 1u << u;
+        else if (in && key[u] == T) { if (eq_rank < quota) take |= 1u << u; ++eq_rank; }
+    }
+    int pos = blk[2 * nblk + b] + block_excl_scan_256(__popc(take), s_w, dummy);
+#pragma unroll
+    for (int u = 0; u < per; ++u) {
+        if ((take >> u) & 1u) {
+            if (pos < budget) {
+                const int i = b * kTkChunk + t * per + u;
+                for (int j = 0; j < P; ++j) out[pos * P + j] = i * P + j;
+            }
+            ++pos;
+        }
+    }
+}
+
 }  // namespace lsb
 using namespace lsb;
 
@@ -401,6 +628,33 @@ LSB_API int lsb_indexer_topk(const void* scores, int ld_scores, const void* n_en
                              void* stream) {
     launch_pdl((indexer_topk_kernel), rows, 1024, 0, (cudaStream_t)stream, (const float*)scores, ld_scores, (const int*)n_entries, (const int*)row_len,
                                                                (const int*)row_seq, budget, P, (int*)sel_idx, (int*)sel_cnt, sel_ld);
+    LSB_CHECK_LAUNCH();
+}
+
+// Bytes of zero-initialised scratch the split selection needs for `rows` rows of up to `max_entries` entries.
+LSB_API int lsb_indexer_topk_split_scratch(int rows, int max_entries) {
+    const long long nblk = (max_entries + kTkChunk - 1) / kTkChunk;
+    const long long n = (long long)rows * (long long)sizeof(TopkSplitRow) + (long long)rows * 4 * nblk * 4;
+    return n > 0x7fffffffLL ? -1 : (int)n;
+}
+
+// The selection of lsb_indexer_topk with every row spread over ceil(max_entries / 2048) blocks (five launches); meant for steps of
+// few rows over long rows.  scratch: lsb_indexer_topk_split_scratch bytes, zeroed once (every launch leaves it zeroed where needed).
+LSB_API int lsb_indexer_topk_split(const void* scores, int ld_scores, const void* n_entries, const void* row_len, const void* row_seq,
+                                   int budget, int P, void* sel_idx, void* sel_cnt, int sel_ld, int rows, int max_entries, void* scratch,
+                                   void* stream) {
+    if (rows <= 0 || max_entries <= 0) return 0;
+    const int nblk = (max_entries + kTkChunk - 1) / kTkChunk;
+    TopkSplitRow* st = (TopkSplitRow*)scratch;
+    int* blk = (int*)((char*)scratch + (size_t)rows * sizeof(TopkSplitRow));
+    const dim3 grid(nblk, rows);
+    cudaStream_t s = (cudaStream_t)stream;
+    launch_pdl((indexer_topk_hist_kernel<0>), grid, kTkThreads, 0, s, (const float*)scores, ld_scores, (const int*)n_entries, (const int*)row_seq, budget, st);
+    launch_pdl((indexer_topk_hist_kernel<1>), grid, kTkThreads, 0, s, (const float*)scores, ld_scores, (const int*)n_entries, (const int*)row_seq, budget, st);
+    launch_pdl((indexer_topk_hist_kernel<2>), grid, kTkThreads, 0, s, (const float*)scores, ld_scores, (const int*)n_entries, (const int*)row_seq, budget, st);
+    launch_pdl((indexer_topk_count_kernel), grid, kTkThreads, 0, s, (const float*)scores, ld_scores, (const int*)n_entries, (const int*)row_seq, budget, st, blk, nblk);
+    launch_pdl((indexer_topk_emit_kernel), grid, kTkThreads, 0, s, (const float*)scores, ld_scores, (const int*)n_entries, (const int*)row_len,
+               (const int*)row_seq, budget, P, (const TopkSplitRow*)st, (const int*)blk, nblk, (int*)sel_idx, (int*)sel_cnt, sel_ld);
     LSB_CHECK_LAUNCH();
 }
 

@@ -116,6 +116,11 @@ KDA_CHUNKED = os.environ.get("LSB_KDA_CHUNKED", "1") not in ("", "0")
 # one per row) and run the block-scaled tensor-core kernel (4-bit x 4-bit) instead of expanding the weights to fp16
 # LSB_INDEXER_TC=0: score prefill chunks with the CUDA-core indexer kernel instead of the tcgen05 one
 INDEXER_TC = os.environ.get("LSB_INDEXER_TC", "1") not in ("", "0")
+# steps of few rows over long index rows (more than TOPK_SPLIT_MIN_ENTRIES entries of capacity): the top-k of a row is spread
+# over many blocks (five small launches) instead of one block per row
+TOPK_SPLIT = os.environ.get("LSB_TOPK_SPLIT", "1") not in ("", "0")
+TOPK_SPLIT_MIN_ENTRIES = 16384
+TOPK_SPLIT_MAX_ROWS = 64
 MOE_BLOCK_SCALED = os.environ.get("LSB_MOE_BLOCK_SCALED", "0") not in ("", "0")
 # LSB_MHC_CLUSTER=0: decode-sized hyper-connection passes fall back to the two-launch path (partials + last-block finalize, contraction)
 MHC_CLUSTER = os.environ.get("LSB_MHC_CLUSTER", "1") not in ("", "0")
@@ -506,6 +511,10 @@ class Workspace:
             self.sel_idx = z(R, self.sel_ld, dtype=i32)
             self.sel_cnt = z(R, dtype=i32)
             self.q_idx = z(R, cfg.index_n_heads, cfg.index_head_dim, dtype=b16)
+            self.topk_scratch = None
+            if TOPK_SPLIT and R <= TOPK_SPLIT_MAX_ROWS and self.max_entries > TOPK_SPLIT_MIN_ENTRIES:
+                nbytes = int(nat.call("lsb_indexer_topk_split_scratch", R, self.max_entries))
+                self.topk_scratch = z((nbytes + 3) // 4, dtype=i32)         # zeroed once; every launch leaves it zeroed
             # tensor-core scoring of single-sequence chunks: the sequence's index keys as a dense bf16 operand + their scales
             self.idx_tc = (INDEXER_TC and R >= 64 and cfg.index_head_dim == 128 and 256 % cfg.index_n_heads == 0)
             if self.idx_tc:
@@ -1193,8 +1202,12 @@ class DeviceModel:
                 else:
                     nat.call("lsb_indexer_score", ws.q_idx, ws.idx_w, cfg.index_n_heads, self.idx_cache[i], self.idx_block_table,
                              self.max_pages, self.page // P, ws.row_seq, ws.n_entries, ws.scores, ws.max_entries, R, ws.max_entries)
-                nat.call("lsb_indexer_topk", ws.scores, ws.max_entries, ws.n_entries, ws.row_len, ws.row_seq,
-                         cfg.index_topk // P, P, ws.sel_idx, ws.sel_cnt, ws.sel_ld, R)
+                if ws.topk_scratch is not None:
+                    nat.call("lsb_indexer_topk_split", ws.scores, ws.max_entries, ws.n_entries, ws.row_len, ws.row_seq,
+                             cfg.index_topk // P, P, ws.sel_idx, ws.sel_cnt, ws.sel_ld, R, ws.max_entries, ws.topk_scratch)
+                else:
+                    nat.call("lsb_indexer_topk", ws.scores, ws.max_entries, ws.n_entries, ws.row_len, ws.row_seq,
+                             cfg.index_topk // P, P, ws.sel_idx, ws.sel_cnt, ws.sel_ld, R)
             sel_idx, sel_cnt, sel_ld = ws.sel_idx, ws.sel_cnt, ws.sel_ld
         if self.dcp is not None:
             # sharded KV: gather the queries of all heads, attend over this rank's token shard, merge on the head owners

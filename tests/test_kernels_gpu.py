@@ -460,3 +460,39 @@ def test_indexer_scores_on_tensor_cores_match_the_cuda_core_kernel(R, IH, pos0):
     assert torch.equal(out[~mask], ref[~mask])              # nothing written beyond a row's causal frontier
     d = (out[mask] - ref[mask]).abs().max().item()
     assert d < 2e-4 * ref[mask].abs().max().item() + 1e-6, d
+
+
+@pytest.mark.parametrize("P,budget,kind", [(4, 512, "normal"), (1, 2048, "normal"), (4, 512, "relu"), (4, 512, "const")])
+def test_split_top_k_selection_equals_the_single_block_kernel(P, budget, kind):
+    """Long index rows: the selection spread over many blocks (three histogram launches, count, emit) gives the single-block
+    kernel's output entry for entry - ascending order, ties to the lower index, tail tokens, count - also for rows shorter than
+    the budget, unused rows, rows full of equal scores, and on a second call over the scratch the first one left behind."""
+    g = torch.Generator(device=DEV).manual_seed(11)
+    ne_list = [70001, budget - 3, 262144, 9000, 0, 2048 * 3]
+    R = len(ne_list)
+    ld = 262144 + 8
+    sc = torch.randn(R, ld, device=DEV, generator=g)
+    if kind == "relu":
+        sc = (sc - 2.2).clamp_min(0)                          # most scores are exactly zero, as after the indexer's ReLU
+    elif kind == "const":
+        sc.fill_(0.25)
+    ne = torch.tensor(ne_list, dtype=torch.int32, device=DEV)
+    row_len = (ne * P + torch.tensor([1, 0, 3, 2, 0, 0], device=DEV).clamp_max(P - 1)).int()
+    row_seq = torch.tensor([0, 1, 2, 3, -1, 4], dtype=torch.int32, device=DEV)
+    sel_ld = budget * P + P
+    ref_idx = torch.full((R, sel_ld), -1, dtype=torch.int32, device=DEV)
+    ref_cnt = torch.full((R,), -1, dtype=torch.int32, device=DEV)
+    nat.call("lsb_indexer_topk", sc, ld, ne, row_len, row_seq, budget, P, ref_idx, ref_cnt, sel_ld, R)
+    scratch = torch.zeros((int(nat.call("lsb_indexer_topk_split_scratch", R, ld)) + 3) // 4, dtype=torch.int32, device=DEV)
+    for _ in range(2):
+        idx = torch.full((R, sel_ld), -1, dtype=torch.int32, device=DEV)
+        cnt = torch.full((R,), -1, dtype=torch.int32, device=DEV)
+        nat.call("lsb_indexer_topk_split", sc, ld, ne, row_len, row_seq, budget, P, idx, cnt, sel_ld, R, ld, scratch)
+        torch.cuda.synchronize()
+        assert torch.equal(cnt, ref_cnt), (cnt.tolist(), ref_cnt.tolist())
+        assert torch.equal(idx, ref_idx)
+    # and against a sort: the budget best entries of the longest row
+    r = 2
+    order = torch.sort(sc[r, :ne_list[r]], descending=True, stable=True).indices[:budget].sort().values
+    got = ref_idx[r, : budget * P].view(budget, P)[:, 0] // P
+    assert torch.equal(got.long(), order)

@@ -180,14 +180,15 @@ def build_engine(cfg: dict, shape: ModelConfig, ckpt: Optional[str], args: argpa
         if not dist.is_initialized():
             dist.init_process_group("nccl", device_id=dev)
     kv_fmt = args.kv_format or {"fp8_e4m3": "fp8", "bf16": "bf16", "fp16": "bf16", "turboquant4": "tq4"}.get(cfg["quantization"]["kv_cache"], "fp8")
+    want_mtp = bool(cfg["speculation"]["enabled"]) and cfg["speculation"]["method"] == "mtp"      # load the MTP block only when it drafts
     if ckpt and not args.random_weights:
         from ..models.checkpoint import open_checkpoint
         _, w = open_checkpoint(ckpt, shape)
-        model = DeviceModel.from_state_dict(shape, w, dev, kv_fmt, page, tp_rank=rank, tp_size=world)
+        model = DeviceModel.from_state_dict(shape, w, dev, kv_fmt, page, tp_rank=rank, tp_size=world, with_mtp=want_mtp)
     else:
         log.warning("serving RANDOM weights of shape %s", shape.name)
         model = DeviceModel.random_init(shape, dev, kv_fmt, page, expert_slots="auto", embed_on_host=shape.vocab * shape.hidden > (1 << 28),
-                                        tp_rank=rank, tp_size=world)
+                                        tp_rank=rank, tp_size=world, with_mtp=want_mtp)
     max_ctx = sv["max_sequence_length"]
     if world > 1:
         from ..parallel.symm import PeerComm
@@ -214,6 +215,16 @@ def build_model_draft(cfg: dict, shape: ModelConfig, engine, args: argparse.Name
     from ..speculation.model_draft import EngineDraft, draft_shape_for
     sp = cfg["speculation"]
     target = getattr(engine, "_engine", engine)                  # unwrap tracing / SPMD facades
+    if sp["method"] == "mtp":
+        # the model's own multi-token-prediction block, kept in step on the device: one proposed token per round
+        from ..speculation.mtp_draft import DeviceMtpDraft, MtpDraft
+        try:
+            if hasattr(target, "enable_mtp"):
+                return DeviceMtpDraft(target, sp["mtp"]), 1
+            return MtpDraft(target, sp["mtp"]), (args.speculation_depth if args.speculation_depth is not None else sp["mtp"]["max_depth"])
+        except (NotImplementedError, ValueError, AttributeError) as e:
+            log.warning("MTP draft unavailable (%s); serving without speculation", e)
+            return None, 0
     if sp["method"] == "self_speculative":
         from ..speculation.self_draft import SelfSpeculativeDraft
         depth = args.speculation_depth if args.speculation_depth is not None else sp["mtp"]["max_depth"]
@@ -269,7 +280,7 @@ def build_server(cfg: dict, shape: ModelConfig, ckpt: Optional[str], engine, arg
         pl = sp["prompt_lookup"]
         draft = PromptLookupDraft(pl["min_ngram_size"], pl["max_ngram_size"], pl["max_continuation_length"])
         depth = args.speculation_depth if args.speculation_depth is not None else pl["max_continuation_length"]
-    elif sp["enabled"] and sp["method"] in ("dspark", "self_speculative"):
+    elif sp["enabled"] and sp["method"] in ("dspark", "self_speculative", "mtp"):
         draft, depth = build_model_draft(cfg, shape, engine, args)
     orch = Orchestrator(engine, eos_token_ids=eos, prefix_cache=pcc, draft=draft, speculation_depth=depth, tokenizer=tok)
     rc = sv["reasoning_config"]

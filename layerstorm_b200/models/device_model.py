@@ -474,6 +474,7 @@ class Workspace:
          self.seq_row0, self.seq_nrows, self.seq_slot) = (self.inp[j] for j in range(9))
         # activations
         self.x = z(R, H, dtype=b16)
+        self.mtp_cat = z(R, 2 * H, dtype=b16) if m.mtp_layers else None       # [RMSNorm(embedding) ; RMSNorm(stream)] of an MTP block
         self.sub = z(R, H)
         self.resid = z(R, n, H)
         self.post = z(R, n); self.comb = z(R, n, n)
@@ -628,6 +629,7 @@ class DeviceModel:
         self.comm = None          # PeerComm for the fused all-reduces
         self.comm_amax = None     # PeerComm for the argmax exchange
         self.layers: List[dict] = []
+        self.mtp_layers: List[dict] = []            # multi-token-prediction blocks (layer ids n_layers ..), see forward_mtp
         self.embed = None
         self.head: Optional[QLinear] = None
         self.final_norm = None
@@ -666,6 +668,11 @@ class DeviceModel:
         v.drift = None
         v.kernel_launches = 0
         return v
+
+    def mtp_supported(self) -> bool:
+        """Whether this model can run multi-token-prediction blocks on the device: one GPU, a plain residual stream (no
+        hyper-connections: their final stream is never materialised un-normalised) and an FP8 / bf16 latent cache."""
+        return self.tp_size == 1 and not self.cfg.mhc and self.kv_fmt != "tq4" and self.cfg.n_mtp > 0
 
     @property
     def _cp(self):
@@ -723,7 +730,9 @@ class DeviceModel:
     @classmethod
     def from_state_dict(cls, cfg: ModelConfig, w: Dict[str, torch.Tensor], device="cuda", kv_fmt="fp8", page=64,
                         expert_quant: Optional[str] = None, dense_quant: Optional[str] = None, tp_rank: int = 0,
-                        tp_size: int = 1, expert_shard: Optional[str] = None) -> "DeviceModel":
+                        tp_size: int = 1, expert_shard: Optional[str] = None, with_mtp: bool = False) -> "DeviceModel":
+        """``with_mtp``: also load the checkpoint's multi-token-prediction blocks (one more decoder layer each, with its experts)
+        for ``forward_mtp`` / ``Engine.enable_mtp``; ignored where ``mtp_supported()`` is false or the checkpoint has none."""
         m = cls(cfg, device, kv_fmt, page, tp_rank, tp_size, expert_shard)
         dev = m.device
         tr, ts = tp_rank, tp_size
@@ -749,10 +758,18 @@ class DeviceModel:
         m.embed = w["embed.weight"].to(dev).to(torch.bfloat16).contiguous()
         m.head = QLinear.from_float(rows(w["head.weight"], cfg.vocab, 1), "bf16", dev)
         m.final_norm = f32(w["final_norm.weight"])
-        for i in range(cfg.n_layers):
+        # multi-token-prediction blocks (layer ids n_layers ..): built like an MLA layer without indexer plus the block's input norms,
+        # its [embedding ; stream] projection and its output norm.  Device path: one GPU, plain residual stream, FP8 / bf16 KV.
+        n_mtp = cfg.n_mtp if (with_mtp and m.mtp_supported() and f"layers.{cfg.n_layers}.mtp.eh_proj" in w) else 0
+        for i in range(cfg.n_layers + n_mtp):
             p = f"layers.{i}."
+            is_mtp = i >= cfg.n_layers
             L: dict = {"attn_norm": f32(w[p + "attn_norm.weight"]), "ffn_norm": f32(w[p + "ffn_norm.weight"])}
-            if cfg.mhc:
+            if is_mtp:
+                L["mtp_enorm"], L["mtp_hnorm"] = f32(w[p + "mtp.enorm"]), f32(w[p + "mtp.hnorm"])
+                L["mtp_eh"] = QLinear.from_float(w[p + "mtp.eh_proj"], "bf16", dev)
+                L["mtp_final_norm"] = f32(w[p + "mtp.final_norm"])
+            if cfg.mhc and not is_mtp:
                 for nm in ("hc_attn", "hc_ffn"):
                     L[nm] = (f32(w[p + nm + ".fn"]), f32(w[p + nm + ".scale"]), f32(w[p + nm + ".base"]))
             if cfg.is_kda_layer(i):
@@ -772,7 +789,7 @@ class DeviceModel:
                 a = p + "attn."
                 parts = [w[a + "q_a"], w[a + "kv_a"]]
                 qb_parts = [rows(w[a + "q_b"], cfg.n_heads, cfg.qk_head)]
-                has_idx = cfg.has_indexer and cfg.index_source_layer(i) == i
+                has_idx = cfg.has_indexer and not is_mtp and cfg.index_source_layer(i) == i
                 if has_idx:
                     x = p + "indexer."
                     parts += [w[x + "wk"], w[x + "weights_proj"]]
@@ -820,14 +837,14 @@ class DeviceModel:
                 f = p + "mlp."
                 L["mlp_gu"] = QLinear.from_float(torch.cat([rows(w[f + "gate"], cfg.dense_inter, 1), rows(w[f + "up"], cfg.dense_inter, 1)], 0), dq, dev)
                 L["mlp_down"] = QLinear.from_float(cols(w[f + "down"], cfg.dense_inter, 1), dq, dev)
-            m.layers.append(L)
+            (m.mtp_layers if is_mtp else m.layers).append(L)
         m._finish()
         return m
 
     @classmethod
     def random_init(cls, cfg: ModelConfig, device="cuda", kv_fmt="fp8", page=64, seed=0, expert_slots=None,
                     embed_on_host: bool = False, reserve_bytes: int = 4 << 30, tp_rank: int = 0, tp_size: int = 1,
-                    expert_shard: Optional[str] = None) -> "DeviceModel":
+                    expert_shard: Optional[str] = None, with_mtp: bool = False) -> "DeviceModel":
         """Random weights generated directly in storage format on the device (full-size models).
         ``expert_slots`` caps the routed-expert slots per MoE layer (VRAM expert cache): an int, None
         (all experts resident) or "auto" (as many as fit while leaving ``reserve_bytes`` of device
@@ -866,9 +883,14 @@ class DeviceModel:
                 lin.w[r0:].normal_(0.0, std, generator=gen)
         m.final_norm = nrm(H)
         n = cfg.hc_mult
-        for i in range(cfg.n_layers):
+        n_mtp = cfg.n_mtp if (with_mtp and m.mtp_supported()) else 0
+        for i in range(cfg.n_layers + n_mtp):
+            is_mtp = i >= cfg.n_layers                # a multi-token-prediction block: an MLA layer without indexer + its own norms / projection
             L: dict = {"attn_norm": nrm(H), "ffn_norm": nrm(H)}
-            if cfg.mhc:
+            if is_mtp:
+                L["mtp_enorm"], L["mtp_hnorm"], L["mtp_final_norm"] = nrm(H), nrm(H), nrm(H)
+                L["mtp_eh"] = QLinear.random(H, 2 * H, "bf16", dev, std=0.05, gen=gen)
+            if cfg.mhc and not is_mtp:
                 for nm in ("hc_attn", "hc_ffn"):
                     L[nm] = (rnd(2 * n + n * n, n * H, std=0.05), torch.ones(3, device=dev), rnd(2 * n + n * n, std=0.5))
             if cfg.is_kda_layer(i):
@@ -885,7 +907,7 @@ class DeviceModel:
                 L["kda_o"] = QLinear.random(H, C, dq, dev, gen=gloc)
             else:
                 Hh = m.Hh
-                has_idx = cfg.has_indexer and cfg.index_source_layer(i) == i
+                has_idx = cfg.has_indexer and not is_mtp and cfg.index_source_layer(i) == i
                 n_in = cfg.q_lora + cfg.kv_lora + cfg.qk_rope
                 n_qb = Hh * cfg.qk_head
                 if has_idx:
@@ -911,8 +933,8 @@ class DeviceModel:
             else:
                 L["mlp_gu"] = QLinear.random(2 * m.Fd, H, dq, dev, gen=gloc)
                 L["mlp_down"] = QLinear.random(H, m.Fd, dq, dev, gen=gloc)
-            m.layers.append(L)
-        moe_layers = [(i, L) for i, L in enumerate(m.layers) if "arena" in L]
+            (m.mtp_layers if is_mtp else m.layers).append(L)
+        moe_layers = [(i, L) for i, L in enumerate(m.layers + m.mtp_layers) if "arena" in L]
         if moe_layers:
             ef = expert_layout(eq, H, m.Fe)
             E_total = cfg.n_routed + cfg.n_shared
@@ -983,7 +1005,7 @@ class DeviceModel:
                 L["kda_gb2"] = torch.cat([L["kda_gb"], L["kda_gb"]], 1).contiguous()
         if self.kv_fmt == "tq4":
             self._fold_turboquant()
-        for L in self.layers:
+        for L in self.layers + self.mtp_layers:
             if "kda_in" in L:
                 self.max_proj = max(self.max_proj, L["kda_in"].N)
             if "mla_in" in L:
@@ -993,7 +1015,7 @@ class DeviceModel:
 
     def weight_bytes(self) -> int:
         tot = self.head.nbytes() + (self.embed.numel() * 2 if self.embed.is_cuda else 0)
-        for L in self.layers:
+        for L in self.layers + self.mtp_layers:
             for v in L.values():
                 if isinstance(v, QLinear):
                     tot += v.nbytes()
@@ -1028,6 +1050,9 @@ class DeviceModel:
                     self.idx_cache[i] = torch.zeros(idx_pages, self.page // P, self.idx_row_bytes, dtype=torch.uint8, device=dev)
                     if P > 1:
                         self.idx_tail[i] = torch.zeros(n_slots, P, 2, cfg.index_head_dim, dtype=torch.bfloat16, device=dev)
+        for k in range(len(self.mtp_layers)):
+            # a multi-token-prediction block keeps its own latent cache over the same pages (same positions, same page table)
+            self.kv_cache[cfg.n_layers + k] = torch.zeros(num_pages, self.page, self.kv_row_bytes, dtype=torch.uint8, device=dev)
 
     def reset_slot(self, slot: int):
         for t in self.kda_state.values():
@@ -1164,7 +1189,8 @@ class DeviceModel:
         L["kda_o"](ws.sub, ws.kda_out, R, comm=self._cp)
         self._reduce(ws, R)
 
-    def _mla(self, i: int, L: dict, ws: Workspace, R: int):
+    def _mla(self, i: int, L: dict, ws: Workspace, R: int, dense: bool = False):
+        """``dense``: the layer has no indexer and attends over the whole prefix (multi-token-prediction blocks)."""
         cfg = self.cfg
         Hh, dl, dr, dn, dv = self.Hh, cfg.kv_lora, cfg.qk_rope, cfg.qk_nope, cfg.v_head
         ldp = self.max_proj
@@ -1172,7 +1198,7 @@ class DeviceModel:
         off_ik = off_kv + dl + dr
         off_iw = off_ik + cfg.index_head_dim
         off_ig = off_iw + cfg.index_n_heads
-        src = cfg.index_source_layer(i) if cfg.has_indexer else -1
+        src = cfg.index_source_layer(i) if (cfg.has_indexer and not dense) else -1
         has_idx = src == i
         L["mla_in"](ws.proj, ws.x, R, ldo=ldp)
         P = cfg.index_kpool
@@ -1189,7 +1215,7 @@ class DeviceModel:
                  dr, self.inv_freq, ws.row_pos)
         sel_idx = sel_cnt = None
         sel_ld = 0
-        if cfg.has_indexer:
+        if cfg.has_indexer and not dense:
             if has_idx:
                 nat.call("lsb_indexer_q_prep", ws.qproj, ldq, Hh * (dn + dr), ws.proj, ldp, off_iw, cfg.index_n_heads,
                          cfg.index_rope_dim, self.inv_freq_idx, ws.row_pos, ws.q_idx, ws.idx_w, ws.kstash, off_ig,
@@ -1354,6 +1380,38 @@ class DeviceModel:
             self.drift["final_norm_out"] = xr.float().cpu()
             self.drift["logits"] = ws.logits[:n_logit_rows].float().cpu()
 
+    def forward_mtp(self, ws: Workspace, R: int, k: int = 0, logit_row0: int = 0, n_logit_rows: int = 0):
+        """Multi-token-prediction block ``k`` over the staged rows.  In: ``ws.resid`` rows = the stream of the previous depth at the
+        rows' positions (after ``forward``: the main model's stream in front of its output norm), ``ws.tok`` = the token one place
+        AHEAD of each row's position, the rows' sequence / position arrays as staged for the main step.  Does
+            x = eh_proj [RMSNorm_e(Emb(tok)) ; RMSNorm_h(stream)],  one decoder block (dense MLA over the block's own latent cache,
+            FFN / MoE),  logits = head(RMSNorm_f(stream'))
+        and leaves the block's output stream in ``ws.resid`` (the input of the next depth), logits of rows
+        [logit_row0, logit_row0 + n_logit_rows) in ``ws.logits``.  Reference: the engine's MtpSpeculationMethod (src/speculation/),
+        python/orchestrator/mtp_draft.py; architecture: DeepSeek-V3 technical report, section 2.2."""
+        cfg = self.cfg
+        if not self.mtp_layers:
+            raise RuntimeError("this model has no multi-token-prediction blocks on the device")
+        if self.streamer is not None or self.row_tier is not None:
+            raise RuntimeError("multi-token-prediction blocks need resident experts and an untiered KV cache")
+        L = self.mtp_layers[k]
+        i = cfg.n_layers + k
+        H = cfg.hidden
+        self._fused = False
+        resid = ws.resid.view(-1)[: ws.R * H].view(ws.R, H)
+        cat = ws.mtp_cat
+        nat.call("lsb_embedding", ws.sub, None, self.embed, ws.tok, R, H, 0, cfg.vocab)
+        nat.call("lsb_rmsnorm", cat, ws.sub, L["mtp_enorm"], R, H, H, 2 * H, cfg.rms_eps, 1, None)
+        nat.call("lsb_rmsnorm", cat.view(-1)[H:], resid, L["mtp_hnorm"], R, H, H, 2 * H, cfg.rms_eps, 1, None)
+        L["mtp_eh"](resid, cat, R)                               # the block's residual stream replaces the previous depth's
+        nat.call("lsb_rmsnorm", ws.x, resid, L["attn_norm"], R, H, H, H, cfg.rms_eps, 1, None)
+        self._mla(i, L, ws, R, dense=True)
+        nat.call("lsb_add_rmsnorm", ws.x, resid, ws.sub, L["ffn_norm"], R, H, cfg.rms_eps, None)
+        self._ffn(i, L, ws, R)
+        nat.call("lsb_add_rmsnorm", ws.x, resid, ws.sub, L["mtp_final_norm"], R, H, cfg.rms_eps, None)
+        if n_logit_rows:
+            self.head(ws.logits, ws.x[logit_row0: logit_row0 + n_logit_rows], n_logit_rows)
+
     def argmax(self, ws: Workspace, n_rows: int):
         """Greedy token per row; with a vocabulary-parallel head the per-rank winners are exchanged
         in-kernel over NVLink (8 bytes per row per rank)."""
@@ -1370,10 +1428,13 @@ class DeviceModel:
         out["embed.weight"] = cpu(self.embed)
         out["head.weight"] = cpu(self.head.dequant())
         out["final_norm.weight"] = cpu(self.final_norm)
-        for i, L in enumerate(self.layers):
+        for i, L in enumerate(self.layers + self.mtp_layers):
             p = f"layers.{i}."
             out[p + "attn_norm.weight"] = cpu(L["attn_norm"]); out[p + "ffn_norm.weight"] = cpu(L["ffn_norm"])
-            if cfg.mhc:
+            if "mtp_eh" in L:
+                out[p + "mtp.enorm"], out[p + "mtp.hnorm"], out[p + "mtp.final_norm"] = cpu(L["mtp_enorm"]), cpu(L["mtp_hnorm"]), cpu(L["mtp_final_norm"])
+                out[p + "mtp.eh_proj"] = cpu(L["mtp_eh"].dequant())
+            if cfg.mhc and "hc_attn" in L:
                 for nm in ("hc_attn", "hc_ffn"):
                     out[p + nm + ".fn"], out[p + nm + ".scale"], out[p + nm + ".base"] = (cpu(t) for t in L[nm])
             if cfg.is_kda_layer(i):
@@ -1399,7 +1460,7 @@ class DeviceModel:
                 wq = cpu(L["mla_qb"].dequant())
                 nq = cfg.n_heads * cfg.qk_head
                 out[a + "q_b"] = wq[:nq]
-                if cfg.has_indexer and cfg.index_source_layer(i) == i:
+                if cfg.has_indexer and i < cfg.n_layers and cfg.index_source_layer(i) == i:
                     x = p + "indexer."
                     out[x + "wk"] = w[o: o + cfg.index_head_dim]; o += cfg.index_head_dim
                     out[x + "weights_proj"] = w[o: o + cfg.index_n_heads]; o += cfg.index_n_heads

@@ -100,6 +100,7 @@ class Engine:
         self.h2d_bytes = 0
         self.d2h_bytes = 0
         self.kernel_launches = 0
+        self.mtp = None               # MtpRunner once enable_mtp() was called (runtime/mtp.py)
 
     # ------------------------------------------------------------------ boot-time memory carve
     def _carve_report(self) -> dict:
@@ -179,6 +180,8 @@ class Engine:
             self.row_tier.on_create(slot)
         with torch.cuda.stream(self.stream):
             self.model.reset_slot(slot)
+        if self.mtp is not None:
+            self.mtp.on_create(slot)
         return slot
 
     def free_sequence(self, sid: int):
@@ -186,6 +189,8 @@ class Engine:
             self.hibernated.pop(sid)
             self.tier.destroy(sid)
         s = self.seqs.pop(sid)
+        if self.mtp is not None:
+            self.mtp.on_free(sid)
         if self.row_tier is not None:
             self.row_tier.on_free(sid)
         self.pa.destroy(s.slot)
@@ -234,6 +239,8 @@ class Engine:
             for t in list(m.kda_state.values()) + list(m.kda_conv.values()) + list(m.idx_tail.values()):
                 t[slot].copy_(t[ps.slot])
             self._sync_block_table(cs)
+            if self.mtp is not None:
+                self.mtp.on_fork(parent, slot, prefix_len)
         return slot
 
     # ------------------------------------------------------------------ KV tiering (hibernate / resume)
@@ -369,6 +376,8 @@ class Engine:
         s.length = length
         del_tokens = s.tokens[length:]
         del s.tokens[length:]
+        if self.mtp is not None:
+            self.mtp.on_rewind(sid, length)
         self.pa.rewind(s.slot, length)
         s.pages = self.pa.pages(s.slot)
         if replay:
@@ -445,6 +454,8 @@ class Engine:
             self.ws_prefill = Workspace(self.model, self.prefill_chunk, 1, self.max_ctx)
         ws = self.ws_prefill
         nxt, logits = None, None
+        if self.mtp is not None and tokens:
+            self.mtp.before_step(sid, tokens[0])
         with torch.cuda.stream(self.stream):
             # all pages of the call up front: running out of pages must fail BEFORE the first chunk is committed, because the
             # caller evicts and calls again with the same tokens (a failure after chunk c would append chunks 0..c twice)
@@ -457,6 +468,8 @@ class Engine:
                 n0 = nat.launch_count()
                 self.model.forward(ws, R, 1, R - 1, 1)
                 self.model.argmax(ws, 1)
+                if self.mtp is not None:
+                    self.mtp.after_prefill_chunk(sid, ws, chunk, s.length, tokens[c0 + R] if c0 + R < len(tokens) else None)
                 self.kernel_launches += nat.launch_count() - n0
                 s.length += R
                 s.tokens.extend(chunk)
@@ -468,6 +481,8 @@ class Engine:
             nxt = int(self.h_out[0])
             if want_logits:
                 logits = ws.logits[0].float().cpu()
+            if self.mtp is not None:
+                self.mtp.release_pins()
         if self.row_tier is not None:
             self.row_tier.slide_window(sid)
         return (nxt, logits) if want_logits else nxt
@@ -492,6 +507,8 @@ class Engine:
         self._require_hot(sid)
         s = self.seqs[sid]
         R = len(tokens)
+        if self.mtp is not None and R:
+            self.mtp.before_step(sid, int(tokens[0]))
         ws = self._ws_rows(R)
         with torch.cuda.stream(self.stream):
             self._ensure_pages(s, s.length + R)
@@ -500,6 +517,8 @@ class Engine:
             n0 = nat.launch_count()
             self.model.forward(ws, R, 1, 0, R)
             self.kernel_launches += nat.launch_count() - n0
+            if self.mtp is not None:
+                self.mtp.stash_rows(sid, ws, 0, R, s.length)
             self._queue_error_readback()
             self.stream.synchronize()
             self._check_errors()
@@ -524,6 +543,8 @@ class Engine:
         draft = [int(t) for t in draft]
         rows_tok = [int(tok)] + draft
         R, gamma = len(rows_tok), len(draft)
+        if self.mtp is not None:
+            self.mtp.before_step(sid, int(tok))
         ws = self._ws_rows(R)
         if not hasattr(ws, "verify_out"):
             ws.verify_out = torch.zeros(2, dtype=torch.int32, device=self.dev)
@@ -542,6 +563,8 @@ class Engine:
             # rows 1..gamma of the staged token ids ARE the draft; out_tok[k] is the target's choice after row k
             nat.call("lsb_spec_verify", ws.tok[1:] if gamma else ws.tok, ws.out_tok, gamma, ws.verify_out)
             self.kernel_launches += nat.launch_count() - n0
+            if self.mtp is not None:
+                self.mtp.stash_rows(sid, ws, 0, R, s.length)
             self.h_out[:2].copy_(ws.verify_out, non_blocking=True)
             self.d2h_bytes += 8
             self._queue_error_readback()
@@ -553,6 +576,23 @@ class Engine:
         if n_acc < gamma:
             self.rewind(sid, s.length - (gamma - n_acc))
         return n_acc, nxt
+
+    def enable_mtp(self):
+        """Keep the model's multi-token-prediction block in step with every sequence from now on (``runtime/mtp.py``) so that
+        :meth:`mtp_draft` can propose a token; costs one pass of the block per committed token.  Raises NotImplementedError when
+        the model has no block on the device or the engine's KV / expert placement rules it out."""
+        if self.mtp is None:
+            from .mtp import MtpRunner
+            self.mtp = MtpRunner(self)
+        return self.mtp
+
+    def mtp_draft(self, sid: int, next_tok: int) -> List[int]:
+        """The MTP block's proposal for the token AFTER ``next_tok`` (the token about to be fed to the sequence); [] when the
+        block is not in step with the sequence.  Verify with :meth:`verify_greedy` ``(sid, next_tok, draft)``."""
+        if self.mtp is None:
+            raise RuntimeError("call enable_mtp() first")
+        self._require_hot(sid)
+        return self.mtp.draft(sid, int(next_tok))
 
     @property
     def supports_device_sampling(self) -> bool:
@@ -587,6 +627,9 @@ class Engine:
         B = len(sids)
         for sid in sids:
             self._require_hot(sid)
+        if self.mtp is not None:
+            for sid, tok in zip(sids, tokens):
+                self.mtp.before_step(sid, int(tok))
         ws = self._ws_decode(B)
         with torch.cuda.stream(self.stream):
             rows, groups = [], []
@@ -610,6 +653,9 @@ class Engine:
                 self.model.forward(ws, B, B, 0, B)
                 self.model.argmax(ws, B)
                 self.kernel_launches += nat.launch_count() - n0
+            if self.mtp is not None:
+                for j, sid in enumerate(sids):
+                    self.mtp.stash_rows(sid, ws, j, 1, self.seqs[sid].length)
             if sample is not None:
                 if not self.supports_device_sampling:
                     raise RuntimeError("device sampling needs the full vocabulary on one GPU")

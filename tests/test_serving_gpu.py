@@ -217,3 +217,73 @@ def test_cosine_similarity_kernel():
     assert float(out[3]) == 0.0
     keep = torch.tensor([0, 1, 2, 4], device="cuda")
     assert torch.allclose(out[keep], ref[keep], atol=1e-5)
+
+
+@pytest.mark.parametrize("name", ["tiny-mla-moe", "tiny-deepseek-v32"])
+def test_device_mtp_block_matches_the_reference_and_stays_in_step_through_speculation(name):
+    """The multi-token-prediction block on the device: after a chunked prefill and after every speculative round (accepted or
+    rejected drafts, plain decode steps in between) its proposal equals the fp32 reference's, which recomputes the main stream and
+    the block from scratch; greedy speculation with it reproduces plain greedy decoding token for token."""
+    import dataclasses
+    from layerstorm_b200.models.config import get_preset
+    from layerstorm_b200.models.device_model import DeviceModel
+    from layerstorm_b200.models.mtp import mtp_block
+    from layerstorm_b200.models.reference import Oracle
+    from layerstorm_b200.models.weights import init_weights
+    from layerstorm_b200.runtime.engine import Engine
+    cfg = dataclasses.replace(get_preset(name), n_mtp=1)
+    w = init_weights(cfg, 3)
+    m = DeviceModel.from_state_dict(cfg, w, "cuda", kv_fmt="bf16", page=16, expert_quant="bf16", dense_quant="bf16", with_mtp=True)
+    assert len(m.mtp_layers) == 1
+    oracle = Oracle(cfg, m.effective_state_dict())
+    g = torch.Generator().manual_seed(4)
+    T = 27                                             # below index_topk: dense selection in the main model on both sides
+    prompt = torch.randint(0, cfg.vocab, (T,), generator=g).tolist()
+
+    def ref_draft(context):
+        """logits of the block at the last fed position: main stream over context[:-1], token ahead = context[1:]."""
+        n = len(context) - 1
+        _, hidden = oracle.forward(torch.tensor(context[:n]), return_hidden=True)
+        logits, _ = mtp_block(oracle, 0, hidden, context[1: n + 1])
+        return logits[-1]
+
+    plain = Engine(m, max_seqs=2, max_ctx=128, prefill_chunk=8, max_batch=1, use_graph=False)
+    sid0 = plain.create_sequence()
+    tok = plain.prefill(sid0, prompt)
+    want = [tok]
+    for _ in range(9):
+        want.append(plain.decode([sid0], [want[-1]])[0])
+    plain.free_sequence(sid0)
+
+    eng = Engine(m, max_seqs=3, max_ctx=128, prefill_chunk=8, max_batch=1, use_graph=False)
+    eng.enable_mtp()
+    sid = eng.create_sequence()
+    tok = eng.prefill(sid, prompt)
+    assert tok == want[0]
+    got, ctx = [tok], prompt + [tok]
+    rounds = accepted = 0
+    while len(got) < 10:
+        d = eng.mtp_draft(sid, tok)
+        assert len(d) == 1
+        ref = ref_draft(ctx)
+        lg = eng.mtp.last_ws.logits[0].float().cpu()
+        assert float((lg - ref).abs().max() / (ref.abs().max() + 1e-9)) < 3e-2
+        assert d[0] == int(ref.argmax())
+        if rounds % 3 == 2:
+            tok = eng.decode([sid], [tok])[0]          # a plain step in between: the block catches up on its own
+            new = [tok]
+        else:
+            n_acc, nxt = eng.verify_greedy(sid, tok, d)
+            accepted += n_acc
+            new = d[:n_acc] + [nxt]
+            tok = nxt
+        rounds += 1
+        got += new
+        ctx += new
+    assert got[:10] == want[:10]
+    assert eng.mtp.block_rows >= T - 1 + rounds
+    # a fork at the frontier keeps the block in step; a fork below it proposes nothing (and never a wrong cache)
+    child = eng.fork_sequence(sid)
+    assert eng.mtp_draft(child, tok) == eng.mtp_draft(sid, tok)
+    low = eng.fork_sequence(sid, (eng.seq_len(sid) // 2))
+    assert eng.mtp_draft(low, tok) == []

@@ -381,3 +381,36 @@ def test_hash_layers_route_by_the_token_table_and_survive_both_checkpoint_format
     assert got.dtype == np.int32 and np.array_equal(got, tab.numpy())
     _, ck2 = open_checkpoint(str(tmp_path / "t.gguf"), cfg)
     assert torch.equal(ck2[f"layers.{hashed[0]}.moe.tid2eid"].long(), tab.long())
+
+
+def test_device_mtp_draft_source_finds_the_sequence_of_a_context():
+    """``DeviceMtpDraft`` maps the orchestrator's token list to the engine sequence that holds it (minus the token about to be fed) and
+    proposes nothing for a context no sequence holds."""
+    from layerstorm_b200.speculation.mtp_draft import DeviceMtpDraft
+
+    class Seq:
+        def __init__(self, toks):
+            self.tokens, self.length = list(toks), len(toks)
+
+    class Eng:
+        class cfg:
+            n_layers, n_mtp = 4, 1
+
+        def __init__(self):
+            self.seqs = {0: Seq([1, 2, 3]), 1: Seq([5, 6, 7, 8])}
+            self.calls, self.on = [], False
+
+        def enable_mtp(self):
+            self.on = True
+
+        def mtp_draft(self, sid, tok):
+            self.calls.append((sid, tok))
+            return [42]
+
+    e = Eng()
+    d = DeviceMtpDraft(e, {"enabled": True, "max_depth": 3})
+    assert e.on
+    assert d.propose([5, 6, 7, 8, 9], 4) == [42] and e.calls == [(1, 9)]
+    assert d.propose([9, 9, 9], 2) == [] and d.propose([5, 6, 7, 8, 9], 0) == []
+    d.feedback(1, 1)
+    assert d.proposed == 1

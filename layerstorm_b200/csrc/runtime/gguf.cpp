@@ -385,6 +385,11 @@ public:
         for (auto& s : v) put_str(kv_, s);
         ++nkv_;
     }
+    void meta_i32_array(const std::string& k, const int32_t* v, uint64_t n) {
+        put_str(kv_, k); put(kv_, (uint32_t)9); put(kv_, (uint32_t)5); put(kv_, n);
+        for (uint64_t i = 0; i < n; ++i) put(kv_, v[i]);
+        ++nkv_;
+    }
     int add_tensor(const std::string& name, int type, int ndims, const uint64_t* dims, const void* data, uint64_t nbytes) {
         TensorInfo t; t.name = name; t.type = type; t.ndims = ndims;
         for (int i = 0; i < ndims; ++i) t.dims[i] = dims[i];
@@ -482,6 +487,15 @@ LSB_RT_API void lsb_gguf_writer_free(void* w) { delete (GgufWriter*)w; }
 LSB_RT_API void lsb_gguf_writer_meta_u32(void* w, const char* k, unsigned int v) { ((GgufWriter*)w)->meta_u32(k, v); }
 LSB_RT_API void lsb_gguf_writer_meta_f32(void* w, const char* k, float v) { ((GgufWriter*)w)->meta_f32(k, v); }
 LSB_RT_API void lsb_gguf_writer_meta_str(void* w, const char* k, const char* v) { ((GgufWriter*)w)->meta_str(k, v); }
+LSB_RT_API void lsb_gguf_writer_meta_str_array(void* w, const char* k, const char* const* items, unsigned long long n) {
+    std::vector<std::string> v;
+    v.reserve(n);
+    for (unsigned long long i = 0; i < n; ++i) v.emplace_back(items[i]);
+    ((GgufWriter*)w)->meta_str_array(k, v);
+}
+LSB_RT_API void lsb_gguf_writer_meta_i32_array(void* w, const char* k, const int* items, unsigned long long n) {
+    ((GgufWriter*)w)->meta_i32_array(k, (const int32_t*)items, n);
+}
 LSB_RT_API int lsb_gguf_writer_add_tensor(void* w, const char* name, int type, int ndims, const unsigned long long* dims, const void* data, unsigned long long nbytes) {
     uint64_t d[4] = {1, 1, 1, 1}; for (int i = 0; i < ndims && i < 4; ++i) d[i] = dims[i];
     return ((GgufWriter*)w)->add_tensor(name, type, ndims, d, data, nbytes);

@@ -207,7 +207,13 @@ class GgufWriter:
 
     def meta(self, key: str, value):
         k = key.encode()
-        if isinstance(value, str):
+        if isinstance(value, (list, tuple)) and value and all(isinstance(v, str) for v in value):
+            arr = (ctypes.c_char_p * len(value))(*[v.encode() for v in value])
+            self.lib.lsb_gguf_writer_meta_str_array(self.h, k, ctypes.cast(arr, ctypes.c_void_p), len(value))
+        elif isinstance(value, (list, tuple)):
+            arr = (ctypes.c_int * len(value))(*[int(v) for v in value])
+            self.lib.lsb_gguf_writer_meta_i32_array(self.h, k, ctypes.cast(arr, ctypes.c_void_p), len(value))
+        elif isinstance(value, str):
             self.lib.lsb_gguf_writer_meta_str(self.h, k, value.encode())
         elif isinstance(value, float):
             self.lib.lsb_gguf_writer_meta_f32(self.h, k, value)

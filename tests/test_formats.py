@@ -145,3 +145,53 @@ def test_gguf_device_layouts_hold_the_file_blocks_unchanged():
         assert d.shape == (6, g.device_row_bytes(t, 512))
         assert np.array_equal(g.from_device_layout(t, d, 6, 512), raw)
     assert g.device_row_bytes(g.GGML_TYPES["Q5_K"], 512) == 2 * 176
+
+
+def test_tokenizer_directory_minted_from_a_gguf_vocabulary(tmp_path):
+    """A GGUF that carries its vocabulary, merges, token types, special ids and chat template -> tokenizer.json / tokenizer_config.json
+    that the serving tokenizer wrapper loads: same ids as the tokenizer the vocabulary came from, specials by id, texts round-trip."""
+    import json
+    from tokenizers import Tokenizer, decoders, models, pre_tokenizers, trainers
+    from layerstorm_b200.formats.gguf import GgufWriter
+    from layerstorm_b200.serving.tokenizer import TokenizerWrapper, resolve_tokenizer_dir
+    from layerstorm_b200.utils import mint_gguf_tokenizer as mint
+    # a small byte-level BPE trained here stands in for a model's vocabulary
+    src = Tokenizer(models.BPE())
+    src.pre_tokenizer = pre_tokenizers.ByteLevel(add_prefix_space=False, use_regex=True)
+    src.decoder = decoders.ByteLevel()
+    corpus = ["the quick brown fox jumps over the lazy dog " * 5, "hello world, hello tokens; numbers 12345 and 678", "def f(x):\n    return x + 1\n"] * 20
+    tr = trainers.BpeTrainer(vocab_size=400, initial_alphabet=pre_tokenizers.ByteLevel.alphabet(), special_tokens=[])
+    src.train_from_iterator(corpus, tr)
+    vocab = src.get_vocab()
+    tokens = [t for t, _ in sorted(vocab.items(), key=lambda kv: kv[1])]
+    merges = [" ".join(m) for m in json.loads(src.to_str())["model"]["merges"]]
+    specials = ["<|bos|>", "<|eos|>", "<think>", "</think>"]
+    types = [1] * len(tokens) + [3, 3, 4, 3]
+    tokens += specials
+    gw = GgufWriter()
+    gw.meta("general.architecture", "deepseek2")
+    gw.meta("tokenizer.ggml.model", "gpt2")
+    gw.meta("tokenizer.ggml.pre", "default")
+    gw.meta("tokenizer.ggml.tokens", tokens)
+    gw.meta("tokenizer.ggml.merges", merges)
+    gw.meta("tokenizer.ggml.token_type", types)
+    gw.meta("tokenizer.ggml.bos_token_id", len(tokens) - 4)
+    gw.meta("tokenizer.ggml.eos_token_id", len(tokens) - 3)
+    gw.meta("tokenizer.chat_template", "{% for m in messages %}{{ m.content }}{% endfor %}")
+    gw.add("token_embd.weight", np.zeros((4, 8), np.float32))
+    path = str(tmp_path / "m.gguf")
+    gw.write(path)
+    rep = mint.mint(path)
+    assert rep["problems"] == [] and rep["tokens"] == len(tokens) and rep["added_tokens"] == 4 and rep["chat_template"]
+    assert resolve_tokenizer_dir("auto", path) == str(tmp_path)
+    tw = TokenizerWrapper(str(tmp_path))
+    assert tw.special == {"<|bos|>": len(tokens) - 4, "<|eos|>": len(tokens) - 3, "</think>": len(tokens) - 1}      # control tokens; <think> is user-defined
+    assert tw.eos_token_ids == [len(tokens) - 3] and tw.chat_template.startswith("{% for")
+    for text in ["hello world 12345", "the lazy dog\n\treturn x", "unseen: Ünïcödé 🙂"]:
+        ids = tw.encode(text)
+        assert tw.decode(ids, skip_special_tokens=False) == text
+    # plain words tokenise as in the tokenizer the vocabulary came from (same merges, same byte-level alphabet)
+    assert tw.encode("hello world") == src.encode("hello world").ids
+    assert tw.encode("a<think>b</think>") [1] == len(tokens) - 2
+    # the command line: exit code 0 and a JSON report
+    assert mint.main(["--gguf", path, "--out", str(tmp_path / "o")]) == 0 and (tmp_path / "o" / "tokenizer.json").exists()

@@ -33,7 +33,7 @@ from . import native as rt
 
 class ExpertStreamer:
     def __init__(self, model, slots_per_layer: int, policy: str = "impact_weighted_lru", waterline: int = 4, prefetch: bool = False,
-                 fetch_deadline_ms: Optional[float] = None, numa_node: int = -1):
+                 fetch_deadline_ms: Optional[float] = None, numa_node: int = -1, place_freq: Optional[str] = None):
         """Takes a fully resident ``DeviceModel`` (every MoE layer's arena holds all of this rank's experts), moves
         the slot images to pinned host memory and shrinks every arena to ``slots_per_layer`` slots."""
         from ..models.device_model import ExpertArena
@@ -45,6 +45,11 @@ class ExpertStreamer:
         self.prefetch = prefetch
         self.trace = open(os.environ["LS_ROUTING_TRACE"], "w") if os.environ.get("LS_ROUTING_TRACE") else None
         self.trace_step = 0
+        # LS_FETCH_TRACE: one line per batch of host->device copies (copies, bytes, device time between events on the copy stream):
+        # the input of the copy cost-model fit (utils/loader_xray.py fit-constants)
+        self.fetch_trace_path = os.environ.get("LS_FETCH_TRACE") or None
+        self._fetch_spans: List[tuple] = []
+        self._span_start = None
         self.weighted = False                                    # True once configure_eviction() has installed the weighted score
         self.stats = {"hits": 0, "misses": 0, "waves": 0, "bytes_h2d": 0, "degraded_steps": 0, "late_experts": 0, "host_waits": 0}
         self._issued: List[tuple] = []
@@ -94,6 +99,24 @@ class ExpertStreamer:
         torch.cuda.empty_cache()
         self._last_layer = max(self.layers) if self.layers else -1
         model.streamer = self
+        place_freq = place_freq or os.environ.get("LS_ARENA_PLACE_FREQ") or None
+        if place_freq:
+            from ..utils.loader_xray import read_freq_table
+            self.prewarm(read_freq_table(place_freq))
+
+    def prewarm(self, freq: Dict[tuple, int]) -> int:
+        """Start with the most often FETCHED experts of every layer resident (``freq``: {(layer, expert): demand fetches}, the table
+        ``utils/loader_xray.py freq-table`` derives from a recorded run).  Returns the number of experts loaded."""
+        n_loaded = 0
+        for li, st in self.layers.items():
+            ranked = sorted((e for (l, e) in freq if l == li and e in st["mine"]), key=lambda e: -freq[(li, e)])
+            for e in ranked[: st["arena"].n_slots]:
+                if st["cache"].lookup(li, e) < 0 and self._reserve(li, st, e):
+                    n_loaded += 1
+            self._issue()
+            self._settle()
+        torch.cuda.synchronize(self.dev)
+        return n_loaded
 
     # ------------------------------------------------------------------ residency
     def _reserve(self, li: int, st: dict, e: int, priority: int = 0) -> bool:
@@ -131,6 +154,9 @@ class ExpertStreamer:
             with torch.cuda.stream(self.copy_stream):
                 if self._slot_free_ev is not None:
                     self.copy_stream.wait_event(self._slot_free_ev)  # the kernels that last read this layer's slots have finished (device side)
+                if self.fetch_trace_path and self._span_start is None:
+                    self._span_start = torch.cuda.Event(enable_timing=True)
+                    self._span_start.record(self.copy_stream)
                 lst["arena"].data[slot].copy_(lst["host"][lst["host_row"][e]], non_blocking=True)
             self.stats["bytes_h2d"] += lst["arena"].ef.stride
             self._issued.append((tok, info["layer"], e, slot))
@@ -150,8 +176,12 @@ class ExpertStreamer:
         self._retire_late()
         if not self._issued:
             return []
-        ev = torch.cuda.Event()
+        ev = torch.cuda.Event(enable_timing=bool(self.fetch_trace_path))
         ev.record(self.copy_stream)
+        if self._span_start is not None:
+            self._fetch_spans.append((self.trace_step, len(self._issued), sum(self.layers[li]["arena"].ef.stride for _, li, _, _ in self._issued),
+                                      self._span_start, ev))
+            self._span_start = None
         late: List[tuple] = []
         now = time.monotonic_ns()
         if self.fetch_deadline_ms is not None:
@@ -214,8 +244,8 @@ class ExpertStreamer:
         todo = sorted(need, key=lambda e: -need[e])              # heaviest experts first
         if self.trace is not None:                               # LS_ROUTING_TRACE: input of the offline cache replay (utils/cache_sim.py)
             self.trace.write(f"{self.trace_step} {li} {' '.join(str(e) for e in todo)}\n")
-            if li == self._last_layer:
-                self.trace_step += 1
+        if li == self._last_layer:
+            self.trace_step += 1                                 # counts steps for both traces (routing, copies)
         st["expert_stats"].observe(todo, [need[e] for e in todo])
         model._moe_prepare(arena, ws, R)
         st["present"].fill_(-1)
@@ -333,7 +363,22 @@ class ExpertStreamer:
         for st in self.layers.values():
             st["cache"].configure(section)
 
+    def flush_fetch_trace(self) -> int:
+        """Write the copy batches recorded so far to ``LS_FETCH_TRACE`` (appending) and forget them; returns how many."""
+        if not self.fetch_trace_path or not self._fetch_spans:
+            return 0
+        torch.cuda.synchronize(self.dev)
+        with open(self.fetch_trace_path, "a") as fh:
+            if fh.tell() == 0:
+                fh.write("# W step copies bytes device_us\n")
+            for step, n, nbytes, e0, e1 in self._fetch_spans:
+                fh.write(f"W {step} {n} {nbytes} {e0.elapsed_time(e1) * 1e3:.1f}\n")
+        n = len(self._fetch_spans)
+        self._fetch_spans = []
+        return n
+
     def summary(self) -> dict:
+        self.flush_fetch_trace()
         tot = max(1, self.stats["hits"] + self.stats["misses"])
         return dict(self.stats, hit_rate=self.stats["hits"] / tot, h2d_gbs=self.te.bandwidth_gbs(0, 0),
                     numa_bound_layers=sum(1 for st in self.layers.values() if st["host_arena"] is not None and st["host_arena"].numa_bound))

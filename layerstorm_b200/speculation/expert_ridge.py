@@ -91,14 +91,43 @@ class ExpertRidge:
         self.A += np.einsum("jef,jeg->jfg", f, f) + (1.0 - self.decay) * self.lam * np.eye(N_FEAT)
         self.b += np.einsum("jef,je->jf", f, y.astype(np.float64))
         self.positions += 1
-        if self.positions % self.refresh == 0:
-            for j in range(self.J):
-                self.w[j] = np.linalg.solve(self.A[j], self.b[j])
+        if self.refresh and self.positions % self.refresh == 0:      # refresh = 0: frozen weights (a trained bundle)
+            self.solve()
         self.prev[:] = y
         self.ema_f += self.fast * (y - self.ema_f)
         self.ema_s += self.slow * (y - self.ema_s)
         self.since = np.where(y > 0, 0.0, self.since + 1.0).astype(np.float32)
         self._pool = None
+
+    def solve(self):
+        """Re-solve every layer's weights from the accumulated sufficient statistics."""
+        for j in range(self.J):
+            self.w[j] = np.linalg.solve(self.A[j], self.b[j])
+
+    def reset_history(self):
+        """Forget the routing history (a new sequence starts); weights and sufficient statistics stay."""
+        self.prev[:] = 0
+        self.ema_f[:] = 0
+        self.ema_s[:] = 0
+        self.since[:] = 1e6
+        self._pool = None
+
+    def save_weights(self, path: str, meta: Optional[dict] = None):
+        """Weights + the hyper-parameters the features depend on, as one ``.npz`` (written by ``utils/expert_predictor_train.py``)."""
+        import json
+        np.savez(path, w=self.w, shape=np.array([self.J, self.E, self.K, self.lag]), ema=np.array([self.fast, self.slow]),
+                 meta=np.array(json.dumps(meta or {})))
+
+    def load_weights(self, path: str, freeze: bool = True):
+        """Install trained weights; with ``freeze`` they are no longer re-solved online."""
+        z = np.load(path, allow_pickle=False)
+        J, E, K, lag = (int(x) for x in z["shape"])
+        if (J, E) != (self.J, self.E) or lag != self.lag:
+            raise ValueError(f"predictor weights are for {J} layers x {E} experts (lag {lag}), this model has {self.J} x {self.E} (lag {self.lag})")
+        self.w[:] = z["w"]
+        self.fast, self.slow = (float(x) for x in z["ema"])
+        if freeze:
+            self.refresh = 0
 
     def coverage(self) -> np.ndarray:
         """Per layer: fraction of routed experts that were inside the last advised pools (calibration of ``pool``)."""

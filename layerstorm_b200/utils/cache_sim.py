@@ -67,7 +67,8 @@ def synthetic_trace(steps: int, layers: int, n_experts: int, top_k: int, zipf: f
 
 
 def simulate(trace: Trace, slots: int, policy: str = "impact_weighted_lru", weights: Optional[Sequence[float]] = None, prefetch_budget: int = 0,
-             slot_bytes: int = 18 << 20, n_experts: Optional[int] = None, top_k: Optional[int] = None, decisions: Optional[TextIO] = None) -> dict:
+             slot_bytes: int = 18 << 20, n_experts: Optional[int] = None, top_k: Optional[int] = None, decisions: Optional[TextIO] = None,
+             predictor_weights: Optional[str] = None) -> dict:
     from ..runtime import native as rt
     layers = sorted({l for _, l, _ in trace})
     lid = {l: i for i, l in enumerate(layers)}
@@ -81,6 +82,8 @@ def simulate(trace: Trace, slots: int, policy: str = "impact_weighted_lru", weig
     if prefetch_budget > 0:
         from ..speculation.expert_ridge import ExpertRidge
         ridge = ExpertRidge(len(layers), n_experts, top_k)
+        if predictor_weights:
+            ridge.load_weights(predictor_weights)          # a trained bundle (utils/expert_predictor_train.py), frozen
     hits = misses = prefetched = useful_prefetch = evictions = 0
     per_step_miss: Dict[int, int] = {}
     pending_prefetch: Dict[int, set] = {l: set() for l in layers}
@@ -163,6 +166,7 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     ap.add_argument("--weights", help="seven comma-separated score weights (alpha .. eta)")
     ap.add_argument("--prefetch-budget", type=int, default=0, help="experts prefetched per layer and step from the reuse predictor")
     ap.add_argument("--slot-mib", type=float, default=18.0)
+    ap.add_argument("--predictor-weights", help="trained reuse-predictor bundle (.npz) for the prefetcher instead of online learning")
     ap.add_argument("--decisions", help="write the miss / eviction stream here")
     ap.add_argument("--synthetic", default="256,8,64,8", help="steps,layers,experts,top_k of the synthetic trace")
     a = ap.parse_args(argv)
@@ -176,7 +180,7 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
         ap.error("--weights needs seven values")
     dec = open(a.decisions, "w") if a.decisions else None
     try:
-        rep = simulate(trace, a.slots, a.policy, w, a.prefetch_budget, int(a.slot_mib * (1 << 20)), ne, k, dec)
+        rep = simulate(trace, a.slots, a.policy, w, a.prefetch_budget, int(a.slot_mib * (1 << 20)), ne, k, dec, a.predictor_weights)
     finally:
         if dec:
             dec.close()

@@ -136,3 +136,85 @@ def test_cpu_expert_bench_runs_every_slot_format(capsys):
     assert rep["threads"] == 2 and len(rep["rows"]) == 8
     assert {r["format"] for r in rep["rows"]} == {"bf16", "fp8_e4m3", "nvfp4", "gguf_q4_k"}
     assert all(r["finite"] and r["ms"] > 0 and r["gflop_s"] > 0 for r in rep["rows"])
+
+
+def test_loader_xray_tables_and_fits(tmp_path):
+    """The loader's trace analysers: demand-fetch frequency table from a routing trace (cold steps left out, concentration profile),
+    least-squares copy cost model from copy batches, eviction weights picked by replaying a grid through the cache simulation."""
+    import json
+    import numpy as np
+    from layerstorm_b200.utils import loader_xray as lx
+    from layerstorm_b200.utils.cache_sim import synthetic_trace, write_trace
+    tr = synthetic_trace(steps=120, layers=3, n_experts=48, top_k=4, zipf=1.2, stickiness=0.4, seed=3)
+    rpath = str(tmp_path / "routing.txt")
+    write_trace(rpath, tr)
+    out = str(tmp_path / "freq.csv")
+    assert lx.main(["freq-table", out, rpath, "--slots", "12", "--skip-steps", "3"]) == 0
+    table = lx.read_freq_table(out)
+    assert table and all(0 <= l < 3 and 0 <= e < 48 and c > 0 for (l, e), c in table.items())
+    counts = lx.fetch_counts([tr], 12, skip_steps=3)
+    assert counts == table
+    # a bigger cache fetches less; a cache that holds every expert fetches each key at most once (its first use)
+    assert sum(lx.fetch_counts([tr], 24).values()) < sum(counts.values())
+    assert max(lx.fetch_counts([tr], 48, skip_steps=0).values()) == 1
+    conc = lx.concentration(counts)
+    assert 0 < conc["top_16"] <= conc["top_64"] <= 1.0
+    # copy batches generated from a known model: 40 GB/s and 30 us per batch, small noise
+    rng = np.random.default_rng(0)
+    fpath = str(tmp_path / "fetch.txt")
+    with open(fpath, "w") as fh:
+        fh.write("# W step copies bytes device_us\n")
+        for i in range(200):
+            n = int(rng.integers(1, 9))
+            b = n * (21 << 20)
+            fh.write(f"W {i} {n} {b} {30.0 + b / 40e3 + rng.normal(0, 2.0):.1f}\n")
+    rep = lx.fit_constants(lx.read_fetch_trace(fpath), calib_gbs=55.0)
+    assert abs(rep["h2d_gb_s"] - 40.0) < 0.5 and abs(rep["batch_overhead_us"] - 30.0) < 3.0 and rep["r2"] > 0.999
+    assert rep["against_calibration"]["scale"] > 1.3                   # the calibration's 55 GB/s was optimistic by 55 / 40
+    assert lx.main(["fit-constants", fpath, "--out", str(tmp_path / "c.json")]) == 0 and json.load(open(tmp_path / "c.json"))["batches"] == 200
+    # policy fit: never worse than the baselines it reports, and the section it writes is loadable by the native cache
+    pol = lx.fit_policy(tr, 12)
+    best = max(pol["best_weighted"]["hit_rate"], max(pol["baselines"].values()))
+    sec = pol["memory.expert_cache"]
+    assert sec["eviction_policy"] in ("impact_weighted_lru", "lru", "lfu") and pol["candidates"] >= 20
+    from layerstorm_b200.utils.cache_sim import simulate
+    w = [sec.get(k, 0.0) for k in lx.WEIGHT_FIELDS] if sec["eviction_policy"] == "impact_weighted_lru" else None
+    assert abs(simulate(tr, 12, sec["eviction_policy"], w)["hit_rate"] - best) < 1e-9
+
+
+def test_expert_predictor_offline_training_beats_fixed_rankings_on_held_out_sequences(tmp_path):
+    """Closed-form ridge fit of the reuse predictor over recorded routing, sequence-level split, recall@m against the fixed
+    rankings, bundle round trip into the online predictor and into the cache replay."""
+    import json
+    import numpy as np
+    import pytest
+    from layerstorm_b200.speculation.expert_ridge import ExpertRidge
+    from layerstorm_b200.utils import expert_predictor_train as ept
+    from layerstorm_b200.utils.cache_sim import simulate, synthetic_trace, write_trace
+    # five sequences over the same expert popularity (one seed), of different lengths and starting points
+    paths = []
+    for i in range(5):
+        p = str(tmp_path / f"r{i}.txt")
+        write_trace(p, synthetic_trace(steps=80 + 7 * i, layers=3, n_experts=40, top_k=4, zipf=1.1, stickiness=0.55, seed=10)[9 * i:])
+        paths.append(p)
+    out = str(tmp_path / "pred.npz")
+    assert ept.main(["--traces", *paths, "--out", out, "--report", str(tmp_path / "rep.json")]) == 0
+    rep = json.load(open(tmp_path / "rep.json"))
+    assert rep["train_sequences"] == 4 and rep["held_out_sequences"] == 1
+    h = rep["held_out"]
+    k = str(h["pools"][1])
+    assert h["trained"][k] >= max(h["previous_position"][k], h["fast_ema"][k], h["slow_ema_frequency"][k]) - 0.01
+    assert h["trained"][k] > h["slow_ema_frequency"][k] + 0.02           # temporal locality is learnt, not only popularity
+    # bundle -> online predictor (frozen) -> same scores as the trainer's weights
+    r = ExpertRidge(3, 40, 4)
+    r.load_weights(out)
+    assert r.refresh == 0 and np.allclose(r.w, np.load(out)["w"])
+    with pytest.raises(ValueError):
+        ExpertRidge(2, 40, 4).load_weights(out)
+    assert ept.main(["--traces", paths[-1], "--evaluate", out]) == 0
+    # the cache replay takes the bundle for its prefetcher
+    from layerstorm_b200.utils.cache_sim import read_trace
+    tr = read_trace(paths[-1])
+    a = simulate(tr, 10, prefetch_budget=2, predictor_weights=out)
+    b = simulate(tr, 10, prefetch_budget=0)
+    assert a["prefetched"] > 0 and a["misses"] <= b["misses"]

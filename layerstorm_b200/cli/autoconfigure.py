@@ -29,6 +29,15 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--hardware", help="JSON hardware descriptor to plan for instead of probing this machine")
     p.add_argument("--assume-gpus", type=int, default=None, help="plan for N B200 GPUs (no probe)")
     p.add_argument("--calibration", help="loader calibration or measured-peaks JSON: replaces the default bandwidths of the step-time model")
+    p.add_argument("--auto-run", action="store_true",
+                   help="the whole pipeline: calibrate this machine (or reuse a matching artifact), derive, train the copy constants on a short "
+                        "real decode, fit the expert placement table from it, derive again (autoconfig/pipeline.py)")
+    p.add_argument("--out-dir", default=".", help="--auto-run: where the configuration and the measured artifacts go")
+    p.add_argument("--reset", action="store_true", help="--auto-run: measure again even where a matching artifact exists")
+    p.add_argument("--trained", help="--auto-run: trained loader constants to reuse")
+    p.add_argument("--placement-table", help="--auto-run: demand-fetch table to carry instead of fitting one")
+    p.add_argument("--train-gen", type=int, default=100, help="--auto-run: tokens of the training decode")
+    p.add_argument("--serve-flag", action="append", default=[], help="--auto-run: extra flag of the training decode's server boot (e.g. --random-weights)")
     p.add_argument("--print", dest="show", action="store_true", help="print the explanation")
     p.add_argument("--probe-only", action="store_true", help="print what the model path is (format, shape, quantisation, size) and exit")
     return p
@@ -55,6 +64,16 @@ def main(argv: Optional[list[str]] = None) -> int:
             hw = synthetic(args.assume_gpus)
         else:
             hw = detect((base or {}).get("hardware", {}).get("nvme_paths"))
+        if args.auto_run:
+            from ..autoconfig.pipeline import AutoRunOptions, run_pipeline
+            rec = run_pipeline(shape, hw, Levers(args.vram_expert_ratio, args.total_active_context_tokens, args.prefer, args.accuracy),
+                               collect_pins(args.pin), base,
+                               AutoRunOptions(model=args.model, out_dir=args.out_dir, reset=args.reset, calibration=args.calibration, trained=args.trained,
+                                              placement_table=args.placement_table, train_gen=args.train_gen, serve_flags=args.serve_flag))
+            for st in rec["steps"]:
+                print("auto-run:", json.dumps(st))
+            print(f"wrote {rec['config']} and {rec['artifacts']['autorun']}")
+            return 0
         if args.calibration:
             from ..autoconfig.calibration import apply_calibration
             hw, notes = apply_calibration(hw, json.load(open(args.calibration)))

@@ -181,14 +181,32 @@ def build_engine(cfg: dict, shape: ModelConfig, ckpt: Optional[str], args: argpa
             dist.init_process_group("nccl", device_id=dev)
     kv_fmt = args.kv_format or {"fp8_e4m3": "fp8", "bf16": "bf16", "fp16": "bf16", "turboquant4": "tq4"}.get(cfg["quantization"]["kv_cache"], "fp8")
     want_mtp = bool(cfg["speculation"]["enabled"]) and cfg["speculation"]["method"] == "mtp"      # load the MTP block only when it drafts
+    # a derived configuration that keeps only part of every GPU's experts in HBM (autoconfig.vram_expert_ratio < 1): the rest lives in
+    # pinned host memory and streams into the slots; the model is loaded layer by layer so that it never has to fit in HBM as a whole
+    streamer = None
+    ratio = float((cfg.get("autoconfig") or {}).get("vram_expert_ratio") or 1.0)
+    if ratio < 1.0 and shape.n_routed > 0:
+        if world > 1:
+            log.warning("expert streaming is wired for one GPU per model; autoconfig.vram_expert_ratio = %.2f ignored with %d ranks", ratio, world)
+        else:
+            from ..runtime.streaming import ExpertStreamer
+            e_total = shape.n_routed + shape.n_shared
+            slots = max(shape.top_k + shape.n_shared, min(e_total, int(ratio * e_total)))
+            streamer = ExpertStreamer(None, slots_per_layer=slots, prefetch=True, cfg=shape, device=dev,
+                                      place_freq=cfg["memory"]["arena_placement"]["freq_table"] or None)
+            log.info("expert cache: %d of %d expert slots per MoE layer in HBM, the rest streams from pinned host memory", slots, e_total)
+    hook = streamer.add_layer if streamer is not None else None
     if ckpt and not args.random_weights:
         from ..models.checkpoint import open_checkpoint
         _, w = open_checkpoint(ckpt, shape)
-        model = DeviceModel.from_state_dict(shape, w, dev, kv_fmt, page, tp_rank=rank, tp_size=world, with_mtp=want_mtp)
+        model = DeviceModel.from_state_dict(shape, w, dev, kv_fmt, page, tp_rank=rank, tp_size=world, with_mtp=want_mtp, layer_hook=hook)
     else:
         log.warning("serving RANDOM weights of shape %s", shape.name)
         model = DeviceModel.random_init(shape, dev, kv_fmt, page, expert_slots="auto", embed_on_host=shape.vocab * shape.hidden > (1 << 28),
-                                        tp_rank=rank, tp_size=world, with_mtp=want_mtp)
+                                        tp_rank=rank, tp_size=world, with_mtp=want_mtp, layer_hook=hook)
+    if streamer is not None:
+        streamer.attach(model)
+        streamer.configure_eviction(cfg["memory"]["expert_cache"])
     max_ctx = sv["max_sequence_length"]
     if world > 1:
         from ..parallel.symm import PeerComm
@@ -203,7 +221,8 @@ def build_engine(cfg: dict, shape: ModelConfig, ckpt: Optional[str], args: argpa
     pages = cfg["memory"]["kv_cache"]["max_pages_per_gpu"]
     eng = Engine(model, max_seqs=sv["max_concurrent_requests"] + 4, max_ctx=max_ctx,
                  prefill_chunk=cfg["orchestrator"]["prefill_chunk_tokens"], max_batch=min(4, cfg["orchestrator"]["max_batch_size"]),
-                 num_pages=None if pages in ("auto", None) else int(pages), use_graph=cfg["compute"]["cuda_graphs"]["enabled"])
+                 num_pages=None if pages in ("auto", None) else int(pages),
+                 use_graph=cfg["compute"]["cuda_graphs"]["enabled"] and streamer is None)      # a streamed layer has a host wait: eager steps
     return eng
 
 

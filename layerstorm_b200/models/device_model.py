@@ -730,8 +730,10 @@ class DeviceModel:
     @classmethod
     def from_state_dict(cls, cfg: ModelConfig, w: Dict[str, torch.Tensor], device="cuda", kv_fmt="fp8", page=64,
                         expert_quant: Optional[str] = None, dense_quant: Optional[str] = None, tp_rank: int = 0,
-                        tp_size: int = 1, expert_shard: Optional[str] = None, with_mtp: bool = False) -> "DeviceModel":
-        """``with_mtp``: also load the checkpoint's multi-token-prediction blocks (one more decoder layer each, with its experts)
+                        tp_size: int = 1, expert_shard: Optional[str] = None, with_mtp: bool = False, layer_hook=None) -> "DeviceModel":
+        """``layer_hook(i, L)``: called after layer ``i`` of the main stack is built (``ExpertStreamer.add_layer`` moves the layer's
+        experts to pinned host memory there, so a model larger than HBM loads layer by layer).
+        ``with_mtp``: also load the checkpoint's multi-token-prediction blocks (one more decoder layer each, with its experts)
         for ``forward_mtp`` / ``Engine.enable_mtp``; ignored where ``mtp_supported()`` is false or the checkpoint has none."""
         m = cls(cfg, device, kv_fmt, page, tp_rank, tp_size, expert_shard)
         dev = m.device
@@ -838,14 +840,18 @@ class DeviceModel:
                 L["mlp_gu"] = QLinear.from_float(torch.cat([rows(w[f + "gate"], cfg.dense_inter, 1), rows(w[f + "up"], cfg.dense_inter, 1)], 0), dq, dev)
                 L["mlp_down"] = QLinear.from_float(cols(w[f + "down"], cfg.dense_inter, 1), dq, dev)
             (m.mtp_layers if is_mtp else m.layers).append(L)
+            if layer_hook is not None and not is_mtp:
+                layer_hook(i, L)
         m._finish()
         return m
 
     @classmethod
     def random_init(cls, cfg: ModelConfig, device="cuda", kv_fmt="fp8", page=64, seed=0, expert_slots=None,
                     embed_on_host: bool = False, reserve_bytes: int = 4 << 30, tp_rank: int = 0, tp_size: int = 1,
-                    expert_shard: Optional[str] = None, with_mtp: bool = False) -> "DeviceModel":
+                    expert_shard: Optional[str] = None, with_mtp: bool = False, layer_hook=None) -> "DeviceModel":
         """Random weights generated directly in storage format on the device (full-size models).
+        ``layer_hook(i, L)``: called after the expert arena of MoE layer ``i`` is filled (``ExpertStreamer.add_layer``: every arena is
+        then built with ALL of this rank's experts and handed over, whatever ``expert_slots`` says).
         ``expert_slots`` caps the routed-expert slots per MoE layer (VRAM expert cache): an int, None
         (all experts resident) or "auto" (as many as fit while leaving ``reserve_bytes`` of device
         memory free for caches and workspaces).  The first slots hold the shared experts followed by
@@ -948,6 +954,8 @@ class DeviceModel:
                 n_slots = max_owned
             else:
                 n_slots = min(max_owned, int(expert_slots) + cfg.n_shared)
+            if layer_hook is not None:
+                n_slots = max_owned
             m.expert_slots = n_slots
             for i, L in moe_layers:
                 # resident order: this rank's shared expert first, then its routed experts by id
@@ -959,6 +967,8 @@ class DeviceModel:
                 m._random_fill_arena(arena, eq, gloc)
                 arena.slot_of.copy_(so)
                 L["arena"] = arena
+                if layer_hook is not None and i < cfg.n_layers:
+                    layer_hook(i, L)
         m._finish()
         return m
 

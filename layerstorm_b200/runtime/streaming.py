@@ -33,12 +33,18 @@ from . import native as rt
 
 class ExpertStreamer:
     def __init__(self, model, slots_per_layer: int, policy: str = "impact_weighted_lru", waterline: int = 4, prefetch: bool = False,
-                 fetch_deadline_ms: Optional[float] = None, numa_node: int = -1, place_freq: Optional[str] = None):
+                 fetch_deadline_ms: Optional[float] = None, numa_node: int = -1, place_freq: Optional[str] = None,
+                 cfg=None, device=None):
         """Takes a fully resident ``DeviceModel`` (every MoE layer's arena holds all of this rank's experts), moves
-        the slot images to pinned host memory and shrinks every arena to ``slots_per_layer`` slots."""
-        from ..models.device_model import ExpertArena
-        self.model, self.dev = model, model.device
+        the slot images to pinned host memory and shrinks every arena to ``slots_per_layer`` slots.
+        With ``model = None`` (and ``cfg`` / ``device`` given) the streamer starts empty: pass :meth:`add_layer` as the ``layer_hook`` of
+        ``DeviceModel.from_state_dict`` / ``random_init`` so that every MoE layer is moved out as soon as it is built - the model then
+        never has to fit in HBM as a whole, only its resident part plus one layer's experts - and call :meth:`attach` at the end."""
+        self.model = model
+        self.cfg = cfg if cfg is not None else model.cfg
+        self.dev = torch.device(device) if device is not None else model.device
         self.slots = slots_per_layer
+        self.policy, self.numa_node = policy, numa_node
         self.copy_stream = torch.cuda.Stream(device=self.dev)
         self.te = rt.TransferEngine(n_gpus=1, levels=3, waterline=waterline)
         self.layers: Dict[int, dict] = {}
@@ -58,51 +64,69 @@ class ExpertStreamer:
         self._late: List[tuple] = []                              # copies that missed a deadline: (event, token, layer, expert, slot)
         self._slot_free_ev = None                                 # compute-stream event after the last expert kernels that read the slots
         self.h_ids = None
-        cfg = model.cfg
+        self._last_layer = -1
+        self._place_freq = place_freq or os.environ.get("LS_ARENA_PLACE_FREQ") or None
+        if model is not None:
+            for i, L in enumerate(model.layers):
+                self.add_layer(i, L)
+            self.attach(model)
+
+    def add_layer(self, i: int, L: dict):
+        """Move the experts of layer ``i`` (``L``: its entry of ``DeviceModel.layers``, arena fully resident) to pinned host memory and
+        replace the arena by one of ``slots_per_layer`` slots.  No-op for layers without experts."""
+        from ..models.device_model import ExpertArena
+        if "arena" not in L or L["arena"] is None:
+            return
+        cfg = self.cfg
         E_total = cfg.n_routed + cfg.n_shared
-        for i, L in enumerate(model.layers):
-            if "arena" not in L:
-                continue
-            old: ExpertArena = L["arena"]
-            so = old.slot_of.cpu().tolist()
-            mine = [e for e in range(E_total) if so[e] >= 0]
-            # backing store: the native host arena (NUMA-bound slab, page-locked with cudaHostRegister); plain pinned memory if the
-            # slab cannot be mapped or registered
-            harena = None
-            try:
-                harena = rt.HostArena(old.ef.stride, len(mine), numa_node=numa_node)
-                if not harena.pin():
-                    harena = None
-            except (MemoryError, OSError):
+        old: ExpertArena = L["arena"]
+        so = old.slot_of.cpu().tolist()
+        mine = [e for e in range(E_total) if so[e] >= 0]
+        # backing store: the native host arena (NUMA-bound slab, page-locked with cudaHostRegister); plain pinned memory if the
+        # slab cannot be mapped or registered
+        harena = None
+        try:
+            harena = rt.HostArena(old.ef.stride, len(mine), numa_node=self.numa_node)
+            if not harena.pin():
                 harena = None
-            host = harena.tensor() if harena is not None else torch.empty(len(mine), old.ef.stride, dtype=torch.uint8).pin_memory()
-            host_row = {}
-            for r, e in enumerate(mine):
-                if harena is not None:
-                    slot_h, _ = harena.begin_load(i, e)
-                    host[slot_h].copy_(old.data[so[e]])
-                    harena.finish_load(slot_h, True)
-                    host_row[e] = slot_h
-                else:
-                    host[r].copy_(old.data[so[e]])
-                    host_row[e] = r
-            n = min(slots_per_layer, len(mine))
-            assert n >= min(len(mine), cfg.top_k + cfg.n_shared), "the layer needs room for one token's experts"
-            new = ExpertArena(old.ef, n, E_total, self.dev)
-            L["arena"] = new
-            self.layers[i] = {"host": host, "host_row": host_row, "host_arena": harena, "cache": rt.ExpertCache(0, n, policy), "arena": new,
-                              "expert_stats": rt.ExpertStats(E_total),
-                              "slot_of_host": torch.full((E_total,), -1, dtype=torch.int32).pin_memory(),
-                              "present": torch.zeros(E_total, dtype=torch.int32, device=self.dev), "mine": set(mine), "pending": {}}
-            del old
+        except (MemoryError, OSError):
+            harena = None
+        host = harena.tensor() if harena is not None else torch.empty(len(mine), old.ef.stride, dtype=torch.uint8).pin_memory()
+        host_row = {}
+        for r, e in enumerate(mine):
+            if harena is not None:
+                slot_h, _ = harena.begin_load(i, e)
+                host[slot_h].copy_(old.data[so[e]])
+                harena.finish_load(slot_h, True)
+                host_row[e] = slot_h
+            else:
+                host[r].copy_(old.data[so[e]])
+                host_row[e] = r
+        n = min(self.slots, len(mine))
+        assert n >= min(len(mine), cfg.top_k + cfg.n_shared), "the layer needs room for one token's experts"
+        new = ExpertArena(old.ef, n, E_total, self.dev)
+        L["arena"] = new
+        self.layers[i] = {"host": host, "host_row": host_row, "host_arena": harena, "cache": rt.ExpertCache(0, n, self.policy), "arena": new,
+                          "expert_stats": rt.ExpertStats(E_total),
+                          "slot_of_host": torch.full((E_total,), -1, dtype=torch.int32).pin_memory(),
+                          "present": torch.zeros(E_total, dtype=torch.int32, device=self.dev), "mine": set(mine), "pending": {}}
+        del old
+        if self.model is None:
+            torch.cuda.synchronize(self.dev)                     # layer-by-layer loading: give the full arena back before the next layer is built
+            torch.cuda.empty_cache()
+
+    def attach(self, model):
+        """The model's MoE layers are all in: make this streamer the one its steps go through (and pre-warm from the configured
+        demand-fetch table)."""
+        self.model = model
         torch.cuda.synchronize(self.dev)
         torch.cuda.empty_cache()
         self._last_layer = max(self.layers) if self.layers else -1
         model.streamer = self
-        place_freq = place_freq or os.environ.get("LS_ARENA_PLACE_FREQ") or None
-        if place_freq:
+        if self._place_freq:
             from ..utils.loader_xray import read_freq_table
-            self.prewarm(read_freq_table(place_freq))
+            self.prewarm(read_freq_table(self._place_freq))
+        return self
 
     def prewarm(self, freq: Dict[tuple, int]) -> int:
         """Start with the most often FETCHED experts of every layer resident (``freq``: {(layer, expert): demand fetches}, the table

@@ -128,25 +128,28 @@ def simulate(trace: Trace, slots: int, policy: str = "impact_weighted_lru", weig
             close_step()
         last_step = step
         cache = caches[l]
-        locked = []
-        for e in ids:
-            if cache.is_ready(l, e):
-                hits += 1
-                if e in pending_prefetch[l]:
-                    useful_prefetch += 1
-            else:
-                misses += 1
-                per_step_miss[step] = per_step_miss.get(step, 0) + 1
-                if not admit(l, cache, e):
-                    raise RuntimeError(f"layer {l}: {slots} slots cannot hold one step's experts")
-                if decisions:
-                    decisions.write(f"M {step} {l} {e}\n")
-            pending_prefetch[l].discard(e)
-            cache.lock(l, e)
-            locked.append(e)
-        for e in locked:
-            cache.touch(l, e, 1.0 / max(len(ids), 1))
-            cache.unlock(l, e)
+        # a step that needs more experts than the layer has slots (a prefill chunk) runs in waves, as the streamer does: at most
+        # ``slots`` experts are locked at a time, the next wave may evict the previous one's
+        for w0 in range(0, max(len(ids), 1), slots):
+            locked = []
+            for e in ids[w0: w0 + slots]:
+                if cache.is_ready(l, e):
+                    hits += 1
+                    if e in pending_prefetch[l]:
+                        useful_prefetch += 1
+                else:
+                    misses += 1
+                    per_step_miss[step] = per_step_miss.get(step, 0) + 1
+                    if not admit(l, cache, e):
+                        raise RuntimeError(f"layer {l}: no slot of {slots} can be freed")
+                    if decisions:
+                        decisions.write(f"M {step} {l} {e}\n")
+                pending_prefetch[l].discard(e)
+                cache.lock(l, e)
+                locked.append(e)
+            for e in locked:
+                cache.touch(l, e, 1.0 / max(len(ids), 1))
+                cache.unlock(l, e)
         cache.end_step()
         if ridge is not None:
             routed_now[lid[l], : len(ids)] = ids[:top_k]

@@ -325,3 +325,60 @@ def test_schema_exports_and_check_cli(tmp_path, capsys):
     bad = tmp_path / "bad.json"
     bad.write_text(json.dumps({"serving": {"port": "x"}}))
     assert schema.main(["--check", str(bad)]) == 1
+
+
+def test_auto_run_pipeline_orders_reuses_and_carries_artifacts(tmp_path):
+    """calibrate -> derive -> train -> place -> derive with fake GPU steps: a model that does not fit runs all four, the second
+    invocation reuses both measured artifacts, --reset measures again, a model that fits stops after the derivation; the final
+    configuration names the trained constants and the placement table."""
+    import json
+    from layerstorm_b200.autoconfig import Levers, synthetic
+    from layerstorm_b200.autoconfig.pipeline import AutoRunOptions, Runners, run_pipeline
+    from layerstorm_b200.models.config import get_preset
+    from layerstorm_b200.utils.cache_sim import synthetic_trace, write_trace
+    calls = []
+
+    def calibrate(path):
+        calls.append("calibrate")
+        return {"version": 2, "h2d_gbs": 50.0}
+
+    def training_decode(config_path, ftrace, rtrace, log):
+        calls.append("train")
+        cfg = json.load(open(config_path))
+        assert cfg["gpu_loader"]["calibration_path"].endswith(".json") and cfg["autoconfig"]["vram_expert_ratio"] < 1.0
+        write_trace(rtrace, synthetic_trace(steps=30, layers=4, n_experts=64, top_k=8, seed=1))
+        with open(ftrace, "w") as fh:
+            for i in range(50):
+                n = 1 + i % 6
+                fh.write(f"W {i} {n} {n * (20 << 20)} {25.0 + n * (20 << 20) / 42e3:.1f}\n")       # 42 GB/s, 25 us per batch
+        return {"value": 7.5, "unit": "tok/s"}
+
+    runners = Runners(calibrate, training_decode)
+    big = get_preset("glm-5.2")                              # does not fit one GPU: experts stream
+    hw1 = synthetic(1)
+    opts = AutoRunOptions(model="glm-5.2", out_dir=str(tmp_path), train_gen=8)
+    rec = run_pipeline(big, hw1, Levers(), {}, None, opts, runners)
+    assert calls == ["calibrate", "train"]
+    names = [(s["step"], s["ran"]) for s in rec["steps"]]
+    assert names == [("calibrate", True), ("derive", True), ("train", True), ("place", True), ("derive", True)]
+    train = next(s for s in rec["steps"] if s["step"] == "train")
+    assert abs(train["h2d_gb_s"] - 42.0) < 0.5
+    cfg = json.load(open(rec["config"]))
+    assert cfg["gpu_loader"]["calibration_path"] == rec["artifacts"]["trained"]
+    assert cfg["memory"]["arena_placement"]["freq_table"] == rec["artifacts"]["placement"]
+    assert open(rec["artifacts"]["placement"]).read().count("\n") > 10
+    assert json.load(open(rec["artifacts"]["autorun"]))["fingerprint"] == rec["fingerprint"]
+    # again: both measured artifacts match this machine and model -> nothing runs on the GPU
+    rec2 = run_pipeline(big, hw1, Levers(), {}, None, opts, runners)
+    assert calls == ["calibrate", "train"]
+    assert [(s["step"], s["ran"]) for s in rec2["steps"]][:1] == [("calibrate", False)] and not any(s["ran"] for s in rec2["steps"] if s["step"] in ("train", "place"))
+    # other hardware: the artifacts do not match -> measured again; so does --reset
+    run_pipeline(big, synthetic(1, vram_gb=96.0), Levers(), {}, None, opts, runners)
+    assert calls == ["calibrate", "train", "calibrate", "train"]
+    run_pipeline(big, synthetic(1, vram_gb=96.0), Levers(), {}, None, AutoRunOptions(model="glm-5.2", out_dir=str(tmp_path), reset=True), runners)
+    assert calls[-2:] == ["calibrate", "train"] and len(calls) == 6
+    # a model that fits: no loader to train
+    calls.clear()
+    small = get_preset("tiny-mla-moe")
+    rec3 = run_pipeline(small, synthetic(1), Levers(), {}, None, AutoRunOptions(model="tiny-mla-moe", out_dir=str(tmp_path / "s")), runners)
+    assert calls == ["calibrate"] and [s["ran"] for s in rec3["steps"] if s["step"] in ("train", "place")] == [False, False]

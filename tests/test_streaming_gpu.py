@@ -78,3 +78,58 @@ def test_fetch_deadline_finishes_the_step_degraded_and_recovers():
         again.append(eng.decode([sid], [again[-1]])[0])
     assert again == ref
     assert not st._late and (stalled == 0 or s["degraded_steps"] >= 1)
+
+
+def test_layer_by_layer_loading_prewarm_and_fetch_trace(tmp_path, monkeypatch):
+    """The streamer as the model's layer hook: every MoE layer's experts leave HBM as soon as the layer is built (a model larger
+    than HBM loads this way), the steps give the resident model's tokens, a demand-fetch table pre-warms the cache, and the copy
+    batches land in the fetch trace with device times the cost-model fit can read."""
+    from layerstorm_b200.utils import loader_xray as lx
+    cfg = get_preset("tiny-mla-moe")
+    w = init_weights(cfg, 9)
+    prompt = torch.randint(0, cfg.vocab, (40,), generator=torch.Generator().manual_seed(4)).tolist()
+    m0 = DeviceModel.from_state_dict(cfg, w, "cuda", kv_fmt="bf16", page=16, expert_quant="bf16")
+    e0 = Engine(m0, max_seqs=1, max_ctx=128, prefill_chunk=8, max_batch=1, use_graph=False)
+    sid = e0.create_sequence()
+    ref = [e0.prefill(sid, prompt)]
+    for _ in range(5):
+        ref.append(e0.decode([sid], [ref[-1]])[0])
+
+    ftrace, rtrace = tmp_path / "fetch.txt", tmp_path / "routing.txt"
+    monkeypatch.setenv("LS_FETCH_TRACE", str(ftrace))
+    monkeypatch.setenv("LS_ROUTING_TRACE", str(rtrace))
+    slots = cfg.top_k + cfg.n_shared + 2
+
+    def run(place_freq=None):
+        st = ExpertStreamer(None, slots_per_layer=slots, prefetch=False, cfg=cfg, device="cuda", place_freq=place_freq)
+        built = []
+        hook = lambda i, L: (built.append((i, L["arena"].n_slots if "arena" in L else 0)), st.add_layer(i, L))
+        m = DeviceModel.from_state_dict(cfg, w, "cuda", kv_fmt="bf16", page=16, expert_quant="bf16", layer_hook=hook)
+        # at hook time each MoE layer still had its full arena; afterwards only the capped one is left
+        assert all(n in (0, cfg.n_routed + cfg.n_shared) for _, n in built) and len(built) == cfg.n_layers
+        assert all(L["arena"].n_slots == slots for L in m.layers if "arena" in L)
+        st.attach(m)
+        eng = Engine(m, max_seqs=1, max_ctx=128, prefill_chunk=8, max_batch=1, use_graph=False)
+        sid = eng.create_sequence()
+        got = [eng.prefill(sid, prompt)]
+        for _ in range(5):
+            got.append(eng.decode([sid], [got[-1]])[0])
+        return got, st
+
+    got, st = run()
+    assert got == ref
+    s = st.summary()                                       # also flushes the fetch trace
+    st.trace.close()
+    assert s["misses"] > 0
+    batches = lx.read_fetch_trace(str(ftrace))
+    assert len(batches) > 3 and (batches[:, 1] > 0).all() and (batches[:, 2] > 0).all()
+    assert int(batches[:, 1].sum()) == s["bytes_h2d"]
+    table = str(tmp_path / "freq.csv")
+    from layerstorm_b200.utils.cache_sim import read_trace
+    lx.write_freq_table(table, lx.fetch_counts([read_trace(str(rtrace))], slots, skip_steps=0), "test")
+    got2, st2 = run(place_freq=table)
+    assert got2 == ref
+    s2 = st2.summary()
+    assert s2["bytes_h2d"] > 0 and sum(len(l["host_row"]) for l in st2.layers.values()) > 0
+    # the pre-warmed run starts with the most-fetched experts resident: fewer demand misses than the cold run
+    assert s2["misses"] <= s["misses"]

@@ -287,3 +287,42 @@ def test_device_mtp_block_matches_the_reference_and_stays_in_step_through_specul
     assert eng.mtp_draft(child, tok) == eng.mtp_draft(sid, tok)
     low = eng.fork_sequence(sid, (eng.seq_len(sid) // 2))
     assert eng.mtp_draft(low, tok) == []
+
+
+def test_serve_streams_experts_when_the_configuration_keeps_part_of_them_in_hbm():
+    """``autoconfig.vram_expert_ratio`` < 1 in the configuration: the server's own boot path builds the expert streamer (layer by
+    layer), the engine runs eager steps through it and a request gives the tokens of the fully resident server."""
+    from layerstorm_b200.cli import serve
+    from layerstorm_b200.serving.orchestrator import InferenceRequest, SamplingParams
+
+    def boot(ratio):
+        args = serve.build_parser().parse_args(["--model", "tiny-mla-moe", "--random-weights", "--tokenizer-mode", "byte", "--max-concurrent", "2",
+                                                "--max-sequence-length", "256"])
+        cfg, shape, ckpt, _ = serve.resolve_config(args)
+        cfg["memory"]["kv_cache"]["page_size_tokens"] = 16
+        cfg.setdefault("autoconfig", {})["vram_expert_ratio"] = ratio
+        eng = serve.build_engine(cfg, shape, ckpt, args)
+        return shape, eng
+
+    prompt = [(7 * i + 3) % 500 + 4 for i in range(40)]
+
+    def tokens(eng):
+        sid = eng.create_sequence()
+        out = [eng.prefill(sid, prompt)]
+        for _ in range(6):
+            out.append(eng.decode([sid], [out[-1]])[0])
+        return out
+
+    shape, full = boot(1.0)
+    assert full.model.streamer is None
+    ref = tokens(full)
+    del full
+    torch.cuda.empty_cache()
+    shape, eng = boot(0.5)
+    st = eng.model.streamer
+    e_total = shape.n_routed + shape.n_shared
+    assert st is not None and not eng.use_graph and st.weighted
+    assert all(l["arena"].n_slots == max(shape.top_k + shape.n_shared, e_total // 2) for l in st.layers.values()) and len(st.layers) == shape.n_moe_layers()
+    assert tokens(eng) == ref
+    s = st.summary()
+    assert s["misses"] > 0 and s["bytes_h2d"] > 0

@@ -16,8 +16,10 @@ _FP4_MID = torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0])
 
 
 # ---------------------------------------------------------------- FP8 block-128
-def quantize_fp8_block(w: torch.Tensor, block: int = 128):
-    """w [N,K] float -> (uint8 e4m3 [N,K], fp32 scales [ceil(N/b), ceil(K/b)])."""
+def quantize_fp8_block(w: torch.Tensor, block: int = 128, pow2: bool = True):
+    """w [N,K] float -> (uint8 e4m3 [N,K], fp32 scales [ceil(N/b), ceil(K/b)]).  ``pow2``: scales rounded up to powers of two
+    (the UE8M0 scale convention of DeepSeek-V3.1+ FP8 checkpoints; lets the block-scaled tensor-core path take the weights as
+    they are - E4M3 is a floating-point format, so the rounding costs range, not relative precision)."""
     N, K = w.shape
     nb, kb = (N + block - 1) // block, (K + block - 1) // block
     wp = torch.zeros(nb * block, kb * block, dtype=torch.float32, device=w.device)
@@ -25,6 +27,8 @@ def quantize_fp8_block(w: torch.Tensor, block: int = 128):
     blocks = wp.view(nb, block, kb, block)
     amax = blocks.abs().amax(dim=(1, 3)).clamp_min(1e-12)
     scale = amax / 448.0
+    if pow2:
+        scale = torch.exp2(torch.ceil(torch.log2(scale)))
     q = (blocks / scale[:, None, :, None]).view(nb * block, kb * block)[:N, :K]
     q8 = q.contiguous().to(torch.float8_e4m3fn).view(torch.uint8)
     return q8, scale.contiguous()

@@ -168,6 +168,18 @@ class TcScratch:
         return cls._inst[idx]
 
 
+def fp8_scale_atoms(scales: torch.Tensor) -> Optional[torch.Tensor]:
+    """UE8M0 scale atoms of an FP8 matrix for the block-scaled tensor-core kernel from its fp32 128 x 128 block scales
+    (``[..., rows / 128, K / 128]``): every block becomes one 512-byte atom filled with the scale's exponent byte.  None when a
+    scale is not a positive power of two (the instruction's scales have no mantissa; DeepSeek-V3.1+ checkpoints store powers of
+    two, others stay on the fp16-operand path)."""
+    bits = scales.contiguous().view(torch.int32)
+    if bool(((bits & 0x7FFFFF) != 0).any()) or bool((bits <= 0).any()):
+        return None
+    e = ((bits >> 23) & 0xFF).to(torch.uint8)
+    return e.reshape(*e.shape[:-2], -1, 1).expand(*e.shape[:-2], e.shape[-2] * e.shape[-1], 512).contiguous()
+
+
 class QLinear:
     """A weight matrix [N, K] in a device storage format, applied to bf16 activations.
     Up to 4 rows (decode) stream the weights through the CUDA-core GEMV; larger row counts with
@@ -224,7 +236,8 @@ class QLinear:
             w = torch.empty(N, K, dtype=torch.uint8, device=device)
             w.random_(0, 256, generator=gen)
             w &= 0xBF   # keep |value| <= 1.875: clear the top exponent bit, never a NaN code
-            s = torch.full(((N + 127) // 128, (K + 127) // 128), std / 0.6, dtype=torch.float32, device=device)
+            # block scales are powers of two (the UE8M0 convention of DeepSeek-V3.1+ checkpoints): the nearest one to std / 0.6
+            s = torch.full(((N + 127) // 128, (K + 127) // 128), 2.0 ** round(math.log2(std / 0.6)), dtype=torch.float32, device=device)
             return QLinear("fp8_e4m3", N, K, w, s)
         if fmt == "nvfp4":
             w = torch.empty(N, K // 2, dtype=torch.uint8, device=device)
@@ -304,15 +317,22 @@ class QLinear:
     _bsbuf: Dict[tuple, tuple] = {}
 
     @classmethod
-    def _bs_operand(cls, device, rows: int, ntiles: int, K: int):
-        """Scratch for the NVFP4 image of a dense activation operand: packed values, scale atoms, per-row scales."""
-        key = (torch.device(device).index or 0, rows, ntiles, K)
+    def _bs_operand(cls, device, rows: int, ntiles: int, K: int, fp8: bool = False):
+        """Scratch for the NVFP4 (or FP8) image of a dense activation operand: packed values, scale atoms, per-row scales."""
+        key = (torch.device(device).index or 0, rows, ntiles, K, fp8)
         if key not in cls._bsbuf:
             if len(cls._bsbuf) > 64:
                 cls._bsbuf.clear()
-            cls._bsbuf[key] = (torch.zeros(rows, K // 2, dtype=torch.uint8, device=device),
-                               torch.zeros(ntiles * (K // 64) * 512, dtype=torch.uint8, device=device), torch.zeros(rows, device=device))
+            cls._bsbuf[key] = (torch.zeros(rows, K if fp8 else K // 2, dtype=torch.uint8, device=device),
+                               torch.zeros(ntiles * (K // (128 if fp8 else 64)) * 512, dtype=torch.uint8, device=device), torch.zeros(rows, device=device))
         return cls._bsbuf[key]
+
+    def bs_scale_atoms(self):
+        """FP8 weights: the UE8M0 scale atoms of this matrix (built once), or None when its block scales are not powers of two."""
+        if not hasattr(self, "_bs_wsf"):
+            self._bs_wsf = fp8_scale_atoms(self.scales.view(torch.float32).reshape((self.N + 127) // 128, (self.K + 127) // 128)) \
+                if (self.fmt == "fp8_e4m3" and self.N % 128 == 0 and self.K % 128 == 0) else None
+        return self._bs_wsf
 
     def dequant(self) -> torch.Tensor:
         if self.fmt in ("bf16", "f32"):
@@ -350,6 +370,15 @@ class QLinear:
             q, sf, al = QLinear._bs_operand(self.w.device, t["n"] * t["bn"], t["n"], self.K)
             nat.call("lsb_quant_nvfp4_tiles", x, 2, None, t["tr"], t["tn"], t["cnt"], 1, self.K, t["bn"], t["n"], q, sf, al)
             nat.call("lsb_gemm_nvfp4_bs", out, q, sf, al, self.w, self.scales, self.alpha, self.N, self.K, ldo, ob, t["tr"], t["tn"], t["cnt"],
+                     t["bn"], t["n"], TcScratch.get(self.w.device).err)
+        elif (self.fmt == "fp8_e4m3" and MOE_BLOCK_SCALED and M >= 16 and comm is None and bias is None and ldx == self.K and self.K % 128 == 0
+              and self.K <= 8192 and self.N % 128 == 0 and self.bs_scale_atoms() is not None):
+            # many rows over FP8 weights, block-scaled mode: the rows are quantised to FP8 with power-of-two group scales, both
+            # operands go to the tensor core as they are (kind::mxf8f6f4.block_scale)
+            t = QLinear._dense_tiles(self.w.device, M)
+            q, sf, al = QLinear._bs_operand(self.w.device, t["n"] * t["bn"], t["n"], self.K, fp8=True)
+            nat.call("lsb_quant_fp8_tiles", x, 2, None, t["tr"], t["tn"], t["cnt"], 1, self.K, t["bn"], t["n"], q, sf, al)
+            nat.call("lsb_gemm_fp8_bs", out, q, sf, al, self.w, self._bs_wsf, self.N, self.K, ldo, ob, t["tr"], t["tn"], t["cnt"],
                      t["bn"], t["n"], TcScratch.get(self.w.device).err)
         elif (self.fmt in ("fp8_e4m3", "nvfp4", "gguf_q4_k") and M >= 16 and comm is None and bias is None and ldx == self.K and self.K % 64 == 0
               and self.N % 128 == 0 and (self.fmt != "fp8_e4m3" or self.K % 128 == 0) and (self.fmt != "gguf_q4_k" or self.K % 256 == 0)):
@@ -428,6 +457,29 @@ class ExpertArena:
             put(ef.off_sg, gate.scales); put(ef.off_su, up.scales); put(ef.off_sd, down.scales)
         if ef.fmt == 2:
             put(ef.off_tail, torch.tensor([gate.alpha, up.alpha, down.alpha], dtype=torch.float32, device=v.device))
+
+    def bs_scale_atoms(self):
+        """FP8 arenas: (atoms [n_slots, bytes], byte offsets of the gate / up / down matrices' atoms) for the block-scaled
+        tensor-core kernel, derived once from the slots' 128 x 128 block scales; None when the format is another one, the
+        widths are not multiples of 128 or a scale is not a power of two.  Built from the slots as they are NOW: arenas whose
+        slots change (expert streaming) must not use it."""
+        if not hasattr(self, "_bs_wsf"):
+            self._bs_wsf = None
+            ef = self.ef
+            if ef.fmt == 1 and ef.H % 128 == 0 and ef.F % 128 == 0:
+                ngu, nd = (ef.F // 128) * (ef.H // 128), (ef.H // 128) * (ef.F // 128)
+                parts = []
+                for off, n, shape in ((ef.off_sg, ngu, (ef.F // 128, ef.H // 128)), (ef.off_su, ngu, (ef.F // 128, ef.H // 128)),
+                                      (ef.off_sd, nd, (ef.H // 128, ef.F // 128))):
+                    sc = self.data[:, off: off + 4 * n].contiguous().view(torch.float32).view(self.n_slots, *shape)
+                    a = fp8_scale_atoms(sc)
+                    if a is None:
+                        parts = None
+                        break
+                    parts.append(a.reshape(self.n_slots, -1))
+                if parts is not None:
+                    self._bs_wsf = (torch.cat(parts, 1).contiguous(), 0, ngu * 512, 2 * ngu * 512)
+        return self._bs_wsf
 
     def read_expert(self, slot: int, fmt: str):
         """Dequantised (gate, up, down) fp32 matrices of a slot (tests / oracle)."""
@@ -555,6 +607,11 @@ class Workspace:
                 # block-scaled path (NVFP4 experts): both operands stay 4-bit, the activations are quantised in tile order
                 fmts = {L["arena"].ef.fmt for L in m.layers if L.get("arena") is not None}
                 self.bs_can = fmts == {2} and H % 256 == 0 and m.Fe % 256 == 0 and H <= 8192 and m.Fe <= 8192
+                # ... or FP8 experts whose block scales are powers of two (FP8 activations with UE8M0 group scales); not with a capped
+                # expert cache, whose slots change under the scale atoms
+                self.bs_fp8 = (fmts == {1} and H % 128 == 0 and m.Fe % 128 == 0 and H <= 8192 and m.Fe <= 8192 and m.streamer is None
+                               and all(L["arena"].bs_scale_atoms() is not None for L in m.layers if L.get("arena") is not None))
+                self.bs_can = self.bs_can or self.bs_fp8
                 self.bs_ok = False
                 self._m, self._z = m, z
         # outputs
@@ -578,9 +635,10 @@ class Workspace:
         if on and not hasattr(self, "bs_xq"):
             rows = self.tc_tiles * self.tc_bn
             u8 = torch.uint8
-            self.bs_xq = z(rows, H // 2, dtype=u8); self.bs_xsf = z(self.tc_tiles * (H // 64) * 512, dtype=u8); self.bs_xa = z(rows)
+            vb, ak = (1, 128) if self.bs_fp8 else (2, 64)          # values per byte, reduction elements per scale atom
+            self.bs_xq = z(rows, H // vb, dtype=u8); self.bs_xsf = z(self.tc_tiles * (H // ak) * 512, dtype=u8); self.bs_xa = z(rows)
             self.bs_act = z(rows, m.Fe, dtype=torch.float16)
-            self.bs_aq = z(rows, m.Fe // 2, dtype=u8); self.bs_asf = z(self.tc_tiles * (m.Fe // 64) * 512, dtype=u8); self.bs_aa = z(rows)
+            self.bs_aq = z(rows, m.Fe // vb, dtype=u8); self.bs_asf = z(self.tc_tiles * (m.Fe // ak) * 512, dtype=u8); self.bs_aa = z(rows)
         if not on and not hasattr(self, "tc_xs"):
             P = self.tc_sorted.shape[0]
             self.tc_xs = z(P, H, dtype=torch.float16)
@@ -979,7 +1037,7 @@ class DeviceModel:
         elif eq == "fp8_e4m3":
             d[:, : ef.off_sg].random_(0, 256, generator=gen)
             d[:, : ef.off_sg] &= 0xBF
-            d[:, ef.off_sg: ef.off_tail].view(torch.float32).fill_(0.02 / 0.6)
+            d[:, ef.off_sg: ef.off_tail].view(torch.float32).fill_(2.0 ** -5)        # a power of two next to 0.02 / 0.6
         elif eq == "gguf_q4_k":
             blocks = d[:, : ef.off_tail].view(d.shape[0], -1, 144)
             blocks.random_(0, 256, generator=gen)
@@ -1138,8 +1196,8 @@ class DeviceModel:
             P = R * S
             nat.call("lsb_moe_tc_sort", ws.ids, P, E_total, ws.tc_bn, ws.tc_sorted, ws.tc_tile_e, ws.tc_tile_r0, ws.tc_tile_n, ws.tc_cnt)
             if ws.bs_ok:
-                nat.call("lsb_quant_nvfp4_tiles", ws.x, 0, ws.tc_sorted, ws.tc_tile_r0, ws.tc_tile_n, ws.tc_cnt, S, cfg.hidden, ws.tc_bn,
-                         min(ws.tc_tiles, P // ws.tc_bn + E_total + 1), ws.bs_xq, ws.bs_xsf, ws.bs_xa)
+                nat.call("lsb_quant_fp8_tiles" if ws.bs_fp8 else "lsb_quant_nvfp4_tiles", ws.x, 0, ws.tc_sorted, ws.tc_tile_r0, ws.tc_tile_n, ws.tc_cnt,
+                         S, cfg.hidden, ws.tc_bn, min(ws.tc_tiles, P // ws.tc_bn + E_total + 1), ws.bs_xq, ws.bs_xsf, ws.bs_xa)
             else:
                 nat.call("lsb_moe_tc_gather", ws.x, ws.tc_sorted, ws.tc_cnt, ws.tc_xs, P, S, cfg.hidden)
         elif mode == "groups":
@@ -1155,6 +1213,14 @@ class DeviceModel:
             P = R * S
             err = TcScratch.get(self.device).err
             tiles = min(ws.tc_tiles, P // ws.tc_bn + E_total + 1)
+            if ws.bs_ok and ws.bs_fp8:
+                wsf, og, ou, od = arena.bs_scale_atoms()
+                a = (arena.data, arena.slot_of, efp, wsf, wsf.shape[1], og, ou, od, ws.tc_tile_e, ws.tc_tile_r0, ws.tc_tile_n, ws.tc_cnt, ws.tc_sorted)
+                nat.call("lsb_moe_bs_ffn_fp8", 1, ws.bs_xq, ws.bs_xsf, ws.bs_xa, *a, ws.bs_act, ws.tc_bn, tiles, cfg.swiglu_limit, miss, err)
+                nat.call("lsb_quant_fp8_tiles", ws.bs_act, 1, None, ws.tc_tile_r0, ws.tc_tile_n, ws.tc_cnt, S, self.Fe, ws.tc_bn, tiles,
+                         ws.bs_aq, ws.bs_asf, ws.bs_aa)
+                nat.call("lsb_moe_bs_ffn_fp8", 0, ws.bs_aq, ws.bs_asf, ws.bs_aa, *a, ws.y, ws.tc_bn, tiles, 0.0, None, err)
+                return
             if ws.bs_ok:
                 a = (arena.data, arena.slot_of, efp, ws.tc_tile_e, ws.tc_tile_r0, ws.tc_tile_n, ws.tc_cnt, ws.tc_sorted)
                 nat.call("lsb_moe_bs_ffn", 1, ws.bs_xq, ws.bs_xsf, ws.bs_xa, *a, ws.bs_act, ws.tc_bn, tiles, cfg.swiglu_limit, miss, err)

@@ -92,29 +92,40 @@ def resident_bytes(mc: ModelConfig, tp: int = 1, n_gpus: int = 1, embed_on_host:
     db = QUANT_BITS.get(mc.dense_quant, 16.0) / 8
     H = mc.hidden
     r = ResidentBytes()
+    n = mc.hc_mult
     for i in range(mc.n_layers):
         if mc.is_kda_layer(i):
             C = mc.kda_heads * mc.kda_head_dim
-            sharded = 3 * C * H + C * H + 2 * C * mc.kda_rank          # q,k,v in; o out; low-rank B tails
+            sharded = 3 * C * H + C * H                                  # q, k, v in; o out (dense format)
             repl = 2 * mc.kda_rank * H + mc.kda_heads * H
             r.attention += int((sharded / tp + repl) * db)
+            # always bf16: the low-rank gate tails and their [W | W] copies for the chunk-parallel path (3 x each); fp32: short
+            # convolutions, dt bias, output norm, decay
+            r.attention += int((2 * 3 * C * mc.kda_rank * 2 + 3 * C * mc.kda_conv * 4 + C * 4 + mc.kda_heads * 4) / tp) + mc.kda_head_dim * 4
         else:
             q_in = (mc.q_lora * H + mc.n_heads * mc.qk_head * mc.q_lora / tp) if mc.q_lora else mc.n_heads * mc.qk_head * H / tp
             kv_a = (mc.kv_lora + mc.qk_rope) * H
-            kv_b = mc.n_heads * (mc.qk_nope + mc.v_head) * mc.kv_lora / tp
             o = H * mc.n_heads * mc.v_head / tp
             idx = 0
+            extra = (mc.q_lora + mc.kv_lora) * 4                         # fp32 norms of the two latents
             if mc.has_indexer and mc.index_source_layer(i) == i:
                 idx = mc.index_n_heads * mc.index_head_dim * (mc.q_lora or H) + (mc.index_head_dim + mc.index_n_heads) * H
-            r.attention += int((q_in + kv_a + kv_b + o + idx) * db)
+                extra += 2 * mc.index_head_dim * 4                       # key LayerNorm weight and bias
+                if mc.index_kpool > 1:
+                    idx += mc.index_head_dim * H                         # pooling gate projection
+                    extra += mc.index_kpool * mc.index_head_dim * 4      # pooled-position embedding
+            r.attention += int((q_in + kv_a + o + idx + 8 * H) * db)     # (+ the fused input projection's rows padded to 8)
+            r.attention += int(mc.n_heads * (mc.qk_nope + mc.v_head) * mc.kv_lora * 2 / tp) + extra      # W_UK / W_UV stay bf16
         if mc.is_moe_layer(i):
             r.router += mc.n_routed * H * 4 + mc.n_routed * 4
-            if mc.n_shared and i % n_gpus == 0:
-                pass
             r.shared_expert += int(mc.n_shared * expert_slot_bytes(mc) / n_gpus + 0.5)
         else:
             r.dense_ffn += int(3 * H * mc.dense_inter * db / tp)
-        r.norms += (2 + (mc.hc_mult * mc.hc_mult + 2 * mc.hc_mult) * mc.hc_mult * (1 if mc.mhc else 0)) * H * 4
+        r.norms += 2 * H * 4
+        if mc.mhc:
+            # two hyper-connection passes per layer: mixing matrix [(2n + n^2), n H] fp32, its base vector and three scales
+            r.norms += 2 * ((2 * n + n * n) * (n * H + 1) + 3) * 4
+    r.norms += H * 4                                                     # output norm
     r.embedding = 0 if embed_on_host else mc.vocab * H * 2
     r.head = int(mc.vocab * H * 2 / tp)
     return r

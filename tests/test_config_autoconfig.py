@@ -382,3 +382,41 @@ def test_auto_run_pipeline_orders_reuses_and_carries_artifacts(tmp_path):
     small = get_preset("tiny-mla-moe")
     rec3 = run_pipeline(small, synthetic(1), Levers(), {}, None, AutoRunOptions(model="tiny-mla-moe", out_dir=str(tmp_path / "s")), runners)
     assert calls == ["calibrate"] and [s["ran"] for s in rec3["steps"] if s["step"] in ("train", "place")] == [False, False]
+
+
+def test_engine_cross_check_table_semantics():
+    """Exact rows fail on any divergence, bound rows warn when the solver over-estimates and fail when it under-estimates, rows
+    without a figure are reported unchecked."""
+    from layerstorm_b200.autoconfig.enginecheck import CheckRow, render, run_checks
+
+    class Eng:
+        cfg = None
+
+    rows = [CheckRow("a", "B", "exact", 0.0, lambda mc, c: 100.0, lambda e: 100.0),
+            CheckRow("b", "B", "exact", 0.0, lambda mc, c: 101.0, lambda e: 100.0),
+            CheckRow("c", "B", "upper_bound", 0.1, lambda mc, c: 105.0, lambda e: 100.0),
+            CheckRow("d", "B", "upper_bound", 0.1, lambda mc, c: 130.0, lambda e: 100.0),
+            CheckRow("e", "B", "upper_bound", 0.1, lambda mc, c: 99.0, lambda e: 100.0),
+            CheckRow("f", "B", "exact", 0.0, lambda mc, c: None, lambda e: 1.0),
+            CheckRow("g", "B", "exact", 0.0, lambda mc, c: 1 / 0, lambda e: 1.0)]
+    res = run_checks(Eng(), ctx={}, rows=rows)
+    assert [r.status for r in res] == ["ok", "FAIL", "ok", "warning", "FAIL", "unchecked", "unchecked"]
+    assert "UNDER-estimates" in res[4].note and "ZeroDivisionError" in res[6].note
+    assert "quantity" in render(res) and "warning" in render(res)
+
+
+def test_solver_resident_bytes_bound_the_models_own_tensors():
+    """The sizing formula for the weights every GPU keeps (everything but the expert arenas) against the tensors the model really
+    builds: never below, and within 2 % above, for every tiny architecture (MLA, KDA + hyper-connections + pooled indexer, DSA)."""
+    from layerstorm_b200.autoconfig import sizing
+    from layerstorm_b200.models.config import get_preset
+    from layerstorm_b200.models.device_model import DeviceModel
+    from layerstorm_b200.models.weights import init_weights
+    for name in ("tiny-mla-moe", "tiny-glm5-next", "tiny-deepseek-v32"):
+        cfg = get_preset(name)
+        m = DeviceModel.from_state_dict(cfg, init_weights(cfg, 0), "cpu", kv_fmt="fp8", page=16)
+        arenas = [L["arena"] for L in m.layers if L.get("arena") is not None]
+        engine = m.weight_bytes() - sum(a.data.numel() for a in arenas) + m.embed.numel() * 2      # (the count skips a host-side embedding)
+        rb = sizing.resident_bytes(cfg, 1, 1, False)
+        solver = rb.total - rb.shared_expert
+        assert engine <= solver <= engine * 1.02, (name, engine, solver)

@@ -326,3 +326,23 @@ def test_serve_streams_experts_when_the_configuration_keeps_part_of_them_in_hbm(
     assert tokens(eng) == ref
     s = st.summary()
     assert s["misses"] > 0 and s["bytes_h2d"] > 0
+
+
+@pytest.mark.parametrize("name,kv", [("tiny-mla-moe", "bf16"), ("tiny-glm5-next", "fp8"), ("tiny-deepseek-v32", "fp8")])
+def test_solver_sizing_agrees_with_the_booted_engine(name, kv):
+    """The cross-check table of the autoconfig solver against a real engine: KV bytes per token, recurrent state per sequence and
+    the page count agree exactly, expert slot and resident weight bytes are never under-estimated."""
+    from layerstorm_b200.autoconfig.enginecheck import render, run_checks
+    from layerstorm_b200.models.config import get_preset
+    from layerstorm_b200.models.device_model import DeviceModel
+    from layerstorm_b200.models.weights import init_weights
+    from layerstorm_b200.runtime.engine import Engine
+    cfg = get_preset(name)
+    m = DeviceModel.from_state_dict(cfg, init_weights(cfg, 0), "cuda", kv_fmt=kv, page=16)
+    eng = Engine(m, max_seqs=3, max_ctx=256, prefill_chunk=32, max_batch=1)
+    res = run_checks(eng)
+    table = render(res)
+    by = {r.name: r for r in res}
+    assert not [r for r in res if r.status == "FAIL"], table
+    assert by["kv_bytes_per_token"].status == "ok" and by["kv_pages"].status == "ok", table
+    assert by["recurrent_state_bytes_per_sequence"].status == ("ok" if any(cfg.is_kda_layer(i) for i in range(cfg.n_layers)) else "unchecked"), table

@@ -291,6 +291,19 @@ def build_server(cfg: dict, shape: ModelConfig, ckpt: Optional[str], engine, arg
     tok = TokenizerWrapper(tpath, vocab_limit=getattr(engine, "vocab", None) or shape.vocab)
     pc = sv["prefix_cache"]
     pcc = PrefixCacheConfig(enabled=pc["enabled"] and pc["max_entries"] > 0, max_tokens=pc["max_cached_tokens"], max_holders=max(1, pc["max_entries"]))
+    pci = cfg.get("_internal-prefix_cache") or {}
+    target = getattr(engine, "_engine", engine)
+    if pcc.enabled and pci.get("hibernate_holders", False) and hasattr(target, "enable_kv_tiering") and int(os.environ.get("WORLD_SIZE", 1)) == 1:
+        # idle prefix holders leave HBM for pinned host memory, and from there for files under the spill directory
+        from ..serving.prefix_cache import PrefixSpillConfig
+        page = cfg["memory"]["kv_cache"]["page_size_tokens"]
+        try:
+            target.enable_kv_tiering(int(pci.get("cold_pages", 0)) or max(64, pc["max_cached_tokens"] // page + pcc.max_holders))
+            pcc.hibernate_holders = True
+            pcc.hibernate_idle_seconds = float(pci.get("hibernate_idle_seconds", 30.0))
+            pcc.spill = PrefixSpillConfig.from_config(cfg)
+        except (NotImplementedError, RuntimeError) as e:
+            log.warning("prefix holders stay in HBM: %s", e)
     eos = list(shape.eos_token_ids) or ([tok.eos_token_id] if getattr(tok, "eos_token_id", None) is not None else [])
     draft, depth = None, 0
     sp = cfg["speculation"]

@@ -14,6 +14,7 @@ measurements identified per-layer host round trips, not bandwidth, as the decode
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence
 
@@ -185,6 +186,12 @@ class Engine:
         return slot
 
     def free_sequence(self, sid: int):
+        if getattr(self, "spilled", None) and sid in self.spilled:
+            path, _ = self.spilled.pop(sid)
+            try:
+                os.remove(path)
+            except OSError:
+                pass
         if getattr(self, "hibernated", None) and sid in self.hibernated:
             self.hibernated.pop(sid)
             self.tier.destroy(sid)
@@ -221,6 +228,7 @@ class Engine:
         rolled back, so models with KDA layers only fork at the parent's full length."""
         if getattr(self.model, "dcp", None) is not None:
             raise NotImplementedError("not available with a sharded KV cache")
+        self._require_hot(parent)                 # a hibernated / spilled holder comes back to HBM before its pages are shared
         ps = self.seqs[parent]
         prefix_len = ps.length if prefix_len is None else prefix_len
         has_kda = any(self.cfg.is_kda_layer(i) for i in range(self.cfg.n_layers))
@@ -305,7 +313,74 @@ class Engine:
         with torch.cuda.stream(self.stream):
             self._sync_block_table(s)
 
+    # ------------------------------------------------------------------ second tiering hop: hibernated sequence -> file
+    def spill(self, sid: int, path: str) -> int:
+        """Write a HIBERNATED sequence's cold KV (and indexer) pages to ``path`` and give its pinned host slots back.  Returns the
+        bytes written.  The file is a cache entry, not a store: ``unspill`` raises when it is gone or damaged and the caller drops
+        the sequence.  Reference: CMD_SEQ_HIBERNATE spill=1 (python/orchestrator/orchestrator.py:455-484, the engine owns the byte moves)."""
+        import json
+        import struct
+        if sid not in getattr(self, "hibernated", {}):
+            raise RuntimeError("only a hibernated sequence can be spilled")
+        slots = self.hibernated[sid]
+        s = self.seqs[sid]
+        parts = [(("kv", i), t) for i, t in sorted(self.cold_kv.items())] + [(("idx", i), t) for i, t in sorted(self.cold_idx.items())]
+        head = json.dumps({"version": 1, "length": s.length, "pages": len(slots), "page": self.page,
+                           "tensors": [[k[0], k[1], list(t.shape[1:]), str(t.dtype)] for k, t in parts]}).encode()
+        idx = torch.tensor(slots, dtype=torch.long)
+        nbytes = 0
+        tmp = path + ".tmp"
+        with open(tmp, "wb") as fh:
+            fh.write(b"LSBSPILL" + struct.pack("<I", len(head)) + head)
+            for _, t in parts:
+                blob = t[idx].contiguous().view(torch.uint8).numpy().tobytes() if len(slots) else b""
+                fh.write(blob)
+                nbytes += len(blob)
+        os.replace(tmp, path)
+        self.tier.destroy(sid)                                                 # the pinned slots are free again
+        self.hibernated.pop(sid)
+        if not hasattr(self, "spilled"):
+            self.spilled: Dict[int, tuple] = {}
+        self.spilled[sid] = (path, len(slots))
+        return nbytes
+
+    def unspill(self, sid: int):
+        """Read a spilled sequence back into pinned host slots (it is then hibernated again; ``resume`` brings it to HBM).  Raises
+        OSError / ValueError when the file is missing, truncated or does not match this engine's cache geometry."""
+        import json
+        import struct
+        path, n = self.spilled[sid]
+        parts = [(("kv", i), t) for i, t in sorted(self.cold_kv.items())] + [(("idx", i), t) for i, t in sorted(self.cold_idx.items())]
+        with open(path, "rb") as fh:
+            if fh.read(8) != b"LSBSPILL":
+                raise ValueError(f"{path}: not a spill file")
+            (hl,) = struct.unpack("<I", fh.read(4))
+            head = json.loads(fh.read(hl))
+            want = [[k[0], k[1], list(t.shape[1:]), str(t.dtype)] for k, t in parts]
+            if head.get("pages") != n or head.get("page") != self.page or head.get("tensors") != want or head.get("length") != self.seqs[sid].length:
+                raise ValueError(f"{path}: written for another cache geometry or sequence")
+            if n > self.tier.free_cold_slots():
+                raise RuntimeError(f"cold pool full: need {n} pages, {self.tier.free_cold_slots()} free")
+            blobs = []
+            for _, t in parts:
+                per = t[0].numel() * t.element_size()
+                b = fh.read(n * per)
+                if len(b) != n * per:
+                    raise ValueError(f"{path}: truncated")
+                blobs.append(b)
+        self.tier.create(sid)
+        self.tier.demotion_candidates(sid, n * self.page + self.page)
+        slots = [self.tier.demote(sid, p) for p in range(n)]
+        idx = torch.tensor(slots, dtype=torch.long)
+        for (_, t), b in zip(parts, blobs):
+            if n:
+                t[idx] = torch.frombuffer(bytearray(b), dtype=torch.uint8).view(t.dtype).view(n, *t.shape[1:])
+        self.hibernated[sid] = slots
+        self.spilled.pop(sid)
+
     def _require_hot(self, sid: int):
+        if getattr(self, "spilled", None) and sid in self.spilled:
+            self.unspill(sid)
         if getattr(self, "hibernated", None) and sid in self.hibernated:
             self.resume(sid)
 

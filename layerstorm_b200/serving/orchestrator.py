@@ -213,8 +213,17 @@ class Orchestrator:
 
     # ---- main loop ----
     def run(self, idle_sleep_s: float = 0.0002):
+        last_sweep = 0.0
         while not self.stop_flag.is_set():
             if not self.step():
+                # nothing to serve: the idle-time tiering of prefix holders (HBM -> pinned host -> file), never on the request path
+                now = time.monotonic()
+                if now - last_sweep >= 1.0:
+                    last_sweep = now
+                    try:
+                        self.prefix.idle_sweep(now)
+                    except Exception as exc:  # noqa: BLE001 - housekeeping must not kill the serving loop
+                        self.last_sweep_error = f"{type(exc).__name__}: {exc}"
                 self.wake.wait(timeout=0.05)
                 self.wake.clear()
 

@@ -7,14 +7,41 @@ of ``grid`` tokens (or the exact prompt body), so cache ON and OFF run the same 
 give identical tokens.  Eviction is leaf-only, least-recently-used first, deepest first among
 equals; the token budget counts unique (edge) tokens.  Models with recurrent state (KDA) can only
 be forked at a holder's exact frontier.
+Tiering of idle holders (``idle_sweep``, called by the serving loop when it has nothing to do, never on the request path):
+first hop - a holder nobody hit for ``hibernate_idle_seconds`` moves its KV pages to pinned host memory (``Engine.hibernate``) and
+gives its HBM pages back; second hop - a hibernated LEAF holder idle for ``spill.idle_seconds`` is written to a file under
+``spill.path`` (``Engine.spill``), least recently used first, at most one per sweep, under a byte cap that is enforced BEFORE the
+write (over the cap: the least recently used spilled holder is dropped with its file, once).  The directory is a cache, never a
+store: its ``ls-spill-*.kvspill`` files are reclaimed at start-up, and a lost or unreadable file degrades to a cache MISS (the
+holder is dropped, the request prefills again).  An unwritable directory disables the second hop at boot, loudly.
 Reference: PrefixCache in python/orchestrator/orchestrator.py:598-643,804-1272 (radix tree of frozen
-holders, touch propagation, leaf-only LRU eviction, fork-with-evict-retry).
+holders, touch propagation, leaf-only LRU eviction, fork-with-evict-retry), PrefixSpillConfig :455-484 (cold spill policy).
 """
 from __future__ import annotations
 
+import glob
 import itertools
+import logging
+import os
+import time
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Tuple
+
+log = logging.getLogger("layerstorm_b200.prefix_cache")
+
+
+@dataclass
+class PrefixSpillConfig:
+    enabled: bool = False
+    path: str = "~/.layerstorm/prefix-cache"
+    max_mib: int = 32768
+    idle_seconds: float = 300.0
+
+    @classmethod
+    def from_config(cls, cfg: dict) -> "PrefixSpillConfig":
+        ps = (cfg or {}).get("_internal-prefix_spill") or {}
+        return cls(bool(ps.get("enabled", True)), str(ps.get("path", "~/.layerstorm/prefix-cache")), int(ps.get("max_mib", 32768)),
+                   float(ps.get("idle_seconds", 300.0)))
 
 
 @dataclass
@@ -24,6 +51,9 @@ class PrefixCacheConfig:
     max_tokens: int = 1 << 20         # budget over unique cached tokens
     max_holders: int = 64
     min_prefix: int = 64
+    hibernate_holders: bool = False   # idle holders move to pinned host memory (needs Engine.enable_kv_tiering)
+    hibernate_idle_seconds: float = 30.0
+    spill: Optional[PrefixSpillConfig] = None
 
 
 @dataclass
@@ -43,6 +73,23 @@ class PrefixCache:
         self.exact: Dict[Tuple[int, ...], Tuple[int, int]] = {}    # recurrent models: full prefix -> (holder, last_used)
         self._clock = itertools.count(1)
         self.hits = self.misses = self.hit_tokens = 0
+        self._hit_time: Dict[int, float] = {}                      # holder -> wall-clock time of its last hit / registration
+        self._spilled: Dict[int, Tuple[str, int]] = {}             # holder -> (file, bytes)
+        self.spill_stats = {"hibernated": 0, "spilled": 0, "spill_bytes": 0, "cap_evictions": 0, "lost_files": 0}
+        self.spill_dir: Optional[str] = None
+        sp = self.cfg.spill
+        if sp is not None and sp.enabled and self.cfg.hibernate_holders:
+            d = os.path.expanduser(sp.path)
+            try:
+                os.makedirs(d, exist_ok=True)
+                for f in glob.glob(os.path.join(d, "ls-spill-*.kvspill")):          # a cache, never a store: start empty
+                    os.remove(f)
+                probe = os.path.join(d, f".probe-{os.getpid()}")
+                open(probe, "wb").close()
+                os.remove(probe)
+                self.spill_dir = d
+            except OSError as e:
+                log.warning("prefix-cache spill DISABLED: %s is not writable (%s)", d, e)
 
     @property
     def recurrent(self) -> bool:
@@ -85,6 +132,7 @@ class PrefixCache:
                 self.misses += 1
                 return None, 0
             self.exact[best[0]] = (best[1], next(self._clock))
+            self._hit_time[best[1]] = time.monotonic()
             self.hits += 1
             self.hit_tokens += len(best[0])
             return best[1], len(best[0])
@@ -105,6 +153,7 @@ class PrefixCache:
             n = n.parent
         self.hits += 1
         self.hit_tokens += node.depth
+        self._hit_time[holder] = time.monotonic()
         return holder, node.depth
 
     def _nodes(self):
@@ -145,6 +194,7 @@ class PrefixCache:
             except Exception:  # noqa: BLE001 - caching is best effort
                 return None
             self.exact[key] = (h, next(self._clock))
+            self._hit_time[h] = time.monotonic()
             return h
         g = self.cfg.grid
         depth = (len(tokens) // g) * g
@@ -169,6 +219,7 @@ class PrefixCache:
             node.children[key] = ch
             node = ch
         node.holder, node.last_used = holder, t
+        self._hit_time[holder] = time.monotonic()
         return holder
 
     def fork_from(self, tokens: List[int]) -> Tuple[Optional[int], int]:
@@ -178,11 +229,103 @@ class PrefixCache:
             return None, 0
         for attempt in range(2):
             try:
-                return self.engine.fork_sequence(holder, n), n
+                sid = self.engine.fork_sequence(holder, n)
+                self._spilled.pop(holder, None)                     # (a spilled holder came back through the engine)
+                return sid, n
+            except (OSError, ValueError) as e:                     # its spill file is gone or unreadable: a cache miss, never a failure
+                log.warning("prefix holder %d lost its spill file (%s): dropped", holder, e)
+                self.spill_stats["lost_files"] += 1
+                self._drop_holder(holder)
+                self.hits -= 1
+                self.misses += 1
+                return None, 0
             except Exception:  # noqa: BLE001
                 if attempt or not self.evict_one(protect=holder):
                     break
         return None, 0
+
+    # ---- tiering of idle holders ----
+    def _holder_entries(self):
+        """(holder, logical last use, is a leaf) of every holder."""
+        if self.recurrent:
+            for k, (h, lu) in self.exact.items():
+                yield h, lu, True
+            return
+        for n in self._nodes():
+            if n.holder is not None:
+                yield n.holder, n.last_used, not n.children
+
+    def _drop_holder(self, holder: int):
+        self._spilled.pop(holder, None)
+        self._hit_time.pop(holder, None)
+        if self.recurrent:
+            for k, (h, _) in list(self.exact.items()):
+                if h == holder:
+                    del self.exact[k]
+        else:
+            for n in self._nodes():
+                if n.holder == holder:
+                    n.holder = None
+                    while n is not self.root and not n.children and n.holder is None:
+                        del n.parent.children[n.key]
+                        n = n.parent
+                    break
+        try:
+            self.engine.free_sequence(holder)
+        except Exception:  # noqa: BLE001 - the engine may already have dropped it
+            pass
+
+    def idle_sweep(self, now: Optional[float] = None) -> dict:
+        """One pass of the idle-time tiering policy (see the module text).  Returns what it did."""
+        eng = self.engine
+        did = {"hibernated": 0, "spilled": 0}
+        if not (self.cfg.enabled and self.cfg.hibernate_holders) or not hasattr(eng, "hibernated"):
+            return did
+        now = time.monotonic() if now is None else now
+        entries = sorted(self._holder_entries(), key=lambda t: t[1])
+        spilled_in_engine = getattr(eng, "spilled", {})
+        for h, _, _ in entries:                                     # first hop: idle holders leave HBM
+            if h in eng.hibernated or h in spilled_in_engine:
+                continue
+            if now - self._hit_time.get(h, now) >= self.cfg.hibernate_idle_seconds:
+                try:
+                    eng.hibernate(h)
+                    did["hibernated"] += 1
+                    self.spill_stats["hibernated"] += 1
+                except (RuntimeError, NotImplementedError):         # cold pool full / not available: stays hot
+                    break
+        sp = self.cfg.spill
+        if self.spill_dir is None or sp is None:
+            return did
+        cap = sp.max_mib << 20
+        for h, _, leaf in entries:                                  # second hop: at most one hibernated leaf per sweep, LRU first
+            if not leaf or h not in eng.hibernated or now - self._hit_time.get(h, now) < sp.idle_seconds:
+                continue
+            per_page = sum(t[0].numel() * t.element_size() for t in list(eng.cold_kv.values()) + list(eng.cold_idx.values()))
+            need = len(eng.hibernated[h]) * per_page
+            used = sum(b for _, b in self._spilled.values())
+            if used + need > cap:                                   # the cap is enforced before the write: drop the LRU spilled holder, once
+                victims = [x for x, _, _ in entries if x in self._spilled and x != h]
+                if not victims or need > cap:
+                    break
+                self._drop_holder(victims[0])
+                self.spill_stats["cap_evictions"] += 1
+                used = sum(b for _, b in self._spilled.values())
+                if used + need > cap:
+                    break
+            path = os.path.join(self.spill_dir, f"ls-spill-{os.getpid()}-{h}-{next(self._clock)}.kvspill")
+            try:
+                nbytes = eng.spill(h, path)
+            except OSError as e:
+                log.warning("prefix-cache spill failed (%s): second hop disabled", e)
+                self.spill_dir = None
+                break
+            self._spilled[h] = (path, nbytes)
+            did["spilled"] += 1
+            self.spill_stats["spilled"] += 1
+            self.spill_stats["spill_bytes"] += nbytes
+            break
+        return did
 
     def evict_one(self, protect: Optional[int] = None) -> bool:
         """Drop the least recently used leaf holder (deepest first among equals)."""
@@ -191,7 +334,10 @@ class PrefixCache:
             if not cands:
                 return False
             k = min(cands)[2]
-            self.engine.free_sequence(self.exact.pop(k)[0])
+            h = self.exact.pop(k)[0]
+            self._spilled.pop(h, None)
+            self._hit_time.pop(h, None)
+            self.engine.free_sequence(h)
             return True
         best = None
         for n in self._nodes():
@@ -201,6 +347,8 @@ class PrefixCache:
                 best = n
         if best is None:
             return False
+        self._spilled.pop(best.holder, None)
+        self._hit_time.pop(best.holder, None)
         self.engine.free_sequence(best.holder)
         best.holder = None
         n = best

@@ -349,3 +349,53 @@ def test_hash_layers_match_oracle_in_prefill_and_graph_decode(name):
     sid = eng.create_sequence()
     _, lg2 = eng.prefill(sid, ids[:T].tolist(), want_logits=True)
     assert rel_err(lg2, ref[T - 1]) > 1e-3
+
+
+@pytest.mark.parametrize("name", ["tiny-glm5-next", "tiny-deepseek-v32"])
+def test_spill_of_a_hibernated_sequence_to_a_file_is_bit_identical(name, tmp_path):
+    """Second tiering hop: a hibernated sequence's cold pages go to a file and its pinned host slots are free again; the next step
+    reads the file back, resumes and continues with the same tokens and logits.  A damaged or missing file raises (the caller drops
+    the sequence); freeing a spilled sequence removes its file."""
+    import os
+    cfg, m, _ = build(name, kv="fp8")
+    eng = Engine(m, max_seqs=3, max_ctx=128, prefill_chunk=16, max_batch=1, num_pages=12, use_graph=False)
+    eng.enable_kv_tiering(cold_pages=8)
+    g = torch.Generator().manual_seed(11)
+    pa = torch.randint(0, cfg.vocab, (70,), generator=g).tolist()
+
+    def run(spill):
+        a = eng.create_sequence()
+        ta = [eng.prefill(a, pa)]
+        if spill:
+            eng.hibernate(a)
+            free_cold = eng.tier.free_cold_slots()
+            path = str(tmp_path / f"a-{spill}.kvspill")
+            nbytes = eng.spill(a, path)
+            assert nbytes == os.path.getsize(path) - 12 - int.from_bytes(open(path, "rb").read(12)[8:], "little")
+            assert a in eng.spilled and a not in eng.hibernated and eng.tier.free_cold_slots() == free_cold + 5
+            with pytest.raises(RuntimeError):
+                eng.spill(a, path)                         # not hibernated any more
+        lgs = []
+        for _ in range(4):                                 # the first decode reads the file back and resumes the sequence
+            out, lg = eng.decode([a], [ta[-1]], return_logits=True)
+            ta.append(out[0]); lgs.append(lg[0].clone())
+        assert not getattr(eng, "spilled", {}) and not eng.hibernated
+        eng.free_sequence(a)
+        return ta, torch.stack(lgs)
+
+    t0, l0 = run(0)
+    t1, l1 = run(1)
+    assert t0 == t1 and torch.equal(l0, l1)
+    # a truncated file is refused, the sequence stays spilled; freeing it removes the file
+    b = eng.create_sequence()
+    eng.prefill(b, pa)
+    eng.hibernate(b)
+    path = str(tmp_path / "b.kvspill")
+    eng.spill(b, path)
+    blob = open(path, "rb").read()
+    open(path, "wb").write(blob[: len(blob) // 2])
+    with pytest.raises(ValueError):
+        eng.decode([b], [5])
+    assert b in eng.spilled
+    eng.free_sequence(b)
+    assert not os.path.exists(path)

@@ -284,3 +284,93 @@ def test_published_state_and_acceptance_statistics():
     assert st["generated_tokens"] == len(r.output_ids) == 12 and st["free_kv_pages"] > 0 and st["state_age_s"] < 60
     assert r.stats.spec_rounds > 0 and orch.acceptance.global_rate() > 0.9 and st["spec_acceptance_windowed"] > 0.9
     assert orch.acceptance.expected_tokens(3) > 3.0
+
+
+def test_idle_prefix_holders_hibernate_then_spill_under_a_byte_cap_and_a_lost_file_is_a_miss(tmp_path):
+    """The idle-time tiering policy of the prefix cache on a fake tiered engine: first hop after ``hibernate_idle_seconds``, second
+    hop (leaf holders only, LRU first, one per sweep) after ``spill.idle_seconds``, the byte cap enforced before the write by
+    dropping the LRU spilled holder, stale files reclaimed at start-up, a hit on a spilled holder brings it back, a lost file
+    degrades to a miss."""
+    import os
+    import torch
+    from layerstorm_b200.runtime.null_engine import NullEngine
+    from layerstorm_b200.serving.prefix_cache import PrefixCache, PrefixCacheConfig, PrefixSpillConfig
+
+    class Tiered(NullEngine):
+        def __init__(self, **kw):
+            super().__init__(**kw)
+            self.hibernated, self.spilled = {}, {}
+            self.cold_kv = {0: torch.zeros(1, 16, 19200, dtype=torch.uint8)}          # 300 KiB per page
+            self.cold_idx = {}
+
+        def hibernate(self, sid):
+            self.hibernated[sid] = list(range((self.seqs[sid].length + self.page - 1) // self.page))
+            return len(self.hibernated[sid])
+
+        def spill(self, sid, path):
+            n = len(self.hibernated.pop(sid)) * 16 * 19200
+            open(path, "wb").write(b"x")
+            self.spilled[sid] = (path, n)
+            return n
+
+        def fork_sequence(self, parent, prefix_len=None):
+            if parent in self.spilled:
+                open(self.spilled[parent][0], "rb").close()                             # OSError when the file is gone
+                self.spilled.pop(parent)
+            self.hibernated.pop(parent, None)
+            return super().fork_sequence(parent, prefix_len)
+
+        def free_sequence(self, sid):
+            if sid in self.spilled:
+                path = self.spilled.pop(sid)[0]
+                if os.path.exists(path):
+                    os.remove(path)
+            self.hibernated.pop(sid, None)
+            super().free_sequence(sid)
+
+    d = tmp_path / "spill"
+    d.mkdir()
+    (d / "ls-spill-999-1-1.kvspill").write_bytes(b"stale")
+    (d / "keep.txt").write_bytes(b"not ours")
+    eng = Tiered(max_seqs=16, max_ctx=512, page=16)
+    cfg = PrefixCacheConfig(grid=64, min_prefix=64, hibernate_holders=True, hibernate_idle_seconds=10.0,
+                            spill=PrefixSpillConfig(enabled=True, path=str(d), max_mib=2, idle_seconds=100.0))
+    pc = PrefixCache(eng, cfg)
+    assert pc.spill_dir == str(d) and not (d / "ls-spill-999-1-1.kvspill").exists() and (d / "keep.txt").exists()
+    prompts = [[100 * k + i % 50 for i in range(64)] for k in range(3)]
+    holders = []
+    for p in prompts:
+        sid = eng.create_sequence()
+        eng.prefill(sid, p)
+        holders.append(pc.register(sid, p))
+        eng.free_sequence(sid)
+    t0 = __import__("time").monotonic()
+    assert pc.idle_sweep(t0 + 1) == {"hibernated": 0, "spilled": 0}                    # nobody idle long enough
+    assert pc.idle_sweep(t0 + 20) == {"hibernated": 3, "spilled": 0} and set(eng.hibernated) == set(holders)
+    # second hop: one per sweep, LRU first; 4 pages of 300 KiB = 1.2 MB each under a 2 MiB cap -> the third spill drops the first
+    assert pc.idle_sweep(t0 + 200)["spilled"] == 1 and list(eng.spilled) == [holders[0]]
+    pc.idle_sweep(t0 + 201)
+    pc.idle_sweep(t0 + 202)
+    assert pc.spill_stats["cap_evictions"] >= 1 and holders[0] not in eng.seqs            # dropped with its file
+    assert sum(b for _, b in pc._spilled.values()) <= 2 << 20
+    assert len([f for f in os.listdir(d) if f.endswith(".kvspill")]) == len(pc._spilled)
+    # a hit on a spilled holder brings it back through the engine
+    spilled = next(iter(pc._spilled))
+    k = holders.index(spilled)
+    sid, n = pc.fork_from(prompts[k] + [7])
+    assert sid is not None and n == 64 and spilled not in pc._spilled and spilled not in eng.spilled
+    eng.free_sequence(sid)
+    # a lost file is a cache miss: the holder is dropped, the request will prefill
+    for h in list(eng.hibernated):
+        pc._hit_time[h] = t0
+    pc.idle_sweep(t0 + 500)
+    victim = next(iter(pc._spilled))
+    os.remove(pc._spilled[victim][0])
+    k = holders.index(victim)
+    misses = pc.misses
+    assert pc.fork_from(prompts[k] + [7]) == (None, 0)
+    assert pc.misses == misses + 1 and victim not in eng.seqs and pc.spill_stats["lost_files"] == 1
+    # an unwritable directory disables the second hop, the first still works
+    pc2 = PrefixCache(Tiered(max_seqs=4, max_ctx=256, page=16),
+                      PrefixCacheConfig(hibernate_holders=True, spill=PrefixSpillConfig(enabled=True, path="/proc/definitely/not/writable")))
+    assert pc2.spill_dir is None

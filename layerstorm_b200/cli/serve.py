@@ -192,14 +192,24 @@ def build_engine(cfg: dict, shape: ModelConfig, ckpt: Optional[str], args: argpa
             from ..runtime.streaming import ExpertStreamer
             e_total = shape.n_routed + shape.n_shared
             slots = max(shape.top_k + shape.n_shared, min(e_total, int(ratio * e_total)))
+            live = None
+            if ckpt and not args.random_weights and str(ckpt).endswith(".gguf") and shape.expert_quant == "gguf":
+                # a GGUF checkpoint: slot images of natively readable layers go from the file straight into the pinned store
+                from ..models.checkpoint import open_checkpoint
+                from ..runtime.live_gguf import LiveGgufExpertSource
+                try:
+                    live = LiveGgufExpertSource(open_checkpoint(ckpt, shape)[1], shape, threads=cfg["preprocessing"]["live_prepack_threads"] or 8)
+                except ValueError as e:
+                    log.warning("live GGUF expert source unavailable: %s", e)
             streamer = ExpertStreamer(None, slots_per_layer=slots, prefetch=True, cfg=shape, device=dev,
-                                      place_freq=cfg["memory"]["arena_placement"]["freq_table"] or None)
+                                      place_freq=cfg["memory"]["arena_placement"]["freq_table"] or None, live_source=live)
             log.info("expert cache: %d of %d expert slots per MoE layer in HBM, the rest streams from pinned host memory", slots, e_total)
     hook = streamer.add_layer if streamer is not None else None
     if ckpt and not args.random_weights:
         from ..models.checkpoint import open_checkpoint
         _, w = open_checkpoint(ckpt, shape)
-        model = DeviceModel.from_state_dict(shape, w, dev, kv_fmt, page, tp_rank=rank, tp_size=world, with_mtp=want_mtp, layer_hook=hook)
+        model = DeviceModel.from_state_dict(shape, w, dev, kv_fmt, page, tp_rank=rank, tp_size=world, with_mtp=want_mtp, layer_hook=hook,
+                                            skip_experts=streamer.covers if (streamer is not None and streamer.live_source is not None) else None)
     else:
         log.warning("serving RANDOM weights of shape %s", shape.name)
         model = DeviceModel.random_init(shape, dev, kv_fmt, page, expert_slots="auto", embed_on_host=shape.vocab * shape.hidden > (1 << 28),

@@ -788,8 +788,10 @@ class DeviceModel:
     @classmethod
     def from_state_dict(cls, cfg: ModelConfig, w: Dict[str, torch.Tensor], device="cuda", kv_fmt="fp8", page=64,
                         expert_quant: Optional[str] = None, dense_quant: Optional[str] = None, tp_rank: int = 0,
-                        tp_size: int = 1, expert_shard: Optional[str] = None, with_mtp: bool = False, layer_hook=None) -> "DeviceModel":
-        """``layer_hook(i, L)``: called after layer ``i`` of the main stack is built (``ExpertStreamer.add_layer`` moves the layer's
+                        tp_size: int = 1, expert_shard: Optional[str] = None, with_mtp: bool = False, layer_hook=None, skip_experts=None) -> "DeviceModel":
+        """``skip_experts(i) -> bool``: leave MoE layer ``i``'s expert arena unbuilt (``L["arena"] = None``) - the layer hook provides it
+        (an ``ExpertStreamer`` with a live GGUF source fills its pinned store from the file and creates the capped arena).
+        ``layer_hook(i, L)``: called after layer ``i`` of the main stack is built (``ExpertStreamer.add_layer`` moves the layer's
         experts to pinned host memory there, so a model larger than HBM loads layer by layer).
         ``with_mtp``: also load the checkpoint's multi-token-prediction blocks (one more decoder layer each, with its experts)
         for ``forward_mtp`` / ``Engine.enable_mtp``; ignored where ``mtp_supported()`` is false or the checkpoint has none."""
@@ -871,6 +873,14 @@ class DeviceModel:
                 if cfg.is_hash_layer(i):
                     L["tid2eid"] = w[mo + "tid2eid"].to(dev).to(torch.int32).contiguous()     # [vocab, top_k]
                 E_total = cfg.n_routed + cfg.n_shared
+                if skip_experts is not None and not is_mtp and ts == 1 and skip_experts(i):
+                    L["arena"] = None                     # provided by the layer hook
+                    m.layers.append(L)
+                    if layer_hook is not None:
+                        layer_hook(i, L)
+                    if L["arena"] is None:
+                        raise RuntimeError(f"layer {i}: the layer hook did not provide the expert arena it asked to skip")
+                    continue
                 mine = [e for e in range(E_total) if m.owns_expert(i, e)]
                 eq_l, eq_dn = eq, eq
                 if gguf_experts and mine:

@@ -34,7 +34,7 @@ from . import native as rt
 class ExpertStreamer:
     def __init__(self, model, slots_per_layer: int, policy: str = "impact_weighted_lru", waterline: int = 4, prefetch: bool = False,
                  fetch_deadline_ms: Optional[float] = None, numa_node: int = -1, place_freq: Optional[str] = None,
-                 cfg=None, device=None):
+                 cfg=None, device=None, live_source=None):
         """Takes a fully resident ``DeviceModel`` (every MoE layer's arena holds all of this rank's experts), moves
         the slot images to pinned host memory and shrinks every arena to ``slots_per_layer`` slots.
         With ``model = None`` (and ``cfg`` / ``device`` given) the streamer starts empty: pass :meth:`add_layer` as the ``layer_hook`` of
@@ -65,6 +65,9 @@ class ExpertStreamer:
         self._slot_free_ev = None                                 # compute-stream event after the last expert kernels that read the slots
         self.h_ids = None
         self._last_layer = -1
+        # GGUF checkpoints: slot images of covered layers come straight from the file into the pinned store (runtime/live_gguf.py);
+        # the model builder then leaves those layers' arenas to this streamer (``DeviceModel.from_state_dict(skip_experts=...)``)
+        self.live_source = live_source
         self._place_freq = place_freq or os.environ.get("LS_ARENA_PLACE_FREQ") or None
         if model is not None:
             for i, L in enumerate(model.layers):
@@ -75,6 +78,8 @@ class ExpertStreamer:
         """Move the experts of layer ``i`` (``L``: its entry of ``DeviceModel.layers``, arena fully resident) to pinned host memory and
         replace the arena by one of ``slots_per_layer`` slots.  No-op for layers without experts."""
         from ..models.device_model import ExpertArena
+        if L.get("arena") is None and self.live_source is not None and self.covers(i):
+            return self._add_layer_live(i, L)
         if "arena" not in L or L["arena"] is None:
             return
         cfg = self.cfg
@@ -114,6 +119,44 @@ class ExpertStreamer:
         if self.model is None:
             torch.cuda.synchronize(self.dev)                     # layer-by-layer loading: give the full arena back before the next layer is built
             torch.cuda.empty_cache()
+
+    def covers(self, i: int) -> bool:
+        """Whether layer ``i``'s experts can come straight from the checkpoint file (the model builder may skip its arena)."""
+        return self.live_source is not None and self.cfg.is_moe_layer(i) and self.live_source.layout(i) is not None
+
+    def _add_layer_live(self, i: int, L: dict):
+        """A covered layer: the host store is filled from the GGUF file, the device arena starts empty with ``slots`` slots."""
+        from ..models.device_model import ExpertArena
+        cfg = self.cfg
+        E_total = cfg.n_routed + cfg.n_shared
+        ef = self.live_source.layout(i)
+        mine = list(range(E_total))
+        harena = None
+        try:
+            harena = rt.HostArena(ef.stride, len(mine), numa_node=self.numa_node)
+            if not harena.pin():
+                harena = None
+        except (MemoryError, OSError):
+            harena = None
+        host = harena.tensor() if harena is not None else torch.empty(len(mine), ef.stride, dtype=torch.uint8).pin_memory()
+        host_row = {}
+        if harena is not None:
+            for e in mine:
+                host_row[e] = harena.begin_load(i, e)[0]
+        else:
+            host_row = {e: e for e in mine}
+        self.live_source.build_layer(i, mine, host, [host_row[e] for e in mine])
+        if harena is not None:
+            for e in mine:
+                harena.finish_load(host_row[e], True)
+        n = min(self.slots, len(mine))
+        assert n >= min(len(mine), cfg.top_k + cfg.n_shared), "the layer needs room for one token's experts"
+        new = ExpertArena(ef, n, E_total, self.dev)
+        L["arena"] = new
+        self.layers[i] = {"host": host, "host_row": host_row, "host_arena": harena, "cache": rt.ExpertCache(0, n, self.policy), "arena": new,
+                          "expert_stats": rt.ExpertStats(E_total),
+                          "slot_of_host": torch.full((E_total,), -1, dtype=torch.int32).pin_memory(),
+                          "present": torch.zeros(E_total, dtype=torch.int32, device=self.dev), "mine": set(mine), "pending": {}}
 
     def attach(self, model):
         """The model's MoE layers are all in: make this streamer the one its steps go through (and pre-warm from the configured

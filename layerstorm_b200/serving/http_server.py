@@ -80,6 +80,8 @@ class LayerStormServer:
         failed = self.failed_ranks() if getattr(self, "failed_ranks", None) else None
         if failed:
             return _error(503, "rank(s) down: " + "; ".join(f"{r}: {why}" for r, why in sorted(failed.items())), "server_error")
+        if getattr(self.orch, "gpu_fatal", None):
+            return _error(503, "gpu_fatal: " + self.orch.gpu_fatal, "server_error")
         # engine-side numbers come from the orchestrator's published state block (seqlock snapshot written by the serving thread)
         state = self.orch.published_state() if hasattr(self.orch, "published_state") else {}
         return {"status": "ok", "uptime_s": round(time.time() - self.started, 1), "queued": self.orch.queued(), "served": self.orch.served,
@@ -91,6 +93,8 @@ class LayerStormServer:
 
     # ---- admission ----
     def _admit(self):
+        if getattr(self.orch, "gpu_fatal", None):
+            return _error(503, "gpu_fatal: " + self.orch.gpu_fatal, "server_error")
         if self.inflight >= self.cfg.max_concurrent + self.cfg.max_queued_requests:
             return _error(503, "server busy: generation queue is full", "server_overloaded", {"Retry-After": str(self.cfg.retry_after_seconds)})
         self.inflight += 1

@@ -21,6 +21,25 @@ import torch
 from ..runtime.native import KvPoolExhausted
 from .prefix_cache import PrefixCache, PrefixCacheConfig
 
+import logging
+
+log = logging.getLogger("layerstorm_b200.orchestrator")
+
+_FATAL_MARKS = ("cuda error", "device-side assert", "illegal memory access", "illegal instruction", "unspecified launch failure",
+                "misaligned address", "an uncorrectable ecc", "device has fallen off", "gpu is lost", "cudaerrorlaunch", "xid ")
+
+
+def is_gpu_fatal(exc: BaseException) -> bool:
+    """Whether an exception of a step means the device context is gone (a sticky CUDA error), as opposed to an error of the request
+    (bad arguments, pool exhaustion, a bounded kernel wait that ran out - ``DeviceWaitError`` leaves the context usable).
+    Reference: CMP_GPU_FATAL, emitted once per GPU when an event query returns an error (src/daemon/dispatch_completion.cpp:60-85)."""
+    if type(exc).__name__ in ("AcceleratorError", "OutOfMemoryError") and "out of memory" in str(exc).lower():
+        return False                             # an allocation failure is reported to the request, the context lives on
+    if type(exc).__name__ == "DeviceWaitError":
+        return False
+    text = f"{type(exc).__name__}: {exc}".lower()
+    return type(exc).__name__ == "AcceleratorError" or any(m in text for m in _FATAL_MARKS)
+
 
 @dataclass
 class SamplingParams:
@@ -153,6 +172,7 @@ class Orchestrator:
         self.stop_flag = threading.Event()
         self.active: Optional[InferenceRequest] = None
         self.served = 0
+        self.gpu_fatal: Optional[str] = None      # set once by the first sticky device error; /health reports it, new work is refused
         # native statistics of the speculation rounds (global / windowed / per-request acceptance, expected tokens per round) and
         # a seqlock-published state block that other threads (the HTTP server's /health) read without taking the serving lock
         from ..runtime import native as _rt
@@ -187,6 +207,11 @@ class Orchestrator:
     # ---- thread-safe entry points ----
     def submit_request(self, req: InferenceRequest):
         req.stats.t_submit = time.time()
+        if self.gpu_fatal is not None:
+            # the device is gone: every step would fail the same way, so the request is refused at once with the recorded cause
+            req.error = f"gpu_fatal: {self.gpu_fatal}"
+            self._finish(req, "error")
+            return
         with self.lock:
             self.queue.append(req)
         self.wake.set()
@@ -238,6 +263,16 @@ class Orchestrator:
             self._generate(req)
         except Exception as exc:  # noqa: BLE001 - a failed request must not kill the serving loop
             req.error = f"{type(exc).__name__}: {exc}"
+            if is_gpu_fatal(exc) and self.gpu_fatal is None:
+                # a sticky device error (illegal access, launch failure, lost device): recorded ONCE, reported by /health, and every
+                # queued or later request is failed with it instead of being run into the same wall
+                self.gpu_fatal = req.error[:300]
+                log.error("GPU fatal error, serving stops accepting work: %s", self.gpu_fatal)
+                with self.lock:
+                    waiting, self.queue = list(self.queue), collections.deque()
+                for r in waiting:
+                    r.error = f"gpu_fatal: {self.gpu_fatal}"
+                    self._finish(r, "error")
             self._finish(req, "error")
         finally:
             with self.lock:

@@ -374,3 +374,66 @@ def test_idle_prefix_holders_hibernate_then_spill_under_a_byte_cap_and_a_lost_fi
     pc2 = PrefixCache(Tiered(max_seqs=4, max_ctx=256, page=16),
                       PrefixCacheConfig(hibernate_holders=True, spill=PrefixSpillConfig(enabled=True, path="/proc/definitely/not/writable")))
     assert pc2.spill_dir is None
+
+
+def test_a_sticky_device_error_is_recorded_once_and_stops_admission():
+    """Host-side injection: the engine's step raises what a lost CUDA context raises.  The failing request and everything queued
+    behind it end with the cause, /health turns 503, new requests are refused at once; an ordinary request error or a bounded
+    device wait that ran out does not trip it."""
+    from fastapi.testclient import TestClient
+    from layerstorm_b200.runtime.null_engine import NullEngine
+    from layerstorm_b200.serving.http_server import LayerStormServer, ServerConfig
+    from layerstorm_b200.serving.orchestrator import InferenceRequest, Orchestrator, SamplingParams, is_gpu_fatal
+    from layerstorm_b200.serving.tokenizer import TokenizerWrapper
+
+    class DeviceWaitError(RuntimeError):
+        pass
+
+    assert is_gpu_fatal(RuntimeError("CUDA error: an illegal memory access was encountered"))
+    assert is_gpu_fatal(RuntimeError("CUDA error: unspecified launch failure"))
+    assert not is_gpu_fatal(ValueError("prompt too long")) and not is_gpu_fatal(DeviceWaitError("all-reduce wait ran out (code 21)"))
+
+    class Flaky(NullEngine):
+        mode = None
+
+        def decode(self, sids, tokens, **kw):
+            if self.mode == "request":
+                self.mode = None
+                raise ValueError("bad request state")
+            if self.mode == "fatal":
+                raise RuntimeError("CUDA error: an illegal memory access was encountered")
+            return super().decode(sids, tokens, **kw)
+
+    eng = Flaky(vocab=300)
+    orch = Orchestrator(eng, eos_token_ids=[1])
+
+    import itertools
+    ids = itertools.count()
+
+    def req(n=4):
+        return InferenceRequest(f"r{next(ids)}", [5, 6, 7, 8], SamplingParams(max_tokens=n, ignore_eos=True))
+
+    eng.mode = "request"
+    r0 = req()
+    orch.submit_request(r0)
+    orch.step()
+    assert r0.error and orch.gpu_fatal is None                                   # an ordinary failure: the next request is served
+    r1 = req()
+    orch.submit_request(r1)
+    orch.step()
+    assert r1.error is None and len(r1.output_ids) == 4
+    eng.mode = "fatal"
+    r2, r3 = req(), req()
+    orch.submit_request(r2)
+    orch.submit_request(r3)
+    orch.step()
+    assert "illegal memory access" in r2.error and orch.gpu_fatal and r3.done.is_set() and r3.error.startswith("gpu_fatal")
+    assert orch.queued() == 0
+    r4 = req()
+    orch.submit_request(r4)                                                       # refused at once, never queued
+    assert r4.done.is_set() and r4.error.startswith("gpu_fatal") and orch.queued() == 0
+    server = LayerStormServer(orch, TokenizerWrapper(None, vocab_limit=300), ServerConfig(model_name="t"))
+    c = TestClient(server.app)
+    h = c.get("/health")
+    assert h.status_code == 503 and "gpu_fatal" in h.text
+    assert c.post("/v1/completions", json={"prompt": "hi", "max_tokens": 2}).status_code == 503

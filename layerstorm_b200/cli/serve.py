@@ -230,7 +230,8 @@ def build_engine(cfg: dict, shape: ModelConfig, ckpt: Optional[str], args: argpa
                                           chunk=int(cfg["memory"]["kv_cache"].get("dcp_chunk_size", 64))))
     pages = cfg["memory"]["kv_cache"]["max_pages_per_gpu"]
     eng = Engine(model, max_seqs=sv["max_concurrent_requests"] + 4, max_ctx=max_ctx,
-                 prefill_chunk=cfg["orchestrator"]["prefill_chunk_tokens"], max_batch=min(4, cfg["orchestrator"]["max_batch_size"]),
+                 prefill_chunk=cfg["orchestrator"]["prefill_chunk_tokens"],
+                 max_batch=max(1, min(32, cfg["orchestrator"]["max_batch_size"], sv["max_concurrent_requests"])),
                  num_pages=None if pages in ("auto", None) else int(pages),
                  use_graph=cfg["compute"]["cuda_graphs"]["enabled"] and streamer is None)      # a streamed layer has a host wait: eager steps
     return eng
@@ -324,7 +325,11 @@ def build_server(cfg: dict, shape: ModelConfig, ckpt: Optional[str], engine, arg
         depth = args.speculation_depth if args.speculation_depth is not None else pl["max_continuation_length"]
     elif sp["enabled"] and sp["method"] in ("dspark", "self_speculative", "mtp"):
         draft, depth = build_model_draft(cfg, shape, engine, args)
-    orch = Orchestrator(engine, eos_token_ids=eos, prefix_cache=pcc, draft=draft, speculation_depth=depth, tokenizer=tok)
+    # continuous batching: as many plain greedy requests decode together as the engine's batched step takes (its CUDA graphs are
+    # captured per batch size), bounded by the admitted concurrency
+    eng_batch = int(getattr(getattr(engine, "_engine", engine), "max_batch", 1) or 1)
+    batch = max(1, min(eng_batch, int(cfg["orchestrator"]["max_batch_size"]), int(sv["max_concurrent_requests"])))
+    orch = Orchestrator(engine, eos_token_ids=eos, prefix_cache=pcc, draft=draft, speculation_depth=depth, tokenizer=tok, max_batch=batch)
     rc = sv["reasoning_config"]
     if rc:
         rc = json.load(open(rc)) if os.path.exists(rc) else json.loads(rc)

@@ -159,8 +159,16 @@ class Orchestrator:
     ``propose(context_ids, gamma) -> List[int]`` (speculative decoding)."""
 
     def __init__(self, engine, eos_token_ids: Sequence[int] = (), prefix_cache: Optional[PrefixCacheConfig] = None,
-                 draft=None, speculation_depth: int = 0, tokenizer=None, governor: Optional[SpecRoundGovernor] = None):
+                 draft=None, speculation_depth: int = 0, tokenizer=None, governor: Optional[SpecRoundGovernor] = None, max_batch: int = 1):
+        """``max_batch`` > 1: continuous batching - up to that many plain greedy requests decode together, one engine step per token
+        of ALL of them; a request joins after its own prefill and leaves when it finishes, the others never wait for it.  Requests
+        that need more than the arg-max of a step (sampling on the host, log-probabilities, guided decoding, speculation) are
+        served one at a time between batches, in arrival order.  The reference serves one request at a time
+        (python/cli/serve.py:273 clamps the batch to 1); this is the serving form of the engine's batched decode step."""
         self.engine = engine
+        self.max_batch = max(1, int(max_batch))
+        self.running: List[list] = []             # continuous batching: [request, sequence id, next token to feed]
+        self.batched_steps = 0
         self.eos = set(int(t) for t in eos_token_ids)
         self.prefix = PrefixCache(engine, prefix_cache or PrefixCacheConfig())
         self.draft, self.gamma = draft, speculation_depth if draft is not None else 0
@@ -226,6 +234,10 @@ class Orchestrator:
             if self.active is not None and self.active.request_id == request_id:
                 self.active.cancelled.set()
                 return True
+            for r in self.running:
+                if r[0].request_id == request_id:
+                    r[0].cancelled.set()                  # leaves the batch at its next token
+                    return True
         return False
 
     def queued(self) -> int:
@@ -253,7 +265,10 @@ class Orchestrator:
                 self.wake.clear()
 
     def step(self) -> bool:
-        """Serve one queued request to completion; False when the queue is empty."""
+        """Serve one queued request to completion (``max_batch`` == 1), or advance the running batch by one token and admit one
+        waiting request (continuous batching); False when there is nothing to do."""
+        if self.max_batch > 1:
+            return self._step_batched()
         with self.lock:
             if not self.queue:
                 return False
@@ -279,6 +294,107 @@ class Orchestrator:
                 self.active = None
             self.served += 1
         return True
+
+    # ---- continuous batching ----
+    def _batchable(self, req: InferenceRequest) -> bool:
+        p = req.params
+        return p.greedy and p.logprobs == 0 and req.logit_mask is None and self.gamma == 0
+
+    def _fail(self, req: InferenceRequest, exc: BaseException):
+        req.error = f"{type(exc).__name__}: {exc}"
+        if is_gpu_fatal(exc) and self.gpu_fatal is None:
+            self.gpu_fatal = req.error[:300]
+            log.error("GPU fatal error, serving stops accepting work: %s", self.gpu_fatal)
+            with self.lock:
+                waiting, self.queue = list(self.queue), collections.deque()
+            for r in waiting:
+                r.error = f"gpu_fatal: {self.gpu_fatal}"
+                self._finish(r, "error")
+        self._finish(req, "error")
+        self.served += 1
+
+    def _step_batched(self) -> bool:
+        eng = self.engine
+        did = False
+        # 1. admission: at most one request per iteration (its prefill runs here, the batch waits one prefill, never a whole request)
+        with self.lock:
+            head = self.queue[0] if self.queue else None
+            take = head is not None and ((self._batchable(head) and len(self.running) < self.max_batch) or (not self._batchable(head) and not self.running))
+            if take:
+                self.queue.popleft()
+        if take:
+            did = True
+            if not self._batchable(head):
+                # needs its own decode arm: served alone, to completion, while no batch is running (arrival order is kept)
+                self.active = head
+                try:
+                    self._generate(head)
+                except Exception as exc:  # noqa: BLE001
+                    self._fail(head, exc)
+                else:
+                    self.served += 1
+                finally:
+                    self.active = None
+            else:
+                sid = None
+                try:
+                    sid, tok, done = self._start(head)
+                    if done:
+                        eng.free_sequence(sid)
+                        self._finish(head, head.finish_reason or "cancelled")
+                        self.served += 1
+                    else:
+                        self.running.append([head, sid, tok])
+                except Exception as exc:  # noqa: BLE001
+                    if sid is not None and sid in getattr(eng, "seqs", {}):
+                        eng.free_sequence(sid)
+                    self._fail(head, exc)
+        # 2. one token for every running request
+        if self.running:
+            did = True
+            sids, toks = [r[1] for r in self.running], [r[2] for r in self.running]
+            try:
+                outs = self._with_pool_evict_retry(self.running[0][0], lambda: eng.decode(sids, toks))
+            except Exception as exc:  # noqa: BLE001 - the step failed for the whole batch
+                for req, sid, _ in self.running:
+                    eng.free_sequence(sid)
+                    self._fail(req, exc)
+                self.running = []
+                return True
+            self.batched_steps += 1
+            keep = []
+            for entry, tok in zip(self.running, outs):
+                req, sid, _ = entry
+                if self._emit(req, int(tok), None):
+                    eng.free_sequence(sid)
+                    self._finish(req, req.finish_reason or ("cancelled" if req.cancelled.is_set() else "stop"))
+                    self.served += 1
+                else:
+                    entry[2] = int(tok)
+                    keep.append(entry)
+            self.running = keep
+        return did
+
+    def _start(self, req: InferenceRequest):
+        """Prefix lookup, prefill and first token of a greedy request: (sequence id, first token, finished already)."""
+        eng, st = self.engine, req.stats
+        st.t_start = time.time()
+        st.prompt_tokens = len(req.prompt_ids)
+        prompt = list(req.prompt_ids)
+        if not prompt:
+            raise ValueError("empty prompt")
+        sid, cached = self.prefix.fork_from(prompt)
+        if sid is None:
+            sid = self._with_pool_evict_retry(req, eng.create_sequence)
+            cached = 0
+        st.cached_tokens = cached
+        try:
+            tok = self._with_pool_evict_retry(req, lambda: eng.prefill(sid, prompt[max(cached, eng.seq_len(sid)):]))
+            self.prefix.register(sid, prompt)
+        except Exception:
+            eng.free_sequence(sid)
+            raise
+        return sid, tok, self._emit(req, tok, None)
 
     def _finish(self, req: InferenceRequest, reason: str):
         req.finish_reason = req.finish_reason or reason

@@ -437,3 +437,56 @@ def test_a_sticky_device_error_is_recorded_once_and_stops_admission():
     h = c.get("/health")
     assert h.status_code == 503 and "gpu_fatal" in h.text
     assert c.post("/v1/completions", json={"prompt": "hi", "max_tokens": 2}).status_code == 503
+
+
+def test_continuous_batching_gives_each_request_its_sequential_tokens():
+    """Plain greedy requests decode together (one engine step per token of all of them), join after their own prefill and leave
+    when they finish; every request gets exactly the tokens it gets when served alone; a request that needs its own decode arm
+    (log-probabilities) is served alone in arrival order; a cancelled request leaves the batch."""
+    import itertools
+    from layerstorm_b200.runtime.null_engine import NullEngine
+    from layerstorm_b200.serving.orchestrator import InferenceRequest, Orchestrator, SamplingParams
+    ids = itertools.count()
+
+    def make(n_prompt, n_gen, **kw):
+        prompt = [(13 * next(ids) + 7 * i) % 250 + 4 for i in range(n_prompt)]
+        return InferenceRequest(f"r{next(ids)}", prompt, SamplingParams(max_tokens=n_gen, ignore_eos=True, **kw))
+
+    specs = [(20, 9), (70, 3), (33, 14), (5, 1), (90, 6), (40, 11)]
+    reqs = [make(a, b) for a, b in specs]
+    seq = Orchestrator(NullEngine(vocab=300, max_seqs=16), eos_token_ids=[1])
+    want = []
+    for r in reqs:
+        c = InferenceRequest(r.request_id + "s", list(r.prompt_ids), r.params)
+        seq.submit_request(c)
+        seq.step()
+        want.append(list(c.output_ids))
+    eng = NullEngine(vocab=300, max_seqs=16)
+    orch = Orchestrator(eng, eos_token_ids=[1], max_batch=4)
+    for r in reqs[:5]:
+        orch.submit_request(r)
+    lp = make(12, 4, logprobs=2)                        # not batchable: waits for the batch to drain, then runs alone
+    orch.submit_request(lp)
+    orch.submit_request(reqs[5])
+    peak = 0
+    for _ in range(400):
+        if not orch.step():
+            break
+        peak = max(peak, len(orch.running))
+    assert all(r.done.is_set() and r.error is None for r in reqs + [lp])
+    assert [list(r.output_ids) for r in reqs] == want
+    assert len(lp.output_ids) == 4 and peak >= 3 and orch.served == 7 and not orch.running and len(eng.seqs) == orch.prefix.holders()
+    assert orch.batched_steps < sum(b for _, b in specs) - len(specs)            # tokens were produced together, not one request at a time
+    # the request behind the unbatchable one started only after it: arrival order is kept
+    assert lp.stats.t_done <= reqs[5].stats.t_first_token
+    # cancellation of a running request frees its sequence at its next token; the others go on
+    a, b = make(10, 50), make(10, 8)
+    orch.submit_request(a)
+    orch.submit_request(b)
+    for _ in range(4):
+        orch.step()
+    assert orch.cancel_request(a.request_id)
+    for _ in range(40):
+        if not orch.step():
+            break
+    assert a.done.is_set() and a.finish_reason == "cancelled" and len(a.output_ids) < 50 and len(b.output_ids) == 8 and len(eng.seqs) == orch.prefix.holders()

@@ -346,3 +346,30 @@ def test_solver_sizing_agrees_with_the_booted_engine(name, kv):
     assert not [r for r in res if r.status == "FAIL"], table
     assert by["kv_bytes_per_token"].status == "ok" and by["kv_pages"].status == "ok", table
     assert by["recurrent_state_bytes_per_sequence"].status == ("ok" if any(cfg.is_kda_layer(i) for i in range(cfg.n_layers)) else "unchecked"), table
+
+
+def test_continuous_batching_on_the_gpu_engine_matches_sequential_serving():
+    """Four concurrent greedy requests through the batched serving loop on the GPU engine (batched decode steps under CUDA graphs,
+    one per batch size) produce the tokens of the same requests served one at a time."""
+    from layerstorm_b200.serving.orchestrator import InferenceRequest, Orchestrator, SamplingParams
+    cfg, eng = _engine("tiny-glm5-next")
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(4, cfg.vocab, (n,), generator=g).tolist() for n in (20, 45, 33, 70)]
+    gens = [9, 4, 12, 6]
+
+    def serve(max_batch):
+        orch = Orchestrator(eng, eos_token_ids=[], max_batch=max_batch)
+        reqs = [InferenceRequest(f"b{max_batch}-{i}", list(p), SamplingParams(max_tokens=n, ignore_eos=True)) for i, (p, n) in enumerate(zip(prompts, gens))]
+        for r in reqs:
+            orch.submit_request(r)
+        for _ in range(200):
+            if not orch.step():
+                break
+        assert all(r.done.is_set() and r.error is None for r in reqs), [r.error for r in reqs]
+        orch.prefix.clear()
+        return [list(r.output_ids) for r in reqs], orch
+
+    want, _ = serve(1)
+    got, orch = serve(4)
+    assert got == want
+    assert 0 < orch.batched_steps < sum(gens) - len(gens)

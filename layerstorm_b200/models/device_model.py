@@ -569,6 +569,7 @@ class Workspace:
                 nbytes = int(nat.call("lsb_indexer_topk_split_scratch", R, self.max_entries))
                 self.topk_scratch = z((nbytes + 3) // 4, dtype=i32)         # zeroed once; every launch leaves it zeroed
             # tensor-core scoring of single-sequence chunks: the sequence's index keys as a dense bf16 operand + their scales
+            # (single-row decode steps stay on the CUDA-core kernel: at 262k entries it takes 88 us against 184 us for key gather + GEMM)
             self.idx_tc = (INDEXER_TC and R >= 64 and cfg.index_head_dim == 128 and 256 % cfg.index_n_heads == 0)
             if self.idx_tc:
                 self.idx_kbf_rows = (self.max_entries + 127) // 128 * 128

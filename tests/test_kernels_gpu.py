@@ -426,7 +426,7 @@ def test_many_row_fp32_matrix_runs_as_split_bf16_tensor_core_gemm():
     assert (few - out[:4]).abs().max().item() < 2e-5 * ref.abs().max().item()
 
 
-@pytest.mark.parametrize("R,IH,pos0", [(200, 32, 2000), (130, 4, 37), (70, 64, 900), (2048, 32, 6144)])
+@pytest.mark.parametrize("R,IH,pos0", [(200, 32, 2000), (130, 4, 37), (70, 64, 900), (2048, 32, 6144), (1, 32, 5000), (3, 64, 777)])
 def test_indexer_scores_on_tensor_cores_match_the_cuda_core_kernel(R, IH, pos0):
     """A single-sequence prefill chunk: the tcgen05 scoring (keys gathered to bf16, one GEMM, ReLU / head weights / head sum in the
     epilogue) against the one-thread-per-(row, entry) kernel on the same paged FP8 index cache, for every causal (row, entry)."""
@@ -460,6 +460,12 @@ def test_indexer_scores_on_tensor_cores_match_the_cuda_core_kernel(R, IH, pos0):
     assert torch.equal(out[~mask], ref[~mask])              # nothing written beyond a row's causal frontier
     d = (out[mask] - ref[mask]).abs().max().item()
     assert d < 2e-4 * ref[mask].abs().max().item() + 1e-6, d
+    if R <= 4:
+        # a decode step under a CUDA graph sizes the grids for the row's CAPACITY, not its fill: same scores, nothing beyond the fill
+        out2 = torch.full((R, ld), -7.0, device=DEV)
+        nat.call("lsb_indexer_score_tc", q, w, IH, cache, bt, n_pages, page_e, row_seq, ne, out2, ld, R, min(ld, kbf_rows), kbf, kbf_rows, ksc, err)
+        torch.cuda.synchronize()
+        assert int(err.item()) == 0 and torch.equal(out2, out)
 
 
 @pytest.mark.parametrize("P,budget,kind", [(4, 512, "normal"), (1, 2048, "normal"), (4, 512, "relu"), (4, 512, "const")])

@@ -159,6 +159,133 @@ __global__ void __launch_bounds__(192) indexer_score_tc_kernel(const __grid_cons
     pdl_launch_dependents();
 }
 
+
+// ---- few-row steps over long index rows: FP8 x FP8 straight over the cached keys ------------------------------------------------
+// A decode row scores every cached entry of its sequence: 262k entries at a 1M-token context, 88 us per indexer layer on the CUDA
+// cores (compute-bound: entries x heads x 128 FMAs).  Here the keys stay E4M3 as they sit in the paged cache - one TMA box per
+// cache page lands them in a 128-byte-swizzled [128 keys][128 bytes] tile, no gather, no conversion - the row's IH query heads are
+// quantised to E4M3 with one scale per head inside the CTA (written in the same swizzle by hand), and
+//   S[key][head] = k_fp8 . q_fp8     (tcgen05.mma kind::f8f6f4, M = 128 keys, N = IH, K = 128 in four instructions)
+// lands in tensor memory; the epilogue applies key scale x head scale, ReLU, the head weights and the sum over heads, one thread
+// per key.  One CTA per (128 entries, row); tiles above the row's fill exit at once, so a CUDA graph can size the grid for the
+// row's capacity.  The query loses mantissa (3 bits) against the bf16 form: the scores move by about a percent, which is the
+// precision FP8 indexers run at.
+constexpr int kF8MaxIH = 64;
+constexpr int kF8Smem = kScKeys * 128 + kF8MaxIH * 128 + 1024 /*align*/ + 64 /*barriers*/ + 2 * kF8MaxIH * 4;
+
+struct ScoreF8Params {
+    const bf16* q; const float* w;       // [rows, IH, 128], [rows, IH]
+    const uint8_t* cache; const int* block_table; int max_pages; int page; int total_pages;
+    const int* row_seq; const int* n_entries;
+    float* scores; int ld_scores; int rows; int IH; int npad;
+    int* err;
+};
+
+__global__ void __launch_bounds__(192) indexer_score_f8_kernel(const __grid_constant__ CUtensorMap map_c, ScoreF8Params p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* ktile = smem;                                   // [128 keys][128 B], 128-byte swizzle (written by TMA)
+    uint8_t* qtile = smem + kScKeys * 128;                   // [npad heads][128 B], same swizzle (written below)
+    uint64_t* full = reinterpret_cast<uint64_t*>(qtile + kF8MaxIH * 128);
+    uint64_t* acc_full = full + 1;
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(acc_full + 1);
+    float* qs = reinterpret_cast<float*>(qtile + kF8MaxIH * 128 + 64);      // [IH] head scale
+    float* wsm = qs + kF8MaxIH;                                             // [IH] head weight
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = blockIdx.y, k0 = blockIdx.x * kScKeys;
+    const uint32_t ncols = p.npad <= 32 ? 32u : 64u;        // tensor-memory allocations are powers of two
+
+    if (threadIdx.x == 0) {
+        mbar_init(full, 1); mbar_init(acc_full, 1);
+        fence_barrier_init();
+        fence_proxy_async();
+        tma_prefetch_desc(&map_c);
+    }
+    if (warp == 1) tmem_alloc(tmem_holder, ncols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_d = *tmem_holder;
+    pdl_wait();
+    pdl_launch_dependents();
+    const int seq = p.row_seq[r];
+    const int ne = seq < 0 ? 0 : p.n_entries[r];
+    const bool live = k0 < ne;                               // the whole CTA takes the same branch
+    if (live) {
+        // the row's heads -> E4M3 with one scale per head, in the operand's swizzle: 16-byte chunk c of row h sits at chunk c ^ (h & 7)
+        for (int h = warp; h < p.npad; h += 6) {
+            uint32_t packed = 0;
+            if (h < p.IH) {
+                const bf16* src = p.q + ((size_t)r * p.IH + h) * kScD + lane * 4;
+                const uint2 raw = *reinterpret_cast<const uint2*>(src);
+                const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x), b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+                const float2 fa = __bfloat1622float2(a), fb = __bfloat1622float2(b);
+                float m = fmaxf(fmaxf(fabsf(fa.x), fabsf(fa.y)), fmaxf(fabsf(fb.x), fabsf(fb.y)));
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+                const float sc = m > 0.f ? m * (1.f / 448.f) : 1.f, inv = 1.f / sc;
+                uint16_t lo, hi;
+                asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(fa.y * inv), "f"(fa.x * inv));
+                asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(fb.y * inv), "f"(fb.x * inv));
+                packed = (uint32_t)lo | ((uint32_t)hi << 16);
+                if (lane == 0) { qs[h] = sc; wsm[h] = p.w[(size_t)r * p.IH + h]; }
+            }
+            const int c = lane >> 2;
+            *reinterpret_cast<uint32_t*>(qtile + h * 128 + ((c ^ (h & 7)) << 4) + (lane & 3) * 4) = packed;
+        }
+        fence_proxy_async();                                 // the tensor core reads the tile through the async proxy
+    }
+    __syncthreads();
+    if (live) {
+        if (warp == 0 && lane == 0) {
+            // one box per cache page: `page` consecutive entries of 144 bytes, their first 128 bytes
+            mbar_expect_tx(full, kScKeys * 128);
+            const int boxes = kScKeys / p.page;
+            for (int j = 0; j < boxes; ++j) {
+                const int n = k0 + j * p.page;
+                int pg = n < ne ? p.block_table[(size_t)seq * p.max_pages + n / p.page] : 0;        // pages above the fill: any valid page, masked below
+                pg = pg < 0 ? 0 : (pg >= p.total_pages ? p.total_pages - 1 : pg);
+                tma_load_2d(ktile + j * p.page * 128, &map_c, full, 0, pg * p.page);
+            }
+        } else if (warp == 1 && lane == 0) {
+            const uint32_t idesc = idesc_f8(kScKeys, p.npad);
+            if (mbar_wait(full, 0, p.err, 33)) {
+                tc_fence_after();
+                const uint64_t da = smem_desc_sw128(ktile), db = smem_desc_sw128(qtile);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) umma_f8(tmem_d, da + 2 * k, db + 2 * k, idesc, k > 0 ? 1u : 0u);
+                umma_commit(acc_full);
+            }
+        } else if (warp >= 2) {
+            const int q = warp & 3;
+            const int n = k0 + q * 32 + lane;                                   // this thread's entry
+            float ks = 0.f;
+            if (n < ne) {
+                const int pg = p.block_table[(size_t)seq * p.max_pages + n / p.page];
+                ks = *reinterpret_cast<const float*>(p.cache + ((size_t)pg * p.page + n % p.page) * kScEntry + kScD);
+            }
+            const bool ok = mbar_wait_relaxed(acc_full, 0, p.err, 34);
+            tc_fence_after();
+            if (ok) {
+                float sum = 0.f;
+#pragma unroll 1
+                for (int c0 = 0; c0 < p.npad; c0 += 16) {
+                    float v[16];
+                    tmem_ld16(tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        if (c0 + j < p.IH) sum = fmaf(fmaxf(v[j] * ks * qs[c0 + j], 0.f), wsm[c0 + j], sum);
+                }
+                if (n < ne) p.scores[(size_t)r * p.ld_scores + n] = sum;
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_d, ncols);
+    pdl_launch_dependents();
+}
+
 }  // namespace lsb
 using namespace lsb;
 
@@ -187,6 +314,28 @@ LSB_API int lsb_indexer_score_tc(const void* q_idx, const void* w, int IH, const
     if (!attr) { cudaFuncSetAttribute(indexer_score_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kScSmem); attr = true; }
     const int rpt = kScN / IH;
     launch_pdl((indexer_score_tc_kernel), dim3(ne_pad / kScKeys, (rows + rpt - 1) / rpt), 192, kScSmem, st, mk, mq, p);
+    LSB_CHECK_LAUNCH();
+}
+
+// Scores of few-row steps (decode rows, each with its own sequence) over long index rows, FP8 x FP8 on the tensor cores (see
+// indexer_score_f8_kernel).  cache: [total_pages, page, 144] bytes; page (entries per page) in {8, 16, 32, 64, 128}; IH <= 64;
+// q_idx 8-byte aligned.  max_entries sizes the grid (a row's capacity); tiles above a row's fill exit.
+LSB_API int lsb_indexer_score_f8(const void* q_idx, const void* w, int IH, const void* cache, int total_pages, const void* block_table,
+                                 int max_pages, int page, const void* row_seq, const void* n_entries, void* scores, int ld_scores, int rows,
+                                 int max_entries, void* err, void* stream) {
+    if (IH <= 0 || IH > kF8MaxIH || rows <= 0 || total_pages <= 0 || ((uintptr_t)q_idx & 7) || ((uintptr_t)cache & 15)) return -1;
+    if (page < 8 || page > kScKeys || (page & (page - 1))) return -1;
+    if (max_entries <= 0) return 0;
+    CUtensorMap mc;
+    int rc = cached_map_2d(&mc, cache, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)total_pages * page, kScD, kScEntry, (uint32_t)page, kScD);
+    if (rc) return rc;
+    ScoreF8Params p;
+    p.q = (const bf16*)q_idx; p.w = (const float*)w; p.cache = (const uint8_t*)cache; p.block_table = (const int*)block_table;
+    p.max_pages = max_pages; p.page = page; p.total_pages = total_pages; p.row_seq = (const int*)row_seq; p.n_entries = (const int*)n_entries;
+    p.scores = (float*)scores; p.ld_scores = ld_scores; p.rows = rows; p.IH = IH; p.npad = (IH + 15) / 16 * 16; p.err = (int*)err;
+    static bool attr = false;
+    if (!attr) { cudaFuncSetAttribute(indexer_score_f8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kF8Smem); attr = true; }
+    launch_pdl((indexer_score_f8_kernel), dim3((max_entries + kScKeys - 1) / kScKeys, rows), 192, kF8Smem, (cudaStream_t)stream, mc, p);
     LSB_CHECK_LAUNCH();
 }
 

@@ -118,6 +118,10 @@ KDA_CHUNKED = os.environ.get("LSB_KDA_CHUNKED", "1") not in ("", "0")
 INDEXER_TC = os.environ.get("LSB_INDEXER_TC", "1") not in ("", "0")
 # steps of few rows over long index rows (more than TOPK_SPLIT_MIN_ENTRIES entries of capacity): the top-k of a row is spread
 # over many blocks (five small launches) instead of one block per row
+# few-row steps over long index rows (capacity of at least INDEXER_F8_MIN_ENTRIES entries): FP8 x FP8 scoring on the tensor cores
+# straight over the cached keys, the query heads quantised to E4M3 per head (scores move by about a percent)
+INDEXER_F8 = os.environ.get("LSB_INDEXER_F8", "1") not in ("", "0")
+INDEXER_F8_MIN_ENTRIES = int(os.environ.get("LSB_INDEXER_F8_MIN_ENTRIES", "32768"))
 TOPK_SPLIT = os.environ.get("LSB_TOPK_SPLIT", "1") not in ("", "0")
 TOPK_SPLIT_MIN_ENTRIES = 16384
 TOPK_SPLIT_MAX_ROWS = 64
@@ -569,7 +573,10 @@ class Workspace:
                 nbytes = int(nat.call("lsb_indexer_topk_split_scratch", R, self.max_entries))
                 self.topk_scratch = z((nbytes + 3) // 4, dtype=i32)         # zeroed once; every launch leaves it zeroed
             # tensor-core scoring of single-sequence chunks: the sequence's index keys as a dense bf16 operand + their scales
-            # (single-row decode steps stay on the CUDA-core kernel: at 262k entries it takes 88 us against 184 us for key gather + GEMM)
+            # (single-row decode steps do not use that path: at 262k entries key gather + GEMM take 184 us against 88 us on the CUDA cores)
+            pe = m.page // P
+            self.idx_f8 = (INDEXER_F8 and R < 64 and self.max_entries >= INDEXER_F8_MIN_ENTRIES and cfg.index_head_dim == 128
+                           and cfg.index_n_heads <= 64 and 8 <= pe <= 128 and pe & (pe - 1) == 0)
             self.idx_tc = (INDEXER_TC and R >= 64 and cfg.index_head_dim == 128 and 256 % cfg.index_n_heads == 0)
             if self.idx_tc:
                 self.idx_kbf_rows = (self.max_entries + 127) // 128 * 128
@@ -1312,6 +1319,11 @@ class DeviceModel:
                     nat.call("lsb_indexer_score_tc", ws.q_idx, ws.idx_w, cfg.index_n_heads, self.idx_cache[i], self.idx_block_table,
                              self.max_pages, self.page // P, ws.row_seq, ws.n_entries, ws.scores, ws.max_entries, R, ws.ne_hint,
                              ws.idx_kbf, ws.idx_kbf_rows, ws.idx_kscale, TcScratch.get(self.device).err)
+                elif getattr(ws, "idx_f8", False):
+                    # few rows over a long index row: FP8 x FP8 on the tensor cores straight over the cached keys
+                    nat.call("lsb_indexer_score_f8", ws.q_idx, ws.idx_w, cfg.index_n_heads, self.idx_cache[i], self.idx_cache[i].shape[0],
+                             self.idx_block_table, self.max_pages, self.page // P, ws.row_seq, ws.n_entries, ws.scores, ws.max_entries, R,
+                             ws.max_entries, TcScratch.get(self.device).err)
                 else:
                     nat.call("lsb_indexer_score", ws.q_idx, ws.idx_w, cfg.index_n_heads, self.idx_cache[i], self.idx_block_table,
                              self.max_pages, self.page // P, ws.row_seq, ws.n_entries, ws.scores, ws.max_entries, R, ws.max_entries)

@@ -502,3 +502,44 @@ def test_split_top_k_selection_equals_the_single_block_kernel(P, budget, kind):
     order = torch.sort(sc[r, :ne_list[r]], descending=True, stable=True).indices[:budget].sort().values
     got = ref_idx[r, : budget * P].view(budget, P)[:, 0] // P
     assert torch.equal(got.long(), order)
+
+
+@pytest.mark.parametrize("R,IH,page_e,ne_list", [(1, 32, 16, [5000]), (3, 64, 16, [777, 4100, 129]), (2, 32, 64, [3000, 2]), (1, 4, 8, [1000])])
+def test_fp8_indexer_scores_over_the_cached_keys_match_the_cuda_core_kernel(R, IH, page_e, ne_list):
+    """Few-row steps over long index rows: keys by TMA straight from the paged FP8 cache, query heads quantised to E4M3 per head,
+    tcgen05.mma kind::f8f6f4, scale / ReLU / head weights / head sum in the epilogue - against the CUDA-core kernel (bf16 queries)
+    over the same cache: within the query's FP8 rounding, nothing written beyond a row's fill, the same top entries."""
+    from layerstorm_b200.models.device_model import TcScratch
+    g = torch.Generator(device=DEV).manual_seed(R * 100 + IH)
+    ne = torch.tensor(ne_list, dtype=torch.int32, device=DEV)
+    ne_max = max(ne_list)
+    pages_per_seq = (ne_max + page_e - 1) // page_e + 1
+    n_pages = R * pages_per_seq + 3
+    cache = torch.zeros(n_pages, page_e, 144, dtype=torch.uint8, device=DEV)
+    cache[:, :, :128] = torch.randint(0, 256, (n_pages, page_e, 128), device=DEV, generator=g, dtype=torch.uint8) & 0x77   # finite e4m3
+    cache[:, :, 128:132] = (torch.rand(n_pages, page_e, 1, device=DEV, generator=g) * 0.05 + 0.01).view(torch.uint8)
+    bt = torch.randperm(n_pages, device=DEV, generator=g)[: R * pages_per_seq].int().view(R, pages_per_seq).contiguous()   # every sequence its own scattered pages
+    q = rnd(R, IH, 128).to(torch.bfloat16)
+    w = rnd(R, IH)
+    row_seq = torch.arange(R, dtype=torch.int32, device=DEV)
+    ld = (ne_max + 127) // 128 * 128 + 64
+    ref = torch.full((R, ld), -7.0, device=DEV)
+    out = torch.full((R, ld), -7.0, device=DEV)
+    nat.call("lsb_indexer_score", q, w, IH, cache, bt, pages_per_seq, page_e, row_seq, ne, ref, ld, R, ld)
+    err = TcScratch.get(DEV).err
+    err.zero_()
+    nat.call("lsb_indexer_score_f8", q, w, IH, cache, n_pages, bt, pages_per_seq, page_e, row_seq, ne, out, ld, R, ld, err)
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+    mask = torch.arange(ld, device=DEV)[None, :] < ne[:, None]
+    assert torch.equal(out[~mask], ref[~mask])              # nothing written beyond a row's fill
+    for r in range(R):
+        a, b = out[r, : ne_list[r]], ref[r, : ne_list[r]]
+        assert torch.isfinite(a).all()
+        # the query heads are rounded to E4M3 (3 mantissa bits): about a percent in RMS, a few percent of the largest score at worst
+        assert float((a - b).norm() / (b.norm() + 1e-9)) < 0.03, (r, float((a - b).norm() / b.norm()))
+        assert (a - b).abs().max().item() < 0.1 * b.abs().max().item() + 1e-6, (r, (a - b).abs().max().item(), b.abs().max().item())
+        if ne_list[r] >= 512:
+            k = 64
+            ta, tb = set(a.topk(k).indices.tolist()), set(b.topk(k).indices.tolist())
+            assert len(ta & tb) >= 0.8 * k, len(ta & tb)

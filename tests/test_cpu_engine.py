@@ -218,3 +218,25 @@ def test_expert_predictor_offline_training_beats_fixed_rankings_on_held_out_sequ
     a = simulate(tr, 10, prefetch_budget=2, predictor_weights=out)
     b = simulate(tr, 10, prefetch_budget=0)
     assert a["prefetched"] > 0 and a["misses"] <= b["misses"]
+
+
+def test_cpu_engine_runs_hash_layers_through_the_native_expert_kernels():
+    """A model whose first MoE layers route by the token-id table: the CPU engine (native expert kernels) gives the reference
+    model's tokens; the table, not the router's ranking, picks the experts."""
+    import dataclasses
+    import torch
+    from layerstorm_b200.models.config import get_preset
+    from layerstorm_b200.models.reference import Oracle
+    from layerstorm_b200.models.weights import init_weights, round_weights_bf16
+    from layerstorm_b200.runtime.cpu_engine import CpuEngine
+    cfg = dataclasses.replace(get_preset("tiny-mla-moe"), num_hash_layers=3)
+    w = round_weights_bf16(init_weights(cfg, 2))
+    prompt = torch.randint(0, cfg.vocab, (24,), generator=torch.Generator().manual_seed(3)).tolist()
+    ref = Oracle(cfg, w).greedy(prompt, 5)
+    eng = CpuEngine(cfg, w, native_experts=True)
+    sid = eng.create_sequence()
+    tok = eng.prefill(sid, prompt)
+    got = [tok]
+    for _ in range(4):
+        got.append(eng.decode([sid], [got[-1]])[0])
+    assert got == ref

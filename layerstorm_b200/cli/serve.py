@@ -329,7 +329,8 @@ def build_server(cfg: dict, shape: ModelConfig, ckpt: Optional[str], engine, arg
     # captured per batch size), bounded by the admitted concurrency
     eng_batch = int(getattr(getattr(engine, "_engine", engine), "max_batch", 1) or 1)
     batch = max(1, min(eng_batch, int(cfg["orchestrator"]["max_batch_size"]), int(sv["max_concurrent_requests"])))
-    orch = Orchestrator(engine, eos_token_ids=eos, prefix_cache=pcc, draft=draft, speculation_depth=depth, tokenizer=tok, max_batch=batch)
+    orch = Orchestrator(engine, eos_token_ids=eos, prefix_cache=pcc, draft=draft, speculation_depth=depth, tokenizer=tok, max_batch=batch,
+                        prefill_slice_tokens=4 * int(cfg["orchestrator"]["prefill_chunk_tokens"]))
     rc = sv["reasoning_config"]
     if rc:
         rc = json.load(open(rc)) if os.path.exists(rc) else json.loads(rc)

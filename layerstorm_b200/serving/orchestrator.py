@@ -159,7 +159,8 @@ class Orchestrator:
     ``propose(context_ids, gamma) -> List[int]`` (speculative decoding)."""
 
     def __init__(self, engine, eos_token_ids: Sequence[int] = (), prefix_cache: Optional[PrefixCacheConfig] = None,
-                 draft=None, speculation_depth: int = 0, tokenizer=None, governor: Optional[SpecRoundGovernor] = None, max_batch: int = 1):
+                 draft=None, speculation_depth: int = 0, tokenizer=None, governor: Optional[SpecRoundGovernor] = None, max_batch: int = 1,
+                 prefill_slice_tokens: int = 0):
         """``max_batch`` > 1: continuous batching - up to that many plain greedy requests decode together, one engine step per token
         of ALL of them; a request joins after its own prefill and leaves when it finishes, the others never wait for it.  Requests
         that need more than the arg-max of a step (sampling on the host, log-probabilities, guided decoding, speculation) are
@@ -169,6 +170,12 @@ class Orchestrator:
         self.max_batch = max(1, int(max_batch))
         self.running: List[list] = []             # continuous batching: [request, sequence id, next token to feed]
         self.batched_steps = 0
+        # continuous batching: a joining request's prompt is prefilled in slices of this many tokens, one slice between two decode
+        # steps of the running batch, so the others wait for a slice (tens of milliseconds), not for a whole long prompt (seconds);
+        # 0 = four of the engine's prefill chunks
+        self.prefill_slice = int(prefill_slice_tokens) or 4 * int(getattr(getattr(engine, "_engine", engine), "prefill_chunk", 0) or 2048)
+        self.joining: Optional[list] = None       # [request, sequence id, prompt, tokens already in the sequence]
+        self.prefill_slices = 0
         self.eos = set(int(t) for t in eos_token_ids)
         self.prefix = PrefixCache(engine, prefix_cache or PrefixCacheConfig())
         self.draft, self.gamma = draft, speculation_depth if draft is not None else 0
@@ -234,9 +241,9 @@ class Orchestrator:
             if self.active is not None and self.active.request_id == request_id:
                 self.active.cancelled.set()
                 return True
-            for r in self.running:
+            for r in self.running + ([self.joining] if self.joining is not None else []):
                 if r[0].request_id == request_id:
-                    r[0].cancelled.set()                  # leaves the batch at its next token
+                    r[0].cancelled.set()                  # leaves the batch at its next token (a joining request: after its current slice)
                     return True
         return False
 
@@ -316,39 +323,58 @@ class Orchestrator:
     def _step_batched(self) -> bool:
         eng = self.engine
         did = False
-        # 1. admission: at most one request per iteration (its prefill runs here, the batch waits one prefill, never a whole request)
-        with self.lock:
-            head = self.queue[0] if self.queue else None
-            take = head is not None and ((self._batchable(head) and len(self.running) < self.max_batch) or (not self._batchable(head) and not self.running))
+        # 1. admission: one request joins at a time; its prompt is prefilled slice by slice, one slice per iteration
+        if self.joining is None:
+            with self.lock:
+                head = self.queue[0] if self.queue else None
+                take = head is not None and ((self._batchable(head) and len(self.running) < self.max_batch) or (not self._batchable(head) and not self.running))
+                if take:
+                    self.queue.popleft()
             if take:
-                self.queue.popleft()
-        if take:
-            did = True
-            if not self._batchable(head):
-                # needs its own decode arm: served alone, to completion, while no batch is running (arrival order is kept)
-                self.active = head
-                try:
-                    self._generate(head)
-                except Exception as exc:  # noqa: BLE001
-                    self._fail(head, exc)
+                did = True
+                if not self._batchable(head):
+                    # needs its own decode arm: served alone, to completion, while no batch is running (arrival order is kept)
+                    self.active = head
+                    try:
+                        self._generate(head)
+                    except Exception as exc:  # noqa: BLE001
+                        self._fail(head, exc)
+                    else:
+                        self.served += 1
+                    finally:
+                        self.active = None
                 else:
+                    try:
+                        self.joining = self._begin(head)
+                    except Exception as exc:  # noqa: BLE001
+                        self._fail(head, exc)
+        if self.joining is not None:
+            did = True
+            req, sid, prompt, _ = self.joining
+            try:
+                done_prefill, tok = self._prefill_slice(self.joining)
+                if req.cancelled.is_set():
+                    eng.free_sequence(sid)
+                    self._finish(req, "cancelled")
                     self.served += 1
-                finally:
-                    self.active = None
-            else:
-                sid = None
-                try:
-                    sid, tok, done = self._start(head)
-                    if done:
+                    self.joining = None
+                elif done_prefill:
+                    self.joining = None
+                    self.prefix.register(sid, prompt)
+                    if self._emit(req, tok, None):
                         eng.free_sequence(sid)
-                        self._finish(head, head.finish_reason or "cancelled")
+                        self._finish(req, req.finish_reason or "cancelled")
                         self.served += 1
                     else:
-                        self.running.append([head, sid, tok])
-                except Exception as exc:  # noqa: BLE001
-                    if sid is not None and sid in getattr(eng, "seqs", {}):
+                        self.running.append([req, sid, tok])
+            except Exception as exc:  # noqa: BLE001
+                self.joining = None
+                if sid in getattr(eng, "seqs", {sid: None}):
+                    try:
                         eng.free_sequence(sid)
-                    self._fail(head, exc)
+                    except Exception:  # noqa: BLE001
+                        pass
+                self._fail(req, exc)
         # 2. one token for every running request
         if self.running:
             did = True
@@ -375,8 +401,8 @@ class Orchestrator:
             self.running = keep
         return did
 
-    def _start(self, req: InferenceRequest):
-        """Prefix lookup, prefill and first token of a greedy request: (sequence id, first token, finished already)."""
+    def _begin(self, req: InferenceRequest) -> list:
+        """Prefix lookup and sequence of a joining greedy request: [request, sequence id, prompt, tokens already in the sequence]."""
         eng, st = self.engine, req.stats
         st.t_start = time.time()
         st.prompt_tokens = len(req.prompt_ids)
@@ -388,13 +414,16 @@ class Orchestrator:
             sid = self._with_pool_evict_retry(req, eng.create_sequence)
             cached = 0
         st.cached_tokens = cached
-        try:
-            tok = self._with_pool_evict_retry(req, lambda: eng.prefill(sid, prompt[max(cached, eng.seq_len(sid)):]))
-            self.prefix.register(sid, prompt)
-        except Exception:
-            eng.free_sequence(sid)
-            raise
-        return sid, tok, self._emit(req, tok, None)
+        return [req, sid, prompt, max(cached, eng.seq_len(sid))]
+
+    def _prefill_slice(self, joining: list):
+        """Feed the next slice of the joining request's prompt: (prompt complete, the engine's next token after the slice)."""
+        req, sid, prompt, fed = joining
+        n = min(self.prefill_slice, len(prompt) - fed)
+        tok = self._with_pool_evict_retry(req, lambda: self.engine.prefill(sid, prompt[fed: fed + n]))
+        joining[3] = fed + n
+        self.prefill_slices += 1
+        return joining[3] >= len(prompt), tok
 
     def _finish(self, req: InferenceRequest, reason: str):
         req.finish_reason = req.finish_reason or reason

@@ -490,3 +490,42 @@ def test_continuous_batching_gives_each_request_its_sequential_tokens():
         if not orch.step():
             break
     assert a.done.is_set() and a.finish_reason == "cancelled" and len(a.output_ids) < 50 and len(b.output_ids) == 8 and len(eng.seqs) == orch.prefix.holders()
+
+
+def test_a_joining_requests_prompt_is_prefilled_in_slices_between_decode_steps():
+    """Continuous batching with a long prompt arriving while another request decodes: the prompt goes in slices, the running
+    request gets a token between every two slices (it never waits for the whole prompt), and both end with their sequential tokens."""
+    from layerstorm_b200.runtime.null_engine import NullEngine
+    from layerstorm_b200.serving.orchestrator import InferenceRequest, Orchestrator, SamplingParams
+    events = []
+    short = InferenceRequest("short", [9, 8, 7, 6, 5], SamplingParams(max_tokens=40, ignore_eos=True), on_token=lambda t, i: events.append("s"))
+    long_prompt = [(11 * i) % 240 + 4 for i in range(200)]
+    long = InferenceRequest("long", long_prompt, SamplingParams(max_tokens=5, ignore_eos=True), on_token=lambda t, i: events.append("L"))
+    seq = Orchestrator(NullEngine(vocab=300), eos_token_ids=[1])
+    want = {}
+    for r in (short, long):
+        c = InferenceRequest(r.request_id, list(r.prompt_ids), r.params)
+        seq.submit_request(c)
+        seq.step()
+        want[r.request_id] = list(c.output_ids)
+
+    class Counting(NullEngine):
+        def prefill(self, sid, tokens, want_logits=False):
+            events.append(f"p{len(tokens)}")
+            return super().prefill(sid, tokens, want_logits)
+
+    orch = Orchestrator(Counting(vocab=300), eos_token_ids=[1], max_batch=4, prefill_slice_tokens=32)
+    orch.submit_request(short)
+    orch.step()
+    orch.step()
+    orch.submit_request(long)
+    for _ in range(200):
+        if not orch.step():
+            break
+    assert list(short.output_ids) == want["short"] and list(long.output_ids) == want["long"]
+    slices = [e for e in events if e.startswith("p")]
+    assert slices == ["p5"] + ["p32"] * 6 + ["p8"] and orch.prefill_slices == 8        # 200 = 6 x 32 + 8
+    # between two consecutive slices of the long prompt the short request produced exactly one token
+    idx = [i for i, e in enumerate(events) if e.startswith("p")][1:]
+    assert all(events[a + 1: b] == ["s"] for a, b in zip(idx, idx[1:]))
+    assert events.index("L") > idx[-1]

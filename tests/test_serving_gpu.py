@@ -358,7 +358,7 @@ def test_continuous_batching_on_the_gpu_engine_matches_sequential_serving():
     gens = [9, 4, 12, 6]
 
     def serve(max_batch):
-        orch = Orchestrator(eng, eos_token_ids=[], max_batch=max_batch)
+        orch = Orchestrator(eng, eos_token_ids=[], max_batch=max_batch, prefill_slice_tokens=16)      # prompts join in several slices
         reqs = [InferenceRequest(f"b{max_batch}-{i}", list(p), SamplingParams(max_tokens=n, ignore_eos=True)) for i, (p, n) in enumerate(zip(prompts, gens))]
         for r in reqs:
             orch.submit_request(r)

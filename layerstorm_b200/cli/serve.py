@@ -328,7 +328,9 @@ def build_server(cfg: dict, shape: ModelConfig, ckpt: Optional[str], engine, arg
     # continuous batching: as many plain greedy requests decode together as the engine's batched step takes (its CUDA graphs are
     # captured per batch size), bounded by the admitted concurrency
     eng_batch = int(getattr(getattr(engine, "_engine", engine), "max_batch", 1) or 1)
-    batch = max(1, min(eng_batch, int(cfg["orchestrator"]["max_batch_size"]), int(sv["max_concurrent_requests"])))
+    # (LSB_SERVE_MAX_BATCH, default 8: every batch size that occurs gets its own step workspace and CUDA graph, which a model that
+    # fills the GPU cannot afford for large batches)
+    batch = max(1, min(eng_batch, int(cfg["orchestrator"]["max_batch_size"]), int(sv["max_concurrent_requests"]), int(os.environ.get("LSB_SERVE_MAX_BATCH", "8"))))
     orch = Orchestrator(engine, eos_token_ids=eos, prefix_cache=pcc, draft=draft, speculation_depth=depth, tokenizer=tok, max_batch=batch,
                         prefill_slice_tokens=4 * int(cfg["orchestrator"]["prefill_chunk_tokens"]))
     rc = sv["reasoning_config"]

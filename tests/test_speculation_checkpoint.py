@@ -414,3 +414,51 @@ def test_device_mtp_draft_source_finds_the_sequence_of_a_context():
     assert d.propose([9, 9, 9], 2) == [] and d.propose([5, 6, 7, 8, 9], 0) == []
     d.feedback(1, 1)
     assert d.proposed == 1
+
+
+def test_live_gguf_source_builds_slot_images_from_a_real_file(tmp_path):
+    """A GGUF file with stacked expert tensors (gate / up in Q4_K, down in Q6_K, shared expert alike) -> ``LiveGgufExpertSource``:
+    the slot image of every expert is its three matrices' file blocks in their device layouts at the slot layout's offsets, zeros
+    elsewhere; a layer whose tensors are not all natively readable is not covered.  No GPU involved."""
+    import dataclasses
+    from layerstorm_b200.formats import gguf as g
+    from layerstorm_b200.models.device_model import EXPERT_FMT
+    from layerstorm_b200.runtime.live_gguf import LiveGgufExpertSource
+    cfg = dataclasses.replace(tiny_mla_moe(), moe_inter=256, n_routed=4, top_k=2)
+    H, F, E = cfg.hidden, cfg.moe_inter, cfg.n_routed
+    gen = torch.Generator().manual_seed(2)
+    gw = g.GgufWriter()
+    gw.meta("general.architecture", "deepseek2")
+    q4, q6, q8 = g.GGML_TYPES["Q4_K"], g.GGML_TYPES["Q6_K"], g.GGML_TYPES["Q8_0"]
+    stacks = {}
+    for layer, (tgu, tdn) in {1: (q4, q6), 2: (q8, q4)}.items():
+        for proj, shape, t in (("gate", (E, F, H), tgu), ("up", (E, F, H), tgu), ("down", (E, H, F), tdn)):
+            x = (torch.randn(*shape, generator=gen) * 0.05).numpy()
+            stacks[(layer, proj)] = (x, t)
+            gw.add(f"blk.{layer}.ffn_{proj}_exps.weight", x, ggml_type=t)
+            gw.add(f"blk.{layer}.ffn_{proj}_shexp.weight", x[0] * 0.5, ggml_type=t)
+    # layer 3: the up matrix in fp16 - not natively readable
+    for proj, shape, t in (("gate", (E, F, H), q4), ("up", (E, F, H), g.GGML_TYPES["F16"]), ("down", (E, H, F), q4)):
+        gw.add(f"blk.3.ffn_{proj}_exps.weight", (torch.randn(*shape, generator=gen) * 0.05).numpy(), ggml_type=t)
+    path = str(tmp_path / "live.gguf")
+    gw.write(path)
+    _, ck = open_checkpoint(path, cfg)
+    src = LiveGgufExpertSource(ck, cfg, threads=3)
+    ef = src.layout(1)
+    assert ef is not None and ef.fmt == EXPERT_FMT["gguf_q4_k"] and ef.fmt_down1 == EXPERT_FMT["gguf_q6_k"] + 1
+    assert src.layout(2).fmt == EXPERT_FMT["gguf_q8_0"] and src.layout(3) is None and src.layout(0) is None
+    host = torch.full((E + cfg.n_shared, ef.stride), 0xAB, dtype=torch.uint8)
+    src.build_layer(1, list(range(E + cfg.n_shared)), host)
+    for e in range(E + cfg.n_shared):
+        img = host[e].numpy()
+        used = np.zeros(ef.stride, dtype=bool)
+        for proj, off in (("gate", ef.off_gate), ("up", ef.off_up), ("down", ef.off_down)):
+            x, t = stacks[(1, proj)]
+            mat = x[e] if e < E else x[0] * 0.5
+            want = g.to_device_layout(t, g.quantize(t, mat), mat.shape[0], mat.shape[1]).reshape(-1)
+            assert np.array_equal(img[off: off + want.size], want), (e, proj)
+            used[off: off + want.size] = True
+        assert not img[~used].any()                                   # zero tail and padding
+    assert src.bytes_built == (E + cfg.n_shared) * ef.stride
+    with pytest.raises(ValueError):
+        src.load_into(3, 0, host[0].numpy())

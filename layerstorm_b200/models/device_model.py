@@ -1195,6 +1195,8 @@ class DeviceModel:
         if defer_combine and self.streamer is None and self._cp is None and self.tp_size == 1:
             return True
         nat.call("lsb_moe_combine", ws.sub, ws.y, ws.wts, ws.ids, present, R, S, cfg.hidden, 0, self._cp)
+        if self.streamer is not None and self.streamer.cpu_partial is not None:
+            ws.sub[:R].add_(self.streamer.cpu_partial)           # the experts the host computed for this step (capped cache, CPU offload)
         self._reduce(ws, R)
         return False
 

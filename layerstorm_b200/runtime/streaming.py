@@ -34,7 +34,7 @@ from . import native as rt
 class ExpertStreamer:
     def __init__(self, model, slots_per_layer: int, policy: str = "impact_weighted_lru", waterline: int = 4, prefetch: bool = False,
                  fetch_deadline_ms: Optional[float] = None, numa_node: int = -1, place_freq: Optional[str] = None,
-                 cfg=None, device=None, live_source=None):
+                 cfg=None, device=None, live_source=None, cpu_offload: Optional[bool] = None, cpu_threads: int = 0):
         """Takes a fully resident ``DeviceModel`` (every MoE layer's arena holds all of this rank's experts), moves
         the slot images to pinned host memory and shrinks every arena to ``slots_per_layer`` slots.
         With ``model = None`` (and ``cfg`` / ``device`` given) the streamer starts empty: pass :meth:`add_layer` as the ``layer_hook`` of
@@ -68,6 +68,19 @@ class ExpertStreamer:
         # GGUF checkpoints: slot images of covered layers come straight from the file into the pinned store (runtime/live_gguf.py);
         # the model builder then leaves those layers' arenas to this streamer (``DeviceModel.from_state_dict(skip_experts=...)``)
         self.live_source = live_source
+        # CPU offload of missed experts (opt-in, LSB_STREAM_CPU_OFFLOAD=1): a decode step's experts that are not resident are split
+        # between the copy engine and the host's expert kernels (csrc/runtime/cpu_experts.cpp reads the same slot images from the
+        # pinned store) so that both finish at about the same time; the CPU never takes work it would finish later than the copy
+        if cpu_offload is None:
+            cpu_offload = os.environ.get("LSB_STREAM_CPU_OFFLOAD", "0") not in ("", "0")
+        self.cpu = rt.CpuExperts(cpu_threads) if cpu_offload else None
+        self.cpu_max_rows = 4
+        self._cpu_pool = None
+        self._cpu_ms = None                                       # measured host time of one expert for one row
+        self._cpu_future = None
+        self.h_x = None
+        self.cpu_partial = None                                   # device fp32 [rows, hidden] to add after the combine (set by run_layer)
+        self.stats.update({"cpu_experts": 0, "cpu_wait_ms": 0.0})
         self._place_freq = place_freq or os.environ.get("LS_ARENA_PLACE_FREQ") or None
         if model is not None:
             for i, L in enumerate(model.layers):
@@ -299,6 +312,14 @@ class ExpertStreamer:
         cur = torch.cuda.current_stream(self.dev)
         self.h_ids[:n_pairs].copy_(ws.ids[:R].reshape(-1), non_blocking=True)
         self.h_ids[n_pairs: 2 * n_pairs].copy_(ws.wts[:R].reshape(-1).view(torch.int32), non_blocking=True)
+        self.cpu_partial = None
+        use_cpu = self.cpu is not None and R <= self.cpu_max_rows and st["arena"].ef.fmt <= 3 and not st["arena"].ef.fmt_down1
+        if use_cpu:
+            if self.h_x is None:
+                self.h_x = torch.zeros(self.cpu_max_rows, self.cfg.hidden, dtype=torch.bfloat16).pin_memory()
+                self.d_ycpu = torch.zeros(self.cpu_max_rows, self.cfg.hidden, device=self.dev)
+                self.h_ycpu = torch.zeros(self.cpu_max_rows, self.cfg.hidden).pin_memory()
+            self.h_x[:R].copy_(ws.x[:R], non_blocking=True)          # the layer's normalised input rows ride along with the routing
         ev_ids = torch.cuda.Event()
         ev_ids.record(cur)
         ev_ids.synchronize()
@@ -314,6 +335,8 @@ class ExpertStreamer:
         if li == self._last_layer:
             self.trace_step += 1                                 # counts steps for both traces (routing, copies)
         st["expert_stats"].observe(todo, [need[e] for e in todo])
+        if use_cpu:
+            todo = self._offload_to_cpu(li, st, ws, R, todo, ids, wts)
         model._moe_prepare(arena, ws, R)
         st["present"].fill_(-1)
         degraded = False
@@ -377,6 +400,16 @@ class ExpertStreamer:
             done = set(wave) | late
             todo = [e for e in todo if e not in done]
             self.stats["waves"] += 1
+        if self._cpu_future is not None:
+            # the host's share: wait for it (it was sized to finish with the copies), ship [rows, hidden] fp32 and let the caller add it
+            t0 = time.perf_counter()
+            y = self._cpu_future.result()
+            self.stats["cpu_wait_ms"] += (time.perf_counter() - t0) * 1e3
+            self._cpu_future = None
+            self.h_ycpu[:R].copy_(y)
+            self.d_ycpu[:R].copy_(self.h_ycpu[:R], non_blocking=True)
+            self.stats["bytes_h2d"] += R * self.cfg.hidden * 4
+            self.cpu_partial = self.d_ycpu[:R]
         if degraded:
             self.stats["degraded_steps"] += 1
         if self.weighted:
@@ -384,6 +417,45 @@ class ExpertStreamer:
         if self.prefetch:
             self._prefetch_next(model, li, ws, R, list(need))
         return st["present"]
+
+    def _offload_to_cpu(self, li: int, st: dict, ws, R: int, todo: List[int], ids, wts) -> List[int]:
+        """Split the step's missed experts between the copy engine and the host kernels; returns the experts left for the GPU.
+        With m missed experts, a copy costing f and a host expert costing c, n = m f / (c + f) of them go to the host: both sides
+        then finish together, and the host is never given an expert it would finish after the copy it replaces."""
+        import ctypes
+        from concurrent.futures import ThreadPoolExecutor
+        cache = st["cache"]
+        miss = [e for e in todo if cache.lookup(li, e) < 0]
+        if not miss:
+            return todo
+        ef = st["arena"].ef
+        if self._cpu_pool is None:
+            self._cpu_pool = ThreadPoolExecutor(max_workers=1)
+        if self._cpu_ms is None:                                    # one timed expert on the host, once
+            x0 = torch.zeros(1, self.cfg.hidden)
+            e0 = miss[0]
+            t0 = time.perf_counter()
+            self.cpu.ffn(ctypes.addressof(ef), st["host"][st["host_row"][e0]], x0, self.cfg.swiglu_limit)
+            self.cpu.ffn(ctypes.addressof(ef), st["host"][st["host_row"][e0]], x0, self.cfg.swiglu_limit)
+            self._cpu_ms = max(1e-3, (time.perf_counter() - t0) * 1e3 / 2)
+        gbs = self.te.bandwidth_gbs(0, 0) or 50.0
+        f_ms = ef.stride / (max(gbs, 1.0) * 1e6)
+        c_ms = self._cpu_ms * R
+        m = len(miss)
+        lo = min(m, int(m * f_ms / (c_ms + f_ms)))
+        n_cpu = min((lo, min(m, lo + 1)), key=lambda n: max(n * c_ms, (m - n) * f_ms))      # both sides finish together, whichever split is faster
+        if n_cpu <= 0:
+            return todo
+        mine = set(miss[-n_cpu:])                                   # the lightest missed experts: the heavier ones are worth caching
+        n_pairs = R * ws.S
+        ids_cpu = torch.where(torch.isin(ids, torch.tensor(sorted(mine), dtype=ids.dtype)), ids, torch.full_like(ids, -1)).view(R, ws.S).clone()
+        wts_cpu = wts.view(R, ws.S).clone()
+        x = self.h_x[:R].float()
+        slots = {e: st["host"][st["host_row"][e]] for e in mine}
+        E_total = self.cfg.n_routed + self.cfg.n_shared
+        self._cpu_future = self._cpu_pool.submit(self.cpu.moe_layer, ctypes.addressof(ef), slots, E_total, x, ids_cpu, wts_cpu, self.cfg.swiglu_limit)
+        self.stats["cpu_experts"] += n_cpu
+        return [e for e in todo if e not in mine]
 
     def _prescope(self, model, nxt: int, ws, R: int) -> List[int]:
         """Pre-gating ("prescope"): run the NEXT MoE layer's router on this layer's input.  The residual stream changes

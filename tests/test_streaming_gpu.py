@@ -133,3 +133,36 @@ def test_layer_by_layer_loading_prewarm_and_fetch_trace(tmp_path, monkeypatch):
     assert s2["bytes_h2d"] > 0 and sum(len(l["host_row"]) for l in st2.layers.values()) > 0
     # the pre-warmed run starts with the most-fetched experts resident: fewer demand misses than the cold run
     assert s2["misses"] <= s["misses"]
+
+
+def test_missed_experts_can_run_on_the_host_kernels_instead_of_being_fetched():
+    """CPU offload under a capped cache: with the host made to look fast, a decode step's missed experts are computed by the host
+    kernels from the pinned slot images and added after the combine; with the host made to look slow nothing is offloaded.  The
+    logits stay within the precision of the two expert implementations and the greedy tokens agree with the resident model."""
+    cfg = get_preset("tiny-mla-moe")
+    w = init_weights(cfg, 9)
+    prompt = torch.randint(0, cfg.vocab, (24,), generator=torch.Generator().manual_seed(4)).tolist()
+
+    def run(offload, cpu_ms=None):
+        m = DeviceModel.from_state_dict(cfg, w, "cuda", kv_fmt="bf16", page=16, expert_quant="bf16")
+        st = ExpertStreamer(m, slots_per_layer=cfg.top_k + cfg.n_shared + 1, cpu_offload=True) if offload else None
+        if st is not None and cpu_ms is not None:
+            st._cpu_ms = cpu_ms
+        eng = Engine(m, max_seqs=1, max_ctx=128, prefill_chunk=8, max_batch=1, use_graph=False)
+        sid = eng.create_sequence()
+        toks, lgs = [eng.prefill(sid, prompt)], []
+        for _ in range(6):
+            out, lg = eng.decode([sid], [toks[-1]], return_logits=True)
+            toks.append(out[0])
+            lgs.append(lg[0].clone())
+        return toks, torch.stack(lgs), st
+
+    ref_t, ref_l, _ = run(False)
+    fast_t, fast_l, st = run(True, cpu_ms=1e-6)             # the host looks free: every missed expert of a decode step goes to it
+    s = st.summary()
+    assert s["cpu_experts"] > 0 and st.cpu.threads >= 1
+    rel = float((fast_l - ref_l).abs().max() / ref_l.abs().max())
+    assert rel < 2e-2, rel
+    assert fast_t == ref_t
+    slow_t, slow_l, st2 = run(True, cpu_ms=1e6)             # the host looks hopeless: never-lose keeps everything on the copy engine
+    assert st2.summary()["cpu_experts"] == 0 and slow_t == ref_t and torch.equal(slow_l, ref_l)

@@ -529,3 +529,58 @@ def test_a_joining_requests_prompt_is_prefilled_in_slices_between_decode_steps()
     idx = [i for i, e in enumerate(events) if e.startswith("p")][1:]
     assert all(events[a + 1: b] == ["s"] for a, b in zip(idx, idx[1:]))
     assert events.index("L") > idx[-1]
+
+
+def test_the_serving_loop_sweeps_idle_prefix_holders_between_requests(tmp_path):
+    """The orchestrator's own loop (a thread, as in the server) runs the prefix cache's idle sweep when it has nothing to serve:
+    holders of finished requests hibernate and spill without any request asking for it, and a later request with the same prefix
+    still hits the cache."""
+    import threading
+    import time as _time
+    import torch
+    from layerstorm_b200.runtime.null_engine import NullEngine
+    from layerstorm_b200.serving.orchestrator import InferenceRequest, Orchestrator, SamplingParams
+    from layerstorm_b200.serving.prefix_cache import PrefixCacheConfig, PrefixSpillConfig
+
+    class Tiered(NullEngine):
+        def __init__(self, **kw):
+            super().__init__(**kw)
+            self.hibernated, self.spilled = {}, {}
+            self.cold_kv, self.cold_idx = {0: torch.zeros(1, 16, 64, dtype=torch.uint8)}, {}
+
+        def hibernate(self, sid):
+            self.hibernated[sid] = [0] * ((self.seqs[sid].length + self.page - 1) // self.page)
+            return len(self.hibernated[sid])
+
+        def spill(self, sid, path):
+            n = len(self.hibernated.pop(sid)) * 1024
+            open(path, "wb").write(b"x")
+            self.spilled[sid] = (path, n)
+            return n
+
+        def fork_sequence(self, parent, prefix_len=None):
+            self.spilled.pop(parent, None)
+            self.hibernated.pop(parent, None)
+            return super().fork_sequence(parent, prefix_len)
+
+    eng = Tiered(vocab=300, max_seqs=8)
+    pcc = PrefixCacheConfig(grid=64, min_prefix=64, hibernate_holders=True, hibernate_idle_seconds=0.0,
+                            spill=PrefixSpillConfig(enabled=True, path=str(tmp_path), max_mib=1, idle_seconds=0.0))
+    orch = Orchestrator(eng, eos_token_ids=[1], prefix_cache=pcc)
+    t = threading.Thread(target=orch.run, daemon=True)
+    t.start()
+    try:
+        prompt = [(7 * i) % 250 + 4 for i in range(80)]
+        r1 = InferenceRequest("a", list(prompt), SamplingParams(max_tokens=3, ignore_eos=True))
+        orch.submit_request(r1)
+        assert r1.done.wait(5)
+        deadline = _time.time() + 8
+        while _time.time() < deadline and not eng.spilled:          # two idle sweeps, one second apart: hibernate, then spill
+            _time.sleep(0.1)
+        assert eng.spilled and orch.prefix.spill_stats["spilled"] == 1 and not getattr(orch, "last_sweep_error", None)
+        r2 = InferenceRequest("b", list(prompt) + [9, 9], SamplingParams(max_tokens=3, ignore_eos=True))
+        orch.submit_request(r2)
+        assert r2.done.wait(5) and r2.error is None and r2.stats.cached_tokens == 64
+    finally:
+        orch.shutdown()
+        t.join(timeout=5)

@@ -259,7 +259,8 @@ def build_model_draft(cfg: dict, shape: ModelConfig, engine, args: argparse.Name
         from ..speculation.self_draft import SelfSpeculativeDraft
         depth = args.speculation_depth if args.speculation_depth is not None else sp["mtp"]["max_depth"]
         try:
-            return SelfSpeculativeDraft(target, sp["self_speculative"], max_gamma=max(1, depth), layer_skip=sp.get("layer_skip_draft")), depth
+            return SelfSpeculativeDraft(target, sp["self_speculative"], max_gamma=max(1, depth), layer_skip=sp.get("layer_skip_draft"),
+                                        calibration=sp.get("calibration")), depth
         except (TypeError, NotImplementedError) as e:
             log.warning("self-speculative draft unavailable (%s); serving without speculation", e)
             return None, 0

@@ -22,12 +22,14 @@ from .policies import SelfSpeculativePlan
 
 
 class SelfSpeculativeDraft(EngineDraft):
-    def __init__(self, engine, cfg: dict, max_gamma: int = 8, layer_skip: dict = None):
+    def __init__(self, engine, cfg: dict, max_gamma: int = 8, layer_skip: dict = None, calibration: dict = None):
         """``engine``: the TARGET engine (or its model holder) offering ``reduced_expert_view``; ``cfg``: ``speculation.self_speculative``;
-        ``layer_skip``: ``speculation.layer_skip_draft`` (optional)."""
+        ``layer_skip``: ``speculation.layer_skip_draft`` (optional); ``calibration``: ``speculation.calibration`` (optional: the draft's
+        expert count and layer skipping then follow the acceptance rate, see ``online_calibrator.py``)."""
         from .policies import LayerSkipPolicy
         k = max(1, int(cfg.get("draft_expert_count", 1)))
         super().__init__(make_reduced_engine(engine, k), max_gamma)
+        self._target = engine
         mc = engine.cfg if hasattr(engine, "cfg") else engine.model.cfg
         self.skip_policy = LayerSkipPolicy(layer_skip or {}, mc.n_layers)
         self.skip_set = set()
@@ -35,6 +37,28 @@ class SelfSpeculativeDraft(EngineDraft):
         moe = [i for i in range(mc.n_layers) if mc.is_moe_layer(i)]
         self.plan = SelfSpeculativePlan(cfg, moe, mc.n_layers, mc.top_k, max_depth=max_gamma)
         self.expert_fraction = self.plan.expert_fraction(mc.top_k)
+        self._model_top_k = mc.top_k
+        self.calibrator = None
+        if calibration is not None:
+            from .online_calibrator import DraftParams, OnlineCalibrator
+            self.calibrator = OnlineCalibrator(calibration, DraftParams(draft_expert_count=self.plan.k, layer_skip_enabled=bool(self.skip_policy.enabled),
+                                                                        max_draft_expert_count=mc.top_k))
+            self._skip_configured = bool(self.skip_policy.enabled)
+
+    def _apply_calibration(self):
+        """The calibrator moved: take over its expert count (a new reduced-expert view of the target; the draft cache is rebuilt from
+        the context by the next proposal) and its layer-skip switch (only ever on when the configuration enabled skipping)."""
+        p = self.calibrator.params
+        if p.draft_expert_count != self.plan.k:
+            self.reset()
+            self.engine = make_reduced_engine(self._target, p.draft_expert_count)
+            self.plan.k = p.draft_expert_count
+            self.expert_fraction = self.plan.expert_fraction(self._model_top_k)
+        self.skip_policy.enabled = bool(p.layer_skip_enabled and self._skip_configured)
+        if not self.skip_policy.enabled:
+            self.skip_set = set()
+            if hasattr(self.engine, "set_layer_skip"):
+                self.engine.set_layer_skip(set(), probe=False)
 
     def propose(self, context: Sequence[int], gamma: int) -> List[int]:
         if not self.plan.enabled:
@@ -54,6 +78,8 @@ class SelfSpeculativeDraft(EngineDraft):
 
     def feedback(self, proposed: int, accepted: int):
         self.plan.record(proposed, accepted)
+        if self.calibrator is not None and self.calibrator.update(proposed, accepted):
+            self._apply_calibration()
 
 
 def make_reduced_engine(engine, top_k: int):

@@ -178,3 +178,48 @@ def test_residual_correction_learns_the_missing_experts():
     target = np.tanh(top1 @ A) + gate @ B
     pred = rc.predict(3, top1, gate)
     assert pred.shape == (4, Hh) and ((pred - target) ** 2).sum() < 0.5 * (target ** 2).sum()
+
+
+def test_online_calibrator_moves_the_self_speculative_draft_with_its_acceptance():
+    """Low acceptance: layer skipping goes first, then the draft runs more experts per token; high acceptance: fewer experts first,
+    then layer skipping comes back - one step per interval, nothing between the thresholds.  On a real (CPU) engine the draft's
+    reduced-expert view is rebuilt with the new count and keeps proposing."""
+    from layerstorm_b200.models.config import get_preset
+    from layerstorm_b200.models.weights import init_weights, round_weights_bf16
+    from layerstorm_b200.runtime.cpu_engine import CpuEngine
+    from layerstorm_b200.speculation.online_calibrator import DraftParams, OnlineCalibrator
+    from layerstorm_b200.speculation.self_draft import SelfSpeculativeDraft
+    cal = OnlineCalibrator({"min_acceptance_rate": 0.3, "target_acceptance_rate": 0.6, "adjustment_interval_tokens": 10, "acceptance_ema_alpha": 1.0},
+                           DraftParams(draft_expert_count=2, layer_skip_enabled=True, max_draft_expert_count=4))
+    assert not cal.update(4, 0)                                   # 4 of 10 tokens: no decision yet
+    assert not cal.update(4, 0)
+    assert cal.update(4, 0) and cal.params.layer_skip_enabled is False and cal.params.draft_expert_count == 2      # skipping goes first
+    for _ in range(3):
+        cal.update(4, 0)
+    assert cal.params.draft_expert_count == 3
+    for _ in range(6):
+        cal.update(4, 0)
+    assert cal.params.draft_expert_count == 4                    # capped at the model's own top-k
+    for _ in range(3):
+        assert not cal.update(4, 2)                               # 0.5 lies between the thresholds: nothing moves
+    assert cal.params.draft_expert_count == 4
+    for _ in range(12):
+        cal.update(4, 4)
+    assert cal.params.draft_expert_count == 1 and cal.params.layer_skip_enabled is True and cal.adjustments >= 6
+    assert not cal.update(0, 0)
+
+    cfg = get_preset("tiny-mla-moe")
+    eng = CpuEngine(cfg, round_weights_bf16(init_weights(cfg, 1)), native_experts=False)
+    d = SelfSpeculativeDraft(eng, {"enabled": True, "draft_expert_count": 1}, max_gamma=3,
+                             calibration={"min_acceptance_rate": 0.3, "target_acceptance_rate": 0.6, "adjustment_interval_tokens": 6,
+                                          "acceptance_ema_alpha": 1.0})
+    ctx = [5, 9, 33, 71, 20, 8]
+    first = d.propose(ctx, 3)
+    assert len(first) == 3 and d.engine.cfg.top_k == 1
+    old_engine = d.engine
+    d.feedback(3, 0)
+    d.feedback(3, 0)                                              # 6 drafted tokens, none accepted -> one more expert per token
+    assert d.plan.k == 2 and d.engine is not old_engine and d.engine.cfg.top_k == 2 and d.sid is None
+    again = d.propose(ctx, 3)
+    assert len(again) == 3                                        # the new view rebuilt its cache from the context
+    assert abs(d.expert_fraction - 2 / cfg.top_k) < 1e-9

@@ -68,7 +68,7 @@ def synthetic_trace(steps: int, layers: int, n_experts: int, top_k: int, zipf: f
 
 def simulate(trace: Trace, slots: int, policy: str = "impact_weighted_lru", weights: Optional[Sequence[float]] = None, prefetch_budget: int = 0,
              slot_bytes: int = 18 << 20, n_experts: Optional[int] = None, top_k: Optional[int] = None, decisions: Optional[TextIO] = None,
-             predictor_weights: Optional[str] = None) -> dict:
+             predictor_weights: Optional[str] = None, h2d_gbs: float = 0.0, cpu_expert_ms: float = 0.0) -> dict:
     from ..runtime import native as rt
     layers = sorted({l for _, l, _ in trace})
     lid = {l: i for i, l in enumerate(layers)}
@@ -86,6 +86,7 @@ def simulate(trace: Trace, slots: int, policy: str = "impact_weighted_lru", weig
             ridge.load_weights(predictor_weights)          # a trained bundle (utils/expert_predictor_train.py), frozen
     hits = misses = prefetched = useful_prefetch = evictions = 0
     per_step_miss: Dict[int, int] = {}
+    per_layer_step_miss: Dict[Tuple[int, int], int] = {}      # (step, layer) -> demand misses: the exposed copies of that layer
     pending_prefetch: Dict[int, set] = {l: set() for l in layers}
     routed_now = np.full((len(layers), top_k), -1, np.int64)
     last_step = None
@@ -140,6 +141,7 @@ def simulate(trace: Trace, slots: int, policy: str = "impact_weighted_lru", weig
                 else:
                     misses += 1
                     per_step_miss[step] = per_step_miss.get(step, 0) + 1
+                    per_layer_step_miss[(step, l)] = per_layer_step_miss.get((step, l), 0) + 1
                     if not admit(l, cache, e):
                         raise RuntimeError(f"layer {l}: no slot of {slots} can be freed")
                     if decisions:
@@ -155,7 +157,19 @@ def simulate(trace: Trace, slots: int, policy: str = "impact_weighted_lru", weig
             routed_now[lid[l], : len(ids)] = ids[:top_k]
     tot = max(1, hits + misses)
     steps = len({s for s, _, _ in trace})
-    return {"steps": steps, "layers": len(layers), "slots_per_layer": slots, "policy": policy, "hits": hits, "misses": misses,
+    projected = None
+    if h2d_gbs > 0:
+        # exposed copy time per step: a layer's demand misses are copied while the layer waits for them (prefetched experts are not
+        # counted: their copies overlap other work).  With host expert kernels (cpu_expert_ms per expert and row) the m misses of a
+        # layer are split so that the copy engine and the host finish together: min over n of max(n c, (m - n) f).
+        f_ms = slot_bytes / (h2d_gbs * 1e6)
+        copy_ms = sum(m * f_ms for m in per_layer_step_miss.values()) / max(steps, 1)
+        projected = {"h2d_gb_s": h2d_gbs, "copy_ms_per_expert": round(f_ms, 4), "exposed_copy_ms_per_step": round(copy_ms, 3)}
+        if cpu_expert_ms > 0:
+            c = cpu_expert_ms
+            split = sum(min(max(n * c, (m - n) * f_ms) for n in range(m + 1)) for m in per_layer_step_miss.values()) / max(steps, 1)
+            projected.update({"cpu_expert_ms": c, "with_cpu_offload_ms_per_step": round(split, 3)})
+    return {**({"projected": projected} if projected else {}), "steps": steps, "layers": len(layers), "slots_per_layer": slots, "policy": policy, "hits": hits, "misses": misses,
             "hit_rate": round(hits / tot, 4), "evictions": evictions, "prefetched": prefetched, "useful_prefetch": useful_prefetch,
             "h2d_bytes": (misses + prefetched) * slot_bytes, "demand_miss_bytes": misses * slot_bytes,
             "max_misses_in_a_step": max(per_step_miss.values(), default=0), "mean_misses_per_step": round(misses / max(steps, 1), 3)}
@@ -169,6 +183,8 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     ap.add_argument("--weights", help="seven comma-separated score weights (alpha .. eta)")
     ap.add_argument("--prefetch-budget", type=int, default=0, help="experts prefetched per layer and step from the reuse predictor")
     ap.add_argument("--slot-mib", type=float, default=18.0)
+    ap.add_argument("--h2d-gbs", type=float, default=0.0, help="host->device rate: adds the projected exposed copy time per step")
+    ap.add_argument("--cpu-expert-ms", type=float, default=0.0, help="host time of one expert for one row: adds the projection with CPU offload of misses")
     ap.add_argument("--predictor-weights", help="trained reuse-predictor bundle (.npz) for the prefetcher instead of online learning")
     ap.add_argument("--decisions", help="write the miss / eviction stream here")
     ap.add_argument("--synthetic", default="256,8,64,8", help="steps,layers,experts,top_k of the synthetic trace")
@@ -183,7 +199,7 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
         ap.error("--weights needs seven values")
     dec = open(a.decisions, "w") if a.decisions else None
     try:
-        rep = simulate(trace, a.slots, a.policy, w, a.prefetch_budget, int(a.slot_mib * (1 << 20)), ne, k, dec, a.predictor_weights)
+        rep = simulate(trace, a.slots, a.policy, w, a.prefetch_budget, int(a.slot_mib * (1 << 20)), ne, k, dec, a.predictor_weights, a.h2d_gbs, a.cpu_expert_ms)
     finally:
         if dec:
             dec.close()

@@ -197,7 +197,8 @@ class Orchestrator:
         self._publish_state()
 
     # ---- published state (single writer: the serving thread; any number of readers) ----
-    _STATE_FMT = "<qqqqdd"      # served, queued, generated tokens, free KV pages, acceptance (windowed), wall time of the last update
+    _STATE_FMT = "<qqqqddqq"    # served, queued, generated tokens, free KV pages, acceptance (windowed), wall time of the last update,
+                                # requests decoding together right now, batched decode steps so far
 
     def _publish_state(self):
         import struct
@@ -206,7 +207,8 @@ class Orchestrator:
             free_pages = int(self.engine.free_page_count())
         except Exception:      # engines without a page pool
             pass
-        blob = struct.pack(self._STATE_FMT, self.served, len(self.queue), self._gen_tokens, free_pages, float(self.acceptance.windowed_rate()), time.time())
+        blob = struct.pack(self._STATE_FMT, self.served, len(self.queue), self._gen_tokens, free_pages, float(self.acceptance.windowed_rate()), time.time(),
+                           len(getattr(self, "running", ())) + (1 if getattr(self, "joining", None) is not None else 0), getattr(self, "batched_steps", 0))
         self._state.begin(); self._state.write(0, blob); self._state.end()
 
     def published_state(self) -> dict:
@@ -215,9 +217,9 @@ class Orchestrator:
         raw, version = self._state.read(0, struct.calcsize(self._STATE_FMT))
         if raw is None:
             return {}
-        served, queued, gen, free_pages, acc, t = struct.unpack(self._STATE_FMT, raw)
+        served, queued, gen, free_pages, acc, t, running, bsteps = struct.unpack(self._STATE_FMT, raw)
         return {"served": served, "queued": queued, "generated_tokens": gen, "free_kv_pages": free_pages, "spec_acceptance_windowed": round(acc, 4),
-                "state_age_s": round(max(0.0, time.time() - t), 3)}
+                "state_age_s": round(max(0.0, time.time() - t), 3), "running": running, "batched_steps": bsteps}
 
     # ---- thread-safe entry points ----
     def submit_request(self, req: InferenceRequest):

@@ -333,7 +333,9 @@ def build_server(cfg: dict, shape: ModelConfig, ckpt: Optional[str], engine, arg
     # fills the GPU cannot afford for large batches)
     batch = max(1, min(eng_batch, int(cfg["orchestrator"]["max_batch_size"]), int(sv["max_concurrent_requests"]), int(os.environ.get("LSB_SERVE_MAX_BATCH", "8"))))
     orch = Orchestrator(engine, eos_token_ids=eos, prefix_cache=pcc, draft=draft, speculation_depth=depth, tokenizer=tok, max_batch=batch,
-                        prefill_slice_tokens=4 * int(cfg["orchestrator"]["prefill_chunk_tokens"]))
+                        prefill_slice_tokens=4 * int(cfg["orchestrator"]["prefill_chunk_tokens"]),
+                        degraded_retry_max=int((cfg.get("_internal-orchestrator") or {}).get("degraded_retry_max", 1)
+                                               if (cfg.get("_internal-orchestrator") or {}).get("degraded_retry_enabled", True) else 0))
     rc = sv["reasoning_config"]
     if rc:
         rc = json.load(open(rc)) if os.path.exists(rc) else json.loads(rc)

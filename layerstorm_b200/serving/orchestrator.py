@@ -70,6 +70,8 @@ class RequestStats:
     spec_rounds: int = 0
     spec_accepted: int = 0
     pool_evict_retries: int = 0
+    moe_degraded_steps: int = 0        # engine steps of the DELIVERED attempt that ran without an expert the router selected (fetch deadline)
+    degraded_retries: int = 0          # times the request was run again because its prefill was degraded (0 = served first try)
 
     @property
     def ttft_s(self) -> float:
@@ -154,19 +156,29 @@ class SpecRoundGovernor:
         return self.gain_ema >= 0 or self.rounds % self.probe_every == 0
 
 
+class _DegradedRetry(Exception):
+    """The prefill of a retry-eligible request ran with an expert missing (a capped expert cache under a fetch deadline finished the
+    step without it): the attempt is abandoned before a single token is emitted, so even a streaming request can be run again."""
+
+
 class Orchestrator:
     """Serves InferenceRequests on one engine.  ``draft`` is an optional proposer with
     ``propose(context_ids, gamma) -> List[int]`` (speculative decoding)."""
 
     def __init__(self, engine, eos_token_ids: Sequence[int] = (), prefix_cache: Optional[PrefixCacheConfig] = None,
                  draft=None, speculation_depth: int = 0, tokenizer=None, governor: Optional[SpecRoundGovernor] = None, max_batch: int = 1,
-                 prefill_slice_tokens: int = 0):
+                 prefill_slice_tokens: int = 0, degraded_retry_max: int = 0):
         """``max_batch`` > 1: continuous batching - up to that many plain greedy requests decode together, one engine step per token
         of ALL of them; a request joins after its own prefill and leaves when it finishes, the others never wait for it.  Requests
         that need more than the arg-max of a step (sampling on the host, log-probabilities, guided decoding, speculation) are
         served one at a time between batches, in arrival order.  The reference serves one request at a time
         (python/cli/serve.py:273 clamps the batch to 1); this is the serving form of the engine's batched decode step."""
         self.engine = engine
+        # a request whose prefill was computed without a router-selected expert (the engine's graceful degradation under a fetch
+        # deadline) is a known-wrong answer: run it again up to this many times before delivering it; every action is counted, a retry
+        # loop that hides a capacity problem would be worse than the problem (reference: orchestrator.py degraded_retry_max)
+        self.degraded_retry_max = max(0, int(degraded_retry_max))
+        self.degraded_retries_total = self.degraded_delivered_total = 0
         self.max_batch = max(1, int(max_batch))
         self.running: List[list] = []             # continuous batching: [request, sequence id, next token to feed]
         self.batched_steps = 0
@@ -174,7 +186,7 @@ class Orchestrator:
         # steps of the running batch, so the others wait for a slice (tens of milliseconds), not for a whole long prompt (seconds);
         # 0 = four of the engine's prefill chunks
         self.prefill_slice = int(prefill_slice_tokens) or 4 * int(getattr(getattr(engine, "_engine", engine), "prefill_chunk", 0) or 2048)
-        self.joining: Optional[list] = None       # [request, sequence id, prompt, tokens already in the sequence]
+        self.joining: Optional[list] = None       # [request, sequence id, prompt, tokens already in the sequence, degraded steps before]
         self.prefill_slices = 0
         self.eos = set(int(t) for t in eos_token_ids)
         self.prefix = PrefixCache(engine, prefix_cache or PrefixCacheConfig())
@@ -284,7 +296,13 @@ class Orchestrator:
             req = self.queue.popleft()
             self.active = req
         try:
-            self._generate(req)
+            while True:
+                try:
+                    self._generate(req)
+                    break
+                except _DegradedRetry:
+                    req.stats.degraded_retries += 1
+                    self.degraded_retries_total += 1
         except Exception as exc:  # noqa: BLE001 - a failed request must not kill the serving loop
             req.error = f"{type(exc).__name__}: {exc}"
             if is_gpu_fatal(exc) and self.gpu_fatal is None:
@@ -352,7 +370,7 @@ class Orchestrator:
                         self._fail(head, exc)
         if self.joining is not None:
             did = True
-            req, sid, prompt, _ = self.joining
+            req, sid, prompt, _, d0 = self.joining
             try:
                 done_prefill, tok = self._prefill_slice(self.joining)
                 if req.cancelled.is_set():
@@ -362,7 +380,12 @@ class Orchestrator:
                     self.joining = None
                 elif done_prefill:
                     self.joining = None
-                    self.prefix.register(sid, prompt)
+                    degraded = self._degraded_count() - d0
+                    if degraded > 0:                       # KV rows computed with an expert missing are never cached
+                        req.stats.moe_degraded_steps += degraded
+                        self.degraded_delivered_total += 1
+                    else:
+                        self.prefix.register(sid, prompt)
                     if self._emit(req, tok, None):
                         eng.free_sequence(sid)
                         self._finish(req, req.finish_reason or "cancelled")
@@ -416,11 +439,11 @@ class Orchestrator:
             sid = self._with_pool_evict_retry(req, eng.create_sequence)
             cached = 0
         st.cached_tokens = cached
-        return [req, sid, prompt, max(cached, eng.seq_len(sid))]
+        return [req, sid, prompt, max(cached, eng.seq_len(sid)), self._degraded_count()]
 
     def _prefill_slice(self, joining: list):
         """Feed the next slice of the joining request's prompt: (prompt complete, the engine's next token after the slice)."""
-        req, sid, prompt, fed = joining
+        req, sid, prompt, fed = joining[:4]
         n = min(self.prefill_slice, len(prompt) - fed)
         tok = self._with_pool_evict_retry(req, lambda: self.engine.prefill(sid, prompt[fed: fed + n]))
         joining[3] = fed + n
@@ -505,8 +528,18 @@ class Orchestrator:
         try:
             # every attempt feeds what is still missing (the engine's prefill reserves its pages up front and fails before it
             # commits anything, and even an engine that failed mid-prompt is continued, never re-fed)
+            d0 = self._degraded_count()
             out = self._with_pool_evict_retry(req, lambda: eng.prefill(sid, prompt[max(cached, eng.seq_len(sid)):], want_logits=need_logits))
-            self.prefix.register(sid, prompt)
+            degraded = self._degraded_count() - d0
+            if degraded > 0:
+                # the KV rows of this prefill were computed with an expert missing: never cached, and the attempt is run again while
+                # the request has retry budget (nothing has been emitted yet)
+                if req.stats.degraded_retries < self.degraded_retry_max:
+                    raise _DegradedRetry()
+                req.stats.moe_degraded_steps += degraded
+                self.degraded_delivered_total += 1
+            else:
+                self.prefix.register(sid, prompt)
             tok, logits = out if need_logits else (out, None)
             if need_logits:
                 tok = self._pick(req, logits, len(prompt))
@@ -526,6 +559,14 @@ class Orchestrator:
             self._finish(req, req.finish_reason or ("cancelled" if req.cancelled.is_set() else "stop"))
         finally:
             eng.free_sequence(sid)
+
+    def _degraded_count(self) -> int:
+        """Degraded steps the engine has run so far (a capped expert cache that finished steps without a late expert), else 0."""
+        eng = getattr(self.engine, "_engine", self.engine)
+        st = getattr(getattr(eng, "model", None), "streamer", None)
+        if st is not None:
+            return int(st.stats.get("degraded_steps", 0))
+        return int(getattr(eng, "degraded_steps", 0) or 0)
 
     def _sample_args(self, req: InferenceRequest):
         p = req.params

@@ -584,3 +584,52 @@ def test_the_serving_loop_sweeps_idle_prefix_holders_between_requests(tmp_path):
     finally:
         orch.shutdown()
         t.join(timeout=5)
+
+
+def test_a_degraded_prefill_is_never_cached_and_is_retried_within_its_budget():
+    """An engine that reports a degraded step during a prefill (an expert missed its fetch deadline): the orchestrator does not
+    register a prefix holder for those KV rows, runs the request again while it has retry budget - nothing was emitted yet - and
+    counts what it did; without budget the degraded answer is delivered and marked."""
+    from layerstorm_b200.runtime.null_engine import NullEngine
+    from layerstorm_b200.serving.orchestrator import InferenceRequest, Orchestrator, SamplingParams
+
+    class Flaky(NullEngine):
+        degraded_steps = 0
+        bad_prefills = 0
+
+        def prefill(self, sid, tokens, want_logits=False):
+            if self.bad_prefills > 0:
+                self.bad_prefills -= 1
+                self.degraded_steps += 1
+            return super().prefill(sid, tokens, want_logits)
+
+    prompt = [(5 * i) % 200 + 4 for i in range(70)]
+
+    def request(name):
+        seen = []
+        return InferenceRequest(name, list(prompt), SamplingParams(max_tokens=4, ignore_eos=True), on_token=lambda t, i: seen.append(t)), seen
+
+    eng = Flaky(vocab=300)
+    orch = Orchestrator(eng, eos_token_ids=[1], degraded_retry_max=1)
+    eng.bad_prefills = 1
+    r, seen = request("a")
+    orch.submit_request(r)
+    orch.step()
+    assert r.error is None and r.stats.degraded_retries == 1 and r.stats.moe_degraded_steps == 0 and len(seen) == 4      # emitted once, from the clean attempt
+    assert orch.degraded_retries_total == 1 and orch.degraded_delivered_total == 0 and orch.prefix.holders() == 1
+    # two degraded prefills in a row with a budget of one: the second attempt is delivered, marked, and not cached
+    orch.prefix.clear()
+    eng.bad_prefills = 2
+    r2, seen2 = request("b")
+    orch.submit_request(r2)
+    orch.step()
+    assert r2.error is None and r2.stats.degraded_retries == 1 and r2.stats.moe_degraded_steps == 1 and len(seen2) == 4
+    assert orch.degraded_delivered_total == 1 and orch.prefix.holders() == 0
+    assert len(eng.seqs) == 0                                  # abandoned attempts freed their sequences
+    # retries off (the default): delivered first try, marked
+    o2 = Orchestrator(Flaky(vocab=300), eos_token_ids=[1])
+    o2.engine.bad_prefills = 1
+    r3, _ = request("c")
+    o2.submit_request(r3)
+    o2.step()
+    assert r3.stats.degraded_retries == 0 and r3.stats.moe_degraded_steps == 1 and o2.prefix.holders() == 0

@@ -120,8 +120,9 @@ class NullEngine:
 
     def decode(self, sids: Sequence[int], tokens: Sequence[int], return_logits: bool = False):
         outs, lgs = [], []
+        for sid in sids:
+            self._grow(sid, 1)                # every sequence gets its page before any advances: a step that runs out of pages can be run again
         for sid, t in zip(sids, tokens):
-            self._grow(sid, 1)
             s = self.seqs[sid]
             s.tokens.append(int(t))
             lg = self._logits(s.tokens)

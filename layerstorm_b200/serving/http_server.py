@@ -85,7 +85,7 @@ class LayerStormServer:
         # engine-side numbers come from the orchestrator's published state block (seqlock snapshot written by the serving thread)
         state = self.orch.published_state() if hasattr(self.orch, "published_state") else {}
         return {"status": "ok", "uptime_s": round(time.time() - self.started, 1), "queued": self.orch.queued(), "served": self.orch.served,
-                "engine": state}
+                "engine": state, "admission_waits": getattr(self.orch, "admission_waits", 0), "preemptions": getattr(self.orch, "preemptions", 0)}
 
     async def models(self):
         return {"object": "list", "data": [{"id": self.cfg.model_name, "object": "model", "created": int(self.started), "owned_by": "layerstorm-b200",

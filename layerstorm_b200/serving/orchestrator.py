@@ -70,6 +70,7 @@ class RequestStats:
     spec_rounds: int = 0
     spec_accepted: int = 0
     pool_evict_retries: int = 0
+    preemptions: int = 0                 # times the request gave its KV pages back in mid-decode and joined again
     moe_degraded_steps: int = 0        # engine steps of the DELIVERED attempt that ran without an expert the router selected (fetch deadline)
     degraded_retries: int = 0          # times the request was run again because its prefill was degraded (0 = served first try)
 
@@ -186,6 +187,11 @@ class Orchestrator:
         # steps of the running batch, so the others wait for a slice (tens of milliseconds), not for a whole long prompt (seconds);
         # 0 = four of the engine's prefill chunks
         self.prefill_slice = int(prefill_slice_tokens) or 4 * int(getattr(getattr(engine, "_engine", engine), "prefill_chunk", 0) or 2048)
+        # admission back-pressure: a request that could not get KV pages or a sequence slot while others are decoding goes back to the
+        # head of the queue and waits until one of them has finished (instead of failing)
+        self._admit_hold: Optional[int] = None    # admit again once fewer than this many requests are running
+        self.admission_waits = 0
+        self.preemptions = 0
         self.joining: Optional[list] = None       # [request, sequence id, prompt, tokens already in the sequence, degraded steps before]
         self.prefill_slices = 0
         self.eos = set(int(t) for t in eos_token_ids)
@@ -344,7 +350,9 @@ class Orchestrator:
         eng = self.engine
         did = False
         # 1. admission: one request joins at a time; its prompt is prefilled slice by slice, one slice per iteration
-        if self.joining is None:
+        if self._admit_hold is not None and len(self.running) < self._admit_hold:
+            self._admit_hold = None                        # somebody finished: try again
+        if self.joining is None and self._admit_hold is None:
             with self.lock:
                 head = self.queue[0] if self.queue else None
                 take = head is not None and ((self._batchable(head) and len(self.running) < self.max_batch) or (not self._batchable(head) and not self.running))
@@ -367,7 +375,10 @@ class Orchestrator:
                     try:
                         self.joining = self._begin(head)
                     except Exception as exc:  # noqa: BLE001
-                        self._fail(head, exc)
+                        if self.running and self._is_capacity_error(exc):
+                            self._wait_for_capacity(head)
+                        else:
+                            self._fail(head, exc)
         if self.joining is not None:
             did = True
             req, sid, prompt, _, d0 = self.joining
@@ -399,7 +410,10 @@ class Orchestrator:
                         eng.free_sequence(sid)
                     except Exception:  # noqa: BLE001
                         pass
-                self._fail(req, exc)
+                if self.running and self._is_capacity_error(exc):
+                    self._wait_for_capacity(req)          # nothing was emitted during the join: the prompt is simply fed again later
+                else:
+                    self._fail(req, exc)
         # 2. one token for every running request
         if self.running:
             did = True
@@ -407,6 +421,16 @@ class Orchestrator:
             try:
                 outs = self._with_pool_evict_retry(self.running[0][0], lambda: eng.decode(sids, toks))
             except Exception as exc:  # noqa: BLE001 - the step failed for the whole batch
+                if len(self.running) > 1 and self._is_capacity_error(exc):
+                    # out of KV pages in mid-decode: the youngest request gives its pages back and joins again later, its prompt
+                    # and the tokens it has produced fed as one prompt (greedy decoding: the continuation is the same); the step
+                    # is run again for the others
+                    req, sid, _ = self.running.pop()
+                    eng.free_sequence(sid)
+                    req.stats.preemptions += 1
+                    self.preemptions += 1
+                    self._wait_for_capacity(req)
+                    return True
                 for req, sid, _ in self.running:
                     eng.free_sequence(sid)
                     self._fail(req, exc)
@@ -426,14 +450,24 @@ class Orchestrator:
             self.running = keep
         return did
 
+    @staticmethod
+    def _is_capacity_error(exc: BaseException) -> bool:
+        return isinstance(exc, KvPoolExhausted) or "no free sequence slot" in str(exc)
+
+    def _wait_for_capacity(self, req: InferenceRequest):
+        with self.lock:
+            self.queue.appendleft(req)
+        self._admit_hold = len(self.running)
+        self.admission_waits += 1
+
     def _begin(self, req: InferenceRequest) -> list:
         """Prefix lookup and sequence of a joining greedy request: [request, sequence id, prompt, tokens already in the sequence]."""
         eng, st = self.engine, req.stats
-        st.t_start = time.time()
+        st.t_start = st.t_start or time.time()
         st.prompt_tokens = len(req.prompt_ids)
-        prompt = list(req.prompt_ids)
-        if not prompt:
+        if not req.prompt_ids:
             raise ValueError("empty prompt")
+        prompt = list(req.prompt_ids) + list(req.output_ids)      # a preempted request resumes behind what it has produced
         sid, cached = self.prefix.fork_from(prompt)
         if sid is None:
             sid = self._with_pool_evict_retry(req, eng.create_sequence)

@@ -633,3 +633,62 @@ def test_a_degraded_prefill_is_never_cached_and_is_retried_within_its_budget():
     o2.submit_request(r3)
     o2.step()
     assert r3.stats.degraded_retries == 0 and r3.stats.moe_degraded_steps == 1 and o2.prefix.holders() == 0
+
+
+def test_a_request_that_finds_no_kv_pages_waits_for_a_running_one_to_finish():
+    """Continuous batching under memory pressure: a joining request that cannot get KV pages (or a sequence slot) while others are
+    decoding goes back to the head of the queue and is admitted when one of them has finished; alone on the engine the same
+    shortage is an error."""
+    from layerstorm_b200.runtime.null_engine import NullEngine
+    from layerstorm_b200.serving.orchestrator import InferenceRequest, Orchestrator, SamplingParams
+    from layerstorm_b200.serving.prefix_cache import PrefixCacheConfig
+    eng = NullEngine(vocab=300, max_seqs=8, page=16, num_pages=10)       # 160 tokens of KV in total
+    orch = Orchestrator(eng, eos_token_ids=[1], max_batch=4, prefix_cache=PrefixCacheConfig(enabled=False))
+    a = InferenceRequest("a", [7] * 60, SamplingParams(max_tokens=20, ignore_eos=True))     # 5 pages
+    b = InferenceRequest("b", [8] * 60, SamplingParams(max_tokens=30, ignore_eos=True))     # 5 pages (6 after 20 tokens)
+    c = InferenceRequest("c", [9] * 40, SamplingParams(max_tokens=5, ignore_eos=True))      # 3 pages: does not fit beside a and b
+    for r in (a, b, c):
+        orch.submit_request(r)
+    for _ in range(300):
+        if not orch.step():
+            break
+    assert all(r.done.is_set() for r in (a, b, c)) and a.error is None and c.error is None and len(c.output_ids) == 5
+    assert orch.admission_waits >= 1 and c.stats.t_first_token >= a.stats.t_done - 1e-3     # c got in only after a had finished
+    assert b.error is None and len(b.output_ids) == 30
+    # alone on the engine a prompt that cannot fit is an error, not an endless wait
+    big = InferenceRequest("big", [5] * 400, SamplingParams(max_tokens=2, ignore_eos=True))
+    orch.submit_request(big)
+    for _ in range(20):
+        if not orch.step():
+            break
+    assert big.done.is_set() and big.error is not None
+
+
+def test_decode_that_runs_out_of_kv_pages_preempts_the_youngest_request_and_resumes_it():
+    """Two requests whose prompts fit but whose generations outgrow the pool: the younger one gives its pages back in mid-decode, joins
+    again behind what it has produced, and both deliver exactly the tokens they deliver when served alone."""
+    from layerstorm_b200.runtime.null_engine import NullEngine
+    from layerstorm_b200.serving.orchestrator import InferenceRequest, Orchestrator, SamplingParams
+    from layerstorm_b200.serving.prefix_cache import PrefixCacheConfig
+
+    def serve(reqs, pages, batch):
+        eng = NullEngine(vocab=300, max_seqs=8, page=16, num_pages=pages)
+        orch = Orchestrator(eng, eos_token_ids=[1], max_batch=batch, prefix_cache=PrefixCacheConfig(enabled=False))
+        for r in reqs:
+            orch.submit_request(r)
+        for _ in range(1000):
+            if not orch.step():
+                break
+        return orch
+
+    def mk():
+        return [InferenceRequest("a", [7] * 30, SamplingParams(max_tokens=60, ignore_eos=True)),      # 2 pages -> 6 pages
+                InferenceRequest("b", [8, 9] * 15, SamplingParams(max_tokens=60, ignore_eos=True))]
+    alone = mk()
+    serve(alone, 64, 1)
+    tight = mk()
+    orch = serve(tight, 9, 4)                                                                        # 12 pages would be needed side by side
+    assert orch.preemptions >= 1 and tight[1].stats.preemptions >= 1 and tight[0].stats.preemptions == 0
+    for x, y in zip(alone, tight):
+        assert y.error is None and y.output_ids == x.output_ids and len(y.output_ids) == 60
+    assert orch.engine.free_page_count() == 9

@@ -237,6 +237,45 @@ def build_engine(cfg: dict, shape: ModelConfig, ckpt: Optional[str], args: argpa
     return eng
 
 
+def build_block_draft(cfg: dict, shape: ModelConfig, target, args: argparse.Namespace):
+    """The DSpark block draft (``speculation/dspark.py``) when ``speculation.dspark.checkpoint_path`` is a speculators-format dspark
+    checkpoint, or - without a checkpoint - when ``speculation.dspark.aux_hidden_state_layer_ids`` is set (RANDOM draft weights of a
+    small geometry: plumbing and timing runs).  None when neither applies or the engine cannot report aux hidden states."""
+    from ..speculation import dspark as dsp
+    ds = cfg["speculation"]["dspark"]
+    path = ds["checkpoint_path"]
+    if path and not dsp.is_dspark_checkpoint(path):
+        return None
+    if not path and not ds["aux_hidden_state_layer_ids"]:
+        return None
+    if not hasattr(target, "enable_aux_capture") or int(os.environ.get("WORLD_SIZE", 1)) > 1:
+        log.warning("the block draft needs an engine that reports aux hidden states (one GPU); serving without it")
+        return None
+    import torch
+    if path:
+        dcfg, tensors = dsp.load_dspark_checkpoint(path)
+        for key, have in (("block_size", dcfg.block_size), ("markov_rank", dcfg.markov_rank), ("mask_token_id", dcfg.mask_token_id),
+                          ("draft_vocab_size", dcfg.draft_vocab_size), ("aux_hidden_state_layer_ids", dcfg.aux_hidden_state_layer_ids)):
+            if ds[key] and ds[key] != have:
+                log.warning("speculation.dspark.%s = %s, the checkpoint says %s: the checkpoint's value is used", key, ds[key], have)
+    else:
+        dcfg = dsp.draft_config_for_target(shape.hidden, shape.vocab, shape.n_layers, block_size=ds["block_size"], markov_rank=min(ds["markov_rank"], 64))
+        dcfg.aux_hidden_state_layer_ids = [int(l) for l in ds["aux_hidden_state_layer_ids"]]
+        log.warning("speculation.dspark.checkpoint_path is empty: RANDOM block-draft weights (%d layers, aux layers %s)", dcfg.num_hidden_layers,
+                    dcfg.aux_hidden_state_layer_ids)
+        tensors = dsp.random_dspark_tensors(dcfg, 0)
+    dev = torch.device("cuda", int(ds["draft_gpus"][0])) if ds["draft_gpus"] else target.dev
+    cap = min(cfg["serving"]["max_sequence_length"], max(ds["draft_context_capacity_tokens"], 4 * dcfg.block_size))
+    try:
+        bb = dsp.DsparkBackbone(dcfg, tensors, dev, torch.bfloat16, ctx_capacity=cap, rotate=ds["ctx_rotate"])
+        return dsp.DeviceDsparkDraft(target, bb, {"speculative_tokens": ds["speculative_tokens"], "confidence_enabled": ds["confidence_enabled"] and dcfg.enable_confidence_head,
+                                                  "confidence_threshold": ds["confidence_threshold"]},
+                                     max_contexts=int(os.environ.get("LSB_DSPARK_CONTEXTS", "4")), output_of_layer=os.environ.get("LSB_DSPARK_AUX_OUTPUT", "0") == "1")
+    except (NotImplementedError, ValueError) as e:
+        log.warning("block draft unavailable (%s); serving without it", e)
+        return None
+
+
 def build_model_draft(cfg: dict, shape: ModelConfig, engine, args: argparse.Namespace):
     """(draft, depth) for the model-backed speculation methods.
     ``self_speculative``: the target drafts for itself with ``speculation.self_speculative.draft_expert_count`` routed experts per token.
@@ -266,6 +305,13 @@ def build_model_draft(cfg: dict, shape: ModelConfig, engine, args: argparse.Name
             return None, 0
     ds = sp["dspark"]
     depth = args.speculation_depth if args.speculation_depth is not None else ds["speculative_tokens"]
+    block = build_block_draft(cfg, shape, target, args)
+    if block is not None:
+        return block, min(depth, block.max_tokens)
+    if ds["checkpoint_path"]:
+        from ..speculation.dspark import is_dspark_checkpoint
+        if is_dspark_checkpoint(ds["checkpoint_path"]):
+            return None, 0                                   # a block-draft checkpoint is no autoregressive draft model
     if args.test_engine:
         from ..runtime.null_engine import NullEngine
         return EngineDraft(NullEngine(vocab=target.vocab, max_seqs=2, max_ctx=target.max_ctx), max_gamma=depth), depth

@@ -688,6 +688,7 @@ class DeviceModel:
         self.idx_identity = False  # the indexer's key cache keeps a page table of its own (row-granular KV tiering: its pages never leave HBM)
         self.skip_layers = frozenset()   # layers whose attention + FFN a step leaves out (self-speculative drafting; never the first or last)
         self.probe = None                # {"prev": bf16 [1, hidden], "sims": fp32 [n_layers]} while layer-input similarities are recorded
+        self.aux_capture = None          # {"slots": {layer: column}, "buf": bf16 [rows, n_aux, hidden]}: layer inputs kept for a block draft model
         self.row_tier = None      # RowTiering (runtime/kv_tiering.py) when old KV pages of active sequences live in pinned host memory
         self.streamer = None      # ExpertStreamer when the VRAM expert cache is capped (runtime/streaming.py)
         self.drift = None         # dict: eager steps store every layer's output rows here (input of utils/determinism_probe.py drift)
@@ -1387,6 +1388,38 @@ class DeviceModel:
         nat.call("lsb_mhc_post_pre", ws.x, ws.resid, ws.sub, ws.post, ws.comb, fn, sc, base, norm_w, ws.part, R, H, n,
                  mode, cfg.hc_sinkhorn_iters, cfg.hc_eps, cfg.rms_eps, cfg.hc_post_mult, ws.hc_done, ws.hc_pre, self._cp)
 
+    def set_aux_capture(self, layer_ids=(), rows: int = 0):
+        """Keep, for every step from now on, the stream that ENTERS each layer of ``layer_ids`` (hyper-connection models: the mean over
+        the residual streams; ``n_layers`` = the stream leaving the last layer, models without hyper-connections only) for the step's
+        rows: ``aux_capture["buf"][:R].view(R, -1)`` is the concatenation in the order of ``layer_ids`` - the features a block draft
+        model is conditioned on (``speculation/dspark.py``).  The copies are part of the step (and of its CUDA graph): the caller
+        drops graphs captured before.  An empty ``layer_ids`` switches the capture off.
+        Reference: the aux-hidden export hook in front of every layer's attention (src/daemon/dispatch_forward.cpp)."""
+        ids = [int(l) for l in layer_ids]
+        if not ids:
+            self.aux_capture = None
+            return
+        n = self.cfg.n_layers
+        if self.tp_size > 1:
+            raise NotImplementedError("aux hidden capture is built for one GPU")
+        if any(l < 0 or l > n or (l == n and self.cfg.mhc) for l in ids) or len(set(ids)) != len(ids):
+            raise ValueError(f"aux layers {ids} do not fit a model of {n} layers" + (" with hyper-connections (no un-normalised final stream)" if self.cfg.mhc else ""))
+        self.aux_capture = {"slots": {l: j for j, l in enumerate(ids)},
+                            "buf": torch.zeros(max(1, int(rows)), len(ids), self.cfg.hidden, dtype=torch.bfloat16, device=self.device)}
+
+    def _capture_aux(self, i: int, ws: Workspace, R: int):
+        ac = self.aux_capture
+        j = ac["slots"].get(i)
+        if j is None:
+            return
+        if R > ac["buf"].shape[0]:
+            raise RuntimeError(f"a step of {R} rows exceeds the aux capture buffer ({ac['buf'].shape[0]} rows)")
+        H = self.cfg.hidden
+        if self.cfg.mhc:
+            ac["buf"][:R, j].copy_(ws.resid[:R].mean(1))
+        else:
+            ac["buf"][:R, j].copy_(ws.resid.view(-1)[: ws.R * H].view(ws.R, H)[:R])
+
     def set_layer_skip(self, skip=(), probe: bool = False):
         """Layer skipping for draft passes: ``skip`` = layers to leave out (the first and the last layer are never skipped), ``probe`` =
         record, per executed layer l, the cosine similarity between the normalised input of l and of the next executed layer (row 0 of
@@ -1441,6 +1474,8 @@ class DeviceModel:
                     continue                 # the pending sublayer output, its gates and the residual streams wait for the next executed pass
                 self._hc_pass(L["hc_attn"], L["attn_norm"], ws, R, 0 if i == 0 else 1, clus, pending, None)
                 pending = None
+                if self.aux_capture is not None:
+                    self._capture_aux(i, ws, R)          # the residual streams now hold what enters layer i
                 last_run = self._probe_input(i, ws, last_run)
                 if cfg.is_kda_layer(i):
                     self._kda(i, L, ws, R, nseq)
@@ -1461,6 +1496,8 @@ class DeviceModel:
             last_run = -1
             for i, L in enumerate(self.layers):
                 nxt = self.layers[i + 1]["attn_norm"] if i + 1 < cfg.n_layers else self.final_norm
+                if self.aux_capture is not None:
+                    self._capture_aux(i, ws, R)
                 if i in self.skip_layers:
                     # the residual stays as it is; only the normalisation weights change to the next layer's
                     nat.call("lsb_rmsnorm", ws.x, resid, nxt, R, H, H, H, cfg.rms_eps, 1, None)
@@ -1475,6 +1512,8 @@ class DeviceModel:
                 nat.call("lsb_add_rmsnorm", ws.x, resid, ws.sub, nxt, R, H, cfg.rms_eps, self._cp)
                 if self.drift is not None:
                     self.drift[f"layer{i:03d}.resid"] = resid[:R].float().cpu()
+            if self.aux_capture is not None:
+                self._capture_aux(cfg.n_layers, ws, R)
         xr = ws.x[logit_row0: logit_row0 + n_logit_rows]
         self.head(ws.logits, xr, n_logit_rows)
         if self.drift is not None:

@@ -272,7 +272,10 @@ class Oracle:
 
     # ---------------- full forward ----------------
     def forward(self, ids: torch.Tensor, pos: Optional[torch.Tensor] = None, sel_override: Optional[dict] = None,
-                trace: Optional[list] = None, return_hidden: bool = False):
+                trace: Optional[list] = None, return_hidden: bool = False, aux: Optional[dict] = None):
+        """``aux``: a dict whose keys are layer numbers; each gets the stream that ENTERS that layer ([T, hidden]; hyper-connection
+        models: the mean over the residual streams), key ``n_layers`` the stream that leaves the last layer - the features a block
+        draft model is conditioned on (``speculation/dspark.py``)."""
         cfg, w = self.cfg, self.w
         ids = torch.as_tensor(ids, dtype=torch.long)
         T = ids.shape[0]
@@ -288,6 +291,8 @@ class Oracle:
                 p = f"layers.{i}."
                 if post is not None:
                     residual = self.mhc_post(x_out, residual, post, comb)
+                if aux is not None and i in aux:
+                    aux[i] = residual.mean(1)
                 post, comb, x = self.mhc_pre(residual, w[p + "hc_attn.fn"], w[p + "hc_attn.scale"], w[p + "hc_attn.base"], w[p + "attn_norm.weight"])
                 a = self.kda(i, x) if cfg.is_kda_layer(i) else self.mla(i, x, pos, (sel_override or {}).get(i))
                 residual = self.mhc_post(a, residual, post, comb)
@@ -300,6 +305,8 @@ class Oracle:
             resid = h
             for i in range(cfg.n_layers):
                 p = f"layers.{i}."
+                if aux is not None and i in aux:
+                    aux[i] = resid.clone()
                 x = rmsnorm(resid, w[p + "attn_norm.weight"], cfg.rms_eps)
                 a = self.kda(i, x) if cfg.is_kda_layer(i) else self.mla(i, x, pos, (sel_override or {}).get(i))
                 resid = resid + a
@@ -308,6 +315,8 @@ class Oracle:
                 if trace is not None:
                     trace.append(resid.clone())
             final = resid
+        if aux is not None and cfg.n_layers in aux:
+            aux[cfg.n_layers] = final.clone()
         logits = rmsnorm(final, w["final_norm.weight"], cfg.rms_eps) @ w["head.weight"].T
         return (logits, final) if return_hidden else logits        # ``final``: the stream before the output norm (input of the MTP blocks)
 

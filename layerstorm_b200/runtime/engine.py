@@ -102,6 +102,7 @@ class Engine:
         self.d2h_bytes = 0
         self.kernel_launches = 0
         self.mtp = None               # MtpRunner once enable_mtp() was called (runtime/mtp.py)
+        self.aux_listener = None      # object with on_rows / on_rewind / on_fork / on_free once enable_aux_capture() was called
 
     # ------------------------------------------------------------------ boot-time memory carve
     def _carve_report(self) -> dict:
@@ -198,6 +199,8 @@ class Engine:
         s = self.seqs.pop(sid)
         if self.mtp is not None:
             self.mtp.on_free(sid)
+        if self.aux_listener is not None:
+            self.aux_listener.on_free(sid)
         if self.row_tier is not None:
             self.row_tier.on_free(sid)
         self.pa.destroy(s.slot)
@@ -249,6 +252,8 @@ class Engine:
             self._sync_block_table(cs)
             if self.mtp is not None:
                 self.mtp.on_fork(parent, slot, prefix_len)
+            if self.aux_listener is not None:
+                self.aux_listener.on_fork(parent, slot, prefix_len)
         return slot
 
     # ------------------------------------------------------------------ KV tiering (hibernate / resume)
@@ -453,6 +458,8 @@ class Engine:
         del s.tokens[length:]
         if self.mtp is not None:
             self.mtp.on_rewind(sid, length)
+        if self.aux_listener is not None:
+            self.aux_listener.on_rewind(sid, length)
         self.pa.rewind(s.slot, length)
         s.pages = self.pa.pages(s.slot)
         if replay:
@@ -545,6 +552,8 @@ class Engine:
                 self.model.argmax(ws, 1)
                 if self.mtp is not None:
                     self.mtp.after_prefill_chunk(sid, ws, chunk, s.length, tokens[c0 + R] if c0 + R < len(tokens) else None)
+                if self.aux_listener is not None:
+                    self._aux_rows(sid, 0, R, s.length, chunk)
                 self.kernel_launches += nat.launch_count() - n0
                 s.length += R
                 s.tokens.extend(chunk)
@@ -594,6 +603,8 @@ class Engine:
             self.kernel_launches += nat.launch_count() - n0
             if self.mtp is not None:
                 self.mtp.stash_rows(sid, ws, 0, R, s.length)
+            if self.aux_listener is not None and commit:
+                self._aux_rows(sid, 0, R, s.length, tokens)
             self._queue_error_readback()
             self.stream.synchronize()
             self._check_errors()
@@ -640,6 +651,8 @@ class Engine:
             self.kernel_launches += nat.launch_count() - n0
             if self.mtp is not None:
                 self.mtp.stash_rows(sid, ws, 0, R, s.length)
+            if self.aux_listener is not None:
+                self._aux_rows(sid, 0, R, s.length, rows_tok)       # all rows; the rewind below takes the rejected ones back
             self.h_out[:2].copy_(ws.verify_out, non_blocking=True)
             self.d2h_bytes += 8
             self._queue_error_readback()
@@ -651,6 +664,23 @@ class Engine:
         if n_acc < gamma:
             self.rewind(sid, s.length - (gamma - n_acc))
         return n_acc, nxt
+
+    def enable_aux_capture(self, layer_ids, listener):
+        """From now on every committed step hands the target's hidden states at ``layer_ids`` to ``listener``:
+        ``listener.on_rows(sid, first_position, aux [rows, len(layer_ids) * hidden], tokens)`` right after the step's kernels were
+        queued, on the engine's stream (the view is overwritten by the next step: the listener consumes it there and then), plus
+        ``on_rewind(sid, length)``, ``on_fork(parent, child, prefix_len)`` and ``on_free(sid)``.  One GPU; steps that are not
+        committed (``forward_rows(commit=False)``) are not reported.  Used by the block draft (``speculation/dspark.py``)."""
+        if self.row_tier is not None or getattr(self.model, "dcp", None) is not None:
+            raise NotImplementedError("aux hidden capture needs an untiered, unsharded KV cache")
+        self.model.set_aux_capture(layer_ids, max(self.prefill_chunk, self.max_batch, 64))
+        self.graphs.clear()                  # graphs captured so far do not contain the copies
+        self.graph_launches.clear()
+        self.aux_listener = listener
+
+    def _aux_rows(self, sid: int, row0: int, n: int, pos0: int, tokens):
+        buf = self.model.aux_capture["buf"]
+        self.aux_listener.on_rows(sid, pos0, buf[row0: row0 + n].view(n, -1), tokens)
 
     def enable_mtp(self):
         """Keep the model's multi-token-prediction block in step with every sequence from now on (``runtime/mtp.py``) so that
@@ -731,6 +761,9 @@ class Engine:
             if self.mtp is not None:
                 for j, sid in enumerate(sids):
                     self.mtp.stash_rows(sid, ws, j, 1, self.seqs[sid].length)
+            if self.aux_listener is not None:
+                for j, (sid, tok) in enumerate(zip(sids, tokens)):
+                    self._aux_rows(sid, j, 1, self.seqs[sid].length, [int(tok)])
             if sample is not None:
                 if not self.supports_device_sampling:
                     raise RuntimeError("device sampling needs the full vocabulary on one GPU")

@@ -373,3 +373,69 @@ def test_continuous_batching_on_the_gpu_engine_matches_sequential_serving():
     got, orch = serve(4)
     assert got == want
     assert 0 < orch.batched_steps < sum(gens) - len(gens)
+
+
+@pytest.mark.parametrize("name,graph", [("tiny-mla-moe", False), ("tiny-mla-moe", True), ("tiny-glm5-next", False)])
+def test_aux_hidden_capture_feeds_a_block_draft_that_matches_the_cpu_draft_and_stays_lossless(name, graph):
+    """The engine reports the stream entering the aux layers of every committed step (prefill chunks, verify steps with rejected
+    rows, decode steps - eager and as a CUDA graph); the block draft's context built from those reports equals the one built from
+    the fp32 reference model's hidden states, so both propose the same block, and greedy speculation with the block draft reproduces
+    plain greedy decoding."""
+    from layerstorm_b200.models.config import get_preset
+    from layerstorm_b200.models.device_model import DeviceModel
+    from layerstorm_b200.models.reference import Oracle
+    from layerstorm_b200.models.weights import init_weights
+    from layerstorm_b200.runtime.engine import Engine
+    from layerstorm_b200.speculation import dspark as dsp
+    cfg = get_preset(name)
+    m = DeviceModel.from_state_dict(cfg, init_weights(cfg, 3), "cuda", kv_fmt="bf16", page=16, expert_quant="bf16", dense_quant="bf16")
+    oracle = Oracle(cfg, m.effective_state_dict())
+    prompt = torch.randint(0, cfg.vocab, (27,), generator=torch.Generator().manual_seed(4)).tolist()
+
+    plain = Engine(m, max_seqs=2, max_ctx=128, prefill_chunk=8, max_batch=1, use_graph=False)
+    s0 = plain.create_sequence()
+    want = [plain.prefill(s0, prompt)]
+    for _ in range(11):
+        want.append(plain.decode([s0], [want[-1]])[0])
+    plain.free_sequence(s0)
+
+    dc = dsp.draft_config_for_target(cfg.hidden, cfg.vocab, cfg.n_layers, layers=2, head_dim=16, block_size=5, markov_rank=8, n_aux=2)
+    tens = dsp.random_dspark_tensors(dc, 1)
+    eng = Engine(m, max_seqs=3, max_ctx=128, prefill_chunk=8, max_batch=1, use_graph=graph)
+    dev = dsp.DeviceDsparkDraft(eng, dsp.DsparkBackbone(dc, tens, "cuda", torch.float32, ctx_capacity=128), {"speculative_tokens": 4})
+    ref = dsp.DsparkDraft(dsp.DsparkBackbone(dc, tens, "cpu", torch.float32, ctx_capacity=128), dsp.oracle_aux_provider(oracle, dc.aux_hidden_state_layer_ids),
+                          {"speculative_tokens": 4})
+    seen = []
+    inner = dev.on_rows
+    dev.on_rows = lambda sid, pos0, aux, toks: (seen.append((pos0, aux.float().cpu().clone())), inner(sid, pos0, aux, toks))[1]
+    sid = eng.create_sequence()
+    tok = eng.prefill(sid, prompt)
+    assert tok == want[0] and [p for p, _ in seen] == [0, 8, 16, 24]
+    aux_ref = dsp.oracle_aux_provider(oracle, dc.aux_hidden_state_layer_ids)(prompt, 0)
+    got_aux = torch.cat([a for _, a in seen])
+    assert got_aux.shape == aux_ref.shape and float((got_aux - aux_ref).abs().max() / aux_ref.abs().max()) < 3e-2
+    got, ctx, rounds = [tok], prompt + [tok], 0
+    while len(got) < 12:
+        d = dev.propose(ctx, 4)
+        assert len(d) == 4
+        c = dev.ctx[sid]
+        rc_ok = ref._follow(ctx[:-1])
+        assert rc_ok and c.length == ref.ctx.length == len(ctx) - 1
+        kd, kr = c.k[:, : c.length].float().cpu(), ref.ctx.k[:, : c.length]
+        assert float((kd - kr).abs().max() / kr.abs().max()) < 5e-2                  # bf16 hidden states against the fp32 model's
+        if rounds % 3 == 2:
+            tok = eng.decode([sid], [tok])[0]
+            new = [tok]
+        else:
+            n_acc, nxt = eng.verify_greedy(sid, tok, d)                               # random draft: mostly rejected rows, overwritten next step
+            new = d[:n_acc] + [nxt]
+            tok = nxt
+        rounds += 1
+        got += new
+        ctx += new
+    assert got[:12] == want[:12]
+    # a fork shares the parent's rows; freeing returns the context
+    child = eng.fork_sequence(sid)
+    assert dev.propose(ctx, 3) != [] and child in dev.ctx and dev.ctx[child].length == dev.ctx[sid].length
+    eng.free_sequence(child)
+    assert child not in dev.ctx and len(dev._spare) == 1

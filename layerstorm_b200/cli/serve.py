@@ -269,7 +269,8 @@ def build_block_draft(cfg: dict, shape: ModelConfig, target, args: argparse.Name
     try:
         bb = dsp.DsparkBackbone(dcfg, tensors, dev, torch.bfloat16, ctx_capacity=cap, rotate=ds["ctx_rotate"])
         return dsp.DeviceDsparkDraft(target, bb, {"speculative_tokens": ds["speculative_tokens"], "confidence_enabled": ds["confidence_enabled"] and dcfg.enable_confidence_head,
-                                                  "confidence_threshold": ds["confidence_threshold"]},
+                                                  "confidence_threshold": ds["confidence_threshold"], "scheduler_mode": ds["scheduler_mode"],
+                                                  "sts_temperatures": ds["sts_temperatures"]},
                                      max_contexts=int(os.environ.get("LSB_DSPARK_CONTEXTS", "4")), output_of_layer=os.environ.get("LSB_DSPARK_AUX_OUTPUT", "0") == "1")
     except (NotImplementedError, ValueError) as e:
         log.warning("block draft unavailable (%s); serving without it", e)

@@ -429,6 +429,110 @@ class DsparkBackbone:
         return ids, conf
 
 
+# ------------------------------------------------------------------------------------------------------------- how much of a block to verify
+class DsparkScheduler:
+    """Decides, per round, how many of the block's tokens go to the target (``speculation.dspark.scheduler_mode``):
+      ``off``               all of them;
+      ``static_threshold``  the longest prefix whose cumulative survival stays at or above ``confidence_threshold``;
+      ``throughput``        the prefix that maximises expected committed tokens per unit of verify cost:
+                            (1 + sum_{j<=k} a_j) / (1 + row_cost * k), a_j = survival of position j, row_cost = what one more verify
+                            row costs relative to a one-row step (decode steps on this GPU are bound by the weight sweep, so a row is
+                            a few per cent of a step; the block pass is already paid when the choice is made).
+    Survival of position j = product of the confidence head's conditional probabilities c_1 .. c_j, each first temperature-scaled
+    on the logit (``sts_temperatures``, fitted offline by ``verify_plan.fit_sts_temperatures`` on the trace kept here); without a
+    confidence head (or with it switched off) the running acceptance rate p stands in: a_j = p^j.
+    Reference: python/orchestrator/dspark_draft.py (survival confidences, STS temperatures, acceptance EMA, confidence trace)."""
+
+    def __init__(self, cfg: Optional[dict] = None):
+        cfg = cfg or {}
+        self.mode = cfg.get("scheduler_mode", "off")
+        if self.mode not in ("off", "static_threshold", "throughput"):
+            raise ValueError(f"speculation.dspark.scheduler_mode {self.mode!r}")
+        self.use_head = bool(cfg.get("confidence_enabled", False))
+        if self.use_head and self.mode == "off":
+            self.mode = "static_threshold"                 # confidence_enabled alone means: cut at the threshold
+        self.threshold = float(cfg.get("confidence_threshold", 0.5))
+        self.temps = [float(t) for t in cfg.get("sts_temperatures") or []]
+        self.alpha = float(cfg.get("acceptance_ema_alpha", 0.3))
+        self.row_cost = float(cfg.get("verify_row_cost", 0.03))
+        self.trace_capacity = int(cfg.get("confidence_trace_capacity", 4096))
+        self.trace: List[Tuple[Tuple[float, ...], int]] = []
+        self.ema = 0.5                                     # the uninformed prior; every round moves it by ``acceptance_ema_alpha``
+        self.probe_every = int(cfg.get("probe_every_rounds", 16))
+        self._idle = 0
+        self.rounds = self.proposed = self.accepted = 0
+
+    def proxy(self) -> float:
+        return self.ema
+
+    def survival(self, conf: Sequence[float], n: int) -> List[float]:
+        from .verify_plan import apply_temperature
+        out, a = [], 1.0
+        if self.use_head and len(conf) >= n:
+            for k in range(n):
+                c = min(max(float(conf[k]), 0.0), 1.0)
+                if k < len(self.temps) and self.temps[k] != 1.0:
+                    c = float(apply_temperature(c, self.temps[k]))
+                a *= c
+                out.append(a)
+        else:
+            p = self.proxy()
+            for _ in range(n):
+                a *= p
+                out.append(a)
+        return out
+
+    def depth(self, conf: Sequence[float], n: int) -> int:
+        if self.mode == "off" or n <= 0:
+            return n
+        k = self._choose(self.survival(conf, n), n)
+        if k == 0:
+            # nothing verified means nothing learned: every ``probe_every`` such rounds one token goes through anyway, so that an
+            # acceptance rate that has recovered (another topic, another request) is noticed
+            self._idle += 1
+            if self.probe_every > 0 and self._idle >= self.probe_every:
+                self._idle, k = 0, 1
+        else:
+            self._idle = 0
+        return k
+
+    def _choose(self, a: Sequence[float], n: int) -> int:
+        if self.mode == "static_threshold":
+            k = 0
+            while k < n and a[k] >= self.threshold:
+                k += 1
+            return k
+        best_k, best, tot = 0, 1.0, 1.0
+        for k in range(1, n + 1):
+            tot += a[k - 1]
+            v = tot / (1.0 + self.row_cost * k)
+            if v > best + 1e-12:
+                best_k, best = k, v
+        return best_k
+
+    def record(self, conf: Sequence[float], proposed: int, accepted: int):
+        if proposed <= 0:
+            return
+        accepted = min(max(int(accepted), 0), proposed)
+        self.rounds += 1
+        self.proposed += proposed
+        self.accepted += accepted
+        if self.use_head and len(conf) >= proposed:
+            self.trace.append((tuple(float(c) for c in conf[:proposed]), accepted))
+            if len(self.trace) > self.trace_capacity:
+                del self.trace[: len(self.trace) - self.trace_capacity]
+        # per-token acceptance of the positions that were actually decided (the first rejected one included)
+        rate = accepted / min(proposed, accepted + 1)
+        self.ema = self.alpha * rate + (1.0 - self.alpha) * self.ema
+
+    def fit_temperatures(self, gamma: Optional[int] = None) -> List[float]:
+        """Refit the per-position temperatures on the recorded rounds and use them from now on."""
+        from .verify_plan import fit_sts_temperatures
+        g = gamma or max((len(c) for c, _ in self.trace), default=0)
+        self.temps = fit_sts_temperatures(self.trace, g) if g else []
+        return self.temps
+
+
 # ------------------------------------------------------------------------------------------------------------- draft sources
 class DsparkDraft:
     """``speculation.method = dspark`` as a draft source of the serving loop: ``propose(context, gamma)``.
@@ -445,7 +549,7 @@ class DsparkDraft:
         self.aux_of = aux_of
         self.ctx = backbone.new_context()
         self.max_tokens = min(int(cfg.get("speculative_tokens", backbone.cfg.speculative_tokens)), backbone.cfg.block_size - 1)
-        self.threshold = float(cfg.get("confidence_threshold", 0.0)) if cfg.get("confidence_enabled") else 0.0
+        self.sched = DsparkScheduler(dict(cfg, confidence_enabled=bool(cfg.get("confidence_enabled")) and backbone.confidence is not None))
         self.proposed = self.accepted = self.failures = 0
         self.last_confidences: List[float] = []
 
@@ -473,16 +577,18 @@ class DsparkDraft:
         try:
             if not self._follow(committed):
                 return []
-            ids, self.last_confidences = self.bb.draft(self.ctx, anchor, len(committed), n, self.threshold)
+            ids, self.last_confidences = self.bb.draft(self.ctx, anchor, len(committed), n)
         except (RuntimeError, ValueError):
             self.failures += 1
             self.ctx.reset()
             return []
+        ids = ids[: self.sched.depth(self.last_confidences, len(ids))]
         self.proposed += len(ids)
         return ids
 
     def feedback(self, proposed: int, accepted: int):
         self.accepted += accepted
+        self.sched.record(self.last_confidences, proposed, accepted)
 
     def acceptance_rate(self) -> float:
         return self.accepted / self.proposed if self.proposed else 0.0
@@ -520,7 +626,7 @@ class DeviceDsparkDraft:
             raise ValueError(f"the draft was trained for hidden {backbone.cfg.hidden_size} / vocabulary {backbone.cfg.vocab_size}, the target has "
                              f"{engine.cfg.hidden} / {engine.cfg.vocab}")
         self.max_tokens = min(int(cfg.get("speculative_tokens", backbone.cfg.speculative_tokens)), backbone.cfg.block_size - 1)
-        self.threshold = float(cfg.get("confidence_threshold", 0.0)) if cfg.get("confidence_enabled") else 0.0
+        self.sched = DsparkScheduler(dict(cfg, confidence_enabled=bool(cfg.get("confidence_enabled")) and backbone.confidence is not None))
         self.max_contexts = max(1, int(max_contexts))
         self.ctx: Dict[int, DsparkContext] = {}
         self._spare: List[DsparkContext] = []
@@ -595,17 +701,19 @@ class DeviceDsparkDraft:
         try:
             stream = getattr(self.engine, "stream", None)
             with (torch.cuda.stream(stream) if stream is not None else contextlib.nullcontext()):
-                ids, self.last_confidences = self.bb.draft(c, int(context[-1]), c.length, n, self.threshold)
+                ids, self.last_confidences = self.bb.draft(c, int(context[-1]), c.length, n)
         except (RuntimeError, ValueError):
             self.failures += 1
             c.valid = False
             return []
         self._used[sid] = self._use = self._use + 1
+        ids = ids[: self.sched.depth(self.last_confidences, len(ids))]
         self.proposed += len(ids)
         return ids
 
     def feedback(self, proposed: int, accepted: int):
         self.accepted += accepted
+        self.sched.record(self.last_confidences, proposed, accepted)
 
     def acceptance_rate(self) -> float:
         return self.accepted / self.proposed if self.proposed else 0.0

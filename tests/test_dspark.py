@@ -474,3 +474,80 @@ def test_serve_builds_the_block_draft_from_a_checkpoint_or_random_weights(tmp_pa
     # mistaken for an autoregressive draft model
     assert build_block_draft(load_config(None, {"speculation.method": "dspark"}, check=False), mc, eng, args) is None
     assert build_model_draft(cfg, mc, object(), args) == (None, 0)
+
+
+def test_scheduler_modes_choose_the_verified_prefix():
+    from layerstorm_b200.speculation.dspark import DsparkScheduler
+    conf = [0.9, 0.8, 0.5, 0.9, 0.2]
+    assert DsparkScheduler({}).depth(conf, 5) == 5                                              # off: the whole block
+    st = DsparkScheduler({"confidence_enabled": True, "confidence_threshold": 0.5})            # the head alone means: cut at the threshold
+    assert st.mode == "static_threshold" and st.survival(conf, 5) == pytest.approx([0.9, 0.72, 0.36, 0.324, 0.0648]) and st.depth(conf, 5) == 2
+    assert DsparkScheduler({"confidence_enabled": True, "scheduler_mode": "static_threshold", "confidence_threshold": 0.3}).depth(conf, 5) == 4
+    # throughput: one more row is verified while it raises expected tokens per unit of verify cost
+    cheap = DsparkScheduler({"confidence_enabled": True, "scheduler_mode": "throughput", "verify_row_cost": 0.03})
+    dear = DsparkScheduler({"confidence_enabled": True, "scheduler_mode": "throughput", "verify_row_cost": 0.4})
+    a = cheap.survival(conf, 5)
+    ratio = lambda k, rc: (1 + sum(a[:k])) / (1 + rc * k)                                      # noqa: E731
+    assert cheap.depth(conf, 5) == max(range(6), key=lambda k: ratio(k, 0.03)) == 4      # the fifth row (survival 0.06) costs more than it brings
+    assert dear.depth(conf, 5) == max(range(6), key=lambda k: ratio(k, 0.4)) == 2
+    assert dear.depth([0.2, 0.9, 0.9], 3) == 0                                                 # a block that starts badly is not worth a wide step
+    # temperatures reshape each conditional probability on the logit before the product
+    hot = DsparkScheduler({"confidence_enabled": True, "confidence_threshold": 0.5, "sts_temperatures": [2.0, 2.0, 2.0, 2.0, 2.0]})
+    assert hot.survival([0.9], 1)[0] == pytest.approx(1 / (1 + math.exp(-math.log(9) / 2))) and hot.depth(conf, 5) < st.depth(conf, 5) + 1
+    # without a confidence head the running acceptance rate stands in: a_j = p^j
+    px = DsparkScheduler({"scheduler_mode": "static_threshold", "confidence_threshold": 0.3})
+    assert px.proxy() == 0.5 and px.depth([], 5) == 1
+    for _ in range(12):
+        px.record([], 4, 4)
+    assert px.proxy() > 0.99 and px.depth([], 5) == 5
+    px.record([], 4, 0)
+    assert px.proxy() == pytest.approx(0.7, abs=0.01) and px.depth([], 5) == 3                  # 0.7^3 = 0.343 >= 0.3 > 0.7^4
+    # a draft that keeps failing is not verified at all - except for one token every few rounds, so that a recovery is noticed
+    for _ in range(12):
+        px.record([], 1, 0)
+    assert px.proxy() < 0.05 and [px.depth([], 5) for _ in range(32)].count(1) == 2 and px.probe_every == 16
+    # the trace of (confidences, accepted) rounds feeds the temperature fit: an over-confident head is cooled down
+    g = torch.Generator().manual_seed(0)
+    over = DsparkScheduler({"confidence_enabled": True, "confidence_trace_capacity": 300})
+    for _ in range(400):
+        c = (0.80 + 0.15 * torch.rand(3, generator=g)).tolist()
+        acc = 0
+        for k in range(3):
+            if float(torch.rand(1, generator=g)) < 0.55:                                        # the draft is right far less often than it claims
+                acc += 1
+            else:
+                break
+        over.record(c, 3, acc)
+    assert len(over.trace) == 300 and over.rounds == 400
+    temps = over.fit_temperatures()
+    assert len(temps) == 3 and temps[0] > 1.5 and over.survival([0.9], 1)[0] < 0.8
+    with pytest.raises(ValueError):
+        DsparkScheduler({"scheduler_mode": "fastest"})
+
+
+def test_draft_source_applies_the_scheduler_and_learns_from_feedback():
+    cfg, w, eng = _target()
+    dc = draft_config_for_target(cfg.hidden, cfg.vocab, cfg.n_layers, layers=1, head_dim=16, block_size=5, markov_rank=8, n_aux=2)
+    bb = DsparkBackbone(dc, random_dspark_tensors(dc, 1, dtype=torch.float32), "cpu", torch.float32, ctx_capacity=64)
+    aux_of = oracle_aux_provider(eng.model, dc.aux_hidden_state_layer_ids)
+    ctx = list(range(9, 30))
+    full = DsparkDraft(bb, aux_of, {"speculative_tokens": 4}).propose(ctx, 4)
+    cut = DsparkDraft(bb, aux_of, {"speculative_tokens": 4, "confidence_enabled": True, "confidence_threshold": 0.3})
+    got = cut.propose(ctx, 4)
+    surv, keep = 1.0, 0
+    for c in cut.last_confidences:
+        surv *= c
+        if surv < 0.3:
+            break
+        keep += 1
+    assert len(cut.last_confidences) == 4 and got == full[:keep] and keep < 4
+    cut.feedback(len(got), 0)
+    assert cut.sched.rounds == (1 if got else 0) and (not got or cut.sched.trace[-1] == (tuple(cut.last_confidences[: len(got)]), 0))
+    # no confidence head in the checkpoint: confidence_enabled falls back to the acceptance proxy instead of failing
+    plain_cfg = dataclasses.replace(dc, enable_confidence_head=False, confidence_head_with_markov=False)
+    pb = DsparkBackbone(plain_cfg, random_dspark_tensors(plain_cfg, 1, dtype=torch.float32), "cpu", torch.float32, ctx_capacity=64)
+    pd = DsparkDraft(pb, aux_of, {"speculative_tokens": 4, "confidence_enabled": True, "scheduler_mode": "static_threshold", "confidence_threshold": 0.2})
+    assert not pd.sched.use_head and len(pd.propose(ctx, 4)) == 2                               # 0.5^2 = 0.25 >= 0.2 > 0.5^3
+    pd.feedback(2, 0)
+    pd.feedback(2, 0)
+    assert pd.sched.proxy() == pytest.approx(0.245) and len(pd.propose(ctx, 4)) == 1            # one token clears 0.2, two do not

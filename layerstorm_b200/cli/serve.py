@@ -267,7 +267,10 @@ def build_block_draft(cfg: dict, shape: ModelConfig, target, args: argparse.Name
     dev = torch.device("cuda", int(ds["draft_gpus"][0])) if ds["draft_gpus"] else target.dev
     cap = min(cfg["serving"]["max_sequence_length"], max(ds["draft_context_capacity_tokens"], 4 * dcfg.block_size))
     try:
-        bb = dsp.DsparkBackbone(dcfg, tensors, dev, torch.bfloat16, ctx_capacity=cap, rotate=ds["ctx_rotate"])
+        # on the GPU the draft's matrices are stored as speculation.dspark.draft_weights_quant and applied by the framework's own kernels
+        # (LSB_DSPARK_TORCH_GEMM=1: library GEMMs over bf16 tensors instead)
+        kernels = ds["draft_weights_quant"] if dev.type == "cuda" and os.environ.get("LSB_DSPARK_TORCH_GEMM", "0") != "1" else None
+        bb = dsp.DsparkBackbone(dcfg, tensors, dev, torch.bfloat16, ctx_capacity=cap, rotate=ds["ctx_rotate"], kernels=kernels)
         return dsp.DeviceDsparkDraft(target, bb, {"speculative_tokens": ds["speculative_tokens"], "confidence_enabled": ds["confidence_enabled"] and dcfg.enable_confidence_head,
                                                   "confidence_threshold": ds["confidence_threshold"], "scheduler_mode": ds["scheduler_mode"],
                                                   "sts_temperatures": ds["sts_temperatures"]},

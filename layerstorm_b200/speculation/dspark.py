@@ -259,6 +259,39 @@ def _rope_half_split(x: torch.Tensor, pos: torch.Tensor, theta: float) -> torch.
     return torch.cat([a * c - b * s, b * c + a * s], -1).to(x.dtype)
 
 
+class _Linear:
+    """y = x @ W^T for the draft's matrices.  ``kernels`` = None: a library GEMM on the tensor as it is (the CPU, fp32 comparisons).
+    ``kernels`` = "bf16" | "fp8_e4m3" | "nvfp4": the weights are stored in that format and applied by the framework's own kernels
+    (``models/device_model.py`` ``QLinear``: weight-streaming kernels for the few rows of a block pass, tcgen05 GEMMs with the
+    de-quantisation in the operand pipeline for the many rows of a context ingest) - ``speculation.dspark.draft_weights_quant``."""
+
+    def __init__(self, w: torch.Tensor, device, dtype, kernels: Optional[str]):
+        self.N, self.K = w.shape
+        self.q = None
+        if kernels is None:
+            self.w = w.to(device, dtype)
+        else:
+            from ..models.device_model import QLinear
+            self.q = QLinear.from_float(w.float(), kernels, device)
+
+    def __call__(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        if self.q is None:
+            y = x @ self.w.T
+            return y if out_dtype is None else y.to(out_dtype)
+        M = x.shape[0]
+        want = out_dtype or x.dtype
+        out = torch.empty(M, self.N, dtype=torch.bfloat16 if want == torch.bfloat16 else torch.float32, device=x.device)
+        self.q(out, x.to(torch.bfloat16).contiguous(), M)
+        return out if out.dtype == want else out.to(want)
+
+    def dense(self) -> torch.Tensor:
+        """The matrix in effect, as fp32 (de-quantised)."""
+        return (self.w if self.q is None else self.q.dequant()).float()
+
+    def nbytes(self) -> int:
+        return self.w.numel() * self.w.element_size() if self.q is None else self.q.nbytes()
+
+
 class DsparkContext:
     """Keys and values of one sequence's committed positions, per draft layer: a window [base, base + capacity) of absolute
     positions; ``length`` = positions [0, length) have been seen (those below ``base`` have left the window)."""
@@ -289,7 +322,9 @@ class DsparkContext:
 
 class DsparkBackbone:
     def __init__(self, cfg: DsparkCheckpointConfig, tensors: Dict[str, torch.Tensor], device="cpu", dtype: Optional[torch.dtype] = None,
-                 ctx_capacity: int = 8192, rotate: bool = True):
+                 ctx_capacity: int = 8192, rotate: bool = True, kernels: Optional[str] = None):
+        """``kernels``: None = library GEMMs over the tensors in ``dtype``; "bf16" / "fp8_e4m3" / "nvfp4" = the draft's matrices are
+        stored in that format on the GPU and applied by the framework's own kernels (see ``_Linear``)."""
         validate_tensors(cfg, tensors)
         self.cfg = cfg
         self.device = torch.device(device)
@@ -298,19 +333,26 @@ class DsparkBackbone:
         self.rotate = rotate
         if self.ctx_capacity < 2 * cfg.block_size:
             raise ValueError(f"draft context capacity {ctx_capacity} is smaller than two blocks")
+        if kernels is not None and self.device.type != "cuda":
+            raise ValueError("the framework's GEMM kernels run on the GPU; on the CPU leave ``kernels`` unset")
+        self.kernels = kernels
+        if kernels is not None:
+            self.dtype = torch.bfloat16                                     # the kernels take bf16 activations
         mv = lambda k: tensors[k].to(self.device, self.dtype)             # noqa: E731
+        lin = lambda w: _Linear(w, self.device, self.dtype, kernels)     # noqa: E731
         self.embed = mv("embed_tokens.weight")
-        self.lm_head = self.embed[: cfg.draft_vocab_size] if cfg.tie_word_embeddings else mv("lm_head.weight")
-        self.fc, self.hidden_norm, self.norm = mv("fc.weight"), mv("hidden_norm.weight"), mv("norm.weight")
+        self.lm_head = lin(tensors["embed_tokens.weight"][: cfg.draft_vocab_size] if cfg.tie_word_embeddings else tensors["lm_head.weight"])
+        self.fc, self.hidden_norm, self.norm = lin(tensors["fc.weight"]), mv("hidden_norm.weight"), mv("norm.weight")
         self.layers = []
         for l in range(cfg.num_hidden_layers):
             p = f"layers.{l}."
             a, m = p + "self_attn.", p + "mlp."
             # k and v of the context are projected together (one GEMM over the fused features), gate and up of the MLP likewise
-            self.layers.append({"q": mv(a + "q_proj.weight"), "kv": torch.cat([mv(a + "k_proj.weight"), mv(a + "v_proj.weight")], 0), "o": mv(a + "o_proj.weight"),
+            self.layers.append({"q": lin(tensors[a + "q_proj.weight"]), "kv": lin(torch.cat([tensors[a + "k_proj.weight"], tensors[a + "v_proj.weight"]], 0)),
+                                "o": lin(tensors[a + "o_proj.weight"]),
                                 "q_norm": mv(a + "q_norm.weight"), "k_norm": mv(a + "k_norm.weight"), "in_norm": mv(p + "input_layernorm.weight"),
                                 "post_norm": mv(p + "post_attention_layernorm.weight"),
-                                "gate_up": torch.cat([mv(m + "gate_proj.weight"), mv(m + "up_proj.weight")], 0), "down": mv(m + "down_proj.weight")})
+                                "gate_up": lin(torch.cat([tensors[m + "gate_proj.weight"], tensors[m + "up_proj.weight"]], 0)), "down": lin(tensors[m + "down_proj.weight"])})
         d2t = tensors.get("d2t")
         self.markov = MarkovHead(mv("markov_head.markov_w1.weight"), mv("markov_head.markov_w2.weight"), None, d2t.to(self.device) if d2t is not None else None)
         self.confidence = None
@@ -318,6 +360,33 @@ class DsparkBackbone:
             self.confidence = ConfidenceHead(mv("confidence_head.proj.weight")[0], float(tensors["confidence_head.proj.bias"].float()[0]))
         self.block_passes = 0
         self.ingested_rows = 0
+
+    def effective_tensors(self) -> Dict[str, torch.Tensor]:
+        """The checkpoint tensors as this backbone applies them (fp32, on the CPU): identical to what was loaded for library GEMMs,
+        the de-quantised values for quantised kernels - what a reference run has to use to be comparable."""
+        c = self.cfg
+        f = lambda t: t.float().cpu()                                     # noqa: E731
+        out = {"embed_tokens.weight": f(self.embed), "fc.weight": f(self.fc.dense()), "hidden_norm.weight": f(self.hidden_norm), "norm.weight": f(self.norm),
+               "markov_head.markov_w1.weight": f(self.markov.w1), "markov_head.markov_w2.weight": f(self.markov.w2)}
+        if not c.tie_word_embeddings:
+            out["lm_head.weight"] = f(self.lm_head.dense())
+        if self.markov.d2t is not None:
+            out["d2t"] = self.markov.d2t.cpu()
+        if self.confidence is not None:
+            out["confidence_head.proj.weight"] = f(self.confidence.w)[None, :]
+            out["confidence_head.proj.bias"] = torch.tensor([self.confidence.b])
+        for l, L in enumerate(self.layers):
+            p = f"layers.{l}."
+            kv, gu = f(L["kv"].dense()), f(L["gate_up"].dense())
+            out.update({p + "self_attn.q_proj.weight": f(L["q"].dense()), p + "self_attn.k_proj.weight": kv[: c.kv_dim], p + "self_attn.v_proj.weight": kv[c.kv_dim:],
+                        p + "self_attn.o_proj.weight": f(L["o"].dense()), p + "self_attn.q_norm.weight": f(L["q_norm"]), p + "self_attn.k_norm.weight": f(L["k_norm"]),
+                        p + "input_layernorm.weight": f(L["in_norm"]), p + "post_attention_layernorm.weight": f(L["post_norm"]),
+                        p + "mlp.gate_proj.weight": gu[: c.intermediate_size], p + "mlp.up_proj.weight": gu[c.intermediate_size:], p + "mlp.down_proj.weight": f(L["down"].dense())})
+        return out
+
+    def weight_bytes(self) -> int:
+        n = self.embed.numel() * self.embed.element_size() + self.fc.nbytes() + (0 if self.cfg.tie_word_embeddings and self.kernels is None else self.lm_head.nbytes())
+        return n + sum(L[k].nbytes() for L in self.layers for k in ("q", "kv", "o", "gate_up", "down"))
 
     # ---------------------------------------------------------------- context
     def new_context(self) -> DsparkContext:
@@ -360,11 +429,11 @@ class DsparkBackbone:
             return False
         if not self._make_room(ctx, start_pos, rows):
             return False
-        feat = _rms(aux.to(self.device, self.dtype) @ self.fc.T, self.hidden_norm, c.rms_norm_eps)
+        feat = _rms(self.fc(aux.to(self.device, self.dtype)), self.hidden_norm, c.rms_norm_eps)
         pos = torch.arange(start_pos, start_pos + rows, device=self.device)
         lo = start_pos - ctx.base
         for l, L in enumerate(self.layers):
-            kv = feat @ L["kv"].T
+            kv = L["kv"](feat)
             k = kv[:, : c.kv_dim].view(rows, c.num_key_value_heads, c.head_dim)
             ctx.k[l, lo: lo + rows] = _rope_half_split(_rms(k, L["k_norm"], c.rms_norm_eps), pos, c.rope_theta)
             ctx.v[l, lo: lo + rows] = kv[:, c.kv_dim:].view(rows, c.num_key_value_heads, c.head_dim)
@@ -396,8 +465,8 @@ class DsparkBackbone:
         scale = 1.0 / math.sqrt(c.head_dim)
         for l, L in enumerate(self.layers):
             h = _rms(x, L["in_norm"], c.rms_norm_eps)
-            q = _rope_half_split(_rms((h @ L["q"].T).view(nq, c.num_attention_heads, c.head_dim), L["q_norm"], c.rms_norm_eps), pos, c.rope_theta)
-            kv = h @ L["kv"].T
+            q = _rope_half_split(_rms(L["q"](h).view(nq, c.num_attention_heads, c.head_dim), L["q_norm"], c.rms_norm_eps), pos, c.rope_theta)
+            kv = L["kv"](h)
             k = _rope_half_split(_rms(kv[:, : c.kv_dim].view(nq, c.num_key_value_heads, c.head_dim), L["k_norm"], c.rms_norm_eps), pos, c.rope_theta)
             v = kv[:, c.kv_dim:].view(nq, c.num_key_value_heads, c.head_dim)
             keys = torch.cat([ctx.k[l, :n_ctx], k], 0)                      # every context position, then every row of the block
@@ -406,13 +475,13 @@ class DsparkBackbone:
                 keys, vals = keys.repeat_interleave(rep, 1), vals.repeat_interleave(rep, 1)
             att = torch.softmax(torch.einsum("qhd,khd->hqk", q.float(), keys.float()) * scale, -1)
             o = torch.einsum("hqk,khd->qhd", att, vals.float()).reshape(nq, c.q_dim).to(self.dtype)
-            x = x + o @ L["o"].T
+            x = x + L["o"](o)
             h = _rms(x, L["post_norm"], c.rms_norm_eps)
-            gu = h @ L["gate_up"].T
-            x = x + (torch.nn.functional.silu(gu[:, : c.intermediate_size].float()) * gu[:, c.intermediate_size:].float()).to(self.dtype) @ L["down"].T
+            gu = L["gate_up"](h)
+            x = x + L["down"]((torch.nn.functional.silu(gu[:, : c.intermediate_size].float()) * gu[:, c.intermediate_size:].float()).to(self.dtype))
         hidden = _rms(x, self.norm, c.rms_norm_eps)
         self.block_passes += 1
-        return (hidden @ self.lm_head.T).float(), hidden
+        return self.lm_head(hidden, torch.float32), hidden
 
     @torch.no_grad()
     def draft(self, ctx: DsparkContext, anchor_token: int, anchor_pos: int, n_draft: int, confidence_threshold: float = 0.0) -> Tuple[List[int], List[float]]:

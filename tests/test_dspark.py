@@ -551,3 +551,15 @@ def test_draft_source_applies_the_scheduler_and_learns_from_feedback():
     pd.feedback(2, 0)
     pd.feedback(2, 0)
     assert pd.sched.proxy() == pytest.approx(0.245) and len(pd.propose(ctx, 4)) == 1            # one token clears 0.2, two do not
+
+
+def test_effective_tensors_are_the_loaded_ones_and_kernels_need_a_gpu():
+    cfg = small_cfg(draft_vocab_size=40)
+    t = random_dspark_tensors(cfg, 12, dtype=torch.float32)
+    bb = DsparkBackbone(cfg, t, "cpu", torch.float32, ctx_capacity=64)
+    eff = bb.effective_tensors()
+    assert set(eff) == set(t) and all(torch.equal(eff[k].to(t[k].dtype), t[k]) for k in t)
+    validate_tensors(cfg, eff)
+    assert bb.weight_bytes() == sum(v.numel() * 4 for k, v in t.items() if k.endswith("proj.weight") and "confidence" not in k or k in ("fc.weight", "lm_head.weight", "embed_tokens.weight"))
+    with pytest.raises(ValueError, match="GPU"):
+        DsparkBackbone(cfg, t, "cpu", kernels="fp8_e4m3")

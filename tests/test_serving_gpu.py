@@ -439,3 +439,33 @@ def test_aux_hidden_capture_feeds_a_block_draft_that_matches_the_cpu_draft_and_s
     assert dev.propose(ctx, 3) != [] and child in dev.ctx and dev.ctx[child].length == dev.ctx[sid].length
     eng.free_sequence(child)
     assert child not in dev.ctx and len(dev._spare) == 1
+
+
+@pytest.mark.parametrize("fmt", ["bf16", "fp8_e4m3", "nvfp4"])
+def test_block_draft_on_the_frameworks_own_gemm_kernels(fmt):
+    """The draft's matrices stored as bf16 / FP8 / NVFP4 and applied by the weight-streaming kernels (a block's few rows) and the
+    tcgen05 GEMMs (a context chunk's many rows): context keys and block logits against the fp32 tensor code over the de-quantised
+    weights."""
+    from layerstorm_b200.speculation import dspark as dsp
+    dc = dsp.draft_config_for_target(256, 1024, 4, layers=2, head_dim=64, inter=512, block_size=8, markov_rank=16, n_aux=2)
+    tens = dsp.random_dspark_tensors(dc, 5)
+    dev = dsp.DsparkBackbone(dc, tens, "cuda", ctx_capacity=128, kernels=fmt)
+    ref = dsp.DsparkBackbone(dc, dev.effective_tensors(), "cpu", torch.float32, ctx_capacity=128)
+    if fmt == "bf16":
+        assert all(torch.equal(v.float(), tens[k].float()) for k, v in dev.effective_tensors().items() if v.is_floating_point())
+    else:
+        assert dev.weight_bytes() < 0.8 * dsp.DsparkBackbone(dc, tens, "cuda", torch.bfloat16, ctx_capacity=16).weight_bytes()
+    aux = torch.randn(43, 512, generator=torch.Generator().manual_seed(6)).to(torch.bfloat16)
+    cd, cr = dev.new_context(), ref.new_context()
+    for a, b in ((0, 5), (5, 24), (24, 43)):                       # 5 rows: streaming kernels; 19 rows: tensor-core GEMMs
+        assert dev.ingest(cd, aux[a:b].cuda(), a) and ref.ingest(cr, aux[a:b].float(), a)
+    kd, kr = cd.k[:, :43].float().cpu(), cr.k[:, :43]
+    vd, vr = cd.v[:, :43].float().cpu(), cr.v[:, :43]
+    assert float((kd - kr).abs().max() / kr.abs().max()) < 3e-2 and float((vd - vr).abs().max() / vr.abs().max()) < 3e-2
+    for n in (7, 3, 1):                                            # 8, 4 and 2 rows
+        ld, hd = dev.run_block(cd, 77, 43, n)
+        lr, hr = ref.run_block(cr, 77, 43, n)
+        assert ld.dtype == torch.float32 and float((ld.cpu() - lr).abs().max() / lr.abs().max()) < 4e-2
+        assert float((hd.float().cpu() - hr).abs().max() / hr.abs().max()) < 4e-2
+    ids, conf = dev.draft(cd, 77, 43, 7)
+    assert len(ids) == 7 and len(conf) == 7 and all(0 <= t < 1024 for t in ids)

@@ -271,10 +271,18 @@ def build_block_draft(cfg: dict, shape: ModelConfig, target, args: argparse.Name
         # (LSB_DSPARK_TORCH_GEMM=1: library GEMMs over bf16 tensors instead)
         kernels = ds["draft_weights_quant"] if dev.type == "cuda" and os.environ.get("LSB_DSPARK_TORCH_GEMM", "0") != "1" else None
         bb = dsp.DsparkBackbone(dcfg, tensors, dev, torch.bfloat16, ctx_capacity=cap, rotate=ds["ctx_rotate"], kernels=kernels)
-        return dsp.DeviceDsparkDraft(target, bb, {"speculative_tokens": ds["speculative_tokens"], "confidence_enabled": ds["confidence_enabled"] and dcfg.enable_confidence_head,
+        draft = dsp.DeviceDsparkDraft(target, bb, {"speculative_tokens": ds["speculative_tokens"], "confidence_enabled": ds["confidence_enabled"] and dcfg.enable_confidence_head,
                                                   "confidence_threshold": ds["confidence_threshold"], "scheduler_mode": ds["scheduler_mode"],
                                                   "sts_temperatures": ds["sts_temperatures"]},
                                      max_contexts=int(os.environ.get("LSB_DSPARK_CONTEXTS", "4")), output_of_layer=os.environ.get("LSB_DSPARK_AUX_OUTPUT", "0") == "1")
+        from ..speculation.epm_corpus import CorpusWriter, effective_dump_dir
+        dump = effective_dump_dir(ds["epm_dump_dir"])
+        if dump:
+            # feature side of the expert-routing prediction corpus (block records + verdicts); the label side (router logits per
+            # position) is recorded by the CPU reference path only
+            draft.attach_corpus(CorpusWriter(dump))
+            log.info("block records of the draft go to %s", dump)
+        return draft
     except (NotImplementedError, ValueError) as e:
         log.warning("block draft unavailable (%s); serving without it", e)
         return None

@@ -125,6 +125,8 @@ class Oracle:
         else:
             ids, wt = route(cfg, logits, w.get(m + "router_bias"))
         self.last_route = (ids, wt)
+        if getattr(self, "route_log", None) is not None:
+            self.route_log[i] = (logits, ids, wt)                 # per row: router logits, chosen experts, their weights
         out = torch.zeros_like(x)
         for t in range(x.shape[0]):
             for k in range(cfg.top_k):

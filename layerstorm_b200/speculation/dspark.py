@@ -360,6 +360,8 @@ class DsparkBackbone:
             self.confidence = ConfidenceHead(mv("confidence_head.proj.weight")[0], float(tensors["confidence_head.proj.bias"].float()[0]))
         self.block_passes = 0
         self.ingested_rows = 0
+        self.collect_layers = False      # keep the residual stream after every layer of the last block pass (corpus recording)
+        self.last_layer_hidden: Optional[torch.Tensor] = None     # [rows, layers, hidden]
 
     def effective_tensors(self) -> Dict[str, torch.Tensor]:
         """The checkpoint tensors as this backbone applies them (fp32, on the CPU): identical to what was loaded for library GEMMs,
@@ -463,6 +465,7 @@ class DsparkBackbone:
         n_ctx = anchor_pos - ctx.base
         rep = c.num_attention_heads // c.num_key_value_heads
         scale = 1.0 / math.sqrt(c.head_dim)
+        per_layer: List[torch.Tensor] = []
         for l, L in enumerate(self.layers):
             h = _rms(x, L["in_norm"], c.rms_norm_eps)
             q = _rope_half_split(_rms(L["q"](h).view(nq, c.num_attention_heads, c.head_dim), L["q_norm"], c.rms_norm_eps), pos, c.rope_theta)
@@ -479,8 +482,11 @@ class DsparkBackbone:
             h = _rms(x, L["post_norm"], c.rms_norm_eps)
             gu = L["gate_up"](h)
             x = x + L["down"]((torch.nn.functional.silu(gu[:, : c.intermediate_size].float()) * gu[:, c.intermediate_size:].float()).to(self.dtype))
+            if self.collect_layers:
+                per_layer.append(x)
         hidden = _rms(x, self.norm, c.rms_norm_eps)
         self.block_passes += 1
+        self.last_layer_hidden = torch.stack(per_layer, 1) if per_layer else None
         return self.lm_head(hidden, torch.float32), hidden
 
     @torch.no_grad()
@@ -603,7 +609,34 @@ class DsparkScheduler:
 
 
 # ------------------------------------------------------------------------------------------------------------- draft sources
-class DsparkDraft:
+class _CorpusHook:
+    """Writes what a block pass knew and what became of it to an expert-routing prediction corpus (``speculation/epm_corpus.py``)."""
+
+    corpus = None
+
+    def attach_corpus(self, writer):
+        self.corpus = writer
+        self.bb.collect_layers = writer is not None
+        self._pending = None
+        self._block_no: Dict[int, int] = {}
+
+    def _corpus_block(self, seq: int, anchor_pos: int, anchor: int, drafted: Sequence[int], conf: Sequence[float], proposed: Sequence[int]):
+        if self.corpus is None or self.bb.last_layer_hidden is None or not drafted:
+            return
+        n = self._block_no.get(seq, 0)
+        self._block_no[seq] = n + 1
+        self.corpus.write_block(seq, n, anchor_pos, anchor, drafted, conf or None, self.bb.last_layer_hidden[1: 1 + len(drafted)])
+        self._pending = (seq, n, anchor_pos, list(proposed), list(conf))
+
+    def _corpus_feedback(self, proposed: int, accepted: int):
+        if self.corpus is None or getattr(self, "_pending", None) is None:
+            return
+        seq, n, pos, ids, conf = self._pending
+        self._pending = None
+        self.corpus.write_manifest(seq, n, pos, proposed, accepted, ids[:accepted], conf)
+
+
+class DsparkDraft(_CorpusHook):
     """``speculation.method = dspark`` as a draft source of the serving loop: ``propose(context, gamma)``.
 
     ``aux_of(tokens, first) -> [len(tokens) - first, N_aux * H]`` supplies the target's aux hidden states of positions
@@ -617,6 +650,7 @@ class DsparkDraft:
         self.bb = backbone
         self.aux_of = aux_of
         self.ctx = backbone.new_context()
+        self.sequence_no = 0
         self.max_tokens = min(int(cfg.get("speculative_tokens", backbone.cfg.speculative_tokens)), backbone.cfg.block_size - 1)
         self.sched = DsparkScheduler(dict(cfg, confidence_enabled=bool(cfg.get("confidence_enabled")) and backbone.confidence is not None))
         self.proposed = self.accepted = self.failures = 0
@@ -631,6 +665,8 @@ class DsparkDraft:
         if not ctx.valid or m < ctx.base or len(ctx.tokens) != ctx.length:
             ctx.reset()
             m = 0
+        if m == 0:
+            self.sequence_no += 1                       # nothing shared with what was held: another conversation
         ctx.rewind(m)
         if len(committed) > ctx.length:
             first = ctx.length
@@ -651,13 +687,16 @@ class DsparkDraft:
             self.failures += 1
             self.ctx.reset()
             return []
+        drafted = ids
         ids = ids[: self.sched.depth(self.last_confidences, len(ids))]
+        self._corpus_block(self.sequence_no, len(committed), anchor, drafted, self.last_confidences, ids)
         self.proposed += len(ids)
         return ids
 
     def feedback(self, proposed: int, accepted: int):
         self.accepted += accepted
         self.sched.record(self.last_confidences, proposed, accepted)
+        self._corpus_feedback(proposed, accepted)
 
     def acceptance_rate(self) -> float:
         return self.accepted / self.proposed if self.proposed else 0.0
@@ -678,7 +717,7 @@ def oracle_aux_provider(oracle, layer_ids: Sequence[int], output_of_layer: bool 
     return aux_of
 
 
-class DeviceDsparkDraft:
+class DeviceDsparkDraft(_CorpusHook):
     """The block draft beside the GPU engine.  The engine reports the aux hidden states of every committed step
     (``Engine.enable_aux_capture``); they are fused and projected into the owning sequence's draft context at once, on the engine's
     stream, so the draft's context is complete the moment the step's token is known and a proposal costs one block pass.
@@ -714,6 +753,8 @@ class DeviceDsparkDraft:
                 self._spare.append(self.ctx.pop(old))
             c = self._spare.pop() if self._spare else self.bb.new_context()
             c.reset()
+            self._seq_counter = getattr(self, "_seq_counter", 0) + 1
+            c.corpus_seq = self._seq_counter
             self.ctx[sid] = c
         if c is not None:
             self._use += 1
@@ -776,13 +817,16 @@ class DeviceDsparkDraft:
             c.valid = False
             return []
         self._used[sid] = self._use = self._use + 1
+        drafted = ids
         ids = ids[: self.sched.depth(self.last_confidences, len(ids))]
+        self._corpus_block(getattr(c, "corpus_seq", sid), c.length, int(context[-1]), drafted, self.last_confidences, ids)
         self.proposed += len(ids)
         return ids
 
     def feedback(self, proposed: int, accepted: int):
         self.accepted += accepted
         self.sched.record(self.last_confidences, proposed, accepted)
+        self._corpus_feedback(proposed, accepted)
 
     def acceptance_rate(self) -> float:
         return self.accepted / self.proposed if self.proposed else 0.0

@@ -4,6 +4,7 @@ import dataclasses
 import json
 import math
 import os
+import struct
 
 import pytest
 import torch
@@ -563,3 +564,60 @@ def test_effective_tensors_are_the_loaded_ones_and_kernels_need_a_gpu():
     assert bb.weight_bytes() == sum(v.numel() * 4 for k, v in t.items() if k.endswith("proj.weight") and "confidence" not in k or k in ("fc.weight", "lm_head.weight", "embed_tokens.weight"))
     with pytest.raises(ValueError, match="GPU"):
         DsparkBackbone(cfg, t, "cpu", kernels="fp8_e4m3")
+
+
+def test_expert_routing_corpus_records_blocks_verdicts_and_routing(tmp_path, monkeypatch):
+    """Serving with the block draft writes what the draft knew (per-layer hidden rows, ids, confidences) and what became of it; the
+    reference model supplies the target's routing per position; the join pairs draft row k with the routing at anchor_pos + 1 + k."""
+    from layerstorm_b200.serving.orchestrator import InferenceRequest, Orchestrator, SamplingParams
+    from layerstorm_b200.speculation import epm_corpus as ec
+    cfg, w, eng = _target()
+    dc = draft_config_for_target(cfg.hidden, cfg.vocab, cfg.n_layers, layers=2, head_dim=16, block_size=5, markov_rank=8, n_aux=2)
+    bb = DsparkBackbone(dc, random_dspark_tensors(dc, 1, dtype=torch.float32), "cpu", torch.float32, ctx_capacity=64)
+    draft = DsparkDraft(bb, oracle_aux_provider(eng.model, dc.aux_hidden_state_layer_ids), {"speculative_tokens": 4})
+    d = str(tmp_path / "corpus")
+    wr = ec.CorpusWriter(d)
+    draft.attach_corpus(wr)
+    prompt = list(range(40, 58))
+    r = InferenceRequest("c", prompt, SamplingParams(max_tokens=9, ignore_eos=True))
+    orch = Orchestrator(eng, draft=draft, speculation_depth=4)
+    orch.submit_request(r)
+    assert orch.step() and r.error is None
+    full = prompt + r.output_ids
+    ec.record_oracle_routing(wr, eng.model, draft.sequence_no, full, first=len(prompt))
+    wr.close()
+    blocks, man, routes = ec.read_blocks(d), ec.read_manifest(d), ec.read_routing(d)
+    assert len(blocks) == wr.blocks == r.stats.spec_rounds and len(man) == wr.manifest_lines == len(blocks) and len(routes) == len(r.output_ids)
+    b0 = blocks[0]
+    assert b0["anchor_pos"] == len(prompt) and b0["anchor_token"] == r.output_ids[0] and len(b0["ids"]) == 4 and len(b0["conf"]) == 4
+    assert b0["hiddens"].shape == (4, 2, cfg.hidden) and b0["hiddens"].dtype == torch.bfloat16 and float(b0["hiddens"].float().abs().max()) > 0
+    assert [b["block"] for b in blocks] == list(range(len(blocks))) and all(b["seq"] == draft.sequence_no for b in blocks)
+    # the verdicts tell the story of the request: anchor + accepted tokens + the target's own token per round
+    pos = len(prompt)
+    for b, m in zip(blocks, man):
+        assert m["anchor_pos"] == b["anchor_pos"] == pos and m["committed"] == b["ids"][: m["accepted"]] == full[pos + 1: pos + 1 + m["accepted"]]
+        pos += m["accepted"] + 1
+    # routing records: every routed layer, logits over all experts, the chosen ones on top
+    moe_layers = [i for i in range(cfg.n_layers) if cfg.is_moe_layer(i)]
+    r0 = routes[0]
+    assert r0["pos"] == len(prompt) and [x["layer"] for x in r0["rows"]] == moe_layers and len(r0["rows"][0]["logits"]) == cfg.n_routed
+    assert len(r0["rows"][0]["ids"]) == cfg.top_k and abs(sum(r0["rows"][0]["weights"])) > 0
+    ex = ec.join_examples(d)
+    assert ex and all(e["features"].shape == (2, cfg.hidden) and set(e["labels"]) == set(moe_layers) for e in ex)
+    assert all(e["pos"] == b0["anchor_pos"] + 1 + e["row"] for e in ex if e["seq"] == b0["seq"] and e["pos"] <= b0["anchor_pos"] + 4 and e["row"] < 4 and e["pos"] - e["row"] == b0["anchor_pos"] + 1)
+    assert sum(1 for e in ex if not e["accepted"]) <= len(blocks)                              # at most the first rejected row of each block
+    cov = ec.previous_position_coverage(d)
+    assert 0.0 <= cov["coverage"] <= 1.0 and cov["pairs"] == (len(routes) - 1) * len(moe_layers) * cfg.top_k
+    # a record cut off by a crash is ignored, everything before it stands; appending continues the corpus
+    with open(os.path.join(d, "blocks.bin"), "ab") as f:
+        f.write(struct.pack("<III", ec.BLOCK_MAGIC, ec.VERSION, 65535) + b"abc")              # announces 64 KB, holds 3 bytes
+    assert len(ec.read_blocks(d)) == len(blocks)
+    # the switch: the environment wins over the configuration, "0" forces it off
+    assert ec.effective_dump_dir("/x", {}) == "/x" and ec.effective_dump_dir("/x", {"LS_EPM_DUMP": "0"}) == "" and ec.effective_dump_dir("", {"LS_EPM_DUMP": "/y"}) == "/y"
+    # a directory that cannot be written switches the writer off instead of failing the request
+    blocked = tmp_path / "file"
+    blocked.write_text("x")
+    off = ec.CorpusWriter(str(blocked / "sub"))
+    assert not off.ok
+    off.write_manifest(1, 0, 0, 1, 0, [])
+    assert off.manifest_lines == 0

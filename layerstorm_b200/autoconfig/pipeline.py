@@ -55,6 +55,7 @@ class AutoRunOptions:
     train_prompt: int = 512
     train_gen: int = 100
     serve_flags: List[str] = dataclasses.field(default_factory=list)     # passed to the training decode's server boot (e.g. --random-weights)
+    draft_bytes: int = 0                        # what a block draft takes on its GPU (the solver keeps it when it fits)
 
 
 @dataclasses.dataclass
@@ -133,7 +134,7 @@ def run_pipeline(shape: ModelConfig, hw: HardwareInfo, levers: Levers, pins: dic
         b.setdefault("gpu_loader", {}).update({"enabled": True, "calibration_mode": "loaded", "calibration_path": constants.get("_path", "")})
         if placement:
             b.setdefault("memory", {}).setdefault("arena_placement", {})["freq_table"] = placement
-        return solve(shape, hw2, levers, pins, b), notes
+        return solve(shape, hw2, levers, pins, b, draft_bytes=opts.draft_bytes), notes
 
     # ---- step 2: derive
     cal["_path"] = paths["calibration"]

@@ -38,9 +38,41 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--placement-table", help="--auto-run: demand-fetch table to carry instead of fitting one")
     p.add_argument("--train-gen", type=int, default=100, help="--auto-run: tokens of the training decode")
     p.add_argument("--serve-flag", action="append", default=[], help="--auto-run: extra flag of the training decode's server boot (e.g. --random-weights)")
+    p.add_argument("--draft-checkpoint", help="a dspark speculator checkpoint (directory with config.json + model.safetensors): the block draft is "
+                                             "sized (weights in speculation.dspark.draft_weights_quant + its contexts) and kept when it fits beside the target")
     p.add_argument("--print", dest="show", action="store_true", help="print the explanation")
     p.add_argument("--probe-only", action="store_true", help="print what the model path is (format, shape, quantisation, size) and exit")
     return p
+
+
+def plan_block_draft(path: str, shape, base: Optional[dict], pins: dict):
+    """(base configuration carrying the draft's settings, bytes the draft takes on its GPU) for a dspark speculator checkpoint; the
+    checkpoint must have been trained for this target (hidden size, vocabulary, aux layers inside the model)."""
+    import os
+    from ..speculation import dspark as dsp
+    if not dsp.is_dspark_checkpoint(path):
+        raise ConfigError([f"--draft-checkpoint: {path} is not a dspark speculator checkpoint (config.json with speculators_model_type = dspark)"])
+    try:
+        dc = dsp.DsparkCheckpointConfig.from_json(json.load(open(os.path.join(path, "config.json"))))
+    except (KeyError, ValueError) as e:
+        raise ConfigError([f"--draft-checkpoint: {e}"])
+    problems = []
+    if dc.hidden_size != shape.hidden or dc.vocab_size != shape.vocab:
+        problems.append(f"the draft was trained for hidden {dc.hidden_size} / vocabulary {dc.vocab_size}, the target has {shape.hidden} / {shape.vocab}")
+    if any(l < 0 or l > shape.n_layers for l in dc.aux_hidden_state_layer_ids):
+        problems.append(f"aux layers {dc.aux_hidden_state_layer_ids} do not fit a target of {shape.n_layers} layers")
+    if problems:
+        raise ConfigError(["--draft-checkpoint: " + p for p in problems])
+    base = json.loads(json.dumps(base)) if base else {}
+    ds = base.setdefault("speculation", {}).setdefault("dspark", {})
+    ds.update({"checkpoint_path": os.path.abspath(path), "block_size": dc.block_size, "speculative_tokens": dc.speculative_tokens, "markov_rank": dc.markov_rank,
+               "mask_token_id": dc.mask_token_id, "draft_vocab_size": dc.draft_vocab_size, "aux_hidden_state_layer_ids": list(dc.aux_hidden_state_layer_ids)})
+    ds.setdefault("confidence_enabled", dc.enable_confidence_head)
+    quant = pins.get("speculation.dspark.draft_weights_quant", ds.get("draft_weights_quant", "bf16"))
+    ctx = int(pins.get("speculation.dspark.draft_context_capacity_tokens", ds.get("draft_context_capacity_tokens", 8192)))
+    mem = dsp.draft_memory_bytes(dc, quant, ctx, int(os.environ.get("LSB_DSPARK_CONTEXTS", "4")))
+    print(f"block draft: {mem['weights'] / 1e9:.2f} GB of {quant} weights + {mem['contexts'] / 1e9:.2f} GB of draft contexts", file=sys.stderr)
+    return base, mem["total"]
 
 
 def main(argv: Optional[list[str]] = None) -> int:
@@ -64,12 +96,16 @@ def main(argv: Optional[list[str]] = None) -> int:
             hw = synthetic(args.assume_gpus)
         else:
             hw = detect((base or {}).get("hardware", {}).get("nvme_paths"))
+        draft_bytes = 0
+        if args.draft_checkpoint:
+            base, draft_bytes = plan_block_draft(args.draft_checkpoint, shape, base, collect_pins(args.pin))
         if args.auto_run:
             from ..autoconfig.pipeline import AutoRunOptions, run_pipeline
             rec = run_pipeline(shape, hw, Levers(args.vram_expert_ratio, args.total_active_context_tokens, args.prefer, args.accuracy),
                                collect_pins(args.pin), base,
                                AutoRunOptions(model=args.model, out_dir=args.out_dir, reset=args.reset, calibration=args.calibration, trained=args.trained,
-                                              placement_table=args.placement_table, train_gen=args.train_gen, serve_flags=args.serve_flag))
+                                              placement_table=args.placement_table, train_gen=args.train_gen, serve_flags=args.serve_flag,
+                                              draft_bytes=draft_bytes))
             for st in rec["steps"]:
                 print("auto-run:", json.dumps(st))
             print(f"wrote {rec['config']} and {rec['artifacts']['autorun']}")
@@ -80,7 +116,7 @@ def main(argv: Optional[list[str]] = None) -> int:
             for n in notes:
                 print("calibration:", n, file=sys.stderr)
         res = solve(shape, hw, Levers(args.vram_expert_ratio, args.total_active_context_tokens, args.prefer, args.accuracy),
-                    collect_pins(args.pin), base)
+                    collect_pins(args.pin), base, draft_bytes=draft_bytes)
     except ConfigError as e:
         print(str(e), file=sys.stderr)
         return 2

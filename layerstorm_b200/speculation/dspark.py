@@ -156,6 +156,22 @@ class DsparkCheckpointConfig:
         return 2 * self.num_hidden_layers * self.kv_dim * bytes_per_element
 
 
+def draft_memory_bytes(cfg: DsparkCheckpointConfig, weights_quant: str = "bf16", context_tokens: int = 8192, contexts: int = 4) -> Dict[str, int]:
+    """What the block draft takes on its GPU: the matrices in their storage format (embedding, norms and the Markov / confidence heads
+    stay bf16), and keys + values of ``contexts`` draft contexts of ``context_tokens`` positions.  The auto-configurator's draft term."""
+    per = {"bf16": 2.0, "fp8_e4m3": 1.0 + 4.0 / (128 * 128), "nvfp4": 0.5 + 1.0 / 16}[weights_quant]
+    mats = small = 0
+    for k, shape in cfg.expected_tensors().items():
+        n = math.prod(shape)
+        if k.endswith("proj.weight") and "confidence" not in k or k in ("fc.weight", "lm_head.weight"):
+            mats += n
+        elif k != "d2t":
+            small += n
+    w = int(mats * per + small * 2 + (8 * cfg.draft_vocab_size if cfg.draft_vocab_size < cfg.vocab_size else 0))
+    ctx = cfg.context_bytes_per_token() * int(context_tokens) * int(contexts)
+    return {"weights": w, "contexts": ctx, "total": w + ctx}
+
+
 def validate_tensors(cfg: DsparkCheckpointConfig, tensors: Dict[str, torch.Tensor]):
     """Fail closed: an unknown, missing, mis-shaped or wrongly typed tensor stops the load (a draft that silently runs on a partly
     matched checkpoint proposes garbage that the target then pays to reject)."""

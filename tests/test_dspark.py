@@ -621,3 +621,39 @@ def test_expert_routing_corpus_records_blocks_verdicts_and_routing(tmp_path, mon
     assert not off.ok
     off.write_manifest(1, 0, 0, 1, 0, [])
     assert off.manifest_lines == 0
+
+
+def test_autoconfigure_sizes_a_block_draft_and_carries_its_settings(tmp_path, capsys):
+    from layerstorm_b200.cli import autoconfigure
+    from layerstorm_b200.models.config import get_preset
+    from layerstorm_b200.speculation.dspark import draft_memory_bytes
+    # the shipped geometry: 7.6 GB in bf16, about half in FP8, 2.7 GB of contexts for four sequences of 8192 positions
+    big = DsparkCheckpointConfig(draft_vocab_size=154880, mask_token_id=154856, aux_hidden_state_layer_ids=[8, 23, 39, 55, 70], hidden_size=6144,
+                                 num_attention_heads=64, num_key_value_heads=64, head_dim=64, intermediate_size=12288, vocab_size=154880,
+                                 enable_confidence_head=True, confidence_head_with_markov=True)
+    m = draft_memory_bytes(big, "bf16")
+    assert m["weights"] == big.weight_bytes() and m["contexts"] == 81920 * 8192 * 4 and m["total"] == m["weights"] + m["contexts"]
+    f8, f4 = draft_memory_bytes(big, "fp8_e4m3")["weights"], draft_memory_bytes(big, "nvfp4")["weights"]
+    assert 0.6 * m["weights"] < f8 < 0.7 * m["weights"] and 0.45 * m["weights"] < f4 < 0.55 * m["weights"]      # the embedding stays bf16
+    shape = get_preset("glm-5.3-flash")
+    dc = draft_config_for_target(shape.hidden, shape.vocab, shape.n_layers, layers=1, head_dim=64, block_size=8, markov_rank=8, n_aux=2)
+    d = str(tmp_path / "draft")
+    os.makedirs(d)
+    json.dump(dc.to_json(), open(os.path.join(d, "config.json"), "w"))              # sizing reads the configuration only
+    out = str(tmp_path / "auto.json")
+    assert autoconfigure.main(["--model", "glm-5.3-flash", "--assume-gpus", "1", "--draft-checkpoint", d, "--output", out]) == 0
+    cfg = json.load(open(out))
+    sp = cfg["speculation"]
+    assert sp["enabled"] and sp["method"] == "dspark" and sp["dspark"]["checkpoint_path"] == d and sp["dspark"]["block_size"] == 8
+    assert sp["dspark"]["aux_hidden_state_layer_ids"] == dc.aux_hidden_state_layer_ids and sp["dspark"]["speculative_tokens"] == 7
+    assert "block draft:" in capsys.readouterr().err
+    # a draft trained for another target, or something that is not a dspark checkpoint, is refused with a reason
+    other = dataclasses.replace(dc, hidden_size=dc.hidden_size // 2, num_attention_heads=dc.num_attention_heads // 2, num_key_value_heads=dc.num_key_value_heads // 2)
+    json.dump(other.to_json(), open(os.path.join(d, "config.json"), "w"))
+    assert autoconfigure.main(["--model", "glm-5.3-flash", "--assume-gpus", "1", "--draft-checkpoint", d, "--output", out]) == 2
+    assert "trained for hidden" in capsys.readouterr().err
+    assert autoconfigure.main(["--model", "glm-5.3-flash", "--assume-gpus", "1", "--draft-checkpoint", str(tmp_path), "--output", out]) == 2
+    broken = dataclasses.replace(dc, num_key_value_heads=3)                          # a configuration that contradicts itself
+    json.dump(broken.to_json(), open(os.path.join(d, "config.json"), "w"))
+    assert autoconfigure.main(["--model", "glm-5.3-flash", "--assume-gpus", "1", "--draft-checkpoint", d, "--output", out]) == 2
+    assert "multiple of num_key_value_heads" in capsys.readouterr().err

@@ -635,12 +635,19 @@ class _CorpusHook:
         self.bb.collect_layers = writer is not None
         self._pending = None
         self._block_no: Dict[int, int] = {}
+        self._ctx_len: Dict[int, int] = {}
 
-    def _corpus_block(self, seq: int, anchor_pos: int, anchor: int, drafted: Sequence[int], conf: Sequence[float], proposed: Sequence[int]):
+    def _corpus_block(self, seq: int, anchor_pos: int, anchor: int, drafted: Sequence[int], conf: Sequence[float], proposed: Sequence[int],
+                      context: Optional[Sequence[int]] = None):
         if self.corpus is None or self.bb.last_layer_hidden is None or not drafted:
             return
         n = self._block_no.get(seq, 0)
         self._block_no[seq] = n + 1
+        if context is not None:
+            # the tokens the sequence gained since its last block (all of them at its first): an offline labeller can re-run the target
+            known = self._ctx_len.get(seq, 0) if n else 0
+            self.corpus.write_context(seq, n, known, context[known:])
+            self._ctx_len[seq] = len(context)
         self.corpus.write_block(seq, n, anchor_pos, anchor, drafted, conf or None, self.bb.last_layer_hidden[1: 1 + len(drafted)])
         self._pending = (seq, n, anchor_pos, list(proposed), list(conf))
 
@@ -705,7 +712,7 @@ class DsparkDraft(_CorpusHook):
             return []
         drafted = ids
         ids = ids[: self.sched.depth(self.last_confidences, len(ids))]
-        self._corpus_block(self.sequence_no, len(committed), anchor, drafted, self.last_confidences, ids)
+        self._corpus_block(self.sequence_no, len(committed), anchor, drafted, self.last_confidences, ids, context)
         self.proposed += len(ids)
         return ids
 
@@ -835,7 +842,7 @@ class DeviceDsparkDraft(_CorpusHook):
         self._used[sid] = self._use = self._use + 1
         drafted = ids
         ids = ids[: self.sched.depth(self.last_confidences, len(ids))]
-        self._corpus_block(getattr(c, "corpus_seq", sid), c.length, int(context[-1]), drafted, self.last_confidences, ids)
+        self._corpus_block(getattr(c, "corpus_seq", sid), c.length, int(context[-1]), drafted, self.last_confidences, ids, context)
         self.proposed += len(ids)
         return ids
 

@@ -9,7 +9,9 @@ writes them during ordinary serving and reads them back:
                     predicting rows ([gamma, L, H], bf16 bits) - the feature side;
   ``routing.bin``   one record per (sequence, token position) the target ran: for every routed layer the router's logits over all
                     experts (fp16) and the chosen experts with their weights - the label side;
-  ``manifest.jsonl`` one line per verified block: how many proposed tokens the target accepted and which tokens were committed.
+  ``manifest.jsonl`` one line per verified block: how many proposed tokens the target accepted and which tokens were committed; and one
+                    line per drafted block with the tokens the sequence gained since its last block, so that the sequences can be
+                    re-run offline (:func:`label_with_oracle` writes the label side that way when it was not recorded live).
 Records are little-endian, length-prefixed (a reader can skip a record type or version it does not know), appended - several runs
 accumulate into one directory - and joined on (sequence, position) by :func:`join_examples`.  Writing never takes serving down: an
 I/O error switches the writer off and is logged once.
@@ -127,6 +129,11 @@ class CorpusWriter:
             self.manifest_lines += 1
 
 
+    def write_context(self, seq: int, block: int, start: int, tokens: Sequence[int]):
+        """The tokens at positions ``start ..`` that the sequence held when block ``block`` was drafted (the anchor is the last one)."""
+        self._append("manifest.jsonl", json.dumps({"seq": int(seq), "block": int(block), "context_from": int(start), "tokens": [int(t) for t in tokens]}) + "\n")
+
+
 def _records(path: str, magic: int) -> Iterator[bytes]:
     if not os.path.exists(path):
         return
@@ -181,7 +188,8 @@ def read_routing(directory: str) -> List[dict]:
     return out
 
 
-def read_manifest(directory: str) -> List[dict]:
+def read_manifest(directory: str, contexts: bool = False) -> List[dict]:
+    """The verdict lines of the manifest (``contexts``: the context lines instead)."""
     p = os.path.join(directory, "manifest.jsonl")
     if not os.path.exists(p):
         return []
@@ -190,10 +198,54 @@ def read_manifest(directory: str) -> List[dict]:
         line = line.strip()
         if line:
             try:
-                out.append(json.loads(line))
+                rec = json.loads(line)
             except ValueError:
                 break                                    # a line cut off by a crash
+            if ("context_from" in rec) == contexts:
+                out.append(rec)
     return out
+
+
+def sequences_of(directory: str) -> Dict[int, List[int]]:
+    """Every recorded sequence's tokens as far as the corpus knows them: the contexts written at each block, plus the tokens the last
+    block's verdict committed."""
+    toks: Dict[int, List[int]] = {}
+    for c in read_manifest(directory, contexts=True):
+        t = toks.setdefault(c["seq"], [])
+        if c["block"] == 0:
+            del t[:]
+        if c["context_from"] <= len(t):
+            del t[c["context_from"]:]
+            t.extend(c["tokens"])
+    last: Dict[int, dict] = {}
+    for m in read_manifest(directory):
+        if m["seq"] not in last or m["block"] >= last[m["seq"]]["block"]:
+            last[m["seq"]] = m
+    for seq, m in last.items():
+        t = toks.get(seq)
+        if t is not None and len(t) == m["anchor_pos"] + 1:
+            t.extend(m["committed"])
+    return toks
+
+
+def label_with_oracle(directory: str, oracle) -> int:
+    """Write the routing records of a corpus whose label side is missing (recorded beside the GPU engine) by re-running the recorded
+    sequences through the fp32 reference model: exact, and as slow as that model - a tool for small targets.  Returns the number of
+    positions labelled."""
+    firsts: Dict[int, int] = {}
+    for b in read_blocks(directory):
+        firsts[b["seq"]] = min(firsts.get(b["seq"], b["anchor_pos"]), b["anchor_pos"])
+    wr = CorpusWriter(directory)
+    n = 0
+    try:
+        for seq, tokens in sorted(sequences_of(directory).items()):
+            if seq in firsts and tokens:
+                first = max(0, firsts[seq] - 1)
+                record_oracle_routing(wr, oracle, seq, tokens, first)
+                n += len(tokens) - first
+    finally:
+        wr.close()
+    return n
 
 
 def join_examples(directory: str, accepted_only: bool = True) -> List[dict]:

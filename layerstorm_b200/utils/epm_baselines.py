@@ -1,7 +1,7 @@
 """Baselines over an expert-routing prediction corpus: how well can the target's routing of a drafted position be guessed?
 
-    python -m layerstorm_b200.utils.epm_baselines CORPUS_DIR [--weights CHECKPOINT] [--holdout 0.25] [--ridge 1.0] [--widths 8,16,32]
-                                                  [--out report.json]
+    python -m layerstorm_b200.utils.epm_baselines CORPUS_DIR [--weights CHECKPOINT] [--label] [--holdout 0.25] [--ridge 1.0]
+                                                  [--widths 8,16,32] [--out report.json]
 
 ``CORPUS_DIR`` holds what ``speculation/epm_corpus.py`` recorded (block records with the draft's per-layer hidden rows, verdicts,
 routing records with router logits).  Three guessers, none of them a trained network - the bars a predictor has to clear:
@@ -223,12 +223,27 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     ap.add_argument("--ridge", type=float, default=1.0)
     ap.add_argument("--widths", default="8,16,32")
     ap.add_argument("--out")
+    ap.add_argument("--label", action="store_true", help="first write the corpus's routing records by re-running its recorded sequences through the fp32 "
+                                                         "reference model of --weights (exact and slow: small targets)")
     a = ap.parse_args(argv)
     weights = None
     if a.weights:
         from ..models.checkpoint import open_checkpoint
-        _, ck = open_checkpoint(a.weights)
-        weights = {k: ck[k] for k in ck.keys() if k.endswith("moe.router") or k.endswith("moe.router_bias")}
+        shape, ck = open_checkpoint(a.weights)
+        if a.label:
+            from ..models.reference import Oracle
+            from ..models.weights import init_weights
+            names = init_weights(shape, 0).keys()              # the tensor names of the architecture (the labeller is for small targets)
+            n = ec.label_with_oracle(a.corpus, Oracle(shape, {k: ck[k].float() if ck[k].is_floating_point() else ck[k] for k in names if k in ck}))
+            print(f"labelled {n} positions", file=sys.stderr)
+        weights = {}
+        for l in range(shape.n_layers):
+            for k in (f"layers.{l}.moe.router", f"layers.{l}.moe.router_bias"):
+                if k in ck:
+                    weights[k] = ck[k]
+    elif a.label:
+        print("--label needs --weights", file=sys.stderr)
+        return 2
     try:
         rep = evaluate(a.corpus, weights, a.holdout, a.ridge, [int(x) for x in a.widths.split(",")])
     except ValueError as e:

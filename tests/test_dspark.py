@@ -657,3 +657,70 @@ def test_autoconfigure_sizes_a_block_draft_and_carries_its_settings(tmp_path, ca
     json.dump(broken.to_json(), open(os.path.join(d, "config.json"), "w"))
     assert autoconfigure.main(["--model", "glm-5.3-flash", "--assume-gpus", "1", "--draft-checkpoint", d, "--output", out]) == 2
     assert "multiple of num_key_value_heads" in capsys.readouterr().err
+
+
+def test_a_corpus_without_labels_is_labelled_offline_from_its_recorded_contexts(tmp_path):
+    from layerstorm_b200.serving.orchestrator import InferenceRequest, Orchestrator, SamplingParams
+    from layerstorm_b200.speculation import epm_corpus as ec
+    from layerstorm_b200.utils import epm_baselines as eb
+    cfg, w, eng = _target()
+    dc = draft_config_for_target(cfg.hidden, cfg.vocab, cfg.n_layers, layers=2, head_dim=16, block_size=5, markov_rank=8, n_aux=2)
+    bb = DsparkBackbone(dc, random_dspark_tensors(dc, 1, dtype=torch.float32), "cpu", torch.float32, ctx_capacity=64)
+    draft = DsparkDraft(bb, oracle_aux_provider(eng.model, dc.aux_hidden_state_layer_ids), {"speculative_tokens": 4})
+    d = str(tmp_path / "corpus")
+    wr = ec.CorpusWriter(d)
+    draft.attach_corpus(wr)
+    orch = Orchestrator(eng, draft=draft, speculation_depth=4)
+    outs = {}
+    for name, prompt in (("a", list(range(40, 58))), ("b", list(range(90, 104)))):
+        r = InferenceRequest(name, prompt, SamplingParams(max_tokens=7, ignore_eos=True))
+        orch.submit_request(r)
+        assert orch.step() and r.error is None
+        outs[name] = prompt + r.output_ids
+    wr.close()
+    assert ec.read_routing(d) == [] and ec.join_examples(d) == []                     # feature side only so far
+    seqs = ec.sequences_of(d)
+    assert len(seqs) == 2
+    for toks, full in zip((seqs[k] for k in sorted(seqs)), (outs["a"], outs["b"])):
+        assert toks == full[: len(toks)] and len(toks) >= len(full) - 5                   # everything up to the last block's verdict
+    n = ec.label_with_oracle(d, eng.model)
+    routes = ec.read_routing(d)
+    assert n == len(routes) > 0
+    # the labels are what the reference model routes at those positions
+    eng.model.route_log = {}
+    eng.model.forward(torch.tensor(outs["a"]))
+    log_a, eng.model.route_log = eng.model.route_log, None
+    first = min(r["pos"] for r in routes if r["seq"] == min(seqs))
+    rec = next(r for r in routes if r["seq"] == min(seqs) and r["pos"] == first + 2)
+    for row in rec["rows"]:
+        assert row["ids"] == log_a[row["layer"]][1][first + 2].tolist()
+    ex = ec.join_examples(d)
+    assert ex and all(e["features"].shape == (2, cfg.hidden) for e in ex)
+    rep = eb.evaluate(d, None, widths=(cfg.top_k,))
+    assert rep["sequences"] == 2 and rep["locality_prev"][f"recall@{cfg.top_k}"]["n"] > 0
+
+
+def test_baselines_command_labels_a_corpus_from_a_checkpoint(tmp_path, capsys):
+    from layerstorm_b200.models.checkpoint import export_hf
+    from layerstorm_b200.serving.orchestrator import InferenceRequest, Orchestrator, SamplingParams
+    from layerstorm_b200.speculation import epm_corpus as ec
+    from layerstorm_b200.utils import epm_baselines as eb
+    cfg, w, eng = _target()
+    ck = str(tmp_path / "ck")
+    export_hf(cfg, w, ck)
+    dc = draft_config_for_target(cfg.hidden, cfg.vocab, cfg.n_layers, layers=1, head_dim=16, block_size=4, markov_rank=8, n_aux=2)
+    draft = DsparkDraft(DsparkBackbone(dc, random_dspark_tensors(dc, 1, dtype=torch.float32), "cpu", torch.float32, ctx_capacity=64),
+                        oracle_aux_provider(eng.model, dc.aux_hidden_state_layer_ids), {"speculative_tokens": 3})
+    d = str(tmp_path / "corpus")
+    draft.attach_corpus(ec.CorpusWriter(d))
+    orch = Orchestrator(eng, draft=draft, speculation_depth=3)
+    for i, prompt in enumerate((list(range(40, 52)), list(range(70, 84)), list(range(100, 110)))):
+        r = InferenceRequest(str(i), prompt, SamplingParams(max_tokens=5, ignore_eos=True))
+        orch.submit_request(r)
+        assert orch.step() and r.error is None
+    draft.corpus.close()
+    assert eb.main([d, "--label"]) == 2 and "--label needs --weights" in capsys.readouterr().err
+    assert eb.main([d, "--weights", ck, "--label", "--widths", str(cfg.top_k)]) == 0
+    cap = capsys.readouterr()
+    line = json.loads(cap.out.strip().splitlines()[-1])
+    assert "labelled" in cap.err and line["examples"] > 0 and "router_probe" in line and not line["in_sample"]

@@ -384,6 +384,16 @@ def build_server(cfg: dict, shape: ModelConfig, ckpt: Optional[str], engine, arg
         depth = args.speculation_depth if args.speculation_depth is not None else pl["max_continuation_length"]
     elif sp["enabled"] and sp["method"] in ("dspark", "self_speculative", "mtp"):
         draft, depth = build_model_draft(cfg, shape, engine, args)
+        dcb, pl = sp["draft_combiner"], sp["prompt_lookup"]
+        if draft is not None and dcb["enabled"] and pl["enabled"] and os.environ.get("LSB_DRAFT_COMBINER", "1") != "0":
+            # the free source first: where the context repeats itself, prompt lookup proposes without running a model; otherwise the
+            # model draft; the proposal with the most expected tokens per unit of cost goes to the target
+            from ..speculation.combiner import DraftCombiner, DraftSource
+            from ..speculation.prompt_lookup import PromptLookupDraft
+            cost = {"dspark": dcb["dspark_compute_cost"], "mtp": dcb["mtp_compute_cost"], "self_speculative": dcb["self_spec_compute_cost"]}[sp["method"]]
+            lookup = PromptLookupDraft(pl["min_ngram_size"], pl["max_ngram_size"], pl["max_continuation_length"])
+            draft = DraftCombiner([DraftSource("prompt_lookup", lookup, cost=0.0, priority_boost=dcb["prompt_lookup_priority_boost"]),
+                                   DraftSource(sp["method"], draft, cost=float(cost))])
     # continuous batching: as many plain greedy requests decode together as the engine's batched step takes (its CUDA graphs are
     # captured per batch size), bounded by the admitted concurrency
     eng_batch = int(getattr(getattr(engine, "_engine", engine), "max_batch", 1) or 1)

@@ -51,7 +51,11 @@ class DraftCombiner:
             p = list(s.proposer.propose(context, gamma))
             if not p:
                 continue
-            score = s.priority_boost * expected_tokens(s.acceptance, len(p)) / (1.0 + s.cost)
+            # a source that knows how far it trusts THIS proposal (a confidence head's survival probabilities) says so itself;
+            # the others are judged by their running acceptance rate
+            hint = getattr(s.proposer, "last_expected_tokens", None)
+            exp = hint() if callable(hint) else None
+            score = s.priority_boost * (exp if exp is not None else expected_tokens(s.acceptance, len(p))) / (1.0 + s.cost)
             if score > best_score:
                 best, best_score, best_src = p, score, s
             if not self.enabled:
@@ -64,6 +68,9 @@ class DraftCombiner:
     def feedback(self, proposed: int, accepted: int):
         if self.last is not None:
             self.last.update(proposed, accepted)
+            fb = getattr(self.last.proposer, "feedback", None)
+            if callable(fb):
+                fb(proposed, accepted)                       # the chosen source's own planner / scheduler / recorder learns too
 
 
 class UtilityScorer:

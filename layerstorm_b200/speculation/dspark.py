@@ -651,6 +651,14 @@ class _CorpusHook:
         self.corpus.write_block(seq, n, anchor_pos, anchor, drafted, conf or None, self.bb.last_layer_hidden[1: 1 + len(drafted)])
         self._pending = (seq, n, anchor_pos, list(proposed), list(conf))
 
+    def last_expected_tokens(self) -> Optional[float]:
+        """Expected committed tokens of the last proposal (the target's own token + the survival of each proposed row), for whoever
+        weighs this proposal against another source's; None without a proposal."""
+        n = getattr(self, "_last_n", 0)
+        if n <= 0:
+            return None
+        return 1.0 + sum(self.sched.survival(self.last_confidences, n))
+
     def _corpus_feedback(self, proposed: int, accepted: int):
         if self.corpus is None or getattr(self, "_pending", None) is None:
             return
@@ -714,6 +722,7 @@ class DsparkDraft(_CorpusHook):
         ids = ids[: self.sched.depth(self.last_confidences, len(ids))]
         self._corpus_block(self.sequence_no, len(committed), anchor, drafted, self.last_confidences, ids, context)
         self.proposed += len(ids)
+        self._last_n = len(ids)
         return ids
 
     def feedback(self, proposed: int, accepted: int):
@@ -844,6 +853,7 @@ class DeviceDsparkDraft(_CorpusHook):
         ids = ids[: self.sched.depth(self.last_confidences, len(ids))]
         self._corpus_block(getattr(c, "corpus_seq", sid), c.length, int(context[-1]), drafted, self.last_confidences, ids, context)
         self.proposed += len(ids)
+        self._last_n = len(ids)
         return ids
 
     def feedback(self, proposed: int, accepted: int):

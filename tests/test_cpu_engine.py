@@ -79,10 +79,19 @@ def test_serve_builds_model_drafts_on_the_test_engine():
     cfg["speculation"]["enabled"], cfg["speculation"]["method"] = True, "dspark"
     eng = serve.build_engine(cfg, shape, ckpt, args)
     _, orch = serve.build_server(cfg, shape, ckpt, eng, args)
-    assert isinstance(orch.draft, EngineDraft) and orch.gamma == 4
+    # the model draft sits behind the free source: prompt lookup proposes where the context repeats itself, the model otherwise
+    from layerstorm_b200.speculation.combiner import DraftCombiner
+    assert isinstance(orch.draft, DraftCombiner) and [s.name for s in orch.draft.sources] == ["prompt_lookup", "dspark"] and orch.gamma == 4
+    assert isinstance(orch.draft.sources[1].proposer, EngineDraft) and orch.draft.sources[1].cost == cfg["speculation"]["draft_combiner"]["dspark_compute_cost"]
     req = InferenceRequest("d", list(range(5, 40)), SamplingParams(max_tokens=10, ignore_eos=True))
     orch.submit_request(req)
     assert orch.step() and req.error is None and len(req.output_ids) == 10 and req.stats.spec_accepted > 0
+    assert orch.draft.last is not None and orch.draft.last.name == "dspark"            # nothing repeats in this prompt
+    # switched off in the configuration: the model draft alone
+    cfg["speculation"]["draft_combiner"]["enabled"] = False
+    _, orch1 = serve.build_server(cfg, shape, ckpt, serve.build_engine(cfg, shape, ckpt, args), args)
+    assert isinstance(orch1.draft, EngineDraft)
+    cfg["speculation"]["draft_combiner"]["enabled"] = True
     # the null engine cannot draft for itself: self_speculative degrades to plain decoding with a warning
     cfg["speculation"]["method"] = "self_speculative"
     _, orch2 = serve.build_server(cfg, shape, ckpt, serve.build_engine(cfg, shape, ckpt, args), args)

@@ -724,3 +724,17 @@ def test_baselines_command_labels_a_corpus_from_a_checkpoint(tmp_path, capsys):
     cap = capsys.readouterr()
     line = json.loads(cap.out.strip().splitlines()[-1])
     assert "labelled" in cap.err and line["examples"] > 0 and "router_probe" in line and not line["in_sample"]
+
+
+def test_draft_source_reports_what_it_expects_of_its_last_proposal():
+    cfg, w, eng = _target()
+    dc = draft_config_for_target(cfg.hidden, cfg.vocab, cfg.n_layers, layers=1, head_dim=16, block_size=5, markov_rank=8, n_aux=2)
+    bb = DsparkBackbone(dc, random_dspark_tensors(dc, 1, dtype=torch.float32), "cpu", torch.float32, ctx_capacity=64)
+    d = DsparkDraft(bb, oracle_aux_provider(eng.model, dc.aux_hidden_state_layer_ids), {"speculative_tokens": 4, "confidence_enabled": True, "confidence_threshold": 0.0})
+    assert d.last_expected_tokens() is None
+    ids = d.propose(list(range(9, 30)), 4)
+    surv, tot = 1.0, 1.0
+    for c in d.last_confidences[: len(ids)]:
+        surv *= c
+        tot += surv
+    assert len(ids) == 4 and d.last_expected_tokens() == pytest.approx(tot) and 1.0 < tot < 5.0

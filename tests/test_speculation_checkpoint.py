@@ -113,6 +113,18 @@ def test_combiner_picks_by_expected_tokens_per_cost_and_learns():
     c.feedback(4, 0)
     assert c.last.acceptance < a0
     assert expected_tokens(0.0, 5) == 1.0 and expected_tokens(0.5, 1) == 1.5
+    # the chosen source hears about the outcome itself (its planner / scheduler learns), and a source that knows how far it trusts a
+    # proposal is weighed by that instead of its running acceptance rate
+
+    class Sure(Fixed):
+        def __init__(self, out, exp): super().__init__(out); self.exp, self.heard = exp, []
+        def last_expected_tokens(self): return self.exp
+        def feedback(self, p, a): self.heard.append((p, a))
+    shy, bold = Sure([1, 2, 3, 4], 1.2), Sure([5, 6], 2.9)
+    c2 = DraftCombiner([DraftSource("shy", shy, cost=0.1), DraftSource("bold", bold, cost=0.1)])
+    assert c2.propose([0], 4) == [5, 6] and c2.last.name == "bold"                 # two trusted tokens beat four doubtful ones
+    c2.feedback(2, 2)
+    assert bold.heard == [(2, 2)] and shy.heard == []
 
 
 def test_utility_scorer_strategies():

@@ -400,7 +400,12 @@ def build_server(cfg: dict, shape: ModelConfig, ckpt: Optional[str], engine, arg
     # (LSB_SERVE_MAX_BATCH, default 8: every batch size that occurs gets its own step workspace and CUDA graph, which a model that
     # fills the GPU cannot afford for large batches)
     batch = max(1, min(eng_batch, int(cfg["orchestrator"]["max_batch_size"]), int(sv["max_concurrent_requests"]), int(os.environ.get("LSB_SERVE_MAX_BATCH", "8"))))
-    orch = Orchestrator(engine, eos_token_ids=eos, prefix_cache=pcc, draft=draft, speculation_depth=depth, tokenizer=tok, max_batch=batch,
+    policy = None
+    if draft is not None and depth > 0 and os.environ.get("LSB_DEPTH_POLICY", "1") != "0":
+        # speculation.utility_scorer / speculation.calibration: the depth asked of the draft follows the measured acceptance
+        from ..speculation.combiner import DepthPolicy
+        policy = DepthPolicy.from_config(sp, depth)
+    orch = Orchestrator(engine, eos_token_ids=eos, prefix_cache=pcc, draft=draft, speculation_depth=depth, tokenizer=tok, max_batch=batch, depth_policy=policy,
                         prefill_slice_tokens=4 * int(cfg["orchestrator"]["prefill_chunk_tokens"]),
                         degraded_retry_max=int((cfg.get("_internal-orchestrator") or {}).get("degraded_retry_max", 1)
                                                if (cfg.get("_internal-orchestrator") or {}).get("degraded_retry_enabled", True) else 0))

@@ -168,7 +168,7 @@ class Orchestrator:
 
     def __init__(self, engine, eos_token_ids: Sequence[int] = (), prefix_cache: Optional[PrefixCacheConfig] = None,
                  draft=None, speculation_depth: int = 0, tokenizer=None, governor: Optional[SpecRoundGovernor] = None, max_batch: int = 1,
-                 prefill_slice_tokens: int = 0, degraded_retry_max: int = 0):
+                 prefill_slice_tokens: int = 0, degraded_retry_max: int = 0, depth_policy=None):
         """``max_batch`` > 1: continuous batching - up to that many plain greedy requests decode together, one engine step per token
         of ALL of them; a request joins after its own prefill and leaves when it finishes, the others never wait for it.  Requests
         that need more than the arg-max of a step (sampling on the host, log-probabilities, guided decoding, speculation) are
@@ -197,6 +197,8 @@ class Orchestrator:
         self.eos = set(int(t) for t in eos_token_ids)
         self.prefix = PrefixCache(engine, prefix_cache or PrefixCacheConfig())
         self.draft, self.gamma = draft, speculation_depth if draft is not None else 0
+        # optional ``speculation.combiner.DepthPolicy``: the depth asked of the draft follows the measured acceptance (0 = a plain step)
+        self.depth_policy = depth_policy if draft is not None else None
         self.tokenizer = tokenizer
         self.governor = governor or SpecRoundGovernor(enabled=False)
         self.queue: Deque[InferenceRequest] = collections.deque()
@@ -585,8 +587,12 @@ class Orchestrator:
             if dev_sample:
                 self._decode_plain(req, sid, tok, False, sample=self._sample_args(req))
             elif self.gamma > 0 and not need_logits:
+                if self.depth_policy is not None:
+                    self.depth_policy.begin_request()
                 self._decode_speculative(req, sid, tok)
             elif self.gamma > 0 and not getattr(eng, "has_recurrent_state", False):
+                if self.depth_policy is not None:
+                    self.depth_policy.begin_request()
                 self._decode_speculative_logits(req, sid, tok)
             else:
                 self._decode_plain(req, sid, tok, need_logits)
@@ -641,7 +647,8 @@ class Orchestrator:
         eng = self.engine
         while True:
             t0 = time.time()
-            if not self.governor.should_draft():
+            gamma = self._round_depth()
+            if gamma <= 0 or not self.governor.should_draft():
                 lg = self._with_pool_evict_retry(req, lambda: eng.decode([sid], [tok], return_logits=True))[1][0]
                 tok = self._pick(req, lg, len(req.prompt_ids) + len(req.output_ids))
                 self.governor.observe_plain((time.time() - t0) * 1e3)
@@ -649,7 +656,7 @@ class Orchestrator:
                     return
                 continue
             ctx = list(req.prompt_ids) + req.output_ids
-            draft = list(self.draft.propose(ctx, self.gamma))[: self.gamma]
+            draft = list(self.draft.propose(ctx, gamma))[:gamma]
             base_len = eng.seq_len(sid)
             rows = [tok] + draft
             logits = self._with_pool_evict_retry(req, lambda: eng.forward_rows(sid, rows, commit=True))
@@ -672,8 +679,13 @@ class Orchestrator:
             self.governor.observe_round(n_new, (time.time() - t0) * 1e3)
             if hasattr(self.draft, "feedback"):
                 self.draft.feedback(len(draft), n_acc)
+            if self.depth_policy is not None:
+                self.depth_policy.record(len(draft), n_acc)
             if stop:
                 return
+
+    def _round_depth(self) -> int:
+        return self.gamma if self.depth_policy is None else min(self.gamma, self.depth_policy.depth())
 
     def _decode_speculative(self, req: InferenceRequest, sid: int, tok: int):
         """Greedy lossless speculation: the draft proposes up to gamma tokens after ``tok``; one batched
@@ -683,7 +695,8 @@ class Orchestrator:
         dev_verify = hasattr(eng, "verify_greedy")            # decides on the device, rolls recurrent state back through anchors
         recurrent = getattr(eng, "has_recurrent_state", False) and not dev_verify
         while True:
-            if recurrent or not self.governor.should_draft():
+            gamma = self._round_depth()
+            if recurrent or gamma <= 0 or not self.governor.should_draft():
                 t0 = time.time()
                 tok = self._with_pool_evict_retry(req, lambda: eng.decode([sid], [tok]))[0]
                 self.governor.observe_plain((time.time() - t0) * 1e3)
@@ -692,7 +705,7 @@ class Orchestrator:
                 continue
             t0 = time.time()
             ctx = list(req.prompt_ids) + req.output_ids
-            draft = list(self.draft.propose(ctx, self.gamma))[: self.gamma]
+            draft = list(self.draft.propose(ctx, gamma))[:gamma]
             base_len = eng.seq_len(sid)
             rows = [tok] + draft
             if dev_verify:
@@ -712,6 +725,8 @@ class Orchestrator:
             self.governor.observe_round(len(new), (time.time() - t0) * 1e3)
             if hasattr(self.draft, "feedback"):
                 self.draft.feedback(len(draft), n_acc)
+            if self.depth_policy is not None:
+                self.depth_policy.record(len(draft), n_acc)
             for t in new:
                 if self._emit(req, t, None):
                     return

@@ -137,3 +137,63 @@ class DepthCalibrator:
     @property
     def acceptance(self) -> float:
         return self._acc
+
+
+class DepthPolicy:
+    """How many tokens to ask the draft for, round by round: the utility scorer's depth under the running acceptance rate, capped by
+    the closed-loop calibrator's depth; 0 = a plain decode step this round.  The calibrator's switch-off holds for the request it
+    happened in (``begin_request`` arms it again); while the depth is 0 one single-token round is tried every ``probe_every`` rounds,
+    so that a draft that started badly gets another look.  Reference: ``speculation.utility_scorer`` and ``speculation.calibration``
+    driving the depth in python/orchestrator/orchestrator_loop.py."""
+
+    def __init__(self, scorer: Optional[UtilityScorer] = None, calibrator: Optional[DepthCalibrator] = None, max_depth: int = 8, alpha: float = 0.2,
+                 probe_every: int = 16):
+        self.scorer, self.calibrator, self.max_depth, self.alpha, self.probe_every = scorer, calibrator, max_depth, alpha, probe_every
+        self.acceptance = 0.6
+        self._idle = 0
+        self.rounds = self.plain_rounds = 0
+
+    def begin_request(self):
+        if self.calibrator is not None:
+            self.calibrator.enabled = True
+
+    def depth(self) -> int:
+        d = self.max_depth
+        if self.calibrator is not None:
+            d = min(d, self.calibrator.depth) if self.calibrator.enabled else 0
+        if self.scorer is not None and d > 0:
+            d = min(d, self.scorer.choose(self.acceptance))
+        if d <= 0:
+            self._idle += 1
+            if self.probe_every > 0 and self._idle >= self.probe_every:
+                self._idle, d = 0, 1
+            else:
+                self.plain_rounds += 1
+        else:
+            self._idle = 0
+        return max(0, d)
+
+    def record(self, proposed: int, accepted: int):
+        if proposed <= 0:
+            return
+        self.rounds += 1
+        # per-token acceptance over the positions that were decided (the first rejected one included)
+        self.acceptance += self.alpha * (accepted / min(proposed, accepted + 1) - self.acceptance)
+        if self.calibrator is not None:
+            self.calibrator.record(proposed, accepted)
+
+    @classmethod
+    def from_config(cls, sp: dict, max_depth: int) -> Optional["DepthPolicy"]:
+        """From the ``speculation`` section; None when neither the scorer nor the calibration is enabled."""
+        us, cal = sp.get("utility_scorer") or {}, sp.get("calibration") or {}
+        scorer = calibrator = None
+        if us.get("enabled"):
+            scorer = UtilityScorer(us.get("strategy", "cascade"), min(int(us.get("static_depth", 3)), max_depth), float(us.get("utility_threshold", 1.0)), max_depth)
+            scorer.depth = min(scorer.depth, max_depth)
+        if cal and cal.get("enabled", True):                # the section has no switch of its own: present means on
+            calibrator = DepthCalibrator(float(cal.get("min_acceptance_rate", 0.3)), float(cal.get("target_acceptance_rate", 0.6)),
+                                         int(cal.get("adjustment_interval_tokens", 500)), float(cal.get("acceptance_ema_alpha", 0.5)),
+                                         depth=min(max_depth, int(us.get("static_depth", 3)) if us else 3), max_depth=max_depth)
+        if scorer is None and calibrator is None:
+            return None
+        return cls(scorer, calibrator, max_depth)

@@ -474,3 +474,54 @@ def test_live_gguf_source_builds_slot_images_from_a_real_file(tmp_path):
     assert src.bytes_built == (E + cfg.n_shared) * ef.stride
     with pytest.raises(ValueError):
         src.load_into(3, 0, host[0].numpy())
+
+
+def test_depth_policy_follows_the_acceptance_and_probes_after_switching_off():
+    from layerstorm_b200.speculation.combiner import DepthPolicy
+    from layerstorm_b200.config.loader import load_config
+    sp = load_config(None, {}, check=False)["speculation"]
+    pol = DepthPolicy.from_config(sp, max_depth=6)
+    assert pol is not None and pol.scorer is not None and pol.calibrator is not None and pol.depth() == 3          # static_depth to begin with
+    for _ in range(30):                                   # a draft that is always right: the depth climbs one step per round to the cap
+        d = pol.depth()
+        pol.record(d, d)
+    assert pol.acceptance > 0.95 and pol.depth() == min(6, pol.calibrator.depth) and pol.depth() >= 3
+    for _ in range(40):                                   # ... that is always wrong: the depth sinks to plain decoding
+        d = pol.depth()
+        pol.record(max(d, 1), 0)
+    assert pol.acceptance < 0.05
+    seq = [pol.depth() for _ in range(32)]
+    assert seq.count(0) == 30 and seq.count(1) == 2       # a single-token probe every 16 rounds
+    # the calibrator's switch-off lasts for the request it happened in
+    pol2 = DepthPolicy.from_config(dict(sp, utility_scorer={"enabled": False}, calibration=dict(sp["calibration"], adjustment_interval_tokens=4)), max_depth=4)
+    assert pol2.scorer is None and pol2.depth() == 3
+    for _ in range(12):
+        pol2.record(3, 0)
+    assert not pol2.calibrator.enabled and pol2.depth() == 0
+    pol2.begin_request()
+    assert pol2.depth() >= 1
+    assert DepthPolicy.from_config({"utility_scorer": {"enabled": False}}, 4) is None
+
+
+def test_orchestrator_asks_the_draft_for_the_policys_depth():
+    from layerstorm_b200.runtime.null_engine import NullEngine
+    from layerstorm_b200.speculation.combiner import DepthPolicy, UtilityScorer
+    asked = []
+
+    class Wrong:
+        def propose(self, ctx, g):
+            asked.append(g)
+            return [3] * g                                 # never what the engine continues with
+    eng = NullEngine(vocab=300, max_seqs=4)
+    pol = DepthPolicy(UtilityScorer("ema", max_depth=4), None, max_depth=4, alpha=0.5, probe_every=5)
+    orch = Orchestrator(eng, eos_token_ids=[1], draft=Wrong(), speculation_depth=4, depth_policy=pol)
+    r = InferenceRequest("x", list(range(5, 25)), SamplingParams(max_tokens=30, ignore_eos=True))
+    orch.submit_request(r)
+    assert orch.step() and r.error is None and len(r.output_ids) == 30
+    plain = NullEngine(vocab=300, max_seqs=4)
+    o0 = Orchestrator(plain, eos_token_ids=[1])
+    r0 = InferenceRequest("y", list(range(5, 25)), SamplingParams(max_tokens=30, ignore_eos=True))
+    o0.submit_request(r0)
+    assert o0.step() and r0.output_ids == r.output_ids
+    # the first rounds ask for several tokens, then the policy gives up and only probes with one
+    assert asked[0] >= 2 and asked[-1] == 1 and pol.plain_rounds > 0 and len(asked) < 20 and r.stats.spec_accepted == 0

@@ -405,7 +405,18 @@ def build_server(cfg: dict, shape: ModelConfig, ckpt: Optional[str], engine, arg
         # speculation.utility_scorer / speculation.calibration: the depth asked of the draft follows the measured acceptance
         from ..speculation.combiner import DepthPolicy
         policy = DepthPolicy.from_config(sp, depth)
+    reasoning = None
+    if draft is not None and sp["reasoning_mode"]["enabled"]:
+        # speculation.reasoning_mode: deeper drafts inside a think block; the block's markers come from serving.reasoning_config
+        # ({"think_open": "...", "think_close": "..."}) or default to <think> ... </think>
+        from ..speculation.policies import ReasoningMode
+        marks = sv["reasoning_config"]
+        marks = (json.load(open(marks)) if os.path.exists(marks) else json.loads(marks)) if marks else {}
+        o, c = tok.encode(marks.get("think_open", "<think>")), tok.encode(marks.get("think_close", "</think>"))
+        if o and c:
+            reasoning = (ReasoningMode(sp["reasoning_mode"]), o, c)
     orch = Orchestrator(engine, eos_token_ids=eos, prefix_cache=pcc, draft=draft, speculation_depth=depth, tokenizer=tok, max_batch=batch, depth_policy=policy,
+                        reasoning=reasoning,
                         prefill_slice_tokens=4 * int(cfg["orchestrator"]["prefill_chunk_tokens"]),
                         degraded_retry_max=int((cfg.get("_internal-orchestrator") or {}).get("degraded_retry_max", 1)
                                                if (cfg.get("_internal-orchestrator") or {}).get("degraded_retry_enabled", True) else 0))

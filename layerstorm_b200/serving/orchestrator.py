@@ -168,7 +168,7 @@ class Orchestrator:
 
     def __init__(self, engine, eos_token_ids: Sequence[int] = (), prefix_cache: Optional[PrefixCacheConfig] = None,
                  draft=None, speculation_depth: int = 0, tokenizer=None, governor: Optional[SpecRoundGovernor] = None, max_batch: int = 1,
-                 prefill_slice_tokens: int = 0, degraded_retry_max: int = 0, depth_policy=None):
+                 prefill_slice_tokens: int = 0, degraded_retry_max: int = 0, depth_policy=None, reasoning=None):
         """``max_batch`` > 1: continuous batching - up to that many plain greedy requests decode together, one engine step per token
         of ALL of them; a request joins after its own prefill and leaves when it finishes, the others never wait for it.  Requests
         that need more than the arg-max of a step (sampling on the host, log-probabilities, guided decoding, speculation) are
@@ -199,6 +199,11 @@ class Orchestrator:
         self.draft, self.gamma = draft, speculation_depth if draft is not None else 0
         # optional ``speculation.combiner.DepthPolicy``: the depth asked of the draft follows the measured acceptance (0 = a plain step)
         self.depth_policy = depth_policy if draft is not None else None
+        # optional (``speculation.policies.ReasoningMode``, think-open ids, think-close ids): inside a think block the depth asked of the
+        # draft is multiplied (long, low-entropy reasoning text accepts deeper drafts)
+        self.reasoning = reasoning if (draft is not None and reasoning is not None and reasoning[0].enabled) else None
+        self._think = None
+        self.think_rounds = 0
         self.tokenizer = tokenizer
         self.governor = governor or SpecRoundGovernor(enabled=False)
         self.queue: Deque[InferenceRequest] = collections.deque()
@@ -514,6 +519,8 @@ class Orchestrator:
         if not req.output_ids:
             req.stats.t_first_token = time.time()
         req.output_ids.append(tok)
+        if self._think is not None:
+            self._think.feed(tok)
         info = None
         if p.logprobs and logits is not None:
             lp = torch.log_softmax(logits.float(), -1)
@@ -587,17 +594,16 @@ class Orchestrator:
             if dev_sample:
                 self._decode_plain(req, sid, tok, False, sample=self._sample_args(req))
             elif self.gamma > 0 and not need_logits:
-                if self.depth_policy is not None:
-                    self.depth_policy.begin_request()
+                self._begin_speculation(req)
                 self._decode_speculative(req, sid, tok)
             elif self.gamma > 0 and not getattr(eng, "has_recurrent_state", False):
-                if self.depth_policy is not None:
-                    self.depth_policy.begin_request()
+                self._begin_speculation(req)
                 self._decode_speculative_logits(req, sid, tok)
             else:
                 self._decode_plain(req, sid, tok, need_logits)
             self._finish(req, req.finish_reason or ("cancelled" if req.cancelled.is_set() else "stop"))
         finally:
+            self._think = None
             eng.free_sequence(sid)
 
     def _degraded_count(self) -> int:
@@ -685,7 +691,22 @@ class Orchestrator:
                 return
 
     def _round_depth(self) -> int:
-        return self.gamma if self.depth_policy is None else min(self.gamma, self.depth_policy.depth())
+        d = self.gamma if self.depth_policy is None else min(self.gamma, self.depth_policy.depth())
+        if self._think is not None and self._think.thinking and d > 0:
+            mode = self.reasoning[0]
+            d = max(d, mode.depth(d, mode.overrides(True)))
+            self.think_rounds += 1
+        return d
+
+    def _begin_speculation(self, req: InferenceRequest):
+        if self.depth_policy is not None:
+            self.depth_policy.begin_request()
+        self._think = None
+        if self.reasoning is not None:
+            from ..speculation.policies import ThinkTracker
+            self._think = ThinkTracker(self.reasoning[1], self.reasoning[2])
+            for t in list(req.prompt_ids)[-4096:] + list(req.output_ids):     # a prompt may end inside an open think block
+                self._think.feed(int(t))
 
     def _decode_speculative(self, req: InferenceRequest, sid: int, tok: int):
         """Greedy lossless speculation: the draft proposes up to gamma tokens after ``tok``; one batched

@@ -525,3 +525,35 @@ def test_orchestrator_asks_the_draft_for_the_policys_depth():
     assert o0.step() and r0.output_ids == r.output_ids
     # the first rounds ask for several tokens, then the policy gives up and only probes with one
     assert asked[0] >= 2 and asked[-1] == 1 and pol.plain_rounds > 0 and len(asked) < 20 and r.stats.spec_accepted == 0
+
+
+def test_drafts_are_deeper_inside_a_think_block():
+    from layerstorm_b200.runtime.null_engine import NullEngine
+    from layerstorm_b200.speculation.policies import ReasoningMode
+    asked = []
+
+    class Asks:
+        def propose(self, ctx, g):
+            asked.append((g, ctx[-1]))
+            return [3] * g
+    OPEN, CLOSE = [250, 251], [252]
+    mode = ReasoningMode({"enabled": True, "aggressive_speculation_depth_multiplier": 2.0})
+    eng = NullEngine(vocab=300, max_seqs=4)
+    orch = Orchestrator(eng, eos_token_ids=[1], draft=Asks(), speculation_depth=3, reasoning=(mode, OPEN, CLOSE))
+    r = InferenceRequest("t", list(range(5, 25)) + OPEN, SamplingParams(max_tokens=12, ignore_eos=True))        # the prompt ends inside a think block
+    orch.submit_request(r)
+    assert orch.step() and r.error is None and len(r.output_ids) == 12
+    assert asked and all(g == 6 for g, _ in asked) and orch.think_rounds == len(asked) and orch._think is None
+    # outside a think block, or with the mode off, the configured depth is asked for
+    asked.clear()
+    r2 = InferenceRequest("u", list(range(5, 25)), SamplingParams(max_tokens=8, ignore_eos=True))
+    orch.submit_request(r2)
+    assert orch.step() and all(g == 3 for g, _ in asked)
+    off = Orchestrator(NullEngine(vocab=300, max_seqs=4), eos_token_ids=[1], draft=Asks(), speculation_depth=3,
+                       reasoning=(ReasoningMode({"enabled": False}), OPEN, CLOSE))
+    assert off.reasoning is None
+    # the tracker itself: open and close markers may be several tokens long
+    from layerstorm_b200.speculation.policies import ThinkTracker
+    tr = ThinkTracker(OPEN, CLOSE)
+    states = [tr.feed(t) for t in [9, 250, 251, 40, 41, 252, 42]]
+    assert states == [False, False, True, True, True, False, False] and tr.think_tokens == 3

@@ -389,9 +389,10 @@ def build_server(cfg: dict, shape: ModelConfig, ckpt: Optional[str], engine, arg
             # the free source first: where the context repeats itself, prompt lookup proposes without running a model; otherwise the
             # model draft; the proposal with the most expected tokens per unit of cost goes to the target
             from ..speculation.combiner import DraftCombiner, DraftSource
-            from ..speculation.prompt_lookup import PromptLookupDraft
+            from ..speculation.prompt_lookup import IncrementalPromptLookup
             cost = {"dspark": dcb["dspark_compute_cost"], "mtp": dcb["mtp_compute_cost"], "self_speculative": dcb["self_spec_compute_cost"]}[sp["method"]]
-            lookup = PromptLookupDraft(pl["min_ngram_size"], pl["max_ngram_size"], pl["max_continuation_length"])
+            # (the indexed form: it is asked every round, and a rescan of a long context would cost more than a decode step)
+            lookup = IncrementalPromptLookup(pl["min_ngram_size"], pl["max_ngram_size"], pl["max_continuation_length"])
             draft = DraftCombiner([DraftSource("prompt_lookup", lookup, cost=0.0, priority_boost=dcb["prompt_lookup_priority_boost"]),
                                    DraftSource(sp["method"], draft, cost=float(cost))])
     # continuous batching: as many plain greedy requests decode together as the engine's batched step takes (its CUDA graphs are

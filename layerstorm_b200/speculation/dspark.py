@@ -224,21 +224,24 @@ def write_dspark_checkpoint(path: str, cfg: DsparkCheckpointConfig, tensors: Dic
     write_safetensors(os.path.join(path, "model.safetensors"), {k: v.contiguous() for k, v in tensors.items()}, {"format": "pt"})
 
 
-def random_dspark_tensors(cfg: DsparkCheckpointConfig, seed: int = 0, dtype: torch.dtype = torch.bfloat16) -> Dict[str, torch.Tensor]:
-    g = torch.Generator().manual_seed(seed)
+def random_dspark_tensors(cfg: DsparkCheckpointConfig, seed: int = 0, dtype: torch.dtype = torch.bfloat16, device="cpu") -> Dict[str, torch.Tensor]:
+    """Random draft weights of the checkpoint's shapes (``device``: made there, matrix by matrix - a full-size draft never exists on
+    the host)."""
+    dev = torch.device(device)
+    g = torch.Generator(device=dev).manual_seed(seed)
     out: Dict[str, torch.Tensor] = {}
     for k, shape in cfg.expected_tensors().items():
         if k == "d2t":
             # an increasing subset of the target vocabulary, stored as offsets: target id = draft id + d2t[draft id]
-            tgt = torch.sort(torch.randperm(cfg.vocab_size, generator=g)[: cfg.draft_vocab_size]).values
-            out[k] = (tgt - torch.arange(cfg.draft_vocab_size)).to(torch.int64)
+            tgt = torch.sort(torch.randperm(cfg.vocab_size, generator=g, device=dev)[: cfg.draft_vocab_size]).values
+            out[k] = (tgt - torch.arange(cfg.draft_vocab_size, device=dev)).to(torch.int64)
         elif k.endswith("norm.weight") or k.endswith("layernorm.weight"):
-            out[k] = (1.0 + 0.1 * torch.randn(shape, generator=g)).to(dtype)
+            out[k] = (1.0 + 0.1 * torch.randn(shape, generator=g, device=dev)).to(dtype)
         elif k.endswith(".bias"):
-            out[k] = torch.zeros(shape, dtype=dtype)
+            out[k] = torch.zeros(shape, dtype=dtype, device=dev)
         else:
             fan_in = shape[-1]
-            out[k] = (torch.randn(shape, generator=g) * (0.5 if "embed" in k or "markov_w1" in k else 1.0 / math.sqrt(fan_in))).to(dtype)
+            out[k] = (torch.randn(shape, generator=g, device=dev) * (0.5 if "embed" in k or "markov_w1" in k else 1.0 / math.sqrt(fan_in))).to(dtype)
     return out
 
 

@@ -738,3 +738,13 @@ def test_draft_source_reports_what_it_expects_of_its_last_proposal():
         surv *= c
         tot += surv
     assert len(ids) == 4 and d.last_expected_tokens() == pytest.approx(tot) and 1.0 < tot < 5.0
+
+
+def test_block_draft_bench_runs_on_the_cpu_with_the_small_geometry(capsys):
+    from layerstorm_b200.utils import dspark_bench
+    assert dspark_bench.geometry("shipped").weight_bytes() > 7e9
+    assert dspark_bench.main(["--geometry", "small", "--device", "cpu", "--context", "96", "--chunk", "32", "--rows", "4", "--iters", "3"]) == 0
+    rep = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert rep["format"] == "fp32-cpu" and rep["block_rows"] == 4 and rep["ingest_ms"] > 0 and rep["block_ms"] > 0 and rep["draft_ms_with_heads"] > 0
+    assert rep["ingest_rows_per_s"] > 0 and rep["weight_sweep_gb_s"] > 0 and rep["context"] == 96
+    assert dspark_bench.main(["--geometry", "none"]) == 2 and dspark_bench.main(["--geometry", "small", "--device", "cpu", "--rows", "9"]) == 2

@@ -237,6 +237,15 @@ def build_engine(cfg: dict, shape: ModelConfig, ckpt: Optional[str], args: argpa
     return eng
 
 
+def prefill_slice_factor(cfg: dict) -> int:
+    """Engine chunks per prefill slice of a joining request (continuous batching: the running requests wait for one slice between two
+    of their decode steps).  ``orchestrator.performance_objective`` decides: the more weight on throughput, the longer the slices (fewer
+    interruptions of the prefill), the more on latency, the shorter (the default 0.6 / 0.4 gives four chunks)."""
+    from ..speculation.policies import PerformanceObjective
+    po = PerformanceObjective.from_config(cfg)
+    return max(1, min(16, int(round(10 * po.throughput_weight))))
+
+
 def build_block_draft(cfg: dict, shape: ModelConfig, target, args: argparse.Namespace):
     """The DSpark block draft (``speculation/dspark.py``) when ``speculation.dspark.checkpoint_path`` is a speculators-format dspark
     checkpoint, or - without a checkpoint - when ``speculation.dspark.aux_hidden_state_layer_ids`` is set (RANDOM draft weights of a
@@ -418,7 +427,7 @@ def build_server(cfg: dict, shape: ModelConfig, ckpt: Optional[str], engine, arg
             reasoning = (ReasoningMode(sp["reasoning_mode"]), o, c)
     orch = Orchestrator(engine, eos_token_ids=eos, prefix_cache=pcc, draft=draft, speculation_depth=depth, tokenizer=tok, max_batch=batch, depth_policy=policy,
                         reasoning=reasoning,
-                        prefill_slice_tokens=4 * int(cfg["orchestrator"]["prefill_chunk_tokens"]),
+                        prefill_slice_tokens=prefill_slice_factor(cfg) * int(cfg["orchestrator"]["prefill_chunk_tokens"]),
                         degraded_retry_max=int((cfg.get("_internal-orchestrator") or {}).get("degraded_retry_max", 1)
                                                if (cfg.get("_internal-orchestrator") or {}).get("degraded_retry_enabled", True) else 0))
     rc = sv["reasoning_config"]

@@ -249,3 +249,18 @@ def test_cpu_engine_runs_hash_layers_through_the_native_expert_kernels():
     for _ in range(4):
         got.append(eng.decode([sid], [got[-1]])[0])
     assert got == ref
+
+
+def test_performance_objective_sets_the_prefill_slice_of_the_batched_server():
+    from layerstorm_b200.cli import serve
+    args = serve.build_parser().parse_args(["--model", "tiny-mla-moe", "--test-engine", "--tokenizer-mode", "byte"])
+    cfg, shape, ckpt, _ = serve.resolve_config(args)
+    chunk = int(cfg["orchestrator"]["prefill_chunk_tokens"])
+    assert serve.prefill_slice_factor(cfg) == 4                                       # the default 0.6 / 0.4
+    _, orch = serve.build_server(cfg, shape, ckpt, serve.build_engine(cfg, shape, ckpt, args), args)
+    assert orch.prefill_slice == 4 * chunk
+    cfg["orchestrator"]["performance_objective"] = {"latency_weight": 0.9, "throughput_weight": 0.1}
+    _, lat = serve.build_server(cfg, shape, ckpt, serve.build_engine(cfg, shape, ckpt, args), args)
+    cfg["orchestrator"]["performance_objective"] = {"latency_weight": 0.2, "throughput_weight": 0.8}
+    _, thr = serve.build_server(cfg, shape, ckpt, serve.build_engine(cfg, shape, ckpt, args), args)
+    assert lat.prefill_slice == chunk and thr.prefill_slice == 8 * chunk

@@ -85,7 +85,25 @@ class LayerStormServer:
         # engine-side numbers come from the orchestrator's published state block (seqlock snapshot written by the serving thread)
         state = self.orch.published_state() if hasattr(self.orch, "published_state") else {}
         return {"status": "ok", "uptime_s": round(time.time() - self.started, 1), "queued": self.orch.queued(), "served": self.orch.served,
+                "speculation": self._speculation_state(),
                 "engine": state, "admission_waits": getattr(self.orch, "admission_waits", 0), "preemptions": getattr(self.orch, "preemptions", 0)}
+
+    def _speculation_state(self) -> dict:
+        """What the draft side is doing (plain attribute reads of numbers the serving thread writes): per-source acceptance estimates and
+        the source chosen last (draft combiner), the depth policy's acceptance and how many rounds it left to plain decoding, rounds
+        drafted inside a think block; empty without a draft."""
+        d = getattr(self.orch, "draft", None)
+        if d is None:
+            return {}
+        out = {"depth": getattr(self.orch, "gamma", 0), "think_rounds": getattr(self.orch, "think_rounds", 0)}
+        if hasattr(d, "sources"):
+            out["sources"] = {s.name: round(float(s.acceptance), 3) for s in d.sources}
+            out["last_source"] = d.last.name if getattr(d, "last", None) is not None else None
+        pol = getattr(self.orch, "depth_policy", None)
+        if pol is not None:
+            out["acceptance"] = round(float(pol.acceptance), 3)
+            out["plain_rounds"] = int(pol.plain_rounds)
+        return out
 
     async def models(self):
         return {"object": "list", "data": [{"id": self.cfg.model_name, "object": "model", "created": int(self.started), "owned_by": "layerstorm-b200",

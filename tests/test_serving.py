@@ -692,3 +692,30 @@ def test_decode_that_runs_out_of_kv_pages_preempts_the_youngest_request_and_resu
     for x, y in zip(alone, tight):
         assert y.error is None and y.output_ids == x.output_ids and len(y.output_ids) == 60
     assert orch.engine.free_page_count() == 9
+
+
+def test_health_reports_the_draft_side():
+    from fastapi.testclient import TestClient
+    from layerstorm_b200.serving.http_server import LayerStormServer, ServerConfig
+    from layerstorm_b200.speculation.combiner import DepthPolicy, DraftCombiner, DraftSource, UtilityScorer
+    from layerstorm_b200.speculation.prompt_lookup import IncrementalPromptLookup
+
+    class Wrong:
+        def propose(self, ctx, g): return [3] * g
+    tok = TokenizerWrapper()
+    eng = NullEngine(vocab=tok.vocab_size)
+    comb = DraftCombiner([DraftSource("prompt_lookup", IncrementalPromptLookup(), cost=0.0), DraftSource("model", Wrong(), cost=0.1)])
+    orch = Orchestrator(eng, eos_token_ids=tok.eos_token_ids, tokenizer=tok, draft=comb, speculation_depth=3,
+                        depth_policy=DepthPolicy(UtilityScorer("ema", max_depth=3), None, max_depth=3, alpha=0.5))
+    srv = LayerStormServer(orch, tok, ServerConfig(model_name="m"))
+    c = TestClient(srv.app)
+    s0 = c.get("/health").json()["speculation"]
+    assert s0["depth"] == 3 and s0["sources"] == {"prompt_lookup": 0.5, "model": 0.5} and s0["last_source"] is None and s0["acceptance"] == 0.6
+    r = InferenceRequest("h", list(range(5, 30)), SamplingParams(max_tokens=20, ignore_eos=True))
+    orch.submit_request(r)
+    assert orch.step() and r.error is None
+    s1 = c.get("/health").json()["speculation"]
+    assert s1["last_source"] == "model" and s1["sources"]["model"] < 0.5 and s1["acceptance"] < 0.3 and s1["plain_rounds"] > 0
+    # no draft: nothing to report
+    plain = LayerStormServer(Orchestrator(NullEngine(vocab=tok.vocab_size), eos_token_ids=tok.eos_token_ids, tokenizer=tok), tok, ServerConfig(model_name="m"))
+    assert TestClient(plain.app).get("/health").json()["speculation"] == {}
